@@ -1,0 +1,130 @@
+// Small host-side open-addressing map used for key dedup / gradient pre-aggregation on the CPU path
+// and inside the host storage shards.
+//
+// Parity: same contract as pico-ps/common/EasyHashMap.h:18-247 - power-of-two bucket count, load
+// factor kept at or below 1/2, triangular probing (step grows by one each probe), one reserved
+// "empty" key, try_emplace / force_emplace / find / at / clear / reserve. Erase (not in the
+// reference's map) is added with backward-shift-free tombstones because the host storage needs it.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <stdexcept>
+#include <utility>
+#include <vector>
+
+#include "hash.h"
+
+namespace psb {
+
+template <class K, class V>
+class EasyHashMap {
+public:
+    struct Entry {
+        K first;
+        V second;
+    };
+
+    explicit EasyHashMap(K empty_key, size_t expected = 0) : empty_(empty_key), tomb_(empty_key + 1) { rehash(buckets_for(expected)); }
+
+    size_t size() const { return size_; }
+    bool empty() const { return size_ == 0; }
+    size_t bucket_count() const { return table_.size(); }
+
+    void reserve(size_t n) {
+        size_t b = buckets_for(n);
+        if (b > table_.size()) rehash(b);
+    }
+
+    void clear() {
+        // shrink when the table is much larger than what it held (keeps clear() cheap for small batches)
+        size_t want = buckets_for(size_);
+        if (table_.size() > 4 * want) {
+            table_.assign(want, Entry{empty_, V()});
+        } else {
+            for (auto& e : table_) e.first = empty_;
+        }
+        size_ = 0;
+        used_ = 0;
+    }
+
+    // Returns (entry*, inserted)
+    std::pair<Entry*, bool> try_emplace(const K& key, const V& value = V()) {
+        if ((used_ + 1) * 2 > table_.size()) rehash(table_.size() * 2);
+        size_t mask = table_.size() - 1;
+        size_t p = (size_t)slot_hash((int64_t)key) & mask;
+        Entry* first_tomb = nullptr;
+        for (size_t np = 1;; ++np) {
+            Entry& e = table_[p];
+            if (e.first == key) return {&e, false};
+            if (e.first == empty_) {
+                Entry* dst = first_tomb ? first_tomb : &e;
+                if (!first_tomb) ++used_;
+                dst->first = key;
+                dst->second = value;
+                ++size_;
+                return {dst, true};
+            }
+            if (e.first == tomb_ && !first_tomb) first_tomb = &e;
+            p = (p + np) & mask;
+        }
+    }
+    // Insert a key that is known to be absent.
+    Entry* force_emplace(const K& key, const V& value = V()) { return try_emplace(key, value).first; }
+
+    Entry* find(const K& key) {
+        size_t mask = table_.size() - 1;
+        size_t p = (size_t)slot_hash((int64_t)key) & mask;
+        for (size_t np = 1;; ++np) {
+            Entry& e = table_[p];
+            if (e.first == key) return &e;
+            if (e.first == empty_) return nullptr;
+            p = (p + np) & mask;
+        }
+    }
+    const Entry* find(const K& key) const { return const_cast<EasyHashMap*>(this)->find(key); }
+    size_t count(const K& key) const { return find(key) ? 1 : 0; }
+    V& at(const K& key) {
+        Entry* e = find(key);
+        if (!e) throw std::out_of_range("EasyHashMap::at");
+        return e->second;
+    }
+    bool erase(const K& key) {
+        Entry* e = find(key);
+        if (!e) return false;
+        e->first = tomb_;
+        --size_;
+        return true;
+    }
+
+    template <class F>
+    void for_each(F&& f) {
+        for (auto& e : table_)
+            if (e.first != empty_ && e.first != tomb_) f(e.first, e.second);
+    }
+    // Resumable iteration by bucket index (ShardIterator support).
+    const std::vector<Entry>& buckets() const { return table_; }
+    bool live(const Entry& e) const { return e.first != empty_ && e.first != tomb_; }
+
+private:
+    static size_t buckets_for(size_t n) {
+        size_t b = 8;
+        while (b < 2 * n) b <<= 1;
+        return b;
+    }
+    void rehash(size_t nb) {
+        std::vector<Entry> old;
+        old.swap(table_);
+        table_.assign(nb, Entry{empty_, V()});
+        size_ = 0;
+        used_ = 0;
+        for (auto& e : old)
+            if (e.first != empty_ && e.first != tomb_) try_emplace(e.first, e.second);
+    }
+
+    K empty_, tomb_;
+    std::vector<Entry> table_;
+    size_t size_ = 0;  // live entries
+    size_t used_ = 0;  // live + tombstones (drives growth)
+};
+
+}  // namespace psb

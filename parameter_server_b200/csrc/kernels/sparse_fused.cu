@@ -1,0 +1,478 @@
+// Fused sparse pull and push for sm_100a: ONE cooperative kernel per call does the client side, the
+// transport and the server side of the reference's sparse operators, with the transport being plain
+// peer stores over NVLink/NVSwitch issued from inside the kernel.
+//
+// fused_pull_kernel  (pico-ps/operator/SparsePullOperator.h:81-110 generate_request_data,
+//                     :112-154 generate_request, :156-254 apply_request, :278-304 fill_pull_items)
+//   P1  dedup the key batch in an open-addressing scratch table, partition the unique keys by
+//       jump_consistent_hash(murmur(key)) -> shard -> owning GPU, stage per-owner key lists
+//   P2  copy the staged lists into the owners' mailboxes (coalesced peer stores), publish count+flag
+//   P3  owner: wait for every source's flag; find-or-insert each received key in the local table,
+//       attach + initialise rows of new keys, store each row into the requesting GPU's row buffer
+//   P5  consumer: wait for every owner's flag; un-dedup and sum/mean-pool rows into the activation
+//       buffer; leave behind the "plan" (inverse map, per-owner lists, owner-side slots) for the push
+// fused_push_kernel  (pico-ps/operator/SparsePushOperator.h:109-154 generate_request_data,
+//                     :197-276 async apply, :278-320 sync apply, :377-409 merge before store)
+//   Q1  segment-sum the gradients of duplicate keys into one row per unique key
+//   Q2  store the merged (key-ordered) gradient rows into the owners' mailboxes, publish flag
+//   Q3  owner: wait for every source; elect one leader entry per table row (lowest source rank), fold
+//       the other ranks' gradients into it, apply the optimizer once per row (or accumulate into the
+//       sync-push delta section), acknowledge the sources
+// A kernel on one GPU waits for kernels on the other GPUs; each GPU runs exactly one of them per
+// call, all waits are bounded, and with world == 1 no cross-GPU wait is executed at all.
+#include <cooperative_groups.h>
+
+#include "sparse_fused.h"
+
+namespace psb {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+enum Where : unsigned {
+    W_P1 = 1, W_P2, W_KEYFLAG, W_P3A, W_P3B, W_P3C, W_ROWFLAG, W_MAILBOX_OVERFLOW, W_INDEX_FULL, W_POOL_FULL,
+    W_Q1 = 32, W_ACK, W_Q2, W_GRADFLAG, W_Q3A, W_Q3B, W_NOROW,
+};
+
+__device__ __forceinline__ void copy_row(float* __restrict__ dst, const float* __restrict__ src, unsigned dim,
+                                         unsigned lane, unsigned lanes) {
+    for (unsigned d = lane * 4; d < dim; d += lanes * 4) *(float4*)(dst + d) = *(const float4*)(src + d);
+}
+
+__device__ __forceinline__ float4 init4(const TableView& t, long long key, unsigned d) {
+    float4 v;
+    v.x = init_uniform(key, d + 0, t.init_seed, t.init_range);
+    v.y = init_uniform(key, d + 1, t.init_seed, t.init_range);
+    v.z = init_uniform(key, d + 2, t.init_seed, t.init_range);
+    v.w = init_uniform(key, d + 3, t.init_seed, t.init_range);
+    return v;
+}
+
+// Each CTA waits until every peer's flag in `flags` (local memory, written remotely) reached `target`.
+__device__ __forceinline__ bool wait_all_flags(const unsigned* flags, unsigned target, const FusedArgs& a,
+                                               unsigned where) {
+    int ok = 1;
+    if (threadIdx.x < (unsigned)a.world && (int)threadIdx.x != a.rank) {
+        if (!wait_flag_ge(flags + threadIdx.x, target, a.limit_ns)) {
+            set_status(a.ctl, kStTimeout, where);
+            ok = 0;
+        }
+    }
+    return __syncthreads_and(ok) != 0;
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a) {
+    const unsigned nblocks = gridDim.x;
+    const unsigned tid = blockIdx.x * kThreads + threadIdx.x;
+    const unsigned nthreads = nblocks * kThreads;
+    const unsigned par = a.epoch & 1u;
+    unsigned* cnt = a.counters + par * 16;
+    unsigned* send_cnt = cnt + 4;
+    unsigned* in_cnt = a.in_cnt + par * kMaxWorld;
+    const int me = a.rank;
+    const unsigned C = a.C;
+    const TableView& T = a.table;
+    const PeerBufs& mine = a.peer[me];
+    const unsigned lanes = lanes_for_dim(a.dim);
+    const unsigned group = tid / lanes, ngroups = nthreads / lanes, lane = tid % lanes;
+
+    __shared__ unsigned s_pre[kMaxWorld + 1];
+
+    // ---- P1: dedup + partition ------------------------------------------------------------------
+    for (unsigned i = tid; i < a.n; i += nthreads) {
+        const long long key = a.keys[i];
+        unsigned long long h = slot_hash(key) & a.dmask;
+        for (;;) {
+            long long cur = *((volatile long long*)&a.dedup[h].key);
+            if (cur == key) break;
+            if (cur == kEmptyKey) {
+                long long prev = (long long)atomicCAS((unsigned long long*)&a.dedup[h].key,
+                                                      (unsigned long long)kEmptyKey, (unsigned long long)key);
+                if (prev == kEmptyKey) {
+                    const int owner = a.shard_owner[sparse_shard_of(key, a.n_shards)];
+                    const unsigned p = atomicAdd(&send_cnt[owner], 1u);
+                    const unsigned u = atomicAdd(&cnt[0], 1u);
+                    if (p < C) {
+                        a.send_keys[(size_t)owner * C + p] = key;
+                        a.send_ret[(size_t)owner * C + p] = u;
+                    } else {
+                        set_status(a.ctl, kStError, W_MAILBOX_OVERFLOW);
+                    }
+                    a.dedup[h].row = u;
+                    a.uniq_row[u] = (owner == me) ? kNoRow : kRemoteRow;
+                    break;
+                }
+                if (prev == key) break;
+            }
+            h = (h + 1) & a.dmask;  // dedup table holds >= 2n slots: an empty slot always exists
+        }
+        a.pos_slot[i] = (unsigned)h;
+    }
+    if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P1)) return;
+
+    // ---- P2: ship staged key lists to the owners ------------------------------------------------
+    if (a.world > 1) {
+        if (threadIdx.x == 0) {
+            unsigned acc = 0;
+            for (int o = 0; o < a.world; ++o) {
+                s_pre[o] = acc;
+                acc += (o == me) ? 0u : min(send_cnt[o], C);
+            }
+            s_pre[a.world] = acc;
+        }
+        __syncthreads();
+        const unsigned total = s_pre[a.world];
+        for (unsigned e = tid; e < total; e += nthreads) {
+            int o = 0;
+            while (e >= s_pre[o + 1]) ++o;
+            const unsigned p = e - s_pre[o];
+            a.peer[o].mail_keys[(size_t)me * C + p] = a.send_keys[(size_t)o * C + p];
+            a.peer[o].mail_ret[(size_t)me * C + p] = a.send_ret[(size_t)o * C + p];
+        }
+        __threadfence_system();
+        if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P2)) return;
+        if (blockIdx.x == 0 && threadIdx.x < (unsigned)a.world && (int)threadIdx.x != me) {
+            const int o = threadIdx.x;
+            a.peer[o].key_cnt[me] = min(send_cnt[o], C);
+            __threadfence_system();
+            st_release_sys(&a.peer[o].key_flag[me], a.epoch);
+        }
+        // ---- P3 (owner): wait for every source's keys
+        if (!wait_all_flags(mine.key_flag, a.epoch, a, W_KEYFLAG)) return;
+    }
+    if (threadIdx.x == 0) {
+        unsigned acc = 0;
+        for (int r = 0; r < a.world; ++r) {
+            s_pre[r] = acc;
+            unsigned c = (r == me) ? min(send_cnt[me], C) : min(ld_relaxed_sys(&mine.key_cnt[r]), C);
+            acc += c;
+        }
+        s_pre[a.world] = acc;
+    }
+    __syncthreads();
+    const unsigned total_in = s_pre[a.world];
+    if (blockIdx.x == 0 && threadIdx.x < (unsigned)a.world)
+        in_cnt[threadIdx.x] = s_pre[threadIdx.x + 1] - s_pre[threadIdx.x];
+
+    // ---- P3a: resolve received keys in the local table ------------------------------------------
+    const bool do_insert = (a.flags & FUSED_INSERT) != 0;
+    for (unsigned e = tid; e < total_in; e += nthreads) {
+        int r = 0;
+        while (e >= s_pre[r + 1]) ++r;
+        const unsigned p = e - s_pre[r];
+        const long long key = (r == me) ? a.send_keys[(size_t)me * C + p] : mine.mail_keys[(size_t)r * C + p];
+        bool inserted = false;
+        unsigned slot = table_find_or_insert(T, key, do_insert, &inserted);
+        if (slot == kNoSlot) {
+            if (do_insert) set_status(a.ctl, kStOom, W_INDEX_FULL);
+        } else if (do_insert) {
+            bool oom = false;
+            if (table_attach_row(T, slot, &oom)) {
+                unsigned j = atomicAdd(&cnt[1], 1u);
+                a.new_list[j] = slot;
+            }
+            if (inserted) atomicAdd(T.n_items, 1ull);
+            if (oom) set_status(a.ctl, kStOom, W_POOL_FULL);
+        }
+        a.res_slot[(size_t)r * C + p] = slot;
+    }
+    if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P3A)) return;
+
+    // ---- P3b: initialise the rows attached by this call -----------------------------------------
+    const unsigned n_new = cnt[1];
+    if (n_new > 0) {
+        for (unsigned j = group; j < n_new; j += ngroups) {
+            const unsigned slot = a.new_list[j];
+            const unsigned row = T.slots[slot].row;
+            row_init(T, T.row_ptr(row), T.slots[slot].key, lane, lanes);
+        }
+        if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P3B)) return;
+    }
+
+    // ---- P3c: return rows: peer stores for remote requesters, row index for local ones ----------
+    for (unsigned e = group; e < total_in; e += ngroups) {
+        int r = 0;
+        while (e >= s_pre[r + 1]) ++r;
+        const unsigned p = e - s_pre[r];
+        const unsigned slot = a.res_slot[(size_t)r * C + p];
+        unsigned row = kNoRow;
+        if (slot != kNoSlot) row = T.slots[slot].row;
+        if (r == me) {
+            if (lane == 0) a.uniq_row[a.send_ret[(size_t)me * C + p]] = row;
+        } else if (a.flags & FUSED_COPY_ROWS) {
+            float* dst = a.peer[r].rows_in + (size_t)mine.mail_ret[(size_t)r * C + p] * a.dim;
+            if (row < kRowPending) {
+                copy_row(dst, T.row_ptr(row), a.dim, lane, lanes);
+            } else {
+                const long long key = mine.mail_keys[(size_t)r * C + p];
+                for (unsigned d = lane * 4; d < a.dim; d += lanes * 4) *(float4*)(dst + d) = init4(T, key, d);
+            }
+        }
+    }
+    if (a.world > 1) {
+        __threadfence_system();
+        if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P3C)) return;
+        if (blockIdx.x == 0 && threadIdx.x < (unsigned)a.world && (int)threadIdx.x != me)
+            st_release_sys(&a.peer[threadIdx.x].row_flag[me], a.epoch);
+        if (!wait_all_flags(mine.row_flag, a.epoch, a, W_ROWFLAG)) return;
+    } else {
+        if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P3C)) return;
+    }
+
+    // ---- P5 (consumer): un-dedup + pool into the activation buffer ------------------------------
+    const unsigned L = a.bag_size;
+    if (a.flags & FUSED_COPY_ROWS) {
+        const unsigned nbags = a.n / L;
+        const float scale = (a.flags & FUSED_MEAN) ? 1.0f / (float)L : 1.0f;
+        for (unsigned b = group; b < nbags; b += ngroups) {
+            for (unsigned d = lane * 4; d < a.dim; d += lanes * 4) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (unsigned j = 0; j < L; ++j) {
+                    const unsigned i = b * L + j;
+                    const unsigned u = a.dedup[a.pos_slot[i]].row;
+                    const unsigned row = a.uniq_row[u];
+                    float4 v;
+                    if (row == kRemoteRow) v = *(const float4*)(mine.rows_in + (size_t)u * a.dim + d);
+                    else if (row < kRowPending) v = *(const float4*)(T.row_ptr(row) + d);
+                    else v = init4(T, a.keys[i], d);
+                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                }
+                if (L > 1) { acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale; }
+                *(float4*)(a.out + (size_t)b * a.dim + d) = acc;
+            }
+        }
+    }
+    for (unsigned i = tid; i < a.n; i += nthreads) {
+        const unsigned h = a.pos_slot[i];
+        a.inverse[i] = (int)a.dedup[h].row;
+        a.dedup[h].key = kEmptyKey;
+    }
+    if (a.flags & FUSED_PREPARE_PUSH) {
+        const unsigned n_uniq = cnt[0];
+        if (n_uniq != a.n) {  // without duplicates the push stores instead of accumulating
+            const size_t words = (size_t)n_uniq * a.dim / 4;
+            float4* z = (float4*)a.agg;
+            for (size_t w = tid; w < words; w += nthreads) z[w] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    if (blockIdx.x == 0 && threadIdx.x < 16) a.counters[(par ^ 1u) * 16 + threadIdx.x] = 0;
+}
+
+__global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a) {
+    const unsigned nblocks = gridDim.x;
+    const unsigned tid = blockIdx.x * kThreads + threadIdx.x;
+    const unsigned nthreads = nblocks * kThreads;
+    const unsigned* cnt = a.counters + a.plan_par * 16;
+    const unsigned* send_cnt = cnt + 4;
+    const unsigned* in_cnt = a.in_cnt + a.plan_par * kMaxWorld;
+    const int me = a.rank;
+    const unsigned C = a.C;
+    const TableView& T = a.table;
+    const PeerBufs& mine = a.peer[me];
+    const unsigned lanes = lanes_for_dim(a.dim);
+    const unsigned group = tid / lanes, ngroups = nthreads / lanes, lane = tid % lanes;
+    const unsigned L = a.bag_size;
+
+    __shared__ unsigned s_pre[kMaxWorld + 1];
+
+    // ---- Q1: segment-sum gradients of duplicate keys --------------------------------------------
+    {
+        const unsigned n_uniq = cnt[0];
+        const bool dups = (n_uniq != a.n);
+        const float scale = (a.flags & FUSED_MEAN) ? 1.0f / (float)L : 1.0f;
+        for (unsigned i = group; i < a.n; i += ngroups) {
+            const unsigned u = (unsigned)a.inverse[i];
+            const float* g = a.grads + (size_t)(i / L) * a.dim;
+            float* dst = a.agg + (size_t)u * a.dim;
+            for (unsigned d = lane * 4; d < a.dim; d += lanes * 4) {
+                float4 v = *(const float4*)(g + d);
+                if (L > 1 && (a.flags & FUSED_MEAN)) { v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale; }
+                if (dups) atomicAdd((float4*)(dst + d), v);
+                else *(float4*)(dst + d) = v;
+            }
+        }
+    }
+    if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_Q1)) return;
+
+    if (a.world > 1) {
+        // the owners must have consumed the previous push before their mailboxes are overwritten
+        if (!wait_all_flags(mine.push_ack, a.epoch - 1u, a, W_ACK)) return;
+        // ---- Q2: ship merged gradient rows to the owners
+        if (threadIdx.x == 0) {
+            unsigned acc = 0;
+            for (int o = 0; o < a.world; ++o) {
+                s_pre[o] = acc;
+                acc += (o == me) ? 0u : min(send_cnt[o], C);
+            }
+            s_pre[a.world] = acc;
+        }
+        __syncthreads();
+        const unsigned total = s_pre[a.world];
+        for (unsigned e = group; e < total; e += ngroups) {
+            int o = 0;
+            while (e >= s_pre[o + 1]) ++o;
+            const unsigned p = e - s_pre[o];
+            const unsigned u = a.send_ret[(size_t)o * C + p];
+            copy_row(a.peer[o].mail_grad + ((size_t)me * C + p) * a.dim, a.agg + (size_t)u * a.dim, a.dim, lane,
+                     lanes);
+        }
+        __threadfence_system();
+        if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_Q2)) return;
+        if (blockIdx.x == 0 && threadIdx.x < (unsigned)a.world && (int)threadIdx.x != me)
+            st_release_sys(&a.peer[threadIdx.x].grad_flag[me], a.epoch);
+        if (!wait_all_flags(mine.grad_flag, a.epoch, a, W_GRADFLAG)) return;
+        __syncthreads();
+    }
+
+    // ---- Q3 (owner) -----------------------------------------------------------------------------
+    if (threadIdx.x == 0) {
+        unsigned acc = 0;
+        for (int r = 0; r < a.world; ++r) {
+            s_pre[r] = acc;
+            acc += in_cnt[r];
+        }
+        s_pre[a.world] = acc;
+    }
+    __syncthreads();
+    const unsigned total_in = s_pre[a.world];
+
+    if (a.world > 1) {
+        // Q3a: leader election per table row: the entry with the lowest (source rank, position) wins
+        for (unsigned e = tid; e < total_in; e += nthreads) {
+            int r = 0;
+            while (e >= s_pre[r + 1]) ++r;
+            const unsigned id = (unsigned)r * C + (e - s_pre[r]);
+            const unsigned slot = a.res_slot[id];
+            if (slot != kNoSlot) atomicMin(&T.slots[slot].aux, id);
+        }
+        if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_Q3A)) return;
+        // Q3b: fold the other ranks' gradients into the leader's row
+        for (unsigned e = group; e < total_in; e += ngroups) {
+            int r = 0;
+            while (e >= s_pre[r + 1]) ++r;
+            const unsigned p = e - s_pre[r];
+            const unsigned id = (unsigned)r * C + p;
+            const unsigned slot = a.res_slot[id];
+            if (slot == kNoSlot) continue;
+            const unsigned lead = T.slots[slot].aux;
+            if (lead == id) continue;
+            const unsigned lr = lead / C, lp = lead % C;
+            const float* src = ((int)r == me) ? a.agg + (size_t)a.send_ret[(size_t)me * C + p] * a.dim
+                                              : mine.mail_grad + (size_t)id * a.dim;
+            float* dst = ((int)lr == me) ? a.agg + (size_t)a.send_ret[(size_t)me * C + lp] * a.dim
+                                         : mine.mail_grad + (size_t)lead * a.dim;
+            for (unsigned d = lane * 4; d < a.dim; d += lanes * 4)
+                atomicAdd((float4*)(dst + d), *(const float4*)(src + d));
+        }
+        if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_Q3B)) return;
+    }
+
+    // Q3c: one optimizer step per touched row
+    const bool sync_mode = (a.flags & FUSED_SYNC_PUSH) != 0;
+    const unsigned dim = a.dim;
+    for (unsigned e = group; e < total_in; e += ngroups) {
+        int r = 0;
+        while (e >= s_pre[r + 1]) ++r;
+        const unsigned p = e - s_pre[r];
+        const unsigned id = (unsigned)r * C + p;
+        const unsigned slot = a.res_slot[id];
+        if (slot == kNoSlot) {
+            if (lane == 0) set_status(a.ctl, kStOom, W_NOROW);
+            continue;
+        }
+        if (a.world > 1) {
+            if (T.slots[slot].aux != id) continue;
+        }
+        const unsigned row = T.slots[slot].row;
+        if (row >= kRowPending) {
+            if (lane == 0) {
+                set_status(a.ctl, kStOom, W_NOROW);
+                T.slots[slot].aux = kNoRow;
+            }
+            continue;
+        }
+        const float* g = (r == me) ? a.agg + (size_t)a.send_ret[(size_t)me * C + p] * dim
+                                   : mine.mail_grad + (size_t)id * dim;
+        float* w = T.row_ptr(row);
+        if (sync_mode) {
+            float* delta = w + (size_t)(T.n_opt_slots + 1) * dim;
+            for (unsigned d = lane * 4; d < dim; d += lanes * 4) {
+                float4 gv = *(const float4*)(g + d);
+                float4 dv = *(float4*)(delta + d);
+                dv.x += gv.x; dv.y += gv.y; dv.z += gv.z; dv.w += gv.w;
+                *(float4*)(delta + d) = dv;
+            }
+            if (lane == 0) {
+                unsigned bit = 1u << (row & 31u);
+                unsigned old = atomicOr(&T.touched_bits[row >> 5], bit);
+                if (!(old & bit)) {
+                    unsigned j = atomicAdd(T.touched_count, 1u);
+                    if (j < T.touched_cap) T.touched_list[j] = row;
+                    else set_status(a.ctl, kStOom, W_NOROW);
+                }
+            }
+        } else {
+            for (unsigned d = lane * 4; d < dim; d += lanes * 4) {
+                float4 gv = *(const float4*)(g + d);
+                float4 wv = *(float4*)(w + d);
+                float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
+                if (T.n_opt_slots > 0) s0 = *(float4*)(w + dim + d);
+                if (T.n_opt_slots > 1) s1 = *(float4*)(w + 2 * dim + d);
+                opt_update(a.opt, wv.x, s0.x, s1.x, gv.x);
+                opt_update(a.opt, wv.y, s0.y, s1.y, gv.y);
+                opt_update(a.opt, wv.z, s0.z, s1.z, gv.z);
+                opt_update(a.opt, wv.w, s0.w, s1.w, gv.w);
+                *(float4*)(w + d) = wv;
+                if (T.n_opt_slots > 0) *(float4*)(w + dim + d) = s0;
+                if (T.n_opt_slots > 1) *(float4*)(w + 2 * dim + d) = s1;
+            }
+        }
+        if (T.dirty_bits != nullptr && lane == 0) atomicOr(&T.dirty_bits[row >> 5], 1u << (row & 31u));
+        if (a.world > 1 && lane == 0) T.slots[slot].aux = kNoRow;
+    }
+
+    if (a.world > 1) {
+        // last CTA out acknowledges the sources: their next push may overwrite our mailboxes
+        __threadfence();
+        __syncthreads();
+        __shared__ unsigned s_last;
+        if (threadIdx.x == 0) s_last = (atomicAdd(&a.ctl->done_blocks, 1u) == nblocks - 1u);
+        __syncthreads();
+        if (s_last) {
+            if (threadIdx.x == 0) a.ctl->done_blocks = 0;
+            if (threadIdx.x < (unsigned)a.world && (int)threadIdx.x != me)
+                st_release_sys(&a.peer[threadIdx.x].push_ack[me], a.epoch);
+        }
+    }
+}
+
+int fused_max_blocks(int device, int* pull_blocks, int* push_blocks) {
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) return (int)e;
+    int per_sm = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_pull_kernel, kThreads, 0);
+    if (e != cudaSuccess) return (int)e;
+    *pull_blocks = per_sm * prop.multiProcessorCount;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_push_kernel, kThreads, 0);
+    if (e != cudaSuccess) return (int)e;
+    *push_blocks = per_sm * prop.multiProcessorCount;
+    return 0;
+}
+
+int launch_fused_pull(const FusedArgs& a, int nblocks, void* stream) {
+    void* params[] = {(void*)&a};
+    return (int)cudaLaunchCooperativeKernel((const void*)fused_pull_kernel, dim3(nblocks), dim3(kThreads), params, 0,
+                                            (cudaStream_t)stream);
+}
+
+int launch_fused_push(const FusedArgs& a, int nblocks, void* stream) {
+    void* params[] = {(void*)&a};
+    return (int)cudaLaunchCooperativeKernel((const void*)fused_push_kernel, dim3(nblocks), dim3(kThreads), params, 0,
+                                            (cudaStream_t)stream);
+}
+
+}  // namespace psb

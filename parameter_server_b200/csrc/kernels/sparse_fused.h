@@ -1,0 +1,75 @@
+// Argument blocks of the fused sparse pull / push kernels (host + device view).
+#pragma once
+#include <cstdint>
+
+#include "common.cuh"
+#include "optim.cuh"
+
+namespace psb {
+
+// Pointers into ONE rank's symmetric (peer-mapped) buffer, as seen from the calling process.
+struct PeerBufs {
+    unsigned* key_flag;    // [kMaxWorld] epoch written by source rank r at index r once its keys landed
+    unsigned* key_cnt;     // [kMaxWorld] number of keys rank r sent
+    unsigned* row_flag;    // [kMaxWorld] epoch written by owner o once the rows for this rank landed
+    unsigned* grad_flag;   // [kMaxWorld] epoch written by source rank r once its gradients landed
+    unsigned* push_ack;    // [kMaxWorld] epoch written by owner o once it consumed this rank's gradients
+    long long* mail_keys;  // [world][C]
+    unsigned* mail_ret;    // [world][C] index in the sender's unique list (where the row must return)
+    float* rows_in;        // [N][dim] rows returned by remote owners, indexed by unique id
+    float* mail_grad;      // [world][C][dim] merged gradients sent by each source rank
+};
+
+enum FusedFlags : unsigned {
+    FUSED_INSERT = 1u,        // missing keys are inserted (pull of a non read-only operator)
+    FUSED_COPY_ROWS = 2u,     // return rows (pull); off when only a push plan is built
+    FUSED_PREPARE_PUSH = 4u,  // zero the gradient aggregation rows for a following push
+    FUSED_MEAN = 8u,          // mean instead of sum pooling
+    FUSED_SYNC_PUSH = 16u,    // push accumulates into the delta section instead of updating
+};
+
+struct FusedArgs {
+    int world;
+    int rank;
+    unsigned C;  // capacity of one (source, owner) mailbox, in entries
+    unsigned N;  // capacity of one call, in key positions
+    unsigned dim;
+    unsigned flags;
+    unsigned epoch;      // call number of this kernel family (same on every rank)
+    unsigned plan_par;   // parity of the pull epoch whose plan a push reuses
+    unsigned long long limit_ns;
+    PeerBufs peer[kMaxWorld];  // peer[rank] is this GPU's own buffer
+    // ---- local scratch -------------------------------------------------------------------
+    Slot* dedup;
+    unsigned long long dmask;
+    unsigned* pos_slot;    // [N] dedup slot of each key position
+    int* inverse;          // [N] unique id of each key position
+    unsigned* uniq_row;    // [N] local row index of a unique key, kRemoteRow when the owner is a peer
+    long long* send_keys;  // [world][C] staged per-owner key lists
+    unsigned* send_ret;    // [world][C] unique id of each staged key
+    float* agg;            // [N][dim] per-unique-key gradient sums
+    unsigned* res_slot;    // [world][C] owner side: table slot of each received key
+    unsigned* new_list;    // [world*C] owner side: slots whose rows were attached by this call
+    unsigned* counters;    // [2][16] per epoch parity: 0 n_uniq, 1 n_new, 4.. send_cnt[world]
+    unsigned* in_cnt;      // [2][kMaxWorld] per epoch parity: keys received from each source rank
+    KernelCtl* ctl;
+    const int* shard_owner;  // [n_shards] owning rank of every global shard
+    int n_shards;
+    TableView table;
+    // ---- call inputs / outputs ----------------------------------------------------------------
+    const long long* keys;  // [n]
+    unsigned n;
+    unsigned bag_size;      // keys pooled per output row (1 = no pooling)
+    float* out;             // [n / bag_size][dim]
+    const float* grads;     // [n / bag_size][dim] gradient w.r.t. `out`
+    OptConfig opt;
+};
+
+constexpr unsigned kRemoteRow = 0xFFFFFFFDu;
+
+// Host launchers (defined in sparse_fused.cu). `stream` is a cudaStream_t. Return cudaError_t as int.
+int launch_fused_pull(const FusedArgs& a, int nblocks, void* stream);
+int launch_fused_push(const FusedArgs& a, int nblocks, void* stream);
+int fused_max_blocks(int device, int* pull_blocks, int* push_blocks);
+
+}  // namespace psb

@@ -1,0 +1,287 @@
+#include "sparse_engine.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <stdexcept>
+
+namespace psb {
+
+namespace {
+size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
+uint64_t pow2_ceil64(uint64_t v) {
+    uint64_t p = 1;
+    while (p < v) p <<= 1;
+    return p;
+}
+__global__ void fill_dedup_kernel(Slot* s, uint64_t n) {
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        Slot e;
+        e.key = kEmptyKey;
+        e.row = kNoRow;
+        e.aux = kNoRow;
+        s[i] = e;
+    }
+}
+const char* where_name(unsigned w) {
+    switch (w) {
+        case 1: return "pull: grid barrier after dedup";
+        case 2: return "pull: grid barrier after key shipment";
+        case 3: return "pull: waiting for a source rank's keys";
+        case 4: return "pull: grid barrier after key resolution";
+        case 5: return "pull: grid barrier after row initialisation";
+        case 6: return "pull: grid barrier after row return";
+        case 7: return "pull: waiting for an owner's rows";
+        case 8: return "pull: (source, owner) mailbox overflow - raise pair_capacity";
+        case 9: return "pull: table index full";
+        case 10: return "pull: row pool exhausted";
+        case 32: return "push: grid barrier after gradient merge";
+        case 33: return "push: waiting for an owner's acknowledgement of the previous push";
+        case 34: return "push: grid barrier after gradient shipment";
+        case 35: return "push: waiting for a source rank's gradients";
+        case 36: return "push: grid barrier after leader election";
+        case 37: return "push: grid barrier after cross-rank merge";
+        case 38: return "push: key without a backing row (pool exhausted)";
+        default: return "unknown site";
+    }
+}
+}  // namespace
+
+SparseEngine::SparseEngine(GpuTable* table, const SparseEngineConfig& cfg) : table_(table), cfg_(cfg) {
+    if (cfg_.world < 1 || cfg_.world > kMaxWorld) throw std::invalid_argument("SparseEngine: world must be 1..8");
+    if (table_->dim() % 4 != 0) throw std::invalid_argument("SparseEngine: dim must be a multiple of 4");
+    cudaSetDevice(table_->device());
+    const uint64_t N = cfg_.max_keys;
+    const int W = cfg_.world;
+    if (cfg_.pair_capacity) C_ = cfg_.pair_capacity;
+    else if (W <= 2) C_ = (uint32_t)N;
+    else C_ = (uint32_t)std::min<uint64_t>(N, std::max<uint64_t>(65536, 2 * N / W + 4096));
+    const uint64_t dim = table_->dim();
+
+    // symmetric part
+    size_t off = 0;
+    off_flags_ = off; off = align_up(off + 5 * kMaxWorld * sizeof(unsigned));
+    if (W > 1) {
+        off_mail_keys_ = off; off = align_up(off + (size_t)W * C_ * 8);
+        off_mail_ret_ = off; off = align_up(off + (size_t)W * C_ * 4);
+        off_rows_in_ = off; off = align_up(off + (size_t)N * dim * 4);
+        off_mail_grad_ = off; off = align_up(off + (size_t)W * C_ * dim * 4);
+    }
+    symm_.reset(new SymmetricBuffer(table_->device(), off));
+
+    // local scratch
+    dedup_slots_ = pow2_ceil64(2 * N);
+    size_t s = 0;
+    auto carve = [&](size_t bytes) { size_t o = s; s = align_up(s + bytes); return o; };
+    const size_t o_dedup = carve(dedup_slots_ * sizeof(Slot));
+    const size_t o_pos = carve(N * 4), o_inv = carve(N * 4), o_urow = carve(N * 4);
+    const size_t o_skeys = carve((size_t)W * C_ * 8), o_sret = carve((size_t)W * C_ * 4);
+    const size_t o_agg = carve(N * dim * 4);
+    const size_t o_res = carve((size_t)W * C_ * 4), o_new = carve((size_t)W * C_ * 4);
+    const size_t o_cnt = carve(2 * 16 * 4), o_in = carve(2 * kMaxWorld * 4);
+    const size_t o_ctl1 = carve(sizeof(KernelCtl)), o_ctl2 = carve(sizeof(KernelCtl));
+    const size_t o_owner = carve((size_t)std::max(cfg_.n_shards, 1) * 4);
+    scratch_bytes_ = s;
+    cudaError_t e = cudaMalloc(&scratch_, s);
+    if (e != cudaSuccess) throw std::runtime_error(std::string("SparseEngine: cudaMalloc scratch: ") + cudaGetErrorString(e));
+    cudaMemset(scratch_, 0, s);
+    dedup_ = (Slot*)(scratch_ + o_dedup);
+    pos_slot_ = (unsigned*)(scratch_ + o_pos);
+    inverse_ = (int*)(scratch_ + o_inv);
+    uniq_row_ = (unsigned*)(scratch_ + o_urow);
+    send_keys_ = (long long*)(scratch_ + o_skeys);
+    send_ret_ = (unsigned*)(scratch_ + o_sret);
+    agg_ = (float*)(scratch_ + o_agg);
+    res_slot_ = (unsigned*)(scratch_ + o_res);
+    new_list_ = (unsigned*)(scratch_ + o_new);
+    counters_ = (unsigned*)(scratch_ + o_cnt);
+    in_cnt_ = (unsigned*)(scratch_ + o_in);
+    ctl_pull_ = (KernelCtl*)(scratch_ + o_ctl1);
+    ctl_push_ = (KernelCtl*)(scratch_ + o_ctl2);
+    shard_owner_dev_ = (int*)(scratch_ + o_owner);
+    fill_dedup_kernel<<<148 * 4, 256>>>(dedup_, dedup_slots_);
+    // default placement: shard s lives on rank s % world
+    std::vector<int> owner(std::max(cfg_.n_shards, 1));
+    for (size_t i = 0; i < owner.size(); ++i) owner[i] = (int)(i % (size_t)W);
+    set_shard_owner(owner);
+    int rc = fused_max_blocks(table_->device(), &pull_blocks_, &push_blocks_);
+    if (rc != 0) throw std::runtime_error("SparseEngine: occupancy query failed");
+    cudaDeviceSynchronize();
+    std::vector<void*> self(1, symm_->local());
+    if (W == 1) symm_->connect_local(self, 0);
+}
+
+SparseEngine::~SparseEngine() {
+    cudaSetDevice(table_->device());
+    cudaDeviceSynchronize();
+    if (scratch_) cudaFree(scratch_);
+}
+
+Status SparseEngine::connect(const std::vector<std::string>& handles) {
+    if ((int)handles.size() != cfg_.world) return Status::InvalidConfig("connect: need one handle per rank");
+    return symm_->connect(handles, cfg_.rank);
+}
+
+void SparseEngine::connect_local(const std::vector<SparseEngine*>& engines) {
+    std::vector<void*> ptrs;
+    for (auto* e : engines) ptrs.push_back(e->symm_->local());
+    symm_->connect_local(ptrs, cfg_.rank);
+}
+
+Status SparseEngine::set_shard_owner(const std::vector<int>& owner) {
+    if ((int)owner.size() != std::max(cfg_.n_shards, 1)) return Status::InvalidConfig("shard_owner length != n_shards");
+    for (int o : owner)
+        if (o < 0 || o >= cfg_.world) return Status::InvalidConfig("shard owner out of range");
+    cudaSetDevice(table_->device());
+    cudaError_t e = cudaMemcpy(shard_owner_dev_, owner.data(), owner.size() * 4, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return Status::Error(cudaGetErrorString(e));
+    shard_owner_host_ = owner;
+    plan_valid_ = false;
+    return Status::Ok();
+}
+
+void SparseEngine::fill_common(FusedArgs& a) const {
+    a.world = cfg_.world;
+    a.rank = cfg_.rank;
+    a.C = C_;
+    a.N = cfg_.max_keys;
+    a.dim = table_->dim();
+    a.limit_ns = (unsigned long long)(cfg_.wait_limit_s * 1e9);
+    for (int r = 0; r < cfg_.world; ++r) {
+        char* base = (char*)symm_->peer(r);
+        unsigned* fl = (unsigned*)(base + off_flags_);
+        a.peer[r].key_flag = fl;
+        a.peer[r].key_cnt = fl + kMaxWorld;
+        a.peer[r].row_flag = fl + 2 * kMaxWorld;
+        a.peer[r].grad_flag = fl + 3 * kMaxWorld;
+        a.peer[r].push_ack = fl + 4 * kMaxWorld;
+        a.peer[r].mail_keys = (long long*)(base + off_mail_keys_);
+        a.peer[r].mail_ret = (unsigned*)(base + off_mail_ret_);
+        a.peer[r].rows_in = (float*)(base + off_rows_in_);
+        a.peer[r].mail_grad = (float*)(base + off_mail_grad_);
+    }
+    a.dedup = dedup_;
+    a.dmask = dedup_slots_ - 1;
+    a.pos_slot = pos_slot_;
+    a.inverse = inverse_;
+    a.uniq_row = uniq_row_;
+    a.send_keys = send_keys_;
+    a.send_ret = send_ret_;
+    a.agg = agg_;
+    a.res_slot = res_slot_;
+    a.new_list = new_list_;
+    a.counters = counters_;
+    a.in_cnt = in_cnt_;
+    a.shard_owner = shard_owner_dev_;
+    a.n_shards = std::max(cfg_.n_shards, 1);
+    a.table = table_->view();
+}
+
+Status SparseEngine::pull(const long long* keys, uint32_t n, uint32_t bag_size, float* out, unsigned flags,
+                          void* stream) {
+    if (n > cfg_.max_keys) return Status::InvalidConfig("pull: n exceeds max_keys of the engine");
+    if (bag_size == 0 || n % bag_size != 0) return Status::InvalidConfig("pull: n must be a multiple of bag_size");
+    if (symm_->world() != cfg_.world) return Status::Error("pull: peers are not connected");
+    cudaSetDevice(table_->device());
+    Status reserve = Status::Ok();
+    if (flags & FUSED_INSERT) {
+        // worst case every rank sends n new keys to this owner; bounded by the mailboxes
+        const uint64_t worst = std::min<uint64_t>((uint64_t)cfg_.world * C_, (uint64_t)cfg_.world * n);  // keys this owner may receive
+        reserve = table_->reserve_rows(worst);
+    }
+    FusedArgs a;
+    fill_common(a);
+    a.flags = flags;
+    a.epoch = ++pull_epoch_;
+    a.plan_par = a.epoch & 1u;
+    a.ctl = ctl_pull_;
+    a.keys = keys;
+    a.n = n;
+    a.bag_size = bag_size;
+    a.out = out;
+    a.grads = nullptr;
+    int rc = launch_fused_pull(a, pull_blocks_, stream);
+    ++launches_;
+    if (flags & FUSED_INSERT) table_->refresh_usage_async(stream);
+    if (rc != 0) return Status::Error(std::string("fused_pull launch: ") + cudaGetErrorString((cudaError_t)rc));
+    plan_keys_ = keys;
+    plan_n_ = n;
+    plan_bag_ = bag_size;
+    plan_flags_ = flags;
+    plan_valid_ = true;
+    plan_used_ = false;
+    if (!reserve.ok() && reserve.code() != StatusCode::OUT_OF_MEMORY) return reserve;
+    return Status::Ok();
+}
+
+Status SparseEngine::push(const float* grads, const OptConfig& opt, unsigned flags, void* stream) {
+    if (!plan_valid_) return Status::Error("push: no plan (call pull or plan first)");
+    cudaSetDevice(table_->device());
+    if (plan_used_) {
+        // a plan pushed twice: the aggregation rows must start from zero again
+        cudaMemsetAsync(agg_, 0, (size_t)plan_n_ * table_->dim() * 4, (cudaStream_t)stream);
+    }
+    FusedArgs a;
+    fill_common(a);
+    a.flags = (plan_flags_ & FUSED_MEAN) | (flags & FUSED_SYNC_PUSH);
+    a.epoch = ++push_epoch_;
+    a.plan_par = pull_epoch_ & 1u;
+    a.ctl = ctl_push_;
+    a.keys = plan_keys_;
+    a.n = plan_n_;
+    a.bag_size = plan_bag_;
+    a.out = nullptr;
+    a.grads = grads;
+    a.opt = opt;
+    int rc = launch_fused_push(a, push_blocks_, stream);
+    ++launches_;
+    if (rc != 0) return Status::Error(std::string("fused_push launch: ") + cudaGetErrorString((cudaError_t)rc));
+    plan_used_ = true;
+    return Status::Ok();
+}
+
+Status SparseEngine::check(void* stream) {
+    cudaSetDevice(table_->device());
+    KernelCtl h[2];
+    cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return Status::Fatal(std::string("stream: ") + cudaGetErrorString(e));
+    e = cudaMemcpy(&h[0], ctl_pull_, sizeof(KernelCtl), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess) e = cudaMemcpy(&h[1], ctl_push_, sizeof(KernelCtl), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return Status::Fatal(std::string("status read: ") + cudaGetErrorString(e));
+    for (int k = 0; k < 2; ++k) {
+        if (h[k].status == 0) continue;
+        std::string msg = where_name(h[k].where);
+        switch (h[k].status) {
+            case kStOom: table_->set_healthy(false); return Status::OOM(msg);
+            case kStTimeout: return Status::Timeout(msg);
+            default: return Status::Error(msg);
+        }
+    }
+    return Status::Ok();
+}
+
+Status SparseEngine::reset(void* stream) {
+    cudaSetDevice(table_->device());
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaStreamSynchronize(s);
+    // keep the shard map (last carve) and the table; clear everything else
+    const size_t keep_from = (char*)shard_owner_dev_ - scratch_;
+    cudaMemsetAsync(scratch_, 0, keep_from, s);
+    fill_dedup_kernel<<<148 * 4, 256, 0, s>>>(dedup_, dedup_slots_);
+    cudaMemsetAsync((char*)symm_->local() + off_flags_, 0, 5 * kMaxWorld * sizeof(unsigned), s);
+    cudaError_t e = cudaStreamSynchronize(s);
+    pull_epoch_ = push_epoch_ = 0;
+    plan_valid_ = false;
+    if (e != cudaSuccess) return Status::Fatal(cudaGetErrorString(e));
+    return Status::Ok();
+}
+
+uint32_t SparseEngine::last_unique(void* stream) {
+    cudaSetDevice(table_->device());
+    cudaStreamSynchronize((cudaStream_t)stream);
+    unsigned v = 0;
+    cudaMemcpy(&v, counters_ + (pull_epoch_ & 1u) * 16, 4, cudaMemcpyDeviceToHost);
+    return v;
+}
+
+}  // namespace psb

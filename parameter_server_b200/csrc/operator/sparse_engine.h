@@ -1,0 +1,90 @@
+// SparseEngine: the collective (all training ranks call together) pull / push path of one sparse
+// table, i.e. the B200 replacement of PullHandler::pull + SparseTablePullOperator and
+// PushHandler::async_push / sync_push + SparseTablePushOperator
+// (pico-ps/handler/PullHandler.cpp:101-141, pico-ps/handler/PushHandler.cpp:53-86). It owns the
+// symmetric mailboxes, the local scratch and the per-call epoch, and launches the fused kernels.
+#pragma once
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../comm/symmetric.h"
+#include "../kernels/sparse_fused.h"
+#include "../storage/gpu_table.h"
+
+namespace psb {
+
+struct SparseEngineConfig {
+    int world = 1;
+    int rank = 0;
+    uint32_t max_keys = 1u << 20;   // N: key positions per call per rank
+    uint32_t pair_capacity = 0;     // C: entries per (source, owner) mailbox; 0 = automatic
+    int n_shards = 1;               // global shard count G
+    double wait_limit_s = 10.0;     // bound of every device-side wait
+};
+
+class SparseEngine {
+public:
+    SparseEngine(GpuTable* table, const SparseEngineConfig& cfg);
+    ~SparseEngine();
+
+    std::string ipc_handle() const { return symm_->ipc_handle(); }
+    Status connect(const std::vector<std::string>& handles);
+    // In-process multi-engine wiring (tests, single process driving several GPUs).
+    void connect_local(const std::vector<SparseEngine*>& engines);
+
+    // shard -> owning rank map (length n_shards); may be changed between calls (reshard).
+    Status set_shard_owner(const std::vector<int>& owner);
+    const std::vector<int>& shard_owner() const { return shard_owner_host_; }
+
+    // Collective pull. keys: device int64[n]; out: device float[n/bag_size][dim] (may be null when
+    // flags lacks FUSED_COPY_ROWS). Leaves a plan for one following push().
+    Status pull(const long long* keys, uint32_t n, uint32_t bag_size, float* out, unsigned flags, void* stream);
+    // Collective push with the plan of the last pull: grads is device float[n/bag_size][dim].
+    Status push(const float* grads, const OptConfig& opt, unsigned flags, void* stream);
+    // Synchronise the stream and translate the device status words of pull and push.
+    Status check(void* stream);
+    // Re-arm after an error (clears scratch, barriers and flags on THIS rank; every rank must do it).
+    Status reset(void* stream);
+
+    uint32_t last_unique(void* stream);  // unique keys of the last pull (synchronises)
+    const SparseEngineConfig& config() const { return cfg_; }
+    GpuTable* table() const { return table_; }
+    uint32_t pair_capacity() const { return C_; }
+    uint64_t scratch_bytes() const { return scratch_bytes_; }
+    uint64_t kernel_launches() const { return launches_; }
+    void set_wait_limit(double s) { cfg_.wait_limit_s = s; }
+
+private:
+    void fill_common(FusedArgs& a) const;
+
+    GpuTable* table_;
+    SparseEngineConfig cfg_;
+    uint32_t C_ = 0;
+    std::unique_ptr<SymmetricBuffer> symm_;
+    size_t off_flags_ = 0, off_mail_keys_ = 0, off_mail_ret_ = 0, off_rows_in_ = 0, off_mail_grad_ = 0;
+    char* scratch_ = nullptr;
+    uint64_t scratch_bytes_ = 0;
+    // carved from scratch_
+    Slot* dedup_ = nullptr;
+    uint64_t dedup_slots_ = 0;
+    unsigned *pos_slot_ = nullptr, *uniq_row_ = nullptr, *send_ret_ = nullptr, *res_slot_ = nullptr,
+             *new_list_ = nullptr, *counters_ = nullptr, *in_cnt_ = nullptr;
+    int* inverse_ = nullptr;
+    long long* send_keys_ = nullptr;
+    float* agg_ = nullptr;
+    KernelCtl* ctl_pull_ = nullptr;
+    KernelCtl* ctl_push_ = nullptr;
+    int* shard_owner_dev_ = nullptr;
+    std::vector<int> shard_owner_host_;
+    unsigned pull_epoch_ = 0, push_epoch_ = 0;
+    int pull_blocks_ = 0, push_blocks_ = 0;
+    // last pull (the plan)
+    const long long* plan_keys_ = nullptr;
+    uint32_t plan_n_ = 0, plan_bag_ = 1;
+    unsigned plan_flags_ = 0;
+    bool plan_valid_ = false, plan_used_ = false;
+    uint64_t launches_ = 0;
+};
+
+}  // namespace psb

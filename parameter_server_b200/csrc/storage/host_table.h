@@ -1,0 +1,354 @@
+// HostTable: the CPU storage back-end (sharded, locked, in host DRAM).
+//
+// Three jobs: (1) the numerical oracle that the GPU kernels are tested against; (2) the storage of
+// servers that run without a GPU (control-plane tests, serving on CPU); (3) the timed "CPU
+// restatement" of the reference algorithm. It follows the reference's structure directly: one
+// hash map per shard guarded by a reader/writer lock, pull that inserts missing keys unless
+// read_only (pico-ps/operator/SparsePullOperator.h:200-229), push that applies the update rule per
+// item under the exclusive lock (pico-ps/operator/SparsePushOperator.h:245-268), sync push into a
+// delta buffer folded by store (pico-ps/operator/SparsePushOperator.h:278-416), resumable shard
+// iteration (pico-ps/storage/KVShardStorage.h:52-92) and a byte budget that turns into
+// OUT_OF_MEMORY (pico-ps/storage/Storage.cpp:114-136).
+#pragma once
+#include <atomic>
+#include <cstdint>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <shared_mutex>
+#include <vector>
+
+#include "../common/easy_hash_map.h"
+#include "../common/hash.h"
+#include "../common/status.h"
+#include "../kernels/optim.cuh"
+
+namespace psb {
+
+struct HostTableConfig {
+    uint32_t dim = 16;
+    int32_t opt_type = OPT_SGD;
+    bool sync_delta = false;
+    int32_t n_shards = 1;  // global shard count
+    uint64_t init_seed = 0;
+    float init_range = 0.01f;
+    float slot_init0 = 0.f;
+    float slot_init1 = 0.f;
+    uint64_t soft_limit_bytes = 0;
+    uint64_t hard_limit_bytes = 0;
+};
+
+constexpr int64_t kHostEmptyKey = (int64_t)0x8000000000000000ull;
+
+class HostTable {
+public:
+    struct Shard {
+        explicit Shard() : map(kHostEmptyKey) {}
+        EasyHashMap<int64_t, uint32_t> map;
+        std::vector<float> rows;
+        std::vector<uint32_t> free_rows;
+        std::vector<uint32_t> touched;       // rows with a pending sync delta
+        std::vector<uint8_t> touched_flag;   // per row
+        std::vector<uint8_t> dirty;          // per row (incremental sync)
+        mutable std::shared_mutex mu;
+    };
+
+    explicit HostTable(const HostTableConfig& cfg) : cfg_(cfg) {
+        n_slots_ = (uint32_t)opt_num_slots(cfg_.opt_type);
+        stride_ = cfg_.dim * (1 + n_slots_ + (cfg_.sync_delta ? 1 : 0));
+    }
+
+    uint32_t dim() const { return cfg_.dim; }
+    uint32_t stride() const { return stride_; }
+    int32_t n_shards() const { return cfg_.n_shards; }
+    const HostTableConfig& config() const { return cfg_; }
+
+    // --- shard lifecycle (create_shard / erase_shard of ShardStorage) --------------------------
+    void create_shard(int s) {
+        std::unique_lock<std::shared_mutex> g(mu_);
+        if (!shards_.count(s)) shards_[s].reset(new Shard());
+    }
+    void erase_shard(int s) {
+        std::unique_lock<std::shared_mutex> g(mu_);
+        auto it = shards_.find(s);
+        if (it != shards_.end()) {
+            bytes_ -= it->second->rows.capacity() * sizeof(float);
+            shards_.erase(it);
+        }
+    }
+    bool has_shard(int s) const {
+        std::shared_lock<std::shared_mutex> g(mu_);
+        return shards_.count(s) != 0;
+    }
+    std::vector<int> shard_list() const {
+        std::shared_lock<std::shared_mutex> g(mu_);
+        std::vector<int> v;
+        for (auto& kv : shards_) v.push_back(kv.first);
+        return v;
+    }
+
+    int shard_of(int64_t key) const { return sparse_shard_of(key, cfg_.n_shards); }
+
+    void init_row(float* row, int64_t key) const {
+        for (uint32_t d = 0; d < cfg_.dim; ++d) row[d] = init_uniform(key, d, cfg_.init_seed, cfg_.init_range);
+        for (uint32_t s = 0; s < n_slots_; ++s) {
+            float iv = s == 0 ? cfg_.slot_init0 : cfg_.slot_init1;
+            for (uint32_t d = 0; d < cfg_.dim; ++d) row[(s + 1) * cfg_.dim + d] = iv;
+        }
+        if (cfg_.sync_delta)
+            for (uint32_t d = 0; d < cfg_.dim; ++d) row[(n_slots_ + 1) * cfg_.dim + d] = 0.f;
+    }
+
+    // Pull one shard's keys (keys must all map to shard `s`). out: n*dim floats.
+    Status pull_shard(int s, const int64_t* keys, size_t n, float* out, bool insert) {
+        Shard* sh = get(s);
+        if (!sh) return Status::InvalidID("shard " + std::to_string(s) + " is not local");
+        if (insert && !healthy_) return Status::OOM("storage is unhealthy");
+        {
+            // fast path: shared lock, no inserts needed
+            std::shared_lock<std::shared_mutex> g(sh->mu);
+            size_t i = 0;
+            for (; i < n; ++i) {
+                auto* e = sh->map.find(keys[i]);
+                if (!e) break;
+                std::copy_n(sh->rows.data() + (size_t)e->second * stride_, cfg_.dim, out + i * cfg_.dim);
+            }
+            if (i == n) return Status::Ok();
+            if (!insert) {
+                for (; i < n; ++i) {
+                    auto* e = sh->map.find(keys[i]);
+                    if (e) std::copy_n(sh->rows.data() + (size_t)e->second * stride_, cfg_.dim, out + i * cfg_.dim);
+                    else for (uint32_t d = 0; d < cfg_.dim; ++d)
+                        out[i * cfg_.dim + d] = init_uniform(keys[i], d, cfg_.init_seed, cfg_.init_range);
+                }
+                return Status::Ok();
+            }
+        }
+        // upgrade: exclusive lock for the inserts (the reference upgrades on the first miss)
+        std::unique_lock<std::shared_mutex> g(sh->mu);
+        for (size_t i = 0; i < n; ++i) {
+            uint32_t row;
+            Status st = find_or_insert(*sh, keys[i], &row);
+            if (!st.ok()) return st;
+            std::copy_n(sh->rows.data() + (size_t)row * stride_, cfg_.dim, out + i * cfg_.dim);
+        }
+        return Status::Ok();
+    }
+
+    // Push one shard's pre-aggregated items. grads: n*dim floats.
+    Status push_shard(int s, const int64_t* keys, const float* grads, size_t n, const OptConfig& opt, bool sync) {
+        Shard* sh = get(s);
+        if (!sh) return Status::InvalidID("shard " + std::to_string(s) + " is not local");
+        std::unique_lock<std::shared_mutex> g(sh->mu);
+        for (size_t i = 0; i < n; ++i) {
+            uint32_t row;
+            Status st = find_or_insert(*sh, keys[i], &row);
+            if (!st.ok()) return st;
+            float* w = sh->rows.data() + (size_t)row * stride_;
+            const float* gr = grads + i * cfg_.dim;
+            if (sync) {
+                if (!cfg_.sync_delta) return Status::InvalidConfig("table was created without sync_delta");
+                float* delta = w + (size_t)(n_slots_ + 1) * cfg_.dim;
+                for (uint32_t d = 0; d < cfg_.dim; ++d) delta[d] += gr[d];
+                if (!sh->touched_flag[row]) { sh->touched_flag[row] = 1; sh->touched.push_back(row); }
+            } else {
+                apply(opt, w, gr);
+                if (track_dirty_) sh->dirty[row] = 1;
+            }
+        }
+        return Status::Ok();
+    }
+
+    // OP_STORE: fold pending deltas of every local shard.
+    Status store(const OptConfig& opt) {
+        for (int s : shard_list()) {
+            Shard* sh = get(s);
+            std::unique_lock<std::shared_mutex> g(sh->mu);
+            for (uint32_t row : sh->touched) {
+                float* w = sh->rows.data() + (size_t)row * stride_;
+                float* delta = w + (size_t)(n_slots_ + 1) * cfg_.dim;
+                apply(opt, w, delta);
+                for (uint32_t d = 0; d < cfg_.dim; ++d) delta[d] = 0.f;
+                sh->touched_flag[row] = 0;
+                if (track_dirty_) sh->dirty[row] = 1;
+            }
+            sh->touched.clear();
+        }
+        return Status::Ok();
+    }
+
+    // DirectPush: overwrite / insert full rows (n*stride floats) or embeddings only (n*dim).
+    Status set_rows(const int64_t* keys, const float* rows, size_t n, bool emb_only) {
+        for (size_t i = 0; i < n; ++i) {
+            Shard* sh = get(shard_of(keys[i]));
+            if (!sh) continue;  // not local: the caller routes, foreign keys are skipped (restore semantics)
+            std::unique_lock<std::shared_mutex> g(sh->mu);
+            uint32_t row;
+            Status st = find_or_insert(*sh, keys[i], &row);
+            if (!st.ok()) return st;
+            float* w = sh->rows.data() + (size_t)row * stride_;
+            if (emb_only) std::copy_n(rows + i * cfg_.dim, cfg_.dim, w);
+            else std::copy_n(rows + i * stride_, stride_, w);
+            if (track_dirty_) sh->dirty[row] = 1;
+        }
+        return Status::Ok();
+    }
+
+    // Read existing rows; found[i] = 0/1. Missing rows are zero-filled.
+    void get_rows(const int64_t* keys, size_t n, float* out, int32_t* found, bool emb_only) const {
+        const uint32_t width = emb_only ? cfg_.dim : stride_;
+        for (size_t i = 0; i < n; ++i) {
+            Shard* sh = get(shard_of(keys[i]));
+            bool ok = false;
+            if (sh) {
+                std::shared_lock<std::shared_mutex> g(sh->mu);
+                auto* e = sh->map.find(keys[i]);
+                if (e) {
+                    std::copy_n(sh->rows.data() + (size_t)e->second * stride_, width, out + i * width);
+                    ok = true;
+                }
+            }
+            if (!ok) std::fill_n(out + i * width, width, 0.f);
+            if (found) found[i] = ok ? 1 : 0;
+        }
+    }
+
+    uint64_t erase_keys(const int64_t* keys, size_t n) {
+        uint64_t erased = 0;
+        for (size_t i = 0; i < n; ++i) {
+            Shard* sh = get(shard_of(keys[i]));
+            if (!sh) continue;
+            std::unique_lock<std::shared_mutex> g(sh->mu);
+            auto* e = sh->map.find(keys[i]);
+            if (!e) continue;
+            uint32_t row = e->second;
+            sh->map.erase(keys[i]);
+            sh->free_rows.push_back(row);
+            sh->dirty[row] = 0;
+            if (sh->touched_flag[row]) {
+                sh->touched_flag[row] = 0;
+                for (auto& t : sh->touched) if (t == row) { t = sh->touched.back(); sh->touched.pop_back(); break; }
+            }
+            ++erased;
+        }
+        n_items_ -= erased;
+        return erased;
+    }
+
+    // Resumable export of shard `s`: examines buckets [cursor, cursor+window) and appends live
+    // entries (optionally only dirty ones). Returns the next cursor; == bucket_count when done.
+    size_t export_shard(int s, size_t cursor, size_t window, bool dirty_only, std::vector<int64_t>* keys,
+                        std::vector<float>* rows, bool* finished) const {
+        Shard* sh = get(s);
+        *finished = true;
+        if (!sh) return 0;
+        std::shared_lock<std::shared_mutex> g(sh->mu);
+        const auto& b = sh->map.buckets();
+        size_t end = std::min(b.size(), cursor + window);
+        for (size_t i = cursor; i < end; ++i) {
+            if (!sh->map.live(b[i])) continue;
+            if (dirty_only && !sh->dirty[b[i].second]) continue;
+            keys->push_back(b[i].first);
+            const float* w = sh->rows.data() + (size_t)b[i].second * stride_;
+            rows->insert(rows->end(), w, w + stride_);
+        }
+        *finished = end >= b.size();
+        return end;
+    }
+
+    uint64_t shard_size(int s) const {
+        Shard* sh = get(s);
+        if (!sh) return 0;
+        std::shared_lock<std::shared_mutex> g(sh->mu);
+        return sh->map.size();
+    }
+    uint64_t size() const { return n_items_; }
+    uint64_t memory_usage() const { return bytes_; }
+    bool healthy() const { return healthy_; }
+    void set_healthy(bool h) { healthy_ = h; }
+    void set_limits(uint64_t soft, uint64_t hard) { cfg_.soft_limit_bytes = soft; cfg_.hard_limit_bytes = hard; }
+    void enable_dirty_tracking() { track_dirty_ = true; }
+    void clear_dirty() {
+        for (int s : shard_list()) {
+            Shard* sh = get(s);
+            std::unique_lock<std::shared_mutex> g(sh->mu);
+            std::fill(sh->dirty.begin(), sh->dirty.end(), 0);
+        }
+    }
+    void clear() {
+        for (int s : shard_list()) {
+            Shard* sh = get(s);
+            std::unique_lock<std::shared_mutex> g(sh->mu);
+            bytes_ -= sh->rows.capacity() * sizeof(float);
+            sh->map.clear();
+            std::vector<float>().swap(sh->rows);
+            sh->free_rows.clear(); sh->touched.clear(); sh->touched_flag.clear(); sh->dirty.clear();
+        }
+        n_items_ = 0;
+        healthy_ = true;
+    }
+
+private:
+    Shard* get(int s) const {
+        std::shared_lock<std::shared_mutex> g(mu_);
+        auto it = shards_.find(s);
+        return it == shards_.end() ? nullptr : it->second.get();
+    }
+
+    Status find_or_insert(Shard& sh, int64_t key, uint32_t* row) {
+        auto* e = sh.map.find(key);
+        if (e) { *row = e->second; return Status::Ok(); }
+        if (!healthy_) return Status::OOM("storage is unhealthy");
+        uint32_t r;
+        if (!sh.free_rows.empty()) {
+            r = sh.free_rows.back();
+            sh.free_rows.pop_back();
+        } else {
+            size_t old_cap = sh.rows.capacity();
+            size_t need = sh.rows.size() + stride_;
+            if (need > old_cap) {
+                size_t new_cap = std::max<size_t>(old_cap * 2, (size_t)stride_ * 64);
+                uint64_t extra = (new_cap - old_cap) * sizeof(float);
+                uint64_t b = bytes_;
+                if ((cfg_.hard_limit_bytes && b + extra > cfg_.hard_limit_bytes) ||
+                    (cfg_.soft_limit_bytes && b + extra > cfg_.soft_limit_bytes)) {
+                    healthy_ = false;
+                    return Status::OOM("host row pool would exceed the memory limit");
+                }
+                sh.rows.reserve(new_cap);
+                bytes_ += (sh.rows.capacity() - old_cap) * sizeof(float);
+            }
+            r = (uint32_t)(sh.rows.size() / stride_);
+            sh.rows.resize(need);
+            sh.touched_flag.push_back(0);
+            sh.dirty.push_back(0);
+        }
+        init_row(sh.rows.data() + (size_t)r * stride_, key);
+        sh.map.force_emplace(key, r);
+        if (track_dirty_) sh.dirty[r] = 1;
+        ++n_items_;
+        *row = r;
+        return Status::Ok();
+    }
+
+    void apply(const OptConfig& opt, float* w, const float* g) const {
+        const uint32_t dim = cfg_.dim;
+        float dummy0 = 0.f, dummy1 = 0.f;
+        for (uint32_t d = 0; d < dim; ++d) {
+            float& s0 = n_slots_ > 0 ? w[dim + d] : dummy0;
+            float& s1 = n_slots_ > 1 ? w[2 * dim + d] : dummy1;
+            opt_update(opt, w[d], s0, s1, g[d]);
+        }
+    }
+
+    HostTableConfig cfg_;
+    uint32_t stride_ = 0, n_slots_ = 0;
+    mutable std::shared_mutex mu_;
+    std::map<int, std::unique_ptr<Shard>> shards_;
+    std::atomic<uint64_t> n_items_{0};
+    std::atomic<uint64_t> bytes_{0};
+    std::atomic<bool> healthy_{true};
+    bool track_dirty_ = false;
+};
+
+}  // namespace psb

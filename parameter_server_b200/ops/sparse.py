@@ -1,0 +1,328 @@
+"""SparseTable: the torch-facing sparse parameter table.
+
+One instance per rank (one process per GPU). ``pull`` and ``push`` are collective calls: every
+rank of the group calls them in the same order, and the fused kernels exchange keys, rows and
+gradients through NVLink peer memory (see ``csrc/kernels/sparse_fused.cu``). They stand for
+``PullHandler::pull`` and ``PushHandler::async_push / sync_push / store``
+(pico-ps/handler/PullHandler.h:45-99, pico-ps/handler/PushHandler.h:43-107).
+
+On a machine without CUDA the same class runs on the host storage back-end (``HostTable``), which
+is also the numerical oracle of the kernels.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from .._lib import C
+from ..utils.status import StatusError, raise_if_error
+from .optim import OPTIMIZERS, make_opt_config, set_adam_step
+
+
+def _dist_info(group=None):
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_world_size(group), dist.get_rank(group)
+    return 1, 0
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class SparseTable:
+    """Sharded ``int64 key -> fp32[dim]`` table with optimizer slots kept next to each row.
+
+    Args:
+        dim: embedding width (a multiple of 4).
+        optimizer: ``sgd | adagrad | ftrl | adam | adamw | sum | set``; options go in ``opt_kwargs``.
+        capacity: expected number of keys held by THIS rank (sizes the index; the row pool grows).
+        max_keys: largest number of key positions in one pull / push call on this rank.
+        n_shards: global shard count G (default: world size); keys map to shards with
+            ``jump_consistent_hash(murmur(key), G)`` and shards to ranks with ``shard_owner``.
+        sync: allocate the per-row delta section needed by ``sync_push`` + ``store``.
+        read_only: pulls never insert (predictor tables).
+        device: ``cuda`` device, or ``cpu`` for the host back-end.
+    """
+
+    def __init__(self, dim: int, optimizer: str = "adagrad", opt_kwargs: Optional[dict] = None, *,
+                 capacity: int = 1 << 20, max_keys: int = 1 << 20, n_shards: Optional[int] = None,
+                 sync: bool = False, read_only: bool = False, init_range: float = 0.01, seed: int = 0,
+                 device=None, group=None, pair_capacity: int = 0, wait_limit_s: float = 10.0,
+                 max_rows: int = 0, slab_shift: Optional[int] = None, memory_limit_bytes: int = 0):
+        if dim % 4:
+            raise ValueError("dim must be a multiple of 4")
+        self.dim = dim
+        self.group = group
+        self.world, self.rank = _dist_info(group)
+        self.n_shards = int(n_shards or self.world)
+        self.read_only = read_only
+        self.opt = make_opt_config(optimizer, **(opt_kwargs or {}))
+        self.opt_name = optimizer.lower()
+        self.step = 0
+        self.max_keys = int(max_keys)
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        self.device = torch.device(device)
+        self.is_cuda = self.device.type == "cuda"
+        self._plan_keys = None
+        if self.is_cuda:
+            tc = C.GpuTableConfig()
+            tc.device = self.device.index if self.device.index is not None else torch.cuda.current_device()
+            tc.dim = dim
+            tc.opt_type = self.opt.type
+            tc.sync_delta = sync
+            tc.index_capacity = max(2 * int(capacity), 1024)
+            tc.max_rows = int(max_rows)
+            stride_bytes = 4 * dim * (1 + C.opt_num_slots(self.opt.type) + (1 if sync else 0))
+            if slab_shift is None:
+                # slabs of about 256 MB, at least 4096 rows
+                slab_shift = max(12, min(22, int(np.log2(max(1, (256 << 20) // stride_bytes)))))
+            tc.slab_shift = slab_shift
+            tc.init_seed = seed
+            tc.init_range = init_range
+            tc.slot_init0 = self.opt.slot_init0
+            tc.slot_init1 = self.opt.slot_init1
+            tc.soft_limit_bytes = int(memory_limit_bytes)
+            tc.hard_limit_bytes = int(memory_limit_bytes)
+            with torch.cuda.device(self.device):
+                self.table = C.GpuTable(tc)
+                ec = C.SparseEngineConfig()
+                ec.world, ec.rank = self.world, self.rank
+                ec.max_keys = self.max_keys
+                ec.pair_capacity = int(pair_capacity)
+                ec.n_shards = self.n_shards
+                ec.wait_limit_s = wait_limit_s
+                self.engine = C.SparseEngine(self.table, ec)
+                if self.world > 1:
+                    self._connect()
+        else:
+            hc = C.HostTableConfig()
+            hc.dim = dim
+            hc.opt_type = self.opt.type
+            hc.sync_delta = sync
+            hc.n_shards = self.n_shards
+            hc.init_seed = seed
+            hc.init_range = init_range
+            hc.slot_init0 = self.opt.slot_init0
+            hc.slot_init1 = self.opt.slot_init1
+            hc.soft_limit_bytes = int(memory_limit_bytes)
+            hc.hard_limit_bytes = int(memory_limit_bytes)
+            self.table = C.HostTable(hc)
+            self.engine = None
+            self._shard_owner = [s % self.world for s in range(self.n_shards)]
+            for s in range(self.n_shards):
+                if self.world == 1 or self._shard_owner[s] == self.rank:
+                    self.table.create_shard(s)
+
+    # ------------------------------------------------------------------------------------------
+    def _connect(self) -> None:
+        import torch.distributed as dist
+
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(self.engine.ipc_handle()), group=self.group)
+        raise_if_error(self.engine.connect(handles))
+        dist.barrier(group=self.group)
+
+    @property
+    def shard_owner(self) -> Sequence[int]:
+        return list(self.engine.shard_owner()) if self.is_cuda else list(self._shard_owner)
+
+    def set_shard_owner(self, owner: Sequence[int]) -> None:
+        if self.is_cuda:
+            raise_if_error(self.engine.set_shard_owner(list(owner)))
+        else:
+            self._shard_owner = list(owner)
+
+    # ------------------------------------------------------------------------------------------
+    def pull(self, keys: torch.Tensor, bag_size: int = 1, mean: bool = False, *, insert: Optional[bool] = None,
+             out: Optional[torch.Tensor] = None, for_push: bool = True) -> torch.Tensor:
+        """Rows (sum/mean pooled over ``bag_size`` consecutive keys) of ``keys``; missing keys are
+        inserted with their initial value unless the table is read-only."""
+        insert = (not self.read_only) if insert is None else insert
+        keys = keys.reshape(-1)
+        n = keys.numel()
+        if self.is_cuda:
+            if keys.dtype != torch.int64 or not keys.is_cuda:
+                raise TypeError("keys must be a CUDA int64 tensor")
+            keys = keys.contiguous()
+            if out is None:
+                out = torch.empty((n // bag_size, self.dim), dtype=torch.float32, device=self.device)
+            flags = C.FUSED_COPY_ROWS
+            if insert:
+                flags |= C.FUSED_INSERT
+            if for_push:
+                flags |= C.FUSED_PREPARE_PUSH
+            if mean:
+                flags |= C.FUSED_MEAN
+            st = self.engine.pull(keys.data_ptr(), n, bag_size, out.data_ptr(), flags, _stream())
+            raise_if_error(st)
+            self._plan_keys = keys  # keep the key buffer alive until the push
+            return out
+        st, rows = self.table.pull(keys.cpu().numpy(), bag_size, mean, insert)
+        raise_if_error(st)
+        self._plan_keys = (keys.cpu().numpy().copy(), bag_size, mean)
+        res = torch.from_numpy(rows)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+
+    def plan(self, keys: torch.Tensor, bag_size: int = 1, mean: bool = False) -> None:
+        """Prepare a push for ``keys`` without returning rows (push without a preceding pull)."""
+        keys = keys.reshape(-1)
+        if self.is_cuda:
+            keys = keys.contiguous()
+            flags = C.FUSED_INSERT | C.FUSED_PREPARE_PUSH | (C.FUSED_MEAN if mean else 0)
+            raise_if_error(self.engine.pull(keys.data_ptr(), keys.numel(), bag_size, 0, flags, _stream()))
+            self._plan_keys = keys
+        else:
+            self._plan_keys = (keys.cpu().numpy().copy(), bag_size, mean)
+
+    def push(self, grads: torch.Tensor, keys: Optional[torch.Tensor] = None, *, sync: bool = False,
+             bag_size: int = 1, mean: bool = False) -> None:
+        """Apply gradients (w.r.t. the pooled pull output) to the rows of the last pull's keys, or of
+        ``keys`` when given. ``sync=True`` buffers into the delta section until :meth:`store`."""
+        if keys is not None:
+            self.plan(keys, bag_size, mean)
+        if self._plan_keys is None:
+            raise RuntimeError("push without keys needs a preceding pull")
+        self.step += 1
+        if self.opt.type == C.OPT_ADAM:
+            set_adam_step(self.opt, self.step)
+        if self.is_cuda:
+            if grads.dtype != torch.float32:
+                grads = grads.float()
+            grads = grads.contiguous()
+            flags = C.FUSED_SYNC_PUSH if sync else 0
+            raise_if_error(self.engine.push(grads.data_ptr(), self.opt, flags, _stream()))
+            self._last_grads = grads  # keep alive until the kernel ran
+        else:
+            k, bag, mn = self._plan_keys
+            g = grads.detach().cpu().float().numpy().reshape(-1, self.dim)
+            raise_if_error(self.table.push(k, g, self.opt, bag, mn, sync))
+
+    def store(self) -> None:
+        """Fold the buffered sync pushes into the weights (OP_STORE)."""
+        if self.is_cuda:
+            raise_if_error(self.table.store_delta(self.opt, _stream()))
+        else:
+            raise_if_error(self.table.store(self.opt))
+
+    def check(self) -> None:
+        """Synchronise and raise :class:`StatusError` if a kernel reported an error."""
+        if self.is_cuda:
+            raise_if_error(self.engine.check(_stream()))
+
+    def status(self):
+        return self.engine.check(_stream()) if self.is_cuda else C.Status()
+
+    def reset(self) -> None:
+        if self.is_cuda:
+            raise_if_error(self.engine.reset(_stream()))
+
+    # ------------------------------------------------------------------------------------------
+    def size(self) -> int:
+        return int(self.table.size())
+
+    def memory_usage(self) -> int:
+        return int(self.table.memory_usage())
+
+    def get_rows(self, keys: torch.Tensor, emb_only: bool = True):
+        """Read rows of LOCAL keys without inserting. Returns (rows, found)."""
+        keys = keys.reshape(-1)
+        if self.is_cuda:
+            keys = keys.contiguous()
+            w = self.dim if emb_only else self.table.stride()
+            out = torch.empty((keys.numel(), w), dtype=torch.float32, device=self.device)
+            found = torch.empty(keys.numel(), dtype=torch.int32, device=self.device)
+            raise_if_error(self.table.get_rows(keys.data_ptr(), keys.numel(), out.data_ptr(), found.data_ptr(),
+                                               emb_only, _stream()))
+            return out, found
+        rows, found = self.table.get_rows(keys.cpu().numpy(), emb_only)
+        return torch.from_numpy(rows), torch.from_numpy(found)
+
+    def set_rows(self, keys: torch.Tensor, rows: torch.Tensor, emb_only: bool = False) -> None:
+        """Insert / overwrite rows of LOCAL keys (DirectPush)."""
+        keys = keys.reshape(-1)
+        if self.is_cuda:
+            keys = keys.contiguous()
+            rows = rows.contiguous().float()
+            raise_if_error(self.table.set_rows(keys.data_ptr(), rows.data_ptr(), keys.numel(), emb_only, _stream()))
+        else:
+            raise_if_error(self.table.set_rows(keys.cpu().numpy(), rows.cpu().float().numpy(), emb_only))
+
+    def erase_keys(self, keys: torch.Tensor) -> int:
+        keys = keys.reshape(-1)
+        if self.is_cuda:
+            keys = keys.contiguous()
+            st, n = self.table.erase_keys(keys.data_ptr(), keys.numel(), _stream())
+            raise_if_error(st)
+            return int(n)
+        return int(self.table.erase_keys(keys.cpu().numpy()))
+
+    def export(self, shard: int = -1, batch: int = 1 << 18, dirty_only: bool = False):
+        """Iterate ``(keys, rows)`` batches of the local entries (of one shard when ``shard >= 0``).
+        ``rows`` carries the full row: embedding, optimizer slots and, if present, the sync delta."""
+        if self.is_cuda:
+            stride = self.table.stride()
+            cap = self.table.index_capacity()
+            window = min(cap, max(1024, batch))
+            kbuf = torch.empty(window, dtype=torch.int64, device=self.device)
+            rbuf = torch.empty((window, stride), dtype=torch.float32, device=self.device)
+            cursor = 0
+            mode = 4 if dirty_only else (1 if shard >= 0 else 0)
+            while cursor < cap:
+                st, n, cursor = self.table.export_window(cursor, window, mode, shard, self.rank, self.n_shards, 0,
+                                                         kbuf.data_ptr(), rbuf.data_ptr(), _stream())
+                raise_if_error(st)
+                if n:
+                    k, r = kbuf[:n].clone(), rbuf[:n].clone()
+                    if dirty_only and shard >= 0:
+                        sel = torch.tensor([C.sparse_shard_of(int(x), self.n_shards) == shard for x in k.tolist()],
+                                           device=self.device)
+                        k, r = k[sel], r[sel]
+                    if k.numel():
+                        yield k, r
+        else:
+            shards = [shard] if shard >= 0 else self.table.shard_list()
+            for s in shards:
+                cursor, finished = 0, False
+                while not finished:
+                    k, r, cursor, finished = self.table.export_shard(s, cursor, batch, dirty_only)
+                    if len(k):
+                        yield torch.from_numpy(k), torch.from_numpy(r)
+
+    def clear(self) -> None:
+        if self.is_cuda:
+            raise_if_error(self.table.clear(_stream()))
+        else:
+            self.table.clear()
+
+    # ------------------------------------------------------------------------------------------
+    def lookup(self, keys: torch.Tensor, bag_size: int = 1, mean: bool = False) -> torch.Tensor:
+        """Differentiable pull: the backward pass pushes the gradient to the parameter server."""
+        return sparse_lookup(self, keys, bag_size, mean)
+
+
+class _SparseLookup(torch.autograd.Function):
+    """Pull in forward, push in backward (the worker side of a PS training step)."""
+
+    @staticmethod
+    def forward(ctx, table: SparseTable, keys: torch.Tensor, bag_size: int, mean: bool, anchor: torch.Tensor):
+        ctx.table = table
+        return table.pull(keys, bag_size, mean)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        ctx.table.push(grad_out)
+        return None, None, None, None, None
+
+
+def sparse_lookup(table: SparseTable, keys: torch.Tensor, bag_size: int = 1, mean: bool = False) -> torch.Tensor:
+    # the anchor makes autograd record the node although no input tensor requires grad
+    anchor = torch.zeros((), device=table.device if table.is_cuda else "cpu", requires_grad=True)
+    return _SparseLookup.apply(table, keys, bag_size, mean, anchor)

@@ -1,0 +1,126 @@
+"""CPU storage + oracle semantics (pull inserts, dedup, pre-aggregation, sync push + store, erase,
+export), modelled on pico-ps/test/ps_service_test.cpp:77-239."""
+import numpy as np
+import pytest
+import torch
+
+from parameter_server_b200 import C, SparseTable, make_opt_config
+
+
+def mk(dim=8, opt="sum", sync=False, n_shards=4, **kw):
+    return SparseTable(dim, opt, kw or None, n_shards=n_shards, sync=sync, device="cpu")
+
+
+def test_pull_inserts_and_is_deterministic():
+    t = mk()
+    keys = torch.tensor([5, 9, 5, 1 << 39, 9], dtype=torch.int64)
+    a = t.pull(keys)
+    assert t.size() == 3
+    b = t.pull(keys)
+    assert torch.equal(a, b)
+    assert torch.equal(a[0], a[2]) and torch.equal(a[1], a[4])
+    exp = np.array([C.init_uniform(5, d, 0, 0.01) for d in range(8)], dtype=np.float32)
+    assert np.array_equal(a[0].numpy(), exp)
+
+
+def test_read_only_pull_does_not_insert():
+    t = SparseTable(8, "sum", n_shards=2, read_only=True, device="cpu")
+    a = t.pull(torch.tensor([1, 2, 3]))
+    assert t.size() == 0
+    exp = np.array([C.init_uniform(2, d, 0, 0.01) for d in range(8)], dtype=np.float32)
+    assert np.array_equal(a[1].numpy(), exp)
+
+
+def test_push_preaggregates_duplicates_sum():
+    t = mk(dim=4)
+    keys = torch.tensor([7, 7, 8, 7])
+    base = t.pull(keys).clone()
+    g = torch.arange(16, dtype=torch.float32).reshape(4, 4)
+    t.push(g)
+    after = t.pull(torch.tensor([7, 8]))
+    assert torch.allclose(after[0], base[0] + g[0] + g[1] + g[3])
+    assert torch.allclose(after[1], base[2] + g[2])
+
+
+def test_adagrad_matches_formula():
+    t = mk(dim=4, opt="adagrad", lr=0.05, init_accumulator=0.1)
+    k = torch.tensor([42])
+    w0 = t.pull(k).clone()
+    g = torch.tensor([[1e-3, -2e-3, 3e-3, 0.0]])
+    t.push(g)
+    w1 = t.pull(k)
+    acc = 0.1 + g * g
+    exp = w0 - 0.05 * g / (acc.sqrt() + 1e-10)
+    assert torch.allclose(w1, exp, rtol=1e-6, atol=1e-9)
+    rows, found = t.get_rows(k, emb_only=False)
+    assert found[0] == 1 and torch.allclose(rows[0, 4:], acc[0])
+
+
+def test_sync_push_is_buffered_until_store():
+    t = mk(dim=4, opt="sgd", sync=True, lr=1.0)
+    k = torch.tensor([1, 2])
+    w0 = t.pull(k).clone()
+    g = torch.ones(2, 4)
+    t.push(g, sync=True)
+    t.pull(k)
+    t.push(g, sync=True)
+    assert torch.equal(t.pull(k), w0)  # nothing applied yet
+    t.store()
+    assert torch.allclose(t.pull(k), w0 - 2.0)
+    t.store()  # idempotent when nothing is pending
+    assert torch.allclose(t.pull(k), w0 - 2.0)
+
+
+def test_pooling_sum_and_mean():
+    t = mk(dim=4)
+    keys = torch.tensor([1, 2, 3, 3, 4, 5])
+    rows = t.pull(keys)
+    s = t.pull(keys, bag_size=3)
+    m = t.pull(keys, bag_size=3, mean=True)
+    assert torch.allclose(s[0], rows[:3].sum(0)) and torch.allclose(s[1], rows[3:].sum(0))
+    assert torch.allclose(m, s / 3)
+
+
+def test_erase_export_set_rows_round_trip():
+    t = mk(dim=4, opt="adagrad", n_shards=3)
+    keys = torch.arange(100, dtype=torch.int64)
+    t.pull(keys)
+    t.push(torch.randn(100, 4))
+    assert t.erase_keys(torch.arange(0, 100, 2)) == 50
+    assert t.size() == 50
+    got = {}
+    for k, r in t.export(batch=16):
+        for kk, rr in zip(k.tolist(), r):
+            got[kk] = rr.clone()
+    assert sorted(got) == list(range(1, 100, 2))
+    t2 = mk(dim=4, opt="adagrad", n_shards=5)  # different sharding: load rehashes
+    ks = torch.tensor(sorted(got))
+    t2.set_rows(ks, torch.stack([got[k] for k in sorted(got)]))
+    a, fa = t.get_rows(ks, emb_only=False)
+    b, fb = t2.get_rows(ks, emb_only=False)
+    assert fa.all() and fb.all() and torch.equal(a, b)
+
+
+def test_memory_limit_turns_into_oom_status():
+    t = SparseTable(64, "adagrad", n_shards=1, device="cpu", memory_limit_bytes=64 * 1024)
+    from parameter_server_b200 import StatusError, StatusCode
+    with pytest.raises(StatusError) as ei:
+        for i in range(100):
+            t.pull(torch.arange(i * 100, (i + 1) * 100))
+    assert ei.value.code == StatusCode.OUT_OF_MEMORY
+    assert not t.table.healthy()
+
+
+@pytest.mark.parametrize("opt,kw", [("sgd", dict(lr=0.1)), ("adagrad", dict(lr=0.05, init_accumulator=0.1)),
+                                    ("ftrl", dict(alpha=0.05, beta=1.0, l1=0.001, l2=0.01)),
+                                    ("adam", dict(lr=0.01))])
+def test_optimizers_move_weights(opt, kw):
+    t = mk(dim=4, opt=opt, **kw)
+    k = torch.tensor([3])
+    w0 = t.pull(k).clone()
+    for _ in range(3):
+        t.pull(k)
+        t.push(torch.full((1, 4), 0.5))
+    w1 = t.pull(k)
+    assert torch.all(w1 < w0) or opt == "ftrl"
+    assert torch.isfinite(w1).all()

@@ -1,0 +1,173 @@
+"""Single-GPU fused pull / push against the CPU oracle (plain fp32 reference of the same op)."""
+import numpy as np
+import pytest
+import torch
+
+from parameter_server_b200 import C, SparseTable, StatusCode, StatusError
+
+pytestmark = pytest.mark.gpu
+
+
+def zipf_keys(n, vocab, s, seed):
+    rng = np.random.default_rng(seed)
+    k = rng.zipf(s, size=n).astype(np.int64) % vocab
+    return torch.from_numpy(k * 2654435761 % (1 << 40))
+
+
+def pair(dim, opt, n_shards=4, sync=False, **kw):
+    g = SparseTable(dim, opt, kw or None, n_shards=n_shards, sync=sync, device="cuda", capacity=1 << 16,
+                    max_keys=1 << 16)
+    c = SparseTable(dim, opt, kw or None, n_shards=n_shards, sync=sync, device="cpu")
+    return g, c
+
+
+@pytest.mark.parametrize("dim", [16, 64, 128, 256])
+def test_pull_matches_oracle_bitwise(dim):
+    g, c = pair(dim, "adagrad", lr=0.05, init_accumulator=0.1)
+    keys = zipf_keys(20000, 5000, 1.1, 0)
+    a = g.pull(keys.cuda())
+    g.check()
+    b = c.pull(keys)
+    assert torch.equal(a.cpu(), b)
+    assert g.size() == c.size()
+    assert g.engine.last_unique(0) == len(set(keys.tolist()))
+    # second pull hits existing rows
+    a2 = g.pull(keys.cuda())
+    g.check()
+    assert torch.equal(a2, a)
+
+
+@pytest.mark.parametrize("opt,kw", [("sgd", dict(lr=0.1)), ("adagrad", dict(lr=0.05, init_accumulator=0.1)),
+                                    ("ftrl", dict(alpha=0.05, beta=1.0, l1=0.001, l2=0.01)),
+                                    ("adam", dict(lr=0.01)), ("sum", {})])
+def test_push_unique_keys_bitwise(opt, kw):
+    g, c = pair(32, opt, **kw)
+    keys = torch.from_numpy(np.random.default_rng(1).permutation(1 << 20)[:8192].astype(np.int64))
+    for step in range(3):
+        grads = torch.randn(8192, 32, generator=torch.Generator().manual_seed(step)) * 1e-2
+        g.pull(keys.cuda())
+        g.push(grads.cuda())
+        c.pull(keys)
+        c.push(grads)
+    g.check()
+    a, fa = g.get_rows(keys.cuda(), emb_only=False)
+    b, fb = c.get_rows(keys, emb_only=False)
+    assert fa.all() and fb.all()
+    assert torch.equal(a.cpu(), b)
+
+
+def test_push_with_duplicates_close_to_oracle():
+    g, c = pair(64, "adagrad", lr=0.05, init_accumulator=0.1)
+    for step in range(4):
+        keys = zipf_keys(30000, 4000, 1.05, step)
+        grads = torch.randn(30000, 64, generator=torch.Generator().manual_seed(step)) * 1e-3
+        g.pull(keys.cuda())
+        g.push(grads.cuda())
+        c.pull(keys)
+        c.push(grads)
+    g.check()
+    uk = torch.unique(keys)
+    a, _ = g.get_rows(uk.cuda(), emb_only=False)
+    b, _ = c.get_rows(uk, emb_only=False)
+    assert torch.allclose(a.cpu(), b, rtol=1e-4, atol=1e-6)
+
+
+def test_pooling_and_mean_backward():
+    g, c = pair(16, "sgd", lr=1.0)
+    keys = zipf_keys(4096 * 4, 3000, 1.1, 3)
+    for mean in (False, True):
+        a = g.pull(keys.cuda(), bag_size=4, mean=mean)
+        b = c.pull(keys, bag_size=4, mean=mean)
+        assert torch.allclose(a.cpu(), b, rtol=1e-6, atol=1e-8)
+        grads = torch.randn(4096, 16) * 1e-2
+        g.push(grads.cuda())
+        c.push(grads)
+    g.check()
+    uk = torch.unique(keys)
+    a, _ = g.get_rows(uk.cuda())
+    b, _ = c.get_rows(uk)
+    assert torch.allclose(a.cpu(), b, rtol=1e-4, atol=1e-6)
+
+
+def test_sync_push_then_store():
+    g, c = pair(16, "adagrad", sync=True, lr=0.05, init_accumulator=0.1)
+    keys = torch.arange(0, 3000, dtype=torch.int64) * 7919
+    w0 = g.pull(keys.cuda()).clone()
+    for step in range(2):
+        grads = torch.randn(3000, 16, generator=torch.Generator().manual_seed(step)) * 1e-2
+        g.pull(keys.cuda()); g.push(grads.cuda(), sync=True)
+        c.pull(keys); c.push(grads, sync=True)
+    assert torch.equal(g.pull(keys.cuda()), w0)
+    g.store(); c.store()
+    g.check()
+    a, _ = g.get_rows(keys.cuda(), emb_only=False)
+    b, _ = c.get_rows(keys, emb_only=False)
+    assert torch.equal(a.cpu(), b)
+
+
+def test_read_only_pull_and_autograd_lookup():
+    t = SparseTable(16, "sgd", dict(lr=0.5), device="cuda", capacity=1 << 12, max_keys=1 << 12)
+    keys = torch.arange(100, device="cuda")
+    r = t.pull(keys, insert=False)
+    assert t.size() == 0
+    exp = torch.tensor([[C.init_uniform(k, d, 0, 0.01) for d in range(16)] for k in range(100)])
+    assert torch.equal(r.cpu(), exp)
+    emb = t.lookup(keys)
+    loss = (emb * 2.0).sum()
+    loss.backward()
+    t.check()
+    after, found = t.get_rows(keys)
+    assert found.all()
+    assert torch.allclose(after.cpu(), exp - 0.5 * 2.0)
+
+
+def test_erase_export_set_rows_clear():
+    g, c = pair(32, "adagrad", n_shards=3, lr=0.05, init_accumulator=0.1)
+    keys = torch.arange(5000, dtype=torch.int64) * 104729
+    g.pull(keys.cuda()); g.push(torch.ones(5000, 32).cuda() * 0.01)
+    g.check()
+    assert g.erase_keys(keys[::2].cuda()) == 2500
+    assert g.size() == 2500
+    ks, rs = [], []
+    for k, r in g.export(batch=4096):
+        ks.append(k); rs.append(r)
+    ks, rs = torch.cat(ks), torch.cat(rs)
+    assert sorted(ks.tolist()) == sorted(keys[1::2].tolist())
+    per_shard = sum(k.numel() for s in range(3) for k, _ in g.export(shard=s))
+    assert per_shard == 2500
+    g2 = SparseTable(32, "adagrad", n_shards=5, device="cuda", capacity=1 << 14, max_keys=1 << 14)
+    g2.set_rows(ks, rs)
+    a, fa = g.get_rows(ks, emb_only=False)
+    b, fb = g2.get_rows(ks, emb_only=False)
+    assert fa.all() and fb.all() and torch.equal(a, b)
+    # erased rows are recycled by later inserts
+    g.pull(keys.cuda()); g.check()
+    assert g.size() == 5000
+    g.clear()
+    assert g.size() == 0
+
+
+def test_row_pool_limit_reports_oom_and_context_survives():
+    t = SparseTable(64, "adagrad", device="cuda", capacity=1 << 14, max_keys=1 << 13, max_rows=4096, slab_shift=12)
+    t.pull(torch.arange(3000, device="cuda")); t.check()
+    t.pull(torch.arange(3000, 8000, device="cuda"))
+    st = t.status()
+    assert st.code() == StatusCode.OUT_OF_MEMORY
+    assert not t.table.healthy()
+    # the context is still usable and existing rows are intact
+    t.reset()
+    r = t.pull(torch.arange(10, device="cuda"), insert=False)
+    t.check()
+    assert torch.isfinite(r).all()
+
+
+def test_large_batch_1m_keys():
+    g = SparseTable(64, "adagrad", dict(lr=0.05, init_accumulator=0.1), device="cuda", capacity=1 << 21,
+                    max_keys=1 << 20)
+    keys = zipf_keys(1 << 20, 1 << 22, 1.05, 9).cuda()
+    out = g.pull(keys)
+    g.push(torch.full((1 << 20, 64), 1e-3, device="cuda"))
+    g.check()
+    nu = g.engine.last_unique(0)
+    assert nu == torch.unique(keys).numel() == g.size()
+    assert torch.isfinite(out).all()
