@@ -1,5 +1,65 @@
 // Dense-table and GEMM kernel bindings.
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
+
+#include "kernels/gemm_tcgen05.h"
+#include "kernels/model_kernels.h"
+#include "operator/dense_engine.h"
+
 namespace py = pybind11;
-void bind_dense(py::module_& m) { (void)m; }
+using namespace psb;
+
+namespace {
+template <class T>
+T* ptr(uintptr_t p) { return reinterpret_cast<T*>(p); }
+}  // namespace
+
+void bind_dense(py::module_& m) {
+    py::class_<DenseEngine>(m, "DenseEngine")
+        .def(py::init<int, int, int, size_t, bool, int, double>(), py::arg("device"), py::arg("world"), py::arg("rank"),
+             py::arg("numel"), py::arg("grad_bf16"), py::arg("opt_type"), py::arg("wait_limit_s") = 10.0)
+        .def("ipc_handle", [](DenseEngine& e) { return py::bytes(e.ipc_handle()); })
+        .def("connect",
+             [](DenseEngine& e, const std::vector<py::bytes>& hs) {
+                 std::vector<std::string> v;
+                 for (auto& h : hs) v.push_back((std::string)h);
+                 return e.connect(v);
+             })
+        .def("connect_local", &DenseEngine::connect_local)
+        .def("numel", &DenseEngine::numel)
+        .def("shard_lo", &DenseEngine::shard_lo)
+        .def("shard_len", &DenseEngine::shard_len)
+        .def("params_ptr", [](DenseEngine& e) { return (uintptr_t)e.params_ptr(); })
+        .def("grads_ptr", [](DenseEngine& e) { return (uintptr_t)e.grads_ptr(); })
+        .def("peer_params_ptr", [](DenseEngine& e, int r) { return (uintptr_t)e.peer_params_ptr(r); })
+        .def("master_ptr", [](DenseEngine& e) { return (uintptr_t)e.master_ptr(); })
+        .def("slot_ptr", [](DenseEngine& e, int s) { return (uintptr_t)e.slot_ptr(s); })
+        .def("grad_bf16", &DenseEngine::grad_bf16)
+        .def("load_full", [](DenseEngine& e, uintptr_t full, uintptr_t s) { return e.load_full(ptr<const float>(full), (void*)s); })
+        .def("step", [](DenseEngine& e, const OptConfig& o, float scale, uintptr_t s) { return e.step(o, scale, (void*)s); })
+        .def("check", [](DenseEngine& e, uintptr_t s) { return e.check((void*)s); })
+        .def("kernel_launches", &DenseEngine::kernel_launches);
+
+    m.def("gemm_bf16",
+          [](uintptr_t a, int64_t lda, bool a_mn, uintptr_t b, int64_t ldb, bool b_mn, int M, int N, int K,
+             uintptr_t out_bf16, uintptr_t out_f32, int64_t ldd, uintptr_t bias, bool relu, uintptr_t mask,
+             int64_t ldmask, bool accumulate, uintptr_t err_flag, double wait_limit_s, uintptr_t stream) {
+              GemmOperand A{ptr<const void>(a), lda, a_mn}, B{ptr<const void>(b), ldb, b_mn};
+              GemmEpilogue ep;
+              ep.out_bf16 = ptr<__nv_bfloat16>(out_bf16);
+              ep.out_f32 = ptr<float>(out_f32);
+              ep.ldd = ldd;
+              ep.bias = ptr<const float>(bias);
+              ep.relu = relu ? 1 : 0;
+              ep.mask = ptr<const __nv_bfloat16>(mask);
+              ep.ldmask = ldmask;
+              ep.accumulate = accumulate ? 1 : 0;
+              return gemm_bf16(A, B, ep, M, N, K, ptr<unsigned>(err_flag), wait_limit_s, (void*)stream);
+          },
+          py::arg("a"), py::arg("lda"), py::arg("a_mn"), py::arg("b"), py::arg("ldb"), py::arg("b_mn"), py::arg("M"),
+          py::arg("N"), py::arg("K"), py::arg("out_bf16") = 0, py::arg("out_f32") = 0, py::arg("ldd") = 0,
+          py::arg("bias") = 0, py::arg("relu") = false, py::arg("mask") = 0, py::arg("ldmask") = 0,
+          py::arg("accumulate") = false, py::arg("err_flag") = 0, py::arg("wait_limit_s") = 2.0, py::arg("stream") = 0);
+
+    bind_model_kernels(m);
+}

@@ -1,0 +1,31 @@
+// Bindings of the non-GEMM model kernels.
+#include <pybind11/pybind11.h>
+
+#include "kernels/model_kernels.h"
+
+namespace py = pybind11;
+using namespace psb;
+
+void bind_model_kernels(py::module_& m) {
+    m.def("interaction_fwd", [](uintptr_t bottom, int64_t ldb, uintptr_t emb, int F, int D, uintptr_t out, int64_t ldo,
+                                int B, uintptr_t s) {
+        return interaction_fwd((const void*)bottom, ldb, (const float*)emb, F, D, (void*)out, ldo, B, (void*)s);
+    });
+    m.def("interaction_bwd", [](uintptr_t dout, int64_t ldo, uintptr_t bottom, int64_t ldb, uintptr_t emb, int F, int D,
+                                uintptr_t dbottom, int64_t lddb, uintptr_t demb, int B, bool relu_mask, uintptr_t s) {
+        return interaction_bwd((const void*)dout, ldo, (const void*)bottom, ldb, (const float*)emb, F, D, (void*)dbottom,
+                               lddb, (float*)demb, B, relu_mask ? 1 : 0, (void*)s);
+    });
+    m.def("bce_head", [](uintptr_t h, int64_t ldh, uintptr_t w, uintptr_t bias, uintptr_t y, int B, int K, float inv_batch,
+                         uintptr_t loss_sum, uintptr_t logits, uintptr_t dz_prev, int64_t lddz, uintptr_t dw, uintptr_t db,
+                         uintptr_t s) {
+        return bce_head((const void*)h, ldh, (const void*)w, (const float*)bias, (const float*)y, B, K, inv_batch,
+                        (float*)loss_sum, (float*)logits, (void*)dz_prev, lddz, (float*)dw, (float*)db, (void*)s);
+    });
+    m.def("bias_grad", [](uintptr_t dz, int64_t ld, int M, int N, uintptr_t db, uintptr_t s) {
+        return bias_grad((const void*)dz, ld, M, N, (float*)db, (void*)s);
+    });
+    m.def("cast_pad", [](uintptr_t x, int B, int Kin, uintptr_t out, int64_t ldo, uintptr_t s) {
+        return cast_pad((const float*)x, B, Kin, (void*)out, ldo, (void*)s);
+    });
+}

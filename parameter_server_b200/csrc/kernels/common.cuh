@@ -97,7 +97,9 @@ struct KernelCtl {
     unsigned status;     // first error (StatusCode) seen by the kernel, 0 = OK
     unsigned where;      // site id of the wait or check that failed
     unsigned done_blocks;
-    unsigned pad[3];
+    unsigned epoch;      // number of completed calls; a kernel runs as call epoch+1 and publishes it at its end,
+                         // so a launch captured in a CUDA graph advances the epoch on every replay
+    unsigned pad[2];
 };
 
 __device__ __forceinline__ void set_status(KernelCtl* ctl, unsigned code, unsigned where) {

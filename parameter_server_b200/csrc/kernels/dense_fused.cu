@@ -1,0 +1,171 @@
+// Dense push for sm_100a: reduce-scatter of the ranks' gradient buffers fused with the partitioned
+// optimizer step on the fp32 master shard and with the all-gather of the updated bf16 parameters,
+// all in ONE kernel over NVLink peer memory.
+//
+// Parity: DenseTablePushOperator splits a dense value into slices, each owned by one shard, and the
+// owner applies the update rule per slice (pico-ps/operator/DensePushOperator.h:76-84, :171-193);
+// DenseTablePullOperator reassembles the slices on the worker (pico-ps/operator/DensePullOperator.h:
+// 153-169, :197-216). Here slice r is the r-th contiguous 1/world of the flat parameter buffer:
+//   1. every rank announces "my gradients are complete" with a release flag on every peer;
+//   2. rank r sums slice r of every peer's gradient buffer with 16-byte peer loads, in rank order
+//      (bitwise reproducible), scales, and runs SGD / Adam(W) on its fp32 master + moments;
+//   3. it stores the new bf16 values of slice r into EVERY rank's parameter buffer (peer stores),
+//      which is the all-gather of the next dense pull;
+//   4. a second flag round tells every rank that all slices of its parameter buffer have landed and
+//      that its gradient buffer may be overwritten.
+// All waits are bounded; world == 1 runs the optimizer only.
+#include <cuda_bf16.h>
+
+#include "dense_fused.h"
+
+namespace psb {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+template <typename GT>
+struct Vec8;  // eight gradient elements
+template <>
+struct Vec8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) {
+        a = *(const float4*)p;
+        b = *(const float4*)(p + 4);
+    }
+    __device__ __forceinline__ void to_float(float* f) const {
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+};
+template <>
+struct Vec8<__nv_bfloat16> {
+    uint4 raw;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { raw = *(const uint4*)p; }
+    __device__ __forceinline__ void to_float(float* f) const {
+        const __nv_bfloat162* h = (const __nv_bfloat162*)&raw;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 t = __bfloat1622float2(h[i]);
+            f[2 * i] = t.x;
+            f[2 * i + 1] = t.y;
+        }
+    }
+};
+
+template <typename GT>
+__global__ void __launch_bounds__(kThreads) dense_rs_opt_ag_kernel(const DenseArgs a) {
+    const int me = a.rank;
+    const unsigned epoch = *((volatile unsigned*)&a.ctl->epoch) + 1u;
+    const int W = a.world;
+    // ---- 1. announce + wait: gradients of every rank are complete --------------------------------
+    if (W > 1) {
+        if (blockIdx.x == 0 && threadIdx.x < (unsigned)W && (int)threadIdx.x != me) {
+            __threadfence_system();
+            st_release_sys(a.peer_flags[threadIdx.x] + me, epoch);
+        }
+        int ok = 1;
+        if (threadIdx.x < (unsigned)W && (int)threadIdx.x != me) {
+            if (!wait_flag_ge(a.peer_flags[me] + threadIdx.x, epoch, a.limit_ns)) {
+                set_status(a.ctl, kStTimeout, 1);
+                ok = 0;
+            }
+        }
+        if (!__syncthreads_and(ok)) return;
+    }
+    // ---- 2+3. reduce, update, scatter bf16 ------------------------------------------------------------
+    const size_t n8 = a.shard_len / 8;
+    const GT* gsrc[kMaxWorld];
+    __nv_bfloat16* pdst[kMaxWorld];
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r) {
+        gsrc[r] = r < W ? (const GT*)a.peer_grads[r] + a.shard_lo : nullptr;
+        pdst[r] = r < W ? a.peer_params[r] + a.shard_lo : nullptr;
+    }
+    for (size_t c = blockIdx.x * (size_t)kThreads + threadIdx.x; c < n8; c += (size_t)gridDim.x * kThreads) {
+        const size_t i = c * 8;
+        float g[8];
+        {
+            Vec8<GT> v;
+            v.load(gsrc[0] + i);
+            v.to_float(g);
+        }
+#pragma unroll
+        for (int r = 1; r < kMaxWorld; ++r) {
+            if (r < W) {
+                Vec8<GT> v;
+                v.load(gsrc[r] + i);
+                float t[8];
+                v.to_float(t);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) g[k] += t[k];
+            }
+        }
+        float w[8], m[8], s[8];
+        *(float4*)&w[0] = *(const float4*)(a.master + i);
+        *(float4*)&w[4] = *(const float4*)(a.master + i + 4);
+        if (a.n_slots > 0) {
+            *(float4*)&m[0] = *(const float4*)(a.slot0 + i);
+            *(float4*)&m[4] = *(const float4*)(a.slot0 + i + 4);
+        }
+        if (a.n_slots > 1) {
+            *(float4*)&s[0] = *(const float4*)(a.slot1 + i);
+            *(float4*)&s[4] = *(const float4*)(a.slot1 + i + 4);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            float s0 = a.n_slots > 0 ? m[k] : 0.f, s1 = a.n_slots > 1 ? s[k] : 0.f;
+            opt_update(a.opt, w[k], s0, s1, g[k] * a.grad_scale);
+            m[k] = s0;
+            s[k] = s1;
+        }
+        *(float4*)(a.master + i) = *(float4*)&w[0];
+        *(float4*)(a.master + i + 4) = *(float4*)&w[4];
+        if (a.n_slots > 0) {
+            *(float4*)(a.slot0 + i) = *(float4*)&m[0];
+            *(float4*)(a.slot0 + i + 4) = *(float4*)&m[4];
+        }
+        if (a.n_slots > 1) {
+            *(float4*)(a.slot1 + i) = *(float4*)&s[0];
+            *(float4*)(a.slot1 + i + 4) = *(float4*)&s[4];
+        }
+        uint4 packed;
+        __nv_bfloat162* h = (__nv_bfloat162*)&packed;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(w[2 * k], w[2 * k + 1]);
+#pragma unroll
+        for (int r = 0; r < kMaxWorld; ++r)
+            if (r < W) *(uint4*)(pdst[r] + i) = packed;
+    }
+    // ---- 4. all slices landed everywhere ----------------------------------------------------------
+    if (W > 1) {
+        __threadfence_system();
+        __syncthreads();
+        __shared__ unsigned s_last;
+        if (threadIdx.x == 0) s_last = (atomicAdd(&a.ctl->done_blocks, 1u) == gridDim.x - 1u);
+        __syncthreads();
+        if (s_last) {
+            // every CTA has read the epoch by now (it counted itself done after reading it)
+            if (threadIdx.x == 0) {
+                a.ctl->done_blocks = 0;
+                a.ctl->epoch = epoch;
+            }
+            if (threadIdx.x < (unsigned)W && (int)threadIdx.x != me) {
+                st_release_sys(a.peer_flags[threadIdx.x] + kMaxWorld + me, epoch);
+                if (!wait_flag_ge(a.peer_flags[me] + kMaxWorld + threadIdx.x, epoch, a.limit_ns))
+                    set_status(a.ctl, kStTimeout, 2);
+            }
+        }
+    }
+}
+
+}  // namespace
+
+int launch_dense_rs_opt_ag(const DenseArgs& a, int grad_is_bf16, int nblocks, void* stream) {
+    if (grad_is_bf16)
+        dense_rs_opt_ag_kernel<__nv_bfloat16><<<nblocks, kThreads, 0, (cudaStream_t)stream>>>(a);
+    else
+        dense_rs_opt_ag_kernel<float><<<nblocks, kThreads, 0, (cudaStream_t)stream>>>(a);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace psb

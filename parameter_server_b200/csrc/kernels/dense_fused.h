@@ -1,0 +1,30 @@
+// Argument block of the fused dense push (reduce-scatter + optimizer + all-gather) kernel.
+#pragma once
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "optim.cuh"
+
+namespace psb {
+
+struct DenseArgs {
+    int world;
+    int rank;
+    unsigned long long limit_ns;
+    const void* peer_grads[kMaxWorld];       // every rank's full gradient buffer
+    __nv_bfloat16* peer_params[kMaxWorld];   // every rank's full bf16 parameter buffer
+    unsigned* peer_flags[kMaxWorld];         // every rank's flag block: [0..8) ready, [8..16) done
+    float* master;                           // fp32 master weights of this rank's slice
+    float* slot0;                            // optimizer moments of the slice
+    float* slot1;
+    int n_slots;
+    size_t shard_lo;                         // first element of this rank's slice
+    size_t shard_len;                        // elements in the slice (multiple of 8)
+    float grad_scale;                        // e.g. 1/world for a mean over data-parallel ranks
+    OptConfig opt;
+    KernelCtl* ctl;
+};
+
+int launch_dense_rs_opt_ag(const DenseArgs& a, int grad_is_bf16, int nblocks, void* stream);
+
+}  // namespace psb

@@ -1,0 +1,397 @@
+// bf16 GEMM for sm_100a on the 5th-generation tensor cores: tcgen05.mma issued by one elected
+// thread, operands staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle, no
+// multicast), fp32 accumulators in TMEM, read back with tcgen05.ld for a fused epilogue.
+//
+//   D[M,N] = epilogue( sum_k A(m,k) * B(n,k) )
+//
+// Each operand is described by a 2-D row-major tensor in global memory and a "major":
+//   K-major  : the tensor is [rows = M or N][cols = K]   (contraction index contiguous)
+//   MN-major : the tensor is [rows = K][cols = M or N]   (contraction index strided)
+// so that the three GEMMs of a linear layer y = x W^T run without any transposed copy:
+//   forward  y  = x  W^T   : A = x  (K-major),  B = W  (K-major)
+//   dgrad    dx = dy W     : A = dy (K-major),  B = W  (MN-major; W is [N_out][K_in] = [k][n])
+//   wgrad    dW = dy^T x   : A = dy (MN-major), B = x  (MN-major)
+// Epilogue (all optional): + bias[n], ReLU, multiply by (mask[m,n] > 0) (ReLU backward), add to the
+// existing fp32 output; output bf16 or fp32, row-major with leading dimension ldd.
+//
+// Not in the reference (it has no model code); this is the dense-MLP kernel of the DLRM and GPT
+// workloads and the compute half of the fused dense pull.
+//
+// Structure per CTA (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..5 = epilogue (each reads its own 32-lane quarter of TMEM). One 128 x BN tile per CTA,
+// BK = 64 (one 128-byte swizzle span), kStages-deep mbarrier ring. Every mbarrier wait is bounded;
+// on a time-out the CTA records an error, still frees its TMEM and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+
+#include "gemm_tcgen05.h"
+
+namespace psb {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long gtimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait; returns false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = gtimer();
+    unsigned spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 255u) == 0 && gtimer() - t0 > limit_ns) return false;
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor (version 1 = Blackwell), 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version
+    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BN>
+struct SmemLayout {
+    static constexpr int kABytes = BM * BK * 2;   // 16 KB
+    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = (BN == 256) ? 4 : 6;
+    static constexpr int kTileBytes = kStages * kStageBytes;
+    static constexpr int kBarBytes = 256;
+    static constexpr int kTotal = kTileBytes + kBarBytes + 1024;  // + alignment slack
+};
+
+// AMN / BMN: operand is MN-major. The box of an MN-major operand is [64 k-rows][64 mn-elements].
+template <int BN, bool AMN, bool BMN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const GemmEpilogue ep, int M, int N, int K, unsigned* err_flag, unsigned long long limit_ns) {
+    using L = SmemLayout<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full_bar = (uint64_t*)(smem + L::kTileBytes);
+    uint64_t* empty_bar = full_bar + L::kStages;
+    uint64_t* acc_bar = empty_bar + L::kStages;
+    uint32_t* tmem_slot = (uint32_t*)(acc_bar + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tile_m = blockIdx.y * BM;
+    const int tile_n = blockIdx.x * BN;
+    const int num_kt = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < L::kStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(acc_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)BN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *((volatile uint32_t*)tmem_slot);
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            for (int kt = 0; kt < num_kt; ++kt) {
+                const int s = kt % L::kStages;
+                const uint32_t ph = (uint32_t)(kt / L::kStages) & 1u;
+                if (!mbar_wait(&empty_bar[s], ph ^ 1u, limit_ns)) {
+                    atomicCAS(err_flag, 0u, 1u);
+                    break;
+                }
+                uint8_t* sa = smem + s * L::kStageBytes;
+                uint8_t* sb = sa + L::kABytes;
+                mbar_expect_tx(&full_bar[s], (uint32_t)L::kStageBytes);
+                const int k0 = kt * BK;
+                if (!AMN) {
+                    tma_load_2d(sa, &map_a, &full_bar[s], k0, tile_m);  // box [128 rows][64 k]
+                } else {
+                    tma_load_2d(sa, &map_a, &full_bar[s], tile_m, k0);               // box [64 k][64 m]
+                    tma_load_2d(sa + 64 * 128, &map_a, &full_bar[s], tile_m + 64, k0);
+                }
+                if (!BMN) {
+                    tma_load_2d(sb, &map_b, &full_bar[s], k0, tile_n);  // box [BN rows][64 k]
+                } else {
+#pragma unroll
+                    for (int j = 0; j < BN / 64; ++j)
+                        tma_load_2d(sb + j * 64 * 128, &map_b, &full_bar[s], tile_n + 64 * j, k0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((AMN ? 1u : 0u) << 15) |
+                                   ((BMN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            bool ok = true;
+            for (int kt = 0; kt < num_kt && ok; ++kt) {
+                const int s = kt % L::kStages;
+                const uint32_t ph = (uint32_t)(kt / L::kStages) & 1u;
+                if (!mbar_wait(&full_bar[s], ph, limit_ns)) {
+                    atomicCAS(err_flag, 0u, 2u);
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t sa = smem_u32(smem + s * L::kStageBytes);
+                const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // K-major: 8-row groups are 1024 B apart, a K step of 16 elements is 32 B inside the
+                    // swizzle span. MN-major: 64-element column blocks are one box (8192 B) apart,
+                    // 8-k-row groups 1024 B apart, a K step of 16 rows is 2048 B.
+                    const uint64_t da = AMN ? make_desc(sa + k * 2048, 8192, 1024) : make_desc(sa + k * 32, 16, 1024);
+                    const uint64_t db = BMN ? make_desc(sb + k * 2048, 8192, 1024) : make_desc(sb + k * 32, 16, 1024);
+                    umma_bf16(tmem_base, da, db, idesc, (kt | k) ? 1u : 0u);
+                }
+                umma_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
+            }
+            umma_commit(acc_bar);  // accumulator complete (also reached on error so the epilogue leaves)
+        }
+    } else {
+        // ------------------------------ epilogue ----------------------------------
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        const bool ok = mbar_wait(acc_bar, 0, limit_ns * 2);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (!ok) {
+            if (lane == 0) atomicCAS(err_flag, 0u, 3u);
+        } else if (num_kt > 0) {
+            const int row = tile_m + q * 32 + lane;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (tile_n + c0 >= N) break;  // warp-uniform
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                if (row < M) {
+                    const int col0 = tile_n + c0;
+                    float f[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                    if (ep.bias != nullptr) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < N) f[j] += ep.bias[col0 + j];
+                    }
+                    if (ep.relu) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) f[j] = fmaxf(f[j], 0.f);
+                    }
+                    const bool full = (col0 + 32 <= N);
+                    if (ep.mask != nullptr) {
+                        const __nv_bfloat16* mp = ep.mask + (size_t)row * ep.ldmask + col0;
+                        if (full && (ep.ldmask % 8 == 0)) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 raw = *(const uint4*)(mp + j);
+                                const __nv_bfloat16* h = (const __nv_bfloat16*)&raw;
+#pragma unroll
+                                for (int t = 0; t < 8; ++t)
+                                    if (!(__bfloat162float(h[t]) > 0.f)) f[j + t] = 0.f;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < N && !(__bfloat162float(mp[j]) > 0.f)) f[j] = 0.f;
+                        }
+                    }
+                    if (ep.out_f32 != nullptr) {
+                        float* op = ep.out_f32 + (size_t)row * ep.ldd + col0;
+                        if (full && (ep.ldd % 4 == 0)) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                float4 o = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                                if (ep.accumulate) {
+                                    float4 old = *(float4*)(op + j);
+                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                                }
+                                *(float4*)(op + j) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < N) op[j] = ep.accumulate ? op[j] + f[j] : f[j];
+                        }
+                    }
+                    if (ep.out_bf16 != nullptr) {
+                        __nv_bfloat16* op = ep.out_bf16 + (size_t)row * ep.ldd + col0;
+                        if (full && (ep.ldd % 8 == 0)) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 raw;
+                                __nv_bfloat162* h = (__nv_bfloat162*)&raw;
+                                h[0] = __floats2bfloat162_rn(f[j], f[j + 1]);
+                                h[1] = __floats2bfloat162_rn(f[j + 2], f[j + 3]);
+                                h[2] = __floats2bfloat162_rn(f[j + 4], f[j + 5]);
+                                h[3] = __floats2bfloat162_rn(f[j + 6], f[j + 7]);
+                                *(uint4*)(op + j) = raw;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < N) op[j] = __float2bfloat16_rn(f[j]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeFn)p;
+    });
+    return fn;
+}
+
+// 2-D bf16 row-major tensor [rows][cols] with leading dimension ld (elements); box [box_rows][64 cols].
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+    EncodeFn enc = get_encode();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <int BN, bool AMN, bool BMN>
+cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const GemmEpilogue& ep, int M, int N, int K,
+                           unsigned* err, unsigned long long limit_ns, cudaStream_t s) {
+    auto kern = gemm_bf16_tcgen05_kernel<BN, AMN, BMN>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::kTotal);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    kern<<<grid, kThreads, SmemLayout<BN>::kTotal, s>>>(ma, mb, ep, M, N, K, err, limit_ns);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+int gemm_bf16(const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep, int M, int N, int K, unsigned* err_flag,
+              double wait_limit_s, void* stream) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if ((A.ld % 8) || (B.ld % 8) || ((uintptr_t)A.ptr % 16) || ((uintptr_t)B.ptr % 16)) return -2;  // TMA: 16-byte rule
+    CUtensorMap ma, mb;
+    const int BN = 128;
+    // K-major: tensor [MN rows][K cols], box [tile rows][64]; MN-major: tensor [K rows][MN cols], box [64][64]
+    bool ok = A.mn_major ? make_map(&ma, A.ptr, (uint64_t)K, (uint64_t)M, (uint64_t)A.ld, 64)
+                         : make_map(&ma, A.ptr, (uint64_t)M, (uint64_t)K, (uint64_t)A.ld, BM);
+    ok = ok && (B.mn_major ? make_map(&mb, B.ptr, (uint64_t)K, (uint64_t)N, (uint64_t)B.ld, 64)
+                           : make_map(&mb, B.ptr, (uint64_t)N, (uint64_t)K, (uint64_t)B.ld, BN));
+    if (!ok) return -3;
+    const unsigned long long lim = (unsigned long long)(wait_limit_s * 1e9);
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (!A.mn_major && !B.mn_major) e = launch_variant<128, false, false>(ma, mb, ep, M, N, K, err_flag, lim, s);
+    else if (!A.mn_major && B.mn_major) e = launch_variant<128, false, true>(ma, mb, ep, M, N, K, err_flag, lim, s);
+    else if (A.mn_major && !B.mn_major) e = launch_variant<128, true, false>(ma, mb, ep, M, N, K, err_flag, lim, s);
+    else e = launch_variant<128, true, true>(ma, mb, ep, M, N, K, err_flag, lim, s);
+    return (int)e;
+}
+
+}  // namespace psb

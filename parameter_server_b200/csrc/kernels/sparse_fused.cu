@@ -68,7 +68,8 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
     const unsigned nblocks = gridDim.x;
     const unsigned tid = blockIdx.x * kThreads + threadIdx.x;
     const unsigned nthreads = nblocks * kThreads;
-    const unsigned par = a.epoch & 1u;
+    const unsigned epoch = *((volatile unsigned*)&a.ctl->epoch) + 1u;
+    const unsigned par = epoch & 1u;
     unsigned* cnt = a.counters + par * 16;
     unsigned* send_cnt = cnt + 4;
     unsigned* in_cnt = a.in_cnt + par * kMaxWorld;
@@ -138,10 +139,10 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
             const int o = threadIdx.x;
             a.peer[o].key_cnt[me] = min(send_cnt[o], C);
             __threadfence_system();
-            st_release_sys(&a.peer[o].key_flag[me], a.epoch);
+            st_release_sys(&a.peer[o].key_flag[me], epoch);
         }
         // ---- P3 (owner): wait for every source's keys
-        if (!wait_all_flags(mine.key_flag, a.epoch, a, W_KEYFLAG)) return;
+        if (!wait_all_flags(mine.key_flag, epoch, a, W_KEYFLAG)) return;
     }
     if (threadIdx.x == 0) {
         unsigned acc = 0;
@@ -216,8 +217,8 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
         __threadfence_system();
         if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P3C)) return;
         if (blockIdx.x == 0 && threadIdx.x < (unsigned)a.world && (int)threadIdx.x != me)
-            st_release_sys(&a.peer[threadIdx.x].row_flag[me], a.epoch);
-        if (!wait_all_flags(mine.row_flag, a.epoch, a, W_ROWFLAG)) return;
+            st_release_sys(&a.peer[threadIdx.x].row_flag[me], epoch);
+        if (!wait_all_flags(mine.row_flag, epoch, a, W_ROWFLAG)) return;
     } else {
         if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P3C)) return;
     }
@@ -259,15 +260,18 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
         }
     }
     if (blockIdx.x == 0 && threadIdx.x < 16) a.counters[(par ^ 1u) * 16 + threadIdx.x] = 0;
+    if (blockIdx.x == 0 && threadIdx.x == 0) a.ctl->epoch = epoch;
 }
 
 __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a) {
     const unsigned nblocks = gridDim.x;
     const unsigned tid = blockIdx.x * kThreads + threadIdx.x;
     const unsigned nthreads = nblocks * kThreads;
-    const unsigned* cnt = a.counters + a.plan_par * 16;
+    const unsigned epoch = *((volatile unsigned*)&a.ctl->epoch) + 1u;
+    const unsigned plan_par = *((volatile const unsigned*)&a.plan_ctl->epoch) & 1u;
+    const unsigned* cnt = a.counters + plan_par * 16;
     const unsigned* send_cnt = cnt + 4;
-    const unsigned* in_cnt = a.in_cnt + a.plan_par * kMaxWorld;
+    const unsigned* in_cnt = a.in_cnt + plan_par * kMaxWorld;
     const int me = a.rank;
     const unsigned C = a.C;
     const TableView& T = a.table;
@@ -299,7 +303,7 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
 
     if (a.world > 1) {
         // the owners must have consumed the previous push before their mailboxes are overwritten
-        if (!wait_all_flags(mine.push_ack, a.epoch - 1u, a, W_ACK)) return;
+        if (!wait_all_flags(mine.push_ack, epoch - 1u, a, W_ACK)) return;
         // ---- Q2: ship merged gradient rows to the owners
         if (threadIdx.x == 0) {
             unsigned acc = 0;
@@ -322,8 +326,8 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
         __threadfence_system();
         if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_Q2)) return;
         if (blockIdx.x == 0 && threadIdx.x < (unsigned)a.world && (int)threadIdx.x != me)
-            st_release_sys(&a.peer[threadIdx.x].grad_flag[me], a.epoch);
-        if (!wait_all_flags(mine.grad_flag, a.epoch, a, W_GRADFLAG)) return;
+            st_release_sys(&a.peer[threadIdx.x].grad_flag[me], epoch);
+        if (!wait_all_flags(mine.grad_flag, epoch, a, W_GRADFLAG)) return;
         __syncthreads();
     }
 
@@ -444,9 +448,11 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
         if (s_last) {
             if (threadIdx.x == 0) a.ctl->done_blocks = 0;
             if (threadIdx.x < (unsigned)a.world && (int)threadIdx.x != me)
-                st_release_sys(&a.peer[threadIdx.x].push_ack[me], a.epoch);
+                st_release_sys(&a.peer[threadIdx.x].push_ack[me], epoch);
         }
     }
+    // every CTA read the epoch before the first grid barrier, so CTA 0 may publish it when it leaves
+    if (blockIdx.x == 0 && threadIdx.x == 0) a.ctl->epoch = epoch;
 }
 
 int fused_max_blocks(int device, int* pull_blocks, int* push_blocks) {

@@ -35,8 +35,6 @@ struct FusedArgs {
     unsigned N;  // capacity of one call, in key positions
     unsigned dim;
     unsigned flags;
-    unsigned epoch;      // call number of this kernel family (same on every rank)
-    unsigned plan_par;   // parity of the pull epoch whose plan a push reuses
     unsigned long long limit_ns;
     PeerBufs peer[kMaxWorld];  // peer[rank] is this GPU's own buffer
     // ---- local scratch -------------------------------------------------------------------
@@ -52,7 +50,8 @@ struct FusedArgs {
     unsigned* new_list;    // [world*C] owner side: slots whose rows were attached by this call
     unsigned* counters;    // [2][16] per epoch parity: 0 n_uniq, 1 n_new, 4.. send_cnt[world]
     unsigned* in_cnt;      // [2][kMaxWorld] per epoch parity: keys received from each source rank
-    KernelCtl* ctl;
+    KernelCtl* ctl;       // control block of this kernel family (holds the call epoch)
+    const KernelCtl* plan_ctl;  // push: control block of the pull family (parity of the plan)
     const int* shard_owner;  // [n_shards] owning rank of every global shard
     int n_shards;
     TableView table;

@@ -192,9 +192,9 @@ Status SparseEngine::pull(const long long* keys, uint32_t n, uint32_t bag_size, 
     FusedArgs a;
     fill_common(a);
     a.flags = flags;
-    a.epoch = ++pull_epoch_;
-    a.plan_par = a.epoch & 1u;
+    ++pull_epoch_;
     a.ctl = ctl_pull_;
+    a.plan_ctl = ctl_pull_;
     a.keys = keys;
     a.n = n;
     a.bag_size = bag_size;
@@ -224,9 +224,9 @@ Status SparseEngine::push(const float* grads, const OptConfig& opt, unsigned fla
     FusedArgs a;
     fill_common(a);
     a.flags = (plan_flags_ & FUSED_MEAN) | (flags & FUSED_SYNC_PUSH);
-    a.epoch = ++push_epoch_;
-    a.plan_par = pull_epoch_ & 1u;
+    ++push_epoch_;
     a.ctl = ctl_push_;
+    a.plan_ctl = ctl_pull_;
     a.keys = plan_keys_;
     a.n = plan_n_;
     a.bag_size = plan_bag_;
@@ -279,8 +279,10 @@ Status SparseEngine::reset(void* stream) {
 uint32_t SparseEngine::last_unique(void* stream) {
     cudaSetDevice(table_->device());
     cudaStreamSynchronize((cudaStream_t)stream);
+    KernelCtl h;
+    cudaMemcpy(&h, ctl_pull_, sizeof(h), cudaMemcpyDeviceToHost);
     unsigned v = 0;
-    cudaMemcpy(&v, counters_ + (pull_epoch_ & 1u) * 16, 4, cudaMemcpyDeviceToHost);
+    cudaMemcpy(&v, counters_ + (h.epoch & 1u) * 16, 4, cudaMemcpyDeviceToHost);
     return v;
 }
 

@@ -1,0 +1,78 @@
+"""bf16 GEMM on tcgen05 / TMEM / TMA (``csrc/kernels/gemm_tcgen05.cu``) and the linear-layer triple
+built on it (forward, dgrad, wgrad) without transposed copies."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .._lib import C
+
+_err_flags = {}
+
+
+def _err_flag(device) -> torch.Tensor:
+    key = torch.device(device).index or 0
+    if key not in _err_flags:
+        _err_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _err_flags[key]
+
+
+def check_gemm_errors(device=None) -> None:
+    """Synchronise and raise if a bounded wait inside a GEMM kernel ran out."""
+    for key, flag in _err_flags.items():
+        v = int(flag.item())
+        if v:
+            flag.zero_()
+            raise RuntimeError(f"tcgen05 GEMM on cuda:{key}: bounded wait ran out (site {v})")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, bias: Optional[torch.Tensor] = None,
+         relu: bool = False, mask: Optional[torch.Tensor] = None, accumulate: bool = False,
+         M: Optional[int] = None, N: Optional[int] = None, K: Optional[int] = None) -> torch.Tensor:
+    """``out[M,N] = epilogue(sum_k A(m,k) B(n,k))``.
+
+    ``a`` is ``[M,K]`` (or ``[K,M]`` with ``a_mn``), ``b`` is ``[N,K]`` (or ``[K,N]`` with ``b_mn``);
+    both bf16, row-major (last stride 1, leading dimension a multiple of 8).
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.is_cuda and b.is_cuda
+    assert a.stride(-1) == 1 and b.stride(-1) == 1
+    if M is None:
+        M = a.shape[1] if a_mn else a.shape[0]
+    if K is None:
+        K = a.shape[0] if a_mn else a.shape[1]
+    if N is None:
+        N = b.shape[1] if b_mn else b.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    assert out.stride(-1) == 1
+    o16 = out if out.dtype == torch.bfloat16 else None
+    o32 = out if out.dtype == torch.float32 else None
+    assert o16 is not None or o32 is not None
+    rc = C.gemm_bf16(a.data_ptr(), a.stride(0), a_mn, b.data_ptr(), b.stride(0), b_mn, M, N, K,
+                     _ptr(o16), _ptr(o32), out.stride(0), _ptr(bias), relu, _ptr(mask),
+                     mask.stride(0) if mask is not None else 0, accumulate, _err_flag(a.device).data_ptr(), 2.0,
+                     torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"gemm_bf16 failed with code {rc}")
+    return out
+
+
+def linear_fwd(x, w, bias=None, relu=False, out=None):
+    """y = act(x @ w.T + bias); x [M,K], w [N,K]."""
+    return gemm(x, w, bias=bias, relu=relu, out=out)
+
+
+def linear_dgrad(dy, w, mask=None, out=None):
+    """dx = (dy @ w) * (mask > 0); dy [M,N], w [N,K] -> dx [M,K]."""
+    return gemm(dy, w, b_mn=True, mask=mask, out=out)
+
+
+def linear_wgrad(dy, x, out=None, accumulate=False):
+    """dw = dy.T @ x; dy [M,N], x [M,K] -> dw [N,K] (fp32 when ``out`` is fp32)."""
+    return gemm(dy, x, a_mn=True, b_mn=True, out=out, out_dtype=torch.float32, accumulate=accumulate)

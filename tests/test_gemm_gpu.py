@@ -1,0 +1,51 @@
+"""tcgen05 GEMM against a plain fp32 PyTorch reference of the same contraction."""
+import pytest
+import torch
+
+from parameter_server_b200.ops import gemm as G
+
+pytestmark = pytest.mark.gpu
+
+
+def ref(a, b, a_mn, b_mn):
+    A = a.float().t() if a_mn else a.float()
+    Bm = b.float().t() if b_mn else b.float()
+    return A @ Bm.t()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 384, 512), (1000, 200, 136), (8192, 1024, 480)])
+def test_gemm_layouts(M, N, K, a_mn, b_mn):
+    torch.manual_seed(M + N + K)
+    pad = lambda v: (v + 7) // 8 * 8
+    a = torch.randn((K, pad(M)) if a_mn else (M, pad(K)), device="cuda").bfloat16()
+    b = torch.randn((K, pad(N)) if b_mn else (N, pad(K)), device="cuda").bfloat16()
+    av = a[:, :M] if a_mn else a[:, :K]
+    bv = b[:, :N] if b_mn else b[:, :K]
+    out = G.gemm(av, bv, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32, M=M, N=N, K=K)
+    G.check_gemm_errors()
+    r = ref(av, bv, a_mn, b_mn)
+    err = (out - r).abs().max().item()
+    assert err <= 1e-2 * (K ** 0.5), f"max abs err {err}"
+    assert torch.allclose(out, r, rtol=2e-2, atol=2e-2 * (K ** 0.5))
+
+
+def test_epilogue_bias_relu_mask_accumulate():
+    torch.manual_seed(0)
+    M, N, K = 512, 256, 192
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    bias = torch.randn(N, device="cuda")
+    y = G.linear_fwd(x, w, bias=bias, relu=True)
+    r = torch.relu(x.float() @ w.float().t() + bias)
+    assert torch.allclose(y.float(), r, rtol=2e-2, atol=2e-2)
+    dy = torch.randn(M, N, device="cuda").bfloat16()
+    mask = torch.randn(M, K, device="cuda").bfloat16()
+    dx = G.linear_dgrad(dy, w, mask=mask)
+    rdx = (dy.float() @ w.float()) * (mask.float() > 0)
+    assert torch.allclose(dx.float(), rdx, rtol=2e-2, atol=5e-2)
+    dw = torch.ones(N, K, device="cuda")
+    G.linear_wgrad(dy, x, out=dw, accumulate=True)
+    rdw = dy.float().t() @ x.float() + 1.0
+    assert torch.allclose(dw, rdw, rtol=2e-2, atol=0.5)
+    G.check_gemm_errors()

@@ -78,7 +78,7 @@ def test_pooling_and_mean_backward():
     for mean in (False, True):
         a = g.pull(keys.cuda(), bag_size=4, mean=mean)
         b = c.pull(keys, bag_size=4, mean=mean)
-        assert torch.allclose(a.cpu(), b, rtol=1e-6, atol=1e-8)
+        assert torch.allclose(a.cpu(), b, rtol=1e-4, atol=1e-6)  # duplicate sums use atomics
         grads = torch.randn(4096, 16) * 1e-2
         g.push(grads.cuda())
         c.push(grads)
