@@ -43,7 +43,7 @@ void bind_dense(py::module_& m) {
     m.def("gemm_bf16",
           [](uintptr_t a, int64_t lda, bool a_mn, uintptr_t b, int64_t ldb, bool b_mn, int M, int N, int K,
              uintptr_t out_bf16, uintptr_t out_f32, int64_t ldd, uintptr_t bias, bool relu, uintptr_t mask,
-             int64_t ldmask, bool accumulate, uintptr_t err_flag, double wait_limit_s, uintptr_t stream) {
+             int64_t ldmask, bool accumulate, uintptr_t bias_bf16, int split_k, uintptr_t err_flag, double wait_limit_s, uintptr_t stream) {
               GemmOperand A{ptr<const void>(a), lda, a_mn}, B{ptr<const void>(b), ldb, b_mn};
               GemmEpilogue ep;
               ep.out_bf16 = ptr<__nv_bfloat16>(out_bf16);
@@ -54,12 +54,14 @@ void bind_dense(py::module_& m) {
               ep.mask = ptr<const __nv_bfloat16>(mask);
               ep.ldmask = ldmask;
               ep.accumulate = accumulate ? 1 : 0;
+              ep.bias_bf16 = ptr<const __nv_bfloat16>(bias_bf16);
+              ep.split_k = split_k;
               return gemm_bf16(A, B, ep, M, N, K, ptr<unsigned>(err_flag), wait_limit_s, (void*)stream);
           },
           py::arg("a"), py::arg("lda"), py::arg("a_mn"), py::arg("b"), py::arg("ldb"), py::arg("b_mn"), py::arg("M"),
           py::arg("N"), py::arg("K"), py::arg("out_bf16") = 0, py::arg("out_f32") = 0, py::arg("ldd") = 0,
           py::arg("bias") = 0, py::arg("relu") = false, py::arg("mask") = 0, py::arg("ldmask") = 0,
-          py::arg("accumulate") = false, py::arg("err_flag") = 0, py::arg("wait_limit_s") = 2.0, py::arg("stream") = 0);
+          py::arg("accumulate") = false, py::arg("bias_bf16") = 0, py::arg("split_k") = 1, py::arg("err_flag") = 0, py::arg("wait_limit_s") = 2.0, py::arg("stream") = 0);
 
     bind_model_kernels(m);
 }

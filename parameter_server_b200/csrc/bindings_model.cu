@@ -19,7 +19,7 @@ void bind_model_kernels(py::module_& m) {
     m.def("bce_head", [](uintptr_t h, int64_t ldh, uintptr_t w, uintptr_t bias, uintptr_t y, int B, int K, float inv_batch,
                          uintptr_t loss_sum, uintptr_t logits, uintptr_t dz_prev, int64_t lddz, uintptr_t dw, uintptr_t db,
                          uintptr_t s) {
-        return bce_head((const void*)h, ldh, (const void*)w, (const float*)bias, (const float*)y, B, K, inv_batch,
+        return bce_head((const void*)h, ldh, (const void*)w, (const void*)bias, (const float*)y, B, K, inv_batch,
                         (float*)loss_sum, (float*)logits, (void*)dz_prev, lddz, (float*)dw, (float*)db, (void*)s);
     });
     m.def("bias_grad", [](uintptr_t dz, int64_t ld, int M, int N, uintptr_t db, uintptr_t s) {

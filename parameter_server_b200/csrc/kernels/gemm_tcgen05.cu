@@ -147,7 +147,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const int lane = threadIdx.x & 31;
     const int tile_m = blockIdx.y * BM;
     const int tile_n = blockIdx.x * BN;
-    const int num_kt = (K + BK - 1) / BK;
+    const int total_kt = (K + BK - 1) / BK;
+    const int kt_per = (total_kt + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int kt_begin = (int)blockIdx.z * kt_per;
+    const int num_kt = max(0, min(total_kt - kt_begin, kt_per));
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < L::kStages; ++s) {
@@ -181,7 +184,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 uint8_t* sa = smem + s * L::kStageBytes;
                 uint8_t* sb = sa + L::kABytes;
                 mbar_expect_tx(&full_bar[s], (uint32_t)L::kStageBytes);
-                const int k0 = kt * BK;
+                const int k0 = (kt_begin + kt) * BK;
                 if (!AMN) {
                     tma_load_2d(sa, &map_a, &full_bar[s], k0, tile_m);  // box [128 rows][64 k]
                 } else {
@@ -251,6 +254,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         for (int j = 0; j < 32; ++j)
                             if (col0 + j < N) f[j] += ep.bias[col0 + j];
                     }
+                    if (ep.bias_bf16 != nullptr) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < N) f[j] += __bfloat162float(ep.bias_bf16[col0 + j]);
+                    }
                     if (ep.relu) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) f[j] = fmaxf(f[j], 0.f);
@@ -275,7 +283,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     }
                     if (ep.out_f32 != nullptr) {
                         float* op = ep.out_f32 + (size_t)row * ep.ldd + col0;
-                        if (full && (ep.ldd % 4 == 0)) {
+                        if (ep.split_k > 1) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < N) atomicAdd(op + j, f[j]);
+                        } else if (full && (ep.ldd % 4 == 0)) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 4) {
                                 float4 o = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
@@ -365,7 +377,7 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const G
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, ep.split_k > 1 ? ep.split_k : 1);
     kern<<<grid, kThreads, SmemLayout<BN>::kTotal, s>>>(ma, mb, ep, M, N, K, err, limit_ns);
     return cudaGetLastError();
 }

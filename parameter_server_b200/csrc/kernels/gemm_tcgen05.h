@@ -17,10 +17,13 @@ struct GemmEpilogue {
     float* out_f32 = nullptr;
     int64_t ldd = 0;                    // leading dimension of the output(s)
     const float* bias = nullptr;        // [N], added before the activation
+    const __nv_bfloat16* bias_bf16 = nullptr;  // same, stored as bf16 (parameters of a dense table)
     int relu = 0;
     const __nv_bfloat16* mask = nullptr;  // [M][N]: result is zeroed where mask <= 0 (ReLU backward)
     int64_t ldmask = 0;
     int accumulate = 0;                 // fp32 output: add to what is there
+    int split_k = 1;                    // >1: K is split over gridDim.z and partial sums are added with
+                                        // red.global.add.f32 into a zero-initialised fp32 output
 };
 
 // D = epilogue(A * B^T-style contraction over K). err_flag: device word, set non-zero when a bounded wait

@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(D) interaction_bwd_kernel(const __nv_bfloat16*
 // loss_sum += sum_b bce(z_b, y_b) * inv_batch;  dz_prev[b][k] = dlogit_b * w[k] * (h > 0);
 // dw[k] += sum_b dlogit_b * h[b][k];  db += sum_b dlogit_b, with dlogit_b = (sigmoid(z_b) - y_b) * inv_batch.
 __global__ void __launch_bounds__(256) bce_head_kernel(const __nv_bfloat16* __restrict__ h, int64_t ldh,
-                                                       const __nv_bfloat16* __restrict__ w, const float* __restrict__ bias,
+                                                       const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ bias,
                                                        const float* __restrict__ y, int B, int K, float inv_batch,
                                                        float* __restrict__ loss_sum, float* __restrict__ logits,
                                                        __nv_bfloat16* __restrict__ dz_prev, int64_t lddz,
@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(256) bce_head_kernel(const __nv_bfloat16* __re
     if (threadIdx.x == 0) { s_loss = 0.f; s_db = 0.f; }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    const float b0 = bias ? bias[0] : 0.f;
+    const float b0 = bias ? __bfloat162float(bias[0]) : 0.f;
     for (int b = blockIdx.x * nwarps + warp; b < B; b += gridDim.x * nwarps) {
         const __nv_bfloat16* hr = h + (size_t)b * ldh;
         float acc = 0.f;
@@ -205,11 +205,11 @@ int interaction_bwd(const void* dout, int64_t ldo, const void* bottom, int64_t l
     return (int)cudaGetLastError();
 }
 
-int bce_head(const void* h, int64_t ldh, const void* w, const float* bias, const float* y, int B, int K, float inv_batch,
+int bce_head(const void* h, int64_t ldh, const void* w, const void* bias, const float* y, int B, int K, float inv_batch,
              float* loss_sum, float* logits, void* dz_prev, int64_t lddz, float* dw, float* db, void* stream) {
     const int grid = 148 * 2;
     bce_head_kernel<<<grid, 256, K * sizeof(float), (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)w, bias, y, B, K, inv_batch, loss_sum, logits,
+        (const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, y, B, K, inv_batch, loss_sum, logits,
         (__nv_bfloat16*)dz_prev, lddz, dw, db);
     return (int)cudaGetLastError();
 }

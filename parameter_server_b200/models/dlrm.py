@@ -1,0 +1,267 @@
+"""DLRM-style CTR model trained against the parameter server.
+
+Embeddings live in a :class:`SparseTable` (fused pull in the forward pass, fused push of the row
+gradients in the backward pass); the MLP weights live in a :class:`DenseTable` (fused
+reduce-scatter + optimizer + all-gather). The dense math is hand-written sm_100a code: the tcgen05
+GEMM for every linear layer (forward, dgrad with the ReLU mask in the epilogue, split-K wgrad), the
+pairwise-dot interaction and the output layer fused with sigmoid + BCE. The forward and backward
+passes are written out explicitly (no autograd graph), with all activations preallocated, so a
+step is a fixed sequence of kernel launches.
+
+The reference ships no model code; this is the consumer that its sparse + dense operators are built
+for (config 3 of the benchmark: 13 dense features, 26 sparse fields, embedding dim 128, bottom MLP
+13-512-256-128, 27x128 pairwise-dot interaction, top MLP 1024-1024-512-256-1, BCE loss).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .._lib import C
+from ..ops import gemm as G
+from ..ops.dense import DenseTable
+from ..ops.sparse import SparseTable, _stream
+
+
+@dataclass
+class DLRMConfig:
+    num_dense: int = 13
+    num_sparse: int = 26
+    emb_dim: int = 128
+    bottom: Sequence[int] = (512, 256, 128)
+    top: Sequence[int] = (1024, 1024, 512, 256)
+    vocab_min: float = 1e3
+    vocab_max: float = 4e7
+    zipf_s: float = 1.1
+    label_rate: float = 0.03
+    sparse_optimizer: str = "adagrad"
+    sparse_opt_kwargs: dict = field(default_factory=lambda: dict(lr=0.05, init_accumulator=0.1))
+    dense_optimizer: str = "adamw"
+    dense_opt_kwargs: dict = field(default_factory=lambda: dict(lr=1e-3, weight_decay=0.0))
+
+    def vocab_sizes(self) -> List[int]:
+        return [int(round(v)) for v in np.logspace(np.log10(self.vocab_min), np.log10(self.vocab_max), self.num_sparse)]
+
+
+def _pad8(v: int) -> int:
+    return (v + 7) // 8 * 8
+
+
+def field_keys(field_ids: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """Globally unique int64 key of (field, id): the field index in the bits above 2^40."""
+    return (field_ids.to(torch.int64) << 40) | ids.to(torch.int64)
+
+
+class SyntheticCTR:
+    """Synthetic click data of the benchmark shape: log-normal dense features, per-field Zipf keys,
+    Bernoulli labels. Batches are generated on the host into pinned memory (the input pipeline of a
+    real job ends there), ``pool`` of them are kept and cycled."""
+
+    def __init__(self, cfg: DLRMConfig, batch: int, pool: int = 8, seed: int = 0, pin: bool = True):
+        rng = np.random.default_rng(seed)
+        vocab = np.array(cfg.vocab_sizes(), dtype=np.int64)
+        self.batches = []
+        fid = np.arange(cfg.num_sparse, dtype=np.int64)[None, :] << 40
+        for _ in range(pool):
+            dense = rng.lognormal(0.0, 1.0, size=(batch, cfg.num_dense)).astype(np.float32)
+            z = rng.zipf(cfg.zipf_s, size=(batch, cfg.num_sparse)).astype(np.int64)
+            ids = (z - 1) % vocab[None, :]
+            keys = fid | ids
+            labels = (rng.random(batch) < cfg.label_rate).astype(np.float32)
+            t = (torch.from_numpy(dense), torch.from_numpy(keys), torch.from_numpy(labels))
+            if pin and torch.cuda.is_available():
+                t = tuple(x.pin_memory() for x in t)
+            self.batches.append(t)
+        self.i = 0
+
+    def next(self):
+        b = self.batches[self.i % len(self.batches)]
+        self.i += 1
+        return b
+
+    def bytes_per_batch(self) -> int:
+        return sum(x.numel() * x.element_size() for x in self.batches[0])
+
+
+class DLRM:
+    """One rank's replica of the model; ``train_step`` is collective over the ranks of ``group``."""
+
+    def __init__(self, cfg: DLRMConfig, batch: int, *, table_capacity: int = 1 << 22, device=None, group=None,
+                 seed: int = 0, wgrad_split_k: int = 4, sparse_kwargs: Optional[dict] = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("DLRM runs on the sm_100a kernels and needs a CUDA device")
+        self.cfg = cfg
+        self.B = batch
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.group = group
+        D, F = cfg.emb_dim, cfg.num_sparse
+        assert cfg.bottom[-1] == D, "bottom MLP must end at the embedding width"
+        self.split_k = wgrad_split_k
+        self.sparse = SparseTable(D, cfg.sparse_optimizer, cfg.sparse_opt_kwargs, capacity=table_capacity,
+                                  max_keys=batch * F, device=self.device, group=group, seed=seed,
+                                  **(sparse_kwargs or {}))
+        # ---- dense parameters ------------------------------------------------------------------
+        self.k_in = _pad8(cfg.num_dense)
+        n_inter = D + (F + 1) * F // 2
+        self.k_top = _pad8(n_inter)
+        self.n_inter = n_inter
+        bdims = [self.k_in] + list(cfg.bottom)
+        tdims = [self.k_top] + list(cfg.top)
+        shapes = {}
+        for i in range(len(bdims) - 1):
+            shapes[f"bot.w{i}"] = (bdims[i + 1], bdims[i])
+            shapes[f"bot.b{i}"] = (bdims[i + 1],)
+        for i in range(len(tdims) - 1):
+            shapes[f"top.w{i}"] = (tdims[i + 1], tdims[i])
+            shapes[f"top.b{i}"] = (tdims[i + 1],)
+        shapes["head.w"] = (tdims[-1],)
+        shapes["head.b"] = (1,)
+        self.dense = DenseTable(shapes, cfg.dense_optimizer, cfg.dense_opt_kwargs, grad_dtype=torch.float32,
+                                device=self.device, group=group)
+        gen = torch.Generator().manual_seed(seed + 1)
+        init = {}
+        for name, shape in shapes.items():
+            if ".w" in name and len(shape) == 2:
+                fan_in = shape[1]
+                w = torch.randn(shape, generator=gen) * (2.0 / fan_in) ** 0.5
+                if name == "bot.w0":
+                    w[:, cfg.num_dense:] = 0
+                if name == "top.w0":
+                    w[:, n_inter:] = 0
+                init[name] = w
+            elif name == "head.w":
+                init[name] = torch.randn(shape, generator=gen) * (1.0 / shape[0]) ** 0.5
+            else:
+                init[name] = torch.zeros(shape)
+        self.dense.load(init)
+        self.bdims, self.tdims = bdims, tdims
+        # ---- preallocated activations --------------------------------------------------------------
+        dev, bf = self.device, torch.bfloat16
+        B = batch
+        self.d_dense = torch.empty((B, cfg.num_dense), dtype=torch.float32, device=dev)
+        self.d_keys = torch.empty((B, F), dtype=torch.int64, device=dev)
+        self.d_labels = torch.empty((B,), dtype=torch.float32, device=dev)
+        self.x16 = torch.empty((B, self.k_in), dtype=bf, device=dev)
+        self.bot_act = [torch.empty((B, n), dtype=bf, device=dev) for n in cfg.bottom]
+        self.emb = torch.empty((B * F, D), dtype=torch.float32, device=dev)
+        self.inter = torch.empty((B, self.k_top), dtype=bf, device=dev)
+        self.top_act = [torch.empty((B, n), dtype=bf, device=dev) for n in cfg.top]
+        self.top_dz = [torch.empty((B, n), dtype=bf, device=dev) for n in cfg.top]
+        self.d_inter = torch.empty((B, self.k_top), dtype=bf, device=dev)
+        self.bot_dz = [torch.empty((B, n), dtype=bf, device=dev) for n in cfg.bottom]
+        self.d_emb = torch.empty((B * F, D), dtype=torch.float32, device=dev)
+        self.loss = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.h_loss = torch.zeros(1, dtype=torch.float32).pin_memory()
+        self.launches_per_step = 0
+
+    # ------------------------------------------------------------------------------------------
+    def load_batch(self, dense: torch.Tensor, keys: torch.Tensor, labels: torch.Tensor) -> None:
+        """Host (pinned) -> device copies of one batch on the current stream."""
+        self.d_dense.copy_(dense, non_blocking=True)
+        self.d_keys.copy_(keys, non_blocking=True)
+        self.d_labels.copy_(labels, non_blocking=True)
+
+    def forward_backward(self) -> torch.Tensor:
+        """One training step on the batch already in the device input buffers. Returns the device
+        loss tensor (mean BCE over this rank's batch)."""
+        cfg, B, D, F = self.cfg, self.B, self.cfg.emb_dim, self.cfg.num_sparse
+        P, Gd = self.dense.params, self.dense.grads
+        s = _stream()
+        n_launch = 0
+
+        def chk(rc):
+            if rc != 0:
+                raise RuntimeError(f"kernel launch failed: {rc}")
+
+        # ---------------- forward ----------------
+        self.dense.zero_grads()  # torch fill kernels (not counted as own launches)
+        self.loss.zero_()
+        chk(C.cast_pad(self.d_dense.data_ptr(), B, cfg.num_dense, self.x16.data_ptr(), self.k_in, s)); n_launch += 1
+        a = self.x16
+        for i, out in enumerate(self.bot_act):
+            G.gemm(a, P[f"bot.w{i}"], bias=P[f"bot.b{i}"], relu=True, out=out); n_launch += 1
+            a = out
+        self.sparse.pull(self.d_keys, out=self.emb); n_launch += 1
+        chk(C.interaction_fwd(self.bot_act[-1].data_ptr(), D, self.emb.data_ptr(), F, D, self.inter.data_ptr(),
+                              self.k_top, B, s)); n_launch += 1
+        a = self.inter
+        for i, out in enumerate(self.top_act):
+            G.gemm(a, P[f"top.w{i}"], bias=P[f"top.b{i}"], relu=True, out=out); n_launch += 1
+            a = out
+        # ---------------- head: logits + loss + first backward step ----------------
+        last = len(self.top_act) - 1
+        chk(C.bce_head(self.top_act[last].data_ptr(), self.tdims[-1], P["head.w"].data_ptr(), P["head.b"].data_ptr(),
+                       self.d_labels.data_ptr(), B, self.tdims[-1], 1.0 / B, self.loss.data_ptr(), 0,
+                       self.top_dz[last].data_ptr(), self.tdims[-1], Gd["head.w"].data_ptr(), Gd["head.b"].data_ptr(), s))
+        n_launch += 1
+        # ---------------- backward: top MLP ----------------
+        for i in range(last, -1, -1):
+            dz = self.top_dz[i]
+            x_in = self.top_act[i - 1] if i > 0 else self.inter
+            G.linear_wgrad(dz, x_in, out=Gd[f"top.w{i}"], split_k=self.split_k); n_launch += 1
+            chk(C.bias_grad(dz.data_ptr(), dz.stride(0), B, dz.shape[1], Gd[f"top.b{i}"].data_ptr(), s)); n_launch += 1
+            if i > 0:
+                G.linear_dgrad(dz, P[f"top.w{i}"], mask=self.top_act[i - 1], out=self.top_dz[i - 1])
+            else:
+                G.linear_dgrad(dz, P["top.w0"], out=self.d_inter)
+            n_launch += 1
+        # ---------------- backward: interaction + sparse push ----------------
+        nb = len(self.bot_act) - 1
+        chk(C.interaction_bwd(self.d_inter.data_ptr(), self.k_top, self.bot_act[nb].data_ptr(), D, self.emb.data_ptr(),
+                              F, D, self.bot_dz[nb].data_ptr(), D, self.d_emb.data_ptr(), B, True, s)); n_launch += 1
+        self.sparse.push(self.d_emb); n_launch += 1
+        # ---------------- backward: bottom MLP ----------------
+        for i in range(nb, -1, -1):
+            dz = self.bot_dz[i]
+            x_in = self.bot_act[i - 1] if i > 0 else self.x16
+            G.linear_wgrad(dz, x_in, out=Gd[f"bot.w{i}"], split_k=self.split_k); n_launch += 1
+            chk(C.bias_grad(dz.data_ptr(), dz.stride(0), B, dz.shape[1], Gd[f"bot.b{i}"].data_ptr(), s)); n_launch += 1
+            if i > 0:
+                G.linear_dgrad(dz, P[f"bot.w{i}"], mask=self.bot_act[i - 1], out=self.bot_dz[i - 1]); n_launch += 1
+        # ---------------- dense push (reduce-scatter + optimizer + all-gather) ----------------
+        self.dense.push(); n_launch += 1
+        self.launches_per_step = n_launch
+        return self.loss
+
+    def train_step(self, dense: torch.Tensor, keys: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+        """Public API: copy one pinned host batch in, run the step, return the device loss."""
+        self.load_batch(dense, keys, labels)
+        return self.forward_backward()
+
+    def read_loss(self) -> float:
+        """Device -> host read of the last step's loss (synchronises the stream)."""
+        self.h_loss.copy_(self.loss, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return float(self.h_loss.item())
+
+    def check(self) -> None:
+        self.sparse.check()
+        self.dense.check()
+        G.check_gemm_errors()
+
+    # ------------------------------------------------------------------------------------------
+    def reference_loss(self) -> float:
+        """Loss of the current device batch computed with plain fp32 PyTorch ops on the current
+        parameters (read-only pull); used by the tests."""
+        cfg, B, D, F = self.cfg, self.B, self.cfg.emb_dim, self.cfg.num_sparse
+        P = {k: v.float() for k, v in self.dense.params.items()}
+        x = torch.zeros((B, self.k_in), device=self.device)
+        x[:, :cfg.num_dense] = self.d_dense
+        x = x.bfloat16().float()
+        for i in range(len(cfg.bottom)):
+            x = torch.relu(x @ P[f"bot.w{i}"].t() + P[f"bot.b{i}"]).bfloat16().float()
+        emb = self.sparse.pull(self.d_keys, insert=False, for_push=False).view(B, F, D)
+        T = torch.cat([x[:, None, :], emb], dim=1)
+        Z = torch.bmm(T, T.transpose(1, 2))
+        ii, jj = torch.tril_indices(F + 1, F + 1, offset=-1)
+        inter = torch.cat([x, Z[:, ii, jj]], dim=1)
+        h = torch.zeros((B, self.k_top), device=self.device)
+        h[:, :inter.shape[1]] = inter
+        h = h.bfloat16().float()
+        for i in range(len(cfg.top)):
+            h = torch.relu(h @ P[f"top.w{i}"].t() + P[f"top.b{i}"]).bfloat16().float()
+        z = h @ P["head.w"] + P["head.b"]
+        return float(torch.nn.functional.binary_cross_entropy_with_logits(z, self.d_labels).item())

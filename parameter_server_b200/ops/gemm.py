@@ -33,7 +33,7 @@ def _ptr(t: Optional[torch.Tensor]) -> int:
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, bias: Optional[torch.Tensor] = None,
-         relu: bool = False, mask: Optional[torch.Tensor] = None, accumulate: bool = False,
+         relu: bool = False, mask: Optional[torch.Tensor] = None, accumulate: bool = False, split_k: int = 1,
          M: Optional[int] = None, N: Optional[int] = None, K: Optional[int] = None) -> torch.Tensor:
     """``out[M,N] = epilogue(sum_k A(m,k) B(n,k))``.
 
@@ -54,9 +54,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     o16 = out if out.dtype == torch.bfloat16 else None
     o32 = out if out.dtype == torch.float32 else None
     assert o16 is not None or o32 is not None
+    b32 = bias if (bias is not None and bias.dtype == torch.float32) else None
+    b16 = bias if (bias is not None and bias.dtype == torch.bfloat16) else None
+    if split_k > 1:
+        assert o32 is not None and o16 is None, "split-K accumulates into a zero-initialised fp32 output"
     rc = C.gemm_bf16(a.data_ptr(), a.stride(0), a_mn, b.data_ptr(), b.stride(0), b_mn, M, N, K,
-                     _ptr(o16), _ptr(o32), out.stride(0), _ptr(bias), relu, _ptr(mask),
-                     mask.stride(0) if mask is not None else 0, accumulate, _err_flag(a.device).data_ptr(), 2.0,
+                     _ptr(o16), _ptr(o32), out.stride(0), _ptr(b32), relu, _ptr(mask),
+                     mask.stride(0) if mask is not None else 0, accumulate, _ptr(b16), split_k,
+                     _err_flag(a.device).data_ptr(), 2.0,
                      torch.cuda.current_stream().cuda_stream)
     if rc != 0:
         raise RuntimeError(f"gemm_bf16 failed with code {rc}")
@@ -73,6 +78,8 @@ def linear_dgrad(dy, w, mask=None, out=None):
     return gemm(dy, w, b_mn=True, mask=mask, out=out)
 
 
-def linear_wgrad(dy, x, out=None, accumulate=False):
-    """dw = dy.T @ x; dy [M,N], x [M,K] -> dw [N,K] (fp32 when ``out`` is fp32)."""
-    return gemm(dy, x, a_mn=True, b_mn=True, out=out, out_dtype=torch.float32, accumulate=accumulate)
+def linear_wgrad(dy, x, out=None, accumulate=False, split_k=1):
+    """dw = dy.T @ x; dy [M,N], x [M,K] -> dw [N,K] fp32. With ``split_k`` > 1 the batch dimension is
+    split over CTAs and ``out`` must be zero-initialised (partials are added atomically)."""
+    return gemm(dy, x, a_mn=True, b_mn=True, out=out, out_dtype=torch.float32, accumulate=accumulate,
+                split_k=split_k)
