@@ -209,7 +209,9 @@ PYBIND11_MODULE(_C, m) {
         .def("pair_capacity", &SparseEngine::pair_capacity)
         .def("scratch_bytes", &SparseEngine::scratch_bytes)
         .def("kernel_launches", &SparseEngine::kernel_launches)
-        .def("set_wait_limit", &SparseEngine::set_wait_limit);
+        .def("set_wait_limit", &SparseEngine::set_wait_limit)
+        .def("set_profile", &SparseEngine::set_profile)
+        .def("phase_stamps", [](SparseEngine& e, uintptr_t s) { return e.phase_stamps(stream_of(s)); });
 
     bind_host(m);
     bind_dense(m);

@@ -190,11 +190,12 @@ __device__ __forceinline__ bool table_attach_row(const TableView& t, unsigned sl
     // reads the row index after the next grid barrier.
     if (atomicCAS(&t.slots[slot].row, kNoRow, kRowPending) != kNoRow) return false;
     unsigned row = kNoRow;
-    int f = atomicSub(t.free_count, 1);
-    if (f > 0) {
+    // the free stack is only popped in this kernel family, so an empty stack stays empty: skip its atomics
+    int f = (*((volatile int*)t.free_count) > 0) ? atomicSub(t.free_count, 1) : 0x7fffffff;
+    if (f > 0 && f != 0x7fffffff) {
         row = t.free_rows[f - 1];
     } else {
-        atomicAdd(t.free_count, 1);
+        if (f != 0x7fffffff) atomicAdd(t.free_count, 1);
         unsigned b = atomicAdd(t.row_bump, 1u);
         if (b < t.rows_avail) {
             row = b;

@@ -64,6 +64,13 @@ __device__ __forceinline__ bool wait_all_flags(const unsigned* flags, unsigned t
 
 }  // namespace
 
+// Phase timestamps (the kernel-side counterpart of the reference's VTIMER scopes): CTA 0 records
+// %globaltimer when it enters each phase.
+#define PROF(slot)                                                                 \
+    do {                                                                           \
+        if (a.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 0) a.prof[slot] = global_timer_ns(); \
+    } while (0)
+
 __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a) {
     const unsigned nblocks = gridDim.x;
     const unsigned tid = blockIdx.x * kThreads + threadIdx.x;
@@ -83,38 +90,63 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
     __shared__ unsigned s_pre[kMaxWorld + 1];
 
     // ---- P1: dedup + partition ------------------------------------------------------------------
-    for (unsigned i = tid; i < a.n; i += nthreads) {
-        const long long key = a.keys[i];
-        unsigned long long h = slot_hash(key) & a.dmask;
-        for (;;) {
-            long long cur = *((volatile long long*)&a.dedup[h].key);
-            if (cur == key) break;
-            if (cur == kEmptyKey) {
-                long long prev = (long long)atomicCAS((unsigned long long*)&a.dedup[h].key,
-                                                      (unsigned long long)kEmptyKey, (unsigned long long)key);
-                if (prev == kEmptyKey) {
-                    const int owner = a.shard_owner[sparse_shard_of(key, a.n_shards)];
-                    const unsigned p = atomicAdd(&send_cnt[owner], 1u);
-                    const unsigned u = atomicAdd(&cnt[0], 1u);
-                    if (p < C) {
-                        a.send_keys[(size_t)owner * C + p] = key;
-                        a.send_ret[(size_t)owner * C + p] = u;
-                    } else {
-                        set_status(a.ctl, kStError, W_MAILBOX_OVERFLOW);
-                    }
-                    a.dedup[h].row = u;
-                    a.uniq_row[u] = (owner == me) ? kNoRow : kRemoteRow;
-                    break;
+    // Counters are bumped once per warp and owner (ballot / match), not once per key: same-address
+    // atomics serialise in L2 and would otherwise bound the phase.
+    PROF(0);
+    const unsigned wlane = threadIdx.x & 31u;
+    for (unsigned i0 = (tid & ~31u); i0 < a.n; i0 += nthreads) {
+        const unsigned i = i0 + wlane;
+        const bool active = i < a.n;
+        long long key = 0;
+        unsigned long long h = 0;
+        bool won = false;
+        if (active) {
+            key = a.keys[i];
+            h = slot_hash(key) & a.dmask;
+            for (;;) {
+                long long cur = *((volatile long long*)&a.dedup[h].key);
+                if (cur == key) break;
+                if (cur == kEmptyKey) {
+                    long long prev = (long long)atomicCAS((unsigned long long*)&a.dedup[h].key,
+                                                          (unsigned long long)kEmptyKey, (unsigned long long)key);
+                    if (prev == kEmptyKey) { won = true; break; }
+                    if (prev == key) break;
                 }
-                if (prev == key) break;
+                h = (h + 1) & a.dmask;  // dedup table holds >= 2n slots: an empty slot always exists
             }
-            h = (h + 1) & a.dmask;  // dedup table holds >= 2n slots: an empty slot always exists
+            a.pos_slot[i] = (unsigned)h;
         }
-        a.pos_slot[i] = (unsigned)h;
+        const unsigned wmask = __ballot_sync(0xffffffffu, won);
+        if (wmask == 0) continue;
+        const int owner = won ? a.shard_owner[sparse_shard_of(key, a.n_shards)] : -1;
+        // unique ids: one atomic per warp
+        unsigned ubase = 0;
+        const int uleader = __ffs(wmask) - 1;
+        if ((int)wlane == uleader) ubase = atomicAdd(&cnt[0], (unsigned)__popc(wmask));
+        ubase = __shfl_sync(0xffffffffu, ubase, uleader);
+        const unsigned u = ubase + __popc(wmask & ((1u << wlane) - 1u));
+        // per-owner positions: one atomic per (warp, owner)
+        const unsigned peers = __match_any_sync(0xffffffffu, owner);
+        const int pleader = __ffs(peers) - 1;
+        unsigned pbase = 0;
+        if (won && (int)wlane == pleader) pbase = atomicAdd(&send_cnt[owner], (unsigned)__popc(peers));
+        pbase = __shfl_sync(0xffffffffu, pbase, pleader);
+        if (won) {
+            const unsigned p = pbase + __popc(peers & ((1u << wlane) - 1u));
+            if (p < C) {
+                a.send_keys[(size_t)owner * C + p] = key;
+                a.send_ret[(size_t)owner * C + p] = u;
+            } else {
+                set_status(a.ctl, kStError, W_MAILBOX_OVERFLOW);
+            }
+            a.dedup[h].row = u;
+            a.uniq_row[u] = (owner == me) ? kNoRow : kRemoteRow;
+        }
     }
     if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P1)) return;
 
     // ---- P2: ship staged key lists to the owners ------------------------------------------------
+    PROF(1);
     if (a.world > 1) {
         if (threadIdx.x == 0) {
             unsigned acc = 0;
@@ -160,29 +192,42 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
 
     // ---- P3a: resolve received keys in the local table ------------------------------------------
     const bool do_insert = (a.flags & FUSED_INSERT) != 0;
-    for (unsigned e = tid; e < total_in; e += nthreads) {
-        int r = 0;
-        while (e >= s_pre[r + 1]) ++r;
-        const unsigned p = e - s_pre[r];
-        const long long key = (r == me) ? a.send_keys[(size_t)me * C + p] : mine.mail_keys[(size_t)r * C + p];
-        bool inserted = false;
-        unsigned slot = table_find_or_insert(T, key, do_insert, &inserted);
-        if (slot == kNoSlot) {
-            if (do_insert) set_status(a.ctl, kStOom, W_INDEX_FULL);
-        } else if (do_insert) {
-            bool oom = false;
-            if (table_attach_row(T, slot, &oom)) {
-                unsigned j = atomicAdd(&cnt[1], 1u);
-                a.new_list[j] = slot;
+    PROF(2);
+    for (unsigned e0 = (tid & ~31u); e0 < total_in; e0 += nthreads) {
+        const unsigned e = e0 + wlane;
+        bool attached = false, inserted = false;
+        unsigned slot = kNoSlot;
+        if (e < total_in) {
+            int r = 0;
+            while (e >= s_pre[r + 1]) ++r;
+            const unsigned p = e - s_pre[r];
+            const long long key = (r == me) ? a.send_keys[(size_t)me * C + p] : mine.mail_keys[(size_t)r * C + p];
+            slot = table_find_or_insert(T, key, do_insert, &inserted);
+            if (slot == kNoSlot) {
+                if (do_insert) set_status(a.ctl, kStOom, W_INDEX_FULL);
+            } else if (do_insert) {
+                bool oom = false;
+                attached = table_attach_row(T, slot, &oom);
+                if (oom) set_status(a.ctl, kStOom, W_POOL_FULL);
             }
-            if (inserted) atomicAdd(T.n_items, 1ull);
-            if (oom) set_status(a.ctl, kStOom, W_POOL_FULL);
+            a.res_slot[(size_t)r * C + p] = slot;
         }
-        a.res_slot[(size_t)r * C + p] = slot;
+        // list of freshly attached rows and the live-key counter: one atomic per warp each
+        const unsigned amask = __ballot_sync(0xffffffffu, attached);
+        if (amask) {
+            const int al = __ffs(amask) - 1;
+            unsigned base = 0;
+            if ((int)wlane == al) base = atomicAdd(&cnt[1], (unsigned)__popc(amask));
+            base = __shfl_sync(0xffffffffu, base, al);
+            if (attached) a.new_list[base + __popc(amask & ((1u << wlane) - 1u))] = slot;
+        }
+        const unsigned imask = __ballot_sync(0xffffffffu, inserted);
+        if (imask && (int)wlane == __ffs(imask) - 1) atomicAdd(T.n_items, (unsigned long long)__popc(imask));
     }
     if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P3A)) return;
 
     // ---- P3b: initialise the rows attached by this call -----------------------------------------
+    PROF(3);
     const unsigned n_new = cnt[1];
     if (n_new > 0) {
         for (unsigned j = group; j < n_new; j += ngroups) {
@@ -194,6 +239,7 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
     }
 
     // ---- P3c: return rows: peer stores for remote requesters, row index for local ones ----------
+    PROF(4);
     for (unsigned e = group; e < total_in; e += ngroups) {
         int r = 0;
         while (e >= s_pre[r + 1]) ++r;
@@ -224,6 +270,7 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
     }
 
     // ---- P5 (consumer): un-dedup + pool into the activation buffer ------------------------------
+    PROF(5);
     const unsigned L = a.bag_size;
     if (a.flags & FUSED_COPY_ROWS) {
         const unsigned nbags = a.n / L;
@@ -260,6 +307,7 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
         }
     }
     if (blockIdx.x == 0 && threadIdx.x < 16) a.counters[(par ^ 1u) * 16 + threadIdx.x] = 0;
+    PROF(6);
     if (blockIdx.x == 0 && threadIdx.x == 0) a.ctl->epoch = epoch;
 }
 
@@ -283,6 +331,7 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
     __shared__ unsigned s_pre[kMaxWorld + 1];
 
     // ---- Q1: segment-sum gradients of duplicate keys --------------------------------------------
+    PROF(8);
     {
         const unsigned n_uniq = cnt[0];
         const bool dups = (n_uniq != a.n);
@@ -305,6 +354,7 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
         // the owners must have consumed the previous push before their mailboxes are overwritten
         if (!wait_all_flags(mine.push_ack, epoch - 1u, a, W_ACK)) return;
         // ---- Q2: ship merged gradient rows to the owners
+        PROF(9);
         if (threadIdx.x == 0) {
             unsigned acc = 0;
             for (int o = 0; o < a.world; ++o) {
@@ -332,6 +382,7 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
     }
 
     // ---- Q3 (owner) -----------------------------------------------------------------------------
+    PROF(10);
     if (threadIdx.x == 0) {
         unsigned acc = 0;
         for (int r = 0; r < a.world; ++r) {
@@ -375,6 +426,7 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
     }
 
     // Q3c: one optimizer step per touched row
+    PROF(11);
     const bool sync_mode = (a.flags & FUSED_SYNC_PUSH) != 0;
     const unsigned dim = a.dim;
     for (unsigned e = group; e < total_in; e += ngroups) {
@@ -451,6 +503,7 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
                 st_release_sys(&a.peer[threadIdx.x].push_ack[me], epoch);
         }
     }
+    PROF(12);
     // every CTA read the epoch before the first grid barrier, so CTA 0 may publish it when it leaves
     if (blockIdx.x == 0 && threadIdx.x == 0) a.ctl->epoch = epoch;
 }

@@ -52,6 +52,7 @@ struct FusedArgs {
     unsigned* in_cnt;      // [2][kMaxWorld] per epoch parity: keys received from each source rank
     KernelCtl* ctl;       // control block of this kernel family (holds the call epoch)
     const KernelCtl* plan_ctl;  // push: control block of the pull family (parity of the plan)
+    unsigned long long* prof;  // [16] phase timestamps written by CTA 0 (nullptr = off)
     const int* shard_owner;  // [n_shards] owning rank of every global shard
     int n_shards;
     TableView table;

@@ -80,6 +80,7 @@ SparseEngine::SparseEngine(GpuTable* table, const SparseEngineConfig& cfg) : tab
     const size_t o_res = carve((size_t)W * C_ * 4), o_new = carve((size_t)W * C_ * 4);
     const size_t o_cnt = carve(2 * 16 * 4), o_in = carve(2 * kMaxWorld * 4);
     const size_t o_ctl1 = carve(sizeof(KernelCtl)), o_ctl2 = carve(sizeof(KernelCtl));
+    const size_t o_prof = carve(16 * 8);
     const size_t o_owner = carve((size_t)std::max(cfg_.n_shards, 1) * 4);
     scratch_bytes_ = s;
     cudaError_t e = cudaMalloc(&scratch_, s);
@@ -98,6 +99,7 @@ SparseEngine::SparseEngine(GpuTable* table, const SparseEngineConfig& cfg) : tab
     in_cnt_ = (unsigned*)(scratch_ + o_in);
     ctl_pull_ = (KernelCtl*)(scratch_ + o_ctl1);
     ctl_push_ = (KernelCtl*)(scratch_ + o_ctl2);
+    prof_ = (unsigned long long*)(scratch_ + o_prof);
     shard_owner_dev_ = (int*)(scratch_ + o_owner);
     fill_dedup_kernel<<<148 * 4, 256>>>(dedup_, dedup_slots_);
     // default placement: shard s lives on rank s % world
@@ -172,6 +174,7 @@ void SparseEngine::fill_common(FusedArgs& a) const {
     a.new_list = new_list_;
     a.counters = counters_;
     a.in_cnt = in_cnt_;
+    a.prof = profile_ ? prof_ : nullptr;
     a.shard_owner = shard_owner_dev_;
     a.n_shards = std::max(cfg_.n_shards, 1);
     a.table = table_->view();
@@ -274,6 +277,14 @@ Status SparseEngine::reset(void* stream) {
     plan_valid_ = false;
     if (e != cudaSuccess) return Status::Fatal(cudaGetErrorString(e));
     return Status::Ok();
+}
+
+std::vector<uint64_t> SparseEngine::phase_stamps(void* stream) {
+    cudaSetDevice(table_->device());
+    cudaStreamSynchronize((cudaStream_t)stream);
+    std::vector<uint64_t> v(16, 0);
+    cudaMemcpy(v.data(), prof_, 16 * 8, cudaMemcpyDeviceToHost);
+    return v;
 }
 
 uint32_t SparseEngine::last_unique(void* stream) {

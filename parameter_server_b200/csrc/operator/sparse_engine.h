@@ -54,6 +54,10 @@ public:
     uint64_t scratch_bytes() const { return scratch_bytes_; }
     uint64_t kernel_launches() const { return launches_; }
     void set_wait_limit(double s) { cfg_.wait_limit_s = s; }
+    // Phase tracing: when on, CTA 0 of each kernel records a timestamp at every phase boundary.
+    void set_profile(bool on) { profile_ = on; }
+    // Raw %globaltimer stamps of the last pull (slots 0..6) and push (slots 8..12), in ns.
+    std::vector<uint64_t> phase_stamps(void* stream);
 
 private:
     void fill_common(FusedArgs& a) const;
@@ -85,6 +89,8 @@ private:
     unsigned plan_flags_ = 0;
     bool plan_valid_ = false, plan_used_ = false;
     uint64_t launches_ = 0;
+    unsigned long long* prof_ = nullptr;
+    bool profile_ = false;
 };
 
 }  // namespace psb

@@ -24,6 +24,8 @@ from .optim import OPTIMIZERS, make_opt_config, set_adam_step
 def _dist_info(group=None):
     import torch.distributed as dist
 
+    if group == "none":  # a private single-rank table inside a distributed job
+        return 1, 0
     if dist.is_available() and dist.is_initialized():
         return dist.get_world_size(group), dist.get_rank(group)
     return 1, 0

@@ -1,0 +1,130 @@
+"""Worker of the multi-GPU tests: started once per GPU by torch.distributed.run.
+
+Checks the fused sparse pull / push and the fused dense push at world > 1 against a CPU oracle that
+sees the concatenation of every rank's batch, then runs DLRM steps. NVLS is irrelevant here (the
+kernels use plain peer loads / stores)."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from parameter_server_b200 import SparseTable  # noqa: E402
+from parameter_server_b200.ops.dense import DenseTable  # noqa: E402
+
+
+def gather(obj):
+    out = [None] * dist.get_world_size()
+    dist.all_gather_object(out, obj)
+    return out
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    which = sys.argv[1] if len(sys.argv) > 1 else "all"
+
+    if which in ("all", "sparse"):
+        for dim, opt, kw in [(64, "adagrad", dict(lr=0.05, init_accumulator=0.1)), (16, "sgd", dict(lr=0.5)),
+                             (128, "adam", dict(lr=0.01))]:
+            n_shards = world * 3 + 1
+            g = SparseTable(dim, opt, kw, n_shards=n_shards, capacity=1 << 16, max_keys=1 << 15, wait_limit_s=5.0)
+            c = SparseTable(dim, opt, kw, n_shards=n_shards, device="cpu", group="none") if rank == 0 else None
+            if c is not None:
+                c.world, c.rank = 1, 0
+                for s in range(n_shards):
+                    c.table.create_shard(s)
+            rng = np.random.default_rng(100 + rank)
+            for step in range(4):
+                n = 20000
+                keys = torch.from_numpy((rng.zipf(1.1, size=n).astype(np.int64) * 7919) % 50000)
+                grads = torch.from_numpy(rng.standard_normal((n, dim)).astype(np.float32) * 1e-2)
+                out = g.pull(keys.cuda())
+                g.push(grads.cuda())
+                g.check()
+                all_keys, all_grads, all_out = gather(keys), gather(grads), gather(out.cpu())
+                if rank == 0:
+                    ck = torch.cat(all_keys)
+                    ref = c.pull(ck)
+                    got = torch.cat(all_out)
+                    tol = dict(rtol=1e-4, atol=1e-6)
+                    assert torch.allclose(got, ref, **tol), f"pull mismatch dim={dim} step={step}: {(got-ref).abs().max()}"
+                    c.push(torch.cat(all_grads))
+            # final table state: every rank exports its local rows; rank 0 compares with the oracle
+            ks, rs = [], []
+            for k, r in g.export():
+                ks.append(k.cpu()); rs.append(r.cpu())
+            ks = torch.cat(ks) if ks else torch.empty(0, dtype=torch.int64)
+            rs = torch.cat(rs) if rs else torch.empty(0, g.table.stride())
+            owners = set(int(g.shard_owner[int(x)]) for x in
+                         [__import__("parameter_server_b200").C.sparse_shard_of(int(k), n_shards) for k in ks[:200].tolist()])
+            assert owners <= {rank}, f"rank {rank} holds foreign keys: {owners}"
+            all_ks, all_rs = gather(ks), gather(rs)
+            if rank == 0:
+                K, R = torch.cat(all_ks), torch.cat(all_rs)
+                assert K.numel() == torch.unique(K).numel() == c.size(), (K.numel(), c.size())
+                ref, found = c.get_rows(K, emb_only=False)
+                assert found.all()
+                assert torch.allclose(R, ref, rtol=2e-4, atol=1e-6), f"table mismatch {opt}: {(R-ref).abs().max()}"
+            dist.barrier()
+        if rank == 0:
+            print("sparse ok", flush=True)
+
+    if which in ("all", "dense"):
+        for gdt in (torch.float32, torch.bfloat16):
+            shapes = {"a": (300, 40), "b": (77,), "c": (1024, 64)}
+            t = DenseTable(shapes, "adamw", dict(lr=1e-2, weight_decay=0.01), grad_dtype=gdt, wait_limit_s=5.0)
+            gen = torch.Generator().manual_seed(0)
+            init = {k: torch.randn(v, generator=gen) for k, v in shapes.items()}
+            t.load(init)
+            ref = {k: v.clone() for k, v in init.items()}
+            m = {k: torch.zeros_like(v) for k, v in init.items()}
+            vv = {k: torch.zeros_like(v) for k, v in init.items()}
+            for step in range(1, 4):
+                local = {k: torch.randn(v, generator=torch.Generator().manual_seed(10 * step + rank)) for k, v in shapes.items()}
+                for k in shapes:
+                    t.grads[k].copy_(local[k].to(gdt))
+                t.push()
+                t.check()
+                alls = gather({k: v.to(gdt).float() for k, v in local.items()})
+                for k in shapes:
+                    gsum = sum(a[k] for a in alls) / world
+                    m[k] = 0.9 * m[k] + 0.1 * gsum
+                    vv[k] = 0.999 * vv[k] + 0.001 * gsum * gsum
+                    ref[k] = ref[k] * (1 - 1e-2 * 0.01)
+                    ref[k] = ref[k] - 1e-2 * (m[k] / (1 - 0.9 ** step)) / ((vv[k] / (1 - 0.999 ** step)).sqrt() + 1e-8)
+                for k in shapes:
+                    got = t.pull(k).float().cpu()
+                    assert torch.allclose(got, ref[k].bfloat16().float(), rtol=2e-2, atol=2e-2), (k, step, (got - ref[k]).abs().max())
+            dist.barrier()
+        if rank == 0:
+            print("dense ok", flush=True)
+
+    if which in ("all", "dlrm"):
+        from parameter_server_b200.models import DLRM, DLRMConfig, SyntheticCTR
+        cfg = DLRMConfig(vocab_max=5e4)
+        model = DLRM(cfg, 1024, table_capacity=1 << 18)
+        data = SyntheticCTR(cfg, 1024, pool=4, seed=rank)
+        losses = []
+        for _ in range(20):
+            model.train_step(*data.next())
+            losses.append(model.read_loss())
+        model.check()
+        assert all(np.isfinite(losses)), losses
+        # dense parameters stay identical on every rank
+        sig = float(model.dense.flat_params.float().sum().item())
+        sigs = gather(sig)
+        assert max(sigs) - min(sigs) == 0.0, sigs
+        if rank == 0:
+            print("dlrm ok", [round(x, 3) for x in losses[:3]], "...", round(losses[-1], 3), flush=True)
+
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
