@@ -44,6 +44,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch-per-gpu", type=int, default=8192)
     ap.add_argument("--no-sparse-micro", action="store_true", help="skip the sparse pull+push microbenchmark")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a CUDA graph")
     ap.add_argument("--micro-keys", type=int, default=1 << 20, help="keys per GPU per step of the microbenchmark")
     return ap.parse_args()
 
@@ -155,6 +156,11 @@ def main():
         model.train_step(*data.next())
     model.check()
     own_launches_per_step = model.launches_per_step
+    if not args.no_graph:
+        model.enable_graph()
+        for _ in range(3):
+            model.train_step(*data.next())
+        model.check()
 
     # ---------------- device-timed region ----------------
     sampler = ClockSampler(uuid)
@@ -211,6 +217,7 @@ def main():
             "seq_len": None,
             "parallelism": f"dp{world} + sparse rows sharded by key hash + dense slices (PS)",
             "vocab": "26 fields log-spaced 1e3..4e7 (~300M rows), rows created on first pull",
+            "launch": "eager" if args.no_graph else "whole step replayed from one CUDA graph",
             "l2": "inputs larger than L2: ~109 MB of embedding rows gathered + ~109 MB of row gradients per step "
                   "per GPU, new batch (pool of 16) every step",
         },

@@ -77,7 +77,8 @@ PYBIND11_MODULE(_C, m) {
         .def_readwrite("bias_corr1", &OptConfig::bias_corr1)
         .def_readwrite("bias_corr2", &OptConfig::bias_corr2)
         .def_readwrite("slot_init0", &OptConfig::slot_init0)
-        .def_readwrite("slot_init1", &OptConfig::slot_init1);
+        .def_readwrite("slot_init1", &OptConfig::slot_init1)
+        .def_readwrite("step_from_epoch", &OptConfig::step_from_epoch);
     m.attr("OPT_SGD") = (int)OPT_SGD;
     m.attr("OPT_ADAGRAD") = (int)OPT_ADAGRAD;
     m.attr("OPT_FTRL") = (int)OPT_FTRL;

@@ -43,7 +43,8 @@ struct TableView {
     unsigned dim;             // embedding floats per row
     unsigned n_opt_slots;     // optimizer slot count (each dim floats)
     unsigned has_delta;       // 1 when rows carry a sync-push delta section after the slots
-    unsigned rows_avail;      // rows backed by memory
+    const unsigned* rows_avail;  // device word: rows backed by memory (the host raises it when it adds slabs, so a
+                                 // launch captured in a CUDA graph sees the growth)
     unsigned max_probe;
     unsigned* row_bump;       // next never-used row
     unsigned* free_rows;      // stack of recycled rows
@@ -197,7 +198,7 @@ __device__ __forceinline__ bool table_attach_row(const TableView& t, unsigned sl
     } else {
         if (f != 0x7fffffff) atomicAdd(t.free_count, 1);
         unsigned b = atomicAdd(t.row_bump, 1u);
-        if (b < t.rows_avail) {
+        if (b < *((volatile const unsigned*)t.rows_avail)) {
             row = b;
         } else {
             atomicSub(t.row_bump, 1u);

@@ -57,6 +57,8 @@ __global__ void __launch_bounds__(kThreads) dense_rs_opt_ag_kernel(const DenseAr
     const int me = a.rank;
     const unsigned epoch = *((volatile unsigned*)&a.ctl->epoch) + 1u;
     const int W = a.world;
+    OptConfig opt = a.opt;
+    if (opt.step_from_epoch) opt_set_step(opt, epoch);
     // ---- 1. announce + wait: gradients of every rank are complete --------------------------------
     if (W > 1) {
         if (blockIdx.x == 0 && threadIdx.x < (unsigned)W && (int)threadIdx.x != me) {
@@ -114,7 +116,7 @@ __global__ void __launch_bounds__(kThreads) dense_rs_opt_ag_kernel(const DenseAr
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             float s0 = a.n_slots > 0 ? m[k] : 0.f, s1 = a.n_slots > 1 ? s[k] : 0.f;
-            opt_update(a.opt, w[k], s0, s1, g[k] * a.grad_scale);
+            opt_update(opt, w[k], s0, s1, g[k] * a.grad_scale);
             m[k] = s0;
             s[k] = s1;
         }
@@ -137,6 +139,14 @@ __global__ void __launch_bounds__(kThreads) dense_rs_opt_ag_kernel(const DenseAr
             if (r < W) *(uint4*)(pdst[r] + i) = packed;
     }
     // ---- 4. all slices landed everywhere ----------------------------------------------------------
+    if (W == 1) {
+        // single rank: the epoch is only the step counter; the last CTA out publishes it
+        __syncthreads();
+        if (threadIdx.x == 0 && atomicAdd(&a.ctl->done_blocks, 1u) == gridDim.x - 1u) {
+            a.ctl->done_blocks = 0;
+            a.ctl->epoch = epoch;
+        }
+    }
     if (W > 1) {
         __threadfence_system();
         __syncthreads();

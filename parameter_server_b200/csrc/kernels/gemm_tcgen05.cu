@@ -130,6 +130,91 @@ struct SmemLayout {
     static constexpr int kTotal = kTileBytes + kBarBytes + 1024;  // + alignment slack
 };
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Epilogue of one 32-column chunk held by one thread (one output row).
+__device__ __forceinline__ void epilogue_chunk(const GemmEpilogue& ep, float* f, int row, int col0, int N) {
+    if (ep.bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < N) f[j] += ep.bias[col0 + j];
+    }
+    if (ep.bias_bf16 != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < N) f[j] += __bfloat162float(ep.bias_bf16[col0 + j]);
+    }
+    if (ep.relu) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = fmaxf(f[j], 0.f);
+    }
+    const bool full = (col0 + 32 <= N);
+    if (ep.mask != nullptr) {
+        const __nv_bfloat16* mp = ep.mask + (size_t)row * ep.ldmask + col0;
+        if (full && (ep.ldmask % 8 == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+                uint4 raw = *(const uint4*)(mp + j);
+                const __nv_bfloat16* h = (const __nv_bfloat16*)&raw;
+#pragma unroll
+                for (int t = 0; t < 8; ++t)
+                    if (!(__bfloat162float(h[t]) > 0.f)) f[j + t] = 0.f;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < N && !(__bfloat162float(mp[j]) > 0.f)) f[j] = 0.f;
+        }
+    }
+    if (ep.out_f32 != nullptr) {
+        float* op = ep.out_f32 + (size_t)row * ep.ldd + col0;
+        if (ep.split_k > 1) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) atomicAdd(op + j, f[j]);
+        } else if (full && (ep.ldd % 4 == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                float4 o = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                if (ep.accumulate) {
+                    float4 old = *(float4*)(op + j);
+                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *(float4*)(op + j) = o;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) op[j] = ep.accumulate ? op[j] + f[j] : f[j];
+        }
+    }
+    if (ep.out_bf16 != nullptr) {
+        __nv_bfloat16* op = ep.out_bf16 + (size_t)row * ep.ldd + col0;
+        if (full && (ep.ldd % 8 == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+                uint4 raw;
+                __nv_bfloat162* h = (__nv_bfloat162*)&raw;
+                h[0] = __floats2bfloat162_rn(f[j], f[j + 1]);
+                h[1] = __floats2bfloat162_rn(f[j + 2], f[j + 3]);
+                h[2] = __floats2bfloat162_rn(f[j + 4], f[j + 5]);
+                h[3] = __floats2bfloat162_rn(f[j + 6], f[j + 7]);
+                *(uint4*)(op + j) = raw;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) op[j] = __float2bfloat16_rn(f[j]);
+        }
+    }
+}
+
+// Persistent kernel: gridDim.x CTAs (one per SM) walk the tile list t = blockIdx.x, +gridDim.x, ...;
+// a tile is (split z, n tile, m tile) with m fastest so that concurrently running CTAs share the B
+// tile in L2. The accumulator is double-buffered in TMEM (2 x BN columns): while the epilogue warps
+// drain buffer b, the MMA warp already fills buffer b^1 with the next tile.
 // AMN / BMN: operand is MN-major. The box of an MN-major operand is [64 k-rows][64 mn-elements].
 template <int BN, bool AMN, bool BMN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -140,29 +225,33 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full_bar = (uint64_t*)(smem + L::kTileBytes);
     uint64_t* empty_bar = full_bar + L::kStages;
-    uint64_t* acc_bar = empty_bar + L::kStages;
-    uint32_t* tmem_slot = (uint32_t*)(acc_bar + 1);
+    uint64_t* tfull_bar = empty_bar + L::kStages;   // [2] accumulator buffer complete
+    uint64_t* tempty_bar = tfull_bar + 2;           // [2] accumulator buffer drained
+    uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int tile_m = blockIdx.y * BM;
-    const int tile_n = blockIdx.x * BN;
+    const int m_tiles = (M + BM - 1) / BM;
+    const int n_tiles = (N + BN - 1) / BN;
+    const int splits = ep.split_k > 1 ? ep.split_k : 1;
+    const int total_tiles = m_tiles * n_tiles * splits;
     const int total_kt = (K + BK - 1) / BK;
-    const int kt_per = (total_kt + (int)gridDim.z - 1) / (int)gridDim.z;
-    const int kt_begin = (int)blockIdx.z * kt_per;
-    const int num_kt = max(0, min(total_kt - kt_begin, kt_per));
+    const int kt_per = (total_kt + splits - 1) / splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < L::kStages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(acc_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tfull_bar[b], 1);
+            mbar_init(&tempty_bar[b], 4);  // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"((uint32_t)BN)
+                     "r"((uint32_t)(2 * BN))
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -174,29 +263,39 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
-            for (int kt = 0; kt < num_kt; ++kt) {
-                const int s = kt % L::kStages;
-                const uint32_t ph = (uint32_t)(kt / L::kStages) & 1u;
-                if (!mbar_wait(&empty_bar[s], ph ^ 1u, limit_ns)) {
-                    atomicCAS(err_flag, 0u, 1u);
-                    break;
-                }
-                uint8_t* sa = smem + s * L::kStageBytes;
-                uint8_t* sb = sa + L::kABytes;
-                mbar_expect_tx(&full_bar[s], (uint32_t)L::kStageBytes);
-                const int k0 = (kt_begin + kt) * BK;
-                if (!AMN) {
-                    tma_load_2d(sa, &map_a, &full_bar[s], k0, tile_m);  // box [128 rows][64 k]
-                } else {
-                    tma_load_2d(sa, &map_a, &full_bar[s], tile_m, k0);               // box [64 k][64 m]
-                    tma_load_2d(sa + 64 * 128, &map_a, &full_bar[s], tile_m + 64, k0);
-                }
-                if (!BMN) {
-                    tma_load_2d(sb, &map_b, &full_bar[s], k0, tile_n);  // box [BN rows][64 k]
-                } else {
+            uint32_t it = 0;  // k-tile counter across all tiles of this CTA (drives the stage ring)
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int z = tile / (m_tiles * n_tiles);
+                const int rem = tile - z * (m_tiles * n_tiles);
+                const int tile_n = (rem / m_tiles) * BN, tile_m = (rem % m_tiles) * BM;
+                const int kt_begin = z * kt_per;
+                const int num_kt = max(0, min(total_kt - kt_begin, kt_per));
+                for (int kt = 0; kt < num_kt; ++kt, ++it) {
+                    const int s = it % L::kStages;
+                    const uint32_t ph = (it / L::kStages) & 1u;
+                    if (!mbar_wait(&empty_bar[s], ph ^ 1u, limit_ns)) {
+                        atomicCAS(err_flag, 0u, 1u);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = smem + s * L::kStageBytes;
+                    uint8_t* sb = sa + L::kABytes;
+                    mbar_expect_tx(&full_bar[s], (uint32_t)L::kStageBytes);
+                    const int k0 = (kt_begin + kt) * BK;
+                    if (!AMN) {
+                        tma_load_2d(sa, &map_a, &full_bar[s], k0, tile_m);  // box [128 rows][64 k]
+                    } else {
+                        tma_load_2d(sa, &map_a, &full_bar[s], tile_m, k0);  // box [64 k][64 m]
+                        tma_load_2d(sa + 64 * 128, &map_a, &full_bar[s], tile_m + 64, k0);
+                    }
+                    if (!BMN) {
+                        tma_load_2d(sb, &map_b, &full_bar[s], k0, tile_n);  // box [BN rows][64 k]
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < BN / 64; ++j)
-                        tma_load_2d(sb + j * 64 * 128, &map_b, &full_bar[s], tile_n + 64 * j, k0);
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_2d(sb + j * 64 * 128, &map_b, &full_bar[s], tile_n + 64 * j, k0);
+                    }
                 }
             }
         }
@@ -205,132 +304,89 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((AMN ? 1u : 0u) << 15) |
                                    ((BMN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            uint32_t it = 0, tc = 0;
             bool ok = true;
-            for (int kt = 0; kt < num_kt && ok; ++kt) {
-                const int s = kt % L::kStages;
-                const uint32_t ph = (uint32_t)(kt / L::kStages) & 1u;
-                if (!mbar_wait(&full_bar[s], ph, limit_ns)) {
-                    atomicCAS(err_flag, 0u, 2u);
-                    ok = false;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int z = tile / (m_tiles * n_tiles);
+                const int kt_begin = z * kt_per;
+                const int num_kt = max(0, min(total_kt - kt_begin, kt_per));
+                if (num_kt == 0) continue;
+                const uint32_t buf = tc & 1u, tph = (tc >> 1) & 1u;
+                if (!mbar_wait(&tempty_bar[buf], tph ^ 1u, limit_ns)) {
+                    atomicCAS(err_flag, 0u, 4u);
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t sa = smem_u32(smem + s * L::kStageBytes);
-                const uint32_t sb = sa + L::kABytes;
+                const uint32_t tmem_d = tmem_base + buf * (uint32_t)BN;
+                for (int kt = 0; kt < num_kt; ++kt, ++it) {
+                    const int s = it % L::kStages;
+                    const uint32_t ph = (it / L::kStages) & 1u;
+                    if (!mbar_wait(&full_bar[s], ph, limit_ns)) {
+                        atomicCAS(err_flag, 0u, 2u);
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = smem_u32(smem + s * L::kStageBytes);
+                    const uint32_t sb = sa + L::kABytes;
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // K-major: 8-row groups are 1024 B apart, a K step of 16 elements is 32 B inside the
-                    // swizzle span. MN-major: 64-element column blocks are one box (8192 B) apart,
-                    // 8-k-row groups 1024 B apart, a K step of 16 rows is 2048 B.
-                    const uint64_t da = AMN ? make_desc(sa + k * 2048, 8192, 1024) : make_desc(sa + k * 32, 16, 1024);
-                    const uint64_t db = BMN ? make_desc(sb + k * 2048, 8192, 1024) : make_desc(sb + k * 32, 16, 1024);
-                    umma_bf16(tmem_base, da, db, idesc, (kt | k) ? 1u : 0u);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // K-major: 8-row groups are 1024 B apart, a K step of 16 elements is 32 B inside the
+                        // swizzle span. MN-major: 64-element column blocks are one box (8192 B) apart,
+                        // 8-k-row groups 1024 B apart, a K step of 16 rows is 2048 B.
+                        const uint64_t da = AMN ? make_desc(sa + k * 2048, 8192, 1024) : make_desc(sa + k * 32, 16, 1024);
+                        const uint64_t db = BMN ? make_desc(sb + k * 2048, 8192, 1024) : make_desc(sb + k * 32, 16, 1024);
+                        umma_bf16(tmem_d, da, db, idesc, (kt | k) ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
                 }
-                umma_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
+                umma_commit(&tfull_bar[buf]);  // accumulator complete (also on error, so the epilogue moves on)
+                ++tc;
             }
-            umma_commit(acc_bar);  // accumulator complete (also reached on error so the epilogue leaves)
         }
     } else {
         // ------------------------------ epilogue ----------------------------------
         const int q = warp & 3;  // TMEM lane quarter this warp may read
-        const bool ok = mbar_wait(acc_bar, 0, limit_ns * 2);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (!ok) {
-            if (lane == 0) atomicCAS(err_flag, 0u, 3u);
-        } else if (num_kt > 0) {
+        uint32_t tc = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            const int z = tile / (m_tiles * n_tiles);
+            const int rem = tile - z * (m_tiles * n_tiles);
+            const int tile_n = (rem / m_tiles) * BN, tile_m = (rem % m_tiles) * BM;
+            const int kt_begin = z * kt_per;
+            const int num_kt = max(0, min(total_kt - kt_begin, kt_per));
+            if (num_kt == 0) continue;
+            const uint32_t buf = tc & 1u, tph = (tc >> 1) & 1u;
+            const bool ok = mbar_wait(&tfull_bar[buf], tph, limit_ns * 2);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (!ok) {
+                if (lane == 0) atomicCAS(err_flag, 0u, 3u);
+                break;
+            }
             const int row = tile_m + q * 32 + lane;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 if (tile_n + c0 >= N) break;  // warp-uniform
                 uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)BN + (uint32_t)c0, v);
                 if (row < M) {
-                    const int col0 = tile_n + c0;
                     float f[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                    if (ep.bias != nullptr) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < N) f[j] += ep.bias[col0 + j];
-                    }
-                    if (ep.bias_bf16 != nullptr) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < N) f[j] += __bfloat162float(ep.bias_bf16[col0 + j]);
-                    }
-                    if (ep.relu) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) f[j] = fmaxf(f[j], 0.f);
-                    }
-                    const bool full = (col0 + 32 <= N);
-                    if (ep.mask != nullptr) {
-                        const __nv_bfloat16* mp = ep.mask + (size_t)row * ep.ldmask + col0;
-                        if (full && (ep.ldmask % 8 == 0)) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                uint4 raw = *(const uint4*)(mp + j);
-                                const __nv_bfloat16* h = (const __nv_bfloat16*)&raw;
-#pragma unroll
-                                for (int t = 0; t < 8; ++t)
-                                    if (!(__bfloat162float(h[t]) > 0.f)) f[j + t] = 0.f;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < N && !(__bfloat162float(mp[j]) > 0.f)) f[j] = 0.f;
-                        }
-                    }
-                    if (ep.out_f32 != nullptr) {
-                        float* op = ep.out_f32 + (size_t)row * ep.ldd + col0;
-                        if (ep.split_k > 1) {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < N) atomicAdd(op + j, f[j]);
-                        } else if (full && (ep.ldd % 4 == 0)) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                float4 o = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-                                if (ep.accumulate) {
-                                    float4 old = *(float4*)(op + j);
-                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                                }
-                                *(float4*)(op + j) = o;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < N) op[j] = ep.accumulate ? op[j] + f[j] : f[j];
-                        }
-                    }
-                    if (ep.out_bf16 != nullptr) {
-                        __nv_bfloat16* op = ep.out_bf16 + (size_t)row * ep.ldd + col0;
-                        if (full && (ep.ldd % 8 == 0)) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                uint4 raw;
-                                __nv_bfloat162* h = (__nv_bfloat162*)&raw;
-                                h[0] = __floats2bfloat162_rn(f[j], f[j + 1]);
-                                h[1] = __floats2bfloat162_rn(f[j + 2], f[j + 3]);
-                                h[2] = __floats2bfloat162_rn(f[j + 4], f[j + 5]);
-                                h[3] = __floats2bfloat162_rn(f[j + 6], f[j + 7]);
-                                *(uint4*)(op + j) = raw;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < N) op[j] = __float2bfloat16_rn(f[j]);
-                        }
-                    }
+                    epilogue_chunk(ep, f, row, tile_n + c0, N);
                 }
             }
+            // this warp is done reading the buffer: hand it back to the MMA warp
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+            ++tc;
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN))
                      : "memory");
     }
 }
@@ -377,7 +433,14 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const G
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, ep.split_k > 1 ? ep.split_k : 1);
+    static int num_sms = 0;
+    if (num_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM) * (ep.split_k > 1 ? ep.split_k : 1);
+    dim3 grid(tiles < num_sms ? tiles : num_sms);
     kern<<<grid, kThreads, SmemLayout<BN>::kTotal, s>>>(ma, mb, ep, M, N, K, err, limit_ns);
     return cudaGetLastError();
 }
@@ -389,7 +452,9 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if ((A.ld % 8) || (B.ld % 8) || ((uintptr_t)A.ptr % 16) || ((uintptr_t)B.ptr % 16)) return -2;  // TMA: 16-byte rule
     CUtensorMap ma, mb;
-    const int BN = 128;
+    // 128 x 256 tiles halve the operand bytes per flop (the 128 x 128 tile is bound by the L2 -> SMEM feed);
+    // they are used whenever N fills them.
+    const int BN = (N >= 256) ? 256 : 128;
     // K-major: tensor [MN rows][K cols], box [tile rows][64]; MN-major: tensor [K rows][MN cols], box [64][64]
     bool ok = A.mn_major ? make_map(&ma, A.ptr, (uint64_t)K, (uint64_t)M, (uint64_t)A.ld, 64)
                          : make_map(&ma, A.ptr, (uint64_t)M, (uint64_t)K, (uint64_t)A.ld, BM);
@@ -399,10 +464,22 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep
     const unsigned long long lim = (unsigned long long)(wait_limit_s * 1e9);
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
-    if (!A.mn_major && !B.mn_major) e = launch_variant<128, false, false>(ma, mb, ep, M, N, K, err_flag, lim, s);
-    else if (!A.mn_major && B.mn_major) e = launch_variant<128, false, true>(ma, mb, ep, M, N, K, err_flag, lim, s);
-    else if (A.mn_major && !B.mn_major) e = launch_variant<128, true, false>(ma, mb, ep, M, N, K, err_flag, lim, s);
-    else e = launch_variant<128, true, true>(ma, mb, ep, M, N, K, err_flag, lim, s);
+    const int v = (A.mn_major ? 2 : 0) | (B.mn_major ? 1 : 0);
+    if (BN == 256) {
+        switch (v) {
+            case 0: e = launch_variant<256, false, false>(ma, mb, ep, M, N, K, err_flag, lim, s); break;
+            case 1: e = launch_variant<256, false, true>(ma, mb, ep, M, N, K, err_flag, lim, s); break;
+            case 2: e = launch_variant<256, true, false>(ma, mb, ep, M, N, K, err_flag, lim, s); break;
+            default: e = launch_variant<256, true, true>(ma, mb, ep, M, N, K, err_flag, lim, s); break;
+        }
+    } else {
+        switch (v) {
+            case 0: e = launch_variant<128, false, false>(ma, mb, ep, M, N, K, err_flag, lim, s); break;
+            case 1: e = launch_variant<128, false, true>(ma, mb, ep, M, N, K, err_flag, lim, s); break;
+            case 2: e = launch_variant<128, true, false>(ma, mb, ep, M, N, K, err_flag, lim, s); break;
+            default: e = launch_variant<128, true, true>(ma, mb, ep, M, N, K, err_flag, lim, s); break;
+        }
+    }
     return (int)e;
 }
 

@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdint>
 
 #include "model_kernels.h"
@@ -15,81 +16,186 @@ namespace {
 
 constexpr int kMaxT = 32;  // interaction vectors per sample (fields + 1)
 
-// ---- interaction forward -----------------------------------------------------------------------
-// T[0] = bottom (bf16), T[1..F] = emb (fp32). out[b] = [bottom (D) | dot(T_i, T_j) for i > j | 0 pad].
+// ---- interaction -------------------------------------------------------------------------------
+// Per sample the interaction is the Gram matrix of T = [bottom; emb_1..emb_F] (F+1 <= 32 rows of D):
+// a 32 x 32 x D product, far too small for a tcgen05 tile and bound by the fp32 row traffic (F*D*4 bytes
+// per sample each way). One warp owns one sample: it stages T as bf16 in shared memory and runs
+// m16n8k16 warp-level MMAs on it (fp32 accumulate); the kernel stays at memory speed.
+
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, const uint32_t* b) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+constexpr int kIntWarps = 4;
+
+// out[b] = [bottom (D) | dot(T_i, T_j) for i > j, row-major over i | 0 pad to ldo]
 template <int D>
-__global__ void __launch_bounds__(128) interaction_fwd_kernel(const __nv_bfloat16* __restrict__ bottom, int64_t ldb,
-                                                              const float* __restrict__ emb, int F,
-                                                              __nv_bfloat16* __restrict__ out, int64_t ldo, int B) {
-    __shared__ float T[kMaxT][D + 1];
+__global__ void __launch_bounds__(kIntWarps * 32) interaction_fwd_kernel(const __nv_bfloat16* __restrict__ bottom,
+                                                                         int64_t ldb, const float* __restrict__ emb, int F,
+                                                                         __nv_bfloat16* __restrict__ out, int64_t ldo,
+                                                                         int B) {
+    constexpr int LD = D + 8;  // bf16 elements per staged row (conflict-free fragment loads)
+    extern __shared__ __align__(16) unsigned char smem_i[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __nv_bfloat16* Ts = (__nv_bfloat16*)smem_i + (size_t)warp * (32 * LD);
+    __nv_bfloat16* Os = (__nv_bfloat16*)smem_i + (size_t)kIntWarps * (32 * LD) + (size_t)warp * ldo;
     const int nT = F + 1;
     const int npairs = nT * (nT - 1) / 2;
-    for (int b = blockIdx.x; b < B; b += gridDim.x) {
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < nT * D; idx += 128) {
-            const int i = idx / D, d = idx % D;
-            T[i][d] = (i == 0) ? __bfloat162float(bottom[(size_t)b * ldb + d]) : emb[((size_t)b * F + (i - 1)) * D + d];
+    const int g = lane >> 2, t = lane & 3;
+    for (int idx = lane; idx < 32 * LD; idx += 32) Ts[idx] = __float2bfloat16_rn(0.f);
+    __syncwarp();
+    for (int b = blockIdx.x * kIntWarps + warp; b < B; b += gridDim.x * kIntWarps) {
+        // stage T: row 0 = bottom (bf16), rows 1..F = emb (fp32 -> bf16)
+        for (int d = lane * 8; d < D; d += 256) {
+            uint4 v = *(const uint4*)(bottom + (size_t)b * ldb + d);
+            *(uint4*)(Ts + d) = v;
+            *(uint4*)(Os + d) = v;
         }
-        __syncthreads();
+        const float* eb = emb + (size_t)b * F * D;
+        for (int r = 0; r < F; ++r) {
+#pragma unroll
+            for (int d = lane * 4; d < D; d += 128) {
+                float4 v = *(const float4*)(eb + (size_t)r * D + d);
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                uint2 pk;
+                pk.x = *(uint32_t*)&lo;
+                pk.y = *(uint32_t*)&hi;
+                *(uint2*)(Ts + (size_t)(r + 1) * LD + d) = pk;
+            }
+        }
+        __syncwarp();
+        // lower-triangular 16x8 tiles of the 32x32 Gram matrix: (mt, nt) with nt*8 < (mt+1)*16
+        float acc[6][4];
+#pragma unroll
+        for (int i = 0; i < 6; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+#pragma unroll 2
+        for (int ks = 0; ks < D / 16; ++ks) {
+            const int k0 = ks * 16 + t * 2;
+            uint32_t a[2][4], bf[4][2];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                a[mt][0] = *(const uint32_t*)(Ts + (size_t)(mt * 16 + g) * LD + k0);
+                a[mt][1] = *(const uint32_t*)(Ts + (size_t)(mt * 16 + g + 8) * LD + k0);
+                a[mt][2] = *(const uint32_t*)(Ts + (size_t)(mt * 16 + g) * LD + k0 + 8);
+                a[mt][3] = *(const uint32_t*)(Ts + (size_t)(mt * 16 + g + 8) * LD + k0 + 8);
+            }
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                bf[nt][0] = *(const uint32_t*)(Ts + (size_t)(nt * 8 + g) * LD + k0);
+                bf[nt][1] = *(const uint32_t*)(Ts + (size_t)(nt * 8 + g) * LD + k0 + 8);
+            }
+            mma_bf16_16816(acc[0], a[0], bf[0]);
+            mma_bf16_16816(acc[1], a[0], bf[1]);
+            mma_bf16_16816(acc[2], a[1], bf[0]);
+            mma_bf16_16816(acc[3], a[1], bf[1]);
+            mma_bf16_16816(acc[4], a[1], bf[2]);
+            mma_bf16_16816(acc[5], a[1], bf[3]);
+        }
+        // scatter the strictly-lower triangle into the staged output row
+#pragma unroll
+        for (int tile = 0; tile < 6; ++tile) {
+            const int mt = tile < 2 ? 0 : 1;
+            const int nt = tile < 2 ? tile : tile - 2;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = mt * 16 + g + (e >= 2 ? 8 : 0);
+                const int j = nt * 8 + t * 2 + (e & 1);
+                if (i < nT && j < i) Os[D + i * (i - 1) / 2 + j] = __float2bfloat16_rn(acc[tile][e]);
+            }
+        }
+        for (int c = D + npairs + lane; c < ldo; c += 32) Os[c] = __float2bfloat16_rn(0.f);
+        __syncwarp();
         __nv_bfloat16* o = out + (size_t)b * ldo;
-        for (int d = threadIdx.x; d < D; d += 128) o[d] = __float2bfloat16_rn(T[0][d]);
-        for (int p = threadIdx.x; p < npairs; p += 128) {
-            int i = (int)((1.0f + sqrtf(1.0f + 8.0f * (float)p)) * 0.5f);
-            while (i * (i - 1) / 2 > p) --i;
-            while ((i + 1) * i / 2 <= p) ++i;
-            const int j = p - i * (i - 1) / 2;
-            float acc = 0.f;
-#pragma unroll 8
-            for (int d = 0; d < D; ++d) acc = fmaf(T[i][d], T[j][d], acc);
-            o[D + p] = __float2bfloat16_rn(acc);
-        }
-        for (int c = D + npairs + threadIdx.x; c < ldo; c += 128) o[c] = __float2bfloat16_rn(0.f);
+        for (int c = lane * 8; c < ldo; c += 256) *(uint4*)(o + c) = *(const uint4*)(Os + c);
+        __syncwarp();
     }
 }
 
-// ---- interaction backward ----------------------------------------------------------------------
-// dT_i = sum_{j != i} G[i][j] T_j with G the symmetric matrix of pair gradients.
-// d_bottom (bf16) = (dout[:, :D] + dT_0) masked by (bottom > 0) when relu_mask; d_emb (fp32) = dT_{1..F}.
+// dT = G T with G the symmetric (zero-diagonal) matrix of pair gradients.
+// d_bottom (bf16) = (dout[:, :D] + dT_0), masked by (bottom > 0) when relu_mask; d_emb (fp32) = dT_{1..F}.
 template <int D>
-__global__ void __launch_bounds__(D) interaction_bwd_kernel(const __nv_bfloat16* __restrict__ dout, int64_t ldo,
-                                                            const __nv_bfloat16* __restrict__ bottom, int64_t ldb,
-                                                            const float* __restrict__ emb, int F,
-                                                            __nv_bfloat16* __restrict__ dbottom, int64_t lddb,
-                                                            float* __restrict__ demb, int B, int relu_mask) {
-    __shared__ float T[kMaxT][D + 1];
-    __shared__ float G[kMaxT][kMaxT + 1];
+__global__ void __launch_bounds__(kIntWarps * 32) interaction_bwd_kernel(const __nv_bfloat16* __restrict__ dout, int64_t ldo,
+                                                                         const __nv_bfloat16* __restrict__ bottom,
+                                                                         int64_t ldb, const float* __restrict__ emb, int F,
+                                                                         __nv_bfloat16* __restrict__ dbottom, int64_t lddb,
+                                                                         float* __restrict__ demb, int B, int relu_mask) {
+    constexpr int LG = 40;  // bf16 per row of G  (80 B: conflict-free fragment loads)
+    constexpr int LT = 34;  // bf16 per row of T^T (68 B: conflict-free transposed stores)
+    extern __shared__ __align__(16) unsigned char smem_i[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __nv_bfloat16* Gs = (__nv_bfloat16*)smem_i + (size_t)warp * (32 * LG + D * LT);
+    __nv_bfloat16* Tt = Gs + 32 * LG;  // Tt[d][j] = T[j][d]
     const int nT = F + 1;
     const int npairs = nT * (nT - 1) / 2;
-    for (int b = blockIdx.x; b < B; b += gridDim.x) {
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < nT * D; idx += D) {
-            const int i = idx / D, d = idx % D;
-            T[i][d] = (i == 0) ? __bfloat162float(bottom[(size_t)b * ldb + d]) : emb[((size_t)b * F + (i - 1)) * D + d];
-        }
+    const int g = lane >> 2, t = lane & 3;
+    for (int idx = lane; idx < 32 * LG + D * LT; idx += 32) Gs[idx] = __float2bfloat16_rn(0.f);
+    __syncwarp();
+    for (int b = blockIdx.x * kIntWarps + warp; b < B; b += gridDim.x * kIntWarps) {
         const __nv_bfloat16* go = dout + (size_t)b * ldo;
-        for (int p = threadIdx.x; p < npairs; p += D) {
+        for (int p = lane; p < npairs; p += 32) {
             int i = (int)((1.0f + sqrtf(1.0f + 8.0f * (float)p)) * 0.5f);
             while (i * (i - 1) / 2 > p) --i;
             while ((i + 1) * i / 2 <= p) ++i;
             const int j = p - i * (i - 1) / 2;
-            const float g = __bfloat162float(go[D + p]);
-            G[i][j] = g;
-            G[j][i] = g;
+            const __nv_bfloat16 v = go[D + p];
+            Gs[i * LG + j] = v;
+            Gs[j * LG + i] = v;
         }
-        if (threadIdx.x < nT) G[threadIdx.x][threadIdx.x] = 0.f;
-        __syncthreads();
-        const int d = threadIdx.x;
-        for (int i = 0; i < nT; ++i) {
-            float acc = 0.f;
-            for (int j = 0; j < nT; ++j) acc = fmaf(G[i][j], T[j][d], acc);
-            if (i == 0) {
-                float v = acc + __bfloat162float(go[d]);
-                if (relu_mask && !(T[0][d] > 0.f)) v = 0.f;
-                dbottom[(size_t)b * lddb + d] = __float2bfloat16_rn(v);
-            } else {
-                demb[((size_t)b * F + (i - 1)) * D + d] = acc;
+        for (int d = lane; d < D; d += 32) Tt[d * LT] = bottom[(size_t)b * ldb + d];
+        const float* eb = emb + (size_t)b * F * D;
+        for (int r = 0; r < F; ++r) {
+#pragma unroll
+            for (int d = lane; d < D; d += 32) Tt[d * LT + r + 1] = __float2bfloat16_rn(eb[(size_t)r * D + d]);
+        }
+        __syncwarp();
+        // A = G (row-major [i][j]), B(k = j, n = d) read as Tt[d][j]; M = 32, N = D, K = 32
+        uint32_t a[2][2][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks) {
+                const int k0 = ks * 16 + t * 2;
+                a[mt][ks][0] = *(const uint32_t*)(Gs + (mt * 16 + g) * LG + k0);
+                a[mt][ks][1] = *(const uint32_t*)(Gs + (mt * 16 + g + 8) * LG + k0);
+                a[mt][ks][2] = *(const uint32_t*)(Gs + (mt * 16 + g) * LG + k0 + 8);
+                a[mt][ks][3] = *(const uint32_t*)(Gs + (mt * 16 + g + 8) * LG + k0 + 8);
             }
+        float* de = demb + (size_t)b * F * D;
+#pragma unroll 4
+        for (int nt = 0; nt < D / 8; ++nt) {
+            float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks) {
+                uint32_t bf[2];
+                const int k0 = ks * 16 + t * 2;
+                bf[0] = *(const uint32_t*)(Tt + (nt * 8 + g) * LT + k0);
+                bf[1] = *(const uint32_t*)(Tt + (nt * 8 + g) * LT + k0 + 8);
+                mma_bf16_16816(acc[0], a[0][ks], bf);
+                mma_bf16_16816(acc[1], a[1][ks], bf);
+            }
+            const int d0 = nt * 8 + t * 2;
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int i = mt * 16 + g + h * 8;
+                    const float v0 = acc[mt][h * 2], v1 = acc[mt][h * 2 + 1];
+                    if (i == 0) {
+                        float r0 = v0 + __bfloat162float(go[d0]), r1 = v1 + __bfloat162float(go[d0 + 1]);
+                        if (relu_mask) {
+                            if (!(__bfloat162float(Tt[d0 * LT]) > 0.f)) r0 = 0.f;
+                            if (!(__bfloat162float(Tt[(d0 + 1) * LT]) > 0.f)) r1 = 0.f;
+                        }
+                        *(__nv_bfloat162*)(dbottom + (size_t)b * lddb + d0) = __floats2bfloat162_rn(r0, r1);
+                    } else if (i < nT) {
+                        *(float2*)(de + (size_t)(i - 1) * D + d0) = make_float2(v0, v1);
+                    }
+                }
         }
+        __syncwarp();
     }
 }
 
@@ -145,22 +251,38 @@ __global__ void __launch_bounds__(256) bce_head_kernel(const __nv_bfloat16* __re
 }
 
 // ---- bias gradient: db[n] = sum_m dz[m][n] -------------------------------------------------------------
+// CTA = 64 columns x 32 row lanes; every thread streams 16-byte (8 x bf16) loads down its column group.
 __global__ void __launch_bounds__(256) bias_grad_kernel(const __nv_bfloat16* __restrict__ dz, int64_t ld, int M, int N,
                                                         float* __restrict__ db) {
-    // CTA handles 32 columns x a stripe of rows; threads (tx: column, ty: row lane)
-    __shared__ float part[8][33];
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const int col = blockIdx.x * 32 + tx;
-    float acc = 0.f;
-    if (col < N)
-        for (int m = blockIdx.y * 8 + ty; m < M; m += gridDim.y * 8) acc += __bfloat162float(dz[(size_t)m * ld + col]);
-    part[ty][tx] = acc;
-    __syncthreads();
-    if (ty == 0 && col < N) {
-        float s = 0.f;
+    __shared__ float part[32][65];
+    const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
+    const int col = blockIdx.x * 64 + tx * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (col + 8 <= N && (ld % 8) == 0) {
+        for (int m = blockIdx.y * 32 + ty; m < M; m += gridDim.y * 32) {
+            const uint4 raw = *(const uint4*)(dz + (size_t)m * ld + col);
+            const __nv_bfloat162* h = (const __nv_bfloat162*)&raw;
 #pragma unroll
-        for (int r = 0; r < 8; ++r) s += part[r][tx];
-        atomicAdd(&db[col], s);
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __bfloat1622float2(h[k]);
+                acc[2 * k] += f.x;
+                acc[2 * k + 1] += f.y;
+            }
+        }
+    } else {
+        for (int m = blockIdx.y * 32 + ty; m < M; m += gridDim.y * 32)
+            for (int k = 0; k < 8; ++k)
+                if (col + k < N) acc[k] += __bfloat162float(dz[(size_t)m * ld + col + k]);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) part[ty][tx * 8 + k] = acc[k];
+    __syncthreads();
+    if (threadIdx.x < 64) {
+        float s = 0.f;
+#pragma unroll 8
+        for (int r = 0; r < 32; ++r) s += part[r][threadIdx.x];
+        const int c = blockIdx.x * 64 + threadIdx.x;
+        if (c < N) atomicAdd(&db[c], s);
     }
 }
 
@@ -173,36 +295,53 @@ __global__ void cast_pad_kernel(const float* __restrict__ x, int B, int Kin, __n
     }
 }
 
+template <int D>
+int launch_int_fwd(const void* bottom, int64_t ldb, const float* emb, int F, void* out, int64_t ldo, int B, cudaStream_t s) {
+    const size_t smem = (size_t)kIntWarps * 32 * (D + 8) * 2 + (size_t)kIntWarps * ldo * 2;
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(interaction_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
+    }
+    const int blocks = std::min((B + kIntWarps - 1) / kIntWarps, 148 * 4);
+    interaction_fwd_kernel<D><<<blocks, kIntWarps * 32, smem, s>>>((const __nv_bfloat16*)bottom, ldb, emb, F,
+                                                                   (__nv_bfloat16*)out, ldo, B);
+    return (int)cudaGetLastError();
+}
+
+template <int D>
+int launch_int_bwd(const void* dout, int64_t ldo, const void* bottom, int64_t ldb, const float* emb, int F, void* dbottom,
+                   int64_t lddb, float* demb, int B, int relu_mask, cudaStream_t s) {
+    const size_t smem = (size_t)kIntWarps * (32 * 40 + D * 34) * 2;
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(interaction_bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
+    }
+    const int blocks = std::min((B + kIntWarps - 1) / kIntWarps, 148 * 4);
+    interaction_bwd_kernel<D><<<blocks, kIntWarps * 32, smem, s>>>((const __nv_bfloat16*)dout, ldo,
+                                                                   (const __nv_bfloat16*)bottom, ldb, emb, F,
+                                                                   (__nv_bfloat16*)dbottom, lddb, demb, B, relu_mask);
+    return (int)cudaGetLastError();
+}
+
 }  // namespace
 
+// bottom / out / dout / dbottom rows must be 16-byte aligned (ld multiples of 8), D in {64, 128}, F <= 31.
 int interaction_fwd(const void* bottom, int64_t ldb, const float* emb, int F, int D, void* out, int64_t ldo, int B,
                     void* stream) {
-    if (D != 128 && D != 64) return -2;
-    if (F + 1 > kMaxT) return -2;
-    const int grid = B < 148 * 16 ? B : 148 * 16;
-    if (D == 128)
-        interaction_fwd_kernel<128><<<grid, 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)bottom, ldb, emb, F,
-                                                                            (__nv_bfloat16*)out, ldo, B);
-    else
-        interaction_fwd_kernel<64><<<grid, 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)bottom, ldb, emb, F,
-                                                                           (__nv_bfloat16*)out, ldo, B);
-    return (int)cudaGetLastError();
+    if ((D != 128 && D != 64) || F + 1 > kMaxT || (ldb % 8) || (ldo % 8) || ldo < D + (F + 1) * F / 2) return -2;
+    return D == 128 ? launch_int_fwd<128>(bottom, ldb, emb, F, out, ldo, B, (cudaStream_t)stream)
+                    : launch_int_fwd<64>(bottom, ldb, emb, F, out, ldo, B, (cudaStream_t)stream);
 }
 
 int interaction_bwd(const void* dout, int64_t ldo, const void* bottom, int64_t ldb, const float* emb, int F, int D,
                     void* dbottom, int64_t lddb, float* demb, int B, int relu_mask, void* stream) {
-    if (D != 128 && D != 64) return -2;
-    if (F + 1 > kMaxT) return -2;
-    const int grid = B < 148 * 16 ? B : 148 * 16;
-    if (D == 128)
-        interaction_bwd_kernel<128><<<grid, 128, 0, (cudaStream_t)stream>>>(
-            (const __nv_bfloat16*)dout, ldo, (const __nv_bfloat16*)bottom, ldb, emb, F, (__nv_bfloat16*)dbottom, lddb, demb,
-            B, relu_mask);
-    else
-        interaction_bwd_kernel<64><<<grid, 64, 0, (cudaStream_t)stream>>>(
-            (const __nv_bfloat16*)dout, ldo, (const __nv_bfloat16*)bottom, ldb, emb, F, (__nv_bfloat16*)dbottom, lddb, demb,
-            B, relu_mask);
-    return (int)cudaGetLastError();
+    if ((D != 128 && D != 64) || F + 1 > kMaxT || (lddb % 2)) return -2;
+    return D == 128 ? launch_int_bwd<128>(dout, ldo, bottom, ldb, emb, F, dbottom, lddb, demb, B, relu_mask, (cudaStream_t)stream)
+                    : launch_int_bwd<64>(dout, ldo, bottom, ldb, emb, F, dbottom, lddb, demb, B, relu_mask, (cudaStream_t)stream);
 }
 
 int bce_head(const void* h, int64_t ldh, const void* w, const void* bias, const float* y, int B, int K, float inv_batch,
@@ -215,7 +354,9 @@ int bce_head(const void* h, int64_t ldh, const void* w, const void* bias, const 
 }
 
 int bias_grad(const void* dz, int64_t ld, int M, int N, float* db, void* stream) {
-    dim3 grid((N + 31) / 32, 64);
+    const int gx = (N + 63) / 64;
+    const int gy = std::max(1, std::min((M + 31) / 32, (148 * 4 + gx - 1) / gx));
+    dim3 grid(gx, gy);
     bias_grad_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dz, ld, M, N, db);
     return (int)cudaGetLastError();
 }

@@ -39,7 +39,17 @@ struct OptConfig {
     float bias_corr2 = 1.f;    // 1 - beta2^t
     float slot_init0 = 0.f;    // initial value of optimizer slot 0 (Adagrad accumulator, FTRL z, Adam m)
     float slot_init1 = 0.f;    // initial value of optimizer slot 1 (FTRL n, Adam v)
+    int32_t step_from_epoch = 0;  // 1: kernels derive the Adam bias corrections from their own call counter
+                                  // (needed when the launch is replayed from a CUDA graph)
 };
+
+// Adam bias corrections for (1-based) step t.
+PSB_HD void opt_set_step(OptConfig& c, unsigned t) {
+    if (c.type == OPT_ADAM) {
+        c.bias_corr1 = 1.f - powf(c.beta1, (float)t);
+        c.bias_corr2 = 1.f - powf(c.beta2, (float)t);
+    }
+}
 
 PSB_HD int opt_num_slots(int type) {
     switch (type) {

@@ -240,16 +240,30 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
 
     // ---- P3c: return rows: peer stores for remote requesters, row index for local ones ----------
     PROF(4);
-    for (unsigned e = group; e < total_in; e += ngroups) {
-        int r = 0;
-        while (e >= s_pre[r + 1]) ++r;
-        const unsigned p = e - s_pre[r];
-        const unsigned slot = a.res_slot[(size_t)r * C + p];
-        unsigned row = kNoRow;
-        if (slot != kNoSlot) row = T.slots[slot].row;
-        if (r == me) {
-            if (lane == 0) a.uniq_row[a.send_ret[(size_t)me * C + p]] = row;
-        } else if (a.flags & FUSED_COPY_ROWS) {
+    {
+        // local requester: only the row index is needed (P5 reads the table directly); thread per entry
+        const unsigned lo = s_pre[me], hi = s_pre[me + 1];
+        for (unsigned e = lo + tid; e < hi; e += nthreads) {
+            const unsigned p = e - lo;
+            const unsigned slot = a.res_slot[(size_t)me * C + p];
+            a.uniq_row[a.send_ret[(size_t)me * C + p]] = (slot != kNoSlot) ? T.slots[slot].row : kNoRow;
+        }
+    }
+    if (a.world > 1 && (a.flags & FUSED_COPY_ROWS)) {
+        // remote requesters: one lane group per entry stores the row into the requester's buffer
+        for (unsigned e = group; e < total_in; e += ngroups) {
+            int r = 0;
+            while (e >= s_pre[r + 1]) ++r;
+            if (r == me) {
+                // skip the local range in one step
+                const unsigned skip = (s_pre[me + 1] - e + ngroups - 1) / ngroups;
+                e += (skip - 1) * ngroups;
+                continue;
+            }
+            const unsigned p = e - s_pre[r];
+            const unsigned slot = a.res_slot[(size_t)r * C + p];
+            unsigned row = kNoRow;
+            if (slot != kNoSlot) row = T.slots[slot].row;
             float* dst = a.peer[r].rows_in + (size_t)mine.mail_ret[(size_t)r * C + p] * a.dim;
             if (row < kRowPending) {
                 copy_row(dst, T.row_ptr(row), a.dim, lane, lanes);
@@ -271,32 +285,42 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
 
     // ---- P5 (consumer): un-dedup + pool into the activation buffer ------------------------------
     PROF(5);
+    // Every CTA owns a contiguous range of bags: pass (a) resolves the index chain
+    // position -> dedup slot -> unique id -> row with one THREAD per position (independent loads in
+    // flight), pass (b) gathers and pools with one lane group per bag. Only a CTA barrier in between.
     const unsigned L = a.bag_size;
-    if (a.flags & FUSED_COPY_ROWS) {
+    {
         const unsigned nbags = a.n / L;
-        const float scale = (a.flags & FUSED_MEAN) ? 1.0f / (float)L : 1.0f;
-        for (unsigned b = group; b < nbags; b += ngroups) {
-            for (unsigned d = lane * 4; d < a.dim; d += lanes * 4) {
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (unsigned j = 0; j < L; ++j) {
-                    const unsigned i = b * L + j;
-                    const unsigned u = a.dedup[a.pos_slot[i]].row;
-                    const unsigned row = a.uniq_row[u];
-                    float4 v;
-                    if (row == kRemoteRow) v = *(const float4*)(mine.rows_in + (size_t)u * a.dim + d);
-                    else if (row < kRowPending) v = *(const float4*)(T.row_ptr(row) + d);
-                    else v = init4(T, a.keys[i], d);
-                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        const unsigned per = (nbags + nblocks - 1) / nblocks;
+        const unsigned b_lo = min(nbags, blockIdx.x * per), b_hi = min(nbags, b_lo + per);
+        for (unsigned i = b_lo * L + threadIdx.x; i < b_hi * L; i += kThreads) {
+            const unsigned h = a.pos_slot[i];
+            const unsigned u = a.dedup[h].row;
+            a.inverse[i] = (int)u;
+            a.pos_slot[i] = a.uniq_row[u];  // from here on: the row of position i
+            a.dedup[h].key = kEmptyKey;     // leave the scratch table empty for the next call
+        }
+        if (a.flags & FUSED_COPY_ROWS) {
+            __syncthreads();
+            const float scale = (a.flags & FUSED_MEAN) ? 1.0f / (float)L : 1.0f;
+            const unsigned lgroup = threadIdx.x / lanes, lgroups = kThreads / lanes;
+            for (unsigned b = b_lo + lgroup; b < b_hi; b += lgroups) {
+                for (unsigned d = lane * 4; d < a.dim; d += lanes * 4) {
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (unsigned j = 0; j < L; ++j) {
+                        const unsigned i = b * L + j;
+                        const unsigned row = a.pos_slot[i];
+                        float4 v;
+                        if (row == kRemoteRow) v = *(const float4*)(mine.rows_in + (size_t)a.inverse[i] * a.dim + d);
+                        else if (row < kRowPending) v = *(const float4*)(T.row_ptr(row) + d);
+                        else v = init4(T, a.keys[i], d);
+                        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                    }
+                    if (L > 1) { acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale; }
+                    *(float4*)(a.out + (size_t)b * a.dim + d) = acc;
                 }
-                if (L > 1) { acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale; }
-                *(float4*)(a.out + (size_t)b * a.dim + d) = acc;
             }
         }
-    }
-    for (unsigned i = tid; i < a.n; i += nthreads) {
-        const unsigned h = a.pos_slot[i];
-        a.inverse[i] = (int)a.dedup[h].row;
-        a.dedup[h].key = kEmptyKey;
     }
     if (a.flags & FUSED_PREPARE_PUSH) {
         const unsigned n_uniq = cnt[0];
@@ -427,6 +451,8 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
 
     // Q3c: one optimizer step per touched row
     PROF(11);
+    OptConfig opt = a.opt;
+    if (opt.step_from_epoch) opt_set_step(opt, epoch);
     const bool sync_mode = (a.flags & FUSED_SYNC_PUSH) != 0;
     const unsigned dim = a.dim;
     for (unsigned e = group; e < total_in; e += ngroups) {
@@ -477,10 +503,10 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
                 float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
                 if (T.n_opt_slots > 0) s0 = *(float4*)(w + dim + d);
                 if (T.n_opt_slots > 1) s1 = *(float4*)(w + 2 * dim + d);
-                opt_update(a.opt, wv.x, s0.x, s1.x, gv.x);
-                opt_update(a.opt, wv.y, s0.y, s1.y, gv.y);
-                opt_update(a.opt, wv.z, s0.z, s1.z, gv.z);
-                opt_update(a.opt, wv.w, s0.w, s1.w, gv.w);
+                opt_update(opt, wv.x, s0.x, s1.x, gv.x);
+                opt_update(opt, wv.y, s0.y, s1.y, gv.y);
+                opt_update(opt, wv.z, s0.z, s1.z, gv.z);
+                opt_update(opt, wv.w, s0.w, s1.w, gv.w);
                 *(float4*)(w + d) = wv;
                 if (T.n_opt_slots > 0) *(float4*)(w + dim + d) = s0;
                 if (T.n_opt_slots > 1) *(float4*)(w + 2 * dim + d) = s1;

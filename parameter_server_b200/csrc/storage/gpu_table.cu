@@ -301,7 +301,7 @@ GpuTable::GpuTable(const GpuTableConfig& cfg) : cfg_(cfg) {
     must(cudaMalloc(&scratch_, 64 * sizeof(unsigned long long)), "scratch");
     must(cudaMemset(scratch_, 0, 64 * sizeof(unsigned long long)), "scratch");
     // scratch layout (8-byte words): 0 n_items, 1 row_bump(u32), 2 free_count(i32), 3 touched_count(u32),
-    //                                4 op counter, 5 op status
+    //                                4 op counter, 5 op status, 6 rows_avail(u32)
     n_items_ = scratch_ + 0;
     row_bump_ = (unsigned*)(scratch_ + 1);
     free_count_ = (int*)(scratch_ + 2);
@@ -354,6 +354,7 @@ Status GpuTable::add_slab() {
     slabs_.push_back(p);
     bytes_ += bytes;
     rows_avail_ = (uint32_t)(slabs_.size() << cfg_.slab_shift);
+    PSB_CUDA_OK(cudaMemcpy(scratch_ + 6, &rows_avail_, sizeof(uint32_t), cudaMemcpyHostToDevice));
     return Status::Ok();
 }
 
@@ -365,9 +366,12 @@ Status GpuTable::reserve_rows(uint64_t n) {
     const int freec = (int)(unsigned)host_mirror_[1];
     const uint64_t used = bump - (uint64_t)std::max(freec, 0);
     const uint64_t need = used + 3 * n;
-    while (need > rows_avail_) {
+    if (need <= rows_avail_) return Status::Ok();
+    // grow geometrically (at least a quarter of the pool) so that allocation calls are amortised
+    const uint64_t target = std::max<uint64_t>(need, (uint64_t)rows_avail_ + rows_avail_ / 4);
+    while (need > rows_avail_ || (target > rows_avail_ && slabs_.size() < max_slabs_)) {
         Status st = add_slab();
-        if (!st.ok()) return st;  // the kernel reports OUT_OF_MEMORY for what does not fit
+        if (!st.ok()) return need <= rows_avail_ ? Status::Ok() : st;  // the kernel reports what does not fit
     }
     return Status::Ok();
 }
@@ -386,7 +390,7 @@ TableView GpuTable::view() const {
     v.dim = cfg_.dim;
     v.n_opt_slots = n_slots_;
     v.has_delta = cfg_.sync_delta ? 1 : 0;
-    v.rows_avail = rows_avail_;
+    v.rows_avail = (const unsigned*)(scratch_ + 6);
     v.max_probe = (unsigned)std::min<uint64_t>(cfg_.max_probe, capacity_);
     v.row_bump = row_bump_;
     v.free_rows = free_rows_;
@@ -539,6 +543,7 @@ Status GpuTable::clear(void* stream) {
     PSB_CUDA_OK(cudaMemsetAsync(scratch_, 0, 64 * sizeof(unsigned long long), s));
     PSB_CUDA_OK(cudaMemsetAsync(touched_bits_, 0, ((max_rows_ + 31) / 32) * 4, s));
     if (dirty_bits_) PSB_CUDA_OK(cudaMemsetAsync(dirty_bits_, 0, ((max_rows_ + 31) / 32) * 4, s));
+    PSB_CUDA_OK(cudaMemcpyAsync(scratch_ + 6, &rows_avail_, sizeof(uint32_t), cudaMemcpyHostToDevice, s));
     PSB_CUDA_OK(cudaStreamSynchronize(s));
     host_mirror_[0] = host_mirror_[1] = 0;
     tombstones_ = 0;

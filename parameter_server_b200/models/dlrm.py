@@ -90,7 +90,7 @@ class DLRM:
     """One rank's replica of the model; ``train_step`` is collective over the ranks of ``group``."""
 
     def __init__(self, cfg: DLRMConfig, batch: int, *, table_capacity: int = 1 << 22, device=None, group=None,
-                 seed: int = 0, wgrad_split_k: int = 4, sparse_kwargs: Optional[dict] = None):
+                 seed: int = 0, wgrad_split_k: int = 0, sparse_kwargs: Optional[dict] = None):
         if not torch.cuda.is_available():
             raise RuntimeError("DLRM runs on the sm_100a kernels and needs a CUDA device")
         self.cfg = cfg
@@ -156,6 +156,7 @@ class DLRM:
         self.loss = torch.zeros(1, dtype=torch.float32, device=dev)
         self.h_loss = torch.zeros(1, dtype=torch.float32).pin_memory()
         self.launches_per_step = 0
+        self.graph = None
 
     # ------------------------------------------------------------------------------------------
     def load_batch(self, dense: torch.Tensor, keys: torch.Tensor, labels: torch.Tensor) -> None:
@@ -226,10 +227,29 @@ class DLRM:
         self.launches_per_step = n_launch
         return self.loss
 
+    def enable_graph(self) -> None:
+        """Capture the step (every launch of ``forward_backward``) in a CUDA graph; later
+        ``train_step`` calls replay it. Call after a few eager steps. What a captured launch cannot do
+        moves out of it: row-pool growth happens on the host before each replay, the call epochs and
+        the Adam step live in device memory and advance with every replay."""
+        self.sparse.opt.step_from_epoch = 1
+        self.dense.opt.step_from_epoch = 1
+        self._worst_new_rows = self.sparse.world * self.B * self.cfg.num_sparse
+        self.sparse.reserve(4 * self._worst_new_rows)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.forward_backward()
+        self.graph = g
+
     def train_step(self, dense: torch.Tensor, keys: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
         """Public API: copy one pinned host batch in, run the step, return the device loss."""
         self.load_batch(dense, keys, labels)
-        return self.forward_backward()
+        if self.graph is None:
+            return self.forward_backward()
+        self.sparse.reserve(self._worst_new_rows)
+        self.graph.replay()
+        return self.loss
 
     def read_loss(self) -> float:
         """Device -> host read of the last step's loss (synchronises the stream)."""

@@ -81,5 +81,10 @@ def linear_dgrad(dy, w, mask=None, out=None):
 def linear_wgrad(dy, x, out=None, accumulate=False, split_k=1):
     """dw = dy.T @ x; dy [M,N], x [M,K] -> dw [N,K] fp32. With ``split_k`` > 1 the batch dimension is
     split over CTAs and ``out`` must be zero-initialised (partials are added atomically)."""
+    if split_k <= 0:  # automatic: enough K slices to give every SM a tile
+        n_out, k_in, batch = dy.shape[1], x.shape[1], dy.shape[0]
+        bn = 256 if k_in >= 256 else 128
+        tiles = ((n_out + 127) // 128) * ((k_in + bn - 1) // bn)
+        split_k = max(1, min(16, 148 // tiles, max(1, batch // 256)))
     return gemm(dy, x, a_mn=True, b_mn=True, out=out, out_dtype=torch.float32, accumulate=accumulate,
                 split_k=split_k)

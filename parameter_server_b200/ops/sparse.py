@@ -214,6 +214,14 @@ class SparseTable:
         else:
             raise_if_error(self.table.store(self.opt))
 
+    def reserve(self, n_new_rows: int) -> None:
+        """Make room for ``n_new_rows`` more rows now (grows the slab pool on the host). Needed before
+        a pull is captured in, or replayed from, a CUDA graph, where the call itself cannot allocate."""
+        if self.is_cuda:
+            st = self.table.reserve_rows(int(n_new_rows))
+            if not st.ok() and st.code() != C.StatusCode.OUT_OF_MEMORY:
+                raise_if_error(st)
+
     def check(self) -> None:
         """Synchronise and raise :class:`StatusError` if a kernel reported an error."""
         if self.is_cuda:

@@ -32,7 +32,7 @@ def test_interaction_kernels_match_reference():
     demb = torch.empty(B, F, D, device="cuda")
     assert C.interaction_bwd(dout.data_ptr(), ldo, bottom.data_ptr(), D, emb.data_ptr(), F, D, dbot.data_ptr(), D,
                              demb.data_ptr(), B, False, 0) == 0
-    assert torch.allclose(demb, Tg.grad[:, 1:], rtol=1e-3, atol=1e-3)
+    assert torch.allclose(demb, Tg.grad[:, 1:], rtol=2e-2, atol=1e-2)  # operands are staged as bf16
     assert torch.allclose(dbot.float(), Tg.grad[:, 0], rtol=2e-2, atol=5e-2)
 
 
@@ -83,3 +83,29 @@ def test_forward_matches_reference_and_loss_decreases():
     later = model.reference_loss()
     assert later < first, (first, later)
     assert model.sparse.size() > 0
+
+
+def test_graph_replay_matches_eager():
+    """The same steps, launched eagerly and replayed from a CUDA graph, end in the same parameters."""
+    cfg = DLRMConfig(vocab_max=2e4)
+    B = 512
+
+    def run(use_graph):
+        model = DLRM(cfg, B, table_capacity=1 << 17, seed=3)
+        data = SyntheticCTR(cfg, B, pool=3, seed=9)
+        for _ in range(3):
+            model.train_step(*data.next())
+        if use_graph:
+            model.enable_graph()
+        losses = []
+        for _ in range(6):
+            model.train_step(*data.next())
+            losses.append(model.read_loss())
+        model.check()
+        return losses, model.dense.flat_params.float().clone(), model.sparse.size()
+
+    le, pe, ne = run(False)
+    lg, pg, ng = run(True)
+    assert ne == ng
+    assert max(abs(a - b) for a, b in zip(le, lg)) < 5e-3, (le, lg)
+    assert torch.allclose(pe, pg, rtol=0, atol=2e-2)
