@@ -64,7 +64,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", self.uuid, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", "-i", self.uuid, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -75,6 +75,10 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def mark(self) -> None:
+        """Samples taken before this call (warm-up) are ignored by stop()."""
+        self.first = len(self.lines)
+
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -84,7 +88,8 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, smax, reasons = [], [], set()
-        for ln in self.lines:
+        region = self.lines[getattr(self, "first", 0):] or self.lines
+        for ln in region:
             p = [x.strip() for x in ln.split(",")]
             if len(p) < 8:
                 continue
@@ -152,6 +157,9 @@ def main():
     uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
 
     # ---------------- warm-up ----------------
+    sampler = ClockSampler(uuid)
+    if rank == 0:
+        sampler.start()  # nvidia-smi needs a moment to come up: start it before the warm-up
     for _ in range(max(W, 3)):
         model.train_step(*data.next())
     model.check()
@@ -163,9 +171,7 @@ def main():
         model.check()
 
     # ---------------- device-timed region ----------------
-    sampler = ClockSampler(uuid)
-    if rank == 0:
-        sampler.start()
+    sampler.mark()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     ev0.record()

@@ -1,5 +1,454 @@
-// Control-plane bindings (master, context, RPC server / client).
+// Control-plane bindings: master, server, client, handlers, controller, model objects, native PS and
+// the small common pieces (archive / message codec, thread coalescing, heap, compression).
+#include <pybind11/functional.h>
+#include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
+
+#include "common/heap.h"
+#include "common/thread_sync.h"
+#include "controller/controller.h"
+#include "handler/handlers.h"
+#include "native_ps/native_ps.h"
+
 namespace py = pybind11;
-void bind_service(py::module_& m) { (void)m; }
+using namespace psb;
+
+using KeyArray = py::array_t<int64_t, py::array::c_style | py::array::forcecast>;
+using F32Array = py::array_t<float, py::array::c_style | py::array::forcecast>;
+using nogil = py::call_guard<py::gil_scoped_release>;
+
+namespace {
+template <class H>
+std::unique_ptr<H> make_handler(Client& c, int32_t sid, int32_t hid) { return std::unique_ptr<H>(new H(&c, sid, hid)); }
+
+py::dict metrics_dict(Handler& h) {
+    py::dict d;
+    d["requests"] = (uint64_t)h.metrics().requests;
+    d["retries"] = (uint64_t)h.metrics().retries;
+    d["errors"] = (uint64_t)h.metrics().errors;
+    d["wait_us"] = (uint64_t)h.metrics().wait_us;
+    return d;
+}
+}  // namespace
+
+void bind_service(py::module_& m) {
+    register_builtin_operators();
+
+    // ---- codec / common ----------------------------------------------------------------------
+    m.def("message_round_trip", [](py::bytes body, int sid, int hid, int ver, int uver, int type) {
+        PSMessage msg;
+        std::string b = body;
+        msg.ar.write_raw(b.data(), b.size());
+        msg.meta.sid = sid; msg.meta.hid = hid; msg.meta.ctx_ver = ver; msg.meta.ctx_u_ver = uver;
+        msg.meta.req_type = (RequestType)type;
+        Bytes wire = msg.seal();
+        PSMessage back = PSMessage::open(wire);
+        return py::make_tuple(py::bytes((const char*)wire.data(), wire.size()),
+                              py::bytes((const char*)back.ar.data(), back.ar.size()), back.meta.sid, back.meta.hid,
+                              back.meta.ctx_ver, back.meta.ctx_u_ver, (int)back.meta.req_type);
+    });
+    m.def("request_type_name", [](int t) { return std::string(request_type_name((RequestType)t)); });
+    m.def("archive_round_trip", [](int64_t i, double d, const std::string& s, const std::vector<int32_t>& v,
+                                   const std::vector<std::string>& vs) {
+        Archive ar;
+        ar << i << d << s << v << vs << Status::OOM("full");
+        int64_t i2; double d2; std::string s2; std::vector<int32_t> v2; std::vector<std::string> vs2; Status st;
+        ar >> i2 >> d2 >> s2 >> v2 >> vs2 >> st;
+        return py::make_tuple(i2, d2, s2, v2, vs2, (int)st.code(), st.msg(), ar.is_exhausted(), ar.size());
+    });
+    m.def("compress_round_trip", [](const std::string& algo, py::bytes data) {
+        Compressor c;
+        Status st = Compressor::create(algo, &c);
+        if (!st.ok()) return py::make_tuple(st, py::bytes(), (size_t)0);
+        std::string in = data;
+        std::vector<uint8_t> packed, plain;
+        st = c.compress((const uint8_t*)in.data(), in.size(), &packed);
+        if (st.ok()) st = c.decompress(packed.data(), packed.size(), &plain);
+        return py::make_tuple(st, py::bytes((const char*)plain.data(), plain.size()), packed.size());
+    });
+    m.def("heap_sort", [](std::vector<double> v) {
+        Heap<double> h;
+        for (double x : v) h.push(x);
+        std::vector<double> out;
+        while (!h.empty()) out.push_back(h.pop());
+        return out;
+    });
+    py::class_<ThreadReduce>(m, "ThreadReduce").def(py::init<>()).def("add", &ThreadReduce::add).def("reduce", &ThreadReduce::reduce);
+    py::class_<ThreadBcast>(m, "ThreadBcast")
+        .def(py::init<>())
+        .def("notify", &ThreadBcast::notify)
+        .def("wait", &ThreadBcast::wait, nogil());
+
+    // ---- table descriptor ----------------------------------------------------------------------
+    py::class_<TableDescriptor>(m, "TableDescriptor")
+        .def(py::init<>())
+        .def_readwrite("version", &TableDescriptor::version)
+        .def_readwrite("update_version", &TableDescriptor::update_version)
+        .def_readwrite("version_uuid", &TableDescriptor::version_uuid)
+        .def_readwrite("table_uri", &TableDescriptor::table_uri)
+        .def("to_json_str", &TableDescriptor::to_json_str)
+        .def("from_json_str", &TableDescriptor::from_json_str, py::arg("json"), py::arg("only_if_newer") = false)
+        .def("status", [](TableDescriptor& t) { return (int)t.status; })
+        .def("global_shard_num", &TableDescriptor::global_shard_num)
+        .def("set_nodes", [](TableDescriptor& t, const std::string& nodes_json) {
+            Json j;
+            if (!Json::parse(nodes_json, &j)) return Status::InvalidConfig("nodes JSON does not parse");
+            t.nodes.clear();
+            Status st = TableDescriptor::parse_nodes(j, &t.nodes);
+            t.refresh_info();
+            return st;
+        })
+        .def("update_node_status", [](TableDescriptor& t, const std::set<int>& live) { return t.update_node_status(live); })
+        .def("try_to_replace_one_dead_node", [](TableDescriptor& t, int my_id) { return t.try_to_replace_one_dead_node(my_id); })
+        .def("set_node_status_to_running", &TableDescriptor::set_node_status_to_running)
+        .def("create_update_info", [](TableDescriptor& t, const std::string& nodes_json) {
+            Json j;
+            std::vector<NodeDescriptor> nodes;
+            if (!Json::parse(nodes_json, &j)) return Status::InvalidConfig("nodes JSON does not parse");
+            Status st = TableDescriptor::parse_nodes(j, &nodes);
+            if (st.ok()) t.create_update_info(nodes);
+            return st;
+        })
+        .def("apply_update", &TableDescriptor::apply_update)
+        .def("drop_update", &TableDescriptor::drop_update)
+        .def("node_status", [](TableDescriptor& t) {
+            std::map<int, int> out;
+            for (auto& n : t.nodes) out[n.node_id] = (int)n.status;
+            return out;
+        })
+        .def("shards", [](TableDescriptor& t) { return t.shards; })
+        .def("pick_one_replica", [](TableDescriptor& t, int shard) { return RuntimeInfo(t, -1).pick_one_replica(shard); });
+
+    // ---- master ----------------------------------------------------------------------------------
+    py::class_<Master>(m, "Master").def(py::init<int>(), py::arg("n_threads") = 4).def("address", &Master::address).def("stop", &Master::stop, nogil());
+    py::class_<MasterClient>(m, "MasterClient")
+        .def(py::init<std::string, int>(), py::arg("address"), py::arg("timeout_ms") = 30000)
+        .def("generate_id", [](MasterClient& c, const std::string& k) { int32_t id = -1; Status st = c.generate_id(k, &id); return std::make_tuple(st, id); }, nogil())
+        .def("acquire_lock", &MasterClient::acquire_lock, nogil())
+        .def("release_lock", &MasterClient::release_lock, nogil())
+        .def("set_context", &MasterClient::set_context, py::arg("key"), py::arg("value"), py::arg("only_if_absent") = false, nogil())
+        .def("get_context", [](MasterClient& c, const std::string& k) { std::string v; Status st = c.get_context(k, &v); return std::make_tuple(st, v); }, nogil())
+        .def("delete_context", &MasterClient::delete_context, nogil())
+        .def("list_contexts", [](MasterClient& c) { std::vector<std::string> k; Status st = c.list_contexts(&k); return std::make_tuple(st, k); }, nogil())
+        .def("register_node", [](MasterClient& c, const std::string& s, const std::string& a) { int32_t id = -1; Status st = c.register_node(s, a, &id); return std::make_tuple(st, id); }, nogil())
+        .def("get_nodes", [](MasterClient& c, const std::string& s) { std::map<int32_t, std::string> n; Status st = c.get_nodes(s, &n); return std::make_tuple(st, n); }, nogil())
+        .def("barrier", &MasterClient::barrier, nogil())
+        .def("tree_node_set", &MasterClient::tree_node_set, nogil())
+        .def("tree_node_get", [](MasterClient& c, const std::string& p) { std::string v; Status st = c.tree_node_get(p, &v); return std::make_tuple(st, v); }, nogil())
+        .def("tree_node_del", &MasterClient::tree_node_del, nogil())
+        .def("close", &MasterClient::close, nogil());
+
+    // ---- server ----------------------------------------------------------------------------------
+    py::class_<ServerConfig>(m, "ServerConfig")
+        .def(py::init<>())
+        .def_readwrite("c2s_thread_num", &ServerConfig::c2s_thread_num)
+        .def_readwrite("s2s_thread_num", &ServerConfig::s2s_thread_num)
+        .def_readwrite("load_thread_num", &ServerConfig::load_thread_num)
+        .def_readwrite("load_block_size", &ServerConfig::load_block_size)
+        .def_readwrite("restore_batch_size", &ServerConfig::restore_batch_size)
+        .def_readwrite("s2s_timeout_ms", &ServerConfig::s2s_timeout_ms);
+    py::class_<Server>(m, "Server")
+        .def(py::init<const std::string&, const ServerConfig&>(), py::arg("master"), py::arg("config") = ServerConfig(), nogil())
+        .def("node_id", &Server::node_id)
+        .def("c2s_address", &Server::c2s_address)
+        .def("s2s_address", &Server::s2s_address)
+        .def("exited", &Server::exited)
+        .def("stop", &Server::stop, nogil())
+        .def("metrics", &Server::metrics)
+        .def("restore_storages", [](Server& s) { int n = 0; Status st = s.restore_storages(&n); return std::make_tuple(st, n); }, nogil())
+        .def("enable_sync", &Server::enable_sync)
+        .def("push_sync_table", [](Server& s, int32_t sid, SyncHandler& h) {
+            uint64_t n = 0;
+            Status st = s.push_sync_table(sid, h.block_size(), [&](const int64_t* k, const float* r, size_t m, uint32_t stride) {
+                return h.sync_block(k, r, m, stride);
+            }, &n);
+            return std::make_tuple(st, n);
+        }, nogil())
+        .def("storage_size", [](Server& s, int32_t sid) -> int64_t {
+            auto e = s.context().get(sid);
+            return e && e->storage ? (int64_t)e->storage->size() : -1;
+        })
+        .def("set_memory_limit", [](Server& s, int32_t sid, uint64_t limit) {
+            auto e = s.context().get(sid);
+            if (!e || !e->storage) return Status::InvalidID("no such storage");
+            e->storage->set_limits(limit, limit);
+            return Status::Ok();
+        })
+        .def("set_healthy", [](Server& s, int32_t sid, bool h) {
+            auto e = s.context().get(sid);
+            if (e && e->storage) e->storage->set_healthy(h);
+        });
+
+    m.def("register_udf", [](const std::string& name, py::function fn) {
+        // fn(storage_id: int, node_items: int, param: bytes) -> bytes
+        auto holder = std::make_shared<py::function>(std::move(fn));
+        UDFRegistry::instance().add(name, [holder](TableEntry& e, const std::string& param, std::string* result) {
+            py::gil_scoped_acquire gil;
+            try {
+                py::object r = (*holder)(e.sid, e.storage ? (int64_t)e.storage->size() : (int64_t)-1, py::bytes(param));
+                *result = (std::string)py::bytes(r);
+            } catch (const std::exception& ex) {
+                return Status::Error(std::string("udf raised: ") + ex.what());
+            }
+            return Status::Ok();
+        });
+    });
+
+    // ---- client + handlers -----------------------------------------------------------------------
+    py::class_<StorageStatisticInfo>(m, "StorageStatisticInfo")
+        .def_readonly("item_number", &StorageStatisticInfo::item_number)
+        .def_readonly("memory_usage", &StorageStatisticInfo::memory_usage)
+        .def_readonly("node_id", &StorageStatisticInfo::node_id)
+        .def_readonly("shard_id", &StorageStatisticInfo::shard_id);
+
+    py::class_<Client>(m, "Client")
+        .def(py::init<const std::string&>(), py::arg("master"))
+        .def("get_pserver_list", [](Client& c) { std::map<int32_t, std::string> n; Status st = c.get_pserver_list(&n); return std::make_tuple(st, n); }, nogil())
+        .def("create_storage", [](Client& c, const std::string& lib, const std::string& op, const std::string& cfg) {
+            int32_t sid = -1;
+            Status st = c.create_storage(lib, op, cfg, &sid);
+            return std::make_tuple(st, sid);
+        }, nogil())
+        .def("initialize_storage", &Client::initialize_storage, nogil())
+        .def("delete_storage", &Client::delete_storage, py::arg("sid"), py::arg("timeout_ms") = 30000, nogil())
+        .def("clear_storage", &Client::clear_storage, py::arg("sid"), py::arg("timeout_ms") = 30000, nogil())
+        .def("query_storage_info", [](Client& c, int32_t sid) {
+            std::vector<StorageStatisticInfo> info;
+            Status st = c.query_storage_info(sid, &info);
+            return std::make_tuple(st, info);
+        }, nogil())
+        .def("query_memory_info", [](Client& c, int node) {
+            NodeMemoryInfo mi;
+            Status st = c.query_memory_info(node, &mi);
+            return std::make_tuple(st, mi.healthy, mi.used, mi.managed);
+        }, nogil())
+        .def("health_check", &Client::health_check, py::arg("node"), py::arg("timeout_ms") = 2000, nogil())
+        .def("close_pserver", &Client::close_pserver, py::arg("node"), py::arg("timeout_ms") = 5000, nogil())
+        .def("load_operator_library", &Client::load_operator_library, py::arg("path"), py::arg("timeout_ms") = 30000, nogil())
+        .def("register_handler", [](Client& c, const std::string& key, const std::string& lib, const std::string& op,
+                                    const std::string& cfg, int32_t sid) {
+            int32_t hid = -1;
+            Status st = c.register_handler(key, lib, op, cfg, sid, &hid);
+            return std::make_tuple(st, hid);
+        }, nogil())
+        .def("deregister_handler", &Client::deregister_handler, py::arg("sid"), py::arg("hid"), py::arg("timeout_ms") = 30000, nogil())
+        .def("handler_by_key", [](Client& c, int32_t sid, const std::string& key) { int32_t h = -1; Status st = c.handler_by_key(sid, key, &h); return py::make_tuple(st, h); })
+        .def("set_table_uri", &Client::set_table_uri, nogil())
+        .def("get_current_ctx", [](Client& c, int32_t sid) { std::string j; Status st = c.get_current_ctx(sid, &j); return py::make_tuple(st, j); })
+        .def("set_ctx", &Client::set_ctx, nogil())
+        .def("pull_context", &Client::pull_context, nogil())
+        .def("notify_ctx_update", [](Client& c, int32_t sid) {
+            auto e = c.context().get(sid);
+            if (!e) return Status::InvalidID("unknown storage");
+            return c.require_update_ctx_nolock(sid, Client::all_nodes(*e));
+        }, nogil())
+        .def("handle_timeout", &Client::handle_timeout, nogil())
+        .def("handle_out_of_memory", &Client::handle_out_of_memory, nogil());
+
+    py::class_<PullHandler>(m, "PullHandler")
+        .def(py::init(&make_handler<PullHandler>), py::keep_alive<1, 2>())
+        .def("dim", &PullHandler::dim)
+        .def("metrics", [](PullHandler& h) { return metrics_dict(h); })
+        .def("pull", [](PullHandler& h, KeyArray keys, int timeout_ms, bool auto_retry) {
+            F32Array out({(py::ssize_t)keys.size(), (py::ssize_t)h.dim()});
+            Status st;
+            {
+                py::gil_scoped_release g;
+                st = h.pull(keys.data(), (size_t)keys.size(), out.mutable_data(), timeout_ms, auto_retry);
+            }
+            return py::make_tuple(st, out);
+        }, py::arg("keys"), py::arg("timeout_ms") = -1, py::arg("auto_retry") = true)
+        .def("pull_dense", [](PullHandler& h, int64_t id, size_t numel, int timeout_ms) {
+            F32Array out((py::ssize_t)numel);
+            Status st;
+            {
+                py::gil_scoped_release g;
+                st = h.pull_dense(id, numel, out.mutable_data(), timeout_ms);
+            }
+            return py::make_tuple(st, out);
+        }, py::arg("id"), py::arg("numel"), py::arg("timeout_ms") = -1);
+
+    py::class_<PushHandler>(m, "PushHandler")
+        .def(py::init(&make_handler<PushHandler>), py::keep_alive<1, 2>())
+        .def("metrics", [](PushHandler& h) { return metrics_dict(h); })
+        .def("async_push", [](PushHandler& h, KeyArray keys, F32Array grads, int timeout_ms) {
+            py::gil_scoped_release g;
+            return h.async_push(keys.data(), grads.data(), (size_t)keys.size(), timeout_ms);
+        }, py::arg("keys"), py::arg("grads"), py::arg("timeout_ms") = -1)
+        .def("sync_push", [](PushHandler& h, KeyArray keys, F32Array grads, int timeout_ms) {
+            py::gil_scoped_release g;
+            return h.sync_push(keys.data(), grads.data(), (size_t)keys.size(), timeout_ms);
+        }, py::arg("keys"), py::arg("grads"), py::arg("timeout_ms") = -1)
+        .def("store", &PushHandler::store, py::arg("timeout_ms") = -1, nogil())
+        .def("push_dense", [](PushHandler& h, int64_t id, F32Array grad, bool sync, int timeout_ms) {
+            py::gil_scoped_release g;
+            return h.push_dense(id, grad.data(), (size_t)grad.size(), sync, timeout_ms);
+        }, py::arg("id"), py::arg("grad"), py::arg("sync") = false, py::arg("timeout_ms") = -1);
+
+    py::class_<ForEachHandler>(m, "ForEachHandler")
+        .def(py::init(&make_handler<ForEachHandler>), py::keep_alive<1, 2>())
+        .def("for_each", [](ForEachHandler& h, const std::string& carried, int timeout_ms) {
+            ForEachResult r;
+            Status st;
+            {
+                py::gil_scoped_release g;
+                st = h.for_each(carried, &r, timeout_ms);
+            }
+            py::dict d;
+            d["count"] = r.count; d["sum"] = r.sum; d["sum_sq"] = r.sum_sq; d["max_abs"] = r.max_abs;
+            return py::make_tuple(st, d);
+        }, py::arg("carried") = "{}", py::arg("timeout_ms") = -1);
+
+    py::class_<EraseIfHandler>(m, "EraseIfHandler")
+        .def(py::init(&make_handler<EraseIfHandler>), py::keep_alive<1, 2>())
+        .def("erase_if", [](EraseIfHandler& h, const std::string& carried, int timeout_ms) {
+            uint64_t n = 0;
+            py::gil_scoped_release g;
+            Status st = h.erase_if(carried, &n, timeout_ms);
+            return std::make_pair(st, n);
+        }, py::arg("carried"), py::arg("timeout_ms") = -1);
+
+    py::class_<DumpHandler>(m, "DumpHandler")
+        .def(py::init(&make_handler<DumpHandler>), py::keep_alive<1, 2>())
+        .def("dump", [](DumpHandler& h, const std::string& uri, int file_number, int timeout_ms) {
+            DumpArgs a;
+            a.uri = uri;
+            a.file_number = file_number;
+            uint64_t n = 0;
+            py::gil_scoped_release g;
+            Status st = h.dump(a, &n, timeout_ms);
+            return std::make_pair(st, n);
+        }, py::arg("uri"), py::arg("file_number") = 1, py::arg("timeout_ms") = -1);
+
+    py::class_<LoadHandler>(m, "LoadHandler")
+        .def(py::init(&make_handler<LoadHandler>), py::keep_alive<1, 2>())
+        .def("load", [](LoadHandler& h, const std::string& uri, int conc, int timeout_ms) {
+            uint64_t n = 0;
+            py::gil_scoped_release g;
+            Status st = h.load(uri, &n, conc, timeout_ms);
+            return std::make_pair(st, n);
+        }, py::arg("uri"), py::arg("server_concurrency") = 4, py::arg("timeout_ms") = -1)
+        .def("restore", [](LoadHandler& h, const std::string& uri, bool drop, int timeout_ms) {
+            uint64_t n = 0;
+            py::gil_scoped_release g;
+            Status st = h.restore(uri, &n, drop, timeout_ms);
+            return std::make_pair(st, n);
+        }, py::arg("uri"), py::arg("drop") = false, py::arg("timeout_ms") = -1);
+
+    py::class_<UpdateContextHandler>(m, "UpdateContextHandler")
+        .def(py::init(&make_handler<UpdateContextHandler>), py::keep_alive<1, 2>())
+        .def("update_context", &UpdateContextHandler::update_context, py::arg("nodes_json"), py::arg("timeout_ms") = 60000, nogil())
+        .def("purge", &UpdateContextHandler::purge, py::arg("timeout_ms") = 60000, nogil());
+
+    py::class_<SyncHandler>(m, "SyncHandler")
+        .def(py::init(&make_handler<SyncHandler>), py::keep_alive<1, 2>())
+        .def("block_size", &SyncHandler::block_size)
+        .def("sync_block", [](SyncHandler& h, KeyArray keys, F32Array rows, int timeout_ms) {
+            const uint32_t stride = (uint32_t)(rows.size() / std::max<py::ssize_t>(1, keys.size()));
+            py::gil_scoped_release g;
+            return h.sync_block(keys.data(), rows.data(), (size_t)keys.size(), stride, timeout_ms);
+        }, py::arg("keys"), py::arg("rows"), py::arg("timeout_ms") = 30000);
+
+    py::class_<UDFHandler>(m, "UDFHandler")
+        .def(py::init(&make_handler<UDFHandler>), py::keep_alive<1, 2>())
+        .def("call", [](UDFHandler& h, py::bytes param, int timeout_ms, bool retry) {
+            std::vector<std::pair<int, std::string>> rs;
+            std::string p = param;
+            Status st;
+            {
+                py::gil_scoped_release g;
+                st = h.call(p, &rs, timeout_ms, retry);
+            }
+            py::list out;
+            for (auto& r : rs) out.append(py::make_tuple(r.first, py::bytes(r.second)));
+            return py::make_tuple(st, out);
+        }, py::arg("param"), py::arg("timeout_ms") = -1, py::arg("retry") = true);
+
+    // ---- controller / model ------------------------------------------------------------------------
+    py::class_<OpSpec>(m, "OpSpec")
+        .def(py::init([](std::string key, std::string lib, std::string op, std::string cfg) { return OpSpec{key, lib, op, cfg}; }),
+             py::arg("key"), py::arg("lib"), py::arg("op"), py::arg("config") = "{}");
+    py::class_<Controller>(m, "Controller")
+        .def(py::init<const std::string&>(), py::arg("master"))
+        .def("client", &Controller::client, py::return_value_policy::reference_internal)
+        .def("load_nodes", [](Controller& c) { std::vector<int> n; Status st = c.load_nodes(&n); return std::make_tuple(st, n); }, nogil())
+        .def("create_table", [](Controller& c, const std::string& name, const std::string& lib, const std::string& sop,
+                                const std::string& cfg, int shards, int replicas, const std::vector<OpSpec>& ops,
+                                const std::string& uri) {
+            int32_t sid = -1;
+            Status st = c.create_table(name, lib, sop, cfg, shards, replicas, ops, uri, &sid);
+            return std::make_tuple(st, sid);
+        }, py::arg("table_name"), py::arg("lib"), py::arg("storage_op"), py::arg("op_config"), py::arg("shard_num"),
+           py::arg("replica_num"), py::arg("ops"), py::arg("table_uri") = "", nogil())
+        .def("delete_table", &Controller::delete_table, nogil())
+        .def("balance_table", &Controller::balance_table, nogil())
+        .def("update_table_shard", &Controller::update_table_shard, nogil())
+        .def("update_table_replica", &Controller::update_table_replica, nogil())
+        .def("update_table", &Controller::update_table, nogil())
+        .def("expand_storage_nodes", &Controller::expand_storage_nodes, nogil())
+        .def("expand_nodes", &Controller::expand_nodes, nogil())
+        .def("clean_unused_storage", [](Controller& c) { int n = 0; Status st = c.clean_unused_storage(&n); return std::make_tuple(st, n); }, nogil())
+        .def("shutdown_node", &Controller::shutdown_node, nogil())
+        .def("show_node", [](Controller& c, int node) { Json j; Status st = c.show_node(node, &j); return std::make_tuple(st, j.dump()); }, nogil())
+        .def("show_nodes", [](Controller& c) { Json j; Status st = c.show_nodes(&j); return std::make_tuple(st, j.dump()); }, nogil())
+        .def("gen_table_json", [](Controller& c, int32_t sid) { Json j; Status st = c.gen_table_json(sid, &j); return std::make_tuple(st, j.dump()); }, nogil());
+
+    m.def("model_round_trip", [](const std::string& json) {
+        Json j;
+        if (!Json::parse(json, &j)) return std::string();
+        ModelObject mo = ModelObject::from_json(j);
+        std::vector<const TableObject*> ts;
+        mo.all_tables(&ts);
+        std::vector<const OperatorObject*> os;
+        mo.all_operators(&os);
+        Json out = mo.to_json();
+        out["n_tables"] = (int)ts.size();
+        out["n_operators"] = (int)os.size();
+        return out.dump();
+    });
+    m.def("set_model", [](MasterClient& mc, const std::string& json) {
+        Json j;
+        if (!Json::parse(json, &j)) return Status::InvalidConfig("model JSON does not parse");
+        return set_model(mc, ModelObject::from_json(j));
+    });
+    m.def("get_model", [](MasterClient& mc, const std::string& name) {
+        ModelObject mo;
+        Status st = get_model(mc, name, &mo);
+        return py::make_tuple(st, st.ok() ? mo.to_json().dump() : std::string());
+    });
+
+    // ---- native PS -----------------------------------------------------------------------------------
+    py::class_<NativePS>(m, "NativePS")
+        .def(py::init<>())
+        .def("create_storage", [](NativePS& p, const std::string& lib, const std::string& op, const std::string& cfg, int shards) {
+            int32_t sid = -1;
+            Status st = p.create_storage(lib, op, cfg, shards, &sid);
+            return py::make_tuple(st, sid);
+        })
+        .def("register_handler", [](NativePS& p, int32_t sid, const std::string& key, const std::string& lib, const std::string& op,
+                                    const std::string& cfg) {
+            int32_t hid = -1;
+            Status st = p.register_handler(sid, key, lib, op, cfg, &hid);
+            return py::make_tuple(st, hid);
+        })
+        .def("size", [](NativePS& p, int32_t sid) -> int64_t {
+            auto e = p.entry(sid);
+            return e && e->storage ? (int64_t)e->storage->size() : -1;
+        });
+    py::class_<NativePullHandler>(m, "NativePullHandler")
+        .def(py::init<NativePS*, int32_t, int32_t>(), py::keep_alive<1, 2>())
+        .def("pull", [](NativePullHandler& h, KeyArray keys, int dim) {
+            F32Array out({(py::ssize_t)keys.size(), (py::ssize_t)dim});
+            Status st = h.pull(keys.data(), (size_t)keys.size(), out.mutable_data());
+            return py::make_tuple(st, out);
+        });
+    py::class_<NativeLoadHandler>(m, "NativeLoadHandler")
+        .def(py::init<NativePS*, int32_t, int32_t>(), py::keep_alive<1, 2>())
+        .def("load", [](NativeLoadHandler& h, const std::string& uri, int threads) {
+            uint64_t n = 0;
+            py::gil_scoped_release g;
+            Status st = h.load(uri, threads, &n);
+            return std::make_pair(st, n);
+        }, py::arg("uri"), py::arg("threads") = 4);
+}

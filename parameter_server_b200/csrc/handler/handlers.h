@@ -1,0 +1,525 @@
+// Handlers: the client-side façade of each operator, with the automatic retry policy.
+//
+// Parity: pico-ps/handler/Handler.{h,cpp} (wait() = wait_no_release + retry loop: Timeout / NoReplica
+// -> dead-node detection then retry (NoReplica only once); ServerTooNewCtx -> refresh the context then
+// retry; OutOfMemory -> wait for a context change then retry; anything else goes to the caller;
+// remaining-time bookkeeping), PullHandler / PushHandler / ForEachHandler / EraseIfHandler /
+// DumpHandler / LoadHandler / UpdateContextHandler / SyncHandler / UDFHandler of pico-ps/handler/*.
+// UpdateContextHandler and SyncHandler never auto-retry (pico-ps/handler/UpdateContextHandler.cpp:
+// 275-277, pico-ps/handler/SyncHandler.h:32-34). Counters mirror ps_wait_request_count /
+// ps_pull_send_request_count (pico-ps/handler/Handler.cpp:14-18, pico-ps/handler/PullHandler.cpp:11-15).
+#pragma once
+#include <atomic>
+#include <chrono>
+#include <functional>
+
+#include "../service/client.h"
+
+namespace psb {
+
+struct HandlerMetrics {
+    std::atomic<uint64_t> requests{0}, retries{0}, errors{0};
+    std::atomic<uint64_t> wait_us{0};
+};
+
+class Handler {
+public:
+    Handler(Client* client, int32_t sid, int32_t hid) : client_(client), sid_(sid), hid_(hid) {}
+    virtual ~Handler() = default;
+    int32_t storage_id() const { return sid_; }
+    int32_t handler_id() const { return hid_; }
+    HandlerMetrics& metrics() { return metrics_; }
+
+protected:
+    std::shared_ptr<TableEntry> entry() { return client_->context().get(sid_); }
+
+    template <class OP>
+    Status op(std::shared_ptr<OP>* out) {
+        auto e = entry();
+        if (!e) return Status::InvalidID("storage " + std::to_string(sid_) + " is not initialised on this client");
+        std::shared_lock<std::shared_mutex> g(e->mu);
+        auto it = e->ops.find(hid_);
+        if (it == e->ops.end()) return Status::InvalidID("handler " + std::to_string(hid_) + " is not registered");
+        *out = std::dynamic_pointer_cast<OP>(it->second);
+        if (!*out) return Status::InvalidID("handler " + std::to_string(hid_) + " has another operator type");
+        return Status::Ok();
+    }
+
+    // Runs `attempt` (which builds the requests against the CURRENT context and waits for them) under
+    // the retry policy. `timeout_ms` < 0 means no limit.
+    Status with_retry(const std::function<Status(int remaining_ms)>& attempt, int timeout_ms, bool auto_retry = true) {
+        auto t0 = std::chrono::steady_clock::now();
+        auto remaining = [&]() -> int {
+            if (timeout_ms < 0) return -1;
+            long el = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+            return (int)std::max<long>(0, timeout_ms - el);
+        };
+        bool no_replica_retried = false;
+        Status st;
+        for (int round = 0;; ++round) {
+            ++metrics_.requests;
+            st = attempt(remaining());
+            if (st.ok() || !auto_retry) break;
+            const int left = remaining();
+            if (timeout_ms >= 0 && left == 0) break;
+            if (st.is(StatusCode::TIMEOUT) || st.is(StatusCode::NO_REPLICA)) {
+                if (st.is(StatusCode::NO_REPLICA)) {
+                    if (no_replica_retried) break;
+                    no_replica_retried = true;
+                }
+                Status h = client_->handle_timeout(sid_);
+                if (!h.ok()) break;
+            } else if (st.is(StatusCode::SERVER_TOO_NEW_CTX) || st.is(StatusCode::SERVER_TOO_NEW_CTX_U)) {
+                if (!client_->handle_server_too_new_ctx(sid_).ok()) break;
+            } else if (st.is(StatusCode::OUT_OF_MEMORY)) {
+                if (!client_->handle_out_of_memory(sid_, left).ok()) break;
+            } else {
+                break;
+            }
+            ++metrics_.retries;
+            if (round > 64) break;
+        }
+        if (!st.ok()) ++metrics_.errors;
+        metrics_.wait_us += (uint64_t)std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
+        return st;
+    }
+
+    Client* client_;
+    int32_t sid_, hid_;
+    HandlerMetrics metrics_;
+};
+
+// ---------------------------------------------------------------------------------------------------
+class PullHandler : public Handler {
+public:
+    using Handler::Handler;
+    // out: n * dim floats, one row per key position.
+    Status pull(const int64_t* keys, size_t n, float* out, int timeout_ms = -1, bool auto_retry = true) {
+        std::shared_ptr<SparseTablePullOperator> p;
+        PSB_RETURN_IF_ERROR(op(&p));
+        return with_retry([&](int left) -> Status {
+            auto e = entry();
+            PullRequestData data;
+            NodeRequests reqs;
+            {
+                std::shared_lock<std::shared_mutex> g(e->mu);
+                p->generate_request_data(*e, keys, n, &data);
+                PSB_RETURN_IF_ERROR(p->generate_requests(*e, data, &reqs));
+            }
+            std::vector<NodeResponse> rs;
+            PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_PULL, reqs.body, left, &rs));
+            for (auto& r : rs) PSB_RETURN_IF_ERROR(p->apply_response(*e, &data, r.body));
+            p->fill_pull_items(*e, data, out);
+            return Status::Ok();
+        }, timeout_ms, auto_retry);
+    }
+    // Dense pull: tensor `id` of `numel` floats, reassembled from its slices.
+    Status pull_dense(int64_t id, size_t numel, float* out, int timeout_ms = -1) {
+        auto e = entry();
+        if (!e) return Status::InvalidID("storage is not initialised on this client");
+        const uint32_t slice = storage_op_of(*e)->dim();
+        std::vector<int64_t> keys;
+        dense_slice_keys(id, numel, slice, &keys);
+        std::vector<float> tmp(keys.size() * slice);
+        PSB_RETURN_IF_ERROR(pull(keys.data(), keys.size(), tmp.data(), timeout_ms));
+        std::copy_n(tmp.data(), numel, out);
+        return Status::Ok();
+    }
+    uint32_t dim() {
+        auto e = entry();
+        return e ? storage_op_of(*e)->dim() : 0;
+    }
+};
+
+class PushHandler : public Handler {
+public:
+    using Handler::Handler;
+    Status async_push(const int64_t* keys, const float* grads, size_t n, int timeout_ms = -1) {
+        return push(keys, grads, n, RequestType::OP_PUSH_ASYNC, timeout_ms);
+    }
+    Status sync_push(const int64_t* keys, const float* grads, size_t n, int timeout_ms = -1) {
+        return push(keys, grads, n, RequestType::OP_PUSH_SYNC, timeout_ms);
+    }
+    // Fold everything sync_push buffered; one request per (node, shard) as in the reference.
+    Status store(int timeout_ms = -1) {
+        return with_retry([&](int left) -> Status {
+            auto e = entry();
+            std::map<int, Archive> bodies;
+            {
+                std::shared_lock<std::shared_mutex> g(e->mu);
+                for (auto& kv : e->rt.nodes()) bodies[kv.first] << (int32_t)(kv.second.empty() ? -1 : kv.second.front());
+            }
+            return client_->send_and_wait(sid_, hid_, RequestType::OP_STORE, bodies, left, nullptr);
+        }, timeout_ms);
+    }
+    Status push_dense(int64_t id, const float* grad, size_t numel, bool sync, int timeout_ms = -1) {
+        auto e = entry();
+        if (!e) return Status::InvalidID("storage is not initialised on this client");
+        const uint32_t slice = storage_op_of(*e)->dim();
+        std::vector<int64_t> keys;
+        dense_slice_keys(id, numel, slice, &keys);
+        std::vector<float> tmp(keys.size() * slice, 0.f);
+        std::copy_n(grad, numel, tmp.data());
+        return push(keys.data(), tmp.data(), keys.size(), sync ? RequestType::OP_PUSH_SYNC : RequestType::OP_PUSH_ASYNC, timeout_ms);
+    }
+
+private:
+    Status push(const int64_t* keys, const float* grads, size_t n, RequestType type, int timeout_ms) {
+        std::shared_ptr<SparseTablePushOperator> p;
+        PSB_RETURN_IF_ERROR(op(&p));
+        return with_retry([&](int left) -> Status {
+            auto e = entry();
+            PushRequestData data;
+            NodeRequests reqs;
+            {
+                std::shared_lock<std::shared_mutex> g(e->mu);
+                p->generate_request_data(*e, keys, grads, n, &data);  // regenerated against the fresh context on retry
+                PSB_RETURN_IF_ERROR(p->generate_requests(*e, data, &reqs));
+            }
+            return client_->send_and_wait(sid_, hid_, type, reqs.body, left, nullptr);
+        }, timeout_ms);
+    }
+};
+
+class ForEachHandler : public Handler {
+public:
+    using Handler::Handler;
+    // One request per (node, shard); results merged on the client.
+    Status for_each(const std::string& carried_json, ForEachResult* result, int timeout_ms = -1) {
+        return with_retry([&](int left) -> Status {
+            *result = ForEachResult();
+            auto e = entry();
+            std::vector<std::pair<int, int32_t>> targets;
+            {
+                std::shared_lock<std::shared_mutex> g(e->mu);
+                for (auto& kv : e->rt.shards()) {
+                    int node = e->rt.pick_one_replica(kv.first);
+                    if (node < 0) return Status::NoReplica("for_each: no live replica of shard " + std::to_string(kv.first));
+                    targets.push_back({node, kv.first});
+                }
+            }
+            for (auto& t : targets) {
+                std::map<int, Archive> body;
+                body[t.first] << t.second << carried_json;
+                std::vector<NodeResponse> rs;
+                PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_FOREACH, body, left, &rs));
+                ForEachResult r;
+                rs[0].body >> r.count >> r.sum >> r.sum_sq >> r.max_abs;
+                result->merge(r);
+            }
+            return Status::Ok();
+        }, timeout_ms);
+    }
+};
+
+class EraseIfHandler : public Handler {
+public:
+    using Handler::Handler;
+    // Every holder of every shard applies the predicate (replicas stay identical).
+    Status erase_if(const std::string& carried_json, uint64_t* erased, int timeout_ms = -1) {
+        return with_retry([&](int left) -> Status {
+            *erased = 0;
+            auto e = entry();
+            std::vector<std::pair<int, int32_t>> targets;
+            std::map<int32_t, int> primary;
+            {
+                std::shared_lock<std::shared_mutex> g(e->mu);
+                for (auto& kv : e->rt.shards())
+                    for (int node : kv.second) {
+                        targets.push_back({node, kv.first});
+                        if (!primary.count(kv.first)) primary[kv.first] = node;
+                    }
+            }
+            for (auto& t : targets) {
+                std::map<int, Archive> body;
+                body[t.first] << t.second << carried_json;
+                std::vector<NodeResponse> rs;
+                PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_ERASEIF, body, left, &rs));
+                uint64_t n = 0;
+                rs[0].body >> n;
+                if (primary[t.second] == t.first) *erased += n;
+            }
+            return Status::Ok();
+        }, timeout_ms);
+    }
+};
+
+class DumpHandler : public Handler {
+public:
+    using Handler::Handler;
+    // One request per (node, file): shard -> file by shard_id % file_number.
+    Status dump(const DumpArgs& args, uint64_t* n_records, int timeout_ms = -1) {
+        std::string dir, format;
+        DumpArgs::split_uri(args.uri, &dir, &format);
+        PSB_RETURN_IF_ERROR(mkdir_p(dir));
+        return with_retry([&](int left) -> Status {
+            *n_records = 0;
+            auto e = entry();
+            std::map<int, std::map<int32_t, std::vector<int32_t>>> plan;  // node -> file -> shards
+            {
+                std::shared_lock<std::shared_mutex> g(e->mu);
+                // every shard is dumped once: by its first live holder
+                for (auto& kv : e->rt.shards()) {
+                    int node = -1;
+                    for (int n : kv.second)
+                        if (e->rt.is_running(n)) { node = n; break; }
+                    if (node < 0) return Status::NoReplica("dump: no live replica of shard " + std::to_string(kv.first));
+                    plan[node][kv.first % args.file_number].push_back(kv.first);
+                }
+            }
+            for (auto& nk : plan)
+                for (auto& fk : nk.second) {
+                    std::map<int, Archive> body;
+                    body[nk.first] << args.uri << args.file_number << fk.first << fk.second;
+                    std::vector<NodeResponse> rs;
+                    PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_DUMP, body, left, &rs));
+                    uint64_t n = 0;
+                    rs[0].body >> n;
+                    *n_records += n;
+                }
+            return Status::Ok();
+        }, timeout_ms);
+    }
+};
+
+class LoadHandler : public Handler {
+public:
+    using Handler::Handler;
+    // load: rehash through the push path (any old / new sharding). Files are dealt to the servers with at
+    // most `server_concurrency` outstanding per server.
+    Status load(const std::string& uri, uint64_t* n_records, int server_concurrency = 4, int timeout_ms = -1) {
+        return run(uri, true, n_records, server_concurrency, timeout_ms);
+    }
+    // restore: same sharding as the dump; every server reads all files and keeps its local keys.
+    Status restore(const std::string& uri, uint64_t* n_records, bool drop = false, int timeout_ms = -1) {
+        Status st = run(uri, false, n_records, 1, timeout_ms);
+        if (st.ok() && drop) {
+            std::string dir, format;
+            DumpArgs::split_uri(uri, &dir, &format);
+            for (auto& f : list_model_files(dir)) ::remove(f.c_str());
+        }
+        return st;
+    }
+
+private:
+    Status run(const std::string& uri, bool rehash, uint64_t* n_records, int conc, int timeout_ms) {
+        std::string dir, format;
+        DumpArgs::split_uri(uri, &dir, &format);
+        std::vector<std::string> files = list_model_files(dir);
+        if (files.empty()) return Status::Error("load: no model_* files under " + dir);
+        return with_retry([&](int left) -> Status {
+            *n_records = 0;
+            auto e = entry();
+            std::vector<int> nodes;
+            {
+                std::shared_lock<std::shared_mutex> g(e->mu);
+                for (auto& kv : e->rt.nodes())
+                    if (e->rt.is_running(kv.first)) nodes.push_back(kv.first);
+            }
+            if (nodes.empty()) return Status::NoReplica("load: no live server");
+            std::map<int, std::vector<std::string>> deal;
+            if (rehash) {
+                for (size_t i = 0; i < files.size(); ++i) deal[nodes[i % nodes.size()]].push_back(files[i]);
+            } else {
+                for (int n : nodes) deal[n] = files;
+            }
+            // waves of at most `conc` files per server
+            for (size_t wave = 0;; ++wave) {
+                std::map<int, Archive> bodies;
+                for (auto& kv : deal) {
+                    std::vector<std::string> part;
+                    for (size_t i = wave * conc; i < std::min<size_t>(kv.second.size(), (wave + 1) * conc); ++i) part.push_back(kv.second[i]);
+                    if (!part.empty()) bodies[kv.first] << uri << (int32_t)(rehash ? 1 : 0) << part;
+                }
+                if (bodies.empty()) break;
+                std::vector<NodeResponse> rs;
+                PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_LOAD, bodies, left, &rs));
+                for (auto& r : rs) {
+                    uint64_t n = 0;
+                    r.body >> n;
+                    *n_records += n;
+                }
+            }
+            return Status::Ok();
+        }, timeout_ms);
+    }
+};
+
+// The reshard / rebalance / replica-change transaction (7 steps; reads are served throughout, writes are
+// refused between step 1 and step 7).
+class UpdateContextHandler : public Handler {
+public:
+    using Handler::Handler;
+    // new_nodes_json: [{"g_rank":..,"shard_list":[..]}, ...]
+    Status update_context(const std::string& new_nodes_json, int timeout_ms = 60000) {
+        Json nodes_cfg;
+        if (!Json::parse(new_nodes_json, &nodes_cfg)) return Status::InvalidConfig("update_context: nodes JSON does not parse");
+        std::vector<NodeDescriptor> new_nodes;
+        PSB_RETURN_IF_ERROR(TableDescriptor::parse_nodes(nodes_cfg, &new_nodes));
+        MasterClient& m = client_->master();
+        std::set<int> involved;
+        int32_t ver = 0, uver = 0;
+        // 1. prepare: publish the update info, status RESHARD (from now on writes get OUT_OF_MEMORY)
+        PSB_RETURN_IF_ERROR(m.acquire_lock(PSERVER_LOCK_NAME));
+        Status st = [&]() -> Status {
+            PSB_RETURN_IF_ERROR(client_->pull_context_nolock(sid_));
+            auto e = entry();
+            {
+                std::unique_lock<std::shared_mutex> g(e->mu);
+                if (e->td.status != StorageStatus::NORMAL) return Status::Error("update_context: table is not in NORMAL state");
+                e->td.create_update_info(new_nodes);
+                e->update_rt.build(e->td, -1, true);
+                ver = e->td.version;
+                uver = e->td.update_version;
+            }
+            involved = Client::all_nodes(*e);
+            PSB_RETURN_IF_ERROR(client_->push_context_nolock(sid_));
+            return client_->require_update_ctx_nolock(sid_, involved, timeout_ms);
+        }();
+        m.release_lock(PSERVER_LOCK_NAME);
+        PSB_RETURN_IF_ERROR(st);
+        auto e = entry();
+        std::set<int> new_set;
+        for (auto& n : new_nodes) new_set.insert(n.node_id);
+        // 2. create the shards of the new placement
+        st = client_->broadcast(sid_, RequestType::NEW_CTX_CREATE_SHARD, new_set, Archive(), timeout_ms, ver, uver);
+        // 3. shuffle: one request per old shard to one live replica
+        if (st.ok()) {
+            std::vector<std::pair<int, int32_t>> targets;
+            {
+                std::shared_lock<std::shared_mutex> g(e->mu);
+                for (auto& kv : e->rt.shards()) {
+                    int node = e->rt.pick_one_replica(kv.first);
+                    if (node < 0) { st = Status::NoReplica("shuffle: no live replica of shard " + std::to_string(kv.first)); break; }
+                    targets.push_back({node, kv.first});
+                }
+            }
+            for (auto& t : targets) {
+                if (!st.ok()) break;
+                std::map<int, Archive> body;
+                body[t.first] << t.second;
+                st = client_->send_and_wait(sid_, hid_, RequestType::NEW_CTX_SHUFFLE, body, timeout_ms, nullptr, ver, uver);
+            }
+        }
+        // 4. store
+        if (st.ok()) st = client_->broadcast(sid_, RequestType::NEW_CTX_STORE, new_set, Archive(), timeout_ms, ver, uver);
+        if (!st.ok()) {
+            purge(timeout_ms);
+            return st;
+        }
+        // 5. commit the new placement (readers switch)
+        PSB_RETURN_IF_ERROR(m.acquire_lock(PSERVER_LOCK_NAME));
+        st = [&]() -> Status {
+            std::string json;
+            PSB_RETURN_IF_ERROR(m.get_context(ctx_key(sid_), &json));
+            TableDescriptor cur;
+            cur.from_json_str(json);
+            if (cur.version != ver || cur.update_version != uver) return Status::Error("update_context: context changed under the transaction");
+            {
+                std::unique_lock<std::shared_mutex> g(e->mu);
+                e->td.apply_update();
+                e->rt.build(e->td, -1);
+                e->update_rt.build(e->td, -1, true);
+            }
+            PSB_RETURN_IF_ERROR(client_->push_context_nolock(sid_));
+            return client_->require_update_ctx_nolock(sid_, involved, timeout_ms);
+        }();
+        m.release_lock(PSERVER_LOCK_NAME);
+        if (!st.ok()) {
+            purge(timeout_ms);
+            return st;
+        }
+        // 6. purge what no longer belongs
+        client_->broadcast(sid_, RequestType::NEW_CTX_PURGE, involved, Archive(), timeout_ms, -1);
+        // 7. back to NORMAL (writes resume)
+        PSB_RETURN_IF_ERROR(m.acquire_lock(PSERVER_LOCK_NAME));
+        st = [&]() -> Status {
+            {
+                std::unique_lock<std::shared_mutex> g(e->mu);
+                e->td.status = StorageStatus::NORMAL;
+                ++e->td.version;
+            }
+            PSB_RETURN_IF_ERROR(client_->push_context_nolock(sid_));
+            return client_->require_update_ctx_nolock(sid_, involved, timeout_ms);
+        }();
+        m.release_lock(PSERVER_LOCK_NAME);
+        return st;
+    }
+    // Abort / clean-up path: drop the update info and the half-built shards.
+    Status purge(int timeout_ms = 60000) {
+        MasterClient& m = client_->master();
+        PSB_RETURN_IF_ERROR(m.acquire_lock(PSERVER_LOCK_NAME));
+        Status st = [&]() -> Status {
+            PSB_RETURN_IF_ERROR(client_->pull_context_nolock(sid_));
+            auto e = entry();
+            std::set<int> involved = Client::all_nodes(*e);
+            {
+                std::unique_lock<std::shared_mutex> g(e->mu);
+                e->td.drop_update();
+                e->rt.build(e->td, -1);
+            }
+            PSB_RETURN_IF_ERROR(client_->push_context_nolock(sid_));
+            PSB_RETURN_IF_ERROR(client_->require_update_ctx_nolock(sid_, involved, timeout_ms));
+            return client_->broadcast(sid_, RequestType::NEW_CTX_PURGE, involved, Archive(), timeout_ms, -1);
+        }();
+        m.release_lock(PSERVER_LOCK_NAME);
+        return st;
+    }
+};
+
+// Incremental sync of (key, full row) blocks into another table (trainer -> predictor). No auto retry:
+// the caller rewinds and backs off (pico-ps/handler/SyncHandler.h:36-74).
+class SyncHandler : public Handler {
+public:
+    using Handler::Handler;
+    Status sync_block(const int64_t* keys, const float* rows, size_t n, uint32_t stride, int timeout_ms = 30000) {
+        std::shared_ptr<KVSyncOperator> p;
+        PSB_RETURN_IF_ERROR(op(&p));
+        auto e = entry();
+        std::map<int, Archive> plain;
+        {
+            std::shared_lock<std::shared_mutex> g(e->mu);
+            PSB_RETURN_IF_ERROR(DirectPushOperator::generate_requests(storage_op_of(*e), e->rt, keys, rows, n, stride, &plain));
+        }
+        std::map<int, Archive> bodies;
+        for (auto& kv : plain) {
+            std::vector<uint8_t> packed;
+            PSB_RETURN_IF_ERROR(p->compressor().compress(kv.second.data(), kv.second.size(), &packed));
+            bodies[kv.first] << packed;
+        }
+        ++metrics_.requests;
+        return client_->send_and_wait(sid_, hid_, RequestType::OP_SYNC, bodies, timeout_ms, nullptr);
+    }
+    size_t block_size() {
+        std::shared_ptr<KVSyncOperator> p;
+        return op(&p).ok() ? p->block_size() : 1000;
+    }
+};
+
+class UDFHandler : public Handler {
+public:
+    using Handler::Handler;
+    // Calls the function on every live node of the table; results in node order.
+    Status call(const std::string& param, std::vector<std::pair<int, std::string>>* results, int timeout_ms = -1, bool retry = true) {
+        return with_retry([&](int left) -> Status {
+            results->clear();
+            auto e = entry();
+            std::map<int, Archive> bodies;
+            {
+                std::shared_lock<std::shared_mutex> g(e->mu);
+                for (auto& kv : e->rt.nodes())
+                    if (e->rt.is_running(kv.first)) bodies[kv.first] << param;
+            }
+            std::vector<NodeResponse> rs;
+            PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_UDF, bodies, left, &rs));
+            for (auto& r : rs) {
+                std::string s;
+                r.body >> s;
+                results->push_back({r.node, s});
+            }
+            return Status::Ok();
+        }, timeout_ms, retry);
+    }
+};
+
+}  // namespace psb

@@ -1,0 +1,809 @@
+// Built-in operators: each class carries the CLIENT half (build requests, digest responses) and the
+// SERVER half (apply a request to the table entry) of one operation, as in the reference.
+//
+//   SparseTableStorageOperator   pico-ps/operator/StorageOperator.h:48-158
+//   SparseTablePullOperator      pico-ps/operator/SparsePullOperator.h:48-346
+//   SparseTablePushOperator      pico-ps/operator/SparsePushOperator.h:60-464   (async, sync, store)
+//   DirectPushOperator           pico-ps/operator/SparsePushOperator.h:479-654  (overwrite; load / reshard / restore)
+//   DenseTablePull/PushOperator  pico-ps/operator/DensePullOperator.h, DensePushOperator.h (slice keys)
+//   ForEachOperator / EraseIfOperator   pico-ps/operator/ForEachOperator.h, EraseIfOperator.h
+//   DumpOperator / LoadOperator / RestoreOperator   pico-ps/operator/{Dump,Load,Restore}Operator.h
+//   ShardUpdateContextOperator   pico-ps/operator/UpdateContextOperator.h
+//   KVSyncOperator               pico-ps/operator/SyncOperator.h
+//   UDFOperator                  pico-ps/operator/UDFOperator.h
+//
+// Request / response bodies keep the content of the reference's messages (Appendix: sparse pull =
+// {i32 shards_num, i32 merge_num, {i32 shard_id, {i32 n_keys, KEY[n]}}}, response = {i32 shards_num,
+// shard ids, values}); the encoding is this build's Archive. The user hooks of the reference
+// (init_store_value, store_push_value, ...) are the configured optimizer / initialiser functors.
+#pragma once
+#include <dirent.h>
+#include <sys/stat.h>
+
+#include <cmath>
+#include <cstdio>
+#include <fstream>
+#include <functional>
+#include <map>
+#include <set>
+#include <string>
+#include <vector>
+
+#include "../common/archive.h"
+#include "../common/compress.h"
+#include "../common/easy_hash_map.h"
+#include "../common/message.h"
+#include "../service/context.h"
+#include "operator.h"
+
+namespace psb {
+
+// ---------------------------------------------------------------------------------------------------
+inline int opt_type_from_name(const std::string& n) {
+    if (n == "sgd") return OPT_SGD;
+    if (n == "adagrad") return OPT_ADAGRAD;
+    if (n == "ftrl") return OPT_FTRL;
+    if (n == "adam" || n == "adamw") return OPT_ADAM;
+    if (n == "sum") return OPT_SUM;
+    if (n == "set") return OPT_SET;
+    return -1;
+}
+
+inline Status parse_opt_config(const Json& c, OptConfig* o) {
+    std::string name = c.has("optimizer") ? c.at("optimizer").as_string() : "sgd";
+    int t = opt_type_from_name(name);
+    if (t < 0) return Status::InvalidConfig("unknown optimizer " + name);
+    o->type = t;
+    if (t == OPT_ADAGRAD) o->eps = 1e-10f;
+    auto f = [&](const char* k, float& dst) { if (c.has(k)) dst = (float)c.at(k).as_double(); };
+    f("lr", o->lr); f("eps", o->eps); f("l1", o->l1); f("l2", o->l2); f("alpha", o->alpha); f("beta", o->beta);
+    f("beta1", o->beta1); f("beta2", o->beta2); f("weight_decay", o->weight_decay);
+    f("slot_init0", o->slot_init0); f("slot_init1", o->slot_init1); f("init_accumulator", o->slot_init0);
+    return Status::Ok();
+}
+
+// ---------------------------------------------------------------------------------------------------
+class SparseTableStorageOperator : public Operator {
+public:
+    explicit SparseTableStorageOperator(const Json& c) : Operator(c) {
+        Status st = parse_opt_config(c, &opt_);
+        if (!st.ok()) throw std::runtime_error(st.msg());
+        dim_ = (uint32_t)c.at("dim").as_int(16);
+        partition_ = c.at("partition").as_string() == "dense" ? 1 : 0;
+        if (partition_ == 1 && !c.has("init_range")) init_range_ = 0.f;
+        else init_range_ = c.has("init_range") ? (float)c.at("init_range").as_double() : 0.01f;
+    }
+    const char* kind() const override { return "storage"; }
+    uint32_t dim() const { return dim_; }
+    const OptConfig& opt() const { return opt_; }
+    int partition() const { return partition_; }
+    int shard_of(int64_t key, int32_t n_shards) const {
+        if (partition_ == 1) return dense_shard_of(key >> 24, (int32_t)(key & 0xFFFFFF), n_shards);
+        return sparse_shard_of(key, n_shards);
+    }
+    HostTableConfig table_config(int32_t n_shards) const {
+        HostTableConfig h;
+        h.dim = dim_;
+        h.opt_type = opt_.type;
+        h.sync_delta = config_.at("sync").as_bool(false);
+        h.n_shards = n_shards;
+        h.partition = partition_;
+        h.init_seed = (uint64_t)config_.at("seed").as_int(0);
+        h.init_range = init_range_;
+        h.slot_init0 = opt_.slot_init0;
+        h.slot_init1 = opt_.slot_init1;
+        h.soft_limit_bytes = h.hard_limit_bytes = (uint64_t)config_.at("memory_limit").as_int(0);
+        return h;
+    }
+    // Server side: build the storage and create the local shards.
+    Status create_storage(int32_t n_shards, const std::set<int32_t>& local_shards, std::unique_ptr<KVStorage>* out) const {
+        const std::string backend = config_.has("backend") ? config_.at("backend").as_string() : "host";
+        if (backend == "gpu") {
+            GpuKVStorageConfig g;
+            g.device = (int)config_.at("device").as_int(0);
+            g.base = table_config(n_shards);
+            g.capacity = (uint64_t)config_.at("capacity").as_int(1 << 20);
+            g.max_batch = (uint32_t)config_.at("max_batch").as_int(1 << 18);
+            PSB_RETURN_IF_ERROR(make_gpu_kv_storage(g, out));
+        } else if (backend == "host") {
+            out->reset(new HostKVStorage(table_config(n_shards)));
+        } else {
+            return Status::InvalidConfig("unknown storage backend " + backend);
+        }
+        for (int32_t s : local_shards) PSB_RETURN_IF_ERROR((*out)->create_shard(s));
+        return Status::Ok();
+    }
+
+private:
+    OptConfig opt_;
+    uint32_t dim_ = 16;
+    int partition_ = 0;
+    float init_range_ = 0.01f;
+};
+
+inline const SparseTableStorageOperator* storage_op_of(const TableEntry& e) {
+    return static_cast<const SparseTableStorageOperator*>(e.storage_op.get());
+}
+
+// ---------------------------------------------------------------------------------------------------
+struct NodeRequests {
+    std::map<int, Archive> body;              // node id -> request body
+    std::map<int, std::vector<int32_t>> shards;  // node id -> shard ids in the order they were written
+};
+
+struct PullRequestData {
+    size_t n = 0;
+    uint32_t n_uniq = 0;
+    std::vector<uint32_t> inverse;                 // position -> unique id
+    std::map<int32_t, std::vector<int64_t>> shard_keys;
+    std::map<int32_t, std::vector<uint32_t>> shard_uid;
+    std::vector<float> uniq_rows;                  // n_uniq * dim
+};
+
+class SparseTablePullOperator : public Operator {
+public:
+    explicit SparseTablePullOperator(const Json& c) : Operator(c) { read_only_ = c.at("read_only").as_bool(false); }
+    const char* kind() const override { return "pull"; }
+    bool read_only() const { return read_only_; }
+
+    // ---- client ----
+    // dedup + partition (HOT LOOP A of the reference)
+    void generate_request_data(const TableEntry& e, const int64_t* keys, size_t n, PullRequestData* d) const {
+        const auto* sop = storage_op_of(e);
+        const int32_t G = e.rt.global_shard_num();
+        EasyHashMap<int64_t, uint32_t> whole(kHostEmptyKey, n);
+        d->n = n;
+        d->n_uniq = 0;
+        d->inverse.resize(n);
+        d->shard_keys.clear();
+        d->shard_uid.clear();
+        for (size_t i = 0; i < n; ++i) {
+            auto r = whole.try_emplace(keys[i], d->n_uniq);
+            if (r.second) {
+                int32_t s = sop->shard_of(keys[i], G);
+                d->shard_keys[s].push_back(keys[i]);
+                d->shard_uid[s].push_back(d->n_uniq);
+                ++d->n_uniq;
+            }
+            d->inverse[i] = r.first->second;
+        }
+        d->uniq_rows.assign((size_t)d->n_uniq * sop->dim(), 0.f);
+    }
+    // one request per node, one random live replica per shard
+    Status generate_requests(const TableEntry& e, const PullRequestData& d, NodeRequests* out) const {
+        std::map<int, std::vector<int32_t>> by_node;
+        for (auto& kv : d.shard_keys) {
+            int node = e.rt.pick_one_replica(kv.first);
+            if (node < 0) return Status::NoReplica("no live replica of shard " + std::to_string(kv.first));
+            by_node[node].push_back(kv.first);
+        }
+        for (auto& kv : by_node) {
+            Archive& ar = out->body[kv.first];
+            ar << (int32_t)kv.second.size() << (int32_t)1;
+            for (int32_t s : kv.second) {
+                const auto& ks = d.shard_keys.at(s);
+                ar << s << (int32_t)ks.size();
+                ar.write_raw(ks.data(), ks.size() * 8);
+            }
+            out->shards[kv.first] = kv.second;
+        }
+        return Status::Ok();
+    }
+    Status apply_response(const TableEntry& e, PullRequestData* d, Archive& resp) const {
+        const uint32_t dim = storage_op_of(e)->dim();
+        int32_t shards_num = 0;
+        resp >> shards_num;
+        std::vector<int32_t> ids(shards_num);
+        for (auto& s : ids) resp >> s;
+        std::vector<float> tmp;
+        for (int32_t s : ids) {
+            auto it = d->shard_uid.find(s);
+            if (it == d->shard_uid.end()) return Status::Error("pull response for a shard that was not requested");
+            tmp.resize(it->second.size() * dim);
+            resp.read_raw(tmp.data(), tmp.size() * 4);
+            for (size_t j = 0; j < it->second.size(); ++j)
+                std::copy_n(tmp.data() + j * dim, dim, d->uniq_rows.data() + (size_t)it->second[j] * dim);
+        }
+        return Status::Ok();
+    }
+    // un-dedup (HOT LOOP C): one row per original key position
+    void fill_pull_items(const TableEntry& e, const PullRequestData& d, float* out) const {
+        const uint32_t dim = storage_op_of(e)->dim();
+        for (size_t i = 0; i < d.n; ++i) std::copy_n(d.uniq_rows.data() + (size_t)d.inverse[i] * dim, dim, out + i * dim);
+    }
+
+    // ---- server (HOT LOOP B) ----
+    Status apply_request(TableEntry& e, Archive& req, Archive* resp) const {
+        KVStorage* st = e.storage.get();
+        if (!read_only_ && !st->healthy()) return Status::OOM("storage unhealthy");
+        const uint32_t dim = st->dim();
+        int32_t shards_num = 0, merge_num = 0;
+        req >> shards_num >> merge_num;
+        std::vector<int32_t> ids;
+        std::vector<std::vector<float>> vals;
+        for (int32_t i = 0; i < shards_num; ++i) {
+            int32_t s = 0;
+            req >> s;
+            ids.push_back(s);
+            vals.emplace_back();
+            for (int32_t m = 0; m < merge_num; ++m) {
+                int32_t n = 0;
+                req >> n;
+                const int64_t* keys = (const int64_t*)req.cursor_ptr();
+                std::vector<int64_t> aligned(keys, keys + n);  // archive bytes may be unaligned
+                req.skip((size_t)n * 8);
+                size_t off = vals.back().size();
+                vals.back().resize(off + (size_t)n * dim);
+                PSB_RETURN_IF_ERROR(st->pull(s, aligned.data(), (size_t)n, vals.back().data() + off, !read_only_));
+            }
+        }
+        *resp << shards_num;
+        for (int32_t s : ids) *resp << s;
+        for (auto& v : vals) resp->write_raw(v.data(), v.size() * 4);
+        return Status::Ok();
+    }
+
+private:
+    bool read_only_ = false;
+};
+
+// ---------------------------------------------------------------------------------------------------
+struct PushRequestData {
+    std::map<int32_t, std::vector<int64_t>> shard_keys;
+    std::map<int32_t, std::vector<float>> shard_grads;
+};
+
+class SparseTablePushOperator : public Operator {
+public:
+    explicit SparseTablePushOperator(const Json& c) : Operator(c) {
+        has_opt_ = c.has("optimizer");
+        if (has_opt_) {
+            Status st = parse_opt_config(c, &opt_);
+            if (!st.ok()) throw std::runtime_error(st.msg());
+        }
+    }
+    const char* kind() const override { return "push"; }
+    OptConfig opt_for(const TableEntry& e) const { return has_opt_ ? opt_ : storage_op_of(e)->opt(); }
+
+    // ---- client: pre-aggregate duplicates, partition (HOT LOOP D) ----
+    void generate_request_data(const TableEntry& e, const int64_t* keys, const float* grads, size_t n,
+                               PushRequestData* d) const {
+        const auto* sop = storage_op_of(e);
+        const uint32_t dim = sop->dim();
+        const int32_t G = e.rt.global_shard_num();
+        EasyHashMap<int64_t, uint32_t> whole(kHostEmptyKey, n);
+        std::vector<int64_t> uk;
+        std::vector<float> agg;
+        for (size_t i = 0; i < n; ++i) {
+            auto r = whole.try_emplace(keys[i], (uint32_t)uk.size());
+            if (r.second) {
+                uk.push_back(keys[i]);
+                agg.resize(agg.size() + dim, 0.f);
+            }
+            float* a = agg.data() + (size_t)r.first->second * dim;
+            for (uint32_t k = 0; k < dim; ++k) a[k] += grads[i * dim + k];
+        }
+        d->shard_keys.clear();
+        d->shard_grads.clear();
+        for (size_t u = 0; u < uk.size(); ++u) {
+            int32_t s = sop->shard_of(uk[u], G);
+            d->shard_keys[s].push_back(uk[u]);
+            auto& g = d->shard_grads[s];
+            g.insert(g.end(), agg.data() + u * dim, agg.data() + (u + 1) * dim);
+        }
+    }
+    // every node that hosts a touched shard gets that shard's items (all replicas are updated)
+    Status generate_requests(const TableEntry& e, const PushRequestData& d, NodeRequests* out) const {
+        std::map<int, std::vector<int32_t>> by_node;
+        for (auto& kv : d.shard_keys) {
+            auto it = e.rt.shards().find(kv.first);
+            if (it == e.rt.shards().end() || it->second.empty())
+                return Status::NoReplica("no live holder of shard " + std::to_string(kv.first));
+            for (int node : it->second) by_node[node].push_back(kv.first);
+        }
+        for (auto& kv : by_node) {
+            Archive& ar = out->body[kv.first];
+            ar << (int32_t)kv.second.size() << (int32_t)1;
+            for (int32_t s : kv.second) {
+                const auto& ks = d.shard_keys.at(s);
+                const auto& gs = d.shard_grads.at(s);
+                ar << s << (int32_t)ks.size();
+                ar.write_raw(ks.data(), ks.size() * 8);
+                ar.write_raw(gs.data(), gs.size() * 4);
+            }
+            out->shards[kv.first] = kv.second;
+        }
+        return Status::Ok();
+    }
+
+    // ---- server (HOT LOOP E / the queueing half of F) ----
+    Status apply_request(TableEntry& e, Archive& req, bool sync) const {
+        KVStorage* st = e.storage.get();
+        if (!st->healthy()) return Status::OOM("storage unhealthy");
+        const uint32_t dim = st->dim();
+        const OptConfig opt = opt_for(e);
+        int32_t shards_num = 0, merge_num = 0;
+        req >> shards_num >> merge_num;
+        std::shared_lock<std::shared_mutex> ig(e.incr.mu);
+        for (int32_t i = 0; i < shards_num; ++i) {
+            int32_t s = 0;
+            req >> s;
+            for (int32_t m = 0; m < merge_num; ++m) {
+                int32_t n = 0;
+                req >> n;
+                std::vector<int64_t> keys((size_t)n);
+                std::vector<float> grads((size_t)n * dim);
+                req.read_raw(keys.data(), (size_t)n * 8);
+                req.read_raw(grads.data(), grads.size() * 4);
+                PSB_RETURN_IF_ERROR(st->push(s, keys.data(), grads.data(), (size_t)n, opt, sync));
+            }
+        }
+        e.incr.updated = true;
+        return Status::Ok();
+    }
+    // OP_STORE: fold what sync pushes buffered (the merging half of HOT LOOP F)
+    Status apply_store(TableEntry& e) const {
+        std::shared_lock<std::shared_mutex> ig(e.incr.mu);
+        e.incr.updated = true;
+        return e.storage->store(opt_for(e));
+    }
+
+private:
+    bool has_opt_ = false;
+    OptConfig opt_;
+};
+
+// ---------------------------------------------------------------------------------------------------
+// DirectPush: records {key, full row} overwrite / insert. Used by load (rehash), reshard shuffle, sync.
+class DirectPushOperator : public Operator {
+public:
+    explicit DirectPushOperator(const Json& c) : Operator(c) {}
+    const char* kind() const override { return "direct_push"; }
+
+    // Partition records by the owners under runtime info `rt` (all holders of a shard receive it).
+    static Status generate_requests(const SparseTableStorageOperator* sop, const RuntimeInfo& rt, const int64_t* keys,
+                                    const float* rows, size_t n, uint32_t stride, std::map<int, Archive>* out) {
+        const int32_t G = rt.global_shard_num();
+        std::map<int, std::pair<std::vector<int64_t>, std::vector<float>>> per_node;
+        for (size_t i = 0; i < n; ++i) {
+            int32_t s = sop->shard_of(keys[i], G);
+            auto it = rt.shards().find(s);
+            if (it == rt.shards().end() || it->second.empty())
+                return Status::NoReplica("direct push: no holder of shard " + std::to_string(s));
+            for (int node : it->second) {
+                auto& p = per_node[node];
+                p.first.push_back(keys[i]);
+                p.second.insert(p.second.end(), rows + i * stride, rows + (i + 1) * stride);
+            }
+        }
+        for (auto& kv : per_node) {
+            Archive& ar = (*out)[kv.first];
+            ar << (int32_t)kv.second.first.size() << (int32_t)stride;
+            ar.write_raw(kv.second.first.data(), kv.second.first.size() * 8);
+            ar.write_raw(kv.second.second.data(), kv.second.second.size() * 4);
+        }
+        return Status::Ok();
+    }
+    // Server: write into `dst` (the serving storage, or the update storage during a reshard).
+    static Status apply_request(KVStorage* dst, Archive& req) {
+        int32_t n = 0, stride = 0;
+        req >> n >> stride;
+        if ((uint32_t)stride != dst->stride() && (uint32_t)stride != dst->dim())
+            return Status::Error("direct push: record width does not match the table");
+        std::vector<int64_t> keys((size_t)n);
+        std::vector<float> rows((size_t)n * stride);
+        req.read_raw(keys.data(), (size_t)n * 8);
+        req.read_raw(rows.data(), rows.size() * 4);
+        return dst->set_rows(keys.data(), rows.data(), (size_t)n, (uint32_t)stride == dst->dim() && dst->dim() != dst->stride());
+    }
+};
+
+// ---------------------------------------------------------------------------------------------------
+// Dense tables: a dense value (tensor `id` of `numel` floats) is cut into slices of `dim` floats
+// (DenseValuePartitioner), slice j has key (id << 24) | j and lives on shard hash(id, j) % G; pull
+// reassembles (DenseValueMerger). The sparse machinery above does the rest.
+inline void dense_slice_keys(int64_t id, size_t numel, uint32_t slice_len, std::vector<int64_t>* keys) {
+    size_t ns = (numel + slice_len - 1) / slice_len;
+    keys->resize(ns);
+    for (size_t j = 0; j < ns; ++j) (*keys)[j] = (id << 24) | (int64_t)j;
+}
+
+class DenseTablePullOperator : public SparseTablePullOperator {
+public:
+    explicit DenseTablePullOperator(const Json& c) : SparseTablePullOperator(c) {}
+};
+class DenseTablePushOperator : public SparseTablePushOperator {
+public:
+    explicit DenseTablePushOperator(const Json& c) : SparseTablePushOperator(c) {}
+};
+
+// ---------------------------------------------------------------------------------------------------
+// for_each: per-shard scan with a built-in reducer; results merge associatively on the client.
+struct ForEachResult {
+    uint64_t count = 0;
+    double sum = 0, sum_sq = 0, max_abs = 0;
+    void merge(const ForEachResult& o) {
+        count += o.count;
+        sum += o.sum;
+        sum_sq += o.sum_sq;
+        max_abs = std::max(max_abs, o.max_abs);
+    }
+};
+
+class ForEachOperator : public Operator {
+public:
+    explicit ForEachOperator(const Json& c) : Operator(c) {}
+    const char* kind() const override { return "for_each"; }
+    // Statistics over the embedding part of every row of one shard. `carried` may hold
+    // {"section": 0|1|2} to look at an optimizer slot instead.
+    Status apply_request(TableEntry& e, int32_t shard, const Json& carried, ForEachResult* r) const {
+        KVStorage* st = e.storage.get();
+        const uint32_t dim = st->dim(), stride = st->stride();
+        const uint32_t section = (uint32_t)carried.at("section").as_int(0);
+        if ((section + 1) * dim > stride) return Status::InvalidConfig("for_each: no such row section");
+        uint64_t cursor = 0;
+        bool finished = false;
+        std::vector<int64_t> keys;
+        std::vector<float> rows;
+        while (!finished) {
+            keys.clear();
+            rows.clear();
+            PSB_RETURN_IF_ERROR(st->export_shard(shard, cursor, 1 << 16, false, &keys, &rows, &cursor, &finished));
+            for (size_t i = 0; i < keys.size(); ++i) {
+                ++r->count;
+                const float* v = rows.data() + i * stride + section * dim;
+                for (uint32_t k = 0; k < dim; ++k) {
+                    r->sum += v[k];
+                    r->sum_sq += (double)v[k] * v[k];
+                    r->max_abs = std::max(r->max_abs, (double)std::fabs(v[k]));
+                }
+            }
+        }
+        return Status::Ok();
+    }
+};
+
+// erase_if: exclusive per-shard scan with a predicate chosen by the carried item:
+//   {"type":"key_mod","mod":m,"rem":r} | {"type":"l2_below","threshold":t} | {"type":"slot0_below","threshold":t}
+//   | {"type":"all"}
+class EraseIfOperator : public Operator {
+public:
+    explicit EraseIfOperator(const Json& c) : Operator(c) {}
+    const char* kind() const override { return "erase_if"; }
+    Status apply_request(TableEntry& e, int32_t shard, const Json& carried, uint64_t* erased) const {
+        KVStorage* st = e.storage.get();
+        const uint32_t dim = st->dim(), stride = st->stride();
+        const std::string type = carried.at("type").as_string();
+        const int64_t mod = carried.at("mod").as_int(2), rem = carried.at("rem").as_int(1);
+        const double thr = carried.at("threshold").as_double(0);
+        uint64_t cursor = 0;
+        bool finished = false;
+        std::vector<int64_t> keys, doomed;
+        std::vector<float> rows;
+        while (!finished) {
+            keys.clear();
+            rows.clear();
+            PSB_RETURN_IF_ERROR(st->export_shard(shard, cursor, 1 << 16, false, &keys, &rows, &cursor, &finished));
+            for (size_t i = 0; i < keys.size(); ++i) {
+                const float* v = rows.data() + i * stride;
+                bool hit = false;
+                if (type == "key_mod") hit = ((keys[i] % mod) + mod) % mod == rem;
+                else if (type == "all") hit = true;
+                else if (type == "l2_below") {
+                    double s = 0;
+                    for (uint32_t k = 0; k < dim; ++k) s += (double)v[k] * v[k];
+                    hit = std::sqrt(s) < thr;
+                } else if (type == "slot0_below") {
+                    if (stride < 2 * dim) return Status::InvalidConfig("erase_if slot0_below: table has no optimizer slot");
+                    double s = 0;
+                    for (uint32_t k = 0; k < dim; ++k) s += v[dim + k];
+                    hit = s / dim < thr;
+                } else {
+                    return Status::InvalidConfig("erase_if: unknown predicate " + type);
+                }
+                if (hit) doomed.push_back(keys[i]);
+            }
+        }
+        *erased = 0;
+        if (!doomed.empty()) PSB_RETURN_IF_ERROR(st->erase_keys(doomed.data(), doomed.size(), erased));
+        return Status::Ok();
+    }
+};
+
+// ---------------------------------------------------------------------------------------------------
+// Dump / load file codec. Layout rules are the reference's (pico-ps/operator/DumpOperator.h:72-83,156):
+// directory <uri>, files model_<node_id>_<file_id>, shard -> file by shard_id % file_number, one record
+// per entry {key, value}. Record encodings ("?format=" option of the uri):
+//   binary      : header "PSB1" u32 stride | records: i64 key, stride * fp32         (default)
+//   archiveline : one text line per record: key \t v0 v1 ... (%.9g round-trips fp32 bit for bit)
+// With a compress_algorithm the whole file body is one compressed block.
+struct DumpArgs {
+    std::string uri;
+    int32_t file_number = 1;
+    static void split_uri(const std::string& uri, std::string* path, std::string* format) {
+        auto q = uri.find('?');
+        *path = uri.substr(0, q);
+        *format = "binary";
+        if (q != std::string::npos) {
+            auto f = uri.find("format=", q);
+            if (f != std::string::npos) {
+                auto end = uri.find('&', f);
+                *format = uri.substr(f + 7, end == std::string::npos ? std::string::npos : end - f - 7);
+            }
+        }
+    }
+};
+
+inline Status mkdir_p(const std::string& path) {
+    std::string cur;
+    for (size_t i = 0; i <= path.size(); ++i) {
+        if (i == path.size() || path[i] == '/') {
+            if (!cur.empty() && ::mkdir(cur.c_str(), 0777) != 0 && errno != EEXIST)
+                return Status::Error("mkdir " + cur + " failed");
+        }
+        if (i < path.size()) cur += path[i];
+    }
+    return Status::Ok();
+}
+
+inline std::vector<std::string> list_model_files(const std::string& dir) {
+    std::vector<std::string> out;
+    DIR* d = ::opendir(dir.c_str());
+    if (!d) return out;
+    while (dirent* e = ::readdir(d)) {
+        std::string n = e->d_name;
+        if (n.compare(0, 6, "model_") == 0) out.push_back(dir + "/" + n);
+    }
+    ::closedir(d);
+    std::sort(out.begin(), out.end());
+    return out;
+}
+
+class DsWriter {
+public:
+    DsWriter(std::string path, std::string format, uint32_t stride, const Compressor* comp)
+        : path_(std::move(path)), format_(std::move(format)), stride_(stride), comp_(comp) {
+        if (format_ == "binary") {
+            body_.insert(body_.end(), {'P', 'S', 'B', '1'});
+            const uint8_t* p = (const uint8_t*)&stride_;
+            body_.insert(body_.end(), p, p + 4);
+        }
+    }
+    void write(int64_t key, const float* row) {
+        if (format_ == "binary") {
+            const uint8_t* k = (const uint8_t*)&key;
+            body_.insert(body_.end(), k, k + 8);
+            const uint8_t* r = (const uint8_t*)row;
+            body_.insert(body_.end(), r, r + (size_t)stride_ * 4);
+        } else {
+            char buf[32];
+            int m = std::snprintf(buf, sizeof buf, "%lld\t", (long long)key);
+            body_.insert(body_.end(), buf, buf + m);
+            for (uint32_t i = 0; i < stride_; ++i) {
+                m = std::snprintf(buf, sizeof buf, i + 1 == stride_ ? "%.9g\n" : "%.9g ", row[i]);
+                body_.insert(body_.end(), buf, buf + m);
+            }
+        }
+    }
+    Status close() {
+        std::vector<uint8_t> out;
+        if (comp_ && comp_->enabled()) PSB_RETURN_IF_ERROR(comp_->compress(body_.data(), body_.size(), &out));
+        else out.swap(body_);
+        std::ofstream f(path_, std::ios::binary | std::ios::trunc);
+        if (!f) return Status::Error("cannot open " + path_ + " for writing");
+        f.write((const char*)out.data(), (std::streamsize)out.size());
+        return f.good() ? Status::Ok() : Status::Error("write to " + path_ + " failed");
+    }
+
+private:
+    std::string path_, format_;
+    uint32_t stride_;
+    const Compressor* comp_;
+    std::vector<uint8_t> body_;
+};
+
+// Reads a whole file and hands out records in blocks.
+class DsReader {
+public:
+    Status open(const std::string& path, const std::string& format, uint32_t stride, const Compressor* comp) {
+        std::ifstream f(path, std::ios::binary);
+        if (!f) return Status::Error("cannot open " + path);
+        std::vector<uint8_t> raw((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+        if (comp && comp->enabled()) PSB_RETURN_IF_ERROR(comp->decompress(raw.data(), raw.size(), &body_));
+        else body_.swap(raw);
+        format_ = format;
+        stride_ = stride;
+        pos_ = 0;
+        if (format_ == "binary") {
+            if (body_.size() < 8 || std::memcmp(body_.data(), "PSB1", 4) != 0) return Status::Error(path + ": not a PSB1 dump file");
+            uint32_t s;
+            std::memcpy(&s, body_.data() + 4, 4);
+            if (s != stride) return Status::Error(path + ": record width differs from the table");
+            pos_ = 8;
+        }
+        return Status::Ok();
+    }
+    // Up to `block` records; returns false when the file is exhausted.
+    bool next_block(size_t block, std::vector<int64_t>* keys, std::vector<float>* rows) {
+        keys->clear();
+        rows->clear();
+        while (keys->size() < block && pos_ < body_.size()) {
+            if (format_ == "binary") {
+                if (pos_ + 8 + (size_t)stride_ * 4 > body_.size()) { pos_ = body_.size(); break; }
+                int64_t k;
+                std::memcpy(&k, body_.data() + pos_, 8);
+                keys->push_back(k);
+                size_t off = rows->size();
+                rows->resize(off + stride_);
+                std::memcpy(rows->data() + off, body_.data() + pos_ + 8, (size_t)stride_ * 4);
+                pos_ += 8 + (size_t)stride_ * 4;
+            } else {
+                const char* p = (const char*)body_.data() + pos_;
+                char* end = nullptr;
+                long long k = std::strtoll(p, &end, 10);
+                keys->push_back(k);
+                for (uint32_t i = 0; i < stride_; ++i) rows->push_back(std::strtof(end, &end));
+                while (*end == '\n' || *end == '\r') ++end;
+                pos_ = (size_t)(end - (const char*)body_.data());
+            }
+        }
+        return !keys->empty();
+    }
+
+private:
+    std::vector<uint8_t> body_;
+    std::string format_;
+    uint32_t stride_ = 0;
+    size_t pos_ = 0;
+};
+
+class DumpOperator : public Operator {
+public:
+    explicit DumpOperator(const Json& c) : Operator(c) {
+        Status st = Compressor::create(c.at("compress_algorithm").as_string(), &comp_);
+        if (!st.ok()) throw std::runtime_error(st.msg());
+    }
+    const char* kind() const override { return "dump"; }
+    // Server: write the local shards that map to file `file_id` into <uri>/model_<node>_<file_id>.
+    Status apply_request(TableEntry& e, int node_id, const DumpArgs& args, int32_t file_id, const std::vector<int32_t>& shards,
+                         uint64_t* n_records) const {
+        std::string dir, format;
+        DumpArgs::split_uri(args.uri, &dir, &format);
+        PSB_RETURN_IF_ERROR(mkdir_p(dir));
+        KVStorage* st = e.storage.get();
+        DsWriter w(dir + "/model_" + std::to_string(node_id) + "_" + std::to_string(file_id), format, st->stride(), &comp_);
+        *n_records = 0;
+        std::vector<int64_t> keys;
+        std::vector<float> rows;
+        for (int32_t s : shards) {
+            uint64_t cursor = 0;
+            bool finished = false;
+            while (!finished) {
+                keys.clear();
+                rows.clear();
+                PSB_RETURN_IF_ERROR(st->export_shard(s, cursor, 1 << 16, false, &keys, &rows, &cursor, &finished));
+                for (size_t i = 0; i < keys.size(); ++i) w.write(keys[i], rows.data() + i * st->stride());
+                *n_records += keys.size();
+            }
+        }
+        return w.close();
+    }
+    const Compressor& compressor() const { return comp_; }
+
+private:
+    Compressor comp_;
+};
+
+class LoadOperator : public Operator {
+public:
+    explicit LoadOperator(const Json& c) : Operator(c) {
+        Status st = Compressor::create(c.at("compress_algorithm").as_string(), &comp_);
+        if (!st.ok()) throw std::runtime_error(st.msg());
+        block_size_ = (size_t)c.at("block_size").as_int(1000);
+    }
+    const char* kind() const override { return "load"; }
+    size_t block_size() const { return block_size_; }
+    const Compressor& compressor() const { return comp_; }
+    // restore (no rehash): read `file`, keep the records whose shard is local.
+    Status restore_file(TableEntry& e, const std::string& file, const std::string& format, uint64_t* kept) const {
+        KVStorage* st = e.storage.get();
+        DsReader r;
+        PSB_RETURN_IF_ERROR(r.open(file, format, st->stride(), &comp_));
+        std::vector<int64_t> keys;
+        std::vector<float> rows;
+        while (r.next_block(block_size_, &keys, &rows)) {
+            PSB_RETURN_IF_ERROR(st->set_rows(keys.data(), rows.data(), keys.size(), false));  // foreign keys are skipped
+            for (int64_t k : keys) *kept += st->has_shard(st->shard_of(k)) ? 1 : 0;
+        }
+        return Status::Ok();
+    }
+
+private:
+    Compressor comp_;
+    size_t block_size_ = 1000;
+};
+
+class RestoreOperator : public LoadOperator {
+public:
+    explicit RestoreOperator(const Json& c) : LoadOperator(c) {}
+    const char* kind() const override { return "restore"; }
+};
+
+// Reshard codec: which items of an old shard must travel, and the purge of what no longer belongs.
+class ShardUpdateContextOperator : public Operator {
+public:
+    explicit ShardUpdateContextOperator(const Json& c) : Operator(c) {
+        block_bytes_ = (size_t)c.at("block_serialized_size").as_int(1000000);
+    }
+    const char* kind() const override { return "update_ctx"; }
+    size_t block_bytes() const { return block_bytes_; }
+
+private:
+    size_t block_bytes_;
+};
+
+class KVSyncOperator : public Operator {
+public:
+    explicit KVSyncOperator(const Json& c) : Operator(c) {
+        block_size_ = (size_t)c.at("block_size").as_int(1000);
+        Status st = Compressor::create(c.at("compress_algorithm").as_string(), &comp_);
+        if (!st.ok()) throw std::runtime_error(st.msg());
+    }
+    const char* kind() const override { return "sync"; }
+    size_t block_size() const { return block_size_; }
+    const Compressor& compressor() const { return comp_; }
+
+private:
+    size_t block_size_;
+    Compressor comp_;
+};
+
+// UDF: named server-side functions. apply(entry, param bytes) -> result bytes. Functions are registered
+// in a process-wide table (C++ or, through the bindings, Python callables).
+class UDFRegistry {
+public:
+    using Fn = std::function<Status(TableEntry&, const std::string& param, std::string* result)>;
+    static UDFRegistry& instance() {
+        static UDFRegistry r;
+        return r;
+    }
+    void add(const std::string& name, Fn f) {
+        std::lock_guard<std::mutex> g(mu_);
+        fns_[name] = std::move(f);
+    }
+    bool get(const std::string& name, Fn* f) {
+        std::lock_guard<std::mutex> g(mu_);
+        auto it = fns_.find(name);
+        if (it == fns_.end()) return false;
+        *f = it->second;
+        return true;
+    }
+
+private:
+    std::mutex mu_;
+    std::map<std::string, Fn> fns_;
+};
+
+class UDFOperator : public Operator {
+public:
+    explicit UDFOperator(const Json& c) : Operator(c) {
+        fn_ = c.at("function").as_string();
+        read_only_ = c.at("read_only").as_bool(true);
+    }
+    const char* kind() const override { return "udf"; }
+    bool read_only() const { return read_only_; }
+    Status apply_request(TableEntry& e, const std::string& param, std::string* result) const {
+        UDFRegistry::Fn f;
+        if (!UDFRegistry::instance().get(fn_, &f)) return Status::InvalidConfig("udf: no function named " + fn_);
+        return f(e, param, result);
+    }
+
+private:
+    std::string fn_;
+    bool read_only_ = true;
+};
+
+// Registers every built-in operator under lib name "psb" (idempotent).
+void register_builtin_operators();
+
+}  // namespace psb

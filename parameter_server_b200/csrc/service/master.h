@@ -1,0 +1,378 @@
+// The master: one small process-wide coordination service (context store, id generator, global lock,
+// barrier, node registry with liveness, tree nodes for broadcast and model objects).
+//
+// Parity: the subset of prpc's Master / MasterClient API that pico-ps calls (listed in
+// pico-ps/common/core.h:128-131 and used in pico-ps/service/Client.cpp:68-106,174-201,359-399 and
+// pico-ps/service/Service.cpp:150-191): acquire_lock / release_lock (PSERVER_LOCK), generate_id
+// ("storage_id", "handler"), add/set/get/delete_context, get_storage_list, the RPC service registry
+// whose membership IS the liveness signal (a node whose session connection closes is unregistered),
+// barrier, tree_node_add / get, get_model / set_model. The in-process TCP master of the reference's
+// tests (pico-ps/test/TestUtils.h:16-92) corresponds to constructing Master directly.
+#pragma once
+#include <map>
+#include <set>
+#include <string>
+#include <vector>
+
+#include "../common/archive.h"
+#include "../common/message.h"
+#include "rpc.h"
+
+namespace psb {
+
+enum class MasterOp : int32_t {
+    GEN_ID = 1, LOCK = 2, UNLOCK = 3, CTX_SET = 4, CTX_GET = 5, CTX_DEL = 6, CTX_LIST = 7, REGISTER = 8,
+    DEREGISTER = 9, NODES = 10, BARRIER = 11, TREE_SET = 12, TREE_GET = 13, TREE_DEL = 14, TREE_LIST = 15, PING = 16,
+};
+
+class Master {
+public:
+    explicit Master(int n_threads = 4)
+        : server_([this](Bytes&& b, RpcServer::Responder r) { handle(std::move(b), r); }, n_threads,
+                  [this](uint64_t conn) { on_disconnect(conn); }) {}
+    std::string address() const { return server_.address(); }
+    void stop() { server_.stop(); }
+
+private:
+    static Bytes ok_reply(Archive&& ar = Archive()) {
+        Archive out;
+        out << Status::Ok();
+        out.write_raw(ar.data(), ar.size());
+        return out.release();
+    }
+    static Bytes err_reply(const Status& st) {
+        Archive out;
+        out << st;
+        return out.release();
+    }
+
+    void handle(Bytes&& bytes, RpcServer::Responder resp) {
+        Archive ar(std::move(bytes));
+        int32_t op = 0;
+        ar >> op;
+        std::unique_lock<std::mutex> g(mu_);
+        switch ((MasterOp)op) {
+            case MasterOp::GEN_ID: {
+                std::string key;
+                ar >> key;
+                Archive out;
+                out << (int32_t)(ids_[key]++);
+                resp.send(ok_reply(std::move(out)));
+                break;
+            }
+            case MasterOp::LOCK: {
+                std::string name;
+                ar >> name;
+                auto& l = locks_[name];
+                if (!l.held) {
+                    l.held = true;
+                    l.owner_conn = resp.conn_id();
+                    resp.send(ok_reply());
+                } else {
+                    l.waiters.push_back(resp);  // answered when the lock is handed over
+                }
+                break;
+            }
+            case MasterOp::UNLOCK: {
+                std::string name;
+                ar >> name;
+                release_lock_locked(name);
+                resp.send(ok_reply());
+                break;
+            }
+            case MasterOp::CTX_SET: {
+                std::string key, value;
+                int32_t only_if_absent = 0;
+                ar >> key >> value >> only_if_absent;
+                if (only_if_absent && ctx_.count(key)) {
+                    resp.send(err_reply(Status::Error("context " + key + " already exists")));
+                } else {
+                    ctx_[key] = value;
+                    resp.send(ok_reply());
+                }
+                break;
+            }
+            case MasterOp::CTX_GET: {
+                std::string key;
+                ar >> key;
+                auto it = ctx_.find(key);
+                if (it == ctx_.end()) {
+                    resp.send(err_reply(Status::InvalidID("no context " + key)));
+                } else {
+                    Archive out;
+                    out << it->second;
+                    resp.send(ok_reply(std::move(out)));
+                }
+                break;
+            }
+            case MasterOp::CTX_DEL: {
+                std::string key;
+                ar >> key;
+                ctx_.erase(key);
+                resp.send(ok_reply());
+                break;
+            }
+            case MasterOp::CTX_LIST: {
+                std::vector<std::string> keys;
+                for (auto& kv : ctx_) keys.push_back(kv.first);
+                Archive out;
+                out << keys;
+                resp.send(ok_reply(std::move(out)));
+                break;
+            }
+            case MasterOp::REGISTER: {
+                // the connection that registers is the node's session: when it closes the node is dead
+                std::string service, addr;
+                int32_t want_id = -1;
+                ar >> service >> addr >> want_id;
+                int32_t id = want_id >= 0 ? want_id : next_node_id_++;
+                if (want_id >= next_node_id_) next_node_id_ = want_id + 1;
+                registry_[service][id] = addr;
+                sessions_[resp.conn_id()].insert({service, id});
+                Archive out;
+                out << id;
+                resp.send(ok_reply(std::move(out)));
+                break;
+            }
+            case MasterOp::DEREGISTER: {
+                std::string service;
+                int32_t id = -1;
+                ar >> service >> id;
+                registry_[service].erase(id);
+                resp.send(ok_reply());
+                break;
+            }
+            case MasterOp::NODES: {
+                std::string service;
+                ar >> service;
+                std::vector<int32_t> ids;
+                std::vector<std::string> addrs;
+                for (auto& kv : registry_[service]) {
+                    ids.push_back(kv.first);
+                    addrs.push_back(kv.second);
+                }
+                Archive out;
+                out << ids << addrs;
+                resp.send(ok_reply(std::move(out)));
+                break;
+            }
+            case MasterOp::BARRIER: {
+                std::string name;
+                int32_t n = 0;
+                ar >> name >> n;
+                auto& b = barriers_[name];
+                b.push_back(resp);
+                if ((int32_t)b.size() >= n) {
+                    for (auto& r : b) r.send(ok_reply());
+                    barriers_.erase(name);
+                }
+                break;
+            }
+            case MasterOp::TREE_SET: {
+                std::string path, value;
+                ar >> path >> value;
+                tree_[path] = value;
+                resp.send(ok_reply());
+                break;
+            }
+            case MasterOp::TREE_GET: {
+                std::string path;
+                ar >> path;
+                auto it = tree_.find(path);
+                if (it == tree_.end()) {
+                    resp.send(err_reply(Status::Empty("no tree node " + path)));
+                } else {
+                    Archive out;
+                    out << it->second;
+                    resp.send(ok_reply(std::move(out)));
+                }
+                break;
+            }
+            case MasterOp::TREE_DEL: {
+                std::string path;
+                ar >> path;
+                tree_.erase(path);
+                resp.send(ok_reply());
+                break;
+            }
+            case MasterOp::TREE_LIST: {
+                std::string prefix;
+                ar >> prefix;
+                std::vector<std::string> keys;
+                for (auto it = tree_.lower_bound(prefix); it != tree_.end() && it->first.compare(0, prefix.size(), prefix) == 0; ++it)
+                    keys.push_back(it->first);
+                Archive out;
+                out << keys;
+                resp.send(ok_reply(std::move(out)));
+                break;
+            }
+            case MasterOp::PING: resp.send(ok_reply()); break;
+            default: resp.send(err_reply(Status::Error("master: unknown op")));
+        }
+    }
+
+    void release_lock_locked(const std::string& name) {
+        auto& l = locks_[name];
+        while (!l.waiters.empty()) {
+            RpcServer::Responder next = l.waiters.front();
+            l.waiters.erase(l.waiters.begin());
+            l.owner_conn = next.conn_id();
+            if (next.send(ok_reply())) return;  // handed over (skips waiters that went away)
+        }
+        l.held = false;
+        l.owner_conn = 0;
+    }
+
+    void on_disconnect(uint64_t conn) {
+        std::lock_guard<std::mutex> g(mu_);
+        auto it = sessions_.find(conn);
+        if (it != sessions_.end()) {
+            for (auto& sn : it->second) registry_[sn.first].erase(sn.second);
+            sessions_.erase(it);
+        }
+        // a client that died while holding a lock must not wedge everyone else
+        for (auto& kv : locks_)
+            if (kv.second.held && kv.second.owner_conn == conn) release_lock_locked(kv.first);
+    }
+
+    struct LockState {
+        bool held = false;
+        uint64_t owner_conn = 0;
+        std::vector<RpcServer::Responder> waiters;
+    };
+    std::mutex mu_;
+    std::map<std::string, int32_t> ids_;
+    std::map<std::string, LockState> locks_;
+    std::map<std::string, std::string> ctx_;
+    std::map<std::string, std::map<int32_t, std::string>> registry_;
+    std::map<uint64_t, std::set<std::pair<std::string, int32_t>>> sessions_;
+    std::map<std::string, std::vector<RpcServer::Responder>> barriers_;
+    std::map<std::string, std::string> tree_;
+    int32_t next_node_id_ = 0;
+    RpcServer server_;  // last member: its threads start using the state above at once
+};
+
+class MasterClient {
+public:
+    explicit MasterClient(std::string master_address, int timeout_ms = 30000)
+        : addr_(std::move(master_address)), timeout_ms_(timeout_ms) {}
+
+    Status generate_id(const std::string& key, int32_t* id) {
+        Archive req, rep;
+        req << (int32_t)MasterOp::GEN_ID << key;
+        PSB_RETURN_IF_ERROR(call(req, &rep));
+        rep >> *id;
+        return Status::Ok();
+    }
+    Status acquire_lock(const std::string& name) {
+        Archive req, rep;
+        req << (int32_t)MasterOp::LOCK << name;
+        return call(req, &rep, -1);
+    }
+    Status release_lock(const std::string& name) {
+        Archive req, rep;
+        req << (int32_t)MasterOp::UNLOCK << name;
+        return call(req, &rep);
+    }
+    Status set_context(const std::string& key, const std::string& value, bool only_if_absent = false) {
+        Archive req, rep;
+        req << (int32_t)MasterOp::CTX_SET << key << value << (int32_t)(only_if_absent ? 1 : 0);
+        return call(req, &rep);
+    }
+    Status add_context(const std::string& key, const std::string& value) { return set_context(key, value, true); }
+    Status get_context(const std::string& key, std::string* value) {
+        Archive req, rep;
+        req << (int32_t)MasterOp::CTX_GET << key;
+        PSB_RETURN_IF_ERROR(call(req, &rep));
+        rep >> *value;
+        return Status::Ok();
+    }
+    Status delete_context(const std::string& key) {
+        Archive req, rep;
+        req << (int32_t)MasterOp::CTX_DEL << key;
+        return call(req, &rep);
+    }
+    Status list_contexts(std::vector<std::string>* keys) {
+        Archive req, rep;
+        req << (int32_t)MasterOp::CTX_LIST;
+        PSB_RETURN_IF_ERROR(call(req, &rep));
+        rep >> *keys;
+        return Status::Ok();
+    }
+    // Registers on THIS client's connection: keep the MasterClient alive as long as the node lives.
+    Status register_node(const std::string& service, const std::string& address, int32_t* node_id, int32_t want_id = -1) {
+        Archive req, rep;
+        req << (int32_t)MasterOp::REGISTER << service << address << want_id;
+        PSB_RETURN_IF_ERROR(call(req, &rep));
+        rep >> *node_id;
+        return Status::Ok();
+    }
+    Status deregister_node(const std::string& service, int32_t node_id) {
+        Archive req, rep;
+        req << (int32_t)MasterOp::DEREGISTER << service << node_id;
+        return call(req, &rep);
+    }
+    Status get_nodes(const std::string& service, std::map<int32_t, std::string>* nodes) {
+        Archive req, rep;
+        req << (int32_t)MasterOp::NODES << service;
+        PSB_RETURN_IF_ERROR(call(req, &rep));
+        std::vector<int32_t> ids;
+        std::vector<std::string> addrs;
+        rep >> ids >> addrs;
+        nodes->clear();
+        for (size_t i = 0; i < ids.size(); ++i) (*nodes)[ids[i]] = addrs[i];
+        return Status::Ok();
+    }
+    Status barrier(const std::string& name, int32_t n) {
+        Archive req, rep;
+        req << (int32_t)MasterOp::BARRIER << name << n;
+        return call(req, &rep, -1);
+    }
+    Status tree_node_set(const std::string& path, const std::string& value) {
+        Archive req, rep;
+        req << (int32_t)MasterOp::TREE_SET << path << value;
+        return call(req, &rep);
+    }
+    Status tree_node_get(const std::string& path, std::string* value) {
+        Archive req, rep;
+        req << (int32_t)MasterOp::TREE_GET << path;
+        PSB_RETURN_IF_ERROR(call(req, &rep));
+        rep >> *value;
+        return Status::Ok();
+    }
+    Status tree_node_del(const std::string& path) {
+        Archive req, rep;
+        req << (int32_t)MasterOp::TREE_DEL << path;
+        return call(req, &rep);
+    }
+    Status tree_node_list(const std::string& prefix, std::vector<std::string>* keys) {
+        Archive req, rep;
+        req << (int32_t)MasterOp::TREE_LIST << prefix;
+        PSB_RETURN_IF_ERROR(call(req, &rep));
+        rep >> *keys;
+        return Status::Ok();
+    }
+    Status ping() {
+        Archive req, rep;
+        req << (int32_t)MasterOp::PING;
+        return call(req, &rep, 2000);
+    }
+    const std::string& address() const { return addr_; }
+    void close() { rpc_.close_all(); }
+
+private:
+    Status call(Archive& req, Archive* rep, int timeout_ms = 0) {
+        Bytes out;
+        Status st = rpc_.call(addr_, req.bytes(), timeout_ms == 0 ? timeout_ms_ : timeout_ms, &out);
+        if (!st.ok()) return Status::Fatal("master unreachable: " + st.msg());
+        *rep = Archive(std::move(out));
+        Status remote;
+        *rep >> remote;
+        return remote;
+    }
+    std::string addr_;
+    int timeout_ms_;
+    RpcClient rpc_;
+};
+
+}  // namespace psb

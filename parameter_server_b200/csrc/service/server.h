@@ -1,0 +1,718 @@
+// Server: one parameter-server process (one per GPU on a B200 box, or CPU-only). Owns the storages of
+// the shards placed on it and answers two RPC services: c2s (clients) and s2s (other servers).
+//
+// Parity: pico-ps/service/Server.h:23-243 + pico-ps/service/Service.cpp: the request dispatch table
+// (:377-541), the context version gates (:1316-1400; writes are refused with OUT_OF_MEMORY "write
+// when update context" while the table is in RESHARD), storage / handler life cycle (:543-699), the
+// data operations (:700-991), the reshard steps (:1052-1272), incremental sync apply (:1274-1301),
+// HA restore (:150-366: take over a dead node's descriptor under a NEW node id, restore every table
+// from a live replica over s2s in resumable batches, fall back to the dump at table_uri), and the
+// memory self-monitor. A request is {body, PSMessageMeta tail}; a response is {Status, payload}.
+#pragma once
+#include <atomic>
+#include <chrono>
+#include <thread>
+
+#include "../operator/operators.h"
+#include "context.h"
+#include "master.h"
+
+namespace psb {
+
+struct ServerConfig {
+    int c2s_thread_num = 4;
+    int s2s_thread_num = 4;
+    int load_thread_num = 4;
+    int load_block_size = 1000;
+    int report_interval_s = -1;
+    int restore_wait_timeout_s = -1;
+    int restore_batch_size = 1000;
+    int s2s_timeout_ms = 60000;
+};
+
+struct StorageStatisticInfo {
+    uint64_t item_number = 0, memory_usage = 0;
+    int32_t node_id = -1, shard_id = -1;
+};
+struct NodeMemoryInfo {
+    bool healthy = true;
+    uint64_t used = 0, managed = 0;
+};
+
+inline std::string ctx_key(int32_t sid) { return "storage/" + std::to_string(sid); }
+
+class Server {
+public:
+    Server(const std::string& master_addr, const ServerConfig& cfg = ServerConfig())
+        : cfg_(cfg), master_(master_addr), session_(master_addr) {
+        register_builtin_operators();
+        s2s_.reset(new RpcServer([this](Bytes&& b, RpcServer::Responder r) { dispatch(std::move(b), r, true); },
+                                 cfg_.s2s_thread_num));
+        Status st = session_.register_node(PSERVER_S2S_RPC_NAME, s2s_->address(), &node_id_);
+        if (!st.ok()) throw std::runtime_error("server: cannot register at the master: " + st.to_string());
+        c2s_.reset(new RpcServer([this](Bytes&& b, RpcServer::Responder r) { dispatch(std::move(b), r, false); },
+                                 cfg_.c2s_thread_num));
+        int32_t same = -1;
+        st = session_.register_node(PSERVER_C2S_RPC_NAME, c2s_->address(), &same, node_id_);
+        if (!st.ok()) throw std::runtime_error("server: cannot register c2s: " + st.to_string());
+    }
+    ~Server() { stop(); }
+
+    int32_t node_id() const { return node_id_; }
+    std::string c2s_address() const { return c2s_->address(); }
+    std::string s2s_address() const { return s2s_->address(); }
+    bool exited() const { return exited_; }
+    Context& context() { return ctx_; }
+
+    void stop() {
+        if (stopped_.exchange(true)) return;
+        session_.close();  // the master drops our registrations: we are gone
+        if (c2s_) c2s_->stop();
+        if (s2s_) s2s_->stop();
+    }
+
+    // Counters in the spirit of ps_requests_total / ps_errors_total (pico-ps/service/Service.cpp:23-33).
+    std::map<std::string, uint64_t> metrics() {
+        std::lock_guard<std::mutex> g(metric_mu_);
+        return metrics_;
+    }
+
+    // ---------------------------------------------------------------------------------------
+    // HA: adopt the descriptors of a dead node in every table and refill the storages.
+    Status restore_storages(int* restored_tables = nullptr) {
+        std::vector<int32_t> mine;
+        PSB_RETURN_IF_ERROR(master_.acquire_lock(PSERVER_LOCK_NAME));
+        Status st = find_dead_node_and_replace(&mine);
+        master_.release_lock(PSERVER_LOCK_NAME);
+        PSB_RETURN_IF_ERROR(st);
+        for (int32_t sid : mine) {
+            std::shared_ptr<TableEntry> e = ctx_.get(sid);
+            {
+                std::unique_lock<std::shared_mutex> g(e->mu);
+                PSB_RETURN_IF_ERROR(ensure_storage(*e));
+            }
+            Status rs = restore_storage_coordinated(*e);
+            if (!rs.ok()) rs = restore_storage_from_fs(*e);
+            PSB_RETURN_IF_ERROR(rs);
+            // LOADING -> RUNNING, publish, tell the peers
+            PSB_RETURN_IF_ERROR(master_.acquire_lock(PSERVER_LOCK_NAME));
+            std::string json;
+            st = master_.get_context(ctx_key(sid), &json);
+            if (st.ok()) {
+                std::unique_lock<std::shared_mutex> g(e->mu);
+                e->td.from_json_str(json);
+                e->td.set_node_status_to_running(node_id_);
+                e->rt.build(e->td, node_id_);
+                st = master_.set_context(ctx_key(sid), e->td.to_json_str());
+            }
+            master_.release_lock(PSERVER_LOCK_NAME);
+            PSB_RETURN_IF_ERROR(st);
+            broadcast_ctx_update(*e);
+        }
+        if (restored_tables) *restored_tables = (int)mine.size();
+        return Status::Ok();
+    }
+
+    // ---------------------------------------------------------------------------------------
+    // Incremental sync (trainer -> predictor, pico-ps/service/Service.cpp:1467-1540): start recording
+    // which rows change, then stream the changed rows of the local shards through `send_block` in
+    // blocks; the marks are cleared only when every block went through, so a failed round is simply
+    // repeated (the reference rewinds its iterator clone).
+    Status enable_sync(int32_t sid) {
+        auto e = ctx_.get(sid);
+        if (!e || !e->storage) return Status::InvalidID("no storage " + std::to_string(sid));
+        e->storage->enable_dirty_tracking();
+        return Status::Ok();
+    }
+    Status push_sync_table(int32_t sid, size_t block,
+                           const std::function<Status(const int64_t*, const float*, size_t, uint32_t)>& send_block,
+                           uint64_t* n_synced) {
+        auto e = ctx_.get(sid);
+        if (!e || !e->storage) return Status::InvalidID("no storage " + std::to_string(sid));
+        *n_synced = 0;
+        std::unique_lock<std::shared_mutex> flip(e->incr.mu);  // pushes wait while the increment is collected
+        if (!e->incr.updated) return Status::Ok();
+        std::vector<int64_t> keys;
+        std::vector<float> rows;
+        for (int s : e->storage->shard_list()) {
+            uint64_t cursor = 0;
+            bool finished = false;
+            while (!finished) {
+                keys.clear();
+                rows.clear();
+                PSB_RETURN_IF_ERROR(e->storage->export_shard(s, cursor, std::max<size_t>(block, 64) * 4, true, &keys, &rows, &cursor, &finished));
+                for (size_t off = 0; off < keys.size(); off += block) {
+                    const size_t m = std::min(block, keys.size() - off);
+                    PSB_RETURN_IF_ERROR(send_block(keys.data() + off, rows.data() + off * e->storage->stride(), m, e->storage->stride()));
+                    *n_synced += m;
+                }
+            }
+        }
+        e->storage->clear_dirty();
+        e->incr.updated = false;
+        return Status::Ok();
+    }
+
+private:
+    // ------------------------------------------------------------------------- plumbing
+    static Bytes reply(const Status& st, const Archive* payload, const PSMessageMeta& meta) {
+        Archive out;
+        out << st;
+        if (payload) out.write_raw(payload->data(), payload->size());
+        out << meta;
+        return out.release();
+    }
+    void count(const std::string& name) {
+        std::lock_guard<std::mutex> g(metric_mu_);
+        ++metrics_[name];
+    }
+
+    void dispatch(Bytes&& bytes, RpcServer::Responder resp, bool s2s) {
+        PSMessage msg = PSMessage::open(std::move(bytes));
+        const PSMessageMeta meta = msg.meta;
+        Archive out;
+        Status st;
+        count(std::string(s2s ? "s2s_" : "c2s_") + request_type_name(meta.req_type));
+        try {
+            st = process(msg, &out, s2s);
+        } catch (const std::exception& ex) {
+            st = Status::Error(std::string("server exception: ") + ex.what());
+        }
+        if (!st.ok()) count("errors_total");
+        resp.send(reply(st, &out, meta));
+        if (meta.req_type == RequestType::EXIT) {
+            exited_ = true;
+            std::thread([this] { stop(); }).detach();
+        }
+    }
+
+    // Context version gate. Self-heals a server that is behind by pulling the context first.
+    Status check_ctx_version(TableEntry& e, const PSMessageMeta& meta) {
+        if (meta.ctx_ver > e.td.version) {
+            std::string json;
+            if (master_.get_context(ctx_key(e.sid), &json).ok()) apply_ctx_json(e, json);
+        }
+        if (meta.ctx_ver > e.td.version) return Status::ServerTooOldCtx("server context older than the client's");
+        if (meta.ctx_ver < e.td.version) return Status::ServerTooNewCtx("server context newer than the client's");
+        return Status::Ok();
+    }
+    Status check_write_ctx_version(TableEntry& e, const PSMessageMeta& meta) {
+        PSB_RETURN_IF_ERROR(check_ctx_version(e, meta));
+        if (e.td.status == StorageStatus::RESHARD) return Status::OOM("write when update context");
+        return Status::Ok();
+    }
+    Status check_table_version(TableEntry& e, const PSMessageMeta& meta) {
+        if (meta.ctx_ver != e.td.version || meta.ctx_u_ver != e.td.update_version) {
+            std::string json;
+            if (master_.get_context(ctx_key(e.sid), &json).ok()) apply_ctx_json(e, json);
+        }
+        if (meta.ctx_ver != e.td.version) return meta.ctx_ver > e.td.version ? Status::ServerTooOldCtx("ctx") : Status::ServerTooNewCtx("ctx");
+        if (meta.ctx_u_ver != e.td.update_version)
+            return meta.ctx_u_ver > e.td.update_version ? Status::ServerTooOldCtxU("update ctx") : Status::ServerTooNewCtxU("update ctx");
+        return Status::Ok();
+    }
+
+    Status ensure_storage(TableEntry& e) {
+        if (e.storage) return Status::Ok();
+        auto* sop = static_cast<SparseTableStorageOperator*>(e.storage_op.get());
+        return sop->create_storage(e.rt.global_shard_num(), e.rt.local_shards(), &e.storage);
+    }
+
+    // Install a context JSON on an existing entry: refresh runtime info, match local shards, and swap
+    // in the reshard result when the new placement has been committed.
+    void apply_ctx_json(TableEntry& e, const std::string& json) {
+        Json j;
+        if (!Json::parse(json, &j)) return;
+        const int32_t old_uv = e.td.update_version;
+        const bool had_update = !e.td.update_nodes.empty();
+        if (!e.td.from_json(j, true)) return;
+        e.rt.build(e.td, node_id_);
+        e.update_rt.build(e.td, node_id_, true);
+        e.update_handlers();
+        const bool committed = had_update && e.td.update_nodes.empty() && e.td.update_version > old_uv;
+        if (committed && e.update_storage) {
+            e.storage = std::move(e.update_storage);  // the reshuffled data becomes the serving data
+        } else if (e.storage) {
+            // plain placement change (e.g. a dead node replaced): create / drop local shards to match
+            if (e.storage->n_shards() == e.rt.global_shard_num()) {
+                for (int s : e.storage->shard_list())
+                    if (!e.rt.local_shards().count(s)) e.storage->erase_shard(s);
+                for (int s : e.rt.local_shards())
+                    if (!e.storage->has_shard(s)) e.storage->create_shard(s);
+            }
+        }
+    }
+
+    Status refresh_from_master(int32_t sid, std::shared_ptr<TableEntry>* out) {
+        std::string json;
+        PSB_RETURN_IF_ERROR(master_.get_context(ctx_key(sid), &json));
+        std::shared_ptr<TableEntry> e = ctx_.get(sid);
+        if (!e) {
+            PSB_RETURN_IF_ERROR(ctx_.set_table_descriptor(sid, json, node_id_, &e));
+            std::unique_lock<std::shared_mutex> g(e->mu);
+            PSB_RETURN_IF_ERROR(ensure_storage(*e));
+        } else {
+            std::unique_lock<std::shared_mutex> g(e->mu);
+            apply_ctx_json(*e, json);
+        }
+        if (out) *out = e;
+        return Status::Ok();
+    }
+
+    Status peers(const char* service, std::map<int32_t, std::string>* nodes) { return master_.get_nodes(service, nodes); }
+
+    // Fan a request out to servers over s2s and collect the statuses.
+    Status s2s_call(const std::map<int, Archive>& bodies, PSMessageMeta meta, RequestType type) {
+        std::map<int32_t, std::string> nodes;
+        PSB_RETURN_IF_ERROR(peers(PSERVER_S2S_RPC_NAME, &nodes));
+        meta.req_type = type;
+        std::vector<RpcClient::Ticket> tickets;
+        for (auto& kv : bodies) {
+            auto it = nodes.find(kv.first);
+            if (it == nodes.end()) return Status::NoReplica("s2s: node " + std::to_string(kv.first) + " is not registered");
+            PSMessage m;
+            m.ar = kv.second;
+            m.meta = meta;
+            tickets.push_back(s2s_client_.send(it->second, m.seal()));
+        }
+        Status result;
+        for (auto& t : tickets) {
+            Bytes b;
+            Status st = s2s_client_.wait(t, cfg_.s2s_timeout_ms, &b);
+            if (st.ok()) {
+                PSMessage r = PSMessage::open(std::move(b));
+                r.ar >> st;
+            }
+            if (!st.ok() && result.ok()) result = st;
+        }
+        return result;
+    }
+
+    void broadcast_ctx_update(TableEntry& e) {
+        std::map<int32_t, std::string> nodes;
+        if (!peers(PSERVER_C2S_RPC_NAME, &nodes).ok()) return;
+        PSMessage m;
+        m.meta.sid = e.sid;
+        m.meta.req_type = RequestType::CTX_UPDATE;
+        std::vector<RpcClient::Ticket> tickets;
+        for (auto& kv : nodes)
+            if (kv.first != node_id_) tickets.push_back(s2s_client_.send(kv.second, m.seal()));
+        for (auto& t : tickets) {
+            Bytes b;
+            s2s_client_.wait(t, 5000, &b);
+        }
+    }
+
+    // ------------------------------------------------------------------------- dispatch
+    Status process(PSMessage& msg, Archive* out, bool s2s) {
+        const PSMessageMeta& meta = msg.meta;
+        Archive& in = msg.ar;
+        switch (meta.req_type) {
+            case RequestType::HEALTH_CHECK: *out << node_id_; return Status::Ok();
+            case RequestType::EXIT: return Status::Ok();
+            case RequestType::OP_LOAD_LIBRARY: {
+                std::string path;
+                in >> path;
+                return OperatorFactory::instance().load_library(path);
+            }
+            case RequestType::MEMORY_INFO: {
+                NodeMemoryInfo mi;
+                for (int32_t sid : ctx_.ids()) {
+                    auto e = ctx_.get(sid);
+                    if (!e || !e->storage) continue;
+                    mi.healthy = mi.healthy && e->storage->healthy();
+                    mi.used += e->storage->memory_usage();
+                    mi.managed += e->storage->memory_usage();
+                }
+                *out << (int32_t)(mi.healthy ? 1 : 0) << mi.used << mi.managed;
+                return Status::Ok();
+            }
+            case RequestType::STORAGE_CREATE: return process_create_storage(meta, in);
+            case RequestType::CTX_UPDATE: return refresh_from_master(meta.sid, nullptr);
+            default: break;
+        }
+        std::shared_ptr<TableEntry> e = ctx_.get(meta.sid);
+        if (!e) {
+            // a server that joined later (new node of a reshard, restored node) learns tables lazily
+            Status st = refresh_from_master(meta.sid, &e);
+            if (!st.ok() || !e) return Status::InvalidID("no storage " + std::to_string(meta.sid) + " on node " + std::to_string(node_id_));
+        }
+        switch (meta.req_type) {
+            case RequestType::STORAGE_DELETE: ctx_.erase(meta.sid); return Status::Ok();
+            case RequestType::STORAGE_CLEAR: {
+                std::shared_lock<std::shared_mutex> g(e->mu);
+                PSB_RETURN_IF_ERROR(check_write_ctx_version(*e, meta));
+                PSB_RETURN_IF_ERROR(e->storage->clear());
+                for (int s : e->rt.local_shards()) e->storage->create_shard(s);
+                return Status::Ok();
+            }
+            case RequestType::STORAGE_STATISTIC: {
+                std::shared_lock<std::shared_mutex> g(e->mu);
+                std::vector<int> shards = e->storage->shard_list();
+                *out << (int32_t)shards.size();
+                for (int s : shards)
+                    *out << (uint64_t)e->storage->shard_size(s) << (uint64_t)(e->storage->memory_usage() / std::max<size_t>(1, shards.size()))
+                         << node_id_ << (int32_t)s;
+                return Status::Ok();
+            }
+            case RequestType::HANDLER_REGISTER: {
+                std::unique_lock<std::shared_mutex> g(e->mu);
+                int32_t hid = 0;
+                OperatorDescriptor d;
+                in >> hid >> d.key >> d.lib_name >> d.op_name >> d.config_str;
+                e->td.handlers[hid] = d;
+                e->td.refresh_info();
+                return e->update_handlers();
+            }
+            case RequestType::HANDLER_DEREGISTER: {
+                std::unique_lock<std::shared_mutex> g(e->mu);
+                int32_t hid = 0;
+                in >> hid;
+                e->td.handlers.erase(hid);
+                e->td.refresh_info();
+                return e->update_handlers();
+            }
+            case RequestType::OP_PULL: return process_pull(*e, meta, in, out);
+            case RequestType::OP_PUSH_ASYNC:
+                if (s2s) return process_direct_push(*e, in, false);
+                return process_push(*e, meta, in, false);
+            case RequestType::OP_PUSH_SYNC: return process_push(*e, meta, in, true);
+            case RequestType::OP_STORE: {
+                std::shared_lock<std::shared_mutex> g(e->mu);
+                PSB_RETURN_IF_ERROR(check_write_ctx_version(*e, meta));
+                auto op = find_op<SparseTablePushOperator>(*e, meta.hid);
+                if (!op) return Status::InvalidID("store: handler is not a push operator");
+                return op->apply_store(*e);
+            }
+            case RequestType::OP_FOREACH:
+            case RequestType::OP_ERASEIF:
+            case RequestType::OP_DUMP: return process_for_each(*e, meta, in, out);
+            case RequestType::OP_LOAD: return process_load(*e, meta, in, out);
+            case RequestType::OP_SYNC: {
+                std::shared_lock<std::shared_mutex> g(e->mu);
+                PSB_RETURN_IF_ERROR(check_write_ctx_version(*e, meta));
+                auto op = find_op<KVSyncOperator>(*e, meta.hid);
+                if (!op) return Status::InvalidID("sync: handler is not a sync operator");
+                Bytes raw;
+                in >> raw;
+                std::vector<uint8_t> plain;
+                PSB_RETURN_IF_ERROR(op->compressor().decompress(raw.data(), raw.size(), &plain));
+                Archive body(std::move(plain));
+                if (!e->storage->healthy()) return Status::OOM("storage unhealthy");
+                return DirectPushOperator::apply_request(e->storage.get(), body);
+            }
+            case RequestType::OP_UDF: {
+                std::shared_lock<std::shared_mutex> g(e->mu);
+                auto op = find_op<UDFOperator>(*e, meta.hid);
+                if (!op) return Status::InvalidID("udf: handler is not a udf operator");
+                PSB_RETURN_IF_ERROR(op->read_only() ? check_ctx_version(*e, meta) : check_write_ctx_version(*e, meta));
+                std::string param, result;
+                in >> param;
+                PSB_RETURN_IF_ERROR(op->apply_request(*e, param, &result));
+                *out << result;
+                return Status::Ok();
+            }
+            case RequestType::OP_COORDINATED_RESTORE_ITERATE: return process_restore_iterate(*e, in, out);
+            case RequestType::NEW_CTX_CREATE_SHARD: return process_new_ctx_create_shard(*e, meta);
+            case RequestType::NEW_CTX_SHUFFLE:
+                if (s2s) return process_direct_push(*e, in, true);
+                return process_new_ctx_shuffle(*e, meta, in);
+            case RequestType::NEW_CTX_STORE: {
+                std::shared_lock<std::shared_mutex> g(e->mu);
+                PSB_RETURN_IF_ERROR(check_table_version(*e, meta));
+                if (e->update_rt.local_shards().empty()) return Status::Ok();
+                return e->update_storage ? Status::Ok() : Status::Error("new ctx store: no update storage on this node");
+            }
+            case RequestType::NEW_CTX_PURGE: {
+                std::unique_lock<std::shared_mutex> g(e->mu);
+                e->update_storage.reset();
+                if (e->storage) {
+                    for (int s : e->storage->shard_list())
+                        if (!e->rt.local_shards().count(s)) e->storage->erase_shard(s);
+                    e->storage->set_healthy(true);
+                }
+                return Status::Ok();
+            }
+            default: return Status::Error(std::string("unhandled request type ") + request_type_name(meta.req_type));
+        }
+    }
+
+    template <class OP>
+    std::shared_ptr<OP> find_op(TableEntry& e, int32_t hid) {
+        auto it = e.ops.find(hid);
+        if (it == e.ops.end()) return nullptr;
+        return std::dynamic_pointer_cast<OP>(it->second);
+    }
+
+    // ------------------------------------------------------------------------- storage life cycle
+    Status process_create_storage(const PSMessageMeta& meta, Archive& in) {
+        std::string lib, op, cfg_str;
+        in >> lib >> op >> cfg_str;
+        Json cfg;
+        if (!Json::parse(cfg_str, &cfg)) return Status::InvalidConfig("storage config is not valid JSON");
+        std::shared_ptr<TableEntry> e;
+        PSB_RETURN_IF_ERROR(ctx_.create_storage(meta.sid, lib, op, cfg, node_id_, &e));
+        if (std::string(e->storage_op->kind()) != "storage") return Status::InvalidConfig(op + " is not a storage operator");
+        std::unique_lock<std::shared_mutex> g(e->mu);
+        Status st = ensure_storage(*e);
+        if (!st.ok()) ctx_.erase(meta.sid);
+        return st;
+    }
+
+    // ------------------------------------------------------------------------- data path
+    Status process_pull(TableEntry& e, const PSMessageMeta& meta, Archive& in, Archive* out) {
+        std::shared_lock<std::shared_mutex> g(e.mu);
+        auto op = find_op<SparseTablePullOperator>(e, meta.hid);
+        if (!op) return Status::InvalidID("pull: handler " + std::to_string(meta.hid) + " is not a pull operator");
+        // read-only pulls keep working during a reshard; pulls that may insert are writes
+        PSB_RETURN_IF_ERROR(op->read_only() ? check_ctx_version(e, meta) : check_write_ctx_version(e, meta));
+        if (!e.storage) return Status::InvalidID("no storage");
+        return op->apply_request(e, in, out);
+    }
+    Status process_push(TableEntry& e, const PSMessageMeta& meta, Archive& in, bool sync) {
+        std::shared_lock<std::shared_mutex> g(e.mu);
+        auto op = find_op<SparseTablePushOperator>(e, meta.hid);
+        if (!op) return Status::InvalidID("push: handler " + std::to_string(meta.hid) + " is not a push operator");
+        PSB_RETURN_IF_ERROR(check_write_ctx_version(e, meta));
+        return op->apply_request(e, in, sync);
+    }
+    Status process_direct_push(TableEntry& e, Archive& in, bool into_update) {
+        std::shared_lock<std::shared_mutex> g(e.mu);
+        KVStorage* dst = into_update ? e.update_storage.get() : e.storage.get();
+        if (!dst) return Status::Error(into_update ? "shuffle target has no update storage" : "no storage");
+        if (!dst->healthy()) return Status::OOM("storage unhealthy");
+        return DirectPushOperator::apply_request(dst, in);
+    }
+
+    Status process_for_each(TableEntry& e, const PSMessageMeta& meta, Archive& in, Archive* out) {
+        std::shared_lock<std::shared_mutex> g(e.mu);
+        PSB_RETURN_IF_ERROR(check_write_ctx_version(e, meta));
+        if (meta.req_type == RequestType::OP_DUMP) {
+            auto op = find_op<DumpOperator>(e, meta.hid);
+            if (!op) return Status::InvalidID("dump: handler is not a dump operator");
+            DumpArgs args;
+            int32_t file_id = 0;
+            std::vector<int32_t> shards;
+            in >> args.uri >> args.file_number >> file_id >> shards;
+            uint64_t n = 0;
+            PSB_RETURN_IF_ERROR(op->apply_request(e, node_id_, args, file_id, shards, &n));
+            *out << n;
+            return Status::Ok();
+        }
+        int32_t shard = 0;
+        std::string carried_str;
+        in >> shard >> carried_str;
+        Json carried = Json::object();
+        if (!carried_str.empty() && !Json::parse(carried_str, &carried)) return Status::InvalidConfig("carried item is not JSON");
+        if (meta.req_type == RequestType::OP_ERASEIF) {
+            auto op = find_op<EraseIfOperator>(e, meta.hid);
+            if (!op) return Status::InvalidID("erase_if: handler is not an erase_if operator");
+            uint64_t erased = 0;
+            PSB_RETURN_IF_ERROR(op->apply_request(e, shard, carried, &erased));
+            *out << erased;
+            return Status::Ok();
+        }
+        auto op = find_op<ForEachOperator>(e, meta.hid);
+        if (!op) return Status::InvalidID("for_each: handler is not a for_each operator");
+        ForEachResult r;
+        PSB_RETURN_IF_ERROR(op->apply_request(e, shard, carried, &r));
+        *out << r.count << r.sum << r.sum_sq << r.max_abs;
+        return Status::Ok();
+    }
+
+    // load: {uri, need_rehash, files}. need_rehash: stream the files and DirectPush every block to the
+    // owners over s2s (works across different shardings); else keep only the local keys.
+    Status process_load(TableEntry& e, const PSMessageMeta& meta, Archive& in, Archive* out) {
+        std::shared_lock<std::shared_mutex> g(e.mu);
+        auto op = find_op<LoadOperator>(e, meta.hid);
+        if (!op) return Status::InvalidID("load: handler is not a load operator");
+        std::string uri;
+        int32_t need_rehash = 0;
+        std::vector<std::string> files;
+        in >> uri >> need_rehash >> files;
+        std::string dir, format;
+        DumpArgs::split_uri(uri, &dir, &format);
+        if (files.empty()) files = list_model_files(dir);
+        uint64_t n = 0;
+        const auto* sop = storage_op_of(e);
+        for (auto& f : files) {
+            if (!need_rehash) {
+                PSB_RETURN_IF_ERROR(op->restore_file(e, f, format, &n));
+                continue;
+            }
+            DsReader r;
+            PSB_RETURN_IF_ERROR(r.open(f, format, e.storage->stride(), &op->compressor()));
+            std::vector<int64_t> keys;
+            std::vector<float> rows;
+            while (r.next_block(op->block_size(), &keys, &rows)) {
+                std::map<int, Archive> bodies;
+                PSB_RETURN_IF_ERROR(DirectPushOperator::generate_requests(sop, e.rt, keys.data(), rows.data(), keys.size(),
+                                                                          e.storage->stride(), &bodies));
+                PSMessageMeta m = meta;
+                PSB_RETURN_IF_ERROR(s2s_call(bodies, m, RequestType::OP_PUSH_ASYNC));
+                n += keys.size();
+            }
+        }
+        *out << n;
+        return Status::Ok();
+    }
+
+    // ------------------------------------------------------------------------- reshard
+    Status process_new_ctx_create_shard(TableEntry& e, const PSMessageMeta& meta) {
+        std::unique_lock<std::shared_mutex> g(e.mu);
+        PSB_RETURN_IF_ERROR(check_table_version(e, meta));
+        if (e.update_rt.local_shards().empty()) return Status::Ok();  // this node leaves the table
+        auto* sop = static_cast<SparseTableStorageOperator*>(e.storage_op.get());
+        return sop->create_storage(e.update_rt.global_shard_num(), e.update_rt.local_shards(), &e.update_storage);
+    }
+    // One old shard: stream its items in blocks to the owners under the NEW placement.
+    Status process_new_ctx_shuffle(TableEntry& e, const PSMessageMeta& meta, Archive& in) {
+        std::shared_lock<std::shared_mutex> g(e.mu);
+        PSB_RETURN_IF_ERROR(check_table_version(e, meta));
+        int32_t old_shard = 0;
+        in >> old_shard;
+        if (!e.storage || !e.storage->has_shard(old_shard)) return Status::InvalidID("shuffle: shard is not on this node");
+        size_t block_bytes = 1000000;
+        for (auto& kv : e.ops)
+            if (auto u = std::dynamic_pointer_cast<ShardUpdateContextOperator>(kv.second)) block_bytes = u->block_bytes();
+        const uint32_t stride = e.storage->stride();
+        const uint64_t window = std::max<uint64_t>(64, block_bytes / (8 + (size_t)stride * 4));
+        const auto* sop = storage_op_of(e);
+        uint64_t cursor = 0;
+        bool finished = false;
+        std::vector<int64_t> keys;
+        std::vector<float> rows;
+        while (!finished) {
+            keys.clear();
+            rows.clear();
+            PSB_RETURN_IF_ERROR(e.storage->export_shard(old_shard, cursor, window, false, &keys, &rows, &cursor, &finished));
+            if (keys.empty()) continue;
+            std::map<int, Archive> bodies;
+            PSB_RETURN_IF_ERROR(DirectPushOperator::generate_requests(sop, e.update_rt, keys.data(), rows.data(), keys.size(),
+                                                                      stride, &bodies));
+            PSB_RETURN_IF_ERROR(s2s_call(bodies, meta, RequestType::NEW_CTX_SHUFFLE));
+        }
+        return Status::Ok();
+    }
+
+    // ------------------------------------------------------------------------- HA restore
+    // Replica side of coordinated restore: {iterator_id, offset, batch_size, shard_id} -> one batch.
+    Status process_restore_iterate(TableEntry& e, Archive& in, Archive* out) {
+        std::shared_lock<std::shared_mutex> g(e.mu);
+        int32_t iterator_id = -1, shard = -1;
+        uint64_t offset = 0, batch = 0;
+        in >> iterator_id >> offset >> batch >> shard;
+        if (!e.storage || !e.storage->has_shard(shard)) return Status::InvalidID("restore: shard is not on this node");
+        {
+            std::lock_guard<std::mutex> ig(e.iter_mu);
+            if (iterator_id < 0 || !e.restore_iters.count(iterator_id)) {
+                iterator_id = e.next_iter_id++;
+                e.restore_iters[iterator_id] = RestoreIterator{shard, offset};
+            }
+        }
+        std::vector<int64_t> keys;
+        std::vector<float> rows;
+        uint64_t next = offset;
+        bool finished = false;
+        PSB_RETURN_IF_ERROR(e.storage->export_shard(shard, offset, std::max<uint64_t>(batch, 1), false, &keys, &rows, &next, &finished));
+        {
+            std::lock_guard<std::mutex> ig(e.iter_mu);
+            if (finished) e.restore_iters.erase(iterator_id);
+            else e.restore_iters[iterator_id].cursor = next;
+        }
+        *out << e.sid << shard << (int32_t)(finished ? 1 : 0) << iterator_id << next << (uint64_t)keys.size() << (int32_t)e.storage->stride();
+        out->write_raw(keys.data(), keys.size() * 8);
+        out->write_raw(rows.data(), rows.size() * 4);
+        return Status::Ok();
+    }
+
+    Status find_dead_node_and_replace(std::vector<int32_t>* mine) {
+        std::map<int32_t, std::string> live;
+        PSB_RETURN_IF_ERROR(master_.get_nodes(PSERVER_S2S_RPC_NAME, &live));
+        std::set<int> live_ids;
+        for (auto& kv : live) live_ids.insert(kv.first);
+        std::vector<std::string> keys;
+        PSB_RETURN_IF_ERROR(master_.list_contexts(&keys));
+        for (auto& k : keys) {
+            if (k.compare(0, 8, "storage/") != 0) continue;
+            const int32_t sid = std::stoi(k.substr(8));
+            std::string json;
+            if (!master_.get_context(k, &json).ok()) continue;
+            TableDescriptor td;
+            if (!td.from_json_str(json)) continue;
+            td.update_node_status(live_ids);
+            if (!td.try_to_replace_one_dead_node(node_id_)) continue;
+            PSB_RETURN_IF_ERROR(master_.set_context(k, td.to_json_str()));
+            std::shared_ptr<TableEntry> e;
+            PSB_RETURN_IF_ERROR(ctx_.set_table_descriptor(sid, td.to_json_str(), node_id_, &e));
+            mine->push_back(sid);
+        }
+        return Status::Ok();
+    }
+
+    // Pull every local shard from one live replica in resumable batches over s2s.
+    Status restore_storage_coordinated(TableEntry& e) {
+        std::map<int32_t, std::string> nodes;
+        PSB_RETURN_IF_ERROR(peers(PSERVER_S2S_RPC_NAME, &nodes));
+        for (int32_t shard : e.rt.local_shards()) {
+            std::set<int> exclude{node_id_};
+            int replica = -1;
+            {
+                std::shared_lock<std::shared_mutex> g(e.mu);
+                replica = e.rt.pick_one_replica(shard, &exclude);
+            }
+            if (replica < 0 || !nodes.count(replica)) return Status::NoReplica("restore: no live replica of shard " + std::to_string(shard));
+            int32_t iterator_id = -1;
+            uint64_t offset = 0;
+            for (;;) {
+                PSMessage m;
+                m.meta.sid = e.sid;
+                m.meta.req_type = RequestType::OP_COORDINATED_RESTORE_ITERATE;
+                m.ar << iterator_id << offset << (uint64_t)cfg_.restore_batch_size << shard;
+                Bytes b;
+                PSB_RETURN_IF_ERROR(s2s_client_.call(nodes[replica], m.seal(), cfg_.s2s_timeout_ms, &b));
+                PSMessage r = PSMessage::open(std::move(b));
+                Status st;
+                r.ar >> st;
+                PSB_RETURN_IF_ERROR(st);
+                int32_t sid = 0, sh = 0, fin = 0, stride = 0;
+                uint64_t num = 0;
+                r.ar >> sid >> sh >> fin >> iterator_id >> offset >> num >> stride;
+                std::vector<int64_t> keys(num);
+                std::vector<float> rows((size_t)num * stride);
+                r.ar.read_raw(keys.data(), num * 8);
+                r.ar.read_raw(rows.data(), rows.size() * 4);
+                if (num) PSB_RETURN_IF_ERROR(e.storage->set_rows(keys.data(), rows.data(), num, false));
+                if (fin) break;
+            }
+        }
+        return Status::Ok();
+    }
+
+    // Fallback: the dump at table_uri, keeping local keys only.
+    Status restore_storage_from_fs(TableEntry& e) {
+        if (e.td.table_uri.empty()) return Status::Error("restore: no replica and no table_uri");
+        std::string dir, format;
+        DumpArgs::split_uri(e.td.table_uri, &dir, &format);
+        Json cfg = Json::object();
+        for (auto& kv : e.td.handlers)
+            if (kv.second.op_name == "DumpOperator" || kv.second.op_name == "LoadOperator") Json::parse(kv.second.config_str, &cfg);
+        LoadOperator op(cfg);
+        uint64_t n = 0;
+        for (auto& f : list_model_files(dir)) PSB_RETURN_IF_ERROR(op.restore_file(e, f, format, &n));
+        return Status::Ok();
+    }
+
+    ServerConfig cfg_;
+    MasterClient master_;   // request / response traffic with the master
+    MasterClient session_;  // holds the registrations: its connection is this node's liveness
+    int32_t node_id_ = -1;
+    Context ctx_;
+    std::unique_ptr<RpcServer> c2s_, s2s_;
+    RpcClient s2s_client_;
+    std::atomic<bool> stopped_{false}, exited_{false};
+    std::mutex metric_mu_;
+    std::map<std::string, uint64_t> metrics_;
+};
+
+}  // namespace psb

@@ -30,6 +30,8 @@ struct HostTableConfig {
     int32_t opt_type = OPT_SGD;
     bool sync_delta = false;
     int32_t n_shards = 1;  // global shard count
+    int32_t partition = 0; // 0: sparse keys, jump_consistent_hash(murmur(key)); 1: dense slices, key = (id << 24) | slice,
+                           //    shard = hash(id, slice) % n_shards (pico-ps/common/dense_common.h:58-65)
     uint64_t init_seed = 0;
     float init_range = 0.01f;
     float slot_init0 = 0.f;
@@ -87,7 +89,12 @@ public:
         return v;
     }
 
-    int shard_of(int64_t key) const { return sparse_shard_of(key, cfg_.n_shards); }
+    int shard_of(int64_t key) const {
+        if (cfg_.partition == 1) return dense_shard_of(key >> 24, (int32_t)(key & 0xFFFFFF), cfg_.n_shards);
+        return sparse_shard_of(key, cfg_.n_shards);
+    }
+    // Change the global shard count (reshard): existing shards keep their ids, the caller migrates keys.
+    void set_n_shards(int32_t n) { cfg_.n_shards = n; }
 
     void init_row(float* row, int64_t key) const {
         for (uint32_t d = 0; d < cfg_.dim; ++d) row[d] = init_uniform(key, d, cfg_.init_seed, cfg_.init_range);

@@ -1,0 +1,113 @@
+// KVStorage: what the operators see of one table on one server - a set of local shards holding
+// key -> row records - independent of where the rows live (host DRAM or GPU HBM).
+//
+// Parity: the ShardStorage contract of pico-ps/storage/Storage.h:129-138,261-289 (create_shard /
+// erase_shard / shard_size / shard_memory_usage / get_shard_iterator / clear / healthy) plus the typed
+// access the operators do through boost::any casts; here the value type is fixed to
+// fp32 rows [embedding | optimizer slots | optional sync delta] so that one interface serves both
+// back-ends.
+#pragma once
+#include <memory>
+#include <vector>
+
+#include "../common/status.h"
+#include "../kernels/optim.cuh"
+#include "host_table.h"
+
+namespace psb {
+
+class KVStorage {
+public:
+    virtual ~KVStorage() = default;
+    virtual uint32_t dim() const = 0;
+    virtual uint32_t stride() const = 0;
+    virtual int32_t n_shards() const = 0;
+    virtual void set_n_shards(int32_t n) = 0;
+    virtual int shard_of(int64_t key) const = 0;
+    virtual const char* backend() const = 0;
+
+    virtual Status create_shard(int s) = 0;
+    virtual Status erase_shard(int s) = 0;
+    virtual bool has_shard(int s) const = 0;
+    virtual std::vector<int> shard_list() const = 0;
+
+    // keys all belong to shard s. out: n*dim.
+    virtual Status pull(int s, const int64_t* keys, size_t n, float* out, bool insert) = 0;
+    // pre-aggregated items of shard s. grads: n*dim.
+    virtual Status push(int s, const int64_t* keys, const float* grads, size_t n, const OptConfig& opt, bool sync) = 0;
+    virtual Status store(const OptConfig& opt) = 0;
+    // rows: n*stride (or n*dim with emb_only); keys of shards that are not local are skipped.
+    virtual Status set_rows(const int64_t* keys, const float* rows, size_t n, bool emb_only) = 0;
+    // Resumable scan of one shard; appends to keys/rows (rows: stride floats per key).
+    virtual Status export_shard(int s, uint64_t cursor, uint64_t window, bool dirty_only, std::vector<int64_t>* keys,
+                                std::vector<float>* rows, uint64_t* next_cursor, bool* finished) = 0;
+    virtual Status erase_keys(const int64_t* keys, size_t n, uint64_t* erased) = 0;
+
+    virtual uint64_t shard_size(int s) = 0;
+    virtual uint64_t size() = 0;
+    virtual uint64_t memory_usage() = 0;
+    virtual bool healthy() = 0;
+    virtual void set_healthy(bool h) = 0;
+    virtual void set_limits(uint64_t soft, uint64_t hard) = 0;
+    virtual void enable_dirty_tracking() = 0;
+    virtual void clear_dirty() = 0;
+    virtual Status clear() = 0;
+};
+
+class HostKVStorage : public KVStorage {
+public:
+    explicit HostKVStorage(const HostTableConfig& cfg) : t_(cfg) {}
+    HostTable& table() { return t_; }
+    uint32_t dim() const override { return t_.dim(); }
+    uint32_t stride() const override { return t_.stride(); }
+    int32_t n_shards() const override { return t_.n_shards(); }
+    void set_n_shards(int32_t n) override { t_.set_n_shards(n); }
+    int shard_of(int64_t key) const override { return t_.shard_of(key); }
+    const char* backend() const override { return "host"; }
+    Status create_shard(int s) override { t_.create_shard(s); return Status::Ok(); }
+    Status erase_shard(int s) override { t_.erase_shard(s); return Status::Ok(); }
+    bool has_shard(int s) const override { return t_.has_shard(s); }
+    std::vector<int> shard_list() const override { return t_.shard_list(); }
+    Status pull(int s, const int64_t* keys, size_t n, float* out, bool insert) override {
+        return t_.pull_shard(s, keys, n, out, insert);
+    }
+    Status push(int s, const int64_t* keys, const float* grads, size_t n, const OptConfig& opt, bool sync) override {
+        return t_.push_shard(s, keys, grads, n, opt, sync);
+    }
+    Status store(const OptConfig& opt) override { return t_.store(opt); }
+    Status set_rows(const int64_t* keys, const float* rows, size_t n, bool emb_only) override {
+        return t_.set_rows(keys, rows, n, emb_only);
+    }
+    Status export_shard(int s, uint64_t cursor, uint64_t window, bool dirty_only, std::vector<int64_t>* keys,
+                        std::vector<float>* rows, uint64_t* next_cursor, bool* finished) override {
+        *next_cursor = t_.export_shard(s, cursor, window, dirty_only, keys, rows, finished);
+        return Status::Ok();
+    }
+    Status erase_keys(const int64_t* keys, size_t n, uint64_t* erased) override {
+        *erased = t_.erase_keys(keys, n);
+        return Status::Ok();
+    }
+    uint64_t shard_size(int s) override { return t_.shard_size(s); }
+    uint64_t size() override { return t_.size(); }
+    uint64_t memory_usage() override { return t_.memory_usage(); }
+    bool healthy() override { return t_.healthy(); }
+    void set_healthy(bool h) override { t_.set_healthy(h); }
+    void set_limits(uint64_t soft, uint64_t hard) override { t_.set_limits(soft, hard); }
+    void enable_dirty_tracking() override { t_.enable_dirty_tracking(); }
+    void clear_dirty() override { t_.clear_dirty(); }
+    Status clear() override { t_.clear(); return Status::Ok(); }
+
+private:
+    HostTable t_;
+};
+
+// Factory of the GPU back-end (defined in gpu_kv_storage.cu; fails with a Status when no device is present).
+struct GpuKVStorageConfig {
+    int device = 0;
+    HostTableConfig base;         // dim, optimizer, init, limits, n_shards
+    uint64_t capacity = 1 << 20;  // expected keys on this server
+    uint32_t max_batch = 1 << 18; // largest request (keys) served in one kernel call
+};
+Status make_gpu_kv_storage(const GpuKVStorageConfig& cfg, std::unique_ptr<KVStorage>* out);
+
+}  // namespace psb

@@ -1,0 +1,77 @@
+"""Service layer: master, servers, clients, handlers, controller, model objects, in-process PS.
+
+These are the native classes of ``csrc/service``, ``csrc/handler``, ``csrc/controller``,
+``csrc/model`` and ``csrc/native_ps`` (the layers L5-L7 of the reference: pico-ps/service,
+pico-ps/handler, pico-ps/controller, pico-ps/model, pico-ps/native_ps). Every process of a job
+creates a :class:`Client` (and, if it holds shards, a :class:`Server`) pointing at one
+:class:`Master`. The built-in operators are registered under the library name ``"psb"``.
+"""
+from __future__ import annotations
+
+import json
+from typing import Dict, Iterable, List, Optional, Sequence
+
+from .._lib import C
+
+Master = C.Master
+MasterClient = C.MasterClient
+Server = C.Server
+ServerConfig = C.ServerConfig
+Client = C.Client
+PullHandler = C.PullHandler
+PushHandler = C.PushHandler
+ForEachHandler = C.ForEachHandler
+EraseIfHandler = C.EraseIfHandler
+DumpHandler = C.DumpHandler
+LoadHandler = C.LoadHandler
+UpdateContextHandler = C.UpdateContextHandler
+SyncHandler = C.SyncHandler
+UDFHandler = C.UDFHandler
+Controller = C.Controller
+OpSpec = C.OpSpec
+NativePS = C.NativePS
+NativePullHandler = C.NativePullHandler
+NativeLoadHandler = C.NativeLoadHandler
+TableDescriptor = C.TableDescriptor
+register_udf = C.register_udf
+
+LIB = "psb"
+
+#: operator keys used by :func:`standard_ops`
+PULL, PULL_RO, PUSH, FOREACH, ERASE, DUMP, LOAD, UPDATE_CTX, SYNC = (
+    "pull", "pull_ro", "push", "for_each", "erase_if", "dump", "load", "update_ctx", "sync")
+
+
+def storage_config(nodes: Dict[int, Sequence[int]], op_config: dict, table_name: str = "") -> str:
+    """Storage config JSON: ``nodes`` maps a server's node id to the shard ids it holds."""
+    return json.dumps({
+        "nodes": [{"g_rank": int(n), "shard_list": [int(s) for s in shards]} for n, shards in nodes.items()],
+        "op_config": op_config,
+        "table_name": table_name,
+    })
+
+
+def nodes_json(nodes: Dict[int, Sequence[int]]) -> str:
+    return json.dumps([{"g_rank": int(n), "shard_list": [int(s) for s in shards]} for n, shards in nodes.items()])
+
+
+def standard_ops(compress: str = "", block_size: int = 1000) -> List["C.OpSpec"]:
+    """The usual operator set of a sparse table (what the reference's tests register one by one)."""
+    c = json.dumps({"compress_algorithm": compress, "block_size": block_size})
+    return [
+        OpSpec(PULL, LIB, "SparseTablePullOperator", "{}"),
+        OpSpec(PULL_RO, LIB, "SparseTablePullOperator", json.dumps({"read_only": True})),
+        OpSpec(PUSH, LIB, "SparseTablePushOperator", "{}"),
+        OpSpec(FOREACH, LIB, "ForEachOperator", "{}"),
+        OpSpec(ERASE, LIB, "EraseIfOperator", "{}"),
+        OpSpec(DUMP, LIB, "DumpOperator", c),
+        OpSpec(LOAD, LIB, "LoadOperator", c),
+        OpSpec(UPDATE_CTX, LIB, "ShardUpdateContextOperator", "{}"),
+        OpSpec(SYNC, LIB, "KVSyncOperator", c),
+    ]
+
+
+def check(st) -> None:
+    from ..utils.status import raise_if_error
+
+    raise_if_error(st)

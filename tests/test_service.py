@@ -1,0 +1,512 @@
+"""Service layer end to end on CPU: master, servers, clients, handlers, controller, HA, reshard.
+
+Modelled on pico-ps/test/ps_service_test.cpp:77-498, ps_ha_loader_puller_test.cpp:34-238 and
+ps_predictor_native_ps_test.cpp:74-191: every "node" is a real server with its own sockets on
+localhost; failures are injected on the host (a server is stopped, a memory limit is lowered)."""
+import json
+import threading
+import time
+
+import numpy as np
+import pytest
+
+from parameter_server_b200 import C, StatusCode
+from parameter_server_b200 import service as S
+
+DIM = 4
+
+
+def op_cfg(**kw):
+    d = dict(dim=DIM, optimizer="sum", init_range=0.0)
+    d.update(kw)
+    return d
+
+
+class Cluster:
+    def __init__(self, n):
+        self.master = S.Master()
+        self.servers = [S.Server(self.master.address()) for _ in range(n)]
+        self.client = S.Client(self.master.address())
+
+    def ids(self):
+        return [s.node_id() for s in self.servers]
+
+    def close(self):
+        for s in self.servers:
+            s.stop()
+        self.master.stop()
+
+
+@pytest.fixture
+def cluster3():
+    c = Cluster(3)
+    yield c
+    c.close()
+
+
+def make_table(cl, nodes, cfg=None, compress=""):
+    st, sid = cl.client.create_storage(S.LIB, "SparseTableStorageOperator", S.storage_config(nodes, cfg or op_cfg()))
+    assert st.ok(), st
+    hids = {}
+    for spec_key, op, c in [("pull", "SparseTablePullOperator", {}), ("pull_ro", "SparseTablePullOperator", {"read_only": True}),
+                            ("push", "SparseTablePushOperator", {}), ("for_each", "ForEachOperator", {}),
+                            ("erase_if", "EraseIfOperator", {}), ("dump", "DumpOperator", {"compress_algorithm": compress}),
+                            ("load", "LoadOperator", {"compress_algorithm": compress, "block_size": 100}),
+                            ("update_ctx", "ShardUpdateContextOperator", {}), ("sync", "KVSyncOperator", {"compress_algorithm": compress})]:
+        st, hid = cl.client.register_handler(spec_key, S.LIB, op, json.dumps(c), sid)
+        assert st.ok(), st
+        hids[spec_key] = hid
+    return sid, hids
+
+
+def uneven(ids):
+    """node i owns i+2 shards (the reference's test placement)."""
+    out, s = {}, 0
+    for i, n in enumerate(ids):
+        out[n] = list(range(s, s + i + 2))
+        s += i + 2
+    return out
+
+
+def test_master_basics():
+    m = S.Master()
+    a, b = S.MasterClient(m.address()), S.MasterClient(m.address())
+    assert a.generate_id("x")[1] == 0 and b.generate_id("x")[1] == 1 and a.generate_id("y")[1] == 0
+    assert a.set_context("k", "v1").ok()
+    assert not a.set_context("k", "v2", True).ok()
+    assert b.get_context("k")[1] == "v1"
+    assert b.get_context("missing")[0].code() == StatusCode.INVALID_ID
+    # the lock is exclusive and handed over in order
+    order = []
+    assert a.acquire_lock("L").ok()
+    t = threading.Thread(target=lambda: (b.acquire_lock("L"), order.append("b"), b.release_lock("L")))
+    t.start()
+    time.sleep(0.1)
+    order.append("a")
+    a.release_lock("L")
+    t.join(5)
+    assert order == ["a", "b"]
+    # registry membership is liveness: closing the session unregisters the node
+    st, nid = a.register_node("svc", "127.0.0.1:1")
+    assert st.ok() and b.get_nodes("svc")[1] == {nid: "127.0.0.1:1"}
+    a.close()
+    for _ in range(50):
+        if b.get_nodes("svc")[1] == {}:
+            break
+        time.sleep(0.05)
+    assert b.get_nodes("svc")[1] == {}
+    # barrier of 3
+    cs = [S.MasterClient(m.address()) for _ in range(3)]
+    done = []
+    ts = [threading.Thread(target=lambda c=c: done.append(c.barrier("bar", 3).ok())) for c in cs]
+    [t.start() for t in ts]
+    [t.join(5) for t in ts]
+    assert done == [True] * 3
+    assert b.tree_node_set("p/q", "1").ok() and b.tree_node_get("p/q")[1] == "1"
+    m.stop()
+
+
+@pytest.mark.parametrize("n_servers", [1, 3])
+@pytest.mark.parametrize("compress", ["", "zstd", "lz4"])
+def test_sparse_end_to_end(tmp_path, n_servers, compress):
+    cl = Cluster(n_servers)
+    try:
+        sid, h = make_table(cl, uneven(cl.ids()), compress=compress)
+        pull, push = S.PullHandler(cl.client, sid, h["pull"]), S.PushHandler(cl.client, sid, h["push"])
+        keys = np.arange(2000, dtype=np.int64)
+        g = np.tile(np.arange(1, DIM + 1, dtype=np.float32), (2000, 1)) * (keys[:, None] % 7 + 1)
+        assert push.async_push(keys, g).ok()
+        assert push.async_push(keys[:500], g[:500]).ok()            # extra pushes on a subset
+        both = np.concatenate([keys, keys[:100]])                     # duplicates are pre-aggregated client-side
+        assert push.async_push(both, np.concatenate([g, g[:100]])).ok()
+        exp = g * 2
+        exp[:500] += g[:500]
+        exp[:100] += g[:100]
+        st, rows = pull.pull(keys)
+        assert st.ok() and np.array_equal(rows, exp)
+        st, info = cl.client.query_storage_info(sid)
+        assert st.ok() and sum(i.item_number for i in info) == 2000
+        assert len(info) == sum(len(v) for v in uneven(cl.ids()).values())
+        # dump with 2 files per node, delete, recreate with a different sharding, load (rehash)
+        uri = str(tmp_path / "dump") + "?format=binary"
+        st, n = S.DumpHandler(cl.client, sid, h["dump"]).dump(uri, 2)
+        assert st.ok() and n == 2000
+        assert cl.client.delete_storage(sid).ok()
+        other = {n_: [i] for i, n_ in enumerate(cl.ids())}
+        sid2, h2 = make_table(cl, other, compress=compress)
+        st, n = S.LoadHandler(cl.client, sid2, h2["load"]).load(uri)
+        assert st.ok() and n == 2000, st
+        pull2 = S.PullHandler(cl.client, sid2, h2["pull_ro"])
+        st, rows = pull2.pull(keys[::-1].copy())
+        assert st.ok() and np.array_equal(rows, exp[::-1])
+        # for_each statistics, erase_if(odd keys), verify
+        st, r = S.ForEachHandler(cl.client, sid2, h2["for_each"]).for_each("{}")
+        assert st.ok() and r["count"] == 2000 and abs(r["sum"] - float(exp.sum())) < 1e-3 * abs(exp.sum())
+        st, erased = S.EraseIfHandler(cl.client, sid2, h2["erase_if"]).erase_if(json.dumps({"type": "key_mod", "mod": 2, "rem": 1}))
+        assert st.ok() and erased == 1000
+        st, rows = pull2.pull(keys)
+        assert np.array_equal(rows[::2], exp[::2]) and np.all(rows[1::2] == 0)   # read-only pull of a missing key = init value
+        assert sum(s.storage_size(sid2) for s in cl.servers) == 1000
+        # clear
+        assert cl.client.clear_storage(sid2).ok()
+        assert sum(s.storage_size(sid2) for s in cl.servers) == 0
+    finally:
+        cl.close()
+
+
+def test_text_dump_round_trip_is_bitwise(tmp_path, cluster3):
+    cl = cluster3
+    sid, h = make_table(cl, uneven(cl.ids()), cfg=op_cfg(optimizer="adagrad", lr=0.05, init_accumulator=0.1, init_range=0.01))
+    pull, push = S.PullHandler(cl.client, sid, h["pull"]), S.PushHandler(cl.client, sid, h["push"])
+    rng = np.random.default_rng(0)
+    keys = rng.integers(0, 1 << 40, size=3000)
+    pull.pull(keys)
+    assert push.async_push(keys, rng.standard_normal((3000, DIM)).astype(np.float32) * 1e-3).ok()
+    st, before = pull.pull(keys)
+    for fmt in ("archiveline", "binary"):
+        uri = str(tmp_path / fmt) + "?format=" + fmt
+        assert S.DumpHandler(cl.client, sid, h["dump"]).dump(uri, 3)[0].ok()
+        sid2, h2 = make_table(cl, {cl.ids()[0]: [0, 1]}, cfg=op_cfg(optimizer="adagrad", lr=0.05, init_accumulator=0.1, init_range=0.01))
+        st, n = S.LoadHandler(cl.client, sid2, h2["load"]).load(uri)
+        assert st.ok() and n == len(set(keys.tolist()))
+        st, after = S.PullHandler(cl.client, sid2, h2["pull_ro"]).pull(keys)
+        assert st.ok() and after.tobytes() == before.tobytes()
+        # restore (no rehash) needs the dump's sharding: same placement as the source
+        sid3, h3 = make_table(cl, uneven(cl.ids()), cfg=op_cfg(optimizer="adagrad", lr=0.05, init_accumulator=0.1, init_range=0.01))
+        st, n = S.LoadHandler(cl.client, sid3, h3["load"]).restore(uri)
+        assert st.ok() and n == len(set(keys.tolist()))
+        st, again = S.PullHandler(cl.client, sid3, h3["pull_ro"]).pull(keys)
+        assert again.tobytes() == before.tobytes()
+
+
+def test_sync_push_store_and_dense(cluster3):
+    cl = cluster3
+    sid, h = make_table(cl, uneven(cl.ids()), cfg=op_cfg(sync=True))
+    pull, push = S.PullHandler(cl.client, sid, h["pull"]), S.PushHandler(cl.client, sid, h["push"])
+    keys = np.arange(300, dtype=np.int64)
+    g = np.ones((300, DIM), np.float32)
+    assert push.sync_push(keys, g).ok() and push.sync_push(keys, 2 * g).ok()
+    assert np.all(pull.pull(keys)[1] == 0)         # buffered, not applied
+    assert push.store().ok()
+    assert np.all(pull.pull(keys)[1] == 3)
+    # dense table: tensors cut into slices of `dim`, slice -> shard by hash % N
+    st, dsid = cl.client.create_storage(S.LIB, "DenseTableStorageOperator", S.storage_config(uneven(cl.ids()), op_cfg(dim=5)))
+    assert st.ok()
+    _, hp = cl.client.register_handler("pull", S.LIB, "DenseTablePullOperator", "{}", dsid)
+    _, hq = cl.client.register_handler("push", S.LIB, "DenseTablePushOperator", "{}", dsid)
+    dpull, dpush = S.PullHandler(cl.client, dsid, hp), S.PushHandler(cl.client, dsid, hq)
+    for tid in (1, 2, 3):
+        n = 7 * tid + 3
+        v = np.arange(n, dtype=np.float32) + tid
+        assert dpush.push_dense(tid, v).ok() and dpush.push_dense(tid, v).ok()
+        st, got = dpull.pull_dense(tid, n)
+        assert st.ok() and np.array_equal(got, 2 * v)
+    st, info = cl.client.query_storage_info(dsid)
+    assert len({i.node_id for i in info if i.item_number}) > 1     # slices are spread over the servers
+
+
+def test_context_version_gate_and_auto_refresh(cluster3):
+    cl = cluster3
+    sid, h = make_table(cl, uneven(cl.ids()))
+    other = S.Client(cl.master.address())
+    assert other.initialize_storage(sid).ok()
+    pull = S.PullHandler(other, sid, h["pull"])
+    assert pull.pull(np.arange(10))[0].ok()
+    # the first client changes the context (table uri): `other` is now behind
+    assert cl.client.set_table_uri(sid, "/tmp/nowhere").ok()
+    st, _ = pull.pull(np.arange(10), 5000, False)
+    assert st.code() == StatusCode.SERVER_TOO_NEW_CTX
+    st, _ = pull.pull(np.arange(10), 5000, True)          # auto retry refreshes the context
+    assert st.ok() and pull.metrics()["retries"] >= 1
+    # attaching by key
+    st, hid = other.handler_by_key(sid, "push")
+    assert st.ok() and hid == h["push"]
+
+
+def test_update_context_reshard_keeps_data_and_blocks_writes(cluster3):
+    cl = cluster3
+    ids = cl.ids()
+    sid, h = make_table(cl, {ids[0]: [0, 1], ids[1]: [2]})
+    pull_ro = S.PullHandler(cl.client, sid, h["pull_ro"])
+    push = S.PushHandler(cl.client, sid, h["push"])
+    keys = np.arange(5000, dtype=np.int64)
+    vals = (keys[:, None] + np.arange(DIM)[None]).astype(np.float32)
+    assert push.async_push(keys, vals).ok()
+    # a reader keeps pulling while the table is resharded 3 -> 6 shards over all three nodes
+    stop, errors = threading.Event(), []
+    reader = S.Client(cl.master.address())
+    reader.initialize_storage(sid)
+    rp = S.PullHandler(reader, sid, h["pull_ro"])
+
+    def read_loop():
+        while not stop.is_set():
+            st, rows = rp.pull(keys[:200], 10000, True)
+            if not st.ok() or not np.array_equal(rows, vals[:200]):
+                errors.append(str(st))
+
+    t = threading.Thread(target=read_loop)
+    t.start()
+    new = {ids[0]: [0, 3], ids[1]: [1, 4], ids[2]: [2, 5]}
+    st = S.UpdateContextHandler(cl.client, sid, h["update_ctx"]).update_context(S.nodes_json(new))
+    stop.set()
+    t.join(10)
+    assert st.ok(), st
+    assert errors == []
+    st, rows = pull_ro.pull(keys)
+    assert st.ok() and np.array_equal(rows, vals)
+    st, info = cl.client.query_storage_info(sid)
+    assert sorted(i.shard_id for i in info) == list(range(6)) and sum(i.item_number for i in info) == 5000
+    assert {i.node_id for i in info} == set(ids)
+    # writes work again after the transaction
+    assert push.async_push(keys[:10], vals[:10]).ok()
+    assert np.array_equal(pull_ro.pull(keys[:10])[1], 2 * vals[:10])
+    # while a table is in RESHARD, writes are refused with OUT_OF_MEMORY and read-only pulls go on
+    td = S.TableDescriptor()
+    td.from_json_str(cl.client.get_current_ctx(sid)[1])
+    assert td.create_update_info(S.nodes_json(new)).ok()
+    mc = S.MasterClient(cl.master.address())
+    assert mc.set_context(f"storage/{sid}", td.to_json_str()).ok()
+    assert cl.client.pull_context(sid).ok()
+    assert cl.client.notify_ctx_update(sid).ok()      # tell the servers
+    w = S.Client(cl.master.address())
+    w.initialize_storage(sid)
+    wp = S.PushHandler(w, sid, h["push"])
+    st = wp.async_push(keys[:5], vals[:5], 1500)
+    assert st.code() in (StatusCode.OUT_OF_MEMORY, StatusCode.TIMEOUT, StatusCode.SERVER_TOO_OLD_CTX), st
+    assert S.PullHandler(w, sid, h["pull_ro"]).pull(keys[:5], 5000)[0].ok()
+    # the abort path cleans up
+    assert S.UpdateContextHandler(w, sid, h["update_ctx"]).purge().ok()
+    assert wp.async_push(keys[:5], vals[:5], 5000).ok()
+
+
+def test_ha_dead_node_detection_and_restore(tmp_path):
+    cl = Cluster(3)
+    try:
+        ids = cl.ids()
+        # 2x replication: every shard on two nodes
+        nodes = {ids[0]: [0, 1], ids[1]: [1, 2], ids[2]: [2, 0]}
+        sid, h = make_table(cl, nodes)
+        push = S.PushHandler(cl.client, sid, h["push"])
+        pull = S.PullHandler(cl.client, sid, h["pull_ro"])
+        keys = np.arange(3000, dtype=np.int64)
+        vals = np.ones((3000, DIM), np.float32) * (keys[:, None] % 11)
+        assert push.async_push(keys, vals).ok()              # pushes update every replica
+        assert sum(s.storage_size(sid) for s in cl.servers) == 6000
+        # node 1 dies (host-side fault: the process' server object is stopped)
+        cl.servers[1].stop()
+        st, rows = pull.pull(keys, 20000, True)              # timeout -> dead-node detection -> other replica
+        assert st.ok() and np.array_equal(rows, vals)
+        td = S.TableDescriptor()
+        td.from_json_str(S.MasterClient(cl.master.address()).get_context(f"storage/{sid}")[1])
+        assert td.node_status()[ids[1]] == 1                 # DEAD, published on the master
+        # a fresh server takes over the dead node's shards from the live replicas
+        fresh = S.Server(cl.master.address())
+        cl.servers.append(fresh)
+        st, n = fresh.restore_storages()
+        assert st.ok() and n == 1, st
+        assert fresh.node_id() not in ids                    # node ids are never reused
+        assert fresh.storage_size(sid) == cl.servers[1].storage_size(sid) or fresh.storage_size(sid) > 0
+        td.from_json_str(S.MasterClient(cl.master.address()).get_context(f"storage/{sid}")[1])
+        assert td.node_status()[fresh.node_id()] == 0        # RUNNING
+        # lose another original node: the restored one must now serve its shards
+        cl.servers[0].stop()
+        st, rows = pull.pull(keys, 20000, True)
+        assert st.ok() and np.array_equal(rows, vals)
+    finally:
+        cl.close()
+
+
+def test_restore_from_dump_when_no_replica(tmp_path):
+    cl = Cluster(2)
+    try:
+        ids = cl.ids()
+        sid, h = make_table(cl, {ids[0]: [0], ids[1]: [1]})
+        keys = np.arange(1000, dtype=np.int64)
+        vals = np.ones((1000, DIM), np.float32) * 3
+        assert S.PushHandler(cl.client, sid, h["push"]).async_push(keys, vals).ok()
+        uri = str(tmp_path / "ckpt")
+        assert S.DumpHandler(cl.client, sid, h["dump"]).dump(uri, 1)[0].ok()
+        assert cl.client.set_table_uri(sid, uri).ok()
+        cl.servers[1].stop()
+        pull = S.PullHandler(cl.client, sid, h["pull_ro"])
+        st, _ = pull.pull(keys, 3000, True)
+        assert st.code() in (StatusCode.NO_REPLICA, StatusCode.TIMEOUT)     # single replica: nothing to fail over to
+        fresh = S.Server(cl.master.address())
+        cl.servers.append(fresh)
+        st, n = fresh.restore_storages()
+        assert st.ok() and n == 1, st
+        st, rows = pull.pull(keys, 20000, True)
+        assert st.ok() and np.array_equal(rows, vals)
+    finally:
+        cl.close()
+
+
+def test_memory_limit_backpressure(cluster3):
+    cl = cluster3
+    sid, h = make_table(cl, uneven(cl.ids()), cfg=op_cfg(dim=64))
+    push = S.PushHandler(cl.client, sid, h["push"])
+    for s in cl.servers:
+        assert s.set_memory_limit(sid, 32 * 1024).ok()
+    st = None
+    for i in range(50):
+        keys = np.arange(i * 500, (i + 1) * 500, dtype=np.int64)
+        st = push.async_push(keys, np.ones((500, 64), np.float32), 1000)
+        if not st.ok():
+            break
+    assert st.code() in (StatusCode.OUT_OF_MEMORY, StatusCode.TIMEOUT)
+    ok, healthy, used, _ = None, None, None, None
+    flags = [cl.client.query_memory_info(n)[1] for n in cl.ids()]
+    assert not all(flags)
+
+
+def test_controller_placement_resize_and_introspection(tmp_path):
+    cl = Cluster(4)
+    try:
+        ctl = S.Controller(cl.master.address())
+        st, nodes = ctl.load_nodes()
+        assert st.ok() and sorted(nodes) == sorted(cl.ids())
+        st, sid = ctl.create_table("ctr_emb", S.LIB, "SparseTableStorageOperator", json.dumps(op_cfg()), 8, 2, S.standard_ops())
+        assert st.ok(), st
+        client = ctl.client()
+        st, hid = client.handler_by_key(sid, "push")
+        push = S.PushHandler(client, sid, hid)
+        pull = S.PullHandler(client, sid, client.handler_by_key(sid, "pull_ro")[1])
+        keys = np.arange(4000, dtype=np.int64)
+        vals = np.ones((4000, DIM), np.float32) * (keys[:, None] % 5)
+        assert push.async_push(keys, vals).ok()
+        table = json.loads(ctl.gen_table_json(sid)[1])
+        per_node = {}
+        for n in table["context"]["nodes"]:
+            per_node[n["g_rank"]] = len(n["shard_list"])
+        assert sum(per_node.values()) == 16 and max(per_node.values()) - min(per_node.values()) <= 1   # least-loaded placement
+        assert sum(s["item_number"] for s in table["shards"]) == 8000                                     # 2 replicas
+        assert ctl.update_table_shard(sid, 12).ok()
+        assert np.array_equal(pull.pull(keys)[1], vals)
+        assert ctl.update_table_replica(sid, 1).ok()
+        table = json.loads(ctl.gen_table_json(sid)[1])
+        assert sum(s["item_number"] for s in table["shards"]) == 4000 and len(table["shards"]) == 12
+        assert ctl.balance_table(sid).ok()
+        assert np.array_equal(pull.pull(keys)[1], vals)
+        # scale out: a new server joins, every new node gets 2 new shards
+        extra = S.Server(cl.master.address())
+        cl.servers.append(extra)
+        assert ctl.expand_storage_nodes(sid, [extra.node_id()], 2).ok()
+        table = json.loads(ctl.gen_table_json(sid)[1])
+        assert len(table["shards"]) == 14 and extra.storage_size(sid) > 0
+        assert np.array_equal(pull.pull(keys)[1], vals)
+        nodes_view = json.loads(ctl.show_nodes()[1])
+        assert len(nodes_view) == 5 and all(n["alive"] for n in nodes_view)
+        # a storage without a table object is cleaned up
+        st, orphan = client.create_storage(S.LIB, "SparseTableStorageOperator", S.storage_config({cl.ids()[0]: [0]}, op_cfg()))
+        st, removed = ctl.clean_unused_storage()
+        assert st.ok() and removed == 1
+        assert ctl.shutdown_node(extra.node_id()).ok()
+        for _ in range(100):
+            if extra.exited():
+                break
+            time.sleep(0.05)
+        assert extra.exited()
+        assert ctl.delete_table(sid).ok()
+    finally:
+        cl.close()
+
+
+def test_predictor_sync_udf_and_native_ps(tmp_path, cluster3):
+    cl = cluster3
+    ids = cl.ids()
+    cfg = op_cfg(optimizer="sgd", lr=1.0)
+    trainer, ht = make_table(cl, {ids[0]: [0], ids[1]: [1]}, cfg=cfg)
+    predictor, hp = make_table(cl, {ids[2]: [0, 1, 2]}, cfg=cfg)
+    for s in cl.servers[:2]:
+        assert s.enable_sync(trainer).ok()
+    push = S.PushHandler(cl.client, trainer, ht["push"])
+    keys = np.arange(500, dtype=np.int64)
+    assert push.async_push(keys, -np.ones((500, DIM), np.float32)).ok()
+    sync = S.SyncHandler(cl.client, predictor, hp["sync"])
+    total = 0
+    for s in cl.servers[:2]:
+        st, n = s.push_sync_table(trainer, sync)
+        assert st.ok(), st
+        total += n
+    assert total == 500
+    ppull = S.PullHandler(cl.client, predictor, hp["pull_ro"])
+    assert np.all(ppull.pull(keys)[1] == 1.0)
+    # only what changed since the last round travels
+    assert push.async_push(keys[:7], -np.ones((7, DIM), np.float32)).ok()
+    assert sum(s.push_sync_table(trainer, sync)[1] for s in cl.servers[:2]) == 7
+    assert np.all(ppull.pull(keys[:7])[1] == 2.0)
+    assert sum(s.push_sync_table(trainer, sync)[1] for s in cl.servers[:2]) == 0
+    # UDF: a Python function registered on the servers
+    S.register_udf("count_items", lambda sid, items, param: f"{items}:{param.decode()}".encode())
+    st, hid = cl.client.register_handler("udf", S.LIB, "UDFOperator", json.dumps({"function": "count_items"}), trainer)
+    st, results = S.UDFHandler(cl.client, trainer, hid).call(b"hello")
+    assert st.ok() and sorted(int(r.split(b":")[0]) for _, r in results) == sorted(s.storage_size(trainer) for s in cl.servers[:2])
+    # NativePS: in-process load of a distributed dump + pull
+    uri = str(tmp_path / "serving")
+    assert S.DumpHandler(cl.client, trainer, ht["dump"]).dump(uri, 2)[0].ok()
+    nps = S.NativePS()
+    st, nsid = nps.create_storage(S.LIB, "SparseTableStorageOperator", json.dumps(cfg), 3)
+    _, lh = nps.register_handler(nsid, "load", S.LIB, "LoadOperator", "{}")
+    _, ph = nps.register_handler(nsid, "pull", S.LIB, "SparseTablePullOperator", json.dumps({"read_only": True}))
+    st, n = S.NativeLoadHandler(nps, nsid, lh).load(uri, 4)
+    assert st.ok() and n == 500 and nps.size(nsid) == 500
+    st, rows = S.NativePullHandler(nps, nsid, ph).pull(keys, DIM)
+    assert st.ok() and np.all(rows[:7] == 2.0) and np.all(rows[7:] == 1.0)
+
+
+def test_common_pieces():
+    wire, body, sid, hid, ver, uver, typ = C.message_round_trip(b"payload", 3, 4, 5, 6, 10)
+    assert body == b"payload" and (sid, hid, ver, uver, typ) == (3, 4, 5, 6, 10) and len(wire) == 7 + 20
+    assert C.request_type_name(10) == "OP_PULL" and C.request_type_name(23) == "OP_COORDINATED_RESTORE_ITERATE"
+    r = C.archive_round_trip(-7, 2.5, "héllo", [1, 2, 3], ["a", "bc"])
+    assert r[:5] == (-7, 2.5, "héllo", [1, 2, 3], ["a", "bc"]) and r[5] == 3 and r[6] == "full" and r[7]
+    data = bytes(range(256)) * 100
+    for algo in ("", "zstd", "lz4", "snappy"):
+        st, back, packed = C.compress_round_trip(algo, data)
+        assert st.ok() and back == data and (algo == "" or packed < len(data))
+    assert not C.compress_round_trip("bogus", b"x")[0].ok()
+    v = list(np.random.default_rng(0).standard_normal(100))
+    assert C.heap_sort(v) == sorted(v)
+    # request coalescing: two threads finish, the second one claims both slots
+    tr = C.ThreadReduce()
+    tr.add(0); tr.add(1)
+    assert tr.reduce(0, 2) == 0
+    assert tr.reduce(1, 2) == 0b11
+    tb = C.ThreadBcast()
+    t = threading.Thread(target=lambda: tb.wait(0))
+    t.start()
+    tb.notify(0b11, 1)
+    t.join(5)
+    assert not t.is_alive()
+    model = {"name": "m", "type": "ctr", "version": "1", "status": 0, "submodels": [
+        {"name": "sub", "type": "", "version": "", "status": 0, "submodels": [], "tables": [
+            {"table_name": "t2", "table_uri": "", "lib_name": "psb", "init_method": 0, "shard_num": 2, "replica_num": 1, "storage_id": 9,
+             "storage_op": {"key": "storage", "lib_name": "psb", "op_name": "S", "config_str": "{}", "handler_id": -1},
+             "ops": [{"key": "pull", "lib_name": "psb", "op_name": "P", "config_str": "{}", "handler_id": 3}]}]}],
+        "tables": []}
+    back = json.loads(C.model_round_trip(json.dumps(model)))
+    assert back["n_tables"] == 1 and back["n_operators"] == 1 and back["submodels"][0]["tables"][0]["storage_id"] == 9
+
+
+def test_table_descriptor_state_machine():
+    td = S.TableDescriptor()
+    assert td.set_nodes(S.nodes_json({0: [0, 1], 1: [1, 2], 2: [2, 0]})).ok()
+    assert td.global_shard_num() == 3 and td.shards()[1] == [0, 1]
+    assert td.update_node_status({0, 2}) and td.node_status()[1] == 1
+    assert td.shards()[1] == [0]
+    picks = {td.pick_one_replica(2) for _ in range(50)}
+    assert picks == {2}
+    v = td.version
+    assert td.try_to_replace_one_dead_node(7) and td.node_status() == {0: 0, 7: 2, 2: 0} and td.version == v + 1
+    assert td.pick_one_replica(1) == 0            # LOADING nodes are not picked
+    assert td.set_node_status_to_running(7) and td.node_status()[7] == 0
+    uv = td.update_version
+    assert td.create_update_info(S.nodes_json({0: [0], 2: [1], 7: [2], 9: [3]})).ok()
+    assert td.status() == 1 and td.update_version == uv + 1
+    td2 = S.TableDescriptor()
+    assert td2.from_json_str(td.to_json_str())
+    assert td2.to_json_str() == td.to_json_str()
+    assert not td2.from_json_str(td.to_json_str(), True)      # not newer: left alone
+    td.apply_update()
+    assert td.global_shard_num() == 4 and td.update_version == uv + 2
+    assert td2.from_json_str(td.to_json_str(), True)
