@@ -1,6 +1,7 @@
 // Bindings of the non-GEMM model kernels.
 #include <pybind11/pybind11.h>
 
+#include "kernels/dedup.h"
 #include "kernels/model_kernels.h"
 
 namespace py = pybind11;
@@ -24,6 +25,16 @@ void bind_model_kernels(py::module_& m) {
     });
     m.def("bias_grad", [](uintptr_t dz, int64_t ld, int M, int N, uintptr_t db, uintptr_t s) {
         return bias_grad((const void*)dz, ld, M, N, (float*)db, (void*)s);
+    });
+    m.def("dedup_fill_scratch", [](uintptr_t scratch, unsigned long long slots, uintptr_t s) {
+        return dedup_fill_scratch((void*)scratch, slots, (void*)s);
+    });
+    m.def("dedup_partition", [](uintptr_t keys, unsigned n, uintptr_t scratch, unsigned long long slots, uintptr_t pos,
+                                uintptr_t shard_owner, int n_shards, int world, uintptr_t uniq_keys, uintptr_t uniq_owner,
+                                uintptr_t inverse, uintptr_t counts, uintptr_t s) {
+        return dedup_partition((const long long*)keys, n, (void*)scratch, slots, (unsigned*)pos, (const int*)shard_owner,
+                               n_shards, world, (long long*)uniq_keys, (int*)uniq_owner, (int*)inverse, (unsigned*)counts,
+                               (void*)s);
     });
     m.def("cast_pad", [](uintptr_t x, int B, int Kin, uintptr_t out, int64_t ldo, uintptr_t s) {
         return cast_pad((const float*)x, B, Kin, (void*)out, ldo, (void*)s);

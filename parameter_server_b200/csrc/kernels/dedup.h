@@ -1,0 +1,17 @@
+// Host interface of the stand-alone key dedup + partition operation (see dedup.cu).
+#pragma once
+#include "common.cuh"
+
+namespace psb {
+
+// Fill `slots` scratch slots (16 bytes each) with the empty marker; needed once after allocation.
+int dedup_fill_scratch(void* scratch, unsigned long long slots, void* stream);
+
+// keys[n] -> uniq_keys[n_uniq], uniq_owner[n_uniq], inverse[n], counts[0] = n_uniq, counts[1 + r] = distinct keys
+// owned by rank r. scratch: `scratch_slots` (power of two, >= 2n) empty slots; pos_scratch: n unsigned.
+// shard_owner may be null (every key is owned by rank 0). Returns 0, a cudaError_t, or -2 (bad sizes).
+int dedup_partition(const long long* keys, unsigned n, void* scratch, unsigned long long scratch_slots, unsigned* pos_scratch,
+                    const int* shard_owner, int n_shards, int world, long long* uniq_keys, int* uniq_owner, int* inverse,
+                    unsigned* counts, void* stream);
+
+}  // namespace psb
