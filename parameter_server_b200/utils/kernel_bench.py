@@ -1,0 +1,198 @@
+"""Micro-benchmarks of the hand-written kernels, one workload per sub-command.
+
+    python -m parameter_server_b200.utils.kernel_bench gemm --m 8192 --n 1024 --k 1024
+    python -m parameter_server_b200.utils.kernel_bench sparse --keys 1048576 --dim 64 --zipf 1.05
+    python -m parameter_server_b200.utils.kernel_bench interaction --batch 8192
+    python -m parameter_server_b200.utils.kernel_bench dense --numel 67108864
+
+Timing: CUDA events on the launching stream, >= 3 warm-up iterations, L2 flushed between timed
+iterations (a 256 MB buffer is overwritten), median over the iterations. Each line reports the achieved
+rate and its fraction of the measured roofline (``MEASURED_PEAKS.json`` at the repository root when
+present, else 6.65 TB/s and 1.59 PFLOP/s).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        j = json.load(open(p))
+        return j["hbm_gbs"] * 1e9, j["bf16_tflops"] * 1e12, "measured"
+    return 6.65e12, 1.59e15, "fallback"
+
+
+_flush = None
+
+
+def flush_l2():
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _flush.fill_(1)
+
+
+def timed(fn, iters=10, warmup=3, flush=True):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e-3)
+    return statistics.median(ts)
+
+
+def cmd_gemm(a):
+    from ..ops import gemm as G
+    hbm, flops_peak, src = peaks()
+    M, N, K = a.m, a.n, a.k
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = torch.randn(N, K, device="cuda").bfloat16()
+    dy = torch.randn(M, N, device="cuda").bfloat16()
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    dx = torch.empty(M, K, device="cuda", dtype=torch.bfloat16)
+    dw = torch.zeros(N, K, device="cuda")
+    cases = {
+        "fwd  y=xW^T (K,K)": lambda: G.gemm(x, w, out=out),
+        "dgrad dx=dyW (K,MN)": lambda: G.gemm(dy, w, b_mn=True, out=dx),
+        "wgrad dW=dy^Tx (MN,MN)": lambda: G.linear_wgrad(dy, x, out=dw, split_k=0),
+    }
+    fl = 2.0 * M * N * K
+    for name, fn in cases.items():
+        if a.only and a.only not in name:
+            continue
+        t = timed(fn, a.iters, flush=not a.no_flush)
+        print(f"gemm {name:24s} M={M} N={N} K={K}: {t*1e6:8.1f} us  {fl/t/1e12:7.1f} TFLOP/s  "
+              f"{fl/t/flops_peak:5.2f} of {src} bf16 peak")
+    if a.cublas:
+        t = timed(lambda: torch.matmul(x, w.t(), out=out), a.iters, flush=not a.no_flush)
+        print(f"gemm torch.matmul (cuBLAS) reference      : {t*1e6:8.1f} us  {fl/t/1e12:7.1f} TFLOP/s")
+    G.check_gemm_errors()
+
+
+def cmd_sparse(a):
+    from ..ops.sparse import SparseTable
+    hbm, _, src = peaks()
+    n, dim = a.keys, a.dim
+    t = SparseTable(dim, "adagrad", dict(lr=0.05, init_accumulator=0.1), capacity=4 * n, max_keys=n)
+    rng = np.random.default_rng(0)
+    pool = []
+    for _ in range(4):
+        k = rng.zipf(a.zipf, size=n).astype(np.uint64) if a.zipf > 1 else rng.integers(0, a.vocab, size=n).astype(np.uint64)
+        k = ((k * np.uint64(0x9E3779B97F4A7C15)) >> np.uint64(2)) % np.uint64(a.vocab)
+        pool.append(torch.from_numpy(k.astype(np.int64)).cuda())
+    grads = torch.randn(n, dim, device="cuda") * 1e-3
+    out = torch.empty(n, dim, device="cuda")
+    t.reserve(8 * n)
+    for i in range(8):
+        t.pull(pool[i % 4], out=out)
+        t.push(grads)
+    t.check()
+    it = [0]
+
+    def pull():
+        t.pull(pool[it[0] % 4], out=out)
+        it[0] += 1
+
+    tp = timed(pull, a.iters, flush=not a.no_flush)
+    uniq = t.engine.last_unique(0)
+
+    def both():
+        t.pull(pool[it[0] % 4], out=out)
+        t.push(grads)
+        it[0] += 1
+
+    tb = timed(both, a.iters, flush=not a.no_flush)
+    t.check()
+    row = dim * 4
+    stride = row * 2
+    pull_bytes = uniq * row + n * row + n * 8
+    push_bytes = n * row + uniq * (2 * stride)
+    print(f"sparse pull  n={n} dim={dim} unique={uniq/n:.2f}: {tp*1e6:8.1f} us  {n/tp/1e9:6.2f} Gkeys/s  "
+          f"algorithmic {pull_bytes/tp/1e9:7.0f} GB/s = {pull_bytes/tp/hbm:4.2f} of {src} HBM copy")
+    print(f"sparse pull+push               : {tb*1e6:8.1f} us  {2*n/tb/1e9:6.2f} Gkeys/s  "
+          f"algorithmic {(pull_bytes+push_bytes)/tb/1e9:7.0f} GB/s = {(pull_bytes+push_bytes)/tb/hbm:4.2f} of {src} HBM copy")
+    if a.phases:
+        t.engine.set_profile(True)
+        both()
+        st = t.engine.phase_stamps(0)
+        names = ["P1 dedup", "P2 ship", "P3a resolve", "P3b init", "P3c rows", "P5 gather"]
+        for i, nm in enumerate(names):
+            print(f"   {nm:12s} {(st[i+1]-st[i])/1e3:8.1f} us")
+        print(f"   {'Q1 segsum':12s} {(st[10]-st[8])/1e3:8.1f} us")
+        print(f"   {'Q3c update':12s} {(st[12]-st[11])/1e3:8.1f} us")
+
+
+def cmd_interaction(a):
+    from .._lib import C
+    hbm, _, src = peaks()
+    B, F, D, ldo = a.batch, 26, 128, 480
+    bottom = torch.randn(B, D, device="cuda").bfloat16()
+    emb = torch.randn(B, F, D, device="cuda") * 0.1
+    out = torch.empty(B, ldo, device="cuda", dtype=torch.bfloat16)
+    dout = torch.randn(B, ldo, device="cuda").bfloat16()
+    dbot = torch.empty(B, D, device="cuda", dtype=torch.bfloat16)
+    demb = torch.empty(B, F, D, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    tf = timed(lambda: C.interaction_fwd(bottom.data_ptr(), D, emb.data_ptr(), F, D, out.data_ptr(), ldo, B, s), a.iters)
+    tb = timed(lambda: C.interaction_bwd(dout.data_ptr(), ldo, bottom.data_ptr(), D, emb.data_ptr(), F, D, dbot.data_ptr(), D,
+                                         demb.data_ptr(), B, True, s), a.iters)
+    fb = B * (F * D * 4 + D * 2 + ldo * 2)
+    bb = B * (2 * F * D * 4 + 2 * D * 2 + ldo * 2)
+    print(f"interaction fwd B={B}: {tf*1e6:7.1f} us  {fb/tf/1e9:6.0f} GB/s = {fb/tf/hbm:4.2f} of {src} HBM copy")
+    print(f"interaction bwd B={B}: {tb*1e6:7.1f} us  {bb/tb/1e9:6.0f} GB/s = {bb/tb/hbm:4.2f} of {src} HBM copy")
+
+
+def cmd_dense(a):
+    from ..ops.dense import DenseTable
+    hbm, _, src = peaks()
+    t = DenseTable({"w": (a.numel,)}, "adamw", dict(lr=1e-3), grad_dtype=torch.bfloat16 if a.bf16_grads else torch.float32)
+    t.load({"w": torch.zeros(a.numel)})
+    t.flat_grads.fill_(1e-3)
+    tt = timed(lambda: t.push(), a.iters)
+    t.check()
+    gb = 2 if a.bf16_grads else 4
+    bytes_ = a.numel * (gb + 3 * 4 * 2 + 2)   # grads read, master/m/v read+write, bf16 params written
+    print(f"dense push (optimizer + bf16 write, world 1) numel={a.numel}: {tt*1e6:8.1f} us  {bytes_/tt/1e9:6.0f} GB/s = "
+          f"{bytes_/tt/hbm:4.2f} of {src} HBM copy")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=8192); g.add_argument("--n", type=int, default=1024); g.add_argument("--k", type=int, default=1024)
+    g.add_argument("--only", default=""); g.add_argument("--cublas", action="store_true")
+    s = sub.add_parser("sparse")
+    s.add_argument("--keys", type=int, default=1 << 20); s.add_argument("--dim", type=int, default=64)
+    s.add_argument("--zipf", type=float, default=1.05); s.add_argument("--vocab", type=int, default=62_500_000)
+    s.add_argument("--phases", action="store_true")
+    i = sub.add_parser("interaction")
+    i.add_argument("--batch", type=int, default=8192)
+    d = sub.add_parser("dense")
+    d.add_argument("--numel", type=int, default=64 << 20); d.add_argument("--bf16-grads", action="store_true")
+    for p in (g, s, i, d):
+        p.add_argument("--iters", type=int, default=10)
+        p.add_argument("--no-flush", action="store_true")
+    a = ap.parse_args()
+    {"gemm": cmd_gemm, "sparse": cmd_sparse, "interaction": cmd_interaction, "dense": cmd_dense}[a.cmd](a)
+
+
+if __name__ == "__main__":
+    main()
