@@ -171,9 +171,14 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpilogue& ep, float* f,
     if (ep.out_f32 != nullptr) {
         float* op = ep.out_f32 + (size_t)row * ep.ldd + col0;
         if (ep.split_k > 1) {
+            if (full && (ep.ldd % 4 == 0)) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-                if (col0 + j < N) atomicAdd(op + j, f[j]);
+                for (int j = 0; j < 32; j += 4) atomicAdd((float4*)(op + j), make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < N) atomicAdd(op + j, f[j]);
+            }
         } else if (full && (ep.ldd % 4 == 0)) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {

@@ -140,6 +140,7 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
                 set_status(a.ctl, kStError, W_MAILBOX_OVERFLOW);
             }
             a.dedup[h].row = u;
+            a.uniq_slot[u] = (unsigned)h;
             a.uniq_row[u] = (owner == me) ? kNoRow : kRemoteRow;
         }
     }
@@ -298,7 +299,6 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
             const unsigned u = a.dedup[h].row;
             a.inverse[i] = (int)u;
             a.pos_slot[i] = a.uniq_row[u];  // from here on: the row of position i
-            a.dedup[h].key = kEmptyKey;     // leave the scratch table empty for the next call
         }
         if (a.flags & FUSED_COPY_ROWS) {
             __syncthreads();
@@ -322,6 +322,9 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
             }
         }
     }
+    // leave the scratch table empty for the next call: one store per DISTINCT key (clearing per position would
+    // make every duplicate of a hot key store to the same address)
+    for (unsigned u = tid; u < cnt[0]; u += nthreads) a.dedup[a.uniq_slot[u]].key = kEmptyKey;
     if (a.flags & FUSED_PREPARE_PUSH) {
         const unsigned n_uniq = cnt[0];
         if (n_uniq != a.n) {  // without duplicates the push stores instead of accumulating

@@ -43,6 +43,7 @@ struct FusedArgs {
     unsigned* pos_slot;    // [N] dedup slot of each key position
     int* inverse;          // [N] unique id of each key position
     unsigned* uniq_row;    // [N] local row index of a unique key, kRemoteRow when the owner is a peer
+    unsigned* uniq_slot;   // [N] dedup-table slot of a unique key (to empty the table afterwards)
     long long* send_keys;  // [world][C] staged per-owner key lists
     unsigned* send_ret;    // [world][C] unique id of each staged key
     float* agg;            // [N][dim] per-unique-key gradient sums

@@ -74,7 +74,7 @@ SparseEngine::SparseEngine(GpuTable* table, const SparseEngineConfig& cfg) : tab
     size_t s = 0;
     auto carve = [&](size_t bytes) { size_t o = s; s = align_up(s + bytes); return o; };
     const size_t o_dedup = carve(dedup_slots_ * sizeof(Slot));
-    const size_t o_pos = carve(N * 4), o_inv = carve(N * 4), o_urow = carve(N * 4);
+    const size_t o_pos = carve(N * 4), o_inv = carve(N * 4), o_urow = carve(N * 4), o_uslot = carve(N * 4);
     const size_t o_skeys = carve((size_t)W * C_ * 8), o_sret = carve((size_t)W * C_ * 4);
     const size_t o_agg = carve(N * dim * 4);
     const size_t o_res = carve((size_t)W * C_ * 4), o_new = carve((size_t)W * C_ * 4);
@@ -90,6 +90,7 @@ SparseEngine::SparseEngine(GpuTable* table, const SparseEngineConfig& cfg) : tab
     pos_slot_ = (unsigned*)(scratch_ + o_pos);
     inverse_ = (int*)(scratch_ + o_inv);
     uniq_row_ = (unsigned*)(scratch_ + o_urow);
+    uniq_slot_ = (unsigned*)(scratch_ + o_uslot);
     send_keys_ = (long long*)(scratch_ + o_skeys);
     send_ret_ = (unsigned*)(scratch_ + o_sret);
     agg_ = (float*)(scratch_ + o_agg);
@@ -167,6 +168,7 @@ void SparseEngine::fill_common(FusedArgs& a) const {
     a.pos_slot = pos_slot_;
     a.inverse = inverse_;
     a.uniq_row = uniq_row_;
+    a.uniq_slot = uniq_slot_;
     a.send_keys = send_keys_;
     a.send_ret = send_ret_;
     a.agg = agg_;

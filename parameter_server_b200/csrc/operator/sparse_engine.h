@@ -72,7 +72,7 @@ private:
     // carved from scratch_
     Slot* dedup_ = nullptr;
     uint64_t dedup_slots_ = 0;
-    unsigned *pos_slot_ = nullptr, *uniq_row_ = nullptr, *send_ret_ = nullptr, *res_slot_ = nullptr,
+    unsigned *pos_slot_ = nullptr, *uniq_row_ = nullptr, *uniq_slot_ = nullptr, *send_ret_ = nullptr, *res_slot_ = nullptr,
              *new_list_ = nullptr, *counters_ = nullptr, *in_cnt_ = nullptr;
     int* inverse_ = nullptr;
     long long* send_keys_ = nullptr;

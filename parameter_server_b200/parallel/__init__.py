@@ -1,0 +1,2 @@
+"""Multi-GPU plumbing: process-group helpers and the NCCL-only baselines of the fused paths."""
+from .nccl_baseline import NcclDenseTable, NcclSparseTable  # noqa: F401
