@@ -29,6 +29,11 @@ namespace psb {
 namespace {
 
 constexpr int kThreads = 256;
+// block-local accumulation of hot gradient rows in the push (Q1)
+constexpr int kHotSlots = 512;   // shared-memory counting table per CTA
+constexpr int kHotRows = 24;     // rows cached per CTA
+constexpr unsigned kHotMaxDim = 128;
+constexpr size_t kPushSmemBytes = (size_t)kHotRows * kHotMaxDim * sizeof(float);
 
 enum Where : unsigned {
     W_P1 = 1, W_P2, W_KEYFLAG, W_P3A, W_P3B, W_P3C, W_ROWFLAG, W_MAILBOX_OVERFLOW, W_INDEX_FULL, W_POOL_FULL,
@@ -358,20 +363,92 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
     __shared__ unsigned s_pre[kMaxWorld + 1];
 
     // ---- Q1: segment-sum gradients of duplicate keys --------------------------------------------
+    // Every CTA owns a contiguous range of positions. Keys that occur several times inside the range
+    // (the head of a Zipf distribution occurs in every range) are first summed in shared memory and reach
+    // global memory once per CTA; everything else goes straight to the per-key row with a vector atomic.
     PROF(8);
     {
         const unsigned n_uniq = cnt[0];
         const bool dups = (n_uniq != a.n);
         const float scale = (a.flags & FUSED_MEAN) ? 1.0f / (float)L : 1.0f;
-        for (unsigned i = group; i < a.n; i += ngroups) {
-            const unsigned u = (unsigned)a.inverse[i];
+        const bool do_scale = L > 1 && (a.flags & FUSED_MEAN);
+        const unsigned per = (a.n + nblocks - 1) / nblocks;
+        const unsigned lo = min(a.n, blockIdx.x * per), hi = min(a.n, lo + per);
+        const unsigned lgroup = threadIdx.x / lanes, lgroups = kThreads / lanes;
+        extern __shared__ __align__(16) float s_cache[];  // [kHotRows][dim]
+        __shared__ unsigned s_hkey[kHotSlots], s_hcnt[kHotSlots];
+        __shared__ int s_hrow[kHotSlots];
+        __shared__ unsigned s_cache_u[kHotRows];
+        __shared__ unsigned s_ncache;
+        const bool use_cache = dups && a.dim <= kHotMaxDim && (hi - lo) >= 64;
+        if (use_cache) {
+            for (unsigned t = threadIdx.x; t < kHotSlots; t += kThreads) { s_hkey[t] = 0xFFFFFFFFu; s_hcnt[t] = 0; s_hrow[t] = -1; }
+            if (threadIdx.x == 0) s_ncache = 0;
+            __syncthreads();
+            // 1. count the keys of this range
+            for (unsigned i = lo + threadIdx.x; i < hi; i += kThreads) {
+                const unsigned u = (unsigned)a.inverse[i];
+                unsigned h = (u * 2654435761u) & (kHotSlots - 1);
+                for (int probe = 0; probe < 8; ++probe) {
+                    const unsigned prev = atomicCAS(&s_hkey[h], 0xFFFFFFFFu, u);
+                    if (prev == 0xFFFFFFFFu || prev == u) { atomicAdd(&s_hcnt[h], 1u); break; }
+                    h = (h + 1) & (kHotSlots - 1);
+                }
+            }
+            __syncthreads();
+            // 2. keys seen at least 4 times get a shared-memory row
+            for (unsigned t = threadIdx.x; t < kHotSlots; t += kThreads)
+                if (s_hkey[t] != 0xFFFFFFFFu && s_hcnt[t] >= 4) {
+                    const unsigned c = atomicAdd(&s_ncache, 1u);
+                    if (c < kHotRows) { s_hrow[t] = (int)c; s_cache_u[c] = s_hkey[t]; }
+                }
+            __syncthreads();
+            const unsigned nc = min(s_ncache, (unsigned)kHotRows);
+            for (unsigned t = threadIdx.x; t < nc * a.dim; t += kThreads) s_cache[t] = 0.f;
+            __syncthreads();
+        }
+        const unsigned gl0 = (threadIdx.x & 31u) / lanes * lanes;  // first lane of this group inside its warp
+        for (unsigned base = lo; base < hi; base += lgroups) {
+            const unsigned i = base + lgroup;
+            const bool active = i < hi;
+            unsigned u = 0;
+            int crow = -1;
+            if (active) u = (unsigned)a.inverse[i];
+            if (use_cache) {
+                if (active && lane == 0) {
+                    unsigned h = (u * 2654435761u) & (kHotSlots - 1);
+                    for (int probe = 0; probe < 8; ++probe) {
+                        const unsigned k = s_hkey[h];
+                        if (k == u) { crow = s_hrow[h]; break; }
+                        if (k == 0xFFFFFFFFu) break;
+                        h = (h + 1) & (kHotSlots - 1);
+                    }
+                }
+                crow = __shfl_sync(0xffffffffu, crow, gl0);
+            }
+            if (!active) continue;
             const float* g = a.grads + (size_t)(i / L) * a.dim;
             float* dst = a.agg + (size_t)u * a.dim;
             for (unsigned d = lane * 4; d < a.dim; d += lanes * 4) {
                 float4 v = *(const float4*)(g + d);
-                if (L > 1 && (a.flags & FUSED_MEAN)) { v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale; }
-                if (dups) atomicAdd((float4*)(dst + d), v);
-                else *(float4*)(dst + d) = v;
+                if (do_scale) { v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale; }
+                if (crow >= 0) {
+                    float* c = s_cache + (size_t)crow * a.dim + d;
+                    atomicAdd(c + 0, v.x); atomicAdd(c + 1, v.y); atomicAdd(c + 2, v.z); atomicAdd(c + 3, v.w);
+                } else if (dups) {
+                    atomicAdd((float4*)(dst + d), v);
+                } else {
+                    *(float4*)(dst + d) = v;
+                }
+            }
+        }
+        if (use_cache) {
+            __syncthreads();
+            const unsigned nc = min(s_ncache, (unsigned)kHotRows);
+            for (unsigned c = lgroup; c < nc; c += lgroups) {
+                float* dst = a.agg + (size_t)s_cache_u[c] * a.dim;
+                for (unsigned d = lane * 4; d < a.dim; d += lanes * 4)
+                    atomicAdd((float4*)(dst + d), *(const float4*)(s_cache + (size_t)c * a.dim + d));
             }
         }
     }
@@ -545,7 +622,7 @@ int fused_max_blocks(int device, int* pull_blocks, int* push_blocks) {
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_pull_kernel, kThreads, 0);
     if (e != cudaSuccess) return (int)e;
     *pull_blocks = per_sm * prop.multiProcessorCount;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_push_kernel, kThreads, 0);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_push_kernel, kThreads, kPushSmemBytes);
     if (e != cudaSuccess) return (int)e;
     *push_blocks = per_sm * prop.multiProcessorCount;
     return 0;
@@ -559,7 +636,7 @@ int launch_fused_pull(const FusedArgs& a, int nblocks, void* stream) {
 
 int launch_fused_push(const FusedArgs& a, int nblocks, void* stream) {
     void* params[] = {(void*)&a};
-    return (int)cudaLaunchCooperativeKernel((const void*)fused_push_kernel, dim3(nblocks), dim3(kThreads), params, 0,
+    return (int)cudaLaunchCooperativeKernel((const void*)fused_push_kernel, dim3(nblocks), dim3(kThreads), params, kPushSmemBytes,
                                             (cudaStream_t)stream);
 }
 

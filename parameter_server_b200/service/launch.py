@@ -1,0 +1,55 @@
+"""Process launchers of the service layer.
+
+    python -m parameter_server_b200.service.launch master            # prints the address, serves until killed
+    python -m parameter_server_b200.service.launch pserver --master 127.0.0.1:PORT [--restore]
+
+A ``pserver`` registers at the master, serves its c2s / s2s ports and exits when a client sends EXIT
+(``Controller.shutdown_node``). With ``--restore`` it first takes over the shards of a dead node
+(``Server.restore_storages``), the restore mode of the reference's pserver binary
+(pico-ps/service/Service.cpp:237-313).
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+import time
+
+from . import Master, Server, ServerConfig
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="parameter_server_b200.service.launch")
+    sub = ap.add_subparsers(dest="role", required=True)
+    m = sub.add_parser("master")
+    m.add_argument("--threads", type=int, default=4)
+    p = sub.add_parser("pserver")
+    p.add_argument("--master", required=True)
+    p.add_argument("--restore", action="store_true")
+    p.add_argument("--c2s-threads", type=int, default=4)
+    p.add_argument("--s2s-threads", type=int, default=4)
+    a = ap.parse_args(argv)
+    if a.role == "master":
+        master = Master(a.threads)
+        print(master.address(), flush=True)
+        try:
+            while True:
+                time.sleep(3600)
+        except KeyboardInterrupt:
+            master.stop()
+        return 0
+    cfg = ServerConfig()
+    cfg.c2s_thread_num, cfg.s2s_thread_num = a.c2s_threads, a.s2s_threads
+    server = Server(a.master, cfg)
+    print(f"pserver node_id={server.node_id()} c2s={server.c2s_address()} s2s={server.s2s_address()}", flush=True)
+    if a.restore:
+        st, n = server.restore_storages()
+        print(f"restore: {st} ({n} tables)", flush=True)
+        if not st.ok():
+            return 1
+    while not server.exited():
+        time.sleep(0.05)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
