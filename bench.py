@@ -41,7 +41,8 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl_baseline"],
+                    help="ours: fused kernels; nccl_baseline: the same model with NCCL-only sparse / dense paths (our own baseline)")
     ap.add_argument("--batch-per-gpu", type=int, default=8192)
     ap.add_argument("--no-sparse-micro", action="store_true", help="skip the sparse pull+push microbenchmark")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a CUDA graph")
@@ -151,7 +152,13 @@ def main():
     K, W = args.steps, args.warmup
     # every step may add up to B*26 new rows on the owners; size the index for the whole run
     capacity = max(1 << 22, (K * 2 + W + 8) * B * cfg.num_sparse * 2)
-    model = DLRM(cfg, B, table_capacity=capacity, seed=0)
+    if args.impl == "nccl_baseline":
+        from parameter_server_b200.parallel import NcclDenseTable, NcclSparseTable
+        model = DLRM(cfg, B, table_capacity=capacity, seed=0, sparse_cls=NcclSparseTable, dense_cls=NcclDenseTable)
+        args.no_graph = True      # variable all-to-all split sizes need the host: not capturable
+        args.no_sparse_micro = True
+    else:
+        model = DLRM(cfg, B, table_capacity=capacity, seed=0)
     data = SyntheticCTR(cfg, B, pool=16, seed=1000 + rank)
     uuid = str(torch.cuda.get_device_properties(local_rank).uuid)
     uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
@@ -214,7 +221,7 @@ def main():
         "vs_baseline": None,
         "dtype": "bf16 MLP, fp32 embeddings + optimizer state",
         "data": "synthetic (Zipf(1.1) keys per field, log-normal dense, Bernoulli(0.03) labels), random-init weights",
-        "impl": "ours",
+        "impl": args.impl,
         "config": {
             "model": "DLRM 13 dense + 26 sparse fields, emb dim 128 fp32 Adagrad on the PS, bottom 13-512-256-128, "
                      "27x128 pairwise-dot interaction, top 1024-1024-512-256-1 bf16 AdamW on the PS, BCE",
@@ -241,6 +248,8 @@ def main():
         "sparse_pull_push_keys_per_sec_in_step": 2 * keys_per_step * K / (ms / 1e3),
         "table_rows_rank0": model.sparse.size(),
     }
+    if args.impl == "nccl_baseline":
+        result["config"]["parallelism"] = f"dp{world} + NCCL all_to_all_single sparse path + reduce_scatter/all_gather dense path (baseline)"
 
     # ---------------- sparse pull+push microbenchmark (config 2 shape, dim 64 + Adagrad) ----------------
     if not args.no_sparse_micro:

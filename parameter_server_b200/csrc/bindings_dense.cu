@@ -38,12 +38,15 @@ void bind_dense(py::module_& m) {
         .def("load_full", [](DenseEngine& e, uintptr_t full, uintptr_t s) { return e.load_full(ptr<const float>(full), (void*)s); })
         .def("step", [](DenseEngine& e, const OptConfig& o, float scale, uintptr_t s) { return e.step(o, scale, (void*)s); })
         .def("check", [](DenseEngine& e, uintptr_t s) { return e.check((void*)s); })
-        .def("kernel_launches", &DenseEngine::kernel_launches);
+        .def("kernel_launches", &DenseEngine::kernel_launches)
+        .def("set_scatter_peers", &DenseEngine::set_scatter_peers);
 
     m.def("gemm_bf16",
           [](uintptr_t a, int64_t lda, bool a_mn, uintptr_t b, int64_t ldb, bool b_mn, int M, int N, int K,
              uintptr_t out_bf16, uintptr_t out_f32, int64_t ldd, uintptr_t bias, bool relu, uintptr_t mask,
-             int64_t ldmask, bool accumulate, uintptr_t bias_bf16, int split_k, uintptr_t err_flag, double wait_limit_s, uintptr_t stream) {
+             int64_t ldmask, bool accumulate, uintptr_t bias_bf16, int split_k, uintptr_t err_flag, double wait_limit_s, uintptr_t stream,
+             const std::vector<uintptr_t>& gather_peers, int gather_rank, int rows_per_rank, uintptr_t gather_ready,
+             unsigned gather_epoch, int gather_ctas) {
               GemmOperand A{ptr<const void>(a), lda, a_mn}, B{ptr<const void>(b), ldb, b_mn};
               GemmEpilogue ep;
               ep.out_bf16 = ptr<__nv_bfloat16>(out_bf16);
@@ -56,12 +59,26 @@ void bind_dense(py::module_& m) {
               ep.accumulate = accumulate ? 1 : 0;
               ep.bias_bf16 = ptr<const __nv_bfloat16>(bias_bf16);
               ep.split_k = split_k;
-              return gemm_bf16(A, B, ep, M, N, K, ptr<unsigned>(err_flag), wait_limit_s, (void*)stream);
+              GemmGather ag;
+              if (!gather_peers.empty()) {
+                  ag.enabled = 1;
+                  ag.world = (int)gather_peers.size();
+                  ag.rank = gather_rank;
+                  for (size_t r = 0; r < gather_peers.size() && r < 8; ++r) ag.peer_b[r] = ptr<const __nv_bfloat16>(gather_peers[r]);
+                  ag.local_b = ptr<__nv_bfloat16>(b);
+                  ag.rows_per_rank = rows_per_rank;
+                  ag.ready = ptr<unsigned>(gather_ready);
+                  ag.epoch = gather_epoch;
+                  ag.gather_ctas = gather_ctas;
+              }
+              return gemm_bf16(A, B, ep, M, N, K, ptr<unsigned>(err_flag), wait_limit_s, (void*)stream, &ag);
           },
           py::arg("a"), py::arg("lda"), py::arg("a_mn"), py::arg("b"), py::arg("ldb"), py::arg("b_mn"), py::arg("M"),
           py::arg("N"), py::arg("K"), py::arg("out_bf16") = 0, py::arg("out_f32") = 0, py::arg("ldd") = 0,
           py::arg("bias") = 0, py::arg("relu") = false, py::arg("mask") = 0, py::arg("ldmask") = 0,
-          py::arg("accumulate") = false, py::arg("bias_bf16") = 0, py::arg("split_k") = 1, py::arg("err_flag") = 0, py::arg("wait_limit_s") = 2.0, py::arg("stream") = 0);
+          py::arg("accumulate") = false, py::arg("bias_bf16") = 0, py::arg("split_k") = 1, py::arg("err_flag") = 0, py::arg("wait_limit_s") = 2.0, py::arg("stream") = 0,
+          py::arg("gather_peers") = std::vector<uintptr_t>(), py::arg("gather_rank") = 0, py::arg("rows_per_rank") = 0,
+          py::arg("gather_ready") = 0, py::arg("gather_epoch") = 0, py::arg("gather_ctas") = 8);
 
     bind_model_kernels(m);
 }

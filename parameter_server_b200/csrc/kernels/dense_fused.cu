@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(kThreads) dense_rs_opt_ag_kernel(const DenseAr
         for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(w[2 * k], w[2 * k + 1]);
 #pragma unroll
         for (int r = 0; r < kMaxWorld; ++r)
-            if (r < W) *(uint4*)(pdst[r] + i) = packed;
+            if (r < W && (a.scatter_peers || r == me)) *(uint4*)(pdst[r] + i) = packed;
     }
     // ---- 4. all slices landed everywhere ----------------------------------------------------------
     if (W == 1) {

@@ -21,6 +21,8 @@ struct DenseArgs {
     size_t shard_lo;                         // first element of this rank's slice
     size_t shard_len;                        // elements in the slice (multiple of 8)
     float grad_scale;                        // e.g. 1/world for a mean over data-parallel ranks
+    int scatter_peers;                       // 1: store the new bf16 values into every rank's buffer (all-gather);
+                                             // 0: only into this rank's own buffer (the consumer gathers lazily)
     OptConfig opt;
     KernelCtl* ctl;
 };

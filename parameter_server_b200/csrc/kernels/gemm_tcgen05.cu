@@ -25,6 +25,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdint>
 #include <cstdio>
 #include <mutex>
@@ -216,6 +217,71 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpilogue& ep, float* f,
     }
 }
 
+__device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Gather role of the all-gather + GEMM kernel (one CTA): copies the remote n-tile row blocks assigned to
+// this CTA from the owners' memory into the local copy of B with bulk async copies staged through shared
+// memory (4 x 32 KB in flight), then publishes the n-tile's flag. Only thread 0 works.
+template <int BN>
+__device__ void gather_rows(const GemmGather& ag, int K, uint8_t* smem, uint64_t* bars, unsigned* err_flag,
+                            unsigned long long limit_ns, int N) {
+    constexpr int kDepth = 4;
+    constexpr uint32_t kPiece = 32768;
+    if (threadIdx.x != 0) return;
+    for (int d = 0; d < kDepth; ++d) mbar_init(&bars[d], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const int n_tiles = (N + BN - 1) / BN;
+    const int tpr = ag.rows_per_rank / BN;
+    const size_t tile_bytes = (size_t)BN * K * 2;
+    uint32_t phase[kDepth] = {0, 0, 0, 0};  // parity of the next completion of each staging barrier
+    int order = 0;
+    // remote n-tiles in the order the GEMM CTAs will ask for them
+    for (int j = tpr; j < n_tiles; ++j, ++order) {
+        if (order % ag.gather_ctas != (int)blockIdx.x) continue;
+        const int nt = (j + ag.rank * tpr) % n_tiles;
+        const int owner = nt / tpr;
+        const uint8_t* src = (const uint8_t*)ag.peer_b[owner] + (size_t)nt * tile_bytes;
+        uint8_t* dst = (uint8_t*)ag.local_b + (size_t)nt * tile_bytes;
+        for (size_t off = 0; off < tile_bytes; off += (size_t)kDepth * kPiece) {
+            int issued = 0;
+            for (int d = 0; d < kDepth; ++d) {
+                const size_t o = off + (size_t)d * kPiece;
+                if (o >= tile_bytes) break;
+                const uint32_t bytes = (uint32_t)min((size_t)kPiece, tile_bytes - o);
+                mbar_expect_tx(&bars[d], bytes);
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 smem_u32(smem + (size_t)d * kPiece)),
+                             "l"(src + o), "r"(bytes), "r"(smem_u32(&bars[d]))
+                             : "memory");
+                ++issued;
+            }
+            for (int d = 0; d < issued; ++d) {
+                const size_t o = off + (size_t)d * kPiece;
+                const uint32_t bytes = (uint32_t)min((size_t)kPiece, tile_bytes - o);
+                if (!mbar_wait(&bars[d], phase[d], limit_ns)) {
+                    atomicCAS(err_flag, 0u, 6u);
+                    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                    return;
+                }
+                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst + o),
+                             "r"(smem_u32(smem + (size_t)d * kPiece)), "r"(bytes)
+                             : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                phase[d] ^= 1u;
+            }
+            // the staging buffers are reused by the next round: their stores must have read them
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        }
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        __threadfence();
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ag.ready + nt), "r"(ag.epoch) : "memory");
+    }
+}
+
 // Persistent kernel: gridDim.x CTAs (one per SM) walk the tile list t = blockIdx.x, +gridDim.x, ...;
 // a tile is (split z, n tile, m tile) with m fastest so that concurrently running CTAs share the B
 // tile in L2. The accumulator is double-buffered in TMEM (2 x BN columns): while the epilogue warps
@@ -224,7 +290,8 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpilogue& ep, float* f,
 template <int BN, bool AMN, bool BMN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                         const GemmEpilogue ep, int M, int N, int K, unsigned* err_flag, unsigned long long limit_ns) {
+                         const GemmEpilogue ep, int M, int N, int K, unsigned* err_flag, unsigned long long limit_ns,
+                         const GemmGather ag) {
     using L = SmemLayout<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -234,6 +301,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     uint64_t* tempty_bar = tfull_bar + 2;           // [2] accumulator buffer drained
     uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
 
+    // ---- all-gather role: the first ag.gather_ctas CTAs move remote row blocks of B into the local copy ----
+    const int n_gather = ag.enabled ? ag.gather_ctas : 0;
+    if ((int)blockIdx.x < n_gather) {
+        gather_rows<BN>(ag, K, smem, full_bar, err_flag, limit_ns, N);
+        return;
+    }
+    const int cta = (int)blockIdx.x - n_gather, n_cta = (int)gridDim.x - n_gather;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int m_tiles = (M + BM - 1) / BM;
@@ -270,10 +344,29 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         if (lane == 0) {
             uint32_t it = 0;  // k-tile counter across all tiles of this CTA (drives the stage ring)
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int tile = cta; tile < total_tiles && ok; tile += n_cta) {
                 const int z = tile / (m_tiles * n_tiles);
                 const int rem = tile - z * (m_tiles * n_tiles);
-                const int tile_n = (rem / m_tiles) * BN, tile_m = (rem % m_tiles) * BM;
+                int nt = rem / m_tiles;
+                if (ag.enabled) {
+                    // local rows first, then the ranks in ring order; a remote n-tile must have landed
+                    const int tpr = ag.rows_per_rank / BN;
+                    nt = (nt + ag.rank * tpr) % n_tiles;
+                    if (nt / tpr != ag.rank) {
+                        const unsigned long long t0 = gtimer();
+                        unsigned spins = 0;
+                        while ((int)(ld_acquire_gpu_u32(ag.ready + nt) - ag.epoch) < 0) {
+                            if ((++spins & 63u) == 0 && gtimer() - t0 > limit_ns) {
+                                atomicCAS(err_flag, 0u, 5u);
+                                ok = false;
+                                break;
+                            }
+                        }
+                        if (!ok) break;
+                        asm volatile("fence.proxy.async.global;" ::: "memory");
+                    }
+                }
+                const int tile_n = nt * BN, tile_m = (rem % m_tiles) * BM;
                 const int kt_begin = z * kt_per;
                 const int num_kt = max(0, min(total_kt - kt_begin, kt_per));
                 for (int kt = 0; kt < num_kt; ++kt, ++it) {
@@ -311,7 +404,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                                    ((BMN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             uint32_t it = 0, tc = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int tile = cta; tile < total_tiles && ok; tile += n_cta) {
                 const int z = tile / (m_tiles * n_tiles);
                 const int kt_begin = z * kt_per;
                 const int num_kt = max(0, min(total_kt - kt_begin, kt_per));
@@ -353,10 +446,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         // ------------------------------ epilogue ----------------------------------
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         uint32_t tc = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        for (int tile = cta; tile < total_tiles; tile += n_cta) {
             const int z = tile / (m_tiles * n_tiles);
             const int rem = tile - z * (m_tiles * n_tiles);
-            const int tile_n = (rem / m_tiles) * BN, tile_m = (rem % m_tiles) * BM;
+            int nt = rem / m_tiles;
+            if (ag.enabled) nt = (nt + ag.rank * (ag.rows_per_rank / BN)) % n_tiles;
+            const int tile_n = nt * BN, tile_m = (rem % m_tiles) * BM;
             const int kt_begin = z * kt_per;
             const int num_kt = max(0, min(total_kt - kt_begin, kt_per));
             if (num_kt == 0) continue;
@@ -430,7 +525,7 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, 
 
 template <int BN, bool AMN, bool BMN>
 cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const GemmEpilogue& ep, int M, int N, int K,
-                           unsigned* err, unsigned long long limit_ns, cudaStream_t s) {
+                           unsigned* err, unsigned long long limit_ns, cudaStream_t s, const GemmGather& ag) {
     auto kern = gemm_bf16_tcgen05_kernel<BN, AMN, BMN>;
     static bool configured = false;
     if (!configured) {
@@ -445,15 +540,25 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const G
         cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     }
     const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM) * (ep.split_k > 1 ? ep.split_k : 1);
-    dim3 grid(tiles < num_sms ? tiles : num_sms);
-    kern<<<grid, kThreads, SmemLayout<BN>::kTotal, s>>>(ma, mb, ep, M, N, K, err, limit_ns);
+    int ctas = tiles < num_sms ? tiles : num_sms;
+    if (ag.enabled) ctas = std::max(ag.gather_ctas + 1, std::min(num_sms, tiles + ag.gather_ctas));
+    dim3 grid(ctas);
+    kern<<<grid, kThreads, SmemLayout<BN>::kTotal, s>>>(ma, mb, ep, M, N, K, err, limit_ns, ag);
     return cudaGetLastError();
 }
 
 }  // namespace
 
 int gemm_bf16(const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep, int M, int N, int K, unsigned* err_flag,
-              double wait_limit_s, void* stream) {
+              double wait_limit_s, void* stream, const GemmGather* gather) {
+    GemmGather ag;
+    if (gather != nullptr) ag = *gather;
+    if (ag.enabled) {
+        // the gather path moves whole 256-row blocks of a contiguous K-major B and never splits K
+        if (A.mn_major || B.mn_major || B.ld != K || N < 256 || (ag.rows_per_rank % 256) || ag.rows_per_rank * ag.world != N ||
+            ep.split_k > 1 || ((size_t)K * 2) % 16)
+            return -2;
+    }
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if ((A.ld % 8) || (B.ld % 8) || ((uintptr_t)A.ptr % 16) || ((uintptr_t)B.ptr % 16)) return -2;  // TMA: 16-byte rule
     CUtensorMap ma, mb;
@@ -472,17 +577,17 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep
     const int v = (A.mn_major ? 2 : 0) | (B.mn_major ? 1 : 0);
     if (BN == 256) {
         switch (v) {
-            case 0: e = launch_variant<256, false, false>(ma, mb, ep, M, N, K, err_flag, lim, s); break;
-            case 1: e = launch_variant<256, false, true>(ma, mb, ep, M, N, K, err_flag, lim, s); break;
-            case 2: e = launch_variant<256, true, false>(ma, mb, ep, M, N, K, err_flag, lim, s); break;
-            default: e = launch_variant<256, true, true>(ma, mb, ep, M, N, K, err_flag, lim, s); break;
+            case 0: e = launch_variant<256, false, false>(ma, mb, ep, M, N, K, err_flag, lim, s, ag); break;
+            case 1: e = launch_variant<256, false, true>(ma, mb, ep, M, N, K, err_flag, lim, s, ag); break;
+            case 2: e = launch_variant<256, true, false>(ma, mb, ep, M, N, K, err_flag, lim, s, ag); break;
+            default: e = launch_variant<256, true, true>(ma, mb, ep, M, N, K, err_flag, lim, s, ag); break;
         }
     } else {
         switch (v) {
-            case 0: e = launch_variant<128, false, false>(ma, mb, ep, M, N, K, err_flag, lim, s); break;
-            case 1: e = launch_variant<128, false, true>(ma, mb, ep, M, N, K, err_flag, lim, s); break;
-            case 2: e = launch_variant<128, true, false>(ma, mb, ep, M, N, K, err_flag, lim, s); break;
-            default: e = launch_variant<128, true, true>(ma, mb, ep, M, N, K, err_flag, lim, s); break;
+            case 0: e = launch_variant<128, false, false>(ma, mb, ep, M, N, K, err_flag, lim, s, ag); break;
+            case 1: e = launch_variant<128, false, true>(ma, mb, ep, M, N, K, err_flag, lim, s, ag); break;
+            case 2: e = launch_variant<128, true, false>(ma, mb, ep, M, N, K, err_flag, lim, s, ag); break;
+            default: e = launch_variant<128, true, true>(ma, mb, ep, M, N, K, err_flag, lim, s, ag); break;
         }
     }
     return (int)e;

@@ -26,9 +26,26 @@ struct GemmEpilogue {
                                         // red.global.add.f32 into a zero-initialised fp32 output
 };
 
+// All-gather fused into the GEMM (dense pull fused with its first consumer): operand B ([N][K], K-major,
+// contiguous rows) is sharded by rows over `world` ranks, rank r holding the current values of rows
+// [r*rows_per_rank, (r+1)*rows_per_rank) in ITS copy of the tensor. `gather_ctas` CTAs of the launch pull the
+// remote row blocks over NVLink into this GPU's copy (bulk copies global -> shared -> global, no multicast)
+// and publish one flag per n-tile; the GEMM CTAs start with the tiles of the local rows and wait (bounded) for
+// the flag of a remote n-tile right before their TMA loads of it, so the transfer overlaps the math.
+struct GemmGather {
+    int enabled = 0;
+    int world = 1, rank = 0;
+    const __nv_bfloat16* peer_b[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    __nv_bfloat16* local_b = nullptr;
+    int rows_per_rank = 0;     // multiple of the n-tile height (256)
+    unsigned* ready = nullptr; // [N / 256] in local memory; n-tile j has landed when ready[j] >= epoch
+    unsigned epoch = 0;
+    int gather_ctas = 8;
+};
+
 // D = epilogue(A * B^T-style contraction over K). err_flag: device word, set non-zero when a bounded wait
 // inside the kernel ran out. Returns 0, a cudaError_t, -2 (alignment) or -3 (tensor map).
 int gemm_bf16(const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep, int M, int N, int K, unsigned* err_flag,
-              double wait_limit_s, void* stream);
+              double wait_limit_s, void* stream, const GemmGather* gather = nullptr);
 
 }  // namespace psb

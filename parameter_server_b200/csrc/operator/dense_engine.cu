@@ -103,6 +103,7 @@ Status DenseEngine::step(const OptConfig& opt, float grad_scale, void* stream) {
     a.shard_lo = shard_lo();
     a.shard_len = shard_len_;
     a.grad_scale = grad_scale;
+    a.scatter_peers = scatter_peers_ ? 1 : 0;
     a.opt = opt;
     a.ctl = ctl_;
     const size_t chunks = shard_len_ / 8;

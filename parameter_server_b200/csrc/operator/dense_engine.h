@@ -38,6 +38,11 @@ public:
     Status step(const OptConfig& opt, float grad_scale, void* stream);
     Status check(void* stream);
     uint64_t kernel_launches() const { return launches_; }
+    // false: dense push leaves the other ranks' copies of this table stale; they are gathered by the
+    // consuming kernel (all-gather fused with the first GEMM).
+    void set_scatter_peers(bool on) { scatter_peers_ = on; }
+    int world() const { return world_; }
+    int rank() const { return rank_; }
 
 private:
     int device_, world_, rank_;
@@ -51,6 +56,7 @@ private:
     KernelCtl* ctl_ = nullptr;
     unsigned epoch_ = 0;
     uint64_t launches_ = 0;
+    bool scatter_peers_ = true;
 };
 
 }  // namespace psb

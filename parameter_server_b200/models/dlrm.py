@@ -90,7 +90,8 @@ class DLRM:
     """One rank's replica of the model; ``train_step`` is collective over the ranks of ``group``."""
 
     def __init__(self, cfg: DLRMConfig, batch: int, *, table_capacity: int = 1 << 22, device=None, group=None,
-                 seed: int = 0, wgrad_split_k: int = 0, sparse_kwargs: Optional[dict] = None):
+                 seed: int = 0, wgrad_split_k: int = 0, sparse_kwargs: Optional[dict] = None,
+                 sparse_cls=SparseTable, dense_cls=DenseTable):
         if not torch.cuda.is_available():
             raise RuntimeError("DLRM runs on the sm_100a kernels and needs a CUDA device")
         self.cfg = cfg
@@ -100,7 +101,8 @@ class DLRM:
         D, F = cfg.emb_dim, cfg.num_sparse
         assert cfg.bottom[-1] == D, "bottom MLP must end at the embedding width"
         self.split_k = wgrad_split_k
-        self.sparse = SparseTable(D, cfg.sparse_optimizer, cfg.sparse_opt_kwargs, capacity=table_capacity,
+        # sparse_cls / dense_cls let the NCCL-only baseline tables stand in for the fused ones
+        self.sparse = sparse_cls(D, cfg.sparse_optimizer, cfg.sparse_opt_kwargs, capacity=table_capacity,
                                   max_keys=batch * F, device=self.device, group=group, seed=seed,
                                   **(sparse_kwargs or {}))
         # ---- dense parameters ------------------------------------------------------------------
@@ -119,7 +121,7 @@ class DLRM:
             shapes[f"top.b{i}"] = (tdims[i + 1],)
         shapes["head.w"] = (tdims[-1],)
         shapes["head.b"] = (1,)
-        self.dense = DenseTable(shapes, cfg.dense_optimizer, cfg.dense_opt_kwargs, grad_dtype=torch.float32,
+        self.dense = dense_cls(shapes, cfg.dense_optimizer, cfg.dense_opt_kwargs, grad_dtype=torch.float32,
                                 device=self.device, group=group)
         gen = torch.Generator().manual_seed(seed + 1)
         init = {}

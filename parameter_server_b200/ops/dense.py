@@ -43,7 +43,8 @@ def _view(ptr: int, numel: int, dtype: torch.dtype, device, owner) -> torch.Tens
 
 class DenseTable:
     def __init__(self, shapes: Dict[str, Sequence[int]], optimizer: str = "adamw", opt_kwargs: Optional[dict] = None, *,
-                 grad_dtype: torch.dtype = torch.float32, device=None, group=None, wait_limit_s: float = 10.0):
+                 grad_dtype: torch.dtype = torch.float32, device=None, group=None, wait_limit_s: float = 10.0,
+                 scatter_peers: bool = True):
         self.group = group
         self.world, self.rank = _dist_info(group)
         self.opt = make_opt_config(optimizer, **(opt_kwargs or {}))
@@ -69,6 +70,11 @@ class DenseTable:
             self.engine = C.DenseEngine(idx, self.world, self.rank, max(off, 64), grad_dtype == torch.bfloat16,
                                         self.opt.type, wait_limit_s)
             self.numel = self.engine.numel()
+            # scatter_peers=False: a push leaves the peers' copies stale; the consumer gathers (ops.gemm.ag_linear)
+            self.engine.set_scatter_peers(bool(scatter_peers))
+            self.scatter_peers = bool(scatter_peers)
+            self._ag_ready = None
+            self._ag_epoch = 0
             if self.world > 1:
                 import torch.distributed as dist
                 handles = [None] * self.world

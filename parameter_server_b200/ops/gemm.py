@@ -34,7 +34,7 @@ def _ptr(t: Optional[torch.Tensor]) -> int:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, bias: Optional[torch.Tensor] = None,
          relu: bool = False, mask: Optional[torch.Tensor] = None, accumulate: bool = False, split_k: int = 1,
-         M: Optional[int] = None, N: Optional[int] = None, K: Optional[int] = None) -> torch.Tensor:
+         M: Optional[int] = None, N: Optional[int] = None, K: Optional[int] = None, gather: Optional[dict] = None) -> torch.Tensor:
     """``out[M,N] = epilogue(sum_k A(m,k) B(n,k))``.
 
     ``a`` is ``[M,K]`` (or ``[K,M]`` with ``a_mn``), ``b`` is ``[N,K]`` (or ``[K,N]`` with ``b_mn``);
@@ -62,7 +62,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
                      _ptr(o16), _ptr(o32), out.stride(0), _ptr(b32), relu, _ptr(mask),
                      mask.stride(0) if mask is not None else 0, accumulate, _ptr(b16), split_k,
                      _err_flag(a.device).data_ptr(), 2.0,
-                     torch.cuda.current_stream().cuda_stream)
+                     torch.cuda.current_stream().cuda_stream, **(gather or {}))
     if rc != 0:
         raise RuntimeError(f"gemm_bf16 failed with code {rc}")
     return out
@@ -88,3 +88,27 @@ def linear_wgrad(dy, x, out=None, accumulate=False, split_k=1):
         split_k = max(1, min(16, 148 // tiles, max(1, batch // 256)))
     return gemm(dy, x, a_mn=True, b_mn=True, out=out, out_dtype=torch.float32, accumulate=accumulate,
                 split_k=split_k)
+
+
+def ag_linear(x: torch.Tensor, table, name: str, *, bias=None, relu: bool = False, out=None, gather_ctas: int = 8) -> torch.Tensor:
+    """``y = act(x @ W.T + bias)`` where ``W = table[name]`` is a dense-table tensor whose rows are sharded over the
+    ranks and whose peer copies are NOT kept current by the dense push (``DenseTable(scatter_peers=False)``):
+    the all-gather of W is fused into this GEMM. The first ``gather_ctas`` CTAs pull the remote row blocks over
+    NVLink into the local copy while the other CTAs already multiply the local rows; a tile of remote rows
+    waits for its block's flag. Dense pull fused with its first consumer
+    (pico-ps/operator/DensePullOperator.h:153-169,197-216)."""
+    W = table.params[name]
+    N, K = W.shape
+    world, rank = table.world, table.rank
+    if world == 1:
+        return gemm(x, W, bias=bias, relu=relu, out=out)
+    off, _ = table.offsets[name]
+    if off != 0 or table.numel != N * K or N % (256 * world):
+        raise ValueError("ag_linear needs a dense table that holds exactly this tensor, rows divisible by 256 * world")
+    if table._ag_ready is None:
+        table._ag_ready = torch.zeros(N // 256, dtype=torch.int32, device=W.device)
+    table._ag_epoch += 1
+    g = dict(gather_peers=[table.engine.peer_params_ptr(r) for r in range(world)], gather_rank=rank,
+             rows_per_rank=N // world, gather_ready=table._ag_ready.data_ptr(), gather_epoch=table._ag_epoch,
+             gather_ctas=gather_ctas)
+    return gemm(x, W, bias=bias, relu=relu, out=out, gather=g)
