@@ -4,6 +4,7 @@
 
 #include "kernels/gemm_tcgen05.h"
 #include "kernels/model_kernels.h"
+#include "comm/symmetric.h"
 #include "operator/dense_engine.h"
 
 namespace py = pybind11;
@@ -15,6 +16,19 @@ T* ptr(uintptr_t p) { return reinterpret_cast<T*>(p); }
 }  // namespace
 
 void bind_dense(py::module_& m) {
+    py::class_<SymmetricBuffer>(m, "SymmetricBuffer")
+        .def(py::init<int, size_t>(), py::arg("device"), py::arg("bytes"))
+        .def("ipc_handle", [](SymmetricBuffer& b) { return py::bytes(b.ipc_handle()); })
+        .def("connect", [](SymmetricBuffer& b, const std::vector<py::bytes>& hs, int rank) {
+            std::vector<std::string> v;
+            for (auto& h : hs) v.push_back((std::string)h);
+            return b.connect(v, rank);
+        })
+        .def("local", [](SymmetricBuffer& b) { return (uintptr_t)b.local(); })
+        .def("peer", [](SymmetricBuffer& b, int r) { return (uintptr_t)b.peer(r); })
+        .def("bytes", &SymmetricBuffer::bytes)
+        .def("world", &SymmetricBuffer::world);
+
     py::class_<DenseEngine>(m, "DenseEngine")
         .def(py::init<int, int, int, size_t, bool, int, double>(), py::arg("device"), py::arg("world"), py::arg("rank"),
              py::arg("numel"), py::arg("grad_bf16"), py::arg("opt_type"), py::arg("wait_limit_s") = 10.0)

@@ -62,6 +62,7 @@ class SparseTable:
         self.world, self.rank = _dist_info(group)
         self.n_shards = int(n_shards or self.world)
         self.read_only = read_only
+        self.sync = bool(sync)
         self.opt = make_opt_config(optimizer, **(opt_kwargs or {}))
         self.opt_name = optimizer.lower()
         self.step = 0

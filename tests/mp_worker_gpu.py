@@ -104,6 +104,47 @@ def main():
         if rank == 0:
             print("dense ok", flush=True)
 
+    if which in ("all", "migrate"):
+        from parameter_server_b200.parallel import ReplicaSet, reshard
+        n_shards = 2 * world
+        t = SparseTable(32, "adagrad", dict(lr=0.05, init_accumulator=0.1), n_shards=n_shards, capacity=1 << 16,
+                        max_keys=1 << 15, wait_limit_s=5.0)
+        rng = np.random.default_rng(7 + rank)
+        keys = torch.from_numpy(rng.integers(0, 1 << 40, size=20000)).cuda()
+        t.pull(keys)
+        t.push(torch.randn(20000, 32, device="cuda") * 1e-2)
+        before = t.pull(keys).clone()
+        t.check()
+        total_before = sum(gather(t.size()))
+        # rebalance: rotate the ownership of every shard by one rank
+        new_owner = [(o + 1) % world for o in t.shard_owner]
+        reshard(t, new_owner)
+        assert sum(gather(t.size())) == total_before
+        ks = torch.cat([k for k, _ in t.export()] or [torch.empty(0, dtype=torch.int64, device="cuda")])
+        owners = {new_owner[__import__("parameter_server_b200").C.sparse_shard_of(int(k), n_shards)] for k in ks[:500].tolist()}
+        assert owners <= {rank}, owners
+        after = t.pull(keys, insert=False)
+        t.check()
+        assert torch.equal(after, before), "rows changed while moving between GPUs"
+        # 2x replication: mirror on the partner, incremental sync, restore after a loss
+        rs = ReplicaSet(t)
+        n0 = t.size()
+        assert rs.sync() == n0 and rs.mirror.size() == gather(n0)[(rank - 1) % world]
+        t.pull(keys[:100]); t.push(torch.ones(100, 32, device="cuda") * 1e-2); t.check()
+        assert 0 < rs.sync() <= 100 * world          # only what changed travels (keys of this rank's shards)
+        want = t.pull(keys, insert=False).clone()
+        if rank == 0:
+            t.clear()                                  # rank 0 "lost" its HBM contents
+        got = rs.restore(0)
+        if rank == 0:
+            assert got == n0 and t.size() == n0
+        again = t.pull(keys, insert=False)
+        t.check()
+        assert torch.equal(again, want)
+        dist.barrier()
+        if rank == 0:
+            print("migrate ok", flush=True)
+
     if which in ("all", "aggemm"):
         from parameter_server_b200.ops import gemm as G
         N, K, M = 512 * world, 384, 1000

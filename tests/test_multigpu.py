@@ -19,7 +19,7 @@ def run_ranks(n, which):
     return p.stdout
 
 
-@pytest.mark.parametrize("which", ["sparse", "dense", "aggemm", "dlrm"])
+@pytest.mark.parametrize("which", ["sparse", "dense", "migrate", "aggemm", "dlrm"])
 def test_two_ranks(which):
     out = run_ranks(2, which)
     assert f"{which} ok" in out
@@ -30,4 +30,4 @@ def test_all_visible_gpus():
     if n <= 2:
         pytest.skip("covered by the 2-rank test")
     out = run_ranks(n, "all")
-    assert "sparse ok" in out and "dense ok" in out and "aggemm ok" in out and "dlrm ok" in out
+    assert "sparse ok" in out and "dense ok" in out and "migrate ok" in out and "aggemm ok" in out and "dlrm ok" in out
