@@ -8,6 +8,7 @@
 #include "common/message.h"
 #include "common/status.h"
 #include "operator/sparse_engine.h"
+#include "storage/cold_tier.h"
 #include "storage/gpu_table.h"
 
 namespace py = pybind11;
@@ -168,6 +169,18 @@ PYBIND11_MODULE(_C, m) {
         .def("store_delta", [](GpuTable& t, const OptConfig& o, uintptr_t s) { return t.store_delta(o, stream_of(s)); })
         .def("clear", [](GpuTable& t, uintptr_t s) { return t.clear(stream_of(s)); })
         .def("rebuild_index", [](GpuTable& t, uint64_t cap, uintptr_t s) { return t.rebuild_index(cap, stream_of(s)); });
+
+    py::class_<HostColdTier>(m, "HostColdTier")
+        .def(py::init<GpuTable*, uint64_t, uint32_t>(), py::arg("table"), py::arg("capacity_rows"), py::arg("window") = 1u << 16,
+             py::keep_alive<1, 2>())
+        .def("spill_if", [](HostColdTier& c, uint32_t section, float thr) { uint64_t n = 0; Status st = c.spill_if(section, thr, &n); return py::make_tuple(st, n); })
+        .def("spill_keys", [](HostColdTier& c, uintptr_t keys, uint64_t n) { uint64_t k = 0; Status st = c.spill_keys((const int64_t*)keys, n, &k); return py::make_tuple(st, k); })
+        .def("fetch", [](HostColdTier& c, uintptr_t keys, uint64_t n) { uint64_t k = 0; Status st = c.fetch((const int64_t*)keys, n, &k); return py::make_tuple(st, k); })
+        .def("size", &HostColdTier::size)
+        .def("capacity", &HostColdTier::capacity)
+        .def("bytes", &HostColdTier::bytes)
+        .def("save", &HostColdTier::save)
+        .def("load", &HostColdTier::load);
 
     py::class_<SparseEngineConfig>(m, "SparseEngineConfig")
         .def(py::init<>())

@@ -307,6 +307,35 @@ class SparseTable:
                     if len(k):
                         yield torch.from_numpy(k), torch.from_numpy(r)
 
+    # ---- cold tier (pinned host DRAM under the HBM table) ---------------------------------------
+    def enable_cold_tier(self, capacity_rows: int, window: int = 1 << 16) -> None:
+        """Attach a pinned-host tier of ``capacity_rows`` rows (the role of the reference's PMEM tier)."""
+        if not self.is_cuda:
+            raise RuntimeError("the cold tier sits under a GPU table")
+        self.cold = C.HostColdTier(self.table, int(capacity_rows), int(window))
+
+    def spill_cold(self, section: int = 1, threshold: float = 0.0) -> int:
+        """Move rows whose mean over row section ``section`` is below ``threshold`` to the cold tier."""
+        torch.cuda.current_stream().synchronize()
+        st, n = self.cold.spill_if(section, threshold)
+        raise_if_error(st)
+        return int(n)
+
+    def spill_keys(self, keys: torch.Tensor) -> int:
+        k = keys.reshape(-1).cpu().contiguous()
+        torch.cuda.current_stream().synchronize()
+        st, n = self.cold.spill_keys(k.data_ptr(), k.numel())
+        raise_if_error(st)
+        return int(n)
+
+    def prefetch_cold(self, keys: torch.Tensor) -> int:
+        """Bring the rows of ``keys`` (a host tensor, e.g. the next batch while it is still in pinned
+        memory) back from the cold tier before they are pulled. Returns how many came back."""
+        k = keys.reshape(-1).cpu().contiguous()
+        st, n = self.cold.fetch(k.data_ptr(), k.numel())
+        raise_if_error(st)
+        return int(n)
+
     def clear(self) -> None:
         if self.is_cuda:
             raise_if_error(self.table.clear(_stream()))

@@ -171,3 +171,30 @@ def test_large_batch_1m_keys():
     nu = g.engine.last_unique(0)
     assert nu == torch.unique(keys).numel() == g.size()
     assert torch.isfinite(out).all()
+
+
+def test_cold_tier_spill_fetch_and_persistence(tmp_path):
+    t = SparseTable(32, "adagrad", dict(lr=0.05, init_accumulator=0.1), device="cuda", capacity=1 << 15, max_keys=1 << 14)
+    t.enable_cold_tier(1 << 14, window=4096)
+    hot, cold = torch.arange(0, 4000, device="cuda"), torch.arange(4000, 10000, device="cuda")
+    t.pull(torch.cat([hot, cold]))
+    for _ in range(3):                      # only the hot keys keep receiving gradient
+        t.pull(hot); t.push(torch.ones(4000, 32, device="cuda"))
+    t.check()
+    full, _ = t.get_rows(torch.cat([hot, cold]), emb_only=False)
+    n = t.spill_cold(section=1, threshold=0.5)          # Adagrad accumulator stayed at 0.1 for the cold keys
+    assert n == 6000 and t.size() == 4000 and t.cold.size() == 6000
+    # persistence with the layout identity check
+    img = str(tmp_path / "cold.img")
+    assert t.cold.save(img, "uuid-A").ok()
+    t2 = SparseTable(32, "adagrad", dict(lr=0.05, init_accumulator=0.1), device="cuda", capacity=1 << 15, max_keys=1 << 14)
+    t2.enable_cold_tier(1 << 14)
+    assert t2.cold.load(img, "uuid-B").code() == StatusCode.INVALID_ID
+    assert t2.cold.load(img, "uuid-A").ok() and t2.cold.size() == 6000
+    # the next batch touches some cold keys: fetch them back first, nothing was lost (slots included)
+    batch = torch.cat([hot[:100], cold[:500]]).cpu()
+    assert t.prefetch_cold(batch) == 500 and t.cold.size() == 5500 and t.size() == 4500
+    rows, found = t.get_rows(batch.cuda(), emb_only=False)
+    assert found.all()
+    assert torch.equal(rows, torch.cat([full[:100], full[4000:4500]]))
+    assert t.spill_keys(hot[:10]) == 10 and t.size() == 4490
