@@ -246,8 +246,13 @@ void bind_service(py::module_& m) {
         .def("handle_timeout", &Client::handle_timeout, nogil())
         .def("handle_out_of_memory", &Client::handle_out_of_memory, nogil());
 
+    py::class_<PullGroup, std::shared_ptr<PullGroup>>(m, "PullGroup")
+        .def(py::init<>())
+        .def("merged_sends", [](PullGroup& g) { return g.merged_sends.load(); })
+        .def("merged_requests", [](PullGroup& g) { return g.merged_requests.load(); });
     py::class_<PullHandler>(m, "PullHandler")
         .def(py::init(&make_handler<PullHandler>), py::keep_alive<1, 2>())
+        .def("join_group", &PullHandler::join_group)
         .def("dim", &PullHandler::dim)
         .def("metrics", [](PullHandler& h) { return metrics_dict(h); })
         .def("pull", [](PullHandler& h, KeyArray keys, int timeout_ms, bool auto_retry) {

@@ -13,6 +13,7 @@
 #include <chrono>
 #include <functional>
 
+#include "../common/thread_sync.h"
 #include "../service/client.h"
 
 namespace psb {
@@ -90,13 +91,38 @@ protected:
 };
 
 // ---------------------------------------------------------------------------------------------------
+// Request-merge group of pull handlers that live on different threads of one client
+// (PullRequestDataGroup of pico-ps/handler/PullHandler.h:22-29): small requests of two threads travel as
+// one message per node.
+struct PullGroup {
+    ThreadReduce reduce;
+    ThreadBcast bcast;
+    PullRequestData data[kThreadGroupSize];
+    Status status[kThreadGroupSize];
+    std::atomic<int> next_tid{0};
+    std::atomic<uint64_t> merged_sends{0}, merged_requests{0};
+};
+
 class PullHandler : public Handler {
 public:
     using Handler::Handler;
+    static constexpr size_t kMergeBelowBytesPerNode = 128 << 10;  // pico-ps/handler/PullHandler.cpp:121-126
+
+    // Join a merge group (at most 32 handlers, one per thread). Returns the slot, or -1 when it is full.
+    int join_group(std::shared_ptr<PullGroup> g) {
+        int t = g->next_tid.fetch_add(1);
+        if (t >= kThreadGroupSize) return -1;
+        group_ = std::move(g);
+        tid_ = t;
+        return t;
+    }
+    PullGroup* group() const { return group_.get(); }
+
     // out: n * dim floats, one row per key position.
     Status pull(const int64_t* keys, size_t n, float* out, int timeout_ms = -1, bool auto_retry = true) {
         std::shared_ptr<SparseTablePullOperator> p;
         PSB_RETURN_IF_ERROR(op(&p));
+        if (group_) return with_retry([&](int left) { return merged_attempt(*p, keys, n, out, left); }, timeout_ms, auto_retry);
         return with_retry([&](int left) -> Status {
             auto e = entry();
             PullRequestData data;
@@ -129,6 +155,54 @@ public:
         auto e = entry();
         return e ? storage_op_of(*e)->dim() : 0;
     }
+
+private:
+    // One attempt inside a merge group. Nothing between add() and reduce() can fail, so a thread that
+    // announced itself always reaches reduce() and nobody waits for it in vain.
+    Status merged_attempt(SparseTablePullOperator& p, const int64_t* keys, size_t n, float* out, int left) {
+        PullGroup& g = *group_;
+        auto e = entry();
+        g.reduce.add(tid_);
+        PullRequestData& mine = g.data[tid_];
+        size_t nodes = 1;
+        {
+            std::shared_lock<std::shared_mutex> lk(e->mu);
+            p.generate_request_data(*e, keys, n, &mine);
+            nodes = std::max<size_t>(1, e->rt.nodes().size());
+        }
+        const int sync_num = (size_t)mine.n_uniq * 8 / nodes < kMergeBelowBytesPerNode ? 2 : 1;
+        const uint32_t tids = g.reduce.reduce(tid_, sync_num);
+        Status st;
+        if (tids == 0) {
+            g.bcast.wait(tid_);  // the owner of the merged request fills our rows and status
+            st = g.status[tid_];
+        } else {
+            std::vector<PullRequestData*> ds;
+            for (int t = 0; t < kThreadGroupSize; ++t)
+                if ((tids >> t) & 1u) ds.push_back(&g.data[t]);
+            st = [&]() -> Status {
+                NodeRequests reqs;
+                {
+                    std::shared_lock<std::shared_mutex> lk(e->mu);
+                    PSB_RETURN_IF_ERROR(p.generate_merged_requests(*e, ds, &reqs));
+                }
+                std::vector<NodeResponse> rs;
+                PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_PULL, reqs.body, left, &rs));
+                for (auto& r : rs) PSB_RETURN_IF_ERROR(p.apply_merged_response(*e, ds, r.body));
+                return Status::Ok();
+            }();
+            ++g.merged_sends;
+            g.merged_requests += ds.size();
+            for (int t = 0; t < kThreadGroupSize; ++t)
+                if ((tids >> t) & 1u) g.status[t] = st;
+            g.bcast.notify(tids, tid_);
+        }
+        if (st.ok()) p.fill_pull_items(*e, mine, out);
+        return st;
+    }
+
+    std::shared_ptr<PullGroup> group_;
+    int tid_ = -1;
 };
 
 class PushHandler : public Handler {

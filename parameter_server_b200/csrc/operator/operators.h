@@ -138,6 +138,7 @@ struct PullRequestData {
     std::map<int32_t, std::vector<int64_t>> shard_keys;
     std::map<int32_t, std::vector<uint32_t>> shard_uid;
     std::vector<float> uniq_rows;                  // n_uniq * dim
+    int32_t global_shard_num = 0;                  // the partitioning these lists were built under
 };
 
 class SparseTablePullOperator : public Operator {
@@ -154,6 +155,7 @@ public:
         EasyHashMap<int64_t, uint32_t> whole(kHostEmptyKey, n);
         d->n = n;
         d->n_uniq = 0;
+        d->global_shard_num = G;
         d->inverse.resize(n);
         d->shard_keys.clear();
         d->shard_uid.clear();
@@ -187,6 +189,56 @@ public:
             }
             out->shards[kv.first] = kv.second;
         }
+        return Status::Ok();
+    }
+    // Several threads' requests in one message per node (request coalescing): the node's shard list is the
+    // union over the merged requests, every shard carries one key list per merged request (possibly empty).
+    Status generate_merged_requests(const TableEntry& e, const std::vector<PullRequestData*>& ds, NodeRequests* out) const {
+        std::map<int32_t, int> shard_node;
+        for (auto* d : ds) {
+            if (d->global_shard_num != e.rt.global_shard_num())
+                return Status::ServerTooNewCtx("the context changed while pull requests were being merged");
+            for (auto& kv : d->shard_keys) shard_node.emplace(kv.first, -1);
+        }
+        std::map<int, std::vector<int32_t>> by_node;
+        for (auto& kv : shard_node) {
+            int node = e.rt.pick_one_replica(kv.first);
+            if (node < 0) return Status::NoReplica("no live replica of shard " + std::to_string(kv.first));
+            by_node[node].push_back(kv.first);
+        }
+        static const std::vector<int64_t> none;
+        for (auto& kv : by_node) {
+            Archive& ar = out->body[kv.first];
+            ar << (int32_t)kv.second.size() << (int32_t)ds.size();
+            for (int32_t s : kv.second) {
+                ar << s;
+                for (auto* d : ds) {
+                    auto it = d->shard_keys.find(s);
+                    const auto& ks = it == d->shard_keys.end() ? none : it->second;
+                    ar << (int32_t)ks.size();
+                    ar.write_raw(ks.data(), ks.size() * 8);
+                }
+            }
+            out->shards[kv.first] = kv.second;
+        }
+        return Status::Ok();
+    }
+    Status apply_merged_response(const TableEntry& e, const std::vector<PullRequestData*>& ds, Archive& resp) const {
+        const uint32_t dim = storage_op_of(e)->dim();
+        int32_t shards_num = 0;
+        resp >> shards_num;
+        std::vector<int32_t> ids(shards_num);
+        for (auto& s : ids) resp >> s;
+        std::vector<float> tmp;
+        for (int32_t s : ids)
+            for (auto* d : ds) {
+                auto it = d->shard_uid.find(s);
+                if (it == d->shard_uid.end()) continue;
+                tmp.resize(it->second.size() * dim);
+                resp.read_raw(tmp.data(), tmp.size() * 4);
+                for (size_t j = 0; j < it->second.size(); ++j)
+                    std::copy_n(tmp.data() + j * dim, dim, d->uniq_rows.data() + (size_t)it->second[j] * dim);
+            }
         return Status::Ok();
     }
     Status apply_response(const TableEntry& e, PullRequestData* d, Archive& resp) const {

@@ -19,6 +19,7 @@ Server = C.Server
 ServerConfig = C.ServerConfig
 Client = C.Client
 PullHandler = C.PullHandler
+PullGroup = C.PullGroup
 PushHandler = C.PushHandler
 ForEachHandler = C.ForEachHandler
 EraseIfHandler = C.EraseIfHandler

@@ -510,3 +510,34 @@ def test_table_descriptor_state_machine():
     td.apply_update()
     assert td.global_shard_num() == 4 and td.update_version == uv + 2
     assert td2.from_json_str(td.to_json_str(), True)
+
+
+def test_pull_requests_of_threads_are_merged(cluster3):
+    """Small pulls of handlers on different threads travel as one message per node and every thread still
+    gets exactly its own rows (ThreadReduce / ThreadBcast coalescing)."""
+    cl = cluster3
+    sid, h = make_table(cl, uneven(cl.ids()))
+    push = S.PushHandler(cl.client, sid, h["push"])
+    keys = np.arange(4000, dtype=np.int64)
+    g = (keys[:, None] * np.ones((1, DIM))).astype(np.float32)
+    assert push.async_push(keys, g).ok()
+    group = S.PullGroup()
+    T = 4
+    hs = [S.PullHandler(cl.client, sid, h["pull_ro"]) for _ in range(T)]
+    assert [x.join_group(group) for x in hs] == list(range(T))
+    rng = np.random.default_rng(0)
+    batches = [[rng.integers(0, 4000, size=300).astype(np.int64) for _ in range(30)] for _ in range(T)]
+    bad = []
+
+    def work(t):
+        for b in batches[t]:
+            st, rows = hs[t].pull(b)
+            if not (st.ok() and np.array_equal(rows, g[b])):
+                bad.append((t, str(st)))
+
+    ts = [threading.Thread(target=work, args=(t,)) for t in range(T)]
+    [t.start() for t in ts]
+    [t.join(60) for t in ts]
+    assert not bad and not any(t.is_alive() for t in ts)
+    assert group.merged_requests() == T * 30
+    assert group.merged_sends() < group.merged_requests()      # some requests did share a message
