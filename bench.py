@@ -265,12 +265,13 @@ def main():
 
 
 def sparse_micro(args, world, rank, barrier, max_over_ranks) -> dict:
-    """Pull+push key throughput: dim 64 fp32 + Adagrad slot, Zipf(1.05) keys with ~30% in-batch
+    """Pull+push key throughput: dim 64 fp32 + Adagrad slot, Zipf(1.05) keys with at least 30% in-batch
     duplicates, ``--micro-keys`` keys per GPU per step. Device-timed, max over ranks."""
     import numpy as np
     import torch
 
     from parameter_server_b200 import SparseTable
+    from parameter_server_b200.utils.keys import zipf_batch
 
     n = args.micro_keys
     steps, warm = 20, 5
@@ -279,12 +280,7 @@ def sparse_micro(args, world, rank, barrier, max_over_ranks) -> dict:
     rng = np.random.default_rng(77 + rank)
     pool = []
     for _ in range(8):
-        k = rng.zipf(1.05, size=n).astype(np.uint64)
-        k = ((k * np.uint64(0x9E3779B97F4A7C15)) >> np.uint64(2)) % np.uint64(500_000_000 * world // 8 + 1)
-        k = k.astype(np.int64)
-        # force ~30% duplicates inside the batch
-        dup = rng.random(n) < 0.3
-        k[dup] = k[rng.integers(0, n, size=int(dup.sum()))]
+        k = zipf_batch(rng, n, 1.05, 500_000_000 * world // 8 + 1, 0.3)
         pool.append(torch.from_numpy(k).cuda())
     grads = torch.randn(n, 64, device="cuda") * 1e-3
     out = torch.empty(n, 64, device="cuda")

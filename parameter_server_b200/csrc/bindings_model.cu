@@ -26,6 +26,9 @@ void bind_model_kernels(py::module_& m) {
     m.def("bias_grad", [](uintptr_t dz, int64_t ld, int M, int N, uintptr_t db, uintptr_t s) {
         return bias_grad((const void*)dz, ld, M, N, (float*)db, (void*)s);
     });
+    m.def("shard_of_keys", [](uintptr_t keys, unsigned long long n, int n_shards, uintptr_t shard_owner, uintptr_t out, uintptr_t s) {
+        return shard_of_keys((const long long*)keys, n, n_shards, (const int*)shard_owner, (int*)out, (void*)s);
+    });
     m.def("dedup_fill_scratch", [](uintptr_t scratch, unsigned long long slots, uintptr_t s) {
         return dedup_fill_scratch((void*)scratch, slots, (void*)s);
     });

@@ -84,6 +84,15 @@ __global__ void dedup_fill_kernel(Slot* table, unsigned long long slots) {
     }
 }
 
+__global__ void shard_of_kernel(const long long* __restrict__ keys, unsigned long long n, int n_shards,
+                                const int* __restrict__ shard_owner, int* __restrict__ out) {
+    for (unsigned long long i = blockIdx.x * (unsigned long long)kThreads + threadIdx.x; i < n;
+         i += (unsigned long long)gridDim.x * kThreads) {
+        const int s = sparse_shard_of(keys[i], n_shards);
+        out[i] = shard_owner ? shard_owner[s] : s;
+    }
+}
+
 int run(const long long* keys, unsigned n, Slot* table, unsigned long long slots, unsigned* pos_slot, const int* shard_owner,
         int n_shards, int world, long long* uniq_keys, int* uniq_owner, int* inverse, unsigned* counts, cudaStream_t s) {
     cudaError_t e = cudaMemsetAsync(counts, 0, (size_t)(1 + world) * sizeof(unsigned), s);
@@ -98,6 +107,15 @@ int run(const long long* keys, unsigned n, Slot* table, unsigned long long slots
 }
 
 }  // namespace
+
+int shard_of_keys(const long long* keys, unsigned long long n, int n_shards, const int* shard_owner, int* out, void* stream) {
+    if (n == 0) return 0;
+    if (n_shards < 1) return -2;
+    const unsigned long long want = (n + kThreads - 1) / kThreads;
+    shard_of_kernel<<<(unsigned)(want < 148 * 8 ? want : 148 * 8), kThreads, 0, (cudaStream_t)stream>>>(keys, n, n_shards,
+                                                                                                       shard_owner, out);
+    return (int)cudaGetLastError();
+}
 
 int dedup_fill_scratch(void* scratch, unsigned long long slots, void* stream) {
     dedup_fill_kernel<<<148 * 4, kThreads, 0, (cudaStream_t)stream>>>((Slot*)scratch, slots);

@@ -14,4 +14,7 @@ int dedup_partition(const long long* keys, unsigned n, void* scratch, unsigned l
                     const int* shard_owner, int n_shards, int world, long long* uniq_keys, int* uniq_owner, int* inverse,
                     unsigned* counts, void* stream);
 
+// out[i] = shard of keys[i] under n_shards, or the owner of that shard when shard_owner (device, n_shards ints) is given.
+int shard_of_keys(const long long* keys, unsigned long long n, int n_shards, const int* shard_owner, int* out, void* stream);
+
 }  // namespace psb

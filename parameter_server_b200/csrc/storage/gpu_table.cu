@@ -164,6 +164,14 @@ __global__ void get_rows_kernel(TableView t, const long long* keys, uint64_t n, 
         if (slot != kNoSlot && row < kRowPending) {
             const float* src = t.row_ptr(row);
             for (unsigned d = lane * 4; d < width; d += lanes * 4) *(float4*)(dst + d) = *(const float4*)(src + d);
+        } else if (slot != kNoSlot) {
+            // key without a backing row: its value is the initial one (same rule as the export kernel)
+            for (unsigned d = lane; d < width; d += lanes) {
+                float v = 0.f;
+                if (d < t.dim) v = init_uniform(keys[i], d, t.init_seed, t.init_range);
+                else if (d < t.dim * (1 + t.n_opt_slots)) v = t.slot_init[(d / t.dim - 1) < 2 ? (d / t.dim - 1) : 1];
+                dst[d] = v;
+            }
         } else {
             for (unsigned d = lane * 4; d < width; d += lanes * 4) *(float4*)(dst + d) = make_float4(0.f, 0.f, 0.f, 0.f);
         }

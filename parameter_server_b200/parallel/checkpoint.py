@@ -1,0 +1,90 @@
+"""Dump / load of a collective-path :class:`SparseTable` in the layout of the RPC path's DumpOperator.
+
+``dump(table, uri, file_number)`` writes ``<uri>/model_<rank>_<file>``; a record goes to file
+``shard % file_number`` of the rank that holds it (pico-ps/operator/DumpOperator.h:109-147). Files are
+in the binary record codec of ``csrc/operator/operators.h`` (header ``PSB1`` + u32 record width, then
+``int64 key, width * fp32`` per record), so dumps written by the RPC servers and by the collective path
+load into each other. ``load(table, uri)`` re-hashes: the ranks split the files of the directory
+between them, whatever number of nodes wrote them, and route every record to its owner under the
+table's current shard map as NVLink peer copies (pico-ps/operator/LoadOperator.h:87-143).
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..ops.sparse import SparseTable
+from .migrate import PeerInbox, route, stream_to_owners
+
+_MAGIC = b"PSB1"
+
+
+def _record_dtype(stride: int) -> np.dtype:
+    return np.dtype([("key", "<i8"), ("row", "<f4", (stride,))])
+
+
+def dump(table: SparseTable, uri: str, file_number: int = 1, batch: int = 1 << 18) -> int:
+    """Collective. Returns the number of records this rank wrote."""
+    path = uri.split("?", 1)[0]
+    os.makedirs(path, exist_ok=True)
+    stride = table.table.stride()
+    rec = _record_dtype(stride)
+    files = []
+    for f in range(file_number):
+        fh = open(os.path.join(path, f"model_{table.rank}_{f}"), "wb")
+        fh.write(_MAGIC + np.uint32(stride).tobytes())
+        files.append(fh)
+    written = 0
+    for keys, rows in table.export(batch=batch):
+        which = (route(table, keys, None) % file_number).cpu().numpy()
+        k, r = keys.cpu().numpy(), rows.cpu().numpy()
+        for f in range(file_number):
+            sel = which == f
+            m = int(sel.sum())
+            if m:
+                block = np.empty(m, dtype=rec)
+                block["key"], block["row"] = k[sel], r[sel]
+                block.tofile(files[f])
+                written += m
+    for fh in files:
+        fh.close()
+    if table.world > 1:
+        dist.barrier(group=table.group)
+    return written
+
+
+def _read_batches(paths, stride: int, batch: int, device):
+    rec = _record_dtype(stride)
+    for p in paths:
+        with open(p, "rb") as fh:
+            head = fh.read(8)
+            if head[:4] != _MAGIC or int(np.frombuffer(head[4:], dtype="<u4")[0]) != stride:
+                raise RuntimeError(f"{p}: not a PSB1 dump of record width {stride}")
+            while True:
+                block = np.fromfile(fh, dtype=rec, count=batch)
+                if block.size == 0:
+                    break
+                yield (torch.from_numpy(np.ascontiguousarray(block["key"])).to(device),
+                       torch.from_numpy(np.ascontiguousarray(block["row"])).to(device))
+
+
+def load(table: SparseTable, uri: str, batch: int = 1 << 18, inbox: Optional[PeerInbox] = None,
+         only_node: Optional[int] = None) -> int:
+    """Collective. Inserts every record of the dump at ``uri`` (of the files written by ``only_node`` when
+    given: the restore of one lost rank) into its owner's table; existing rows are overwritten. Returns
+    the number of records that landed on this rank."""
+    path = uri.split("?", 1)[0]
+    prefix = "model_" if only_node is None else f"model_{only_node}_"
+    names = sorted(n for n in os.listdir(path) if n.startswith(prefix))
+    mine = [os.path.join(path, n) for n in names[table.rank::table.world]]
+    owner_dev = torch.tensor(table.shard_owner, dtype=torch.int32, device=table.device)
+    inbox = inbox or PeerInbox(table, batch)
+    got, _ = stream_to_owners(table, _read_batches(mine, table.table.stride(), batch, table.device), owner_dev, inbox,
+                              keep_local=True)
+    if table.world > 1:
+        dist.barrier(group=table.group)
+    return got

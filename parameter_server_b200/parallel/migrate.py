@@ -23,7 +23,6 @@ import torch
 import torch.distributed as dist
 
 from .._lib import C
-from ..ops.dedup import KeyDeduper
 from ..ops.dense import _view
 from ..ops.sparse import SparseTable
 from ..utils.status import raise_if_error
@@ -52,6 +51,14 @@ class PeerInbox:
         keys = _view(base, self.cap, torch.int64, self.table.device, self.buf)
         rows = _view(base + self.cap * 8, self.cap * self.stride, torch.float32, self.table.device, self.buf).view(self.cap, self.stride)
         return keys, rows
+
+    def region_ptrs(self, owner_rank: int, src_rank: int):
+        """Raw device addresses (keys, rows) of the region of ``owner_rank``'s inbox that ``src_rank`` fills."""
+        base = (self.buf.peer(owner_rank) if self.world > 1 else self.buf.local()) + src_rank * self.cap * self.rec_bytes
+        return base, base + self.cap * 8
+
+    def keys_view(self, owner_rank: int, src_rank: int) -> torch.Tensor:
+        return self._region(owner_rank, src_rank)[0]
 
     def send(self, dst: int, keys: torch.Tensor, rows: torch.Tensor) -> None:
         n = keys.numel()
@@ -104,42 +111,116 @@ def _ship(table: SparseTable, inbox: PeerInbox, keys: torch.Tensor, rows: torch.
     return total
 
 
-def reshard(table: SparseTable, new_owner: Sequence[int], batch: int = 1 << 18) -> int:
+def route(table: SparseTable, keys: torch.Tensor, owner_dev: Optional[torch.Tensor]) -> torch.Tensor:
+    """Shard of every key (``owner_dev`` None) or the rank that owns it under the map ``owner_dev``."""
+    out = torch.empty(keys.numel(), dtype=torch.int32, device=table.device)
+    rc = C.shard_of_keys(keys.data_ptr(), keys.numel(), table.n_shards, 0 if owner_dev is None else owner_dev.data_ptr(),
+                         out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"shard_of_keys failed: {rc}")
+    return out
+
+
+def _any_rank(table: SparseTable, flag: bool) -> bool:
+    if table.world == 1:
+        return flag
+    t = torch.tensor([1 if flag else 0], device=table.device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=table.group)
+    return bool(t.item())
+
+
+def stream_to_owners(table: SparseTable, batches, owner_dev: torch.Tensor, inbox: PeerInbox, keep_local: bool):
+    """Drive ``batches`` (an iterator of ``(keys, rows)`` on this rank) to the owners under ``owner_dev``:
+    rows for other ranks travel as peer copies, rows that stay are inserted locally when ``keep_local``.
+    Every rank loops until all ranks are out of batches. Returns (rows received, keys that left)."""
+    rank = table.rank
+    stride = table.table.stride()
+    received, leaving = 0, []
+    it = iter(batches)
+    while True:
+        nxt = next(it, None)
+        if not _any_rank(table, nxt is not None):
+            break
+        if nxt is None:
+            keys = torch.empty(0, dtype=torch.int64, device=table.device)
+            rows = torch.empty((0, stride), device=table.device)
+        else:
+            keys, rows = nxt
+        dest = route(table, keys, owner_dev).long()
+        move = dest != rank
+        if keep_local and (~move).any():
+            table.set_rows(keys[~move], rows[~move], emb_only=False)
+            received += int((~move).sum().item())
+        leaving.append(keys[move])
+        received += _ship(table, inbox, keys[move], rows[move], dest[move])
+    return received, leaving
+
+
+def _leaving_keys(table: SparseTable, owner_dev: torch.Tensor) -> torch.Tensor:
+    """Keys held by this rank whose shard belongs to another rank under the map ``owner_dev`` (one scan of
+    the index, keys only)."""
+    n_local = table.size()
+    buf = torch.empty(max(n_local, 1), dtype=torch.int64, device=table.device)
+    st, n, _ = table.table.export_window(0, table.table.index_capacity(), 2, -1, table.rank, table.n_shards,
+                                         owner_dev.data_ptr(), buf.data_ptr(), 0, torch.cuda.current_stream().cuda_stream)
+    raise_if_error(st)
+    return buf[:n]
+
+
+def reshard(table: SparseTable, new_owner: Sequence[int], batch: int = 1 << 18, inbox: Optional[PeerInbox] = None) -> int:
     """Move every row whose shard changes hands to its new owner; returns the number of rows this rank
-    received. Pulls and pushes must not run concurrently (writes pause, as in the reference)."""
+    received. Pulls and pushes must not run concurrently (writes pause, as in the reference).
+
+    One index scan lists the keys that leave; they are sorted by destination and the per-pair totals are
+    exchanged once, so every rank knows the whole schedule. Then, per round, the row-fetch kernel writes
+    up to ``inbox.cap`` rows per destination straight into that rank's inbox over NVLink (peer stores),
+    and the destination inserts what arrived. The work is proportional to the rows that move, not to the
+    size of the table."""
     world, rank = table.world, table.rank
     new_owner = list(new_owner)
     owner_dev = torch.tensor(new_owner, dtype=torch.int32, device=table.device)
-    inbox = PeerInbox(table, batch)
-    dedup = KeyDeduper(batch, table.device)
-    received = 0
-    # export in windows so that one batch fits the inbox; every rank loops the same number of times
-    batches = list(table.export(batch=batch))
-    n_rounds = len(batches)
+    inbox = inbox or PeerInbox(table, batch)
+    cap = inbox.cap
+    stream = torch.cuda.current_stream().cuda_stream
+    leaving = _leaving_keys(table, owner_dev)
+    dest = route(table, leaving, owner_dev).long()
+    leaving = leaving[torch.argsort(dest, stable=True)]
+    send = torch.bincount(dest, minlength=world).tolist()
+    recv = _exchange_counts(table, send)
+    offs = [0] * world
+    for d in range(1, world):
+        offs[d] = offs[d - 1] + send[d - 1]
+    rounds = (max(send + [0]) + cap - 1) // cap
     if world > 1:
-        t = torch.tensor([n_rounds], device=table.device)
+        t = torch.tensor([rounds], device=table.device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=table.group)
-        n_rounds = int(t.item())
-    leaving: List[torch.Tensor] = []
-    for i in range(n_rounds):
-        if i < len(batches):
-            keys, rows = batches[i]
-            _, owner, inverse, _ = dedup(keys, owner_dev, world)
-            dest = owner[inverse.long()].long()
-            move = dest != rank
-            leaving.append(keys[move])
-            received += _ship(table, inbox, keys[move], rows[move], dest[move])
-        else:
-            empty_k = torch.empty(0, dtype=torch.int64, device=table.device)
-            empty_r = torch.empty((0, table.table.stride()), device=table.device)
-            received += _ship(table, inbox, empty_k, empty_r, torch.empty(0, dtype=torch.int64, device=table.device))
-    for k in leaving:
-        if k.numel():
-            table.erase_keys(k)       # purge: what moved away no longer belongs here
+        rounds = int(t.item())
+    found = torch.empty(cap, dtype=torch.int32, device=table.device)
+    for i in range(rounds):
+        for d in range(world):
+            n = min(cap, send[d] - i * cap)
+            if n > 0:
+                ks = leaving[offs[d] + i * cap: offs[d] + i * cap + n]
+                kptr, rptr = inbox.region_ptrs(d, rank)
+                inbox.keys_view(d, rank)[:n].copy_(ks)
+                raise_if_error(table.table.get_rows(ks.data_ptr(), n, rptr, found.data_ptr(), False, stream))
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier(group=table.group)        # every peer store has landed
+        for src in range(world):
+            n = min(cap, recv[src] - i * cap)
+            if n > 0:
+                k, r = inbox.received(src, n)
+                table.set_rows(k, r, emb_only=False)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier(group=table.group)        # the inboxes may be overwritten again
+    if leaving.numel():
+        table.erase_keys(leaving)                  # purge: what moved away no longer belongs here
     table.set_shard_owner(new_owner)
     if world > 1:
         dist.barrier(group=table.group)
-    return received
+    return sum(recv)
 
 
 class ReplicaSet:

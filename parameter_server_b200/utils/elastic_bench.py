@@ -1,0 +1,196 @@
+"""Elastic rescaling + HA benchmark of the collective path (benchmark config 5).
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29533 \\
+        -m parameter_server_b200.utils.elastic_bench --keys 134217728
+
+A table of ``--keys`` int64 keys (dim 32 fp32 + FTRL z / n slots) is first served by half of the ranks.
+Under a pull + push load of Zipf(1.1) batches (``--batch`` keys per GPU per step) it is rebalanced onto
+all ranks in ``--stages`` steps of shard migration over NVLink peer copies, with load steps between the
+stages. Then every rank's shards are mirrored on a neighbour (2x replication, full + incremental sync),
+one rank loses its table (its contents are cleared on the host side, as if its process had been
+replaced) and is restored from the mirror, and once more from a dump. Every time is taken with CUDA
+events around the operation on each rank, maximum over ranks; rank 0 prints one JSON line.
+
+The reference does the same through UpdateContextHandler / RestoreOperator / LoadOperator on CPU servers
+(pico-ps/handler/UpdateContextHandler.cpp:62-153, pico-ps/operator/RestoreOperator.h:94-151).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import tempfile
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--keys", type=int, default=1 << 27)
+    ap.add_argument("--batch", type=int, default=1 << 19)
+    ap.add_argument("--stages", type=int, default=4)
+    ap.add_argument("--steps", type=int, default=10, help="load steps per measurement window")
+    ap.add_argument("--lost-rank", type=int, default=1)
+    ap.add_argument("--dump-dir", default="")
+    a = ap.parse_args()
+
+    from parameter_server_b200 import SparseTable
+    from parameter_server_b200.utils.keys import zipf_batch
+    from parameter_server_b200.parallel import PeerInbox, ReplicaSet, checkpoint, reshard
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank = dist.get_rank() if world > 1 else 0
+    dev = torch.device("cuda", local)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def rank_max(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def rank_sum(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    def timed(fn):
+        """fn() bracketed by barrier + CUDA events; milliseconds, max over ranks. Returns (ms, result)."""
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        r = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return rank_max(e0.elapsed_time(e1)), r
+
+    K, B = a.keys, a.batch
+    serving0 = max(1, world // 2)
+    n_shards = 8 * world
+    owner0 = [s % serving0 for s in range(n_shards)]
+    owner1 = [s % world for s in range(n_shards)]
+    t = SparseTable(32, "ftrl", dict(lr=0.05), n_shards=n_shards, capacity=int(K / serving0 * 1.15) + (1 << 16),
+                    max_keys=B, wait_limit_s=20.0, pair_capacity=min(B, B // serving0 + B // 16 + 4096))
+    t.set_shard_owner(owner0)
+    stride_bytes = t.table.stride() * 4 + 8
+
+    # ---- populate: rank r inserts the keys r, r + world, ... --------------------------------------
+    out = torch.empty(B, 32, device=dev)
+    if rank < serving0:
+        t.reserve(int(K / serving0 * 1.02) + B)
+
+    def populate():
+        per = (K + world - 1) // world
+        for lo in range(0, per, B):
+            n = min(B, per - lo)
+            ks = (torch.arange(lo, lo + n, device=dev, dtype=torch.int64) * world + rank).clamp_(max=K - 1)
+            if n < B:
+                ks = torch.cat([ks, ks[-1:].expand(B - n)])
+            t.pull(ks, out=out, for_push=False)
+    pop_ms, _ = timed(populate)
+    t.check()
+    rows_total = int(rank_sum(t.size()))
+
+    # ---- load generator ---------------------------------------------------------------------------
+    rng = np.random.default_rng(100 + rank)
+    pool = []
+    for _ in range(4):
+        pool.append(torch.from_numpy(zipf_batch(rng, B, 1.1, K)).to(dev))
+    grads = torch.randn(B, 32, device=dev) * 1e-3
+    it = [0]
+
+    def load_steps(n):
+        for _ in range(n):
+            t.pull(pool[it[0] % 4], out=out)
+            t.push(grads)
+            it[0] += 1
+
+    def throughput(n):
+        ms, _ = timed(lambda: load_steps(n))
+        t.check()
+        return 2.0 * B * world * n / (ms / 1e3)
+
+    load_steps(3)
+    res = {"metric": "elastic_rescale_and_restore", "n_gpus": world, "keys": K, "rows_in_table": rows_total, "dim": 32,
+           "optimizer": "ftrl", "batch_per_gpu": B, "n_shards": n_shards, "populate_ms": pop_ms,
+           "keys_per_sec_before": throughput(a.steps)}
+
+    # ---- rebalance serving0 -> world ranks in stages, load running between the stages ---------------
+    inbox = PeerInbox(t, 1 << 20)
+    moving = [s for s in range(n_shards) if owner0[s] != owner1[s]]
+    cur = list(owner0)
+    stage_ms, during = [], []
+    moved_rows = 0
+    for j in range(a.stages):
+        for s in moving[j::a.stages]:
+            cur[s] = owner1[s]
+        ms, got = timed(lambda: reshard(t, cur, batch=1 << 20, inbox=inbox))
+        moved_rows += int(rank_sum(got))
+        stage_ms.append(ms)
+        during.append(throughput(max(2, a.steps // 2)))
+    res.update({"rebalance_ms_total": sum(stage_ms), "rebalance_stage_ms": stage_ms, "rows_moved": moved_rows,
+                "rebalance_gbytes": moved_rows * stride_bytes / 1e9,
+                "rebalance_gbytes_per_sec": moved_rows * stride_bytes / 1e9 / (sum(stage_ms) / 1e3),
+                "keys_per_sec_between_stages": during, "keys_per_sec_after": throughput(a.steps),
+                "rows_after": int(rank_sum(t.size()))})
+
+    # ---- 2x replication: full mirror, then incremental -------------------------------------------
+    rs = ReplicaSet(t, batch=1 << 20)
+    ms, sent = timed(rs.sync)
+    res.update({"replica_full_sync_ms": ms, "replica_full_sync_rows": int(rank_sum(sent))})
+    load_steps(2)
+    ms, sent = timed(rs.sync)
+    res.update({"replica_incremental_sync_ms": ms, "replica_incremental_rows": int(rank_sum(sent))})
+
+    # ---- one rank loses its table; restore from the mirror -----------------------------------------
+    lost = a.lost_rank % world
+    probe = pool[0][:4096]
+    want = t.pull(probe, out=out[:4096].clone(), insert=False, for_push=False).clone()
+    size_lost = t.size()
+    dump_dir = [a.dump_dir or (tempfile.mkdtemp(prefix="psb_elastic_") if rank == 0 else None)]
+    if world > 1:
+        dist.broadcast_object_list(dump_dir, src=0)
+    ms, _ = timed(lambda: checkpoint.dump(t, dump_dir[0], file_number=2))
+    res["dump_ms"] = ms
+    if rank == lost:
+        t.clear()
+    ms, got = timed(lambda: rs.restore(lost))
+    ok = bool(torch.equal(t.pull(probe, out=out[:4096].clone(), insert=False, for_push=False), want)) and t.size() == size_lost
+    res.update({"restore_from_replica_ms": ms, "restore_rows": int(rank_sum(got)), "restore_from_replica_exact": bool(rank_sum(0.0 if ok else 1.0) == 0),
+                "keys_per_sec_after_restore": throughput(a.steps)})
+
+    # ---- and from the dump (only the lost rank's files are read, the ranks share the work) ------------
+    want = t.pull(probe, out=out[:4096].clone(), insert=False, for_push=False).clone()
+    ms2, _ = timed(lambda: checkpoint.dump(t, dump_dir[0], file_number=2))
+    size_lost = t.size()
+    if rank == lost:
+        t.clear()
+    ms, got = timed(lambda: checkpoint.load(t, dump_dir[0], batch=1 << 20, inbox=inbox, only_node=lost))
+    ok = bool(torch.equal(t.pull(probe, out=out[:4096].clone(), insert=False, for_push=False), want)) and t.size() == size_lost
+    res.update({"restore_from_dump_ms": ms, "restore_from_dump_exact": bool(rank_sum(0.0 if ok else 1.0) == 0)})
+    t.check()
+    barrier()
+    if rank == 0:
+        if not a.dump_dir:
+            shutil.rmtree(dump_dir[0], ignore_errors=True)
+        print(json.dumps(res))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,115 @@
+"""Sparse key-value micro-benchmark over 1..8 GPUs (benchmark config 2).
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29534 \\
+        -m parameter_server_b200.utils.sparse_bench --rows-per-gpu 62500000 --impl ours
+
+One table of ``world * rows-per-gpu`` int64 keys (62.5 M per GPU = 500 M keys on 8 GPUs), dim 64 fp32 +
+an Adagrad slot, sharded by key hash and populated before anything is timed. Pull and pull+push key
+throughput over batch sizes 64 Ki .. 4 Mi keys per GPU per step; keys Zipf(1.05) over the whole table
+at least 30 % of the positions of a batch repeat another key of the batch (Zipf alone already gives more). CUDA events
+on the launching stream, maximum over ranks; the batches rotate through four different key sets and the
+rows touched per step exceed L2 from 256 Ki keys up. ``--impl nccl`` runs the NCCL-only baseline
+(torch.unique + all_to_all_single) on the same table code. Rank 0 prints one JSON line per batch size.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--rows-per-gpu", type=int, default=1 << 24)
+    ap.add_argument("--sizes", default="65536,262144,1048576,4194304")
+    ap.add_argument("--impl", default="ours", choices=["ours", "nccl"])
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args()
+
+    from parameter_server_b200 import SparseTable
+    from parameter_server_b200.parallel import NcclSparseTable
+    from parameter_server_b200.utils.keys import zipf_batch
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank = dist.get_rank() if world > 1 else 0
+    dev = torch.device("cuda", local)
+    sizes = [int(s) for s in a.sizes.split(",")]
+    nmax = max(sizes)
+    K = a.rows_per_gpu * world
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def rank_max(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    cls = SparseTable if a.impl == "ours" else NcclSparseTable
+    t = cls(64, "adagrad", dict(lr=0.05, init_accumulator=0.1), capacity=int(a.rows_per_gpu * 1.1) + nmax, max_keys=nmax, seed=3)
+    t.reserve(int(a.rows_per_gpu * 1.05) + nmax)
+    out = torch.empty(nmax, 64, device=dev)
+    grads = torch.randn(nmax, 64, device=dev) * 1e-3
+    # populate: rank r inserts keys r, r + world, ...
+    for lo in range(0, a.rows_per_gpu, nmax):
+        n = min(nmax, a.rows_per_gpu - lo)
+        ks = torch.arange(lo, lo + n, device=dev, dtype=torch.int64) * world + rank
+        t.pull(ks, out=out[:n], for_push=False)
+    t.check()
+    barrier()
+    rows = int(rank_max(t.size()))
+
+    rng = np.random.default_rng(77 + rank)
+    for n in sizes:
+        pool = []
+        for _ in range(4):
+            k = zipf_batch(rng, n, 1.05, K, 0.3)
+            pool.append(torch.from_numpy(k).to(dev))
+        uniq = float(np.mean([torch.unique(p).numel() / n for p in pool]))
+        o, g = out[:n], grads[:n]
+        for i in range(a.warmup):
+            t.pull(pool[i % 4], out=o)
+            t.push(g)
+        t.check()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for i in range(a.steps):
+            t.pull(pool[i % 4], out=o, for_push=False)
+        e1.record()
+        torch.cuda.synchronize()
+        pull_ms = rank_max(e0.elapsed_time(e1)) / a.steps
+        barrier()
+        e0.record()
+        for i in range(a.steps):
+            t.pull(pool[i % 4], out=o)
+            t.push(g)
+        e1.record()
+        torch.cuda.synchronize()
+        both_ms = rank_max(e0.elapsed_time(e1)) / a.steps
+        t.check()
+        if rank == 0:
+            print(json.dumps({"metric": "sparse_pull_push_keys_per_sec", "impl": a.impl, "n_gpus": world, "keys_per_gpu_per_step": n,
+                              "table_rows_max_per_gpu": rows, "table_keys": K, "dim": 64, "optimizer": "adagrad", "zipf_s": 1.05,
+                              "unique_fraction": uniq, "pull_ms": pull_ms, "pull_push_ms": both_ms,
+                              "pull_keys_per_sec": n * world / (pull_ms / 1e3),
+                              "pull_push_keys_per_sec": 2 * n * world / (both_ms / 1e3)}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

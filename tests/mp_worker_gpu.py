@@ -141,8 +141,22 @@ def main():
         again = t.pull(keys, insert=False)
         t.check()
         assert torch.equal(again, want)
+        # dump with 2 files per rank, load into a table with another shard count (rehash) and from all ranks' files
+        from parameter_server_b200.parallel import checkpoint
+        import tempfile
+        box = [tempfile.mkdtemp(prefix="psb_dump_") if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        assert checkpoint.dump(t, box[0], file_number=2) == t.size()
+        t2 = SparseTable(32, "adagrad", dict(lr=0.05, init_accumulator=0.1), n_shards=3 * world, capacity=1 << 16,
+                         max_keys=1 << 15, wait_limit_s=5.0)
+        checkpoint.load(t2, box[0])
+        assert sum(gather(t2.size())) == total_before
+        assert torch.equal(t2.pull(keys, insert=False), want)
+        t2.check()
         dist.barrier()
         if rank == 0:
+            import shutil
+            shutil.rmtree(box[0], ignore_errors=True)
             print("migrate ok", flush=True)
 
     if which in ("all", "aggemm"):

@@ -1,4 +1,5 @@
 """Single-GPU fused pull / push against the CPU oracle (plain fp32 reference of the same op)."""
+import os
 import numpy as np
 import pytest
 import torch
@@ -198,3 +199,22 @@ def test_cold_tier_spill_fetch_and_persistence(tmp_path):
     assert found.all()
     assert torch.equal(rows, torch.cat([full[:100], full[4000:4500]]))
     assert t.spill_keys(hot[:10]) == 10 and t.size() == 4490
+
+
+def test_collective_dump_load_rehash_and_rpc_codec(tmp_path):
+    from parameter_server_b200.parallel import checkpoint
+    t = SparseTable(16, "ftrl", dict(lr=0.05), device="cuda", n_shards=4, capacity=1 << 14, max_keys=1 << 13)
+    keys = torch.randint(0, 1 << 40, (5000,), device="cuda")
+    t.pull(keys); t.push(torch.randn(5000, 16, device="cuda") * 1e-2); t.check()
+    uniq = torch.unique(keys)
+    want, _ = t.get_rows(uniq, emb_only=False)
+    assert checkpoint.dump(t, str(tmp_path / "d"), file_number=3) == t.size()
+    assert sorted(os.listdir(tmp_path / "d")) == ["model_0_0", "model_0_1", "model_0_2"]
+    t2 = SparseTable(16, "ftrl", dict(lr=0.05), device="cuda", n_shards=7, capacity=1 << 14, max_keys=1 << 13)
+    assert checkpoint.load(t2, str(tmp_path / "d")) == t.size()
+    got, found = t2.get_rows(uniq, emb_only=False)
+    assert found.all() and torch.equal(got, want)
+    # the files are the RPC path's binary codec: a host table behind the service layer's reader gets the same rows
+    raw = open(tmp_path / "d" / "model_0_0", "rb").read()
+    assert raw[:4] == b"PSB1" and int.from_bytes(raw[4:8], "little") == t.table.stride()
+    assert (len(raw) - 8) % (8 + 4 * t.table.stride()) == 0
