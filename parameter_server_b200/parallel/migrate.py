@@ -156,71 +156,81 @@ def stream_to_owners(table: SparseTable, batches, owner_dev: torch.Tensor, inbox
     return received, leaving
 
 
-def _leaving_keys(table: SparseTable, owner_dev: torch.Tensor) -> torch.Tensor:
-    """Keys held by this rank whose shard belongs to another rank under the map ``owner_dev`` (one scan of
-    the index, keys only)."""
+def _scan_keys(table: SparseTable, mode: int, owner_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Keys of this rank's table that pass an index scan filter, keys only, one kernel: mode 0 = all,
+    2 = keys whose shard belongs to another rank under the map ``owner_dev``, 4 = rows changed since the
+    dirty bits were last cleared."""
     n_local = table.size()
     buf = torch.empty(max(n_local, 1), dtype=torch.int64, device=table.device)
-    st, n, _ = table.table.export_window(0, table.table.index_capacity(), 2, -1, table.rank, table.n_shards,
-                                         owner_dev.data_ptr(), buf.data_ptr(), 0, torch.cuda.current_stream().cuda_stream)
+    st, n, _ = table.table.export_window(0, table.table.index_capacity(), mode, -1, table.rank, table.n_shards,
+                                         0 if owner_dev is None else owner_dev.data_ptr(), buf.data_ptr(), 0,
+                                         torch.cuda.current_stream().cuda_stream)
     raise_if_error(st)
     return buf[:n]
 
 
-def reshard(table: SparseTable, new_owner: Sequence[int], batch: int = 1 << 18, inbox: Optional[PeerInbox] = None) -> int:
-    """Move every row whose shard changes hands to its new owner; returns the number of rows this rank
-    received. Pulls and pushes must not run concurrently (writes pause, as in the reference).
-
-    One index scan lists the keys that leave; they are sorted by destination and the per-pair totals are
-    exchanged once, so every rank knows the whole schedule. Then, per round, the row-fetch kernel writes
-    up to ``inbox.cap`` rows per destination straight into that rank's inbox over NVLink (peer stores),
-    and the destination inserts what arrived. The work is proportional to the rows that move, not to the
-    size of the table."""
-    world, rank = table.world, table.rank
-    new_owner = list(new_owner)
-    owner_dev = torch.tensor(new_owner, dtype=torch.int32, device=table.device)
-    inbox = inbox or PeerInbox(table, batch)
+def exchange_by_keys(source: SparseTable, keys: torch.Tensor, send: List[int], inbox: PeerInbox, target: SparseTable,
+                     comm: SparseTable) -> int:
+    """Ship the rows of ``keys`` (sorted by destination rank, ``send[d]`` of them for rank ``d``) from the
+    local table ``source`` into the tables ``target`` of their destinations. Collective over ``comm``'s
+    group. The per-pair totals are exchanged once, so every rank knows the whole schedule; per round the
+    row-fetch kernel writes up to ``inbox.cap`` rows per destination straight into that rank's inbox
+    over NVLink (peer stores) and the destination inserts what arrived. Returns rows received."""
+    world, rank = comm.world, comm.rank
     cap = inbox.cap
     stream = torch.cuda.current_stream().cuda_stream
-    leaving = _leaving_keys(table, owner_dev)
-    dest = route(table, leaving, owner_dev).long()
-    leaving = leaving[torch.argsort(dest, stable=True)]
-    send = torch.bincount(dest, minlength=world).tolist()
-    recv = _exchange_counts(table, send)
+    recv = _exchange_counts(comm, send)
     offs = [0] * world
     for d in range(1, world):
         offs[d] = offs[d - 1] + send[d - 1]
     rounds = (max(send + [0]) + cap - 1) // cap
     if world > 1:
-        t = torch.tensor([rounds], device=table.device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=table.group)
+        t = torch.tensor([rounds], device=comm.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=comm.group)
         rounds = int(t.item())
-    found = torch.empty(cap, dtype=torch.int32, device=table.device)
+    found = torch.empty(cap, dtype=torch.int32, device=comm.device)
     for i in range(rounds):
         for d in range(world):
             n = min(cap, send[d] - i * cap)
             if n > 0:
-                ks = leaving[offs[d] + i * cap: offs[d] + i * cap + n]
-                kptr, rptr = inbox.region_ptrs(d, rank)
+                ks = keys[offs[d] + i * cap: offs[d] + i * cap + n]
+                _, rptr = inbox.region_ptrs(d, rank)
                 inbox.keys_view(d, rank)[:n].copy_(ks)
-                raise_if_error(table.table.get_rows(ks.data_ptr(), n, rptr, found.data_ptr(), False, stream))
+                raise_if_error(source.table.get_rows(ks.data_ptr(), n, rptr, found.data_ptr(), False, stream))
         torch.cuda.synchronize()
         if world > 1:
-            dist.barrier(group=table.group)        # every peer store has landed
+            dist.barrier(group=comm.group)        # every peer store has landed
         for src in range(world):
             n = min(cap, recv[src] - i * cap)
             if n > 0:
                 k, r = inbox.received(src, n)
-                table.set_rows(k, r, emb_only=False)
+                target.set_rows(k, r, emb_only=False)
         torch.cuda.synchronize()
         if world > 1:
-            dist.barrier(group=table.group)        # the inboxes may be overwritten again
+            dist.barrier(group=comm.group)        # the inboxes may be overwritten again
+    return sum(recv)
+
+
+def reshard(table: SparseTable, new_owner: Sequence[int], batch: int = 1 << 18, inbox: Optional[PeerInbox] = None) -> int:
+    """Move every row whose shard changes hands to its new owner; returns the number of rows this rank
+    received. Pulls and pushes must not run concurrently (writes pause, as in the reference). One index
+    scan lists the keys that leave, they are sorted by destination and shipped with
+    :func:`exchange_by_keys`: the work is proportional to the rows that move, not to the table."""
+    world = table.world
+    new_owner = list(new_owner)
+    owner_dev = torch.tensor(new_owner, dtype=torch.int32, device=table.device)
+    inbox = inbox or PeerInbox(table, batch)
+    leaving = _scan_keys(table, 2, owner_dev)
+    dest = route(table, leaving, owner_dev).long()
+    leaving = leaving[torch.argsort(dest, stable=True)]
+    send = torch.bincount(dest, minlength=world).tolist()
+    received = exchange_by_keys(table, leaving, send, inbox, table, table)
     if leaving.numel():
         table.erase_keys(leaving)                  # purge: what moved away no longer belongs here
     table.set_shard_owner(new_owner)
     if world > 1:
         dist.barrier(group=table.group)
-    return sum(recv)
+    return received
 
 
 class ReplicaSet:
@@ -239,45 +249,28 @@ class ReplicaSet:
         self.mirrored = (self.rank - 1) % self.world     # whose rows my mirror holds
         self._full_next = True                           # the first sync ships everything
 
-    def _rounds(self, n_local: int) -> int:
-        if self.world == 1:
-            return n_local
-        t = torch.tensor([n_local], device=self.table.device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.table.group)
-        return int(t.item())
+    def _one_dest(self, n: int, dest: int) -> List[int]:
+        send = [0] * self.world
+        send[dest] = n
+        return send
 
     def sync(self) -> int:
         """Ship the rows that changed since the last sync (everything, the first time) to the partner's
         mirror. Returns rows sent."""
         t = self.table
-        batches = list(t.export(batch=self.batch, dirty_only=not self._full_next))
+        keys = _scan_keys(t, 0 if self._full_next else 4)
         self._full_next = False
-        sent = 0
-        for i in range(self._rounds(len(batches))):
-            if i < len(batches):
-                keys, rows = batches[i]
-            else:
-                keys = torch.empty(0, dtype=torch.int64, device=t.device)
-                rows = torch.empty((0, t.table.stride()), device=t.device)
-            dest = torch.full((keys.numel(),), self.partner, dtype=torch.int64, device=t.device)
-            _ship(t, self.inbox, keys, rows, dest, target=self.mirror)
-            sent += keys.numel()
+        exchange_by_keys(t, keys, self._one_dest(keys.numel(), self.partner), self.inbox, self.mirror, t)
         raise_if_error(t.table.clear_dirty(torch.cuda.current_stream().cuda_stream))
-        return sent
+        return int(keys.numel())
 
     def restore(self, lost_rank: int) -> int:
         """Refill the primary table of ``lost_rank`` (cleared, e.g. after its process was replaced) from
         the mirror kept by its partner. Collective. Returns rows restored on ``lost_rank``."""
         t = self.table
         holder = (lost_rank + 1) % self.world
-        batches = list(self.mirror.export(batch=self.batch)) if self.rank == holder else []
-        got = 0
-        for i in range(self._rounds(len(batches))):
-            if i < len(batches):
-                keys, rows = batches[i]
-            else:
-                keys = torch.empty(0, dtype=torch.int64, device=t.device)
-                rows = torch.empty((0, t.table.stride()), device=t.device)
-            dest = torch.full((keys.numel(),), lost_rank, dtype=torch.int64, device=t.device)
-            got += _ship(t, self.inbox, keys, rows, dest)
-        return got
+        if self.rank == holder:
+            keys = _scan_keys(self.mirror, 0)
+        else:
+            keys = torch.empty(0, dtype=torch.int64, device=t.device)
+        return exchange_by_keys(self.mirror, keys, self._one_dest(keys.numel(), lost_rank), self.inbox, t, t)

@@ -131,6 +131,9 @@ def main() -> None:
 
     # ---- rebalance serving0 -> world ranks in stages, load running between the stages ---------------
     inbox = PeerInbox(t, 1 << 20)
+    # the joining ranks allocate their row pools first (the create-storage step of a scale-out), timed on its own
+    ms, _ = timed(lambda: t.reserve(int(K / world * 1.1) + B) if rank >= serving0 else None)
+    res["joining_ranks_alloc_ms"] = ms
     moving = [s for s in range(n_shards) if owner0[s] != owner1[s]]
     cur = list(owner0)
     stage_ms, during = [], []
