@@ -211,25 +211,44 @@ def exchange_by_keys(source: SparseTable, keys: torch.Tensor, send: List[int], i
     return sum(recv)
 
 
-def reshard(table: SparseTable, new_owner: Sequence[int], batch: int = 1 << 18, inbox: Optional[PeerInbox] = None) -> int:
+def reshard(table: SparseTable, new_owner: Sequence[int], batch: int = 1 << 18, inbox: Optional[PeerInbox] = None,
+            stats: Optional[dict] = None) -> int:
     """Move every row whose shard changes hands to its new owner; returns the number of rows this rank
     received. Pulls and pushes must not run concurrently (writes pause, as in the reference). One index
     scan lists the keys that leave, they are sorted by destination and shipped with
-    :func:`exchange_by_keys`: the work is proportional to the rows that move, not to the table."""
+    :func:`exchange_by_keys`: the work is proportional to the rows that move, not to the table.
+    ``stats`` (optional) receives the host-side duration of each phase in milliseconds."""
+    import time
     world = table.world
+    marks = []
+
+    def mark(name):
+        if stats is not None:
+            torch.cuda.synchronize()
+            marks.append((name, time.perf_counter()))
+
+    mark("start")
     new_owner = list(new_owner)
     owner_dev = torch.tensor(new_owner, dtype=torch.int32, device=table.device)
     inbox = inbox or PeerInbox(table, batch)
     leaving = _scan_keys(table, 2, owner_dev)
+    mark("scan")
     dest = route(table, leaving, owner_dev).long()
     leaving = leaving[torch.argsort(dest, stable=True)]
     send = torch.bincount(dest, minlength=world).tolist()
+    mark("sort")
     received = exchange_by_keys(table, leaving, send, inbox, table, table)
+    mark("exchange")
     if leaving.numel():
         table.erase_keys(leaving)                  # purge: what moved away no longer belongs here
+    mark("purge")
     table.set_shard_owner(new_owner)
     if world > 1:
         dist.barrier(group=table.group)
+    mark("swap")
+    if stats is not None:
+        for (_, t0), (name, t1) in zip(marks, marks[1:]):
+            stats[name] = stats.get(name, 0.0) + (t1 - t0) * 1e3
     return received
 
 

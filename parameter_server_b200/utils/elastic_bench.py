@@ -35,6 +35,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=10, help="load steps per measurement window")
     ap.add_argument("--lost-rank", type=int, default=1)
     ap.add_argument("--dump-dir", default="")
+    ap.add_argument("--no-dump", action="store_true", help="skip the dump / restore-from-dump part (it writes the whole table to disk)")
     a = ap.parse_args()
 
     from parameter_server_b200 import SparseTable
@@ -136,16 +137,18 @@ def main() -> None:
     res["joining_ranks_alloc_ms"] = ms
     moving = [s for s in range(n_shards) if owner0[s] != owner1[s]]
     cur = list(owner0)
-    stage_ms, during = [], []
+    stage_ms, during, phases = [], [], []
     moved_rows = 0
     for j in range(a.stages):
         for s in moving[j::a.stages]:
             cur[s] = owner1[s]
-        ms, got = timed(lambda: reshard(t, cur, batch=1 << 20, inbox=inbox))
+        st = {}
+        ms, got = timed(lambda: reshard(t, cur, batch=1 << 20, inbox=inbox, stats=st))
+        phases.append({k: round(v, 2) for k, v in st.items()})
         moved_rows += int(rank_sum(got))
         stage_ms.append(ms)
         during.append(throughput(max(2, a.steps // 2)))
-    res.update({"rebalance_ms_total": sum(stage_ms), "rebalance_stage_ms": stage_ms, "rows_moved": moved_rows,
+    res.update({"rebalance_ms_total": sum(stage_ms), "rebalance_stage_ms": stage_ms, "rebalance_stage_phases_rank0_ms": phases, "rows_moved": moved_rows,
                 "rebalance_gbytes": moved_rows * stride_bytes / 1e9,
                 "rebalance_gbytes_per_sec": moved_rows * stride_bytes / 1e9 / (sum(stage_ms) / 1e3),
                 "keys_per_sec_between_stages": during, "keys_per_sec_after": throughput(a.steps),
@@ -167,8 +170,6 @@ def main() -> None:
     dump_dir = [a.dump_dir or (tempfile.mkdtemp(prefix="psb_elastic_") if rank == 0 else None)]
     if world > 1:
         dist.broadcast_object_list(dump_dir, src=0)
-    ms, _ = timed(lambda: checkpoint.dump(t, dump_dir[0], file_number=2))
-    res["dump_ms"] = ms
     if rank == lost:
         t.clear()
     ms, got = timed(lambda: rs.restore(lost))
@@ -176,15 +177,17 @@ def main() -> None:
     res.update({"restore_from_replica_ms": ms, "restore_rows": int(rank_sum(got)), "restore_from_replica_exact": bool(rank_sum(0.0 if ok else 1.0) == 0),
                 "keys_per_sec_after_restore": throughput(a.steps)})
 
-    # ---- and from the dump (only the lost rank's files are read, the ranks share the work) ------------
-    want = t.pull(probe, out=out[:4096].clone(), insert=False, for_push=False).clone()
-    ms2, _ = timed(lambda: checkpoint.dump(t, dump_dir[0], file_number=2))
-    size_lost = t.size()
-    if rank == lost:
-        t.clear()
-    ms, got = timed(lambda: checkpoint.load(t, dump_dir[0], batch=1 << 20, inbox=inbox, only_node=lost))
-    ok = bool(torch.equal(t.pull(probe, out=out[:4096].clone(), insert=False, for_push=False), want)) and t.size() == size_lost
-    res.update({"restore_from_dump_ms": ms, "restore_from_dump_exact": bool(rank_sum(0.0 if ok else 1.0) == 0)})
+    # ---- and from a dump (only the lost rank's files are read, the ranks share the work) ---------------
+    if not a.no_dump:
+        want = t.pull(probe, out=out[:4096].clone(), insert=False, for_push=False).clone()
+        ms, _ = timed(lambda: checkpoint.dump(t, dump_dir[0], file_number=2))
+        res["dump_ms"] = ms
+        size_lost = t.size()
+        if rank == lost:
+            t.clear()
+        ms, got = timed(lambda: checkpoint.load(t, dump_dir[0], batch=1 << 20, inbox=inbox, only_node=lost))
+        ok = bool(torch.equal(t.pull(probe, out=out[:4096].clone(), insert=False, for_push=False), want)) and t.size() == size_lost
+        res.update({"restore_from_dump_ms": ms, "restore_from_dump_exact": bool(rank_sum(0.0 if ok else 1.0) == 0)})
     t.check()
     barrier()
     if rank == 0:
