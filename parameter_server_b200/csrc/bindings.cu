@@ -123,6 +123,7 @@ PYBIND11_MODULE(_C, m) {
         .def("index_capacity", &GpuTable::index_capacity)
         .def("tombstones", &GpuTable::tombstones)
         .def("reserve_rows", &GpuTable::reserve_rows)
+        .def("reserve_exact", &GpuTable::reserve_exact)
         .def("enable_dirty_tracking", &GpuTable::enable_dirty_tracking)
         .def("clear_dirty", [](GpuTable& t, uintptr_t s) { return t.clear_dirty(stream_of(s)); })
         .def("export_window",

@@ -384,6 +384,13 @@ Status GpuTable::reserve_rows(uint64_t n) {
     return Status::Ok();
 }
 
+Status GpuTable::reserve_exact(uint64_t n_new) {
+    // Explicit pre-allocation: reads the counters synchronously, so no margin for calls in flight is needed.
+    const uint64_t need = rows_used() + n_new;
+    while (need > rows_avail_) PSB_RETURN_IF_ERROR(add_slab());
+    return Status::Ok();
+}
+
 void GpuTable::refresh_usage_async(void* stream) {
     cudaMemcpyAsync((void*)host_mirror_, scratch_ + 1, 16, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
 }

@@ -64,6 +64,8 @@ public:
 
     // Make sure `n` more rows can be attached without running out; grows the pool by slabs.
     Status reserve_rows(uint64_t n);
+    // Room for exactly n_new more rows than are in use now (synchronous; for explicit pre-allocation).
+    Status reserve_exact(uint64_t n_new);
     // Enqueue a copy of the allocation counters into pinned host memory (read by reserve_rows).
     void refresh_usage_async(void* stream);
     TableView view() const;

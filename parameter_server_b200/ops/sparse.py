@@ -215,11 +215,14 @@ class SparseTable:
         else:
             raise_if_error(self.table.store(self.opt))
 
-    def reserve(self, n_new_rows: int) -> None:
+    def reserve(self, n_new_rows: int, exact: bool = False) -> None:
         """Make room for ``n_new_rows`` more rows now (grows the slab pool on the host). Needed before
-        a pull is captured in, or replayed from, a CUDA graph, where the call itself cannot allocate."""
+        a pull is captured in, or replayed from, a CUDA graph, where the call itself cannot allocate.
+        The default never blocks: it reads counters that the device mirrored to pinned memory and adds a
+        3x margin for calls still in flight. ``exact=True`` reads the counters synchronously and
+        allocates exactly what is asked (for sizing a table up front)."""
         if self.is_cuda:
-            st = self.table.reserve_rows(int(n_new_rows))
+            st = self.table.reserve_exact(int(n_new_rows)) if exact else self.table.reserve_rows(int(n_new_rows))
             if not st.ok() and st.code() != C.StatusCode.OUT_OF_MEMORY:
                 raise_if_error(st)
 

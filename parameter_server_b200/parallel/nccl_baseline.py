@@ -86,8 +86,8 @@ class NcclSparseTable:
         if recv_keys.numel():
             self.local.push(recv, keys=recv_keys)   # the local engine merges keys that several ranks sent
 
-    def reserve(self, n: int) -> None:
-        self.local.reserve(n)
+    def reserve(self, n: int, exact: bool = False) -> None:
+        self.local.reserve(n, exact)
 
     def check(self) -> None:
         self.local.check()

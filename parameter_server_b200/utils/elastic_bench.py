@@ -6,7 +6,7 @@
 A table of ``--keys`` int64 keys (dim 32 fp32 + FTRL z / n slots) is first served by half of the ranks.
 Under a pull + push load of Zipf(1.1) batches (``--batch`` keys per GPU per step) it is rebalanced onto
 all ranks in ``--stages`` steps of shard migration over NVLink peer copies, with load steps between the
-stages. Then every rank's shards are mirrored on a neighbour (2x replication, full + incremental sync),
+stages (one-time start-up costs of the joining ranks are paid in a warm-up and reported separately). Then every rank's shards are mirrored on a neighbour (2x replication, full + incremental sync),
 one rank loses its table (its contents are cleared on the host side, as if its process had been
 replaced) and is restored from the mirror, and once more from a dump. Every time is taken with CUDA
 events around the operation on each rank, maximum over ranks; rank 0 prints one JSON line.
@@ -92,7 +92,7 @@ def main() -> None:
     # ---- populate: rank r inserts the keys r, r + world, ... --------------------------------------
     out = torch.empty(B, 32, device=dev)
     if rank < serving0:
-        t.reserve(int(K / serving0 * 1.02) + B)
+        t.reserve(int(K / serving0 * 1.02) + 4 * B, exact=True)
 
     def populate():
         per = (K + world - 1) // world
@@ -132,8 +132,21 @@ def main() -> None:
 
     # ---- rebalance serving0 -> world ranks in stages, load running between the stages ---------------
     inbox = PeerInbox(t, 1 << 20)
+    # One-time costs of a rank that has just joined (NCCL point-to-point connections for the count exchange,
+    # lazy kernel loading, the stream-ordered allocator's pool, first touch of every peer's inbox) are paid
+    # here, by moving one scratch row between every pair of ranks, and reported on their own.
+    def warm():
+        from parameter_server_b200.parallel.migrate import exchange_by_keys
+        scratch = SparseTable(32, "ftrl", dict(lr=0.05), capacity=4096, max_keys=1024, group="none")
+        ks = torch.arange(world, device=dev, dtype=torch.int64) + (1 << 50)
+        scratch.set_rows(ks, torch.zeros(world, scratch.table.stride(), device=dev))
+        exchange_by_keys(scratch, ks, [1] * world, inbox, scratch, t)
+        scratch.erase_keys(ks)
+        reshard(t, owner0, batch=1 << 20, inbox=inbox)      # nothing moves
+    ms, _ = timed(warm)
+    res["one_time_warmup_ms"] = ms
     # the joining ranks allocate their row pools first (the create-storage step of a scale-out), timed on its own
-    ms, _ = timed(lambda: t.reserve(int(K / world * 1.1) + B) if rank >= serving0 else None)
+    ms, _ = timed(lambda: t.reserve(int(K / world * 1.1) + 4 * B, exact=True) if rank >= serving0 else None)
     res["joining_ranks_alloc_ms"] = ms
     moving = [s for s in range(n_shards) if owner0[s] != owner1[s]]
     cur = list(owner0)

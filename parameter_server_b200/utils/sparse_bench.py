@@ -60,7 +60,7 @@ def main() -> None:
 
     cls = SparseTable if a.impl == "ours" else NcclSparseTable
     t = cls(64, "adagrad", dict(lr=0.05, init_accumulator=0.1), capacity=int(a.rows_per_gpu * 1.1) + nmax, max_keys=nmax, seed=3)
-    t.reserve(int(a.rows_per_gpu * 1.05) + nmax)
+    t.reserve(int(a.rows_per_gpu * 1.05) + 2 * nmax, exact=True)
     out = torch.empty(nmax, 64, device=dev)
     grads = torch.randn(nmax, 64, device=dev) * 1e-3
     # populate: rank r inserts keys r, r + world, ...

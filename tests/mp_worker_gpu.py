@@ -208,4 +208,10 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException:
+        import traceback
+        # one line per rank on stdout, so that the launcher's own noise cannot hide the cause
+        print(f"WORKER-FAILED rank {os.environ.get('RANK')}: " + traceback.format_exc().replace("\n", " | ")[-1500:], flush=True)
+        os._exit(1)

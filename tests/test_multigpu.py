@@ -15,7 +15,9 @@ def run_ranks(n, which):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
            "127.0.0.1", "--master-port", str(29600 + n), os.path.join(HERE, "mp_worker_gpu.py"), which]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
-    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    if p.returncode != 0:
+        causes = [ln for ln in p.stdout.splitlines() if "WORKER-FAILED" in ln or ln.endswith(" ok")]
+        raise AssertionError("\n".join(causes[:4]) or (p.stdout[-1500:] + p.stderr[-1500:]))
     return p.stdout
 
 
