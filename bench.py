@@ -45,6 +45,7 @@ def parse_args():
                     help="ours: fused kernels; nccl_baseline: the same model with NCCL-only sparse / dense paths (our own baseline)")
     ap.add_argument("--batch-per-gpu", type=int, default=8192)
     ap.add_argument("--no-sparse-micro", action="store_true", help="skip the sparse pull+push microbenchmark")
+    ap.add_argument("--breakdown", action="store_true", help="after the timed regions, add per-section device times of an eager step")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a CUDA graph")
     ap.add_argument("--micro-keys", type=int, default=1 << 20, help="keys per GPU per step of the microbenchmark")
     return ap.parse_args()
@@ -248,6 +249,10 @@ def main():
         "sparse_pull_push_keys_per_sec_in_step": 2 * keys_per_step * K / (ms / 1e3),
         "table_rows_rank0": model.sparse.size(),
     }
+    if args.breakdown and hasattr(model, "step_breakdown"):
+        barrier()
+        result["breakdown_us_rank0"] = model.step_breakdown()
+        barrier()
     if args.impl == "nccl_baseline":
         result["config"]["parallelism"] = f"dp{world} + NCCL all_to_all_single sparse path + reduce_scatter/all_gather dense path (baseline)"
 

@@ -159,6 +159,7 @@ class DLRM:
         self.h_loss = torch.zeros(1, dtype=torch.float32).pin_memory()
         self.launches_per_step = 0
         self.graph = None
+        self.trace = None   # list of (section, CUDA event) while a step is being traced
 
     # ------------------------------------------------------------------------------------------
     def load_batch(self, dense: torch.Tensor, keys: torch.Tensor, labels: torch.Tensor) -> None:
@@ -166,6 +167,45 @@ class DLRM:
         self.d_dense.copy_(dense, non_blocking=True)
         self.d_keys.copy_(keys, non_blocking=True)
         self.d_labels.copy_(labels, non_blocking=True)
+
+    def _mark(self, name: str) -> None:
+        if self.trace is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self.trace.append((name, e))
+
+    def step_breakdown(self, repeats: int = 5) -> dict:
+        """Device time of each section of the step in microseconds (median over ``repeats`` eager steps on
+        the batch in the input buffers), plus the in-kernel phase times of the fused sparse pull / push.
+        Sections that wait for other ranks include the skew between the ranks."""
+        import statistics
+        acc: dict = {}
+        prof = getattr(self.sparse, "engine", None)
+        if prof is not None and hasattr(prof, "set_profile"):
+            prof.set_profile(True)
+        for _ in range(repeats):
+            self.trace = []
+            self._mark("start")
+            self.forward_backward()
+            torch.cuda.synchronize()
+            for (_, e0), (name, e1) in zip(self.trace, self.trace[1:]):
+                acc.setdefault(name, []).append(e0.elapsed_time(e1) * 1e3)
+            if prof is not None and hasattr(prof, "phase_stamps"):
+                st = prof.phase_stamps(0)
+                for i, nm in enumerate(["pull.P1_dedup", "pull.P2_ship_keys", "pull.P3a_resolve", "pull.P3b_init", "pull.P3c_rows",
+                                        "pull.P5_gather"]):
+                    acc.setdefault(nm, []).append((st[i + 1] - st[i]) / 1e3)
+                if self.sparse.world > 1:
+                    spans = [(8, 9, "push.Q1_segsum_ack_wait"), (9, 10, "push.Q2_ship_wait_grads"), (10, 11, "push.Q3ab_elect_fold"),
+                             (11, 12, "push.Q3c_update")]
+                else:   # a single rank has no ship phase and leaves stamp 9 unwritten
+                    spans = [(8, 10, "push.Q1_segsum"), (10, 11, "push.Q3ab_elect_fold"), (11, 12, "push.Q3c_update")]
+                for lo, hi, nm in spans:
+                    acc.setdefault(nm, []).append((st[hi] - st[lo]) / 1e3)
+        self.trace = None
+        if prof is not None and hasattr(prof, "set_profile"):
+            prof.set_profile(False)
+        return {k: round(statistics.median(v), 1) for k, v in acc.items()}
 
     def forward_backward(self) -> torch.Tensor:
         """One training step on the batch already in the device input buffers. Returns the device
@@ -187,7 +227,9 @@ class DLRM:
         for i, out in enumerate(self.bot_act):
             G.gemm(a, P[f"bot.w{i}"], bias=P[f"bot.b{i}"], relu=True, out=out); n_launch += 1
             a = out
+        self._mark("bottom_fwd")
         self.sparse.pull(self.d_keys, out=self.emb); n_launch += 1
+        self._mark("sparse_pull")
         chk(C.interaction_fwd(self.bot_act[-1].data_ptr(), D, self.emb.data_ptr(), F, D, self.inter.data_ptr(),
                               self.k_top, B, s)); n_launch += 1
         a = self.inter
@@ -200,6 +242,7 @@ class DLRM:
                        self.d_labels.data_ptr(), B, self.tdims[-1], 1.0 / B, self.loss.data_ptr(), 0,
                        self.top_dz[last].data_ptr(), self.tdims[-1], Gd["head.w"].data_ptr(), Gd["head.b"].data_ptr(), s))
         n_launch += 1
+        self._mark("interaction_top_fwd_head")
         # ---------------- backward: top MLP ----------------
         for i in range(last, -1, -1):
             dz = self.top_dz[i]
@@ -211,11 +254,14 @@ class DLRM:
             else:
                 G.linear_dgrad(dz, P["top.w0"], out=self.d_inter)
             n_launch += 1
+        self._mark("top_bwd")
         # ---------------- backward: interaction + sparse push ----------------
         nb = len(self.bot_act) - 1
         chk(C.interaction_bwd(self.d_inter.data_ptr(), self.k_top, self.bot_act[nb].data_ptr(), D, self.emb.data_ptr(),
                               F, D, self.bot_dz[nb].data_ptr(), D, self.d_emb.data_ptr(), B, True, s)); n_launch += 1
+        self._mark("interaction_bwd")
         self.sparse.push(self.d_emb); n_launch += 1
+        self._mark("sparse_push")
         # ---------------- backward: bottom MLP ----------------
         for i in range(nb, -1, -1):
             dz = self.bot_dz[i]
@@ -225,7 +271,9 @@ class DLRM:
             if i > 0:
                 G.linear_dgrad(dz, P[f"bot.w{i}"], mask=self.bot_act[i - 1], out=self.bot_dz[i - 1]); n_launch += 1
         # ---------------- dense push (reduce-scatter + optimizer + all-gather) ----------------
+        self._mark("bottom_bwd")
         self.dense.push(); n_launch += 1
+        self._mark("dense_push")
         self.launches_per_step = n_launch
         return self.loss
 
