@@ -94,5 +94,32 @@ void bind_dense(py::module_& m) {
           py::arg("gather_peers") = std::vector<uintptr_t>(), py::arg("gather_rank") = 0, py::arg("rows_per_rank") = 0,
           py::arg("gather_ready") = 0, py::arg("gather_epoch") = 0, py::arg("gather_ctas") = 8);
 
+    // problems: (a, lda, b, ldb, M, N, K, out_bf16, out_f32, ldd, accumulate, split_k)
+    m.def("gemm_bf16_grouped",
+          [](const std::vector<std::tuple<uintptr_t, int64_t, uintptr_t, int64_t, int, int, int, uintptr_t, uintptr_t, int64_t, bool, int>>& probs,
+             bool a_mn, bool b_mn, uintptr_t err_flag, double wait_limit_s, uintptr_t stream) {
+              const int n = (int)probs.size();
+              if (n > 8) return -2;
+              GemmOperand A[8], B[8];
+              GemmEpilogue ep[8];
+              int M[8], N[8], K[8];
+              for (int i = 0; i < n; ++i) {
+                  const auto& t = probs[i];
+                  A[i] = GemmOperand{ptr<const void>(std::get<0>(t)), std::get<1>(t), a_mn};
+                  B[i] = GemmOperand{ptr<const void>(std::get<2>(t)), std::get<3>(t), b_mn};
+                  M[i] = std::get<4>(t);
+                  N[i] = std::get<5>(t);
+                  K[i] = std::get<6>(t);
+                  ep[i].out_bf16 = ptr<__nv_bfloat16>(std::get<7>(t));
+                  ep[i].out_f32 = ptr<float>(std::get<8>(t));
+                  ep[i].ldd = std::get<9>(t);
+                  ep[i].accumulate = std::get<10>(t) ? 1 : 0;
+                  ep[i].split_k = std::get<11>(t);
+              }
+              return gemm_bf16_grouped(A, B, ep, M, N, K, n, ptr<unsigned>(err_flag), wait_limit_s, (void*)stream);
+          },
+          py::arg("problems"), py::arg("a_mn"), py::arg("b_mn"), py::arg("err_flag") = 0, py::arg("wait_limit_s") = 2.0,
+          py::arg("stream") = 0);
+
     bind_model_kernels(m);
 }

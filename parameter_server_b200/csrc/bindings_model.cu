@@ -1,5 +1,9 @@
 // Bindings of the non-GEMM model kernels.
 #include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <tuple>
+#include <vector>
 
 #include "kernels/dedup.h"
 #include "kernels/model_kernels.h"
@@ -38,6 +42,20 @@ void bind_model_kernels(py::module_& m) {
         return dedup_partition((const long long*)keys, n, (void*)scratch, slots, (unsigned*)pos, (const int*)shard_owner,
                                n_shards, world, (long long*)uniq_keys, (int*)uniq_owner, (int*)inverse, (unsigned*)counts,
                                (void*)s);
+    });
+    // items: (dz, ld, N, db); all tensors have M rows
+    m.def("bias_grad_multi", [](const std::vector<std::tuple<uintptr_t, int64_t, int, uintptr_t>>& items, int M, uintptr_t s) {
+        BiasGradSet set;
+        if (items.size() > 8) return -2;
+        set.count = (int)items.size();
+        set.M = M;
+        for (int i = 0; i < set.count; ++i) {
+            set.dz[i] = (const void*)std::get<0>(items[i]);
+            set.ld[i] = std::get<1>(items[i]);
+            set.N[i] = std::get<2>(items[i]);
+            set.db[i] = (float*)std::get<3>(items[i]);
+        }
+        return bias_grad_multi(set, (void*)s);
     });
     m.def("cast_pad", [](uintptr_t x, int B, int Kin, uintptr_t out, int64_t ldo, uintptr_t s) {
         return cast_pad((const float*)x, B, Kin, (void*)out, ldo, (void*)s);

@@ -7,7 +7,7 @@
 // DenseTablePullOperator reassembles the slices on the worker (pico-ps/operator/DensePullOperator.h:
 // 153-169, :197-216). Here slice r is the r-th contiguous 1/world of the flat parameter buffer:
 //   1. every rank announces "my gradients are complete" with a release flag on every peer;
-//   2. rank r sums slice r of every peer's gradient buffer with 16-byte peer loads, in rank order
+//   2. rank r sums slice r of every peer's gradient buffer with vector peer loads (a warp reads one contiguous span), in rank order
 //      (bitwise reproducible), scales, and runs SGD / Adam(W) on its fp32 master + moments;
 //   3. it stores the new bf16 values of slice r into EVERY rank's parameter buffer (peer stores),
 //      which is the all-gather of the next dense pull;
@@ -25,35 +25,26 @@ namespace {
 constexpr int kThreads = 256;
 
 template <typename GT>
-struct Vec8;  // eight gradient elements
+struct Vec4;  // four gradient elements; a warp's loads cover one contiguous 512-byte (fp32) / 256-byte (bf16) span
 template <>
-struct Vec8<float> {
-    float4 a, b;
-    __device__ __forceinline__ void load(const float* p) {
-        a = *(const float4*)p;
-        b = *(const float4*)(p + 4);
-    }
-    __device__ __forceinline__ void to_float(float* f) const {
-        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
-    }
+struct Vec4<float> {
+    float4 a;
+    __device__ __forceinline__ void load(const float* p) { a = *(const float4*)p; }
+    __device__ __forceinline__ void to_float(float* f) const { f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; }
 };
 template <>
-struct Vec8<__nv_bfloat16> {
-    uint4 raw;
-    __device__ __forceinline__ void load(const __nv_bfloat16* p) { raw = *(const uint4*)p; }
+struct Vec4<__nv_bfloat16> {
+    uint2 raw;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { raw = *(const uint2*)p; }
     __device__ __forceinline__ void to_float(float* f) const {
         const __nv_bfloat162* h = (const __nv_bfloat162*)&raw;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float2 t = __bfloat1622float2(h[i]);
-            f[2 * i] = t.x;
-            f[2 * i + 1] = t.y;
-        }
+        float2 t0 = __bfloat1622float2(h[0]), t1 = __bfloat1622float2(h[1]);
+        f[0] = t0.x; f[1] = t0.y; f[2] = t1.x; f[3] = t1.y;
     }
 };
 
 template <typename GT>
-__global__ void __launch_bounds__(kThreads) dense_rs_opt_ag_kernel(const DenseArgs a) {
+__global__ void __launch_bounds__(kThreads, 4) dense_rs_opt_ag_kernel(const DenseArgs a) {
     const int me = a.rank;
     const unsigned epoch = *((volatile unsigned*)&a.ctl->epoch) + 1u;
     const int W = a.world;
@@ -75,68 +66,50 @@ __global__ void __launch_bounds__(kThreads) dense_rs_opt_ag_kernel(const DenseAr
         if (!__syncthreads_and(ok)) return;
     }
     // ---- 2+3. reduce, update, scatter bf16 ------------------------------------------------------------
-    const size_t n8 = a.shard_len / 8;
-    const GT* gsrc[kMaxWorld];
-    __nv_bfloat16* pdst[kMaxWorld];
-#pragma unroll
-    for (int r = 0; r < kMaxWorld; ++r) {
-        gsrc[r] = r < W ? (const GT*)a.peer_grads[r] + a.shard_lo : nullptr;
-        pdst[r] = r < W ? a.peer_params[r] + a.shard_lo : nullptr;
-    }
-    for (size_t c = blockIdx.x * (size_t)kThreads + threadIdx.x; c < n8; c += (size_t)gridDim.x * kThreads) {
-        const size_t i = c * 8;
-        float g[8];
+    const size_t n4 = a.shard_len / 4;
+    // peer pointers are read from the kernel parameters (constant bank) where they are used: keeping
+    // sixteen of them in registers would cost a third of the register budget
+#pragma unroll 1
+    for (size_t c = blockIdx.x * (size_t)kThreads + threadIdx.x; c < n4; c += (size_t)gridDim.x * kThreads) {
+        const size_t i = c * 4;
+        float g[4];
         {
-            Vec8<GT> v;
-            v.load(gsrc[0] + i);
+            Vec4<GT> v;
+            v.load((const GT*)a.peer_grads[0] + a.shard_lo + i);
             v.to_float(g);
         }
 #pragma unroll
         for (int r = 1; r < kMaxWorld; ++r) {
             if (r < W) {
-                Vec8<GT> v;
-                v.load(gsrc[r] + i);
-                float t[8];
+                Vec4<GT> v;
+                v.load((const GT*)a.peer_grads[r] + a.shard_lo + i);
+                float t[4];
                 v.to_float(t);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) g[k] += t[k];
+                for (int k = 0; k < 4; ++k) g[k] += t[k];
             }
         }
-        float w[8], m[8], s[8];
-        *(float4*)&w[0] = *(const float4*)(a.master + i);
-        *(float4*)&w[4] = *(const float4*)(a.master + i + 4);
-        if (a.n_slots > 0) {
-            *(float4*)&m[0] = *(const float4*)(a.slot0 + i);
-            *(float4*)&m[4] = *(const float4*)(a.slot0 + i + 4);
-        }
-        if (a.n_slots > 1) {
-            *(float4*)&s[0] = *(const float4*)(a.slot1 + i);
-            *(float4*)&s[4] = *(const float4*)(a.slot1 + i + 4);
-        }
+        __align__(16) float w[4], m[4], s[4];
+        *(float4*)w = *(const float4*)(a.master + i);
+        if (a.n_slots > 0) *(float4*)m = *(const float4*)(a.slot0 + i);
+        if (a.n_slots > 1) *(float4*)s = *(const float4*)(a.slot1 + i);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int k = 0; k < 4; ++k) {
             float s0 = a.n_slots > 0 ? m[k] : 0.f, s1 = a.n_slots > 1 ? s[k] : 0.f;
             opt_update(opt, w[k], s0, s1, g[k] * a.grad_scale);
             m[k] = s0;
             s[k] = s1;
         }
-        *(float4*)(a.master + i) = *(float4*)&w[0];
-        *(float4*)(a.master + i + 4) = *(float4*)&w[4];
-        if (a.n_slots > 0) {
-            *(float4*)(a.slot0 + i) = *(float4*)&m[0];
-            *(float4*)(a.slot0 + i + 4) = *(float4*)&m[4];
-        }
-        if (a.n_slots > 1) {
-            *(float4*)(a.slot1 + i) = *(float4*)&s[0];
-            *(float4*)(a.slot1 + i + 4) = *(float4*)&s[4];
-        }
-        uint4 packed;
+        *(float4*)(a.master + i) = *(float4*)w;
+        if (a.n_slots > 0) *(float4*)(a.slot0 + i) = *(float4*)m;
+        if (a.n_slots > 1) *(float4*)(a.slot1 + i) = *(float4*)s;
+        uint2 packed;
         __nv_bfloat162* h = (__nv_bfloat162*)&packed;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(w[2 * k], w[2 * k + 1]);
+        h[0] = __floats2bfloat162_rn(w[0], w[1]);
+        h[1] = __floats2bfloat162_rn(w[2], w[3]);
 #pragma unroll
         for (int r = 0; r < kMaxWorld; ++r)
-            if (r < W && (a.scatter_peers || r == me)) *(uint4*)(pdst[r] + i) = packed;
+            if (r < W && (a.scatter_peers || r == me)) *(uint2*)(a.peer_params[r] + a.shard_lo + i) = packed;
     }
     // ---- 4. all slices landed everywhere ----------------------------------------------------------
     if (W == 1) {

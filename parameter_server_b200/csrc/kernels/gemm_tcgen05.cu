@@ -282,6 +282,50 @@ __device__ void gather_rows(const GemmGather& ag, int K, uint8_t* smem, uint64_t
     }
 }
 
+// One launch can carry several independent GEMMs (a "group": e.g. the weight gradients of every layer of an
+// MLP, which all become computable at the end of the backward pass). The persistent CTAs walk one list of
+// work units that covers the problems back to back, so small problems fill the machine together and pay one
+// prologue. All problems of a launch share the tile shape and the operand majors.
+constexpr int kMaxGroup = 8;
+struct GemmProblemSet {
+    CUtensorMap map_a[kMaxGroup];
+    CUtensorMap map_b[kMaxGroup];
+    GemmEpilogue ep[kMaxGroup];
+    int M[kMaxGroup], N[kMaxGroup], K[kMaxGroup];
+    int unit_end[kMaxGroup];  // running total of work units (m tile x n tile x k split) up to and including problem i
+    int count;
+};
+
+struct WorkUnit {
+    int p;                    // problem index
+    int tile_m, tile_n, nt;   // element offsets of the tile, n-tile index
+    int kt_begin, num_kt;     // k-tile range of this split
+};
+
+template <int BN>
+__device__ __forceinline__ WorkUnit decode_unit(const GemmProblemSet& ps, int u, const GemmGather& ag) {
+    WorkUnit w;
+    int p = 0;
+    while (p + 1 < ps.count && u >= ps.unit_end[p]) ++p;
+    w.p = p;
+    const int local = u - (p > 0 ? ps.unit_end[p - 1] : 0);
+    const int m_tiles = (ps.M[p] + BM - 1) / BM;
+    const int n_tiles = (ps.N[p] + BN - 1) / BN;
+    const int splits = ps.ep[p].split_k > 1 ? ps.ep[p].split_k : 1;
+    const int total_kt = (ps.K[p] + BK - 1) / BK;
+    const int kt_per = (total_kt + splits - 1) / splits;
+    const int z = local / (m_tiles * n_tiles);
+    const int rem = local - z * (m_tiles * n_tiles);
+    int nt = rem / m_tiles;  // m fastest: CTAs that run together share the B tile in L2
+    if (ag.enabled) nt = (nt + ag.rank * (ag.rows_per_rank / BN)) % n_tiles;  // local rows first, then ring order
+    w.nt = nt;
+    w.tile_n = nt * BN;
+    w.tile_m = (rem % m_tiles) * BM;
+    w.kt_begin = z * kt_per;
+    w.num_kt = max(0, min(total_kt - w.kt_begin, kt_per));
+    return w;
+}
+
 // Persistent kernel: gridDim.x CTAs (one per SM) walk the tile list t = blockIdx.x, +gridDim.x, ...;
 // a tile is (split z, n tile, m tile) with m fastest so that concurrently running CTAs share the B
 // tile in L2. The accumulator is double-buffered in TMEM (2 x BN columns): while the epilogue warps
@@ -289,8 +333,7 @@ __device__ void gather_rows(const GemmGather& ag, int K, uint8_t* smem, uint64_t
 // AMN / BMN: operand is MN-major. The box of an MN-major operand is [64 k-rows][64 mn-elements].
 template <int BN, bool AMN, bool BMN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                         const GemmEpilogue ep, int M, int N, int K, unsigned* err_flag, unsigned long long limit_ns,
+gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* err_flag, unsigned long long limit_ns,
                          const GemmGather ag) {
     using L = SmemLayout<BN>;
     extern __shared__ uint8_t smem_raw[];
@@ -304,18 +347,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     // ---- all-gather role: the first ag.gather_ctas CTAs move remote row blocks of B into the local copy ----
     const int n_gather = ag.enabled ? ag.gather_ctas : 0;
     if ((int)blockIdx.x < n_gather) {
-        gather_rows<BN>(ag, K, smem, full_bar, err_flag, limit_ns, N);
+        gather_rows<BN>(ag, ps.K[0], smem, full_bar, err_flag, limit_ns, ps.N[0]);
         return;
     }
     const int cta = (int)blockIdx.x - n_gather, n_cta = (int)gridDim.x - n_gather;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int m_tiles = (M + BM - 1) / BM;
-    const int n_tiles = (N + BN - 1) / BN;
-    const int splits = ep.split_k > 1 ? ep.split_k : 1;
-    const int total_tiles = m_tiles * n_tiles * splits;
-    const int total_kt = (K + BK - 1) / BK;
-    const int kt_per = (total_kt + splits - 1) / splits;
+    const int total_units = ps.unit_end[ps.count - 1];
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < L::kStages; ++s) {
@@ -344,14 +382,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         if (lane == 0) {
             uint32_t it = 0;  // k-tile counter across all tiles of this CTA (drives the stage ring)
             bool ok = true;
-            for (int tile = cta; tile < total_tiles && ok; tile += n_cta) {
-                const int z = tile / (m_tiles * n_tiles);
-                const int rem = tile - z * (m_tiles * n_tiles);
-                int nt = rem / m_tiles;
+            for (int unit = cta; unit < total_units && ok; unit += n_cta) {
+                const WorkUnit w = decode_unit<BN>(ps, unit, ag);
                 if (ag.enabled) {
-                    // local rows first, then the ranks in ring order; a remote n-tile must have landed
+                    // a remote n-tile must have landed before it is loaded
                     const int tpr = ag.rows_per_rank / BN;
-                    nt = (nt + ag.rank * tpr) % n_tiles;
+                    const int nt = w.nt;
                     if (nt / tpr != ag.rank) {
                         const unsigned long long t0 = gtimer();
                         unsigned spins = 0;
@@ -366,9 +402,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         asm volatile("fence.proxy.async.global;" ::: "memory");
                     }
                 }
-                const int tile_n = nt * BN, tile_m = (rem % m_tiles) * BM;
-                const int kt_begin = z * kt_per;
-                const int num_kt = max(0, min(total_kt - kt_begin, kt_per));
+                const CUtensorMap* map_a = &ps.map_a[w.p];
+                const CUtensorMap* map_b = &ps.map_b[w.p];
+                const int tile_n = w.tile_n, tile_m = w.tile_m, kt_begin = w.kt_begin, num_kt = w.num_kt;
                 for (int kt = 0; kt < num_kt; ++kt, ++it) {
                     const int s = it % L::kStages;
                     const uint32_t ph = (it / L::kStages) & 1u;
@@ -382,17 +418,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     mbar_expect_tx(&full_bar[s], (uint32_t)L::kStageBytes);
                     const int k0 = (kt_begin + kt) * BK;
                     if (!AMN) {
-                        tma_load_2d(sa, &map_a, &full_bar[s], k0, tile_m);  // box [128 rows][64 k]
+                        tma_load_2d(sa, map_a, &full_bar[s], k0, tile_m);  // box [128 rows][64 k]
                     } else {
-                        tma_load_2d(sa, &map_a, &full_bar[s], tile_m, k0);  // box [64 k][64 m]
-                        tma_load_2d(sa + 64 * 128, &map_a, &full_bar[s], tile_m + 64, k0);
+                        tma_load_2d(sa, map_a, &full_bar[s], tile_m, k0);  // box [64 k][64 m]
+                        tma_load_2d(sa + 64 * 128, map_a, &full_bar[s], tile_m + 64, k0);
                     }
                     if (!BMN) {
-                        tma_load_2d(sb, &map_b, &full_bar[s], k0, tile_n);  // box [BN rows][64 k]
+                        tma_load_2d(sb, map_b, &full_bar[s], k0, tile_n);  // box [BN rows][64 k]
                     } else {
 #pragma unroll
                         for (int j = 0; j < BN / 64; ++j)
-                            tma_load_2d(sb + j * 64 * 128, &map_b, &full_bar[s], tile_n + 64 * j, k0);
+                            tma_load_2d(sb + j * 64 * 128, map_b, &full_bar[s], tile_n + 64 * j, k0);
                     }
                 }
             }
@@ -404,10 +440,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                                    ((BMN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             uint32_t it = 0, tc = 0;
             bool ok = true;
-            for (int tile = cta; tile < total_tiles && ok; tile += n_cta) {
-                const int z = tile / (m_tiles * n_tiles);
-                const int kt_begin = z * kt_per;
-                const int num_kt = max(0, min(total_kt - kt_begin, kt_per));
+            for (int unit = cta; unit < total_units && ok; unit += n_cta) {
+                const int num_kt = decode_unit<BN>(ps, unit, ag).num_kt;
                 if (num_kt == 0) continue;
                 const uint32_t buf = tc & 1u, tph = (tc >> 1) & 1u;
                 if (!mbar_wait(&tempty_bar[buf], tph ^ 1u, limit_ns)) {
@@ -446,14 +480,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         // ------------------------------ epilogue ----------------------------------
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         uint32_t tc = 0;
-        for (int tile = cta; tile < total_tiles; tile += n_cta) {
-            const int z = tile / (m_tiles * n_tiles);
-            const int rem = tile - z * (m_tiles * n_tiles);
-            int nt = rem / m_tiles;
-            if (ag.enabled) nt = (nt + ag.rank * (ag.rows_per_rank / BN)) % n_tiles;
-            const int tile_n = nt * BN, tile_m = (rem % m_tiles) * BM;
-            const int kt_begin = z * kt_per;
-            const int num_kt = max(0, min(total_kt - kt_begin, kt_per));
+        for (int unit = cta; unit < total_units; unit += n_cta) {
+            const WorkUnit w = decode_unit<BN>(ps, unit, ag);
+            const int tile_n = w.tile_n, tile_m = w.tile_m, num_kt = w.num_kt;
+            const GemmEpilogue& ep = ps.ep[w.p];
+            const int M = ps.M[w.p], N = ps.N[w.p];
             if (num_kt == 0) continue;
             const uint32_t buf = tc & 1u, tph = (tc >> 1) & 1u;
             const bool ok = mbar_wait(&tfull_bar[buf], tph, limit_ns * 2);
@@ -524,8 +555,8 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, 
 }
 
 template <int BN, bool AMN, bool BMN>
-cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const GemmEpilogue& ep, int M, int N, int K,
-                           unsigned* err, unsigned long long limit_ns, cudaStream_t s, const GemmGather& ag) {
+cudaError_t launch_variant(const GemmProblemSet& ps, unsigned* err, unsigned long long limit_ns, cudaStream_t s,
+                           const GemmGather& ag) {
     auto kern = gemm_bf16_tcgen05_kernel<BN, AMN, BMN>;
     static bool configured = false;
     if (!configured) {
@@ -539,12 +570,50 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const G
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     }
-    const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM) * (ep.split_k > 1 ? ep.split_k : 1);
-    int ctas = tiles < num_sms ? tiles : num_sms;
-    if (ag.enabled) ctas = std::max(ag.gather_ctas + 1, std::min(num_sms, tiles + ag.gather_ctas));
+    const int units = ps.unit_end[ps.count - 1];
+    int ctas = units < num_sms ? units : num_sms;
+    if (ag.enabled) ctas = std::max(ag.gather_ctas + 1, std::min(num_sms, units + ag.gather_ctas));
     dim3 grid(ctas);
-    kern<<<grid, kThreads, SmemLayout<BN>::kTotal, s>>>(ma, mb, ep, M, N, K, err, limit_ns, ag);
+    kern<<<grid, kThreads, SmemLayout<BN>::kTotal, s>>>(ps, err, limit_ns, ag);
     return cudaGetLastError();
+}
+
+cudaError_t dispatch(int BN, bool a_mn, bool b_mn, const GemmProblemSet& ps, unsigned* err, unsigned long long lim,
+                     cudaStream_t s, const GemmGather& ag) {
+    const int v = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
+    if (BN == 256) {
+        switch (v) {
+            case 0: return launch_variant<256, false, false>(ps, err, lim, s, ag);
+            case 1: return launch_variant<256, false, true>(ps, err, lim, s, ag);
+            case 2: return launch_variant<256, true, false>(ps, err, lim, s, ag);
+            default: return launch_variant<256, true, true>(ps, err, lim, s, ag);
+        }
+    }
+    switch (v) {
+        case 0: return launch_variant<128, false, false>(ps, err, lim, s, ag);
+        case 1: return launch_variant<128, false, true>(ps, err, lim, s, ag);
+        case 2: return launch_variant<128, true, false>(ps, err, lim, s, ag);
+        default: return launch_variant<128, true, true>(ps, err, lim, s, ag);
+    }
+}
+
+// Fills slot i of a problem set; returns 0, -2 (alignment) or -3 (tensor map).
+int add_problem(GemmProblemSet* ps, int i, int BN, const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep, int M,
+                int N, int K) {
+    if ((A.ld % 8) || (B.ld % 8) || ((uintptr_t)A.ptr % 16) || ((uintptr_t)B.ptr % 16)) return -2;  // TMA: 16-byte rule
+    // K-major: tensor [MN rows][K cols], box [tile rows][64]; MN-major: tensor [K rows][MN cols], box [64][64]
+    bool ok = A.mn_major ? make_map(&ps->map_a[i], A.ptr, (uint64_t)K, (uint64_t)M, (uint64_t)A.ld, 64)
+                         : make_map(&ps->map_a[i], A.ptr, (uint64_t)M, (uint64_t)K, (uint64_t)A.ld, BM);
+    ok = ok && (B.mn_major ? make_map(&ps->map_b[i], B.ptr, (uint64_t)K, (uint64_t)N, (uint64_t)B.ld, 64)
+                           : make_map(&ps->map_b[i], B.ptr, (uint64_t)N, (uint64_t)K, (uint64_t)B.ld, BN));
+    if (!ok) return -3;
+    ps->ep[i] = ep;
+    ps->M[i] = M;
+    ps->N[i] = N;
+    ps->K[i] = K;
+    const int units = ((N + BN - 1) / BN) * ((M + BM - 1) / BM) * (ep.split_k > 1 ? ep.split_k : 1);
+    ps->unit_end[i] = (i > 0 ? ps->unit_end[i - 1] : 0) + units;
+    return 0;
 }
 
 }  // namespace
@@ -560,37 +629,36 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep
             return -2;
     }
     if (M <= 0 || N <= 0 || K <= 0) return 0;
-    if ((A.ld % 8) || (B.ld % 8) || ((uintptr_t)A.ptr % 16) || ((uintptr_t)B.ptr % 16)) return -2;  // TMA: 16-byte rule
-    CUtensorMap ma, mb;
     // 128 x 256 tiles halve the operand bytes per flop (the 128 x 128 tile is bound by the L2 -> SMEM feed);
     // they are used whenever N fills them.
     const int BN = (N >= 256) ? 256 : 128;
-    // K-major: tensor [MN rows][K cols], box [tile rows][64]; MN-major: tensor [K rows][MN cols], box [64][64]
-    bool ok = A.mn_major ? make_map(&ma, A.ptr, (uint64_t)K, (uint64_t)M, (uint64_t)A.ld, 64)
-                         : make_map(&ma, A.ptr, (uint64_t)M, (uint64_t)K, (uint64_t)A.ld, BM);
-    ok = ok && (B.mn_major ? make_map(&mb, B.ptr, (uint64_t)K, (uint64_t)N, (uint64_t)B.ld, 64)
-                           : make_map(&mb, B.ptr, (uint64_t)N, (uint64_t)K, (uint64_t)B.ld, BN));
-    if (!ok) return -3;
+    GemmProblemSet ps;
+    ps.count = 1;
+    int rc = add_problem(&ps, 0, BN, A, B, ep, M, N, K);
+    if (rc != 0) return rc;
     const unsigned long long lim = (unsigned long long)(wait_limit_s * 1e9);
-    cudaStream_t s = (cudaStream_t)stream;
-    cudaError_t e;
-    const int v = (A.mn_major ? 2 : 0) | (B.mn_major ? 1 : 0);
-    if (BN == 256) {
-        switch (v) {
-            case 0: e = launch_variant<256, false, false>(ma, mb, ep, M, N, K, err_flag, lim, s, ag); break;
-            case 1: e = launch_variant<256, false, true>(ma, mb, ep, M, N, K, err_flag, lim, s, ag); break;
-            case 2: e = launch_variant<256, true, false>(ma, mb, ep, M, N, K, err_flag, lim, s, ag); break;
-            default: e = launch_variant<256, true, true>(ma, mb, ep, M, N, K, err_flag, lim, s, ag); break;
-        }
-    } else {
-        switch (v) {
-            case 0: e = launch_variant<128, false, false>(ma, mb, ep, M, N, K, err_flag, lim, s, ag); break;
-            case 1: e = launch_variant<128, false, true>(ma, mb, ep, M, N, K, err_flag, lim, s, ag); break;
-            case 2: e = launch_variant<128, true, false>(ma, mb, ep, M, N, K, err_flag, lim, s, ag); break;
-            default: e = launch_variant<128, true, true>(ma, mb, ep, M, N, K, err_flag, lim, s, ag); break;
-        }
+    return (int)dispatch(BN, A.mn_major, B.mn_major, ps, err_flag, lim, (cudaStream_t)stream, ag);
+}
+
+int gemm_bf16_grouped(const GemmOperand* A, const GemmOperand* B, const GemmEpilogue* ep, const int* M, const int* N,
+                      const int* K, int count, unsigned* err_flag, double wait_limit_s, void* stream) {
+    if (count <= 0) return 0;
+    if (count > kMaxGroup) return -2;
+    int BN = 256;
+    for (int i = 0; i < count; ++i) {
+        if (M[i] <= 0 || N[i] <= 0 || K[i] <= 0) return -2;
+        if (A[i].mn_major != A[0].mn_major || B[i].mn_major != B[0].mn_major) return -2;  // one kernel variant per launch
+        if (N[i] < 256) BN = 128;
     }
-    return (int)e;
+    GemmProblemSet ps;
+    ps.count = count;
+    for (int i = 0; i < count; ++i) {
+        int rc = add_problem(&ps, i, BN, A[i], B[i], ep[i], M[i], N[i], K[i]);
+        if (rc != 0) return rc;
+    }
+    const unsigned long long lim = (unsigned long long)(wait_limit_s * 1e9);
+    GemmGather none;
+    return (int)dispatch(BN, A[0].mn_major, B[0].mn_major, ps, err_flag, lim, (cudaStream_t)stream, none);
 }
 
 }  // namespace psb

@@ -48,4 +48,10 @@ struct GemmGather {
 int gemm_bf16(const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep, int M, int N, int K, unsigned* err_flag,
               double wait_limit_s, void* stream, const GemmGather* gather = nullptr);
 
+// Up to 8 independent GEMMs in ONE persistent launch (same operand majors for all; 128 x 256 tiles when every
+// N >= 256, else 128 x 128). Meant for work that becomes available together, e.g. the weight gradients of all
+// layers of an MLP at the end of the backward pass. Same return codes as gemm_bf16.
+int gemm_bf16_grouped(const GemmOperand* A, const GemmOperand* B, const GemmEpilogue* ep, const int* M, const int* N,
+                      const int* K, int count, unsigned* err_flag, double wait_limit_s, void* stream);
+
 }  // namespace psb

@@ -252,11 +252,11 @@ __global__ void __launch_bounds__(256) bce_head_kernel(const __nv_bfloat16* __re
 
 // ---- bias gradient: db[n] = sum_m dz[m][n] -------------------------------------------------------------
 // CTA = 64 columns x 32 row lanes; every thread streams 16-byte (8 x bf16) loads down its column group.
-__global__ void __launch_bounds__(256) bias_grad_kernel(const __nv_bfloat16* __restrict__ dz, int64_t ld, int M, int N,
-                                                        float* __restrict__ db) {
+__device__ __forceinline__ void bias_grad_block(const __nv_bfloat16* __restrict__ dz, int64_t ld, int M, int N,
+                                                float* __restrict__ db, int col_block) {
     __shared__ float part[32][65];
     const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
-    const int col = blockIdx.x * 64 + tx * 8;
+    const int col = col_block * 64 + tx * 8;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     if (col + 8 <= N && (ld % 8) == 0) {
         for (int m = blockIdx.y * 32 + ty; m < M; m += gridDim.y * 32) {
@@ -281,9 +281,22 @@ __global__ void __launch_bounds__(256) bias_grad_kernel(const __nv_bfloat16* __r
         float s = 0.f;
 #pragma unroll 8
         for (int r = 0; r < 32; ++r) s += part[r][threadIdx.x];
-        const int c = blockIdx.x * 64 + threadIdx.x;
+        const int c = col_block * 64 + threadIdx.x;
         if (c < N) atomicAdd(&db[c], s);
     }
+}
+
+__global__ void __launch_bounds__(256) bias_grad_kernel(const __nv_bfloat16* __restrict__ dz, int64_t ld, int M, int N,
+                                                        float* __restrict__ db) {
+    bias_grad_block(dz, ld, M, N, db, (int)blockIdx.x);
+}
+
+// The bias gradients of several layers in one launch: blockIdx.x walks the 64-column groups of all layers.
+__global__ void __launch_bounds__(256) bias_grad_multi_kernel(const BiasGradSet set) {
+    int p = 0;
+    while (p + 1 < set.count && (int)blockIdx.x >= set.group_end[p]) ++p;
+    const int col_block = (int)blockIdx.x - (p > 0 ? set.group_end[p - 1] : 0);
+    bias_grad_block((const __nv_bfloat16*)set.dz[p], set.ld[p], set.M, set.N[p], set.db[p], col_block);
 }
 
 __global__ void cast_pad_kernel(const float* __restrict__ x, int B, int Kin, __nv_bfloat16* __restrict__ out, int64_t ldo) {
@@ -358,6 +371,20 @@ int bias_grad(const void* dz, int64_t ld, int M, int N, float* db, void* stream)
     const int gy = std::max(1, std::min((M + 31) / 32, (148 * 4 + gx - 1) / gx));
     dim3 grid(gx, gy);
     bias_grad_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dz, ld, M, N, db);
+    return (int)cudaGetLastError();
+}
+
+int bias_grad_multi(BiasGradSet set, void* stream) {
+    if (set.count <= 0) return 0;
+    if (set.count > 8) return -2;
+    int groups = 0;
+    for (int i = 0; i < set.count; ++i) {
+        groups += (set.N[i] + 63) / 64;
+        set.group_end[i] = groups;
+    }
+    const int gy = std::max(1, std::min((set.M + 31) / 32, (148 * 4 + groups - 1) / groups));
+    dim3 grid(groups, gy);
+    bias_grad_multi_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(set);
     return (int)cudaGetLastError();
 }
 

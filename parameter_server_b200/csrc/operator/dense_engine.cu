@@ -106,8 +106,8 @@ Status DenseEngine::step(const OptConfig& opt, float grad_scale, void* stream) {
     a.scatter_peers = scatter_peers_ ? 1 : 0;
     a.opt = opt;
     a.ctl = ctl_;
-    const size_t chunks = shard_len_ / 8;
-    int nblocks = (int)std::min<size_t>(148 * 8, std::max<size_t>(1, (chunks + 255) / 256));
+    const size_t chunks = shard_len_ / 4;
+    int nblocks = (int)std::min<size_t>(148 * 4, std::max<size_t>(1, (chunks + 255) / 256));  // 4 resident CTAs per SM, one wave
     int rc = launch_dense_rs_opt_ag(a, grad_bf16_ ? 1 : 0, nblocks, stream);
     ++launches_;
     if (rc != 0) return Status::Error(std::string("dense_rs_opt_ag launch: ") + cudaGetErrorString((cudaError_t)rc));

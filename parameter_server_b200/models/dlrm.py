@@ -243,12 +243,15 @@ class DLRM:
                        self.top_dz[last].data_ptr(), self.tdims[-1], Gd["head.w"].data_ptr(), Gd["head.b"].data_ptr(), s))
         n_launch += 1
         self._mark("interaction_top_fwd_head")
-        # ---------------- backward: top MLP ----------------
+        # ---------------- backward: the dgrad chain first; every layer's dz stays in its own buffer, so the
+        # weight and bias gradients of ALL layers run at the end as one grouped GEMM launch (two when a layer
+        # is too narrow for the wide tile) and one bias-gradient launch ----------------
+        wg, bg = [], []
         for i in range(last, -1, -1):
             dz = self.top_dz[i]
             x_in = self.top_act[i - 1] if i > 0 else self.inter
-            G.linear_wgrad(dz, x_in, out=Gd[f"top.w{i}"], split_k=self.split_k); n_launch += 1
-            chk(C.bias_grad(dz.data_ptr(), dz.stride(0), B, dz.shape[1], Gd[f"top.b{i}"].data_ptr(), s)); n_launch += 1
+            wg.append((dz, x_in, Gd[f"top.w{i}"]))
+            bg.append((dz, Gd[f"top.b{i}"]))
             if i > 0:
                 G.linear_dgrad(dz, P[f"top.w{i}"], mask=self.top_act[i - 1], out=self.top_dz[i - 1])
             else:
@@ -266,12 +269,15 @@ class DLRM:
         for i in range(nb, -1, -1):
             dz = self.bot_dz[i]
             x_in = self.bot_act[i - 1] if i > 0 else self.x16
-            G.linear_wgrad(dz, x_in, out=Gd[f"bot.w{i}"], split_k=self.split_k); n_launch += 1
-            chk(C.bias_grad(dz.data_ptr(), dz.stride(0), B, dz.shape[1], Gd[f"bot.b{i}"].data_ptr(), s)); n_launch += 1
+            wg.append((dz, x_in, Gd[f"bot.w{i}"]))
+            bg.append((dz, Gd[f"bot.b{i}"]))
             if i > 0:
                 G.linear_dgrad(dz, P[f"bot.w{i}"], mask=self.bot_act[i - 1], out=self.bot_dz[i - 1]); n_launch += 1
-        # ---------------- dense push (reduce-scatter + optimizer + all-gather) ----------------
-        self._mark("bottom_bwd")
+        self._mark("bottom_dgrad")
+        G.grouped_wgrad(wg, split_k=self.split_k)
+        n_launch += (1 if any(x.shape[1] >= 256 for _, x, _ in wg) else 0) + (1 if any(x.shape[1] < 256 for _, x, _ in wg) else 0)
+        G.bias_grads(bg); n_launch += (len(bg) + 7) // 8
+        self._mark("wgrad_bias_grad")
         self.dense.push(); n_launch += 1
         self._mark("dense_push")
         self.launches_per_step = n_launch

@@ -90,6 +90,44 @@ def linear_wgrad(dy, x, out=None, accumulate=False, split_k=1):
                 split_k=split_k)
 
 
+def grouped_wgrad(items, split_k: int = 0) -> None:
+    """Weight gradients of several linear layers in as few launches as possible. ``items`` is a list of
+    ``(dy, x, out)`` with ``dy [M, N_i]``, ``x [M, K_i]`` bf16 and ``out [N_i, K_i]`` fp32, zero-initialised (the
+    batch dimension is split over CTAs and partial sums are added atomically). Layers whose input width fills a
+    256-wide tile share one persistent launch, the narrow ones another: the small problems of an MLP fill the
+    machine together instead of each paying its own ramp-up and tail."""
+    wide = [it for it in items if it[1].shape[1] >= 256]
+    narrow = [it for it in items if it[1].shape[1] < 256]
+    for group, bn in ((wide, 256), (narrow, 128)):
+        for lo in range(0, len(group), 8):
+            part = group[lo:lo + 8]
+            batch = part[0][0].shape[0]
+            tiles = sum(((dy.shape[1] + 127) // 128) * ((x.shape[1] + bn - 1) // bn) for dy, x, _ in part)
+            sk = split_k
+            if sk <= 0:   # about two waves of work units over the 148 SMs, at least 8 k-tiles per unit
+                sk = max(1, min(16, round(296 / tiles), max(1, batch // 512)))
+            probs = []
+            for dy, x, out in part:
+                assert dy.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and out.dtype == torch.float32
+                assert dy.stride(-1) == 1 and x.stride(-1) == 1 and out.stride(-1) == 1 and dy.shape[0] == x.shape[0]
+                probs.append((dy.data_ptr(), dy.stride(0), x.data_ptr(), x.stride(0), dy.shape[1], x.shape[1], dy.shape[0],
+                              0, out.data_ptr(), out.stride(0), False, sk))
+            rc = C.gemm_bf16_grouped(probs, True, True, _err_flag(part[0][0].device).data_ptr(), 2.0,
+                                     torch.cuda.current_stream().cuda_stream)
+            if rc != 0:
+                raise RuntimeError(f"gemm_bf16_grouped failed with code {rc}")
+
+
+def bias_grads(items) -> None:
+    """``db_i += dz_i.sum(0)`` for a list of ``(dz, db)`` (bf16 ``[M, N_i]``, fp32 ``[N_i]``) in one launch per 8."""
+    for lo in range(0, len(items), 8):
+        part = items[lo:lo + 8]
+        rc = C.bias_grad_multi([(dz.data_ptr(), dz.stride(0), dz.shape[1], db.data_ptr()) for dz, db in part],
+                               part[0][0].shape[0], torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"bias_grad_multi failed: {rc}")
+
+
 def ag_linear(x: torch.Tensor, table, name: str, *, bias=None, relu: bool = False, out=None, gather_ctas: int = 8) -> torch.Tensor:
     """``y = act(x @ W.T + bias)`` where ``W = table[name]`` is a dense-table tensor whose rows are sharded over the
     ranks and whose peer copies are NOT kept current by the dense push (``DenseTable(scatter_peers=False)``):

@@ -99,7 +99,7 @@ def cmd_sparse(a):
         pool.append(torch.from_numpy(k.astype(np.int64)).cuda())
     grads = torch.randn(n, dim, device="cuda") * 1e-3
     out = torch.empty(n, dim, device="cuda")
-    t.reserve(8 * n)
+    t.reserve(8 * n, exact=True)
     for i in range(8):
         t.pull(pool[i % 4], out=out)
         t.push(grads)

@@ -29,6 +29,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "nccl"])
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--phases", action="store_true", help="add rank 0's in-kernel phase times of one pull + push (fused path only)")
     a = ap.parse_args()
 
     from parameter_server_b200 import SparseTable
@@ -101,8 +102,24 @@ def main() -> None:
         torch.cuda.synchronize()
         both_ms = rank_max(e0.elapsed_time(e1)) / a.steps
         t.check()
+        phases = None
+        if a.phases and a.impl == "ours":
+            t.engine.set_profile(True)
+            barrier()
+            t.pull(pool[0], out=o)
+            t.push(g)
+            torch.cuda.synchronize()
+            st = t.engine.phase_stamps(0)
+            t.engine.set_profile(False)
+            names = ["P1_dedup", "P2_ship_keys", "P3a_resolve", "P3b_init", "P3c_rows", "P5_gather"]
+            phases = {nm: round((st[i + 1] - st[i]) / 1e3, 1) for i, nm in enumerate(names)}
+            if world > 1:
+                phases.update({"Q1_segsum_ack_wait": round((st[9] - st[8]) / 1e3, 1), "Q2_ship_wait_grads": round((st[10] - st[9]) / 1e3, 1)})
+            else:
+                phases["Q1_segsum"] = round((st[10] - st[8]) / 1e3, 1)
+            phases.update({"Q3ab_elect_fold": round((st[11] - st[10]) / 1e3, 1), "Q3c_update": round((st[12] - st[11]) / 1e3, 1)})
         if rank == 0:
-            print(json.dumps({"metric": "sparse_pull_push_keys_per_sec", "impl": a.impl, "n_gpus": world, "keys_per_gpu_per_step": n,
+            print(json.dumps({"metric": "sparse_pull_push_keys_per_sec", "phases_us_rank0": phases, "impl": a.impl, "n_gpus": world, "keys_per_gpu_per_step": n,
                               "table_rows_max_per_gpu": rows, "table_keys": K, "dim": 64, "optimizer": "adagrad", "zipf_s": 1.05,
                               "unique_fraction": uniq, "pull_ms": pull_ms, "pull_push_ms": both_ms,
                               "pull_keys_per_sec": n * world / (pull_ms / 1e3),

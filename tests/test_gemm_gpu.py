@@ -49,3 +49,34 @@ def test_epilogue_bias_relu_mask_accumulate():
     rdw = dy.float().t() @ x.float() + 1.0
     assert torch.allclose(dw, rdw, rtol=2e-2, atol=0.5)
     G.check_gemm_errors()
+
+
+def test_grouped_wgrad_and_bias_grads_match_fp32_reference():
+    """Several weight gradients in one persistent launch (wide group + narrow group) and all bias gradients in one."""
+    torch.manual_seed(5)
+    M = 2048
+    shapes = [(1024, 480), (512, 1024), (256, 512), (128, 256), (512, 16), (64, 72)]   # (N_out, K_in)
+    items, refs, bitems, brefs = [], [], [], []
+    for n_out, k_in in shapes:
+        ld = (k_in + 7) // 8 * 8
+        dy = (torch.randn(M, n_out, device="cuda") * 0.5).bfloat16()
+        xfull = (torch.randn(M, ld, device="cuda") * 0.5).bfloat16()
+        x = xfull[:, :k_in]
+        out = torch.zeros(n_out, k_in, device="cuda")
+        items.append((dy, x, out))
+        refs.append(dy.float().t() @ x.float())
+        db = torch.zeros(n_out, device="cuda")
+        bitems.append((dy, db))
+        brefs.append(dy.float().sum(0))
+    G.grouped_wgrad(items)
+    G.bias_grads(bitems)
+    G.check_gemm_errors()
+    for (_, _, out), ref in zip(items, refs):
+        assert torch.allclose(out, ref, rtol=2e-3, atol=2e-2), (out - ref).abs().max()
+    for (_, db), ref in zip(bitems, brefs):
+        assert torch.allclose(db, ref, rtol=1e-3, atol=1e-2)
+    # explicit split and a second call accumulating on top (the outputs are not re-zeroed)
+    G.grouped_wgrad(items[:3], split_k=3)
+    G.check_gemm_errors()
+    for (_, _, out), ref in zip(items[:3], refs[:3]):
+        assert torch.allclose(out, 2 * ref, rtol=2e-3, atol=4e-2)
