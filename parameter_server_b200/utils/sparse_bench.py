@@ -27,6 +27,7 @@ def main() -> None:
     ap.add_argument("--rows-per-gpu", type=int, default=1 << 24)
     ap.add_argument("--sizes", default="65536,262144,1048576,4194304")
     ap.add_argument("--impl", default="ours", choices=["ours", "nccl"])
+    ap.add_argument("--dim", type=int, default=64)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--phases", action="store_true", help="add rank 0's in-kernel phase times of one pull + push (fused path only)")
@@ -60,10 +61,10 @@ def main() -> None:
         return float(t.item())
 
     cls = SparseTable if a.impl == "ours" else NcclSparseTable
-    t = cls(64, "adagrad", dict(lr=0.05, init_accumulator=0.1), capacity=int(a.rows_per_gpu * 1.1) + nmax, max_keys=nmax, seed=3)
+    t = cls(a.dim, "adagrad", dict(lr=0.05, init_accumulator=0.1), capacity=int(a.rows_per_gpu * 1.1) + nmax, max_keys=nmax, seed=3)
     t.reserve(int(a.rows_per_gpu * 1.05) + 2 * nmax, exact=True)
-    out = torch.empty(nmax, 64, device=dev)
-    grads = torch.randn(nmax, 64, device=dev) * 1e-3
+    out = torch.empty(nmax, a.dim, device=dev)
+    grads = torch.randn(nmax, a.dim, device=dev) * 1e-3
     # populate: rank r inserts keys r, r + world, ...
     for lo in range(0, a.rows_per_gpu, nmax):
         n = min(nmax, a.rows_per_gpu - lo)
@@ -120,7 +121,7 @@ def main() -> None:
             phases.update({"Q3ab_elect_fold": round((st[11] - st[10]) / 1e3, 1), "Q3c_update": round((st[12] - st[11]) / 1e3, 1)})
         if rank == 0:
             print(json.dumps({"metric": "sparse_pull_push_keys_per_sec", "phases_us_rank0": phases, "impl": a.impl, "n_gpus": world, "keys_per_gpu_per_step": n,
-                              "table_rows_max_per_gpu": rows, "table_keys": K, "dim": 64, "optimizer": "adagrad", "zipf_s": 1.05,
+                              "table_rows_max_per_gpu": rows, "table_keys": K, "dim": a.dim, "optimizer": "adagrad", "zipf_s": 1.05,
                               "unique_fraction": uniq, "pull_ms": pull_ms, "pull_push_ms": both_ms,
                               "pull_keys_per_sec": n * world / (pull_ms / 1e3),
                               "pull_push_keys_per_sec": 2 * n * world / (both_ms / 1e3)}), flush=True)
