@@ -164,7 +164,12 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
         }
         __syncthreads();
         const unsigned total = s_pre[a.world];
-        for (unsigned e = tid; e < total; e += nthreads) {
+        // every rank starts with its right-hand neighbour and walks the ring, so that at any moment the ranks
+        // write to different peers (starting at peer 0 everywhere would funnel all traffic into one link)
+        const unsigned rot = s_pre[(me + 1) % a.world];
+        for (unsigned e0 = tid; e0 < total; e0 += nthreads) {
+            unsigned e = e0 + rot;
+            if (e >= total) e -= total;
             int o = 0;
             while (e >= s_pre[o + 1]) ++o;
             const unsigned p = e - s_pre[o];
@@ -256,16 +261,20 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
         }
     }
     if (a.world > 1 && (a.flags & FUSED_COPY_ROWS)) {
-        // remote requesters: one lane group per entry stores the row into the requester's buffer
-        for (unsigned e = group; e < total_in; e += ngroups) {
+        // remote requesters: one lane group per entry stores the row into the requester's buffer. The entries
+        // of the local requester are skipped, and every owner starts with the requester to its right and walks
+        // the ring: if all owners served requester 0 first, its one link would carry everything while the
+        // others idle.
+        const unsigned local_lo = s_pre[me], local_cnt = s_pre[me + 1] - s_pre[me];
+        const unsigned total_rem = total_in - local_cnt;
+        const int nxt = (me + 1) % a.world;
+        const unsigned rot = s_pre[nxt] - (nxt > me ? local_cnt : 0u);
+        for (unsigned e0 = group; e0 < total_rem; e0 += ngroups) {
+            unsigned e = e0 + rot;
+            if (e >= total_rem) e -= total_rem;
+            if (e >= local_lo) e += local_cnt;  // back to the index space that includes the local range
             int r = 0;
             while (e >= s_pre[r + 1]) ++r;
-            if (r == me) {
-                // skip the local range in one step
-                const unsigned skip = (s_pre[me + 1] - e + ngroups - 1) / ngroups;
-                e += (skip - 1) * ngroups;
-                continue;
-            }
             const unsigned p = e - s_pre[r];
             const unsigned slot = a.res_slot[(size_t)r * C + p];
             unsigned row = kNoRow;
@@ -469,7 +478,10 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
         }
         __syncthreads();
         const unsigned total = s_pre[a.world];
-        for (unsigned e = group; e < total; e += ngroups) {
+        const unsigned rot = s_pre[(me + 1) % a.world];  // ring order, see the key shipment of the pull
+        for (unsigned e0 = group; e0 < total; e0 += ngroups) {
+            unsigned e = e0 + rot;
+            if (e >= total) e -= total;
             int o = 0;
             while (e >= s_pre[o + 1]) ++o;
             const unsigned p = e - s_pre[o];

@@ -190,7 +190,8 @@ def exchange_by_keys(source: SparseTable, keys: torch.Tensor, send: List[int], i
         rounds = int(t.item())
     found = torch.empty(cap, dtype=torch.int32, device=comm.device)
     for i in range(rounds):
-        for d in range(world):
+        for step in range(world):
+            d = (rank + 1 + step) % world          # ring order: the ranks write to different peers at any moment
             n = min(cap, send[d] - i * cap)
             if n > 0:
                 ks = keys[offs[d] + i * cap: offs[d] + i * cap + n]
