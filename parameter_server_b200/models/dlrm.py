@@ -205,7 +205,17 @@ class DLRM:
         self.trace = None
         if prof is not None and hasattr(prof, "set_profile"):
             prof.set_profile(False)
-        return {k: round(statistics.median(v), 1) for k, v in acc.items()}
+        out = {k: round(statistics.median(v), 1) for k, v in acc.items()}
+        if prof is not None and hasattr(prof, "last_unique"):
+            # distinct keys of this rank's last pull, and the time their rows need on one NVLink direction
+            # (770 GB/s measured peer copy): the floor of the row-return phase of the pull and of the gradient
+            # shipment of the push when there is more than one rank
+            uniq = int(prof.last_unique(0))
+            w = self.sparse.world
+            out["unique_keys_last_pull"] = uniq
+            out["remote_row_bytes"] = int(uniq * (w - 1) / w * self.cfg.emb_dim * 4)
+            out["nvlink_floor_us_per_direction"] = round(out["remote_row_bytes"] / 770e9 * 1e6, 1)
+        return out
 
     def forward_backward(self) -> torch.Tensor:
         """One training step on the batch already in the device input buffers. Returns the device
