@@ -274,8 +274,13 @@ void bind_service(py::module_& m) {
             return py::make_tuple(st, out);
         }, py::arg("id"), py::arg("numel"), py::arg("timeout_ms") = -1);
 
+    py::class_<PushGroup, std::shared_ptr<PushGroup>>(m, "PushGroup")
+        .def(py::init<>())
+        .def("merged_sends", [](PushGroup& g) { return g.merged_sends.load(); })
+        .def("merged_requests", [](PushGroup& g) { return g.merged_requests.load(); });
     py::class_<PushHandler>(m, "PushHandler")
         .def(py::init(&make_handler<PushHandler>), py::keep_alive<1, 2>())
+        .def("join_group", &PushHandler::join_group)
         .def("metrics", [](PushHandler& h) { return metrics_dict(h); })
         .def("async_push", [](PushHandler& h, KeyArray keys, F32Array grads, int timeout_ms) {
             py::gil_scoped_release g;

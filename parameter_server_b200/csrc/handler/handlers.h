@@ -205,9 +205,29 @@ private:
     int tid_ = -1;
 };
 
+// Request-merge group of push handlers on different threads of one client (PushRequestDataGroup of
+// pico-ps/handler/PushHandler.h:20-27).
+struct PushGroup {
+    ThreadReduce reduce;
+    ThreadBcast bcast;
+    PushRequestData data[kThreadGroupSize];
+    RequestType type[kThreadGroupSize];  // async or sync push, per slot
+    Status status[kThreadGroupSize];
+    std::atomic<int> next_tid{0};
+    std::atomic<uint64_t> merged_sends{0}, merged_requests{0};
+};
+
 class PushHandler : public Handler {
 public:
     using Handler::Handler;
+    // Join a merge group (at most 32 handlers, one per thread). Returns the slot, or -1 when it is full.
+    int join_group(std::shared_ptr<PushGroup> g) {
+        int t = g->next_tid.fetch_add(1);
+        if (t >= kThreadGroupSize) return -1;
+        group_ = std::move(g);
+        tid_ = t;
+        return t;
+    }
     Status async_push(const int64_t* keys, const float* grads, size_t n, int timeout_ms = -1) {
         return push(keys, grads, n, RequestType::OP_PUSH_ASYNC, timeout_ms);
     }
@@ -241,6 +261,7 @@ private:
     Status push(const int64_t* keys, const float* grads, size_t n, RequestType type, int timeout_ms) {
         std::shared_ptr<SparseTablePushOperator> p;
         PSB_RETURN_IF_ERROR(op(&p));
+        if (group_) return with_retry([&](int left) { return merged_attempt(*p, keys, grads, n, type, left); }, timeout_ms);
         return with_retry([&](int left) -> Status {
             auto e = entry();
             PushRequestData data;
@@ -253,6 +274,57 @@ private:
             return client_->send_and_wait(sid_, hid_, type, reqs.body, left, nullptr);
         }, timeout_ms);
     }
+
+    // One attempt inside a merge group; requests of different kinds (async / sync) are not merged: a thread
+    // that finds another kind among the claimed slots sends one message per kind.
+    Status merged_attempt(SparseTablePushOperator& p, const int64_t* keys, const float* grads, size_t n, RequestType type,
+                          int left) {
+        PushGroup& g = *group_;
+        auto e = entry();
+        g.reduce.add(tid_);
+        PushRequestData& mine = g.data[tid_];
+        size_t nodes = 1, bytes = 0;
+        {
+            std::shared_lock<std::shared_mutex> lk(e->mu);
+            p.generate_request_data(*e, keys, grads, n, &mine);
+            nodes = std::max<size_t>(1, e->rt.nodes().size());
+        }
+        for (auto& kv : mine.shard_keys) bytes += kv.second.size() * 8 + mine.shard_grads[kv.first].size() * 4;
+        g.type[tid_] = type;
+        const int sync_num = bytes / nodes < PullHandler::kMergeBelowBytesPerNode ? 2 : 1;
+        const uint32_t tids = g.reduce.reduce(tid_, sync_num);
+        if (tids == 0) {
+            g.bcast.wait(tid_);
+            return g.status[tid_];
+        }
+        for (RequestType kind : {RequestType::OP_PUSH_ASYNC, RequestType::OP_PUSH_SYNC}) {
+            std::vector<PushRequestData*> ds;
+            uint32_t members = 0;
+            for (int t = 0; t < kThreadGroupSize; ++t)
+                if (((tids >> t) & 1u) && g.type[t] == kind) {
+                    ds.push_back(&g.data[t]);
+                    members |= 1u << t;
+                }
+            if (ds.empty()) continue;
+            Status st = [&]() -> Status {
+                NodeRequests reqs;
+                {
+                    std::shared_lock<std::shared_mutex> lk(e->mu);
+                    PSB_RETURN_IF_ERROR(p.generate_merged_requests(*e, ds, &reqs));
+                }
+                return client_->send_and_wait(sid_, hid_, kind, reqs.body, left, nullptr);
+            }();
+            ++g.merged_sends;
+            g.merged_requests += ds.size();
+            for (int t = 0; t < kThreadGroupSize; ++t)
+                if ((members >> t) & 1u) g.status[t] = st;
+        }
+        g.bcast.notify(tids, tid_);
+        return g.status[tid_];
+    }
+
+    std::shared_ptr<PushGroup> group_;
+    int tid_ = -1;
 };
 
 class ForEachHandler : public Handler {

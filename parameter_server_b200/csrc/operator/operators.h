@@ -303,6 +303,7 @@ private:
 struct PushRequestData {
     std::map<int32_t, std::vector<int64_t>> shard_keys;
     std::map<int32_t, std::vector<float>> shard_grads;
+    int32_t global_shard_num = 0;  // the partitioning these lists were built under
 };
 
 class SparseTablePushOperator : public Operator {
@@ -337,6 +338,7 @@ public:
         }
         d->shard_keys.clear();
         d->shard_grads.clear();
+        d->global_shard_num = G;
         for (size_t u = 0; u < uk.size(); ++u) {
             int32_t s = sop->shard_of(uk[u], G);
             d->shard_keys[s].push_back(uk[u]);
@@ -362,6 +364,45 @@ public:
                 ar << s << (int32_t)ks.size();
                 ar.write_raw(ks.data(), ks.size() * 8);
                 ar.write_raw(gs.data(), gs.size() * 4);
+            }
+            out->shards[kv.first] = kv.second;
+        }
+        return Status::Ok();
+    }
+
+    // Several threads' pushes in one message per node: the node's shard list is the union over the merged
+    // requests, every shard carries one item list per merged request (possibly empty).
+    Status generate_merged_requests(const TableEntry& e, const std::vector<PushRequestData*>& ds, NodeRequests* out) const {
+        std::map<int, std::vector<int32_t>> by_node;
+        std::map<int32_t, bool> seen;
+        for (auto* d : ds) {
+            if (d->global_shard_num != e.rt.global_shard_num())
+                return Status::ServerTooNewCtx("the context changed while push requests were being merged");
+            for (auto& kv : d->shard_keys) {
+                if (seen.count(kv.first)) continue;
+                seen[kv.first] = true;
+                auto it = e.rt.shards().find(kv.first);
+                if (it == e.rt.shards().end() || it->second.empty())
+                    return Status::NoReplica("no live holder of shard " + std::to_string(kv.first));
+                for (int node : it->second) by_node[node].push_back(kv.first);
+            }
+        }
+        static const std::vector<int64_t> no_keys;
+        static const std::vector<float> no_grads;
+        for (auto& kv : by_node) {
+            std::sort(kv.second.begin(), kv.second.end());
+            Archive& ar = out->body[kv.first];
+            ar << (int32_t)kv.second.size() << (int32_t)ds.size();
+            for (int32_t s : kv.second) {
+                ar << s;
+                for (auto* d : ds) {
+                    auto it = d->shard_keys.find(s);
+                    const auto& ks = it == d->shard_keys.end() ? no_keys : it->second;
+                    const auto& gs = it == d->shard_keys.end() ? no_grads : d->shard_grads.at(s);
+                    ar << (int32_t)ks.size();
+                    ar.write_raw(ks.data(), ks.size() * 8);
+                    ar.write_raw(gs.data(), gs.size() * 4);
+                }
             }
             out->shards[kv.first] = kv.second;
         }

@@ -20,6 +20,7 @@ ServerConfig = C.ServerConfig
 Client = C.Client
 PullHandler = C.PullHandler
 PullGroup = C.PullGroup
+PushGroup = C.PushGroup
 PushHandler = C.PushHandler
 ForEachHandler = C.ForEachHandler
 EraseIfHandler = C.EraseIfHandler

@@ -541,3 +541,32 @@ def test_pull_requests_of_threads_are_merged(cluster3):
     assert not bad and not any(t.is_alive() for t in ts)
     assert group.merged_requests() == T * 30
     assert group.merged_sends() < group.merged_requests()      # some requests did share a message
+
+
+def test_push_requests_of_threads_are_merged(cluster3):
+    """Small pushes of handlers on different threads share messages; every gradient is applied exactly once."""
+    cl = cluster3
+    sid, h = make_table(cl, uneven(cl.ids()))
+    group = S.PushGroup()
+    T = 4
+    hs = [S.PushHandler(cl.client, sid, h["push"]) for _ in range(T)]
+    assert [x.join_group(group) for x in hs] == list(range(T))
+    rng = np.random.default_rng(1)
+    batches = [[rng.integers(0, 3000, size=200).astype(np.int64) for _ in range(25)] for _ in range(T)]
+    bad = []
+
+    def work(t):
+        for b in batches[t]:
+            st = hs[t].async_push(b, np.ones((len(b), DIM), dtype=np.float32))
+            if not st.ok():
+                bad.append((t, str(st)))
+
+    ts = [threading.Thread(target=work, args=(t,)) for t in range(T)]
+    [t.start() for t in ts]
+    [t.join(60) for t in ts]
+    assert not bad and not any(t.is_alive() for t in ts)
+    assert group.merged_requests() == T * 25 and group.merged_sends() < group.merged_requests()
+    counts = np.bincount(np.concatenate([b for bs in batches for b in bs]), minlength=3000).astype(np.float32)
+    keys = np.arange(3000, dtype=np.int64)
+    st, rows = S.PullHandler(cl.client, sid, h["pull_ro"]).pull(keys)
+    assert st.ok() and np.array_equal(rows, counts[:, None] * np.ones((1, DIM), dtype=np.float32))
