@@ -156,6 +156,7 @@ void bind_service(py::module_& m) {
         .def("exited", &Server::exited)
         .def("stop", &Server::stop, nogil())
         .def("metrics", &Server::metrics)
+        .def("metrics_text", &Server::metrics_text)
         .def("restore_storages", [](Server& s) { int n = 0; Status st = s.restore_storages(&n); return std::make_tuple(st, n); }, nogil())
         .def("enable_sync", &Server::enable_sync)
         .def("push_sync_table", [](Server& s, int32_t sid, SyncHandler& h) {

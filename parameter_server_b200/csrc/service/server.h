@@ -41,6 +41,9 @@ struct NodeMemoryInfo {
 
 inline std::string ctx_key(int32_t sid) { return "storage/" + std::to_string(sid); }
 
+constexpr int kDurationBuckets = 10;
+constexpr double kDurationBoundsMs[kDurationBuckets] = {0.05, 0.1, 0.25, 0.5, 1, 2.5, 5, 10, 50, 250};
+
 class Server {
 public:
     Server(const std::string& master_addr, const ServerConfig& cfg = ServerConfig())
@@ -72,6 +75,34 @@ public:
     }
 
     // Counters in the spirit of ps_requests_total / ps_errors_total (pico-ps/service/Service.cpp:23-33).
+    // Prometheus text exposition of the per-request series.
+    std::string metrics_text() {
+        std::lock_guard<std::mutex> g(metric_mu_);
+        std::string out;
+        auto labels = [&](const std::pair<std::string, int32_t>& k) {
+            return "{node_id=\"" + std::to_string(node_id_) + "\",request_type=\"" + k.first + "\",storage_id=\"" + std::to_string(k.second) + "\"";
+        };
+        out += "# TYPE ps_requests_total counter\n";
+        for (auto& kv : series_) out += "ps_requests_total" + labels(kv.first) + "} " + std::to_string(kv.second.requests) + "\n";
+        out += "# TYPE ps_errors_total counter\n";
+        for (auto& kv : series_) out += "ps_errors_total" + labels(kv.first) + "} " + std::to_string(kv.second.errors) + "\n";
+        out += "# TYPE ps_requests_size_bytes counter\n";
+        for (auto& kv : series_) out += "ps_requests_size_bytes" + labels(kv.first) + "} " + std::to_string(kv.second.req_bytes) + "\n";
+        out += "# TYPE ps_response_size_bytes counter\n";
+        for (auto& kv : series_) out += "ps_response_size_bytes" + labels(kv.first) + "} " + std::to_string(kv.second.resp_bytes) + "\n";
+        out += "# TYPE ps_request_duration_ms histogram\n";
+        for (auto& kv : series_) {
+            uint64_t cum = 0;
+            for (int b = 0; b <= kDurationBuckets; ++b) {
+                cum += kv.second.buckets[b];
+                const std::string le = b < kDurationBuckets ? std::to_string(kDurationBoundsMs[b]) : "+Inf";
+                out += "ps_request_duration_ms_bucket" + labels(kv.first) + ",le=\"" + le + "\"} " + std::to_string(cum) + "\n";
+            }
+            out += "ps_request_duration_ms_sum" + labels(kv.first) + "} " + std::to_string(kv.second.sum_ms) + "\n";
+            out += "ps_request_duration_ms_count" + labels(kv.first) + "} " + std::to_string(kv.second.requests) + "\n";
+        }
+        return out;
+    }
     std::map<std::string, uint64_t> metrics() {
         std::lock_guard<std::mutex> g(metric_mu_);
         return metrics_;
@@ -166,19 +197,44 @@ private:
         std::lock_guard<std::mutex> g(metric_mu_);
         ++metrics_[name];
     }
+    // Per (request type, storage) series in the spirit of ps_requests_total / ps_requests_size_bytes /
+    // ps_response_size_bytes / ps_errors_total / ps_request_duration_ms_bucket
+    // (pico-ps/service/Service.cpp:23-33).
+    struct Series {
+        uint64_t requests = 0, errors = 0, req_bytes = 0, resp_bytes = 0;
+        double sum_ms = 0;
+        uint64_t buckets[kDurationBuckets + 1] = {};
+    };
+    void observe(const std::string& type, int32_t sid, size_t req_bytes, size_t resp_bytes, bool error, double ms) {
+        std::lock_guard<std::mutex> g(metric_mu_);
+        Series& x = series_[{type, sid}];
+        ++x.requests;
+        x.errors += error ? 1 : 0;
+        x.req_bytes += req_bytes;
+        x.resp_bytes += resp_bytes;
+        x.sum_ms += ms;
+        int b = 0;
+        while (b < kDurationBuckets && ms > kDurationBoundsMs[b]) ++b;
+        ++x.buckets[b];
+    }
 
     void dispatch(Bytes&& bytes, RpcServer::Responder resp, bool s2s) {
         PSMessage msg = PSMessage::open(std::move(bytes));
         const PSMessageMeta meta = msg.meta;
         Archive out;
         Status st;
-        count(std::string(s2s ? "s2s_" : "c2s_") + request_type_name(meta.req_type));
+        const std::string label = std::string(s2s ? "s2s_" : "c2s_") + request_type_name(meta.req_type);
+        count(label);
+        const size_t req_bytes = msg.ar.size();
+        const auto t0 = std::chrono::steady_clock::now();
         try {
             st = process(msg, &out, s2s);
         } catch (const std::exception& ex) {
             st = Status::Error(std::string("server exception: ") + ex.what());
         }
         if (!st.ok()) count("errors_total");
+        observe(label, meta.sid, req_bytes, out.size(), !st.ok(),
+                std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count());
         resp.send(reply(st, &out, meta));
         if (meta.req_type == RequestType::EXIT) {
             exited_ = true;
@@ -713,6 +769,7 @@ private:
     std::atomic<bool> stopped_{false}, exited_{false};
     std::mutex metric_mu_;
     std::map<std::string, uint64_t> metrics_;
+    std::map<std::pair<std::string, int32_t>, Series> series_;
 };
 
 }  // namespace psb

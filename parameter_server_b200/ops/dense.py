@@ -20,6 +20,7 @@ import torch
 from .._lib import C
 from ..utils.status import raise_if_error
 from .optim import make_opt_config, set_adam_step
+from ..utils.trace import nvtx
 from .sparse import _dist_info, _stream
 
 
@@ -132,7 +133,8 @@ class DenseTable:
             set_adam_step(self.opt, self.step_count)
         scale = (1.0 / self.world) if grad_scale is None else grad_scale
         if self.is_cuda:
-            raise_if_error(self.engine.step(self.opt, scale, _stream()))
+            with nvtx("ps.dense_push"):
+                raise_if_error(self.engine.step(self.opt, scale, _stream()))
             return
         g = self.flat_grads
         if self.world > 1:

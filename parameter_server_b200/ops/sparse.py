@@ -18,6 +18,7 @@ import torch
 
 from .._lib import C
 from ..utils.status import StatusError, raise_if_error
+from ..utils.trace import nvtx
 from .optim import OPTIMIZERS, make_opt_config, set_adam_step
 
 
@@ -161,7 +162,9 @@ class SparseTable:
                 flags |= C.FUSED_PREPARE_PUSH
             if mean:
                 flags |= C.FUSED_MEAN
-            st = self.engine.pull(keys.data_ptr(), n, bag_size, out.data_ptr(), flags, _stream())
+            with nvtx("ps.sparse_pull"):
+                with nvtx("ps.sparse_pull"):
+                st = self.engine.pull(keys.data_ptr(), n, bag_size, out.data_ptr(), flags, _stream())
             raise_if_error(st)
             self._plan_keys = keys  # keep the key buffer alive until the push
             return out
@@ -201,7 +204,8 @@ class SparseTable:
                 grads = grads.float()
             grads = grads.contiguous()
             flags = C.FUSED_SYNC_PUSH if sync else 0
-            raise_if_error(self.engine.push(grads.data_ptr(), self.opt, flags, _stream()))
+            with nvtx("ps.sparse_push"):
+                raise_if_error(self.engine.push(grads.data_ptr(), self.opt, flags, _stream()))
             self._last_grads = grads  # keep alive until the kernel ran
         else:
             k, bag, mn = self._plan_keys

@@ -570,3 +570,25 @@ def test_push_requests_of_threads_are_merged(cluster3):
     keys = np.arange(3000, dtype=np.int64)
     st, rows = S.PullHandler(cl.client, sid, h["pull_ro"]).pull(keys)
     assert st.ok() and np.array_equal(rows, counts[:, None] * np.ones((1, DIM), dtype=np.float32))
+
+
+def test_prometheus_metrics_endpoint(cluster3):
+    import urllib.request
+    from parameter_server_b200.service.metrics import handler_metrics_text, serve_metrics
+    cl = cluster3
+    sid, h = make_table(cl, uneven(cl.ids()))
+    push, pull = S.PushHandler(cl.client, sid, h["push"]), S.PullHandler(cl.client, sid, h["pull_ro"])
+    keys = np.arange(500, dtype=np.int64)
+    assert push.async_push(keys, np.ones((500, DIM), np.float32)).ok()
+    assert pull.pull(keys)[0].ok()
+    httpd, port = serve_metrics(cl.servers[0], 0, [sid])
+    try:
+        text = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5).read().decode()
+    finally:
+        httpd.shutdown()
+    node = cl.servers[0].node_id()
+    assert f'ps_requests_total{{node_id="{node}",request_type="c2s_OP_PULL",storage_id="{sid}"}} 1' in text
+    assert f'ps_requests_total{{node_id="{node}",request_type="c2s_OP_PUSH_ASYNC",storage_id="{sid}"}} 1' in text
+    assert 'ps_request_duration_ms_bucket' in text and 'le="+Inf"' in text and "ps_response_size_bytes" in text
+    assert f'ps_storage_items{{node_id="{node}",storage_id="{sid}"}}' in text
+    assert "ps_wait_request_count" in handler_metrics_text(pull, "pull")
