@@ -163,7 +163,6 @@ class SparseTable:
             if mean:
                 flags |= C.FUSED_MEAN
             with nvtx("ps.sparse_pull"):
-                with nvtx("ps.sparse_pull"):
                 st = self.engine.pull(keys.data_ptr(), n, bag_size, out.data_ptr(), flags, _stream())
             raise_if_error(st)
             self._plan_keys = keys  # keep the key buffer alive until the push
