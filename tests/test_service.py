@@ -294,10 +294,15 @@ def test_ha_dead_node_detection_and_restore(tmp_path):
         assert sum(s.storage_size(sid) for s in cl.servers) == 6000
         # node 1 dies (host-side fault: the process' server object is stopped)
         cl.servers[1].stop()
-        st, rows = pull.pull(keys, 20000, True)              # timeout -> dead-node detection -> other replica
-        assert st.ok() and np.array_equal(rows, vals)
+        # a pull picks one replica per shard at random: it meets the dead node after a few pulls at most, then
+        # timeout -> dead-node detection -> retry on the other replica, all inside the handler
         td = S.TableDescriptor()
-        td.from_json_str(S.MasterClient(cl.master.address()).get_context(f"storage/{sid}")[1])
+        for _ in range(64):
+            st, rows = pull.pull(keys, 20000, True)
+            assert st.ok() and np.array_equal(rows, vals)
+            td.from_json_str(S.MasterClient(cl.master.address()).get_context(f"storage/{sid}")[1])
+            if td.node_status()[ids[1]] == 1:
+                break
         assert td.node_status()[ids[1]] == 1                 # DEAD, published on the master
         # a fresh server takes over the dead node's shards from the live replicas
         fresh = S.Server(cl.master.address())
