@@ -177,6 +177,8 @@ PYBIND11_MODULE(_C, m) {
         .def("spill_if", [](HostColdTier& c, uint32_t section, float thr) { uint64_t n = 0; Status st = c.spill_if(section, thr, &n); return py::make_tuple(st, n); })
         .def("spill_keys", [](HostColdTier& c, uintptr_t keys, uint64_t n) { uint64_t k = 0; Status st = c.spill_keys((const int64_t*)keys, n, &k); return py::make_tuple(st, k); })
         .def("fetch", [](HostColdTier& c, uintptr_t keys, uint64_t n) { uint64_t k = 0; Status st = c.fetch((const int64_t*)keys, n, &k); return py::make_tuple(st, k); })
+        .def("stage_fetch_async", [](HostColdTier& c, uintptr_t keys, uint64_t n) { c.stage_fetch_async((const int64_t*)keys, n); })
+        .def("commit_fetch", [](HostColdTier& c, uintptr_t stream) { uint64_t k = 0; Status st = c.commit_fetch(stream_of(stream), &k); return py::make_tuple(st, k); })
         .def("size", &HostColdTier::size)
         .def("capacity", &HostColdTier::capacity)
         .def("bytes", &HostColdTier::bytes)

@@ -19,6 +19,9 @@ HostColdTier::HostColdTier(GpuTable* table, uint64_t capacity_rows, uint32_t win
     cudaStream_t s;
     must(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "side stream");
     stream_ = s;
+    cudaEvent_t ev;
+    must(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "event");
+    copied_ = ev;
     must(cudaMalloc(&d_keys_, (size_t)window_ * 8), "staging");
     must(cudaMalloc(&d_rows_, (size_t)window_ * stride_ * 4), "staging");
     must(cudaHostAlloc((void**)&h_keys_, (size_t)window_ * 8, cudaHostAllocDefault), "staging");
@@ -27,7 +30,9 @@ HostColdTier::HostColdTier(GpuTable* table, uint64_t capacity_rows, uint32_t win
 
 HostColdTier::~HostColdTier() {
     cudaSetDevice(table_->device());
+    if (staging_active_) staging_.wait();
     cudaStreamSynchronize((cudaStream_t)stream_);
+    cudaEventDestroy((cudaEvent_t)copied_);
     cudaFree(d_keys_);
     cudaFree(d_rows_);
     cudaFreeHost(h_keys_);
@@ -57,6 +62,7 @@ Status HostColdTier::store_row(int64_t key, const float* row) {
 }
 
 Status HostColdTier::spill_if(uint32_t section, float threshold, uint64_t* n_spilled) {
+    if (staging_active_) staging_.wait();  // the worker thread owns the map and the staging buffers until it is done
     cudaSetDevice(table_->device());
     cudaStream_t s = (cudaStream_t)stream_;
     *n_spilled = 0;
@@ -96,6 +102,7 @@ Status HostColdTier::spill_if(uint32_t section, float threshold, uint64_t* n_spi
 }
 
 Status HostColdTier::spill_keys(const int64_t* keys, uint64_t n, uint64_t* n_spilled) {
+    if (staging_active_) staging_.wait();  // the worker thread owns the map and the staging buffers until it is done
     cudaSetDevice(table_->device());
     cudaStream_t s = (cudaStream_t)stream_;
     *n_spilled = 0;
@@ -130,6 +137,7 @@ Status HostColdTier::spill_keys(const int64_t* keys, uint64_t n, uint64_t* n_spi
 }
 
 Status HostColdTier::fetch(const int64_t* keys, uint64_t n, uint64_t* n_fetched) {
+    if (staging_active_) staging_.wait();  // the worker thread owns the map and the staging buffers until it is done
     cudaSetDevice(table_->device());
     cudaStream_t s = (cudaStream_t)stream_;
     *n_fetched = 0;
@@ -153,6 +161,46 @@ Status HostColdTier::fetch(const int64_t* keys, uint64_t n, uint64_t* n_fetched)
         if (++m == window_) PSB_RETURN_IF_ERROR(flush());
     }
     return flush();
+}
+
+void HostColdTier::stage_fetch_async(const int64_t* keys, uint64_t n) {
+    if (staging_active_) staging_.wait();
+    std::vector<int64_t> copy(keys, keys + n);  // the caller's buffer may go away
+    staging_active_ = true;
+    staging_ = std::async(std::launch::async, [this, copy = std::move(copy)]() -> uint64_t {
+        cudaSetDevice(table_->device());
+        cudaStream_t s = (cudaStream_t)stream_;
+        uint64_t m = 0;
+        for (uint64_t i = 0; i < copy.size() && m < window_; ++i) {
+            auto* e = map_.find(copy[i]);
+            if (!e) continue;
+            h_keys_[m] = copy[i];
+            std::memcpy(h_rows_ + m * stride_, pool_ + (size_t)e->second * stride_, (size_t)stride_ * 4);
+            free_.push_back(e->second);
+            map_.erase(copy[i]);
+            ++m;
+        }
+        if (m) {
+            cudaMemcpyAsync(d_keys_, h_keys_, m * 8, cudaMemcpyHostToDevice, s);
+            cudaMemcpyAsync(d_rows_, h_rows_, m * (size_t)stride_ * 4, cudaMemcpyHostToDevice, s);
+        }
+        cudaEventRecord((cudaEvent_t)copied_, s);
+        return m;
+    });
+}
+
+Status HostColdTier::commit_fetch(void* stream, uint64_t* n_fetched) {
+    *n_fetched = 0;
+    if (!staging_active_) return Status::Ok();
+    const uint64_t m = staging_.get();
+    staging_active_ = false;
+    if (m == 0) return Status::Ok();
+    cudaSetDevice(table_->device());
+    if (cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)copied_, 0) != cudaSuccess)
+        return Status::Error("cold tier: cudaStreamWaitEvent failed");
+    PSB_RETURN_IF_ERROR(table_->set_rows(d_keys_, d_rows_, m, false, stream));
+    *n_fetched = m;
+    return Status::Ok();
 }
 
 Status HostColdTier::save(const std::string& path, const std::string& version_uuid) const {

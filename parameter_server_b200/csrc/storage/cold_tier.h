@@ -9,6 +9,7 @@
 // (pico-ps/storage/DCPmemory.h:493-507).
 #pragma once
 #include <cstdint>
+#include <future>
 #include <string>
 #include <vector>
 
@@ -32,6 +33,14 @@ public:
     // Bring back the rows of `keys` that live in the cold tier (call before pulling those keys).
     Status fetch(const int64_t* keys, uint64_t n, uint64_t* n_fetched);
 
+    // Asynchronous fetch in two steps, so that the host-side gather and the PCIe copy of the NEXT batch's cold
+    // rows overlap the current training step: stage_fetch_async returns at once (a worker thread looks the keys
+    // up, packs at most `window` rows into pinned staging and starts their copy on the side stream);
+    // commit_fetch joins the worker, makes `stream` wait for the copy and inserts the rows with a kernel on
+    // `stream` (call it between two steps, before the pull that needs the rows).
+    void stage_fetch_async(const int64_t* keys, uint64_t n);
+    Status commit_fetch(void* stream, uint64_t* n_fetched);
+
     uint64_t size() const { return map_.size(); }
     uint64_t capacity() const { return capacity_; }
     uint64_t bytes() const { return capacity_ * (uint64_t)stride_ * 4; }
@@ -51,6 +60,9 @@ private:
     void* stream_ = nullptr;          // side stream
     long long* d_keys_ = nullptr;     // device staging
     float* d_rows_ = nullptr;
+    std::future<uint64_t> staging_;   // rows staged by the worker thread
+    bool staging_active_ = false;
+    void* copied_ = nullptr;          // event: staged rows are on the device
     int64_t* h_keys_ = nullptr;       // pinned staging
     float* h_rows_ = nullptr;
 };

@@ -342,6 +342,20 @@ class SparseTable:
         raise_if_error(st)
         return int(n)
 
+    def prefetch_cold_async(self, keys: torch.Tensor) -> None:
+        """Start bringing back the cold rows among ``keys`` (at most one staging window of them) without
+        blocking: lookup, packing and the host-to-device copy run on a worker thread and a side stream while
+        the current step computes. ``commit_prefetch()`` inserts them."""
+        k = keys.reshape(-1).cpu().contiguous()
+        self.cold.stage_fetch_async(k.data_ptr(), k.numel())
+
+    def commit_prefetch(self) -> int:
+        """Insert the rows staged by ``prefetch_cold_async`` (call between two steps, before the pull that
+        needs them). Returns how many rows came back."""
+        st, n = self.cold.commit_fetch(_stream())
+        raise_if_error(st)
+        return int(n)
+
     def clear(self) -> None:
         if self.is_cuda:
             raise_if_error(self.table.clear(_stream()))

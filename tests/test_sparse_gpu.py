@@ -199,6 +199,14 @@ def test_cold_tier_spill_fetch_and_persistence(tmp_path):
     assert found.all()
     assert torch.equal(rows, torch.cat([full[:100], full[4000:4500]]))
     assert t.spill_keys(hot[:10]) == 10 and t.size() == 4490
+    # asynchronous prefetch of the next batch's cold rows: staged off the critical path, inserted between steps
+    nxt = torch.cat([cold[1000:1300], hot[:10]]).cpu()
+    t.prefetch_cold_async(nxt)
+    t.pull(hot[100:200]); t.push(torch.zeros(100, 32, device="cuda"))     # the current step keeps running
+    assert t.commit_prefetch() == 310 and t.size() == 4800
+    rows, found = t.get_rows(cold[1000:1300], emb_only=False)
+    assert found.all() and torch.equal(rows, full[5000:5300])
+    t.check()
 
 
 def test_collective_dump_load_rehash_and_rpc_codec(tmp_path):
