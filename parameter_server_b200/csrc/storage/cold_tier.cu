@@ -62,7 +62,8 @@ Status HostColdTier::store_row(int64_t key, const float* row) {
 }
 
 Status HostColdTier::spill_if(uint32_t section, float threshold, uint64_t* n_spilled) {
-    if (staging_active_) staging_.wait();  // the worker thread owns the map and the staging buffers until it is done
+    // staged rows live only in the staging buffers until commit_fetch inserts them
+    if (staging_active_) return Status::Error("cold tier: a staged prefetch is pending, call commit_fetch first");
     cudaSetDevice(table_->device());
     cudaStream_t s = (cudaStream_t)stream_;
     *n_spilled = 0;
@@ -102,7 +103,8 @@ Status HostColdTier::spill_if(uint32_t section, float threshold, uint64_t* n_spi
 }
 
 Status HostColdTier::spill_keys(const int64_t* keys, uint64_t n, uint64_t* n_spilled) {
-    if (staging_active_) staging_.wait();  // the worker thread owns the map and the staging buffers until it is done
+    // staged rows live only in the staging buffers until commit_fetch inserts them
+    if (staging_active_) return Status::Error("cold tier: a staged prefetch is pending, call commit_fetch first");
     cudaSetDevice(table_->device());
     cudaStream_t s = (cudaStream_t)stream_;
     *n_spilled = 0;
@@ -137,7 +139,8 @@ Status HostColdTier::spill_keys(const int64_t* keys, uint64_t n, uint64_t* n_spi
 }
 
 Status HostColdTier::fetch(const int64_t* keys, uint64_t n, uint64_t* n_fetched) {
-    if (staging_active_) staging_.wait();  // the worker thread owns the map and the staging buffers until it is done
+    // staged rows live only in the staging buffers until commit_fetch inserts them
+    if (staging_active_) return Status::Error("cold tier: a staged prefetch is pending, call commit_fetch first");
     cudaSetDevice(table_->device());
     cudaStream_t s = (cudaStream_t)stream_;
     *n_fetched = 0;
@@ -164,7 +167,7 @@ Status HostColdTier::fetch(const int64_t* keys, uint64_t n, uint64_t* n_fetched)
 }
 
 void HostColdTier::stage_fetch_async(const int64_t* keys, uint64_t n) {
-    if (staging_active_) staging_.wait();
+    if (staging_active_) return;  // one staged batch at a time: commit_fetch first
     std::vector<int64_t> copy(keys, keys + n);  // the caller's buffer may go away
     staging_active_ = true;
     staging_ = std::async(std::launch::async, [this, copy = std::move(copy)]() -> uint64_t {
