@@ -117,7 +117,8 @@ def reexec_under_torchrun(args) -> None:
 def main():
     args = parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REF_UNAVAILABLE}))
+        if int(os.environ.get("RANK", "0")) == 0:   # one line, also when launched once per GPU
+            print(json.dumps({"impl": "reference", "unavailable": REF_UNAVAILABLE}))
         return
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
         reexec_under_torchrun(args)
