@@ -28,6 +28,7 @@
 #include <algorithm>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "gemm_tcgen05.h"
@@ -376,6 +377,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *((volatile uint32_t*)tmem_slot);
+    // Programmatic dependent launch: everything above (barriers, TMEM) touched no global memory, so it may
+    // run while the previous kernel of the stream drains; from here on its results are needed. Without the
+    // launch attribute both instructions do nothing.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -554,6 +560,14 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, 
     return r == CUDA_SUCCESS;
 }
 
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("PSB_GEMM_PDL");
+        return e != nullptr && e[0] != '\0' && e[0] != '0';
+    }();
+    return on;
+}
+
 template <int BN, bool AMN, bool BMN>
 cudaError_t launch_variant(const GemmProblemSet& ps, unsigned* err, unsigned long long limit_ns, cudaStream_t s,
                            const GemmGather& ag) {
@@ -573,9 +587,17 @@ cudaError_t launch_variant(const GemmProblemSet& ps, unsigned* err, unsigned lon
     const int units = ps.unit_end[ps.count - 1];
     int ctas = units < num_sms ? units : num_sms;
     if (ag.enabled) ctas = std::max(ag.gather_ctas + 1, std::min(num_sms, units + ag.gather_ctas));
-    dim3 grid(ctas);
-    kern<<<grid, kThreads, SmemLayout<BN>::kTotal, s>>>(ps, err, limit_ns, ag);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = SmemLayout<BN>::kTotal;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() && !ag.enabled ? 1 : 0;  // the prologue of this launch may overlap the previous kernel's tail
+    return cudaLaunchKernelEx(&cfg, kern, ps, err, limit_ns, ag);
 }
 
 cudaError_t dispatch(int BN, bool a_mn, bool b_mn, const GemmProblemSet& ps, unsigned* err, unsigned long long lim,
