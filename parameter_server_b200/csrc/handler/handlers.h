@@ -212,6 +212,7 @@ struct PushGroup {
     ThreadBcast bcast;
     PushRequestData data[kThreadGroupSize];
     RequestType type[kThreadGroupSize];  // async or sync push, per slot
+    PushAckState* ack[kThreadGroupSize] = {};  // progress of each member's push across its retries
     Status status[kThreadGroupSize];
     std::atomic<int> next_tid{0};
     std::atomic<uint64_t> merged_sends{0}, merged_requests{0};
@@ -261,7 +262,8 @@ private:
     Status push(const int64_t* keys, const float* grads, size_t n, RequestType type, int timeout_ms) {
         std::shared_ptr<SparseTablePushOperator> p;
         PSB_RETURN_IF_ERROR(op(&p));
-        if (group_) return with_retry([&](int left) { return merged_attempt(*p, keys, grads, n, type, left); }, timeout_ms);
+        PushAckState ack;  // lives for this call: what the retries need not send again
+        if (group_) return with_retry([&](int left) { return merged_attempt(*p, keys, grads, n, type, left, &ack); }, timeout_ms);
         return with_retry([&](int left) -> Status {
             auto e = entry();
             PushRequestData data;
@@ -269,16 +271,22 @@ private:
             {
                 std::shared_lock<std::shared_mutex> g(e->mu);
                 p->generate_request_data(*e, keys, grads, n, &data);  // regenerated against the fresh context on retry
-                PSB_RETURN_IF_ERROR(p->generate_requests(*e, data, &reqs));
+                if (ack.G != data.global_shard_num) ack.reset(data.global_shard_num);  // other shard count: start over
+                PSB_RETURN_IF_ERROR(p->generate_requests(*e, data, &reqs, &ack));
             }
-            return client_->send_and_wait(sid_, hid_, type, reqs.body, left, nullptr);
+            if (reqs.body.empty()) return Status::Ok();  // everything was applied by earlier attempts
+            std::vector<NodeResponse> rs;
+            Status st = client_->send_and_wait(sid_, hid_, type, reqs.body, left, &rs);
+            for (auto& r : rs)
+                for (int32_t sh : reqs.shards[r.node]) ack.record(sh, r.node, r.status.ok());
+            return st;
         }, timeout_ms);
     }
 
     // One attempt inside a merge group; requests of different kinds (async / sync) are not merged: a thread
     // that finds another kind among the claimed slots sends one message per kind.
     Status merged_attempt(SparseTablePushOperator& p, const int64_t* keys, const float* grads, size_t n, RequestType type,
-                          int left) {
+                          int left, PushAckState* ack) {
         PushGroup& g = *group_;
         auto e = entry();
         g.reduce.add(tid_);
@@ -291,6 +299,8 @@ private:
         }
         for (auto& kv : mine.shard_keys) bytes += kv.second.size() * 8 + mine.shard_grads[kv.first].size() * 4;
         g.type[tid_] = type;
+        if (ack->G != mine.global_shard_num) ack->reset(mine.global_shard_num);
+        g.ack[tid_] = ack;
         const int sync_num = bytes / nodes < PullHandler::kMergeBelowBytesPerNode ? 2 : 1;
         const uint32_t tids = g.reduce.reduce(tid_, sync_num);
         if (tids == 0) {
@@ -299,20 +309,30 @@ private:
         }
         for (RequestType kind : {RequestType::OP_PUSH_ASYNC, RequestType::OP_PUSH_SYNC}) {
             std::vector<PushRequestData*> ds;
+            std::vector<PushAckState*> acks;
             uint32_t members = 0;
             for (int t = 0; t < kThreadGroupSize; ++t)
                 if (((tids >> t) & 1u) && g.type[t] == kind) {
                     ds.push_back(&g.data[t]);
+                    acks.push_back(g.ack[t]);
                     members |= 1u << t;
                 }
             if (ds.empty()) continue;
             Status st = [&]() -> Status {
                 NodeRequests reqs;
+                std::vector<std::vector<std::pair<int, int32_t>>> sent;
                 {
                     std::shared_lock<std::shared_mutex> lk(e->mu);
-                    PSB_RETURN_IF_ERROR(p.generate_merged_requests(*e, ds, &reqs));
+                    PSB_RETURN_IF_ERROR(p.generate_merged_requests(*e, ds, acks, &reqs, &sent));
                 }
-                return client_->send_and_wait(sid_, hid_, kind, reqs.body, left, nullptr);
+                if (reqs.body.empty()) return Status::Ok();
+                std::vector<NodeResponse> rs;
+                Status sst = client_->send_and_wait(sid_, hid_, kind, reqs.body, left, &rs);
+                std::map<int, bool> node_ok;
+                for (auto& r : rs) node_ok[r.node] = r.status.ok();
+                for (size_t i = 0; i < ds.size(); ++i)   // the members sleep until the broadcast: their state is ours to update
+                    for (auto& ns : sent[i]) acks[i]->record(ns.second, ns.first, node_ok[ns.first]);
+                return sst;
             }();
             ++g.merged_sends;
             g.merged_requests += ds.size();

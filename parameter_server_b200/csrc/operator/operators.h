@@ -300,6 +300,33 @@ private:
 };
 
 // ---------------------------------------------------------------------------------------------------
+// What a push has achieved so far, kept across the retries of ONE push call so that a retry resends only what
+// no server applied. A push fans out to several nodes; when some of them apply it and another refuses (it
+// already switched to a newer context, or it blocks writes during a reshard) the reference resends the whole
+// request and the first nodes apply it twice. Here a (shard, node) pair that answered OK is never sent again, a
+// node that was a target and did not answer OK is retried while it still holds the shard, and a node that
+// received the shard through a reshard in between is skipped: the rows it was given already contain the update.
+struct PushAckState {
+    int32_t G = -1;
+    std::map<int32_t, std::set<int>> targeted, acked;
+    void reset(int32_t g) {
+        G = g;
+        targeted.clear();
+        acked.clear();
+    }
+    bool wants(int32_t shard, int node) const {
+        auto a = acked.find(shard);
+        if (a == acked.end() || a->second.empty()) return true;
+        if (a->second.count(node)) return false;
+        auto t = targeted.find(shard);
+        return t != targeted.end() && t->second.count(node) > 0;
+    }
+    void record(int32_t shard, int node, bool ok) {
+        targeted[shard].insert(node);
+        if (ok) acked[shard].insert(node);
+    }
+};
+
 struct PushRequestData {
     std::map<int32_t, std::vector<int64_t>> shard_keys;
     std::map<int32_t, std::vector<float>> shard_grads;
@@ -347,13 +374,15 @@ public:
         }
     }
     // every node that hosts a touched shard gets that shard's items (all replicas are updated)
-    Status generate_requests(const TableEntry& e, const PushRequestData& d, NodeRequests* out) const {
+    Status generate_requests(const TableEntry& e, const PushRequestData& d, NodeRequests* out,
+                             const PushAckState* ack = nullptr) const {
         std::map<int, std::vector<int32_t>> by_node;
         for (auto& kv : d.shard_keys) {
             auto it = e.rt.shards().find(kv.first);
             if (it == e.rt.shards().end() || it->second.empty())
                 return Status::NoReplica("no live holder of shard " + std::to_string(kv.first));
-            for (int node : it->second) by_node[node].push_back(kv.first);
+            for (int node : it->second)
+                if (ack == nullptr || ack->wants(kv.first, node)) by_node[node].push_back(kv.first);
         }
         for (auto& kv : by_node) {
             Archive& ar = out->body[kv.first];
@@ -372,39 +401,47 @@ public:
 
     // Several threads' pushes in one message per node: the node's shard list is the union over the merged
     // requests, every shard carries one item list per merged request (possibly empty).
-    Status generate_merged_requests(const TableEntry& e, const std::vector<PushRequestData*>& ds, NodeRequests* out) const {
-        std::map<int, std::vector<int32_t>> by_node;
-        std::map<int32_t, bool> seen;
-        for (auto* d : ds) {
-            if (d->global_shard_num != e.rt.global_shard_num())
+    // `acks[i]` (may be null) filters what member i still has to send; `sent[i]` receives the (node, shard) pairs
+    // that carry member i's items in this message set.
+    Status generate_merged_requests(const TableEntry& e, const std::vector<PushRequestData*>& ds,
+                                    const std::vector<PushAckState*>& acks, NodeRequests* out,
+                                    std::vector<std::vector<std::pair<int, int32_t>>>* sent) const {
+        std::map<int, std::set<int32_t>> by_node;
+        sent->assign(ds.size(), {});
+        for (size_t i = 0; i < ds.size(); ++i) {
+            if (ds[i]->global_shard_num != e.rt.global_shard_num())
                 return Status::ServerTooNewCtx("the context changed while push requests were being merged");
-            for (auto& kv : d->shard_keys) {
-                if (seen.count(kv.first)) continue;
-                seen[kv.first] = true;
+            for (auto& kv : ds[i]->shard_keys) {
                 auto it = e.rt.shards().find(kv.first);
                 if (it == e.rt.shards().end() || it->second.empty())
                     return Status::NoReplica("no live holder of shard " + std::to_string(kv.first));
-                for (int node : it->second) by_node[node].push_back(kv.first);
+                for (int node : it->second)
+                    if (acks[i] == nullptr || acks[i]->wants(kv.first, node)) {
+                        by_node[node].insert(kv.first);
+                        (*sent)[i].push_back({node, kv.first});
+                    }
             }
         }
-        static const std::vector<int64_t> no_keys;
-        static const std::vector<float> no_grads;
         for (auto& kv : by_node) {
-            std::sort(kv.second.begin(), kv.second.end());
-            Archive& ar = out->body[kv.first];
+            const int node = kv.first;
+            Archive& ar = out->body[node];
             ar << (int32_t)kv.second.size() << (int32_t)ds.size();
             for (int32_t s : kv.second) {
                 ar << s;
-                for (auto* d : ds) {
-                    auto it = d->shard_keys.find(s);
-                    const auto& ks = it == d->shard_keys.end() ? no_keys : it->second;
-                    const auto& gs = it == d->shard_keys.end() ? no_grads : d->shard_grads.at(s);
-                    ar << (int32_t)ks.size();
-                    ar.write_raw(ks.data(), ks.size() * 8);
+                for (size_t i = 0; i < ds.size(); ++i) {
+                    auto it = ds[i]->shard_keys.find(s);
+                    const bool include = it != ds[i]->shard_keys.end() && (acks[i] == nullptr || acks[i]->wants(s, node));
+                    if (!include) {
+                        ar << (int32_t)0;
+                        continue;
+                    }
+                    const auto& gs = ds[i]->shard_grads.at(s);
+                    ar << (int32_t)it->second.size();
+                    ar.write_raw(it->second.data(), it->second.size() * 8);
                     ar.write_raw(gs.data(), gs.size() * 4);
                 }
             }
-            out->shards[kv.first] = kv.second;
+            out->shards[node] = std::vector<int32_t>(kv.second.begin(), kv.second.end());
         }
         return Status::Ok();
     }

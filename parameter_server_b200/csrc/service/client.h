@@ -49,7 +49,11 @@ public:
         meta.ctx_u_ver = ctx_u_ver;
         if (ctx_ver == -2) {
             auto e = ctx_.get(sid);
-            meta.ctx_ver = e ? e->td.version : -1;
+            meta.ctx_ver = -1;
+            if (e) {
+                std::shared_lock<std::shared_mutex> g(e->mu);
+                meta.ctx_ver = e->td.version;
+            }
         } else {
             meta.ctx_ver = ctx_ver;
         }
@@ -347,12 +351,20 @@ public:
     Status handle_out_of_memory(int32_t sid, int timeout_ms) {
         auto e = ctx_.get(sid);
         if (!e) return Status::InvalidID("unknown storage");
-        const int32_t v0 = e->td.version;
+        auto snapshot = [&](int32_t* ver, StorageStatus* status) {
+            std::shared_lock<std::shared_mutex> g(e->mu);
+            *ver = e->td.version;
+            *status = e->td.status;
+        };
+        int32_t v0 = 0, v = 0;
+        StorageStatus status;
+        snapshot(&v0, &status);
         double wait_ms = 100;
         auto t0 = std::chrono::steady_clock::now();
         for (;;) {
             PSB_RETURN_IF_ERROR(pull_context(sid));
-            if (e->td.version != v0 && e->td.status == StorageStatus::NORMAL) return Status::Ok();
+            snapshot(&v, &status);
+            if (v != v0 && status == StorageStatus::NORMAL) return Status::Ok();
             auto el = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
             if (timeout_ms >= 0 && el + (long)wait_ms > timeout_ms) return Status::Timeout("still out of memory / resharding");
             std::this_thread::sleep_for(std::chrono::milliseconds((long)wait_ms));

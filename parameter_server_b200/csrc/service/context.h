@@ -6,6 +6,7 @@
 // (storage / update_storage / incr_storage / handlers, pico-ps/service/TableDescriptor.h:103-130).
 // The same class serves the client (no storages, node id -1) and the server.
 #pragma once
+#include <atomic>
 #include <map>
 #include <memory>
 #include <mutex>
@@ -24,7 +25,7 @@ namespace psb {
 // serialises "collect + clear" against concurrent pushes.
 struct IncrementStorage {
     std::shared_mutex mu;
-    bool updated = false;
+    std::atomic<bool> updated{false};  // set by concurrent pushes under the shared lock
 };
 
 struct RestoreIterator {

@@ -1,0 +1,133 @@
+// Race-detection stress of the host control plane, built with -fsanitize=thread by tests/test_tsan_service.py.
+//
+// One master, three servers and one client in this process (real sockets on localhost, as in the
+// reference's integration tests, pico-ps/test/ps_service_test.cpp:77-145). Four worker threads push and pull
+// through handlers that share merge groups (request coalescing) while the main thread moves shards between
+// the servers four times (the reshard transaction with its context-version gates and client retries). The program
+// checks that every gradient was applied exactly once; ThreadSanitizer checks the rest.
+#include <atomic>
+#include <cstdio>
+#include <memory>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "handler/handlers.h"
+#include "service/master.h"
+#include "service/server.h"
+
+namespace psb {
+// this host-only binary has no CUDA objects: a table that asks for the GPU back-end is refused
+Status make_gpu_kv_storage(const GpuKVStorageConfig&, std::unique_ptr<KVStorage>*) {
+    return Status::Error("no GPU back-end in this build");
+}
+}  // namespace psb
+
+using namespace psb;
+
+static std::string nodes_json(const std::vector<std::pair<int, std::vector<int>>>& nodes) {
+    std::string s = "[";
+    for (size_t i = 0; i < nodes.size(); ++i) {
+        s += std::string(i ? "," : "") + "{\"g_rank\":" + std::to_string(nodes[i].first) + ",\"shard_list\":[";
+        for (size_t j = 0; j < nodes[i].second.size(); ++j) s += std::string(j ? "," : "") + std::to_string(nodes[i].second[j]);
+        s += "]}";
+    }
+    return s + "]";
+}
+
+#define MUST(expr)                                                              \
+    do {                                                                        \
+        Status _st = (expr);                                                    \
+        if (!_st.ok()) {                                                        \
+            std::fprintf(stderr, "FAILED %s: %s\n", #expr, _st.msg().c_str()); \
+            return 1;                                                           \
+        }                                                                       \
+    } while (0)
+
+int main() {
+    constexpr int kDim = 4, kThreads = 4, kIters = 120, kKeys = 2000, kBatch = 128;
+    Master master(4);
+    std::vector<std::unique_ptr<Server>> servers;
+    for (int i = 0; i < 3; ++i) servers.emplace_back(new Server(master.address()));
+    Client client(master.address());
+    const int n0 = servers[0]->node_id(), n1 = servers[1]->node_id(), n2 = servers[2]->node_id();
+    const std::string cfg = "{\"nodes\":" + nodes_json({{n0, {0, 1}}, {n1, {2, 3}}, {n2, {4, 5}}}) +
+                            ",\"op_config\":{\"dim\":4,\"optimizer\":\"sum\",\"init_range\":0.0},\"table_name\":\"t\"}";
+    int32_t sid = -1, h_pull = -1, h_push = -1, h_ctx = -1;
+    MUST(client.create_storage("psb", "SparseTableStorageOperator", cfg, &sid));
+    MUST(client.register_handler("pull_ro", "psb", "SparseTablePullOperator", "{\"read_only\":true}", sid, &h_pull));
+    MUST(client.register_handler("push", "psb", "SparseTablePushOperator", "{}", sid, &h_push));
+    MUST(client.register_handler("update_ctx", "psb", "ShardUpdateContextOperator", "{}", sid, &h_ctx));
+
+    auto pull_group = std::make_shared<PullGroup>();
+    auto push_group = std::make_shared<PushGroup>();
+    std::vector<std::unique_ptr<PullHandler>> pulls;
+    std::vector<std::unique_ptr<PushHandler>> pushes;
+    for (int t = 0; t < kThreads; ++t) {
+        pulls.emplace_back(new PullHandler(&client, sid, h_pull));
+        pushes.emplace_back(new PushHandler(&client, sid, h_push));
+        pulls.back()->join_group(pull_group);
+        pushes.back()->join_group(push_group);
+    }
+    std::vector<std::atomic<uint64_t>> pushed(kKeys);
+    for (auto& p : pushed) p = 0;
+    std::atomic<int> failures{0};
+    std::vector<std::thread> workers;
+    for (int t = 0; t < kThreads; ++t)
+        workers.emplace_back([&, t] {
+            uint64_t x = 88172645463325252ull + (uint64_t)t * 7919;
+            std::vector<int64_t> keys(kBatch);
+            std::vector<float> grads((size_t)kBatch * kDim, 1.0f), rows((size_t)kBatch * kDim);
+            for (int it = 0; it < kIters; ++it) {
+                for (auto& k : keys) {
+                    x ^= x << 13; x ^= x >> 7; x ^= x << 17;
+                    k = (int64_t)(x % kKeys);
+                }
+                Status st = pushes[t]->async_push(keys.data(), grads.data(), keys.size(), 20000);
+                if (!st.ok()) { std::fprintf(stderr, "push: %s\n", st.msg().c_str()); ++failures; continue; }
+                for (auto k : keys) ++pushed[(size_t)k];
+                st = pulls[t]->pull(keys.data(), keys.size(), rows.data(), 20000);
+                if (!st.ok()) { std::fprintf(stderr, "pull: %s\n", st.msg().c_str()); ++failures; continue; }
+                for (size_t i = 0; i < keys.size(); ++i)
+                    if (rows[i * kDim] < 1.0f) ++failures;   // at least this thread's own push is visible
+            }
+        });
+    // two reshards while the load runs: rotate the shard placement, then spread it unevenly
+    {
+        UpdateContextHandler uc(&client, sid, h_ctx);
+        const std::vector<std::vector<std::pair<int, std::vector<int>>>> plans = {
+            {{n0, {4, 5}}, {n1, {0, 1}}, {n2, {2, 3}}},       // rotate the placement
+            {{n0, {0}}, {n1, {1, 2}}, {n2, {3, 4, 5}}},       // uneven
+            {{n0, {0, 1, 2, 3}}, {n1, {4}}, {n2, {5}}},       // pile up on one node
+            {{n0, {0, 1}}, {n1, {2, 3}}, {n2, {4, 5}}},       // back to the start
+        };
+        for (size_t i = 0; i < plans.size(); ++i) {
+            std::this_thread::sleep_for(std::chrono::milliseconds(15));
+            Status st = uc.update_context(nodes_json(plans[i]));
+            if (!st.ok()) { std::fprintf(stderr, "reshard %zu: %s\n", i, st.msg().c_str()); ++failures; }
+        }
+    }
+    for (auto& w : workers) w.join();
+    // every gradient exactly once
+    std::vector<int64_t> all(kKeys);
+    for (int k = 0; k < kKeys; ++k) all[k] = k;
+    std::vector<float> rows((size_t)kKeys * kDim);
+    MUST(pulls[0]->pull(all.data(), all.size(), rows.data(), 20000));
+    int wrong = 0;
+    for (int k = 0; k < kKeys; ++k)
+        for (int d = 0; d < kDim; ++d)
+            if (rows[(size_t)k * kDim + d] != (float)pushed[k].load()) ++wrong;
+    std::printf("merged pull sends %llu of %llu, merged push sends %llu of %llu, failures %d, wrong %d\n",
+                (unsigned long long)pull_group->merged_sends.load(), (unsigned long long)pull_group->merged_requests.load(),
+                (unsigned long long)push_group->merged_sends.load(), (unsigned long long)push_group->merged_requests.load(),
+                failures.load(), wrong);
+    pulls.clear();
+    pushes.clear();
+    for (auto& s : servers) s->stop();
+    master.stop();
+    if (failures.load() == 0 && wrong == 0) {
+        std::printf("STRESS OK\n");
+        return 0;
+    }
+    return 1;
+}
