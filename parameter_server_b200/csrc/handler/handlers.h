@@ -12,6 +12,7 @@
 #include <atomic>
 #include <chrono>
 #include <functional>
+#include <thread>
 
 #include "../common/thread_sync.h"
 #include "../service/client.h"
@@ -74,6 +75,11 @@ protected:
                 if (!client_->handle_server_too_new_ctx(sid_).ok()) break;
             } else if (st.is(StatusCode::OUT_OF_MEMORY)) {
                 if (!client_->handle_out_of_memory(sid_, left).ok()) break;
+            } else if (st.is(StatusCode::SERVER_TOO_OLD_CTX) || st.is(StatusCode::SERVER_TOO_OLD_CTX_U)) {
+                // The server has not seen a context that this client already uses (the publisher updates its own
+                // copy a moment before the master's). The server refreshes from the master on every such
+                // request, so a short pause and a retry are enough.
+                std::this_thread::sleep_for(std::chrono::milliseconds(20));
             } else {
                 break;
             }

@@ -280,12 +280,15 @@ public:
             ch = it->second;
             channels_.erase(it);
         }
+        // Other threads may still hold this channel and be writing to it: shut the socket down (their calls
+        // fail) but leave the descriptor open until the last holder lets go, or its number could be handed to
+        // a new connection under their feet.
         ::shutdown(ch->fd, SHUT_RDWR);
+        std::lock_guard<std::mutex> g(ch->join_mu);
         if (ch->reader.joinable()) {
             if (ch->reader.get_id() == std::this_thread::get_id()) ch->reader.detach();
             else ch->reader.join();
         }
-        ::close(ch->fd);
     }
     void close_all() {
         std::vector<std::string> addrs;
@@ -304,10 +307,14 @@ public:
 private:
     struct Channel {
         int fd = -1;
-        std::mutex mu, wmu;
+        std::mutex mu, wmu, join_mu;
         std::map<uint64_t, Ticket> pending;
         std::thread reader;
         std::atomic<bool> alive{true};
+        ~Channel() {
+            if (reader.joinable()) reader.detach();  // only reached on the reader thread itself, as its last act
+            if (fd >= 0) ::close(fd);
+        }
     };
 
     std::shared_ptr<Channel> channel(const std::string& address) {
@@ -317,8 +324,8 @@ private:
             if (it->second->alive) return it->second;
             auto dead = it->second;
             channels_.erase(it);
-            if (dead->reader.joinable()) dead->reader.join();
-            ::close(dead->fd);
+            std::lock_guard<std::mutex> jg(dead->join_mu);
+            if (dead->reader.joinable()) dead->reader.join();   // the descriptor closes with the last holder
         }
         auto colon = address.rfind(':');
         if (colon == std::string::npos) return nullptr;

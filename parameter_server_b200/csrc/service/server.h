@@ -242,12 +242,23 @@ private:
         }
     }
 
-    // Context version gate. Self-heals a server that is behind by pulling the context first.
-    Status check_ctx_version(TableEntry& e, const PSMessageMeta& meta) {
-        if (meta.ctx_ver > e.td.version) {
-            std::string json;
-            if (master_.get_context(ctx_key(e.sid), &json).ok()) apply_ctx_json(e, json);
+    // Self-healing of a server that is behind: when a request carries a context version (or update version)
+    // that this server has not seen, the context is fetched from the master and installed under the table's
+    // exclusive lock BEFORE the request takes its shared lock. The version gates below only compare.
+    void refresh_if_behind(TableEntry& e, const PSMessageMeta& meta) {
+        bool behind = false;
+        {
+            std::shared_lock<std::shared_mutex> g(e.mu);
+            behind = meta.ctx_ver > e.td.version || (meta.ctx_u_ver >= 0 && meta.ctx_u_ver != e.td.update_version);
         }
+        if (!behind) return;
+        std::string json;
+        if (!master_.get_context(ctx_key(e.sid), &json).ok()) return;
+        std::unique_lock<std::shared_mutex> g(e.mu);
+        if (meta.ctx_ver > e.td.version || (meta.ctx_u_ver >= 0 && meta.ctx_u_ver != e.td.update_version)) apply_ctx_json(e, json);
+    }
+    // Context version gates (callers hold the table's lock).
+    Status check_ctx_version(TableEntry& e, const PSMessageMeta& meta) {
         if (meta.ctx_ver > e.td.version) return Status::ServerTooOldCtx("server context older than the client's");
         if (meta.ctx_ver < e.td.version) return Status::ServerTooNewCtx("server context newer than the client's");
         return Status::Ok();
@@ -258,10 +269,6 @@ private:
         return Status::Ok();
     }
     Status check_table_version(TableEntry& e, const PSMessageMeta& meta) {
-        if (meta.ctx_ver != e.td.version || meta.ctx_u_ver != e.td.update_version) {
-            std::string json;
-            if (master_.get_context(ctx_key(e.sid), &json).ok()) apply_ctx_json(e, json);
-        }
         if (meta.ctx_ver != e.td.version) return meta.ctx_ver > e.td.version ? Status::ServerTooOldCtx("ctx") : Status::ServerTooNewCtx("ctx");
         if (meta.ctx_u_ver != e.td.update_version)
             return meta.ctx_u_ver > e.td.update_version ? Status::ServerTooOldCtxU("update ctx") : Status::ServerTooNewCtxU("update ctx");
@@ -393,6 +400,7 @@ private:
             Status st = refresh_from_master(meta.sid, &e);
             if (!st.ok() || !e) return Status::InvalidID("no storage " + std::to_string(meta.sid) + " on node " + std::to_string(node_id_));
         }
+        if (meta.ctx_ver >= 0) refresh_if_behind(*e, meta);
         switch (meta.req_type) {
             case RequestType::STORAGE_DELETE: ctx_.erase(meta.sid); return Status::Ok();
             case RequestType::STORAGE_CLEAR: {

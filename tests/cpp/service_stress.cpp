@@ -4,7 +4,9 @@
 // reference's integration tests, pico-ps/test/ps_service_test.cpp:77-145). Four worker threads push and pull
 // through handlers that share merge groups (request coalescing) while the main thread moves shards between
 // the servers four times (the reshard transaction with its context-version gates and client retries). The program
-// checks that every gradient was applied exactly once; ThreadSanitizer checks the rest.
+// checks that every gradient was applied exactly once. A second phase reads a table with two replicas per
+// shard from four threads while one server is stopped, a fresh one restores the lost shards from the live
+// replicas, and a second original server is stopped. ThreadSanitizer checks the rest.
 #include <atomic>
 #include <cstdio>
 #include <memory>
@@ -123,6 +125,60 @@ int main() {
                 failures.load(), wrong);
     pulls.clear();
     pushes.clear();
+
+    // ---- phase 2: a replicated table keeps serving reads while a node dies and a fresh server takes over ----
+    int wrong2 = 0;
+    MUST(client.delete_storage(sid));   // the unreplicated table could not survive the loss of a node
+    {
+        const std::string cfg2 = "{\"nodes\":" + nodes_json({{n0, {0, 1}}, {n1, {1, 2}}, {n2, {2, 0}}}) +
+                                 ",\"op_config\":{\"dim\":4,\"optimizer\":\"sum\",\"init_range\":0.0},\"table_name\":\"r\"}";
+        int32_t sid2 = -1, hp = -1, hq = -1;
+        MUST(client.create_storage("psb", "SparseTableStorageOperator", cfg2, &sid2));
+        MUST(client.register_handler("pull_ro", "psb", "SparseTablePullOperator", "{\"read_only\":true}", sid2, &hp));
+        MUST(client.register_handler("push", "psb", "SparseTablePushOperator", "{}", sid2, &hq));
+        std::vector<float> vals((size_t)kKeys * kDim);
+        for (int k = 0; k < kKeys; ++k)
+            for (int d = 0; d < kDim; ++d) vals[(size_t)k * kDim + d] = (float)(k % 13 + 1);
+        {
+            PushHandler seed(&client, sid2, hq);
+            MUST(seed.async_push(all.data(), vals.data(), all.size(), 20000));   // every replica gets it
+        }
+        std::atomic<bool> stop_readers{false};
+        std::atomic<int> bad_reads{0}, reads{0};
+        std::vector<std::thread> readers;
+        for (int t = 0; t < kThreads; ++t)
+            readers.emplace_back([&, t] {
+                PullHandler h(&client, sid2, hp);
+                std::vector<int64_t> keys(kBatch);
+                std::vector<float> got((size_t)kBatch * kDim);
+                uint64_t x = 1234567 + (uint64_t)t;
+                while (!stop_readers.load()) {
+                    for (auto& k : keys) {
+                        x ^= x << 13; x ^= x >> 7; x ^= x << 17;
+                        k = (int64_t)(x % kKeys);
+                    }
+                    Status st = h.pull(keys.data(), keys.size(), got.data(), 20000);   // time-out -> dead-node detection -> other replica
+                    if (!st.ok()) { std::fprintf(stderr, "read: %s\n", st.msg().c_str()); ++bad_reads; continue; }
+                    for (size_t i = 0; i < keys.size(); ++i)
+                        if (got[i * kDim] != (float)(keys[i] % 13 + 1)) ++bad_reads;
+                    ++reads;
+                }
+            });
+        std::this_thread::sleep_for(std::chrono::milliseconds(30));
+        servers[1]->stop();                                        // host-side fault: this node is gone
+        std::this_thread::sleep_for(std::chrono::milliseconds(200));
+        servers.emplace_back(new Server(master.address()));        // a fresh server replaces it from the live replicas
+        int restored = 0;
+        Status st = servers.back()->restore_storages(&restored);
+        if (!st.ok() || restored < 1) { std::fprintf(stderr, "restore: %s (%d tables)\n", st.msg().c_str(), restored); ++wrong2; }
+        servers[0]->stop();                                        // now the restored copy has to serve
+        std::this_thread::sleep_for(std::chrono::milliseconds(300));
+        stop_readers = true;
+        for (auto& r : readers) r.join();
+        wrong2 += bad_reads.load();
+        std::printf("phase 2: %d reads, %d bad, %d tables restored\n", reads.load(), bad_reads.load(), restored);
+    }
+    wrong += wrong2;
     for (auto& s : servers) s->stop();
     master.stop();
     if (failures.load() == 0 && wrong == 0) {
