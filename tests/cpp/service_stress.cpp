@@ -6,9 +6,12 @@
 // the servers four times (the reshard transaction with its context-version gates and client retries). The program
 // checks that every gradient was applied exactly once. A second phase reads a table with two replicas per
 // shard from four threads while one server is stopped, a fresh one restores the lost shards from the live
-// replicas, and a second original server is stopped. ThreadSanitizer checks the rest.
+// replicas, and a second original server is stopped. A third phase mixes immediate and buffered (sync + store)
+// pushes from four threads with statistics scans and dumps. ThreadSanitizer checks the rest.
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
+#include <map>
 #include <memory>
 #include <string>
 #include <thread>
@@ -179,6 +182,82 @@ int main() {
         std::printf("phase 2: %d reads, %d bad, %d tables restored\n", reads.load(), bad_reads.load(), restored);
     }
     wrong += wrong2;
+
+    // ---- phase 3: scans (statistics, dump) and sync push + store run against concurrent async pushes ----------
+    {
+        std::map<int32_t, std::string> live;
+        MUST(client.get_pserver_list(&live));
+        std::vector<std::pair<int, std::vector<int>>> placement;
+        int shard = 0;
+        for (auto& kv : live) {
+            placement.push_back({kv.first, {shard, shard + 1}});
+            shard += 2;
+        }
+        const std::string cfg3 = "{\"nodes\":" + nodes_json(placement) +
+                                 ",\"op_config\":{\"dim\":4,\"optimizer\":\"sum\",\"init_range\":0.0,\"sync\":true},\"table_name\":\"s\"}";
+        int32_t sid3 = -1, hp = -1, hq = -1, hf = -1, hd = -1;
+        MUST(client.create_storage("psb", "SparseTableStorageOperator", cfg3, &sid3));
+        MUST(client.register_handler("pull_ro", "psb", "SparseTablePullOperator", "{\"read_only\":true}", sid3, &hp));
+        MUST(client.register_handler("push", "psb", "SparseTablePushOperator", "{}", sid3, &hq));
+        MUST(client.register_handler("for_each", "psb", "ForEachOperator", "{}", sid3, &hf));
+        MUST(client.register_handler("dump", "psb", "DumpOperator", "{}", sid3, &hd));
+        std::vector<std::atomic<uint64_t>> sent(kKeys);
+        for (auto& x : sent) x = 0;
+        std::atomic<int> bad{0};
+        std::vector<std::thread> ts;
+        for (int t = 0; t < kThreads; ++t)
+            ts.emplace_back([&, t] {
+                PushHandler h(&client, sid3, hq);
+                std::vector<int64_t> keys(kBatch);
+                std::vector<float> grads((size_t)kBatch * kDim, 1.0f);
+                uint64_t x = 99991 + (uint64_t)t * 31;
+                for (int it = 0; it < 40; ++it) {
+                    for (auto& k : keys) {
+                        x ^= x << 13; x ^= x >> 7; x ^= x << 17;
+                        k = (int64_t)(x % kKeys);
+                    }
+                    // even threads apply at once, odd threads buffer on the servers until the store below
+                    Status st = (t % 2 == 0) ? h.async_push(keys.data(), grads.data(), keys.size(), 20000)
+                                             : h.sync_push(keys.data(), grads.data(), keys.size(), 20000);
+                    if (!st.ok()) { std::fprintf(stderr, "phase 3 push: %s\n", st.msg().c_str()); ++bad; continue; }
+                    for (auto k : keys) ++sent[(size_t)k];
+                }
+            });
+        {
+            ForEachHandler fe(&client, sid3, hf);
+            DumpHandler dh(&client, sid3, hd);
+            char tmpl[] = "/tmp/psb_stress_dump_XXXXXX";
+            const char* dir = ::mkdtemp(tmpl);
+            for (int round = 0; round < 6 && dir != nullptr; ++round) {
+                ForEachResult r;
+                Status st = fe.for_each("{}", &r, 20000);
+                if (!st.ok()) { std::fprintf(stderr, "for_each: %s\n", st.msg().c_str()); ++bad; }
+                DumpArgs da;
+                da.uri = std::string(dir) + "/d" + std::to_string(round);
+                da.file_number = 2;
+                uint64_t n = 0;
+                st = dh.dump(da, &n, 20000);
+                if (!st.ok() || n > (uint64_t)kKeys) { std::fprintf(stderr, "dump: %s (%llu records)\n", st.msg().c_str(), (unsigned long long)n); ++bad; }
+            }
+            if (dir != nullptr) {
+                std::string cmd = std::string("rm -rf ") + dir;
+                if (std::system(cmd.c_str()) != 0) ++bad;
+            }
+        }
+        for (auto& t : ts) t.join();
+        {
+            PushHandler h(&client, sid3, hq);
+            MUST(h.store(20000));   // fold what the sync pushes buffered
+        }
+        PullHandler ph(&client, sid3, hp);
+        std::vector<float> got((size_t)kKeys * kDim);
+        MUST(ph.pull(all.data(), all.size(), got.data(), 20000));
+        int wrong3 = bad.load();
+        for (int k = 0; k < kKeys; ++k)
+            if (got[(size_t)k * kDim] != (float)sent[k].load()) ++wrong3;
+        std::printf("phase 3: %d wrong\n", wrong3);
+        wrong += wrong3;
+    }
     for (auto& s : servers) s->stop();
     master.stop();
     if (failures.load() == 0 && wrong == 0) {
