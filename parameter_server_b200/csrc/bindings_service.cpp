@@ -206,6 +206,8 @@ void bind_service(py::module_& m) {
     py::class_<Client>(m, "Client")
         .def(py::init<const std::string&>(), py::arg("master"))
         .def("get_pserver_list", [](Client& c) { std::map<int32_t, std::string> n; Status st = c.get_pserver_list(&n); return std::make_tuple(st, n); }, nogil())
+        .def("get_available_pserver_list", [](Client& c, int timeout_ms) { std::vector<int32_t> n; Status st = c.get_available_pserver_list(&n, timeout_ms); return std::make_tuple(st, n); },
+             py::arg("timeout_ms") = 2000, nogil())
         .def("create_storage", [](Client& c, const std::string& lib, const std::string& op, const std::string& cfg) {
             int32_t sid = -1;
             Status st = c.create_storage(lib, op, cfg, &sid);

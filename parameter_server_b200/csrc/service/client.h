@@ -34,6 +34,16 @@ public:
     Context& context() { return ctx_; }
 
     Status get_pserver_list(std::map<int32_t, std::string>* nodes) { return master_.get_nodes(PSERVER_C2S_RPC_NAME, nodes); }
+    // Servers that are registered AND answer a health check within `timeout_ms`
+    // (Client::get_available_pserver_list of pico-ps/service/Client.h:36-116).
+    Status get_available_pserver_list(std::vector<int32_t>* nodes, int timeout_ms = 2000) {
+        std::map<int32_t, std::string> all;
+        PSB_RETURN_IF_ERROR(get_pserver_list(&all));
+        nodes->clear();
+        for (auto& kv : all)
+            if (health_check(kv.first, timeout_ms).ok()) nodes->push_back(kv.first);
+        return Status::Ok();
+    }
 
     // ---- scatter / gather -------------------------------------------------------------------
     // Sends one request per node and waits for all. The result is the first non-OK status (transport

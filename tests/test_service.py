@@ -577,6 +577,15 @@ def test_push_requests_of_threads_are_merged(cluster3):
     assert st.ok() and np.array_equal(rows, counts[:, None] * np.ones((1, DIM), dtype=np.float32))
 
 
+def test_available_server_list_excludes_stopped_nodes(cluster3):
+    cl = cluster3
+    st, nodes = cl.client.get_available_pserver_list()
+    assert st.ok() and sorted(nodes) == sorted(cl.ids())
+    cl.servers[2].stop()
+    st, nodes = cl.client.get_available_pserver_list(500)
+    assert st.ok() and sorted(nodes) == sorted(cl.ids()[:2])
+
+
 def test_prometheus_metrics_endpoint(cluster3):
     import urllib.request
     from parameter_server_b200.service.metrics import handler_metrics_text, serve_metrics
