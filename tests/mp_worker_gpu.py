@@ -212,6 +212,62 @@ def main():
         if rank == 0:
             print("dlrm ok", [round(x, 3) for x in losses[:3]], "...", round(losses[-1], 3), flush=True)
 
+    if which == "elastic":
+        # A rank leaves between two steps; the others learn of it on the host (heartbeat store) before their next
+        # launch, rebuild the table on the survivors and refill it from the last dump. No kernel ever waits for
+        # the rank that left. (Run with NCCL_NVLS_ENABLE=0; the kernels of this repository use plain peer
+        # loads / stores.)
+        import shutil
+        import tempfile
+        from parameter_server_b200.parallel import checkpoint
+        from parameter_server_b200.parallel.membership import Membership, RankLost
+        t = SparseTable(32, "adagrad", dict(lr=0.05, init_accumulator=0.1), n_shards=2 * world, capacity=1 << 16,
+                        max_keys=1 << 14, wait_limit_s=5.0)
+        rng = np.random.default_rng(21 + rank)
+        keys = torch.from_numpy(rng.integers(0, 1 << 40, size=8000)).cuda()
+        for _ in range(2):
+            t.pull(keys); t.push(torch.randn(8000, 32, device="cuda") * 1e-2)
+        t.check()
+        box = [tempfile.mkdtemp(prefix="psb_elastic_") if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        checkpoint.dump(t, box[0], file_number=2)
+        mine = [(k.cpu(), r.cpu()) for k, r in t.export()]
+        everything = gather(mine)                                   # what the dump must bring back, known to rank 0
+        m = Membership(dist.distributed_c10d._get_default_store(), rank, world, timeout_s=2.0, prefix="psb/test_elastic")
+        leaver = world - 1
+        lost = None
+        for step in range(1, 5):
+            if rank == leaver and step == 3:
+                torch.cuda.synchronize()                            # nothing of this rank is in flight
+                m.leave()
+                print(f"rank {rank} left", flush=True)
+                os._exit(0)
+            try:
+                m.step(step)
+            except RankLost as e:
+                lost = e
+                break
+            t.pull(keys); t.push(torch.randn(8000, 32, device="cuda") * 1e-2)
+            t.check()
+        assert lost is not None and lost.ranks == [leaver] and lost.left == [leaver], lost
+        torch.cuda.synchronize()
+        if rank == 0:
+            # with two ranks the survivor serves alone: a private table, refilled from every file of the dump
+            t2 = SparseTable(32, "adagrad", dict(lr=0.05, init_accumulator=0.1), n_shards=4, capacity=1 << 16,
+                             max_keys=1 << 14, group="none")
+            n = checkpoint.load(t2, box[0])
+            ks = torch.cat([k for part in everything for k, _ in part])
+            rs = torch.cat([r for part in everything for _, r in part])
+            assert n == ks.numel() == t2.size(), (n, ks.numel(), t2.size())
+            got, found = t2.get_rows(ks.cuda(), emb_only=False)
+            assert found.all() and torch.equal(got.cpu(), rs)
+            out = t2.pull(keys)                                     # and it trains on
+            t2.push(torch.zeros(8000, 32, device="cuda")); t2.check()
+            assert torch.isfinite(out).all()
+            shutil.rmtree(box[0], ignore_errors=True)
+            print("elastic ok", flush=True)
+        os._exit(0)                                                 # the group lost a member: no collective teardown
+
     dist.barrier()
     dist.destroy_process_group()
 

@@ -27,6 +27,13 @@ def test_two_ranks(which):
     assert f"{which} ok" in out
 
 
+def test_rank_leaves_between_steps_and_survivor_restores_from_dump(monkeypatch):
+    """Host-side failure detection + recovery on real GPUs: no kernel waits for the rank that left."""
+    monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
+    out = run_ranks(2, "elastic")
+    assert "rank 1 left" in out and "elastic ok" in out
+
+
 def test_all_visible_gpus():
     n = torch.cuda.device_count()
     if n <= 2:
