@@ -318,6 +318,37 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
             __syncthreads();
             const float scale = (a.flags & FUSED_MEAN) ? 1.0f / (float)L : 1.0f;
             const unsigned lgroup = threadIdx.x / lanes, lgroups = kThreads / lanes;
+            if (L == 1) {
+                // one key per bag (the common embedding lookup): two bags per lane group and iteration, so that
+                // two row loads are in flight before the first store (the loop is bound by load latency; four
+                // would cost a resident CTA per SM in registers)
+                constexpr int kBags = 2;
+                for (unsigned b0 = b_lo; b0 < b_hi; b0 += lgroups * kBags) {
+                    unsigned bb[kBags];
+                    const float* src[kBags];
+                    bool act[kBags];
+#pragma unroll
+                    for (int k = 0; k < kBags; ++k) {
+                        bb[k] = b0 + (unsigned)k * lgroups + lgroup;
+                        act[k] = bb[k] < b_hi;
+                        src[k] = nullptr;
+                        if (act[k]) {
+                            const unsigned row = a.pos_slot[bb[k]];
+                            if (row == kRemoteRow) src[k] = mine.rows_in + (size_t)a.inverse[bb[k]] * a.dim;
+                            else if (row < kRowPending) src[k] = T.row_ptr(row);
+                        }
+                    }
+                    for (unsigned d = lane * 4; d < a.dim; d += lanes * 4) {
+                        float4 v[kBags];
+#pragma unroll
+                        for (int k = 0; k < kBags; ++k)
+                            if (act[k]) v[k] = src[k] != nullptr ? *(const float4*)(src[k] + d) : init4(T, a.keys[bb[k]], d);
+#pragma unroll
+                        for (int k = 0; k < kBags; ++k)
+                            if (act[k]) *(float4*)(a.out + (size_t)bb[k] * a.dim + d) = v[k];
+                    }
+                }
+            } else
             for (unsigned b = b_lo + lgroup; b < b_hi; b += lgroups) {
                 for (unsigned d = lane * 4; d < a.dim; d += lanes * 4) {
                     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
