@@ -34,6 +34,11 @@ def lib_path() -> Path:
     return PKG / ("_C" + _ext_suffix())
 
 
+def node_path() -> Path:
+    """The native master / pserver executable (``csrc/apps/psb_node.cpp``)."""
+    return PKG / "bin" / "psb_node"
+
+
 def _includes() -> list[str]:
     import pybind11
 
@@ -106,8 +111,21 @@ def build(jobs: int | None = None, force: bool = False, verbose: bool = False) -
     for o in BUILD.glob("*.o"):
         if o.name not in keep:
             o.unlink()
+    # the shared object takes everything except the executables' mains; the node executable takes everything
+    # except the Python bindings
+    lib_objs = [o for o in objs if not o.name.startswith("apps__")]
+    node_objs = [o for o in objs if not o.name.startswith("bindings")]
+    node = node_path()
+    if todo or not node.exists():
+        node.parent.mkdir(parents=True, exist_ok=True)
+        cmd = [NVCC, *ARCH, "-o", str(node), *[str(o) for o in node_objs], "-lpthread", "-ldl", "-lrt"]
+        p = subprocess.run(cmd, capture_output=True, text=True)
+        if p.returncode != 0:
+            print(p.stdout + p.stderr)
+            raise RuntimeError("link of psb_node failed")
+        print(f"[build] linked {node.relative_to(PKG.parent)}", flush=True)
     if todo or not out.exists():
-        cmd = [NVCC, *ARCH, "-shared", "-o", str(out), *[str(o) for o in objs], "-lpthread", "-ldl", "-lrt"]
+        cmd = [NVCC, *ARCH, "-shared", "-o", str(out), *[str(o) for o in lib_objs], "-lpthread", "-ldl", "-lrt"]
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
             print(p.stdout + p.stderr)

@@ -1,0 +1,86 @@
+// psb_node: the parameter server's processes as one native executable (no Python in the serving path).
+//
+//   psb_node master [--threads N]
+//       prints the master's address on the first line of stdout and serves until it is killed.
+//   psb_node pserver --master HOST:PORT [--restore] [--c2s-threads N] [--s2s-threads N]
+//       registers at the master, prints "pserver node_id=.. c2s=.. s2s=..", serves both ports and exits when a
+//       client sends EXIT (Client::close_pserver / Controller::shutdown_node). With --restore it first takes
+//       over the shards of a dead node from their live replicas or from the table's dump
+//       (the restore mode of the reference's server process, pico-ps/service/Service.cpp:237-313).
+//
+// The same objects as the Python bindings: tables with "backend": "gpu" are served by the fused kernels.
+#include <chrono>
+#include <csignal>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <thread>
+
+#include "../service/master.h"
+#include "../service/server.h"
+
+using namespace psb;
+
+namespace {
+volatile std::sig_atomic_t g_stop = 0;
+void on_signal(int) { g_stop = 1; }
+
+int usage() {
+    std::fprintf(stderr,
+                 "usage: psb_node master [--threads N]\n"
+                 "       psb_node pserver --master HOST:PORT [--restore] [--c2s-threads N] [--s2s-threads N]\n");
+    return 2;
+}
+}  // namespace
+
+int main(int argc, char** argv) {
+    if (argc < 2) return usage();
+    std::signal(SIGINT, on_signal);
+    std::signal(SIGTERM, on_signal);
+    const std::string role = argv[1];
+    std::string master_addr;
+    bool restore = false;
+    int threads = 4;
+    ServerConfig cfg;
+    for (int i = 2; i < argc; ++i) {
+        const std::string a = argv[i];
+        auto next = [&](int* out) {
+            if (i + 1 >= argc) return false;
+            *out = std::atoi(argv[++i]);
+            return true;
+        };
+        if (a == "--master" && i + 1 < argc) master_addr = argv[++i];
+        else if (a == "--restore") restore = true;
+        else if (a == "--threads") { if (!next(&threads)) return usage(); }
+        else if (a == "--c2s-threads") { if (!next(&cfg.c2s_thread_num)) return usage(); }
+        else if (a == "--s2s-threads") { if (!next(&cfg.s2s_thread_num)) return usage(); }
+        else return usage();
+    }
+    if (role == "master") {
+        Master master(threads);
+        std::printf("%s\n", master.address().c_str());
+        std::fflush(stdout);
+        while (!g_stop) std::this_thread::sleep_for(std::chrono::milliseconds(50));
+        master.stop();
+        return 0;
+    }
+    if (role != "pserver" || master_addr.empty()) return usage();
+    try {
+        Server server(master_addr, cfg);
+        std::printf("pserver node_id=%d c2s=%s s2s=%s\n", server.node_id(), server.c2s_address().c_str(), server.s2s_address().c_str());
+        std::fflush(stdout);
+        if (restore) {
+            int n = 0;
+            Status st = server.restore_storages(&n);
+            std::printf("restore: %s (%d tables)\n", st.ok() ? "OK" : st.msg().c_str(), n);
+            std::fflush(stdout);
+            if (!st.ok()) return 1;
+        }
+        while (!server.exited() && !g_stop) std::this_thread::sleep_for(std::chrono::milliseconds(20));
+        server.stop();
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "psb_node: %s\n", e.what());
+        return 1;
+    }
+    return 0;
+}

@@ -1,0 +1,80 @@
+"""The native executable (csrc/apps/psb_node.cpp) as master and as parameter servers: a Python client creates a
+table on two native server processes, pushes, pulls, loses one server (SIGKILL), starts a replacement in
+restore mode and shuts everything down through the admin API. No Python in the serving processes."""
+import json
+import os
+import signal
+import subprocess
+import time
+
+import numpy as np
+import pytest
+
+from parameter_server_b200 import _build
+from parameter_server_b200 import service as S
+
+NODE = str(_build.node_path())
+
+
+def _spawn(*args):
+    return subprocess.Popen([NODE, *args], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+
+
+def _first_line(p, timeout=20.0):
+    t0 = time.time()
+    while time.time() - t0 < timeout:
+        line = p.stdout.readline()
+        if line:
+            return line.strip()
+        time.sleep(0.01)
+    raise AssertionError("no output from psb_node")
+
+
+@pytest.mark.skipif(not os.path.exists(NODE), reason="psb_node is not built")
+def test_native_master_and_servers_serve_a_python_client():
+    master = _spawn("master")
+    procs = [master]
+    try:
+        addr = _first_line(master)
+        servers = [_spawn("pserver", "--master", addr) for _ in range(2)]
+        procs += servers
+        ids = [int(_first_line(p).split("node_id=")[1].split()[0]) for p in servers]
+        client = S.Client(addr)
+        # 2x replication so that the table survives the loss of one process
+        cfg = S.storage_config({ids[0]: [0, 1], ids[1]: [0, 1]}, dict(dim=4, optimizer="sum", init_range=0.0))
+        st, sid = client.create_storage(S.LIB, "SparseTableStorageOperator", cfg)
+        assert st.ok(), st
+        st, h_push = client.register_handler("push", S.LIB, "SparseTablePushOperator", "{}", sid)
+        assert st.ok()
+        st, h_pull = client.register_handler("pull_ro", S.LIB, "SparseTablePullOperator", json.dumps({"read_only": True}), sid)
+        assert st.ok()
+        keys = np.arange(1000, dtype=np.int64)
+        vals = (keys[:, None] % 7 + 1) * np.ones((1, 4), np.float32)
+        assert S.PushHandler(client, sid, h_push).async_push(keys, vals.astype(np.float32)).ok()
+        pull = S.PullHandler(client, sid, h_pull)
+        st, rows = pull.pull(keys)
+        assert st.ok() and np.array_equal(rows, vals)
+        # one server process dies the hard way; reads go on from the other replica
+        servers[1].send_signal(signal.SIGKILL)
+        servers[1].wait(timeout=10)
+        for _ in range(8):
+            st, rows = pull.pull(keys, 20000, True)
+            assert st.ok() and np.array_equal(rows, vals)
+        # a replacement restores the lost shards from the live replica
+        fresh = _spawn("pserver", "--master", addr, "--restore")
+        procs.append(fresh)
+        assert "node_id=" in _first_line(fresh)
+        assert _first_line(fresh, 30.0) == "restore: OK (1 tables)"
+        # admin shutdown: EXIT to every live server, then the master
+        st, live = client.get_pserver_list()
+        assert st.ok() and len(live) == 2
+        for node in live:
+            assert client.close_pserver(node).ok()
+        for p in (servers[0], fresh):
+            assert p.wait(timeout=15) == 0
+        master.send_signal(signal.SIGTERM)
+        assert master.wait(timeout=15) == 0
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
