@@ -226,3 +226,32 @@ def test_collective_dump_load_rehash_and_rpc_codec(tmp_path):
     raw = open(tmp_path / "d" / "model_0_0", "rb").read()
     assert raw[:4] == b"PSB1" and int.from_bytes(raw[4:8], "little") == t.table.stride()
     assert (len(raw) - 8) % (8 + 4 * t.table.stride()) == 0
+
+
+def test_cold_tier_policy_keeps_hbm_rows_under_budget_and_loses_nothing():
+    from parameter_server_b200.ops.cold_policy import ColdTierPolicy
+    t = SparseTable(16, "adagrad", dict(lr=0.05, init_accumulator=0.1), device="cuda", capacity=1 << 15, max_keys=1 << 12)
+    ref = SparseTable(16, "adagrad", dict(lr=0.05, init_accumulator=0.1), device="cuda", capacity=1 << 15, max_keys=1 << 12)
+    pol = ColdTierPolicy(t, hbm_budget_rows=3000, cold_capacity_rows=1 << 14, interval=5, headroom=0.2)
+    g = torch.Generator().manual_seed(0)
+    batches = [torch.randint(0, 8000, (2048,), generator=g) for _ in range(40)]
+    over = []
+    for i, kh in enumerate(batches):
+        k = kh.cuda()
+        out = pol.pull(k, kh)
+        grads = torch.ones(2048, 16, device="cuda") * 0.01 * (1 + (k % 3)).float()[:, None]
+        t.push(grads)
+        want = ref.pull(k); ref.push(grads)
+        assert torch.equal(out, want), f"step {i}: a row came back different from the never-spilled table"
+        pol.maybe_spill()
+        over.append(t.size())
+    t.check(); ref.check()
+    assert pol.spilled_total > 0 and pol.fetched_total > 0
+    assert t.size() + t.cold.size() == ref.size()
+    # right after a spill the table is under its budget
+    assert min(over[4::5]) <= 3000
+    # staged prefetch one step ahead
+    nxt = batches[0]
+    pol.stage_next(nxt)
+    out = pol.pull(nxt.cuda(), nxt)
+    assert torch.equal(out, ref.pull(nxt.cuda()))
