@@ -170,7 +170,7 @@ def _scan_keys(table: SparseTable, mode: int, owner_dev: Optional[torch.Tensor] 
 
 
 def exchange_by_keys(source: SparseTable, keys: torch.Tensor, send: List[int], inbox: PeerInbox, target: SparseTable,
-                     comm: SparseTable) -> int:
+                     comm: SparseTable, between_rounds=None) -> int:
     """Ship the rows of ``keys`` (sorted by destination rank, ``send[d]`` of them for rank ``d``) from the
     local table ``source`` into the tables ``target`` of their destinations. Collective over ``comm``'s
     group. The per-pair totals are exchanged once, so every rank knows the whole schedule; per round the
@@ -209,16 +209,22 @@ def exchange_by_keys(source: SparseTable, keys: torch.Tensor, send: List[int], i
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier(group=comm.group)        # the inboxes may be overwritten again
+        if between_rounds is not None:
+            between_rounds()                      # e.g. read-only pulls: the old owners still hold every row
     return sum(recv)
 
 
 def reshard(table: SparseTable, new_owner: Sequence[int], batch: int = 1 << 18, inbox: Optional[PeerInbox] = None,
-            stats: Optional[dict] = None) -> int:
+            stats: Optional[dict] = None, between_rounds=None) -> int:
     """Move every row whose shard changes hands to its new owner; returns the number of rows this rank
     received. Pulls and pushes must not run concurrently (writes pause, as in the reference). One index
     scan lists the keys that leave, they are sorted by destination and shipped with
     :func:`exchange_by_keys`: the work is proportional to the rows that move, not to the table.
-    ``stats`` (optional) receives the host-side duration of each phase in milliseconds."""
+    ``stats`` (optional) receives the host-side duration of each phase in milliseconds. ``between_rounds``
+    (optional, collective) runs after every round of the exchange: reads stay served during a migration by
+    issuing read-only pulls (``insert=False``) there, since rows are purged from their old owners and the owner
+    map is swapped only at the very end, every key is still found where the current map says (the reference keeps
+    serving reads during a reshard the same way, pico-ps/handler/UpdateContextHandler.cpp:62-153)."""
     import time
     world = table.world
     marks = []
@@ -238,7 +244,7 @@ def reshard(table: SparseTable, new_owner: Sequence[int], batch: int = 1 << 18, 
     leaving = leaving[torch.argsort(dest, stable=True)]
     send = torch.bincount(dest, minlength=world).tolist()
     mark("sort")
-    received = exchange_by_keys(table, leaving, send, inbox, table, table)
+    received = exchange_by_keys(table, leaving, send, inbox, table, table, between_rounds)
     mark("exchange")
     if leaving.numel():
         table.erase_keys(leaving)                  # purge: what moved away no longer belongs here

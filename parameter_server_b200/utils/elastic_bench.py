@@ -35,6 +35,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=10, help="load steps per measurement window")
     ap.add_argument("--lost-rank", type=int, default=1)
     ap.add_argument("--dump-dir", default="")
+    ap.add_argument("--reads-during", action="store_true", help="issue one read-only pull between the rounds of every migration stage")
     ap.add_argument("--no-dump", action="store_true", help="skip the dump / restore-from-dump part (it writes the whole table to disk)")
     a = ap.parse_args()
 
@@ -150,18 +151,27 @@ def main() -> None:
     res["joining_ranks_alloc_ms"] = ms
     moving = [s for s in range(n_shards) if owner0[s] != owner1[s]]
     cur = list(owner0)
+    reads_done = [0]
+
+    def read_between():     # one read-only pull per exchange round: reads are served while rows move
+        t.pull(pool[it[0] % 4], out=out, insert=False, for_push=False)
+        it[0] += 1
+        reads_done[0] += 1
+
     stage_ms, during, phases = [], [], []
     moved_rows = 0
     for j in range(a.stages):
         for s in moving[j::a.stages]:
             cur[s] = owner1[s]
         st = {}
-        ms, got = timed(lambda: reshard(t, cur, batch=1 << 20, inbox=inbox, stats=st))
+        ms, got = timed(lambda: reshard(t, cur, batch=1 << 20, inbox=inbox, stats=st,
+                                        between_rounds=read_between if a.reads_during else None))
         phases.append({k: round(v, 2) for k, v in st.items()})
         moved_rows += int(rank_sum(got))
         stage_ms.append(ms)
         during.append(throughput(max(2, a.steps // 2)))
-    res.update({"rebalance_ms_total": sum(stage_ms), "rebalance_stage_ms": stage_ms, "rebalance_stage_phases_rank0_ms": phases, "rows_moved": moved_rows,
+    res.update({"rebalance_ms_total": sum(stage_ms), "rebalance_stage_ms": stage_ms, "read_only_pulls_during_rebalance": reads_done[0],
+                "read_keys_per_sec_during_rebalance": reads_done[0] * B * world / (sum(stage_ms) / 1e3), "rebalance_stage_phases_rank0_ms": phases, "rows_moved": moved_rows,
                 "rebalance_gbytes": moved_rows * stride_bytes / 1e9,
                 "rebalance_gbytes_per_sec": moved_rows * stride_bytes / 1e9 / (sum(stage_ms) / 1e3),
                 "keys_per_sec_between_stages": during, "keys_per_sec_after": throughput(a.steps),

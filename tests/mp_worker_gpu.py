@@ -127,7 +127,14 @@ def main():
         total_before = sum(gather(t.size()))
         # rebalance: rotate the ownership of every shard by one rank
         new_owner = [(o + 1) % world for o in t.shard_owner]
-        reshard(t, new_owner)
+        reads = []
+
+        def read_during():      # reads stay served while rows are on the move
+            reads.append(bool(torch.equal(t.pull(keys, insert=False, for_push=False), before)))
+
+        reshard(t, new_owner, batch=4096, between_rounds=read_during)
+        t.check()
+        assert reads and all(reads), reads
         assert sum(gather(t.size())) == total_before
         ks = torch.cat([k for k, _ in t.export()] or [torch.empty(0, dtype=torch.int64, device="cuda")])
         owners = {new_owner[__import__("parameter_server_b200").C.sparse_shard_of(int(k), n_shards)] for k in ks[:500].tolist()}
