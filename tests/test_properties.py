@@ -1,0 +1,125 @@
+"""Property tests of the host storage / oracle against an independent numpy model, and of the codecs.
+
+The CPU oracle (`HostTable`) is what every GPU kernel is compared with bit for bit, so it is itself
+checked here against the textbook formulas written out in numpy (float32 arithmetic, the same order of
+operations), over random sequences of pulls, pushes with duplicates, sync pushes + store, erases and
+set_rows. Modelled on the per-key invariants that the reference asserts inside its test operators
+(pico-ps/test/TestOps.h:87-118)."""
+import numpy as np
+import pytest
+import torch
+from hypothesis import HealthCheck, given, settings
+from hypothesis import strategies as st
+
+from parameter_server_b200 import C, SparseTable
+
+DIM = 4
+F = np.float32
+
+
+class Model:
+    """key -> [w | slots] in float32, updated with the formulas of each optimizer."""
+
+    def __init__(self, opt, kw):
+        self.opt, self.kw, self.rows = opt, kw, {}
+
+    def _init(self, key):
+        w = np.array([C.init_uniform(int(key), d, 0, 0.01) for d in range(DIM)], dtype=F)
+        if self.opt == "adagrad":
+            return [w, np.full(DIM, self.kw.get("init_accumulator", 0.1), dtype=F)]
+        if self.opt in ("sgd", "sum"):
+            return [w]
+        raise NotImplementedError(self.opt)
+
+    def pull(self, keys):
+        out = []
+        for k in keys:
+            if k not in self.rows:
+                self.rows[k] = self._init(k)
+            out.append(self.rows[k][0].copy())
+        return np.stack(out)
+
+    def push(self, keys, grads):
+        agg = {}
+        for k, g in zip(keys, grads):          # client-side pre-aggregation in batch order
+            agg[k] = agg.get(k, np.zeros(DIM, dtype=F)) + g.astype(F)
+        for k, g in agg.items():
+            if k not in self.rows:
+                self.rows[k] = self._init(k)
+            r = self.rows[k]
+            if self.opt == "sum":
+                r[0] = (r[0] + g).astype(F)
+            elif self.opt == "sgd":
+                r[0] = (r[0] - F(self.kw["lr"]) * g).astype(F)
+            elif self.opt == "adagrad":
+                r[1] = (r[1] + g * g).astype(F)
+                r[0] = (r[0] - F(self.kw["lr"]) * g / (np.sqrt(r[1]) + F(1e-10))).astype(F)
+
+    def erase(self, keys):
+        for k in set(keys):
+            self.rows.pop(k, None)
+
+
+ops = st.lists(st.tuples(st.sampled_from(["pull", "push", "erase"]),
+                         st.lists(st.integers(min_value=0, max_value=40), min_size=1, max_size=24),
+                         st.integers(min_value=0, max_value=2 ** 31 - 1)), min_size=1, max_size=25)
+
+
+@pytest.mark.parametrize("opt,kw,exact", [("sum", {}, True), ("sgd", {"lr": 0.5}, True),
+                                          ("adagrad", {"lr": 0.05, "init_accumulator": 0.1}, False)])
+@settings(max_examples=60, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@given(ops=ops, n_shards=st.integers(min_value=1, max_value=7))
+def test_host_table_follows_the_textbook_model(opt, kw, exact, ops, n_shards):
+    t = SparseTable(DIM, opt, kw or None, n_shards=n_shards, device="cpu")
+    m = Model(opt, kw)
+    for kind, keys, seed in ops:
+        k = torch.tensor(keys, dtype=torch.int64)
+        if kind == "pull":
+            got = t.pull(k).numpy()
+            want = m.pull(keys)
+            assert np.array_equal(got, want) if exact else np.allclose(got, want, rtol=1e-6, atol=1e-9)
+        elif kind == "push":
+            g = np.random.default_rng(seed).standard_normal((len(keys), DIM)).astype(F) * F(0.01)
+            t.pull(k)                       # the push plan comes from the last pull
+            m.pull(keys)
+            t.push(torch.from_numpy(g))
+            m.push(keys, g)
+        else:
+            t.erase_keys(k)
+            m.erase(keys)
+        assert t.size() == len(m.rows)
+    # final state, slots included
+    if m.rows:
+        ks = sorted(m.rows)
+        rows, found = t.get_rows(torch.tensor(ks, dtype=torch.int64), emb_only=False)
+        assert found.all()
+        want = np.stack([np.concatenate(m.rows[k]) for k in ks])
+        assert np.array_equal(rows.numpy(), want) if exact else np.allclose(rows.numpy(), want, rtol=1e-6, atol=1e-9)
+
+
+@settings(max_examples=80, deadline=None)
+@given(keys=st.lists(st.integers(min_value=-(2 ** 62), max_value=2 ** 62), min_size=1, max_size=64, unique=True),
+       n_old=st.integers(min_value=1, max_value=64), grow=st.integers(min_value=1, max_value=8))
+def test_jump_hash_moves_keys_only_to_new_shards(keys, n_old, grow):
+    """Consistent hashing: growing the shard count from n to n + g never moves a key between OLD shards."""
+    for k in keys:
+        a, b = C.sparse_shard_of(k, n_old), C.sparse_shard_of(k, n_old + grow)
+        assert 0 <= a < n_old and 0 <= b < n_old + grow
+        assert b == a or b >= n_old
+
+
+@settings(max_examples=100, deadline=None)
+@given(i=st.integers(min_value=-(2 ** 63), max_value=2 ** 63 - 1), d=st.floats(allow_nan=False),
+       s=st.text(max_size=40), v=st.lists(st.integers(min_value=-(2 ** 31), max_value=2 ** 31 - 1), max_size=20),
+       vs=st.lists(st.text(max_size=12), max_size=6))
+def test_archive_round_trip(i, d, s, v, vs):
+    i2, d2, s2, v2, vs2, code, msg, exhausted, _ = C.archive_round_trip(i, d, s, v, vs)
+    assert (i2, s2, list(v2), list(vs2)) == (i, s, v, vs) and d2 == d
+    assert code == 3 and msg == "full" and exhausted            # the Status that follows survives too
+
+
+@settings(max_examples=40, deadline=None)
+@given(data=st.binary(max_size=4096), algo=st.sampled_from(["", "zstd", "lz4", "snappy"]))
+def test_compression_round_trip(data, algo):
+    stt, back, _ = C.compress_round_trip(algo, data)
+    assert stt.ok() and back == data
