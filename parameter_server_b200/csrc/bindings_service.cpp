@@ -356,6 +356,12 @@ void bind_service(py::module_& m) {
 
     py::class_<SyncHandler>(m, "SyncHandler")
         .def(py::init(&make_handler<SyncHandler>), py::keep_alive<1, 2>())
+        .def("metrics", [](SyncHandler& h) { return metrics_dict(h); })
+        .def("sync_pred", [](SyncHandler& h, Server& trainer, int32_t trainer_sid, int max_attempts, double backoff_scale) {
+            uint64_t n = 0;
+            Status st = h.sync_pred(trainer, trainer_sid, &n, max_attempts, backoff_scale);
+            return std::make_tuple(st, n);
+        }, py::arg("trainer"), py::arg("trainer_sid"), py::arg("max_attempts") = 5, py::arg("backoff_scale") = 1.0, nogil())
         .def("block_size", &SyncHandler::block_size)
         .def("sync_block", [](SyncHandler& h, KeyArray keys, F32Array rows, int timeout_ms) {
             const uint32_t stride = (uint32_t)(rows.size() / std::max<py::ssize_t>(1, keys.size()));

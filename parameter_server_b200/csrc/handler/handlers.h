@@ -666,6 +666,45 @@ public:
         std::shared_ptr<KVSyncOperator> p;
         return op(&p).ok() ? p->block_size() : 1000;
     }
+
+    // One incremental sync of the trainer table `trainer_sid` (held by `trainer`) into the predictor table behind
+    // this handler, with the retry policy of SyncHandler::sync_pred (pico-ps/handler/SyncHandler.h:36-138): a
+    // failed pass leaves the dirty marks in place (the iterator is rewound), the handler backs off - NoReplica
+    // 5 s, ServerTooNewCtx 1 s (after refreshing the context), Timeout 3 s, InvalidID re-initialises the storage
+    // on this client - and tries again, at most `max_attempts` times. `backoff_scale` scales the pauses.
+    Status sync_pred(Server& trainer, int32_t trainer_sid, uint64_t* n_synced, int max_attempts = 5, double backoff_scale = 1.0) {
+        Status st;
+        uint64_t total = 0;
+        for (int attempt = 0; attempt < max_attempts; ++attempt) {
+            uint64_t n = 0;
+            st = trainer.push_sync_table(trainer_sid, block_size(),
+                                         [&](const int64_t* k, const float* r, size_t m, uint32_t stride) { return sync_block(k, r, m, stride); }, &n);
+            total += n;
+            if (st.ok()) break;
+            ++metrics_.retries;
+            double pause_s = 0;
+            bool refresh_after_pause = false;
+            if (st.is(StatusCode::NO_REPLICA)) {
+                pause_s = 5;  // somebody may restore the shard meanwhile: look at the published context again afterwards
+                refresh_after_pause = true;
+            }
+            else if (st.is(StatusCode::SERVER_TOO_NEW_CTX) || st.is(StatusCode::SERVER_TOO_NEW_CTX_U)) {
+                client_->handle_server_too_new_ctx(sid_);
+                pause_s = 1;
+            } else if (st.is(StatusCode::TIMEOUT)) {
+                client_->handle_timeout(sid_);
+                pause_s = 3;
+            } else if (st.is(StatusCode::INVALID_ID)) {
+                client_->initialize_storage(sid_);
+                pause_s = 0.1;
+            } else break;  // anything else goes to the caller
+            std::this_thread::sleep_for(std::chrono::milliseconds((long)(pause_s * 1000 * backoff_scale)));
+            if (refresh_after_pause) client_->pull_context(sid_);
+        }
+        if (!st.ok()) ++metrics_.errors;
+        *n_synced = total;
+        return st;
+    }
 };
 
 class UDFHandler : public Handler {

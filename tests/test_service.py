@@ -606,3 +606,46 @@ def test_prometheus_metrics_endpoint(cluster3):
     assert 'ps_request_duration_ms_bucket' in text and 'le="+Inf"' in text and "ps_response_size_bytes" in text
     assert f'ps_storage_items{{node_id="{node}",storage_id="{sid}"}}' in text
     assert "ps_wait_request_count" in handler_metrics_text(pull, "pull")
+
+
+def test_sync_pred_backs_off_and_resumes_after_the_predictor_comes_back():
+    """The predictor's only server is down when the sync starts: the pass fails (time-out -> dead node ->
+    no replica), the dirty marks stay, the handler backs off; meanwhile a fresh server restores the predictor table
+    from its dump, and a later attempt delivers everything."""
+    import tempfile
+    cl = Cluster(3)
+    try:
+        ids = cl.ids()
+        cfg = op_cfg(optimizer="sgd", lr=1.0)
+        trainer, ht = make_table(cl, {ids[0]: [0, 1]}, cfg=cfg)
+        predictor, hp = make_table(cl, {ids[2]: [0, 1]}, cfg=cfg)
+        assert cl.servers[0].enable_sync(trainer).ok()
+        uri = tempfile.mkdtemp(prefix="psb_pred_")
+        assert S.DumpHandler(cl.client, predictor, hp["dump"]).dump(uri, 1)[0].ok()   # (empty) image for the restore
+        assert cl.client.set_table_uri(predictor, uri).ok()
+        keys = np.arange(300, dtype=np.int64)
+        assert S.PushHandler(cl.client, trainer, ht["push"]).async_push(keys, -np.ones((300, DIM), np.float32)).ok()
+        cl.servers[2].stop()                                     # the predictor's server is gone
+        sync = S.SyncHandler(cl.client, predictor, hp["sync"])
+        result = {}
+
+        def run_sync():
+            result["out"] = sync.sync_pred(cl.servers[0], trainer, max_attempts=8, backoff_scale=0.1)
+
+        th = threading.Thread(target=run_sync)
+        th.start()
+        time.sleep(0.8)                                          # a few failed passes with back-off
+        fresh = S.Server(cl.master.address())
+        cl.servers.append(fresh)
+        st, n = fresh.restore_storages()
+        assert st.ok() and n == 1, st
+        th.join(60)
+        assert not th.is_alive()
+        st, n = result["out"]
+        assert st.ok(), st
+        assert n >= 300                                          # everything arrived (a failed pass may have re-sent blocks)
+        assert sync.metrics()["retries"] >= 1
+        st, rows = S.PullHandler(cl.client, predictor, hp["pull_ro"]).pull(keys, 20000, True)
+        assert st.ok() and np.all(rows == 1.0)
+    finally:
+        cl.close()
