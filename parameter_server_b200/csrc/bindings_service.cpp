@@ -382,7 +382,26 @@ void bind_service(py::module_& m) {
             py::list out;
             for (auto& r : rs) out.append(py::make_tuple(r.first, py::bytes(r.second)));
             return py::make_tuple(st, out);
-        }, py::arg("param"), py::arg("timeout_ms") = -1, py::arg("retry") = true);
+        }, py::arg("param"), py::arg("timeout_ms") = -1, py::arg("retry") = true)
+        .def("generate_request", [](UDFHandler& h, py::bytes param) {
+            auto req = std::make_shared<UDFHandler::Request>();
+            Status st = h.generate_request(std::string(param), req.get());
+            return py::make_tuple(st, req);
+        })
+        .def("send_request", [](UDFHandler& h, std::shared_ptr<UDFHandler::Request> req, int timeout_ms) {
+            std::vector<std::pair<int, std::string>> rs;
+            Status st;
+            {
+                py::gil_scoped_release g;
+                st = h.send_request(*req, &rs, timeout_ms);
+            }
+            py::list out;
+            for (auto& r : rs) out.append(py::make_tuple(r.first, py::bytes(r.second)));
+            return py::make_tuple(st, out);
+        }, py::arg("request"), py::arg("timeout_ms") = -1);
+    py::class_<UDFHandler::Request, std::shared_ptr<UDFHandler::Request>>(m, "UDFRequest")
+        .def_readonly("ctx_version", &UDFHandler::Request::ctx_version)
+        .def("nodes", [](UDFHandler::Request& r) { std::vector<int> n; for (auto& kv : r.bodies) n.push_back(kv.first); return n; });
 
     // ---- controller / model ------------------------------------------------------------------------
     py::class_<OpSpec>(m, "OpSpec")

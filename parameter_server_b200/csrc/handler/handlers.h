@@ -731,6 +731,43 @@ public:
             return Status::Ok();
         }, timeout_ms, retry);
     }
+
+    // Request building split from sending (pico-ps/handler/UDFHandler.cpp:26-36,59-84): a request can be
+    // prepared on another thread; send_request refuses it when the table's context has changed since (the node
+    // list it was built for may be stale) and the caller generates it again.
+    struct Request {
+        std::map<int, Archive> bodies;
+        int32_t ctx_version = -1;
+    };
+    Status generate_request(const std::string& param, Request* req) {
+        auto e = entry();
+        if (!e) return Status::InvalidID("storage is not initialised on this client");
+        req->bodies.clear();
+        std::shared_lock<std::shared_mutex> g(e->mu);
+        req->ctx_version = e->td.version;
+        for (auto& kv : e->rt.nodes())
+            if (e->rt.is_running(kv.first)) req->bodies[kv.first] << param;
+        return Status::Ok();
+    }
+    Status send_request(const Request& req, std::vector<std::pair<int, std::string>>* results, int timeout_ms = -1) {
+        auto e = entry();
+        if (!e) return Status::InvalidID("storage is not initialised on this client");
+        {
+            std::shared_lock<std::shared_mutex> g(e->mu);
+            if (e->td.version != req.ctx_version)
+                return Status::ServerTooNewCtx("the context changed since the request was generated");
+        }
+        results->clear();
+        std::vector<NodeResponse> rs;
+        ++metrics_.requests;
+        PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_UDF, req.bodies, timeout_ms, &rs, req.ctx_version));
+        for (auto& r : rs) {
+            std::string s;
+            r.body >> s;
+            results->push_back({r.node, s});
+        }
+        return Status::Ok();
+    }
 };
 
 }  // namespace psb

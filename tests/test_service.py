@@ -446,6 +446,18 @@ def test_predictor_sync_udf_and_native_ps(tmp_path, cluster3):
     st, hid = cl.client.register_handler("udf", S.LIB, "UDFOperator", json.dumps({"function": "count_items"}), trainer)
     st, results = S.UDFHandler(cl.client, trainer, hid).call(b"hello")
     assert st.ok() and sorted(int(r.split(b":")[0]) for _, r in results) == sorted(s.storage_size(trainer) for s in cl.servers[:2])
+    # request building split from sending: a request built before a context change is refused, a fresh one passes
+    udf = S.UDFHandler(cl.client, trainer, hid)
+    st, req = udf.generate_request(b"x")
+    assert st.ok() and sorted(req.nodes()) == sorted(ids[:2])
+    st, results = udf.send_request(req)
+    assert st.ok() and len(results) == 2
+    assert S.UpdateContextHandler(cl.client, trainer, ht["update_ctx"]).update_context(
+        S.nodes_json({ids[0]: [1], ids[1]: [0]})).ok()                     # a reshard: new context version
+    st, _ = udf.send_request(req)
+    assert st.code() == StatusCode.SERVER_TOO_NEW_CTX
+    st, req = udf.generate_request(b"y")
+    assert udf.send_request(req)[0].ok()
     # NativePS: in-process load of a distributed dump + pull
     uri = str(tmp_path / "serving")
     assert S.DumpHandler(cl.client, trainer, ht["dump"]).dump(uri, 2)[0].ok()
