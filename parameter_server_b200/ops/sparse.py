@@ -167,8 +167,11 @@ class SparseTable:
             raise_if_error(st)
             self._plan_keys = keys  # keep the key buffer alive until the push
             return out
-        st, rows = self.table.pull(keys.cpu().numpy(), bag_size, mean, insert)
-        raise_if_error(st)
+        if self.world > 1:
+            rows = self._cpu_collective_pull(keys.cpu().numpy(), bag_size, mean, insert)
+        else:
+            st, rows = self.table.pull(keys.cpu().numpy(), bag_size, mean, insert)
+            raise_if_error(st)
         self._plan_keys = (keys.cpu().numpy().copy(), bag_size, mean)
         res = torch.from_numpy(rows)
         if out is not None:
@@ -209,7 +212,66 @@ class SparseTable:
         else:
             k, bag, mn = self._plan_keys
             g = grads.detach().cpu().float().numpy().reshape(-1, self.dim)
-            raise_if_error(self.table.push(k, g, self.opt, bag, mn, sync))
+            if self.world > 1:
+                self._cpu_collective_push(k, g, bag, mn, sync)
+            else:
+                raise_if_error(self.table.push(k, g, self.opt, bag, mn, sync))
+
+    # ---- host back-end with more than one rank: the collective protocol over the process group ---------
+    # The same owner-computes scheme as the fused kernels, spelled out with object collectives (any backend,
+    # e.g. gloo): every rank dedups its keys, the owner of a key serves every requester in rank order (so
+    # inserts and the cross-rank gradient fold happen in one fixed order), rows travel back. It exists for
+    # CPU-only jobs and as the multi-process oracle of the host-side logic; it is not a fast path.
+    def _owners_of(self, keys_np: np.ndarray) -> np.ndarray:
+        return np.fromiter((self._shard_owner[C.sparse_shard_of(int(k), self.n_shards)] for k in keys_np), dtype=np.int64,
+                           count=len(keys_np))
+
+    def _cpu_collective_pull(self, keys_np: np.ndarray, bag_size: int, mean: bool, insert: bool) -> np.ndarray:
+        import torch.distributed as dist
+
+        uniq, inv = np.unique(keys_np, return_inverse=True)
+        asked = [None] * self.world
+        dist.all_gather_object(asked, uniq, group=self.group)
+        served = []
+        for r in range(self.world):                      # requester order: inserts happen in one fixed order
+            ks = asked[r]
+            mine = ks[self._owners_of(ks) == self.rank] if len(ks) else ks
+            st, rows = self.table.pull(mine.astype(np.int64), 1, False, insert)
+            raise_if_error(st)
+            served.append(rows)
+        answers = [None] * self.world
+        dist.all_gather_object(answers, served, group=self.group)
+        owners = self._owners_of(uniq)
+        rows = np.empty((len(uniq), self.dim), dtype=np.float32)
+        for o in range(self.world):
+            rows[owners == o] = answers[o][self.rank]
+        out = rows[inv]
+        if bag_size > 1:
+            out = out.reshape(-1, bag_size, self.dim).sum(axis=1, dtype=np.float32)
+            if mean:
+                out = (out / np.float32(bag_size)).astype(np.float32)
+        return out
+
+    def _cpu_collective_push(self, keys_np: np.ndarray, grads: np.ndarray, bag_size: int, mean: bool, sync: bool) -> None:
+        import torch.distributed as dist
+
+        per_pos = np.repeat(grads, bag_size, axis=0) if bag_size > 1 else grads
+        if bag_size > 1 and mean:
+            per_pos = (per_pos / np.float32(bag_size)).astype(np.float32)
+        uniq, inv = np.unique(keys_np, return_inverse=True)
+        agg = np.zeros((len(uniq), self.dim), dtype=np.float32)
+        np.add.at(agg, inv, per_pos.astype(np.float32))   # client-side pre-aggregation
+        sent = [None] * self.world
+        dist.all_gather_object(sent, (uniq, agg), group=self.group)
+        ks, gs = [], []
+        for r in range(self.world):                      # fold the sources in rank order, then ONE update per row
+            u, a = sent[r]
+            if len(u):
+                own = self._owners_of(u) == self.rank
+                ks.append(u[own])
+                gs.append(a[own])
+        if ks and sum(len(k) for k in ks):
+            raise_if_error(self.table.push(np.concatenate(ks).astype(np.int64), np.concatenate(gs), self.opt, 1, False, sync))
 
     def store(self) -> None:
         """Fold the buffered sync pushes into the weights (OP_STORE)."""

@@ -1,0 +1,67 @@
+"""Worker of the CPU multi-process tests (gloo): the collective sparse / dense API on the host back-end against a
+single-process oracle that sees the concatenation of every rank's batch (same checks as the GPU worker)."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from parameter_server_b200 import SparseTable  # noqa: E402
+from parameter_server_b200.ops.dense import DenseTable  # noqa: E402
+
+
+def gather(obj):
+    out = [None] * dist.get_world_size()
+    dist.all_gather_object(out, obj)
+    return out
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo")
+    for dim, opt, kw, bag in [(8, "adagrad", dict(lr=0.05, init_accumulator=0.1), 1), (4, "sgd", dict(lr=0.5), 2),
+                              (8, "adam", dict(lr=0.01), 1)]:
+        n_shards = 2 * world + 1
+        t = SparseTable(dim, opt, kw, n_shards=n_shards, device="cpu")
+        ref = SparseTable(dim, opt, kw, n_shards=n_shards, device="cpu", group="none") if rank == 0 else None
+        rng = np.random.default_rng(5 + rank)
+        for step in range(4):
+            keys = torch.from_numpy((rng.zipf(1.2, size=600).astype(np.int64) * 7919) % 3000)
+            grads = torch.from_numpy(rng.standard_normal((600 // bag, dim)).astype(np.float32) * 1e-2)
+            out = t.pull(keys, bag_size=bag, mean=(bag > 1))
+            t.push(grads, bag_size=bag, mean=(bag > 1))
+            all_keys, all_grads, all_out = gather(keys), gather(grads), gather(out)
+            if rank == 0:
+                want = ref.pull(torch.cat(all_keys), bag_size=bag, mean=(bag > 1))
+                got = torch.cat(all_out)
+                assert torch.allclose(got, want, rtol=1e-5, atol=1e-7), (opt, step, (got - want).abs().max())
+                ref.push(torch.cat(all_grads), bag_size=bag, mean=(bag > 1))
+        sizes = gather(t.size())
+        if rank == 0:
+            assert sum(sizes) == ref.size(), (sizes, ref.size())
+        # every rank holds only keys of its own shards
+        for k, _ in t.export():
+            owners = {t.shard_owner[__import__("parameter_server_b200").C.sparse_shard_of(int(x), n_shards)] for x in k.tolist()}
+            assert owners <= {rank}, owners
+    # dense table: all-reduce + optimizer on every rank, identical parameters everywhere
+    d = DenseTable({"w": (64, 8), "b": (64,)}, "adamw", dict(lr=1e-2, weight_decay=0.01), device="cpu")
+    d.load({"w": torch.ones(64, 8), "b": torch.zeros(64)})
+    for step in range(3):
+        d.zero_grads()
+        d.grads["w"].add_(torch.full((64, 8), float(rank + 1 + step)))
+        d.grads["b"].add_(torch.full((64,), 0.5 * (rank + 1)))
+        d.push()
+    sigs = gather((float(d.pull("w").sum()), float(d.pull("b").sum())))
+    assert all(s == sigs[0] for s in sigs), sigs
+    assert d.pull("w").mean().item() < 1.0           # the weights moved against the (positive) gradient
+    dist.barrier()
+    if rank == 0:
+        print("cpu collective ok", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
