@@ -24,6 +24,10 @@ struct HandlerMetrics {
     std::atomic<uint64_t> wait_us{0};
 };
 
+// Every request carries the context version it was BUILT under (read under the same lock as the placement it was
+// routed by). The client's copy can move on between building and sending when another thread refreshes it; a
+// request stamped with the newer version but routed by the older placement would pass the server's version gate
+// and reach a node that no longer holds the shard.
 class Handler {
 public:
     Handler(Client* client, int32_t sid, int32_t hid) : client_(client), sid_(sid), hid_(hid) {}
@@ -133,13 +137,15 @@ public:
             auto e = entry();
             PullRequestData data;
             NodeRequests reqs;
+            int32_t built_under = -1;
             {
                 std::shared_lock<std::shared_mutex> g(e->mu);
+                built_under = e->td.version;
                 p->generate_request_data(*e, keys, n, &data);
                 PSB_RETURN_IF_ERROR(p->generate_requests(*e, data, &reqs));
             }
             std::vector<NodeResponse> rs;
-            PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_PULL, reqs.body, left, &rs));
+            PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_PULL, reqs.body, left, &rs, built_under));
             for (auto& r : rs) PSB_RETURN_IF_ERROR(p->apply_response(*e, &data, r.body));
             p->fill_pull_items(*e, data, out);
             return Status::Ok();
@@ -188,12 +194,14 @@ private:
                 if ((tids >> t) & 1u) ds.push_back(&g.data[t]);
             st = [&]() -> Status {
                 NodeRequests reqs;
+                int32_t built_under = -1;
                 {
                     std::shared_lock<std::shared_mutex> lk(e->mu);
+                    built_under = e->td.version;
                     PSB_RETURN_IF_ERROR(p.generate_merged_requests(*e, ds, &reqs));
                 }
                 std::vector<NodeResponse> rs;
-                PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_PULL, reqs.body, left, &rs));
+                PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_PULL, reqs.body, left, &rs, built_under));
                 for (auto& r : rs) PSB_RETURN_IF_ERROR(p.apply_merged_response(*e, ds, r.body));
                 return Status::Ok();
             }();
@@ -246,11 +254,13 @@ public:
         return with_retry([&](int left) -> Status {
             auto e = entry();
             std::map<int, Archive> bodies;
+            int32_t built_under = -1;
             {
                 std::shared_lock<std::shared_mutex> g(e->mu);
+                built_under = e->td.version;
                 for (auto& kv : e->rt.nodes()) bodies[kv.first] << (int32_t)(kv.second.empty() ? -1 : kv.second.front());
             }
-            return client_->send_and_wait(sid_, hid_, RequestType::OP_STORE, bodies, left, nullptr);
+            return client_->send_and_wait(sid_, hid_, RequestType::OP_STORE, bodies, left, nullptr, built_under);
         }, timeout_ms);
     }
     Status push_dense(int64_t id, const float* grad, size_t numel, bool sync, int timeout_ms = -1) {
@@ -274,15 +284,17 @@ private:
             auto e = entry();
             PushRequestData data;
             NodeRequests reqs;
+            int32_t built_under = -1;
             {
                 std::shared_lock<std::shared_mutex> g(e->mu);
+                built_under = e->td.version;
                 p->generate_request_data(*e, keys, grads, n, &data);  // regenerated against the fresh context on retry
                 if (ack.G != data.global_shard_num) ack.reset(data.global_shard_num);  // other shard count: start over
                 PSB_RETURN_IF_ERROR(p->generate_requests(*e, data, &reqs, &ack));
             }
             if (reqs.body.empty()) return Status::Ok();  // everything was applied by earlier attempts
             std::vector<NodeResponse> rs;
-            Status st = client_->send_and_wait(sid_, hid_, type, reqs.body, left, &rs);
+            Status st = client_->send_and_wait(sid_, hid_, type, reqs.body, left, &rs, built_under);
             for (auto& r : rs)
                 for (int32_t sh : reqs.shards[r.node]) ack.record(sh, r.node, r.status.ok());
             return st;
@@ -327,13 +339,15 @@ private:
             Status st = [&]() -> Status {
                 NodeRequests reqs;
                 std::vector<std::vector<std::pair<int, int32_t>>> sent;
+                int32_t built_under = -1;
                 {
                     std::shared_lock<std::shared_mutex> lk(e->mu);
+                    built_under = e->td.version;
                     PSB_RETURN_IF_ERROR(p.generate_merged_requests(*e, ds, acks, &reqs, &sent));
                 }
                 if (reqs.body.empty()) return Status::Ok();
                 std::vector<NodeResponse> rs;
-                Status sst = client_->send_and_wait(sid_, hid_, kind, reqs.body, left, &rs);
+                Status sst = client_->send_and_wait(sid_, hid_, kind, reqs.body, left, &rs, built_under);
                 std::map<int, bool> node_ok;
                 for (auto& r : rs) node_ok[r.node] = r.status.ok();
                 for (size_t i = 0; i < ds.size(); ++i)   // the members sleep until the broadcast: their state is ours to update
@@ -362,8 +376,10 @@ public:
             *result = ForEachResult();
             auto e = entry();
             std::vector<std::pair<int, int32_t>> targets;
+            int32_t built_under = -1;
             {
                 std::shared_lock<std::shared_mutex> g(e->mu);
+                built_under = e->td.version;
                 for (auto& kv : e->rt.shards()) {
                     int node = e->rt.pick_one_replica(kv.first);
                     if (node < 0) return Status::NoReplica("for_each: no live replica of shard " + std::to_string(kv.first));
@@ -374,7 +390,7 @@ public:
                 std::map<int, Archive> body;
                 body[t.first] << t.second << carried_json;
                 std::vector<NodeResponse> rs;
-                PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_FOREACH, body, left, &rs));
+                PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_FOREACH, body, left, &rs, built_under));
                 ForEachResult r;
                 rs[0].body >> r.count >> r.sum >> r.sum_sq >> r.max_abs;
                 result->merge(r);
@@ -394,8 +410,10 @@ public:
             auto e = entry();
             std::vector<std::pair<int, int32_t>> targets;
             std::map<int32_t, int> primary;
+            int32_t built_under = -1;
             {
                 std::shared_lock<std::shared_mutex> g(e->mu);
+                built_under = e->td.version;
                 for (auto& kv : e->rt.shards())
                     for (int node : kv.second) {
                         targets.push_back({node, kv.first});
@@ -406,7 +424,7 @@ public:
                 std::map<int, Archive> body;
                 body[t.first] << t.second << carried_json;
                 std::vector<NodeResponse> rs;
-                PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_ERASEIF, body, left, &rs));
+                PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_ERASEIF, body, left, &rs, built_under));
                 uint64_t n = 0;
                 rs[0].body >> n;
                 if (primary[t.second] == t.first) *erased += n;
@@ -428,8 +446,10 @@ public:
             *n_records = 0;
             auto e = entry();
             std::map<int, std::map<int32_t, std::vector<int32_t>>> plan;  // node -> file -> shards
+            int32_t built_under = -1;
             {
                 std::shared_lock<std::shared_mutex> g(e->mu);
+                built_under = e->td.version;
                 // every shard is dumped once: by its first live holder
                 for (auto& kv : e->rt.shards()) {
                     int node = -1;
@@ -444,7 +464,7 @@ public:
                     std::map<int, Archive> body;
                     body[nk.first] << args.uri << args.file_number << fk.first << fk.second;
                     std::vector<NodeResponse> rs;
-                    PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_DUMP, body, left, &rs));
+                    PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_DUMP, body, left, &rs, built_under));
                     uint64_t n = 0;
                     rs[0].body >> n;
                     *n_records += n;
@@ -483,8 +503,10 @@ private:
             *n_records = 0;
             auto e = entry();
             std::vector<int> nodes;
+            int32_t built_under = -1;
             {
                 std::shared_lock<std::shared_mutex> g(e->mu);
+                built_under = e->td.version;
                 for (auto& kv : e->rt.nodes())
                     if (e->rt.is_running(kv.first)) nodes.push_back(kv.first);
             }
@@ -505,7 +527,7 @@ private:
                 }
                 if (bodies.empty()) break;
                 std::vector<NodeResponse> rs;
-                PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_LOAD, bodies, left, &rs));
+                PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_LOAD, bodies, left, &rs, built_under));
                 for (auto& r : rs) {
                     uint64_t n = 0;
                     r.body >> n;
@@ -649,8 +671,10 @@ public:
         PSB_RETURN_IF_ERROR(op(&p));
         auto e = entry();
         std::map<int, Archive> plain;
+        int32_t built_under = -1;
         {
             std::shared_lock<std::shared_mutex> g(e->mu);
+            built_under = e->td.version;
             PSB_RETURN_IF_ERROR(DirectPushOperator::generate_requests(storage_op_of(*e), e->rt, keys, rows, n, stride, &plain));
         }
         std::map<int, Archive> bodies;
@@ -660,7 +684,7 @@ public:
             bodies[kv.first] << packed;
         }
         ++metrics_.requests;
-        return client_->send_and_wait(sid_, hid_, RequestType::OP_SYNC, bodies, timeout_ms, nullptr);
+        return client_->send_and_wait(sid_, hid_, RequestType::OP_SYNC, bodies, timeout_ms, nullptr, built_under);
     }
     size_t block_size() {
         std::shared_ptr<KVSyncOperator> p;
@@ -716,13 +740,15 @@ public:
             results->clear();
             auto e = entry();
             std::map<int, Archive> bodies;
+            int32_t built_under = -1;
             {
                 std::shared_lock<std::shared_mutex> g(e->mu);
+                built_under = e->td.version;
                 for (auto& kv : e->rt.nodes())
                     if (e->rt.is_running(kv.first)) bodies[kv.first] << param;
             }
             std::vector<NodeResponse> rs;
-            PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_UDF, bodies, left, &rs));
+            PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_UDF, bodies, left, &rs, built_under));
             for (auto& r : rs) {
                 std::string s;
                 r.body >> s;

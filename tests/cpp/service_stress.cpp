@@ -7,7 +7,8 @@
 // checks that every gradient was applied exactly once. A second phase reads a table with two replicas per
 // shard from four threads while one server is stopped, a fresh one restores the lost shards from the live
 // replicas, and a second original server is stopped. A third phase mixes immediate and buffered (sync + store)
-// pushes from four threads with statistics scans and dumps. ThreadSanitizer checks the rest.
+// pushes from four threads with statistics scans and dumps. In a fourth the controller changes the shard count
+// and the replica count of a table and rebalances it while four threads read it. ThreadSanitizer checks the rest.
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
@@ -17,6 +18,7 @@
 #include <thread>
 #include <vector>
 
+#include "controller/controller.h"
 #include "handler/handlers.h"
 #include "service/master.h"
 #include "service/server.h"
@@ -257,6 +259,64 @@ int main() {
             if (got[(size_t)k * kDim] != (float)sent[k].load()) ++wrong3;
         std::printf("phase 3: %d wrong\n", wrong3);
         wrong += wrong3;
+    }
+    // ---- phase 4: the controller (its own client) reshapes a table - more shards, two replicas, rebalance - while
+    // four threads of the first client keep reading it -------------------------------------------------------------
+    {
+        Controller ctl(master.address());
+        std::vector<OpSpec> ops = {{"pull_ro", "psb", "SparseTablePullOperator", "{\"read_only\":true}"},
+                                   {"push", "psb", "SparseTablePushOperator", "{}"},
+                                   {"update_ctx", "psb", "ShardUpdateContextOperator", "{}"}};
+        int32_t sid4 = -1;
+        MUST(ctl.create_table("ctl_table", "psb", "SparseTableStorageOperator",
+                              "{\"dim\":4,\"optimizer\":\"sum\",\"init_range\":0.0}", 4, 1, ops, "", &sid4));
+        MUST(client.initialize_storage(sid4));
+        int32_t hp = -1, hq = -1;
+        MUST(client.handler_by_key(sid4, "pull_ro", &hp));
+        MUST(client.handler_by_key(sid4, "push", &hq));
+        std::vector<float> vals((size_t)kKeys * kDim);
+        for (int k = 0; k < kKeys; ++k)
+            for (int d = 0; d < kDim; ++d) vals[(size_t)k * kDim + d] = (float)(k % 5 + 2);
+        {
+            PushHandler seed(&client, sid4, hq);
+            MUST(seed.async_push(all.data(), vals.data(), all.size(), 20000));
+        }
+        std::atomic<bool> stop_readers{false};
+        std::atomic<int> bad_reads{0}, reads{0};
+        std::vector<std::thread> readers;
+        for (int t = 0; t < kThreads; ++t)
+            readers.emplace_back([&, t] {
+                PullHandler h(&client, sid4, hp);
+                std::vector<int64_t> keys(kBatch);
+                std::vector<float> got((size_t)kBatch * kDim);
+                uint64_t x = 424242 + (uint64_t)t;
+                while (!stop_readers.load()) {
+                    for (auto& k : keys) {
+                        x ^= x << 13; x ^= x >> 7; x ^= x << 17;
+                        k = (int64_t)(x % kKeys);
+                    }
+                    Status st = h.pull(keys.data(), keys.size(), got.data(), 20000);
+                    if (!st.ok()) { std::fprintf(stderr, "phase 4 read: %s\n", st.msg().c_str()); ++bad_reads; continue; }
+                    for (size_t i = 0; i < keys.size(); ++i)
+                        if (got[i * kDim] != (float)(keys[i] % 5 + 2)) ++bad_reads;
+                    ++reads;
+                }
+            });
+        int ctl_bad = 0;
+        Status st = ctl.update_table_shard(sid4, 6);
+        if (!st.ok()) { std::fprintf(stderr, "update_table_shard: %s\n", st.msg().c_str()); ++ctl_bad; }
+        st = ctl.update_table_replica(sid4, 2);
+        if (!st.ok()) { std::fprintf(stderr, "update_table_replica: %s\n", st.msg().c_str()); ++ctl_bad; }
+        st = ctl.balance_table(sid4);
+        if (!st.ok()) { std::fprintf(stderr, "balance_table: %s\n", st.msg().c_str()); ++ctl_bad; }
+        Json shown;
+        st = ctl.show_nodes(&shown);
+        if (!st.ok()) ++ctl_bad;
+        std::this_thread::sleep_for(std::chrono::milliseconds(100));
+        stop_readers = true;
+        for (auto& r : readers) r.join();
+        std::printf("phase 4: %d reads, %d bad, %d controller errors\n", reads.load(), bad_reads.load(), ctl_bad);
+        wrong += bad_reads.load() + ctl_bad;
     }
     for (auto& s : servers) s->stop();
     master.stop();
