@@ -8,7 +8,9 @@
 // shard from four threads while one server is stopped, a fresh one restores the lost shards from the live
 // replicas, and a second original server is stopped. A third phase mixes immediate and buffered (sync + store)
 // pushes from four threads with statistics scans and dumps. In a fourth the controller changes the shard count
-// and the replica count of a table and rebalances it while four threads read it. ThreadSanitizer checks the rest.
+// and the replica count of a table and rebalances it while four threads read it. In a fifth the rows that change
+// on a trainer table are shipped to a predictor table again and again while four threads keep pushing, and the
+// predictor must end up equal to the trainer. ThreadSanitizer checks the rest.
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
@@ -317,6 +319,75 @@ int main() {
         for (auto& r : readers) r.join();
         std::printf("phase 4: %d reads, %d bad, %d controller errors\n", reads.load(), bad_reads.load(), ctl_bad);
         wrong += bad_reads.load() + ctl_bad;
+    }
+    // ---- phase 5: incremental sync trainer -> predictor while the trainer is being pushed to ----------------------
+    {
+        std::map<int32_t, std::string> live;
+        MUST(client.get_pserver_list(&live));
+        std::vector<int> ids;
+        for (auto& kv : live) ids.push_back(kv.first);
+        std::vector<Server*> by_id;
+        for (int id : ids)
+            for (auto& sp : servers)
+                if (sp->node_id() == id && !sp->exited()) by_id.push_back(sp.get());
+        const std::string opc = ",\"op_config\":{\"dim\":4,\"optimizer\":\"sum\",\"init_range\":0.0},\"table_name\":\"";
+        int32_t trainer = -1, predictor = -1, hq = -1, hs = -1, hp = -1;
+        MUST(client.create_storage("psb", "SparseTableStorageOperator",
+                                   "{\"nodes\":" + nodes_json({{ids[0], {0, 1}}}) + opc + "tr\"}", &trainer));
+        MUST(client.create_storage("psb", "SparseTableStorageOperator",
+                                   "{\"nodes\":" + nodes_json({{ids[1], {0, 1, 2}}}) + opc + "pr\"}", &predictor));
+        MUST(client.register_handler("push", "psb", "SparseTablePushOperator", "{}", trainer, &hq));
+        MUST(client.register_handler("sync", "psb", "KVSyncOperator", "{\"block_size\":64}", predictor, &hs));
+        MUST(client.register_handler("pull_ro", "psb", "SparseTablePullOperator", "{\"read_only\":true}", predictor, &hp));
+        Server* tsrv = by_id.empty() ? nullptr : by_id[0];
+        if (tsrv == nullptr) { std::fprintf(stderr, "phase 5: trainer server not found\n"); return 1; }
+        MUST(tsrv->enable_sync(trainer));
+        std::vector<std::atomic<uint64_t>> sent(kKeys);
+        for (auto& x : sent) x = 0;
+        std::atomic<int> bad{0};
+        std::atomic<bool> pushing{true};
+        std::vector<std::thread> ts;
+        for (int t = 0; t < kThreads; ++t)
+            ts.emplace_back([&, t] {
+                PushHandler h(&client, trainer, hq);
+                std::vector<int64_t> keys(kBatch);
+                std::vector<float> grads((size_t)kBatch * kDim, 1.0f);
+                uint64_t x = 777 + (uint64_t)t * 13;
+                for (int it = 0; it < 50; ++it) {
+                    for (auto& k : keys) {
+                        x ^= x << 13; x ^= x >> 7; x ^= x << 17;
+                        k = (int64_t)(x % kKeys);
+                    }
+                    Status st = h.async_push(keys.data(), grads.data(), keys.size(), 20000);
+                    if (!st.ok()) { std::fprintf(stderr, "phase 5 push: %s\n", st.msg().c_str()); ++bad; continue; }
+                    for (auto k : keys) ++sent[(size_t)k];
+                }
+            });
+        SyncHandler sync(&client, predictor, hs);
+        uint64_t synced_total = 0;
+        std::thread syncer([&] {
+            while (pushing.load()) {
+                uint64_t n = 0;
+                Status st = sync.sync_pred(*tsrv, trainer, &n, 3, 0.01);
+                if (!st.ok()) { std::fprintf(stderr, "phase 5 sync: %s\n", st.msg().c_str()); ++bad; }
+                synced_total += n;
+                std::this_thread::sleep_for(std::chrono::milliseconds(2));
+            }
+        });
+        for (auto& t : ts) t.join();
+        pushing = false;
+        syncer.join();
+        uint64_t n = 0;
+        MUST(sync.sync_pred(*tsrv, trainer, &n, 3, 0.01));        // what the last round left
+        synced_total += n;
+        PullHandler ph(&client, predictor, hp);
+        std::vector<float> got((size_t)kKeys * kDim);
+        MUST(ph.pull(all.data(), all.size(), got.data(), 20000));
+        int wrong5 = bad.load();
+        for (int k = 0; k < kKeys; ++k)
+            if (got[(size_t)k * kDim] != (float)sent[k].load()) ++wrong5;
+        std::printf("phase 5: %llu rows synced, %d wrong\n", (unsigned long long)synced_total, wrong5);
+        wrong += wrong5;
     }
     for (auto& s : servers) s->stop();
     master.stop();
