@@ -10,7 +10,8 @@
 // pushes from four threads with statistics scans and dumps. In a fourth the controller changes the shard count
 // and the replica count of a table and rebalances it while four threads read it. In a fifth the rows that change
 // on a trainer table are shipped to a predictor table again and again while four threads keep pushing, and the
-// predictor must end up equal to the trainer. ThreadSanitizer checks the rest.
+// predictor must end up equal to the trainer. A sixth loads the trainer's dump into an in-process table with four
+// threads and reads it from four. ThreadSanitizer checks the rest.
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
@@ -22,6 +23,7 @@
 
 #include "controller/controller.h"
 #include "handler/handlers.h"
+#include "native_ps/native_ps.h"
 #include "service/master.h"
 #include "service/server.h"
 
@@ -388,6 +390,43 @@ int main() {
             if (got[(size_t)k * kDim] != (float)sent[k].load()) ++wrong5;
         std::printf("phase 5: %llu rows synced, %d wrong\n", (unsigned long long)synced_total, wrong5);
         wrong += wrong5;
+
+        // ---- phase 6: the trainer's dump is loaded into an in-process table by four threads and read by four ----
+        int32_t hd = -1;
+        MUST(client.register_handler("dump", "psb", "DumpOperator", "{}", trainer, &hd));
+        char tmpl[] = "/tmp/psb_stress_native_XXXXXX";
+        const char* dir = ::mkdtemp(tmpl);
+        if (dir == nullptr) return 1;
+        DumpArgs da;
+        da.uri = dir;
+        da.file_number = 4;
+        uint64_t dumped = 0;
+        MUST(DumpHandler(&client, trainer, hd).dump(da, &dumped, 20000));
+        NativePS nps;
+        int32_t nsid = -1, nl = -1, np_ = -1;
+        MUST(nps.create_storage("psb", "SparseTableStorageOperator", "{\"dim\":4,\"optimizer\":\"sum\",\"init_range\":0.0}", 3, &nsid));
+        MUST(nps.register_handler(nsid, "load", "psb", "LoadOperator", "{}", &nl));
+        MUST(nps.register_handler(nsid, "pull", "psb", "SparseTablePullOperator", "{\"read_only\":true}", &np_));
+        uint64_t loaded = 0;
+        MUST(NativeLoadHandler(&nps, nsid, nl).load(dir, 4, &loaded));
+        std::atomic<int> bad6{0};
+        std::vector<std::thread> rs;
+        for (int t = 0; t < kThreads; ++t)
+            rs.emplace_back([&, t] {
+                NativePullHandler h(&nps, nsid, np_);
+                std::vector<float> rows((size_t)kKeys * kDim);
+                for (int it = 0; it < 5; ++it) {
+                    Status st = h.pull(all.data(), all.size(), rows.data());
+                    if (!st.ok()) { ++bad6; continue; }
+                    for (int k = 0; k < kKeys; ++k)
+                        if (rows[(size_t)k * kDim] != (float)sent[k].load()) ++bad6;
+                }
+            });
+        for (auto& t : rs) t.join();
+        std::string cmd = std::string("rm -rf ") + dir;
+        if (std::system(cmd.c_str()) != 0) ++bad6;
+        std::printf("phase 6: dumped %llu, loaded %llu, %d wrong\n", (unsigned long long)dumped, (unsigned long long)loaded, bad6.load());
+        wrong += bad6.load() + (dumped == loaded ? 0 : 1);
     }
     for (auto& s : servers) s->stop();
     master.stop();
