@@ -58,7 +58,7 @@ public:
 
     // --- reading -------------------------------------------------------------------------
     void read_raw(void* p, size_t n) {
-        if (cur_ + n > buf_.size()) throw std::out_of_range("Archive::read_raw past end");
+        if (n > buf_.size() - cur_) throw std::out_of_range("Archive::read_raw past end");  // no overflow: cur_ <= size
         std::memcpy(p, buf_.data() + cur_, n);
         cur_ += n;
     }
@@ -70,7 +70,7 @@ public:
     Archive& operator>>(std::string& s) {
         uint64_t n = 0;
         read_raw(&n, 8);
-        if (cur_ + n > buf_.size()) throw std::out_of_range("Archive: string past end");
+        if (n > buf_.size() - cur_) throw std::out_of_range("Archive: string past end");
         s.assign((const char*)buf_.data() + cur_, n);
         cur_ += n;
         return *this;
@@ -79,7 +79,7 @@ public:
     typename std::enable_if<std::is_trivially_copyable<T>::value, Archive&>::type operator>>(std::vector<T>& v) {
         uint64_t n = 0;
         read_raw(&n, 8);
-        if (cur_ + n * sizeof(T) > buf_.size()) throw std::out_of_range("Archive: vector past end");
+        if (n > (buf_.size() - cur_) / sizeof(T)) throw std::out_of_range("Archive: vector past end");
         v.resize(n);
         if (n) read_raw(v.data(), n * sizeof(T));
         return *this;
@@ -87,6 +87,7 @@ public:
     Archive& operator>>(std::vector<std::string>& v) {
         uint64_t n = 0;
         read_raw(&n, 8);
+        if (n > (buf_.size() - cur_) / 8) throw std::out_of_range("Archive: string vector past end");  // each entry has an 8-byte length
         v.resize(n);
         for (auto& s : v) *this >> s;
         return *this;
@@ -102,12 +103,14 @@ public:
 
     bool is_exhausted() const { return cur_ == buf_.size(); }
     size_t remaining() const { return buf_.size() - cur_; }
+    // A count read from the wire may claim at most what is left: `n` records of `record_bytes` each.
+    bool can_hold(int64_t n, size_t record_bytes) const { return n >= 0 && (uint64_t)n <= remaining() / (record_bytes ? record_bytes : 1); }
     size_t size() const { return buf_.size(); }
     size_t cursor() const { return cur_; }
     const uint8_t* data() const { return buf_.data(); }
     const uint8_t* cursor_ptr() const { return buf_.data() + cur_; }
     void skip(size_t n) {
-        if (cur_ + n > buf_.size()) throw std::out_of_range("Archive::skip past end");
+        if (n > buf_.size() - cur_) throw std::out_of_range("Archive::skip past end");
         cur_ += n;
     }
     void rewind() { cur_ = 0; }

@@ -271,6 +271,8 @@ public:
         const uint32_t dim = st->dim();
         int32_t shards_num = 0, merge_num = 0;
         req >> shards_num >> merge_num;
+        // counts come from the wire: each shard carries at least an id and merge_num list lengths
+        if (merge_num < 0 || !req.can_hold(shards_num, 4 + (size_t)merge_num * 4)) return Status::Error("pull: malformed request");
         std::vector<int32_t> ids;
         std::vector<std::vector<float>> vals;
         for (int32_t i = 0; i < shards_num; ++i) {
@@ -281,6 +283,7 @@ public:
             for (int32_t m = 0; m < merge_num; ++m) {
                 int32_t n = 0;
                 req >> n;
+                if (!req.can_hold(n, 8)) return Status::Error("pull: malformed request");
                 const int64_t* keys = (const int64_t*)req.cursor_ptr();
                 std::vector<int64_t> aligned(keys, keys + n);  // archive bytes may be unaligned
                 req.skip((size_t)n * 8);
@@ -454,6 +457,7 @@ public:
         const OptConfig opt = opt_for(e);
         int32_t shards_num = 0, merge_num = 0;
         req >> shards_num >> merge_num;
+        if (merge_num < 0 || !req.can_hold(shards_num, 4 + (size_t)merge_num * 4)) return Status::Error("push: malformed request");
         std::shared_lock<std::shared_mutex> ig(e.incr.mu);
         for (int32_t i = 0; i < shards_num; ++i) {
             int32_t s = 0;
@@ -461,6 +465,7 @@ public:
             for (int32_t m = 0; m < merge_num; ++m) {
                 int32_t n = 0;
                 req >> n;
+                if (!req.can_hold(n, 8 + (size_t)dim * 4)) return Status::Error("push: malformed request");
                 std::vector<int64_t> keys((size_t)n);
                 std::vector<float> grads((size_t)n * dim);
                 req.read_raw(keys.data(), (size_t)n * 8);
@@ -520,6 +525,7 @@ public:
         req >> n >> stride;
         if ((uint32_t)stride != dst->stride() && (uint32_t)stride != dst->dim())
             return Status::Error("direct push: record width does not match the table");
+        if (!req.can_hold(n, 8 + (size_t)stride * 4)) return Status::Error("direct push: malformed request");
         std::vector<int64_t> keys((size_t)n);
         std::vector<float> rows((size_t)n * stride);
         req.read_raw(keys.data(), (size_t)n * 8);

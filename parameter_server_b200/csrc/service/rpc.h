@@ -63,6 +63,8 @@ inline bool write_full(int fd, const void* buf, size_t n) {
     }
     return true;
 }
+constexpr uint32_t kMaxFrameBytes = 1u << 30;
+
 inline bool write_frame(int fd, std::mutex& mu, uint64_t id, uint8_t kind, const Bytes& payload) {
     uint8_t hdr[13];
     uint32_t len = (uint32_t)payload.size();
@@ -79,6 +81,7 @@ inline bool read_frame(int fd, uint64_t* id, uint8_t* kind, Bytes* payload) {
     std::memcpy(&len, hdr, 4);
     std::memcpy(id, hdr + 4, 8);
     *kind = hdr[12];
+    if (len > kMaxFrameBytes) return false;  // nobody sends this: drop the connection instead of allocating for it
     payload->resize(len);
     return len == 0 || read_full(fd, payload->data(), len);
 }

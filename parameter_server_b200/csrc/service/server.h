@@ -424,9 +424,20 @@ private:
                 int32_t hid = 0;
                 OperatorDescriptor d;
                 in >> hid >> d.key >> d.lib_name >> d.op_name >> d.config_str;
+                // nothing is touched unless the operator exists and can be built; a failed registration leaves the
+                // table's handlers as they were
+                if (hid < 0 || !OperatorFactory::instance().has(d.lib_name, d.op_name))
+                    return Status::InvalidConfig("register handler: no operator (" + d.lib_name + ", " + d.op_name + ")");
+                const auto before = e->td.handlers;
                 e->td.handlers[hid] = d;
                 e->td.refresh_info();
-                return e->update_handlers();
+                Status st = e->update_handlers();
+                if (!st.ok()) {
+                    e->td.handlers = before;
+                    e->td.refresh_info();
+                    e->update_handlers();
+                }
+                return st;
             }
             case RequestType::HANDLER_DEREGISTER: {
                 std::unique_lock<std::shared_mutex> g(e->mu);

@@ -11,7 +11,7 @@
 // and the replica count of a table and rebalances it while four threads read it. In a fifth the rows that change
 // on a trainer table are shipped to a predictor table again and again while four threads keep pushing, and the
 // predictor must end up equal to the trainer. A sixth loads the trainer's dump into an in-process table with four
-// threads and reads it from four. ThreadSanitizer checks the rest.
+// threads and reads it from four. A seventh sends malformed requests. The sanitizers check the rest.
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
@@ -427,6 +427,51 @@ int main() {
         if (std::system(cmd.c_str()) != 0) ++bad6;
         std::printf("phase 6: dumped %llu, loaded %llu, %d wrong\n", (unsigned long long)dumped, (unsigned long long)loaded, bad6.load());
         wrong += bad6.load() + (dumped == loaded ? 0 : 1);
+    }
+    // ---- phase 7: malformed requests (random bodies behind a tail that passes every gate) must be answered with an
+    // error or dropped, never read out of bounds (the address sanitizer build watches) --------------------------
+    {
+        std::map<int32_t, std::string> live;
+        MUST(client.get_pserver_list(&live));
+        const int node = live.begin()->first;
+        int32_t fsid = -1;
+        MUST(client.create_storage("psb", "SparseTableStorageOperator",
+                                   "{\"nodes\":" + nodes_json({{node, {0, 1}}}) +
+                                       ",\"op_config\":{\"dim\":4,\"optimizer\":\"sum\",\"init_range\":0.0},\"table_name\":\"fz\"}",
+                                   &fsid));
+        std::map<std::string, int32_t> h;
+        const char* specs[][2] = {{"pull", "SparseTablePullOperator"}, {"push", "SparseTablePushOperator"}, {"for_each", "ForEachOperator"},
+                                  {"erase_if", "EraseIfOperator"}, {"load", "LoadOperator"}, {"update_ctx", "ShardUpdateContextOperator"},
+                                  {"sync", "KVSyncOperator"}};
+        for (auto& sp : specs) MUST(client.register_handler(sp[0], "psb", sp[1], "{}", fsid, &h[sp[0]]));
+        const std::pair<RequestType, const char*> kinds[] = {
+            {RequestType::OP_FOREACH, "for_each"}, {RequestType::OP_ERASEIF, "erase_if"}, {RequestType::OP_LOAD, "load"},
+            {RequestType::OP_PULL, "pull"}, {RequestType::OP_PUSH_ASYNC, "push"}, {RequestType::OP_PUSH_SYNC, "push"},
+            {RequestType::OP_STORE, "push"}, {RequestType::NEW_CTX_CREATE_SHARD, "update_ctx"}, {RequestType::NEW_CTX_SHUFFLE, "update_ctx"},
+            {RequestType::NEW_CTX_STORE, "update_ctx"}, {RequestType::OP_SYNC, "sync"}, {RequestType::OP_COORDINATED_RESTORE_ITERATE, "pull"}};
+        uint64_t x = 0x9E3779B97F4A7C15ull;
+        auto rnd = [&] { x ^= x << 13; x ^= x >> 7; x ^= x << 17; return x; };
+        int answered = 0;
+        for (auto& kd : kinds)
+            for (int it = 0; it < 150; ++it) {
+                Archive body;
+                if (rnd() % 2) body << (int32_t)(rnd() % 4) << (int32_t)(rnd() % 3);          // plausible counts first
+                if (rnd() % 4 == 0) body << (int32_t)(rnd() % 3) << (int32_t)0x7FFFFFF0;       // then a hostile one
+                const size_t len = rnd() % 200;
+                for (size_t i = 0; i < len; ++i) body << (uint8_t)rnd();
+                std::map<int, Archive> bodies;
+                bodies[node] = body;
+                std::vector<NodeResponse> rs;
+                client.send_and_wait(fsid, h[kd.second], kd.first, bodies, 2000, &rs);
+                answered += rs.empty() ? 0 : 1;
+            }
+        // the server still works
+        std::vector<float> one(kDim, 2.0f), got(kDim);
+        int64_t k = 5;
+        MUST(PushHandler(&client, fsid, h["push"]).async_push(&k, one.data(), 1, 20000));
+        MUST(PullHandler(&client, fsid, h["pull"]).pull(&k, 1, got.data(), 20000));
+        std::printf("phase 7: %d malformed requests answered\n", answered);
+        if (got[0] < 2.0f) ++wrong;
     }
     for (auto& s : servers) s->stop();
     master.stop();

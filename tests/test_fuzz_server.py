@@ -1,0 +1,108 @@
+"""A server must survive whatever arrives on its port: truncated frames, bodies shorter than the message tail,
+random bytes behind a well-formed tail for every request type, counts that point far past the end of the body.
+After the barrage the same server still answers a real client correctly. (The reference asserts
+`archive().is_exhausted()` after every decode and aborts on a malformed request; a serving process should
+answer with an error instead.)"""
+import json
+import socket
+import struct
+
+import numpy as np
+
+from parameter_server_b200 import service as S
+
+DIM = 4
+
+
+def _frame(payload: bytes, req_id: int = 1, kind: int = 0) -> bytes:
+    return struct.pack("<IQB", len(payload), req_id, kind) + payload
+
+
+def _tail(sid, hid, ver, uver, req_type) -> bytes:
+    return struct.pack("<iiiib3x", sid, hid, ver, uver, req_type)   # int8 request type + padding: 20 bytes
+
+
+def _send(addr, data: bytes, expect_reply: bool):
+    host, port = addr.rsplit(":", 1)
+    with socket.create_connection((host, int(port)), timeout=5) as s:
+        s.sendall(data)
+        if expect_reply:
+            s.settimeout(5)
+            try:
+                hdr = s.recv(13)
+                if len(hdr) == 13:
+                    n = struct.unpack("<I", hdr[:4])[0]
+                    while n > 0:
+                        chunk = s.recv(min(n, 1 << 16))
+                        if not chunk:
+                            break
+                        n -= len(chunk)
+            except socket.timeout:
+                pass
+
+
+def test_server_survives_malformed_requests():
+    master = S.Master()
+    server = S.Server(master.address())
+    client = S.Client(master.address())
+    try:
+        node = server.node_id()
+        cfg = S.storage_config({node: [0, 1, 2]}, dict(dim=DIM, optimizer="sum", init_range=0.0))
+        st, sid = client.create_storage(S.LIB, "SparseTableStorageOperator", cfg)
+        assert st.ok()
+        hids = {}
+        for key, op, c in [("pull", "SparseTablePullOperator", {}), ("push", "SparseTablePushOperator", {}),
+                           ("for_each", "ForEachOperator", {}), ("erase_if", "EraseIfOperator", {}), ("dump", "DumpOperator", {}),
+                           ("load", "LoadOperator", {}), ("update_ctx", "ShardUpdateContextOperator", {}), ("sync", "KVSyncOperator", {})]:
+            st, hids[key] = client.register_handler(key, S.LIB, op, json.dumps(c), sid)
+            assert st.ok()
+        keys = np.arange(200, dtype=np.int64)
+        vals = np.ones((200, DIM), np.float32) * 3
+        assert S.PushHandler(client, sid, hids["push"]).async_push(keys, vals).ok()
+        st, ctx_json = client.get_current_ctx(sid)
+        ver = json.loads(ctx_json)["version"] if st.ok() else 0
+        rng = np.random.default_rng(0)
+        for addr in (server.c2s_address(), server.s2s_address()):
+            # frames that are not even frames
+            _send(addr, b"", False)
+            _send(addr, b"\x01\x02\x03", False)
+            _send(addr, struct.pack("<IQB", 1000, 7, 0) + b"short", False)          # announces more than it sends
+            # bodies shorter than the 20-byte tail
+            for n in (0, 1, 19):
+                _send(addr, _frame(bytes(rng.integers(0, 256, n, dtype=np.uint8))), True)
+            # every request type with a valid tail and garbage / hostile bodies
+            for req_type in list(range(0, 26)) + [77, -3]:
+                for hid in list(hids.values()) + [-1, 9999]:
+                    for body in (b"", bytes(rng.integers(0, 256, 7, dtype=np.uint8)), bytes(rng.integers(0, 256, 200, dtype=np.uint8)),
+                                 struct.pack("<iiii", 1, 1, 0, 0x7FFFFFFF) + b"\x00" * 16,        # one shard, one list, count 2^31-1
+                                 struct.pack("<iiii", 0x7FFFFFFF, 0x7FFFFFFF, 0, -5),              # absurd shard / merge counts
+                                 struct.pack("<q", 1 << 60) + b"abc"):                             # string length 2^60
+                        if req_type in (1, 2, 5, 15):   # STORAGE_DELETE / STORAGE_CLEAR / HANDLER_DEREGISTER / EXIT would do what they say
+                            continue
+                        _send(addr, _frame(body + _tail(sid, hid, ver, -1, req_type)), True)
+                        _send(addr, _frame(body + _tail(12345, hid, ver, -1, req_type)), True)  # unknown storage
+        # random bodies of random lengths behind a tail that passes every gate (right storage, handler, version)
+        by_type = {6: "for_each", 7: "erase_if", 8: "dump", 9: "load", 10: "pull", 11: "push", 12: "push", 13: "push", 16: "update_ctx",
+                   17: "update_ctx", 18: "update_ctx", 21: "sync", 23: "pull", 25: "pull"}
+        for req_type, key in by_type.items():
+            for _ in range(40):
+                body = bytes(rng.integers(0, 256, int(rng.integers(0, 300)), dtype=np.uint8))
+                if rng.random() < 0.5:      # small plausible counts in front, garbage behind
+                    body = struct.pack("<ii", int(rng.integers(0, 4)), int(rng.integers(0, 3))) + body
+                _send(server.c2s_address(), _frame(body + _tail(sid, hids[key], ver, -1, req_type)), False)
+        # the master gets its share: unknown operations, truncated arguments, absurd lengths, an oversized frame
+        maddr = master.address()
+        for op in list(range(-2, 24)) + [1000]:
+            for body in (b"", bytes(rng.integers(0, 256, 5, dtype=np.uint8)), struct.pack("<q", 1 << 61) + b"xy",
+                         struct.pack("<q", 3) + b"abc" + struct.pack("<q", -1)):
+                _send(maddr, _frame(struct.pack("<i", op) + body), False)
+        _send(maddr, struct.pack("<IQB", 0xFFFFFFF0, 1, 0) + b"x" * 64, False)
+        st, nodes = client.get_pserver_list()
+        assert st.ok() and node in nodes
+        # the server is still there and still right
+        st, rows = S.PullHandler(client, sid, hids["pull"]).pull(keys, 10000)
+        assert st.ok() and np.array_equal(rows, vals)
+        assert client.health_check(node).ok()
+    finally:
+        server.stop()
+        master.stop()
