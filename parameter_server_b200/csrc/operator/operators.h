@@ -750,8 +750,11 @@ public:
         format_ = format;
         stride_ = stride;
         pos_ = 0;
+        size_ = body_.size();
+        bad_ = false;
+        body_.push_back(0);  // the text parser (strtoll / strtof) needs a terminator behind the last byte
         if (format_ == "binary") {
-            if (body_.size() < 8 || std::memcmp(body_.data(), "PSB1", 4) != 0) return Status::Error(path + ": not a PSB1 dump file");
+            if (size_ < 8 || std::memcmp(body_.data(), "PSB1", 4) != 0) return Status::Error(path + ": not a PSB1 dump file");
             uint32_t s;
             std::memcpy(&s, body_.data() + 4, 4);
             if (s != stride) return Status::Error(path + ": record width differs from the table");
@@ -759,13 +762,17 @@ public:
         }
         return Status::Ok();
     }
-    // Up to `block` records; returns false when the file is exhausted.
+    // Up to `block` records; returns false when the file is exhausted (or damaged: see ok()).
     bool next_block(size_t block, std::vector<int64_t>* keys, std::vector<float>* rows) {
         keys->clear();
         rows->clear();
-        while (keys->size() < block && pos_ < body_.size()) {
+        while (keys->size() < block && pos_ < size_) {
             if (format_ == "binary") {
-                if (pos_ + 8 + (size_t)stride_ * 4 > body_.size()) { pos_ = body_.size(); break; }
+                if (8 + (size_t)stride_ * 4 > size_ - pos_) {  // a record cut short: the file was truncated
+                    bad_ = true;
+                    pos_ = size_;
+                    break;
+                }
                 int64_t k;
                 std::memcpy(&k, body_.data() + pos_, 8);
                 keys->push_back(k);
@@ -774,23 +781,39 @@ public:
                 std::memcpy(rows->data() + off, body_.data() + pos_ + 8, (size_t)stride_ * 4);
                 pos_ += 8 + (size_t)stride_ * 4;
             } else {
-                const char* p = (const char*)body_.data() + pos_;
+                const char* base = (const char*)body_.data();
+                const char* p = base + pos_;
                 char* end = nullptr;
                 long long k = std::strtoll(p, &end, 10);
+                bool good = end != p;
+                std::vector<float> row(stride_);
+                for (uint32_t i = 0; good && i < stride_; ++i) {
+                    const char* q = end;
+                    row[i] = std::strtof(q, &end);
+                    good = end != q && (size_t)(end - base) <= size_;
+                }
+                if (!good) {  // not a record: stop instead of looping on the same bytes
+                    bad_ = true;
+                    pos_ = size_;
+                    break;
+                }
                 keys->push_back(k);
-                for (uint32_t i = 0; i < stride_; ++i) rows->push_back(std::strtof(end, &end));
-                while (*end == '\n' || *end == '\r') ++end;
-                pos_ = (size_t)(end - (const char*)body_.data());
+                rows->insert(rows->end(), row.begin(), row.end());
+                while ((size_t)(end - base) < size_ && (*end == '\n' || *end == '\r')) ++end;
+                pos_ = (size_t)(end - base);
             }
         }
         return !keys->empty();
     }
+    // False once a truncated or unparsable record was met; what was returned before it is valid.
+    bool ok() const { return !bad_; }
 
 private:
     std::vector<uint8_t> body_;
     std::string format_;
     uint32_t stride_ = 0;
-    size_t pos_ = 0;
+    size_t pos_ = 0, size_ = 0;
+    bool bad_ = false;
 };
 
 class DumpOperator : public Operator {
@@ -851,7 +874,7 @@ public:
             PSB_RETURN_IF_ERROR(st->set_rows(keys.data(), rows.data(), keys.size(), false));  // foreign keys are skipped
             for (int64_t k : keys) *kept += st->has_shard(st->shard_of(k)) ? 1 : 0;
         }
-        return Status::Ok();
+        return r.ok() ? Status::Ok() : Status::Error(file + ": damaged dump file (a record is cut short or does not parse)");
     }
 
 private:

@@ -627,6 +627,7 @@ private:
                 PSB_RETURN_IF_ERROR(s2s_call(bodies, m, RequestType::OP_PUSH_ASYNC));
                 n += keys.size();
             }
+            if (!r.ok()) return Status::Error(f + ": damaged dump file (a record is cut short or does not parse)");
         }
         *out << n;
         return Status::Ok();

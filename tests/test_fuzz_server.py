@@ -106,3 +106,53 @@ def test_server_survives_malformed_requests():
     finally:
         server.stop()
         master.stop()
+
+
+def test_damaged_dump_files_are_reported_not_followed(tmp_path):
+    """Truncated and garbled dump files (both codecs) end a load with an error status; nothing hangs or crashes and
+    intact files still load."""
+    import os
+    master = S.Master()
+    server = S.Server(master.address())
+    client = S.Client(master.address())
+    try:
+        node = server.node_id()
+        cfg = S.storage_config({node: [0, 1]}, dict(dim=DIM, optimizer="sum", init_range=0.0))
+        for fmt in ("binary", "archiveline"):
+            st, sid = client.create_storage(S.LIB, "SparseTableStorageOperator", cfg)
+            assert st.ok()
+            h = {}
+            for key, op in [("push", "SparseTablePushOperator"), ("pull_ro", "SparseTablePullOperator"), ("dump", "DumpOperator"),
+                            ("load", "LoadOperator")]:
+                st, h[key] = client.register_handler(key, S.LIB, op, json.dumps({"read_only": True} if key == "pull_ro" else {}), sid)
+                assert st.ok()
+            keys = np.arange(500, dtype=np.int64)
+            assert S.PushHandler(client, sid, h["push"]).async_push(keys, np.ones((500, DIM), np.float32)).ok()
+            good = str(tmp_path / f"good_{fmt}")
+            assert S.DumpHandler(client, sid, h["dump"]).dump(good + f"?format={fmt}", 1)[0].ok()
+            src = os.path.join(good, os.listdir(good)[0])
+            raw = open(src, "rb").read()
+            rng = np.random.default_rng(1)
+            variants = {"truncated": raw[: len(raw) * 2 // 3 + 3], "tail_garbage": raw + bytes(rng.integers(0, 256, 37, dtype=np.uint8)),
+                        "garbled": raw[:20] + bytes(rng.integers(0, 256, 300, dtype=np.uint8)) + raw[320:], "empty": b"",
+                        "no_newline": raw.rstrip(b"\n")}
+            for name, data in variants.items():
+                d = tmp_path / f"{fmt}_{name}"
+                d.mkdir()
+                (d / "model_0_0").write_bytes(data)
+                st, n = S.LoadHandler(client, sid, h["load"]).load(str(d) + f"?format={fmt}", 4, 20000)
+                if name == "no_newline":
+                    assert st.ok() and n == 500, (fmt, name, st, n)       # a missing final newline is not damage
+                elif name == "empty" and fmt == "archiveline":
+                    assert st.ok() and n == 0
+                elif fmt == "binary" and name != "garbled":
+                    assert not st.ok(), (fmt, name, st, n)      # a cut record / missing header is noticed
+                # garbled bytes of the right length are just other records (the format has no checksum), and text
+                # garbage may still parse as numbers: those only have to come back, with whatever status
+            st, n = S.LoadHandler(client, sid, h["load"]).load(good + f"?format={fmt}", 4, 20000)
+            assert st.ok() and n == 500
+            st, rows = S.PullHandler(client, sid, h["pull_ro"]).pull(keys, 10000)
+            assert st.ok() and rows.shape == (500, DIM)
+    finally:
+        server.stop()
+        master.stop()
