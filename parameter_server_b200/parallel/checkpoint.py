@@ -72,6 +72,20 @@ def _read_batches(paths, stride: int, batch: int, device):
                        torch.from_numpy(np.ascontiguousarray(block["row"])).to(device))
 
 
+def _damaged(paths, stride: int) -> Optional[str]:
+    """The first file that is not an intact dump of this record width (header, whole records), or None."""
+    rec_bytes = _record_dtype(stride).itemsize
+    for p in paths:
+        size = os.path.getsize(p)
+        with open(p, "rb") as fh:
+            head = fh.read(8)
+        if len(head) < 8 or head[:4] != _MAGIC or int(np.frombuffer(head[4:8], dtype="<u4")[0]) != stride:
+            return f"{p}: not a PSB1 dump of record width {stride}"
+        if (size - 8) % rec_bytes:
+            return f"{p}: truncated (the last record is cut short)"
+    return None
+
+
 def load(table: SparseTable, uri: str, batch: int = 1 << 18, inbox: Optional[PeerInbox] = None,
          only_node: Optional[int] = None) -> int:
     """Collective. Inserts every record of the dump at ``uri`` (of the files written by ``only_node`` when
@@ -81,6 +95,14 @@ def load(table: SparseTable, uri: str, batch: int = 1 << 18, inbox: Optional[Pee
     prefix = "model_" if only_node is None else f"model_{only_node}_"
     names = sorted(n for n in os.listdir(path) if n.startswith(prefix))
     mine = [os.path.join(path, n) for n in names[table.rank::table.world]]
+    # every rank checks its files BEFORE the collective part and the ranks agree on the verdict: a rank that
+    # raised alone would leave the others waiting in a collective
+    problem = _damaged(mine, table.table.stride())
+    flag = torch.tensor([1 if problem else 0], device=table.device)
+    if table.world > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=table.group)
+    if int(flag.item()):
+        raise RuntimeError(problem or "load: another rank found a damaged dump file")
     owner_dev = torch.tensor(table.shard_owner, dtype=torch.int32, device=table.device)
     inbox = inbox or PeerInbox(table, batch)
     got, _ = stream_to_owners(table, _read_batches(mine, table.table.stride(), batch, table.device), owner_dev, inbox,
