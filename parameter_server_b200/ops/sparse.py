@@ -155,6 +155,9 @@ class SparseTable:
             keys = keys.contiguous()
             if out is None:
                 out = torch.empty((n // bag_size, self.dim), dtype=torch.float32, device=self.device)
+            elif (out.dtype != torch.float32 or not out.is_cuda or not out.is_contiguous()
+                  or out.numel() != (n // bag_size) * self.dim):
+                raise ValueError("out must be a contiguous CUDA float32 tensor of n / bag_size rows of dim columns")
             flags = C.FUSED_COPY_ROWS
             if insert:
                 flags |= C.FUSED_INSERT
@@ -205,6 +208,10 @@ class SparseTable:
             if grads.dtype != torch.float32:
                 grads = grads.float()
             grads = grads.contiguous()
+            planned = self._plan_keys.numel() if torch.is_tensor(self._plan_keys) else None
+            if not grads.is_cuda or grads.numel() % self.dim or (planned is not None and bag_size == 1 and keys is None
+                                                                 and grads.numel() // self.dim > planned):
+                raise ValueError("grads must be a CUDA tensor with one row of dim columns per pulled bag")
             flags = C.FUSED_SYNC_PUSH if sync else 0
             with nvtx("ps.sparse_push"):
                 raise_if_error(self.engine.push(grads.data_ptr(), self.opt, flags, _stream()))
