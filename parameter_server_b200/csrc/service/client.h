@@ -121,7 +121,8 @@ public:
         std::shared_ptr<TableEntry> e;
         PSB_RETURN_IF_ERROR(ctx_.create_storage(*sid, lib, op, cfg, -1, &e));
         Archive body;
-        body << lib << op << cfg_json;
+        cfg["version_uuid"] = Json(e->td.version_uuid);
+        body << lib << op << cfg.dump();
         std::set<int> nodes;
         for (auto& n : e->td.nodes) nodes.insert(n.node_id);
         Status st = broadcast(*sid, RequestType::STORAGE_CREATE, nodes, body, timeout_ms, -1);

@@ -77,7 +77,9 @@ public:
         PSB_RETURN_IF_ERROR(TableDescriptor::parse_nodes(cfg.at("nodes"), &e->td.nodes));
         e->td.storage_op = OperatorDescriptor{"storage", lib, op_name, cfg.at("op_config").dump()};
         e->td.table_name = cfg.at("table_name").as_string();
-        e->td.gen_new_version_uuid();
+        // the creator's identity of the data layout travels in the config, so that every process holds the same one
+        if (cfg.has("version_uuid") && !cfg.at("version_uuid").as_string().empty()) e->td.version_uuid = cfg.at("version_uuid").as_string();
+        else e->td.gen_new_version_uuid();
         e->td.refresh_info();
         PSB_RETURN_IF_ERROR(OperatorFactory::instance().create(lib, op_name, e->td.storage_op.config_str, &e->storage_op));
         e->rt.build(e->td, my_node_id);

@@ -9,6 +9,9 @@
 // from a live replica over s2s in resumable batches, fall back to the dump at table_uri), and the
 // memory self-monitor. A request is {body, PSMessageMeta tail}; a response is {Status, payload}.
 #pragma once
+#include <cstdio>
+#include <cstring>
+#include <fstream>
 #include <atomic>
 #include <chrono>
 #include <thread>
@@ -28,6 +31,9 @@ struct ServerConfig {
     int restore_wait_timeout_s = -1;
     int restore_batch_size = 1000;
     int s2s_timeout_ms = 60000;
+    // Directory of this host's persistent table images (empty: none). A server in restore mode that finds the image
+    // of the node it replaces, with the table's version_uuid, opens it instead of the table's dump.
+    std::string local_image_dir;
 };
 
 struct StorageStatisticInfo {
@@ -122,8 +128,17 @@ public:
                 std::unique_lock<std::shared_mutex> g(e->mu);
                 PSB_RETURN_IF_ERROR(ensure_storage(*e));
             }
+            // a live replica has the current data; without one, this host's own image of the dead node (if its
+            // layout identity matches); then the table's dump
             Status rs = restore_storage_coordinated(*e);
-            if (!rs.ok()) rs = restore_storage_from_fs(*e);
+            if (!rs.ok()) {
+                Status li = restore_storage_from_local_image(*e);
+                if (li.ok()) rs = li;
+                else {
+                    Status fs = restore_storage_from_fs(*e);
+                    rs = fs.ok() ? fs : Status(fs.code(), fs.msg() + " (replica: " + rs.msg() + "; local image: " + li.msg() + ")");
+                }
+            }
             PSB_RETURN_IF_ERROR(rs);
             // LOADING -> RUNNING, publish, tell the peers
             PSB_RETURN_IF_ERROR(master_.acquire_lock(PSERVER_LOCK_NAME));
@@ -141,6 +156,58 @@ public:
             broadcast_ctx_update(*e);
         }
         if (restored_tables) *restored_tables = (int)mine.size();
+        return Status::Ok();
+    }
+
+    // Write the persistent image of every local table under `local_image_dir` (atomically: temp file + rename).
+    // Call it at checkpoints or before a planned shutdown; see restore_storage_from_local_image.
+    Status save_local_images(int* n_tables = nullptr) {
+        if (cfg_.local_image_dir.empty()) return Status::InvalidConfig("local_image_dir is not set");
+        int saved = 0;
+        for (int32_t sid : ctx_.ids()) {
+            auto e = ctx_.get(sid);
+            if (!e || !e->storage) continue;
+            std::shared_lock<std::shared_mutex> g(e->mu);
+            const std::string path = image_path(cfg_.local_image_dir, node_id_, sid);
+            PSB_RETURN_IF_ERROR(mkdir_p(path.substr(0, path.rfind('/'))));
+            const std::string tmp = path + ".tmp";
+            {
+                std::ofstream f(tmp, std::ios::binary | std::ios::trunc);
+                if (!f) return Status::Error("cannot write " + tmp);
+                const char magic[8] = {'P', 'S', 'B', 'I', 'M', 'G', '1', 0};
+                const uint64_t ulen = e->td.version_uuid.size();
+                const uint32_t stride = e->storage->stride();
+                uint64_t n = 0;
+                f.write(magic, 8);
+                f.write((const char*)&ulen, 8);
+                f.write(e->td.version_uuid.data(), (std::streamsize)ulen);
+                f.write((const char*)&stride, 4);
+                const auto n_pos = f.tellp();
+                f.write((const char*)&n, 8);
+                std::vector<int64_t> keys;
+                std::vector<float> rows;
+                for (int s : e->storage->shard_list()) {
+                    uint64_t cursor = 0;
+                    bool finished = false;
+                    while (!finished) {
+                        keys.clear();
+                        rows.clear();
+                        PSB_RETURN_IF_ERROR(e->storage->export_shard(s, cursor, 1 << 14, false, &keys, &rows, &cursor, &finished));
+                        for (size_t i = 0; i < keys.size(); ++i) {
+                            f.write((const char*)&keys[i], 8);
+                            f.write((const char*)(rows.data() + i * stride), (std::streamsize)stride * 4);
+                        }
+                        n += keys.size();
+                    }
+                }
+                f.seekp(n_pos);
+                f.write((const char*)&n, 8);
+                if (!f.good()) return Status::Error("write to " + tmp + " failed");
+            }
+            if (std::rename(tmp.c_str(), path.c_str()) != 0) return Status::Error("cannot move " + tmp + " into place");
+            ++saved;
+        }
+        if (n_tables) *n_tables = saved;
         return Status::Ok();
     }
 
@@ -717,7 +784,9 @@ private:
             TableDescriptor td;
             if (!td.from_json_str(json)) continue;
             td.update_node_status(live_ids);
-            if (!td.try_to_replace_one_dead_node(node_id_)) continue;
+            int replaced = -1;
+            if (!td.try_to_replace_one_dead_node(node_id_, &replaced)) continue;
+            replaced_node_[sid] = replaced;
             PSB_RETURN_IF_ERROR(master_.set_context(k, td.to_json_str()));
             std::shared_ptr<TableEntry> e;
             PSB_RETURN_IF_ERROR(ctx_.set_table_descriptor(sid, td.to_json_str(), node_id_, &e));
@@ -754,6 +823,8 @@ private:
                 int32_t sid = 0, sh = 0, fin = 0, stride = 0;
                 uint64_t num = 0;
                 r.ar >> sid >> sh >> fin >> iterator_id >> offset >> num >> stride;
+                if (stride < 0 || num > (1ull << 40) || !r.ar.can_hold((int64_t)num, 8 + (size_t)stride * 4))
+                    return Status::Error("restore: malformed batch from node " + std::to_string(replica));
                 std::vector<int64_t> keys(num);
                 std::vector<float> rows((size_t)num * stride);
                 r.ar.read_raw(keys.data(), num * 8);
@@ -761,6 +832,51 @@ private:
                 if (num) PSB_RETURN_IF_ERROR(e.storage->set_rows(keys.data(), rows.data(), num, false));
                 if (fin) break;
             }
+        }
+        return Status::Ok();
+    }
+
+    // Persistent image of one table on this host: <dir>/node_<id>/storage_<sid>.img = "PSBIMG1\0", version_uuid,
+    // stride, then {key, row} records. The role of the reference's persistent-memory pool per storage, which a
+    // restarted server opens locally when its version_uuid matches and otherwise discards in favour of a remote
+    // restore (pico-ps/storage/DCPmemory.h:493-507, pico-ps/service/Service.cpp:275-294).
+    static std::string image_path(const std::string& dir, int node, int32_t sid) {
+        return dir + "/node_" + std::to_string(node) + "/storage_" + std::to_string(sid) + ".img";
+    }
+    Status restore_storage_from_local_image(TableEntry& e) {
+        if (cfg_.local_image_dir.empty()) return Status::Error("no local image directory");
+        auto it = replaced_node_.find(e.sid);
+        if (it == replaced_node_.end()) return Status::Error("no replaced node recorded");
+        const std::string path = image_path(cfg_.local_image_dir, it->second, e.sid);
+        std::ifstream f(path, std::ios::binary);
+        if (!f) return Status::Error("no image " + path);
+        char magic[8];
+        uint64_t ulen = 0, n = 0;
+        uint32_t stride = 0;
+        f.read(magic, 8);
+        f.read((char*)&ulen, 8);
+        if (!f || std::memcmp(magic, "PSBIMG1", 8) != 0 || ulen > 4096) return Status::Error(path + ": not a table image");
+        std::string uuid(ulen, '\0');
+        f.read(&uuid[0], (std::streamsize)ulen);
+        f.read((char*)&stride, 4);
+        f.read((char*)&n, 8);
+        if (!f) return Status::Error(path + ": truncated image");
+        if (uuid != e.td.version_uuid) return Status::InvalidID(path + ": version_uuid differs, restore remotely");
+        if (stride != e.storage->stride()) return Status::Error(path + ": record width differs from the table");
+        const size_t block = 4096;
+        std::vector<int64_t> keys;
+        std::vector<float> rows;
+        for (uint64_t done = 0; done < n;) {
+            const size_t m = (size_t)std::min<uint64_t>(block, n - done);
+            keys.resize(m);
+            rows.resize(m * stride);
+            for (size_t i = 0; i < m; ++i) {
+                f.read((char*)&keys[i], 8);
+                f.read((char*)(rows.data() + i * stride), (std::streamsize)stride * 4);
+            }
+            if (!f) return Status::Error(path + ": truncated image");
+            PSB_RETURN_IF_ERROR(e.storage->set_rows(keys.data(), rows.data(), m, false));  // rows of shards that moved away are skipped
+            done += m;
         }
         return Status::Ok();
     }
@@ -786,6 +902,7 @@ private:
     Context ctx_;
     std::unique_ptr<RpcServer> c2s_, s2s_;
     RpcClient s2s_client_;
+    std::map<int32_t, int> replaced_node_;  // storage id -> the dead node this server took over
     std::atomic<bool> stopped_{false}, exited_{false};
     std::mutex metric_mu_;
     std::map<std::string, uint64_t> metrics_;

@@ -661,3 +661,51 @@ def test_sync_pred_backs_off_and_resumes_after_the_predictor_comes_back():
         assert st.ok() and np.all(rows == 1.0)
     finally:
         cl.close()
+
+
+def test_restore_from_the_hosts_own_image_when_no_replica(tmp_path):
+    """No replica, no dump: the replacement server opens the persistent image that the dead node left on this host
+    (the role of the reference's persistent-memory pool). An image of another data layout is refused."""
+    cfg = S.ServerConfig()
+    cfg.local_image_dir = str(tmp_path / "images")
+    master = S.Master()
+    servers = [S.Server(master.address(), cfg) for _ in range(2)]
+    client = S.Client(master.address())
+    try:
+        ids = [s.node_id() for s in servers]
+        st, sid = client.create_storage(S.LIB, "SparseTableStorageOperator", S.storage_config({ids[0]: [0, 1], ids[1]: [2]}, op_cfg()))
+        assert st.ok()
+        _, hq = client.register_handler("push", S.LIB, "SparseTablePushOperator", "{}", sid)
+        _, hp = client.register_handler("pull_ro", S.LIB, "SparseTablePullOperator", json.dumps({"read_only": True}), sid)
+        keys = np.arange(1500, dtype=np.int64)
+        vals = np.ones((1500, DIM), np.float32) * (keys[:, None] % 5 + 1)
+        assert S.PushHandler(client, sid, hq).async_push(keys, vals).ok()
+        for s in servers:
+            st, n = s.save_local_images()
+            assert st.ok() and n == 1
+        servers[0].stop()                                           # the node with shards 0 and 1 is gone
+        pull = S.PullHandler(client, sid, hp)
+        assert not pull.pull(keys, 3000, True)[0].ok()              # nobody holds those shards now
+        fresh = S.Server(master.address(), cfg)
+        servers.append(fresh)
+        st, n = fresh.restore_storages()
+        assert st.ok() and n == 1, st
+        st, rows = pull.pull(keys, 20000, True)
+        assert st.ok() and np.array_equal(rows, vals)
+        # a table created anew has another version_uuid: an old image with the same ids must not be opened
+        st, sid2 = client.create_storage(S.LIB, "SparseTableStorageOperator", S.storage_config({fresh.node_id(): [0]}, op_cfg()))
+        assert st.ok()
+        import shutil
+        src = tmp_path / "images" / f"node_{ids[0]}" / f"storage_{sid}.img"
+        dst = tmp_path / "images" / f"node_{fresh.node_id()}" / f"storage_{sid2}.img"
+        dst.parent.mkdir(parents=True, exist_ok=True)
+        shutil.copy(src, dst)
+        fresh.stop()
+        last = S.Server(master.address(), cfg)
+        servers.append(last)
+        st, n = last.restore_storages()
+        assert not st.ok()                                          # no replica, foreign image refused, no dump either
+    finally:
+        for s in servers:
+            s.stop()
+        master.stop()
