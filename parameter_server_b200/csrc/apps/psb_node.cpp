@@ -2,11 +2,13 @@
 //
 //   psb_node master [--threads N]
 //       prints the master's address on the first line of stdout and serves until it is killed.
-//   psb_node pserver --master HOST:PORT [--restore] [--c2s-threads N] [--s2s-threads N]
+//   psb_node pserver --master HOST:PORT [--restore] [--image-dir DIR] [--c2s-threads N] [--s2s-threads N]
 //       registers at the master, prints "pserver node_id=.. c2s=.. s2s=..", serves both ports and exits when a
 //       client sends EXIT (Client::close_pserver / Controller::shutdown_node). With --restore it first takes
 //       over the shards of a dead node from their live replicas or from the table's dump
-//       (the restore mode of the reference's server process, pico-ps/service/Service.cpp:237-313).
+//       (the restore mode of the reference's server process, pico-ps/service/Service.cpp:237-313). With --image-dir
+//       it writes its tables' persistent images there on a planned shutdown (EXIT, SIGTERM) and, in restore mode,
+//       opens the image of the node it replaces when no live replica has the shards.
 //
 // The same objects as the Python bindings: tables with "backend": "gpu" are served by the fused kernels.
 #include <chrono>
@@ -28,7 +30,7 @@ void on_signal(int) { g_stop = 1; }
 int usage() {
     std::fprintf(stderr,
                  "usage: psb_node master [--threads N]\n"
-                 "       psb_node pserver --master HOST:PORT [--restore] [--c2s-threads N] [--s2s-threads N]\n");
+                 "       psb_node pserver --master HOST:PORT [--restore] [--image-dir DIR] [--c2s-threads N] [--s2s-threads N]\n");
     return 2;
 }
 }  // namespace
@@ -51,6 +53,7 @@ int main(int argc, char** argv) {
         };
         if (a == "--master" && i + 1 < argc) master_addr = argv[++i];
         else if (a == "--restore") restore = true;
+        else if (a == "--image-dir" && i + 1 < argc) cfg.local_image_dir = argv[++i];
         else if (a == "--threads") { if (!next(&threads)) return usage(); }
         else if (a == "--c2s-threads") { if (!next(&cfg.c2s_thread_num)) return usage(); }
         else if (a == "--s2s-threads") { if (!next(&cfg.s2s_thread_num)) return usage(); }
@@ -77,6 +80,12 @@ int main(int argc, char** argv) {
             if (!st.ok()) return 1;
         }
         while (!server.exited() && !g_stop) std::this_thread::sleep_for(std::chrono::milliseconds(20));
+        if (!cfg.local_image_dir.empty()) {  // a planned shutdown leaves this node's tables on the host
+            int n = 0;
+            Status st = server.save_local_images(&n);
+            std::printf("images: %s (%d tables)\n", st.ok() ? "OK" : st.msg().c_str(), n);
+            std::fflush(stdout);
+        }
         server.stop();
     } catch (const std::exception& e) {
         std::fprintf(stderr, "psb_node: %s\n", e.what());

@@ -78,3 +78,42 @@ def test_native_master_and_servers_serve_a_python_client():
         for p in procs:
             if p.poll() is None:
                 p.kill()
+
+
+@pytest.mark.skipif(not os.path.exists(NODE), reason="psb_node is not built")
+def test_planned_shutdown_leaves_an_image_that_a_replacement_opens(tmp_path):
+    master = _spawn("master")
+    procs = [master]
+    try:
+        addr = _first_line(master)
+        img = str(tmp_path / "img")
+        first = _spawn("pserver", "--master", addr, "--image-dir", img)
+        procs.append(first)
+        node = int(_first_line(first).split("node_id=")[1].split()[0])
+        client = S.Client(addr)
+        st, sid = client.create_storage(S.LIB, "SparseTableStorageOperator",
+                                        S.storage_config({node: [0, 1]}, dict(dim=4, optimizer="sum", init_range=0.0)))
+        assert st.ok(), st
+        _, h_push = client.register_handler("push", S.LIB, "SparseTablePushOperator", "{}", sid)
+        _, h_pull = client.register_handler("pull_ro", S.LIB, "SparseTablePullOperator", json.dumps({"read_only": True}), sid)
+        keys = np.arange(800, dtype=np.int64)
+        vals = ((keys[:, None] % 9 + 1) * np.ones((1, 4))).astype(np.float32)
+        assert S.PushHandler(client, sid, h_push).async_push(keys, vals).ok()
+        first.send_signal(signal.SIGTERM)                       # planned shutdown: the image is written
+        out, _ = first.communicate(timeout=20)
+        assert "images: OK (1 tables)" in out and first.returncode == 0
+        second = _spawn("pserver", "--master", addr, "--image-dir", img, "--restore")
+        procs.append(second)
+        assert "node_id=" in _first_line(second)
+        assert _first_line(second, 30.0) == "restore: OK (1 tables)"
+        st, rows = S.PullHandler(client, sid, h_pull).pull(keys, 20000, True)
+        assert st.ok() and np.array_equal(rows, vals)
+        for n in client.get_pserver_list()[1]:
+            client.close_pserver(n)
+        second.wait(timeout=15)
+        master.send_signal(signal.SIGTERM)
+        master.wait(timeout=15)
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
