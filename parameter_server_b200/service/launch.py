@@ -1,7 +1,7 @@
 """Process launchers of the service layer.
 
     python -m parameter_server_b200.service.launch master            # prints the address, serves until killed
-    python -m parameter_server_b200.service.launch pserver --master 127.0.0.1:PORT [--restore]
+    python -m parameter_server_b200.service.launch pserver --master 127.0.0.1:PORT [--restore] [--image-dir DIR]
 
 A ``pserver`` registers at the master, serves its c2s / s2s ports and exits when a client sends EXIT
 (``Controller.shutdown_node``). With ``--restore`` it first takes over the shards of a dead node
@@ -25,6 +25,7 @@ def main(argv=None) -> int:
     p = sub.add_parser("pserver")
     p.add_argument("--master", required=True)
     p.add_argument("--restore", action="store_true")
+    p.add_argument("--image-dir", default="", help="persistent table images: written on a planned shutdown, opened in restore mode")
     p.add_argument("--c2s-threads", type=int, default=4)
     p.add_argument("--s2s-threads", type=int, default=4)
     a = ap.parse_args(argv)
@@ -39,6 +40,7 @@ def main(argv=None) -> int:
         return 0
     cfg = ServerConfig()
     cfg.c2s_thread_num, cfg.s2s_thread_num = a.c2s_threads, a.s2s_threads
+    cfg.local_image_dir = a.image_dir
     server = Server(a.master, cfg)
     print(f"pserver node_id={server.node_id()} c2s={server.c2s_address()} s2s={server.s2s_address()}", flush=True)
     if a.restore:
@@ -46,8 +48,15 @@ def main(argv=None) -> int:
         print(f"restore: {st} ({n} tables)", flush=True)
         if not st.ok():
             return 1
-    while not server.exited():
-        time.sleep(0.05)
+    try:
+        while not server.exited():
+            time.sleep(0.05)
+    except KeyboardInterrupt:
+        pass
+    if a.image_dir:
+        st, n = server.save_local_images()
+        print(f"images: {st} ({n} tables)", flush=True)
+    server.stop()
     return 0
 
 
