@@ -148,7 +148,9 @@ void bind_service(py::module_& m) {
         .def_readwrite("load_block_size", &ServerConfig::load_block_size)
         .def_readwrite("restore_batch_size", &ServerConfig::restore_batch_size)
         .def_readwrite("s2s_timeout_ms", &ServerConfig::s2s_timeout_ms)
-        .def_readwrite("local_image_dir", &ServerConfig::local_image_dir);
+        .def_readwrite("local_image_dir", &ServerConfig::local_image_dir)
+        .def_readwrite("report_interval_s", &ServerConfig::report_interval_s)
+        .def_readwrite("restore_wait_timeout_s", &ServerConfig::restore_wait_timeout_s);
     py::class_<Server>(m, "Server")
         .def(py::init<const std::string&, const ServerConfig&>(), py::arg("master"), py::arg("config") = ServerConfig(), nogil())
         .def("node_id", &Server::node_id)
@@ -158,6 +160,8 @@ void bind_service(py::module_& m) {
         .def("stop", &Server::stop, nogil())
         .def("metrics", &Server::metrics)
         .def("metrics_text", &Server::metrics_text)
+        .def("report_line", &Server::report_line)
+        .def("last_report", &Server::last_report)
         .def("save_local_images", [](Server& s) { int n = 0; Status st = s.save_local_images(&n); return std::make_tuple(st, n); }, nogil())
         .def("restore_storages", [](Server& s) { int n = 0; Status st = s.restore_storages(&n); return std::make_tuple(st, n); }, nogil())
         .def("enable_sync", &Server::enable_sync)

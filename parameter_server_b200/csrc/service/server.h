@@ -14,6 +14,7 @@
 #include <fstream>
 #include <atomic>
 #include <chrono>
+#include <condition_variable>
 #include <thread>
 
 #include "../operator/operators.h"
@@ -64,8 +65,44 @@ public:
         int32_t same = -1;
         st = session_.register_node(PSERVER_C2S_RPC_NAME, c2s_->address(), &same, node_id_);
         if (!st.ok()) throw std::runtime_error("server: cannot register c2s: " + st.to_string());
+        if (cfg_.report_interval_s > 0)
+            reporter_ = std::thread([this] {
+                // one line per interval on stderr (ServerConfig::report_interval of the reference)
+                std::unique_lock<std::mutex> g(report_mu_);
+                while (!report_cv_.wait_for(g, std::chrono::seconds(cfg_.report_interval_s), [this] { return stopped_.load(); })) {
+                    last_report_ = report_line();
+                    std::fprintf(stderr, "%s\n", last_report_.c_str());
+                }
+            });
     }
     ~Server() { stop(); }
+
+    // "node=.. requests=.. errors=.. storages=[sid:items:bytes ...]"
+    std::string report_line() {
+        uint64_t requests = 0, errors = 0;
+        {
+            std::lock_guard<std::mutex> g(metric_mu_);
+            for (auto& kv : series_) {
+                requests += kv.second.requests;
+                errors += kv.second.errors;
+            }
+        }
+        std::string out = "pserver node=" + std::to_string(node_id_) + " requests=" + std::to_string(requests) +
+                          " errors=" + std::to_string(errors) + " storages=[";
+        bool first = true;
+        for (int32_t sid : ctx_.ids()) {
+            auto e = ctx_.get(sid);
+            if (!e || !e->storage) continue;
+            out += std::string(first ? "" : " ") + std::to_string(sid) + ":" + std::to_string(e->storage->size()) + ":" +
+                   std::to_string(e->storage->memory_usage());
+            first = false;
+        }
+        return out + "]";
+    }
+    std::string last_report() {
+        std::lock_guard<std::mutex> g(report_mu_);
+        return last_report_;
+    }
 
     int32_t node_id() const { return node_id_; }
     std::string c2s_address() const { return c2s_->address(); }
@@ -75,6 +112,8 @@ public:
 
     void stop() {
         if (stopped_.exchange(true)) return;
+        report_cv_.notify_all();
+        if (reporter_.joinable()) reporter_.join();
         session_.close();  // the master drops our registrations: we are gone
         if (c2s_) c2s_->stop();
         if (s2s_) s2s_->stop();
@@ -118,10 +157,19 @@ public:
     // HA: adopt the descriptors of a dead node in every table and refill the storages.
     Status restore_storages(int* restored_tables = nullptr) {
         std::vector<int32_t> mine;
-        PSB_RETURN_IF_ERROR(master_.acquire_lock(PSERVER_LOCK_NAME));
-        Status st = find_dead_node_and_replace(&mine);
-        master_.release_lock(PSERVER_LOCK_NAME);
-        PSB_RETURN_IF_ERROR(st);
+        Status st;
+        // a server started in restore mode may be faster than the detection of the node it is meant to replace:
+        // with restore_wait_timeout_s > 0 it keeps looking for a dead node for that long
+        const auto t0 = std::chrono::steady_clock::now();
+        for (;;) {
+            PSB_RETURN_IF_ERROR(master_.acquire_lock(PSERVER_LOCK_NAME));
+            st = find_dead_node_and_replace(&mine);
+            master_.release_lock(PSERVER_LOCK_NAME);
+            PSB_RETURN_IF_ERROR(st);
+            const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+            if (!mine.empty() || cfg_.restore_wait_timeout_s <= 0 || waited >= cfg_.restore_wait_timeout_s) break;
+            std::this_thread::sleep_for(std::chrono::milliseconds(100));
+        }
         for (int32_t sid : mine) {
             std::shared_ptr<TableEntry> e = ctx_.get(sid);
             {
@@ -675,27 +723,51 @@ private:
         std::string dir, format;
         DumpArgs::split_uri(uri, &dir, &format);
         if (files.empty()) files = list_model_files(dir);
-        uint64_t n = 0;
         const auto* sop = storage_op_of(e);
-        for (auto& f : files) {
-            if (!need_rehash) {
-                PSB_RETURN_IF_ERROR(op->restore_file(e, f, format, &n));
-                continue;
-            }
+        const size_t block = op->block_size() ? op->block_size() : (size_t)cfg_.load_block_size;
+        // the files of one request are read by up to load_thread_num threads (ServerConfig of the reference:
+        // load_thread_num = 4, load_block_size = 1000)
+        auto load_one = [&](const std::string& f, uint64_t* count) -> Status {
+            if (!need_rehash) return op->restore_file(e, f, format, count);
             DsReader r;
             PSB_RETURN_IF_ERROR(r.open(f, format, e.storage->stride(), &op->compressor()));
             std::vector<int64_t> keys;
             std::vector<float> rows;
-            while (r.next_block(op->block_size(), &keys, &rows)) {
+            while (r.next_block(block, &keys, &rows)) {
                 std::map<int, Archive> bodies;
                 PSB_RETURN_IF_ERROR(DirectPushOperator::generate_requests(sop, e.rt, keys.data(), rows.data(), keys.size(),
                                                                           e.storage->stride(), &bodies));
                 PSMessageMeta m = meta;
                 PSB_RETURN_IF_ERROR(s2s_call(bodies, m, RequestType::OP_PUSH_ASYNC));
-                n += keys.size();
+                *count += keys.size();
             }
             if (!r.ok()) return Status::Error(f + ": damaged dump file (a record is cut short or does not parse)");
-        }
+            return Status::Ok();
+        };
+        std::atomic<size_t> next{0};
+        std::atomic<uint64_t> total{0};
+        std::mutex first_mu;
+        Status first;
+        auto worker = [&] {
+            for (;;) {
+                const size_t i = next++;
+                if (i >= files.size()) return;
+                uint64_t c = 0;
+                Status st = load_one(files[i], &c);
+                total += c;
+                if (!st.ok()) {
+                    std::lock_guard<std::mutex> lg(first_mu);
+                    if (first.ok()) first = st;
+                }
+            }
+        };
+        const int nthreads = (int)std::min<size_t>(std::max(1, cfg_.load_thread_num), files.size());
+        std::vector<std::thread> pool;
+        for (int t = 1; t < nthreads; ++t) pool.emplace_back(worker);
+        worker();
+        for (auto& t : pool) t.join();
+        PSB_RETURN_IF_ERROR(first);
+        const uint64_t n = total;
         *out << n;
         return Status::Ok();
     }
@@ -902,6 +974,10 @@ private:
     Context ctx_;
     std::unique_ptr<RpcServer> c2s_, s2s_;
     RpcClient s2s_client_;
+    std::thread reporter_;
+    std::mutex report_mu_;
+    std::condition_variable report_cv_;
+    std::string last_report_;
     std::map<int32_t, int> replaced_node_;  // storage id -> the dead node this server took over
     std::atomic<bool> stopped_{false}, exited_{false};
     std::mutex metric_mu_;

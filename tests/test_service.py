@@ -709,3 +709,63 @@ def test_restore_from_the_hosts_own_image_when_no_replica(tmp_path):
         for s in servers:
             s.stop()
         master.stop()
+
+
+def test_server_config_report_restore_wait_and_threaded_load(tmp_path):
+    """ServerConfig knobs: the periodic report line, a restore-mode server that waits for a node to die, and a
+    load request whose files are read by several threads."""
+    cfg = S.ServerConfig()
+    cfg.report_interval_s = 1
+    cfg.load_thread_num = 3
+    master = S.Master()
+    servers = [S.Server(master.address(), cfg) for _ in range(2)]
+    client = S.Client(master.address())
+    try:
+        ids = [s.node_id() for s in servers]
+        st, sid = client.create_storage(S.LIB, "SparseTableStorageOperator",
+                                        S.storage_config({ids[0]: [0, 1, 2], ids[1]: [0, 1, 2]}, op_cfg()))
+        assert st.ok()
+        h = {}
+        for key, op, c in [("push", "SparseTablePushOperator", {}), ("pull_ro", "SparseTablePullOperator", {"read_only": True}),
+                           ("dump", "DumpOperator", {}), ("load", "LoadOperator", {"block_size": 50})]:
+            st, h[key] = client.register_handler(key, S.LIB, op, json.dumps(c), sid)
+            assert st.ok()
+        keys = np.arange(3000, dtype=np.int64)
+        vals = np.ones((3000, DIM), np.float32) * (keys[:, None] % 3 + 1)
+        assert S.PushHandler(client, sid, h["push"]).async_push(keys, vals).ok()
+        uri = str(tmp_path / "d")
+        st, n = S.DumpHandler(client, sid, h["dump"]).dump(uri, 5)          # several files per node
+        assert st.ok() and n == 3000
+        assert client.clear_storage(sid).ok()
+        st, n = S.LoadHandler(client, sid, h["load"]).load(uri, 8, 30000)   # one wave: a server gets many files at once
+        assert st.ok() and n == 3000
+        st, rows = S.PullHandler(client, sid, h["pull_ro"]).pull(keys)
+        assert st.ok() and np.array_equal(rows, vals)
+        line = servers[0].report_line()
+        assert line.startswith(f"pserver node={ids[0]} requests=") and f"{sid}:" in line
+        time.sleep(1.5)
+        assert servers[0].last_report().startswith(f"pserver node={ids[0]}")
+        # restore mode with a wait: the replacement starts BEFORE the node dies and still takes over
+        rcfg = S.ServerConfig()
+        rcfg.restore_wait_timeout_s = 10
+        box = {}
+
+        def replacement():
+            fresh = S.Server(master.address(), rcfg)
+            box["server"] = fresh
+            box["out"] = fresh.restore_storages()
+
+        th = threading.Thread(target=replacement)
+        th.start()
+        time.sleep(0.5)
+        servers[1].stop()
+        th.join(30)
+        assert not th.is_alive()
+        st, n = box["out"]
+        assert st.ok() and n == 1, st
+        servers.append(box["server"])
+        assert box["server"].storage_size(sid) == 3000
+    finally:
+        for s in servers:
+            s.stop()
+        master.stop()
