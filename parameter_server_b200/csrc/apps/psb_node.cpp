@@ -30,7 +30,8 @@ void on_signal(int) { g_stop = 1; }
 int usage() {
     std::fprintf(stderr,
                  "usage: psb_node master [--threads N]\n"
-                 "       psb_node pserver --master HOST:PORT [--restore] [--image-dir DIR] [--c2s-threads N] [--s2s-threads N]\n");
+                 "       psb_node pserver --master HOST:PORT [--restore] [--restore-wait S] [--image-dir DIR] [--report-interval S]\n"
+                 "                        [--load-threads N] [--c2s-threads N] [--s2s-threads N]\n");
     return 2;
 }
 }  // namespace
@@ -54,6 +55,9 @@ int main(int argc, char** argv) {
         if (a == "--master" && i + 1 < argc) master_addr = argv[++i];
         else if (a == "--restore") restore = true;
         else if (a == "--image-dir" && i + 1 < argc) cfg.local_image_dir = argv[++i];
+        else if (a == "--report-interval") { if (!next(&cfg.report_interval_s)) return usage(); }
+        else if (a == "--restore-wait") { if (!next(&cfg.restore_wait_timeout_s)) return usage(); }
+        else if (a == "--load-threads") { if (!next(&cfg.load_thread_num)) return usage(); }
         else if (a == "--threads") { if (!next(&threads)) return usage(); }
         else if (a == "--c2s-threads") { if (!next(&cfg.c2s_thread_num)) return usage(); }
         else if (a == "--s2s-threads") { if (!next(&cfg.s2s_thread_num)) return usage(); }
