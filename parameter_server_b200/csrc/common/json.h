@@ -116,7 +116,11 @@ private:
     static void skip_ws(const std::string& s, size_t& p) {
         while (p < s.size() && (s[p] == ' ' || s[p] == '\n' || s[p] == '\t' || s[p] == '\r')) ++p;
     }
-    static Json parse_value(const std::string& s, size_t& p) {
+    // Nesting is bounded: configs and contexts are a few levels deep, and a recursive parser must not be walked off
+    // the stack by a hostile or damaged input.
+    static constexpr int kMaxDepth = 128;
+    static Json parse_value(const std::string& s, size_t& p, int depth = 0) {
+        if (depth > kMaxDepth) throw std::runtime_error("nested too deeply");
         skip_ws(s, p);
         if (p >= s.size()) throw std::runtime_error("unexpected end");
         char c = s[p];
@@ -131,7 +135,7 @@ private:
                 skip_ws(s, p);
                 if (p >= s.size() || s[p] != ':') throw std::runtime_error("expected ':'");
                 ++p;
-                j.obj_[k] = parse_value(s, p);
+                j.obj_[k] = parse_value(s, p, depth + 1);
                 skip_ws(s, p);
                 if (p < s.size() && s[p] == ',') { ++p; continue; }
                 if (p < s.size() && s[p] == '}') { ++p; return j; }
@@ -144,7 +148,7 @@ private:
             skip_ws(s, p);
             if (p < s.size() && s[p] == ']') { ++p; return j; }
             for (;;) {
-                j.arr_.push_back(parse_value(s, p));
+                j.arr_.push_back(parse_value(s, p, depth + 1));
                 skip_ws(s, p);
                 if (p < s.size() && s[p] == ',') { ++p; continue; }
                 if (p < s.size() && s[p] == ']') { ++p; return j; }

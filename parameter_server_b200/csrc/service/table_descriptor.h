@@ -123,6 +123,8 @@ struct TableDescriptor {
     // Replace the content from JSON. With `only_if_newer` the descriptor is left alone (returns
     // false) unless the incoming version or update_version is larger.
     bool from_json(const Json& j, bool only_if_newer = false) {
+        // anything that is not a context object leaves the descriptor alone
+        if (!j.has("version") || !j.has("update_version") || !j.has("nodes") || !j.has("storage_op")) return false;
         int32_t v = (int32_t)j.at("version").as_int(), uv = (int32_t)j.at("update_version").as_int();
         if (only_if_newer && v <= version && uv <= update_version) return false;
         version = v;

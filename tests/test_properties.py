@@ -123,3 +123,32 @@ def test_archive_round_trip(i, d, s, v, vs):
 def test_compression_round_trip(data, algo):
     stt, back, _ = C.compress_round_trip(algo, data)
     assert stt.ok() and back == data
+
+
+json_values = st.recursive(st.none() | st.booleans() | st.integers(min_value=-(2 ** 53), max_value=2 ** 53) |
+                           st.floats(allow_nan=False, allow_infinity=False, width=32) | st.text(max_size=12),
+                           lambda children: st.lists(children, max_size=4) | st.dictionaries(st.text(max_size=6), children, max_size=4),
+                           max_leaves=20)
+
+
+@settings(max_examples=150, deadline=None)
+@given(text=st.text(max_size=200) | json_values.map(lambda v: __import__("json").dumps(v)))
+def test_descriptor_parser_never_crashes_and_rejects_what_is_not_a_context(text):
+    from parameter_server_b200 import service as S
+    td = S.TableDescriptor()
+    before = td.to_json_str()
+    ok = td.from_json_str(text)
+    if not ok:
+        assert td.to_json_str() == before                  # a rejected input leaves the descriptor alone
+
+
+def test_deeply_nested_json_is_refused_not_followed():
+    from parameter_server_b200 import service as S
+    td = S.TableDescriptor()
+    for n in (200, 100000, 2000000):
+        assert td.from_json_str("[" * n + "]" * n) is False
+        assert td.from_json_str('{"a":' * n + "1" + "}" * n) is False
+    # a real context still round-trips
+    good = td.to_json_str()
+    td2 = S.TableDescriptor()
+    assert td2.from_json_str(good) and td2.to_json_str() == good
