@@ -84,6 +84,7 @@ void bind_host(py::module_& m) {
              })
         .def("push_shard",
              [](HostTable& t, int s, KeyArray keys, F32Array grads, const OptConfig& o, bool sync) {
+                 if ((size_t)grads.size() != (size_t)keys.size() * t.dim()) throw std::invalid_argument("grads shape");
                  return t.push_shard(s, keys.data(), grads.data(), (size_t)keys.size(), o, sync);
              })
         .def("set_rows",

@@ -292,10 +292,12 @@ void bind_service(py::module_& m) {
         .def("join_group", &PushHandler::join_group)
         .def("metrics", [](PushHandler& h) { return metrics_dict(h); })
         .def("async_push", [](PushHandler& h, KeyArray keys, F32Array grads, int timeout_ms) {
+            if ((size_t)grads.size() != (size_t)keys.size() * h.dim()) throw std::invalid_argument("grads must hold one row of dim floats per key");
             py::gil_scoped_release g;
             return h.async_push(keys.data(), grads.data(), (size_t)keys.size(), timeout_ms);
         }, py::arg("keys"), py::arg("grads"), py::arg("timeout_ms") = -1)
         .def("sync_push", [](PushHandler& h, KeyArray keys, F32Array grads, int timeout_ms) {
+            if ((size_t)grads.size() != (size_t)keys.size() * h.dim()) throw std::invalid_argument("grads must hold one row of dim floats per key");
             py::gil_scoped_release g;
             return h.sync_push(keys.data(), grads.data(), (size_t)keys.size(), timeout_ms);
         }, py::arg("keys"), py::arg("grads"), py::arg("timeout_ms") = -1)
@@ -371,6 +373,7 @@ void bind_service(py::module_& m) {
         .def("block_size", &SyncHandler::block_size)
         .def("sync_block", [](SyncHandler& h, KeyArray keys, F32Array rows, int timeout_ms) {
             const uint32_t stride = (uint32_t)(rows.size() / std::max<py::ssize_t>(1, keys.size()));
+            if ((size_t)stride * (size_t)keys.size() != (size_t)rows.size()) throw std::invalid_argument("rows must hold the same number of floats per key");
             py::gil_scoped_release g;
             return h.sync_block(keys.data(), rows.data(), (size_t)keys.size(), stride, timeout_ms);
         }, py::arg("keys"), py::arg("rows"), py::arg("timeout_ms") = 30000);

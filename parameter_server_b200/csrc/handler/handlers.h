@@ -243,6 +243,10 @@ public:
         tid_ = t;
         return t;
     }
+    uint32_t dim() {
+        auto e = entry();
+        return e ? storage_op_of(*e)->dim() : 0;
+    }
     Status async_push(const int64_t* keys, const float* grads, size_t n, int timeout_ms = -1) {
         return push(keys, grads, n, RequestType::OP_PUSH_ASYNC, timeout_ms);
     }
