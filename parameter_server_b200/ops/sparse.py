@@ -337,6 +337,9 @@ class SparseTable:
         if self.is_cuda:
             keys = keys.contiguous()
             rows = rows.contiguous().float()
+            width = self.dim if emb_only else self.table.stride()
+            if not keys.is_cuda or not rows.is_cuda or keys.dtype != torch.int64 or rows.numel() != keys.numel() * width:
+                raise ValueError("set_rows needs CUDA int64 keys and one row of %d floats per key" % width)
             raise_if_error(self.table.set_rows(keys.data_ptr(), rows.data_ptr(), keys.numel(), emb_only, _stream()))
         else:
             raise_if_error(self.table.set_rows(keys.cpu().numpy(), rows.cpu().float().numpy(), emb_only))
