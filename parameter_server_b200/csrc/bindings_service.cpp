@@ -67,6 +67,22 @@ void bind_service(py::module_& m) {
         if (st.ok()) st = c.decompress(packed.data(), packed.size(), &plain);
         return py::make_tuple(st, py::bytes((const char*)plain.data(), plain.size()), packed.size());
     });
+    m.def("compress_only", [](const std::string& algo, py::bytes data) {
+        Compressor c;
+        Status st = Compressor::create(algo, &c);
+        std::vector<uint8_t> packed;
+        std::string in = data;
+        if (st.ok()) st = c.compress((const uint8_t*)in.data(), in.size(), &packed);
+        return py::make_tuple(st, py::bytes((const char*)packed.data(), packed.size()));
+    });
+    m.def("decompress_only", [](const std::string& algo, py::bytes data) {
+        Compressor c;
+        Status st = Compressor::create(algo, &c);
+        std::vector<uint8_t> plain;
+        std::string in = data;
+        if (st.ok()) st = c.decompress((const uint8_t*)in.data(), in.size(), &plain);
+        return py::make_tuple(st, py::bytes((const char*)plain.data(), plain.size()));
+    });
     m.def("heap_sort", [](std::vector<double> v) {
         Heap<double> h;
         for (double x : v) h.push(x);

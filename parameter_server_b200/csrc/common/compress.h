@@ -85,7 +85,15 @@ public:
         if (n < 8) return Status::Error("compressed block too short");
         uint64_t raw;
         std::memcpy(&raw, src, 8);
-        out->resize(raw);
+        // the announced size comes from a file or from the wire: refuse what no compressor could have produced from
+        // n bytes before sizing a buffer by it
+        if (raw > (1ull << 40) || raw > (uint64_t)(n - 8) * 16384 + (1u << 20) || (kind_ != 1 && raw > 0x7FFFFFFFull))
+            return Status::Error("compressed block announces an implausible size");
+        try {
+            out->resize(raw);
+        } catch (const std::exception&) {
+            return Status::OOM("cannot allocate the decompressed block");
+        }
         if (kind_ == 1) {
             size_t d = z_decomp_(out->data(), raw, src + 8, n - 8);
             if (z_err_(d) || d != raw) return Status::Error("zstd decompress failed");

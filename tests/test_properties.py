@@ -152,3 +152,20 @@ def test_deeply_nested_json_is_refused_not_followed():
     good = td.to_json_str()
     td2 = S.TableDescriptor()
     assert td2.from_json_str(good) and td2.to_json_str() == good
+
+
+@settings(max_examples=60, deadline=None)
+@given(data=st.binary(min_size=1, max_size=2048), algo=st.sampled_from(["zstd", "lz4"]), flips=st.lists(st.integers(0, 4095), min_size=1, max_size=8),
+       cut=st.integers(0, 64))
+def test_damaged_compressed_blocks_are_refused_not_followed(data, algo, flips, cut):
+    """Bit flips, truncation and hostile size headers in a compressed block end in an error status (or, by chance,
+    in other data): never in a crash or an absurd allocation."""
+    stt, packed = C.compress_only(algo, data)
+    assert stt.ok()
+    b = bytearray(packed)
+    for f in flips:
+        b[f % len(b)] ^= 1 << (f % 8)
+    b = bytes(b[: max(1, len(b) - cut)])
+    stt, _ = C.decompress_only(algo, b)                      # any status, but it returns
+    hostile = (2 ** 62).to_bytes(8, "little") + packed[8:]
+    assert not C.decompress_only(algo, hostile)[0].ok()
