@@ -87,7 +87,7 @@ public:
         std::memcpy(&raw, src, 8);
         // the announced size comes from a file or from the wire: refuse what no compressor could have produced from
         // n bytes before sizing a buffer by it
-        if (raw > (1ull << 40) || raw > (uint64_t)(n - 8) * 16384 + (1u << 20) || (kind_ != 1 && raw > 0x7FFFFFFFull))
+        if (raw > (1ull << 40) || raw > (uint64_t)(n - 8) * (1u << 20) + (1u << 20) || (kind_ != 1 && raw > 0x7FFFFFFFull))
             return Status::Error("compressed block announces an implausible size");
         try {
             out->resize(raw);
