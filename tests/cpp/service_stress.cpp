@@ -12,6 +12,7 @@
 // on a trainer table are shipped to a predictor table again and again while four threads keep pushing, and the
 // predictor must end up equal to the trainer. A sixth loads the trainer's dump into an in-process table with four
 // threads and reads it from four. A seventh sends malformed requests. The sanitizers check the rest.
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
@@ -56,7 +57,9 @@ static std::string nodes_json(const std::vector<std::pair<int, std::vector<int>>
     } while (0)
 
 int main() {
-    constexpr int kDim = 4, kThreads = 4, kIters = 120, kKeys = 2000, kBatch = 128;
+    constexpr int kDim = 4, kIters = 120, kKeys = 2000, kBatch = 128;
+    const char* env_threads = std::getenv("PSB_STRESS_THREADS");   // worker threads per phase (default 4, at most 32)
+    const int kThreads = std::max(1, std::min(32, env_threads ? std::atoi(env_threads) : 4));
     Master master(4);
     std::vector<std::unique_ptr<Server>> servers;
     for (int i = 0; i < 3; ++i) servers.emplace_back(new Server(master.address()));
