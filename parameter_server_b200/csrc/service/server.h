@@ -31,6 +31,7 @@ struct ServerConfig {
     int report_interval_s = -1;
     int restore_wait_timeout_s = -1;
     int restore_batch_size = 1000;
+    int restore_thread_num = 4;
     int s2s_timeout_ms = 60000;
     // Directory of this host's persistent table images (empty: none). A server in restore mode that finds the image
     // of the node it replaces, with the table's version_uuid, opens it instead of the table's dump.
@@ -871,6 +872,9 @@ private:
     Status restore_storage_coordinated(TableEntry& e) {
         std::map<int32_t, std::string> nodes;
         PSB_RETURN_IF_ERROR(peers(PSERVER_S2S_RPC_NAME, &nodes));
+        // one live replica per shard, chosen up front: without one for every shard nothing is fetched at all
+        // (CoordinatedRestoreProgress: queue of local shards, `no_replica` abort flag)
+        std::vector<std::pair<int32_t, int>> plan;
         for (int32_t shard : e.rt.local_shards()) {
             std::set<int> exclude{node_id_};
             int replica = -1;
@@ -879,31 +883,60 @@ private:
                 replica = e.rt.pick_one_replica(shard, &exclude);
             }
             if (replica < 0 || !nodes.count(replica)) return Status::NoReplica("restore: no live replica of shard " + std::to_string(shard));
-            int32_t iterator_id = -1;
-            uint64_t offset = 0;
+            plan.push_back({shard, replica});
+        }
+        // the shards are fetched by restore_thread_num workers (CoordinatedRestoreController spawns thread_num workers)
+        std::atomic<size_t> next{0};
+        std::atomic<bool> failed{false};
+        std::mutex first_mu;
+        Status first;
+        auto worker = [&] {
+            RpcClient rpc;  // a connection of its own: the batches of different shards travel side by side
             for (;;) {
-                PSMessage m;
-                m.meta.sid = e.sid;
-                m.meta.req_type = RequestType::OP_COORDINATED_RESTORE_ITERATE;
-                m.ar << iterator_id << offset << (uint64_t)cfg_.restore_batch_size << shard;
-                Bytes b;
-                PSB_RETURN_IF_ERROR(s2s_client_.call(nodes[replica], m.seal(), cfg_.s2s_timeout_ms, &b));
-                PSMessage r = PSMessage::open(std::move(b));
-                Status st;
-                r.ar >> st;
-                PSB_RETURN_IF_ERROR(st);
-                int32_t sid = 0, sh = 0, fin = 0, stride = 0;
-                uint64_t num = 0;
-                r.ar >> sid >> sh >> fin >> iterator_id >> offset >> num >> stride;
-                if (stride < 0 || num > (1ull << 40) || !r.ar.can_hold((int64_t)num, 8 + (size_t)stride * 4))
-                    return Status::Error("restore: malformed batch from node " + std::to_string(replica));
-                std::vector<int64_t> keys(num);
-                std::vector<float> rows((size_t)num * stride);
-                r.ar.read_raw(keys.data(), num * 8);
-                r.ar.read_raw(rows.data(), rows.size() * 4);
-                if (num) PSB_RETURN_IF_ERROR(e.storage->set_rows(keys.data(), rows.data(), num, false));
-                if (fin) break;
+                const size_t i = next++;
+                if (i >= plan.size() || failed.load()) return;
+                Status st = restore_one_shard(e, plan[i].first, plan[i].second, nodes[plan[i].second], rpc);
+                if (!st.ok()) {
+                    failed = true;
+                    std::lock_guard<std::mutex> g(first_mu);
+                    if (first.ok()) first = st;
+                }
             }
+        };
+        const int nthreads = (int)std::min<size_t>(std::max(1, cfg_.restore_thread_num), plan.size());
+        std::vector<std::thread> pool;
+        for (int t = 1; t < nthreads; ++t) pool.emplace_back(worker);
+        worker();
+        for (auto& t : pool) t.join();
+        return first;
+    }
+    // One shard from one replica in resumable batches (CoordinatedRestoreWorker: loop RestoreBatch(iterator_id,
+    // offset, batch_size) over s2s until finished).
+    Status restore_one_shard(TableEntry& e, int32_t shard, int replica, const std::string& address, RpcClient& rpc) {
+        int32_t iterator_id = -1;
+        uint64_t offset = 0;
+        for (;;) {
+            PSMessage m;
+            m.meta.sid = e.sid;
+            m.meta.req_type = RequestType::OP_COORDINATED_RESTORE_ITERATE;
+            m.ar << iterator_id << offset << (uint64_t)cfg_.restore_batch_size << shard;
+            Bytes b;
+            PSB_RETURN_IF_ERROR(rpc.call(address, m.seal(), cfg_.s2s_timeout_ms, &b));
+            PSMessage r = PSMessage::open(std::move(b));
+            Status st;
+            r.ar >> st;
+            PSB_RETURN_IF_ERROR(st);
+            int32_t sid = 0, sh = 0, fin = 0, stride = 0;
+            uint64_t num = 0;
+            r.ar >> sid >> sh >> fin >> iterator_id >> offset >> num >> stride;
+            if (stride < 0 || num > (1ull << 40) || !r.ar.can_hold((int64_t)num, 8 + (size_t)stride * 4))
+                return Status::Error("restore: malformed batch from node " + std::to_string(replica));
+            std::vector<int64_t> keys(num);
+            std::vector<float> rows((size_t)num * stride);
+            r.ar.read_raw(keys.data(), num * 8);
+            r.ar.read_raw(rows.data(), rows.size() * 4);
+            if (num) PSB_RETURN_IF_ERROR(e.storage->set_rows(keys.data(), rows.data(), num, false));
+            if (fin) break;
         }
         return Status::Ok();
     }
