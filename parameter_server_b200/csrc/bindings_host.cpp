@@ -30,6 +30,19 @@ void bind_host(py::module_& m) {
         .def_readwrite("soft_limit_bytes", &HostTableConfig::soft_limit_bytes)
         .def_readwrite("hard_limit_bytes", &HostTableConfig::hard_limit_bytes);
 
+    // shard (or, with `owner`, the owning rank) of every key of an int64 array: the vector form of sparse_shard_of
+    m.def("sparse_shards_of", [](KeyArray keys, int n_shards, std::vector<int> owner) {
+        if (n_shards < 1 || (!owner.empty() && (int)owner.size() != n_shards)) throw std::invalid_argument("n_shards / owner map");
+        py::array_t<int64_t> out((py::ssize_t)keys.size());
+        const int64_t* k = keys.data();
+        int64_t* o = out.mutable_data();
+        for (py::ssize_t i = 0; i < keys.size(); ++i) {
+            const int s = sparse_shard_of(k[i], n_shards);
+            o[i] = owner.empty() ? s : owner[s];
+        }
+        return out;
+    }, py::arg("keys"), py::arg("n_shards"), py::arg("owner") = std::vector<int>());
+
     py::class_<HostTable>(m, "HostTable")
         .def(py::init<const HostTableConfig&>())
         .def("dim", &HostTable::dim)

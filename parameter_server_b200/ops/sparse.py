@@ -230,8 +230,7 @@ class SparseTable:
     # inserts and the cross-rank gradient fold happen in one fixed order), rows travel back. It exists for
     # CPU-only jobs and as the multi-process oracle of the host-side logic; it is not a fast path.
     def _owners_of(self, keys_np: np.ndarray) -> np.ndarray:
-        return np.fromiter((self._shard_owner[C.sparse_shard_of(int(k), self.n_shards)] for k in keys_np), dtype=np.int64,
-                           count=len(keys_np))
+        return C.sparse_shards_of(np.ascontiguousarray(keys_np, dtype=np.int64), self.n_shards, list(self._shard_owner))
 
     def _cpu_collective_pull(self, keys_np: np.ndarray, bag_size: int, mean: bool, insert: bool) -> np.ndarray:
         import torch.distributed as dist
@@ -371,8 +370,7 @@ class SparseTable:
                 if n:
                     k, r = kbuf[:n].clone(), rbuf[:n].clone()
                     if dirty_only and shard >= 0:
-                        sel = torch.tensor([C.sparse_shard_of(int(x), self.n_shards) == shard for x in k.tolist()],
-                                           device=self.device)
+                        sel = torch.from_numpy(C.sparse_shards_of(k.cpu().numpy(), self.n_shards) == shard).to(self.device)
                         k, r = k[sel], r[sel]
                     if k.numel():
                         yield k, r
