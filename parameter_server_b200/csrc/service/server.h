@@ -76,7 +76,12 @@ public:
                 }
             });
     }
-    ~Server() { stop(); }
+    ~Server() {
+        stop();
+        // the thread an EXIT request started may still be inside stop() (or about to enter it): wait for it
+        std::lock_guard<std::mutex> g(exit_mu_);
+        if (exit_thread_.joinable()) exit_thread_.join();
+    }
 
     // "node=.. requests=.. errors=.. storages=[sid:items:bytes ...]"
     std::string report_line() {
@@ -111,7 +116,10 @@ public:
     bool exited() const { return exited_; }
     Context& context() { return ctx_; }
 
+    // Safe to call from several threads: the callers after the first wait until the first one is done, so that
+    // nobody destroys the server while its thread pools are still being joined.
     void stop() {
+        std::lock_guard<std::mutex> sg(stop_mu_);
         if (stopped_.exchange(true)) return;
         report_cv_.notify_all();
         if (reporter_.joinable()) reporter_.join();
@@ -352,9 +360,11 @@ private:
         observe(label, meta.sid, req_bytes, out.size(), !st.ok(),
                 std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count());
         resp.send(reply(st, &out, meta));
-        if (meta.req_type == RequestType::EXIT) {
-            exited_ = true;
-            std::thread([this] { stop(); }).detach();
+        if (meta.req_type == RequestType::EXIT && !exited_.exchange(true)) {
+            // stop() joins the worker pools, this thread among them: it runs on a thread of its own, which the
+            // destructor joins
+            std::lock_guard<std::mutex> g(exit_mu_);
+            exit_thread_ = std::thread([this] { stop(); });
         }
     }
 
@@ -1013,6 +1023,8 @@ private:
     std::string last_report_;
     std::map<int32_t, int> replaced_node_;  // storage id -> the dead node this server took over
     std::atomic<bool> stopped_{false}, exited_{false};
+    std::mutex stop_mu_, exit_mu_;
+    std::thread exit_thread_;
     std::mutex metric_mu_;
     std::map<std::string, uint64_t> metrics_;
     std::map<std::pair<std::string, int32_t>, Series> series_;

@@ -104,7 +104,8 @@ def load(table: SparseTable, uri: str, batch: int = 1 << 18, inbox: Optional[Pee
     if int(flag.item()):
         raise RuntimeError(problem or "load: another rank found a damaged dump file")
     owner_dev = torch.tensor(table.shard_owner, dtype=torch.int32, device=table.device)
-    inbox = inbox or PeerInbox(table, batch)
+    if table.is_cuda:
+        inbox = inbox or PeerInbox(table, batch)
     got, _ = stream_to_owners(table, _read_batches(mine, table.table.stride(), batch, table.device), owner_dev, inbox,
                               keep_local=True)
     if table.world > 1:

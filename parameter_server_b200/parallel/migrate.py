@@ -26,6 +26,7 @@ from .._lib import C
 from ..ops.dense import _view
 from ..ops.sparse import SparseTable
 from ..utils.status import raise_if_error
+from . import migrate_host as _host
 
 
 class PeerInbox:
@@ -87,6 +88,8 @@ def _ship(table: SparseTable, inbox: PeerInbox, keys: torch.Tensor, rows: torch.
     """Send (keys, rows) to the ranks in ``dest`` and insert what this rank receives into ``target``."""
     target = target or table
     world = table.world
+    if not table.is_cuda:
+        return _host.ship(table, keys, rows, dest, target)
     order = torch.argsort(dest, stable=True)
     keys, rows, dest = keys[order], rows[order], dest[order]
     counts = torch.bincount(dest, minlength=world).tolist()
@@ -113,6 +116,8 @@ def _ship(table: SparseTable, inbox: PeerInbox, keys: torch.Tensor, rows: torch.
 
 def route(table: SparseTable, keys: torch.Tensor, owner_dev: Optional[torch.Tensor]) -> torch.Tensor:
     """Shard of every key (``owner_dev`` None) or the rank that owns it under the map ``owner_dev``."""
+    if not table.is_cuda:
+        return _host.shards_of(table, keys, None if owner_dev is None else owner_dev.tolist()).to(torch.int32)
     out = torch.empty(keys.numel(), dtype=torch.int32, device=table.device)
     rc = C.shard_of_keys(keys.data_ptr(), keys.numel(), table.n_shards, 0 if owner_dev is None else owner_dev.data_ptr(),
                          out.data_ptr(), torch.cuda.current_stream().cuda_stream)
@@ -226,6 +231,8 @@ def reshard(table: SparseTable, new_owner: Sequence[int], batch: int = 1 << 18, 
     map is swapped only at the very end, every key is still found where the current map says (the reference keeps
     serving reads during a reshard the same way, pico-ps/handler/UpdateContextHandler.cpp:62-153)."""
     import time
+    if not table.is_cuda:
+        return _host.reshard(table, new_owner, stats, between_rounds)
     world = table.world
     marks = []
 

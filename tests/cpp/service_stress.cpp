@@ -11,7 +11,8 @@
 // and the replica count of a table and rebalances it while four threads read it. In a fifth the rows that change
 // on a trainer table are shipped to a predictor table again and again while four threads keep pushing, and the
 // predictor must end up equal to the trainer. A sixth loads the trainer's dump into an in-process table with four
-// threads and reads it from four. A seventh sends malformed requests. The sanitizers check the rest.
+// threads and reads it from four. A seventh sends malformed requests. An eighth closes servers by request and destroys
+// them the moment they report that they have left. The sanitizers check the rest.
 #include <algorithm>
 #include <atomic>
 #include <cstdio>
@@ -475,6 +476,20 @@ int main() {
         MUST(PullHandler(&client, fsid, h["pull"]).pull(&k, 1, got.data(), 20000));
         std::printf("phase 7: %d malformed requests answered\n", answered);
         if (got[0] < 2.0f) ++wrong;
+    }
+    // ---- phase 8: servers asked to leave (EXIT) are destroyed the moment they report exited(), while the thread that
+    // the request started may still be joining their worker pools -----------------------------------------------------
+    {
+        int closed = 0;
+        for (int round = 0; round < 8; ++round) {
+            std::unique_ptr<Server> extra(new Server(master.address()));
+            const int node = extra->node_id();
+            MUST(client.close_pserver(node));
+            while (!extra->exited()) std::this_thread::yield();
+            extra.reset();
+            ++closed;
+        }
+        std::printf("phase 8: %d servers closed by request\n", closed);
     }
     for (auto& s : servers) s->stop();
     master.stop();
