@@ -75,6 +75,7 @@ public:
         auto it = shards_.find(s);
         if (it != shards_.end()) {
             bytes_ -= it->second->rows.capacity() * sizeof(float);
+            n_items_ -= it->second->map.size();
             shards_.erase(it);
         }
     }

@@ -268,7 +268,13 @@ def reshard(table: SparseTable, new_owner: Sequence[int], batch: int = 1 << 18, 
 
 class ReplicaSet:
     """2x replication for a collective table: rank ``r`` mirrors the shards of rank ``(r - 1) % world`` in a
-    second table and ships its own changes to rank ``(r + 1) % world``."""
+    second table and ships its own changes to rank ``(r + 1) % world``. For a table on the host back-end the
+    constructor hands back the host implementation with the same methods."""
+
+    def __new__(cls, table: SparseTable, batch: int = 1 << 18):
+        if not table.is_cuda:
+            return _host.HostReplicaSet(table)
+        return super().__new__(cls)
 
     def __init__(self, table: SparseTable, batch: int = 1 << 18):
         self.table = table

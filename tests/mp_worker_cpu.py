@@ -19,6 +19,73 @@ def gather(obj):
     return out
 
 
+def elastic(rank, world):
+    """Reshard, 2x replication (sync / restore) and dump / load of a host table, 3 ranks."""
+    import tempfile
+    from parameter_server_b200.parallel import ReplicaSet, checkpoint, reshard
+
+    dim, n_shards = 4, 7
+    kw = dict(lr=0.1, init_accumulator=0.2)
+    t = SparseTable(dim, "adagrad", kw, n_shards=n_shards, device="cpu")
+    rng = np.random.default_rng(11)                   # the same keys on every rank: everybody can check everything
+    keys = torch.from_numpy(rng.choice(1 << 30, size=900, replace=False).astype(np.int64))
+    mine = keys[rank::world]
+    t.pull(mine)
+    t.push(torch.from_numpy(np.random.default_rng(rank).standard_normal((mine.numel(), dim)).astype(np.float32)))
+    want = t.pull(keys, insert=False)
+    total = sum(gather(t.size()))
+    assert total == 900, total
+    # rebalance: everything to rank 0 and 1, then a rotation; reads in the middle of the move still see every row
+    seen = []
+    for new_owner in ([s % 2 for s in range(n_shards)], [(s + 1) % world for s in range(n_shards)]):
+        reshard(t, new_owner, between_rounds=lambda: seen.append(torch.equal(t.pull(keys, insert=False), want)))
+        assert list(t.shard_owner) == new_owner
+        assert torch.equal(t.pull(keys, insert=False), want)
+        sizes = gather(t.size()); assert sum(sizes) == 900, (sizes, new_owner, t.table.shard_list())
+        for k, _ in t.export():
+            owners = {new_owner[int(s)] for s in __import__("parameter_server_b200").C.sparse_shards_of(k.numpy(), n_shards)}
+            assert owners <= {rank}, owners
+    assert seen == [True, True], seen
+    # 2x replication: full sync, an incremental one after a small push, then rank 1 loses its table
+    rep = ReplicaSet(t)
+    sent = gather(rep.sync())
+    assert sum(sent) == 900, sent
+    some = keys[:40]
+    t.pull(some)
+    t.push(torch.ones(40, dim))
+    want = t.pull(keys, insert=False)
+    sent = gather(rep.sync())
+    assert sum(sent) == 40, sent
+    assert sum(gather(rep.sync())) == 0
+    lost = 1
+    before = t.size()
+    if rank == lost:
+        t.table.clear()
+        assert t.size() == 0
+    got = rep.restore(lost)
+    if rank == lost:
+        assert got == before and t.size() == before
+    assert torch.equal(t.pull(keys, insert=False), want)
+    # dump with 2 files per rank, load into a table with another shard count; one rank's files alone restore that rank
+    uri = [tempfile.mkdtemp(prefix="psb_ckpt_") if rank == 0 else None]
+    dist.broadcast_object_list(uri, src=0)
+    written = gather(checkpoint.dump(t, uri[0], file_number=2))
+    assert sum(written) == 900, written
+    t2 = SparseTable(dim, "adagrad", kw, n_shards=5, device="cpu")
+    landed = gather(checkpoint.load(t2, uri[0], batch=128))
+    assert sum(landed) == 900 and sum(gather(t2.size())) == 900, landed
+    assert torch.equal(t2.pull(keys, insert=False), want)
+    if rank == lost:
+        t.table.clear()
+    dist.barrier()
+    checkpoint.load(t, uri[0], only_node=lost)
+    assert torch.equal(t.pull(keys, insert=False), want)
+    dist.barrier()
+    if rank == 0:
+        import shutil
+        shutil.rmtree(uri[0], ignore_errors=True)
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dist.init_process_group("gloo")
@@ -46,6 +113,7 @@ def main():
         for k, _ in t.export():
             owners = {t.shard_owner[__import__("parameter_server_b200").C.sparse_shard_of(int(x), n_shards)] for x in k.tolist()}
             assert owners <= {rank}, owners
+    elastic(rank, world)
     # dense table: all-reduce + optimizer on every rank, identical parameters everywhere
     d = DenseTable({"w": (64, 8), "b": (64,)}, "adamw", dict(lr=1e-2, weight_decay=0.01), device="cpu")
     d.load({"w": torch.ones(64, 8), "b": torch.zeros(64)})

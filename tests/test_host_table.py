@@ -124,3 +124,17 @@ def test_optimizers_move_weights(opt, kw):
     w1 = t.pull(k)
     assert torch.all(w1 < w0) or opt == "ftrl"
     assert torch.isfinite(w1).all()
+
+
+def test_dropping_a_shard_takes_its_items_out_of_the_count():
+    t = mk(n_shards=4)
+    keys = torch.arange(400, dtype=torch.int64)
+    t.pull(keys)
+    assert t.size() == 400
+    per_shard = {s: t.table.shard_size(s) for s in t.table.shard_list()}
+    assert sum(per_shard.values()) == 400
+    t.table.erase_shard(2)
+    assert t.size() == 400 - per_shard[2] and 2 not in t.table.shard_list()
+    assert t.memory_usage() >= 0
+    t.table.create_shard(2)
+    assert t.table.shard_size(2) == 0 and t.size() == 400 - per_shard[2]
