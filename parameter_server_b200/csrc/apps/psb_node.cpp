@@ -8,7 +8,9 @@
 //       over the shards of a dead node from their live replicas or from the table's dump
 //       (the restore mode of the reference's server process, pico-ps/service/Service.cpp:237-313). With --image-dir
 //       it writes its tables' persistent images there on a planned shutdown (EXIT, SIGTERM) and, in restore mode,
-//       opens the image of the node it replaces when no live replica has the shards.
+//       opens the image of the node it replaces when no live replica has the shards. With --sync-master it runs the
+//       sync thread: rows changed by pushes on tables whose push operator names follower tables ("sync_table") are
+//       shipped to those tables, found through the model registry of that master.
 //
 // The same objects as the Python bindings: tables with "backend": "gpu" are served by the fused kernels.
 #include <chrono>
@@ -20,6 +22,7 @@
 
 #include "../service/master.h"
 #include "../service/server.h"
+#include "../service/table_syncer.h"
 
 using namespace psb;
 
@@ -31,7 +34,7 @@ int usage() {
     std::fprintf(stderr,
                  "usage: psb_node master [--threads N]\n"
                  "       psb_node pserver --master HOST:PORT [--restore] [--restore-wait S] [--image-dir DIR] [--report-interval S]\n"
-                 "                        [--load-threads N] [--c2s-threads N] [--s2s-threads N]\n");
+                 "                        [--load-threads N] [--c2s-threads N] [--s2s-threads N] [--sync-master HOST:PORT]\n");
     return 2;
 }
 }  // namespace
@@ -41,7 +44,7 @@ int main(int argc, char** argv) {
     std::signal(SIGINT, on_signal);
     std::signal(SIGTERM, on_signal);
     const std::string role = argv[1];
-    std::string master_addr;
+    std::string master_addr, sync_master;
     bool restore = false;
     int threads = 4;
     ServerConfig cfg;
@@ -53,6 +56,7 @@ int main(int argc, char** argv) {
             return true;
         };
         if (a == "--master" && i + 1 < argc) master_addr = argv[++i];
+        else if (a == "--sync-master" && i + 1 < argc) sync_master = argv[++i];
         else if (a == "--restore") restore = true;
         else if (a == "--image-dir" && i + 1 < argc) cfg.local_image_dir = argv[++i];
         else if (a == "--report-interval") { if (!next(&cfg.report_interval_s)) return usage(); }
@@ -76,6 +80,10 @@ int main(int argc, char** argv) {
         Server server(master_addr, cfg);
         std::printf("pserver node_id=%d c2s=%s s2s=%s\n", server.node_id(), server.c2s_address().c_str(), server.s2s_address().c_str());
         std::fflush(stdout);
+        // tables whose push operator names follower tables are mirrored to them in the background; the followers
+        // live in the cluster of `--sync-master` (which may be this server's own master)
+        std::unique_ptr<TableSyncer> syncer;
+        if (!sync_master.empty()) syncer.reset(new TableSyncer(&server, sync_master));
         if (restore) {
             int n = 0;
             Status st = server.restore_storages(&n);
@@ -84,6 +92,10 @@ int main(int argc, char** argv) {
             if (!st.ok()) return 1;
         }
         while (!server.exited() && !g_stop) std::this_thread::sleep_for(std::chrono::milliseconds(20));
+        if (syncer) {
+            syncer->wait_idle(5000);   // what the last pushes changed still goes out
+            syncer->stop();
+        }
         if (!cfg.local_image_dir.empty()) {  // a planned shutdown leaves this node's tables on the host
             int n = 0;
             Status st = server.save_local_images(&n);

@@ -119,6 +119,7 @@ PYBIND11_MODULE(_C, m) {
         .def("memory_usage", &GpuTable::memory_usage)
         .def("healthy", &GpuTable::healthy)
         .def("set_healthy", &GpuTable::set_healthy)
+        .def("check_healthy", &GpuTable::check_healthy)
         .def("set_limits", &GpuTable::set_limits)
         .def("index_capacity", &GpuTable::index_capacity)
         .def("tombstones", &GpuTable::tombstones)

@@ -58,6 +58,7 @@ void bind_host(py::module_& m) {
         .def("memory_usage", &HostTable::memory_usage)
         .def("healthy", &HostTable::healthy)
         .def("set_healthy", &HostTable::set_healthy)
+        .def("check_healthy", &HostTable::check_healthy)
         .def("set_limits", &HostTable::set_limits)
         .def("enable_dirty_tracking", &HostTable::enable_dirty_tracking)
         .def("clear_dirty", &HostTable::clear_dirty)

@@ -10,6 +10,7 @@
 #include "controller/controller.h"
 #include "handler/handlers.h"
 #include "native_ps/native_ps.h"
+#include "service/table_syncer.h"
 
 namespace py = pybind11;
 using namespace psb;
@@ -168,6 +169,21 @@ void bind_service(py::module_& m) {
         .def_readwrite("local_image_dir", &ServerConfig::local_image_dir)
         .def_readwrite("report_interval_s", &ServerConfig::report_interval_s)
         .def_readwrite("restore_wait_timeout_s", &ServerConfig::restore_wait_timeout_s);
+    // the sync thread of a server: keeps the follower tables named by push operators ("sync_table") fresh
+    py::class_<TableSyncer>(m, "TableSyncer")
+        .def(py::init<Server*, const std::string&, int, double>(), py::arg("server"), py::arg("follower_master"),
+             py::arg("max_attempts") = 5, py::arg("backoff_scale") = 1.0, py::keep_alive<1, 2>(), nogil())
+        .def("stop", &TableSyncer::stop, nogil())
+        .def("wait_idle", &TableSyncer::wait_idle, py::arg("timeout_ms") = 10000, nogil())
+        .def("stats", [](TableSyncer& t) {
+            auto s = t.stats();
+            py::dict d;
+            d["rounds"] = s.rounds;
+            d["rows"] = s.rows;
+            d["errors"] = s.errors;
+            d["last_error"] = s.last_error;
+            return d;
+        });
     py::class_<Server>(m, "Server")
         .def(py::init<const std::string&, const ServerConfig&>(), py::arg("master"), py::arg("config") = ServerConfig(), nogil())
         .def("node_id", &Server::node_id)
@@ -206,7 +222,10 @@ void bind_service(py::module_& m) {
 
     m.def("register_udf", [](const std::string& name, py::function fn) {
         // fn(storage_id: int, node_items: int, param: bytes) -> bytes
-        auto holder = std::make_shared<py::function>(std::move(fn));
+        // The registry is a process-wide static that outlives the interpreter, so the reference to the Python
+        // function is deliberately never dropped: releasing it during static destruction, after the interpreter has
+        // been finalised, crashes the process on its way out.
+        std::shared_ptr<py::function> holder(new py::function(std::move(fn)), [](py::function*) {});
         UDFRegistry::instance().add(name, [holder](TableEntry& e, const std::string& param, std::string* result) {
             py::gil_scoped_acquire gil;
             try {

@@ -701,12 +701,24 @@ public:
     // 5 s, ServerTooNewCtx 1 s (after refreshing the context), Timeout 3 s, InvalidID re-initialises the storage
     // on this client - and tries again, at most `max_attempts` times. `backoff_scale` scales the pauses.
     Status sync_pred(Server& trainer, int32_t trainer_sid, uint64_t* n_synced, int max_attempts = 5, double backoff_scale = 1.0) {
+        return sync_pred_impl(trainer, trainer_sid, n_synced, max_attempts, backoff_scale, true);
+    }
+    // The same pass, but the changed-row marks stay: for a table with several followers, every follower but the last.
+    Status sync_pred_keep_marks(Server& trainer, int32_t trainer_sid, uint64_t* n_synced, int max_attempts = 5,
+                                double backoff_scale = 1.0) {
+        return sync_pred_impl(trainer, trainer_sid, n_synced, max_attempts, backoff_scale, false);
+    }
+
+private:
+    Status sync_pred_impl(Server& trainer, int32_t trainer_sid, uint64_t* n_synced, int max_attempts, double backoff_scale,
+                          bool clear_marks) {
         Status st;
         uint64_t total = 0;
         for (int attempt = 0; attempt < max_attempts; ++attempt) {
             uint64_t n = 0;
             st = trainer.push_sync_table(trainer_sid, block_size(),
-                                         [&](const int64_t* k, const float* r, size_t m, uint32_t stride) { return sync_block(k, r, m, stride); }, &n);
+                                         [&](const int64_t* k, const float* r, size_t m, uint32_t stride) { return sync_block(k, r, m, stride); }, &n,
+                                         clear_marks);
             total += n;
             if (st.ok()) break;
             ++metrics_.retries;

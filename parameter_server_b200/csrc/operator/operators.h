@@ -344,7 +344,16 @@ public:
             Status st = parse_opt_config(c, &opt_);
             if (!st.ok()) throw std::runtime_error(st.msg());
         }
+        // tables (of this or of another cluster) that follow this one: what pushes change here is shipped to them
+        // by the server's sync thread (pico-ps/operator/PushOperator.h:45-55)
+        if (c.has("sync_table"))
+            for (auto& t : c.at("sync_table").elements())
+                sync_tables_.push_back({t.at("model_name").as_string(), t.at("table_name").as_string(), t.at("op_key").as_string()});
     }
+    struct SyncTarget {
+        std::string model_name, table_name, op_key;
+    };
+    const std::vector<SyncTarget>& sync_tables() const { return sync_tables_; }
     const char* kind() const override { return "push"; }
     OptConfig opt_for(const TableEntry& e) const { return has_opt_ ? opt_ : storage_op_of(e)->opt(); }
 
@@ -486,6 +495,7 @@ public:
 private:
     bool has_opt_ = false;
     OptConfig opt_;
+    std::vector<SyncTarget> sync_tables_;
 };
 
 // ---------------------------------------------------------------------------------------------------

@@ -41,6 +41,8 @@ struct TableEntry {
     std::unique_ptr<KVStorage> storage;         // serving data
     std::unique_ptr<KVStorage> update_storage;  // receives shuffled items during a reshard
     IncrementStorage incr;
+    std::atomic<bool> sync_enabled{false};      // changed rows are being recorded for follower tables
+    std::mutex sync_mu;                         // serialises switching the recording on
     std::map<int32_t, std::shared_ptr<Operator>> ops;  // handler id -> operator
     std::map<int32_t, RestoreIterator> restore_iters;
     int32_t next_iter_id = 0;

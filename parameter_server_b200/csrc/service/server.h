@@ -71,6 +71,15 @@ public:
                 // one line per interval on stderr (ServerConfig::report_interval of the reference)
                 std::unique_lock<std::mutex> g(report_mu_);
                 while (!report_cv_.wait_for(g, std::chrono::seconds(cfg_.report_interval_s), [this] { return stopped_.load(); })) {
+                    // the memory monitor rides on the same interval (Server::self_monitor of the reference,
+                    // pico-ps/service/Service.cpp:368-375): tables over a limit stop taking new rows, tables with
+                    // room again take them again
+                    for (int32_t sid : ctx_.ids()) {
+                        auto e = ctx_.get(sid);
+                        if (!e) continue;
+                        std::shared_lock<std::shared_mutex> tg(e->mu);
+                        if (e->storage) e->storage->check_healthy();
+                    }
                     last_report_ = report_line();
                     std::fprintf(stderr, "%s\n", last_report_.c_str());
                 }
@@ -276,12 +285,36 @@ public:
     Status enable_sync(int32_t sid) {
         auto e = ctx_.get(sid);
         if (!e || !e->storage) return Status::InvalidID("no storage " + std::to_string(sid));
-        e->storage->enable_dirty_tracking();
+        std::shared_lock<std::shared_mutex> g(e->mu);
+        ensure_tracking(*e);
         return Status::Ok();
+    }
+
+    // ---------------------------------------------------------------------------------------
+    // Hook of the sync thread (pico-ps/service/Service.cpp:1467-1540; the thread itself lives in
+    // service/table_syncer.h because it drives handlers, which sit above this header). The listener is called with
+    // (storage id, deleted) after every applied async push or store on a table whose push operator names follower
+    // tables (`sync_table` in its config), and once more when such a table is deleted. It must only take a note and
+    // return: it runs on a request thread.
+    using SyncListener = std::function<void(int32_t, bool)>;
+    void set_sync_listener(SyncListener fn) {
+        std::lock_guard<std::mutex> g(listener_mu_);
+        sync_listener_ = fn ? std::make_shared<SyncListener>(std::move(fn)) : nullptr;
+    }
+    // The follower tables named by the push operators of table `sid`.
+    std::vector<SparseTablePushOperator::SyncTarget> sync_targets(int32_t sid) {
+        std::vector<SparseTablePushOperator::SyncTarget> out;
+        auto e = ctx_.get(sid);
+        if (!e) return out;
+        std::shared_lock<std::shared_mutex> g(e->mu);
+        for (auto& kv : e->ops)
+            if (auto p = std::dynamic_pointer_cast<SparseTablePushOperator>(kv.second))
+                out.insert(out.end(), p->sync_tables().begin(), p->sync_tables().end());
+        return out;
     }
     Status push_sync_table(int32_t sid, size_t block,
                            const std::function<Status(const int64_t*, const float*, size_t, uint32_t)>& send_block,
-                           uint64_t* n_synced) {
+                           uint64_t* n_synced, bool clear_marks = true) {
         auto e = ctx_.get(sid);
         if (!e || !e->storage) return Status::InvalidID("no storage " + std::to_string(sid));
         *n_synced = 0;
@@ -303,8 +336,10 @@ public:
                 }
             }
         }
-        e->storage->clear_dirty();
-        e->incr.updated = false;
+        if (clear_marks) {   // with several followers only the pass for the last one clears
+            e->storage->clear_dirty();
+            e->incr.updated = false;
+        }
         return Status::Ok();
     }
 
@@ -421,6 +456,8 @@ private:
         const bool committed = had_update && e.td.update_nodes.empty() && e.td.update_version > old_uv;
         if (committed && e.update_storage) {
             e.storage = std::move(e.update_storage);  // the reshuffled data becomes the serving data
+            // the rows arrived marked (see process_new_ctx_create_shard): the next sync round re-ships them
+            if (e.sync_enabled) e.incr.updated = true;
         } else if (e.storage) {
             // plain placement change (e.g. a dead node replaced): create / drop local shards to match
             if (e.storage->n_shards() == e.rt.global_shard_num()) {
@@ -528,7 +565,13 @@ private:
         }
         if (meta.ctx_ver >= 0) refresh_if_behind(*e, meta);
         switch (meta.req_type) {
-            case RequestType::STORAGE_DELETE: ctx_.erase(meta.sid); return Status::Ok();
+            case RequestType::STORAGE_DELETE: {
+                auto gone = ctx_.get(meta.sid);
+                const bool followed = gone && gone->sync_enabled;
+                ctx_.erase(meta.sid);
+                if (followed) notify_sync(meta.sid, true);
+                return Status::Ok();
+            }
             case RequestType::STORAGE_CLEAR: {
                 std::shared_lock<std::shared_mutex> g(e->mu);
                 PSB_RETURN_IF_ERROR(check_write_ctx_version(*e, meta));
@@ -583,7 +626,9 @@ private:
                 PSB_RETURN_IF_ERROR(check_write_ctx_version(*e, meta));
                 auto op = find_op<SparseTablePushOperator>(*e, meta.hid);
                 if (!op) return Status::InvalidID("store: handler is not a push operator");
-                return op->apply_store(*e);
+                Status st = op->apply_store(*e);
+                if (st.ok() && !op->sync_tables().empty()) notify_sync(meta.sid, false);
+                return st;
             }
             case RequestType::OP_FOREACH:
             case RequestType::OP_ERASEIF:
@@ -675,7 +720,33 @@ private:
         auto op = find_op<SparseTablePushOperator>(e, meta.hid);
         if (!op) return Status::InvalidID("push: handler " + std::to_string(meta.hid) + " is not a push operator");
         PSB_RETURN_IF_ERROR(check_write_ctx_version(e, meta));
-        return op->apply_request(e, in, sync);
+        const bool followed = !op->sync_tables().empty() && has_sync_listener();
+        // rows must be marked from the first push on, so the marks are switched on before it is applied
+        if (followed) ensure_tracking(e);
+        Status st = op->apply_request(e, in, sync);
+        if (st.ok() && followed && !sync) notify_sync(meta.sid, false);   // a sync push changes nothing before its store
+        return st;
+    }
+    // The flag is raised only after the storage records changes, so a push that sees it set is recorded.
+    static void ensure_tracking(TableEntry& e) {
+        if (e.sync_enabled.load(std::memory_order_acquire)) return;
+        std::lock_guard<std::mutex> g(e.sync_mu);
+        if (!e.sync_enabled.load(std::memory_order_relaxed)) {
+            e.storage->enable_dirty_tracking();
+            e.sync_enabled.store(true, std::memory_order_release);
+        }
+    }
+    bool has_sync_listener() {
+        std::lock_guard<std::mutex> g(listener_mu_);
+        return sync_listener_ != nullptr;
+    }
+    void notify_sync(int32_t sid, bool deleted) {
+        std::shared_ptr<SyncListener> fn;
+        {
+            std::lock_guard<std::mutex> g(listener_mu_);
+            fn = sync_listener_;
+        }
+        if (fn) (*fn)(sid, deleted);
     }
     Status process_direct_push(TableEntry& e, Archive& in, bool into_update) {
         std::shared_lock<std::shared_mutex> g(e.mu);
@@ -789,7 +860,11 @@ private:
         PSB_RETURN_IF_ERROR(check_table_version(e, meta));
         if (e.update_rt.local_shards().empty()) return Status::Ok();  // this node leaves the table
         auto* sop = static_cast<SparseTableStorageOperator*>(e.storage_op.get());
-        return sop->create_storage(e.update_rt.global_shard_num(), e.update_rt.local_shards(), &e.update_storage);
+        PSB_RETURN_IF_ERROR(sop->create_storage(e.update_rt.global_shard_num(), e.update_rt.local_shards(), &e.update_storage));
+        // a followed table keeps recording changes across the reshard: rows that move are marked on arrival, so what
+        // was still waiting to be shipped on their old owner is not lost (some rows are shipped twice instead)
+        if (e.sync_enabled) e.update_storage->enable_dirty_tracking();
+        return Status::Ok();
     }
     // One old shard: stream its items in blocks to the owners under the NEW placement.
     Status process_new_ctx_shuffle(TableEntry& e, const PSMessageMeta& meta, Archive& in) {
@@ -1023,7 +1098,8 @@ private:
     std::string last_report_;
     std::map<int32_t, int> replaced_node_;  // storage id -> the dead node this server took over
     std::atomic<bool> stopped_{false}, exited_{false};
-    std::mutex stop_mu_, exit_mu_;
+    std::mutex stop_mu_, exit_mu_, listener_mu_;
+    std::shared_ptr<SyncListener> sync_listener_;
     std::thread exit_thread_;
     std::mutex metric_mu_;
     std::map<std::string, uint64_t> metrics_;

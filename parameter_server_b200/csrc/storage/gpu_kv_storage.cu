@@ -219,6 +219,7 @@ public:
     uint64_t memory_usage() override { return table_->memory_usage(); }
     bool healthy() override { return table_->healthy(); }
     void set_healthy(bool h) override { table_->set_healthy(h); }
+    bool check_healthy() override { return table_->check_healthy(); }
     void set_limits(uint64_t soft, uint64_t hard) override { table_->set_limits(soft, hard); }
     void enable_dirty_tracking() override { table_->enable_dirty_tracking(); }
     void clear_dirty() override {

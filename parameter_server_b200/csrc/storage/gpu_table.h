@@ -11,6 +11,7 @@
 //   * a soft/hard byte budget makes allocation fail with OUT_OF_MEMORY and flips `healthy`, which
 //     the service layer turns into the reference's back-pressure (pico-ps/storage/Storage.cpp:114-136).
 #pragma once
+#include <atomic>
 #include <cstdint>
 #include <string>
 #include <vector>
@@ -76,6 +77,13 @@ public:
     bool healthy() const { return healthy_; }
     void set_limits(uint64_t soft, uint64_t hard) { cfg_.soft_limit_bytes = soft; cfg_.hard_limit_bytes = hard; }
     void set_healthy(bool h) { healthy_ = h; }
+    // Periodic re-evaluation by the server's monitor: over a limit means unhealthy. The way back is explicit here
+    // (clear, a purge after a reshard, set_healthy): slabs are never returned to the driver while the table lives.
+    bool check_healthy() {
+        if ((cfg_.hard_limit_bytes && bytes_ > cfg_.hard_limit_bytes) || (cfg_.soft_limit_bytes && bytes_ > cfg_.soft_limit_bytes))
+            healthy_ = false;
+        return healthy_;
+    }
 
     // Resumable scan (the reference's ShardIterator, pico-ps/storage/Storage.h:49-77): examines at
     // most `window` slots starting at `cursor`, appends matching (key, full row) records to the
@@ -131,7 +139,7 @@ private:
     unsigned long long* scratch_ = nullptr;  // small device scratch for counters
     uint64_t bytes_ = 0;
     uint64_t tombstones_ = 0;
-    bool healthy_ = true;
+    std::atomic<bool> healthy_{true};   // read by request threads, re-evaluated by the server's monitor
 };
 
 }  // namespace psb

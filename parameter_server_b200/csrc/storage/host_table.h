@@ -275,6 +275,32 @@ public:
     bool healthy() const { return healthy_; }
     void set_healthy(bool h) { healthy_ = h; }
     void set_limits(uint64_t soft, uint64_t hard) { cfg_.soft_limit_bytes = soft; cfg_.hard_limit_bytes = hard; }
+    // Re-evaluation of the health flag, called periodically by the server's monitor
+    // (ShardStorageMemory::check_healthy, pico-ps/storage/Storage.cpp:114-136): over a limit means unhealthy; a table
+    // that went unhealthy because a row pool could not grow is healthy again once there is room - rows were erased
+    // (their slots are on the free lists), memory was given back (a shard dropped, a clear) or the limits were
+    // raised far enough for the growth that failed.
+    bool check_healthy() {
+        const uint64_t b = bytes_;
+        const uint64_t soft = cfg_.soft_limit_bytes, hard = cfg_.hard_limit_bytes;
+        if ((hard && b > hard) || (soft && b > soft)) {
+            healthy_ = false;
+            return false;
+        }
+        if (!healthy_) {
+            const uint64_t extra = failed_extra_;
+            const bool fits = (!hard || b + extra <= hard) && (!soft || b + extra <= soft);
+            bool free_rows = false;
+            for (int s : shard_list()) {
+                Shard* sh = get(s);
+                if (!sh) continue;
+                std::shared_lock<std::shared_mutex> g(sh->mu);
+                free_rows = free_rows || !sh->free_rows.empty();
+            }
+            if (fits || free_rows || b < failed_at_bytes_) healthy_ = true;
+        }
+        return healthy_;
+    }
     void enable_dirty_tracking() { track_dirty_ = true; }
     void clear_dirty() {
         for (int s : shard_list()) {
@@ -320,6 +346,8 @@ private:
                 uint64_t b = bytes_;
                 if ((cfg_.hard_limit_bytes && b + extra > cfg_.hard_limit_bytes) ||
                     (cfg_.soft_limit_bytes && b + extra > cfg_.soft_limit_bytes)) {
+                    failed_extra_ = extra;
+                    failed_at_bytes_ = b;
                     healthy_ = false;
                     return Status::OOM("host row pool would exceed the memory limit");
                 }
@@ -356,7 +384,8 @@ private:
     std::atomic<uint64_t> n_items_{0};
     std::atomic<uint64_t> bytes_{0};
     std::atomic<bool> healthy_{true};
-    bool track_dirty_ = false;
+    std::atomic<uint64_t> failed_extra_{0}, failed_at_bytes_{0};   // the growth that made the table unhealthy
+    std::atomic<bool> track_dirty_{false};   // may be switched on while pushes run (a follower table appears)
 };
 
 }  // namespace psb

@@ -48,6 +48,7 @@ public:
     virtual uint64_t memory_usage() = 0;
     virtual bool healthy() = 0;
     virtual void set_healthy(bool h) = 0;
+    virtual bool check_healthy() = 0;   // re-evaluate the flag against the limits (the server's monitor calls it)
     virtual void set_limits(uint64_t soft, uint64_t hard) = 0;
     virtual void enable_dirty_tracking() = 0;
     virtual void clear_dirty() = 0;
@@ -92,6 +93,7 @@ public:
     uint64_t memory_usage() override { return t_.memory_usage(); }
     bool healthy() override { return t_.healthy(); }
     void set_healthy(bool h) override { t_.set_healthy(h); }
+    bool check_healthy() override { return t_.check_healthy(); }
     void set_limits(uint64_t soft, uint64_t hard) override { t_.set_limits(soft, hard); }
     void enable_dirty_tracking() override { t_.enable_dirty_tracking(); }
     void clear_dirty() override { t_.clear_dirty(); }

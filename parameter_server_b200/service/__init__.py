@@ -28,6 +28,7 @@ DumpHandler = C.DumpHandler
 LoadHandler = C.LoadHandler
 UpdateContextHandler = C.UpdateContextHandler
 SyncHandler = C.SyncHandler
+TableSyncer = C.TableSyncer
 UDFHandler = C.UDFHandler
 Controller = C.Controller
 OpSpec = C.OpSpec

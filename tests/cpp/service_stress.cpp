@@ -12,7 +12,8 @@
 // on a trainer table are shipped to a predictor table again and again while four threads keep pushing, and the
 // predictor must end up equal to the trainer. A sixth loads the trainer's dump into an in-process table with four
 // threads and reads it from four. A seventh sends malformed requests. An eighth closes servers by request and destroys
-// them the moment they report that they have left. The sanitizers check the rest.
+// them the moment they report that they have left. In a ninth the sync thread of a server keeps a follower table equal
+// to a table that four threads push to. The sanitizers check the rest.
 #include <algorithm>
 #include <atomic>
 #include <cstdio>
@@ -28,6 +29,7 @@
 #include "native_ps/native_ps.h"
 #include "service/master.h"
 #include "service/server.h"
+#include "service/table_syncer.h"
 
 namespace psb {
 // this host-only binary has no CUDA objects: a table that asks for the GPU back-end is refused
@@ -490,6 +492,69 @@ int main() {
             ++closed;
         }
         std::printf("phase 8: %d servers closed by request\n", closed);
+    }
+    // ---- phase 9: the sync thread of a server ships what concurrent pushes change to a follower table -------------
+    {
+        std::unique_ptr<Server> tr(new Server(master.address())), pr(new Server(master.address()));
+        Client c9(master.address());
+        const std::string opc9 = ",\"op_config\":{\"dim\":4,\"optimizer\":\"sum\",\"init_range\":0.0},\"table_name\":\"";
+        int32_t fsid = -1, fh_sync = -1, fh_pull = -1, tsid = -1, th_push = -1;
+        MUST(c9.create_storage("psb", "SparseTableStorageOperator",
+                               "{\"nodes\":" + nodes_json({{pr->node_id(), {0, 1, 2}}}) + opc9 + "followed\"}", &fsid));
+        MUST(c9.register_handler("sync", "psb", "KVSyncOperator", "{\"block_size\":64}", fsid, &fh_sync));
+        MUST(c9.register_handler("pull_ro", "psb", "SparseTablePullOperator", "{\"read_only\":true}", fsid, &fh_pull));
+        ModelObject model;
+        model.name = "stress_model";
+        TableObject tobj;
+        tobj.table_name = "followed";
+        tobj.storage_id = fsid;
+        tobj.ops.push_back(OperatorObject{"sync", "psb", "KVSyncOperator", "{}", fh_sync});
+        model.tables.push_back(tobj);
+        MUST(set_model(c9.master(), model));
+        MUST(c9.create_storage("psb", "SparseTableStorageOperator",
+                               "{\"nodes\":" + nodes_json({{tr->node_id(), {0, 1}}}) + opc9 + "leader\"}", &tsid));
+        MUST(c9.register_handler("push", "psb", "SparseTablePushOperator",
+                                 "{\"sync_table\":[{\"model_name\":\"stress_model\",\"table_name\":\"followed\",\"op_key\":\"sync\"}]}",
+                                 tsid, &th_push));
+        TableSyncer syncer(tr.get(), master.address(), 3, 0.01);
+        std::vector<std::atomic<uint64_t>> sent9(kKeys);
+        for (auto& x : sent9) x = 0;
+        std::atomic<int> bad9{0};
+        std::vector<std::thread> ts;
+        for (int t = 0; t < kThreads; ++t)
+            ts.emplace_back([&, t] {
+                PushHandler h(&c9, tsid, th_push);
+                std::vector<int64_t> keys(kBatch);
+                std::vector<float> grads((size_t)kBatch * kDim, 1.0f);
+                uint64_t x = 4242 + (uint64_t)t * 17;
+                for (int it = 0; it < 50; ++it) {
+                    for (auto& k : keys) {
+                        x ^= x << 13; x ^= x >> 7; x ^= x << 17;
+                        k = (int64_t)(x % kKeys);
+                    }
+                    Status st = h.async_push(keys.data(), grads.data(), keys.size(), 20000);
+                    if (!st.ok()) { std::fprintf(stderr, "phase 9 push: %s\n", st.msg().c_str()); ++bad9; continue; }
+                    for (auto k : keys) ++sent9[(size_t)k];
+                }
+            });
+        for (auto& t : ts) t.join();
+        if (!syncer.wait_idle(30000)) { std::fprintf(stderr, "phase 9: the sync thread did not settle\n"); ++bad9; }
+        std::vector<int64_t> all9(kKeys);
+        for (int k = 0; k < kKeys; ++k) all9[k] = k;
+        std::vector<float> got9((size_t)kKeys * kDim);
+        MUST(PullHandler(&c9, fsid, fh_pull).pull(all9.data(), all9.size(), got9.data(), 20000));
+        int wrong9 = bad9.load();
+        for (int k = 0; k < kKeys; ++k)
+            if (got9[(size_t)k * kDim] != (float)sent9[k].load()) ++wrong9;
+        const auto stats9 = syncer.stats();
+        std::printf("phase 9: %llu rows in %llu rounds, %llu errors, %d wrong\n", (unsigned long long)stats9.rows,
+                    (unsigned long long)stats9.rounds, (unsigned long long)stats9.errors, wrong9);
+        wrong += wrong9 + (int)stats9.errors;
+        MUST(c9.delete_storage(tsid));
+        syncer.wait_idle(5000);
+        syncer.stop();
+        tr->stop();
+        pr->stop();
     }
     for (auto& s : servers) s->stop();
     master.stop();

@@ -138,3 +138,30 @@ def test_dropping_a_shard_takes_its_items_out_of_the_count():
     assert t.memory_usage() >= 0
     t.table.create_shard(2)
     assert t.table.shard_size(2) == 0 and t.size() == 400 - per_shard[2]
+
+
+def test_health_comes_back_when_there_is_room_again():
+    from parameter_server_b200 import StatusError
+    t = SparseTable(64, "adagrad", n_shards=1, device="cpu", memory_limit_bytes=64 * 1024)
+    keys = []
+    with pytest.raises(StatusError):
+        for i in range(100):
+            k = torch.arange(i * 20, (i + 1) * 20)
+            t.pull(k)
+            keys.append(k)
+    assert not t.table.healthy()
+    assert not t.table.check_healthy()                 # still no room: the monitor leaves the flag down
+    assert t.erase_keys(torch.cat(keys)[:60]) == 60    # room again: 60 row slots on the free list
+    assert t.table.check_healthy() and t.table.healthy()
+    t.pull(torch.arange(10**6, 10**6 + 50))            # new rows fit into the freed slots
+    assert t.table.healthy()
+    # raising the limits is the other way back
+    with pytest.raises(StatusError):
+        for i in range(100):
+            t.pull(torch.arange(2 * 10**6 + i * 50, 2 * 10**6 + (i + 1) * 50))
+    assert not t.table.check_healthy()
+    t.table.set_limits(1 << 20, 1 << 20)
+    assert t.table.check_healthy()
+    # and a table pushed over a limit that was lowered afterwards is marked without waiting for a failed insert
+    t.table.set_limits(1024, 1024)
+    assert not t.table.check_healthy() and not t.table.healthy()

@@ -364,6 +364,40 @@ def test_memory_limit_backpressure(cluster3):
     assert not all(flags)
 
 
+def test_monitor_thread_brings_a_table_back_after_rows_were_erased():
+    """report_interval also drives the memory monitor: a table that refused new rows takes them again once an
+    erase_if made room, without anybody touching the health flag."""
+    master = S.Master()
+    cfg = S.ServerConfig()
+    cfg.report_interval_s = 1
+    server = S.Server(master.address(), cfg)
+    try:
+        client = S.Client(master.address())
+        sid, h = make_table(type("C", (), {"client": client})(), {server.node_id(): [0, 1]}, cfg=op_cfg(dim=64))
+        assert server.set_memory_limit(sid, 64 * 1024).ok()
+        push = S.PushHandler(client, sid, h["push"])
+        st, pushed = None, 0
+        for i in range(50):
+            keys = np.arange(i * 100, (i + 1) * 100, dtype=np.int64)
+            st = push.async_push(keys, np.ones((100, 64), np.float32), 500)
+            if not st.ok():
+                break
+            pushed += 100
+        assert st.code() in (StatusCode.OUT_OF_MEMORY, StatusCode.TIMEOUT) and pushed > 0
+        assert not client.query_memory_info(server.node_id())[1]
+        st, erased = S.EraseIfHandler(client, sid, h["erase_if"]).erase_if(json.dumps({"type": "key_mod", "mod": 2, "rem": 0}))
+        assert st.ok() and erased > 0
+        deadline = time.time() + 10
+        while time.time() < deadline and not client.query_memory_info(server.node_id())[1]:
+            time.sleep(0.1)
+        assert client.query_memory_info(server.node_id())[1]
+        fresh = np.arange(10**6, 10**6 + 20, dtype=np.int64)
+        assert push.async_push(fresh, np.ones((20, 64), np.float32), 5000).ok()
+    finally:
+        server.stop()
+        master.stop()
+
+
 def test_controller_placement_resize_and_introspection(tmp_path):
     cl = Cluster(4)
     try:
