@@ -255,6 +255,12 @@ void bind_service(py::module_& m) {
             Status st = c.create_storage(lib, op, cfg, &sid);
             return std::make_tuple(st, sid);
         }, nogil())
+        .def("pred_create_storage", [](Client& c, const std::string& lib, const std::string& op, const std::string& cfg) {
+            int32_t sid = -1;
+            Status st = c.pred_create_storage(lib, op, cfg, &sid);
+            return std::make_tuple(st, sid);
+        }, nogil())
+        .def("require_update_ctx_async", &Client::require_update_ctx_async, nogil())
         .def("initialize_storage", &Client::initialize_storage, nogil())
         .def("delete_storage", &Client::delete_storage, py::arg("sid"), py::arg("timeout_ms") = 30000, nogil())
         .def("clear_storage", &Client::clear_storage, py::arg("sid"), py::arg("timeout_ms") = 30000, nogil())

@@ -136,6 +136,11 @@ public:
         master_.release_lock(PSERVER_LOCK_NAME);
         return st;
     }
+    // Predictor-side alias of create_storage (pico-ps/service/Client.cpp:108-114).
+    Status pred_create_storage(const std::string& lib, const std::string& op, const std::string& cfg_json, int32_t* sid,
+                               int timeout_ms = 30000) {
+        return create_storage(lib, op, cfg_json, sid, timeout_ms);
+    }
     Status initialize_storage(int32_t sid) { return pull_context(sid); }
     Status delete_storage(int32_t sid, int timeout_ms = 30000) {
         PSB_RETURN_IF_ERROR(pull_context(sid));
@@ -320,6 +325,30 @@ public:
         for (int n : nodes)
             if (live.count(n)) targets.insert(n);
         return broadcast(sid, RequestType::CTX_UPDATE, targets, Archive(), timeout_ms, -1);
+    }
+    // Fire-and-forget form (pico-ps/service/Client.cpp:233-237): every live node of the table is told to re-read its
+    // context; nobody waits for the answers, which the connection's reader drops when they arrive.
+    void require_update_ctx_async(int32_t sid) {
+        auto e = ctx_.get(sid);
+        std::map<int32_t, std::string> live;
+        if (!e || !get_pserver_list(&live).ok()) return;
+        std::set<int> targets;
+        {
+            std::shared_lock<std::shared_mutex> g(e->mu);
+            for (auto& kv : e->rt.nodes())
+                if (live.count(kv.first)) targets.insert(kv.first);
+        }
+        PSMessageMeta meta;
+        meta.sid = sid;
+        meta.hid = -1;
+        meta.ctx_ver = -1;
+        meta.ctx_u_ver = -1;
+        meta.req_type = RequestType::CTX_UPDATE;
+        for (int n : targets) {
+            PSMessage m;
+            m.meta = meta;
+            rpc_.send(live[n], m.seal());
+        }
     }
     // Timeout / NoReplica: find out who died. A node that is no longer registered at the master is DEAD
     // for everybody (published); a registered node that does not answer is UNAVAILABLE for this client.

@@ -632,6 +632,24 @@ def test_available_server_list_excludes_stopped_nodes(cluster3):
     assert st.ok() and sorted(nodes) == sorted(cl.ids()[:2])
 
 
+def test_one_way_context_refresh_and_predictor_create(cluster3):
+    """require_update_ctx_async tells the servers to re-read a table's context without waiting for them;
+    pred_create_storage is the predictor-side name of create_storage."""
+    cl = cluster3
+    st, sid = cl.client.pred_create_storage(S.LIB, "SparseTableStorageOperator", S.storage_config(uneven(cl.ids()), op_cfg()))
+    assert st.ok() and sid >= 0
+    before = [s.metrics_text().count("CTX_UPDATE") for s in cl.servers]
+    cl.client.require_update_ctx_async(sid)            # returns at once
+    deadline = time.time() + 5
+    while time.time() < deadline and not all('request_type="c2s_CTX_UPDATE"' in s.metrics_text() for s in cl.servers):
+        time.sleep(0.02)
+    assert all('request_type="c2s_CTX_UPDATE"' in s.metrics_text() for s in cl.servers), before
+    # the channel is still good for ordinary calls afterwards (the late answers were dropped by the reader)
+    st, hid = cl.client.register_handler("pull_ro", S.LIB, "SparseTablePullOperator", json.dumps({"read_only": True}), sid)
+    assert st.ok() and S.PullHandler(cl.client, sid, hid).pull(np.arange(10, dtype=np.int64))[0].ok()
+    cl.client.require_update_ctx_async(12345)          # unknown table: nothing happens
+
+
 def test_prometheus_metrics_endpoint(cluster3):
     import urllib.request
     from parameter_server_b200.service.metrics import handler_metrics_text, serve_metrics
