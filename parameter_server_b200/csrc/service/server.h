@@ -9,6 +9,9 @@
 // from a live replica over s2s in resumable batches, fall back to the dump at table_uri), and the
 // memory self-monitor. A request is {body, PSMessageMeta tail}; a response is {Status, payload}.
 #pragma once
+#include <dirent.h>
+#include <unistd.h>
+
 #include <cstdio>
 #include <cstring>
 #include <fstream>
@@ -222,6 +225,50 @@ public:
             broadcast_ctx_update(*e);
         }
         if (restored_tables) *restored_tables = (int)mine.size();
+        // the images that the replaced node left on this host are used up (this server writes its own, under its own
+        // node id), and images of tables that no longer exist are of no use to anybody
+        if (!cfg_.local_image_dir.empty() && !mine.empty()) clean_local_images(nullptr);
+        return Status::Ok();
+    }
+
+    // Housekeeping of `local_image_dir` (DCPmemory::remove_storage / remove_storage_exclude in the reference's restore,
+    // pico-ps/service/Service.cpp:284-303; scripts/clear_lvs.sh for whole volumes): removes the images of nodes that
+    // this server replaced, of storages that the master no longer knows, and of another layout identity
+    // (`version_uuid`) than the table has now. Images of other live nodes' current tables stay.
+    Status clean_local_images(int* removed) {
+        if (removed) *removed = 0;
+        if (cfg_.local_image_dir.empty()) return Status::InvalidConfig("local_image_dir is not set");
+        std::set<int> replaced;
+        for (auto& kv : replaced_node_) replaced.insert(kv.second);
+        std::map<int32_t, std::string> uuid_of;   // storage id -> current version_uuid ("" = unknown to the master)
+        for (const std::string& node_dir : list_dir(cfg_.local_image_dir)) {
+            if (node_dir.compare(0, 5, "node_") != 0) continue;
+            const int node = std::atoi(node_dir.c_str() + 5);
+            const std::string dir = cfg_.local_image_dir + "/" + node_dir;
+            size_t left = 0;
+            for (const std::string& name : list_dir(dir)) {
+                const bool is_image = name.compare(0, 8, "storage_") == 0 && name.size() > 12 && name.compare(name.size() - 4, 4, ".img") == 0;
+                if (!is_image) {
+                    if (name.size() > 4 && name.compare(name.size() - 4, 4, ".tmp") == 0 && node != node_id_) ::unlink((dir + "/" + name).c_str());
+                    else ++left;
+                    continue;
+                }
+                const int32_t sid = (int32_t)std::atoi(name.c_str() + 8);
+                if (!uuid_of.count(sid)) {
+                    std::string json;
+                    TableDescriptor td;
+                    uuid_of[sid] = master_.get_context(ctx_key(sid), &json).ok() && td.from_json_str(json) ? td.version_uuid : "";
+                }
+                bool drop = replaced.count(node) || uuid_of[sid].empty();
+                if (!drop) drop = image_uuid(dir + "/" + name) != uuid_of[sid];
+                if (drop && ::unlink((dir + "/" + name).c_str()) == 0) {
+                    if (removed) ++*removed;
+                } else {
+                    ++left;
+                }
+            }
+            if (left == 0 && node != node_id_) ::rmdir(dir.c_str());
+        }
         return Status::Ok();
     }
 
@@ -1032,6 +1079,29 @@ private:
     // restore (pico-ps/storage/DCPmemory.h:493-507, pico-ps/service/Service.cpp:275-294).
     static std::string image_path(const std::string& dir, int node, int32_t sid) {
         return dir + "/node_" + std::to_string(node) + "/storage_" + std::to_string(sid) + ".img";
+    }
+    static std::vector<std::string> list_dir(const std::string& dir) {
+        std::vector<std::string> out;
+        if (DIR* d = ::opendir(dir.c_str())) {
+            while (dirent* ent = ::readdir(d)) {
+                const std::string name = ent->d_name;
+                if (name != "." && name != "..") out.push_back(name);
+            }
+            ::closedir(d);
+        }
+        return out;
+    }
+    // version_uuid recorded in an image file ("" when the file is not an image)
+    static std::string image_uuid(const std::string& path) {
+        std::ifstream f(path, std::ios::binary);
+        char magic[8];
+        uint64_t ulen = 0;
+        f.read(magic, 8);
+        f.read((char*)&ulen, 8);
+        if (!f || std::memcmp(magic, "PSBIMG1", 8) != 0 || ulen > 4096) return "";
+        std::string uuid(ulen, '\0');
+        f.read(&uuid[0], (std::streamsize)ulen);
+        return f ? uuid : "";
     }
     Status restore_storage_from_local_image(TableEntry& e) {
         if (cfg_.local_image_dir.empty()) return Status::Error("no local image directory");

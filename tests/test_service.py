@@ -735,6 +735,12 @@ def test_restore_from_the_hosts_own_image_when_no_replica(tmp_path):
         for s in servers:
             st, n = s.save_local_images()
             assert st.ok() and n == 1
+        import shutil
+        src = tmp_path / "images" / f"node_{ids[0]}" / f"storage_{sid}.img"
+        kept = tmp_path / "kept.img"
+        shutil.copy(src, kept)
+        stale = tmp_path / "images" / f"node_{ids[1]}" / "storage_4242.img"   # a table that the master does not know
+        shutil.copy(src, stale)
         servers[0].stop()                                           # the node with shards 0 and 1 is gone
         pull = S.PullHandler(client, sid, hp)
         assert not pull.pull(keys, 3000, True)[0].ok()              # nobody holds those shards now
@@ -744,11 +750,14 @@ def test_restore_from_the_hosts_own_image_when_no_replica(tmp_path):
         assert st.ok() and n == 1, st
         st, rows = pull.pull(keys, 20000, True)
         assert st.ok() and np.array_equal(rows, vals)
+        # housekeeping after the restore: the replaced node's images are used up, the unknown table's image is stale,
+        # the live neighbour's image of the current table stays
+        assert not src.exists() and not src.parent.exists() and not stale.exists()
+        assert (tmp_path / "images" / f"node_{ids[1]}" / f"storage_{sid}.img").exists()
         # a table created anew has another version_uuid: an old image with the same ids must not be opened
         st, sid2 = client.create_storage(S.LIB, "SparseTableStorageOperator", S.storage_config({fresh.node_id(): [0]}, op_cfg()))
         assert st.ok()
-        import shutil
-        src = tmp_path / "images" / f"node_{ids[0]}" / f"storage_{sid}.img"
+        src = kept
         dst = tmp_path / "images" / f"node_{fresh.node_id()}" / f"storage_{sid2}.img"
         dst.parent.mkdir(parents=True, exist_ok=True)
         shutil.copy(src, dst)
@@ -757,6 +766,8 @@ def test_restore_from_the_hosts_own_image_when_no_replica(tmp_path):
         servers.append(last)
         st, n = last.restore_storages()
         assert not st.ok()                                          # no replica, foreign image refused, no dump either
+        st, n = last.clean_local_images()
+        assert st.ok() and n == 1 and not dst.exists()              # the foreign image goes when somebody cleans up
     finally:
         for s in servers:
             s.stop()
