@@ -87,7 +87,9 @@ int main(int argc, char** argv) {
         if (restore) {
             int n = 0;
             Status st = server.restore_storages(&n);
-            std::printf("restore: %s (%d tables)\n", st.ok() ? "OK" : st.msg().c_str(), n);
+            std::string from;
+            for (auto& kv : server.restore_sources()) from += (from.empty() ? " from " : ", ") + kv.second;
+            std::printf("restore: %s (%d tables)%s\n", st.ok() ? "OK" : st.msg().c_str(), n, from.c_str());
             std::fflush(stdout);
             if (!st.ok()) return 1;
         }

@@ -117,6 +117,11 @@ public:
         }
         return out + "]";
     }
+    // Where the data of each table restored by restore_storages came from: "replica", "image" or "dump".
+    std::map<int32_t, std::string> restore_sources() {
+        std::lock_guard<std::mutex> g(report_mu_);
+        return restore_source_;
+    }
     std::string last_report() {
         std::lock_guard<std::mutex> g(report_mu_);
         return last_report_;
@@ -200,15 +205,22 @@ public:
             // a live replica has the current data; without one, this host's own image of the dead node (if its
             // layout identity matches); then the table's dump
             Status rs = restore_storage_coordinated(*e);
+            const char* source = "replica";
             if (!rs.ok()) {
                 Status li = restore_storage_from_local_image(*e);
+                source = "image";
                 if (li.ok()) rs = li;
                 else {
                     Status fs = restore_storage_from_fs(*e);
+                    source = "dump";
                     rs = fs.ok() ? fs : Status(fs.code(), fs.msg() + " (replica: " + rs.msg() + "; local image: " + li.msg() + ")");
                 }
             }
             PSB_RETURN_IF_ERROR(rs);
+            {
+                std::lock_guard<std::mutex> g(report_mu_);
+                restore_source_[sid] = source;
+            }
             // LOADING -> RUNNING, publish, tell the peers
             PSB_RETURN_IF_ERROR(master_.acquire_lock(PSERVER_LOCK_NAME));
             std::string json;
@@ -1166,6 +1178,7 @@ private:
     std::mutex report_mu_;
     std::condition_variable report_cv_;
     std::string last_report_;
+    std::map<int32_t, std::string> restore_source_;
     std::map<int32_t, int> replaced_node_;  // storage id -> the dead node this server took over
     std::atomic<bool> stopped_{false}, exited_{false};
     std::mutex stop_mu_, exit_mu_, listener_mu_;

@@ -1,0 +1,178 @@
+"""Rounds of failures against native server processes, in the spirit of the reference's process-level restore test
+(pico-ps/test/ps_pmem_test.cpp:367-532: rounds of kill-one / kill-all / lose-the-local-pool followed by a restart in
+restore mode, with context updates in between, while a client keeps pulling until it is served and checks values).
+
+Every failure is made on the host: SIGKILL or SIGTERM of a `psb_node pserver` process, or deleting its image files.
+Restore sources by round: a live replica (kill one), the host's own images (planned stop of every server), the
+table's dump (every server killed and the images gone).
+"""
+import json
+import os
+import shutil
+import signal
+import subprocess
+import time
+
+import numpy as np
+import pytest
+
+from parameter_server_b200 import _build
+from parameter_server_b200 import service as S
+
+NODE = str(_build.node_path())
+DIM = 4
+
+
+def _spawn(*args):
+    return subprocess.Popen([NODE, *args], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+
+
+def _line(p, timeout=30.0):
+    t0 = time.time()
+    while time.time() - t0 < timeout:
+        line = p.stdout.readline()
+        if line:
+            return line.strip()
+        if p.poll() is not None:
+            break
+        time.sleep(0.01)
+    raise AssertionError("no output from psb_node")
+
+
+class Farm:
+    def __init__(self, addr, image_dir):
+        self.addr, self.image_dir = addr, image_dir
+        self.live = {}          # node id -> process
+        self.all = []
+
+    def start(self, restore=False, sources=("replica", "image", "dump")):
+        args = ["pserver", "--master", self.addr, "--image-dir", self.image_dir]
+        if restore:
+            args += ["--restore", "--restore-wait", "10"]
+        p = _spawn(*args)
+        self.all.append(p)
+        node = int(_line(p).split("node_id=")[1].split()[0])
+        if restore:
+            line = _line(p, 60.0)
+            assert line.startswith("restore: OK (1 tables) from ") and line.split(" from ")[1] in sources, line
+        self.live[node] = p
+        return node
+
+    def kill(self, node, sig):
+        p = self.live.pop(node)
+        p.send_signal(sig)
+        out, _ = p.communicate(timeout=30)
+        return out
+
+    def close(self):
+        for p in self.all:
+            if p.poll() is None:
+                p.kill()
+
+
+def _pull_until_served(pull, keys, want, seconds=40.0):
+    """The reference's client loop: short timeouts, retry until the cluster serves again, then check the values."""
+    t0 = time.time()
+    st = None
+    while time.time() - t0 < seconds:
+        st, rows = pull.pull(keys, 2000, True)
+        if st.ok():
+            assert np.array_equal(rows, want), np.abs(rows - want).max()
+            return
+        time.sleep(0.05)
+    raise AssertionError(f"not served within {seconds} s: {st}")
+
+
+def _push_until_applied(push, keys, grads, seconds=40.0):
+    t0 = time.time()
+    st = None
+    while time.time() - t0 < seconds:
+        st = push.async_push(keys, grads, 5000)
+        if st.ok():
+            return
+        time.sleep(0.05)
+    raise AssertionError(f"push not applied within {seconds} s: {st}")
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.skipif(not os.path.exists(NODE), reason="psb_node is not built")
+def test_rounds_of_failures_and_restores(tmp_path):
+    master = _spawn("master")
+    addr = _line(master)
+    farm = Farm(addr, str(tmp_path / "images"))
+    try:
+        ids = [farm.start() for _ in range(3)]
+        client = S.Client(addr)
+        # 3 shards x 2 replicas, node i holds shards i and i+1
+        place = {ids[i]: [i, (i + 1) % 3] for i in range(3)}
+        st, sid = client.create_storage(S.LIB, "SparseTableStorageOperator",
+                                        S.storage_config(place, dict(dim=DIM, optimizer="sum", init_range=0.0)))
+        assert st.ok(), st
+        h = {}
+        for key, op, cfg in [("push", "SparseTablePushOperator", {}), ("pull_ro", "SparseTablePullOperator", {"read_only": True}),
+                             ("dump", "DumpOperator", {}), ("load", "LoadOperator", {}),
+                             ("update_ctx", "ShardUpdateContextOperator", {})]:
+            st, h[key] = client.register_handler(key, S.LIB, op, json.dumps(cfg), sid)
+            assert st.ok(), st
+        uri = str(tmp_path / "dump")
+        assert client.set_table_uri(sid, uri).ok()
+        push, pull = S.PushHandler(client, sid, h["push"]), S.PullHandler(client, sid, h["pull_ro"])
+        keys = np.arange(3000, dtype=np.int64)
+        want = np.zeros((3000, DIM), np.float32)
+        rng = np.random.default_rng(17)
+
+        def train():
+            g = rng.integers(1, 5, size=(3000, 1)).astype(np.float32) * np.ones((1, DIM), np.float32)
+            _push_until_applied(push, keys, g)
+            want[:] += g
+
+        train()
+        _pull_until_served(pull, keys, want)
+        plan = ["kill_one", "reshard", "stop_all", "kill_one", "lose_everything", "reshard", "kill_one", "stop_all"]
+        for rnd, what in enumerate(plan):
+            nodes = sorted(farm.live)
+            if what == "kill_one":
+                farm.kill(nodes[rnd % len(nodes)], signal.SIGKILL)      # restore source: the live replicas
+                farm.start(restore=True, sources=("replica",))
+            elif what == "stop_all":
+                for n in nodes:                                          # planned stop: every server leaves its images
+                    assert "images: OK" in farm.kill(n, signal.SIGTERM)
+                farm.start(restore=True, sources=("image",))             # restore source: the host's images (nobody is alive)
+                for _ in nodes[1:]:                                      # later ones may find a restored replica first
+                    farm.start(restore=True, sources=("image", "replica"))
+            elif what == "lose_everything":
+                st, n = S.DumpHandler(client, sid, h["dump"]).dump(uri, 2)
+                assert st.ok() and n == 3000, st
+                for n_ in nodes:
+                    farm.kill(n_, signal.SIGKILL)                        # no images are written
+                shutil.rmtree(farm.image_dir, ignore_errors=True)        # and whatever was there is gone
+                farm.start(restore=True, sources=("dump",))              # restore source: the dump at table_uri
+                for _ in nodes[1:]:
+                    farm.start(restore=True, sources=("dump", "replica"))
+            elif what == "reshard":
+                live = sorted(farm.live)
+                shift = 1 + rnd % 2
+                new_place = {live[i]: [(i + shift) % 3, (i + shift + 1) % 3] for i in range(3)}
+                t0 = time.time()
+                while True:                                              # the client may first have to learn the new nodes
+                    st = S.UpdateContextHandler(client, sid, h["update_ctx"]).update_context(S.nodes_json(new_place))
+                    if st.ok() or time.time() - t0 > 30:
+                        break
+                    client.pull_context(sid)
+                    time.sleep(0.2)
+                assert st.ok(), st
+            _pull_until_served(pull, keys, want)                         # nothing lost, whatever the source was
+            train()
+            _pull_until_served(pull, keys, want)
+            st, info = client.query_storage_info(sid)
+            assert st.ok() and sum(i.item_number for i in info) == 2 * 3000, (what, [(i.node_id, i.shard_id, i.item_number) for i in info])
+        for n in sorted(farm.live):
+            client.close_pserver(n)
+        for p in list(farm.live.values()):
+            assert p.wait(timeout=20) == 0
+        master.send_signal(signal.SIGTERM)
+        assert master.wait(timeout=15) == 0
+    finally:
+        farm.close()
+        if master.poll() is None:
+            master.kill()

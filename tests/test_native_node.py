@@ -64,7 +64,7 @@ def test_native_master_and_servers_serve_a_python_client():
         fresh = _spawn("pserver", "--master", addr, "--restore")
         procs.append(fresh)
         assert "node_id=" in _first_line(fresh)
-        assert _first_line(fresh, 30.0) == "restore: OK (1 tables)"
+        assert _first_line(fresh, 30.0) == "restore: OK (1 tables) from replica"
         # admin shutdown: EXIT to every live server, then the master
         st, live = client.get_pserver_list()
         assert st.ok() and len(live) == 2
@@ -105,7 +105,7 @@ def test_planned_shutdown_leaves_an_image_that_a_replacement_opens(tmp_path):
         second = _spawn("pserver", "--master", addr, "--image-dir", img, "--restore")
         procs.append(second)
         assert "node_id=" in _first_line(second)
-        assert _first_line(second, 30.0) == "restore: OK (1 tables)"
+        assert _first_line(second, 30.0) == "restore: OK (1 tables) from image"
         st, rows = S.PullHandler(client, sid, h_pull).pull(keys, 20000, True)
         assert st.ok() and np.array_equal(rows, vals)
         for n in client.get_pserver_list()[1]:
