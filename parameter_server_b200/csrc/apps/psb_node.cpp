@@ -8,11 +8,13 @@
 //       over the shards of a dead node from their live replicas or from the table's dump
 //       (the restore mode of the reference's server process, pico-ps/service/Service.cpp:237-313). With --image-dir
 //       it writes its tables' persistent images there on a planned shutdown (EXIT, SIGTERM) and, in restore mode,
-//       opens the image of the node it replaces when no live replica has the shards. With --sync-master it runs the
+//       opens the image of the node it replaces when no live replica has the shards; --image-interval-ms N also
+//       refreshes the images every N ms while serving. With --sync-master it runs the
 //       sync thread: rows changed by pushes on tables whose push operator names follower tables ("sync_table") are
 //       shipped to those tables, found through the model registry of that master.
 //
 // The same objects as the Python bindings: tables with "backend": "gpu" are served by the fused kernels.
+#include <algorithm>
 #include <chrono>
 #include <csignal>
 #include <cstdio>
@@ -33,7 +35,7 @@ void on_signal(int) { g_stop = 1; }
 int usage() {
     std::fprintf(stderr,
                  "usage: psb_node master [--threads N]\n"
-                 "       psb_node pserver --master HOST:PORT [--restore] [--restore-wait S] [--image-dir DIR] [--report-interval S]\n"
+                 "       psb_node pserver --master HOST:PORT [--restore] [--restore-wait S] [--image-dir DIR] [--image-interval-ms N] [--report-interval S]\n"
                  "                        [--load-threads N] [--c2s-threads N] [--s2s-threads N] [--sync-master HOST:PORT]\n");
     return 2;
 }
@@ -46,7 +48,7 @@ int main(int argc, char** argv) {
     const std::string role = argv[1];
     std::string master_addr, sync_master;
     bool restore = false;
-    int threads = 4;
+    int threads = 4, image_interval_ms = 0;
     ServerConfig cfg;
     for (int i = 2; i < argc; ++i) {
         const std::string a = argv[i];
@@ -59,6 +61,7 @@ int main(int argc, char** argv) {
         else if (a == "--sync-master" && i + 1 < argc) sync_master = argv[++i];
         else if (a == "--restore") restore = true;
         else if (a == "--image-dir" && i + 1 < argc) cfg.local_image_dir = argv[++i];
+        else if (a == "--image-interval-ms") { if (!next(&image_interval_ms)) return usage(); }
         else if (a == "--report-interval") { if (!next(&cfg.report_interval_s)) return usage(); }
         else if (a == "--restore-wait") { if (!next(&cfg.restore_wait_timeout_s)) return usage(); }
         else if (a == "--load-threads") { if (!next(&cfg.load_thread_num)) return usage(); }
@@ -93,7 +96,18 @@ int main(int argc, char** argv) {
             std::fflush(stdout);
             if (!st.ok()) return 1;
         }
-        while (!server.exited() && !g_stop) std::this_thread::sleep_for(std::chrono::milliseconds(20));
+        // with --image-interval-ms the images are also refreshed while serving (checkpoints on the host: a process
+        // that is killed leaves the last complete image, never a torn one - temp file + rename)
+        auto last_image = std::chrono::steady_clock::now();
+        while (!server.exited() && !g_stop) {
+            std::this_thread::sleep_for(std::chrono::milliseconds(image_interval_ms > 0 ? std::min(image_interval_ms, 20) : 20));
+            if (image_interval_ms > 0 && !cfg.local_image_dir.empty() &&
+                std::chrono::steady_clock::now() - last_image >= std::chrono::milliseconds(image_interval_ms)) {
+                Status st = server.save_local_images(nullptr);
+                if (!st.ok()) std::fprintf(stderr, "psb_node: periodic image: %s\n", st.msg().c_str());
+                last_image = std::chrono::steady_clock::now();
+            }
+        }
         if (syncer) {
             syncer->wait_idle(5000);   // what the last pushes changed still goes out
             syncer->stop();

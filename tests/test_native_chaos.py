@@ -176,3 +176,80 @@ def test_rounds_of_failures_and_restores(tmp_path):
         farm.close()
         if master.poll() is None:
             master.kill()
+
+
+def _read_image(path, stride):
+    """Parse a table image; raises when it is torn (short header, short body, trailing bytes)."""
+    raw = path.read_bytes()
+    assert raw[:8] == b"PSBIMG1\x00", raw[:8]
+    ulen = int(np.frombuffer(raw[8:16], "<u8")[0])
+    off = 16 + ulen
+    width = int(np.frombuffer(raw[off:off + 4], "<u4")[0])
+    n = int(np.frombuffer(raw[off + 4:off + 12], "<u8")[0])
+    assert width == stride
+    rec = np.dtype([("key", "<i8"), ("row", "<f4", (stride,))])
+    body = raw[off + 12:]
+    assert len(body) == n * rec.itemsize, (len(body), n, rec.itemsize)
+    return np.frombuffer(body, rec)
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.skipif(not os.path.exists(NODE), reason="psb_node is not built")
+def test_a_killed_server_never_leaves_a_torn_image(tmp_path):
+    """Crash consistency of the periodic images (the reference kills a child in the middle of persistent-memory
+    transactions and checks invariants afterwards, pico-ps/test/ps_pmem_test.cpp:188-251): a server that refreshes
+    its image every few milliseconds is SIGKILLed at random moments under a stream of pushes; whatever is on disk
+    afterwards is a complete image whose rows are each from one moment, and a replacement serves it."""
+    master = _spawn("master")
+    addr = _line(master)
+    procs = [master]
+    rng = np.random.default_rng(5)
+    try:
+        client = S.Client(addr)
+        img = tmp_path / "images"
+        sid = h_push = h_pull = None
+        keys = np.arange(2000, dtype=np.int64)
+        ones = np.ones((2000, DIM), np.float32)
+        pushed = 0
+        for rnd in range(4):
+            args = ["pserver", "--master", addr, "--image-dir", str(img), "--image-interval-ms", "5"]
+            p = _spawn(*(args + (["--restore", "--restore-wait", "10"] if rnd else [])))
+            procs.append(p)
+            node = int(_line(p).split("node_id=")[1].split()[0])
+            if rnd == 0:
+                st, sid = client.create_storage(S.LIB, "SparseTableStorageOperator",
+                                                S.storage_config({node: [0, 1]}, dict(dim=DIM, optimizer="sum", init_range=0.0)))
+                assert st.ok(), st
+                _, h_push = client.register_handler("push", S.LIB, "SparseTablePushOperator", "{}", sid)
+                _, h_pull = client.register_handler("pull_ro", S.LIB, "SparseTablePullOperator", json.dumps({"read_only": True}), sid)
+            else:
+                assert _line(p, 60.0) == "restore: OK (1 tables) from image"
+                st, rows = S.PullHandler(client, sid, h_pull).pull(keys, 20000, True)
+                assert st.ok()
+                # the restored state is what the last complete image held: every row from one moment, nothing newer
+                # than what was pushed, and not older than the image that was checked on disk
+                assert np.all(rows == rows[:, :1]) and rows.max() <= pushed and rows.min() >= floor
+                pushed = int(rows.min())            # rows may differ by the pushes that the image caught half-way
+                # level the table again so that the next round starts from equal rows
+                top = rows[:, :1].max()
+                assert S.PushHandler(client, sid, h_push).async_push(keys, (top - rows[:, :1]) * ones, 20000).ok()
+                pushed = int(top)
+            push = S.PushHandler(client, sid, h_push)
+            deadline = time.time() + 0.3 + float(rng.random()) * 0.5
+            while time.time() < deadline:
+                assert push.async_push(keys, ones, 20000).ok()
+                pushed += 1
+            p.send_signal(signal.SIGKILL)                       # somewhere between, or inside, two image refreshes
+            p.wait(timeout=10)
+            path = img / f"node_{node}" / f"storage_{sid}.img"
+            assert path.exists()
+            image = _read_image(path, DIM)                      # complete: header, count and body agree
+            assert len(image) == 2000 and np.all(image["row"] == image["row"][:, :1])
+            floor = float(image["row"].min())
+            assert floor >= 1 and image["row"].max() <= pushed
+        master.send_signal(signal.SIGTERM)
+        master.wait(timeout=15)
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
