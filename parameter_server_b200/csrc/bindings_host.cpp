@@ -59,6 +59,8 @@ void bind_host(py::module_& m) {
         .def("healthy", &HostTable::healthy)
         .def("set_healthy", &HostTable::set_healthy)
         .def("check_healthy", &HostTable::check_healthy)
+        .def("overflow_size", &HostTable::overflow_size)
+        .def("drain_overflow", &HostTable::drain_overflow)
         .def("set_limits", &HostTable::set_limits)
         .def("enable_dirty_tracking", &HostTable::enable_dirty_tracking)
         .def("clear_dirty", &HostTable::clear_dirty)

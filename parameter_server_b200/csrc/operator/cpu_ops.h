@@ -58,6 +58,9 @@ inline Status cpu_pull(HostTable& t, const int64_t* keys, size_t n, size_t bag_s
 // grads: n_bags*dim (gradient w.r.t. the pooled output).
 inline Status cpu_push(HostTable& t, const int64_t* keys, const float* grads, size_t n, size_t bag_size, bool mean,
                        const OptConfig& opt, bool sync) {
+    // an unhealthy table refuses a push before anything of it is applied (what a push that was let in cannot place is
+    // parked by the table, so a request is never half applied)
+    if (!t.healthy()) return Status::OOM("storage is unhealthy");
     const uint32_t dim = t.dim();
     EasyHashMap<int64_t, uint32_t> whole(kHostEmptyKey, n);
     std::vector<int64_t> uniq_keys;

@@ -735,6 +735,7 @@ private:
                     for (int s : e->storage->shard_list())
                         if (!e->rt.local_shards().count(s)) e->storage->erase_shard(s);
                     e->storage->set_healthy(true);
+                    e->storage->drain_overflow();   // what waited for memory is applied now that shards have left
                 }
                 return Status::Ok();
             }
@@ -947,6 +948,16 @@ private:
             rows.clear();
             PSB_RETURN_IF_ERROR(e.storage->export_shard(old_shard, cursor, window, false, &keys, &rows, &cursor, &finished));
             if (keys.empty()) continue;
+            std::map<int, Archive> bodies;
+            PSB_RETURN_IF_ERROR(DirectPushOperator::generate_requests(sop, e.update_rt, keys.data(), rows.data(), keys.size(),
+                                                                      stride, &bodies));
+            PSB_RETURN_IF_ERROR(s2s_call(bodies, meta, RequestType::NEW_CTX_SHUFFLE));
+        }
+        // pushed items that were waiting for memory on this node travel as rows too: the new owners may have room
+        keys.clear();
+        rows.clear();
+        e.storage->overflow_rows(old_shard, &keys, &rows);
+        if (!keys.empty()) {
             std::map<int, Archive> bodies;
             PSB_RETURN_IF_ERROR(DirectPushOperator::generate_requests(sop, e.update_rt, keys.data(), rows.data(), keys.size(),
                                                                       stride, &bodies));

@@ -52,6 +52,18 @@ public:
         std::vector<uint32_t> touched;       // rows with a pending sync delta
         std::vector<uint8_t> touched_flag;   // per row
         std::vector<uint8_t> dirty;          // per row (incremental sync)
+        // Pushed items whose key could not get a row (memory limit). The request they came with was accepted as a
+        // whole, so they are kept here and applied once there is room again (ShardData::data_vector of the
+        // reference: pico-ps/operator/SparsePushOperator.h:257-259, re-inserted by the purge,
+        // pico-ps/operator/UpdateContextOperator.h:165-187). While the list is not empty pulls of the shard answer
+        // OUT_OF_MEMORY (pico-ps/operator/SparsePullOperator.h:195-199).
+        struct Parked {
+            int64_t key;
+            std::vector<float> grad;
+            OptConfig opt;
+            bool sync;
+        };
+        std::vector<Parked> overflow;
         mutable std::shared_mutex mu;
     };
 
@@ -76,6 +88,7 @@ public:
         if (it != shards_.end()) {
             bytes_ -= it->second->rows.capacity() * sizeof(float);
             n_items_ -= it->second->map.size();
+            n_parked_ -= it->second->overflow.size();
             shards_.erase(it);
         }
     }
@@ -115,6 +128,7 @@ public:
         {
             // fast path: shared lock, no inserts needed
             std::shared_lock<std::shared_mutex> g(sh->mu);
+            if (!sh->overflow.empty()) return Status::OOM("shard holds pushed items that are waiting for memory");
             size_t i = 0;
             for (; i < n; ++i) {
                 auto* e = sh->map.find(keys[i]);
@@ -147,15 +161,23 @@ public:
     Status push_shard(int s, const int64_t* keys, const float* grads, size_t n, const OptConfig& opt, bool sync) {
         Shard* sh = get(s);
         if (!sh) return Status::InvalidID("shard " + std::to_string(s) + " is not local");
+        if (sync && !cfg_.sync_delta) return Status::InvalidConfig("table was created without sync_delta");
         std::unique_lock<std::shared_mutex> g(sh->mu);
         for (size_t i = 0; i < n; ++i) {
             uint32_t row;
+            const float* gr = grads + i * cfg_.dim;
             Status st = find_or_insert(*sh, keys[i], &row);
+            if (st.is(StatusCode::OUT_OF_MEMORY)) {
+                // A request is applied as a whole or not at all (a client that is told OUT_OF_MEMORY sends it again,
+                // and what had been applied would then count twice): items that find no room are parked, the
+                // request succeeds, and the table - unhealthy from now on - refuses the NEXT requests up front.
+                sh->overflow.push_back(typename Shard::Parked{keys[i], std::vector<float>(gr, gr + cfg_.dim), opt, sync});
+                ++n_parked_;
+                continue;
+            }
             if (!st.ok()) return st;
             float* w = sh->rows.data() + (size_t)row * stride_;
-            const float* gr = grads + i * cfg_.dim;
             if (sync) {
-                if (!cfg_.sync_delta) return Status::InvalidConfig("table was created without sync_delta");
                 float* delta = w + (size_t)(n_slots_ + 1) * cfg_.dim;
                 for (uint32_t d = 0; d < cfg_.dim; ++d) delta[d] += gr[d];
                 if (!sh->touched_flag[row]) { sh->touched_flag[row] = 1; sh->touched.push_back(row); }
@@ -299,7 +321,67 @@ public:
             }
             if (fits || free_rows || b < failed_at_bytes_) healthy_ = true;
         }
+        if (healthy_ && n_parked_) drain_overflow();
         return healthy_;
+    }
+    // Items parked by pushes that found no room.
+    uint64_t overflow_size() const { return n_parked_; }
+    // The parked items of shard `s` as full rows - initial value with the parked gradients applied in their order: a
+    // reshard sends them to the shard's new owners together with its stored rows. The list itself stays (it goes
+    // with the old storage when the reshard commits, and is still needed when the reshard is abandoned).
+    void overflow_rows(int s, std::vector<int64_t>* keys, std::vector<float>* rows) const {
+        Shard* sh = get(s);
+        if (!sh) return;
+        std::shared_lock<std::shared_mutex> g(sh->mu);
+        EasyHashMap<int64_t, uint32_t> at(kHostEmptyKey, sh->overflow.size());
+        for (auto& it : sh->overflow) {
+            auto r = at.try_emplace(it.key, (uint32_t)keys->size());
+            if (r.second) {
+                keys->push_back(it.key);
+                rows->resize(rows->size() + stride_);
+                float* fresh = rows->data() + (size_t)r.first->second * stride_;
+                // the key may have got a row since (a push after the table had recovered, before the list was
+                // drained): the parked gradients then go on top of that row, which this record will overwrite
+                if (auto* have = sh->map.find(it.key)) std::copy_n(sh->rows.data() + (size_t)have->second * stride_, stride_, fresh);
+                else init_row(fresh, it.key);
+            }
+            float* w = rows->data() + (size_t)r.first->second * stride_;
+            if (it.sync) {
+                float* delta = w + (size_t)(n_slots_ + 1) * cfg_.dim;
+                for (uint32_t d = 0; d < cfg_.dim; ++d) delta[d] += it.grad[d];
+            } else {
+                apply(it.opt, w, it.grad.data());
+            }
+        }
+    }
+    // Apply the parked items now (after memory came back: the monitor, a purge, raised limits). Items that still find
+    // no room stay parked. Returns how many are left.
+    uint64_t drain_overflow() {
+        for (int s : shard_list()) {
+            Shard* sh = get(s);
+            if (!sh) continue;
+            std::unique_lock<std::shared_mutex> g(sh->mu);
+            std::vector<typename Shard::Parked> still;
+            for (auto& it : sh->overflow) {
+                uint32_t row;
+                if (!still.empty() || !find_or_insert(*sh, it.key, &row).ok()) {   // keep the order of what is left
+                    still.push_back(std::move(it));
+                    continue;
+                }
+                float* w = sh->rows.data() + (size_t)row * stride_;
+                if (it.sync) {
+                    float* delta = w + (size_t)(n_slots_ + 1) * cfg_.dim;
+                    for (uint32_t d = 0; d < cfg_.dim; ++d) delta[d] += it.grad[d];
+                    if (!sh->touched_flag[row]) { sh->touched_flag[row] = 1; sh->touched.push_back(row); }
+                } else {
+                    apply(it.opt, w, it.grad.data());
+                    if (track_dirty_) sh->dirty[row] = 1;
+                }
+                --n_parked_;
+            }
+            sh->overflow.swap(still);
+        }
+        return n_parked_;
     }
     void enable_dirty_tracking() { track_dirty_ = true; }
     void clear_dirty() {
@@ -317,8 +399,10 @@ public:
             sh->map.clear();
             std::vector<float>().swap(sh->rows);
             sh->free_rows.clear(); sh->touched.clear(); sh->touched_flag.clear(); sh->dirty.clear();
+            sh->overflow.clear();
         }
         n_items_ = 0;
+        n_parked_ = 0;
         healthy_ = true;
     }
 
@@ -384,6 +468,7 @@ private:
     std::atomic<uint64_t> n_items_{0};
     std::atomic<uint64_t> bytes_{0};
     std::atomic<bool> healthy_{true};
+    std::atomic<uint64_t> n_parked_{0};
     std::atomic<uint64_t> failed_extra_{0}, failed_at_bytes_{0};   // the growth that made the table unhealthy
     std::atomic<bool> track_dirty_{false};   // may be switched on while pushes run (a follower table appears)
 };

@@ -49,6 +49,10 @@ public:
     virtual bool healthy() = 0;
     virtual void set_healthy(bool h) = 0;
     virtual bool check_healthy() = 0;   // re-evaluate the flag against the limits (the server's monitor calls it)
+    // Pushed items that found no room and wait for memory (host storage only; a GPU table refuses the whole launch).
+    virtual uint64_t overflow_size() { return 0; }
+    virtual uint64_t drain_overflow() { return 0; }
+    virtual void overflow_rows(int /*shard*/, std::vector<int64_t>* /*keys*/, std::vector<float>* /*rows*/) {}
     virtual void set_limits(uint64_t soft, uint64_t hard) = 0;
     virtual void enable_dirty_tracking() = 0;
     virtual void clear_dirty() = 0;
@@ -94,6 +98,9 @@ public:
     bool healthy() override { return t_.healthy(); }
     void set_healthy(bool h) override { t_.set_healthy(h); }
     bool check_healthy() override { return t_.check_healthy(); }
+    uint64_t overflow_size() override { return t_.overflow_size(); }
+    uint64_t drain_overflow() override { return t_.drain_overflow(); }
+    void overflow_rows(int s, std::vector<int64_t>* keys, std::vector<float>* rows) override { t_.overflow_rows(s, keys, rows); }
     void set_limits(uint64_t soft, uint64_t hard) override { t_.set_limits(soft, hard); }
     void enable_dirty_tracking() override { t_.enable_dirty_tracking(); }
     void clear_dirty() override { t_.clear_dirty(); }

@@ -165,3 +165,27 @@ def test_health_comes_back_when_there_is_room_again():
     # and a table pushed over a limit that was lowered afterwards is marked without waiting for a failed insert
     t.table.set_limits(1024, 1024)
     assert not t.table.check_healthy() and not t.table.healthy()
+
+
+def test_a_push_that_hits_the_memory_limit_is_applied_exactly_once():
+    """A push is taken as a whole or refused as a whole: items that find no row when the limit is hit are parked (the
+    reference's overflow list), the next requests are refused up front, and the parked items are applied when there
+    is room again - so a client that retries after OUT_OF_MEMORY never counts a gradient twice."""
+    from parameter_server_b200 import StatusError, StatusCode
+    t = SparseTable(64, "sum", n_shards=2, device="cpu", memory_limit_bytes=64 * 1024, init_range=0.0)
+    keys = torch.arange(1000)
+    t._plan_keys = None
+    ones = torch.ones(1000, 64)
+    t.table.push(keys.numpy(), ones.numpy(), t.opt)               # accepted as a whole although only part fits
+    placed, parked = t.size(), t.table.overflow_size()
+    assert 0 < placed < 1000 and placed + parked == 1000 and not t.table.healthy()
+    st = t.table.push(keys.numpy(), ones.numpy(), t.opt)          # refused before anything is applied
+    assert st.code() == StatusCode.OUT_OF_MEMORY and t.table.overflow_size() == parked
+    st, _ = t.table.pull(keys.numpy())                            # pulls of a shard with parked items say so
+    assert st.code() == StatusCode.OUT_OF_MEMORY
+    t.table.set_limits(1 << 22, 1 << 22)                          # room again: the monitor drains the list
+    assert t.table.check_healthy() and t.table.overflow_size() == 0 and t.size() == 1000
+    st = t.table.push(keys.numpy(), ones.numpy(), t.opt)          # the client's retry
+    assert st.ok()
+    rows, found = t.get_rows(keys)
+    assert bool(found.all()) and torch.equal(rows, 2 * ones)      # every gradient exactly once

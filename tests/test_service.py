@@ -398,6 +398,49 @@ def test_monitor_thread_brings_a_table_back_after_rows_were_erased():
         master.stop()
 
 
+def test_scale_out_under_memory_pressure_applies_every_push_exactly_once():
+    """A table fills its node: the push that hits the limit is taken as a whole (what finds no row is parked), later
+    pushes are refused up front and their client waits; an operator moves a shard to a new node; the parked items
+    travel with the shard, the waiting client goes on, and every gradient counts exactly once."""
+    master = S.Master()
+    a = S.Server(master.address())
+    servers = [a]
+    try:
+        client = S.Client(master.address())
+        sid, h = make_table(type("C", (), {"client": client})(), {a.node_id(): [0, 1]}, cfg=op_cfg(memory_limit=64 * 1024))
+        keys = np.arange(6000, dtype=np.int64)
+        ones = np.ones((6000, DIM), np.float32)
+        done = []
+
+        def trainer():
+            push = S.PushHandler(client, sid, h["push"])
+            for _ in range(3):
+                done.append(push.async_push(keys, ones, 60000))
+
+        t = threading.Thread(target=trainer)
+        t.start()
+        deadline = time.time() + 20
+        while time.time() < deadline and client.query_memory_info(a.node_id())[1]:
+            time.sleep(0.02)
+        assert not client.query_memory_info(a.node_id())[1]            # the node is full, the trainer is waiting
+        assert a.storage_size(sid) < 6000
+        b = S.Server(master.address())
+        servers.append(b)
+        admin = S.Client(master.address())
+        assert admin.initialize_storage(sid).ok()
+        st = S.UpdateContextHandler(admin, sid, h["update_ctx"]).update_context(S.nodes_json({a.node_id(): [0], b.node_id(): [1]}))
+        assert st.ok(), st
+        t.join(60)
+        assert not t.is_alive() and len(done) == 3 and all(s.ok() for s in done), done
+        st, rows = S.PullHandler(admin, sid, h["pull_ro"]).pull(keys, 20000, True)
+        assert st.ok() and np.array_equal(rows, 3 * ones), (rows[:, 0].min(), rows[:, 0].max())
+        assert a.storage_size(sid) + b.storage_size(sid) == 6000
+    finally:
+        for s in servers:
+            s.stop()
+        master.stop()
+
+
 def test_controller_placement_resize_and_introspection(tmp_path):
     cl = Cluster(4)
     try:
