@@ -36,7 +36,7 @@ int usage() {
     std::fprintf(stderr,
                  "usage: psb_node master [--threads N]\n"
                  "       psb_node pserver --master HOST:PORT [--restore] [--restore-wait S] [--image-dir DIR] [--image-interval-ms N] [--report-interval S]\n"
-                 "                        [--load-threads N] [--c2s-threads N] [--s2s-threads N] [--sync-master HOST:PORT]\n");
+                 "                        [--load-threads N] [--c2s-threads N] [--s2s-threads N] [--sync-master HOST:PORT] [--hadoop-bin PATH]\n");
     return 2;
 }
 }  // namespace
@@ -61,6 +61,7 @@ int main(int argc, char** argv) {
         else if (a == "--sync-master" && i + 1 < argc) sync_master = argv[++i];
         else if (a == "--restore") restore = true;
         else if (a == "--image-dir" && i + 1 < argc) cfg.local_image_dir = argv[++i];
+        else if (a == "--hadoop-bin" && i + 1 < argc) cfg.hadoop_bin = argv[++i];
         else if (a == "--image-interval-ms") { if (!next(&image_interval_ms)) return usage(); }
         else if (a == "--report-interval") { if (!next(&cfg.report_interval_s)) return usage(); }
         else if (a == "--restore-wait") { if (!next(&cfg.restore_wait_timeout_s)) return usage(); }

@@ -167,6 +167,7 @@ void bind_service(py::module_& m) {
         .def_readwrite("restore_thread_num", &ServerConfig::restore_thread_num)
         .def_readwrite("s2s_timeout_ms", &ServerConfig::s2s_timeout_ms)
         .def_readwrite("local_image_dir", &ServerConfig::local_image_dir)
+        .def_readwrite("hadoop_bin", &ServerConfig::hadoop_bin)
         .def_readwrite("report_interval_s", &ServerConfig::report_interval_s)
         .def_readwrite("restore_wait_timeout_s", &ServerConfig::restore_wait_timeout_s);
     // the sync thread of a server: keeps the follower tables named by push operators ("sync_table") fresh
@@ -226,6 +227,9 @@ void bind_service(py::module_& m) {
             if (e && e->storage) e->storage->set_healthy(h);
         });
 
+    // dump / load paths with a remote scheme (hdfs://...) go through this command (`<bin> fs -cat / -put / -ls ...`)
+    m.def("set_hadoop_bin", &fs::set_hadoop_bin);
+    m.def("hadoop_bin", &fs::hadoop_bin);
     m.def("register_udf", [](const std::string& name, py::function fn) {
         // fn(storage_id: int, node_items: int, param: bytes) -> bytes
         // The registry is a process-wide static that outlives the interpreter, so the reference to the Python

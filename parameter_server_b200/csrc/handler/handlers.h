@@ -492,7 +492,7 @@ public:
         if (st.ok() && drop) {
             std::string dir, format;
             DumpArgs::split_uri(uri, &dir, &format);
-            for (auto& f : list_model_files(dir)) ::remove(f.c_str());
+            for (auto& f : list_model_files(dir)) fs::remove_file(f);
         }
         return st;
     }

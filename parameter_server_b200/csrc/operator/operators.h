@@ -32,6 +32,7 @@
 #include "../common/archive.h"
 #include "../common/compress.h"
 #include "../common/easy_hash_map.h"
+#include "../common/filesystem.h"
 #include "../common/message.h"
 #include "../service/context.h"
 #include "operator.h"
@@ -680,30 +681,10 @@ struct DumpArgs {
     }
 };
 
-inline Status mkdir_p(const std::string& path) {
-    std::string cur;
-    for (size_t i = 0; i <= path.size(); ++i) {
-        if (i == path.size() || path[i] == '/') {
-            if (!cur.empty() && ::mkdir(cur.c_str(), 0777) != 0 && errno != EEXIST)
-                return Status::Error("mkdir " + cur + " failed");
-        }
-        if (i < path.size()) cur += path[i];
-    }
-    return Status::Ok();
-}
+// Local paths or a Hadoop file system behind the `hadoop fs` command: common/filesystem.h.
+inline Status mkdir_p(const std::string& path) { return fs::mkdir_p(path); }
 
-inline std::vector<std::string> list_model_files(const std::string& dir) {
-    std::vector<std::string> out;
-    DIR* d = ::opendir(dir.c_str());
-    if (!d) return out;
-    while (dirent* e = ::readdir(d)) {
-        std::string n = e->d_name;
-        if (n.compare(0, 6, "model_") == 0) out.push_back(dir + "/" + n);
-    }
-    ::closedir(d);
-    std::sort(out.begin(), out.end());
-    return out;
-}
+inline std::vector<std::string> list_model_files(const std::string& dir) { return fs::list(dir, "model_"); }
 
 class DsWriter {
 public:
@@ -735,10 +716,7 @@ public:
         std::vector<uint8_t> out;
         if (comp_ && comp_->enabled()) PSB_RETURN_IF_ERROR(comp_->compress(body_.data(), body_.size(), &out));
         else out.swap(body_);
-        std::ofstream f(path_, std::ios::binary | std::ios::trunc);
-        if (!f) return Status::Error("cannot open " + path_ + " for writing");
-        f.write((const char*)out.data(), (std::streamsize)out.size());
-        return f.good() ? Status::Ok() : Status::Error("write to " + path_ + " failed");
+        return fs::write_file(path_, out);
     }
 
 private:
@@ -752,9 +730,8 @@ private:
 class DsReader {
 public:
     Status open(const std::string& path, const std::string& format, uint32_t stride, const Compressor* comp) {
-        std::ifstream f(path, std::ios::binary);
-        if (!f) return Status::Error("cannot open " + path);
-        std::vector<uint8_t> raw((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+        std::vector<uint8_t> raw;
+        PSB_RETURN_IF_ERROR(fs::read_file(path, &raw));
         if (comp && comp->enabled()) PSB_RETURN_IF_ERROR(comp->decompress(raw.data(), raw.size(), &body_));
         else body_.swap(raw);
         format_ = format;

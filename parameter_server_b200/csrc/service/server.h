@@ -39,6 +39,7 @@ struct ServerConfig {
     // Directory of this host's persistent table images (empty: none). A server in restore mode that finds the image
     // of the node it replaces, with the table's version_uuid, opens it instead of the table's dump.
     std::string local_image_dir;
+    std::string hadoop_bin;       // command behind hdfs:// dump paths ("" = $PSB_HADOOP_BIN, else "hadoop"); process-wide
 };
 
 struct StorageStatisticInfo {
@@ -60,6 +61,7 @@ public:
     Server(const std::string& master_addr, const ServerConfig& cfg = ServerConfig())
         : cfg_(cfg), master_(master_addr), session_(master_addr) {
         register_builtin_operators();
+        if (!cfg_.hadoop_bin.empty()) fs::set_hadoop_bin(cfg_.hadoop_bin);
         s2s_.reset(new RpcServer([this](Bytes&& b, RpcServer::Responder r) { dispatch(std::move(b), r, true); },
                                  cfg_.s2s_thread_num));
         Status st = session_.register_node(PSERVER_S2S_RPC_NAME, s2s_->address(), &node_id_);

@@ -29,6 +29,7 @@ LoadHandler = C.LoadHandler
 UpdateContextHandler = C.UpdateContextHandler
 SyncHandler = C.SyncHandler
 TableSyncer = C.TableSyncer
+set_hadoop_bin = C.set_hadoop_bin
 UDFHandler = C.UDFHandler
 Controller = C.Controller
 OpSpec = C.OpSpec
