@@ -7,10 +7,17 @@ in the binary record codec of ``csrc/operator/operators.h`` (header ``PSB1`` + u
 load into each other. ``load(table, uri)`` re-hashes: the ranks split the files of the directory
 between them, whatever number of nodes wrote them, and route every record to its owner under the
 table's current shard map as NVLink peer copies (pico-ps/operator/LoadOperator.h:87-143).
+
+``uri`` may also name a directory of a Hadoop file system (``hdfs://...``): the files are then staged through a local
+temporary directory and moved with the ``hadoop`` command configured for the service layer
+(``service.set_hadoop_bin`` / ``$PSB_HADOOP_BIN``), the same way the RPC servers reach such paths.
 """
 from __future__ import annotations
 
 import os
+import shutil
+import subprocess
+import tempfile
 from typing import Optional
 
 import numpy as np
@@ -21,6 +28,19 @@ from ..ops.sparse import SparseTable
 from .migrate import PeerInbox, route, stream_to_owners
 
 _MAGIC = b"PSB1"
+_REMOTE = ("hdfs://", "viewfs://", "s3a://", "gs://", "abfs://")
+
+
+def _is_remote(path: str) -> bool:
+    return path.startswith(_REMOTE)
+
+
+def _hadoop(*args: str, capture: bool = False) -> str:
+    from .._lib import C
+    p = subprocess.run([C.hadoop_bin(), "fs", *args], capture_output=capture, text=capture)
+    if p.returncode != 0:
+        raise RuntimeError(f"hadoop fs {' '.join(args)} failed with exit code {p.returncode}")
+    return p.stdout if capture else ""
 
 
 def _record_dtype(stride: int) -> np.dtype:
@@ -29,7 +49,9 @@ def _record_dtype(stride: int) -> np.dtype:
 
 def dump(table: SparseTable, uri: str, file_number: int = 1, batch: int = 1 << 18) -> int:
     """Collective. Returns the number of records this rank wrote."""
-    path = uri.split("?", 1)[0]
+    target = uri.split("?", 1)[0]
+    remote = _is_remote(target)
+    path = tempfile.mkdtemp(prefix="psb_dump_") if remote else target
     os.makedirs(path, exist_ok=True)
     stride = table.table.stride()
     rec = _record_dtype(stride)
@@ -52,6 +74,14 @@ def dump(table: SparseTable, uri: str, file_number: int = 1, batch: int = 1 << 1
                 written += m
     for fh in files:
         fh.close()
+    if remote:
+        try:
+            _hadoop("-mkdir", "-p", target)
+            for f in range(file_number):
+                name = f"model_{table.rank}_{f}"
+                _hadoop("-put", "-f", os.path.join(path, name), f"{target}/{name}")
+        finally:
+            shutil.rmtree(path, ignore_errors=True)
     if table.world > 1:
         dist.barrier(group=table.group)
     return written
@@ -93,8 +123,19 @@ def load(table: SparseTable, uri: str, batch: int = 1 << 18, inbox: Optional[Pee
     the number of records that landed on this rank."""
     path = uri.split("?", 1)[0]
     prefix = "model_" if only_node is None else f"model_{only_node}_"
-    names = sorted(n for n in os.listdir(path) if n.startswith(prefix))
-    mine = [os.path.join(path, n) for n in names[table.rank::table.world]]
+    staged = None
+    if _is_remote(path):
+        listing = _hadoop("-ls", path, capture=True).splitlines()
+        names = sorted(line.rsplit("/", 1)[1] for line in listing if line[:1] in "-d" and "/" in line)
+        names = [n for n in names if n.startswith(prefix)]
+        staged = tempfile.mkdtemp(prefix="psb_load_")
+        mine = []
+        for n in names[table.rank::table.world]:          # every rank fetches only the files it will read
+            _hadoop("-get", f"{path}/{n}", os.path.join(staged, n))
+            mine.append(os.path.join(staged, n))
+    else:
+        names = sorted(n for n in os.listdir(path) if n.startswith(prefix))
+        mine = [os.path.join(path, n) for n in names[table.rank::table.world]]
     # every rank checks its files BEFORE the collective part and the ranks agree on the verdict: a rank that
     # raised alone would leave the others waiting in a collective
     problem = _damaged(mine, table.table.stride())
@@ -108,6 +149,8 @@ def load(table: SparseTable, uri: str, batch: int = 1 << 18, inbox: Optional[Pee
         inbox = inbox or PeerInbox(table, batch)
     got, _ = stream_to_owners(table, _read_batches(mine, table.table.stride(), batch, table.device), owner_dev, inbox,
                               keep_local=True)
+    if staged is not None:
+        shutil.rmtree(staged, ignore_errors=True)
     if table.world > 1:
         dist.barrier(group=table.group)
     return got

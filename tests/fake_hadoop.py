@@ -1,5 +1,5 @@
 #!/usr/bin/env python3
-"""Stand-in for the `hadoop` command in tests: `fake_hadoop.py fs -mkdir -p | -put -f - | -cat | -ls | -rm -f`.
+"""Stand-in for the `hadoop` command in tests: `fake_hadoop.py fs -mkdir -p | -put -f (- | FILE) | -get | -cat | -ls | -rm -f`.
 `hdfs://<anything>/<path>` maps to `$FAKE_HDFS_ROOT/<path>`; every call is appended to `$FAKE_HDFS_ROOT/calls.log`,
 so a test can check that the files really went through the command."""
 import os
@@ -23,11 +23,17 @@ def main():
     if op == "-mkdir":
         os.makedirs(local(rest[0]), exist_ok=True)
     elif op == "-put":
-        assert rest[0] == "-"
         dst = local(rest[1])
         with open(dst + ".part", "wb") as f:
-            f.write(sys.stdin.buffer.read())
+            if rest[0] == "-":
+                f.write(sys.stdin.buffer.read())
+            else:
+                with open(rest[0], "rb") as src:
+                    f.write(src.read())
         os.replace(dst + ".part", dst)
+    elif op == "-get":
+        with open(local(rest[0]), "rb") as src, open(rest[1], "wb") as f:
+            f.write(src.read())
     elif op == "-cat":
         with open(local(rest[0]), "rb") as f:
             sys.stdout.buffer.write(f.read())

@@ -64,6 +64,21 @@ def test_dump_load_restore_over_the_hadoop_command(tmp_path, monkeypatch):
         calls = (root / "calls.log").read_text()
         for verb in ("fs -mkdir -p hdfs://", "fs -put -f - hdfs://", "fs -ls hdfs://", "fs -cat hdfs://", "fs -rm -f hdfs://"):
             assert verb in calls, verb
+        # the collective path reaches the same directory: an RPC-server dump loads into a collective table and back
+        import torch
+        from parameter_server_b200 import SparseTable
+        from parameter_server_b200.parallel import checkpoint
+        sid4, h4 = table({ids[0]: [0, 1], ids[1]: [2]}, "")
+        assert S.PushHandler(client, sid4, h4["push"]).async_push(keys, vals).ok()
+        assert S.DumpHandler(client, sid4, h4["dump"]).dump("hdfs://namenode:8020/models/shared", 2)[0].ok()
+        t = SparseTable(DIM, "sum", n_shards=3, init_range=0.0, device="cpu", group="none")
+        assert checkpoint.load(t, "hdfs://namenode:8020/models/shared") == 1200
+        assert np.array_equal(t.pull(torch.from_numpy(keys), insert=False).numpy(), vals)
+        assert checkpoint.dump(t, "hdfs://namenode:8020/models/from_collective", file_number=2) == 1200
+        sid5, h5 = table({ids[0]: [0], ids[1]: [1]}, "")
+        st, n = S.LoadHandler(client, sid5, h5["load"]).load("hdfs://namenode:8020/models/from_collective")
+        assert st.ok() and n == 1200, st
+        assert np.array_equal(S.PullHandler(client, sid5, h5["pull_ro"]).pull(keys)[1], vals)
         # a command that is not there is an error for the caller, not a crash
         S.set_hadoop_bin(str(tmp_path / "no_such_hadoop"))
         st, _ = S.DumpHandler(client, sid, h["dump"]).dump("hdfs://namenode:8020/models/other", 1, 5000)
