@@ -13,6 +13,10 @@
 //       sync thread: rows changed by pushes on tables whose push operator names follower tables ("sync_table") are
 //       shipped to those tables, found through the model registry of that master.
 //
+//   psb_node ctl --master HOST:PORT VERB ...
+//       the controller from the command line: show nodes / a table, create, delete, balance, change the shard or
+//       replica count of a table, add nodes to it, clean up storages without a table, shut a node down.
+//
 // The same objects as the Python bindings: tables with "backend": "gpu" are served by the fused kernels.
 #include <algorithm>
 #include <chrono>
@@ -21,7 +25,9 @@
 #include <cstring>
 #include <string>
 #include <thread>
+#include <vector>
 
+#include "../controller/controller.h"
 #include "../service/master.h"
 #include "../service/server.h"
 #include "../service/table_syncer.h"
@@ -32,9 +38,71 @@ namespace {
 volatile std::sig_atomic_t g_stop = 0;
 void on_signal(int) { g_stop = 1; }
 
+// psb_node ctl --master HOST:PORT <verb> [args]: the controller from the command line. JSON answers go to stdout.
+int ctl_usage() {
+    std::fprintf(stderr,
+                 "usage: psb_node ctl --master HOST:PORT VERB ...\n"
+                 "  nodes | node ID | table SID | clean | shutdown NODE | delete SID | balance SID\n"
+                 "  shards SID N | replicas SID N | expand SID SHARDS_PER_NODE NODE [NODE ...]\n"
+                 "  create NAME SHARDS REPLICAS OP_CONFIG_JSON [TABLE_URI]   (prints storage_id=N)\n");
+    return 2;
+}
+int ctl_main(int argc, char** argv) {
+    std::string master;
+    std::vector<std::string> a;
+    for (int i = 2; i < argc; ++i) {
+        if (std::string(argv[i]) == "--master" && i + 1 < argc) master = argv[++i];
+        else a.push_back(argv[i]);
+    }
+    if (master.empty() || a.empty()) return ctl_usage();
+    try {
+        Controller ctl(master);
+        const std::string& verb = a[0];
+        auto num = [&](size_t i) { return std::atoi(a.at(i).c_str()); };
+        Status st;
+        Json out;
+        bool has_out = false;
+        if (verb == "nodes") { st = ctl.show_nodes(&out); has_out = true; }
+        else if (verb == "node" && a.size() == 2) { st = ctl.show_node(num(1), &out); has_out = true; }
+        else if (verb == "table" && a.size() == 2) { st = ctl.gen_table_json(num(1), &out); has_out = true; }
+        else if (verb == "clean") {
+            int removed = 0;
+            st = ctl.clean_unused_storage(&removed);
+            if (st.ok()) std::printf("removed=%d\n", removed);
+        }
+        else if (verb == "shutdown" && a.size() == 2) st = ctl.shutdown_node(num(1));
+        else if (verb == "delete" && a.size() == 2) st = ctl.delete_table(num(1));
+        else if (verb == "balance" && a.size() == 2) st = ctl.balance_table(num(1));
+        else if (verb == "shards" && a.size() == 3) st = ctl.update_table_shard(num(1), num(2));
+        else if (verb == "replicas" && a.size() == 3) st = ctl.update_table_replica(num(1), num(2));
+        else if (verb == "expand" && a.size() >= 4) {
+            std::vector<int> nodes;
+            for (size_t i = 3; i < a.size(); ++i) nodes.push_back(num(i));
+            st = ctl.expand_storage_nodes(num(1), nodes, num(2));
+        }
+        else if (verb == "create" && (a.size() == 5 || a.size() == 6)) {
+            int32_t sid = -1;
+            st = ctl.create_table(a[1], "psb", "SparseTableStorageOperator", a[4], num(2), num(3), Controller::standard_ops(),
+                                  a.size() == 6 ? a[5] : "", &sid);
+            if (st.ok()) std::printf("storage_id=%d\n", sid);
+        }
+        else return ctl_usage();
+        if (!st.ok()) {
+            std::fprintf(stderr, "psb_node ctl: %s\n", st.to_string().c_str());
+            return 1;
+        }
+        if (has_out) std::printf("%s\n", out.dump().c_str());
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "psb_node ctl: %s\n", e.what());
+        return 1;
+    }
+    return 0;
+}
+
 int usage() {
     std::fprintf(stderr,
                  "usage: psb_node master [--threads N]\n"
+                 "       psb_node ctl --master HOST:PORT VERB ...   (the controller; `psb_node ctl` lists the verbs)\n"
                  "       psb_node pserver --master HOST:PORT [--restore] [--restore-wait S] [--image-dir DIR] [--image-interval-ms N] [--report-interval S]\n"
                  "                        [--load-threads N] [--c2s-threads N] [--s2s-threads N] [--sync-master HOST:PORT] [--hadoop-bin PATH]\n");
     return 2;
@@ -46,6 +114,7 @@ int main(int argc, char** argv) {
     std::signal(SIGINT, on_signal);
     std::signal(SIGTERM, on_signal);
     const std::string role = argv[1];
+    if (role == "ctl") return ctl_main(argc, argv);
     std::string master_addr, sync_master;
     bool restore = false;
     int threads = 4, image_interval_ms = 0;

@@ -25,6 +25,20 @@ public:
     explicit Controller(const std::string& master_addr) : client_(master_addr), rng_(std::random_device{}()) {}
     Client& client() { return client_; }
 
+    // The usual operator set of a sparse table, under the keys that the tools look handlers up by.
+    static std::vector<OpSpec> standard_ops(const std::string& compress = "", int block_size = 1000) {
+        const std::string c = "{\"compress_algorithm\":\"" + compress + "\",\"block_size\":" + std::to_string(block_size) + "}";
+        return {{"pull", "psb", "SparseTablePullOperator", "{}"},
+                {"pull_ro", "psb", "SparseTablePullOperator", "{\"read_only\":true}"},
+                {"push", "psb", "SparseTablePushOperator", "{}"},
+                {"for_each", "psb", "ForEachOperator", "{}"},
+                {"erase_if", "psb", "EraseIfOperator", "{}"},
+                {"dump", "psb", "DumpOperator", c},
+                {"load", "psb", "LoadOperator", c},
+                {"update_ctx", "psb", "ShardUpdateContextOperator", "{}"},
+                {"sync", "psb", "KVSyncOperator", c}};
+    }
+
     Status load_nodes(std::vector<int>* nodes) {
         std::map<int32_t, std::string> m;
         PSB_RETURN_IF_ERROR(client_.get_pserver_list(&m));

@@ -117,3 +117,62 @@ def test_planned_shutdown_leaves_an_image_that_a_replacement_opens(tmp_path):
         for p in procs:
             if p.poll() is None:
                 p.kill()
+
+
+def _ctl(addr, *args):
+    p = subprocess.run([NODE, "ctl", "--master", addr, *args], capture_output=True, text=True, timeout=60)
+    return p.returncode, p.stdout.strip(), p.stderr.strip()
+
+
+@pytest.mark.skipif(not os.path.exists(NODE), reason="psb_node is not built")
+def test_controller_from_the_command_line():
+    """`psb_node ctl`: create a table on native servers, look at it, resize it, add a node, clean up, shut down."""
+    master = _spawn("master")
+    procs = [master]
+    try:
+        addr = _first_line(master)
+        servers = [_spawn("pserver", "--master", addr) for _ in range(2)]
+        procs += servers
+        ids = [int(_first_line(p).split("node_id=")[1].split()[0]) for p in servers]
+        rc, out, err = _ctl(addr, "nodes")
+        assert rc == 0 and sorted(n["node_id"] for n in json.loads(out)) == sorted(ids), (out, err)
+        rc, out, err = _ctl(addr, "create", "emb", "4", "2", json.dumps(dict(dim=4, optimizer="sum", init_range=0.0)))
+        assert rc == 0 and out.startswith("storage_id="), (out, err)
+        sid = int(out.split("=")[1])
+        client = S.Client(addr)
+        assert client.initialize_storage(sid).ok()
+        push = S.PushHandler(client, sid, client.handler_by_key(sid, "push")[1])
+        pull = S.PullHandler(client, sid, client.handler_by_key(sid, "pull_ro")[1])
+        keys = np.arange(900, dtype=np.int64)
+        vals = ((keys[:, None] % 5 + 1) * np.ones((1, 4))).astype(np.float32)
+        assert push.async_push(keys, vals).ok()
+        rc, out, err = _ctl(addr, "table", str(sid))
+        table = json.loads(out)
+        assert rc == 0 and len(table["shards"]) == 8 and sum(s["item_number"] for s in table["shards"]) == 1800   # 4 shards x 2 replicas
+        assert _ctl(addr, "shards", str(sid), "6")[0] == 0
+        assert _ctl(addr, "replicas", str(sid), "1")[0] == 0
+        table = json.loads(_ctl(addr, "table", str(sid))[1])
+        assert len(table["shards"]) == 6 and sum(s["item_number"] for s in table["shards"]) == 900
+        extra = _spawn("pserver", "--master", addr)
+        procs.append(extra)
+        new_id = int(_first_line(extra).split("node_id=")[1].split()[0])
+        assert _ctl(addr, "expand", str(sid), "2", str(new_id))[0] == 0
+        assert _ctl(addr, "balance", str(sid))[0] == 0
+        st, rows = pull.pull(keys, 20000, True)
+        assert st.ok() and np.array_equal(rows, vals)
+        rc, out, err = _ctl(addr, "node", str(new_id))
+        assert rc == 0 and json.loads(out)["alive"], (out, err)
+        assert _ctl(addr, "table", "4242")[0] == 1                      # an unknown table is an error, with a message
+        assert _ctl(addr, "bogus")[0] == 2
+        assert _ctl(addr, "delete", str(sid))[0] == 0
+        assert _ctl(addr, "clean")[0] == 0
+        for n in ids + [new_id]:
+            assert _ctl(addr, "shutdown", str(n))[0] == 0
+        for p in servers + [extra]:
+            assert p.wait(timeout=15) == 0
+        master.send_signal(signal.SIGTERM)
+        assert master.wait(timeout=15) == 0
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
