@@ -11,7 +11,8 @@
 //       opens the image of the node it replaces when no live replica has the shards; --image-interval-ms N also
 //       refreshes the images every N ms while serving. With --sync-master it runs the
 //       sync thread: rows changed by pushes on tables whose push operator names follower tables ("sync_table") are
-//       shipped to those tables, found through the model registry of that master.
+//       shipped to those tables, found through the model registry of that master. With --metrics-port P it serves
+//       the Prometheus text of its request series on GET /metrics (P = 0: any free port, printed as "metrics port=N").
 //
 //   psb_node ctl --master HOST:PORT VERB ...
 //       the controller from the command line: show nodes / a table, create, delete, balance, change the shard or
@@ -29,6 +30,7 @@
 
 #include "../controller/controller.h"
 #include "../service/master.h"
+#include "../service/metrics_http.h"
 #include "../service/server.h"
 #include "../service/table_syncer.h"
 
@@ -104,7 +106,8 @@ int usage() {
                  "usage: psb_node master [--threads N]\n"
                  "       psb_node ctl --master HOST:PORT VERB ...   (the controller; `psb_node ctl` lists the verbs)\n"
                  "       psb_node pserver --master HOST:PORT [--restore] [--restore-wait S] [--image-dir DIR] [--image-interval-ms N] [--report-interval S]\n"
-                 "                        [--load-threads N] [--c2s-threads N] [--s2s-threads N] [--sync-master HOST:PORT] [--hadoop-bin PATH]\n");
+                 "                        [--load-threads N] [--c2s-threads N] [--s2s-threads N] [--sync-master HOST:PORT] [--hadoop-bin PATH]\n"
+                 "                        [--metrics-port P]\n");
     return 2;
 }
 }  // namespace
@@ -117,7 +120,7 @@ int main(int argc, char** argv) {
     if (role == "ctl") return ctl_main(argc, argv);
     std::string master_addr, sync_master;
     bool restore = false;
-    int threads = 4, image_interval_ms = 0;
+    int threads = 4, image_interval_ms = 0, metrics_port = -1;
     ServerConfig cfg;
     for (int i = 2; i < argc; ++i) {
         const std::string a = argv[i];
@@ -131,6 +134,7 @@ int main(int argc, char** argv) {
         else if (a == "--restore") restore = true;
         else if (a == "--image-dir" && i + 1 < argc) cfg.local_image_dir = argv[++i];
         else if (a == "--hadoop-bin" && i + 1 < argc) cfg.hadoop_bin = argv[++i];
+        else if (a == "--metrics-port") { if (!next(&metrics_port)) return usage(); }
         else if (a == "--image-interval-ms") { if (!next(&image_interval_ms)) return usage(); }
         else if (a == "--report-interval") { if (!next(&cfg.report_interval_s)) return usage(); }
         else if (a == "--restore-wait") { if (!next(&cfg.restore_wait_timeout_s)) return usage(); }
@@ -153,6 +157,13 @@ int main(int argc, char** argv) {
         Server server(master_addr, cfg);
         std::printf("pserver node_id=%d c2s=%s s2s=%s\n", server.node_id(), server.c2s_address().c_str(), server.s2s_address().c_str());
         std::fflush(stdout);
+        // Prometheus endpoint of this server's request series (GET /metrics); port 0 = any free port, printed below
+        std::unique_ptr<MetricsHttpServer> metrics;
+        if (metrics_port >= 0) {
+            metrics.reset(new MetricsHttpServer(metrics_port, [&server] { return server.metrics_text(); }));
+            std::printf("metrics port=%d\n", metrics->port());
+            std::fflush(stdout);
+        }
         // tables whose push operator names follower tables are mirrored to them in the background; the followers
         // live in the cluster of `--sync-master` (which may be this server's own master)
         std::unique_ptr<TableSyncer> syncer;
@@ -178,6 +189,7 @@ int main(int argc, char** argv) {
                 last_image = std::chrono::steady_clock::now();
             }
         }
+        if (metrics) metrics->stop();
         if (syncer) {
             syncer->wait_idle(5000);   // what the last pushes changed still goes out
             syncer->stop();

@@ -176,3 +176,39 @@ def test_controller_from_the_command_line():
         for p in procs:
             if p.poll() is None:
                 p.kill()
+
+
+@pytest.mark.skipif(not os.path.exists(NODE), reason="psb_node is not built")
+def test_native_server_exports_prometheus_metrics():
+    import urllib.error
+    import urllib.request
+    master = _spawn("master")
+    procs = [master]
+    try:
+        addr = _first_line(master)
+        server = _spawn("pserver", "--master", addr, "--metrics-port", "0")
+        procs.append(server)
+        node = int(_first_line(server).split("node_id=")[1].split()[0])
+        port = int(_first_line(server).split("metrics port=")[1])
+        client = S.Client(addr)
+        st, sid = client.create_storage(S.LIB, "SparseTableStorageOperator",
+                                        S.storage_config({node: [0]}, dict(dim=4, optimizer="sum", init_range=0.0)))
+        assert st.ok()
+        _, h_push = client.register_handler("push", S.LIB, "SparseTablePushOperator", "{}", sid)
+        keys = np.arange(100, dtype=np.int64)
+        for _ in range(3):
+            assert S.PushHandler(client, sid, h_push).async_push(keys, np.ones((100, 4), np.float32)).ok()
+        text = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5).read().decode()
+        assert f'ps_requests_total{{node_id="{node}",request_type="c2s_OP_PUSH_ASYNC",storage_id="{sid}"}} 3' in text
+        assert "ps_request_duration_ms_bucket" in text
+        with pytest.raises(urllib.error.HTTPError) as ei:
+            urllib.request.urlopen(f"http://127.0.0.1:{port}/other", timeout=5)
+        assert ei.value.code == 404
+        client.close_pserver(node)
+        assert server.wait(timeout=15) == 0
+        master.send_signal(signal.SIGTERM)
+        assert master.wait(timeout=15) == 0
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
