@@ -107,7 +107,7 @@ int usage() {
                  "       psb_node ctl --master HOST:PORT VERB ...   (the controller; `psb_node ctl` lists the verbs)\n"
                  "       psb_node pserver --master HOST:PORT [--restore] [--restore-wait S] [--image-dir DIR] [--image-interval-ms N] [--report-interval S]\n"
                  "                        [--load-threads N] [--c2s-threads N] [--s2s-threads N] [--sync-master HOST:PORT] [--hadoop-bin PATH]\n"
-                 "                        [--metrics-port P]\n");
+                 "                        [--metrics-port P] [--log-level debug|info|warning|error|off]\n");
     return 2;
 }
 }  // namespace
@@ -134,6 +134,7 @@ int main(int argc, char** argv) {
         else if (a == "--restore") restore = true;
         else if (a == "--image-dir" && i + 1 < argc) cfg.local_image_dir = argv[++i];
         else if (a == "--hadoop-bin" && i + 1 < argc) cfg.hadoop_bin = argv[++i];
+        else if (a == "--log-level" && i + 1 < argc) set_log_level(log_detail::parse(argv[++i], LogLevel::WARNING));
         else if (a == "--metrics-port") { if (!next(&metrics_port)) return usage(); }
         else if (a == "--image-interval-ms") { if (!next(&image_interval_ms)) return usage(); }
         else if (a == "--report-interval") { if (!next(&cfg.report_interval_s)) return usage(); }

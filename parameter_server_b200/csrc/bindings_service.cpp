@@ -29,6 +29,8 @@ py::dict metrics_dict(Handler& h) {
     d["retries"] = (uint64_t)h.metrics().retries;
     d["errors"] = (uint64_t)h.metrics().errors;
     d["wait_us"] = (uint64_t)h.metrics().wait_us;
+    d["sends"] = (uint64_t)h.metrics().sends;
+    d["send_us"] = (uint64_t)h.metrics().send_us;
     return d;
 }
 }  // namespace
@@ -227,6 +229,27 @@ void bind_service(py::module_& m) {
             if (e && e->storage) e->storage->set_healthy(h);
         });
 
+    // logging of the host runtime: level by name ("debug", "info", "warning", "error", "off"); lines go to stderr or,
+    // with a sink, to a Python callable (level: int, message: str) - e.g. a forwarder into the `logging` module
+    m.def("set_log_level", [](const std::string& name) { set_log_level(log_detail::parse(name.c_str(), LogLevel::WARNING)); });
+    m.def("log_level", [] { return (int)log_level(); });
+    m.def("set_log_sink", [](py::object fn) {
+        if (fn.is_none()) {
+            set_log_sink(nullptr);
+            return;
+        }
+        // like the UDF registry: the sink is a process-wide static, the reference to the callable is never dropped
+        std::shared_ptr<py::object> holder(new py::object(std::move(fn)), [](py::object*) {});
+        set_log_sink([holder](LogLevel l, const std::string& msg) {
+            if (!Py_IsInitialized()) return;
+            py::gil_scoped_acquire gil;
+            try {
+                (*holder)((int)l, msg);
+            } catch (const std::exception&) {
+                // a failing sink must not take the serving thread along
+            }
+        });
+    });
     // dump / load paths with a remote scheme (hdfs://...) go through this command (`<bin> fs -cat / -put / -ls ...`)
     m.def("set_hadoop_bin", &fs::set_hadoop_bin);
     m.def("hadoop_bin", &fs::hadoop_bin);

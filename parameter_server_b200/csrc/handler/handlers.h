@@ -22,6 +22,9 @@ namespace psb {
 struct HandlerMetrics {
     std::atomic<uint64_t> requests{0}, retries{0}, errors{0};
     std::atomic<uint64_t> wait_us{0};
+    // pulls only: requests built (dedup, partition, serialisation) and the time that took - the send side of a pull,
+    // ps_pull_send_request_count / ps_pull_send_duration_ms of the reference (pico-ps/handler/PullHandler.cpp:11-15)
+    std::atomic<uint64_t> sends{0}, send_us{0};
 };
 
 // Every request carries the context version it was BUILT under (read under the same lock as the placement it was
@@ -138,12 +141,15 @@ public:
             PullRequestData data;
             NodeRequests reqs;
             int32_t built_under = -1;
+            const auto b0 = std::chrono::steady_clock::now();
             {
                 std::shared_lock<std::shared_mutex> g(e->mu);
                 built_under = e->td.version;
                 p->generate_request_data(*e, keys, n, &data);
                 PSB_RETURN_IF_ERROR(p->generate_requests(*e, data, &reqs));
             }
+            ++metrics_.sends;
+            metrics_.send_us += (uint64_t)std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - b0).count();
             std::vector<NodeResponse> rs;
             PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_PULL, reqs.body, left, &rs, built_under));
             for (auto& r : rs) PSB_RETURN_IF_ERROR(p->apply_response(*e, &data, r.body));
@@ -189,24 +195,30 @@ private:
             g.bcast.wait(tid_);  // the owner of the merged request fills our rows and status
             st = g.status[tid_];
         } else {
-            std::vector<PullRequestData*> ds;
+            std::vector<PullRequestData*> all;
             for (int t = 0; t < kThreadGroupSize; ++t)
-                if ((tids >> t) & 1u) ds.push_back(&g.data[t]);
-            st = [&]() -> Status {
-                NodeRequests reqs;
-                int32_t built_under = -1;
-                {
-                    std::shared_lock<std::shared_mutex> lk(e->mu);
-                    built_under = e->td.version;
-                    PSB_RETURN_IF_ERROR(p.generate_merged_requests(*e, ds, &reqs));
-                }
-                std::vector<NodeResponse> rs;
-                PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_PULL, reqs.body, left, &rs, built_under));
-                for (auto& r : rs) PSB_RETURN_IF_ERROR(p.apply_merged_response(*e, ds, r.body));
-                return Status::Ok();
-            }();
-            ++g.merged_sends;
-            g.merged_requests += ds.size();
+                if ((tids >> t) & 1u) all.push_back(&g.data[t]);
+            // one message carries at most max_request_merge_num requests; what was claimed beyond that goes out in
+            // further messages of the same size
+            const size_t cap = (size_t)p.max_request_merge_num();
+            for (size_t lo = 0; lo < all.size() && st.ok(); lo += cap) {
+                std::vector<PullRequestData*> ds(all.begin() + lo, all.begin() + std::min(all.size(), lo + cap));
+                st = [&]() -> Status {
+                    NodeRequests reqs;
+                    int32_t built_under = -1;
+                    {
+                        std::shared_lock<std::shared_mutex> lk(e->mu);
+                        built_under = e->td.version;
+                        PSB_RETURN_IF_ERROR(p.generate_merged_requests(*e, ds, &reqs));
+                    }
+                    std::vector<NodeResponse> rs;
+                    PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_PULL, reqs.body, left, &rs, built_under));
+                    for (auto& r : rs) PSB_RETURN_IF_ERROR(p.apply_merged_response(*e, ds, r.body));
+                    return Status::Ok();
+                }();
+                ++g.merged_sends;
+                g.merged_requests += ds.size();
+            }
             for (int t = 0; t < kThreadGroupSize; ++t)
                 if ((tids >> t) & 1u) g.status[t] = st;
             g.bcast.notify(tids, tid_);
@@ -340,7 +352,15 @@ private:
                     members |= 1u << t;
                 }
             if (ds.empty()) continue;
-            Status st = [&]() -> Status {
+            const std::vector<PushRequestData*> all_ds = ds;
+            const std::vector<PushAckState*> all_acks = acks;
+            const size_t cap = (size_t)p.max_request_merge_num();
+            Status st;
+            for (size_t lo = 0; lo < all_ds.size(); lo += cap) {
+            const size_t hi = std::min(all_ds.size(), lo + cap);
+            ds.assign(all_ds.begin() + lo, all_ds.begin() + hi);
+            acks.assign(all_acks.begin() + lo, all_acks.begin() + hi);
+            Status part = [&]() -> Status {
                 NodeRequests reqs;
                 std::vector<std::vector<std::pair<int, int32_t>>> sent;
                 int32_t built_under = -1;
@@ -360,6 +380,8 @@ private:
             }();
             ++g.merged_sends;
             g.merged_requests += ds.size();
+            if (!part.ok() && st.ok()) st = part;   // every member retries; what its nodes acknowledged is not resent
+            }
             for (int t = 0; t < kThreadGroupSize; ++t)
                 if ((members >> t) & 1u) g.status[t] = st;
         }

@@ -94,6 +94,9 @@ public:
         h.slot_init0 = opt_.slot_init0;
         h.slot_init1 = opt_.slot_init1;
         h.soft_limit_bytes = h.hard_limit_bytes = (uint64_t)config_.at("memory_limit").as_int(0);
+        // "expected_max_items": N, or the reference's spelling "pool_hash_map": {"expected_max_items": N}
+        h.expected_max_items = (uint64_t)std::max<int64_t>(0, config_.at("expected_max_items").as_int(
+            config_.at("pool_hash_map").at("expected_max_items").as_int(0)));
         return h;
     }
     // Server side: build the storage and create the local shards.
@@ -144,9 +147,19 @@ struct PullRequestData {
 
 class SparseTablePullOperator : public Operator {
 public:
-    explicit SparseTablePullOperator(const Json& c) : Operator(c) { read_only_ = c.at("read_only").as_bool(false); }
+    explicit SparseTablePullOperator(const Json& c) : Operator(c) {
+        read_only_ = c.at("read_only").as_bool(false);
+        // how a replica is picked for a shard: uniformly at random per request, the only policy there is
+        // (`node_selection`, pico-ps/service/Context.cpp:176-192)
+        if (c.has("node_selection") && c.at("node_selection").as_string() != "random")
+            throw std::runtime_error("node_selection: only \"random\" is supported");
+        max_merge_ = (int)std::max<int64_t>(1, c.at("max_request_merge_num").as_int(32));
+    }
     const char* kind() const override { return "pull"; }
     bool read_only() const { return read_only_; }
+    // how many requests of sibling threads one message may carry (`max_request_merge_num`,
+    // pico-ps/operator/SparsePullOperator.h:71-73); 1 switches merging off
+    int max_request_merge_num() const { return max_merge_; }
 
     // ---- client ----
     // dedup + partition (HOT LOOP A of the reference)
@@ -301,6 +314,7 @@ public:
 
 private:
     bool read_only_ = false;
+    int max_merge_ = 32;
 };
 
 // ---------------------------------------------------------------------------------------------------
@@ -350,7 +364,9 @@ public:
         if (c.has("sync_table"))
             for (auto& t : c.at("sync_table").elements())
                 sync_tables_.push_back({t.at("model_name").as_string(), t.at("table_name").as_string(), t.at("op_key").as_string()});
+        max_merge_ = (int)std::max<int64_t>(1, c.at("max_request_merge_num").as_int(32));
     }
+    int max_request_merge_num() const { return max_merge_; }   // see SparseTablePullOperator
     struct SyncTarget {
         std::string model_name, table_name, op_key;
     };
@@ -497,6 +513,7 @@ private:
     bool has_opt_ = false;
     OptConfig opt_;
     std::vector<SyncTarget> sync_tables_;
+    int max_merge_ = 32;
 };
 
 // ---------------------------------------------------------------------------------------------------

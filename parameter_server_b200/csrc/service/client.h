@@ -16,6 +16,7 @@
 #include "../operator/operators.h"
 #include "context.h"
 #include "master.h"
+#include "../common/log.h"
 #include "server.h"
 
 namespace psb {
@@ -370,12 +371,14 @@ public:
                 e->rt.build(e->td, -1);
             }
             if (changed) {
+                PSB_LOG(WARNING) << "storage " << sid << ": nodes that left the registry are marked DEAD, context version " << e->td.version;
                 PSB_RETURN_IF_ERROR(master_.set_context(ctx_key(sid), e->td.to_json_str()));
                 require_update_ctx_nolock(sid, nodes);
             }
             for (auto& kv : live) {
                 if (!nodes.count(kv.first)) continue;
                 if (!health_check(kv.first, 1000).ok()) {
+                    PSB_LOG(WARNING) << "storage " << sid << ": node " << kv.first << " is registered but does not answer, avoiding it";
                     std::unique_lock<std::shared_mutex> g(e->mu);
                     e->td.mark_node(kv.first, NodeStatus::UNAVAILABLE);
                     e->rt.build(e->td, -1);
@@ -399,6 +402,7 @@ public:
         int32_t v0 = 0, v = 0;
         StorageStatus status;
         snapshot(&v0, &status);
+        PSB_LOG(INFO) << "storage " << sid << ": out of memory or resharding, waiting for a context newer than " << v0;
         double wait_ms = 100;
         auto t0 = std::chrono::steady_clock::now();
         for (;;) {

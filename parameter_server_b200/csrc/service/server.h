@@ -20,6 +20,7 @@
 #include <condition_variable>
 #include <thread>
 
+#include "../common/log.h"
 #include "../operator/operators.h"
 #include "context.h"
 #include "master.h"
@@ -71,6 +72,7 @@ public:
         int32_t same = -1;
         st = session_.register_node(PSERVER_C2S_RPC_NAME, c2s_->address(), &same, node_id_);
         if (!st.ok()) throw std::runtime_error("server: cannot register c2s: " + st.to_string());
+        PSB_LOG(INFO) << "pserver node " << node_id_ << " serves c2s " << c2s_->address() << ", s2s " << s2s_->address();
         if (cfg_.report_interval_s > 0)
             reporter_ = std::thread([this] {
                 // one line per interval on stderr (ServerConfig::report_interval of the reference)
@@ -83,7 +85,11 @@ public:
                         auto e = ctx_.get(sid);
                         if (!e) continue;
                         std::shared_lock<std::shared_mutex> tg(e->mu);
-                        if (e->storage) e->storage->check_healthy();
+                        if (!e->storage) continue;
+                        const bool was = e->storage->healthy();
+                        const bool now = e->storage->check_healthy();
+                        if (was && !now) PSB_LOG(WARNING) << "storage " << sid << " on node " << node_id_ << " is over its memory limit: " << e->storage->memory_usage() << " bytes, new rows are refused";
+                        if (!was && now) PSB_LOG(INFO) << "storage " << sid << " on node " << node_id_ << " has room again";
                     }
                     last_report_ = report_line();
                     std::fprintf(stderr, "%s\n", last_report_.c_str());
@@ -218,7 +224,9 @@ public:
                     rs = fs.ok() ? fs : Status(fs.code(), fs.msg() + " (replica: " + rs.msg() + "; local image: " + li.msg() + ")");
                 }
             }
+            if (!rs.ok()) PSB_LOG(ERROR) << "storage " << sid << ": restore failed: " << rs.to_string();
             PSB_RETURN_IF_ERROR(rs);
+            PSB_LOG(INFO) << "storage " << sid << ": restored from " << source << ", " << e->storage->size() << " items on node " << node_id_;
             {
                 std::lock_guard<std::mutex> g(report_mu_);
                 restore_source_[sid] = source;
@@ -457,6 +465,7 @@ private:
                 std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count());
         resp.send(reply(st, &out, meta));
         if (meta.req_type == RequestType::EXIT && !exited_.exchange(true)) {
+            PSB_LOG(INFO) << "pserver node " << node_id_ << " was asked to leave";
             // stop() joins the worker pools, this thread among them: it runs on a thread of its own, which the
             // destructor joins
             std::lock_guard<std::mutex> g(exit_mu_);
@@ -517,6 +526,7 @@ private:
         const bool committed = had_update && e.td.update_nodes.empty() && e.td.update_version > old_uv;
         if (committed && e.update_storage) {
             e.storage = std::move(e.update_storage);  // the reshuffled data becomes the serving data
+            PSB_LOG(INFO) << "storage " << e.sid << ": reshard committed on node " << node_id_ << ", update version " << e.td.update_version << ", " << e.storage->size() << " items";
             // the rows arrived marked (see process_new_ctx_create_shard): the next sync round re-ships them
             if (e.sync_enabled) e.incr.updated = true;
         } else if (e.storage) {
@@ -630,6 +640,7 @@ private:
                 auto gone = ctx_.get(meta.sid);
                 const bool followed = gone && gone->sync_enabled;
                 ctx_.erase(meta.sid);
+                PSB_LOG(INFO) << "storage " << meta.sid << " deleted on node " << node_id_;
                 if (followed) notify_sync(meta.sid, true);
                 return Status::Ok();
             }
@@ -764,6 +775,7 @@ private:
         std::unique_lock<std::shared_mutex> g(e->mu);
         Status st = ensure_storage(*e);
         if (!st.ok()) ctx_.erase(meta.sid);
+        else PSB_LOG(INFO) << "storage " << meta.sid << " created on node " << node_id_ << " with " << e->rt.local_shards().size() << " local shards";
         return st;
     }
 
@@ -1017,6 +1029,7 @@ private:
             int replaced = -1;
             if (!td.try_to_replace_one_dead_node(node_id_, &replaced)) continue;
             replaced_node_[sid] = replaced;
+            PSB_LOG(INFO) << "storage " << sid << ": node " << node_id_ << " takes the place of dead node " << replaced;
             PSB_RETURN_IF_ERROR(master_.set_context(k, td.to_json_str()));
             std::shared_ptr<TableEntry> e;
             PSB_RETURN_IF_ERROR(ctx_.set_table_descriptor(sid, td.to_json_str(), node_id_, &e));

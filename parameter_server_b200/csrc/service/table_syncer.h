@@ -138,6 +138,7 @@ private:
                 if (!st.ok()) {
                     ++stats_.errors;
                     stats_.last_error = st.to_string();
+                    PSB_LOG(WARNING) << "sync of storage " << sid << " failed, the marks stay for the next round: " << stats_.last_error;
                 }
                 if (gone.count(sid)) {
                     followers_.erase(sid);

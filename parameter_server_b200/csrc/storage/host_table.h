@@ -38,6 +38,10 @@ struct HostTableConfig {
     float slot_init1 = 0.f;
     uint64_t soft_limit_bytes = 0;
     uint64_t hard_limit_bytes = 0;
+    // Expected number of items of the whole table: every new shard sizes its index for its share up front, so that
+    // the index is not rebuilt again and again while the table fills (`pool_hash_map.expected_max_items` of the
+    // reference's default storage, pico-ps/storage/KVShardStorage.h:881-897).
+    uint64_t expected_max_items = 0;
 };
 
 constexpr int64_t kHostEmptyKey = (int64_t)0x8000000000000000ull;
@@ -80,7 +84,13 @@ public:
     // --- shard lifecycle (create_shard / erase_shard of ShardStorage) --------------------------
     void create_shard(int s) {
         std::unique_lock<std::shared_mutex> g(mu_);
-        if (!shards_.count(s)) shards_[s].reset(new Shard());
+        if (!shards_.count(s)) {
+            shards_[s].reset(new Shard());
+            if (cfg_.expected_max_items) {
+                const uint64_t share = cfg_.expected_max_items / (uint64_t)std::max<int32_t>(1, cfg_.n_shards);
+                shards_[s]->map.reserve((size_t)(share + share / 8 + 16));   // shards are not perfectly even
+            }
+        }
     }
     void erase_shard(int s) {
         std::unique_lock<std::shared_mutex> g(mu_);

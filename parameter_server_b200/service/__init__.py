@@ -30,6 +30,16 @@ UpdateContextHandler = C.UpdateContextHandler
 SyncHandler = C.SyncHandler
 TableSyncer = C.TableSyncer
 set_hadoop_bin = C.set_hadoop_bin
+set_log_level = C.set_log_level
+
+
+def log_to_python(logger_name: str = "parameter_server_b200") -> None:
+    """Route the native runtime's log lines into the ``logging`` module (levels map DEBUG..ERROR)."""
+    import logging
+
+    logger = logging.getLogger(logger_name)
+    levels = [logging.DEBUG, logging.INFO, logging.WARNING, logging.ERROR]
+    C.set_log_sink(lambda level, msg: logger.log(levels[min(level, 3)], msg))
 UDFHandler = C.UDFHandler
 Controller = C.Controller
 OpSpec = C.OpSpec

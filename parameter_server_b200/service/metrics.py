@@ -26,10 +26,14 @@ def server_metrics_text(server, storage_ids: Optional[Iterable[int]] = None) -> 
 def handler_metrics_text(handler, name: str) -> str:
     m = handler.metrics()
     lab = f'{{handler="{name}"}}'
-    return (f"ps_wait_request_count{lab} {m['requests']}\n"
+    text = (f"ps_wait_request_count{lab} {m['requests']}\n"
             f"ps_wait_retry_count{lab} {m['retries']}\n"
             f"ps_wait_error_count{lab} {m['errors']}\n"
             f"ps_wait_duration_ms_sum{lab} {m['wait_us'] / 1e3}\n")
+    if m.get("sends"):      # pull handlers: the request-building side (pico-ps/handler/PullHandler.cpp:11-15)
+        text += (f"ps_pull_send_request_count{lab} {m['sends']}\n"
+                 f"ps_pull_send_duration_ms_sum{lab} {m['send_us'] / 1e3}\n")
+    return text
 
 
 def serve_metrics(server, port: int = 0, storage_ids: Optional[Iterable[int]] = None, host: str = "127.0.0.1"):

@@ -189,3 +189,20 @@ def test_a_push_that_hits_the_memory_limit_is_applied_exactly_once():
     assert st.ok()
     rows, found = t.get_rows(keys)
     assert bool(found.all()) and torch.equal(rows, 2 * ones)      # every gradient exactly once
+
+
+def test_expected_max_items_sizes_the_index_up_front():
+    hc = C.HostTableConfig()
+    hc.dim, hc.n_shards = 4, 2
+    small = C.HostTable(hc)
+    hc.expected_max_items = 100_000
+    big = C.HostTable(hc)
+    for t in (small, big):
+        t.create_shard(0)
+    buckets = lambda t: t.export_shard(0, 0, 1 << 30, False)[2]      # the scan cursor ends at the bucket count
+    assert buckets(big) >= 2 * 50_000 and buckets(small) < 1024      # load factor <= 1/2 for the shard's share
+    keys = np.arange(20_000, dtype=np.int64)
+    before = buckets(big)
+    big.create_shard(1)
+    big.set_rows(keys, np.zeros((20_000, 4), np.float32), False)
+    assert buckets(big) == before                                     # filling it did not rebuild the index

@@ -666,6 +666,102 @@ def test_push_requests_of_threads_are_merged(cluster3):
     assert st.ok() and np.array_equal(rows, counts[:, None] * np.ones((1, DIM), dtype=np.float32))
 
 
+@pytest.mark.parametrize("cap", [1, 2])
+def test_max_request_merge_num_caps_what_one_message_carries(cluster3, cap):
+    """`max_request_merge_num` in the operator config: 1 switches the coalescing off (one message per request), 2 lets
+    at most two requests share a message; results and exactly-once application are unaffected."""
+    cl = cluster3
+    sid, h = make_table(cl, uneven(cl.ids()))
+    st, h_pull = cl.client.register_handler("pull_capped", S.LIB, "SparseTablePullOperator",
+                                            json.dumps({"read_only": True, "max_request_merge_num": cap}), sid)
+    assert st.ok()
+    st, h_push = cl.client.register_handler("push_capped", S.LIB, "SparseTablePushOperator",
+                                            json.dumps({"max_request_merge_num": cap}), sid)
+    assert st.ok()
+    T = 4
+    pgroup, qgroup = S.PullGroup(), S.PushGroup()
+    pulls = [S.PullHandler(cl.client, sid, h_pull) for _ in range(T)]
+    pushes = [S.PushHandler(cl.client, sid, h_push) for _ in range(T)]
+    assert [x.join_group(pgroup) for x in pulls] == list(range(T)) and [x.join_group(qgroup) for x in pushes] == list(range(T))
+    rng = np.random.default_rng(2)
+    batches = [[rng.integers(0, 2000, size=150).astype(np.int64) for _ in range(20)] for _ in range(T)]
+    bad = []
+
+    def work(t):
+        for b in batches[t]:
+            if not pushes[t].async_push(b, np.ones((len(b), DIM), dtype=np.float32)).ok():
+                bad.append(("push", t))
+            st, rows = pulls[t].pull(b)
+            if not st.ok() or rows.shape != (len(b), DIM):
+                bad.append(("pull", t))
+
+    ts = [threading.Thread(target=work, args=(t,)) for t in range(T)]
+    [t.start() for t in ts]
+    [t.join(60) for t in ts]
+    assert not bad and not any(t.is_alive() for t in ts)
+    for g in (pgroup, qgroup):
+        assert g.merged_requests() == T * 20
+        assert g.merged_sends() * cap >= g.merged_requests()           # no message carried more than `cap` requests
+        if cap == 1:
+            assert g.merged_sends() == g.merged_requests()
+    counts = np.bincount(np.concatenate([b for bs in batches for b in bs]), minlength=2000).astype(np.float32)
+    st, rows = S.PullHandler(cl.client, sid, h["pull_ro"]).pull(np.arange(2000, dtype=np.int64))
+    assert st.ok() and np.array_equal(rows, counts[:, None] * np.ones((1, DIM), dtype=np.float32))
+
+
+def test_operator_config_keys_of_the_reference_are_understood(cluster3):
+    cl = cluster3
+    cfg = op_cfg()
+    cfg["pool_hash_map"] = {"expected_max_items": 50000, "grow_ratio": 2.0}
+    sid, h = make_table(cl, uneven(cl.ids()), cfg=cfg)
+    st, hid = cl.client.register_handler("pull_random", S.LIB, "SparseTablePullOperator",
+                                         json.dumps({"read_only": True, "node_selection": "random"}), sid)
+    assert st.ok()
+    st, _ = cl.client.register_handler("pull_nearest", S.LIB, "SparseTablePullOperator",
+                                       json.dumps({"node_selection": "nearest"}), sid)
+    assert not st.ok() and "node_selection" in str(st)
+    # the refused registration left nothing behind: the table still works with the handlers it had
+    keys = np.arange(100, dtype=np.int64)
+    assert S.PushHandler(cl.client, sid, h["push"]).async_push(keys, np.ones((100, DIM), np.float32)).ok()
+    st, rows = S.PullHandler(cl.client, sid, hid).pull(keys)
+    assert st.ok() and np.all(rows == 1.0)
+
+
+def test_runtime_log_lines_reach_python_logging(caplog):
+    """The native runtime logs its life-cycle events (a server joining, storages created, a node found dead, a restore
+    and its source); `service.log_to_python` hands the lines to the logging module."""
+    import logging
+    S.set_log_level("info")
+    S.log_to_python("psb_test")
+    try:
+        with caplog.at_level(logging.INFO, logger="psb_test"):
+            cl = Cluster(2)
+            try:
+                ids = cl.ids()
+                sid, h = make_table(cl, {ids[0]: [0, 1], ids[1]: [0, 1]})
+                keys = np.arange(50, dtype=np.int64)
+                assert S.PushHandler(cl.client, sid, h["push"]).async_push(keys, np.ones((50, DIM), np.float32)).ok()
+                cl.servers[1].stop()
+                pull = S.PullHandler(cl.client, sid, h["pull_ro"])
+                for _ in range(20):
+                    assert pull.pull(keys, 20000, True)[0].ok()
+                fresh = S.Server(cl.master.address())
+                cl.servers.append(fresh)
+                st, n = fresh.restore_storages()
+                assert st.ok() and n == 1
+            finally:
+                cl.close()
+        text = "\n".join(r.getMessage() for r in caplog.records)
+        assert f"pserver node {ids[0]} serves c2s" in text
+        assert f"storage {sid} created on node {ids[0]}" in text
+        assert "marked DEAD" in text and f"takes the place of dead node {ids[1]}" in text
+        assert f"storage {sid}: restored from replica, 50 items" in text
+        assert any(r.levelno == logging.WARNING for r in caplog.records)
+    finally:
+        C.set_log_sink(None)
+        S.set_log_level("warning")
+
+
 def test_available_server_list_excludes_stopped_nodes(cluster3):
     cl = cluster3
     st, nodes = cl.client.get_available_pserver_list()
@@ -713,6 +809,8 @@ def test_prometheus_metrics_endpoint(cluster3):
     assert 'ps_request_duration_ms_bucket' in text and 'le="+Inf"' in text and "ps_response_size_bytes" in text
     assert f'ps_storage_items{{node_id="{node}",storage_id="{sid}"}}' in text
     assert "ps_wait_request_count" in handler_metrics_text(pull, "pull")
+    assert 'ps_pull_send_request_count{handler="pull"} 1' in handler_metrics_text(pull, "pull")
+    assert "ps_pull_send" not in handler_metrics_text(push, "push")
 
 
 def test_sync_pred_backs_off_and_resumes_after_the_predictor_comes_back():
