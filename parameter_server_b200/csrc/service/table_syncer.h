@@ -91,9 +91,10 @@ private:
         if (followers.empty())
             for (auto& t : server_->sync_targets(sid)) followers.push_back(Follower{t, nullptr});
         Status first;
-        // The increment is collected once per follower: the marks are cleared by the pass that succeeds last, so with
-        // several followers every one of them must see the rows before the marks go. One follower is the common case;
-        // with more, the table is walked once per follower and the marks are kept until the last one.
+        // The increment is collected once per follower, and the marks go only with the pass for the last follower, and
+        // only if every follower before it got the rows: a follower that is down keeps the marks in place, so the
+        // others receive those rows again next round (overwrites of equal rows) and the one that was down misses
+        // nothing. One follower is the common case.
         for (size_t i = 0; i < followers.size(); ++i) {
             auto& f = followers[i];
             if (!f.handler) {
@@ -104,7 +105,7 @@ private:
                 }
             }
             uint64_t n = 0;
-            const bool last = i + 1 == followers.size();
+            const bool last = i + 1 == followers.size() && first.ok();
             Status st = last ? f.handler->sync_pred(*server_, sid, &n, max_attempts_, backoff_scale_)
                              : f.handler->sync_pred_keep_marks(*server_, sid, &n, max_attempts_, backoff_scale_);
             *rows += n;

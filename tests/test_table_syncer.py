@@ -118,3 +118,37 @@ def test_a_follower_that_does_not_exist_is_an_error_not_a_hang():
             syncer.stop()
         server.stop()
         m.stop()
+
+
+def test_two_followers_and_one_of_them_appears_late():
+    """A table with two followers: while one of them cannot be found the other still receives every change, and the
+    late one gets everything once it exists (the marks stay until every follower has the rows)."""
+    m = S.Master()
+    server = S.Server(m.address())
+    syncer = None
+    try:
+        client = S.Client(m.address())
+        a_sid, a_h = _table(client, {server.node_id(): [0, 1]}, {})
+        assert C.set_model(S.MasterClient(m.address()), json.dumps(_model("first", "emb", a_sid, a_h))).ok()
+        follow = {"sync_table": [{"model_name": "late", "table_name": "emb", "op_key": "sync"},
+                                 {"model_name": "first", "table_name": "emb", "op_key": "sync"}]}
+        sid, h = _table(client, {server.node_id(): [0]}, follow)
+        syncer = S.TableSyncer(server, m.address(), 2, 0.01)
+        push = S.PushHandler(client, sid, h["push"])
+        keys = np.arange(40, dtype=np.int64)
+        assert push.async_push(keys, -np.ones((40, DIM), np.float32)).ok()
+        assert syncer.wait_idle(10000)
+        assert np.all(S.PullHandler(client, a_sid, a_h["pull_ro"]).pull(keys)[1] == 1.0)      # the follower that exists is served
+        assert syncer.stats()["errors"] >= 1
+        b_sid, b_h = _table(client, {server.node_id(): [0, 1, 2]}, {})
+        assert C.set_model(S.MasterClient(m.address()), json.dumps(_model("late", "emb", b_sid, b_h))).ok()
+        assert push.async_push(keys[:3], -np.ones((3, DIM), np.float32)).ok()
+        assert syncer.wait_idle(10000)
+        want = S.PullHandler(client, sid, h["pull_ro"]).pull(keys)[1]
+        for fsid, fh in ((a_sid, a_h), (b_sid, b_h)):
+            assert np.array_equal(S.PullHandler(client, fsid, fh["pull_ro"]).pull(keys)[1], want)
+    finally:
+        if syncer:
+            syncer.stop()
+        server.stop()
+        m.stop()
