@@ -60,6 +60,7 @@ void bind_host(py::module_& m) {
         .def("healthy", &HostTable::healthy)
         .def("set_healthy", &HostTable::set_healthy)
         .def("check_healthy", &HostTable::check_healthy)
+        .def("inject_insert_failures", &HostTable::inject_insert_failures)
         .def("overflow_size", &HostTable::overflow_size)
         .def("drain_overflow", &HostTable::drain_overflow)
         .def("set_limits", &HostTable::set_limits)

@@ -334,6 +334,10 @@ public:
         if (healthy_ && n_parked_) drain_overflow();
         return healthy_;
     }
+    // Fault injection for tests of the out-of-memory paths: every `period`-th insert of a NEW key fails as if the
+    // row pool could not grow (0 switches it off). The role of the reference's TestBadAllocator, which throws
+    // bad_alloc on every other large allocation (pico-ps/test/TestOps.h:437-476).
+    void inject_insert_failures(uint32_t period) { fail_period_ = period; }
     // Items parked by pushes that found no room.
     uint64_t overflow_size() const { return n_parked_; }
     // The parked items of shard `s` as full rows - initial value with the parked gradients applied in their order: a
@@ -427,6 +431,12 @@ private:
         auto* e = sh.map.find(key);
         if (e) { *row = e->second; return Status::Ok(); }
         if (!healthy_) return Status::OOM("storage is unhealthy");
+        if (fail_period_ && ++fail_counter_ % fail_period_ == 0) {   // fault injection, see inject_insert_failures
+            failed_extra_ = 0;
+            failed_at_bytes_ = bytes_.load();
+            healthy_ = false;
+            return Status::OOM("injected allocation failure");
+        }
         uint32_t r;
         if (!sh.free_rows.empty()) {
             r = sh.free_rows.back();
@@ -479,6 +489,7 @@ private:
     std::atomic<uint64_t> bytes_{0};
     std::atomic<bool> healthy_{true};
     std::atomic<uint64_t> n_parked_{0};
+    std::atomic<uint32_t> fail_period_{0}, fail_counter_{0};
     std::atomic<uint64_t> failed_extra_{0}, failed_at_bytes_{0};   // the growth that made the table unhealthy
     std::atomic<bool> track_dirty_{false};   // may be switched on while pushes run (a follower table appears)
 };
