@@ -51,8 +51,33 @@ public:
     // failures are Timeout); per-node outcomes are in `out`.
     Status send_and_wait(int32_t sid, int32_t hid, RequestType type, const std::map<int, Archive>& bodies, int timeout_ms,
                          std::vector<NodeResponse>* out, int32_t ctx_ver = -2, int32_t ctx_u_ver = -1) {
+        // the addresses come from a short-lived copy of the registry (a request does not cost a round trip to the
+        // master, and the data path outlives a master that is away for a moment); a node that the copy does not
+        // know, or any failure below, makes the next look-up go to the master again
         std::map<int32_t, std::string> nodes;
-        PSB_RETURN_IF_ERROR(get_pserver_list(&nodes));
+        bool need_fresh = false;
+        {
+            std::lock_guard<std::mutex> g(nodes_mu_);
+            const auto age = std::chrono::steady_clock::now() - nodes_at_;
+            need_fresh = nodes_cache_.empty() || age > std::chrono::milliseconds(kNodeCacheMs);
+            if (!need_fresh) {
+                nodes = nodes_cache_;
+                for (auto& kv : bodies)
+                    if (!nodes.count(kv.first)) need_fresh = true;
+            }
+        }
+        if (need_fresh) {
+            Status ls = get_pserver_list(&nodes);
+            std::lock_guard<std::mutex> g(nodes_mu_);
+            if (ls.ok()) {
+                nodes_cache_ = nodes;
+                nodes_at_ = std::chrono::steady_clock::now();
+            } else if (nodes_cache_.empty()) {
+                return ls;
+            } else {
+                nodes = nodes_cache_;   // the master is away: go on with what was known
+            }
+        }
         PSMessageMeta meta;
         meta.sid = sid;
         meta.hid = hid;
@@ -102,6 +127,10 @@ public:
             }
             if (!r.status.ok() && result.ok()) result = r.status;
             if (out) out->push_back(std::move(r));
+        }
+        if (!result.ok()) {
+            std::lock_guard<std::mutex> g(nodes_mu_);
+            nodes_at_ = std::chrono::steady_clock::time_point();   // look the registry up again next time
         }
         return result;
     }
@@ -426,6 +455,10 @@ public:
     }
 
 private:
+    static constexpr int kNodeCacheMs = 500;
+    std::mutex nodes_mu_;
+    std::map<int32_t, std::string> nodes_cache_;
+    std::chrono::steady_clock::time_point nodes_at_{};
     MasterClient master_;
     RpcClient rpc_;
     Context ctx_;
