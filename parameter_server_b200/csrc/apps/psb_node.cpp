@@ -1,7 +1,9 @@
 // psb_node: the parameter server's processes as one native executable (no Python in the serving path).
 //
-//   psb_node master [--threads N]
-//       prints the master's address on the first line of stdout and serves until it is killed.
+//   psb_node master [--threads N] [--port P] [--state-file FILE]
+//       prints the master's address on the first line of stdout and serves until it is killed. With a state file
+//       (and a fixed port) a restarted master carries on where the old one stopped: ids, contexts and the model
+//       registry are read back, the servers register again, clients reconnect.
 //   psb_node pserver --master HOST:PORT [--restore] [--image-dir DIR] [--c2s-threads N] [--s2s-threads N]
 //       registers at the master, prints "pserver node_id=.. c2s=.. s2s=..", serves both ports and exits when a
 //       client sends EXIT (Client::close_pserver / Controller::shutdown_node). With --restore it first takes
@@ -103,7 +105,7 @@ int ctl_main(int argc, char** argv) {
 
 int usage() {
     std::fprintf(stderr,
-                 "usage: psb_node master [--threads N]\n"
+                 "usage: psb_node master [--threads N] [--port P] [--state-file FILE]\n"
                  "       psb_node ctl --master HOST:PORT VERB ...   (the controller; `psb_node ctl` lists the verbs)\n"
                  "       psb_node pserver --master HOST:PORT [--restore] [--restore-wait S] [--image-dir DIR] [--image-interval-ms N] [--report-interval S]\n"
                  "                        [--load-threads N] [--c2s-threads N] [--s2s-threads N] [--sync-master HOST:PORT] [--hadoop-bin PATH]\n"
@@ -118,7 +120,8 @@ int main(int argc, char** argv) {
     std::signal(SIGTERM, on_signal);
     const std::string role = argv[1];
     if (role == "ctl") return ctl_main(argc, argv);
-    std::string master_addr, sync_master;
+    std::string master_addr, sync_master, state_file;
+    int master_port = 0;
     bool restore = false;
     int threads = 4, image_interval_ms = 0, metrics_port = -1;
     ServerConfig cfg;
@@ -131,6 +134,8 @@ int main(int argc, char** argv) {
         };
         if (a == "--master" && i + 1 < argc) master_addr = argv[++i];
         else if (a == "--sync-master" && i + 1 < argc) sync_master = argv[++i];
+        else if (a == "--state-file" && i + 1 < argc) state_file = argv[++i];
+        else if (a == "--port") { if (!next(&master_port)) return usage(); }
         else if (a == "--restore") restore = true;
         else if (a == "--image-dir" && i + 1 < argc) cfg.local_image_dir = argv[++i];
         else if (a == "--hadoop-bin" && i + 1 < argc) cfg.hadoop_bin = argv[++i];
@@ -146,7 +151,14 @@ int main(int argc, char** argv) {
         else return usage();
     }
     if (role == "master") {
-        Master master(threads);
+        std::unique_ptr<Master> owned;
+        try {
+            owned.reset(new Master(threads, master_port, state_file));
+        } catch (const std::exception& e) {
+            std::fprintf(stderr, "psb_node: %s\n", e.what());
+            return 1;
+        }
+        Master& master = *owned;
         std::printf("%s\n", master.address().c_str());
         std::fflush(stdout);
         while (!g_stop) std::this_thread::sleep_for(std::chrono::milliseconds(50));

@@ -140,7 +140,7 @@ void bind_service(py::module_& m) {
         .def("pick_one_replica", [](TableDescriptor& t, int shard) { return RuntimeInfo(t, -1).pick_one_replica(shard); });
 
     // ---- master ----------------------------------------------------------------------------------
-    py::class_<Master>(m, "Master").def(py::init<int>(), py::arg("n_threads") = 4).def("address", &Master::address).def("stop", &Master::stop, nogil());
+    py::class_<Master>(m, "Master").def(py::init<int, int, std::string, int>(), py::arg("n_threads") = 4, py::arg("port") = 0, py::arg("state_file") = "", py::arg("recover_ms") = 3000).def("address", &Master::address).def("stop", &Master::stop, nogil());
     py::class_<MasterClient>(m, "MasterClient")
         .def(py::init<std::string, int>(), py::arg("address"), py::arg("timeout_ms") = 30000)
         .def("generate_id", [](MasterClient& c, const std::string& k) { int32_t id = -1; Status st = c.generate_id(k, &id); return std::make_tuple(st, id); }, nogil())
@@ -170,6 +170,7 @@ void bind_service(py::module_& m) {
         .def_readwrite("s2s_timeout_ms", &ServerConfig::s2s_timeout_ms)
         .def_readwrite("local_image_dir", &ServerConfig::local_image_dir)
         .def_readwrite("hadoop_bin", &ServerConfig::hadoop_bin)
+        .def_readwrite("session_check_ms", &ServerConfig::session_check_ms)
         .def_readwrite("report_interval_s", &ServerConfig::report_interval_s)
         .def_readwrite("restore_wait_timeout_s", &ServerConfig::restore_wait_timeout_s);
     // the sync thread of a server: keeps the follower tables named by push operators ("sync_table") fresh

@@ -9,6 +9,10 @@
 // barrier, tree_node_add / get, get_model / set_model. The in-process TCP master of the reference's
 // tests (pico-ps/test/TestUtils.h:16-92) corresponds to constructing Master directly.
 #pragma once
+#include <chrono>
+#include <cstdio>
+#include <fstream>
+#include <iterator>
 #include <map>
 #include <set>
 #include <string>
@@ -27,9 +31,16 @@ enum class MasterOp : int32_t {
 
 class Master {
 public:
-    explicit Master(int n_threads = 4)
-        : server_([this](Bytes&& b, RpcServer::Responder r) { handle(std::move(b), r); }, n_threads,
-                  [this](uint64_t conn) { on_disconnect(conn); }) {}
+    // `state_file`: the durable part of the master's state (id counters, contexts, tree nodes, the next node id) is
+    // written there after every change (temp file + rename) and read back at start, so a master that is restarted
+    // on the same `port` carries on: servers notice that their registration is gone and register again under their
+    // node ids, clients reconnect on their next call. For `recover_ms` after a start from a state file the node
+    // list is not served (TIMEOUT "recovering"): nobody must take the not-yet-re-registered servers for dead.
+    // Locks and barriers are not durable: a holder that outlives the master simply fails to release.
+    explicit Master(int n_threads = 4, int port = 0, std::string state_file = "", int recover_ms = 3000)
+        : state_file_(std::move(state_file)),
+          server_((load_state(recover_ms), [this](Bytes&& b, RpcServer::Responder r) { handle(std::move(b), r); }), n_threads,
+                  [this](uint64_t conn) { on_disconnect(conn); }, port) {}
     std::string address() const { return server_.address(); }
     void stop() { server_.stop(); }
 
@@ -57,6 +68,7 @@ private:
                 ar >> key;
                 Archive out;
                 out << (int32_t)(ids_[key]++);
+                save_state_locked();
                 resp.send(ok_reply(std::move(out)));
                 break;
             }
@@ -88,6 +100,7 @@ private:
                     resp.send(err_reply(Status::Error("context " + key + " already exists")));
                 } else {
                     ctx_[key] = value;
+                    save_state_locked();
                     resp.send(ok_reply());
                 }
                 break;
@@ -109,6 +122,7 @@ private:
                 std::string key;
                 ar >> key;
                 ctx_.erase(key);
+                save_state_locked();
                 resp.send(ok_reply());
                 break;
             }
@@ -127,6 +141,7 @@ private:
                 ar >> service >> addr >> want_id;
                 int32_t id = want_id >= 0 ? want_id : next_node_id_++;
                 if (want_id >= next_node_id_) next_node_id_ = want_id + 1;
+                if (want_id < 0) save_state_locked();   // ids are never handed out twice, also across a restart
                 registry_[service][id] = addr;
                 sessions_[resp.conn_id()].insert({service, id});
                 Archive out;
@@ -145,6 +160,10 @@ private:
             case MasterOp::NODES: {
                 std::string service;
                 ar >> service;
+                if (std::chrono::steady_clock::now() < recovering_until_) {
+                    resp.send(err_reply(Status::Timeout("master is recovering: the servers are registering again")));
+                    break;
+                }
                 std::vector<int32_t> ids;
                 std::vector<std::string> addrs;
                 for (auto& kv : registry_[service]) {
@@ -172,6 +191,7 @@ private:
                 std::string path, value;
                 ar >> path >> value;
                 tree_[path] = value;
+                save_state_locked();
                 resp.send(ok_reply());
                 break;
             }
@@ -192,6 +212,7 @@ private:
                 std::string path;
                 ar >> path;
                 tree_.erase(path);
+                save_state_locked();
                 resp.send(ok_reply());
                 break;
             }
@@ -209,6 +230,51 @@ private:
             case MasterOp::PING: resp.send(ok_reply()); break;
             default: resp.send(err_reply(Status::Error("master: unknown op")));
         }
+    }
+
+    // ---- durable state: {"PSBM1", next_node_id, ids, ctx, tree} as one archive ----
+    void save_state_locked() {
+        if (state_file_.empty()) return;
+        Archive ar;
+        ar << std::string("PSBM1") << next_node_id_;
+        ar << (uint64_t)ids_.size();
+        for (auto& kv : ids_) ar << kv.first << kv.second;
+        ar << (uint64_t)ctx_.size();
+        for (auto& kv : ctx_) ar << kv.first << kv.second;
+        ar << (uint64_t)tree_.size();
+        for (auto& kv : tree_) ar << kv.first << kv.second;
+        const std::string tmp = state_file_ + ".tmp";
+        {
+            std::ofstream f(tmp, std::ios::binary | std::ios::trunc);
+            f.write((const char*)ar.data(), (std::streamsize)ar.size());
+            if (!f.good()) return;   // the old file stays
+        }
+        ::rename(tmp.c_str(), state_file_.c_str());
+    }
+    // Returns 0 so that it can run inside the member initialiser list before the server starts its threads.
+    int load_state(int recover_ms) {
+        if (state_file_.empty()) return 0;
+        std::ifstream f(state_file_, std::ios::binary);
+        if (!f) return 0;   // first start
+        std::vector<uint8_t> raw((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+        try {
+            Archive ar(std::move(raw));
+            std::string magic;
+            ar >> magic;
+            if (magic != "PSBM1") throw std::runtime_error("not a master state file");
+            uint64_t n = 0;
+            ar >> next_node_id_;
+            ar >> n;
+            for (uint64_t i = 0; i < n; ++i) { std::string k; int32_t v = 0; ar >> k >> v; ids_[k] = v; }
+            ar >> n;
+            for (uint64_t i = 0; i < n; ++i) { std::string k, v; ar >> k >> v; ctx_[k] = v; }
+            ar >> n;
+            for (uint64_t i = 0; i < n; ++i) { std::string k, v; ar >> k >> v; tree_[k] = v; }
+        } catch (const std::exception& e) {
+            throw std::runtime_error("master: cannot read " + state_file_ + ": " + e.what());
+        }
+        recovering_until_ = std::chrono::steady_clock::now() + std::chrono::milliseconds(recover_ms);
+        return 0;
     }
 
     void release_lock_locked(const std::string& name) {
@@ -249,6 +315,8 @@ private:
     std::map<std::string, std::vector<RpcServer::Responder>> barriers_;
     std::map<std::string, std::string> tree_;
     int32_t next_node_id_ = 0;
+    std::string state_file_;
+    std::chrono::steady_clock::time_point recovering_until_{};
     RpcServer server_;  // last member: its threads start using the state above at once
 };
 

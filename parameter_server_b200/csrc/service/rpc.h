@@ -113,7 +113,9 @@ public:
     using Handler = std::function<void(Bytes&&, Responder)>;
     using DisconnectHandler = std::function<void(uint64_t conn_id)>;
 
-    RpcServer(Handler h, int n_threads, DisconnectHandler on_disconnect = nullptr)
+    // port 0 = any free port (the usual case: addresses are published through the master); a fixed port is for the
+    // master itself, which clients must find again after it was restarted
+    RpcServer(Handler h, int n_threads, DisconnectHandler on_disconnect = nullptr, int port = 0)
         : handler_(std::move(h)), on_disconnect_(std::move(on_disconnect)) {
         listen_fd_ = ::socket(AF_INET, SOCK_STREAM, 0);
         int one = 1;
@@ -121,9 +123,11 @@ public:
         sockaddr_in addr{};
         addr.sin_family = AF_INET;
         addr.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
-        addr.sin_port = 0;
-        if (::bind(listen_fd_, (sockaddr*)&addr, sizeof addr) != 0 || ::listen(listen_fd_, 256) != 0)
-            throw std::runtime_error("RpcServer: bind/listen failed");
+        addr.sin_port = htons((uint16_t)port);
+        if (::bind(listen_fd_, (sockaddr*)&addr, sizeof addr) != 0 || ::listen(listen_fd_, 256) != 0) {
+            ::close(listen_fd_);
+            throw std::runtime_error("RpcServer: cannot listen on port " + std::to_string(port));
+        }
         socklen_t len = sizeof addr;
         ::getsockname(listen_fd_, (sockaddr*)&addr, &len);
         port_ = ntohs(addr.sin_port);

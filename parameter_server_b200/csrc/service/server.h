@@ -40,6 +40,8 @@ struct ServerConfig {
     // Directory of this host's persistent table images (empty: none). A server in restore mode that finds the image
     // of the node it replaces, with the table's version_uuid, opens it instead of the table's dump.
     std::string local_image_dir;
+    int session_check_ms = 1000;  // how often the server checks that the master still lists it (0 = never); a master that
+                                  // was restarted has lost the registrations, and the server registers again under its id
     std::string hadoop_bin;       // command behind hdfs:// dump paths ("" = $PSB_HADOOP_BIN, else "hadoop"); process-wide
 };
 
@@ -73,6 +75,15 @@ public:
         st = session_.register_node(PSERVER_C2S_RPC_NAME, c2s_->address(), &same, node_id_);
         if (!st.ok()) throw std::runtime_error("server: cannot register c2s: " + st.to_string());
         PSB_LOG(INFO) << "pserver node " << node_id_ << " serves c2s " << c2s_->address() << ", s2s " << s2s_->address();
+        if (cfg_.session_check_ms > 0)
+            keeper_ = std::thread([this] {
+                std::unique_lock<std::mutex> g(keeper_mu_);
+                while (!keeper_cv_.wait_for(g, std::chrono::milliseconds(cfg_.session_check_ms), [this] { return stopped_.load(); })) {
+                    g.unlock();
+                    ensure_registered();
+                    g.lock();
+                }
+            });
         if (cfg_.report_interval_s > 0)
             reporter_ = std::thread([this] {
                 // one line per interval on stderr (ServerConfig::report_interval of the reference)
@@ -101,6 +112,24 @@ public:
         // the thread an EXIT request started may still be inside stop() (or about to enter it): wait for it
         std::lock_guard<std::mutex> g(exit_mu_);
         if (exit_thread_.joinable()) exit_thread_.join();
+    }
+
+    // The master's registry is the liveness record: if it no longer lists this node although the node is alive (the
+    // master was restarted from its state file, or the session's connection broke), both services are registered
+    // again under the same node id. A master that cannot be reached is simply asked again at the next check.
+    void ensure_registered() {
+        std::map<int32_t, std::string> nodes;
+        if (!session_.get_nodes(PSERVER_S2S_RPC_NAME, &nodes).ok()) {
+            // "recovering" is answered to everybody; registering is what the master waits for
+            if (!session_.ping().ok()) return;
+        } else if (nodes.count(node_id_)) {
+            return;
+        }
+        if (stopped_) return;
+        int32_t same = -1;
+        Status a = session_.register_node(PSERVER_S2S_RPC_NAME, s2s_->address(), &same, node_id_);
+        Status b = session_.register_node(PSERVER_C2S_RPC_NAME, c2s_->address(), &same, node_id_);
+        if (a.ok() && b.ok()) PSB_LOG(WARNING) << "pserver node " << node_id_ << " was missing from the master's registry and registered again";
     }
 
     // "node=.. requests=.. errors=.. storages=[sid:items:bytes ...]"
@@ -148,6 +177,8 @@ public:
         if (stopped_.exchange(true)) return;
         report_cv_.notify_all();
         if (reporter_.joinable()) reporter_.join();
+        keeper_cv_.notify_all();
+        if (keeper_.joinable()) keeper_.join();   // before the session closes: it must not register us again
         session_.close();  // the master drops our registrations: we are gone
         if (c2s_) c2s_->stop();
         if (s2s_) s2s_->stop();
@@ -1200,7 +1231,9 @@ private:
     Context ctx_;
     std::unique_ptr<RpcServer> c2s_, s2s_;
     RpcClient s2s_client_;
-    std::thread reporter_;
+    std::thread reporter_, keeper_;
+    std::mutex keeper_mu_;
+    std::condition_variable keeper_cv_;
     std::mutex report_mu_;
     std::condition_variable report_cv_;
     std::string last_report_;

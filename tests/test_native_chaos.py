@@ -253,3 +253,87 @@ def test_a_killed_server_never_leaves_a_torn_image(tmp_path):
         for p in procs:
             if p.poll() is None:
                 p.kill()
+
+
+def _free_port():
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.skipif(not os.path.exists(NODE), reason="psb_node is not built")
+def test_the_master_is_killed_and_restarted_from_its_state_file(tmp_path):
+    """The master keeps ids, contexts and the model registry in a state file. While it is gone the data path goes on
+    (clients know the servers' addresses); a new master on the same port reads the file back, the servers register
+    again under their node ids and nobody is taken for dead; afterwards everything that needs the master works."""
+    port, state = _free_port(), str(tmp_path / "master.state")
+    margs = ["master", "--port", str(port), "--state-file", state]
+    master = _spawn(*margs)
+    procs = [master]
+    try:
+        addr = _line(master)
+        assert addr.endswith(f":{port}")
+        servers = [_spawn("pserver", "--master", addr) for _ in range(2)]
+        procs += servers
+        ids = [int(_line(p).split("node_id=")[1].split()[0]) for p in servers]
+        client = S.Client(addr)
+        st, sid = client.create_storage(S.LIB, "SparseTableStorageOperator",
+                                        S.storage_config({ids[0]: [0], ids[1]: [1]}, dict(dim=DIM, optimizer="sum", init_range=0.0)))
+        assert st.ok(), st
+        h = {}
+        for key, op, cfg in [("push", "SparseTablePushOperator", {}), ("pull_ro", "SparseTablePullOperator", {"read_only": True}),
+                             ("update_ctx", "ShardUpdateContextOperator", {})]:
+            st, h[key] = client.register_handler(key, S.LIB, op, json.dumps(cfg), sid)
+            assert st.ok(), st
+        push, pull = S.PushHandler(client, sid, h["push"]), S.PullHandler(client, sid, h["pull_ro"])
+        keys = np.arange(1000, dtype=np.int64)
+        ones = np.ones((1000, DIM), np.float32)
+        assert push.async_push(keys, ones).ok()
+        master.send_signal(signal.SIGKILL)
+        master.wait(timeout=10)
+        # the data path does not need the master
+        for _ in range(5):
+            assert push.async_push(keys, ones, 5000).ok()
+        st, rows = pull.pull(keys, 5000, True)
+        assert st.ok() and np.all(rows == 6.0)
+        st, _ = client.create_storage(S.LIB, "SparseTableStorageOperator", S.storage_config({ids[0]: [0]}, dict(dim=DIM, optimizer="sum")))
+        assert not st.ok()                                          # what needs the master fails cleanly meanwhile
+        master2 = _spawn(*margs)
+        procs.append(master2)
+        assert _line(master2) == addr
+        # the servers come back into the registry under their old ids
+        t0 = time.time()
+        nodes = {}
+        while time.time() - t0 < 15:
+            st, nodes = client.get_pserver_list()
+            if st.ok() and sorted(nodes) == sorted(ids):
+                break
+            time.sleep(0.2)
+        assert sorted(nodes) == sorted(ids), (st, nodes)
+        st, rows = pull.pull(keys, 5000, True)
+        assert st.ok() and np.all(rows == 6.0)
+        # the table's context survived: a reshard (published through the master) works, ids go on where they were
+        st = S.UpdateContextHandler(client, sid, h["update_ctx"]).update_context(S.nodes_json({ids[0]: [1], ids[1]: [0]}))
+        assert st.ok(), st
+        st, rows = pull.pull(keys, 20000, True)
+        assert st.ok() and np.all(rows == 6.0)
+        st, sid2 = client.create_storage(S.LIB, "SparseTableStorageOperator", S.storage_config({ids[0]: [0]}, dict(dim=DIM, optimizer="sum")))
+        assert st.ok() and sid2 > sid
+        extra = _spawn("pserver", "--master", addr)
+        procs.append(extra)
+        new_id = int(_line(extra).split("node_id=")[1].split()[0])
+        assert new_id not in ids                                     # node ids are never handed out twice
+        for n in ids + [new_id]:
+            assert client.close_pserver(n).ok()
+        for p in servers + [extra]:
+            assert p.wait(timeout=15) == 0
+        master2.send_signal(signal.SIGTERM)
+        assert master2.wait(timeout=15) == 0
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
