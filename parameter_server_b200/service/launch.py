@@ -1,6 +1,6 @@
 """Process launchers of the service layer.
 
-    python -m parameter_server_b200.service.launch master            # prints the address, serves until killed
+    python -m parameter_server_b200.service.launch master [--port P] [--state-file F]   # prints the address, serves until killed
     python -m parameter_server_b200.service.launch pserver --master 127.0.0.1:PORT [--restore] [--image-dir DIR]
         [--restore-wait S] [--report-interval S] [--sync-master ADDR] [--metrics-port P] [--hadoop-bin PATH] [--log-level L]
 
@@ -23,6 +23,8 @@ def main(argv=None) -> int:
     sub = ap.add_subparsers(dest="role", required=True)
     m = sub.add_parser("master")
     m.add_argument("--threads", type=int, default=4)
+    m.add_argument("--port", type=int, default=0, help="fixed port (needed to find a restarted master again)")
+    m.add_argument("--state-file", default="", help="durable state: a restarted master carries on from it")
     p = sub.add_parser("pserver")
     p.add_argument("--master", required=True)
     p.add_argument("--restore", action="store_true")
@@ -39,7 +41,7 @@ def main(argv=None) -> int:
     if a.role == "pserver" and a.log_level:
         set_log_level(a.log_level)
     if a.role == "master":
-        master = Master(a.threads)
+        master = Master(a.threads, a.port, a.state_file)
         print(master.address(), flush=True)
         try:
             while True:
