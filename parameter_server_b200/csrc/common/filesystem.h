@@ -61,16 +61,27 @@ inline Status run(const std::vector<std::string>& argv, const uint8_t* in, size_
     static std::once_flag once;
     std::call_once(once, [] { ::signal(SIGPIPE, SIG_IGN); });   // a child that dies early must not take the server along
     int to_child[2] = {-1, -1}, from_child[2] = {-1, -1};
-    if (::pipe(to_child) != 0 || ::pipe(from_child) != 0) return Status::Error("pipe failed");
+    if (::pipe(to_child) != 0) return Status::Error("pipe failed");
+    if (::pipe(from_child) != 0) {
+        ::close(to_child[0]);
+        ::close(to_child[1]);
+        return Status::Error("pipe failed");
+    }
+    // everything the child needs is laid out before the fork: in a process with other threads the child may only
+    // make async-signal-safe calls (no allocation) until it has exec'ed
+    std::vector<char*> args;
+    for (auto& a : argv) args.push_back(const_cast<char*>(a.c_str()));
+    args.push_back(nullptr);
+    const int fds[4] = {to_child[0], to_child[1], from_child[0], from_child[1]};
     const pid_t pid = ::fork();
-    if (pid < 0) return Status::Error("fork failed");
+    if (pid < 0) {
+        for (int fd : fds) ::close(fd);
+        return Status::Error("fork failed");
+    }
     if (pid == 0) {
         ::dup2(to_child[0], 0);
         ::dup2(from_child[1], 1);
-        for (int fd : {to_child[0], to_child[1], from_child[0], from_child[1]}) ::close(fd);
-        std::vector<char*> args;
-        for (auto& a : argv) args.push_back(const_cast<char*>(a.c_str()));
-        args.push_back(nullptr);
+        for (int fd : fds) ::close(fd);
         ::execvp(args[0], args.data());
         ::_exit(127);
     }
