@@ -61,8 +61,9 @@ inline Status run(const std::vector<std::string>& argv, const uint8_t* in, size_
     static std::once_flag once;
     std::call_once(once, [] { ::signal(SIGPIPE, SIG_IGN); });   // a child that dies early must not take the server along
     int to_child[2] = {-1, -1}, from_child[2] = {-1, -1};
-    if (::pipe(to_child) != 0) return Status::Error("pipe failed");
-    if (::pipe(from_child) != 0) {
+    // close-on-exec: a command started by another thread at the same time must not inherit (and hold open) these ends
+    if (::pipe2(to_child, O_CLOEXEC) != 0) return Status::Error("pipe failed");
+    if (::pipe2(from_child, O_CLOEXEC) != 0) {
         ::close(to_child[0]);
         ::close(to_child[1]);
         return Status::Error("pipe failed");
