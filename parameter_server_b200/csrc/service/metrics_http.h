@@ -23,7 +23,7 @@ class MetricsHttpServer {
 public:
     // port 0 = any free port (see port()). `body` is called for every scrape.
     MetricsHttpServer(int port, std::function<std::string()> body) : body_(std::move(body)) {
-        fd_ = ::socket(AF_INET, SOCK_STREAM, 0);
+        fd_ = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
         if (fd_ < 0) throw std::runtime_error("metrics: socket failed");
         int one = 1;
         ::setsockopt(fd_, SOL_SOCKET, SO_REUSEADDR, &one, sizeof one);
@@ -56,7 +56,7 @@ private:
         while (running_) {
             pollfd p{fd_, POLLIN, 0};
             if (::poll(&p, 1, 100) <= 0) continue;
-            const int c = ::accept(fd_, nullptr, nullptr);
+            const int c = ::accept4(fd_, nullptr, nullptr, SOCK_CLOEXEC);
             if (c < 0) continue;
             serve(c);
             ::close(c);

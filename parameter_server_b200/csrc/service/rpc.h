@@ -117,7 +117,7 @@ public:
     // master itself, which clients must find again after it was restarted
     RpcServer(Handler h, int n_threads, DisconnectHandler on_disconnect = nullptr, int port = 0)
         : handler_(std::move(h)), on_disconnect_(std::move(on_disconnect)) {
-        listen_fd_ = ::socket(AF_INET, SOCK_STREAM, 0);
+        listen_fd_ = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
         int one = 1;
         ::setsockopt(listen_fd_, SOL_SOCKET, SO_REUSEADDR, &one, sizeof one);
         sockaddr_in addr{};
@@ -170,7 +170,7 @@ private:
 
     void accept_loop() {
         while (running_) {
-            int fd = ::accept(listen_fd_, nullptr, nullptr);
+            int fd = ::accept4(listen_fd_, nullptr, nullptr, SOCK_CLOEXEC);   // not inherited by commands that a server starts
             if (fd < 0) {
                 if (!running_) break;
                 continue;
@@ -340,7 +340,7 @@ private:
         addr.sin_family = AF_INET;
         addr.sin_port = htons((uint16_t)std::stoi(address.substr(colon + 1)));
         if (::inet_pton(AF_INET, address.substr(0, colon).c_str(), &addr.sin_addr) != 1) return nullptr;
-        int fd = ::socket(AF_INET, SOCK_STREAM, 0);
+        int fd = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
         if (fd < 0) return nullptr;
         if (::connect(fd, (sockaddr*)&addr, sizeof addr) != 0) {
             ::close(fd);
