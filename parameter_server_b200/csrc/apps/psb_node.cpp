@@ -20,6 +20,9 @@
 //       the controller from the command line: show nodes / a table, create, delete, balance, change the shard or
 //       replica count of a table, add nodes to it, clean up storages without a table, shut a node down.
 //
+// --host ADDR (or $PSB_HOST), for master and pserver: the address of this machine that the process publishes; its
+// servers then listen on every interface instead of loopback only, so the roles may run on different machines.
+//
 // The same objects as the Python bindings: tables with "backend": "gpu" are served by the fused kernels.
 #include <algorithm>
 #include <chrono>
@@ -105,11 +108,11 @@ int ctl_main(int argc, char** argv) {
 
 int usage() {
     std::fprintf(stderr,
-                 "usage: psb_node master [--threads N] [--port P] [--state-file FILE]\n"
+                 "usage: psb_node master [--threads N] [--port P] [--state-file FILE] [--host ADDR]\n"
                  "       psb_node ctl --master HOST:PORT VERB ...   (the controller; `psb_node ctl` lists the verbs)\n"
                  "       psb_node pserver --master HOST:PORT [--restore] [--restore-wait S] [--image-dir DIR] [--image-interval-ms N] [--report-interval S]\n"
                  "                        [--load-threads N] [--c2s-threads N] [--s2s-threads N] [--sync-master HOST:PORT] [--hadoop-bin PATH]\n"
-                 "                        [--metrics-port P] [--log-level debug|info|warning|error|off]\n");
+                 "                        [--metrics-port P] [--log-level debug|info|warning|error|off] [--host ADDR]\n");
     return 2;
 }
 }  // namespace
@@ -135,6 +138,7 @@ int main(int argc, char** argv) {
         if (a == "--master" && i + 1 < argc) master_addr = argv[++i];
         else if (a == "--sync-master" && i + 1 < argc) sync_master = argv[++i];
         else if (a == "--state-file" && i + 1 < argc) state_file = argv[++i];
+        else if (a == "--host" && i + 1 < argc) ::setenv("PSB_HOST", argv[++i], 1);   // before any server is created
         else if (a == "--port") { if (!next(&master_port)) return usage(); }
         else if (a == "--restore") restore = true;
         else if (a == "--image-dir" && i + 1 < argc) cfg.local_image_dir = argv[++i];

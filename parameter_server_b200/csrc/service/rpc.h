@@ -11,6 +11,7 @@
 // Frame: u32 payload_len | u64 request_id | u8 kind (0 request, 1 response) | payload bytes.
 #pragma once
 #include <arpa/inet.h>
+#include <netdb.h>
 #include <netinet/in.h>
 #include <netinet/tcp.h>
 #include <poll.h>
@@ -19,6 +20,7 @@
 
 #include <atomic>
 #include <chrono>
+#include <cstdlib>
 #include <condition_variable>
 #include <cstring>
 #include <deque>
@@ -37,6 +39,22 @@ namespace psb {
 using Bytes = std::vector<uint8_t>;
 
 namespace rpc_detail {
+// The address this process publishes for its servers: $PSB_HOST, else loopback.
+inline std::string local_host() {
+    const char* h = std::getenv("PSB_HOST");
+    return h && *h ? std::string(h) : std::string("127.0.0.1");
+}
+// Dotted address or host name -> IPv4 address.
+inline bool resolve(const std::string& host, in_addr* out) {
+    if (::inet_pton(AF_INET, host.c_str(), out) == 1) return true;
+    addrinfo hints{}, *res = nullptr;
+    hints.ai_family = AF_INET;
+    hints.ai_socktype = SOCK_STREAM;
+    if (::getaddrinfo(host.c_str(), nullptr, &hints, &res) != 0 || !res) return false;
+    *out = ((sockaddr_in*)res->ai_addr)->sin_addr;
+    ::freeaddrinfo(res);
+    return true;
+}
 inline bool read_full(int fd, void* buf, size_t n) {
     uint8_t* p = (uint8_t*)buf;
     while (n) {
@@ -122,7 +140,13 @@ public:
         ::setsockopt(listen_fd_, SOL_SOCKET, SO_REUSEADDR, &one, sizeof one);
         sockaddr_in addr{};
         addr.sin_family = AF_INET;
-        addr.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+        // One box is the default: listen on loopback. With $PSB_HOST (psb_node --host) set to this machine's address
+        // or name the servers listen on every interface and publish that address, so that masters, servers and
+        // clients may sit on different machines (the reference's deployment; its tests use localhost as well).
+        host_ = rpc_detail::local_host();
+        if (host_ == "127.0.0.1") addr.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+        else if (host_.compare(0, 4, "127.") == 0) ::inet_pton(AF_INET, host_.c_str(), &addr.sin_addr);
+        else addr.sin_addr.s_addr = htonl(INADDR_ANY);
         addr.sin_port = htons((uint16_t)port);
         if (::bind(listen_fd_, (sockaddr*)&addr, sizeof addr) != 0 || ::listen(listen_fd_, 256) != 0) {
             ::close(listen_fd_);
@@ -137,7 +161,7 @@ public:
     ~RpcServer() { stop(); }
 
     int port() const { return port_; }
-    std::string address() const { return "127.0.0.1:" + std::to_string(port_); }
+    std::string address() const { return host_ + ":" + std::to_string(port_); }
 
     void stop() {
         bool was = running_.exchange(false);
@@ -219,6 +243,7 @@ private:
     Handler handler_;
     DisconnectHandler on_disconnect_;
     int listen_fd_ = -1, port_ = 0;
+    std::string host_ = "127.0.0.1";
     std::atomic<bool> running_{true};
     std::atomic<uint64_t> next_conn_{0};
     std::thread accept_thread_;
@@ -339,7 +364,7 @@ private:
         sockaddr_in addr{};
         addr.sin_family = AF_INET;
         addr.sin_port = htons((uint16_t)std::stoi(address.substr(colon + 1)));
-        if (::inet_pton(AF_INET, address.substr(0, colon).c_str(), &addr.sin_addr) != 1) return nullptr;
+        if (!rpc_detail::resolve(address.substr(0, colon), &addr.sin_addr)) return nullptr;
         int fd = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
         if (fd < 0) return nullptr;
         if (::connect(fd, (sockaddr*)&addr, sizeof addr) != 0) {

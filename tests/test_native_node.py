@@ -212,3 +212,39 @@ def test_native_server_exports_prometheus_metrics():
         for p in procs:
             if p.poll() is None:
                 p.kill()
+
+
+@pytest.mark.skipif(not os.path.exists(NODE), reason="psb_node is not built")
+def test_processes_publish_the_address_they_are_given():
+    """--host (or $PSB_HOST): the address a process publishes for its servers. Another loopback address stands in for
+    another machine's address here; `localhost` checks that names are resolved."""
+    master = _spawn("master", "--host", "127.0.0.2")
+    procs = [master]
+    try:
+        addr = _first_line(master)
+        assert addr.startswith("127.0.0.2:")
+        server = _spawn("pserver", "--master", addr, "--host", "localhost")
+        procs.append(server)
+        line = _first_line(server)
+        node = int(line.split("node_id=")[1].split()[0])
+        assert "c2s=localhost:" in line and "s2s=localhost:" in line
+        client = S.Client(addr)
+        st, nodes = client.get_pserver_list()
+        assert st.ok() and nodes[node].startswith("localhost:")
+        st, sid = client.create_storage(S.LIB, "SparseTableStorageOperator",
+                                        S.storage_config({node: [0]}, dict(dim=4, optimizer="sum", init_range=0.0)))
+        assert st.ok(), st
+        _, h_push = client.register_handler("push", S.LIB, "SparseTablePushOperator", "{}", sid)
+        _, h_pull = client.register_handler("pull_ro", S.LIB, "SparseTablePullOperator", json.dumps({"read_only": True}), sid)
+        keys = np.arange(64, dtype=np.int64)
+        assert S.PushHandler(client, sid, h_push).async_push(keys, np.ones((64, 4), np.float32)).ok()
+        st, rows = S.PullHandler(client, sid, h_pull).pull(keys)
+        assert st.ok() and np.all(rows == 1.0)
+        assert client.close_pserver(node).ok()
+        assert server.wait(timeout=15) == 0
+        master.send_signal(signal.SIGTERM)
+        assert master.wait(timeout=15) == 0
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
