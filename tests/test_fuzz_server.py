@@ -156,3 +156,34 @@ def test_damaged_dump_files_are_reported_not_followed(tmp_path):
     finally:
         server.stop()
         master.stop()
+
+
+def test_master_refuses_a_damaged_state_file_and_reads_back_its_own(tmp_path):
+    import pytest
+    from parameter_server_b200 import service as S
+    path = tmp_path / "master.state"
+    m = S.Master(2, 0, str(path))
+    c = S.MasterClient(m.address())
+    assert c.generate_id("x")[1] == 0 and c.generate_id("x")[1] == 1
+    assert c.set_context("storage/7", '{"a": 1}').ok() and c.tree_node_set("model/m", "{}").ok()
+    m.stop()
+    again = S.Master(2, 0, str(path), 0)                      # no recovery window: answer at once
+    c2 = S.MasterClient(again.address())
+    assert c2.generate_id("x")[1] == 2 and c2.get_context("storage/7")[1] == '{"a": 1}' and c2.tree_node_get("model/m")[1] == "{}"
+    again.stop()
+    good = path.read_bytes()
+    rng = np.random.default_rng(3)
+    for trial in range(40):
+        raw = bytearray(good)
+        if trial % 2:
+            raw = raw[: int(rng.integers(1, len(raw)))]          # cut short
+        else:
+            for i in rng.integers(0, len(raw), size=4):
+                raw[int(i)] = int(rng.integers(0, 256))          # bytes flipped: lengths and counts go wild
+        path.write_bytes(bytes(raw))
+        try:
+            mm = S.Master(1, 0, str(path), 0)
+        except RuntimeError as e:
+            assert "master" in str(e)
+            continue
+        mm.stop()                                                  # damage that still parses is accepted: no crash either way
