@@ -201,6 +201,7 @@ void bind_service(py::module_& m) {
         .def("last_report", &Server::last_report)
         .def("save_local_images", [](Server& s) { int n = 0; Status st = s.save_local_images(&n); return std::make_tuple(st, n); }, nogil())
         .def("restore_storages", [](Server& s) { int n = 0; Status st = s.restore_storages(&n); return std::make_tuple(st, n); }, nogil())
+        .def("drop_master_session", &Server::drop_master_session, nogil())
         .def("restore_sources", &Server::restore_sources)
         .def("clean_local_images", [](Server& s) {
             int n = 0;

@@ -126,11 +126,30 @@ public:
             return;
         }
         if (stopped_) return;
+        // A node that the tables' contexts already call DEAD has been (or is about to be) replaced under a new id: it
+        // must stay out of the registry, or clients with an old context would find it again and read stale rows.
+        for (int32_t sid : ctx_.ids()) {
+            std::string json;
+            TableDescriptor td;
+            if (!session_.get_context(ctx_key(sid), &json).ok() || !td.from_json_str(json)) continue;
+            for (auto& n : td.nodes)
+                if (n.node_id == node_id_ && n.status == NodeStatus::DEAD) {
+                    if (!declared_dead_.exchange(true))
+                        PSB_LOG(ERROR) << "pserver node " << node_id_ << " lost its registration and storage " << sid
+                                       << " already counts it as dead: it stays out of the registry (start a server in restore mode)";
+                    return;
+                }
+        }
         int32_t same = -1;
         Status a = session_.register_node(PSERVER_S2S_RPC_NAME, s2s_->address(), &same, node_id_);
         Status b = session_.register_node(PSERVER_C2S_RPC_NAME, c2s_->address(), &same, node_id_);
         if (a.ok() && b.ok()) PSB_LOG(WARNING) << "pserver node " << node_id_ << " was missing from the master's registry and registered again";
     }
+
+    // Fault injection on the host: the connection to the master that carries this node's registration is closed, as
+    // a network fault between server and master would close it. The master forgets the node until ensure_registered
+    // puts it back.
+    void drop_master_session() { session_.close(); }
 
     // "node=.. requests=.. errors=.. storages=[sid:items:bytes ...]"
     std::string report_line() {
@@ -1231,6 +1250,7 @@ private:
     Context ctx_;
     std::unique_ptr<RpcServer> c2s_, s2s_;
     RpcClient s2s_client_;
+    std::atomic<bool> declared_dead_{false};
     std::thread reporter_, keeper_;
     std::mutex keeper_mu_;
     std::condition_variable keeper_cv_;

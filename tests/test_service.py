@@ -762,6 +762,51 @@ def test_runtime_log_lines_reach_python_logging(caplog):
         S.set_log_level("warning")
 
 
+def test_a_server_that_lost_its_master_session_registers_again_unless_it_was_declared_dead():
+    cfg = S.ServerConfig()
+    cfg.session_check_ms = 100
+    master = S.Master()
+    servers = [S.Server(master.address(), cfg) for _ in range(2)]
+    try:
+        client = S.Client(master.address())
+        ids = [s.node_id() for s in servers]
+        sid, h = make_table(type("C", (), {"client": client})(), {ids[0]: [0, 1], ids[1]: [0, 1]})
+        keys = np.arange(200, dtype=np.int64)
+        assert S.PushHandler(client, sid, h["push"]).async_push(keys, np.ones((200, DIM), np.float32)).ok()
+
+        def listed():
+            st, nodes = client.get_pserver_list()
+            return sorted(nodes) if st.ok() else None
+
+        # a dropped connection alone: the node is back in the registry within a few checks, nobody noticed
+        servers[0].drop_master_session()
+        deadline = time.time() + 5
+        while time.time() < deadline and listed() != sorted(ids):
+            time.sleep(0.02)
+        assert listed() == sorted(ids)
+        # the same fault, but this time a client sees the gap and publishes the node as DEAD before it is back:
+        # the node must stay out (a replacement will take its place under a new id)
+        slow = S.ServerConfig()
+        slow.session_check_ms = 1500
+        late = S.Server(master.address(), slow)
+        servers.append(late)
+        sid2, h2 = make_table(type("C", (), {"client": client})(), {late.node_id(): [0], ids[1]: [0]})
+        late.drop_master_session()
+        pull = S.PullHandler(client, sid2, h2["pull_ro"])
+        deadline = time.time() + 1.2
+        while time.time() < deadline:
+            assert pull.pull(keys, 5000, True)[0].ok()          # reads go on from the other replica; the gap gets noticed
+        td = S.TableDescriptor()
+        td.from_json_str(S.MasterClient(master.address()).get_context(f"storage/{sid2}")[1])
+        assert td.node_status()[late.node_id()] == 1               # DEAD in the published context
+        time.sleep(2.0)                                             # several checks of the late server pass
+        assert late.node_id() not in (listed() or [])
+    finally:
+        for s in servers:
+            s.stop()
+        master.stop()
+
+
 def test_available_server_list_excludes_stopped_nodes(cluster3):
     cl = cluster3
     st, nodes = cl.client.get_available_pserver_list()
