@@ -13,7 +13,9 @@
 // predictor must end up equal to the trainer. A sixth loads the trainer's dump into an in-process table with four
 // threads and reads it from four. A seventh sends malformed requests. An eighth closes servers by request and destroys
 // them the moment they report that they have left. In a ninth the sync thread of a server keeps a follower table equal
-// to a table that four threads push to. The sanitizers check the rest.
+// to a table that four threads push to. In a tenth a table sits at its memory limit while four threads push new keys:
+// items are parked, requests refused and sent again, the limit is raised under load, and every gradient counts once.
+// The sanitizers check the rest.
 #include <algorithm>
 #include <atomic>
 #include <cstdio>
@@ -555,6 +557,71 @@ int main() {
         syncer.stop();
         tr->stop();
         pr->stop();
+    }
+    // ---- phase 10: a table at its memory limit: pushes that hit it are parked, later ones refused and sent again, the
+    // limit is raised under load and the monitor thread drains what was parked - every gradient counts exactly once ----
+    {
+        ServerConfig mcfg;
+        mcfg.report_interval_s = 1;   // the monitor (and a status line on stderr per second)
+        std::unique_ptr<Server> srv(new Server(master.address(), mcfg));
+        Client c10(master.address());
+        int32_t msid = -1, mh_push = -1, mh_pull = -1;
+        MUST(c10.create_storage("psb", "SparseTableStorageOperator",
+                                "{\"nodes\":" + nodes_json({{srv->node_id(), {0, 1}}}) +
+                                    ",\"op_config\":{\"dim\":4,\"optimizer\":\"sum\",\"init_range\":0.0,\"memory_limit\":65536},\"table_name\":\"tight\"}",
+                                &msid));
+        MUST(c10.register_handler("push", "psb", "SparseTablePushOperator", "{}", msid, &mh_push));
+        MUST(c10.register_handler("pull_ro", "psb", "SparseTablePullOperator", "{\"read_only\":true}", msid, &mh_pull));
+        constexpr int kNew = 8000;   // about twice what fits under the first limit
+        std::vector<std::atomic<uint64_t>> sent10(kNew);
+        for (auto& x : sent10) x = 0;
+        std::atomic<int> bad10{0}, refused{0};
+        std::vector<std::thread> ts;
+        for (int t = 0; t < kThreads; ++t)
+            ts.emplace_back([&, t] {
+                PushHandler h(&c10, msid, mh_push);
+                std::vector<int64_t> keys(200);
+                std::vector<float> grads(keys.size() * kDim, 1.0f);
+                uint64_t x = 99 + (uint64_t)t * 31;
+                for (int it = 0; it < 12; ++it) {
+                    for (auto& k : keys) {
+                        x ^= x << 13; x ^= x >> 7; x ^= x << 17;
+                        k = (int64_t)(x % kNew);
+                    }
+                    Status st;
+                    for (int attempt = 0; attempt < 100; ++attempt) {
+                        st = h.async_push(keys.data(), grads.data(), keys.size(), 150);
+                        if (st.ok()) break;
+                        ++refused;
+                        std::this_thread::sleep_for(std::chrono::milliseconds(20));
+                    }
+                    if (!st.ok()) { std::fprintf(stderr, "phase 10 push: %s\n", st.msg().c_str()); ++bad10; continue; }
+                    for (auto k : keys) ++sent10[(size_t)k];
+                }
+            });
+        std::this_thread::sleep_for(std::chrono::milliseconds(1200));
+        {
+            auto e = srv->context().get(msid);
+            if (e && e->storage) e->storage->set_limits(1 << 24, 1 << 24);   // the operator gives the table more room
+        }
+        for (auto& t : ts) t.join();
+        std::this_thread::sleep_for(std::chrono::milliseconds(1500));      // one more monitor round drains the rest
+        std::vector<int64_t> all10(kNew);
+        for (int k = 0; k < kNew; ++k) all10[k] = k;
+        std::vector<float> got10((size_t)kNew * kDim);
+        Status pst;
+        for (int attempt = 0; attempt < 50; ++attempt) {
+            pst = PullHandler(&c10, msid, mh_pull).pull(all10.data(), all10.size(), got10.data(), 2000);
+            if (pst.ok()) break;
+            std::this_thread::sleep_for(std::chrono::milliseconds(100));
+        }
+        MUST(pst);
+        int wrong10 = bad10.load();
+        for (int k = 0; k < kNew; ++k)
+            if (got10[(size_t)k * kDim] != (float)sent10[k].load()) ++wrong10;
+        std::printf("phase 10: %d refusals on the way, %d wrong\n", refused.load(), wrong10);
+        wrong += wrong10;
+        srv->stop();
     }
     for (auto& s : servers) s->stop();
     master.stop();
