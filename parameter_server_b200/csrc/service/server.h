@@ -506,7 +506,13 @@ private:
         const size_t req_bytes = msg.ar.size();
         const auto t0 = std::chrono::steady_clock::now();
         try {
-            st = process(msg, &out, s2s);
+            // A node that the tables count as dead (see ensure_registered) answers data requests of clients from
+            // TIMEOUT, the status that makes a client look at the registry and the published context again; requests
+            // of other servers (a replacement fetching shards) and the admin's EXIT are still served.
+            const bool data_op = meta.req_type == RequestType::OP_PULL || meta.req_type == RequestType::OP_PUSH_ASYNC ||
+                                 meta.req_type == RequestType::OP_PUSH_SYNC || meta.req_type == RequestType::OP_STORE;
+            if (!s2s && data_op && declared_dead_.load()) st = Status::Timeout("node " + std::to_string(node_id_) + " has been replaced");
+            else st = process(msg, &out, s2s);
         } catch (const std::exception& ex) {
             st = Status::Error(std::string("server exception: ") + ex.what());
         }

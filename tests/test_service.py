@@ -799,8 +799,13 @@ def test_a_server_that_lost_its_master_session_registers_again_unless_it_was_dec
         td = S.TableDescriptor()
         td.from_json_str(S.MasterClient(master.address()).get_context(f"storage/{sid2}")[1])
         assert td.node_status()[late.node_id()] == 1               # DEAD in the published context
+        stale = S.Client(master.address())                          # a client that will not hear of the change by itself
         time.sleep(2.0)                                             # several checks of the late server pass
         assert late.node_id() not in (listed() or [])
+        # data requests that still reach the replaced node are turned away with the status that makes clients refresh
+        assert stale.initialize_storage(sid2).ok()
+        for _ in range(10):
+            assert S.PullHandler(stale, sid2, h2["pull_ro"]).pull(keys, 5000, True)[0].ok()
     finally:
         for s in servers:
             s.stop()
