@@ -89,3 +89,45 @@ def check(st) -> None:
     from ..utils.status import raise_if_error
 
     raise_if_error(st)
+
+
+class Pending:
+    """A handler call in flight: the start / ``wait()`` pattern of the reference's handlers
+    (pico-ps/handler/Handler.h:40-83: ``pull(...)`` sends, ``wait()`` blocks until the answers are in).
+
+    ``start(handler.pull, keys)`` returns at once; the call runs on a thread of its own (the bindings release the GIL
+    while they wait for the servers, so several calls really overlap), and ``wait()`` hands back what the call
+    returned or raises what it raised. One handler object carries one call at a time, as in the reference: use one
+    handler per call in flight.
+    """
+
+    def __init__(self, fn, *args, **kwargs):
+        import threading
+
+        self._result = None
+        self._error: Optional[BaseException] = None
+
+        def run():
+            try:
+                self._result = fn(*args, **kwargs)
+            except BaseException as e:  # noqa: BLE001 - handed to the waiter
+                self._error = e
+
+        self._thread = threading.Thread(target=run, daemon=True)
+        self._thread.start()
+
+    def done(self) -> bool:
+        return not self._thread.is_alive()
+
+    def wait(self, timeout: Optional[float] = None):
+        self._thread.join(timeout)
+        if self._thread.is_alive():
+            raise TimeoutError("the call is still in flight")
+        if self._error is not None:
+            raise self._error
+        return self._result
+
+
+def start(fn, *args, **kwargs) -> Pending:
+    """``start(PullHandler(...).pull, keys)`` -> :class:`Pending`."""
+    return Pending(fn, *args, **kwargs)

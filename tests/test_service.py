@@ -812,6 +812,24 @@ def test_a_server_that_lost_its_master_session_registers_again_unless_it_was_dec
         master.stop()
 
 
+def test_calls_in_flight_overlap_and_are_waited_for(cluster3):
+    """start(...) / wait(): pushes and pulls of several handlers are in flight together."""
+    cl = cluster3
+    sid, h = make_table(cl, uneven(cl.ids()))
+    keys = np.arange(3000, dtype=np.int64)
+    parts = np.array_split(keys, 6)
+    pending = [S.start(S.PushHandler(cl.client, sid, h["push"]).async_push, p, np.ones((len(p), DIM), np.float32)) for p in parts]
+    assert all(p.wait(30).ok() for p in pending)
+    pulls = [S.start(S.PullHandler(cl.client, sid, h["pull_ro"]).pull, p) for p in parts]
+    for p, part in zip(pulls, parts):
+        st, rows = p.wait(30)
+        assert st.ok() and rows.shape == (len(part), DIM) and np.all(rows == 1.0)
+    assert all(p.done() for p in pulls)
+    bad = S.start(S.PushHandler(cl.client, sid, h["push"]).async_push, keys, np.ones((5, DIM), np.float32))   # wrong shape
+    with pytest.raises(ValueError):
+        bad.wait(30)
+
+
 def test_available_server_list_excludes_stopped_nodes(cluster3):
     cl = cluster3
     st, nodes = cl.client.get_available_pserver_list()
