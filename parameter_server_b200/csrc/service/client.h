@@ -221,7 +221,10 @@ public:
         return broadcast(-1, RequestType::HEALTH_CHECK, {node}, Archive(), timeout_ms, -1);
     }
     Status close_pserver(int node, int timeout_ms = 5000) {
-        return broadcast(-1, RequestType::EXIT, {node}, Archive(), timeout_ms, -1);
+        Status st = broadcast(-1, RequestType::EXIT, {node}, Archive(), timeout_ms, -1);
+        std::lock_guard<std::mutex> g(nodes_mu_);
+        nodes_at_ = std::chrono::steady_clock::time_point();   // the registry has just changed
+        return st;
     }
     Status load_operator_library(const std::string& path, int timeout_ms = 30000) {
         PSB_RETURN_IF_ERROR(OperatorFactory::instance().load_library(path));

@@ -118,6 +118,7 @@ public:
     // master was restarted from its state file, or the session's connection broke), both services are registered
     // again under the same node id. A master that cannot be reached is simply asked again at the next check.
     void ensure_registered() {
+        if (leaving_) return;
         std::map<int32_t, std::string> nodes;
         if (!session_.get_nodes(PSERVER_S2S_RPC_NAME, &nodes).ok()) {
             // "recovering" is answered to everybody; registering is what the master waits for
@@ -125,7 +126,7 @@ public:
         } else if (nodes.count(node_id_)) {
             return;
         }
-        if (stopped_) return;
+        if (stopped_ || leaving_) return;
         // A node that the tables' contexts already call DEAD has been (or is about to be) replaced under a new id: it
         // must stay out of the registry, or clients with an old context would find it again and read stale rows.
         for (int32_t sid : ctx_.ids()) {
@@ -511,6 +512,13 @@ private:
             // of other servers (a replacement fetching shards) and the admin's EXIT are still served.
             const bool data_op = meta.req_type == RequestType::OP_PULL || meta.req_type == RequestType::OP_PUSH_ASYNC ||
                                  meta.req_type == RequestType::OP_PUSH_SYNC || meta.req_type == RequestType::OP_STORE;
+            if (meta.req_type == RequestType::EXIT) {
+                // leave the registry before the answer goes out: whoever asked this node to leave must not find it
+                // listed any more once the call has returned
+                leaving_ = true;
+                session_.deregister_node(PSERVER_C2S_RPC_NAME, node_id_);
+                session_.deregister_node(PSERVER_S2S_RPC_NAME, node_id_);
+            }
             if (!s2s && data_op && declared_dead_.load()) st = Status::Timeout("node " + std::to_string(node_id_) + " has been replaced");
             else st = process(msg, &out, s2s);
         } catch (const std::exception& ex) {
@@ -1256,7 +1264,7 @@ private:
     Context ctx_;
     std::unique_ptr<RpcServer> c2s_, s2s_;
     RpcClient s2s_client_;
-    std::atomic<bool> declared_dead_{false};
+    std::atomic<bool> declared_dead_{false}, leaving_{false};
     std::thread reporter_, keeper_;
     std::mutex keeper_mu_;
     std::condition_variable keeper_cv_;
