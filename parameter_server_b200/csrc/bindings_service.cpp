@@ -5,6 +5,7 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include "common/base64.h"
 #include "common/heap.h"
 #include "common/thread_sync.h"
 #include "controller/controller.h"
@@ -231,6 +232,26 @@ void bind_service(py::module_& m) {
             if (e && e->storage) e->storage->set_healthy(h);
         });
 
+    // binary values inside configs (compressed + base64) and the hex printer
+    m.def("base64_encode", [](py::bytes b) { std::string s = b; return base64_encode((const uint8_t*)s.data(), s.size()); });
+    m.def("base64_decode", [](const std::string& text) -> py::object {
+        std::vector<uint8_t> out;
+        if (!base64_decode(text, &out)) return py::none();
+        return py::bytes((const char*)out.data(), out.size());
+    });
+    m.def("add_base64_config", [](const std::string& conf_json, const std::string& key, py::bytes value) {
+        Json j = Json::parse_or_throw(conf_json);
+        std::string v = value;
+        Status st = add_base64_config(j, key, (const uint8_t*)v.data(), v.size());
+        if (!st.ok()) throw std::runtime_error(st.to_string());
+        return j.dump();
+    });
+    m.def("get_base64_config", [](const std::string& conf_json, const std::string& key) {
+        std::vector<uint8_t> out;
+        Status st = get_base64_config(Json::parse_or_throw(conf_json), key, &out);
+        return std::make_tuple(st, py::bytes((const char*)out.data(), out.size()));
+    });
+    m.def("byte2str", [](py::bytes b) { std::string s = b; return byte2str((const uint8_t*)s.data(), s.size()); });
     // logging of the host runtime: level by name ("debug", "info", "warning", "error", "off"); lines go to stderr or,
     // with a sink, to a Python callable (level: int, message: str) - e.g. a forwarder into the `logging` module
     m.def("set_log_level", [](const std::string& name) { set_log_level(log_detail::parse(name.c_str(), LogLevel::WARNING)); });

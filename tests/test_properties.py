@@ -210,3 +210,35 @@ def test_pushes_are_applied_exactly_once_whatever_inserts_fail(batches, period, 
         # parked gradients of one key are applied after later pushes of that key were refused and sent again, never
         # interleaved differently from the order of acceptance; Adagrad is order-sensitive only in rounding
         assert torch.allclose(got, want, rtol=1e-5, atol=1e-6)
+
+
+@settings(max_examples=150, deadline=None)
+@given(data=st.binary(max_size=3000))
+def test_base64_and_config_blobs_round_trip(data):
+    import base64
+    import json
+    text = C.base64_encode(data)
+    assert text == base64.b64encode(data).decode()              # the standard alphabet and padding
+    assert C.base64_decode(text) == data
+    conf = C.add_base64_config(json.dumps({"dim": 8}), "blob", data)
+    assert json.loads(conf)["dim"] == 8 and isinstance(json.loads(conf)["blob"], str)
+    status, back = C.get_base64_config(conf, "blob")
+    assert status.ok() and back == data
+    assert C.byte2str(data) == data.hex()
+
+
+@settings(max_examples=150, deadline=None)
+@given(text=st.text(alphabet="ABCDabcd0189+/=_ \n", max_size=40))
+def test_base64_decoder_refuses_what_is_not_base64(text):
+    import base64
+    import binascii
+    got = C.base64_decode(text)
+    try:
+        want = base64.b64decode(text, validate=True) if len(text) % 4 == 0 else None
+    except binascii.Error:
+        want = None
+    if want is None:
+        assert got is None
+    else:
+        assert got == want
+    assert not C.get_base64_config('{"k": 5}', "k")[0].ok() and not C.get_base64_config('{}', "k")[0].ok()
