@@ -195,8 +195,11 @@ public:
     void stop() {
         std::lock_guard<std::mutex> sg(stop_mu_);
         if (stopped_.exchange(true)) return;
+        // taking each mutex once orders the flag before the waiter's next look at it: no wake-up is lost
+        { std::lock_guard<std::mutex> g(report_mu_); }
         report_cv_.notify_all();
         if (reporter_.joinable()) reporter_.join();
+        { std::lock_guard<std::mutex> g(keeper_mu_); }
         keeper_cv_.notify_all();
         if (keeper_.joinable()) keeper_.join();   // before the session closes: it must not register us again
         session_.close();  // the master drops our registrations: we are gone
