@@ -59,6 +59,7 @@ public:
     // --- reading -------------------------------------------------------------------------
     void read_raw(void* p, size_t n) {
         if (n > buf_.size() - cur_) throw std::out_of_range("Archive::read_raw past end");  // no overflow: cur_ <= size
+        if (n == 0) return;   // an empty block may come with a null destination (an empty vector's data())
         std::memcpy(p, buf_.data() + cur_, n);
         cur_ += n;
     }
