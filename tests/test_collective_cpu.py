@@ -1,13 +1,20 @@
 """The collective API on the host back-end over gloo, 3 ranks, against a single-process oracle."""
 import os
+import socket
 import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def test_sparse_and_dense_tables_over_gloo():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
-           "--master-port", "29733", os.path.join(HERE, "mp_worker_cpu.py")]
+           "--master-port", str(_free_port()), os.path.join(HERE, "mp_worker_cpu.py")]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
     assert p.returncode == 0 and "cpu collective ok" in p.stdout, p.stdout[-2000:] + p.stderr[-3000:]
