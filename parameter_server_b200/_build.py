@@ -118,7 +118,8 @@ def build(jobs: int | None = None, force: bool = False, verbose: bool = False) -
     node = node_path()
     if todo or not node.exists():
         node.parent.mkdir(parents=True, exist_ok=True)
-        cmd = [NVCC, *ARCH, "-o", str(node), *[str(o) for o in node_objs], "-lpthread", "-ldl", "-lrt"]
+        # --export-dynamic: operator plug-ins bind to the executable's registry accessor (psb_operator_factory)
+        cmd = [NVCC, *ARCH, "-o", str(node), *[str(o) for o in node_objs], "-lpthread", "-ldl", "-lrt", "-Xlinker", "--export-dynamic"]
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
             print(p.stdout + p.stderr)

@@ -10,9 +10,22 @@ import importlib
 import os
 
 
-def _load():
+def _import_native():
+    # RTLD_GLOBAL: operator plug-ins opened later (load_operator_library) bind to the registry accessor that the
+    # module exports (its only symbol with default visibility besides the Python init and the C entry points)
+    import sys
+
+    flags = sys.getdlopenflags()
+    sys.setdlopenflags(flags | os.RTLD_GLOBAL)
     try:
         return importlib.import_module("parameter_server_b200._C")
+    finally:
+        sys.setdlopenflags(flags)
+
+
+def _load():
+    try:
+        return _import_native()
     except ImportError as first:
         import torch
 
@@ -25,7 +38,7 @@ def _load():
 
         _build.build()
         importlib.invalidate_caches()
-        return importlib.import_module("parameter_server_b200._C")
+        return _import_native()
 
 
 C = _load()

@@ -200,6 +200,7 @@ PYBIND11_MODULE(_C, m) {
     m.attr("FUSED_PREPARE_PUSH") = (unsigned)FUSED_PREPARE_PUSH;
     m.attr("FUSED_MEAN") = (unsigned)FUSED_MEAN;
     m.attr("FUSED_SYNC_PUSH") = (unsigned)FUSED_SYNC_PUSH;
+    m.attr("FUSED_OUT_BF16") = (unsigned)FUSED_OUT_BF16;
 
     py::class_<SparseEngine>(m, "SparseEngine")
         .def(py::init<GpuTable*, const SparseEngineConfig&>(), py::keep_alive<1, 2>())
@@ -215,11 +216,11 @@ PYBIND11_MODULE(_C, m) {
         .def("shard_owner", &SparseEngine::shard_owner)
         .def("pull",
              [](SparseEngine& e, uintptr_t keys, uint32_t n, uint32_t bag, uintptr_t out, unsigned flags, uintptr_t s) {
-                 return e.pull(ptr<const long long>(keys), n, bag, ptr<float>(out), flags, stream_of(s));
+                 return e.pull(ptr<const long long>(keys), n, bag, ptr<void>(out), flags, stream_of(s));
              })
         .def("push",
-             [](SparseEngine& e, uintptr_t grads, const OptConfig& o, unsigned flags, uintptr_t s) {
-                 return e.push(ptr<const float>(grads), o, flags, stream_of(s));
+             [](SparseEngine& e, uintptr_t grads, uint32_t n_rows, const OptConfig& o, unsigned flags, uintptr_t s) {
+                 return e.push(ptr<const float>(grads), n_rows, o, flags, stream_of(s));
              })
         .def("check", [](SparseEngine& e, uintptr_t s) { return e.check(stream_of(s)); })
         .def("reset", [](SparseEngine& e, uintptr_t s) { return e.reset(stream_of(s)); })
@@ -228,6 +229,9 @@ PYBIND11_MODULE(_C, m) {
         .def("scratch_bytes", &SparseEngine::scratch_bytes)
         .def("kernel_launches", &SparseEngine::kernel_launches)
         .def("set_wait_limit", &SparseEngine::set_wait_limit)
+        .def("set_cta_budget", &SparseEngine::set_cta_budget)
+        .def("pull_blocks", &SparseEngine::pull_blocks)
+        .def("push_blocks", &SparseEngine::push_blocks)
         .def("set_profile", &SparseEngine::set_profile)
         .def("phase_stamps", [](SparseEngine& e, uintptr_t s) { return e.phase_stamps(stream_of(s)); });
 

@@ -52,6 +52,7 @@ void bind_dense(py::module_& m) {
         .def("load_full", [](DenseEngine& e, uintptr_t full, uintptr_t s) { return e.load_full(ptr<const float>(full), (void*)s); })
         .def("step", [](DenseEngine& e, const OptConfig& o, float scale, uintptr_t s) { return e.step(o, scale, (void*)s); })
         .def("check", [](DenseEngine& e, uintptr_t s) { return e.check((void*)s); })
+        .def("reset", [](DenseEngine& e, uintptr_t s) { return e.reset((void*)s); })
         .def("kernel_launches", &DenseEngine::kernel_launches)
         .def("set_scatter_peers", &DenseEngine::set_scatter_peers);
 
@@ -120,6 +121,37 @@ void bind_dense(py::module_& m) {
           },
           py::arg("problems"), py::arg("a_mn"), py::arg("b_mn"), py::arg("err_flag") = 0, py::arg("wait_limit_s") = 2.0,
           py::arg("stream") = 0);
+
+    // layers: (a, lda, b, ldb, M, N, K, out_bf16, ldd, bias_bf16, relu, mask, ldmask); layer i + 1 must read layer i's output
+    m.def("gemm_bf16_chain",
+          [](const std::vector<std::tuple<uintptr_t, int64_t, uintptr_t, int64_t, int, int, int, uintptr_t, int64_t, uintptr_t, bool,
+                                          uintptr_t, int64_t>>& layers,
+             bool b_mn, uintptr_t chain_done, uintptr_t err_flag, double wait_limit_s, uintptr_t stream) {
+              const int n = (int)layers.size();
+              if (n > 8 || chain_done == 0) return -2;
+              GemmOperand A[8], B[8];
+              GemmEpilogue ep[8];
+              int M[8], N[8], K[8];
+              for (int i = 0; i < n; ++i) {
+                  const auto& t = layers[i];
+                  A[i] = GemmOperand{ptr<const void>(std::get<0>(t)), std::get<1>(t), false};
+                  B[i] = GemmOperand{ptr<const void>(std::get<2>(t)), std::get<3>(t), b_mn};
+                  M[i] = std::get<4>(t);
+                  N[i] = std::get<5>(t);
+                  K[i] = std::get<6>(t);
+                  ep[i].out_bf16 = ptr<__nv_bfloat16>(std::get<7>(t));
+                  ep[i].ldd = std::get<8>(t);
+                  ep[i].bias_bf16 = ptr<const __nv_bfloat16>(std::get<9>(t));
+                  ep[i].relu = std::get<10>(t) ? 1 : 0;
+                  ep[i].mask = ptr<const __nv_bfloat16>(std::get<11>(t));
+                  ep[i].ldmask = std::get<12>(t);
+              }
+              return gemm_bf16_grouped(A, B, ep, M, N, K, n, ptr<unsigned>(err_flag), wait_limit_s, (void*)stream,
+                                       ptr<unsigned>(chain_done));
+          },
+          py::arg("layers"), py::arg("b_mn"), py::arg("chain_done"), py::arg("err_flag") = 0, py::arg("wait_limit_s") = 2.0,
+          py::arg("stream") = 0);
+    m.def("gemm_chain_scratch_words", &gemm_chain_scratch_words);
 
     bind_model_kernels(m);
 }

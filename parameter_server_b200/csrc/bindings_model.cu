@@ -12,15 +12,21 @@ namespace py = pybind11;
 using namespace psb;
 
 void bind_model_kernels(py::module_& m) {
+    // emb_bf16: the embedding rows are bf16 (a pull with bf16 output) instead of fp32
     m.def("interaction_fwd", [](uintptr_t bottom, int64_t ldb, uintptr_t emb, int F, int D, uintptr_t out, int64_t ldo,
-                                int B, uintptr_t s) {
-        return interaction_fwd((const void*)bottom, ldb, (const float*)emb, F, D, (void*)out, ldo, B, (void*)s);
-    });
+                                int B, uintptr_t s, bool emb_bf16) {
+        return interaction_fwd((const void*)bottom, ldb, (const void*)emb, emb_bf16 ? 1 : 0, F, D, (void*)out, ldo, B, (void*)s);
+    }, py::arg("bottom"), py::arg("ldb"), py::arg("emb"), py::arg("F"), py::arg("D"), py::arg("out"), py::arg("ldo"),
+       py::arg("B"), py::arg("stream"), py::arg("emb_bf16") = false);
     m.def("interaction_bwd", [](uintptr_t dout, int64_t ldo, uintptr_t bottom, int64_t ldb, uintptr_t emb, int F, int D,
-                                uintptr_t dbottom, int64_t lddb, uintptr_t demb, int B, bool relu_mask, uintptr_t s) {
-        return interaction_bwd((const void*)dout, ldo, (const void*)bottom, ldb, (const float*)emb, F, D, (void*)dbottom,
-                               lddb, (float*)demb, B, relu_mask ? 1 : 0, (void*)s);
-    });
+                                uintptr_t dbottom, int64_t lddb, uintptr_t demb, int B, bool relu_mask, uintptr_t s,
+                                bool emb_bf16) {
+        return interaction_bwd((const void*)dout, ldo, (const void*)bottom, ldb, (const void*)emb, emb_bf16 ? 1 : 0, F, D,
+                               (void*)dbottom, lddb, (float*)demb, B, relu_mask ? 1 : 0, (void*)s);
+    }, py::arg("dout"), py::arg("ldo"), py::arg("bottom"), py::arg("ldb"), py::arg("emb"), py::arg("F"), py::arg("D"),
+       py::arg("dbottom"), py::arg("lddb"), py::arg("demb"), py::arg("B"), py::arg("relu_mask"), py::arg("stream"),
+       py::arg("emb_bf16") = false);
+    m.def("timestamp", [](uintptr_t slot, uintptr_t s) { return timestamp((unsigned long long*)slot, (void*)s); });
     m.def("bce_head", [](uintptr_t h, int64_t ldh, uintptr_t w, uintptr_t bias, uintptr_t y, int B, int K, float inv_batch,
                          uintptr_t loss_sum, uintptr_t logits, uintptr_t dz_prev, int64_t lddz, uintptr_t dw, uintptr_t db,
                          uintptr_t s) {

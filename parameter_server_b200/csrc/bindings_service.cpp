@@ -417,6 +417,16 @@ void bind_service(py::module_& m) {
             py::dict d;
             d["count"] = r.count; d["sum"] = r.sum; d["sum_sq"] = r.sum_sq; d["max_abs"] = r.max_abs;
             return py::make_tuple(st, d);
+        }, py::arg("carried") = "{}", py::arg("timeout_ms") = -1)
+        .def("for_each_raw", [](ForEachHandler& h, const std::string& carried, int timeout_ms) {
+            // the operator's own result bytes (a plug-in reducer defines the layout)
+            std::string raw;
+            Status st;
+            {
+                py::gil_scoped_release rel;
+                st = h.for_each_raw(carried, &raw, timeout_ms);
+            }
+            return py::make_tuple(st, py::bytes(raw));
         }, py::arg("carried") = "{}", py::arg("timeout_ms") = -1);
 
     py::class_<EraseIfHandler>(m, "EraseIfHandler")

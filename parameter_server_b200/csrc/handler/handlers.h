@@ -157,16 +157,27 @@ public:
             return Status::Ok();
         }, timeout_ms, auto_retry);
     }
-    // Dense pull: tensor `id` of `numel` floats, reassembled from its slices.
+    // Dense pull: tensor `id` of `numel` floats, reassembled from its slices. A DenseTablePullOperator decides the cut
+    // and the reassembly; a plain sparse pull operator gets the default (consecutive slices).
     Status pull_dense(int64_t id, size_t numel, float* out, int timeout_ms = -1) {
         auto e = entry();
         if (!e) return Status::InvalidID("storage is not initialised on this client");
         const uint32_t slice = storage_op_of(*e)->dim();
-        std::vector<int64_t> keys;
-        dense_slice_keys(id, numel, slice, &keys);
+        std::shared_ptr<SparseTablePullOperator> p;
+        PSB_RETURN_IF_ERROR(op(&p));
+        const auto* dp = dynamic_cast<const DenseTablePullOperator*>(p.get());
+        std::vector<DenseSlice> slices;
+        if (dp) dp->partition(id, numel, slice, &slices);
+        else dense_default_partition(id, numel, slice, &slices);
+        std::vector<int64_t> keys(slices.size());
+        for (size_t j = 0; j < slices.size(); ++j) keys[j] = slices[j].key;
         std::vector<float> tmp(keys.size() * slice);
         PSB_RETURN_IF_ERROR(pull(keys.data(), keys.size(), tmp.data(), timeout_ms));
-        std::copy_n(tmp.data(), numel, out);
+        for (size_t j = 0; j < slices.size(); ++j) {
+            if (slices[j].offset + slices[j].len > numel || slices[j].len > slice) return Status::Error("dense pull: the partitioner left the value");
+            if (dp) dp->merge(slices[j], tmp.data() + j * slice, out);
+            else std::copy_n(tmp.data() + j * slice, slices[j].len, out + slices[j].offset);
+        }
         return Status::Ok();
     }
     uint32_t dim() {
@@ -283,10 +294,20 @@ public:
         auto e = entry();
         if (!e) return Status::InvalidID("storage is not initialised on this client");
         const uint32_t slice = storage_op_of(*e)->dim();
-        std::vector<int64_t> keys;
-        dense_slice_keys(id, numel, slice, &keys);
-        std::vector<float> tmp(keys.size() * slice, 0.f);
-        std::copy_n(grad, numel, tmp.data());
+        std::shared_ptr<SparseTablePushOperator> p;
+        PSB_RETURN_IF_ERROR(op(&p));
+        const auto* dp = dynamic_cast<const DenseTablePushOperator*>(p.get());
+        std::vector<DenseSlice> slices;
+        if (dp) dp->partition(id, numel, slice, &slices);
+        else dense_default_partition(id, numel, slice, &slices);
+        std::vector<int64_t> keys(slices.size());
+        std::vector<float> tmp(slices.size() * slice, 0.f);
+        for (size_t j = 0; j < slices.size(); ++j) {
+            if (slices[j].offset + slices[j].len > numel || slices[j].len > slice) return Status::Error("dense push: the partitioner left the value");
+            keys[j] = slices[j].key;
+            if (dp) dp->extract(slices[j], grad, tmp.data() + j * slice);
+            else std::copy_n(grad + slices[j].offset, slices[j].len, tmp.data() + j * slice);
+        }
         return push(keys.data(), tmp.data(), keys.size(), sync ? RequestType::OP_PUSH_SYNC : RequestType::OP_PUSH_ASYNC, timeout_ms);
     }
 
@@ -396,10 +417,15 @@ private:
 class ForEachHandler : public Handler {
 public:
     using Handler::Handler;
-    // One request per (node, shard); results merged on the client.
-    Status for_each(const std::string& carried_json, ForEachResult* result, int timeout_ms = -1) {
+    // One request per (node, shard); the operator's merge_result folds the answers on the client
+    // (pico-ps/handler/ForEachHandler.cpp:16-46 wait_and_merge_result). *result holds the operator's bytes.
+    Status for_each_raw(const std::string& carried_json, std::string* result, int timeout_ms = -1) {
+        std::shared_ptr<ForEachOperatorBase> fop;
+        PSB_RETURN_IF_ERROR(op(&fop));
+        Json carried = Json::object();
+        if (!carried_json.empty() && !Json::parse(carried_json, &carried)) return Status::InvalidConfig("carried item is not JSON");
         return with_retry([&](int left) -> Status {
-            *result = ForEachResult();
+            *result = fop->init_result(carried);
             auto e = entry();
             std::vector<std::pair<int, int32_t>> targets;
             int32_t built_under = -1;
@@ -417,12 +443,19 @@ public:
                 body[t.first] << t.second << carried_json;
                 std::vector<NodeResponse> rs;
                 PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_FOREACH, body, left, &rs, built_under));
-                ForEachResult r;
-                rs[0].body >> r.count >> r.sum >> r.sum_sq >> r.max_abs;
-                result->merge(r);
+                std::string part;
+                rs[0].body >> part;
+                fop->merge_result(part, result);
             }
             return Status::Ok();
         }, timeout_ms);
+    }
+    // The built-in statistics operator, unpacked.
+    Status for_each(const std::string& carried_json, ForEachResult* result, int timeout_ms = -1) {
+        std::string raw;
+        PSB_RETURN_IF_ERROR(for_each_raw(carried_json, &raw, timeout_ms));
+        if (!ForEachResult::unpack(raw, result)) return Status::Error("for_each: the operator's result is not the built-in statistics record");
+        return Status::Ok();
     }
 };
 

@@ -100,11 +100,42 @@ struct KernelCtl {
     unsigned done_blocks;
     unsigned epoch;      // number of completed calls; a kernel runs as call epoch+1 and publishes it at its end,
                          // so a launch captured in a CUDA graph advances the epoch on every replay
-    unsigned pad[2];
+    unsigned soft;       // first NON-fatal condition (OUT_OF_MEMORY: a key without a row); the call still runs to
+                         // its end, so scratch state and epochs stay consistent; the host reports and clears it
+    unsigned soft_where;
+    unsigned arrive[4];  // "last CTA publishes" counters, one per hand-off point of a kernel
+    unsigned pad[4];
 };
 
+// Fatal: every CTA leaves at its next barrier. The word is sticky until the host resets the engine.
 __device__ __forceinline__ void set_status(KernelCtl* ctl, unsigned code, unsigned where) {
     if (atomicCAS(&ctl->status, 0u, code) == 0u) ctl->where = where;
+}
+// Non-fatal (memory pressure): recorded, the call completes. Reads of a row-less key see the initial value,
+// writes to it are dropped - the analogue of the reference answering OUT_OF_MEMORY while a shard's overflow
+// list is non-empty (pico-ps/operator/SparsePullOperator.h:195-199).
+__device__ __forceinline__ void set_soft_status(KernelCtl* ctl, unsigned code, unsigned where) {
+    if (atomicCAS(&ctl->soft, 0u, code) == 0u) ctl->soft_where = where;
+}
+
+// Hand-off without a grid barrier: every CTA calls this after its last store of a phase; it returns true
+// (uniformly per CTA) in the CTA that arrived last, which may then publish the phase's flags to the peers.
+// The fences make every CTA's stores visible system-wide before the flag can be written.
+__device__ __forceinline__ bool cta_arrive_last(unsigned* counter, unsigned nblocks) {
+    __shared__ unsigned s_last_arrival;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(counter, 1u);
+        const unsigned last = (prev == nblocks - 1u) ? 1u : 0u;
+        if (last) {
+            *((volatile unsigned*)counter) = 0;  // re-armed for the next call (ordered by the stream)
+            __threadfence_system();
+        }
+        s_last_arrival = last;
+    }
+    __syncthreads();
+    return s_last_arrival != 0u;
 }
 
 // Bounded grid-wide barrier for cooperative launches. Returns false (uniformly per CTA) when the
@@ -126,6 +157,11 @@ __device__ __forceinline__ bool grid_sync(KernelCtl* ctl, unsigned nblocks, unsi
             unsigned spins = 0;
             while (ld_acquire_gpu(&ctl->bar_gen) == gen) {
                 if ((++spins & 63u) == 0) {
+                    // a CTA that failed leaves without arriving: do not wait for it
+                    if (ld_acquire_gpu(&ctl->status) != 0u) {
+                        ok = 0;
+                        break;
+                    }
                     if (global_timer_ns() - t0 > limit_ns) {
                         set_status(ctl, kStTimeout, where);
                         ok = 0;

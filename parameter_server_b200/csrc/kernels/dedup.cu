@@ -18,8 +18,11 @@ namespace {
 
 constexpr int kThreads = 256;
 
+// Bit 31 of counts[0] is the error mark of a call: the scratch table was exhausted (it was not empty on entry:
+// two calls overlapped on it), a key equals one of the two reserved values, or a shard owner is outside
+// [0, world). Positions of such keys get inverse -1; everything else is still valid.
 __global__ void dedup_claim_kernel(const long long* __restrict__ keys, unsigned n, Slot* table, unsigned long long mask,
-                                   const int* __restrict__ shard_owner, int n_shards, long long* uniq_keys,
+                                   const int* __restrict__ shard_owner, int n_shards, int world, long long* uniq_keys,
                                    int* uniq_owner, unsigned* pos_slot, unsigned* counts) {
     const unsigned lane = threadIdx.x & 31u;
     const unsigned nthreads = gridDim.x * kThreads;
@@ -30,29 +33,38 @@ __global__ void dedup_claim_kernel(const long long* __restrict__ keys, unsigned 
         bool won = false;
         if (i < n) {
             key = keys[i];
-            h = slot_hash(key) & mask;
-            for (;;) {
-                long long cur = *((volatile long long*)&table[h].key);
-                if (cur == key) break;
-                if (cur == kEmptyKey) {
-                    long long prev = (long long)atomicCAS((unsigned long long*)&table[h].key, (unsigned long long)kEmptyKey,
-                                                          (unsigned long long)key);
-                    if (prev == kEmptyKey) { won = true; break; }
-                    if (prev == key) break;
+            bool found = false;
+            if (key > kTombstoneKey) {
+                h = slot_hash(key) & mask;
+                // every probe sequence ends: at most mask + 1 slots are examined
+                for (unsigned long long probes = 0; probes <= mask; ++probes) {
+                    long long cur = *((volatile long long*)&table[h].key);
+                    if (cur == key) { found = true; break; }
+                    if (cur == kEmptyKey) {
+                        long long prev = (long long)atomicCAS((unsigned long long*)&table[h].key, (unsigned long long)kEmptyKey,
+                                                              (unsigned long long)key);
+                        if (prev == kEmptyKey) { won = true; found = true; break; }
+                        if (prev == key) { found = true; break; }
+                    }
+                    h = (h + 1) & mask;
                 }
-                h = (h + 1) & mask;
             }
-            pos_slot[i] = (unsigned)h;
+            if (!found) atomicOr(&counts[0], kDedupErrorBit);
+            pos_slot[i] = found ? (unsigned)h : kNoSlot;
         }
         const unsigned wmask = __ballot_sync(0xffffffffu, won);
         if (wmask == 0) continue;
         unsigned base = 0;
         const int leader = __ffs(wmask) - 1;
-        if ((int)lane == leader) base = atomicAdd(&counts[0], (unsigned)__popc(wmask));
+        if ((int)lane == leader) base = atomicAdd(&counts[0], (unsigned)__popc(wmask)) & ~kDedupErrorBit;
         base = __shfl_sync(0xffffffffu, base, leader);
         if (won) {
             const unsigned u = base + __popc(wmask & ((1u << lane) - 1u));
-            const int owner = shard_owner ? shard_owner[sparse_shard_of(key, n_shards)] : 0;
+            int owner = shard_owner ? shard_owner[sparse_shard_of(key, n_shards)] : 0;
+            if (owner < 0 || owner >= world) {
+                atomicOr(&counts[0], kDedupErrorBit);
+                owner = 0;
+            }
             table[h].row = u;
             uniq_keys[u] = key;
             uniq_owner[u] = owner;
@@ -64,13 +76,13 @@ __global__ void dedup_claim_kernel(const long long* __restrict__ keys, unsigned 
 __global__ void dedup_inverse_kernel(unsigned n, Slot* table, const unsigned* __restrict__ pos_slot, int* inverse) {
     for (unsigned i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads) {
         const unsigned h = pos_slot[i];
-        inverse[i] = (int)table[h].row;
+        inverse[i] = (h == kNoSlot) ? -1 : (int)table[h].row;
     }
 }
 
 __global__ void dedup_clear_kernel(unsigned n, Slot* table, const unsigned* __restrict__ pos_slot) {
     for (unsigned i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads)
-        table[pos_slot[i]].key = kEmptyKey;
+        if (pos_slot[i] != kNoSlot) table[pos_slot[i]].key = kEmptyKey;
 }
 
 __global__ void dedup_fill_kernel(Slot* table, unsigned long long slots) {
@@ -99,8 +111,8 @@ int run(const long long* keys, unsigned n, Slot* table, unsigned long long slots
     if (e != cudaSuccess) return (int)e;
     if (n == 0) return 0;
     const int blocks = (int)((n + kThreads - 1) / kThreads) < 148 * 8 ? (int)((n + kThreads - 1) / kThreads) : 148 * 8;
-    dedup_claim_kernel<<<blocks, kThreads, 0, s>>>(keys, n, table, slots - 1, shard_owner, n_shards, uniq_keys, uniq_owner,
-                                                   pos_slot, counts);
+    dedup_claim_kernel<<<blocks, kThreads, 0, s>>>(keys, n, table, slots - 1, shard_owner, n_shards, world, uniq_keys,
+                                                   uniq_owner, pos_slot, counts);
     dedup_inverse_kernel<<<blocks, kThreads, 0, s>>>(n, table, pos_slot, inverse);
     dedup_clear_kernel<<<blocks, kThreads, 0, s>>>(n, table, pos_slot);
     return (int)cudaGetLastError();

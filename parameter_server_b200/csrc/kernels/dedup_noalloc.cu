@@ -4,6 +4,8 @@
 // device with cudaGetSymbolAddress (with that device current) and that pointer is what the kernels get.
 #include "dedup_noalloc.h"
 
+#include <mutex>
+
 #include "dedup.h"
 
 namespace psb {
@@ -21,6 +23,7 @@ struct PerDevice {
     unsigned* pos = nullptr;
 };
 PerDevice g_per_device[kMaxDevices];
+std::mutex g_setup_mutex;  // host threads making the first call on a device take turns at the set-up
 
 }  // namespace
 }  // namespace psb
@@ -37,14 +40,19 @@ extern "C" __attribute__((visibility("default"))) int psb_dedup_partition_noallo
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= kMaxDevices) return PSB_DEDUP_ERR_BAD_ARGUMENT;
-    PerDevice& d = g_per_device[dev];
-    if (!d.ready) {
-        // one-time set-up for this device: turn the symbols into device addresses
-        e = cudaGetSymbolAddress((void**)&d.slots, g_dedup_slots);
-        if (e != cudaSuccess) return (int)e;
-        e = cudaGetSymbolAddress((void**)&d.pos, g_dedup_pos);
-        if (e != cudaSuccess) return (int)e;
-        d.ready = true;
+    PerDevice d;
+    {
+        std::lock_guard<std::mutex> guard(g_setup_mutex);
+        PerDevice& slot = g_per_device[dev];
+        if (!slot.ready) {
+            // one-time set-up for this device: turn the symbols into device addresses
+            e = cudaGetSymbolAddress((void**)&slot.slots, g_dedup_slots);
+            if (e != cudaSuccess) return (int)e;
+            e = cudaGetSymbolAddress((void**)&slot.pos, g_dedup_pos);
+            if (e != cudaSuccess) return (int)e;
+            slot.ready = true;
+        }
+        d = slot;
     }
     // The array still holds the previous call's state (an interrupted call may have left claimed
     // slots): empty it first, in stream order with the work that follows.

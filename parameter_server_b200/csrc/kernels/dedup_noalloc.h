@@ -17,6 +17,13 @@
  *   - Every call on a device shares the one array, which still holds what the previous call left; the
  *     function empties it on the caller's stream before use. Two calls whose kernels overlap on the
  *     GPU (different streams without ordering, or different host threads) race on it: serialise them.
+ *     Such a race cannot hang a kernel (every probe loop is bounded by the size of the array); it shows
+ *     as wrong output or as the error mark below. The one-time address look-up is guarded by a mutex,
+ *     so host threads may make their first calls concurrently.
+ *   - Error mark: bit 31 of counts[0] (PSB_DEDUP_COUNT_ERROR_BIT) is set when the array was found
+ *     occupied (overlapping calls), when a key equals INT64_MIN or INT64_MIN + 1 (reserved), or when a
+ *     shard_owner entry lies outside [0, world). Positions of such keys get inverse -1. The call is
+ *     asynchronous, so the mark is read with the outputs; counts[0] & 0x7fffffff is the distinct count.
  *   - All pointers are device pointers valid on the current device; `stream` is a cudaStream_t.
  *
  * Outputs (same meaning as psb::dedup_partition): uniq_keys[n], uniq_owner[n] (first counts[0] entries are
@@ -30,6 +37,7 @@
 #define PSB_DEDUP_NOALLOC_MAX_KEYS 65536u
 #define PSB_DEDUP_ERR_TOO_LARGE (-10)
 #define PSB_DEDUP_ERR_BAD_ARGUMENT (-11)
+#define PSB_DEDUP_COUNT_ERROR_BIT 0x80000000u
 
 #ifdef __cplusplus
 extern "C" {

@@ -295,7 +295,13 @@ struct GemmProblemSet {
     int M[kMaxGroup], N[kMaxGroup], K[kMaxGroup];
     int unit_end[kMaxGroup];  // running total of work units (m tile x n tile x k split) up to and including problem i
     int count;
+    // Chain: problem i + 1 reads the output of problem i as its A operand (the layers of an MLP, forward or dgrad).
+    // done[i * kMaxChainMTiles + m] counts the epilogue warps that have stored their part of an n-tile of row block m
+    // of problem i; a unit of problem i + 1 waits until all of row block m is there. Zeroed before every launch.
+    int chain;
+    unsigned* done;
 };
+constexpr int kMaxChainMTiles = 1024;
 
 struct WorkUnit {
     int p;                    // problem index
@@ -318,10 +324,17 @@ __device__ __forceinline__ WorkUnit decode_unit(const GemmProblemSet& ps, int u,
     const int z = local / (m_tiles * n_tiles);
     const int rem = local - z * (m_tiles * n_tiles);
     int nt = rem / m_tiles;  // m fastest: CTAs that run together share the B tile in L2
+    int mt = rem % m_tiles;
+    if (ps.chain) {
+        // n fastest: a row block of this layer is complete after n_tiles consecutive units, so the next layer can
+        // start on it while this layer is still working on later row blocks (the weights stay in L2 either way)
+        nt = rem % n_tiles;
+        mt = rem / n_tiles;
+    }
     if (ag.enabled) nt = (nt + ag.rank * (ag.rows_per_rank / BN)) % n_tiles;  // local rows first, then ring order
     w.nt = nt;
     w.tile_n = nt * BN;
-    w.tile_m = (rem % m_tiles) * BM;
+    w.tile_m = mt * BM;
     w.kt_begin = z * kt_per;
     w.num_kt = max(0, min(total_kt - w.kt_begin, kt_per));
     return w;
@@ -407,6 +420,24 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                         if (!ok) break;
                         asm volatile("fence.proxy.async.global;" ::: "memory");
                     }
+                }
+                if (ps.chain && w.p > 0) {
+                    // the A operand is the previous layer's output: all n-tiles of this row block must be stored
+                    const int prev_n_tiles = (ps.N[w.p - 1] + BN - 1) / BN;
+                    const unsigned target = 4u * (unsigned)prev_n_tiles;  // four epilogue warps per tile
+                    const unsigned* cnt = ps.done + (size_t)(w.p - 1) * kMaxChainMTiles + w.tile_m / BM;
+                    const unsigned long long t0 = gtimer();
+                    unsigned spins = 0;
+                    while (ld_acquire_gpu_u32(cnt) < target) {
+                        if ((++spins & 63u) == 0 && gtimer() - t0 > limit_ns) {
+                            atomicCAS(err_flag, 0u, 7u);
+                            ok = false;
+                            break;
+                        }
+                    }
+                    if (!ok) break;
+                    // the rows were written with ordinary stores; the loads below go through the async proxy
+                    asm volatile("fence.proxy.async.global;" ::: "memory");
                 }
                 const CUtensorMap* map_a = &ps.map_a[w.p];
                 const CUtensorMap* map_b = &ps.map_b[w.p];
@@ -514,8 +545,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
             }
             // this warp is done reading the buffer: hand it back to the MMA warp
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            if (ps.chain) {
+                // publish this warp's 32 rows of the tile to the next layer: stores -> fence -> counter
+                __threadfence();
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+            }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+            if (lane == 0) {
+                mbar_arrive(&tempty_bar[buf]);
+                if (ps.chain) atomicAdd(ps.done + (size_t)w.p * kMaxChainMTiles + tile_m / BM, 1u);
+            }
             ++tc;
         }
     }
@@ -656,14 +695,18 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep
     const int BN = (N >= 256) ? 256 : 128;
     GemmProblemSet ps;
     ps.count = 1;
+    ps.chain = 0;
+    ps.done = nullptr;
     int rc = add_problem(&ps, 0, BN, A, B, ep, M, N, K);
     if (rc != 0) return rc;
     const unsigned long long lim = (unsigned long long)(wait_limit_s * 1e9);
     return (int)dispatch(BN, A.mn_major, B.mn_major, ps, err_flag, lim, (cudaStream_t)stream, ag);
 }
 
+int gemm_chain_scratch_words() { return kMaxGroup * kMaxChainMTiles; }
+
 int gemm_bf16_grouped(const GemmOperand* A, const GemmOperand* B, const GemmEpilogue* ep, const int* M, const int* N,
-                      const int* K, int count, unsigned* err_flag, double wait_limit_s, void* stream) {
+                      const int* K, int count, unsigned* err_flag, double wait_limit_s, void* stream, unsigned* chain_done) {
     if (count <= 0) return 0;
     if (count > kMaxGroup) return -2;
     int BN = 256;
@@ -674,6 +717,18 @@ int gemm_bf16_grouped(const GemmOperand* A, const GemmOperand* B, const GemmEpil
     }
     GemmProblemSet ps;
     ps.count = count;
+    ps.chain = chain_done != nullptr ? 1 : 0;
+    ps.done = chain_done;
+    if (ps.chain) {
+        // layer i + 1 consumes the bf16 output of layer i: same rows, K of the consumer = N of the producer
+        for (int i = 0; i < count; ++i) {
+            if (M[i] != M[0] || A[i].mn_major || ep[i].split_k > 1) return -2;
+            if (i > 0 && (K[i] != N[i - 1] || A[i].ptr != (const void*)ep[i - 1].out_bf16)) return -2;
+        }
+        if ((M[0] + BM - 1) / BM > kMaxChainMTiles) return -2;
+        cudaError_t e = cudaMemsetAsync(chain_done, 0, (size_t)count * kMaxChainMTiles * sizeof(unsigned), (cudaStream_t)stream);
+        if (e != cudaSuccess) return (int)e;
+    }
     for (int i = 0; i < count; ++i) {
         int rc = add_problem(&ps, i, BN, A[i], B[i], ep[i], M[i], N[i], K[i]);
         if (rc != 0) return rc;

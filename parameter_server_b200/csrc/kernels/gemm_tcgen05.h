@@ -51,7 +51,17 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep
 // Up to 8 independent GEMMs in ONE persistent launch (same operand majors for all; 128 x 256 tiles when every
 // N >= 256, else 128 x 128). Meant for work that becomes available together, e.g. the weight gradients of all
 // layers of an MLP at the end of the backward pass. Same return codes as gemm_bf16.
+//
+// With `chain_done` (device scratch of gemm_chain_scratch_words() unsigned, zeroed by the call) the problems form a
+// CHAIN: problem i + 1 takes the bf16 output of problem i as its A operand (the layers of an MLP in the forward
+// pass, or the dgrad sequence of the backward pass). All layers then run in this one launch: the work units are
+// ordered row block by row block, the epilogue counts the stored tiles of every row block, and the TMA producer
+// of the next layer waits (bounded) for the row block it is about to load, so the tail of one layer overlaps the
+// head of the next instead of paying a kernel boundary per layer. Every problem must have the same M and a
+// K-major A; split_k is not allowed.
 int gemm_bf16_grouped(const GemmOperand* A, const GemmOperand* B, const GemmEpilogue* ep, const int* M, const int* N,
-                      const int* K, int count, unsigned* err_flag, double wait_limit_s, void* stream);
+                      const int* K, int count, unsigned* err_flag, double wait_limit_s, void* stream,
+                      unsigned* chain_done = nullptr);
+int gemm_chain_scratch_words();
 
 }  // namespace psb

@@ -31,10 +31,48 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, cons
 
 constexpr int kIntWarps = 4;
 
+// Stage the F embedding rows of one sample into rows 1..F of the bf16 tile Ts (row stride LD elements).
+// fp32 rows are rounded here; bf16 rows (a pull that delivered the consumer's dtype) are copied 16 bytes a lane.
+template <int D, int LD>
+__device__ __forceinline__ void stage_emb(__nv_bfloat16* Ts, const float* __restrict__ eb, int F, int lane) {
+    for (int r = 0; r < F; ++r) {
+#pragma unroll
+        for (int d = lane * 4; d < D; d += 128) {
+            float4 v = *(const float4*)(eb + (size_t)r * D + d);
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+            uint2 pk;
+            pk.x = *(uint32_t*)&lo;
+            pk.y = *(uint32_t*)&hi;
+            *(uint2*)(Ts + (size_t)(r + 1) * LD + d) = pk;
+        }
+    }
+}
+template <int D, int LD>
+__device__ __forceinline__ void stage_emb(__nv_bfloat16* Ts, const __nv_bfloat16* __restrict__ eb, int F, int lane) {
+    constexpr int kLanesPerRow = D / 8;            // 16-byte pieces per row
+    constexpr int kRowsPerIter = 32 / kLanesPerRow;
+    const int sub = lane / kLanesPerRow, piece = lane % kLanesPerRow;
+    // the loads are independent: eight are issued back to back, then stored
+    constexpr int kBatch = 8;
+    for (int r0 = 0; r0 < F; r0 += kBatch * kRowsPerIter) {
+        uint4 v[kBatch];
+#pragma unroll
+        for (int it = 0; it < kBatch; ++it) {
+            const int r = r0 + it * kRowsPerIter + sub;
+            if (r < F) v[it] = *(const uint4*)(eb + (size_t)r * D + piece * 8);
+        }
+#pragma unroll
+        for (int it = 0; it < kBatch; ++it) {
+            const int r = r0 + it * kRowsPerIter + sub;
+            if (r < F) *(uint4*)(Ts + (size_t)(r + 1) * LD + piece * 8) = v[it];
+        }
+    }
+}
+
 // out[b] = [bottom (D) | dot(T_i, T_j) for i > j, row-major over i | 0 pad to ldo]
-template <int D>
+template <int D, typename EmbT>
 __global__ void __launch_bounds__(kIntWarps * 32) interaction_fwd_kernel(const __nv_bfloat16* __restrict__ bottom,
-                                                                         int64_t ldb, const float* __restrict__ emb, int F,
+                                                                         int64_t ldb, const EmbT* __restrict__ emb, int F,
                                                                          __nv_bfloat16* __restrict__ out, int64_t ldo,
                                                                          int B) {
     constexpr int LD = D + 8;  // bf16 elements per staged row (conflict-free fragment loads)
@@ -48,24 +86,13 @@ __global__ void __launch_bounds__(kIntWarps * 32) interaction_fwd_kernel(const _
     for (int idx = lane; idx < 32 * LD; idx += 32) Ts[idx] = __float2bfloat16_rn(0.f);
     __syncwarp();
     for (int b = blockIdx.x * kIntWarps + warp; b < B; b += gridDim.x * kIntWarps) {
-        // stage T: row 0 = bottom (bf16), rows 1..F = emb (fp32 -> bf16)
+        // stage T: row 0 = bottom (bf16), rows 1..F = emb
         for (int d = lane * 8; d < D; d += 256) {
             uint4 v = *(const uint4*)(bottom + (size_t)b * ldb + d);
             *(uint4*)(Ts + d) = v;
             *(uint4*)(Os + d) = v;
         }
-        const float* eb = emb + (size_t)b * F * D;
-        for (int r = 0; r < F; ++r) {
-#pragma unroll
-            for (int d = lane * 4; d < D; d += 128) {
-                float4 v = *(const float4*)(eb + (size_t)r * D + d);
-                __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-                uint2 pk;
-                pk.x = *(uint32_t*)&lo;
-                pk.y = *(uint32_t*)&hi;
-                *(uint2*)(Ts + (size_t)(r + 1) * LD + d) = pk;
-            }
-        }
+        stage_emb<D, LD>(Ts, emb + (size_t)b * F * D, F, lane);
         __syncwarp();
         // lower-triangular 16x8 tiles of the 32x32 Gram matrix: (mt, nt) with nt*8 < (mt+1)*16
         float acc[6][4];
@@ -114,44 +141,56 @@ __global__ void __launch_bounds__(kIntWarps * 32) interaction_fwd_kernel(const _
     }
 }
 
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* smem_row) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
 // dT = G T with G the symmetric (zero-diagonal) matrix of pair gradients.
 // d_bottom (bf16) = (dout[:, :D] + dT_0), masked by (bottom > 0) when relu_mask; d_emb (fp32) = dT_{1..F}.
-template <int D>
+// T is staged row-major ([j][d], as in the forward kernel, 16 bytes a lane); the B fragments of G x T, which want
+// the two k (= j) values of a register next to each other, come out of ldmatrix.trans, so no transposed copy of T
+// is ever written.
+template <int D, typename EmbT>
 __global__ void __launch_bounds__(kIntWarps * 32) interaction_bwd_kernel(const __nv_bfloat16* __restrict__ dout, int64_t ldo,
                                                                          const __nv_bfloat16* __restrict__ bottom,
-                                                                         int64_t ldb, const float* __restrict__ emb, int F,
+                                                                         int64_t ldb, const EmbT* __restrict__ emb, int F,
                                                                          __nv_bfloat16* __restrict__ dbottom, int64_t lddb,
                                                                          float* __restrict__ demb, int B, int relu_mask) {
-    constexpr int LG = 40;  // bf16 per row of G  (80 B: conflict-free fragment loads)
-    constexpr int LT = 34;  // bf16 per row of T^T (68 B: conflict-free transposed stores)
+    constexpr int LG = 40;     // bf16 per row of G (80 B: conflict-free fragment loads)
+    constexpr int LD = D + 8;  // bf16 per row of T (rows 16 bytes apart modulo 128: conflict-free ldmatrix)
     extern __shared__ __align__(16) unsigned char smem_i[];
+    __shared__ unsigned char s_pi[kMaxT * (kMaxT - 1) / 2], s_pj[kMaxT * (kMaxT - 1) / 2];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    __nv_bfloat16* Gs = (__nv_bfloat16*)smem_i + (size_t)warp * (32 * LG + D * LT);
-    __nv_bfloat16* Tt = Gs + 32 * LG;  // Tt[d][j] = T[j][d]
+    __nv_bfloat16* Ts = (__nv_bfloat16*)smem_i + (size_t)warp * (32 * LD + 32 * LG);
+    __nv_bfloat16* Gs = Ts + 32 * LD;
     const int nT = F + 1;
     const int npairs = nT * (nT - 1) / 2;
     const int g = lane >> 2, t = lane & 3;
-    for (int idx = lane; idx < 32 * LG + D * LT; idx += 32) Gs[idx] = __float2bfloat16_rn(0.f);
-    __syncwarp();
+    // pair index -> (i, j), i > j, once per CTA
+    for (int p = threadIdx.x; p < npairs; p += blockDim.x) {
+        int i = (int)((1.0f + sqrtf(1.0f + 8.0f * (float)p)) * 0.5f);
+        while (i * (i - 1) / 2 > p) --i;
+        while ((i + 1) * i / 2 <= p) ++i;
+        s_pi[p] = (unsigned char)i;
+        s_pj[p] = (unsigned char)(p - i * (i - 1) / 2);
+    }
+    for (int idx = lane; idx < 32 * LD + 32 * LG; idx += 32) Ts[idx] = __float2bfloat16_rn(0.f);
+    __syncthreads();
     for (int b = blockIdx.x * kIntWarps + warp; b < B; b += gridDim.x * kIntWarps) {
         const __nv_bfloat16* go = dout + (size_t)b * ldo;
         for (int p = lane; p < npairs; p += 32) {
-            int i = (int)((1.0f + sqrtf(1.0f + 8.0f * (float)p)) * 0.5f);
-            while (i * (i - 1) / 2 > p) --i;
-            while ((i + 1) * i / 2 <= p) ++i;
-            const int j = p - i * (i - 1) / 2;
+            const int i = s_pi[p], j = s_pj[p];
             const __nv_bfloat16 v = go[D + p];
             Gs[i * LG + j] = v;
             Gs[j * LG + i] = v;
         }
-        for (int d = lane; d < D; d += 32) Tt[d * LT] = bottom[(size_t)b * ldb + d];
-        const float* eb = emb + (size_t)b * F * D;
-        for (int r = 0; r < F; ++r) {
-#pragma unroll
-            for (int d = lane; d < D; d += 32) Tt[d * LT + r + 1] = __float2bfloat16_rn(eb[(size_t)r * D + d]);
-        }
+        for (int d = lane * 8; d < D; d += 256) *(uint4*)(Ts + d) = *(const uint4*)(bottom + (size_t)b * ldb + d);
+        stage_emb<D, LD>(Ts, emb + (size_t)b * F * D, F, lane);
         __syncwarp();
-        // A = G (row-major [i][j]), B(k = j, n = d) read as Tt[d][j]; M = 32, N = D, K = 32
+        // A = G (row-major [i][j]); M = 32, N = D, K = 32
         uint32_t a[2][2][4];
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt)
@@ -166,16 +205,14 @@ __global__ void __launch_bounds__(kIntWarps * 32) interaction_bwd_kernel(const _
         float* de = demb + (size_t)b * F * D;
 #pragma unroll 4
         for (int nt = 0; nt < D / 8; ++nt) {
+            // four 8x8 pieces of T: rows (= k) 0-7, 8-15, 16-23, 24-31 of columns nt*8 .. nt*8+7; lane l names row l
+            uint32_t bf[4];
+            ldmatrix_x4_trans(bf, Ts + (size_t)lane * LD + nt * 8);
             float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-            for (int ks = 0; ks < 2; ++ks) {
-                uint32_t bf[2];
-                const int k0 = ks * 16 + t * 2;
-                bf[0] = *(const uint32_t*)(Tt + (nt * 8 + g) * LT + k0);
-                bf[1] = *(const uint32_t*)(Tt + (nt * 8 + g) * LT + k0 + 8);
-                mma_bf16_16816(acc[0], a[0][ks], bf);
-                mma_bf16_16816(acc[1], a[1][ks], bf);
-            }
+            mma_bf16_16816(acc[0], a[0][0], bf);
+            mma_bf16_16816(acc[1], a[1][0], bf);
+            mma_bf16_16816(acc[0], a[0][1], bf + 2);
+            mma_bf16_16816(acc[1], a[1][1], bf + 2);
             const int d0 = nt * 8 + t * 2;
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt)
@@ -186,8 +223,8 @@ __global__ void __launch_bounds__(kIntWarps * 32) interaction_bwd_kernel(const _
                     if (i == 0) {
                         float r0 = v0 + __bfloat162float(go[d0]), r1 = v1 + __bfloat162float(go[d0 + 1]);
                         if (relu_mask) {
-                            if (!(__bfloat162float(Tt[d0 * LT]) > 0.f)) r0 = 0.f;
-                            if (!(__bfloat162float(Tt[(d0 + 1) * LT]) > 0.f)) r1 = 0.f;
+                            if (!(__bfloat162float(Ts[d0]) > 0.f)) r0 = 0.f;
+                            if (!(__bfloat162float(Ts[d0 + 1]) > 0.f)) r1 = 0.f;
                         }
                         *(__nv_bfloat162*)(dbottom + (size_t)b * lddb + d0) = __floats2bfloat162_rn(r0, r1);
                     } else if (i < nT) {
@@ -308,53 +345,66 @@ __global__ void cast_pad_kernel(const float* __restrict__ x, int B, int Kin, __n
     }
 }
 
-template <int D>
-int launch_int_fwd(const void* bottom, int64_t ldb, const float* emb, int F, void* out, int64_t ldo, int B, cudaStream_t s) {
+template <int D, typename EmbT>
+int launch_int_fwd(const void* bottom, int64_t ldb, const EmbT* emb, int F, void* out, int64_t ldo, int B, cudaStream_t s) {
     const size_t smem = (size_t)kIntWarps * 32 * (D + 8) * 2 + (size_t)kIntWarps * ldo * 2;
     static size_t configured = 0;
     if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(interaction_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(interaction_fwd_kernel<D, EmbT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
     const int blocks = std::min((B + kIntWarps - 1) / kIntWarps, 148 * 4);
-    interaction_fwd_kernel<D><<<blocks, kIntWarps * 32, smem, s>>>((const __nv_bfloat16*)bottom, ldb, emb, F,
-                                                                   (__nv_bfloat16*)out, ldo, B);
+    interaction_fwd_kernel<D, EmbT><<<blocks, kIntWarps * 32, smem, s>>>((const __nv_bfloat16*)bottom, ldb, emb, F,
+                                                                         (__nv_bfloat16*)out, ldo, B);
     return (int)cudaGetLastError();
 }
 
-template <int D>
-int launch_int_bwd(const void* dout, int64_t ldo, const void* bottom, int64_t ldb, const float* emb, int F, void* dbottom,
+template <int D, typename EmbT>
+int launch_int_bwd(const void* dout, int64_t ldo, const void* bottom, int64_t ldb, const EmbT* emb, int F, void* dbottom,
                    int64_t lddb, float* demb, int B, int relu_mask, cudaStream_t s) {
-    const size_t smem = (size_t)kIntWarps * (32 * 40 + D * 34) * 2;
+    const size_t smem = (size_t)kIntWarps * (32 * (D + 8) + 32 * 40) * 2;
     static size_t configured = 0;
     if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(interaction_bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(interaction_bwd_kernel<D, EmbT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    const int blocks = std::min((B + kIntWarps - 1) / kIntWarps, 148 * 4);
-    interaction_bwd_kernel<D><<<blocks, kIntWarps * 32, smem, s>>>((const __nv_bfloat16*)dout, ldo,
-                                                                   (const __nv_bfloat16*)bottom, ldb, emb, F,
-                                                                   (__nv_bfloat16*)dbottom, lddb, demb, B, relu_mask);
+    const int blocks = std::min((B + kIntWarps - 1) / kIntWarps, 148 * 5);
+    interaction_bwd_kernel<D, EmbT><<<blocks, kIntWarps * 32, smem, s>>>((const __nv_bfloat16*)dout, ldo,
+                                                                         (const __nv_bfloat16*)bottom, ldb, emb, F,
+                                                                         (__nv_bfloat16*)dbottom, lddb, demb, B, relu_mask);
     return (int)cudaGetLastError();
 }
 
 }  // namespace
 
 // bottom / out / dout / dbottom rows must be 16-byte aligned (ld multiples of 8), D in {64, 128}, F <= 31.
-int interaction_fwd(const void* bottom, int64_t ldb, const float* emb, int F, int D, void* out, int64_t ldo, int B,
-                    void* stream) {
+// emb is fp32 [B][F][D], or bf16 when emb_bf16 (what a pull with bf16 output delivers).
+int interaction_fwd(const void* bottom, int64_t ldb, const void* emb, int emb_bf16, int F, int D, void* out, int64_t ldo,
+                    int B, void* stream) {
     if ((D != 128 && D != 64) || F + 1 > kMaxT || (ldb % 8) || (ldo % 8) || ldo < D + (F + 1) * F / 2) return -2;
-    return D == 128 ? launch_int_fwd<128>(bottom, ldb, emb, F, out, ldo, B, (cudaStream_t)stream)
-                    : launch_int_fwd<64>(bottom, ldb, emb, F, out, ldo, B, (cudaStream_t)stream);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (emb_bf16) {
+        const __nv_bfloat16* e = (const __nv_bfloat16*)emb;
+        return D == 128 ? launch_int_fwd<128>(bottom, ldb, e, F, out, ldo, B, s) : launch_int_fwd<64>(bottom, ldb, e, F, out, ldo, B, s);
+    }
+    const float* e = (const float*)emb;
+    return D == 128 ? launch_int_fwd<128>(bottom, ldb, e, F, out, ldo, B, s) : launch_int_fwd<64>(bottom, ldb, e, F, out, ldo, B, s);
 }
 
-int interaction_bwd(const void* dout, int64_t ldo, const void* bottom, int64_t ldb, const float* emb, int F, int D,
-                    void* dbottom, int64_t lddb, float* demb, int B, int relu_mask, void* stream) {
-    if ((D != 128 && D != 64) || F + 1 > kMaxT || (lddb % 2)) return -2;
-    return D == 128 ? launch_int_bwd<128>(dout, ldo, bottom, ldb, emb, F, dbottom, lddb, demb, B, relu_mask, (cudaStream_t)stream)
-                    : launch_int_bwd<64>(dout, ldo, bottom, ldb, emb, F, dbottom, lddb, demb, B, relu_mask, (cudaStream_t)stream);
+int interaction_bwd(const void* dout, int64_t ldo, const void* bottom, int64_t ldb, const void* emb, int emb_bf16, int F,
+                    int D, void* dbottom, int64_t lddb, float* demb, int B, int relu_mask, void* stream) {
+    if ((D != 128 && D != 64) || F + 1 > kMaxT || (lddb % 2) || (ldb % 8)) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (emb_bf16) {
+        const __nv_bfloat16* e = (const __nv_bfloat16*)emb;
+        return D == 128 ? launch_int_bwd<128>(dout, ldo, bottom, ldb, e, F, dbottom, lddb, demb, B, relu_mask, s)
+                        : launch_int_bwd<64>(dout, ldo, bottom, ldb, e, F, dbottom, lddb, demb, B, relu_mask, s);
+    }
+    const float* e = (const float*)emb;
+    return D == 128 ? launch_int_bwd<128>(dout, ldo, bottom, ldb, e, F, dbottom, lddb, demb, B, relu_mask, s)
+                    : launch_int_bwd<64>(dout, ldo, bottom, ldb, e, F, dbottom, lddb, demb, B, relu_mask, s);
 }
 
 int bce_head(const void* h, int64_t ldh, const void* w, const void* bias, const float* y, int B, int K, float inv_batch,
@@ -385,6 +435,19 @@ int bias_grad_multi(BiasGradSet set, void* stream) {
     const int gy = std::max(1, std::min((set.M + 31) / 32, (148 * 4 + groups - 1) / groups));
     dim3 grid(groups, gy);
     bias_grad_multi_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(set);
+    return (int)cudaGetLastError();
+}
+
+__global__ void timestamp_kernel(unsigned long long* slot) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    *slot = t;
+}
+
+// Writes %globaltimer (ns) into *slot when the stream reaches this point: a tracing probe that also works inside a
+// captured CUDA graph, where events cannot be read back per replay.
+int timestamp(unsigned long long* slot, void* stream) {
+    timestamp_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(slot);
     return (int)cudaGetLastError();
 }
 

@@ -7,10 +7,11 @@ namespace pybind11 { class module_; }
 
 namespace psb {
 
-int interaction_fwd(const void* bottom, int64_t ldb, const float* emb, int F, int D, void* out, int64_t ldo, int B,
-                    void* stream);
-int interaction_bwd(const void* dout, int64_t ldo, const void* bottom, int64_t ldb, const float* emb, int F, int D,
-                    void* dbottom, int64_t lddb, float* demb, int B, int relu_mask, void* stream);
+// emb: fp32 [B][F][D], or bf16 when emb_bf16 != 0
+int interaction_fwd(const void* bottom, int64_t ldb, const void* emb, int emb_bf16, int F, int D, void* out, int64_t ldo,
+                    int B, void* stream);
+int interaction_bwd(const void* dout, int64_t ldo, const void* bottom, int64_t ldb, const void* emb, int emb_bf16, int F,
+                    int D, void* dbottom, int64_t lddb, float* demb, int B, int relu_mask, void* stream);
 int bce_head(const void* h, int64_t ldh, const void* w, const void* bias, const float* y, int B, int K, float inv_batch,
              float* loss_sum, float* logits, void* dz_prev, int64_t lddz, float* dw, float* db, void* stream);
 int bias_grad(const void* dz, int64_t ld, int M, int N, float* db, void* stream);
@@ -26,6 +27,7 @@ struct BiasGradSet {
 };
 int bias_grad_multi(BiasGradSet set, void* stream);
 int cast_pad(const float* x, int B, int Kin, void* out, int64_t ldo, void* stream);
+int timestamp(unsigned long long* slot, void* stream);
 
 }  // namespace psb
 

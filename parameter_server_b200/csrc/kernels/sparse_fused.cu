@@ -4,23 +4,30 @@
 //
 // fused_pull_kernel  (pico-ps/operator/SparsePullOperator.h:81-110 generate_request_data,
 //                     :112-154 generate_request, :156-254 apply_request, :278-304 fill_pull_items)
-//   P1  dedup the key batch in an open-addressing scratch table, partition the unique keys by
-//       jump_consistent_hash(murmur(key)) -> shard -> owning GPU, stage per-owner key lists
-//   P2  copy the staged lists into the owners' mailboxes (coalesced peer stores), publish count+flag
-//   P3  owner: wait for every source's flag; find-or-insert each received key in the local table,
-//       attach + initialise rows of new keys, store each row into the requesting GPU's row buffer
-//   P5  consumer: wait for every owner's flag; un-dedup and sum/mean-pool rows into the activation
-//       buffer; leave behind the "plan" (inverse map, per-owner lists, owner-side slots) for the push
+//   P1  dedup the key batch (warp-local match first, then an open-addressing scratch table), partition the
+//       unique keys by jump_consistent_hash(murmur(key)) -> shard -> owning GPU, stage per-owner key lists
+//   P2  copy the staged lists into the owners' mailboxes (coalesced peer stores); the CTA that finishes last
+//       publishes count + flag to every owner (no grid barrier)
+//   P3  owner: resolve the local requester's keys at once, then wait for every source's flag and resolve
+//       theirs: find-or-insert in the local table, attach + initialise rows of new keys, store each row
+//       (fp32, or bf16 when the consumer wants bf16) into the requesting GPU's row buffer; last CTA publishes
+//   P5  consumer: resolve position -> row while the remote rows are in flight, wait for every owner's flag,
+//       un-dedup and sum/mean-pool rows into the activation buffer; leave behind the "plan" (inverse map,
+//       per-owner lists, owner-side slots) for the push
 // fused_push_kernel  (pico-ps/operator/SparsePushOperator.h:109-154 generate_request_data,
 //                     :197-276 async apply, :278-320 sync apply, :377-409 merge before store)
+//   Q0  owner: chain the received entries that name the same table row (one entry per source rank)
 //   Q1  segment-sum the gradients of duplicate keys into one row per unique key
-//   Q2  store the merged (key-ordered) gradient rows into the owners' mailboxes, publish flag
-//   Q3  owner: wait for every source; elect one leader entry per table row (lowest source rank), fold
-//       the other ranks' gradients into it, apply the optimizer once per row (or accumulate into the
-//       sync-push delta section), acknowledge the sources
+//   Q2  store the merged gradient rows into the owners' mailboxes, last CTA publishes the flag
+//   Q3  owner: wait for every source; the head entry of each row's chain folds the sources' gradients in
+//       rank order (reproducible) and applies the optimizer once per row (or accumulates into the sync-push
+//       delta section); last CTA acknowledges the sources
 // A kernel on one GPU waits for kernels on the other GPUs; each GPU runs exactly one of them per
-// call, all waits are bounded, and with world == 1 no cross-GPU wait is executed at all.
+// call, all waits are bounded, and with world == 1 no cross-GPU wait is executed at all. The grid is a
+// parameter: a full-residency grid when the kernel runs alone, a bounded CTA budget when it shares the SMs
+// with the dense GEMMs of the same training step on another stream.
 #include <cooperative_groups.h>
+#include <cuda_bf16.h>
 
 #include "sparse_fused.h"
 
@@ -31,19 +38,15 @@ namespace {
 constexpr int kThreads = 256;
 // block-local accumulation of hot gradient rows in the push (Q1)
 constexpr int kHotSlots = 512;   // shared-memory counting table per CTA
-constexpr int kHotRows = 24;     // rows cached per CTA
+constexpr int kHotRows = 24;     // most rows cached per CTA (FusedArgs::hot_rows chooses; dynamic shared memory)
 constexpr unsigned kHotMaxDim = 128;
 constexpr size_t kPushSmemBytes = (size_t)kHotRows * kHotMaxDim * sizeof(float);
 
 enum Where : unsigned {
     W_P1 = 1, W_P2, W_KEYFLAG, W_P3A, W_P3B, W_P3C, W_ROWFLAG, W_MAILBOX_OVERFLOW, W_INDEX_FULL, W_POOL_FULL,
+    W_DEDUP_FULL, W_RESERVED_KEY,
     W_Q1 = 32, W_ACK, W_Q2, W_GRADFLAG, W_Q3A, W_Q3B, W_NOROW,
 };
-
-__device__ __forceinline__ void copy_row(float* __restrict__ dst, const float* __restrict__ src, unsigned dim,
-                                         unsigned lane, unsigned lanes) {
-    for (unsigned d = lane * 4; d < dim; d += lanes * 4) *(float4*)(dst + d) = *(const float4*)(src + d);
-}
 
 __device__ __forceinline__ float4 init4(const TableView& t, long long key, unsigned d) {
     float4 v;
@@ -52,6 +55,14 @@ __device__ __forceinline__ float4 init4(const TableView& t, long long key, unsig
     v.z = init_uniform(key, d + 2, t.init_seed, t.init_range);
     v.w = init_uniform(key, d + 3, t.init_seed, t.init_range);
     return v;
+}
+
+__device__ __forceinline__ uint2 pack_bf16x4(const float4& v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 p;
+    p.x = *(const unsigned*)&lo;
+    p.y = *(const unsigned*)&hi;
+    return p;
 }
 
 // Each CTA waits until every peer's flag in `flags` (local memory, written remotely) reached `target`.
@@ -64,8 +75,15 @@ __device__ __forceinline__ bool wait_all_flags(const unsigned* flags, unsigned t
             ok = 0;
         }
     }
+    if (ld_acquire_gpu(&a.ctl->status) != 0u) ok = 0;
     return __syncthreads_and(ok) != 0;
 }
+
+// Row source of one key position in P5.
+struct RowSrc {
+    const float* f32;            // table row or fp32 row returned by a remote owner
+    const __nv_bfloat16* b16;    // bf16 row returned by a remote owner
+};
 
 }  // namespace
 
@@ -76,51 +94,73 @@ __device__ __forceinline__ bool wait_all_flags(const unsigned* flags, unsigned t
         if (a.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 0) a.prof[slot] = global_timer_ns(); \
     } while (0)
 
-__global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a) {
+__global__ void __launch_bounds__(kThreads, 4) fused_pull_kernel(const FusedArgs a) {
     const unsigned nblocks = gridDim.x;
     const unsigned tid = blockIdx.x * kThreads + threadIdx.x;
     const unsigned nthreads = nblocks * kThreads;
+    // a fatal status of an earlier call stays until the host resets the engine: do nothing, touch nothing
+    if (ld_acquire_gpu(&a.ctl->status) != 0u) return;
     const unsigned epoch = *((volatile unsigned*)&a.ctl->epoch) + 1u;
     const unsigned par = epoch & 1u;
     unsigned* cnt = a.counters + par * 16;
     unsigned* send_cnt = cnt + 4;
     unsigned* in_cnt = a.in_cnt + par * kMaxWorld;
     const int me = a.rank;
+    const int W = a.world;
     const unsigned C = a.C;
     const TableView& T = a.table;
     const PeerBufs& mine = a.peer[me];
     const unsigned lanes = lanes_for_dim(a.dim);
     const unsigned group = tid / lanes, ngroups = nthreads / lanes, lane = tid % lanes;
+    const bool out16 = (a.flags & FUSED_OUT_BF16) != 0;
+    const bool rows16 = out16 && a.bag_size == 1;  // remote rows travel as bf16
 
     __shared__ unsigned s_pre[kMaxWorld + 1];
 
     // ---- P1: dedup + partition ------------------------------------------------------------------
-    // Counters are bumped once per warp and owner (ballot / match), not once per key: same-address
-    // atomics serialise in L2 and would otherwise bound the phase.
+    // Duplicates inside a warp are folded with a match before anything touches memory (the head of a Zipf
+    // batch otherwise sends many lanes to one slot); counters are bumped once per warp and owner (ballot /
+    // match), not once per key: same-address atomics serialise in L2 and would otherwise bound the phase.
     PROF(0);
     const unsigned wlane = threadIdx.x & 31u;
+    const unsigned long long probe_limit = a.dmask + 1ull;
     for (unsigned i0 = (tid & ~31u); i0 < a.n; i0 += nthreads) {
         const unsigned i = i0 + wlane;
-        const bool active = i < a.n;
-        long long key = 0;
-        unsigned long long h = 0;
-        bool won = false;
+        bool active = i < a.n;
+        long long key = kEmptyKey;
         if (active) {
             key = a.keys[i];
-            h = slot_hash(key) & a.dmask;
-            for (;;) {
-                long long cur = *((volatile long long*)&a.dedup[h].key);
+            if (key <= kTombstoneKey) {  // the two reserved values can never be stored
+                set_status(a.ctl, kStError, W_RESERVED_KEY);
+                active = false;
+                key = kEmptyKey;
+            }
+        }
+        const unsigned same = __match_any_sync(0xffffffffu, key);
+        const int klead = __ffs(same) - 1;
+        unsigned h = 0;
+        bool won = false;
+        if (active && (int)wlane == klead) {
+            unsigned long long hh = slot_hash(key) & a.dmask;
+            unsigned long long probes = 0;
+            for (; probes < probe_limit; ++probes) {
+                long long cur = *((volatile long long*)&a.dedup[hh].key);
                 if (cur == key) break;
                 if (cur == kEmptyKey) {
-                    long long prev = (long long)atomicCAS((unsigned long long*)&a.dedup[h].key,
+                    long long prev = (long long)atomicCAS((unsigned long long*)&a.dedup[hh].key,
                                                           (unsigned long long)kEmptyKey, (unsigned long long)key);
                     if (prev == kEmptyKey) { won = true; break; }
                     if (prev == key) break;
                 }
-                h = (h + 1) & a.dmask;  // dedup table holds >= 2n slots: an empty slot always exists
+                hh = (hh + 1) & a.dmask;
             }
-            a.pos_slot[i] = (unsigned)h;
+            // the table holds >= 2n slots and is emptied by every call; a full table means an earlier call was
+            // cut short or two calls overlap on one engine
+            if (probes == probe_limit) set_status(a.ctl, kStError, W_DEDUP_FULL);
+            h = (unsigned)hh;
         }
+        h = __shfl_sync(0xffffffffu, h, klead);
+        if (active) a.pos_slot[i] = h;
         const unsigned wmask = __ballot_sync(0xffffffffu, won);
         if (wmask == 0) continue;
         const int owner = won ? a.shard_owner[sparse_shard_of(key, a.n_shards)] : -1;
@@ -145,28 +185,28 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
                 set_status(a.ctl, kStError, W_MAILBOX_OVERFLOW);
             }
             a.dedup[h].row = u;
-            a.uniq_slot[u] = (unsigned)h;
-            a.uniq_row[u] = (owner == me) ? kNoRow : kRemoteRow;
+            a.uniq_slot[u] = h;
+            a.uniq_row[u] = (owner == me) ? kNoSlot : kRemoteRow;
         }
     }
     if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P1)) return;
 
     // ---- P2: ship staged key lists to the owners ------------------------------------------------
     PROF(1);
-    if (a.world > 1) {
+    if (W > 1) {
         if (threadIdx.x == 0) {
             unsigned acc = 0;
-            for (int o = 0; o < a.world; ++o) {
+            for (int o = 0; o < W; ++o) {
                 s_pre[o] = acc;
                 acc += (o == me) ? 0u : min(send_cnt[o], C);
             }
-            s_pre[a.world] = acc;
+            s_pre[W] = acc;
         }
         __syncthreads();
-        const unsigned total = s_pre[a.world];
+        const unsigned total = s_pre[W];
         // every rank starts with its right-hand neighbour and walks the ring, so that at any moment the ranks
         // write to different peers (starting at peer 0 everywhere would funnel all traffic into one link)
-        const unsigned rot = s_pre[(me + 1) % a.world];
+        const unsigned rot = s_pre[(me + 1) % W];
         for (unsigned e0 = tid; e0 < total; e0 += nthreads) {
             unsigned e = e0 + rot;
             if (e >= total) e -= total;
@@ -176,65 +216,80 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
             a.peer[o].mail_keys[(size_t)me * C + p] = a.send_keys[(size_t)o * C + p];
             a.peer[o].mail_ret[(size_t)me * C + p] = a.send_ret[(size_t)o * C + p];
         }
-        __threadfence_system();
-        if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P2)) return;
-        if (blockIdx.x == 0 && threadIdx.x < (unsigned)a.world && (int)threadIdx.x != me) {
-            const int o = threadIdx.x;
-            a.peer[o].key_cnt[me] = min(send_cnt[o], C);
-            __threadfence_system();
-            st_release_sys(&a.peer[o].key_flag[me], epoch);
+        if (cta_arrive_last(&a.ctl->arrive[0], nblocks)) {
+            if (threadIdx.x < (unsigned)W && (int)threadIdx.x != me) {
+                const int o = threadIdx.x;
+                a.peer[o].key_cnt[me] = min(send_cnt[o], C);
+                __threadfence_system();
+                st_release_sys(&a.peer[o].key_flag[me], epoch);
+            }
         }
-        // ---- P3 (owner): wait for every source's keys
-        if (!wait_all_flags(mine.key_flag, epoch, a, W_KEYFLAG)) return;
+        __syncthreads();  // s_pre is rewritten below
     }
-    if (threadIdx.x == 0) {
-        unsigned acc = 0;
-        for (int r = 0; r < a.world; ++r) {
-            s_pre[r] = acc;
-            unsigned c = (r == me) ? min(send_cnt[me], C) : min(ld_relaxed_sys(&mine.key_cnt[r]), C);
-            acc += c;
-        }
-        s_pre[a.world] = acc;
-    }
-    __syncthreads();
-    const unsigned total_in = s_pre[a.world];
-    if (blockIdx.x == 0 && threadIdx.x < (unsigned)a.world)
-        in_cnt[threadIdx.x] = s_pre[threadIdx.x + 1] - s_pre[threadIdx.x];
 
-    // ---- P3a: resolve received keys in the local table ------------------------------------------
+    // ---- P3a: resolve keys in the local table: the local requester's list first (nothing to wait for), then
+    // the lists of the other source ranks as one flattened range ---------------------------------------
     const bool do_insert = (a.flags & FUSED_INSERT) != 0;
     PROF(2);
-    for (unsigned e0 = (tid & ~31u); e0 < total_in; e0 += nthreads) {
-        const unsigned e = e0 + wlane;
-        bool attached = false, inserted = false;
-        unsigned slot = kNoSlot;
-        if (e < total_in) {
-            int r = 0;
-            while (e >= s_pre[r + 1]) ++r;
-            const unsigned p = e - s_pre[r];
-            const long long key = (r == me) ? a.send_keys[(size_t)me * C + p] : mine.mail_keys[(size_t)r * C + p];
-            slot = table_find_or_insert(T, key, do_insert, &inserted);
-            if (slot == kNoSlot) {
-                if (do_insert) set_status(a.ctl, kStOom, W_INDEX_FULL);
-            } else if (do_insert) {
-                bool oom = false;
-                attached = table_attach_row(T, slot, &oom);
-                if (oom) set_status(a.ctl, kStOom, W_POOL_FULL);
+    for (int pass = 0; pass < (W > 1 ? 2 : 1); ++pass) {
+        unsigned total_e;
+        if (pass == 0) {
+            total_e = min(send_cnt[me], C);
+        } else {
+            if (!wait_all_flags(mine.key_flag, epoch, a, W_KEYFLAG)) return;
+            if (threadIdx.x == 0) {
+                unsigned acc = 0;
+                for (int r = 0; r < W; ++r) {
+                    s_pre[r] = acc;
+                    acc += (r == me) ? 0u : min(ld_relaxed_sys(&mine.key_cnt[r]), C);
+                }
+                s_pre[W] = acc;
             }
-            a.res_slot[(size_t)r * C + p] = slot;
+            __syncthreads();
+            total_e = s_pre[W];
+            if (blockIdx.x == 0 && threadIdx.x < (unsigned)W)
+                in_cnt[threadIdx.x] = ((int)threadIdx.x == me) ? min(send_cnt[me], C)
+                                                               : s_pre[threadIdx.x + 1] - s_pre[threadIdx.x];
         }
-        // list of freshly attached rows and the live-key counter: one atomic per warp each
-        const unsigned amask = __ballot_sync(0xffffffffu, attached);
-        if (amask) {
-            const int al = __ffs(amask) - 1;
-            unsigned base = 0;
-            if ((int)wlane == al) base = atomicAdd(&cnt[1], (unsigned)__popc(amask));
-            base = __shfl_sync(0xffffffffu, base, al);
-            if (attached) a.new_list[base + __popc(amask & ((1u << wlane) - 1u))] = slot;
+        for (unsigned e0 = (tid & ~31u); e0 < total_e; e0 += nthreads) {
+            const unsigned e = e0 + wlane;
+            bool attached = false, inserted = false;
+            unsigned slot = kNoSlot;
+            if (e < total_e) {
+                int r = me;
+                unsigned p = e;
+                if (pass == 1) {
+                    r = 0;
+                    while (e >= s_pre[r + 1]) ++r;
+                    p = e - s_pre[r];
+                }
+                const long long key = (r == me) ? a.send_keys[(size_t)me * C + p] : mine.mail_keys[(size_t)r * C + p];
+                slot = table_find_or_insert(T, key, do_insert, &inserted);
+                if (slot == kNoSlot) {
+                    if (do_insert) set_soft_status(a.ctl, kStOom, W_INDEX_FULL);
+                } else if (do_insert) {
+                    bool oom = false;
+                    attached = table_attach_row(T, slot, &oom);
+                    if (oom) set_soft_status(a.ctl, kStOom, W_POOL_FULL);
+                }
+                a.res_slot[(size_t)r * C + p] = slot;
+                // a local requester reads the table directly in P5: it only needs the slot
+                if (r == me) a.uniq_row[a.send_ret[(size_t)me * C + p]] = slot;
+            }
+            // list of freshly attached rows and the live-key counter: one atomic per warp each
+            const unsigned amask = __ballot_sync(0xffffffffu, attached);
+            if (amask) {
+                const int al = __ffs(amask) - 1;
+                unsigned base = 0;
+                if ((int)wlane == al) base = atomicAdd(&cnt[1], (unsigned)__popc(amask));
+                base = __shfl_sync(0xffffffffu, base, al);
+                if (attached) a.new_list[base + __popc(amask & ((1u << wlane) - 1u))] = slot;
+            }
+            const unsigned imask = __ballot_sync(0xffffffffu, inserted);
+            if (imask && (int)wlane == __ffs(imask) - 1) atomicAdd(T.n_items, (unsigned long long)__popc(imask));
         }
-        const unsigned imask = __ballot_sync(0xffffffffu, inserted);
-        if (imask && (int)wlane == __ffs(imask) - 1) atomicAdd(T.n_items, (unsigned long long)__popc(imask));
     }
+    if (W == 1 && blockIdx.x == 0 && threadIdx.x == 0) in_cnt[0] = min(send_cnt[0], C);
     if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P3A)) return;
 
     // ---- P3b: initialise the rows attached by this call -----------------------------------------
@@ -249,60 +304,71 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
         if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P3B)) return;
     }
 
-    // ---- P3c: return rows: peer stores for remote requesters, row index for local ones ----------
+    // ---- P3c: return rows to the remote requesters by peer stores -------------------------------------
     PROF(4);
-    {
-        // local requester: only the row index is needed (P5 reads the table directly); thread per entry
-        const unsigned lo = s_pre[me], hi = s_pre[me + 1];
-        for (unsigned e = lo + tid; e < hi; e += nthreads) {
-            const unsigned p = e - lo;
-            const unsigned slot = a.res_slot[(size_t)me * C + p];
-            a.uniq_row[a.send_ret[(size_t)me * C + p]] = (slot != kNoSlot) ? T.slots[slot].row : kNoRow;
-        }
-    }
-    if (a.world > 1 && (a.flags & FUSED_COPY_ROWS)) {
-        // remote requesters: one lane group per entry stores the row into the requester's buffer. The entries
-        // of the local requester are skipped, and every owner starts with the requester to its right and walks
-        // the ring: if all owners served requester 0 first, its one link would carry everything while the
-        // others idle.
-        const unsigned local_lo = s_pre[me], local_cnt = s_pre[me + 1] - s_pre[me];
-        const unsigned total_rem = total_in - local_cnt;
-        const int nxt = (me + 1) % a.world;
-        const unsigned rot = s_pre[nxt] - (nxt > me ? local_cnt : 0u);
-        for (unsigned e0 = group; e0 < total_rem; e0 += ngroups) {
-            unsigned e = e0 + rot;
-            if (e >= total_rem) e -= total_rem;
-            if (e >= local_lo) e += local_cnt;  // back to the index space that includes the local range
-            int r = 0;
-            while (e >= s_pre[r + 1]) ++r;
-            const unsigned p = e - s_pre[r];
-            const unsigned slot = a.res_slot[(size_t)r * C + p];
-            unsigned row = kNoRow;
-            if (slot != kNoSlot) row = T.slots[slot].row;
-            float* dst = a.peer[r].rows_in + (size_t)mine.mail_ret[(size_t)r * C + p] * a.dim;
-            if (row < kRowPending) {
-                copy_row(dst, T.row_ptr(row), a.dim, lane, lanes);
-            } else {
-                const long long key = mine.mail_keys[(size_t)r * C + p];
-                for (unsigned d = lane * 4; d < a.dim; d += lanes * 4) *(float4*)(dst + d) = init4(T, key, d);
+    if (W > 1) {
+        if (a.flags & FUSED_COPY_ROWS) {
+            // one lane group per entry, two entries in flight; every owner starts with the requester to its right
+            // and walks the ring: if all owners served requester 0 first, its one link would carry everything
+            // while the others idle
+            const unsigned total_rem = s_pre[W];
+            const unsigned rot = s_pre[(me + 1) % W];
+            constexpr int kIn = 2;
+            for (unsigned e0 = group; e0 < total_rem; e0 += ngroups * kIn) {
+                const float* src[kIn];
+                long long key[kIn];
+                size_t dst_off[kIn];
+                int rr[kIn];
+                bool act[kIn];
+#pragma unroll
+                for (int k = 0; k < kIn; ++k) {
+                    unsigned e = e0 + (unsigned)k * ngroups;
+                    act[k] = e < total_rem;
+                    src[k] = nullptr;
+                    key[k] = 0;
+                    dst_off[k] = 0;
+                    rr[k] = 0;
+                    if (!act[k]) continue;
+                    e += rot;
+                    if (e >= total_rem) e -= total_rem;
+                    int r = 0;
+                    while (e >= s_pre[r + 1]) ++r;
+                    const unsigned p = e - s_pre[r];
+                    const unsigned slot = a.res_slot[(size_t)r * C + p];
+                    unsigned row = kNoRow;
+                    if (slot != kNoSlot) row = T.slots[slot].row;
+                    rr[k] = r;
+                    dst_off[k] = (size_t)mine.mail_ret[(size_t)r * C + p] * a.dim;
+                    if (row < kRowPending) src[k] = T.row_ptr(row);
+                    else key[k] = mine.mail_keys[(size_t)r * C + p];
+                }
+                for (unsigned d = lane * 4; d < a.dim; d += lanes * 4) {
+                    float4 v[kIn];
+#pragma unroll
+                    for (int k = 0; k < kIn; ++k)
+                        if (act[k]) v[k] = src[k] != nullptr ? *(const float4*)(src[k] + d) : init4(T, key[k], d);
+#pragma unroll
+                    for (int k = 0; k < kIn; ++k) {
+                        if (!act[k]) continue;
+                        if (rows16) *(uint2*)((__nv_bfloat16*)a.peer[rr[k]].rows_in + dst_off[k] + d) = pack_bf16x4(v[k]);
+                        else *(float4*)(a.peer[rr[k]].rows_in + dst_off[k] + d) = v[k];
+                    }
+                }
             }
         }
-    }
-    if (a.world > 1) {
-        __threadfence_system();
-        if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P3C)) return;
-        if (blockIdx.x == 0 && threadIdx.x < (unsigned)a.world && (int)threadIdx.x != me)
-            st_release_sys(&a.peer[threadIdx.x].row_flag[me], epoch);
-        if (!wait_all_flags(mine.row_flag, epoch, a, W_ROWFLAG)) return;
-    } else {
-        if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P3C)) return;
+        // the row flag also tells the requester that its key mailbox on this owner may be overwritten
+        if (cta_arrive_last(&a.ctl->arrive[1], nblocks)) {
+            if (threadIdx.x < (unsigned)W && (int)threadIdx.x != me)
+                st_release_sys(&a.peer[threadIdx.x].row_flag[me], epoch);
+        }
     }
 
     // ---- P5 (consumer): un-dedup + pool into the activation buffer ------------------------------
     PROF(5);
     // Every CTA owns a contiguous range of bags: pass (a) resolves the index chain
-    // position -> dedup slot -> unique id -> row with one THREAD per position (independent loads in
-    // flight), pass (b) gathers and pools with one lane group per bag. Only a CTA barrier in between.
+    // position -> dedup slot -> unique id -> table slot -> row with one THREAD per position (independent loads
+    // in flight; it needs nothing from the peers, so it runs while their rows are still arriving), pass (b)
+    // gathers and pools with one lane group per bag. Only a CTA barrier in between.
     const unsigned L = a.bag_size;
     {
         const unsigned nbags = a.n / L;
@@ -312,40 +378,65 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
             const unsigned h = a.pos_slot[i];
             const unsigned u = a.dedup[h].row;
             a.inverse[i] = (int)u;
-            a.pos_slot[i] = a.uniq_row[u];  // from here on: the row of position i
+            const unsigned s = a.uniq_row[u];
+            unsigned row = s;  // kRemoteRow stays
+            if (s != kRemoteRow) row = (s == kNoSlot) ? kNoRow : T.slots[s].row;
+            a.pos_slot[i] = row;  // from here on: the row of position i
+        }
+        if (W > 1) {
+            if (!wait_all_flags(mine.row_flag, epoch, a, W_ROWFLAG)) return;
+        } else {
+            __syncthreads();
         }
         if (a.flags & FUSED_COPY_ROWS) {
-            __syncthreads();
             const float scale = (a.flags & FUSED_MEAN) ? 1.0f / (float)L : 1.0f;
             const unsigned lgroup = threadIdx.x / lanes, lgroups = kThreads / lanes;
+            float* outf = (float*)a.out;
+            __nv_bfloat16* outh = (__nv_bfloat16*)a.out;
+            const __nv_bfloat16* rin16 = (const __nv_bfloat16*)mine.rows_in;
             if (L == 1) {
-                // one key per bag (the common embedding lookup): two bags per lane group and iteration, so that
-                // two row loads are in flight before the first store (the loop is bound by load latency; four
-                // would cost a resident CTA per SM in registers)
-                constexpr int kBags = 2;
+                // one key per bag (the common embedding lookup): four bags per lane group and iteration, so that
+                // four row loads are in flight before the first store (the loop is bound by load latency)
+                constexpr int kBags = 4;
                 for (unsigned b0 = b_lo; b0 < b_hi; b0 += lgroups * kBags) {
                     unsigned bb[kBags];
-                    const float* src[kBags];
+                    RowSrc src[kBags];
                     bool act[kBags];
 #pragma unroll
                     for (int k = 0; k < kBags; ++k) {
                         bb[k] = b0 + (unsigned)k * lgroups + lgroup;
                         act[k] = bb[k] < b_hi;
-                        src[k] = nullptr;
+                        src[k].f32 = nullptr;
+                        src[k].b16 = nullptr;
                         if (act[k]) {
                             const unsigned row = a.pos_slot[bb[k]];
-                            if (row == kRemoteRow) src[k] = mine.rows_in + (size_t)a.inverse[bb[k]] * a.dim;
-                            else if (row < kRowPending) src[k] = T.row_ptr(row);
+                            if (row == kRemoteRow) {
+                                if (rows16) src[k].b16 = rin16 + (size_t)a.inverse[bb[k]] * a.dim;
+                                else src[k].f32 = mine.rows_in + (size_t)a.inverse[bb[k]] * a.dim;
+                            } else if (row < kRowPending) {
+                                src[k].f32 = T.row_ptr(row);
+                            }
                         }
                     }
                     for (unsigned d = lane * 4; d < a.dim; d += lanes * 4) {
                         float4 v[kBags];
+                        uint2 hv[kBags];
 #pragma unroll
-                        for (int k = 0; k < kBags; ++k)
-                            if (act[k]) v[k] = src[k] != nullptr ? *(const float4*)(src[k] + d) : init4(T, a.keys[bb[k]], d);
+                        for (int k = 0; k < kBags; ++k) {
+                            if (!act[k]) continue;
+                            if (src[k].b16 != nullptr) hv[k] = *(const uint2*)(src[k].b16 + d);
+                            else v[k] = src[k].f32 != nullptr ? *(const float4*)(src[k].f32 + d) : init4(T, a.keys[bb[k]], d);
+                        }
 #pragma unroll
-                        for (int k = 0; k < kBags; ++k)
-                            if (act[k]) *(float4*)(a.out + (size_t)bb[k] * a.dim + d) = v[k];
+                        for (int k = 0; k < kBags; ++k) {
+                            if (!act[k]) continue;
+                            if (out16) {
+                                if (src[k].b16 == nullptr) hv[k] = pack_bf16x4(v[k]);
+                                *(uint2*)(outh + (size_t)bb[k] * a.dim + d) = hv[k];
+                            } else {
+                                *(float4*)(outf + (size_t)bb[k] * a.dim + d) = v[k];
+                            }
+                        }
                     }
                 }
             } else
@@ -362,7 +453,8 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
                         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
                     }
                     if (L > 1) { acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale; }
-                    *(float4*)(a.out + (size_t)b * a.dim + d) = acc;
+                    if (out16) *(uint2*)(outh + (size_t)b * a.dim + d) = pack_bf16x4(acc);
+                    else *(float4*)(outf + (size_t)b * a.dim + d) = acc;
                 }
             }
         }
@@ -383,16 +475,19 @@ __global__ void __launch_bounds__(kThreads) fused_pull_kernel(const FusedArgs a)
     if (blockIdx.x == 0 && threadIdx.x == 0) a.ctl->epoch = epoch;
 }
 
-__global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a) {
+__global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs a) {
     const unsigned nblocks = gridDim.x;
     const unsigned tid = blockIdx.x * kThreads + threadIdx.x;
     const unsigned nthreads = nblocks * kThreads;
+    // a fatal status of this family or of the pull that made the plan: do nothing
+    if (ld_acquire_gpu(&a.ctl->status) != 0u || ld_acquire_gpu(&a.plan_ctl->status) != 0u) return;
     const unsigned epoch = *((volatile unsigned*)&a.ctl->epoch) + 1u;
     const unsigned plan_par = *((volatile const unsigned*)&a.plan_ctl->epoch) & 1u;
     const unsigned* cnt = a.counters + plan_par * 16;
     const unsigned* send_cnt = cnt + 4;
     const unsigned* in_cnt = a.in_cnt + plan_par * kMaxWorld;
     const int me = a.rank;
+    const int W = a.world;
     const unsigned C = a.C;
     const TableView& T = a.table;
     const PeerBufs& mine = a.peer[me];
@@ -400,14 +495,37 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
     const unsigned group = tid / lanes, ngroups = nthreads / lanes, lane = tid % lanes;
     const unsigned L = a.bag_size;
 
-    __shared__ unsigned s_pre[kMaxWorld + 1];
+    __shared__ unsigned s_pre[kMaxWorld + 1];   // shipment prefix (Q2)
+    __shared__ unsigned s_in[kMaxWorld + 1];    // received-entry prefix (Q0 / Q3)
+    if (threadIdx.x == 0) {
+        unsigned acc = 0;
+        for (int r = 0; r < W; ++r) {
+            s_in[r] = acc;
+            acc += in_cnt[r];
+        }
+        s_in[W] = acc;
+    }
+    __syncthreads();
+    const unsigned total_in = s_in[W];
+
+    // ---- Q0 (owner): chain the entries that name the same table row. Each source rank sends a key at most once,
+    // so a chain holds at most one entry per rank; it needs the slots resolved by the pull, not the gradients.
+    PROF(8);
+    if (W > 1) {
+        for (unsigned e = tid; e < total_in; e += nthreads) {
+            int r = 0;
+            while (e >= s_in[r + 1]) ++r;
+            const unsigned id = (unsigned)r * C + (e - s_in[r]);
+            const unsigned slot = a.res_slot[id];
+            if (slot != kNoSlot) a.ent_next[id] = atomicExch(&T.slots[slot].aux, id);
+        }
+    }
 
     // ---- Q1: segment-sum gradients of duplicate keys --------------------------------------------
     // Every CTA owns a contiguous range of positions. Keys that occur several times inside the range
     // (the head of a Zipf distribution occurs in every range) are first summed in shared memory and reach
     // global memory once per CTA; everything else goes straight to the per-key row with a vector atomic.
-    PROF(8);
-    {
+    if (!(a.flags & FUSED_AGG_READY)) {
         const unsigned n_uniq = cnt[0];
         const bool dups = (n_uniq != a.n);
         const float scale = (a.flags & FUSED_MEAN) ? 1.0f / (float)L : 1.0f;
@@ -420,7 +538,8 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
         __shared__ int s_hrow[kHotSlots];
         __shared__ unsigned s_cache_u[kHotRows];
         __shared__ unsigned s_ncache;
-        const bool use_cache = dups && a.dim <= kHotMaxDim && (hi - lo) >= 64;
+        const unsigned hot_rows = min(a.hot_rows, (unsigned)kHotRows);
+        const bool use_cache = dups && hot_rows > 0 && a.dim <= kHotMaxDim && (hi - lo) >= 64;
         if (use_cache) {
             for (unsigned t = threadIdx.x; t < kHotSlots; t += kThreads) { s_hkey[t] = 0xFFFFFFFFu; s_hcnt[t] = 0; s_hrow[t] = -1; }
             if (threadIdx.x == 0) s_ncache = 0;
@@ -440,17 +559,16 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
             for (unsigned t = threadIdx.x; t < kHotSlots; t += kThreads)
                 if (s_hkey[t] != 0xFFFFFFFFu && s_hcnt[t] >= 4) {
                     const unsigned c = atomicAdd(&s_ncache, 1u);
-                    if (c < kHotRows) { s_hrow[t] = (int)c; s_cache_u[c] = s_hkey[t]; }
+                    if (c < hot_rows) { s_hrow[t] = (int)c; s_cache_u[c] = s_hkey[t]; }
                 }
             __syncthreads();
-            const unsigned nc = min(s_ncache, (unsigned)kHotRows);
+            const unsigned nc = min(s_ncache, hot_rows);
             for (unsigned t = threadIdx.x; t < nc * a.dim; t += kThreads) s_cache[t] = 0.f;
             __syncthreads();
         }
         const unsigned gl0 = (threadIdx.x & 31u) / lanes * lanes;  // first lane of this group inside its warp
         // Four positions per lane group and iteration: their index lookups and gradient-row loads are all issued
-        // before the first accumulation. The loop is bound by load latency, not by bytes: with one position in
-        // flight the phase took 78 us on the DLRM batch, with two 68 us, with four 62 us (same registers).
+        // before the first accumulation (the loop is bound by load latency, not by bytes).
         constexpr int kPos = 4;
         for (unsigned base = lo; base < hi; base += lgroups * kPos) {
             unsigned pos[kPos], u[kPos];
@@ -501,7 +619,7 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
         }
         if (use_cache) {
             __syncthreads();
-            const unsigned nc = min(s_ncache, (unsigned)kHotRows);
+            const unsigned nc = min(s_ncache, hot_rows);
             for (unsigned c = lgroup; c < nc; c += lgroups) {
                 float* dst = a.agg + (size_t)s_cache_u[c] * a.dim;
                 for (unsigned d = lane * 4; d < a.dim; d += lanes * 4)
@@ -511,85 +629,63 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
     }
     if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_Q1)) return;
 
-    if (a.world > 1) {
+    if (W > 1) {
         // the owners must have consumed the previous push before their mailboxes are overwritten
         if (!wait_all_flags(mine.push_ack, epoch - 1u, a, W_ACK)) return;
-        // ---- Q2: ship merged gradient rows to the owners
+        // ---- Q2: ship merged gradient rows to the owners, two rows in flight per lane group
         PROF(9);
         if (threadIdx.x == 0) {
             unsigned acc = 0;
-            for (int o = 0; o < a.world; ++o) {
+            for (int o = 0; o < W; ++o) {
                 s_pre[o] = acc;
                 acc += (o == me) ? 0u : min(send_cnt[o], C);
             }
-            s_pre[a.world] = acc;
+            s_pre[W] = acc;
         }
         __syncthreads();
-        const unsigned total = s_pre[a.world];
-        const unsigned rot = s_pre[(me + 1) % a.world];  // ring order, see the key shipment of the pull
-        for (unsigned e0 = group; e0 < total; e0 += ngroups) {
-            unsigned e = e0 + rot;
-            if (e >= total) e -= total;
-            int o = 0;
-            while (e >= s_pre[o + 1]) ++o;
-            const unsigned p = e - s_pre[o];
-            const unsigned u = a.send_ret[(size_t)o * C + p];
-            copy_row(a.peer[o].mail_grad + ((size_t)me * C + p) * a.dim, a.agg + (size_t)u * a.dim, a.dim, lane,
-                     lanes);
+        const unsigned total = s_pre[W];
+        const unsigned rot = s_pre[(me + 1) % W];  // ring order, see the key shipment of the pull
+        constexpr int kIn = 2;
+        for (unsigned e0 = group; e0 < total; e0 += ngroups * kIn) {
+            const float* src[kIn];
+            float* dst[kIn];
+            bool act[kIn];
+#pragma unroll
+            for (int k = 0; k < kIn; ++k) {
+                unsigned e = e0 + (unsigned)k * ngroups;
+                act[k] = e < total;
+                src[k] = nullptr;
+                dst[k] = nullptr;
+                if (!act[k]) continue;
+                e += rot;
+                if (e >= total) e -= total;
+                int o = 0;
+                while (e >= s_pre[o + 1]) ++o;
+                const unsigned p = e - s_pre[o];
+                src[k] = a.agg + (size_t)a.send_ret[(size_t)o * C + p] * a.dim;
+                dst[k] = a.peer[o].mail_grad + ((size_t)me * C + p) * a.dim;
+            }
+            for (unsigned d = lane * 4; d < a.dim; d += lanes * 4) {
+                float4 v[kIn];
+#pragma unroll
+                for (int k = 0; k < kIn; ++k)
+                    if (act[k]) v[k] = *(const float4*)(src[k] + d);
+#pragma unroll
+                for (int k = 0; k < kIn; ++k)
+                    if (act[k]) *(float4*)(dst[k] + d) = v[k];
+            }
         }
-        __threadfence_system();
-        if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_Q2)) return;
-        if (blockIdx.x == 0 && threadIdx.x < (unsigned)a.world && (int)threadIdx.x != me)
-            st_release_sys(&a.peer[threadIdx.x].grad_flag[me], epoch);
+        if (cta_arrive_last(&a.ctl->arrive[0], nblocks)) {
+            if (threadIdx.x < (unsigned)W && (int)threadIdx.x != me)
+                st_release_sys(&a.peer[threadIdx.x].grad_flag[me], epoch);
+        }
         if (!wait_all_flags(mine.grad_flag, epoch, a, W_GRADFLAG)) return;
-        __syncthreads();
     }
 
-    // ---- Q3 (owner) -----------------------------------------------------------------------------
+    // ---- Q3 (owner): one optimizer step per touched row. With several ranks the head of each row's chain
+    // collects the chain (at most one entry per source rank), orders it by source rank and adds the gradients in
+    // that order, so the result does not depend on which entry arrived first.
     PROF(10);
-    if (threadIdx.x == 0) {
-        unsigned acc = 0;
-        for (int r = 0; r < a.world; ++r) {
-            s_pre[r] = acc;
-            acc += in_cnt[r];
-        }
-        s_pre[a.world] = acc;
-    }
-    __syncthreads();
-    const unsigned total_in = s_pre[a.world];
-
-    if (a.world > 1) {
-        // Q3a: leader election per table row: the entry with the lowest (source rank, position) wins
-        for (unsigned e = tid; e < total_in; e += nthreads) {
-            int r = 0;
-            while (e >= s_pre[r + 1]) ++r;
-            const unsigned id = (unsigned)r * C + (e - s_pre[r]);
-            const unsigned slot = a.res_slot[id];
-            if (slot != kNoSlot) atomicMin(&T.slots[slot].aux, id);
-        }
-        if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_Q3A)) return;
-        // Q3b: fold the other ranks' gradients into the leader's row
-        for (unsigned e = group; e < total_in; e += ngroups) {
-            int r = 0;
-            while (e >= s_pre[r + 1]) ++r;
-            const unsigned p = e - s_pre[r];
-            const unsigned id = (unsigned)r * C + p;
-            const unsigned slot = a.res_slot[id];
-            if (slot == kNoSlot) continue;
-            const unsigned lead = T.slots[slot].aux;
-            if (lead == id) continue;
-            const unsigned lr = lead / C, lp = lead % C;
-            const float* src = ((int)r == me) ? a.agg + (size_t)a.send_ret[(size_t)me * C + p] * a.dim
-                                              : mine.mail_grad + (size_t)id * a.dim;
-            float* dst = ((int)lr == me) ? a.agg + (size_t)a.send_ret[(size_t)me * C + lp] * a.dim
-                                         : mine.mail_grad + (size_t)lead * a.dim;
-            for (unsigned d = lane * 4; d < a.dim; d += lanes * 4)
-                atomicAdd((float4*)(dst + d), *(const float4*)(src + d));
-        }
-        if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_Q3B)) return;
-    }
-
-    // Q3c: one optimizer step per touched row
     PROF(11);
     OptConfig opt = a.opt;
     if (opt.step_from_epoch) opt_set_step(opt, epoch);
@@ -597,48 +693,72 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
     const unsigned dim = a.dim;
     for (unsigned e = group; e < total_in; e += ngroups) {
         int r = 0;
-        while (e >= s_pre[r + 1]) ++r;
-        const unsigned p = e - s_pre[r];
+        while (e >= s_in[r + 1]) ++r;
+        const unsigned p = e - s_in[r];
         const unsigned id = (unsigned)r * C + p;
         const unsigned slot = a.res_slot[id];
         if (slot == kNoSlot) {
-            if (lane == 0) set_status(a.ctl, kStOom, W_NOROW);
+            if (lane == 0) set_soft_status(a.ctl, kStOom, W_NOROW);
             continue;
         }
-        if (a.world > 1) {
-            if (T.slots[slot].aux != id) continue;
+        unsigned ids[kMaxWorld];
+        ids[0] = id;
+#pragma unroll
+        for (int k = 1; k < kMaxWorld; ++k) ids[k] = kNoRow;
+        if (W > 1) {
+            if (*((volatile unsigned*)&T.slots[slot].aux) != id) continue;  // not the head of its chain
+            unsigned cur = id;
+#pragma unroll
+            for (int k = 1; k < kMaxWorld; ++k) {
+                if (cur != kNoRow) cur = a.ent_next[cur];
+                ids[k] = cur;
+            }
+            // ascending entry id = ascending source rank (sorting network for 8 keys; kNoRow sorts last)
+#define PSB_CSWAP(i, j)                                          \
+    do {                                                         \
+        const unsigned lo_ = min(ids[i], ids[j]), hi_ = max(ids[i], ids[j]); \
+        ids[i] = lo_;                                            \
+        ids[j] = hi_;                                            \
+    } while (0)
+            PSB_CSWAP(0, 1); PSB_CSWAP(2, 3); PSB_CSWAP(4, 5); PSB_CSWAP(6, 7);
+            PSB_CSWAP(0, 2); PSB_CSWAP(1, 3); PSB_CSWAP(4, 6); PSB_CSWAP(5, 7);
+            PSB_CSWAP(1, 2); PSB_CSWAP(5, 6); PSB_CSWAP(0, 4); PSB_CSWAP(3, 7);
+            PSB_CSWAP(1, 5); PSB_CSWAP(2, 6);
+            PSB_CSWAP(1, 4); PSB_CSWAP(3, 6);
+            PSB_CSWAP(2, 4); PSB_CSWAP(3, 5);
+            PSB_CSWAP(3, 4);
+#undef PSB_CSWAP
         }
         const unsigned row = T.slots[slot].row;
         if (row >= kRowPending) {
             if (lane == 0) {
-                set_status(a.ctl, kStOom, W_NOROW);
+                set_soft_status(a.ctl, kStOom, W_NOROW);
                 T.slots[slot].aux = kNoRow;
             }
             continue;
         }
-        const float* g = (r == me) ? a.agg + (size_t)a.send_ret[(size_t)me * C + p] * dim
-                                   : mine.mail_grad + (size_t)id * dim;
+        // at most one entry of a chain is this rank's own (its gradient sits in `agg`, the others in the mailbox)
+        const float* own = nullptr;
+#pragma unroll
+        for (int k = 0; k < kMaxWorld; ++k)
+            if (ids[k] != kNoRow && (int)(ids[k] / C) == me)
+                own = a.agg + (size_t)a.send_ret[(size_t)me * C + (ids[k] - (unsigned)me * C)] * dim;
         float* w = T.row_ptr(row);
-        if (sync_mode) {
-            float* delta = w + (size_t)(T.n_opt_slots + 1) * dim;
-            for (unsigned d = lane * 4; d < dim; d += lanes * 4) {
-                float4 gv = *(const float4*)(g + d);
+        float* delta = w + (size_t)(T.n_opt_slots + 1) * dim;
+        for (unsigned d = lane * 4; d < dim; d += lanes * 4) {
+            float4 gv = *(const float4*)(((int)(ids[0] / C) == me ? own : mine.mail_grad + (size_t)ids[0] * dim) + d);
+#pragma unroll
+            for (int k = 1; k < kMaxWorld; ++k) {
+                if (ids[k] == kNoRow) continue;
+                const float4 o = *(const float4*)(((int)(ids[k] / C) == me ? own : mine.mail_grad + (size_t)ids[k] * dim) + d);
+                gv.x = __fadd_rn(gv.x, o.x); gv.y = __fadd_rn(gv.y, o.y);
+                gv.z = __fadd_rn(gv.z, o.z); gv.w = __fadd_rn(gv.w, o.w);
+            }
+            if (sync_mode) {
                 float4 dv = *(float4*)(delta + d);
                 dv.x += gv.x; dv.y += gv.y; dv.z += gv.z; dv.w += gv.w;
                 *(float4*)(delta + d) = dv;
-            }
-            if (lane == 0) {
-                unsigned bit = 1u << (row & 31u);
-                unsigned old = atomicOr(&T.touched_bits[row >> 5], bit);
-                if (!(old & bit)) {
-                    unsigned j = atomicAdd(T.touched_count, 1u);
-                    if (j < T.touched_cap) T.touched_list[j] = row;
-                    else set_status(a.ctl, kStOom, W_NOROW);
-                }
-            }
-        } else {
-            for (unsigned d = lane * 4; d < dim; d += lanes * 4) {
-                float4 gv = *(const float4*)(g + d);
+            } else {
                 float4 wv = *(float4*)(w + d);
                 float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
                 if (T.n_opt_slots > 0) s0 = *(float4*)(w + dim + d);
@@ -652,20 +772,23 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
                 if (T.n_opt_slots > 1) *(float4*)(w + 2 * dim + d) = s1;
             }
         }
+        if (sync_mode && lane == 0) {
+            unsigned bit = 1u << (row & 31u);
+            unsigned old = atomicOr(&T.touched_bits[row >> 5], bit);
+            if (!(old & bit)) {
+                unsigned j = atomicAdd(T.touched_count, 1u);
+                if (j < T.touched_cap) T.touched_list[j] = row;
+                else set_soft_status(a.ctl, kStOom, W_NOROW);
+            }
+        }
         if (T.dirty_bits != nullptr && lane == 0) atomicOr(&T.dirty_bits[row >> 5], 1u << (row & 31u));
-        if (a.world > 1 && lane == 0) T.slots[slot].aux = kNoRow;
+        if (W > 1 && lane == 0) T.slots[slot].aux = kNoRow;
     }
 
-    if (a.world > 1) {
+    if (W > 1) {
         // last CTA out acknowledges the sources: their next push may overwrite our mailboxes
-        __threadfence();
-        __syncthreads();
-        __shared__ unsigned s_last;
-        if (threadIdx.x == 0) s_last = (atomicAdd(&a.ctl->done_blocks, 1u) == nblocks - 1u);
-        __syncthreads();
-        if (s_last) {
-            if (threadIdx.x == 0) a.ctl->done_blocks = 0;
-            if (threadIdx.x < (unsigned)a.world && (int)threadIdx.x != me)
+        if (cta_arrive_last(&a.ctl->arrive[1], nblocks)) {
+            if (threadIdx.x < (unsigned)W && (int)threadIdx.x != me)
                 st_release_sys(&a.peer[threadIdx.x].push_ack[me], epoch);
         }
     }
@@ -673,6 +796,8 @@ __global__ void __launch_bounds__(kThreads) fused_push_kernel(const FusedArgs a)
     // every CTA read the epoch before the first grid barrier, so CTA 0 may publish it when it leaves
     if (blockIdx.x == 0 && threadIdx.x == 0) a.ctl->epoch = epoch;
 }
+
+int fused_threads_per_block() { return kThreads; }
 
 int fused_max_blocks(int device, int* pull_blocks, int* push_blocks) {
     cudaDeviceProp prop;
@@ -696,7 +821,8 @@ int launch_fused_pull(const FusedArgs& a, int nblocks, void* stream) {
 
 int launch_fused_push(const FusedArgs& a, int nblocks, void* stream) {
     void* params[] = {(void*)&a};
-    return (int)cudaLaunchCooperativeKernel((const void*)fused_push_kernel, dim3(nblocks), dim3(kThreads), params, kPushSmemBytes,
+    const size_t smem = (size_t)(a.hot_rows < (unsigned)kHotRows ? a.hot_rows : (unsigned)kHotRows) * kHotMaxDim * sizeof(float);
+    return (int)cudaLaunchCooperativeKernel((const void*)fused_push_kernel, dim3(nblocks), dim3(kThreads), params, smem,
                                             (cudaStream_t)stream);
 }
 

@@ -16,7 +16,8 @@ struct PeerBufs {
     unsigned* push_ack;    // [kMaxWorld] epoch written by owner o once it consumed this rank's gradients
     long long* mail_keys;  // [world][C]
     unsigned* mail_ret;    // [world][C] index in the sender's unique list (where the row must return)
-    float* rows_in;        // [N][dim] rows returned by remote owners, indexed by unique id
+    float* rows_in;        // [N][dim] rows returned by remote owners, indexed by unique id (fp32, or bf16 in the
+                           // first half of the buffer when the pull asked for bf16 output without pooling)
     float* mail_grad;      // [world][C][dim] merged gradients sent by each source rank
 };
 
@@ -26,6 +27,9 @@ enum FusedFlags : unsigned {
     FUSED_PREPARE_PUSH = 4u,  // zero the gradient aggregation rows for a following push
     FUSED_MEAN = 8u,          // mean instead of sum pooling
     FUSED_SYNC_PUSH = 16u,    // push accumulates into the delta section instead of updating
+    FUSED_OUT_BF16 = 32u,     // pull output is bf16 (the consumer's activation dtype); with bag_size 1 the rows
+                              // also cross NVLink as bf16, which halves the bytes of the row-return phase
+    FUSED_AGG_READY = 64u,    // push: the per-unique gradient sums are already in `agg` (deterministic pre-pass)
 };
 
 struct FusedArgs {
@@ -49,6 +53,7 @@ struct FusedArgs {
     float* agg;            // [N][dim] per-unique-key gradient sums
     unsigned* res_slot;    // [world][C] owner side: table slot of each received key
     unsigned* new_list;    // [world*C] owner side: slots whose rows were attached by this call
+    unsigned* ent_next;    // [world*C] owner side, push: next entry (other source rank) that holds the same table row
     unsigned* counters;    // [2][16] per epoch parity: 0 n_uniq, 1 n_new, 4.. send_cnt[world]
     unsigned* in_cnt;      // [2][kMaxWorld] per epoch parity: keys received from each source rank
     KernelCtl* ctl;       // control block of this kernel family (holds the call epoch)
@@ -61,7 +66,8 @@ struct FusedArgs {
     const long long* keys;  // [n]
     unsigned n;
     unsigned bag_size;      // keys pooled per output row (1 = no pooling)
-    float* out;             // [n / bag_size][dim]
+    unsigned hot_rows;      // push: gradient rows of hot keys a CTA may sum in shared memory (0..24; 512 B each at dim 128)
+    void* out;              // [n / bag_size][dim] fp32, or bf16 with FUSED_OUT_BF16
     const float* grads;     // [n / bag_size][dim] gradient w.r.t. `out`
     OptConfig opt;
 };
@@ -72,5 +78,6 @@ constexpr unsigned kRemoteRow = 0xFFFFFFFDu;
 int launch_fused_pull(const FusedArgs& a, int nblocks, void* stream);
 int launch_fused_push(const FusedArgs& a, int nblocks, void* stream);
 int fused_max_blocks(int device, int* pull_blocks, int* push_blocks);
+int fused_threads_per_block();
 
 }  // namespace psb

@@ -114,6 +114,18 @@ Status DenseEngine::step(const OptConfig& opt, float grad_scale, void* stream) {
     return Status::Ok();
 }
 
+Status DenseEngine::reset(void* stream) {
+    cudaSetDevice(device_);
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaStreamSynchronize(s);
+    cudaMemsetAsync(ctl_, 0, sizeof(KernelCtl), s);
+    cudaMemsetAsync((char*)symm_->local() + off_flags_, 0, 2 * kMaxWorld * sizeof(unsigned), s);
+    cudaError_t e = cudaStreamSynchronize(s);
+    epoch_ = 0;
+    if (e != cudaSuccess) return Status::Fatal(cudaGetErrorString(e));
+    return Status::Ok();
+}
+
 Status DenseEngine::check(void* stream) {
     cudaSetDevice(device_);
     cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);

@@ -37,6 +37,8 @@ public:
     // Collective: reduce-scatter + optimizer + all-gather.
     Status step(const OptConfig& opt, float grad_scale, void* stream);
     Status check(void* stream);
+    // Re-arm after a time-out: clears the status word, the call epoch and the flags on THIS rank (every rank must).
+    Status reset(void* stream);
     uint64_t kernel_launches() const { return launches_; }
     // false: dense push leaves the other ranks' copies of this table stale; they are gathered by the
     // consuming kernel (all-gather fused with the first GEMM).

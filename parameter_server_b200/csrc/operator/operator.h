@@ -5,6 +5,11 @@
 // (lib_name, op_name) is the cross-process identity of an operator: it travels in the context JSON
 // so that every client and server builds the same object. load_library is real here (dlopen of a
 // shared object whose static initialisers register more operators); in the reference it is a stub.
+// A plug-in includes operators.h, derives from the *Base classes (or from a built-in operator), registers its classes
+// with PSB_REGISTER_OPERATOR(lib, Class) and is compiled with
+//   g++ -std=c++17 -shared -fPIC -DPSB_OPERATOR_PLUGIN -I <csrc> plugin.cpp -o libplugin.so
+// Every process that builds operators from the context (servers AND clients) must load it: Client::load_operator_library
+// does so locally and on every server.
 #pragma once
 #include <dlfcn.h>
 
@@ -32,14 +37,21 @@ protected:
     Json config_;
 };
 
+class OperatorFactory;
+}  // namespace psb
+
+// The one registry of a process. The host (the Python module or the psb_node executable) defines and exports this
+// accessor; a plug-in library compiled with -DPSB_OPERATOR_PLUGIN leaves it undefined, so that the dynamic loader
+// binds it to the host's registry when the library is opened and the plug-in's static registrations land there.
+extern "C" void* psb_operator_factory();
+
+namespace psb {
+
 class OperatorFactory {
 public:
     using Producer = std::function<std::shared_ptr<Operator>(const Json&)>;
 
-    static OperatorFactory& instance() {
-        static OperatorFactory f;
-        return f;
-    }
+    static OperatorFactory& instance() { return *static_cast<OperatorFactory*>(psb_operator_factory()); }
     void register_producer(const std::string& lib, const std::string& op, Producer p) {
         std::lock_guard<std::mutex> g(mu_);
         producers_[lib + "\x1f" + op] = std::move(p);

@@ -1,5 +1,13 @@
 #include "operators.h"
 
+#if !defined(PSB_OPERATOR_PLUGIN)
+// The registry of this process (see operator.h). Default visibility: plug-in libraries bind to it.
+extern "C" __attribute__((visibility("default"))) void* psb_operator_factory() {
+    static psb::OperatorFactory factory;
+    return &factory;
+}
+#endif
+
 namespace psb {
 
 void register_builtin_operators() {

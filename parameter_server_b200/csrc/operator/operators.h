@@ -22,6 +22,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstring>
 #include <fstream>
 #include <functional>
 #include <map>
@@ -566,23 +567,92 @@ public:
 // Dense tables: a dense value (tensor `id` of `numel` floats) is cut into slices of `dim` floats
 // (DenseValuePartitioner), slice j has key (id << 24) | j and lives on shard hash(id, j) % G; pull
 // reassembles (DenseValueMerger). The sparse machinery above does the rest.
+struct DenseSlice {
+    int64_t key;     // (id << 24) | slice index
+    size_t offset;   // first element of the dense value held by this slice
+    uint32_t len;    // elements of the value in this slice (<= the table's slice width)
+};
+// The default cut: consecutive slices of `slice_len` elements.
+inline void dense_default_partition(int64_t id, size_t numel, uint32_t slice_len, std::vector<DenseSlice>* out) {
+    const size_t ns = (numel + slice_len - 1) / slice_len;
+    out->resize(ns);
+    for (size_t j = 0; j < ns; ++j)
+        (*out)[j] = DenseSlice{(id << 24) | (int64_t)j, j * slice_len, (uint32_t)std::min<size_t>(slice_len, numel - j * slice_len)};
+}
 inline void dense_slice_keys(int64_t id, size_t numel, uint32_t slice_len, std::vector<int64_t>* keys) {
-    size_t ns = (numel + slice_len - 1) / slice_len;
-    keys->resize(ns);
-    for (size_t j = 0; j < ns; ++j) (*keys)[j] = (id << 24) | (int64_t)j;
+    std::vector<DenseSlice> sl;
+    dense_default_partition(id, numel, slice_len, &sl);
+    keys->resize(sl.size());
+    for (size_t j = 0; j < sl.size(); ++j) (*keys)[j] = sl[j].key;
 }
 
+// The two customisation points of dense tables (pico-ps/common/dense_common.h:135-171): a subclass registered by a
+// plug-in may cut a value differently (DenseValuePartitioner::partition) and reassemble it differently
+// (DenseValueMerger::merge), e.g. to keep rows of a matrix together or to interleave for balance. Pull and push
+// operators of one table must agree on the cut.
 class DenseTablePullOperator : public SparseTablePullOperator {
 public:
     explicit DenseTablePullOperator(const Json& c) : SparseTablePullOperator(c) {}
+    virtual void partition(int64_t id, size_t numel, uint32_t slice_len, std::vector<DenseSlice>* out) const {
+        dense_default_partition(id, numel, slice_len, out);
+    }
+    // Place one pulled slice (slice_len floats, the first `len` meaningful) into the reassembled value.
+    virtual void merge(const DenseSlice& s, const float* slice_values, float* value) const {
+        std::copy_n(slice_values, s.len, value + s.offset);
+    }
 };
 class DenseTablePushOperator : public SparseTablePushOperator {
 public:
     explicit DenseTablePushOperator(const Json& c) : SparseTablePushOperator(c) {}
+    virtual void partition(int64_t id, size_t numel, uint32_t slice_len, std::vector<DenseSlice>* out) const {
+        dense_default_partition(id, numel, slice_len, out);
+    }
+    // Fill one slice to push (slice_len floats, zero padded) from the dense gradient.
+    virtual void extract(const DenseSlice& s, const float* value, float* slice_values) const {
+        std::copy_n(value + s.offset, s.len, slice_values);
+    }
 };
 
 // ---------------------------------------------------------------------------------------------------
-// for_each: per-shard scan with a built-in reducer; results merge associatively on the client.
+// for_each: a per-shard scan that folds every entry into a result; results merge associatively on the client.
+// The three hooks are the extension points of the reference (init_result / for_each / merge_result,
+// pico-ps/operator/ForEachOperator.h:214-232, :340-358): a plug-in library registers a subclass under its own
+// (lib, class) name and the server runs it. A result travels as bytes whose layout only the operator knows.
+class ForEachOperatorBase : public Operator {
+public:
+    explicit ForEachOperatorBase(const Json& c) : Operator(c) {}
+    const char* kind() const override { return "for_each"; }
+    // The empty result (the neutral element of merge_result).
+    virtual std::string init_result(const Json& carried) const = 0;
+    // Fold one entry (key, full row of `stride` floats whose first `dim` are the embedding) into *result.
+    virtual void for_each(int64_t key, const float* row, uint32_t dim, uint32_t stride, const Json& carried,
+                          std::string* result) const = 0;
+    // *out = merge(*out, in); must be associative and commutative (shards answer in any order).
+    virtual void merge_result(const std::string& in, std::string* out) const = 0;
+    // A mutating scan (the reference's SparseTableForEachWriteOperator) would return rows to write back; this build
+    // keeps scans read-only and offers UDF operators for writes.
+
+    // Server half: the scan of one shard. The default walks the shard in windows and calls for_each per entry.
+    virtual Status apply_request(TableEntry& e, int32_t shard, const Json& carried, std::string* result) const {
+        KVStorage* st = e.storage.get();
+        const uint32_t dim = st->dim(), stride = st->stride();
+        *result = init_result(carried);
+        uint64_t cursor = 0;
+        bool finished = false;
+        std::vector<int64_t> keys;
+        std::vector<float> rows;
+        while (!finished) {
+            keys.clear();
+            rows.clear();
+            PSB_RETURN_IF_ERROR(st->export_shard(shard, cursor, 1 << 16, false, &keys, &rows, &cursor, &finished));
+            for (size_t i = 0; i < keys.size(); ++i) for_each(keys[i], rows.data() + i * stride, dim, stride, carried, result);
+        }
+        return Status::Ok();
+    }
+};
+
+// The built-in reducer: count, sum, sum of squares and max |x| over one row section (`carried` may hold
+// {"section": 0|1|2}: 0 = embedding, 1 / 2 = optimizer slots).
 struct ForEachResult {
     uint64_t count = 0;
     double sum = 0, sum_sq = 0, max_abs = 0;
@@ -592,54 +662,69 @@ struct ForEachResult {
         sum_sq += o.sum_sq;
         max_abs = std::max(max_abs, o.max_abs);
     }
-};
-
-class ForEachOperator : public Operator {
-public:
-    explicit ForEachOperator(const Json& c) : Operator(c) {}
-    const char* kind() const override { return "for_each"; }
-    // Statistics over the embedding part of every row of one shard. `carried` may hold
-    // {"section": 0|1|2} to look at an optimizer slot instead.
-    Status apply_request(TableEntry& e, int32_t shard, const Json& carried, ForEachResult* r) const {
-        KVStorage* st = e.storage.get();
-        const uint32_t dim = st->dim(), stride = st->stride();
-        const uint32_t section = (uint32_t)carried.at("section").as_int(0);
-        if ((section + 1) * dim > stride) return Status::InvalidConfig("for_each: no such row section");
-        uint64_t cursor = 0;
-        bool finished = false;
-        std::vector<int64_t> keys;
-        std::vector<float> rows;
-        while (!finished) {
-            keys.clear();
-            rows.clear();
-            PSB_RETURN_IF_ERROR(st->export_shard(shard, cursor, 1 << 16, false, &keys, &rows, &cursor, &finished));
-            for (size_t i = 0; i < keys.size(); ++i) {
-                ++r->count;
-                const float* v = rows.data() + i * stride + section * dim;
-                for (uint32_t k = 0; k < dim; ++k) {
-                    r->sum += v[k];
-                    r->sum_sq += (double)v[k] * v[k];
-                    r->max_abs = std::max(r->max_abs, (double)std::fabs(v[k]));
-                }
-            }
-        }
-        return Status::Ok();
+    std::string pack() const { return std::string((const char*)this, sizeof(*this)); }
+    static bool unpack(const std::string& s, ForEachResult* r) {
+        if (s.size() != sizeof(ForEachResult)) return false;
+        std::memcpy(r, s.data(), sizeof(ForEachResult));
+        return true;
     }
 };
 
-// erase_if: exclusive per-shard scan with a predicate chosen by the carried item:
-//   {"type":"key_mod","mod":m,"rem":r} | {"type":"l2_below","threshold":t} | {"type":"slot0_below","threshold":t}
-//   | {"type":"all"}
-class EraseIfOperator : public Operator {
+class ForEachOperator : public ForEachOperatorBase {
 public:
-    explicit EraseIfOperator(const Json& c) : Operator(c) {}
-    const char* kind() const override { return "erase_if"; }
-    Status apply_request(TableEntry& e, int32_t shard, const Json& carried, uint64_t* erased) const {
+    explicit ForEachOperator(const Json& c) : ForEachOperatorBase(c) {}
+    std::string init_result(const Json&) const override { return ForEachResult().pack(); }
+    void for_each(int64_t, const float* row, uint32_t dim, uint32_t stride, const Json& carried, std::string* result) const override {
+        const uint32_t section = (uint32_t)carried.at("section").as_int(0);
+        if ((section + 1) * dim > stride) return;
+        ForEachResult* r = (ForEachResult*)&(*result)[0];
+        ++r->count;
+        const float* v = row + section * dim;
+        for (uint32_t k = 0; k < dim; ++k) {
+            r->sum += v[k];
+            r->sum_sq += (double)v[k] * v[k];
+            r->max_abs = std::max(r->max_abs, (double)std::fabs(v[k]));
+        }
+    }
+    void merge_result(const std::string& in, std::string* out) const override {
+        ForEachResult a, b;
+        if (!ForEachResult::unpack(in, &a) || !ForEachResult::unpack(*out, &b)) return;
+        b.merge(a);
+        *out = b.pack();
+    }
+    // The built-in reduction runs where the rows are when the storage can do that (GPU tables: one kernel over the
+    // slot array, four numbers come back); otherwise the generic host scan.
+    Status apply_request(TableEntry& e, int32_t shard, const Json& carried, std::string* result) const override {
         KVStorage* st = e.storage.get();
+        const uint32_t section = (uint32_t)carried.at("section").as_int(0);
+        if ((section + 1) * st->dim() > st->stride()) return Status::InvalidConfig("for_each: no such row section");
+        ScanStats s;
+        Status status;
+        if (st->reduce_builtin(shard, section, &s, &status)) {
+            PSB_RETURN_IF_ERROR(status);
+            ForEachResult r;
+            r.count = s.count; r.sum = s.sum; r.sum_sq = s.sum_sq; r.max_abs = s.max_abs;
+            *result = r.pack();
+            return Status::Ok();
+        }
+        return ForEachOperatorBase::apply_request(e, shard, carried, result);
+    }
+};
+
+// erase_if: exclusive per-shard scan; entries for which the predicate holds are erased
+// (pico-ps/operator/EraseIfOperator.h:39-58: `virtual bool erase_if(key, value) = 0`). A plug-in subclass supplies
+// its own predicate; it is evaluated on the host over the exported rows of the shard.
+class EraseIfOperatorBase : public Operator {
+public:
+    explicit EraseIfOperatorBase(const Json& c) : Operator(c) {}
+    const char* kind() const override { return "erase_if"; }
+    virtual bool erase_if(int64_t key, const float* row, uint32_t dim, uint32_t stride, const Json& carried) const = 0;
+    // Checked once per request before the scan (bad carried items are refused, not ignored).
+    virtual Status check_carried(const KVStorage&, const Json&) const { return Status::Ok(); }
+    virtual Status apply_request(TableEntry& e, int32_t shard, const Json& carried, uint64_t* erased) const {
+        KVStorage* st = e.storage.get();
+        PSB_RETURN_IF_ERROR(check_carried(*st, carried));
         const uint32_t dim = st->dim(), stride = st->stride();
-        const std::string type = carried.at("type").as_string();
-        const int64_t mod = carried.at("mod").as_int(2), rem = carried.at("rem").as_int(1);
-        const double thr = carried.at("threshold").as_double(0);
         uint64_t cursor = 0;
         bool finished = false;
         std::vector<int64_t> keys, doomed;
@@ -648,29 +733,70 @@ public:
             keys.clear();
             rows.clear();
             PSB_RETURN_IF_ERROR(st->export_shard(shard, cursor, 1 << 16, false, &keys, &rows, &cursor, &finished));
-            for (size_t i = 0; i < keys.size(); ++i) {
-                const float* v = rows.data() + i * stride;
-                bool hit = false;
-                if (type == "key_mod") hit = ((keys[i] % mod) + mod) % mod == rem;
-                else if (type == "all") hit = true;
-                else if (type == "l2_below") {
-                    double s = 0;
-                    for (uint32_t k = 0; k < dim; ++k) s += (double)v[k] * v[k];
-                    hit = std::sqrt(s) < thr;
-                } else if (type == "slot0_below") {
-                    if (stride < 2 * dim) return Status::InvalidConfig("erase_if slot0_below: table has no optimizer slot");
-                    double s = 0;
-                    for (uint32_t k = 0; k < dim; ++k) s += v[dim + k];
-                    hit = s / dim < thr;
-                } else {
-                    return Status::InvalidConfig("erase_if: unknown predicate " + type);
-                }
-                if (hit) doomed.push_back(keys[i]);
-            }
+            for (size_t i = 0; i < keys.size(); ++i)
+                if (erase_if(keys[i], rows.data() + i * stride, dim, stride, carried)) doomed.push_back(keys[i]);
         }
         *erased = 0;
         if (!doomed.empty()) PSB_RETURN_IF_ERROR(st->erase_keys(doomed.data(), doomed.size(), erased));
         return Status::Ok();
+    }
+};
+
+// The built-in predicates, chosen by the carried item:
+//   {"type":"key_mod","mod":m,"rem":r} | {"type":"l2_below","threshold":t} | {"type":"slot0_below","threshold":t}
+//   | {"type":"all"}
+class EraseIfOperator : public EraseIfOperatorBase {
+public:
+    explicit EraseIfOperator(const Json& c) : EraseIfOperatorBase(c) {}
+    static bool parse(const Json& carried, ScanPredicate* p) {
+        const std::string type = carried.at("type").as_string();
+        if (type == "key_mod") p->type = ScanPredicate::KEY_MOD;
+        else if (type == "l2_below") p->type = ScanPredicate::L2_BELOW;
+        else if (type == "slot0_below") p->type = ScanPredicate::SLOT0_BELOW;
+        else if (type == "all") p->type = ScanPredicate::ALL;
+        else return false;
+        p->mod = carried.at("mod").as_int(2);
+        p->rem = carried.at("rem").as_int(1);
+        p->threshold = carried.at("threshold").as_double(0);
+        return true;
+    }
+    Status check_carried(const KVStorage& st, const Json& carried) const override {
+        ScanPredicate p;
+        if (!parse(carried, &p)) return Status::InvalidConfig("erase_if: unknown predicate " + carried.at("type").as_string());
+        if (p.type == ScanPredicate::KEY_MOD && p.mod == 0) return Status::InvalidConfig("erase_if key_mod: mod must not be 0");
+        if (p.type == ScanPredicate::SLOT0_BELOW && st.stride() < 2 * st.dim())
+            return Status::InvalidConfig("erase_if slot0_below: table has no optimizer slot");
+        return Status::Ok();
+    }
+    bool erase_if(int64_t key, const float* v, uint32_t dim, uint32_t, const Json& carried) const override {
+        ScanPredicate p;
+        if (!parse(carried, &p)) return false;
+        switch (p.type) {
+            case ScanPredicate::KEY_MOD: return ((key % p.mod) + p.mod) % p.mod == p.rem;
+            case ScanPredicate::ALL: return true;
+            case ScanPredicate::L2_BELOW: {
+                double s = 0;
+                for (uint32_t k = 0; k < dim; ++k) s += (double)v[k] * v[k];
+                return std::sqrt(s) < p.threshold;
+            }
+            case ScanPredicate::SLOT0_BELOW: {
+                double s = 0;
+                for (uint32_t k = 0; k < dim; ++k) s += v[dim + k];
+                return s / dim < p.threshold;
+            }
+        }
+        return false;
+    }
+    // Built-in predicates are evaluated where the rows are when the storage can do that.
+    Status apply_request(TableEntry& e, int32_t shard, const Json& carried, uint64_t* erased) const override {
+        KVStorage* st = e.storage.get();
+        PSB_RETURN_IF_ERROR(check_carried(*st, carried));
+        ScanPredicate p;
+        parse(carried, &p);
+        Status status;
+        *erased = 0;
+        if (st->erase_if_builtin(shard, p, erased, &status)) return status;
+        return EraseIfOperatorBase::apply_request(e, shard, carried, erased);
     }
 };
 
@@ -892,14 +1018,73 @@ public:
     const char* kind() const override { return "restore"; }
 };
 
-// Reshard codec: which items of an old shard must travel, and the purge of what no longer belongs.
+// Reshard codec (pico-ps/operator/UpdateContextOperator.h:59-309): the server half of the update-context
+// transaction is owned by this operator, so a table may replace it with a subclass registered by a plug-in:
+//   create_new_shards        the storage that receives shuffled items on a node of the NEW placement (:136-141)
+//   generate_shuffle_requests which items of an old shard travel, in blocks of at most block_serialized_size bytes,
+//                            addressed to their owners under the new placement (PushItemsGenerator, :215-304)
+//   apply_purge_request      after the commit: drop what no longer belongs here, re-apply what waited for memory
+//                            (:143-193)
 class ShardUpdateContextOperator : public Operator {
 public:
+    // Sends one block of per-node DirectPush bodies over s2s and waits for the owners' answers.
+    using SendBlock = std::function<Status(const std::map<int, Archive>&)>;
+
     explicit ShardUpdateContextOperator(const Json& c) : Operator(c) {
         block_bytes_ = (size_t)c.at("block_serialized_size").as_int(1000000);
     }
     const char* kind() const override { return "update_ctx"; }
     size_t block_bytes() const { return block_bytes_; }
+
+    virtual Status create_new_shards(TableEntry& e) const {
+        if (e.update_rt.local_shards().empty()) return Status::Ok();  // this node leaves the table
+        PSB_RETURN_IF_ERROR(storage_op_of(e)->create_storage(e.update_rt.global_shard_num(), e.update_rt.local_shards(),
+                                                             &e.update_storage));
+        // a followed table keeps recording changes across the reshard: rows that move are marked on arrival, so what
+        // was still waiting to be shipped on their old owner is not lost (some rows are shipped twice instead)
+        if (e.sync_enabled) e.update_storage->enable_dirty_tracking();
+        return Status::Ok();
+    }
+
+    virtual Status generate_shuffle_requests(TableEntry& e, int32_t old_shard, const SendBlock& send) const {
+        if (!e.storage || !e.storage->has_shard(old_shard)) return Status::InvalidID("shuffle: shard is not on this node");
+        const uint32_t stride = e.storage->stride();
+        const uint64_t window = std::max<uint64_t>(64, block_bytes_ / (8 + (size_t)stride * 4));
+        const auto* sop = storage_op_of(e);
+        uint64_t cursor = 0;
+        bool finished = false;
+        std::vector<int64_t> keys;
+        std::vector<float> rows;
+        auto ship = [&]() -> Status {
+            if (keys.empty()) return Status::Ok();
+            std::map<int, Archive> bodies;
+            PSB_RETURN_IF_ERROR(DirectPushOperator::generate_requests(sop, e.update_rt, keys.data(), rows.data(), keys.size(),
+                                                                      stride, &bodies));
+            return send(bodies);
+        };
+        while (!finished) {
+            keys.clear();
+            rows.clear();
+            PSB_RETURN_IF_ERROR(e.storage->export_shard(old_shard, cursor, window, false, &keys, &rows, &cursor, &finished));
+            PSB_RETURN_IF_ERROR(ship());
+        }
+        // pushed items that were waiting for memory on this node travel as rows too: the new owners may have room
+        keys.clear();
+        rows.clear();
+        e.storage->overflow_rows(old_shard, &keys, &rows);
+        return ship();
+    }
+
+    virtual Status apply_purge_request(TableEntry& e) const {
+        e.update_storage.reset();
+        if (e.storage) {
+            for (int s : e.storage->shard_list())
+                if (!e.rt.local_shards().count(s)) e.storage->erase_shard(s);
+            e.storage->set_healthy(true);
+            e.storage->drain_overflow();   // what waited for memory is applied now that shards have left
+        }
+        return Status::Ok();
+    }
 
 private:
     size_t block_bytes_;

@@ -35,6 +35,8 @@ const char* where_name(unsigned w) {
         case 8: return "pull: (source, owner) mailbox overflow - raise pair_capacity";
         case 9: return "pull: table index full";
         case 10: return "pull: row pool exhausted";
+        case 11: return "pull: dedup scratch table full (an earlier call was cut short, or two calls overlap on one engine)";
+        case 12: return "pull: a key equals one of the two reserved values (INT64_MIN, INT64_MIN + 1)";
         case 32: return "push: grid barrier after gradient merge";
         case 33: return "push: waiting for an owner's acknowledgement of the previous push";
         case 34: return "push: grid barrier after gradient shipment";
@@ -77,7 +79,7 @@ SparseEngine::SparseEngine(GpuTable* table, const SparseEngineConfig& cfg) : tab
     const size_t o_pos = carve(N * 4), o_inv = carve(N * 4), o_urow = carve(N * 4), o_uslot = carve(N * 4);
     const size_t o_skeys = carve((size_t)W * C_ * 8), o_sret = carve((size_t)W * C_ * 4);
     const size_t o_agg = carve(N * dim * 4);
-    const size_t o_res = carve((size_t)W * C_ * 4), o_new = carve((size_t)W * C_ * 4);
+    const size_t o_res = carve((size_t)W * C_ * 4), o_new = carve((size_t)W * C_ * 4), o_next = carve((size_t)W * C_ * 4);
     const size_t o_cnt = carve(2 * 16 * 4), o_in = carve(2 * kMaxWorld * 4);
     const size_t o_ctl1 = carve(sizeof(KernelCtl)), o_ctl2 = carve(sizeof(KernelCtl));
     const size_t o_prof = carve(16 * 8);
@@ -96,6 +98,7 @@ SparseEngine::SparseEngine(GpuTable* table, const SparseEngineConfig& cfg) : tab
     agg_ = (float*)(scratch_ + o_agg);
     res_slot_ = (unsigned*)(scratch_ + o_res);
     new_list_ = (unsigned*)(scratch_ + o_new);
+    ent_next_ = (unsigned*)(scratch_ + o_next);
     counters_ = (unsigned*)(scratch_ + o_cnt);
     in_cnt_ = (unsigned*)(scratch_ + o_in);
     ctl_pull_ = (KernelCtl*)(scratch_ + o_ctl1);
@@ -107,8 +110,10 @@ SparseEngine::SparseEngine(GpuTable* table, const SparseEngineConfig& cfg) : tab
     std::vector<int> owner(std::max(cfg_.n_shards, 1));
     for (size_t i = 0; i < owner.size(); ++i) owner[i] = (int)(i % (size_t)W);
     set_shard_owner(owner);
-    int rc = fused_max_blocks(table_->device(), &pull_blocks_, &push_blocks_);
+    int rc = fused_max_blocks(table_->device(), &max_pull_blocks_, &max_push_blocks_);
     if (rc != 0) throw std::runtime_error("SparseEngine: occupancy query failed");
+    cudaDeviceGetAttribute(&num_sms_, cudaDevAttrMultiProcessorCount, table_->device());
+    set_cta_budget(0);
     cudaDeviceSynchronize();
     std::vector<void*> self(1, symm_->local());
     if (W == 1) symm_->connect_local(self, 0);
@@ -123,6 +128,18 @@ SparseEngine::~SparseEngine() {
 Status SparseEngine::connect(const std::vector<std::string>& handles) {
     if ((int)handles.size() != cfg_.world) return Status::InvalidConfig("connect: need one handle per rank");
     return symm_->connect(handles, cfg_.rank);
+}
+
+void SparseEngine::set_cta_budget(int ctas_per_sm) {
+    pull_blocks_ = max_pull_blocks_;
+    push_blocks_ = max_push_blocks_;
+    // a budgeted push also keeps its shared memory small (8 hot rows = 4 KB), so that two of its CTAs fit beside
+    // the ~194 KB of a GEMM CTA
+    hot_rows_ = ctas_per_sm > 0 ? 8u : 24u;
+    if (ctas_per_sm > 0 && num_sms_ > 0) {
+        pull_blocks_ = std::min(max_pull_blocks_, ctas_per_sm * num_sms_);
+        push_blocks_ = std::min(max_push_blocks_, ctas_per_sm * num_sms_);
+    }
 }
 
 void SparseEngine::connect_local(const std::vector<SparseEngine*>& engines) {
@@ -174,6 +191,7 @@ void SparseEngine::fill_common(FusedArgs& a) const {
     a.agg = agg_;
     a.res_slot = res_slot_;
     a.new_list = new_list_;
+    a.ent_next = ent_next_;
     a.counters = counters_;
     a.in_cnt = in_cnt_;
     a.prof = profile_ ? prof_ : nullptr;
@@ -182,9 +200,11 @@ void SparseEngine::fill_common(FusedArgs& a) const {
     a.table = table_->view();
 }
 
-Status SparseEngine::pull(const long long* keys, uint32_t n, uint32_t bag_size, float* out, unsigned flags,
+Status SparseEngine::pull(const long long* keys, uint32_t n, uint32_t bag_size, void* out, unsigned flags,
                           void* stream) {
+    if (failed_) return Status::Error("pull: the engine saw a fatal device status; call reset() on every rank first");
     if (n > cfg_.max_keys) return Status::InvalidConfig("pull: n exceeds max_keys of the engine");
+    if ((flags & FUSED_OUT_BF16) && (table_->dim() % 8)) return Status::InvalidConfig("pull: bf16 output needs dim % 8 == 0");
     if (bag_size == 0 || n % bag_size != 0) return Status::InvalidConfig("pull: n must be a multiple of bag_size");
     if (symm_->world() != cfg_.world) return Status::Error("pull: peers are not connected");
     cudaSetDevice(table_->device());
@@ -205,6 +225,7 @@ Status SparseEngine::pull(const long long* keys, uint32_t n, uint32_t bag_size, 
     a.bag_size = bag_size;
     a.out = out;
     a.grads = nullptr;
+    a.hot_rows = 0;
     int rc = launch_fused_pull(a, pull_blocks_, stream);
     ++launches_;
     if (flags & FUSED_INSERT) table_->refresh_usage_async(stream);
@@ -219,16 +240,21 @@ Status SparseEngine::pull(const long long* keys, uint32_t n, uint32_t bag_size, 
     return Status::Ok();
 }
 
-Status SparseEngine::push(const float* grads, const OptConfig& opt, unsigned flags, void* stream) {
+Status SparseEngine::push(const float* grads, uint32_t n_rows, const OptConfig& opt, unsigned flags, void* stream) {
+    if (failed_) return Status::Error("push: the engine saw a fatal device status; call reset() on every rank first");
     if (!plan_valid_) return Status::Error("push: no plan (call pull or plan first)");
+    if (n_rows != 0 && n_rows != plan_n_ / plan_bag_)
+        return Status::InvalidConfig("push: gradient rows (" + std::to_string(n_rows) + ") != pulled bags (" +
+                                     std::to_string(plan_n_ / plan_bag_) + ")");
     cudaSetDevice(table_->device());
-    if (plan_used_) {
-        // a plan pushed twice: the aggregation rows must start from zero again
+    if (plan_used_ || !(plan_flags_ & FUSED_PREPARE_PUSH)) {
+        // a plan pushed twice, or made by a pull that did not prepare a push: the aggregation rows must start
+        // from zero
         cudaMemsetAsync(agg_, 0, (size_t)plan_n_ * table_->dim() * 4, (cudaStream_t)stream);
     }
     FusedArgs a;
     fill_common(a);
-    a.flags = (plan_flags_ & FUSED_MEAN) | (flags & FUSED_SYNC_PUSH);
+    a.flags = (plan_flags_ & FUSED_MEAN) | (flags & (FUSED_SYNC_PUSH | FUSED_AGG_READY));
     ++push_epoch_;
     a.ctl = ctl_push_;
     a.plan_ctl = ctl_pull_;
@@ -238,6 +264,7 @@ Status SparseEngine::push(const float* grads, const OptConfig& opt, unsigned fla
     a.out = nullptr;
     a.grads = grads;
     a.opt = opt;
+    a.hot_rows = hot_rows_;
     int rc = launch_fused_push(a, push_blocks_, stream);
     ++launches_;
     if (rc != 0) return Status::Error(std::string("fused_push launch: ") + cudaGetErrorString((cudaError_t)rc));
@@ -255,12 +282,22 @@ Status SparseEngine::check(void* stream) {
     if (e != cudaSuccess) return Status::Fatal(std::string("status read: ") + cudaGetErrorString(e));
     for (int k = 0; k < 2; ++k) {
         if (h[k].status == 0) continue;
+        failed_ = true;
         std::string msg = where_name(h[k].where);
         switch (h[k].status) {
-            case kStOom: table_->set_healthy(false); return Status::OOM(msg);
             case kStTimeout: return Status::Timeout(msg);
             default: return Status::Error(msg);
         }
+    }
+    for (int k = 0; k < 2; ++k) {
+        if (h[k].soft == 0) continue;
+        // memory pressure: the call ran to its end (reads of a row-less key saw its initial value, writes to it
+        // were dropped); report it once
+        KernelCtl* ctl = k == 0 ? ctl_pull_ : ctl_push_;
+        cudaMemset(&ctl->soft, 0, 2 * sizeof(unsigned));
+        if (k == 0) cudaMemset(&ctl_push_->soft, 0, 2 * sizeof(unsigned));
+        table_->set_healthy(false);
+        return Status::OOM(where_name(h[k].soft_where));
     }
     return Status::Ok();
 }
@@ -274,9 +311,11 @@ Status SparseEngine::reset(void* stream) {
     cudaMemsetAsync(scratch_, 0, keep_from, s);
     fill_dedup_kernel<<<148 * 4, 256, 0, s>>>(dedup_, dedup_slots_);
     cudaMemsetAsync((char*)symm_->local() + off_flags_, 0, 5 * kMaxWorld * sizeof(unsigned), s);
+    table_->clear_aux(s);  // a push that was cut short leaves its row chains behind
     cudaError_t e = cudaStreamSynchronize(s);
     pull_epoch_ = push_epoch_ = 0;
     plan_valid_ = false;
+    failed_ = false;
     if (e != cudaSuccess) return Status::Fatal(cudaGetErrorString(e));
     return Status::Ok();
 }

@@ -37,15 +37,24 @@ public:
     Status set_shard_owner(const std::vector<int>& owner);
     const std::vector<int>& shard_owner() const { return shard_owner_host_; }
 
-    // Collective pull. keys: device int64[n]; out: device float[n/bag_size][dim] (may be null when
-    // flags lacks FUSED_COPY_ROWS). Leaves a plan for one following push().
-    Status pull(const long long* keys, uint32_t n, uint32_t bag_size, float* out, unsigned flags, void* stream);
-    // Collective push with the plan of the last pull: grads is device float[n/bag_size][dim].
-    Status push(const float* grads, const OptConfig& opt, unsigned flags, void* stream);
-    // Synchronise the stream and translate the device status words of pull and push.
+    // Collective pull. keys: device int64[n]; out: device [n/bag_size][dim], fp32 or (FUSED_OUT_BF16) bf16; may be
+    // null when flags lacks FUSED_COPY_ROWS. Leaves a plan for one following push().
+    Status pull(const long long* keys, uint32_t n, uint32_t bag_size, void* out, unsigned flags, void* stream);
+    // Collective push with the plan of the last pull: grads is device float[n_rows][dim] and n_rows must equal the
+    // plan's n / bag_size (0 skips the check: the caller vouches for the buffer).
+    Status push(const float* grads, uint32_t n_rows, const OptConfig& opt, unsigned flags, void* stream);
+    // Synchronise the stream and translate the device status words of pull and push. OUT_OF_MEMORY is reported
+    // once and cleared (the call that met it ran to its end); TIMEOUT / ERROR stay until reset() and make the
+    // engine refuse further launches.
     Status check(void* stream);
     // Re-arm after an error (clears scratch, barriers and flags on THIS rank; every rank must do it).
     Status reset(void* stream);
+    // CTA budget of the two kernels: 0 = as many CTAs as can be resident on the idle GPU; n > 0 = at most n CTAs
+    // per SM, which leaves registers and thread slots for kernels of another stream (the dense GEMMs of the same
+    // step) to run beside them.
+    void set_cta_budget(int ctas_per_sm);
+    int pull_blocks() const { return pull_blocks_; }
+    int push_blocks() const { return push_blocks_; }
 
     uint32_t last_unique(void* stream);  // unique keys of the last pull (synchronises)
     const SparseEngineConfig& config() const { return cfg_; }
@@ -73,7 +82,7 @@ private:
     Slot* dedup_ = nullptr;
     uint64_t dedup_slots_ = 0;
     unsigned *pos_slot_ = nullptr, *uniq_row_ = nullptr, *uniq_slot_ = nullptr, *send_ret_ = nullptr, *res_slot_ = nullptr,
-             *new_list_ = nullptr, *counters_ = nullptr, *in_cnt_ = nullptr;
+             *new_list_ = nullptr, *ent_next_ = nullptr, *counters_ = nullptr, *in_cnt_ = nullptr;
     int* inverse_ = nullptr;
     long long* send_keys_ = nullptr;
     float* agg_ = nullptr;
@@ -82,7 +91,11 @@ private:
     int* shard_owner_dev_ = nullptr;
     std::vector<int> shard_owner_host_;
     unsigned pull_epoch_ = 0, push_epoch_ = 0;
-    int pull_blocks_ = 0, push_blocks_ = 0;
+    int pull_blocks_ = 0, push_blocks_ = 0;          // grid of the next launches
+    int max_pull_blocks_ = 0, max_push_blocks_ = 0;  // full residency on the idle GPU
+    int num_sms_ = 0;
+    unsigned hot_rows_ = 24;
+    bool failed_ = false;                            // a fatal device status was seen: reset() first
     // last pull (the plan)
     const long long* plan_keys_ = nullptr;
     uint32_t plan_n_ = 0, plan_bag_ = 1;

@@ -810,14 +810,7 @@ private:
             }
             case RequestType::NEW_CTX_PURGE: {
                 std::unique_lock<std::shared_mutex> g(e->mu);
-                e->update_storage.reset();
-                if (e->storage) {
-                    for (int s : e->storage->shard_list())
-                        if (!e->rt.local_shards().count(s)) e->storage->erase_shard(s);
-                    e->storage->set_healthy(true);
-                    e->storage->drain_overflow();   // what waited for memory is applied now that shards have left
-                }
-                return Status::Ok();
+                return update_ctx_op(*e)->apply_purge_request(*e);
             }
             default: return Status::Error(std::string("unhandled request type ") + request_type_name(meta.req_type));
         }
@@ -918,18 +911,18 @@ private:
         Json carried = Json::object();
         if (!carried_str.empty() && !Json::parse(carried_str, &carried)) return Status::InvalidConfig("carried item is not JSON");
         if (meta.req_type == RequestType::OP_ERASEIF) {
-            auto op = find_op<EraseIfOperator>(e, meta.hid);
+            auto op = find_op<EraseIfOperatorBase>(e, meta.hid);
             if (!op) return Status::InvalidID("erase_if: handler is not an erase_if operator");
             uint64_t erased = 0;
             PSB_RETURN_IF_ERROR(op->apply_request(e, shard, carried, &erased));
             *out << erased;
             return Status::Ok();
         }
-        auto op = find_op<ForEachOperator>(e, meta.hid);
+        auto op = find_op<ForEachOperatorBase>(e, meta.hid);
         if (!op) return Status::InvalidID("for_each: handler is not a for_each operator");
-        ForEachResult r;
-        PSB_RETURN_IF_ERROR(op->apply_request(e, shard, carried, &r));
-        *out << r.count << r.sum << r.sum_sq << r.max_abs;
+        std::string result;
+        PSB_RETURN_IF_ERROR(op->apply_request(e, shard, carried, &result));
+        *out << result;   // bytes whose layout the operator defines
         return Status::Ok();
     }
 
@@ -996,16 +989,17 @@ private:
     }
 
     // ------------------------------------------------------------------------- reshard
+    // The table's reshard codec: the update_ctx operator registered for it (a plug-in may have replaced it), else the
+    // built-in one with default settings.
+    std::shared_ptr<ShardUpdateContextOperator> update_ctx_op(TableEntry& e) {
+        for (auto& kv : e.ops)
+            if (auto u = std::dynamic_pointer_cast<ShardUpdateContextOperator>(kv.second)) return u;
+        return std::make_shared<ShardUpdateContextOperator>(Json::object());
+    }
     Status process_new_ctx_create_shard(TableEntry& e, const PSMessageMeta& meta) {
         std::unique_lock<std::shared_mutex> g(e.mu);
         PSB_RETURN_IF_ERROR(check_table_version(e, meta));
-        if (e.update_rt.local_shards().empty()) return Status::Ok();  // this node leaves the table
-        auto* sop = static_cast<SparseTableStorageOperator*>(e.storage_op.get());
-        PSB_RETURN_IF_ERROR(sop->create_storage(e.update_rt.global_shard_num(), e.update_rt.local_shards(), &e.update_storage));
-        // a followed table keeps recording changes across the reshard: rows that move are marked on arrival, so what
-        // was still waiting to be shipped on their old owner is not lost (some rows are shipped twice instead)
-        if (e.sync_enabled) e.update_storage->enable_dirty_tracking();
-        return Status::Ok();
+        return update_ctx_op(e)->create_new_shards(e);
     }
     // One old shard: stream its items in blocks to the owners under the NEW placement.
     Status process_new_ctx_shuffle(TableEntry& e, const PSMessageMeta& meta, Archive& in) {
@@ -1013,38 +1007,9 @@ private:
         PSB_RETURN_IF_ERROR(check_table_version(e, meta));
         int32_t old_shard = 0;
         in >> old_shard;
-        if (!e.storage || !e.storage->has_shard(old_shard)) return Status::InvalidID("shuffle: shard is not on this node");
-        size_t block_bytes = 1000000;
-        for (auto& kv : e.ops)
-            if (auto u = std::dynamic_pointer_cast<ShardUpdateContextOperator>(kv.second)) block_bytes = u->block_bytes();
-        const uint32_t stride = e.storage->stride();
-        const uint64_t window = std::max<uint64_t>(64, block_bytes / (8 + (size_t)stride * 4));
-        const auto* sop = storage_op_of(e);
-        uint64_t cursor = 0;
-        bool finished = false;
-        std::vector<int64_t> keys;
-        std::vector<float> rows;
-        while (!finished) {
-            keys.clear();
-            rows.clear();
-            PSB_RETURN_IF_ERROR(e.storage->export_shard(old_shard, cursor, window, false, &keys, &rows, &cursor, &finished));
-            if (keys.empty()) continue;
-            std::map<int, Archive> bodies;
-            PSB_RETURN_IF_ERROR(DirectPushOperator::generate_requests(sop, e.update_rt, keys.data(), rows.data(), keys.size(),
-                                                                      stride, &bodies));
-            PSB_RETURN_IF_ERROR(s2s_call(bodies, meta, RequestType::NEW_CTX_SHUFFLE));
-        }
-        // pushed items that were waiting for memory on this node travel as rows too: the new owners may have room
-        keys.clear();
-        rows.clear();
-        e.storage->overflow_rows(old_shard, &keys, &rows);
-        if (!keys.empty()) {
-            std::map<int, Archive> bodies;
-            PSB_RETURN_IF_ERROR(DirectPushOperator::generate_requests(sop, e.update_rt, keys.data(), rows.data(), keys.size(),
-                                                                      stride, &bodies));
-            PSB_RETURN_IF_ERROR(s2s_call(bodies, meta, RequestType::NEW_CTX_SHUFFLE));
-        }
-        return Status::Ok();
+        return update_ctx_op(e)->generate_shuffle_requests(e, old_shard, [&](const std::map<int, Archive>& bodies) {
+            return s2s_call(bodies, meta, RequestType::NEW_CTX_SHUFFLE);
+        });
     }
 
     // ------------------------------------------------------------------------- HA restore

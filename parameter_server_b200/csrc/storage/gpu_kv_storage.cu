@@ -95,10 +95,28 @@ public:
         return std::vector<int>(local_.begin(), local_.end());
     }
 
+    // Keys arrive from the network: the two values the index reserves for "empty" and "erased" are refused
+    // before anything is launched.
+    static Status screen_keys(const int64_t* keys, size_t n) {
+        for (size_t i = 0; i < n; ++i)
+            if (keys[i] <= (int64_t)kTombstoneKey)
+                return Status::InvalidConfig("key " + std::to_string(keys[i]) + " is reserved by the GPU table (INT64_MIN, INT64_MIN + 1)");
+        return Status::Ok();
+    }
+    // After a fatal device status (time-out, scratch inconsistency) the private engine is re-armed at once, so
+    // that the failed request does not poison the requests after it.
+    Status checked(Status st) {
+        if (!st.ok() && st.code() != StatusCode::OUT_OF_MEMORY && st.code() != StatusCode::INVALID_CONFIG &&
+            st.code() != StatusCode::INVALID_ID)
+            engine_->reset(stream_);
+        return st;
+    }
+
     Status pull(int s, const int64_t* keys, size_t n, float* out, bool insert) override {
         std::lock_guard<std::mutex> g(mu_);
         if (!local_.count(s)) return Status::InvalidID("shard " + std::to_string(s) + " is not local");
         if (insert && !table_->healthy()) return Status::OOM("storage is unhealthy");
+        PSB_RETURN_IF_ERROR(screen_keys(keys, n));
         cudaSetDevice(cfg_.device);
         const uint32_t dim = table_->dim();
         for (size_t off = 0; off < n; off += cfg_.max_batch) {
@@ -106,29 +124,39 @@ public:
             std::copy_n(keys + off, m, h_keys_);
             cudaMemcpyAsync(d_keys_, h_keys_, m * 8, cudaMemcpyHostToDevice, stream_);
             unsigned flags = FUSED_COPY_ROWS | (insert ? FUSED_INSERT : 0);
-            PSB_RETURN_IF_ERROR(engine_->pull(d_keys_, (uint32_t)m, 1, d_rows_, flags, stream_));
+            PSB_RETURN_IF_ERROR(checked(engine_->pull(d_keys_, (uint32_t)m, 1, d_rows_, flags, stream_)));
             cudaMemcpyAsync(h_rows_, d_rows_, m * dim * 4, cudaMemcpyDeviceToHost, stream_);
-            PSB_RETURN_IF_ERROR(engine_->check(stream_));
+            PSB_RETURN_IF_ERROR(checked(engine_->check(stream_)));
             std::copy_n(h_rows_, m * dim, out + off * dim);
         }
         return Status::Ok();
     }
 
+    // All or nothing on memory pressure, as the client's retry after OUT_OF_MEMORY expects
+    // (pico-ps/handler/Handler.cpp:65-103): rows are attached by the plan step (a pull without output); only
+    // when every key of the request has a row is the first gradient applied. A request larger than one batch
+    // plans all its batches before it applies any.
     Status push(int s, const int64_t* keys, const float* grads, size_t n, const OptConfig& opt, bool sync) override {
         std::lock_guard<std::mutex> g(mu_);
         if (!local_.count(s)) return Status::InvalidID("shard " + std::to_string(s) + " is not local");
         if (!table_->healthy()) return Status::OOM("storage is unhealthy");
+        PSB_RETURN_IF_ERROR(screen_keys(keys, n));
         cudaSetDevice(cfg_.device);
         const uint32_t dim = table_->dim();
-        for (size_t off = 0; off < n; off += cfg_.max_batch) {
-            const size_t m = std::min<size_t>(cfg_.max_batch, n - off);
-            std::copy_n(keys + off, m, h_keys_);
-            std::copy_n(grads + off * dim, m * dim, h_rows_);
-            cudaMemcpyAsync(d_keys_, h_keys_, m * 8, cudaMemcpyHostToDevice, stream_);
-            cudaMemcpyAsync(d_rows_, h_rows_, m * dim * 4, cudaMemcpyHostToDevice, stream_);
-            PSB_RETURN_IF_ERROR(engine_->pull(d_keys_, (uint32_t)m, 1, nullptr, FUSED_INSERT | FUSED_PREPARE_PUSH, stream_));
-            PSB_RETURN_IF_ERROR(engine_->push(d_rows_, opt, sync ? FUSED_SYNC_PUSH : 0, stream_));
-            PSB_RETURN_IF_ERROR(engine_->check(stream_));
+        const bool one_batch = n <= cfg_.max_batch;
+        for (int pass = one_batch ? 1 : 0; pass < 2; ++pass) {
+            for (size_t off = 0; off < n; off += cfg_.max_batch) {
+                const size_t m = std::min<size_t>(cfg_.max_batch, n - off);
+                std::copy_n(keys + off, m, h_keys_);
+                cudaMemcpyAsync(d_keys_, h_keys_, m * 8, cudaMemcpyHostToDevice, stream_);
+                PSB_RETURN_IF_ERROR(checked(engine_->pull(d_keys_, (uint32_t)m, 1, nullptr, FUSED_INSERT | FUSED_PREPARE_PUSH, stream_)));
+                PSB_RETURN_IF_ERROR(checked(engine_->check(stream_)));  // OUT_OF_MEMORY here: nothing was applied
+                if (pass == 0) continue;
+                std::copy_n(grads + off * dim, m * dim, h_rows_);
+                cudaMemcpyAsync(d_rows_, h_rows_, m * dim * 4, cudaMemcpyHostToDevice, stream_);
+                PSB_RETURN_IF_ERROR(checked(engine_->push(d_rows_, (uint32_t)m, opt, sync ? FUSED_SYNC_PUSH : 0, stream_)));
+                PSB_RETURN_IF_ERROR(checked(engine_->check(stream_)));
+            }
         }
         return Status::Ok();
     }
@@ -142,6 +170,7 @@ public:
 
     Status set_rows(const int64_t* keys, const float* rows, size_t n, bool emb_only) override {
         std::lock_guard<std::mutex> g(mu_);
+        PSB_RETURN_IF_ERROR(screen_keys(keys, n));
         cudaSetDevice(cfg_.device);
         const uint32_t w = emb_only ? table_->dim() : table_->stride();
         size_t m = 0;
@@ -195,6 +224,7 @@ public:
 
     Status erase_keys(const int64_t* keys, size_t n, uint64_t* erased) override {
         std::lock_guard<std::mutex> g(mu_);
+        PSB_RETURN_IF_ERROR(screen_keys(keys, n));
         cudaSetDevice(cfg_.device);
         *erased = 0;
         for (size_t off = 0; off < n; off += cfg_.max_batch) {
@@ -206,6 +236,35 @@ public:
             *erased += e;
         }
         return Status::Ok();
+    }
+
+    bool erase_if_builtin(int s, const ScanPredicate& p, uint64_t* erased, Status* st) override {
+        std::lock_guard<std::mutex> g(mu_);
+        *erased = 0;
+        if (!local_.count(s)) {
+            *st = Status::Ok();
+            return true;
+        }
+        ShardFilter f;
+        f.mode = 1;
+        f.shard = s;
+        f.n_shards = n_shards_;
+        *st = table_->erase_if(f, p.type, p.mod, p.rem, p.threshold, erased, stream_);
+        return true;
+    }
+    bool reduce_builtin(int s, uint32_t section, ScanStats* out, Status* st) override {
+        std::lock_guard<std::mutex> g(mu_);
+        *out = ScanStats();
+        if (!local_.count(s)) {
+            *st = Status::Ok();
+            return true;
+        }
+        ShardFilter f;
+        f.mode = 1;
+        f.shard = s;
+        f.n_shards = n_shards_;
+        *st = table_->reduce_section(f, section, &out->count, &out->sum, &out->sum_sq, &out->max_abs, stream_);
+        return true;
     }
 
     uint64_t shard_size(int s) override {
@@ -228,7 +287,8 @@ public:
     }
     Status clear() override {
         std::lock_guard<std::mutex> g(mu_);
-        return table_->clear(stream_);
+        PSB_RETURN_IF_ERROR(table_->clear(stream_));
+        return engine_->reset(stream_);
     }
 
 private:

@@ -213,6 +213,84 @@ __global__ void erase_filter_kernel(TableView t, ShardFilter f, uint64_t cap, un
     }
 }
 
+// ---- scans evaluated where the rows live -------------------------------------------------------------------
+// A warp examines 32 consecutive slots; the entries that pass the shard filter are then visited one by one by the
+// whole warp, which reads the row with 16-byte loads and reduces across lanes. Only counters leave the GPU.
+struct DeviceScan {
+    int pred_type;          // ScanPredicate::Type, or -1: statistics over `section`
+    long long mod, rem;
+    double threshold;
+    unsigned section;
+};
+
+__device__ __forceinline__ float row_value(const TableView& t, const float* row, long long key, unsigned d) {
+    // value of float d of the full row; a key without a backing row has its initial value
+    if (row != nullptr) return row[d];
+    if (d < t.dim) return init_uniform(key, d, t.init_seed, t.init_range);
+    if (d < t.dim * (1 + t.n_opt_slots)) return t.slot_init[(d / t.dim - 1) < 2 ? (d / t.dim - 1) : 1];
+    return 0.f;
+}
+
+__global__ void scan_kernel(TableView t, ShardFilter f, DeviceScan sc, uint64_t cap, unsigned long long* n_erased,
+                            double* stats /* count, sum, sum_sq, max_abs (bits) */) {
+    const unsigned lane = threadIdx.x & 31u;
+    const uint64_t warp = (blockIdx.x * (uint64_t)blockDim.x + threadIdx.x) >> 5;
+    const uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+    double w_count = 0, w_sum = 0, w_sq = 0, w_max = 0;   // per-warp partials (lane 0 holds them)
+    for (uint64_t base = warp * 32; base < cap; base += nwarps * 32) {
+        const uint64_t s = base + lane;
+        long long key = kEmptyKey;
+        unsigned row = kNoRow;
+        bool cand = false;
+        if (s < cap) {
+            key = t.slots[s].key;
+            row = t.slots[s].row;
+            cand = key != kEmptyKey && key != kTombstoneKey && filter_match(f, t, key, row);
+        }
+        bool doomed = false;
+        if (cand && sc.pred_type == 0) doomed = ((key % sc.mod) + sc.mod) % sc.mod == sc.rem;   // KEY_MOD needs no row
+        if (cand && sc.pred_type == 3) doomed = true;                                          // ALL
+        const bool need_row = cand && (sc.pred_type < 0 || sc.pred_type == 1 || sc.pred_type == 2);
+        unsigned rem = __ballot_sync(0xffffffffu, need_row);
+        while (rem) {
+            const int src = __ffs(rem) - 1;
+            rem &= rem - 1;
+            const unsigned r = __shfl_sync(0xffffffffu, row, src);
+            const long long rk = __shfl_sync(0xffffffffu, key, src);
+            const float* rp = r < kRowPending ? t.row_ptr(r) : nullptr;
+            const unsigned sec = sc.pred_type == 2 ? 1u : (sc.pred_type == 1 ? 0u : sc.section);
+            double a = 0, q = 0, m = 0;
+            for (unsigned d = lane; d < t.dim; d += 32) {
+                const double v = (double)row_value(t, rp, rk, sec * t.dim + d);
+                a += v;
+                q += v * v;
+                m = fmax(m, fabs(v));
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                a += __shfl_xor_sync(0xffffffffu, a, o);
+                q += __shfl_xor_sync(0xffffffffu, q, o);
+                m = fmax(m, __shfl_xor_sync(0xffffffffu, m, o));
+            }
+            if (sc.pred_type < 0) {
+                w_count += 1;
+                w_sum += a;
+                w_sq += q;
+                w_max = fmax(w_max, m);
+            } else if ((int)lane == src) {
+                doomed = sc.pred_type == 1 ? sqrt(q) < sc.threshold : a / (double)t.dim < sc.threshold;
+            }
+        }
+        if (doomed) erase_slot(t, s, key, n_erased);
+    }
+    if (sc.pred_type < 0 && lane == 0 && w_count > 0) {
+        atomicAdd(&stats[0], w_count);
+        atomicAdd(&stats[1], w_sum);
+        atomicAdd(&stats[2], w_sq);
+        atomicMax((unsigned long long*)&stats[3], (unsigned long long)__double_as_longlong(w_max));  // non-negative doubles order like their bits
+    }
+}
+
 __global__ void shard_count_kernel(TableView t, uint64_t cap, int n_shards, unsigned long long* counts) {
     for (uint64_t s = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; s < cap; s += (uint64_t)gridDim.x * blockDim.x) {
         const long long key = t.slots[s].key;
@@ -229,6 +307,14 @@ __global__ void store_delta_kernel(TableView t, OptConfig opt, unsigned n_touche
     const unsigned dim = t.dim;
     for (unsigned j = group; j < n_touched; j += ngroups) {
         const unsigned row = t.touched_list[j];
+        // Test-and-clear: a row that was erased (and maybe recycled and touched again) since it entered the list
+        // may be listed twice or with its bit already clear; only the entry that clears the bit applies the delta.
+        unsigned had = 0;
+        if (lane == 0) had = atomicAnd(&t.touched_bits[row >> 5], ~(1u << (row & 31u))) & (1u << (row & 31u));
+        const unsigned gl0 = (threadIdx.x & 31u) / lanes * lanes;  // first lane of this group inside its warp
+        const unsigned gmask = (lanes >= 32u ? 0xffffffffu : ((1u << lanes) - 1u)) << gl0;
+        had = __shfl_sync(gmask, had, gl0);
+        if (!had) continue;
         float* w = t.row_ptr(row);
         float* delta = w + (size_t)(t.n_opt_slots + 1) * dim;
         for (unsigned d = lane * 4; d < dim; d += lanes * 4) {
@@ -246,11 +332,14 @@ __global__ void store_delta_kernel(TableView t, OptConfig opt, unsigned n_touche
             if (t.n_opt_slots > 1) *(float4*)(w + 2 * dim + d) = s1;
             *(float4*)(delta + d) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        if (lane == 0) {
-            atomicAnd(&t.touched_bits[row >> 5], ~(1u << (row & 31u)));
-            if (t.dirty_bits != nullptr) atomicOr(&t.dirty_bits[row >> 5], 1u << (row & 31u));
-        }
+        if (lane == 0 && t.dirty_bits != nullptr) atomicOr(&t.dirty_bits[row >> 5], 1u << (row & 31u));
     }
+}
+
+// Puts the election word of every slot back to its rest value (after a push that was cut short).
+__global__ void clear_aux_kernel(Slot* s, uint64_t n) {
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+        s[i].aux = kNoRow;
 }
 
 __global__ void rehash_kernel(const Slot* old_slots, uint64_t old_cap, Slot* new_slots, unsigned long long new_mask,
@@ -521,6 +610,41 @@ Status GpuTable::erase_filter(const ShardFilter& f, uint64_t* n_erased, void* st
     return Status::Ok();
 }
 
+Status GpuTable::erase_if(const ShardFilter& f, int pred_type, long long mod, long long rem, double threshold,
+                          uint64_t* n_erased, void* stream) {
+    cudaSetDevice(cfg_.device);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (pred_type == 2 && n_slots_ == 0) return Status::InvalidConfig("erase_if slot0_below: table has no optimizer slot");
+    PSB_CUDA_OK(cudaMemsetAsync(scratch_ + 4, 0, 8, s));
+    DeviceScan sc{pred_type, mod, rem, threshold, 0};
+    scan_kernel<<<grid_for(capacity_), kThreads, 0, s>>>(view(), f, sc, capacity_, scratch_ + 4, nullptr);
+    unsigned long long c = 0;
+    PSB_CUDA_OK(cudaMemcpyAsync(&c, scratch_ + 4, 8, cudaMemcpyDeviceToHost, s));
+    PSB_CUDA_OK(cudaStreamSynchronize(s));
+    *n_erased = c;
+    tombstones_ += c;
+    return Status::Ok();
+}
+
+Status GpuTable::reduce_section(const ShardFilter& f, uint32_t section, uint64_t* count, double* sum, double* sum_sq,
+                                double* max_abs, void* stream) {
+    cudaSetDevice(cfg_.device);
+    cudaStream_t s = (cudaStream_t)stream;
+    if ((section + 1) * cfg_.dim > stride_) return Status::InvalidConfig("for_each: no such row section");
+    double* d = (double*)(scratch_ + 8);   // words 8..11 of the scratch block
+    PSB_CUDA_OK(cudaMemsetAsync(d, 0, 4 * sizeof(double), s));
+    DeviceScan sc{-1, 1, 0, 0.0, section};
+    scan_kernel<<<grid_for(capacity_), kThreads, 0, s>>>(view(), f, sc, capacity_, scratch_ + 4, d);
+    double h[4];
+    PSB_CUDA_OK(cudaMemcpyAsync(h, d, sizeof(h), cudaMemcpyDeviceToHost, s));
+    PSB_CUDA_OK(cudaStreamSynchronize(s));
+    *count = (uint64_t)h[0];
+    *sum = h[1];
+    *sum_sq = h[2];
+    *max_abs = h[3];
+    return Status::Ok();
+}
+
 Status GpuTable::shard_counts(int n_shards, std::vector<uint64_t>* counts, void* stream) {
     cudaSetDevice(cfg_.device);
     cudaStream_t s = (cudaStream_t)stream;
@@ -547,6 +671,13 @@ Status GpuTable::store_delta(const OptConfig& opt, void* stream) {
     const unsigned lanes = lanes_for_dim(cfg_.dim);
     store_delta_kernel<<<grid_for((uint64_t)n_touched * lanes), kThreads, 0, s>>>(view(), opt, n_touched);
     PSB_CUDA_OK(cudaMemsetAsync(touched_count_, 0, 4, s));
+    PSB_CUDA_OK(cudaGetLastError());
+    return Status::Ok();
+}
+
+Status GpuTable::clear_aux(void* stream) {
+    cudaSetDevice(cfg_.device);
+    clear_aux_kernel<<<grid_for(capacity_, 4), kThreads, 0, (cudaStream_t)stream>>>(slots_, capacity_);
     PSB_CUDA_OK(cudaGetLastError());
     return Status::Ok();
 }

@@ -98,10 +98,21 @@ public:
     Status get_rows(const long long* keys, uint64_t n, float* out, int* found, bool emb_only, void* stream);
     Status erase_keys(const long long* keys, uint64_t n, uint64_t* n_erased, void* stream);
     Status erase_filter(const ShardFilter& f, uint64_t* n_erased, void* stream);
+    // In-place predicate erase over the entries matched by `f` (pico-ps/operator/EraseIfOperator.h:39-48 iterates a
+    // shard under its lock and erases in place). pred_type: 0 key_mod (mod, rem), 1 ||emb||_2 < threshold,
+    // 2 mean(slot 0) < threshold, 3 all. One kernel over the slot array; only the count returns to the host.
+    Status erase_if(const ShardFilter& f, int pred_type, long long mod, long long rem, double threshold, uint64_t* n_erased,
+                    void* stream);
+    // count / sum / sum of squares / max |x| over row section `section` of the entries matched by `f`
+    // (the reduction of pico-ps/operator/ForEachOperator.h:182-191 done where the rows live).
+    Status reduce_section(const ShardFilter& f, uint32_t section, uint64_t* count, double* sum, double* sum_sq, double* max_abs,
+                          void* stream);
     Status shard_counts(int n_shards, std::vector<uint64_t>* counts, void* stream);
     // Fold the sync-push delta sections into the weights (OP_STORE).
     Status store_delta(const OptConfig& opt, void* stream);
     Status clear(void* stream);
+    // Reset the per-slot election word used by the fused push (only needed after a push that did not finish).
+    Status clear_aux(void* stream);
     // Rebuild the index with `new_capacity` slots (drops tombstones; rows do not move).
     Status rebuild_index(uint64_t new_capacity, void* stream);
     uint64_t index_capacity() const { return capacity_; }

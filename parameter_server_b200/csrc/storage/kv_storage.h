@@ -16,9 +16,28 @@
 
 namespace psb {
 
+// Built-in scan predicates and reductions that a storage may evaluate where its rows live (a GPU table scans its
+// slot array in a kernel; nothing but counters crosses PCIe). A storage that does not implement a hook returns
+// false and the operator scans through export_shard on the host.
+struct ScanPredicate {
+    enum Type : int { KEY_MOD = 0, L2_BELOW = 1, SLOT0_BELOW = 2, ALL = 3 };
+    int type = ALL;
+    int64_t mod = 2, rem = 1;   // KEY_MOD: ((key % mod) + mod) % mod == rem
+    double threshold = 0;       // L2_BELOW: ||emb||_2 < t;  SLOT0_BELOW: mean(slot 0) < t
+};
+struct ScanStats {
+    uint64_t count = 0;
+    double sum = 0, sum_sq = 0, max_abs = 0;
+};
+
 class KVStorage {
 public:
     virtual ~KVStorage() = default;
+    // Erase the entries of shard s that satisfy a built-in predicate, in place. Returns false when the storage has
+    // no in-place scan (the caller falls back to the host scan); *st carries the outcome otherwise.
+    virtual bool erase_if_builtin(int /*s*/, const ScanPredicate& /*p*/, uint64_t* /*erased*/, Status* /*st*/) { return false; }
+    // count / sum / sum of squares / max |x| over row section `section` of every entry of shard s, in place.
+    virtual bool reduce_builtin(int /*s*/, uint32_t /*section*/, ScanStats* /*out*/, Status* /*st*/) { return false; }
     virtual uint32_t dim() const = 0;
     virtual uint32_t stride() const = 0;
     virtual int32_t n_shards() const = 0;
@@ -117,6 +136,8 @@ struct GpuKVStorageConfig {
     uint64_t capacity = 1 << 20;  // expected keys on this server
     uint32_t max_batch = 1 << 18; // largest request (keys) served in one kernel call
 };
-Status make_gpu_kv_storage(const GpuKVStorageConfig& cfg, std::unique_ptr<KVStorage>* out);
+// Default visibility: operator plug-ins that subclass a built-in operator reference it through the inline code of
+// the storage operator and bind to the host's definition.
+__attribute__((visibility("default"))) Status make_gpu_kv_storage(const GpuKVStorageConfig& cfg, std::unique_ptr<KVStorage>* out);
 
 }  // namespace psb

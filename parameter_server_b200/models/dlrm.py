@@ -91,7 +91,8 @@ class DLRM:
 
     def __init__(self, cfg: DLRMConfig, batch: int, *, table_capacity: int = 1 << 22, device=None, group=None,
                  seed: int = 0, wgrad_split_k: int = 0, sparse_kwargs: Optional[dict] = None,
-                 sparse_cls=SparseTable, dense_cls=DenseTable):
+                 sparse_cls=SparseTable, dense_cls=DenseTable, overlap: bool = True, sparse_ctas_per_sm: int = 2,
+                 chain_gemms: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("DLRM runs on the sm_100a kernels and needs a CUDA device")
         self.cfg = cfg
@@ -148,7 +149,9 @@ class DLRM:
         self.d_labels = torch.empty((B,), dtype=torch.float32, device=dev)
         self.x16 = torch.empty((B, self.k_in), dtype=bf, device=dev)
         self.bot_act = [torch.empty((B, n), dtype=bf, device=dev) for n in cfg.bottom]
-        self.emb = torch.empty((B * F, D), dtype=torch.float32, device=dev)
+        # the pull delivers the embedding rows in the dtype their consumer (the interaction kernels) computes in
+        self.emb_bf16 = bool(getattr(self.sparse, "supports_bf16_out", False))
+        self.emb = torch.empty((B * F, D), dtype=bf if self.emb_bf16 else torch.float32, device=dev)
         self.inter = torch.empty((B, self.k_top), dtype=bf, device=dev)
         self.top_act = [torch.empty((B, n), dtype=bf, device=dev) for n in cfg.top]
         self.top_dz = [torch.empty((B, n), dtype=bf, device=dev) for n in cfg.top]
@@ -158,8 +161,18 @@ class DLRM:
         self.loss = torch.zeros(1, dtype=torch.float32, device=dev)
         self.h_loss = torch.zeros(1, dtype=torch.float32).pin_memory()
         self.launches_per_step = 0
+        # the layers of each MLP pass (bottom forward, top forward, top dgrad, bottom dgrad) run as one chained launch
+        self.chain_gemms = bool(chain_gemms)
+        # Overlap: the sparse pull runs on a side stream beside the bottom MLP forward, the sparse push beside the
+        # bottom dgrad + weight / bias gradients. The fused sparse kernels then get a bounded CTA budget, which
+        # leaves registers, thread slots and shared memory on every SM for one GEMM CTA.
+        self.overlap = bool(overlap) and hasattr(self.sparse, "set_cta_budget")
+        if self.overlap:
+            self.side = torch.cuda.Stream(device=dev)
+            self.sparse.set_cta_budget(sparse_ctas_per_sm)
         self.graph = None
         self.trace = None   # list of (section, CUDA event) while a step is being traced
+        self.stamps = None  # device buffer of %globaltimer probes while a traced graph is being captured
 
     # ------------------------------------------------------------------------------------------
     def load_batch(self, dense: torch.Tensor, keys: torch.Tensor, labels: torch.Tensor) -> None:
@@ -173,6 +186,39 @@ class DLRM:
             e = torch.cuda.Event(enable_timing=True)
             e.record()
             self.trace.append((name, e))
+        if self.stamps is not None:
+            # a one-thread kernel writes %globaltimer when the current stream gets here (works inside a graph)
+            i = len(self.stamp_names)
+            self.stamp_names.append(name + ("@side" if torch.cuda.current_stream() != self._main_stream else ""))
+            C.timestamp(self.stamps[i:].data_ptr(), _stream())
+
+    def graph_timeline(self, repeats: int = 20) -> dict:
+        """Where the time goes inside the captured step: the step is captured once more with one-thread timestamp
+        kernels between its sections (on the main stream, and around the pull / push on the side stream), replayed
+        ``repeats`` times on the batch in the input buffers, and the median time of every probe since the first one is
+        returned in microseconds (probes of the side stream are marked ``@side``). Each probe adds a launch of about
+        2 us to its stream, so the last offset is a little above the plain step."""
+        import statistics
+        self.stamps = torch.zeros(64, dtype=torch.int64, device=self.device)
+        self.stamp_names = []
+        self._main_stream = None
+        self.sparse.reserve(4 * self.sparse.world * self.B * self.cfg.num_sparse)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._main_stream = torch.cuda.current_stream()
+            self._mark("start")
+            self.forward_backward()
+        names = list(self.stamp_names)
+        runs = []
+        for _ in range(repeats):
+            g.replay()
+            torch.cuda.synchronize()
+            runs.append(self.stamps[:len(names)].tolist())
+        self.stamps = None
+        # offset of every probe from the first one, median over the replays
+        out = {nm: round(statistics.median((r[i] - r[0]) / 1e3 for r in runs), 1) for i, nm in enumerate(names) if i > 0}
+        return out
 
     def step_breakdown(self, repeats: int = 5) -> dict:
         """Device time of each section of the step in microseconds (median over ``repeats`` eager steps on
@@ -230,68 +276,119 @@ class DLRM:
                 raise RuntimeError(f"kernel launch failed: {rc}")
 
         # ---------------- forward ----------------
+        main = torch.cuda.current_stream()
+        if self.overlap:
+            # fork: the pull needs only the keys; it runs beside the dense-feature cast and the bottom MLP
+            self.side.wait_stream(main)
+            with torch.cuda.stream(self.side):
+                self.sparse.pull(self.d_keys, out=self.emb); n_launch += 1
+                if self.stamps is not None:
+                    self._mark("pull_done")
         self.dense.zero_grads()  # torch fill kernels (not counted as own launches)
         self.loss.zero_()
         chk(C.cast_pad(self.d_dense.data_ptr(), B, cfg.num_dense, self.x16.data_ptr(), self.k_in, s)); n_launch += 1
-        a = self.x16
-        for i, out in enumerate(self.bot_act):
-            G.gemm(a, P[f"bot.w{i}"], bias=P[f"bot.b{i}"], relu=True, out=out); n_launch += 1
-            a = out
+        self._mark("zero_cast")
+        n_launch += self._mlp_forward(self.x16, self.bot_act, "bot")
         self._mark("bottom_fwd")
-        self.sparse.pull(self.d_keys, out=self.emb); n_launch += 1
+        if self.overlap:
+            main.wait_stream(self.side)   # join: the interaction needs the embedding rows
+        else:
+            self.sparse.pull(self.d_keys, out=self.emb); n_launch += 1
         self._mark("sparse_pull")
         chk(C.interaction_fwd(self.bot_act[-1].data_ptr(), D, self.emb.data_ptr(), F, D, self.inter.data_ptr(),
-                              self.k_top, B, s)); n_launch += 1
-        a = self.inter
-        for i, out in enumerate(self.top_act):
-            G.gemm(a, P[f"top.w{i}"], bias=P[f"top.b{i}"], relu=True, out=out); n_launch += 1
-            a = out
+                              self.k_top, B, s, self.emb_bf16)); n_launch += 1
+        self._mark("interaction_fwd")
+        n_launch += self._mlp_forward(self.inter, self.top_act, "top")
+        self._mark("top_fwd")
         # ---------------- head: logits + loss + first backward step ----------------
         last = len(self.top_act) - 1
         chk(C.bce_head(self.top_act[last].data_ptr(), self.tdims[-1], P["head.w"].data_ptr(), P["head.b"].data_ptr(),
                        self.d_labels.data_ptr(), B, self.tdims[-1], 1.0 / B, self.loss.data_ptr(), 0,
                        self.top_dz[last].data_ptr(), self.tdims[-1], Gd["head.w"].data_ptr(), Gd["head.b"].data_ptr(), s))
         n_launch += 1
-        self._mark("interaction_top_fwd_head")
+        self._mark("head")
         # ---------------- backward: the dgrad chain first; every layer's dz stays in its own buffer, so the
         # weight and bias gradients of ALL layers run at the end as one grouped GEMM launch (two when a layer
         # is too narrow for the wide tile) and one bias-gradient launch ----------------
         wg, bg = [], []
+        dgrad = []
         for i in range(last, -1, -1):
             dz = self.top_dz[i]
             x_in = self.top_act[i - 1] if i > 0 else self.inter
             wg.append((dz, x_in, Gd[f"top.w{i}"]))
             bg.append((dz, Gd[f"top.b{i}"]))
             if i > 0:
-                G.linear_dgrad(dz, P[f"top.w{i}"], mask=self.top_act[i - 1], out=self.top_dz[i - 1])
+                dgrad.append(dict(a=dz, w=P[f"top.w{i}"], mask=self.top_act[i - 1], out=self.top_dz[i - 1]))
             else:
-                G.linear_dgrad(dz, P["top.w0"], out=self.d_inter)
-            n_launch += 1
+                dgrad.append(dict(a=dz, w=P["top.w0"], out=self.d_inter))
+        n_launch += self._dgrad_chain(dgrad)
         self._mark("top_bwd")
         # ---------------- backward: interaction + sparse push ----------------
         nb = len(self.bot_act) - 1
         chk(C.interaction_bwd(self.d_inter.data_ptr(), self.k_top, self.bot_act[nb].data_ptr(), D, self.emb.data_ptr(),
-                              F, D, self.bot_dz[nb].data_ptr(), D, self.d_emb.data_ptr(), B, True, s)); n_launch += 1
+                              F, D, self.bot_dz[nb].data_ptr(), D, self.d_emb.data_ptr(), B, True, s, self.emb_bf16)); n_launch += 1
         self._mark("interaction_bwd")
-        self.sparse.push(self.d_emb); n_launch += 1
+        if self.overlap:
+            # fork: the push needs only the row gradients; the rest of the backward pass does not need the push
+            self.side.wait_stream(main)
+            with torch.cuda.stream(self.side):
+                self.sparse.push(self.d_emb); n_launch += 1
+                if self.stamps is not None:
+                    self._mark("push_done")
+        else:
+            self.sparse.push(self.d_emb); n_launch += 1
         self._mark("sparse_push")
         # ---------------- backward: bottom MLP ----------------
+        dgrad = []
         for i in range(nb, -1, -1):
             dz = self.bot_dz[i]
             x_in = self.bot_act[i - 1] if i > 0 else self.x16
             wg.append((dz, x_in, Gd[f"bot.w{i}"]))
             bg.append((dz, Gd[f"bot.b{i}"]))
             if i > 0:
-                G.linear_dgrad(dz, P[f"bot.w{i}"], mask=self.bot_act[i - 1], out=self.bot_dz[i - 1]); n_launch += 1
+                dgrad.append(dict(a=dz, w=P[f"bot.w{i}"], mask=self.bot_act[i - 1], out=self.bot_dz[i - 1]))
+        n_launch += self._dgrad_chain(dgrad)
         self._mark("bottom_dgrad")
         G.grouped_wgrad(wg, split_k=self.split_k)
         n_launch += (1 if any(x.shape[1] >= 256 for _, x, _ in wg) else 0) + (1 if any(x.shape[1] < 256 for _, x, _ in wg) else 0)
+        self._mark("wgrad")
         G.bias_grads(bg); n_launch += (len(bg) + 7) // 8
-        self._mark("wgrad_bias_grad")
+        self._mark("bias_grad")
+        if self.overlap:
+            # join before the dense push: it waits for the other ranks like the sparse push does, and two kernels
+            # that wait for peers must not compete for the same SMs
+            main.wait_stream(self.side)
+            self._mark("join_push")
         self.dense.push(); n_launch += 1
         self._mark("dense_push")
         self.launches_per_step = n_launch
         return self.loss
+
+    def _mlp_forward(self, x: torch.Tensor, acts, prefix: str) -> int:
+        """``acts[i] = relu(acts[i-1] @ W_i^T + b_i)``; returns the number of launches."""
+        P = self.dense.params
+        layers = []
+        a = x
+        for i, out in enumerate(acts):
+            layers.append(dict(a=a, w=P[f"{prefix}.w{i}"], bias=P[f"{prefix}.b{i}"], relu=True, out=out))
+            a = out
+        if self.chain_gemms:
+            G.chain(layers)
+            return 1
+        for l in layers:
+            G.gemm(l["a"], l["w"], bias=l["bias"], relu=True, out=l["out"])
+        return len(layers)
+
+    def _dgrad_chain(self, layers) -> int:
+        """``dz_{i-1} = (dz_i @ W_i) * (act_{i-1} > 0)`` down an MLP; returns the number of launches."""
+        if not layers:
+            return 0
+        if self.chain_gemms:
+            G.chain(layers, b_mn=True)
+            return 1
+        for l in layers:
+            G.linear_dgrad(l["a"], l["w"], mask=l.get("mask"), out=l["out"])
+        return len(layers)
 
     def enable_graph(self) -> None:
         """Capture the step (every launch of ``forward_backward``) in a CUDA graph; later

@@ -22,7 +22,10 @@ class KeyDeduper:
         self.slots = slots
         self.scratch = torch.empty(slots * 16, dtype=torch.uint8, device=self.device)
         self.pos = torch.empty(self.max_keys, dtype=torch.int32, device=self.device)
-        rc = C.dedup_fill_scratch(self.scratch.data_ptr(), slots, torch.cuda.current_stream().cuda_stream)
+        self._refill()
+
+    def _refill(self) -> None:
+        rc = C.dedup_fill_scratch(self.scratch.data_ptr(), self.slots, torch.cuda.current_stream().cuda_stream)
         if rc != 0:
             raise RuntimeError(f"dedup_fill_scratch failed: {rc}")
 
@@ -47,4 +50,8 @@ class KeyDeduper:
         if rc != 0:
             raise RuntimeError(f"dedup_partition failed: {rc}")
         nu = int(counts[0].item())
+        if nu < 0:   # bit 31: the error mark of the kernels
+            self._refill()
+            raise ValueError("dedup_partition: a key equals a reserved value (INT64_MIN, INT64_MIN + 1), a shard owner is "
+                             "outside [0, world), or the scratch table was in use by an overlapping call")
         return uniq[:nu], owner[:nu], inverse, counts

@@ -34,7 +34,8 @@ def _ptr(t: Optional[torch.Tensor]) -> int:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, bias: Optional[torch.Tensor] = None,
          relu: bool = False, mask: Optional[torch.Tensor] = None, accumulate: bool = False, split_k: int = 1,
-         M: Optional[int] = None, N: Optional[int] = None, K: Optional[int] = None, gather: Optional[dict] = None) -> torch.Tensor:
+         M: Optional[int] = None, N: Optional[int] = None, K: Optional[int] = None, gather: Optional[dict] = None,
+         wait_limit_s: float = 2.0) -> torch.Tensor:
     """``out[M,N] = epilogue(sum_k A(m,k) B(n,k))``.
 
     ``a`` is ``[M,K]`` (or ``[K,M]`` with ``a_mn``), ``b`` is ``[N,K]`` (or ``[K,N]`` with ``b_mn``);
@@ -61,7 +62,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     rc = C.gemm_bf16(a.data_ptr(), a.stride(0), a_mn, b.data_ptr(), b.stride(0), b_mn, M, N, K,
                      _ptr(o16), _ptr(o32), out.stride(0), _ptr(b32), relu, _ptr(mask),
                      mask.stride(0) if mask is not None else 0, accumulate, _ptr(b16), split_k,
-                     _err_flag(a.device).data_ptr(), 2.0,
+                     _err_flag(a.device).data_ptr(), wait_limit_s,
                      torch.cuda.current_stream().cuda_stream, **(gather or {}))
     if rc != 0:
         raise RuntimeError(f"gemm_bf16 failed with code {rc}")
@@ -88,6 +89,39 @@ def linear_wgrad(dy, x, out=None, accumulate=False, split_k=1):
         split_k = max(1, min(16, 148 // tiles, max(1, batch // 256)))
     return gemm(dy, x, a_mn=True, b_mn=True, out=out, out_dtype=torch.float32, accumulate=accumulate,
                 split_k=split_k)
+
+
+_chain_scratch = {}
+
+
+def chain(layers, *, b_mn: bool = False, wait_limit_s: float = 2.0) -> None:
+    """The layers of an MLP (forward: ``b_mn=False``, ``w`` is ``[N, K]``; dgrad: ``b_mn=True``, ``w`` is ``[K, N]``) in
+    ONE persistent launch. ``layers`` is a list of dicts ``a, w, out`` (+ ``bias`` bf16, ``relu``, ``mask``); layer
+    ``i + 1`` must read ``out`` of layer ``i`` as its ``a``. Inside the kernel the next layer starts on a row block as
+    soon as the previous layer has stored it, so no layer pays a launch, a ramp-up or a drained tail of its own."""
+    if not 1 <= len(layers) <= 8:
+        raise ValueError("a chain holds 1..8 layers")
+    dev = layers[0]["a"].device
+    stream = torch.cuda.current_stream().cuda_stream
+    key = (dev.index or 0, stream)
+    if key not in _chain_scratch:
+        _chain_scratch[key] = torch.zeros(C.gemm_chain_scratch_words(), dtype=torch.int32, device=dev)
+    probs = []
+    for i, l in enumerate(layers):
+        a, w, out = l["a"], l["w"], l["out"]
+        bias, mask = l.get("bias"), l.get("mask")
+        assert a.dtype == w.dtype == out.dtype == torch.bfloat16 and a.stride(-1) == w.stride(-1) == out.stride(-1) == 1
+        assert bias is None or bias.dtype == torch.bfloat16
+        M, K = a.shape
+        N = w.shape[1] if b_mn else w.shape[0]
+        assert (w.shape[0] if b_mn else w.shape[1]) == K and out.shape[0] == M and out.shape[1] >= N
+        if i > 0:
+            assert a.data_ptr() == layers[i - 1]["out"].data_ptr(), "layer i + 1 must read the output of layer i"
+        probs.append((a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), M, N, K, out.data_ptr(), out.stride(0),
+                      _ptr(bias), bool(l.get("relu", False)), _ptr(mask), mask.stride(0) if mask is not None else 0))
+    rc = C.gemm_bf16_chain(probs, b_mn, _chain_scratch[key].data_ptr(), _err_flag(dev).data_ptr(), wait_limit_s, stream)
+    if rc != 0:
+        raise RuntimeError(f"gemm_bf16_chain failed with code {rc}")
 
 
 def grouped_wgrad(items, split_k: int = 0) -> None:

@@ -39,6 +39,8 @@ def _stream() -> int:
 class SparseTable:
     """Sharded ``int64 key -> fp32[dim]`` table with optimizer slots kept next to each row.
 
+    ``pull`` can deliver bfloat16 rows (``supports_bf16_out``): the table stays fp32.
+
     Args:
         dim: embedding width (a multiple of 4).
         optimizer: ``sgd | adagrad | ftrl | adam | adamw | sum | set``; options go in ``opt_kwargs``.
@@ -50,6 +52,8 @@ class SparseTable:
         read_only: pulls never insert (predictor tables).
         device: ``cuda`` device, or ``cpu`` for the host back-end.
     """
+
+    supports_bf16_out = True
 
     def __init__(self, dim: int, optimizer: str = "adagrad", opt_kwargs: Optional[dict] = None, *,
                  capacity: int = 1 << 20, max_keys: int = 1 << 20, n_shards: Optional[int] = None,
@@ -143,9 +147,10 @@ class SparseTable:
 
     # ------------------------------------------------------------------------------------------
     def pull(self, keys: torch.Tensor, bag_size: int = 1, mean: bool = False, *, insert: Optional[bool] = None,
-             out: Optional[torch.Tensor] = None, for_push: bool = True) -> torch.Tensor:
+             out: Optional[torch.Tensor] = None, for_push: bool = True, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """Rows (sum/mean pooled over ``bag_size`` consecutive keys) of ``keys``; missing keys are
-        inserted with their initial value unless the table is read-only."""
+        inserted with their initial value unless the table is read-only. ``out`` (or ``out_dtype``) may be
+        bfloat16: the table stays fp32, the rows are rounded where they are read."""
         insert = (not self.read_only) if insert is None else insert
         keys = keys.reshape(-1)
         n = keys.numel()
@@ -154,11 +159,14 @@ class SparseTable:
                 raise TypeError("keys must be a CUDA int64 tensor")
             keys = keys.contiguous()
             if out is None:
-                out = torch.empty((n // bag_size, self.dim), dtype=torch.float32, device=self.device)
-            elif (out.dtype != torch.float32 or not out.is_cuda or not out.is_contiguous()
+                out = torch.empty((n // bag_size, self.dim), dtype=out_dtype or torch.float32, device=self.device)
+            elif (out.dtype not in (torch.float32, torch.bfloat16) or not out.is_cuda or not out.is_contiguous()
                   or out.numel() != (n // bag_size) * self.dim):
-                raise ValueError("out must be a contiguous CUDA float32 tensor of n / bag_size rows of dim columns")
+                raise ValueError("out must be a contiguous CUDA float32 or bfloat16 tensor of n / bag_size rows of dim columns")
             flags = C.FUSED_COPY_ROWS
+            if out.dtype == torch.bfloat16:
+                # the consumer's activation dtype: rows are rounded once, by their owner, and cross NVLink as bf16
+                flags |= C.FUSED_OUT_BF16
             if insert:
                 flags |= C.FUSED_INSERT
             if for_push:
@@ -208,13 +216,12 @@ class SparseTable:
             if grads.dtype != torch.float32:
                 grads = grads.float()
             grads = grads.contiguous()
-            planned = self._plan_keys.numel() if torch.is_tensor(self._plan_keys) else None
-            if not grads.is_cuda or grads.numel() % self.dim or (planned is not None and bag_size == 1 and keys is None
-                                                                 and grads.numel() // self.dim > planned):
+            if not grads.is_cuda or grads.numel() % self.dim:
                 raise ValueError("grads must be a CUDA tensor with one row of dim columns per pulled bag")
             flags = C.FUSED_SYNC_PUSH if sync else 0
             with nvtx("ps.sparse_push"):
-                raise_if_error(self.engine.push(grads.data_ptr(), self.opt, flags, _stream()))
+                # the engine refuses a gradient buffer whose row count differs from the plan's bags
+                raise_if_error(self.engine.push(grads.data_ptr(), grads.numel() // self.dim, self.opt, flags, _stream()))
             self._last_grads = grads  # keep alive until the kernel ran
         else:
             k, bag, mn = self._plan_keys
@@ -306,8 +313,15 @@ class SparseTable:
         return self.engine.check(_stream()) if self.is_cuda else C.Status()
 
     def reset(self) -> None:
+        """Re-arm the engine after a fatal device status (time-out, error). Every rank of the group must call it."""
         if self.is_cuda:
             raise_if_error(self.engine.reset(_stream()))
+
+    def set_cta_budget(self, ctas_per_sm: int) -> None:
+        """Bound the grid of the fused kernels to ``ctas_per_sm`` CTAs per SM (0 = fill the idle GPU), so that
+        kernels of another stream can run beside them."""
+        if self.is_cuda:
+            self.engine.set_cta_budget(int(ctas_per_sm))
 
     # ------------------------------------------------------------------------------------------
     def size(self) -> int:

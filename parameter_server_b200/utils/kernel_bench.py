@@ -173,6 +173,65 @@ def cmd_dense(a):
           f"{bytes_/tt/hbm:4.2f} of {src} HBM copy")
 
 
+def graph_timed(fn, iters=20):
+    """Median device time of ``fn`` replayed from a CUDA graph (no host launch gaps), L2 flushed before each replay."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    ts = []
+    for _ in range(iters):
+        flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e-3)
+    return statistics.median(ts)
+
+
+def cmd_mlp(a):
+    """The MLP passes of the DLRM step (batch rows x layer widths): one launch per layer, one chained launch for the
+    whole pass, and torch.matmul (cuBLAS, without the bias / ReLU epilogues) for reference. Graph replays."""
+    from ..ops import gemm as G
+    _, flops_peak, src = peaks()
+    M = a.batch
+    for name, dims in (("top forward", (480, 1024, 1024, 512, 256)), ("bottom forward", (16, 512, 256, 128))):
+        ws = [(torch.randn(dims[i + 1], dims[i], device="cuda") * (2.0 / dims[i]) ** 0.5).bfloat16() for i in range(len(dims) - 1)]
+        bs = [(torch.randn(dims[i + 1], device="cuda") * 0.1).bfloat16() for i in range(len(dims) - 1)]
+        x = torch.randn(M, dims[0], device="cuda").bfloat16()
+        outs = [torch.empty(M, d, device="cuda", dtype=torch.bfloat16) for d in dims[1:]]
+        layers, prev = [], x
+        for w, b, o in zip(ws, bs, outs):
+            layers.append(dict(a=prev, w=w, bias=b, relu=True, out=o))
+            prev = o
+
+        def separate():
+            for l in layers:
+                G.gemm(l["a"], l["w"], bias=l["bias"], relu=True, out=l["out"])
+
+        def chained():
+            G.chain(layers)
+
+        def cublas():
+            for l in layers:
+                torch.matmul(l["a"], l["w"].t(), out=l["out"])
+
+        fl = sum(2.0 * M * dims[i] * dims[i + 1] for i in range(len(dims) - 1))
+        for tag, fn in (("one launch per layer", separate), ("one chained launch", chained), ("torch.matmul per layer", cublas)):
+            t = graph_timed(fn, a.iters)
+            print(f"mlp {name:15s} M={M} {tag:24s}: {t*1e6:8.1f} us  {fl/t/1e12:7.1f} TFLOP/s  {fl/t/flops_peak:5.2f} of {src} bf16 peak")
+        for i, l in enumerate(layers):
+            t = graph_timed(lambda: G.gemm(l["a"], l["w"], bias=l["bias"], relu=True, out=l["out"]), a.iters)
+            t2 = graph_timed(lambda: torch.matmul(l["a"], l["w"].t(), out=l["out"]), a.iters)
+            f1 = 2.0 * M * dims[i] * dims[i + 1]
+            print(f"    layer {i} [{M} x {dims[i + 1]} x {dims[i]}]: {t*1e6:7.1f} us ({f1/t/1e12:6.1f} TFLOP/s)   cuBLAS {t2*1e6:7.1f} us")
+    G.check_gemm_errors()
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -187,11 +246,13 @@ def main():
     i.add_argument("--batch", type=int, default=8192)
     d = sub.add_parser("dense")
     d.add_argument("--numel", type=int, default=64 << 20); d.add_argument("--bf16-grads", action="store_true")
-    for p in (g, s, i, d):
+    m = sub.add_parser("mlp")
+    m.add_argument("--batch", type=int, default=8192)
+    for p in (g, s, i, d, m):
         p.add_argument("--iters", type=int, default=10)
         p.add_argument("--no-flush", action="store_true")
     a = ap.parse_args()
-    {"gemm": cmd_gemm, "sparse": cmd_sparse, "interaction": cmd_interaction, "dense": cmd_dense}[a.cmd](a)
+    {"gemm": cmd_gemm, "sparse": cmd_sparse, "interaction": cmd_interaction, "dense": cmd_dense, "mlp": cmd_mlp}[a.cmd](a)
 
 
 if __name__ == "__main__":

@@ -9,18 +9,24 @@ from parameter_server_b200.models import DLRM, DLRMConfig, SyntheticCTR
 pytestmark = pytest.mark.gpu
 
 
-def test_interaction_kernels_match_reference():
+@pytest.mark.parametrize("D,F,emb_bf16", [(128, 26, False), (128, 26, True), (64, 9, False), (64, 9, True)])
+def test_interaction_kernels_match_reference(D, F, emb_bf16):
+    """fp32 PyTorch reference of the same op; the kernels stage their operands as bf16, hence the tolerances. With
+    bf16 embedding rows (what a bf16 pull delivers) the result must equal the fp32-input run bit for bit, because the
+    fp32 path rounds the rows to bf16 the same way."""
     torch.manual_seed(0)
-    B, F, D = 300, 26, 128
-    ldo = 480
+    B = 300
+    npairs = (F + 1) * F // 2
+    ldo = (D + npairs + 7) // 8 * 8
     bottom = torch.randn(B, D, device="cuda").bfloat16()
     emb = torch.randn(B, F, D, device="cuda") * 0.1
+    emb_in = emb.bfloat16() if emb_bf16 else emb
     out = torch.empty(B, ldo, device="cuda", dtype=torch.bfloat16)
-    assert C.interaction_fwd(bottom.data_ptr(), D, emb.data_ptr(), F, D, out.data_ptr(), ldo, B, 0) == 0
+    assert C.interaction_fwd(bottom.data_ptr(), D, emb_in.data_ptr(), F, D, out.data_ptr(), ldo, B, 0, emb_bf16) == 0
     T = torch.cat([bottom.float()[:, None], emb], 1)
     Z = torch.bmm(T, T.transpose(1, 2))
     ii, jj = torch.tril_indices(F + 1, F + 1, offset=-1)
-    ref = torch.cat([bottom.float(), Z[:, ii, jj], torch.zeros(B, 1, device="cuda")], 1)
+    ref = torch.cat([bottom.float(), Z[:, ii, jj], torch.zeros(B, ldo - D - npairs, device="cuda")], 1)
     assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2)
     # backward against autograd
     Tg = T.clone().requires_grad_(True)
@@ -30,10 +36,25 @@ def test_interaction_kernels_match_reference():
     o.backward(dout.float()[:, :o.shape[1]])
     dbot = torch.empty(B, D, device="cuda", dtype=torch.bfloat16)
     demb = torch.empty(B, F, D, device="cuda")
-    assert C.interaction_bwd(dout.data_ptr(), ldo, bottom.data_ptr(), D, emb.data_ptr(), F, D, dbot.data_ptr(), D,
-                             demb.data_ptr(), B, False, 0) == 0
+    assert C.interaction_bwd(dout.data_ptr(), ldo, bottom.data_ptr(), D, emb_in.data_ptr(), F, D, dbot.data_ptr(), D,
+                             demb.data_ptr(), B, False, 0, emb_bf16) == 0
     assert torch.allclose(demb, Tg.grad[:, 1:], rtol=2e-2, atol=1e-2)  # operands are staged as bf16
     assert torch.allclose(dbot.float(), Tg.grad[:, 0], rtol=2e-2, atol=5e-2)
+    if emb_bf16:
+        out32 = torch.empty_like(out)
+        demb32 = torch.empty_like(demb)
+        dbot32 = torch.empty_like(dbot)
+        assert C.interaction_fwd(bottom.data_ptr(), D, emb.data_ptr(), F, D, out32.data_ptr(), ldo, B, 0, False) == 0
+        assert C.interaction_bwd(dout.data_ptr(), ldo, bottom.data_ptr(), D, emb.data_ptr(), F, D, dbot32.data_ptr(), D,
+                                 demb32.data_ptr(), B, False, 0, False) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(out, out32) and torch.equal(demb, demb32) and torch.equal(dbot, dbot32)
+    # relu mask on the bottom gradient
+    dbot_m = torch.empty_like(dbot)
+    assert C.interaction_bwd(dout.data_ptr(), ldo, bottom.data_ptr(), D, emb_in.data_ptr(), F, D, dbot_m.data_ptr(), D,
+                             demb.data_ptr(), B, True, 0, emb_bf16) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dbot_m, torch.where(bottom > 0, dbot, torch.zeros_like(dbot)))
 
 
 def test_bce_head_and_bias_grad():
@@ -109,3 +130,31 @@ def test_graph_replay_matches_eager():
     assert ne == ng
     assert max(abs(a - b) for a, b in zip(le, lg)) < 5e-3, (le, lg)
     assert torch.allclose(pe, pg, rtol=0, atol=2e-2)
+
+
+def test_overlapped_step_matches_the_serial_step():
+    """The sparse pull / push on a side stream with a bounded CTA budget, beside the dense GEMMs, computes the same
+    step as the serial launch order (up to the order of fp32 atomics in the gradient sums)."""
+    cfg = DLRMConfig(vocab_max=2e4)
+    B = 512
+
+    def run(overlap, graph):
+        model = DLRM(cfg, B, table_capacity=1 << 17, seed=3, overlap=overlap)
+        data = SyntheticCTR(cfg, B, pool=3, seed=9)
+        for _ in range(3):
+            model.train_step(*data.next())
+        if graph:
+            model.enable_graph()
+        losses = []
+        for _ in range(6):
+            model.train_step(*data.next())
+            losses.append(model.read_loss())
+        model.check()
+        return losses, model.dense.flat_params.float().clone(), model.sparse.size()
+
+    ls, ps_, ns = run(False, False)
+    for graph in (False, True):
+        lo, po, no = run(True, graph)
+        assert no == ns
+        assert max(abs(a - b) for a, b in zip(ls, lo)) < 5e-3, (ls, lo)
+        assert torch.allclose(ps_, po, rtol=0, atol=2e-2)

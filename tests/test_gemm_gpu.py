@@ -80,3 +80,57 @@ def test_grouped_wgrad_and_bias_grads_match_fp32_reference():
     G.check_gemm_errors()
     for (_, _, out), ref in zip(items[:3], refs[:3]):
         assert torch.allclose(out, 2 * ref, rtol=2e-3, atol=4e-2)
+
+
+@pytest.mark.parametrize("M,dims", [(8192, (480, 1024, 1024, 512, 256)), (1000, (16, 512, 256, 128)), (300, (64, 256))])
+def test_chained_mlp_forward_equals_layer_by_layer(M, dims):
+    """All layers of an MLP in one persistent launch (a layer starts on a row block once the previous layer has stored
+    it) must give bit for bit what one launch per layer gives: same tiles, same accumulation order."""
+    torch.manual_seed(len(dims))
+    ws = [(torch.randn(dims[i + 1], dims[i], device="cuda") * (2.0 / dims[i]) ** 0.5).bfloat16() for i in range(len(dims) - 1)]
+    bs = [(torch.randn(dims[i + 1], device="cuda") * 0.1).bfloat16() for i in range(len(dims) - 1)]
+    x = torch.randn(M, dims[0], device="cuda").bfloat16()
+    one = [torch.empty(M, d, device="cuda", dtype=torch.bfloat16) for d in dims[1:]]
+    two = [torch.empty(M, d, device="cuda", dtype=torch.bfloat16) for d in dims[1:]]
+    a = x
+    for w, b, o in zip(ws, bs, one):
+        G.gemm(a, w, bias=b, relu=True, out=o)
+        a = o
+    layers, a = [], x
+    for w, b, o in zip(ws, bs, two):
+        layers.append(dict(a=a, w=w, bias=b, relu=True, out=o))
+        a = o
+    for _ in range(3):                       # the scratch counters are re-armed by every call
+        for o in two:
+            o.zero_()
+        G.chain(layers)
+        G.check_gemm_errors()
+        for o1, o2 in zip(one, two):
+            assert torch.equal(o1, o2)
+    # and against the fp32 reference of the whole MLP
+    r = x.float()
+    for w, b in zip(ws, bs):
+        r = torch.relu(r @ w.float().t() + b.float()).bfloat16().float()
+    assert torch.allclose(two[-1].float(), r, rtol=5e-2, atol=5e-2)
+
+
+def test_chained_dgrad_equals_layer_by_layer():
+    torch.manual_seed(11)
+    M, dims = 4096, (256, 512, 1024, 480)     # dz widths walking down an MLP: dz_i [M, dims[i]] -> dz_{i+1} [M, dims[i+1]]
+    ws = [(torch.randn(dims[i], dims[i + 1], device="cuda") * 0.05).bfloat16() for i in range(len(dims) - 1)]   # [k][n]
+    masks = [torch.randn(M, dims[i + 1], device="cuda").bfloat16() for i in range(len(dims) - 2)] + [None]
+    dz = torch.randn(M, dims[0], device="cuda").bfloat16()
+    one = [torch.empty(M, d, device="cuda", dtype=torch.bfloat16) for d in dims[1:]]
+    two = [torch.zeros(M, d, device="cuda", dtype=torch.bfloat16) for d in dims[1:]]
+    a = dz
+    for w, m, o in zip(ws, masks, one):
+        G.linear_dgrad(a, w, mask=m, out=o)
+        a = o
+    layers, a = [], dz
+    for w, m, o in zip(ws, masks, two):
+        layers.append(dict(a=a, w=w, mask=m, out=o))
+        a = o
+    G.chain(layers, b_mn=True)
+    G.check_gemm_errors()
+    for o1, o2 in zip(one, two):
+        assert torch.equal(o1, o2)

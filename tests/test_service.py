@@ -106,7 +106,7 @@ def test_master_basics():
     m.stop()
 
 
-@pytest.mark.parametrize("n_servers", [1, 3])
+@pytest.mark.parametrize("n_servers", [1, 3, 5, 8])     # the reference's matrix: {1, 3, 5, 8} processes x compression
 @pytest.mark.parametrize("compress", ["", "zstd", "lz4"])
 def test_sparse_end_to_end(tmp_path, n_servers, compress):
     cl = Cluster(n_servers)

@@ -148,18 +148,109 @@ def test_erase_export_set_rows_clear():
     assert g.size() == 0
 
 
-def test_row_pool_limit_reports_oom_and_context_survives():
+def test_row_pool_limit_reports_oom_once_and_the_engine_keeps_working():
+    """Memory pressure is not fatal: the call that met it runs to its end (scratch emptied, epoch advanced), the
+    status is reported once, and later calls need no reset (pico-ps/operator/SparsePullOperator.h:195-199: pulls
+    answer OUT_OF_MEMORY while items are parked, the server stays up)."""
     t = SparseTable(64, "adagrad", device="cuda", capacity=1 << 14, max_keys=1 << 13, max_rows=4096, slab_shift=12)
-    t.pull(torch.arange(3000, device="cuda")); t.check()
+    first = t.pull(torch.arange(3000, device="cuda")); t.check()
     t.pull(torch.arange(3000, 8000, device="cuda"))
     st = t.status()
     assert st.code() == StatusCode.OUT_OF_MEMORY
     assert not t.table.healthy()
-    # the context is still usable and existing rows are intact
-    t.reset()
-    r = t.pull(torch.arange(10, device="cuda"), insert=False)
+    assert t.status().ok()                      # reported once
+    # no reset: read-only pulls keep answering and existing rows are intact
+    for _ in range(3):
+        r = t.pull(torch.arange(3000, device="cuda"), insert=False)
+        t.check()
+        assert torch.equal(r, first)
+    # a key that found no row reads as its initial value and a push to it is dropped with OUT_OF_MEMORY again
+    t.pull(torch.arange(7990, 8000, device="cuda"))
+    t.push(torch.ones(10, 64, device="cuda"))
+    assert t.status().code() == StatusCode.OUT_OF_MEMORY
+    r = t.pull(torch.arange(10, device="cuda"), insert=False); t.check()
+    assert torch.equal(r, first[:10])
+
+
+def test_reserved_keys_are_refused_and_reset_rearms():
+    t = SparseTable(16, "sgd", dict(lr=0.1), device="cuda", capacity=1 << 12, max_keys=1 << 10)
+    good = torch.arange(100, device="cuda")
+    want = t.pull(good); t.check()
+    for reserved in (-(1 << 63), -(1 << 63) + 1):
+        bad = good.clone()
+        bad[7] = reserved
+        t.pull(bad)
+        st = t.status()
+        assert st.code() == StatusCode.ERROR and "reserved" in st.msg()
+        with pytest.raises(StatusError):        # a fatal status makes the engine refuse launches until reset()
+            t.pull(good)
+        t.reset()
+        assert torch.equal(t.pull(good), want)
+        t.check()
+    assert t.size() == 100
+
+
+def test_push_checks_the_gradient_row_count_and_an_unprepared_plan():
+    t = SparseTable(16, "sum", device="cuda", capacity=1 << 12, max_keys=1 << 10)
+    keys = torch.tensor([1, 2, 2, 3, 3, 3], device="cuda")
+    t.pull(keys)
+    with pytest.raises(StatusError):
+        t.push(torch.ones(5, 16, device="cuda"))          # one row short: would read past the buffer
+    with pytest.raises(StatusError):
+        t.push(torch.ones(7, 16, device="cuda"))
     t.check()
-    assert torch.isfinite(r).all()
+    base = t.pull(keys, for_push=False).clone()           # the plan did not zero the aggregation rows ...
+    t.push(torch.ones(6, 16, device="cuda"))              # ... so the push does it
+    t.check()
+    after = t.pull(keys, insert=False, for_push=False); t.check()
+    assert torch.allclose(after - base, torch.tensor([1., 2., 2., 3., 3., 3.], device="cuda")[:, None].expand(6, 16), atol=1e-6)
+
+
+@pytest.mark.parametrize("dim,bag", [(128, 1), (64, 1), (32, 4)])
+def test_pull_in_bf16_is_the_fp32_pull_rounded_once(dim, bag):
+    t = SparseTable(dim, "adagrad", dict(lr=0.05, init_accumulator=0.1), device="cuda", capacity=1 << 15, max_keys=1 << 14)
+    keys = zipf_keys(8192, 3000, 1.1, 4).cuda()
+    full = t.pull(keys, bag_size=bag, mean=bag > 1); t.check()
+    half = t.pull(keys, bag_size=bag, mean=bag > 1, out_dtype=torch.bfloat16); t.check()
+    assert half.dtype == torch.bfloat16 and torch.equal(half, full.to(torch.bfloat16))
+    # the plan of a bf16 pull serves the push like any other
+    t.push(torch.ones(8192 // bag, dim, device="cuda") * 1e-2); t.check()
+
+
+def test_bounded_cta_budget_gives_the_same_results():
+    g, c = pair(32, "adagrad", lr=0.05, init_accumulator=0.1)
+    g.set_cta_budget(1)
+    assert g.engine.pull_blocks() <= 148 and g.engine.push_blocks() <= 148
+    keys = torch.from_numpy(np.random.default_rng(3).permutation(1 << 20)[:20000].astype(np.int64))
+    for step in range(3):
+        grads = torch.randn(20000, 32, generator=torch.Generator().manual_seed(step)) * 1e-2
+        a = g.pull(keys.cuda()); g.push(grads.cuda())
+        b = c.pull(keys); c.push(grads)
+        assert torch.equal(a.cpu(), b)
+    g.check()
+    a, _ = g.get_rows(keys.cuda(), emb_only=False)
+    b, _ = c.get_rows(keys, emb_only=False)
+    assert torch.equal(a.cpu(), b)
+
+
+def test_sync_push_erase_reinsert_store_matches_oracle():
+    """A row erased between sync_push and store leaves a stale entry in the touched list; when the row is recycled
+    and touched again it must be folded exactly once."""
+    g, c = pair(16, "ftrl", sync=True, alpha=0.05, beta=1.0, l1=0.001, l2=0.01)
+    a_keys, b_keys = torch.arange(0, 512), torch.arange(512, 1024)
+    for t_ in (g, c):
+        dev = "cuda" if t_ is g else "cpu"
+        gr = torch.ones(512, 16, device=dev) * 0.25
+        t_.pull(a_keys.to(dev)); t_.push(gr, sync=True)
+        assert t_.erase_keys(a_keys[:256].to(dev)) == 256
+        t_.pull(b_keys.to(dev)); t_.push(gr * 2, sync=True)        # recycles the erased rows
+        t_.pull(a_keys[:256].to(dev)); t_.push(gr[:256] * 3, sync=True)
+        t_.store()
+    g.check()
+    allk = torch.arange(0, 1024)
+    a, fa = g.get_rows(allk.cuda(), emb_only=False)
+    b, fb = c.get_rows(allk, emb_only=False)
+    assert fa.all() and fb.all() and torch.equal(a.cpu(), b)
 
 
 def test_large_batch_1m_keys():
