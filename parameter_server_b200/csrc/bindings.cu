@@ -125,6 +125,9 @@ PYBIND11_MODULE(_C, m) {
         .def("tombstones", &GpuTable::tombstones)
         .def("reserve_rows", &GpuTable::reserve_rows)
         .def("reserve_exact", &GpuTable::reserve_exact)
+        .def("maybe_grow", &GpuTable::maybe_grow)
+        .def("set_auto_grow", &GpuTable::set_auto_grow)
+        .def("grow_count", &GpuTable::grow_count)
         .def("enable_dirty_tracking", &GpuTable::enable_dirty_tracking)
         .def("clear_dirty", [](GpuTable& t, uintptr_t s) { return t.clear_dirty(stream_of(s)); })
         .def("export_window",
@@ -193,7 +196,8 @@ PYBIND11_MODULE(_C, m) {
         .def_readwrite("max_keys", &SparseEngineConfig::max_keys)
         .def_readwrite("pair_capacity", &SparseEngineConfig::pair_capacity)
         .def_readwrite("n_shards", &SparseEngineConfig::n_shards)
-        .def_readwrite("wait_limit_s", &SparseEngineConfig::wait_limit_s);
+        .def_readwrite("wait_limit_s", &SparseEngineConfig::wait_limit_s)
+        .def_readwrite("replicate", &SparseEngineConfig::replicate);
 
     m.attr("FUSED_INSERT") = (unsigned)FUSED_INSERT;
     m.attr("FUSED_COPY_ROWS") = (unsigned)FUSED_COPY_ROWS;
@@ -230,6 +234,9 @@ PYBIND11_MODULE(_C, m) {
         .def("kernel_launches", &SparseEngine::kernel_launches)
         .def("set_wait_limit", &SparseEngine::set_wait_limit)
         .def("set_cta_budget", &SparseEngine::set_cta_budget)
+        .def("set_deterministic", &SparseEngine::set_deterministic)
+        .def("set_mirror", &SparseEngine::set_mirror, py::keep_alive<1, 2>())
+        .def("deterministic", &SparseEngine::deterministic)
         .def("pull_blocks", &SparseEngine::pull_blocks)
         .def("push_blocks", &SparseEngine::push_blocks)
         .def("set_profile", &SparseEngine::set_profile)

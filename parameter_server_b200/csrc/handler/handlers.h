@@ -31,6 +31,15 @@ struct HandlerMetrics {
 // routed by). The client's copy can move on between building and sending when another thread refreshes it; a
 // request stamped with the newer version but routed by the older placement would pass the server's version gate
 // and reach a node that no longer holds the shard.
+// The two smallest int64 values are the "empty" and "erased" markers of every key map in this build (the client's
+// dedup map, the host table, the GPU index): a request that carries one is refused where it enters.
+inline Status check_request_keys(const int64_t* keys, size_t n) {
+    for (size_t i = 0; i < n; ++i)
+        if (keys[i] <= kHostEmptyKey + 1)
+            return Status::InvalidConfig("key " + std::to_string(keys[i]) + " is reserved (INT64_MIN and INT64_MIN + 1 cannot be stored)");
+    return Status::Ok();
+}
+
 class Handler {
 public:
     Handler(Client* client, int32_t sid, int32_t hid) : client_(client), sid_(sid), hid_(hid) {}
@@ -133,6 +142,7 @@ public:
 
     // out: n * dim floats, one row per key position.
     Status pull(const int64_t* keys, size_t n, float* out, int timeout_ms = -1, bool auto_retry = true) {
+        PSB_RETURN_IF_ERROR(check_request_keys(keys, n));
         std::shared_ptr<SparseTablePullOperator> p;
         PSB_RETURN_IF_ERROR(op(&p));
         if (group_) return with_retry([&](int left) { return merged_attempt(*p, keys, n, out, left); }, timeout_ms, auto_retry);
@@ -313,6 +323,7 @@ public:
 
 private:
     Status push(const int64_t* keys, const float* grads, size_t n, RequestType type, int timeout_ms) {
+        PSB_RETURN_IF_ERROR(check_request_keys(keys, n));
         std::shared_ptr<SparseTablePushOperator> p;
         PSB_RETURN_IF_ERROR(op(&p));
         PushAckState ack;  // lives for this call: what the retries need not send again

@@ -17,8 +17,10 @@
 // Not in the reference (it has no model code); this is the dense-MLP kernel of the DLRM and GPT
 // workloads and the compute half of the fused dense pull.
 //
-// Structure per CTA (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2..5 = epilogue (each reads its own 32-lane quarter of TMEM). One 128 x BN tile per CTA,
+// Structure per CTA (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..9 = epilogue (two warps per 32-lane quarter of TMEM, each taking half of the tile's columns; the
+// TMEM load of the next 32-column chunk is in flight while the current one is converted and stored, and the
+// tile's bias is staged in shared memory before the accumulator is ready). One 128 x BN tile per CTA,
 // BK = 64 (one 128-byte swizzle span), kStages-deep mbarrier ring. Every mbarrier wait is bounded;
 // on a time-out the CTA records an error, still frees its TMEM and returns.
 #include <cuda.h>
@@ -40,7 +42,8 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -84,6 +87,13 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
         : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
 // Shared-memory matrix descriptor (version 1 = Blackwell), 128-byte swizzle.
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     uint64_t d = 0;
@@ -108,7 +118,8 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
+// Issue the load of 32 accumulator columns (one row per lane); the registers are valid after tmem_wait_ld.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* v) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -117,8 +128,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
           "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
           "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
           "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        : "r"(taddr)
+        : "memory");
+}
+// Wait for every TMEM load this thread has issued. The registers of the chunk about to be used are operands, so
+// that nothing that reads them can be scheduled ahead of the wait.
+__device__ __forceinline__ void tmem_wait_ld(uint32_t* v) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                   "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+                   "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]),
+                   "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+                 :
+                 : "memory");
 }
 
 template <int BN>
@@ -129,24 +151,24 @@ struct SmemLayout {
     static constexpr int kStages = (BN == 256) ? 4 : 6;
     static constexpr int kTileBytes = kStages * kStageBytes;
     static constexpr int kBarBytes = 256;
-    static constexpr int kTotal = kTileBytes + kBarBytes + 1024;  // + alignment slack
+    static constexpr int kBiasBytes = 2 * 256 * 4;  // the bias of a tile's columns, double-buffered with the accumulator
+    static constexpr int kTotal = kTileBytes + kBarBytes + kBiasBytes + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// Epilogue of one 32-column chunk held by one thread (one output row).
-__device__ __forceinline__ void epilogue_chunk(const GemmEpilogue& ep, float* f, int row, int col0, int N) {
-    if (ep.bias != nullptr) {
+// Epilogue of one 32-column chunk held by one thread (one output row). `bias_s`: the chunk's 32 bias values in
+// shared memory (every lane reads the same words: a broadcast), or nullptr.
+__device__ __forceinline__ void epilogue_chunk(const GemmEpilogue& ep, float* f, int row, int col0, int N,
+                                               const float* bias_s) {
+    if (bias_s != nullptr) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-            if (col0 + j < N) f[j] += ep.bias[col0 + j];
-    }
-    if (ep.bias_bf16 != nullptr) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-            if (col0 + j < N) f[j] += __bfloat162float(ep.bias_bf16[col0 + j]);
+        for (int j = 0; j < 32; j += 4) {
+            const float4 b = *(const float4*)(bias_s + j);
+            f[j] += b.x; f[j + 1] += b.y; f[j + 2] += b.z; f[j + 3] += b.w;
+        }
     }
     if (ep.relu) {
 #pragma unroll
@@ -294,6 +316,11 @@ struct GemmProblemSet {
     GemmEpilogue ep[kMaxGroup];
     int M[kMaxGroup], N[kMaxGroup], K[kMaxGroup];
     int unit_end[kMaxGroup];  // running total of work units (m tile x n tile x k split) up to and including problem i
+    // An MN-major operand whose MN extent is a multiple of 64 is described by a 3-D tensor map
+    // (64 elements, K rows, MN / 64 column blocks), so that ONE bulk-tensor load brings all the 64-wide column blocks
+    // of a stage (2 for A, BN / 64 for B) instead of one load per block: the single producer thread then issues two
+    // loads per k-step for every operand layout.
+    unsigned char a_blocked[kMaxGroup], b_blocked[kMaxGroup];
     int count;
     // Chain: problem i + 1 reads the output of problem i as its A operand (the layers of an MLP, forward or dgrad).
     // done[i * kMaxChainMTiles + m] counts the epilogue warps that have stored their part of an n-tile of row block m
@@ -357,6 +384,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
     uint64_t* tfull_bar = empty_bar + L::kStages;   // [2] accumulator buffer complete
     uint64_t* tempty_bar = tfull_bar + 2;           // [2] accumulator buffer drained
     uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
+    float* bias_smem = (float*)(smem + L::kTileBytes + L::kBarBytes);   // [2][256]
 
     // ---- all-gather role: the first ag.gather_ctas CTAs move remote row blocks of B into the local copy ----
     const int n_gather = ag.enabled ? ag.gather_ctas : 0;
@@ -376,7 +404,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tfull_bar[b], 1);
-            mbar_init(&tempty_bar[b], 4);  // one arrival per epilogue warp
+            mbar_init(&tempty_bar[b], kEpilogueWarps);  // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -399,6 +427,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
+            for (int p = 0; p < ps.count; ++p) {
+                asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&ps.map_a[p]) : "memory");
+                asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&ps.map_b[p]) : "memory");
+            }
             uint32_t it = 0;  // k-tile counter across all tiles of this CTA (drives the stage ring)
             bool ok = true;
             for (int unit = cta; unit < total_units && ok; unit += n_cta) {
@@ -424,7 +456,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                 if (ps.chain && w.p > 0) {
                     // the A operand is the previous layer's output: all n-tiles of this row block must be stored
                     const int prev_n_tiles = (ps.N[w.p - 1] + BN - 1) / BN;
-                    const unsigned target = 4u * (unsigned)prev_n_tiles;  // four epilogue warps per tile
+                    const unsigned target = (unsigned)kEpilogueWarps * (unsigned)prev_n_tiles;  // every epilogue warp of every tile
                     const unsigned* cnt = ps.done + (size_t)(w.p - 1) * kMaxChainMTiles + w.tile_m / BM;
                     const unsigned long long t0 = gtimer();
                     unsigned spins = 0;
@@ -456,12 +488,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                     const int k0 = (kt_begin + kt) * BK;
                     if (!AMN) {
                         tma_load_2d(sa, map_a, &full_bar[s], k0, tile_m);  // box [128 rows][64 k]
+                    } else if (ps.a_blocked[w.p]) {
+                        tma_load_3d(sa, map_a, &full_bar[s], 0, k0, tile_m / 64);  // box [2 blocks][64 k][64 m]
                     } else {
                         tma_load_2d(sa, map_a, &full_bar[s], tile_m, k0);  // box [64 k][64 m]
                         tma_load_2d(sa + 64 * 128, map_a, &full_bar[s], tile_m + 64, k0);
                     }
                     if (!BMN) {
                         tma_load_2d(sb, map_b, &full_bar[s], k0, tile_n);  // box [BN rows][64 k]
+                    } else if (ps.b_blocked[w.p]) {
+                        tma_load_3d(sb, map_b, &full_bar[s], 0, k0, tile_n / 64);  // box [BN / 64 blocks][64 k][64 n]
                     } else {
 #pragma unroll
                         for (int j = 0; j < BN / 64; ++j)
@@ -490,7 +526,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                 for (int kt = 0; kt < num_kt; ++kt, ++it) {
                     const int s = it % L::kStages;
                     const uint32_t ph = (it / L::kStages) & 1u;
-                    if (!mbar_wait(&full_bar[s], ph, limit_ns)) {
+                    // consumers wait longer than producers, so that the wait that reports is the one at the root
+                    if (!mbar_wait(&full_bar[s], ph, limit_ns * 2)) {
                         atomicCAS(err_flag, 0u, 2u);
                         ok = false;
                         break;
@@ -515,7 +552,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
         }
     } else {
         // ------------------------------ epilogue ----------------------------------
-        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        const int ew = warp - 2;             // 0 .. kEpilogueWarps-1
+        const int q = warp & 3;              // TMEM lane quarter this warp may read
+        const int half = ew >> 2;            // which half of the tile's columns this warp drains
+        const int etid = ew * 32 + lane;     // 0 .. 255
+        constexpr int kChunks = BN / 64;     // 32-column chunks per warp
         uint32_t tc = 0;
         for (int unit = cta; unit < total_units; unit += n_cta) {
             const WorkUnit w = decode_unit<BN>(ps, unit, ag);
@@ -524,29 +565,56 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
             const int M = ps.M[w.p], N = ps.N[w.p];
             if (num_kt == 0) continue;
             const uint32_t buf = tc & 1u, tph = (tc >> 1) & 1u;
-            const bool ok = mbar_wait(&tfull_bar[buf], tph, limit_ns * 2);
+            // the bias of the tile's columns does not depend on the MMAs: stage it while they run
+            float* bs = bias_smem + buf * 256;
+            const bool has_bias = ep.bias != nullptr || ep.bias_bf16 != nullptr;
+            if (has_bias && etid < BN) {
+                const int col = tile_n + etid;
+                float v = 0.f;
+                if (col < N) v = ep.bias != nullptr ? ep.bias[col] : __bfloat162float(ep.bias_bf16[col]);
+                bs[etid] = v;
+            }
+            const bool waited = mbar_wait(&tfull_bar[buf], tph, limit_ns * 4);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (!ok) {
-                if (lane == 0) atomicCAS(err_flag, 0u, 3u);
+            // One barrier of the epilogue warps per tile: it publishes the staged bias and makes the decision to give
+            // up uniform (a warp that timed out must not leave the others waiting at the next tile's barrier).
+            uint32_t all_ok;
+            asm volatile(
+                "{\n\t.reg .pred p, q;\n\t"
+                "setp.ne.u32 q, %1, 0;\n\t"
+                "bar.red.and.pred p, 1, %2, q;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(all_ok)
+                : "r"(waited ? 1u : 0u), "r"(32 * kEpilogueWarps)
+                : "memory");
+            if (!all_ok) {
+                if (!waited && lane == 0) atomicCAS(err_flag, 0u, 3u);
                 break;
             }
             const int row = tile_m + q * 32 + lane;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (tile_n + c0 >= N) break;  // warp-uniform
-                uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)BN + (uint32_t)c0, v);
+            const int cbase = half * (BN / 2);
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)BN + (uint32_t)cbase;
+            uint32_t va[32], vb[32];
+            if (tile_n + cbase < N) tmem_ld32_issue(taddr, va);
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) {
+                uint32_t* cur = (c & 1) ? vb : va;
+                uint32_t* nxt = (c & 1) ? va : vb;
+                const int col0 = tile_n + cbase + c * 32;
+                if (col0 >= N) break;  // warp-uniform
+                tmem_wait_ld(cur);
+                if (c + 1 < kChunks && col0 + 32 < N) tmem_ld32_issue(taddr + (uint32_t)(c + 1) * 32u, nxt);
                 if (row < M) {
                     float f[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                    epilogue_chunk(ep, f, row, tile_n + c0, N);
+                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(cur[j]);
+                    epilogue_chunk(ep, f, row, col0, N, has_bias ? bs + cbase + c * 32 : nullptr);
                 }
             }
             // this warp is done reading the buffer: hand it back to the MMA warp
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             if (ps.chain) {
-                // publish this warp's 32 rows of the tile to the next layer: stores -> fence -> counter
+                // publish this warp's part of the tile to the next layer: stores -> fence -> counter
                 __threadfence();
                 asm volatile("fence.proxy.async.global;" ::: "memory");
             }
@@ -594,6 +662,22 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, 
     cuuint32_t box[2] = {64, box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+// MN-major operand [K rows][MN cols] (MN a multiple of 64) as (64, K, MN / 64) with box (64, 64, blocks): the box
+// lands in shared memory block by block ([block][64 k][64 mn], 8 KB per block), which is the layout the MMA
+// descriptors of an MN-major operand walk.
+bool make_map_blocked(CUtensorMap* map, const void* base, uint64_t k_rows, uint64_t mn, uint64_t ld, uint32_t blocks) {
+    EncodeFn enc = get_encode();
+    if (!enc) return false;
+    cuuint64_t dims[3] = {64, k_rows, mn / 64};
+    cuuint64_t strides[2] = {ld * 2, 128};
+    cuuint32_t box[3] = {64, 64, blocks};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
@@ -662,10 +746,18 @@ cudaError_t dispatch(int BN, bool a_mn, bool b_mn, const GemmProblemSet& ps, uns
 int add_problem(GemmProblemSet* ps, int i, int BN, const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep, int M,
                 int N, int K) {
     if ((A.ld % 8) || (B.ld % 8) || ((uintptr_t)A.ptr % 16) || ((uintptr_t)B.ptr % 16)) return -2;  // TMA: 16-byte rule
-    // K-major: tensor [MN rows][K cols], box [tile rows][64]; MN-major: tensor [K rows][MN cols], box [64][64]
-    bool ok = A.mn_major ? make_map(&ps->map_a[i], A.ptr, (uint64_t)K, (uint64_t)M, (uint64_t)A.ld, 64)
+    // K-major: tensor [MN rows][K cols], box [tile rows][64]; MN-major: tensor [K rows][MN cols], box [64][64], or the
+    // blocked 3-D form (one load per stage) when the MN extent is a whole number of 64-wide blocks covering the tile
+    ps->a_blocked[i] = (A.mn_major && M % 64 == 0 && M >= BM) ? 1 : 0;
+    ps->b_blocked[i] = (B.mn_major && N % 64 == 0 && N >= BN) ? 1 : 0;
+    // (if the driver refuses the blocked form, the per-block form does the same job with more loads)
+    if (ps->a_blocked[i] && !make_map_blocked(&ps->map_a[i], A.ptr, (uint64_t)K, (uint64_t)M, (uint64_t)A.ld, BM / 64)) ps->a_blocked[i] = 0;
+    if (ps->b_blocked[i] && !make_map_blocked(&ps->map_b[i], B.ptr, (uint64_t)K, (uint64_t)N, (uint64_t)B.ld, BN / 64)) ps->b_blocked[i] = 0;
+    bool ok = A.mn_major ? (ps->a_blocked[i] ? make_map_blocked(&ps->map_a[i], A.ptr, (uint64_t)K, (uint64_t)M, (uint64_t)A.ld, BM / 64)
+                                             : make_map(&ps->map_a[i], A.ptr, (uint64_t)K, (uint64_t)M, (uint64_t)A.ld, 64))
                          : make_map(&ps->map_a[i], A.ptr, (uint64_t)M, (uint64_t)K, (uint64_t)A.ld, BM);
-    ok = ok && (B.mn_major ? make_map(&ps->map_b[i], B.ptr, (uint64_t)K, (uint64_t)N, (uint64_t)B.ld, 64)
+    ok = ok && (B.mn_major ? (ps->b_blocked[i] ? make_map_blocked(&ps->map_b[i], B.ptr, (uint64_t)K, (uint64_t)N, (uint64_t)B.ld, BN / 64)
+                                               : make_map(&ps->map_b[i], B.ptr, (uint64_t)K, (uint64_t)N, (uint64_t)B.ld, 64))
                            : make_map(&ps->map_b[i], B.ptr, (uint64_t)N, (uint64_t)K, (uint64_t)B.ld, BN));
     if (!ok) return -3;
     ps->ep[i] = ep;

@@ -31,10 +31,32 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, cons
 
 constexpr int kIntWarps = 4;
 
-// Stage the F embedding rows of one sample into rows 1..F of the bf16 tile Ts (row stride LD elements).
-// fp32 rows are rounded here; bf16 rows (a pull that delivered the consumer's dtype) are copied 16 bytes a lane.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Staging of one sample's tile T = [bottom; emb_1..emb_F] as bf16 rows of LD elements.
+//  * bf16 embedding rows (a pull that delivered the consumer's dtype): asynchronous 16-byte copies straight into
+//    shared memory. The kernels keep two tiles per warp and start the copies of the NEXT sample before they compute
+//    on the current one, so every warp always has a whole sample in flight and the loop runs at memory speed.
+//  * fp32 embedding rows: loaded into registers, rounded to bf16, stored (no overlap with the compute).
 template <int D, int LD>
-__device__ __forceinline__ void stage_emb(__nv_bfloat16* Ts, const float* __restrict__ eb, int F, int lane) {
+__device__ __forceinline__ void stage_tile_async(__nv_bfloat16* Ts, const __nv_bfloat16* __restrict__ bottom_row,
+                                                 const __nv_bfloat16* __restrict__ eb, int F, int lane) {
+    constexpr int kLanesPerRow = D / 8;            // 16-byte pieces per row
+    constexpr int kRowsPerIter = 32 / kLanesPerRow;
+    const int sub = lane / kLanesPerRow, piece = lane % kLanesPerRow;
+    if (lane < kLanesPerRow) cp_async16(Ts + lane * 8, bottom_row + lane * 8);
+    for (int r = sub; r < F; r += kRowsPerIter) cp_async16(Ts + (size_t)(r + 1) * LD + piece * 8, eb + (size_t)r * D + piece * 8);
+}
+template <int D, int LD>
+__device__ __forceinline__ void stage_tile_sync(__nv_bfloat16* Ts, const __nv_bfloat16* __restrict__ bottom_row,
+                                                const float* __restrict__ eb, int F, int lane) {
+    for (int d = lane * 8; d < D; d += 256) *(uint4*)(Ts + d) = *(const uint4*)(bottom_row + d);
     for (int r = 0; r < F; ++r) {
 #pragma unroll
         for (int d = lane * 4; d < D; d += 128) {
@@ -47,27 +69,17 @@ __device__ __forceinline__ void stage_emb(__nv_bfloat16* Ts, const float* __rest
         }
     }
 }
-template <int D, int LD>
-__device__ __forceinline__ void stage_emb(__nv_bfloat16* Ts, const __nv_bfloat16* __restrict__ eb, int F, int lane) {
-    constexpr int kLanesPerRow = D / 8;            // 16-byte pieces per row
-    constexpr int kRowsPerIter = 32 / kLanesPerRow;
-    const int sub = lane / kLanesPerRow, piece = lane % kLanesPerRow;
-    // the loads are independent: eight are issued back to back, then stored
-    constexpr int kBatch = 8;
-    for (int r0 = 0; r0 < F; r0 += kBatch * kRowsPerIter) {
-        uint4 v[kBatch];
-#pragma unroll
-        for (int it = 0; it < kBatch; ++it) {
-            const int r = r0 + it * kRowsPerIter + sub;
-            if (r < F) v[it] = *(const uint4*)(eb + (size_t)r * D + piece * 8);
-        }
-#pragma unroll
-        for (int it = 0; it < kBatch; ++it) {
-            const int r = r0 + it * kRowsPerIter + sub;
-            if (r < F) *(uint4*)(Ts + (size_t)(r + 1) * LD + piece * 8) = v[it];
-        }
-    }
-}
+
+template <typename EmbT>
+struct EmbTraits {
+    static constexpr bool kAsync = false;
+    static constexpr int kTiles = 1;
+};
+template <>
+struct EmbTraits<__nv_bfloat16> {
+    static constexpr bool kAsync = true;
+    static constexpr int kTiles = 2;   // double-buffered
+};
 
 // out[b] = [bottom (D) | dot(T_i, T_j) for i > j, row-major over i | 0 pad to ldo]
 template <int D, typename EmbT>
@@ -76,24 +88,36 @@ __global__ void __launch_bounds__(kIntWarps * 32) interaction_fwd_kernel(const _
                                                                          __nv_bfloat16* __restrict__ out, int64_t ldo,
                                                                          int B) {
     constexpr int LD = D + 8;  // bf16 elements per staged row (conflict-free fragment loads)
+    constexpr int kTiles = EmbTraits<EmbT>::kTiles;
     extern __shared__ __align__(16) unsigned char smem_i[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    __nv_bfloat16* Ts = (__nv_bfloat16*)smem_i + (size_t)warp * (32 * LD);
-    __nv_bfloat16* Os = (__nv_bfloat16*)smem_i + (size_t)kIntWarps * (32 * LD) + (size_t)warp * ldo;
+    __nv_bfloat16* T0 = (__nv_bfloat16*)smem_i + (size_t)warp * (kTiles * 32 * LD);
+    __nv_bfloat16* Os = (__nv_bfloat16*)smem_i + (size_t)kIntWarps * (kTiles * 32 * LD) + (size_t)warp * ldo;
     const int nT = F + 1;
     const int npairs = nT * (nT - 1) / 2;
     const int g = lane >> 2, t = lane & 3;
-    for (int idx = lane; idx < 32 * LD; idx += 32) Ts[idx] = __float2bfloat16_rn(0.f);
+    for (int idx = lane; idx < kTiles * 32 * LD; idx += 32) T0[idx] = __float2bfloat16_rn(0.f);
     __syncwarp();
-    for (int b = blockIdx.x * kIntWarps + warp; b < B; b += gridDim.x * kIntWarps) {
-        // stage T: row 0 = bottom (bf16), rows 1..F = emb
-        for (int d = lane * 8; d < D; d += 256) {
-            uint4 v = *(const uint4*)(bottom + (size_t)b * ldb + d);
-            *(uint4*)(Ts + d) = v;
-            *(uint4*)(Os + d) = v;
+    const int stride = gridDim.x * kIntWarps;
+    int b = blockIdx.x * kIntWarps + warp;
+    if constexpr (EmbTraits<EmbT>::kAsync) {
+        if (b < B) stage_tile_async<D, LD>(T0, bottom + (size_t)b * ldb, emb + (size_t)b * F * D, F, lane);
+        cp_async_commit();
+    }
+    for (int cur = 0; b < B; b += stride, cur ^= (kTiles - 1)) {
+        __nv_bfloat16* Ts = T0 + (size_t)cur * (32 * LD);
+        if constexpr (EmbTraits<EmbT>::kAsync) {
+            // start the next sample's copies into the other tile, then wait for this sample's
+            const int nb = b + stride;
+            if (nb < B)
+                stage_tile_async<D, LD>(T0 + (size_t)(cur ^ 1) * (32 * LD), bottom + (size_t)nb * ldb, emb + (size_t)nb * F * D, F, lane);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            stage_tile_sync<D, LD>(Ts, bottom + (size_t)b * ldb, emb + (size_t)b * F * D, F, lane);
         }
-        stage_emb<D, LD>(Ts, emb + (size_t)b * F * D, F, lane);
         __syncwarp();
+        for (int d = lane * 8; d < D; d += 256) *(uint4*)(Os + d) = *(const uint4*)(Ts + d);
         // lower-triangular 16x8 tiles of the 32x32 Gram matrix: (mt, nt) with nt*8 < (mt+1)*16
         float acc[6][4];
 #pragma unroll
@@ -139,6 +163,7 @@ __global__ void __launch_bounds__(kIntWarps * 32) interaction_fwd_kernel(const _
         for (int c = lane * 8; c < ldo; c += 256) *(uint4*)(o + c) = *(const uint4*)(Os + c);
         __syncwarp();
     }
+    if constexpr (EmbTraits<EmbT>::kAsync) cp_async_wait<0>();
 }
 
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* smem_row) {
@@ -150,9 +175,10 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* smem_
 
 // dT = G T with G the symmetric (zero-diagonal) matrix of pair gradients.
 // d_bottom (bf16) = (dout[:, :D] + dT_0), masked by (bottom > 0) when relu_mask; d_emb (fp32) = dT_{1..F}.
-// T is staged row-major ([j][d], as in the forward kernel, 16 bytes a lane); the B fragments of G x T, which want
-// the two k (= j) values of a register next to each other, come out of ldmatrix.trans, so no transposed copy of T
-// is ever written.
+// T is staged row-major ([j][d], as in the forward kernel); the B fragments of G x T, which want the two k (= j)
+// values of a register next to each other, come out of ldmatrix.trans, so no transposed copy of T is ever written.
+// The incoming gradient row (dout) is staged next to T, and with bf16 embedding rows both are double-buffered
+// asynchronous copies (see stage_tile_async).
 template <int D, typename EmbT>
 __global__ void __launch_bounds__(kIntWarps * 32) interaction_bwd_kernel(const __nv_bfloat16* __restrict__ dout, int64_t ldo,
                                                                          const __nv_bfloat16* __restrict__ bottom,
@@ -161,11 +187,15 @@ __global__ void __launch_bounds__(kIntWarps * 32) interaction_bwd_kernel(const _
                                                                          float* __restrict__ demb, int B, int relu_mask) {
     constexpr int LG = 40;     // bf16 per row of G (80 B: conflict-free fragment loads)
     constexpr int LD = D + 8;  // bf16 per row of T (rows 16 bytes apart modulo 128: conflict-free ldmatrix)
+    constexpr int kTiles = EmbTraits<EmbT>::kTiles;
+    constexpr int kMaxPairs = kMaxT * (kMaxT - 1) / 2;
+    constexpr int kGin = (D + kMaxPairs + 7) / 8 * 8;   // staged copy of one dout row, elements
+    constexpr int kPerWarp = kTiles * (32 * LD + kGin) + 32 * LG;
     extern __shared__ __align__(16) unsigned char smem_i[];
-    __shared__ unsigned char s_pi[kMaxT * (kMaxT - 1) / 2], s_pj[kMaxT * (kMaxT - 1) / 2];
+    __shared__ unsigned char s_pi[kMaxPairs], s_pj[kMaxPairs];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    __nv_bfloat16* Ts = (__nv_bfloat16*)smem_i + (size_t)warp * (32 * LD + 32 * LG);
-    __nv_bfloat16* Gs = Ts + 32 * LD;
+    __nv_bfloat16* T0 = (__nv_bfloat16*)smem_i + (size_t)warp * kPerWarp;   // [kTiles][32*LD + kGin]
+    __nv_bfloat16* Gs = T0 + kTiles * (32 * LD + kGin);
     const int nT = F + 1;
     const int npairs = nT * (nT - 1) / 2;
     const int g = lane >> 2, t = lane & 3;
@@ -177,18 +207,42 @@ __global__ void __launch_bounds__(kIntWarps * 32) interaction_bwd_kernel(const _
         s_pi[p] = (unsigned char)i;
         s_pj[p] = (unsigned char)(p - i * (i - 1) / 2);
     }
-    for (int idx = lane; idx < 32 * LD + 32 * LG; idx += 32) Ts[idx] = __float2bfloat16_rn(0.f);
+    for (int idx = lane; idx < kPerWarp; idx += 32) T0[idx] = __float2bfloat16_rn(0.f);
     __syncthreads();
-    for (int b = blockIdx.x * kIntWarps + warp; b < B; b += gridDim.x * kIntWarps) {
-        const __nv_bfloat16* go = dout + (size_t)b * ldo;
+    const int row_pieces = (int)((D + npairs + 7) / 8);   // 16-byte pieces of a dout row that hold data
+    const int stride = gridDim.x * kIntWarps;
+    int b = blockIdx.x * kIntWarps + warp;
+    auto stage_async = [&](int sample, __nv_bfloat16* tile) {
+        if constexpr (EmbTraits<EmbT>::kAsync) {
+            stage_tile_async<D, LD>(tile, bottom + (size_t)sample * ldb, emb + (size_t)sample * F * D, F, lane);
+            const __nv_bfloat16* go = dout + (size_t)sample * ldo;
+            for (int c = lane; c < row_pieces && c * 8 + 8 <= ldo; c += 32) cp_async16(tile + 32 * LD + c * 8, go + c * 8);
+        }
+    };
+    if constexpr (EmbTraits<EmbT>::kAsync) {
+        if (b < B) stage_async(b, T0);
+        cp_async_commit();
+    }
+    for (int cur = 0; b < B; b += stride, cur ^= (kTiles - 1)) {
+        __nv_bfloat16* Ts = T0 + (size_t)cur * (32 * LD + kGin);
+        __nv_bfloat16* Gin = Ts + 32 * LD;
+        if constexpr (EmbTraits<EmbT>::kAsync) {
+            const int nb = b + stride;
+            if (nb < B) stage_async(nb, T0 + (size_t)(cur ^ 1) * (32 * LD + kGin));
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            stage_tile_sync<D, LD>(Ts, bottom + (size_t)b * ldb, emb + (size_t)b * F * D, F, lane);
+            const __nv_bfloat16* go = dout + (size_t)b * ldo;
+            for (int c = lane; c < row_pieces && c * 8 + 8 <= ldo; c += 32) *(uint4*)(Gin + c * 8) = *(const uint4*)(go + c * 8);
+        }
+        __syncwarp();
         for (int p = lane; p < npairs; p += 32) {
             const int i = s_pi[p], j = s_pj[p];
-            const __nv_bfloat16 v = go[D + p];
+            const __nv_bfloat16 v = Gin[D + p];
             Gs[i * LG + j] = v;
             Gs[j * LG + i] = v;
         }
-        for (int d = lane * 8; d < D; d += 256) *(uint4*)(Ts + d) = *(const uint4*)(bottom + (size_t)b * ldb + d);
-        stage_emb<D, LD>(Ts, emb + (size_t)b * F * D, F, lane);
         __syncwarp();
         // A = G (row-major [i][j]); M = 32, N = D, K = 32
         uint32_t a[2][2][4];
@@ -221,7 +275,7 @@ __global__ void __launch_bounds__(kIntWarps * 32) interaction_bwd_kernel(const _
                     const int i = mt * 16 + g + h * 8;
                     const float v0 = acc[mt][h * 2], v1 = acc[mt][h * 2 + 1];
                     if (i == 0) {
-                        float r0 = v0 + __bfloat162float(go[d0]), r1 = v1 + __bfloat162float(go[d0 + 1]);
+                        float r0 = v0 + __bfloat162float(Gin[d0]), r1 = v1 + __bfloat162float(Gin[d0 + 1]);
                         if (relu_mask) {
                             if (!(__bfloat162float(Ts[d0]) > 0.f)) r0 = 0.f;
                             if (!(__bfloat162float(Ts[d0 + 1]) > 0.f)) r1 = 0.f;
@@ -234,6 +288,7 @@ __global__ void __launch_bounds__(kIntWarps * 32) interaction_bwd_kernel(const _
         }
         __syncwarp();
     }
+    if constexpr (EmbTraits<EmbT>::kAsync) cp_async_wait<0>();
 }
 
 // ---- output layer + sigmoid + BCE, forward and backward ------------------------------------------
@@ -347,14 +402,14 @@ __global__ void cast_pad_kernel(const float* __restrict__ x, int B, int Kin, __n
 
 template <int D, typename EmbT>
 int launch_int_fwd(const void* bottom, int64_t ldb, const EmbT* emb, int F, void* out, int64_t ldo, int B, cudaStream_t s) {
-    const size_t smem = (size_t)kIntWarps * 32 * (D + 8) * 2 + (size_t)kIntWarps * ldo * 2;
+    const size_t smem = (size_t)kIntWarps * EmbTraits<EmbT>::kTiles * 32 * (D + 8) * 2 + (size_t)kIntWarps * ldo * 2;
     static size_t configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(interaction_fwd_kernel<D, EmbT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    const int blocks = std::min((B + kIntWarps - 1) / kIntWarps, 148 * 4);
+    const int blocks = std::min((B + kIntWarps - 1) / kIntWarps, 148 * (EmbTraits<EmbT>::kAsync ? 3 : 4));
     interaction_fwd_kernel<D, EmbT><<<blocks, kIntWarps * 32, smem, s>>>((const __nv_bfloat16*)bottom, ldb, emb, F,
                                                                          (__nv_bfloat16*)out, ldo, B);
     return (int)cudaGetLastError();
@@ -363,14 +418,15 @@ int launch_int_fwd(const void* bottom, int64_t ldb, const EmbT* emb, int F, void
 template <int D, typename EmbT>
 int launch_int_bwd(const void* dout, int64_t ldo, const void* bottom, int64_t ldb, const EmbT* emb, int F, void* dbottom,
                    int64_t lddb, float* demb, int B, int relu_mask, cudaStream_t s) {
-    const size_t smem = (size_t)kIntWarps * (32 * (D + 8) + 32 * 40) * 2;
+    constexpr int kGin = (D + kMaxT * (kMaxT - 1) / 2 + 7) / 8 * 8;
+    const size_t smem = (size_t)kIntWarps * (EmbTraits<EmbT>::kTiles * (32 * (D + 8) + kGin) + 32 * 40) * 2;
     static size_t configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(interaction_bwd_kernel<D, EmbT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    const int blocks = std::min((B + kIntWarps - 1) / kIntWarps, 148 * 5);
+    const int blocks = std::min((B + kIntWarps - 1) / kIntWarps, 148 * (EmbTraits<EmbT>::kAsync ? 2 : 4));
     interaction_bwd_kernel<D, EmbT><<<blocks, kIntWarps * 32, smem, s>>>((const __nv_bfloat16*)dout, ldo,
                                                                          (const __nv_bfloat16*)bottom, ldb, emb, F,
                                                                          (__nv_bfloat16*)dbottom, lddb, demb, B, relu_mask);
@@ -395,7 +451,7 @@ int interaction_fwd(const void* bottom, int64_t ldb, const void* emb, int emb_bf
 
 int interaction_bwd(const void* dout, int64_t ldo, const void* bottom, int64_t ldb, const void* emb, int emb_bf16, int F,
                     int D, void* dbottom, int64_t lddb, float* demb, int B, int relu_mask, void* stream) {
-    if ((D != 128 && D != 64) || F + 1 > kMaxT || (lddb % 2) || (ldb % 8)) return -2;
+    if ((D != 128 && D != 64) || F + 1 > kMaxT || (lddb % 2) || (ldb % 8) || (ldo % 8) || ldo < D + (F + 1) * F / 2) return -2;
     cudaStream_t s = (cudaStream_t)stream;
     if (emb_bf16) {
         const __nv_bfloat16* e = (const __nv_bfloat16*)emb;

@@ -21,7 +21,11 @@
 //   Q2  store the merged gradient rows into the owners' mailboxes, last CTA publishes the flag
 //   Q3  owner: wait for every source; the head entry of each row's chain folds the sources' gradients in
 //       rank order (reproducible) and applies the optimizer once per row (or accumulates into the sync-push
-//       delta section); last CTA acknowledges the sources
+//       delta section); last CTA acknowledges the sources. With replication the head also appends (key, folded
+//       gradient) to a log in the memory of the GPU that mirrors this rank's shards
+//   Q4  replica holder: wait for the mirrored rank's log, find-or-insert its keys in the mirror table and apply the
+//       same optimizer step to the mirror rows, so a replica is exact after every push
+//       (pico-ps/operator/SparsePushOperator.h:161-168: a push reaches every node that hosts the shard)
 // A kernel on one GPU waits for kernels on the other GPUs; each GPU runs exactly one of them per
 // call, all waits are bounded, and with world == 1 no cross-GPU wait is executed at all. The grid is a
 // parameter: a full-residency grid when the kernel runs alone, a bounded CTA budget when it shares the SMs
@@ -45,7 +49,7 @@ constexpr size_t kPushSmemBytes = (size_t)kHotRows * kHotMaxDim * sizeof(float);
 enum Where : unsigned {
     W_P1 = 1, W_P2, W_KEYFLAG, W_P3A, W_P3B, W_P3C, W_ROWFLAG, W_MAILBOX_OVERFLOW, W_INDEX_FULL, W_POOL_FULL,
     W_DEDUP_FULL, W_RESERVED_KEY,
-    W_Q1 = 32, W_ACK, W_Q2, W_GRADFLAG, W_Q3A, W_Q3B, W_NOROW,
+    W_Q1 = 32, W_ACK, W_Q2, W_GRADFLAG, W_Q3A, W_Q3B, W_NOROW, W_REPACK, W_REPFLAG, W_REP_A, W_REP_FULL,
 };
 
 __device__ __forceinline__ float4 init4(const TableView& t, long long key, unsigned d) {
@@ -108,7 +112,7 @@ __global__ void __launch_bounds__(kThreads, 4) fused_pull_kernel(const FusedArgs
     const int me = a.rank;
     const int W = a.world;
     const unsigned C = a.C;
-    const TableView& T = a.table;
+    const TableView T = *a.table;
     const PeerBufs& mine = a.peer[me];
     const unsigned lanes = lanes_for_dim(a.dim);
     const unsigned group = tid / lanes, ngroups = nthreads / lanes, lane = tid % lanes;
@@ -489,7 +493,7 @@ __global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs
     const int me = a.rank;
     const int W = a.world;
     const unsigned C = a.C;
-    const TableView& T = a.table;
+    const TableView T = *a.table;
     const PeerBufs& mine = a.peer[me];
     const unsigned lanes = lanes_for_dim(a.dim);
     const unsigned group = tid / lanes, ngroups = nthreads / lanes, lane = tid % lanes;
@@ -691,6 +695,24 @@ __global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs
     if (opt.step_from_epoch) opt_set_step(opt, epoch);
     const bool sync_mode = (a.flags & FUSED_SYNC_PUSH) != 0;
     const unsigned dim = a.dim;
+    // Replication: this rank's updates go to the GPU to its right, and it applies the updates of the GPU to its left.
+    // (a sync push only buffers deltas: it appends nothing, but it keeps the hand-shake of the log going so that
+    // the epochs of later pushes line up)
+    const bool replicate = (a.flags & FUSED_REPLICATE) != 0;
+    const bool rep_log = replicate && !sync_mode;
+    const int partner = (me + 1) % W, mirrored = (me + W - 1) % W;
+    unsigned* rep_fill = a.ctl->pad;   // entries appended to the partner's log by this call (reset by the last CTA)
+    if (replicate) {
+        // the partner must have applied the log of the previous push before it is overwritten
+        int ok = 1;
+        if (threadIdx.x == 0 && !wait_flag_ge(mine.rep_ack, epoch - 1u, a.limit_ns)) {
+            set_status(a.ctl, kStTimeout, W_REPACK);
+            ok = 0;
+        }
+        if (!__syncthreads_and(ok)) return;
+    }
+    const unsigned gl0 = (threadIdx.x & 31u) / lanes * lanes;  // first lane of this group inside its warp
+    const unsigned gmask = (lanes >= 32u ? 0xffffffffu : ((1u << lanes) - 1u)) << gl0;
     for (unsigned e = group; e < total_in; e += ngroups) {
         int r = 0;
         while (e >= s_in[r + 1]) ++r;
@@ -745,6 +767,17 @@ __global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs
                 own = a.agg + (size_t)a.send_ret[(size_t)me * C + (ids[k] - (unsigned)me * C)] * dim;
         float* w = T.row_ptr(row);
         float* delta = w + (size_t)(T.n_opt_slots + 1) * dim;
+        float* rep_dst = nullptr;
+        if (rep_log) {
+            unsigned j = 0;
+            if (lane == 0) {
+                j = atomicAdd(rep_fill, 1u);
+                if (j < (unsigned)W * C) a.peer[partner].rep_keys[j] = T.slots[slot].key;
+                else set_status(a.ctl, kStError, W_REP_FULL);
+            }
+            j = __shfl_sync(gmask, j, gl0);
+            if (j < (unsigned)W * C) rep_dst = a.peer[partner].rep_grad + (size_t)j * dim;
+        }
         for (unsigned d = lane * 4; d < dim; d += lanes * 4) {
             float4 gv = *(const float4*)(((int)(ids[0] / C) == me ? own : mine.mail_grad + (size_t)ids[0] * dim) + d);
 #pragma unroll
@@ -754,6 +787,7 @@ __global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs
                 gv.x = __fadd_rn(gv.x, o.x); gv.y = __fadd_rn(gv.y, o.y);
                 gv.z = __fadd_rn(gv.z, o.z); gv.w = __fadd_rn(gv.w, o.w);
             }
+            if (rep_dst != nullptr) *(float4*)(rep_dst + d) = gv;   // the replica gets what the row is updated with
             if (sync_mode) {
                 float4 dv = *(float4*)(delta + d);
                 dv.x += gv.x; dv.y += gv.y; dv.z += gv.z; dv.w += gv.w;
@@ -790,6 +824,106 @@ __global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs
         if (cta_arrive_last(&a.ctl->arrive[1], nblocks)) {
             if (threadIdx.x < (unsigned)W && (int)threadIdx.x != me)
                 st_release_sys(&a.peer[threadIdx.x].push_ack[me], epoch);
+        }
+    }
+    // ---- Q4 (replica holder) -----------------------------------------------------------------------------
+    if (replicate) {
+        TableView R = *a.mirror;
+        // a mirror row starts from the OWNER's initial value of the key
+        R.init_seed = T.init_seed;
+        R.init_range = T.init_range;
+        R.slot_init[0] = T.slot_init[0];
+        R.slot_init[1] = T.slot_init[1];
+        // the log this rank WROTE is complete when every CTA is past Q3: the last one publishes count + flag
+        if (cta_arrive_last(&a.ctl->arrive[2], nblocks)) {
+            if (threadIdx.x == 0) {
+                const unsigned filled = min(*((volatile unsigned*)rep_fill), (unsigned)W * C);
+                *rep_fill = 0;
+                *a.peer[partner].rep_cnt = filled;
+                __threadfence_system();
+                st_release_sys(a.peer[partner].rep_flag, epoch);
+            }
+        }
+        // the log this rank RECEIVES (from the rank it mirrors)
+        {
+            int ok = 1;
+            if (threadIdx.x == 0 && !wait_flag_ge(mine.rep_flag, epoch, a.limit_ns)) {
+                set_status(a.ctl, kStTimeout, W_REPFLAG);
+                ok = 0;
+            }
+            if (ld_acquire_gpu(&a.ctl->status) != 0u) ok = 0;
+            if (!__syncthreads_and(ok)) return;
+        }
+        const unsigned n_log = min(ld_relaxed_sys(mine.rep_cnt), (unsigned)W * C);
+        unsigned* n_new_rep = a.ctl->pad + 1;
+        // (a) one thread per entry: find or insert the key in the mirror and give it a row
+        const unsigned wl = threadIdx.x & 31u;
+        for (unsigned j0 = (tid & ~31u); j0 < n_log; j0 += nthreads) {
+            const unsigned j = j0 + wl;
+            bool attached = false, inserted = false;
+            unsigned slot = kNoSlot;
+            if (j < n_log) {
+                slot = table_find_or_insert(R, mine.rep_keys[j], true, &inserted);
+                if (slot == kNoSlot) {
+                    set_soft_status(a.ctl, kStOom, W_INDEX_FULL);
+                } else {
+                    bool oom = false;
+                    attached = table_attach_row(R, slot, &oom);
+                    if (oom) set_soft_status(a.ctl, kStOom, W_POOL_FULL);
+                }
+                a.rep_slot[j] = slot;
+            }
+            const unsigned amask = __ballot_sync(0xffffffffu, attached);
+            if (amask) {
+                const int al = __ffs(amask) - 1;
+                unsigned base = 0;
+                if ((int)wl == al) base = atomicAdd(n_new_rep, (unsigned)__popc(amask));
+                base = __shfl_sync(0xffffffffu, base, al);
+                if (attached) a.rep_new[base + __popc(amask & ((1u << wl) - 1u))] = slot;
+            }
+            const unsigned imask = __ballot_sync(0xffffffffu, inserted);
+            if (imask && (int)wl == __ffs(imask) - 1) atomicAdd(R.n_items, (unsigned long long)__popc(imask));
+        }
+        if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_REP_A)) return;
+        // (b) rows the mirror did not have yet start from the key's initial value, exactly like on the owner
+        const unsigned n_new = *((volatile unsigned*)n_new_rep);
+        for (unsigned j = group; j < n_new; j += ngroups) {
+            const unsigned slot = a.rep_new[j];
+            const unsigned row = R.slots[slot].row;
+            if (row < kRowPending) row_init(R, R.row_ptr(row), R.slots[slot].key, lane, lanes);
+        }
+        if (n_new > 0) {
+            if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_REP_A)) return;
+        }
+        // (c) the same optimizer step with the same gradient: the mirror row stays bit-identical to the owner's
+        for (unsigned j = group; j < n_log; j += ngroups) {
+            const unsigned slot = a.rep_slot[j];
+            if (slot == kNoSlot) continue;
+            const unsigned row = R.slots[slot].row;
+            if (row >= kRowPending) continue;
+            float* w = R.row_ptr(row);
+            const float* g = mine.rep_grad + (size_t)j * dim;
+            for (unsigned d = lane * 4; d < dim; d += lanes * 4) {
+                const float4 gv = *(const float4*)(g + d);
+                float4 wv = *(float4*)(w + d);
+                float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
+                if (R.n_opt_slots > 0) s0 = *(float4*)(w + dim + d);
+                if (R.n_opt_slots > 1) s1 = *(float4*)(w + 2 * dim + d);
+                opt_update(opt, wv.x, s0.x, s1.x, gv.x);
+                opt_update(opt, wv.y, s0.y, s1.y, gv.y);
+                opt_update(opt, wv.z, s0.z, s1.z, gv.z);
+                opt_update(opt, wv.w, s0.w, s1.w, gv.w);
+                *(float4*)(w + d) = wv;
+                if (R.n_opt_slots > 0) *(float4*)(w + dim + d) = s0;
+                if (R.n_opt_slots > 1) *(float4*)(w + 2 * dim + d) = s1;
+            }
+        }
+        // last CTA out: the log may be overwritten by the mirrored rank's next push
+        if (cta_arrive_last(&a.ctl->arrive[3], nblocks)) {
+            if (threadIdx.x == 0) {
+                *n_new_rep = 0;
+                st_release_sys(a.peer[mirrored].rep_ack, epoch);
+            }
         }
     }
     PROF(12);

@@ -19,6 +19,12 @@ struct PeerBufs {
     float* rows_in;        // [N][dim] rows returned by remote owners, indexed by unique id (fp32, or bf16 in the
                            // first half of the buffer when the pull asked for bf16 output without pooling)
     float* mail_grad;      // [world][C][dim] merged gradients sent by each source rank
+    // ---- replica log (only with replication): written by the rank whose shards this GPU mirrors ----
+    unsigned* rep_flag;    // [1] epoch written by the mirrored rank once its log of this push is complete
+    unsigned* rep_cnt;     // [1] entries in the log
+    unsigned* rep_ack;     // [1] epoch written by the rank that holds MY mirror once it has applied my log
+    long long* rep_keys;   // [world*C] keys of the rows the mirrored rank updated
+    float* rep_grad;       // [world*C][dim] the gradient each of them was updated with (all sources folded)
 };
 
 enum FusedFlags : unsigned {
@@ -30,6 +36,7 @@ enum FusedFlags : unsigned {
     FUSED_OUT_BF16 = 32u,     // pull output is bf16 (the consumer's activation dtype); with bag_size 1 the rows
                               // also cross NVLink as bf16, which halves the bytes of the row-return phase
     FUSED_AGG_READY = 64u,    // push: the per-unique gradient sums are already in `agg` (deterministic pre-pass)
+    FUSED_REPLICATE = 128u,   // push: every row update is also applied to the row's replica on the partner GPU
 };
 
 struct FusedArgs {
@@ -61,7 +68,12 @@ struct FusedArgs {
     unsigned long long* prof;  // [16] phase timestamps written by CTA 0 (nullptr = off)
     const int* shard_owner;  // [n_shards] owning rank of every global shard
     int n_shards;
-    TableView table;
+    // The table views live in device memory (GpuTable::view_dev): a launch replayed from a CUDA graph then sees an
+    // index that the host has grown, or dirty tracking that was switched on, since the capture.
+    const TableView* table;
+    const TableView* mirror;  // push with FUSED_REPLICATE: the local table that mirrors rank (rank - 1) % world
+    unsigned* rep_slot;       // [world*C] mirror slot of each log entry (scratch of the replica phase)
+    unsigned* rep_new;        // [world*C] list of log entries whose mirror row was attached by this call
     // ---- call inputs / outputs ----------------------------------------------------------------
     const long long* keys;  // [n]
     unsigned n;

@@ -109,6 +109,7 @@ public:
             g.base = table_config(n_shards);
             g.capacity = (uint64_t)config_.at("capacity").as_int(1 << 20);
             g.max_batch = (uint32_t)config_.at("max_batch").as_int(1 << 18);
+            g.max_rows = (uint64_t)std::max<int64_t>(0, config_.at("max_rows").as_int(0));   // fixed size: no index growth
             PSB_RETURN_IF_ERROR(make_gpu_kv_storage(g, out));
         } else if (backend == "host") {
             out->reset(new HostKVStorage(table_config(n_shards)));

@@ -2,6 +2,8 @@
 
 #include <cuda_runtime.h>
 
+#include "../kernels/segment_sum.h"
+
 #include <algorithm>
 #include <stdexcept>
 
@@ -44,6 +46,10 @@ const char* where_name(unsigned w) {
         case 36: return "push: grid barrier after leader election";
         case 37: return "push: grid barrier after cross-rank merge";
         case 38: return "push: key without a backing row (pool exhausted)";
+        case 39: return "push: waiting for the replica holder to apply the previous push's log";
+        case 40: return "push: waiting for the mirrored rank's replica log";
+        case 41: return "push: grid barrier of the replica phase";
+        case 42: return "push: replica log overflow";
         default: return "unknown site";
     }
 }
@@ -69,6 +75,11 @@ SparseEngine::SparseEngine(GpuTable* table, const SparseEngineConfig& cfg) : tab
         off_rows_in_ = off; off = align_up(off + (size_t)N * dim * 4);
         off_mail_grad_ = off; off = align_up(off + (size_t)W * C_ * dim * 4);
     }
+    if (cfg_.replicate) {
+        off_rep_words_ = off; off = align_up(off + 4 * sizeof(unsigned));
+        off_rep_keys_ = off; off = align_up(off + (size_t)W * C_ * 8);
+        off_rep_grad_ = off; off = align_up(off + (size_t)W * C_ * dim * 4);
+    }
     symm_.reset(new SymmetricBuffer(table_->device(), off));
 
     // local scratch
@@ -80,6 +91,7 @@ SparseEngine::SparseEngine(GpuTable* table, const SparseEngineConfig& cfg) : tab
     const size_t o_skeys = carve((size_t)W * C_ * 8), o_sret = carve((size_t)W * C_ * 4);
     const size_t o_agg = carve(N * dim * 4);
     const size_t o_res = carve((size_t)W * C_ * 4), o_new = carve((size_t)W * C_ * 4), o_next = carve((size_t)W * C_ * 4);
+    const size_t o_rslot = carve(cfg_.replicate ? (size_t)W * C_ * 4 : 0), o_rnew = carve(cfg_.replicate ? (size_t)W * C_ * 4 : 0);
     const size_t o_cnt = carve(2 * 16 * 4), o_in = carve(2 * kMaxWorld * 4);
     const size_t o_ctl1 = carve(sizeof(KernelCtl)), o_ctl2 = carve(sizeof(KernelCtl));
     const size_t o_prof = carve(16 * 8);
@@ -99,6 +111,8 @@ SparseEngine::SparseEngine(GpuTable* table, const SparseEngineConfig& cfg) : tab
     res_slot_ = (unsigned*)(scratch_ + o_res);
     new_list_ = (unsigned*)(scratch_ + o_new);
     ent_next_ = (unsigned*)(scratch_ + o_next);
+    rep_slot_ = (unsigned*)(scratch_ + o_rslot);
+    rep_new_ = (unsigned*)(scratch_ + o_rnew);
     counters_ = (unsigned*)(scratch_ + o_cnt);
     in_cnt_ = (unsigned*)(scratch_ + o_in);
     ctl_pull_ = (KernelCtl*)(scratch_ + o_ctl1);
@@ -123,6 +137,33 @@ SparseEngine::~SparseEngine() {
     cudaSetDevice(table_->device());
     cudaDeviceSynchronize();
     if (scratch_) cudaFree(scratch_);
+    if (sorted_ids_) cudaFree(sorted_ids_);
+    if (sorted_pos_) cudaFree(sorted_pos_);
+    if (sort_temp_) cudaFree(sort_temp_);
+}
+
+Status SparseEngine::set_mirror(GpuTable* mirror) {
+    if (mirror != nullptr) {
+        if (!cfg_.replicate) return Status::InvalidConfig("set_mirror: the engine was built without the replica log (replicate=false)");
+        if (mirror->dim() != table_->dim() || mirror->stride() != table_->stride() || mirror->device() != table_->device())
+            return Status::InvalidConfig("set_mirror: the mirror table must have the layout and the device of the primary");
+    }
+    mirror_ = mirror;
+    return Status::Ok();
+}
+
+Status SparseEngine::set_deterministic(bool on) {
+    if (on && sort_temp_ == nullptr) {
+        cudaSetDevice(table_->device());
+        sort_temp_bytes_ = ordered_segment_sum_temp_bytes(cfg_.max_keys);
+        if (cudaMalloc(&sorted_ids_, (size_t)cfg_.max_keys * 4) != cudaSuccess || cudaMalloc(&sorted_pos_, (size_t)cfg_.max_keys * 4) != cudaSuccess ||
+            cudaMalloc(&sort_temp_, sort_temp_bytes_) != cudaSuccess) {
+            cudaGetLastError();
+            return Status::OOM("set_deterministic: no memory for the sort scratch");
+        }
+    }
+    deterministic_ = on;
+    return Status::Ok();
 }
 
 Status SparseEngine::connect(const std::vector<std::string>& handles) {
@@ -179,6 +220,12 @@ void SparseEngine::fill_common(FusedArgs& a) const {
         a.peer[r].mail_ret = (unsigned*)(base + off_mail_ret_);
         a.peer[r].rows_in = (float*)(base + off_rows_in_);
         a.peer[r].mail_grad = (float*)(base + off_mail_grad_);
+        unsigned* rw = (unsigned*)(base + off_rep_words_);
+        a.peer[r].rep_flag = rw;
+        a.peer[r].rep_cnt = rw + 1;
+        a.peer[r].rep_ack = rw + 2;
+        a.peer[r].rep_keys = (long long*)(base + off_rep_keys_);
+        a.peer[r].rep_grad = (float*)(base + off_rep_grad_);
     }
     a.dedup = dedup_;
     a.dmask = dedup_slots_ - 1;
@@ -197,7 +244,10 @@ void SparseEngine::fill_common(FusedArgs& a) const {
     a.prof = profile_ ? prof_ : nullptr;
     a.shard_owner = shard_owner_dev_;
     a.n_shards = std::max(cfg_.n_shards, 1);
-    a.table = table_->view();
+    a.table = table_->view_dev();
+    a.mirror = mirror_ != nullptr ? mirror_->view_dev() : a.table;
+    a.rep_slot = rep_slot_;
+    a.rep_new = rep_new_;
 }
 
 Status SparseEngine::pull(const long long* keys, uint32_t n, uint32_t bag_size, void* out, unsigned flags,
@@ -212,6 +262,8 @@ Status SparseEngine::pull(const long long* keys, uint32_t n, uint32_t bag_size, 
     if (flags & FUSED_INSERT) {
         // worst case every rank sends n new keys to this owner; bounded by the mailboxes
         const uint64_t worst = std::min<uint64_t>((uint64_t)cfg_.world * C_, (uint64_t)cfg_.world * n);  // keys this owner may receive
+        Status grown = table_->maybe_grow(worst);   // index load: grows between launches, also under graph replay
+        if (!grown.ok() && grown.code() != StatusCode::OUT_OF_MEMORY) return grown;
         reserve = table_->reserve_rows(worst);
     }
     FusedArgs a;
@@ -252,9 +304,23 @@ Status SparseEngine::push(const float* grads, uint32_t n_rows, const OptConfig& 
         // from zero
         cudaMemsetAsync(agg_, 0, (size_t)plan_n_ * table_->dim() * 4, (cudaStream_t)stream);
     }
+    if (deterministic_ && !(flags & FUSED_AGG_READY)) {
+        // position-ordered sums of the duplicates, then the fused kernel without its own (atomic) segment sum
+        const float scale = (plan_flags_ & FUSED_MEAN) && plan_bag_ > 1 ? 1.0f / (float)plan_bag_ : 1.0f;
+        int rc0 = ordered_segment_sum(inverse_, plan_n_, counters_, &ctl_pull_->epoch, grads, plan_bag_, table_->dim(), scale,
+                                      agg_, sorted_ids_, sorted_pos_, sort_temp_, sort_temp_bytes_, stream);
+        if (rc0 != 0) return Status::Error(std::string("ordered_segment_sum: ") + cudaGetErrorString((cudaError_t)rc0));
+        flags |= FUSED_AGG_READY;
+    }
     FusedArgs a;
     fill_common(a);
     a.flags = (plan_flags_ & FUSED_MEAN) | (flags & (FUSED_SYNC_PUSH | FUSED_AGG_READY));
+    if (mirror_ != nullptr) {
+        a.flags |= FUSED_REPLICATE;
+        // the mirror may get a row for every entry of the mirrored rank's log
+        Status rs = mirror_->reserve_rows(std::min<uint64_t>((uint64_t)cfg_.world * C_, (uint64_t)cfg_.world * plan_n_));
+        if (!rs.ok() && rs.code() != StatusCode::OUT_OF_MEMORY) return rs;
+    }
     ++push_epoch_;
     a.ctl = ctl_push_;
     a.plan_ctl = ctl_pull_;
@@ -267,6 +333,7 @@ Status SparseEngine::push(const float* grads, uint32_t n_rows, const OptConfig& 
     a.hot_rows = hot_rows_;
     int rc = launch_fused_push(a, push_blocks_, stream);
     ++launches_;
+    if (mirror_ != nullptr) mirror_->refresh_usage_async(stream);
     if (rc != 0) return Status::Error(std::string("fused_push launch: ") + cudaGetErrorString((cudaError_t)rc));
     plan_used_ = true;
     return Status::Ok();
@@ -311,6 +378,7 @@ Status SparseEngine::reset(void* stream) {
     cudaMemsetAsync(scratch_, 0, keep_from, s);
     fill_dedup_kernel<<<148 * 4, 256, 0, s>>>(dedup_, dedup_slots_);
     cudaMemsetAsync((char*)symm_->local() + off_flags_, 0, 5 * kMaxWorld * sizeof(unsigned), s);
+    if (cfg_.replicate) cudaMemsetAsync((char*)symm_->local() + off_rep_words_, 0, 4 * sizeof(unsigned), s);
     table_->clear_aux(s);  // a push that was cut short leaves its row chains behind
     cudaError_t e = cudaStreamSynchronize(s);
     pull_epoch_ = push_epoch_ = 0;

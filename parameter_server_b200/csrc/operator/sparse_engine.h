@@ -21,6 +21,7 @@ struct SparseEngineConfig {
     uint32_t pair_capacity = 0;     // C: entries per (source, owner) mailbox; 0 = automatic
     int n_shards = 1;               // global shard count G
     double wait_limit_s = 10.0;     // bound of every device-side wait
+    bool replicate = false;         // allocate the replica log: pushes can keep a mirror on the next rank exact
 };
 
 class SparseEngine {
@@ -53,6 +54,17 @@ public:
     // per SM, which leaves registers and thread slots for kernels of another stream (the dense GEMMs of the same
     // step) to run beside them.
     void set_cta_budget(int ctas_per_sm);
+    // Reproducible pushes: duplicate keys of a batch are summed in position order (a stable sort + an ordered
+    // segment sum before the fused kernel) instead of with fp32 atomics. Together with the rank-ordered fold of the
+    // owners this makes the table after a push a function of the requests alone. Allocates its scratch on first use.
+    Status set_deterministic(bool on);
+    // Replication inside the push (needs SparseEngineConfig::replicate on every rank): `mirror` is the table on THIS
+    // GPU that mirrors the shards of rank (rank - 1) % world (with world 1: of this rank). From then on every push
+    // forwards, per updated row, the key and the folded gradient to rank (rank + 1) % world, whose kernel applies
+    // the same optimizer step to its mirror row: the mirror is exact after every push, no separate sync needed.
+    // nullptr switches it off again (collectively).
+    Status set_mirror(GpuTable* mirror);
+    bool deterministic() const { return deterministic_; }
     int pull_blocks() const { return pull_blocks_; }
     int push_blocks() const { return push_blocks_; }
 
@@ -76,6 +88,9 @@ private:
     uint32_t C_ = 0;
     std::unique_ptr<SymmetricBuffer> symm_;
     size_t off_flags_ = 0, off_mail_keys_ = 0, off_mail_ret_ = 0, off_rows_in_ = 0, off_mail_grad_ = 0;
+    size_t off_rep_words_ = 0, off_rep_keys_ = 0, off_rep_grad_ = 0;
+    GpuTable* mirror_ = nullptr;
+    unsigned *rep_slot_ = nullptr, *rep_new_ = nullptr;
     char* scratch_ = nullptr;
     uint64_t scratch_bytes_ = 0;
     // carved from scratch_
@@ -96,6 +111,10 @@ private:
     int num_sms_ = 0;
     unsigned hot_rows_ = 24;
     bool failed_ = false;                            // a fatal device status was seen: reset() first
+    bool deterministic_ = false;
+    unsigned *sorted_ids_ = nullptr, *sorted_pos_ = nullptr;   // scratch of the ordered pre-aggregation
+    void* sort_temp_ = nullptr;
+    size_t sort_temp_bytes_ = 0;
     // last pull (the plan)
     const long long* plan_keys_ = nullptr;
     uint32_t plan_n_ = 0, plan_bag_ = 1;

@@ -25,6 +25,7 @@ public:
         tc.opt_type = cfg.base.opt_type;
         tc.sync_delta = cfg.base.sync_delta;
         tc.index_capacity = std::max<uint64_t>(2 * cfg.capacity, 4096);
+        tc.max_rows = cfg.max_rows;
         tc.init_seed = cfg.base.init_seed;
         tc.init_range = cfg.base.init_range;
         tc.slot_init0 = cfg.base.slot_init0;

@@ -405,6 +405,9 @@ GpuTable::GpuTable(const GpuTableConfig& cfg) : cfg_(cfg) {
     touched_count_ = (unsigned*)(scratch_ + 3);
     must(cudaHostAlloc((void**)&host_mirror_, 64, cudaHostAllocDefault), "pinned mirror");
     host_mirror_[0] = host_mirror_[1] = 0;
+    must(cudaMalloc(&view_dev_, sizeof(TableView)), "device view");
+    auto_grow_ = cfg_.max_rows == 0;   // an explicit row ceiling is a limit the caller wants kept
+    if (!publish_view().ok()) throw std::runtime_error("GpuTable: cannot publish the device view");
     must(cudaDeviceSynchronize(), "init");
 }
 
@@ -418,7 +421,72 @@ GpuTable::~GpuTable() {
     if (touched_list_) cudaFree(touched_list_);
     if (dirty_bits_) cudaFree(dirty_bits_);
     cudaFree(scratch_);
+    if (view_dev_) cudaFree(view_dev_);
     if (host_mirror_) cudaFreeHost((void*)host_mirror_);
+}
+
+Status GpuTable::publish_view() {
+    const TableView v = view();
+    PSB_CUDA_OK(cudaMemcpy(view_dev_, &v, sizeof(TableView), cudaMemcpyHostToDevice));
+    return Status::Ok();
+}
+
+// Raise the row ceiling: the free stack, the per-row bit sets and the slab pointer table are sized by it.
+Status GpuTable::grow_row_ceiling(uint64_t new_max_rows) {
+    const uint64_t slab_rows = 1ull << cfg_.slab_shift;
+    if (new_max_rows > 0xFFFFFF00ull) new_max_rows = 0xFFFFFF00ull;
+    const uint32_t new_slabs = (uint32_t)((new_max_rows + slab_rows - 1) / slab_rows);
+    new_max_rows = (uint64_t)new_slabs * slab_rows;
+    if (new_max_rows <= max_rows_) return Status::Ok();
+    const uint64_t old_words = (max_rows_ + 31) / 32, new_words = (new_max_rows + 31) / 32;
+    auto regrow = [&](void** p, uint64_t old_bytes, uint64_t new_bytes, bool zero_tail) -> Status {
+        void* q = nullptr;
+        if (cudaMalloc(&q, new_bytes) != cudaSuccess) {
+            cudaGetLastError();
+            return Status::OOM("GpuTable: no memory to raise the row ceiling");
+        }
+        if (*p != nullptr && old_bytes) cudaMemcpy(q, *p, old_bytes, cudaMemcpyDeviceToDevice);
+        if (zero_tail && new_bytes > old_bytes) cudaMemset((char*)q + old_bytes, 0, new_bytes - old_bytes);
+        if (*p != nullptr) cudaFree(*p);
+        *p = q;
+        bytes_ += new_bytes - old_bytes;
+        return Status::Ok();
+    };
+    PSB_RETURN_IF_ERROR(check_budget((new_max_rows - max_rows_) * 4 + (new_words - old_words) * 8));
+    PSB_RETURN_IF_ERROR(regrow((void**)&free_rows_, free_cap_ * 4, new_max_rows * 4, false));
+    PSB_RETURN_IF_ERROR(regrow((void**)&touched_bits_, old_words * 4, new_words * 4, true));
+    if (dirty_bits_) PSB_RETURN_IF_ERROR(regrow((void**)&dirty_bits_, old_words * 4, new_words * 4, true));
+    if (touched_list_) {
+        PSB_RETURN_IF_ERROR(regrow((void**)&touched_list_, (uint64_t)touched_cap_ * 4, new_max_rows * 4, false));
+        touched_cap_ = (uint32_t)std::min<uint64_t>(new_max_rows, 0xFFFFFFFFull);
+    }
+    {
+        uint64_t before = bytes_;
+        PSB_RETURN_IF_ERROR(regrow((void**)&slabs_dev_, (uint64_t)max_slabs_ * sizeof(float*), (uint64_t)new_slabs * sizeof(float*), true));
+        bytes_ = before;   // the pointer table is not counted (it never was)
+    }
+    free_cap_ = new_max_rows;
+    max_rows_ = new_max_rows;
+    max_slabs_ = new_slabs;
+    return Status::Ok();
+}
+
+Status GpuTable::maybe_grow(uint64_t n_new) {
+    if (!auto_grow_) return Status::Ok();
+    // live keys as of the last completed usage refresh, plus a margin for calls still in flight (as reserve_rows)
+    const uint64_t bump = (unsigned)host_mirror_[0];
+    const int freec = (int)(unsigned)host_mirror_[1];
+    const uint64_t used = bump - (uint64_t)std::max(freec, 0);
+    if ((used + 3 * n_new) * 2 <= capacity_) return Status::Ok();
+    cudaSetDevice(cfg_.device);
+    PSB_CUDA_OK(cudaDeviceSynchronize());   // nothing may still be probing the old index
+    uint64_t want = capacity_;
+    while ((rows_used() + 3 * n_new) * 2 > want) want *= 2;
+    if (want == capacity_) return Status::Ok();   // the mirror was stale: there is room
+    PSB_RETURN_IF_ERROR(rebuild_index(want, nullptr));
+    PSB_RETURN_IF_ERROR(grow_row_ceiling(capacity_ / 4 * 3));
+    ++grows_;
+    return publish_view();
 }
 
 Status GpuTable::check_budget(uint64_t extra) {
@@ -724,7 +792,7 @@ Status GpuTable::rebuild_index(uint64_t new_capacity, void* stream) {
     slots_ = ns;
     capacity_ = ncap;
     tombstones_ = 0;
-    return Status::Ok();
+    return publish_view();
 }
 
 void GpuTable::enable_dirty_tracking() {
@@ -737,6 +805,7 @@ void GpuTable::enable_dirty_tracking() {
     }
     cudaMemset(dirty_bits_, 0, bit_words * 4);
     bytes_ += bit_words * 4;
+    publish_view();
 }
 
 Status GpuTable::clear_dirty(void* stream) {

@@ -70,6 +70,17 @@ public:
     // Enqueue a copy of the allocation counters into pinned host memory (read by reserve_rows).
     void refresh_usage_async(void* stream);
     TableView view() const;
+    // The same view in device memory, kept current by the table. Kernels whose launch is captured in a CUDA graph
+    // read the table through this pointer, so that what the host changes between replays (a grown index, a larger
+    // row ceiling, dirty tracking switched on) reaches them.
+    const TableView* view_dev() const { return view_dev_; }
+    // Grow the index (and the row ceiling with it) when `n_new` more keys would push its load above one half:
+    // the reference's maps rehash on their own (pico-ps/storage/KVShardStorage.h:861-877 grow_ratio); here the
+    // host calls this between launches (it synchronises the device when it has to grow, which is rare).
+    // `auto_grow` off (the default for tables with an explicit max_rows) makes it a no-op.
+    Status maybe_grow(uint64_t n_new);
+    void set_auto_grow(bool on) { auto_grow_ = on; }
+    uint64_t grow_count() const { return grows_; }
 
     uint64_t size();       // live keys (synchronises)
     uint64_t rows_used();  // rows handed out minus rows on the free stack (synchronises)
@@ -126,6 +137,8 @@ public:
 private:
     Status add_slab();
     Status check_budget(uint64_t extra) ;
+    Status publish_view();
+    Status grow_row_ceiling(uint64_t new_max_rows);
 
     GpuTableConfig cfg_;
     uint32_t stride_ = 0, n_slots_ = 0;
@@ -151,6 +164,9 @@ private:
     uint64_t bytes_ = 0;
     uint64_t tombstones_ = 0;
     std::atomic<bool> healthy_{true};   // read by request threads, re-evaluated by the server's monitor
+    TableView* view_dev_ = nullptr;
+    bool auto_grow_ = true;
+    uint64_t grows_ = 0;
 };
 
 }  // namespace psb

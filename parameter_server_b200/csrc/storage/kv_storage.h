@@ -135,6 +135,7 @@ struct GpuKVStorageConfig {
     HostTableConfig base;         // dim, optimizer, init, limits, n_shards
     uint64_t capacity = 1 << 20;  // expected keys on this server
     uint32_t max_batch = 1 << 18; // largest request (keys) served in one kernel call
+    uint64_t max_rows = 0;        // row ceiling; 0 = follows the index, which then grows with the table
 };
 // Default visibility: operator plug-ins that subclass a built-in operator reference it through the inline code of
 // the storage operator and bind to the host's definition.

@@ -50,6 +50,10 @@ def _pad8(v: int) -> int:
     return (v + 7) // 8 * 8
 
 
+def _pad64(v: int) -> int:
+    return (v + 63) // 64 * 64
+
+
 def field_keys(field_ids: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     """Globally unique int64 key of (field, id): the field index in the bits above 2^40."""
     return (field_ids.to(torch.int64) << 40) | ids.to(torch.int64)
@@ -109,7 +113,9 @@ class DLRM:
         # ---- dense parameters ------------------------------------------------------------------
         self.k_in = _pad8(cfg.num_dense)
         n_inter = D + (F + 1) * F // 2
-        self.k_top = _pad8(n_inter)
+        # the interaction output is padded to whole 64-column blocks (zero columns, zero weight columns): the GEMMs
+        # that read it transposed (dgrad, wgrad) then fetch each operand stage with one bulk-tensor load
+        self.k_top = _pad64(n_inter)
         self.n_inter = n_inter
         bdims = [self.k_in] + list(cfg.bottom)
         tdims = [self.k_top] + list(cfg.top)
@@ -144,9 +150,16 @@ class DLRM:
         # ---- preallocated activations --------------------------------------------------------------
         dev, bf = self.device, torch.bfloat16
         B = batch
-        self.d_dense = torch.empty((B, cfg.num_dense), dtype=torch.float32, device=dev)
-        self.d_keys = torch.empty((B, F), dtype=torch.int64, device=dev)
-        self.d_labels = torch.empty((B,), dtype=torch.float32, device=dev)
+        # Two sets of input buffers: while step t computes on one set, the host -> device copy of batch t + 1 lands in
+        # the other (a copy stream of its own), so the PCIe transfer is off the critical path of the step.
+        self._inputs = [(torch.empty((B, cfg.num_dense), dtype=torch.float32, device=dev),
+                         torch.empty((B, F), dtype=torch.int64, device=dev),
+                         torch.empty((B,), dtype=torch.float32, device=dev)) for _ in range(2)]
+        self._slot = 0
+        self.d_dense, self.d_keys, self.d_labels = self._inputs[0]
+        self.copy_stream = torch.cuda.Stream(device=dev)
+        self._in_ready = [torch.cuda.Event() for _ in range(2)]
+        self._in_consumed = [torch.cuda.Event() for _ in range(2)]
         self.x16 = torch.empty((B, self.k_in), dtype=bf, device=dev)
         self.bot_act = [torch.empty((B, n), dtype=bf, device=dev) for n in cfg.bottom]
         # the pull delivers the embedding rows in the dtype their consumer (the interaction kernels) computes in
@@ -171,6 +184,7 @@ class DLRM:
             self.side = torch.cuda.Stream(device=dev)
             self.sparse.set_cta_budget(sparse_ctas_per_sm)
         self.graph = None
+        self.graphs = [None, None]   # one captured step per input-buffer set
         self.trace = None   # list of (section, CUDA event) while a step is being traced
         self.stamps = None  # device buffer of %globaltimer probes while a traced graph is being captured
 
@@ -390,9 +404,13 @@ class DLRM:
             G.linear_dgrad(l["a"], l["w"], mask=l.get("mask"), out=l["out"])
         return len(layers)
 
+    def _use_slot(self, slot: int) -> None:
+        self._slot = slot
+        self.d_dense, self.d_keys, self.d_labels = self._inputs[slot]
+
     def enable_graph(self) -> None:
-        """Capture the step (every launch of ``forward_backward``) in a CUDA graph; later
-        ``train_step`` calls replay it. Call after a few eager steps. What a captured launch cannot do
+        """Capture the step (every launch of ``forward_backward``) in a CUDA graph, once per input-buffer set; later
+        ``train_step`` calls replay them in turn. Call after a few eager steps. What a captured launch cannot do
         moves out of it: row-pool growth happens on the host before each replay, the call epochs and
         the Adam step live in device memory and advance with every replay."""
         self.sparse.opt.step_from_epoch = 1
@@ -400,19 +418,38 @@ class DLRM:
         self._worst_new_rows = self.sparse.world * self.B * self.cfg.num_sparse
         self.sparse.reserve(4 * self._worst_new_rows)
         torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            self.forward_backward()
-        self.graph = g
+        keep = self._slot
+        for slot in range(2):
+            self._use_slot(slot)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.forward_backward()
+            self.graphs[slot] = g
+        self._use_slot(keep)
+        self.graph = self.graphs[keep]
 
     def train_step(self, dense: torch.Tensor, keys: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
-        """Public API: copy one pinned host batch in, run the step, return the device loss."""
-        self.load_batch(dense, keys, labels)
-        if self.graph is None:
-            return self.forward_backward()
-        self.sparse.reserve(self._worst_new_rows)
-        self.graph.replay()
-        return self.loss
+        """Public API: copy one pinned host batch in, run the step, return the device loss. The copy goes into the
+        input-buffer set that the previous step is NOT using, on a copy stream: when the caller queues steps without
+        waiting for each (the usual training loop), the transfer of batch t + 1 overlaps the compute of step t."""
+        main = torch.cuda.current_stream()
+        slot = self._slot ^ 1
+        self._use_slot(slot)
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(self._in_consumed[slot])   # the step that last read this set has finished
+            self.d_dense.copy_(dense, non_blocking=True)
+            self.d_keys.copy_(keys, non_blocking=True)
+            self.d_labels.copy_(labels, non_blocking=True)
+            self._in_ready[slot].record(self.copy_stream)
+        main.wait_event(self._in_ready[slot])
+        if self.graphs[slot] is None:
+            out = self.forward_backward()
+        else:
+            self.sparse.reserve(self._worst_new_rows)
+            self.graphs[slot].replay()
+            out = self.loss
+        self._in_consumed[slot].record(main)
+        return out
 
     def read_loss(self) -> float:
         """Device -> host read of the last step's loss (synchronises the stream)."""

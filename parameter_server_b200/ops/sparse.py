@@ -49,6 +49,8 @@ class SparseTable:
         n_shards: global shard count G (default: world size); keys map to shards with
             ``jump_consistent_hash(murmur(key), G)`` and shards to ranks with ``shard_owner``.
         sync: allocate the per-row delta section needed by ``sync_push`` + ``store``.
+        replicate: allocate the replica log, so that pushes can keep a mirror on the next rank exact
+            (``parallel.ReplicaSet(table, in_push=True)``).
         read_only: pulls never insert (predictor tables).
         device: ``cuda`` device, or ``cpu`` for the host back-end.
     """
@@ -59,7 +61,7 @@ class SparseTable:
                  capacity: int = 1 << 20, max_keys: int = 1 << 20, n_shards: Optional[int] = None,
                  sync: bool = False, read_only: bool = False, init_range: float = 0.01, seed: int = 0,
                  device=None, group=None, pair_capacity: int = 0, wait_limit_s: float = 10.0,
-                 max_rows: int = 0, slab_shift: Optional[int] = None, memory_limit_bytes: int = 0):
+                 max_rows: int = 0, slab_shift: Optional[int] = None, memory_limit_bytes: int = 0, replicate: bool = False):
         if dim % 4:
             raise ValueError("dim must be a multiple of 4")
         self.dim = dim
@@ -104,6 +106,7 @@ class SparseTable:
                 ec.pair_capacity = int(pair_capacity)
                 ec.n_shards = self.n_shards
                 ec.wait_limit_s = wait_limit_s
+                ec.replicate = bool(replicate)   # room for the replica log (see parallel.ReplicaSet(in_push=True))
                 self.engine = C.SparseEngine(self.table, ec)
                 if self.world > 1:
                     self._connect()
@@ -300,6 +303,10 @@ class SparseTable:
         3x margin for calls still in flight. ``exact=True`` reads the counters synchronously and
         allocates exactly what is asked (for sizing a table up front)."""
         if self.is_cuda:
+            # the index grows with the table (load kept under one half), also between replays of a captured step
+            st = self.table.maybe_grow(int(n_new_rows))
+            if not st.ok() and st.code() != C.StatusCode.OUT_OF_MEMORY:
+                raise_if_error(st)
             st = self.table.reserve_exact(int(n_new_rows)) if exact else self.table.reserve_rows(int(n_new_rows))
             if not st.ok() and st.code() != C.StatusCode.OUT_OF_MEMORY:
                 raise_if_error(st)
@@ -316,6 +323,12 @@ class SparseTable:
         """Re-arm the engine after a fatal device status (time-out, error). Every rank of the group must call it."""
         if self.is_cuda:
             raise_if_error(self.engine.reset(_stream()))
+
+    def set_deterministic(self, on: bool = True) -> None:
+        """Reproducible pushes: duplicate keys are summed in position order and the owners fold the ranks in rank
+        order, so the table after a push is a function of the requests alone (slower on batches with very hot keys)."""
+        if self.is_cuda:
+            raise_if_error(self.engine.set_deterministic(bool(on)))
 
     def set_cta_budget(self, ctas_per_sm: int) -> None:
         """Bound the grid of the fused kernels to ``ctas_per_sm`` CTAs per SM (0 = fill the idle GPU), so that

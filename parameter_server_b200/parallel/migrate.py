@@ -271,13 +271,18 @@ class ReplicaSet:
     second table and ships its own changes to rank ``(r + 1) % world``. For a table on the host back-end the
     constructor hands back the host implementation with the same methods."""
 
-    def __new__(cls, table: SparseTable, batch: int = 1 << 18):
+    def __new__(cls, table: SparseTable, batch: int = 1 << 18, in_push: bool = False):
         if not table.is_cuda:
             return _host.HostReplicaSet(table)
         return super().__new__(cls)
 
-    def __init__(self, table: SparseTable, batch: int = 1 << 18):
+    def __init__(self, table: SparseTable, batch: int = 1 << 18, in_push: bool = False):
+        """``in_push=True`` (the table must have been created with ``replicate=True``): every fused push also
+        applies its row updates to the mirror on the partner GPU from inside the kernel, as the reference's push
+        reaches every node that hosts a shard (pico-ps/operator/SparsePushOperator.h:161-168). The mirror is then
+        exact after every push and ``sync()`` is only needed for rows that changed by other means (set_rows, load)."""
         self.table = table
+        self.in_push = bool(in_push)
         self.world, self.rank = table.world, table.rank
         self.batch = batch
         table.table.enable_dirty_tracking()
@@ -287,6 +292,8 @@ class ReplicaSet:
         self.partner = (self.rank + 1) % self.world      # holds my mirror
         self.mirrored = (self.rank - 1) % self.world     # whose rows my mirror holds
         self._full_next = True                           # the first sync ships everything
+        if self.in_push:
+            raise_if_error(table.engine.set_mirror(self.mirror.table))
 
     def _one_dest(self, n: int, dest: int) -> List[int]:
         send = [0] * self.world

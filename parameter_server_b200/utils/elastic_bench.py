@@ -160,8 +160,11 @@ def main() -> None:
 
     stage_ms, during, phases = [], [], []
     moved_rows = 0
+    per_stage = (len(moving) + a.stages - 1) // a.stages
     for j in range(a.stages):
-        for s in moving[j::a.stages]:
+        # consecutive moving shards: every stage involves every (old owner -> new owner) pair, so all NVLink pairs
+        # carry rows at the same time (a strided choice would single out one pair per stage)
+        for s in moving[j * per_stage:(j + 1) * per_stage]:
             cur[s] = owner1[s]
         st = {}
         ms, got = timed(lambda: reshard(t, cur, batch=1 << 20, inbox=inbox, stats=st,

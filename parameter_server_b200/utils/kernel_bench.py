@@ -199,7 +199,7 @@ def cmd_mlp(a):
     from ..ops import gemm as G
     _, flops_peak, src = peaks()
     M = a.batch
-    for name, dims in (("top forward", (480, 1024, 1024, 512, 256)), ("bottom forward", (16, 512, 256, 128))):
+    for name, dims in (("top forward", (512, 1024, 1024, 512, 256)), ("bottom forward", (16, 512, 256, 128))):
         ws = [(torch.randn(dims[i + 1], dims[i], device="cuda") * (2.0 / dims[i]) ** 0.5).bfloat16() for i in range(len(dims) - 1)]
         bs = [(torch.randn(dims[i + 1], device="cuda") * 0.1).bfloat16() for i in range(len(dims) - 1)]
         x = torch.randn(M, dims[0], device="cuda").bfloat16()
@@ -229,7 +229,80 @@ def cmd_mlp(a):
             t2 = graph_timed(lambda: torch.matmul(l["a"], l["w"].t(), out=l["out"]), a.iters)
             f1 = 2.0 * M * dims[i] * dims[i + 1]
             print(f"    layer {i} [{M} x {dims[i + 1]} x {dims[i]}]: {t*1e6:7.1f} us ({f1/t/1e12:6.1f} TFLOP/s)   cuBLAS {t2*1e6:7.1f} us")
+    # ---- backward: the dgrad chain of the top MLP and the grouped weight gradients of all layers ----
+    dims = (256, 512, 1024, 1024, 512)          # dz widths walking down the top MLP
+    ws = [(torch.randn(dims[i], dims[i + 1], device="cuda") * 0.05).bfloat16() for i in range(len(dims) - 1)]   # [k][n]
+    masks = [torch.randn(M, dims[i + 1], device="cuda").bfloat16() for i in range(len(dims) - 2)] + [None]
+    dz = torch.randn(M, dims[0], device="cuda").bfloat16()
+    outs = [torch.empty(M, d, device="cuda", dtype=torch.bfloat16) for d in dims[1:]]
+    layers, prev = [], dz
+    for w, m, o in zip(ws, masks, outs):
+        layers.append(dict(a=prev, w=w, mask=m, out=o))
+        prev = o
+    fl = sum(2.0 * M * dims[i] * dims[i + 1] for i in range(len(dims) - 1))
+
+    def d_separate():
+        for l in layers:
+            G.linear_dgrad(l["a"], l["w"], mask=l["mask"], out=l["out"])
+
+    def d_cublas():
+        for l in layers:
+            torch.matmul(l["a"], l["w"], out=l["out"])
+
+    for tag, fn in (("one launch per layer", d_separate), ("one chained launch", lambda: G.chain(layers, b_mn=True)),
+                    ("torch.matmul per layer", d_cublas)):
+        t = graph_timed(fn, a.iters)
+        print(f"mlp top dgrad       M={M} {tag:24s}: {t*1e6:8.1f} us  {fl/t/1e12:7.1f} TFLOP/s  {fl/t/flops_peak:5.2f} of {src} bf16 peak")
+    shapes = [(1024, 512), (1024, 1024), (512, 1024), (256, 512), (256, 512), (128, 256)]    # (N_out, K_in) of the wide layers
+    items, fl = [], 0.0
+    for n_out, k_in in shapes:
+        items.append(((torch.randn(M, n_out, device="cuda") * 0.5).bfloat16(), (torch.randn(M, k_in, device="cuda") * 0.5).bfloat16(),
+                      torch.zeros(n_out, k_in, device="cuda")))
+        fl += 2.0 * M * n_out * k_in
+
+    def w_cublas():
+        for dy, x, out in items:
+            torch.matmul(dy.t(), x, out=out.bfloat16() if False else None)
+
+    for tag, fn in (("grouped, one launch", lambda: G.grouped_wgrad(items)),
+                    ("one launch per layer", lambda: [G.linear_wgrad(dy, x, out=out, split_k=0) for dy, x, out in items]),
+                    ("torch.matmul per layer", w_cublas)):
+        t = graph_timed(fn, a.iters)
+        print(f"mlp wgrad (6 layers) M={M} {tag:24s}: {t*1e6:8.1f} us  {fl/t/1e12:7.1f} TFLOP/s  {fl/t/flops_peak:5.2f} of {src} bf16 peak")
     G.check_gemm_errors()
+
+
+def cmd_chain(a):
+    """One MLP pass of the DLRM step as the model launches it (eager launches, for a profiler): ``top_fwd`` and
+    ``top_dgrad`` are one chained launch each, ``wgrad`` is the grouped weight-gradient launch."""
+    from ..ops import gemm as G
+    M = a.batch
+    if a.which == "wgrad":
+        shapes = [(1024, 512), (1024, 1024), (512, 1024), (256, 512), (256, 512), (128, 256)]
+        items = [((torch.randn(M, n, device="cuda") * 0.5).bfloat16(), (torch.randn(M, k, device="cuda") * 0.5).bfloat16(),
+                  torch.zeros(n, k, device="cuda")) for n, k in shapes]
+        fn = lambda: G.grouped_wgrad(items)
+        fl = sum(2.0 * M * n * k for n, k in shapes)
+    else:
+        fwd = a.which == "top_fwd"
+        dims = (512, 1024, 1024, 512, 256) if fwd else (256, 512, 1024, 1024, 512)
+        if fwd:
+            ws = [(torch.randn(dims[i + 1], dims[i], device="cuda") * 0.05).bfloat16() for i in range(4)]
+        else:
+            ws = [(torch.randn(dims[i], dims[i + 1], device="cuda") * 0.05).bfloat16() for i in range(4)]
+        bs = [(torch.randn(dims[i + 1], device="cuda") * 0.1).bfloat16() for i in range(4)]
+        masks = [torch.randn(M, dims[i + 1], device="cuda").bfloat16() for i in range(3)] + [None]
+        x = torch.randn(M, dims[0], device="cuda").bfloat16()
+        outs = [torch.empty(M, d, device="cuda", dtype=torch.bfloat16) for d in dims[1:]]
+        layers, prev = [], x
+        for i in range(4):
+            layers.append(dict(a=prev, w=ws[i], bias=bs[i], relu=True, out=outs[i]) if fwd else dict(a=prev, w=ws[i], mask=masks[i], out=outs[i]))
+            prev = outs[i]
+        fn = lambda: G.chain(layers, b_mn=not fwd)
+        fl = sum(2.0 * M * dims[i] * dims[i + 1] for i in range(4))
+    t = timed(fn, a.iters, flush=not a.no_flush)
+    G.check_gemm_errors()
+    print(f"chain {a.which} M={M}: {t*1e6:8.1f} us (eager launch, CUDA events)  {fl/t/1e12:7.1f} TFLOP/s")
 
 
 def main():
@@ -248,11 +321,14 @@ def main():
     d.add_argument("--numel", type=int, default=64 << 20); d.add_argument("--bf16-grads", action="store_true")
     m = sub.add_parser("mlp")
     m.add_argument("--batch", type=int, default=8192)
-    for p in (g, s, i, d, m):
+    c = sub.add_parser("chain")
+    c.add_argument("--which", default="top_fwd", choices=["top_fwd", "top_dgrad", "wgrad"])
+    c.add_argument("--batch", type=int, default=8192)
+    for p in (g, s, i, d, m, c):
         p.add_argument("--iters", type=int, default=10)
         p.add_argument("--no-flush", action="store_true")
     a = ap.parse_args()
-    {"gemm": cmd_gemm, "sparse": cmd_sparse, "interaction": cmd_interaction, "dense": cmd_dense, "mlp": cmd_mlp}[a.cmd](a)
+    {"gemm": cmd_gemm, "sparse": cmd_sparse, "interaction": cmd_interaction, "dense": cmd_dense, "mlp": cmd_mlp, "chain": cmd_chain}[a.cmd](a)
 
 
 if __name__ == "__main__":

@@ -38,48 +38,67 @@ def main():
     which = sys.argv[1] if len(sys.argv) > 1 else "all"
 
     if which in ("all", "sparse"):
-        for dim, opt, kw in [(64, "adagrad", dict(lr=0.05, init_accumulator=0.1)), (16, "sgd", dict(lr=0.5)),
-                             (128, "adam", dict(lr=0.01))]:
-            n_shards = world * 3 + 1
-            g = SparseTable(dim, opt, kw, n_shards=n_shards, capacity=1 << 16, max_keys=1 << 15, wait_limit_s=5.0)
-            c = SparseTable(dim, opt, kw, n_shards=n_shards, device="cpu", group="none") if rank == 0 else None
-            if c is not None:
-                c.world, c.rank = 1, 0
-                for s in range(n_shards):
-                    c.table.create_shard(s)
-            rng = np.random.default_rng(100 + rank)
-            for step in range(4):
-                n = 20000
-                keys = torch.from_numpy((rng.zipf(1.1, size=n).astype(np.int64) * 7919) % 50000)
-                grads = torch.from_numpy(rng.standard_normal((n, dim)).astype(np.float32) * 1e-2)
-                out = g.pull(keys.cuda())
-                g.push(grads.cuda())
-                g.check()
-                all_keys, all_grads, all_out = gather(keys), gather(grads), gather(out.cpu())
+        # Twice: with the default (atomic) duplicate sums, compared within a tolerance, and in reproducible mode, where
+        # every rank sums its duplicates in position order and the owners fold the ranks in rank order: then the tables
+        # must equal, bit for bit, an oracle that adds in that same order.
+        for deterministic in (False, True):
+            for dim, opt, kw in [(64, "adagrad", dict(lr=0.05, init_accumulator=0.1)), (16, "sgd", dict(lr=0.5)),
+                                 (128, "adam", dict(lr=0.01))]:
+                n_shards = world * 3 + 1
+                g = SparseTable(dim, opt, kw, n_shards=n_shards, capacity=1 << 16, max_keys=1 << 15, wait_limit_s=5.0)
+                g.set_deterministic(deterministic)
+                c = SparseTable(dim, opt, kw, n_shards=n_shards, device="cpu", group="none") if rank == 0 else None
+                if c is not None:
+                    c.world, c.rank = 1, 0
+                    for s in range(n_shards):
+                        c.table.create_shard(s)
+                rng = np.random.default_rng(100 + rank)
+                for step in range(4):
+                    n = 20000
+                    keys = torch.from_numpy((rng.zipf(1.1, size=n).astype(np.int64) * 7919) % 50000)
+                    grads = torch.from_numpy(rng.standard_normal((n, dim)).astype(np.float32) * 1e-2)
+                    out = g.pull(keys.cuda())
+                    g.push(grads.cuda())
+                    g.check()
+                    all_keys, all_grads, all_out = gather(keys), gather(grads), gather(out.cpu())
+                    if rank == 0:
+                        ck = torch.cat(all_keys)
+                        ref = c.pull(ck)
+                        got = torch.cat(all_out)
+                        if deterministic:
+                            assert torch.equal(got, ref), f"pull differs dim={dim} step={step}: {(got-ref).abs().max()}"
+                            # the oracle adds like the kernels: per rank in position order, then the ranks in rank order
+                            us, aggs = [], []
+                            for k_r, g_r in zip(all_keys, all_grads):
+                                u, inv = np.unique(k_r.numpy(), return_inverse=True)
+                                agg = np.zeros((len(u), dim), dtype=np.float32)
+                                np.add.at(agg, inv, g_r.numpy())
+                                us.append(torch.from_numpy(u)); aggs.append(torch.from_numpy(agg))
+                            c.push(torch.cat(aggs), keys=torch.cat(us))
+                        else:
+                            assert mostly_close(got, ref, 1e-3, 2e-5, 2e-3 if opt == "adam" else 2e-5), \
+                                f"pull mismatch dim={dim} step={step}: {(got-ref).abs().max()}"
+                            c.push(torch.cat(all_grads))
+                # final table state: every rank exports its local rows; rank 0 compares with the oracle
+                ks, rs = [], []
+                for k, r in g.export():
+                    ks.append(k.cpu()); rs.append(r.cpu())
+                ks = torch.cat(ks) if ks else torch.empty(0, dtype=torch.int64)
+                rs = torch.cat(rs) if rs else torch.empty(0, g.table.stride())
+                owners = set(int(g.shard_owner[int(x)]) for x in
+                             [__import__("parameter_server_b200").C.sparse_shard_of(int(k), n_shards) for k in ks[:200].tolist()])
+                assert owners <= {rank}, f"rank {rank} holds foreign keys: {owners}"
+                all_ks, all_rs = gather(ks), gather(rs)
                 if rank == 0:
-                    ck = torch.cat(all_keys)
-                    ref = c.pull(ck)
-                    got = torch.cat(all_out)
-                    assert mostly_close(got, ref, 1e-3, 2e-5, 2e-3 if opt == "adam" else 2e-5), \
-                        f"pull mismatch dim={dim} step={step}: {(got-ref).abs().max()}"
-                    c.push(torch.cat(all_grads))
-            # final table state: every rank exports its local rows; rank 0 compares with the oracle
-            ks, rs = [], []
-            for k, r in g.export():
-                ks.append(k.cpu()); rs.append(r.cpu())
-            ks = torch.cat(ks) if ks else torch.empty(0, dtype=torch.int64)
-            rs = torch.cat(rs) if rs else torch.empty(0, g.table.stride())
-            owners = set(int(g.shard_owner[int(x)]) for x in
-                         [__import__("parameter_server_b200").C.sparse_shard_of(int(k), n_shards) for k in ks[:200].tolist()])
-            assert owners <= {rank}, f"rank {rank} holds foreign keys: {owners}"
-            all_ks, all_rs = gather(ks), gather(rs)
-            if rank == 0:
-                K, R = torch.cat(all_ks), torch.cat(all_rs)
-                assert K.numel() == torch.unique(K).numel() == c.size(), (K.numel(), c.size())
-                ref, found = c.get_rows(K, emb_only=False)
-                assert found.all()
-                assert mostly_close(R, ref, 2e-3, 1e-4, 4e-3 if opt == "adam" else 1e-4), f"table mismatch {opt}: {(R-ref).abs().max()}"
-            dist.barrier()
+                    K, R = torch.cat(all_ks), torch.cat(all_rs)
+                    assert K.numel() == torch.unique(K).numel() == c.size(), (K.numel(), c.size())
+                    ref, found = c.get_rows(K, emb_only=False)
+                    assert found.all()
+                    if deterministic:
+                        assert torch.equal(R, ref), f"table differs from the oracle, {opt}: {(R-ref).abs().max()}"
+                    else:
+                        assert mostly_close(R, ref, 2e-3, 1e-4, 4e-3 if opt == "adam" else 1e-4), f"table mismatch {opt}: {(R-ref).abs().max()}"
+                dist.barrier()
         if rank == 0:
             print("sparse ok", flush=True)
 
@@ -157,6 +176,29 @@ def main():
         again = t.pull(keys, insert=False)
         t.check()
         assert torch.equal(again, want)
+        # replication inside the push: the mirror on the partner is exact after every push, so a table that is lost
+        # BETWEEN two steps, with no sync() ever called, comes back bit for bit
+        t3 = SparseTable(32, "adagrad", dict(lr=0.05, init_accumulator=0.1), n_shards=n_shards, capacity=1 << 16,
+                         max_keys=1 << 15, wait_limit_s=5.0, replicate=True)
+        rs3 = ReplicaSet(t3, in_push=True)
+        zk = torch.from_numpy((rng.zipf(1.1, size=20000).astype(np.int64) * 7919) % 30000).cuda()
+        for _ in range(3):
+            t3.pull(zk); t3.push(torch.randn(20000, 32, device="cuda") * 1e-2)
+        t3.check()
+        mine = torch.cat([k for k, _ in t3.export()] or [torch.empty(0, dtype=torch.int64, device="cuda")])
+        want3, _ = t3.get_rows(mine, emb_only=False)
+        n3 = t3.size()
+        assert rs3.mirror.size() == gather(n3)[(rank - 1) % world]
+        if rank == 0:
+            t3.clear()
+        got3 = rs3.restore(0)
+        if rank == 0:
+            assert got3 == n3 == t3.size()
+        back3, found3 = t3.get_rows(mine, emb_only=False)
+        t3.check()
+        assert found3.all() and torch.equal(back3, want3), "the replica kept by the push is not exact"
+        t3.pull(zk); t3.push(torch.randn(20000, 32, device="cuda") * 1e-2); t3.check()     # and training goes on
+        dist.barrier()
         # dump with 2 files per rank, load into a table with another shard count (rehash) and from all ranks' files
         from parameter_server_b200.parallel import checkpoint
         import tempfile

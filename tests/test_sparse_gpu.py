@@ -73,6 +73,63 @@ def test_push_with_duplicates_close_to_oracle():
     assert torch.allclose(a.cpu(), b, rtol=1e-4, atol=1e-6)
 
 
+@pytest.mark.parametrize("opt,kw", [("adagrad", dict(lr=0.05, init_accumulator=0.1)), ("ftrl", dict(alpha=0.05, beta=1.0, l1=0.001, l2=0.01))])
+def test_deterministic_push_with_duplicates_is_bitwise_the_oracle(opt, kw):
+    """In reproducible mode the duplicates of a batch are summed in position order, which is what the host table
+    (and the reference's client-side merge, pico-ps/operator/SparsePushOperator.h:130-146) computes: the tables agree
+    bit for bit, also for a batch whose head key repeats thousands of times."""
+    g, c = pair(64, opt, **kw)
+    g.set_deterministic(True)
+    for step in range(4):
+        keys = zipf_keys(30000, 4000, 1.05, step)
+        grads = torch.randn(30000, 64, generator=torch.Generator().manual_seed(step)) * 1e-3
+        g.pull(keys.cuda())
+        g.push(grads.cuda())
+        c.pull(keys)
+        c.push(grads)
+    g.check()
+    uk = torch.unique(torch.cat([zipf_keys(30000, 4000, 1.05, s_) for s_ in range(4)]))
+    a, fa = g.get_rows(uk.cuda(), emb_only=False)
+    b, fb = c.get_rows(uk, emb_only=False)
+    assert fa.all() and fb.all() and torch.equal(a.cpu(), b)
+
+
+def test_push_keeps_the_replica_exact_without_a_sync():
+    """Replication inside the fused push (pico-ps/operator/SparsePushOperator.h:161-168: a push reaches every holder
+    of a shard): the owner forwards key + folded gradient of every row it updates, the holder of the mirror applies
+    the same step. After any number of pushes the mirror rows equal the primary rows bit for bit, with no sync in
+    between, and a lost table is rebuilt from the mirror exactly. One GPU: the rank is its own partner."""
+    from parameter_server_b200.parallel.migrate import ReplicaSet
+    t = SparseTable(32, "adagrad", dict(lr=0.05, init_accumulator=0.1), device="cuda", capacity=1 << 15, max_keys=1 << 14,
+                    replicate=True)
+    rs = ReplicaSet(t, in_push=True)
+    seen = []
+    for step in range(5):
+        keys = zipf_keys(12000, 3000 + 500 * step, 1.05, step).cuda()
+        t.pull(keys)
+        t.push(torch.randn(12000, 32, device="cuda") * 1e-2)
+        seen.append(keys)
+    t.check()
+    uk = torch.unique(torch.cat(seen))
+    a, fa = t.get_rows(uk, emb_only=False)
+    b, fb = rs.mirror.get_rows(uk, emb_only=False)
+    assert fa.all() and fb.all() and torch.equal(a, b)
+    assert rs.mirror.size() == t.size() == uk.numel()
+    # sync pushes append nothing but keep the hand-shake going; the next plain push still lands in the mirror
+    # the table is lost between two steps; no sync() was ever called
+    t.clear()
+    assert t.size() == 0
+    assert rs.restore(0) == uk.numel()
+    c, fc = t.get_rows(uk, emb_only=False)
+    assert fc.all() and torch.equal(c, a)
+    # training goes on and the mirror keeps up
+    t.pull(seen[0]); t.push(torch.ones(12000, 32, device="cuda") * 1e-2); t.check()
+    u0 = torch.unique(seen[0])
+    a, _ = t.get_rows(u0, emb_only=False)
+    b, _ = rs.mirror.get_rows(u0, emb_only=False)
+    assert torch.equal(a, b)
+
+
 def test_pooling_and_mean_backward():
     g, c = pair(16, "sgd", lr=1.0)
     keys = zipf_keys(4096 * 4, 3000, 1.1, 3)
@@ -249,6 +306,43 @@ def test_sync_push_erase_reinsert_store_matches_oracle():
     g.check()
     allk = torch.arange(0, 1024)
     a, fa = g.get_rows(allk.cuda(), emb_only=False)
+    b, fb = c.get_rows(allk, emb_only=False)
+    assert fa.all() and fb.all() and torch.equal(a.cpu(), b)
+
+
+def test_index_grows_between_replays_of_a_captured_step():
+    """A job that keeps meeting new keys outgrows the index it started with. The host hook that runs before every
+    launch (and before every replay of a captured step) doubles the index when its load would pass one half; the
+    captured kernels read the table through a view in device memory, so they follow the growth."""
+    g, c = pair(16, "adagrad", lr=0.05, init_accumulator=0.1)
+    t = SparseTable(16, "adagrad", dict(lr=0.05, init_accumulator=0.1), n_shards=4, device="cuda", capacity=2048, max_keys=4096)
+    assert t.table.index_capacity() == 4096
+    keys_buf = torch.zeros(4096, dtype=torch.int64, device="cuda")
+    grads = torch.full((4096, 16), 1e-2, device="cuda")
+    out = torch.empty(4096, 16, device="cuda")
+    t.opt.step_from_epoch = 1
+    for _ in range(2):                                   # eager warm-up on the first keys
+        keys_buf.copy_(torch.arange(4096, device="cuda") * 31)
+        t.reserve(4096); t.pull(keys_buf, out=out); t.push(grads)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    t.reserve(4 * 4096)
+    with torch.cuda.graph(graph):
+        t.pull(keys_buf, out=out); t.push(grads)
+    seen = [torch.arange(4096) * 31] * 2
+    for step in range(40):                               # 40 x 4096 new keys through a graph captured at 4096 slots
+        k = torch.arange(4096) * 31 + (step + 1) * 1000003
+        keys_buf.copy_(k.cuda())
+        t.reserve(4096)
+        graph.replay()
+        seen.append(k)
+    t.check()
+    assert t.table.grow_count() >= 3 and t.table.index_capacity() >= 2 * t.size()
+    for k in seen:
+        c.pull(k); c.push(grads.cpu())
+    allk = torch.unique(torch.cat(seen))
+    assert t.size() == allk.numel() == c.size()
+    a, fa = t.get_rows(allk.cuda(), emb_only=False)
     b, fb = c.get_rows(allk, emb_only=False)
     assert fa.all() and fb.all() and torch.equal(a.cpu(), b)
 
