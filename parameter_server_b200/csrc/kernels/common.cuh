@@ -258,7 +258,7 @@ __device__ __forceinline__ void row_init(const TableView& t, float* row, long lo
         *(float4*)(row + d) = v;
     }
     for (unsigned s = 0; s < t.n_opt_slots; ++s) {
-        float iv = t.slot_init[s < 2 ? s : 1];
+        const float iv = s == 0 ? t.slot_init[0] : t.slot_init[1];   // static indices: the view stays in registers
         float4 v = make_float4(iv, iv, iv, iv);
         for (unsigned d = lane * 4; d < t.dim; d += lanes * 4) *(float4*)(row + (s + 1) * t.dim + d) = v;
     }

@@ -94,6 +94,26 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
         : "memory");
 }
 
+// Output path of the epilogue: a warp stages a [32 rows][64 bytes] piece of the tile in shared memory and one lane
+// hands it to the TMA unit, which writes whole lines (rows and columns outside the tensor are clipped by the map).
+// A thread-per-row store would touch 32 different lines per instruction and keeps the load/store unit busy for
+// longer than the MMAs of a small-K tile take.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"((uint64_t)map), "r"(smem_u32(src)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+// Same, adding to what is in global memory (fp32): the split-K partial sums and `accumulate` outputs.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"((uint64_t)map), "r"(smem_u32(src)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 // Shared-memory matrix descriptor (version 1 = Blackwell), 128-byte swizzle.
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     uint64_t d = 0;
@@ -152,7 +172,8 @@ struct SmemLayout {
     static constexpr int kTileBytes = kStages * kStageBytes;
     static constexpr int kBarBytes = 256;
     static constexpr int kBiasBytes = 2 * 256 * 4;  // the bias of a tile's columns, double-buffered with the accumulator
-    static constexpr int kTotal = kTileBytes + kBarBytes + kBiasBytes + 1024;  // + alignment slack
+    static constexpr int kStageOutBytes = kEpilogueWarps * 2048;  // per epilogue warp: [32 rows][64 bytes] output staging
+    static constexpr int kTotal = kTileBytes + kBarBytes + kBiasBytes + kStageOutBytes + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -162,7 +183,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // Epilogue of one 32-column chunk held by one thread (one output row). `bias_s`: the chunk's 32 bias values in
 // shared memory (every lane reads the same words: a broadcast), or nullptr.
 __device__ __forceinline__ void epilogue_chunk(const GemmEpilogue& ep, float* f, int row, int col0, int N,
-                                               const float* bias_s) {
+                                               const float* bias_s, bool row_valid) {
     if (bias_s != nullptr) {
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
@@ -175,7 +196,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpilogue& ep, float* f,
         for (int j = 0; j < 32; ++j) f[j] = fmaxf(f[j], 0.f);
     }
     const bool full = (col0 + 32 <= N);
-    if (ep.mask != nullptr) {
+    if (ep.mask != nullptr && row_valid) {
         const __nv_bfloat16* mp = ep.mask + (size_t)row * ep.ldmask + col0;
         if (full && (ep.ldmask % 8 == 0)) {
 #pragma unroll
@@ -192,6 +213,11 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpilogue& ep, float* f,
                 if (col0 + j < N && !(__bfloat162float(mp[j]) > 0.f)) f[j] = 0.f;
         }
     }
+}
+
+// The thread-per-row output path (d_mode 0).
+__device__ __forceinline__ void store_chunk_rows(const GemmEpilogue& ep, const float* f, int row, int col0, int N) {
+    const bool full = (col0 + 32 <= N);
     if (ep.out_f32 != nullptr) {
         float* op = ep.out_f32 + (size_t)row * ep.ldd + col0;
         if (ep.split_k > 1) {
@@ -321,6 +347,11 @@ struct GemmProblemSet {
     // of a stage (2 for A, BN / 64 for B) instead of one load per block: the single producer thread then issues two
     // loads per k-step for every operand layout.
     unsigned char a_blocked[kMaxGroup], b_blocked[kMaxGroup];
+    // How the epilogue writes problem i: 0 = one thread per row (any alignment, both outputs), 1 = TMA store of bf16
+    // [32 rows][32 cols] pieces, 2 = TMA reduce-add of fp32 [32 rows][16 cols] pieces (split-K partial sums,
+    // `accumulate`), 3 = TMA store of fp32 pieces.
+    CUtensorMap map_d[kMaxGroup];
+    unsigned char d_mode[kMaxGroup];
     int count;
     // Chain: problem i + 1 reads the output of problem i as its A operand (the layers of an MLP, forward or dgrad).
     // done[i * kMaxChainMTiles + m] counts the epilogue warps that have stored their part of an n-tile of row block m
@@ -385,6 +416,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
     uint64_t* tempty_bar = tfull_bar + 2;           // [2] accumulator buffer drained
     uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
     float* bias_smem = (float*)(smem + L::kTileBytes + L::kBarBytes);   // [2][256]
+    uint8_t* stage_out = smem + L::kTileBytes + L::kBarBytes + L::kBiasBytes;   // [kEpilogueWarps][2048]
 
     // ---- all-gather role: the first ag.gather_ctas CTAs move remote row blocks of B into the local copy ----
     const int n_gather = ag.enabled ? ag.gather_ctas : 0;
@@ -430,6 +462,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
             for (int p = 0; p < ps.count; ++p) {
                 asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&ps.map_a[p]) : "memory");
                 asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&ps.map_b[p]) : "memory");
+                if (ps.d_mode[p]) asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&ps.map_d[p]) : "memory");
             }
             uint32_t it = 0;  // k-tile counter across all tiles of this CTA (drives the stage ring)
             bool ok = true;
@@ -596,6 +629,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)BN + (uint32_t)cbase;
             uint32_t va[32], vb[32];
             if (tile_n + cbase < N) tmem_ld32_issue(taddr, va);
+            const int d_mode = ps.d_mode[w.p];
+            const CUtensorMap* map_d = &ps.map_d[w.p];
+            uint8_t* my_stage = stage_out + ew * 2048 + lane * 64;   // this lane's row of the warp's staging piece
+            const int row0 = tile_m + q * 32;
 #pragma unroll
             for (int c = 0; c < kChunks; ++c) {
                 uint32_t* cur = (c & 1) ? vb : va;
@@ -604,17 +641,62 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                 if (col0 >= N) break;  // warp-uniform
                 tmem_wait_ld(cur);
                 if (c + 1 < kChunks && col0 + 32 < N) tmem_ld32_issue(taddr + (uint32_t)(c + 1) * 32u, nxt);
-                if (row < M) {
-                    float f[32];
+                float f[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(cur[j]);
-                    epilogue_chunk(ep, f, row, col0, N, has_bias ? bs + cbase + c * 32 : nullptr);
+                for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(cur[j]);
+                if (d_mode == 0) {
+                    if (row < M) {
+                        epilogue_chunk(ep, f, row, col0, N, has_bias ? bs + cbase + c * 32 : nullptr, true);
+                        store_chunk_rows(ep, f, row, col0, N);
+                    }
+                    continue;
+                }
+                epilogue_chunk(ep, f, row, col0, N, has_bias ? bs + cbase + c * 32 : nullptr, row < M);
+                if (d_mode == 1) {
+                    // bf16: the warp's [32 rows][32 cols] piece, one row (64 bytes) per lane
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 raw;
+                        __nv_bfloat162* h = (__nv_bfloat162*)&raw;
+                        h[0] = __floats2bfloat162_rn(f[j], f[j + 1]);
+                        h[1] = __floats2bfloat162_rn(f[j + 2], f[j + 3]);
+                        h[2] = __floats2bfloat162_rn(f[j + 4], f[j + 5]);
+                        h[3] = __floats2bfloat162_rn(f[j + 6], f[j + 7]);
+                        *(uint4*)(my_stage + j * 2) = raw;
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(map_d, stage_out + ew * 2048, col0, row0);
+                        bulk_commit();
+                        bulk_wait_read0();   // the piece is reused by the next chunk
+                    }
+                    __syncwarp();
+                } else {
+                    // fp32: two [32 rows][16 cols] pieces per chunk
+#pragma unroll
+                    for (int hcol = 0; hcol < 32; hcol += 16) {
+                        if (col0 + hcol >= N) break;   // warp-uniform
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4)
+                            *(float4*)(my_stage + j * 4) = make_float4(f[hcol + j], f[hcol + j + 1], f[hcol + j + 2], f[hcol + j + 3]);
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (d_mode == 2) tma_reduce_add_2d(map_d, stage_out + ew * 2048, col0 + hcol, row0);
+                            else tma_store_2d(map_d, stage_out + ew * 2048, col0 + hcol, row0);
+                            bulk_commit();
+                            bulk_wait_read0();
+                        }
+                        __syncwarp();
+                    }
                 }
             }
             // this warp is done reading the buffer: hand it back to the MMA warp
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             if (ps.chain) {
-                // publish this warp's part of the tile to the next layer: stores -> fence -> counter
+                // publish this warp's part of the tile to the next layer: stores complete -> fence -> counter
+                if (lane == 0) bulk_wait0();
                 __threadfence();
                 asm volatile("fence.proxy.async.global;" ::: "memory");
             }
@@ -679,6 +761,22 @@ bool make_map_blocked(CUtensorMap* map, const void* base, uint64_t k_rows, uint6
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+// Output tensor [rows][cols] (bf16 or fp32, leading dimension ld) with a [32 rows][64 bytes] box, no swizzle.
+bool make_map_out(CUtensorMap* map, void* base, bool f32, uint64_t rows, uint64_t cols, uint64_t ld) {
+    EncodeFn enc = get_encode();
+    if (!enc) return false;
+    const uint64_t elem = f32 ? 4 : 2;
+    if (((uintptr_t)base % 16) || ((ld * elem) % 16)) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * elem};
+    cuuint32_t box[2] = {f32 ? 16u : 32u, 32u};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
@@ -760,6 +858,13 @@ int add_problem(GemmProblemSet* ps, int i, int BN, const GemmOperand& A, const G
                                                : make_map(&ps->map_b[i], B.ptr, (uint64_t)K, (uint64_t)N, (uint64_t)B.ld, 64))
                            : make_map(&ps->map_b[i], B.ptr, (uint64_t)N, (uint64_t)K, (uint64_t)B.ld, BN));
     if (!ok) return -3;
+    ps->d_mode[i] = 0;
+    if (ep.out_bf16 != nullptr && ep.out_f32 == nullptr) {
+        if (make_map_out(&ps->map_d[i], ep.out_bf16, false, (uint64_t)M, (uint64_t)N, (uint64_t)ep.ldd)) ps->d_mode[i] = 1;
+    } else if (ep.out_f32 != nullptr && ep.out_bf16 == nullptr) {
+        if (make_map_out(&ps->map_d[i], ep.out_f32, true, (uint64_t)M, (uint64_t)N, (uint64_t)ep.ldd))
+            ps->d_mode[i] = (ep.split_k > 1 || ep.accumulate) ? 2 : 3;
+    }
     ps->ep[i] = ep;
     ps->M[i] = M;
     ps->N[i] = N;

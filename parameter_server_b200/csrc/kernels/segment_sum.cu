@@ -36,12 +36,12 @@ __global__ void __launch_bounds__(kThreads) ordered_sum_kernel(const unsigned* _
         unsigned lo = 0, hi = n;
         while (lo < hi) {
             const unsigned mid = (lo + hi) >> 1;
-            if (sorted_ids[mid] < u) lo = mid + 1; else hi = mid;
+            if ((sorted_ids[mid] & 0x7fffffffu) < u) lo = mid + 1; else hi = mid;
         }
         unsigned end = lo, top = n;
         while (end < top) {
             const unsigned mid = (end + top) >> 1;
-            if (sorted_ids[mid] <= u) end = mid + 1; else top = mid;
+            if ((sorted_ids[mid] & 0x7fffffffu) <= u) end = mid + 1; else top = mid;
         }
         for (unsigned d = lane * 4; d < dim; d += lanes * 4) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -83,7 +83,7 @@ int ordered_segment_sum(const int* inverse, unsigned n, const unsigned* counters
     size_t cub_bytes = temp_bytes - (size_t)n * sizeof(unsigned);
     iota_kernel<<<148 * 2, kThreads, 0, s>>>(iota, n);
     int bits = 1;
-    while (bits < 32 && (1ull << bits) < (unsigned long long)n) ++bits;   // unique ids are below n
+    while (bits < 31 && (1ull << bits) < (unsigned long long)n) ++bits;   // unique ids are below n; bit 31 is a flag, not part of the id
     cudaError_t e = cub::DeviceRadixSort::SortPairs(cub_temp, cub_bytes, (const unsigned*)inverse, sorted_ids, (const unsigned*)iota,
                                                     sorted_pos, (int)n, 0, bits, s);
     if (e != cudaSuccess) return (int)e;

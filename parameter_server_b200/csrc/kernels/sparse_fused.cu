@@ -128,6 +128,7 @@ __global__ void __launch_bounds__(kThreads, 4) fused_pull_kernel(const FusedArgs
     PROF(0);
     const unsigned wlane = threadIdx.x & 31u;
     const unsigned long long probe_limit = a.dmask + 1ull;
+    const unsigned dup_tag = (epoch << 1) | 1u;
     for (unsigned i0 = (tid & ~31u); i0 < a.n; i0 += nthreads) {
         const unsigned i = i0 + wlane;
         bool active = i < a.n;
@@ -158,6 +159,10 @@ __global__ void __launch_bounds__(kThreads, 4) fused_pull_kernel(const FusedArgs
                 }
                 hh = (hh + 1) & a.dmask;
             }
+            // A key met more than once (by another warp before, or by several lanes of this warp) is tagged with
+            // this call's epoch: the push then knows which gradient rows need summing and which are plain copies.
+            // Nobody ever clears the tag: a value left by an earlier call differs from the current one.
+            if (probes < probe_limit && (!won || __popc(same) > 1)) a.dedup[hh].aux = dup_tag;
             // the table holds >= 2n slots and is emptied by every call; a full table means an earlier call was
             // cut short or two calls overlap on one engine
             if (probes == probe_limit) set_status(a.ctl, kStError, W_DEDUP_FULL);
@@ -380,8 +385,10 @@ __global__ void __launch_bounds__(kThreads, 4) fused_pull_kernel(const FusedArgs
         const unsigned b_lo = min(nbags, blockIdx.x * per), b_hi = min(nbags, b_lo + per);
         for (unsigned i = b_lo * L + threadIdx.x; i < b_hi * L; i += kThreads) {
             const unsigned h = a.pos_slot[i];
-            const unsigned u = a.dedup[h].row;
-            a.inverse[i] = (int)u;
+            const Slot ds = a.dedup[h];
+            const unsigned u = ds.row;
+            // bit 31 of the inverse map: the key occurs more than once in this batch
+            a.inverse[i] = (int)(u | (ds.aux == dup_tag ? kDupBit : 0u));
             const unsigned s = a.uniq_row[u];
             unsigned row = s;  // kRemoteRow stays
             if (s != kRemoteRow) row = (s == kNoSlot) ? kNoRow : T.slots[s].row;
@@ -415,8 +422,9 @@ __global__ void __launch_bounds__(kThreads, 4) fused_pull_kernel(const FusedArgs
                         if (act[k]) {
                             const unsigned row = a.pos_slot[bb[k]];
                             if (row == kRemoteRow) {
-                                if (rows16) src[k].b16 = rin16 + (size_t)a.inverse[bb[k]] * a.dim;
-                                else src[k].f32 = mine.rows_in + (size_t)a.inverse[bb[k]] * a.dim;
+                                const size_t uq = (unsigned)a.inverse[bb[k]] & ~kDupBit;
+                                if (rows16) src[k].b16 = rin16 + uq * a.dim;
+                                else src[k].f32 = mine.rows_in + uq * a.dim;
                             } else if (row < kRowPending) {
                                 src[k].f32 = T.row_ptr(row);
                             }
@@ -451,7 +459,7 @@ __global__ void __launch_bounds__(kThreads, 4) fused_pull_kernel(const FusedArgs
                         const unsigned i = b * L + j;
                         const unsigned row = a.pos_slot[i];
                         float4 v;
-                        if (row == kRemoteRow) v = *(const float4*)(mine.rows_in + (size_t)a.inverse[i] * a.dim + d);
+                        if (row == kRemoteRow) v = *(const float4*)(mine.rows_in + (size_t)((unsigned)a.inverse[i] & ~kDupBit) * a.dim + d);
                         else if (row < kRowPending) v = *(const float4*)(T.row_ptr(row) + d);
                         else v = init4(T, a.keys[i], d);
                         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
@@ -467,11 +475,15 @@ __global__ void __launch_bounds__(kThreads, 4) fused_pull_kernel(const FusedArgs
     // make every duplicate of a hot key store to the same address)
     for (unsigned u = tid; u < cnt[0]; u += nthreads) a.dedup[a.uniq_slot[u]].key = kEmptyKey;
     if (a.flags & FUSED_PREPARE_PUSH) {
+        // the push adds the gradients of a duplicated key into its aggregation row, which must start at zero; the
+        // rows of keys that occur once are written with a plain store and need nothing
         const unsigned n_uniq = cnt[0];
-        if (n_uniq != a.n) {  // without duplicates the push stores instead of accumulating
-            const size_t words = (size_t)n_uniq * a.dim / 4;
-            float4* z = (float4*)a.agg;
-            for (size_t w = tid; w < words; w += nthreads) z[w] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (n_uniq != a.n) {
+            for (unsigned u = group; u < n_uniq; u += ngroups) {
+                if (a.dedup[a.uniq_slot[u]].aux != dup_tag) continue;
+                float4* z = (float4*)(a.agg + (size_t)u * a.dim);
+                for (unsigned d = lane; d < a.dim / 4; d += lanes) z[d] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
     }
     if (blockIdx.x == 0 && threadIdx.x < 16) a.counters[(par ^ 1u) * 16 + threadIdx.x] = 0;
@@ -512,17 +524,24 @@ __global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs
     __syncthreads();
     const unsigned total_in = s_in[W];
 
-    // ---- Q0 (owner): chain the entries that name the same table row. Each source rank sends a key at most once,
-    // so a chain holds at most one entry per rank; it needs the slots resolved by the pull, not the gradients.
+    // ---- Q0 (owner): one thread per received entry resolves entry -> slot -> row once (Q3 then starts from the row
+    // index instead of walking that chain of dependent loads per lane group) and, with several ranks, chains the
+    // entries that name the same table row. Each source rank sends a key at most once, so a chain holds at most one
+    // entry per rank. All of this needs the slots resolved by the pull, not the gradients.
     PROF(8);
-    if (W > 1) {
-        for (unsigned e = tid; e < total_in; e += nthreads) {
-            int r = 0;
-            while (e >= s_in[r + 1]) ++r;
-            const unsigned id = (unsigned)r * C + (e - s_in[r]);
-            const unsigned slot = a.res_slot[id];
-            if (slot != kNoSlot) a.ent_next[id] = atomicExch(&T.slots[slot].aux, id);
+    unsigned* ent_row = a.new_list;   // free during a push: [world*C] row of every received entry
+    for (unsigned e = tid; e < total_in; e += nthreads) {
+        int r = 0;
+        while (e >= s_in[r + 1]) ++r;
+        const unsigned id = (unsigned)r * C + (e - s_in[r]);
+        const unsigned slot = a.res_slot[id];
+        unsigned row = kNoRow;
+        if (slot != kNoSlot) {
+            row = T.slots[slot].row;
+            if (row >= kRowPending) row = kNoRow;
+            if (W > 1) a.ent_next[id] = atomicExch(&T.slots[slot].aux, id);
         }
+        ent_row[id] = row;
     }
 
     // ---- Q1: segment-sum gradients of duplicate keys --------------------------------------------
@@ -543,14 +562,16 @@ __global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs
         __shared__ unsigned s_cache_u[kHotRows];
         __shared__ unsigned s_ncache;
         const unsigned hot_rows = min(a.hot_rows, (unsigned)kHotRows);
-        const bool use_cache = dups && hot_rows > 0 && a.dim <= kHotMaxDim && (hi - lo) >= 64;
+        // the block-local sums pay for their three extra passes only when a CTA's range is long enough to hold a hot
+        // key many times
+        const bool use_cache = dups && hot_rows > 0 && a.dim <= kHotMaxDim && (hi - lo) >= 1024;
         if (use_cache) {
             for (unsigned t = threadIdx.x; t < kHotSlots; t += kThreads) { s_hkey[t] = 0xFFFFFFFFu; s_hcnt[t] = 0; s_hrow[t] = -1; }
             if (threadIdx.x == 0) s_ncache = 0;
             __syncthreads();
             // 1. count the keys of this range
             for (unsigned i = lo + threadIdx.x; i < hi; i += kThreads) {
-                const unsigned u = (unsigned)a.inverse[i];
+                const unsigned u = (unsigned)a.inverse[i] & ~kDupBit;
                 unsigned h = (u * 2654435761u) & (kHotSlots - 1);
                 for (int probe = 0; probe < 8; ++probe) {
                     const unsigned prev = atomicCAS(&s_hkey[h], 0xFFFFFFFFu, u);
@@ -577,12 +598,14 @@ __global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs
         for (unsigned base = lo; base < hi; base += lgroups * kPos) {
             unsigned pos[kPos], u[kPos];
             int crow[kPos];
-            bool active[kPos];
+            bool active[kPos], dup[kPos];
 #pragma unroll
             for (int k = 0; k < kPos; ++k) {
                 pos[k] = base + (unsigned)k * lgroups + lgroup;
                 active[k] = pos[k] < hi;
-                u[k] = active[k] ? (unsigned)a.inverse[pos[k]] : 0u;
+                const unsigned iv = active[k] ? (unsigned)a.inverse[pos[k]] : 0u;
+                u[k] = iv & ~kDupBit;
+                dup[k] = (iv & kDupBit) != 0u;
                 crow[k] = -1;
             }
             if (use_cache) {
@@ -613,7 +636,7 @@ __global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs
                     if (crow[k] >= 0) {
                         float* c = s_cache + (size_t)crow[k] * a.dim + d;
                         atomicAdd(c + 0, w.x); atomicAdd(c + 1, w.y); atomicAdd(c + 2, w.z); atomicAdd(c + 3, w.w);
-                    } else if (dups) {
+                    } else if (dup[k]) {
                         atomicAdd((float4*)(a.agg + (size_t)u[k] * a.dim + d), w);
                     } else {
                         *(float4*)(a.agg + (size_t)u[k] * a.dim + d) = w;
@@ -713,21 +736,41 @@ __global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs
     }
     const unsigned gl0 = (threadIdx.x & 31u) / lanes * lanes;  // first lane of this group inside its warp
     const unsigned gmask = (lanes >= 32u ? 0xffffffffu : ((1u << lanes) - 1u)) << gl0;
-    for (unsigned e = group; e < total_in; e += ngroups) {
+    // the row index and (single rank) the gradient row of the NEXT entry are fetched while the current one is updated
+    unsigned row_nx = kNoRow, u_nx = 0;
+    auto entry_id = [&](unsigned e, int* r_out) -> unsigned {
         int r = 0;
         while (e >= s_in[r + 1]) ++r;
-        const unsigned p = e - s_in[r];
-        const unsigned id = (unsigned)r * C + p;
-        const unsigned slot = a.res_slot[id];
-        if (slot == kNoSlot) {
-            if (lane == 0) set_soft_status(a.ctl, kStOom, W_NOROW);
-            continue;
+        *r_out = r;
+        return (unsigned)r * C + (e - s_in[r]);
+    };
+    if (group < total_in) {
+        int r0;
+        const unsigned id0 = entry_id(group, &r0);
+        row_nx = ent_row[id0];
+        if (W == 1) u_nx = a.send_ret[id0];
+    }
+    for (unsigned e = group; e < total_in; e += ngroups) {
+        int r;
+        const unsigned id = entry_id(e, &r);
+        const unsigned row = row_nx, u_own = u_nx;
+        if (e + ngroups < total_in) {
+            int rn;
+            const unsigned idn = entry_id(e + ngroups, &rn);
+            row_nx = ent_row[idn];
+            if (W == 1) u_nx = a.send_ret[idn];
         }
+        unsigned slot = kNoSlot;
         unsigned ids[kMaxWorld];
         ids[0] = id;
 #pragma unroll
         for (int k = 1; k < kMaxWorld; ++k) ids[k] = kNoRow;
         if (W > 1) {
+            slot = a.res_slot[id];
+            if (slot == kNoSlot) {
+                if (lane == 0) set_soft_status(a.ctl, kStOom, W_NOROW);
+                continue;
+            }
             if (*((volatile unsigned*)&T.slots[slot].aux) != id) continue;  // not the head of its chain
             unsigned cur = id;
 #pragma unroll
@@ -751,20 +794,23 @@ __global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs
             PSB_CSWAP(3, 4);
 #undef PSB_CSWAP
         }
-        const unsigned row = T.slots[slot].row;
-        if (row >= kRowPending) {
+        if (row == kNoRow) {
             if (lane == 0) {
                 set_soft_status(a.ctl, kStOom, W_NOROW);
-                T.slots[slot].aux = kNoRow;
+                if (W > 1) T.slots[slot].aux = kNoRow;
             }
             continue;
         }
         // at most one entry of a chain is this rank's own (its gradient sits in `agg`, the others in the mailbox)
         const float* own = nullptr;
+        if (W == 1) {
+            own = a.agg + (size_t)u_own * dim;
+        } else {
 #pragma unroll
-        for (int k = 0; k < kMaxWorld; ++k)
-            if (ids[k] != kNoRow && (int)(ids[k] / C) == me)
-                own = a.agg + (size_t)a.send_ret[(size_t)me * C + (ids[k] - (unsigned)me * C)] * dim;
+            for (int k = 0; k < kMaxWorld; ++k)
+                if (ids[k] != kNoRow && (int)(ids[k] / C) == me)
+                    own = a.agg + (size_t)a.send_ret[(size_t)me * C + (ids[k] - (unsigned)me * C)] * dim;
+        }
         float* w = T.row_ptr(row);
         float* delta = w + (size_t)(T.n_opt_slots + 1) * dim;
         float* rep_dst = nullptr;
@@ -772,7 +818,8 @@ __global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs
             unsigned j = 0;
             if (lane == 0) {
                 j = atomicAdd(rep_fill, 1u);
-                if (j < (unsigned)W * C) a.peer[partner].rep_keys[j] = T.slots[slot].key;
+                if (j < (unsigned)W * C)
+                    a.peer[partner].rep_keys[j] = (r == me) ? a.send_keys[(size_t)me * C + (id - (unsigned)me * C)] : mine.mail_keys[id];
                 else set_status(a.ctl, kStError, W_REP_FULL);
             }
             j = __shfl_sync(gmask, j, gl0);

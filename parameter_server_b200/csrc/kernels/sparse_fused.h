@@ -52,7 +52,7 @@ struct FusedArgs {
     Slot* dedup;
     unsigned long long dmask;
     unsigned* pos_slot;    // [N] dedup slot of each key position
-    int* inverse;          // [N] unique id of each key position
+    int* inverse;          // [N] unique id of each key position (bit 31: kDupBit)
     unsigned* uniq_row;    // [N] local row index of a unique key, kRemoteRow when the owner is a peer
     unsigned* uniq_slot;   // [N] dedup-table slot of a unique key (to empty the table afterwards)
     long long* send_keys;  // [world][C] staged per-owner key lists
@@ -85,6 +85,7 @@ struct FusedArgs {
 };
 
 constexpr unsigned kRemoteRow = 0xFFFFFFFDu;
+constexpr unsigned kDupBit = 0x80000000u;   // in FusedArgs::inverse: the position's key occurs more than once in the batch
 
 // Host launchers (defined in sparse_fused.cu). `stream` is a cudaStream_t. Return cudaError_t as int.
 int launch_fused_pull(const FusedArgs& a, int nblocks, void* stream);
