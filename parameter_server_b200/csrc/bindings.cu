@@ -240,7 +240,8 @@ PYBIND11_MODULE(_C, m) {
         .def("pull_blocks", &SparseEngine::pull_blocks)
         .def("push_blocks", &SparseEngine::push_blocks)
         .def("set_profile", &SparseEngine::set_profile)
-        .def("phase_stamps", [](SparseEngine& e, uintptr_t s) { return e.phase_stamps(stream_of(s)); });
+        .def("phase_stamps", [](SparseEngine& e, uintptr_t s) { return e.phase_stamps(stream_of(s)); })
+        .def("cta_stamps", [](SparseEngine& e, int which, uintptr_t s) { return e.cta_stamps(which, stream_of(s)); });
 
     bind_host(m);
     bind_dense(m);

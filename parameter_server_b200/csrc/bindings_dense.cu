@@ -152,6 +152,7 @@ void bind_dense(py::module_& m) {
           py::arg("layers"), py::arg("b_mn"), py::arg("chain_done"), py::arg("err_flag") = 0, py::arg("wait_limit_s") = 2.0,
           py::arg("stream") = 0);
     m.def("gemm_chain_scratch_words", &gemm_chain_scratch_words);
+    m.def("gemm_set_trace", [](uintptr_t p) { gemm_set_trace((void*)p); });
 
     bind_model_kernels(m);
 }

@@ -111,6 +111,11 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const 
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
 __device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -182,8 +187,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 
 // Epilogue of one 32-column chunk held by one thread (one output row). `bias_s`: the chunk's 32 bias values in
 // shared memory (every lane reads the same words: a broadcast), or nullptr.
+// mpre != nullptr: the chunk's 32 mask values were loaded ahead of time (4 x uint4, this lane's row).
 __device__ __forceinline__ void epilogue_chunk(const GemmEpilogue& ep, float* f, int row, int col0, int N,
-                                               const float* bias_s, bool row_valid) {
+                                               const float* bias_s, bool row_valid, const uint4* mpre = nullptr) {
     if (bias_s != nullptr) {
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
@@ -196,6 +202,16 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpilogue& ep, float* f,
         for (int j = 0; j < 32; ++j) f[j] = fmaxf(f[j], 0.f);
     }
     const bool full = (col0 + 32 <= N);
+    if (mpre != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            const __nv_bfloat16* h = (const __nv_bfloat16*)&mpre[j / 8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t)
+                if (!(__bfloat162float(h[t]) > 0.f)) f[j + t] = 0.f;
+        }
+        return;
+    }
     if (ep.mask != nullptr && row_valid) {
         const __nv_bfloat16* mp = ep.mask + (size_t)row * ep.ldmask + col0;
         if (full && (ep.ldmask % 8 == 0)) {
@@ -352,6 +368,13 @@ struct GemmProblemSet {
     // `accumulate`), 3 = TMA store of fp32 pieces.
     CUtensorMap map_d[kMaxGroup];
     unsigned char d_mode[kMaxGroup];
+    // Tracing (off when null): CTA 0 writes %globaltimer stamps, 32 slots for each of the first 8 work units it runs:
+    // 0 producer starts the unit's loads, 1 producer issued the last load, 2 MMA warp owns an accumulator buffer,
+    // 3 first operand stage arrived, 4 accumulator complete (committed), 8 epilogue warp 0 sees the accumulator,
+    // 5 all epilogue warps do, 9 first TMEM piece in registers, 10 first piece staged, 11 first piece handed to
+    // the TMA store, 6 last piece handed to the TMA store, 7 unit index; inside the first piece:
+    // 15 bias / activation / mask applied, 16 piece written to shared memory.
+    unsigned long long* trace;
     int count;
     // Chain: problem i + 1 reads the output of problem i as its A operand (the layers of an MLP, forward or dgrad).
     // done[i * kMaxChainMTiles + m] counts the epilogue warps that have stored their part of an n-tile of row block m
@@ -507,6 +530,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                 const CUtensorMap* map_a = &ps.map_a[w.p];
                 const CUtensorMap* map_b = &ps.map_b[w.p];
                 const int tile_n = w.tile_n, tile_m = w.tile_m, kt_begin = w.kt_begin, num_kt = w.num_kt;
+                const int tslot = (unit - cta) / n_cta;
+                if (ps.trace != nullptr && cta == 0 && tslot < 8) {
+                    ps.trace[tslot * 32 + 0] = gtimer();
+                    ps.trace[tslot * 32 + 7] = (unsigned long long)unit;
+                }
                 for (int kt = 0; kt < num_kt; ++kt, ++it) {
                     const int s = it % L::kStages;
                     const uint32_t ph = (it / L::kStages) & 1u;
@@ -537,6 +565,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                             tma_load_2d(sb + j * 64 * 128, map_b, &full_bar[s], tile_n + 64 * j, k0);
                     }
                 }
+                if (ps.trace != nullptr && cta == 0 && tslot < 8) ps.trace[tslot * 32 + 1] = gtimer();
             }
         }
     } else if (warp == 1) {
@@ -556,6 +585,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + buf * (uint32_t)BN;
+                const int tslot = (unit - cta) / n_cta;
+                const bool tr = ps.trace != nullptr && cta == 0 && tslot < 8;
+                if (tr) ps.trace[tslot * 32 + 2] = gtimer();
                 for (int kt = 0; kt < num_kt; ++kt, ++it) {
                     const int s = it % L::kStages;
                     const uint32_t ph = (it / L::kStages) & 1u;
@@ -566,6 +598,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                         break;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (tr && kt == 0) ps.trace[tslot * 32 + 3] = gtimer();
                     const uint32_t sa = smem_u32(smem + s * L::kStageBytes);
                     const uint32_t sb = sa + L::kABytes;
 #pragma unroll
@@ -580,6 +613,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                     umma_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
                 }
                 umma_commit(&tfull_bar[buf]);  // accumulator complete (also on error, so the epilogue moves on)
+                if (tr) ps.trace[tslot * 32 + 4] = gtimer();
                 ++tc;
             }
         }
@@ -591,6 +625,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
         const int etid = ew * 32 + lane;     // 0 .. 255
         constexpr int kChunks = BN / 64;     // 32-column chunks per warp
         uint32_t tc = 0;
+        bool pending_publish = false;        // chain mode: a finished tile whose completion counter is not bumped yet
+        unsigned* pending_counter = nullptr;
+        bool store_in_flight = false;        // lane 0: a TMA store may still be reading this warp's staging piece
         for (int unit = cta; unit < total_units; unit += n_cta) {
             const WorkUnit w = decode_unit<BN>(ps, unit, ag);
             const int tile_n = w.tile_n, tile_m = w.tile_m, num_kt = w.num_kt;
@@ -601,14 +638,42 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
             // the bias of the tile's columns does not depend on the MMAs: stage it while they run
             float* bs = bias_smem + buf * 256;
             const bool has_bias = ep.bias != nullptr || ep.bias_bf16 != nullptr;
+            float bias_v = 0.f;
             if (has_bias && etid < BN) {
                 const int col = tile_n + etid;
-                float v = 0.f;
-                if (col < N) v = ep.bias != nullptr ? ep.bias[col] : __bfloat162float(ep.bias_bf16[col]);
-                bs[etid] = v;
+                if (col < N) bias_v = ep.bias != nullptr ? ep.bias[col] : __bfloat162float(ep.bias_bf16[col]);
             }
+            // Mask (ReLU backward) of this lane's row: the first piece is requested here, before the wait for the
+            // accumulator, and each following piece while the one before it is converted and stored, so that no
+            // piece waits for memory.
+            const int row = tile_m + q * 32 + lane;
+            const int cbase = half * (BN / 2);
+            const bool mask_fast = ep.mask != nullptr && (ep.ldmask % 8 == 0) && row < M;
+            const __nv_bfloat16* mrow = mask_fast ? ep.mask + (size_t)row * ep.ldmask + tile_n + cbase : nullptr;
+            uint4 mreg[4];
+            bool mhave = false;
+            if (mask_fast && tile_n + cbase + 32 <= N) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mreg[j] = ld_nc_v4(mrow + j * 8);
+                mhave = true;
+            }
+            if (pending_publish) {
+                // The tile before this one (chain mode): its stores must be complete before the next layer reads them.
+                // Lane 0 issued the TMA stores; rows stored by the other lanes (the non-TMA path) are ordered before
+                // its fence by the warp barrier.
+                __syncwarp();
+                if (lane == 0) {
+                    bulk_wait0();
+                    __threadfence();
+                    atomicAdd(pending_counter, 1u);
+                }
+                pending_publish = false;
+            }
+            if (has_bias && etid < BN) bs[etid] = bias_v;
             const bool waited = mbar_wait(&tfull_bar[buf], tph, limit_ns * 4);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (ps.trace != nullptr && cta == 0 && (unit - cta) / n_cta < 8 && ew == 0 && lane == 0)
+                ps.trace[(unit - cta) / n_cta * 32 + 8] = gtimer();
             // One barrier of the epilogue warps per tile: it publishes the staged bias and makes the decision to give
             // up uniform (a warp that timed out must not leave the others waiting at the next tile's barrier).
             uint32_t all_ok;
@@ -624,56 +689,80 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                 if (!waited && lane == 0) atomicCAS(err_flag, 0u, 3u);
                 break;
             }
-            const int row = tile_m + q * 32 + lane;
-            const int cbase = half * (BN / 2);
+            const int tslot = (unit - cta) / n_cta;
+            const bool tr = ps.trace != nullptr && cta == 0 && tslot < 8 && ew == 0 && lane == 0;
+            if (tr) ps.trace[tslot * 32 + 5] = gtimer();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)BN + (uint32_t)cbase;
-            uint32_t va[32], vb[32];
-            if (tile_n + cbase < N) tmem_ld32_issue(taddr, va);
+            uint32_t v[32];
+            if (tile_n + cbase < N) tmem_ld32_issue(taddr, v);
             const int d_mode = ps.d_mode[w.p];
             const CUtensorMap* map_d = &ps.map_d[w.p];
             uint8_t* my_stage = stage_out + ew * 2048 + lane * 64;   // this lane's row of the warp's staging piece
             const int row0 = tile_m + q * 32;
-#pragma unroll
+            // not unrolled: the body is long, and four copies of it per output mode cost more in instruction fetch
+            // than the loop saves
+#pragma unroll 1
             for (int c = 0; c < kChunks; ++c) {
-                uint32_t* cur = (c & 1) ? vb : va;
-                uint32_t* nxt = (c & 1) ? va : vb;
                 const int col0 = tile_n + cbase + c * 32;
                 if (col0 >= N) break;  // warp-uniform
-                tmem_wait_ld(cur);
-                if (c + 1 < kChunks && col0 + 32 < N) tmem_ld32_issue(taddr + (uint32_t)(c + 1) * 32u, nxt);
+                const bool more = c + 1 < kChunks && col0 + 32 < N;
+                tmem_wait_ld(v);
+                if (tr && c == 0) ps.trace[tslot * 32 + 9] = gtimer();
                 float f[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(cur[j]);
+                for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
                 if (d_mode == 0) {
                     if (row < M) {
                         epilogue_chunk(ep, f, row, col0, N, has_bias ? bs + cbase + c * 32 : nullptr, true);
                         store_chunk_rows(ep, f, row, col0, N);
                     }
+                    if (more) tmem_ld32_issue(taddr + (uint32_t)(c + 1) * 32u, v);
                     continue;
                 }
-                epilogue_chunk(ep, f, row, col0, N, has_bias ? bs + cbase + c * 32 : nullptr, row < M);
-                if (d_mode == 1) {
-                    // bf16: the warp's [32 rows][32 cols] piece, one row (64 bytes) per lane
+                epilogue_chunk(ep, f, row, col0, N, has_bias ? bs + cbase + c * 32 : nullptr, row < M, mhave ? mreg : nullptr);
+                mhave = false;
+                if (mask_fast && c + 1 < kChunks && col0 + 64 <= N) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        uint4 raw;
-                        __nv_bfloat162* h = (__nv_bfloat162*)&raw;
-                        h[0] = __floats2bfloat162_rn(f[j], f[j + 1]);
-                        h[1] = __floats2bfloat162_rn(f[j + 2], f[j + 3]);
-                        h[2] = __floats2bfloat162_rn(f[j + 4], f[j + 5]);
-                        h[3] = __floats2bfloat162_rn(f[j + 6], f[j + 7]);
-                        *(uint4*)(my_stage + j * 2) = raw;
+                    for (int j = 0; j < 4; ++j) mreg[j] = ld_nc_v4(mrow + (c + 1) * 32 + j * 8);
+                    mhave = true;
+                }
+                if (tr && c == 0) ps.trace[tslot * 32 + 15] = gtimer();
+                if (d_mode == 1) {
+                    // bf16: the warp's [32 rows][32 cols] piece, one row (64 bytes) per lane. Once the values are
+                    // packed their registers are free: the next piece leaves TMEM while this one is stored.
+                    uint4 raw[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        __nv_bfloat162* h = (__nv_bfloat162*)&raw[j];
+                        h[0] = __floats2bfloat162_rn(f[8 * j], f[8 * j + 1]);
+                        h[1] = __floats2bfloat162_rn(f[8 * j + 2], f[8 * j + 3]);
+                        h[2] = __floats2bfloat162_rn(f[8 * j + 4], f[8 * j + 5]);
+                        h[3] = __floats2bfloat162_rn(f[8 * j + 6], f[8 * j + 7]);
                     }
+                    if (more) tmem_ld32_issue(taddr + (uint32_t)(c + 1) * 32u, v);
+                    // the staging piece is free once the store before this one has read it
+                    if (store_in_flight) {
+                        if (lane == 0) bulk_wait_read0();
+                        __syncwarp();
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) *(uint4*)(my_stage + j * 16) = raw[j];
+                    if (tr && c == 0) ps.trace[tslot * 32 + 16] = gtimer();
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) {
+                        if (tr && c == 0) ps.trace[tslot * 32 + 10] = gtimer();
                         tma_store_2d(map_d, stage_out + ew * 2048, col0, row0);
                         bulk_commit();
-                        bulk_wait_read0();   // the piece is reused by the next chunk
+                        if (tr && c == 0) ps.trace[tslot * 32 + 11] = gtimer();
                     }
-                    __syncwarp();
+                    store_in_flight = true;
                 } else {
                     // fp32: two [32 rows][16 cols] pieces per chunk
+                    if (store_in_flight) {
+                        if (lane == 0) bulk_wait_read0();
+                        __syncwarp();
+                    }
 #pragma unroll
                     for (int hcol = 0; hcol < 32; hcol += 16) {
                         if (col0 + hcol >= N) break;   // warp-uniform
@@ -686,26 +775,38 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                             if (d_mode == 2) tma_reduce_add_2d(map_d, stage_out + ew * 2048, col0 + hcol, row0);
                             else tma_store_2d(map_d, stage_out + ew * 2048, col0 + hcol, row0);
                             bulk_commit();
-                            bulk_wait_read0();
+                            if (hcol == 0) bulk_wait_read0();   // the second half follows at once
                         }
-                        __syncwarp();
+                        if (hcol == 0) __syncwarp();
                     }
+                    store_in_flight = true;
+                    if (more) tmem_ld32_issue(taddr + (uint32_t)(c + 1) * 32u, v);
                 }
             }
+            if (tr) ps.trace[tslot * 32 + 6] = gtimer();
             // this warp is done reading the buffer: hand it back to the MMA warp
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            if (ps.chain) {
-                // publish this warp's part of the tile to the next layer: stores complete -> fence -> counter
-                if (lane == 0) bulk_wait0();
-                __threadfence();
-                asm volatile("fence.proxy.async.global;" ::: "memory");
-            }
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&tempty_bar[buf]);
-                if (ps.chain) atomicAdd(ps.done + (size_t)w.p * kMaxChainMTiles + tile_m / BM, 1u);
+            if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+            if (ps.chain) {
+                // This warp's part of the tile is published to the next layer (stores complete -> fence -> counter)
+                // right before the warp next waits for an accumulator, or after the loop: the latency of the
+                // completion overlaps the set-up of the next tile, and nothing this CTA waits for can depend on a
+                // tile it has not published.
+                pending_publish = true;
+                pending_counter = ps.done + (size_t)w.p * kMaxChainMTiles + tile_m / BM;
             }
             ++tc;
+        }
+        __syncwarp();
+        if (lane == 0) {
+            if (pending_publish) {
+                bulk_wait0();
+                __threadfence();
+                atomicAdd(pending_counter, 1u);
+            } else if (store_in_flight) {
+                bulk_wait_read0();   // the staging piece must outlive the store that reads it
+            }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -841,6 +942,8 @@ cudaError_t dispatch(int BN, bool a_mn, bool b_mn, const GemmProblemSet& ps, uns
 }
 
 // Fills slot i of a problem set; returns 0, -2 (alignment) or -3 (tensor map).
+unsigned long long* g_gemm_trace = nullptr;
+
 int add_problem(GemmProblemSet* ps, int i, int BN, const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep, int M,
                 int N, int K) {
     if ((A.ld % 8) || (B.ld % 8) || ((uintptr_t)A.ptr % 16) || ((uintptr_t)B.ptr % 16)) return -2;  // TMA: 16-byte rule
@@ -894,11 +997,14 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep
     ps.count = 1;
     ps.chain = 0;
     ps.done = nullptr;
+    ps.trace = g_gemm_trace;
     int rc = add_problem(&ps, 0, BN, A, B, ep, M, N, K);
     if (rc != 0) return rc;
     const unsigned long long lim = (unsigned long long)(wait_limit_s * 1e9);
     return (int)dispatch(BN, A.mn_major, B.mn_major, ps, err_flag, lim, (cudaStream_t)stream, ag);
 }
+
+void gemm_set_trace(void* device_buffer_of_256_u64) { g_gemm_trace = (unsigned long long*)device_buffer_of_256_u64; }
 
 int gemm_chain_scratch_words() { return kMaxGroup * kMaxChainMTiles; }
 
@@ -916,6 +1022,7 @@ int gemm_bf16_grouped(const GemmOperand* A, const GemmOperand* B, const GemmEpil
     ps.count = count;
     ps.chain = chain_done != nullptr ? 1 : 0;
     ps.done = chain_done;
+    ps.trace = g_gemm_trace;
     if (ps.chain) {
         // layer i + 1 consumes the bf16 output of layer i: same rows, K of the consumer = N of the producer
         for (int i = 0; i < count; ++i) {

@@ -63,5 +63,8 @@ int gemm_bf16_grouped(const GemmOperand* A, const GemmOperand* B, const GemmEpil
                       const int* K, int count, unsigned* err_flag, double wait_limit_s, void* stream,
                       unsigned* chain_done = nullptr);
 int gemm_chain_scratch_words();
+// Tracing of the following launches (nullptr = off): CTA 0 writes %globaltimer stamps for the first 8 work units it runs
+// into this device buffer of 256 x u64, 32 slots per unit (producer, MMA and epilogue milestones; unit index in slot 7). The tool behind the per-tile timelines in profiles/.
+void gemm_set_trace(void* device_buffer_of_256_u64);
 
 }  // namespace psb

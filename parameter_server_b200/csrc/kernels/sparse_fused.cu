@@ -93,6 +93,13 @@ struct RowSrc {
 
 // Phase timestamps (the kernel-side counterpart of the reference's VTIMER scopes): CTA 0 records
 // %globaltimer when it enters each phase.
+// Per-CTA stamps (same switch): when each CTA started and when it reached a grid barrier; the spread tells a phase
+// that is bound by throughput (all CTAs arrive late) from one that waits for stragglers.
+#define PROF_CTA(k)                                                                                              \
+    do {                                                                                                         \
+        if (a.prof != nullptr && threadIdx.x == 0 && blockIdx.x < kProfMaxCtas)                                  \
+            a.prof[16 + (k) * kProfMaxCtas + blockIdx.x] = global_timer_ns();                                    \
+    } while (0)
 #define PROF(slot)                                                                 \
     do {                                                                           \
         if (a.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 0) a.prof[slot] = global_timer_ns(); \
@@ -126,11 +133,21 @@ __global__ void __launch_bounds__(kThreads, 4) fused_pull_kernel(const FusedArgs
     // batch otherwise sends many lanes to one slot); counters are bumped once per warp and owner (ballot /
     // match), not once per key: same-address atomics serialise in L2 and would otherwise bound the phase.
     PROF(0);
+    PROF_CTA(0);
     const unsigned wlane = threadIdx.x & 31u;
     const unsigned long long probe_limit = a.dmask + 1ull;
     const unsigned dup_tag = (epoch << 1) | 1u;
-    for (unsigned i0 = (tid & ~31u); i0 < a.n; i0 += nthreads) {
-        const unsigned i = i0 + wlane;
+    // Unique ids and per-owner mailbox positions are handed out per CTA: the warps add their counts to shared
+    // counters, one thread per counter fetches the CTA's base from global memory, and every winner adds its rank
+    // inside the CTA. One global atomic per CTA and counter instead of one per warp: all of them hit the same two
+    // or three addresses, and that many same-address atomics serialised in L2 left the last warps waiting.
+    __shared__ unsigned s_cnt[kMaxWorld + 1];    // [0] uniques, [1 + o] keys for owner o (this iteration)
+    __shared__ unsigned s_base[kMaxWorld + 1];
+    if (threadIdx.x <= (unsigned)kMaxWorld) s_cnt[threadIdx.x] = 0;
+    __syncthreads();
+    const unsigned n_ceil = (a.n + kThreads - 1) / kThreads * kThreads;
+    for (unsigned i0 = blockIdx.x * kThreads; i0 < n_ceil; i0 += nthreads) {   // trip count uniform in the CTA
+        const unsigned i = i0 + threadIdx.x;
         bool active = i < a.n;
         long long key = kEmptyKey;
         if (active) {
@@ -161,8 +178,12 @@ __global__ void __launch_bounds__(kThreads, 4) fused_pull_kernel(const FusedArgs
             }
             // A key met more than once (by another warp before, or by several lanes of this warp) is tagged with
             // this call's epoch: the push then knows which gradient rows need summing and which are plain copies.
-            // Nobody ever clears the tag: a value left by an earlier call differs from the current one.
-            if (probes < probe_limit && (!won || __popc(same) > 1)) a.dedup[hh].aux = dup_tag;
+            // Nobody ever clears the tag: a value left by an earlier call differs from the current one. Read before
+            // write: the head keys of a skewed batch are met by thousands of warps, and that many stores to one
+            // address serialise in L2 where the reads (same sector as the key just probed) do not.
+            if (probes < probe_limit && (!won || __popc(same) > 1) &&
+                *((volatile unsigned*)&a.dedup[hh].aux) != dup_tag)
+                a.dedup[hh].aux = dup_tag;
             // the table holds >= 2n slots and is emptied by every call; a full table means an earlier call was
             // cut short or two calls overlap on one engine
             if (probes == probe_limit) set_status(a.ctl, kStError, W_DEDUP_FULL);
@@ -171,22 +192,28 @@ __global__ void __launch_bounds__(kThreads, 4) fused_pull_kernel(const FusedArgs
         h = __shfl_sync(0xffffffffu, h, klead);
         if (active) a.pos_slot[i] = h;
         const unsigned wmask = __ballot_sync(0xffffffffu, won);
-        if (wmask == 0) continue;
         const int owner = won ? a.shard_owner[sparse_shard_of(key, a.n_shards)] : -1;
-        // unique ids: one atomic per warp
-        unsigned ubase = 0;
-        const int uleader = __ffs(wmask) - 1;
-        if ((int)wlane == uleader) ubase = atomicAdd(&cnt[0], (unsigned)__popc(wmask));
-        ubase = __shfl_sync(0xffffffffu, ubase, uleader);
-        const unsigned u = ubase + __popc(wmask & ((1u << wlane) - 1u));
-        // per-owner positions: one atomic per (warp, owner)
+        // rank of this winner among the CTA's winners (all, and of the same owner)
+        unsigned uoff = 0, poff = 0;
         const unsigned peers = __match_any_sync(0xffffffffu, owner);
-        const int pleader = __ffs(peers) - 1;
-        unsigned pbase = 0;
-        if (won && (int)wlane == pleader) pbase = atomicAdd(&send_cnt[owner], (unsigned)__popc(peers));
-        pbase = __shfl_sync(0xffffffffu, pbase, pleader);
+        if (wmask) {
+            const int uleader = __ffs(wmask) - 1;
+            if ((int)wlane == uleader) uoff = atomicAdd(&s_cnt[0], (unsigned)__popc(wmask));
+            uoff = __shfl_sync(0xffffffffu, uoff, uleader) + __popc(wmask & ((1u << wlane) - 1u));
+            const int pleader = __ffs(peers) - 1;
+            if (won && (int)wlane == pleader) poff = atomicAdd(&s_cnt[1 + owner], (unsigned)__popc(peers));
+            poff = __shfl_sync(0xffffffffu, poff, pleader) + __popc(peers & ((1u << wlane) - 1u));
+        }
+        __syncthreads();
+        if (threadIdx.x <= (unsigned)W) {
+            const unsigned c = s_cnt[threadIdx.x];
+            s_base[threadIdx.x] = c ? atomicAdd(threadIdx.x == 0 ? &cnt[0] : &send_cnt[threadIdx.x - 1], c) : 0u;
+            s_cnt[threadIdx.x] = 0;
+        }
+        __syncthreads();
         if (won) {
-            const unsigned p = pbase + __popc(peers & ((1u << wlane) - 1u));
+            const unsigned u = s_base[0] + uoff;
+            const unsigned p = s_base[1 + owner] + poff;
             if (p < C) {
                 a.send_keys[(size_t)owner * C + p] = key;
                 a.send_ret[(size_t)owner * C + p] = u;
@@ -198,6 +225,7 @@ __global__ void __launch_bounds__(kThreads, 4) fused_pull_kernel(const FusedArgs
             a.uniq_row[u] = (owner == me) ? kNoSlot : kRemoteRow;
         }
     }
+    PROF_CTA(1);
     if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P1)) return;
 
     // ---- P2: ship staged key lists to the owners ------------------------------------------------
@@ -299,6 +327,7 @@ __global__ void __launch_bounds__(kThreads, 4) fused_pull_kernel(const FusedArgs
         }
     }
     if (W == 1 && blockIdx.x == 0 && threadIdx.x == 0) in_cnt[0] = min(send_cnt[0], C);
+    PROF_CTA(2);
     if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_P3A)) return;
 
     // ---- P3b: initialise the rows attached by this call -----------------------------------------
@@ -654,6 +683,7 @@ __global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs
             }
         }
     }
+    PROF_CTA(3);
     if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_Q1)) return;
 
     if (W > 1) {

@@ -85,6 +85,7 @@ struct FusedArgs {
 };
 
 constexpr unsigned kRemoteRow = 0xFFFFFFFDu;
+constexpr unsigned kProfMaxCtas = 2048;   // per-CTA profile stamps: prof[16 + k * kProfMaxCtas + cta], k < 4
 constexpr unsigned kDupBit = 0x80000000u;   // in FusedArgs::inverse: the position's key occurs more than once in the batch
 
 // Host launchers (defined in sparse_fused.cu). `stream` is a cudaStream_t. Return cudaError_t as int.

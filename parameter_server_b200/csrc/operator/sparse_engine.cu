@@ -94,7 +94,7 @@ SparseEngine::SparseEngine(GpuTable* table, const SparseEngineConfig& cfg) : tab
     const size_t o_rslot = carve(cfg_.replicate ? (size_t)W * C_ * 4 : 0), o_rnew = carve(cfg_.replicate ? (size_t)W * C_ * 4 : 0);
     const size_t o_cnt = carve(2 * 16 * 4), o_in = carve(2 * kMaxWorld * 4);
     const size_t o_ctl1 = carve(sizeof(KernelCtl)), o_ctl2 = carve(sizeof(KernelCtl));
-    const size_t o_prof = carve(16 * 8);
+    const size_t o_prof = carve((16 + 4 * kProfMaxCtas) * 8);
     const size_t o_owner = carve((size_t)std::max(cfg_.n_shards, 1) * 4);
     scratch_bytes_ = s;
     cudaError_t e = cudaMalloc(&scratch_, s);
@@ -393,6 +393,15 @@ std::vector<uint64_t> SparseEngine::phase_stamps(void* stream) {
     cudaStreamSynchronize((cudaStream_t)stream);
     std::vector<uint64_t> v(16, 0);
     cudaMemcpy(v.data(), prof_, 16 * 8, cudaMemcpyDeviceToHost);
+    return v;
+}
+
+std::vector<uint64_t> SparseEngine::cta_stamps(int which, void* stream) {
+    cudaSetDevice(table_->device());
+    cudaStreamSynchronize((cudaStream_t)stream);
+    std::vector<uint64_t> v(kProfMaxCtas, 0);
+    if (which < 0 || which > 3) return v;
+    cudaMemcpy(v.data(), prof_ + 16 + (size_t)which * kProfMaxCtas, kProfMaxCtas * 8, cudaMemcpyDeviceToHost);
     return v;
 }
 

@@ -79,6 +79,9 @@ public:
     void set_profile(bool on) { profile_ = on; }
     // Raw %globaltimer stamps of the last pull (slots 0..6) and push (slots 8..12), in ns.
     std::vector<uint64_t> phase_stamps(void* stream);
+    // Per-CTA %globaltimer stamps of the last profiled calls: 0 = CTA entered the pull, 1 = reached the barrier after
+    // the dedup phase, 2 = after the resolve phase, 3 = (push) after the segment sum. Zero where a CTA did not run.
+    std::vector<uint64_t> cta_stamps(int which, void* stream);
 
 private:
     void fill_common(FusedArgs& a) const;

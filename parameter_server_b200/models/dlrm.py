@@ -240,6 +240,7 @@ class DLRM:
         Sections that wait for other ranks include the skew between the ranks."""
         import statistics
         acc: dict = {}
+        cta_spread: dict = {}
         prof = getattr(self.sparse, "engine", None)
         if prof is not None and hasattr(prof, "set_profile"):
             prof.set_profile(True)
@@ -262,6 +263,17 @@ class DLRM:
                     spans = [(8, 10, "push.Q1_segsum"), (10, 11, "push.Q3ab_elect_fold"), (11, 12, "push.Q3c_update")]
                 for lo, hi, nm in spans:
                     acc.setdefault(nm, []).append((st[hi] - st[lo]) / 1e3)
+                if hasattr(prof, "cta_stamps"):
+                    # when each CTA reached the barrier that ends a phase, relative to the phase's start in CTA 0
+                    t_in = [x for x in prof.cta_stamps(0, 0) if x]
+                    for which, ref, nm in ((1, st[0], "pull.P1_cta_arrival"), (2, st[2], "pull.P3a_cta_arrival"),
+                                           (3, st[8], "push.Q1_cta_arrival")):
+                        v = sorted((x - ref) / 1e3 for x in prof.cta_stamps(which, 0) if x)
+                        if v:
+                            cta_spread[nm] = [round(v[0], 1), round(v[len(v) // 2], 1), round(v[-1], 1)]
+                    if t_in:
+                        cta_spread["pull.cta_start_spread"] = [0.0, round((sorted(t_in)[len(t_in) // 2] - min(t_in)) / 1e3, 1),
+                                                               round((max(t_in) - min(t_in)) / 1e3, 1)]
         self.trace = None
         if prof is not None and hasattr(prof, "set_profile"):
             prof.set_profile(False)
@@ -275,6 +287,8 @@ class DLRM:
             out["unique_keys_last_pull"] = uniq
             out["remote_row_bytes"] = int(uniq * (w - 1) / w * self.cfg.emb_dim * 4)
             out["nvlink_floor_us_per_direction"] = round(out["remote_row_bytes"] / 770e9 * 1e6, 1)
+        if cta_spread:
+            out["cta_us_min_median_max"] = cta_spread
         return out
 
     def forward_backward(self) -> torch.Tensor:

@@ -303,6 +303,24 @@ def cmd_chain(a):
     t = timed(fn, a.iters, flush=not a.no_flush)
     G.check_gemm_errors()
     print(f"chain {a.which} M={M}: {t*1e6:8.1f} us (eager launch, CUDA events)  {fl/t/1e12:7.1f} TFLOP/s")
+    if a.trace:
+        # per-unit timeline of CTA 0 (ns since its first stamp): where a tile's time goes
+        from .._lib import C
+        buf = torch.zeros(256, dtype=torch.int64, device="cuda")
+        C.gemm_set_trace(buf.data_ptr())
+        if not a.no_flush:
+            flush_l2()
+        fn()
+        torch.cuda.synchronize()
+        C.gemm_set_trace(0)
+        v = buf.view(8, 32).tolist()
+        t0 = min(r[0] for r in v if r[0])
+        names = ["load0", "loadN", "mma0", "data0", "commit", "epi_w0", "epi_all", "tmem0", "math0", "smem0", "stage0", "issue0", "epi_end"]
+        order = [0, 1, 2, 3, 4, 8, 5, 9, 15, 16, 10, 11, 6]
+        print(" unit " + " ".join(f"{n:>8s}" for n in names) + "   (ns after CTA 0's first load)")
+        for r in v:
+            if r[0]:
+                print(f"{r[7]:5d} " + " ".join(f"{(r[k] - t0) if r[k] else -1:8d}" for k in order))
 
 
 def main():
@@ -324,6 +342,7 @@ def main():
     c = sub.add_parser("chain")
     c.add_argument("--which", default="top_fwd", choices=["top_fwd", "top_dgrad", "wgrad"])
     c.add_argument("--batch", type=int, default=8192)
+    c.add_argument("--trace", action="store_true", help="print the per-tile timeline of CTA 0")
     for p in (g, s, i, d, m, c):
         p.add_argument("--iters", type=int, default=10)
         p.add_argument("--no-flush", action="store_true")
