@@ -43,7 +43,8 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kEpilogueWarps = 8;
-constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+constexpr int kPublisherWarp = 2 + kEpilogueWarps;   // chain mode: bumps the completion counters for the epilogue warps
+constexpr int kThreads = 64 + 32 * kEpilogueWarps + 32;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -143,6 +144,59 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
 }
+// ---- CTA pairs (cta_group::2) -------------------------------------------------------------------------
+// Two CTAs of a cluster work on one 256-row tile: each holds its own 128 rows of A, HALF of the B tile and the
+// accumulator of its 128 rows in its own TMEM; one thread of the leader (cluster rank 0) issues the MMAs for both.
+// Each SM then reads and fills half as many B bytes per flop: the 1-CTA 128 x 256 tile needs about 96 B/clk of
+// operand reads plus as much again for the TMA fill, more than one SM's shared memory delivers.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of `local` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_cluster(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Loads of a pair: the data lands in this CTA, the bytes are counted on the LEADER's barrier (no multicast: every
+// CTA fetches its own tiles).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(bar_cluster), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on the barrier at this offset in BOTH CTAs of the pair once the MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+                 : "memory");
+}
+
 // Issue the load of 32 accumulator columns (one row per lane); the registers are valid after tmem_wait_ld.
 __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* v) {
     asm volatile(
@@ -168,12 +222,12 @@ __device__ __forceinline__ void tmem_wait_ld(uint32_t* v) {
                  : "memory");
 }
 
-template <int BN>
+template <int BN, bool PAIR = false>
 struct SmemLayout {
     static constexpr int kABytes = BM * BK * 2;   // 16 KB
-    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kBBytes = (PAIR ? BN / 2 : BN) * BK * 2;   // a CTA of a pair holds half of the B tile
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = (BN == 256) ? 4 : 6;
+    static constexpr int kStages = PAIR ? ((BN == 256) ? 6 : 8) : ((BN == 256) ? 4 : 6);
     static constexpr int kTileBytes = kStages * kStageBytes;
     static constexpr int kBarBytes = 256;
     static constexpr int kBiasBytes = 2 * 256 * 4;  // the bias of a tile's columns, double-buffered with the accumulator
@@ -184,6 +238,30 @@ struct SmemLayout {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+constexpr uint32_t kPubExit = 0xFFFFFFFFu;
+__device__ __forceinline__ uint32_t ld_acquire_cta_smem(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_cta_smem(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+// One lane of an epilogue warp hands a request to the publisher warp (waits, bounded, for the slot to be free).
+__device__ __forceinline__ void post_publish(uint32_t* box, uint32_t req, unsigned long long limit_ns, unsigned* err_flag) {
+    if (ld_acquire_cta_smem(box) != 0u) {
+        const unsigned long long t0 = gtimer();
+        unsigned spins = 0;
+        while (ld_acquire_cta_smem(box) != 0u) {
+            if ((++spins & 63u) == 0 && gtimer() - t0 > limit_ns) {
+                atomicCAS(err_flag, 0u, 8u);
+                return;
+            }
+        }
+    }
+    st_release_cta_smem(box, req);
+}
+
 
 // Epilogue of one 32-column chunk held by one thread (one output row). `bias_s`: the chunk's 32 bias values in
 // shared memory (every lane reads the same words: a broadcast), or nullptr.
@@ -363,16 +441,16 @@ struct GemmProblemSet {
     // of a stage (2 for A, BN / 64 for B) instead of one load per block: the single producer thread then issues two
     // loads per k-step for every operand layout.
     unsigned char a_blocked[kMaxGroup], b_blocked[kMaxGroup];
-    // How the epilogue writes problem i: 0 = one thread per row (any alignment, both outputs), 1 = TMA store of bf16
-    // [32 rows][32 cols] pieces, 2 = TMA reduce-add of fp32 [32 rows][16 cols] pieces (split-K partial sums,
-    // `accumulate`), 3 = TMA store of fp32 pieces.
+    // How the epilogue writes problem i: 0 = one thread per row (any alignment, both outputs), 1 = bf16 through a
+    // shared-memory piece and 16-byte stores that cover whole row segments, 2 = TMA reduce-add of fp32
+    // [32 rows][16 cols] pieces (split-K partial sums, `accumulate`), 3 = TMA store of fp32 pieces (map_d: 2 and 3).
     CUtensorMap map_d[kMaxGroup];
     unsigned char d_mode[kMaxGroup];
     // Tracing (off when null): CTA 0 writes %globaltimer stamps, 32 slots for each of the first 8 work units it runs:
     // 0 producer starts the unit's loads, 1 producer issued the last load, 2 MMA warp owns an accumulator buffer,
     // 3 first operand stage arrived, 4 accumulator complete (committed), 8 epilogue warp 0 sees the accumulator,
     // 5 all epilogue warps do, 9 first TMEM piece in registers, 10 first piece staged, 11 first piece handed to
-    // the TMA store, 6 last piece handed to the TMA store, 7 unit index; inside the first piece:
+    // the TMA store, 6 last piece handed to the TMA store, 7 unit index, 20 / 21 the SM's cycle counter at 3 and 4 (their ratio to the timer gives the SM clock); inside the first piece:
     // 15 bias / activation / mask applied, 16 piece written to shared memory.
     unsigned long long* trace;
     int count;
@@ -390,14 +468,17 @@ struct WorkUnit {
     int kt_begin, num_kt;     // k-tile range of this split
 };
 
-template <int BN>
-__device__ __forceinline__ WorkUnit decode_unit(const GemmProblemSet& ps, int u, const GemmGather& ag) {
+// PAIR: a unit covers 256 rows; the CTA of cluster rank `cr` works on rows [tile_m, tile_m + 128) = the unit's
+// rows + 128 * cr (which may lie past M: the loads then read zeros and the stores are clipped).
+template <int BN, bool PAIR>
+__device__ __forceinline__ WorkUnit decode_unit(const GemmProblemSet& ps, int u, const GemmGather& ag, int cr) {
+    constexpr int BMU = PAIR ? 2 * BM : BM;
     WorkUnit w;
     int p = 0;
     while (p + 1 < ps.count && u >= ps.unit_end[p]) ++p;
     w.p = p;
     const int local = u - (p > 0 ? ps.unit_end[p - 1] : 0);
-    const int m_tiles = (ps.M[p] + BM - 1) / BM;
+    const int m_tiles = (ps.M[p] + BMU - 1) / BMU;
     const int n_tiles = (ps.N[p] + BN - 1) / BN;
     const int splits = ps.ep[p].split_k > 1 ? ps.ep[p].split_k : 1;
     const int total_kt = (ps.K[p] + BK - 1) / BK;
@@ -415,7 +496,7 @@ __device__ __forceinline__ WorkUnit decode_unit(const GemmProblemSet& ps, int u,
     if (ag.enabled) nt = (nt + ag.rank * (ag.rows_per_rank / BN)) % n_tiles;  // local rows first, then ring order
     w.nt = nt;
     w.tile_n = nt * BN;
-    w.tile_m = mt * BM;
+    w.tile_m = mt * BMU + cr * BM;
     w.kt_begin = z * kt_per;
     w.num_kt = max(0, min(total_kt - w.kt_begin, kt_per));
     return w;
@@ -426,11 +507,13 @@ __device__ __forceinline__ WorkUnit decode_unit(const GemmProblemSet& ps, int u,
 // tile in L2. The accumulator is double-buffered in TMEM (2 x BN columns): while the epilogue warps
 // drain buffer b, the MMA warp already fills buffer b^1 with the next tile.
 // AMN / BMN: operand is MN-major. The box of an MN-major operand is [64 k-rows][64 mn-elements].
-template <int BN, bool AMN, bool BMN>
+// PAIR: launched as clusters of two CTAs that share every work unit (see the CTA-pair helpers above); the gather
+// role exists only without it.
+template <int BN, bool AMN, bool BMN, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* err_flag, unsigned long long limit_ns,
                          const GemmGather ag) {
-    using L = SmemLayout<BN>;
+    using L = SmemLayout<BN, PAIR>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full_bar = (uint64_t*)(smem + L::kTileBytes);
@@ -438,20 +521,31 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
     uint64_t* tfull_bar = empty_bar + L::kStages;   // [2] accumulator buffer complete
     uint64_t* tempty_bar = tfull_bar + 2;           // [2] accumulator buffer drained
     uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
+    // Chain mode: one mailbox per epilogue warp. The warp posts (index of a completion counter) + 1 once the stores
+    // of a tile are complete; a lane of the publisher warp fences and bumps the counter, so that no epilogue warp
+    // ever waits for a device-scope fence. 0 = empty, kPubExit = no more requests.
+    uint32_t* pub_req = tmem_slot + 2;   // [kEpilogueWarps]
     float* bias_smem = (float*)(smem + L::kTileBytes + L::kBarBytes);   // [2][256]
     uint8_t* stage_out = smem + L::kTileBytes + L::kBarBytes + L::kBiasBytes;   // [kEpilogueWarps][2048]
 
     // ---- all-gather role: the first ag.gather_ctas CTAs move remote row blocks of B into the local copy ----
-    const int n_gather = ag.enabled ? ag.gather_ctas : 0;
-    if ((int)blockIdx.x < n_gather) {
-        gather_rows<BN>(ag, ps.K[0], smem, full_bar, err_flag, limit_ns, ps.N[0]);
-        return;
+    const int n_gather = (!PAIR && ag.enabled) ? ag.gather_ctas : 0;
+    if constexpr (!PAIR) {
+        if ((int)blockIdx.x < n_gather) {
+            gather_rows<BN>(ag, ps.K[0], smem, full_bar, err_flag, limit_ns, ps.N[0]);
+            return;
+        }
     }
-    const int cta = (int)blockIdx.x - n_gather, n_cta = (int)gridDim.x - n_gather;
+    // the walker index: a CTA, or a pair of CTAs
+    const int cr = PAIR ? (int)cluster_ctarank() : 0;
+    const int cta = PAIR ? (int)blockIdx.x / 2 : (int)blockIdx.x - n_gather;
+    const int n_cta = PAIR ? (int)gridDim.x / 2 : (int)gridDim.x - n_gather;
+    const bool leader = cr == 0;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int total_units = ps.unit_end[ps.count - 1];
 
+    if (threadIdx.x < kEpilogueWarps) pub_req[threadIdx.x] = 0;
     if (threadIdx.x == 0) {
         for (int s = 0; s < L::kStages; ++s) {
             mbar_init(&full_bar[s], 1);
@@ -459,18 +553,28 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tfull_bar[b], 1);
-            mbar_init(&tempty_bar[b], kEpilogueWarps);  // one arrival per epilogue warp
+            // one arrival per epilogue warp (of both CTAs of a pair: the leader's barrier collects them)
+            mbar_init(&tempty_bar[b], PAIR ? 2 * kEpilogueWarps : kEpilogueWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"((uint32_t)(2 * BN))
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {
+            // executed by one warp of each CTA of the pair: the columns are allocated in both tensor memories
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                         "r"((uint32_t)(2 * BN))
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                         "r"((uint32_t)(2 * BN))
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();   // the peer's barriers must exist before anything is signalled on them
+    else __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *((volatile uint32_t*)tmem_slot);
     // Programmatic dependent launch: everything above (barriers, TMEM) touched no global memory, so it may
@@ -485,12 +589,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
             for (int p = 0; p < ps.count; ++p) {
                 asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&ps.map_a[p]) : "memory");
                 asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&ps.map_b[p]) : "memory");
-                if (ps.d_mode[p]) asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&ps.map_d[p]) : "memory");
+                if (ps.d_mode[p] >= 2) asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&ps.map_d[p]) : "memory");
             }
             uint32_t it = 0;  // k-tile counter across all tiles of this CTA (drives the stage ring)
             bool ok = true;
             for (int unit = cta; unit < total_units && ok; unit += n_cta) {
-                const WorkUnit w = decode_unit<BN>(ps, unit, ag);
+                const WorkUnit w = decode_unit<BN, PAIR>(ps, unit, ag, cr);
                 if (ag.enabled) {
                     // a remote n-tile must have landed before it is loaded
                     const int tpr = ag.rows_per_rank / BN;
@@ -509,7 +613,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                         asm volatile("fence.proxy.async.global;" ::: "memory");
                     }
                 }
-                if (ps.chain && w.p > 0) {
+                if (ps.chain && w.p > 0 && w.tile_m < ps.M[w.p]) {
                     // the A operand is the previous layer's output: all n-tiles of this row block must be stored
                     const int prev_n_tiles = (ps.N[w.p - 1] + BN - 1) / BN;
                     const unsigned target = (unsigned)kEpilogueWarps * (unsigned)prev_n_tiles;  // every epilogue warp of every tile
@@ -531,7 +635,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                 const CUtensorMap* map_b = &ps.map_b[w.p];
                 const int tile_n = w.tile_n, tile_m = w.tile_m, kt_begin = w.kt_begin, num_kt = w.num_kt;
                 const int tslot = (unit - cta) / n_cta;
-                if (ps.trace != nullptr && cta == 0 && tslot < 8) {
+                if (ps.trace != nullptr && cta == 0 && leader && tslot < 8) {
                     ps.trace[tslot * 32 + 0] = gtimer();
                     ps.trace[tslot * 32 + 7] = (unsigned long long)unit;
                 }
@@ -545,8 +649,32 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                     }
                     uint8_t* sa = smem + s * L::kStageBytes;
                     uint8_t* sb = sa + L::kABytes;
-                    mbar_expect_tx(&full_bar[s], (uint32_t)L::kStageBytes);
                     const int k0 = (kt_begin + kt) * BK;
+                    if constexpr (PAIR) {
+                        // both CTAs' bytes are counted on the leader's barrier
+                        if (leader) mbar_expect_tx(&full_bar[s], 2u * (uint32_t)L::kStageBytes);
+                        const uint32_t fb = mapa_cluster(smem_u32(&full_bar[s]), 0);
+                        const int bn0 = tile_n + cr * (BN / 2);   // this CTA's half of the B tile
+                        if (!AMN) {
+                            tma_load_2d_pair(sa, map_a, fb, k0, tile_m);  // box [128 rows][64 k]
+                        } else if (ps.a_blocked[w.p]) {
+                            tma_load_3d_pair(sa, map_a, fb, 0, k0, tile_m / 64);  // box [2 blocks][64 k][64 m]
+                        } else {
+                            tma_load_2d_pair(sa, map_a, fb, tile_m, k0);  // box [64 k][64 m]
+                            tma_load_2d_pair(sa + 64 * 128, map_a, fb, tile_m + 64, k0);
+                        }
+                        if (!BMN) {
+                            tma_load_2d_pair(sb, map_b, fb, k0, bn0);  // box [BN / 2 rows][64 k]
+                        } else if (ps.b_blocked[w.p]) {
+                            tma_load_3d_pair(sb, map_b, fb, 0, k0, bn0 / 64);  // box [BN / 128 blocks][64 k][64 n]
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < BN / 128; ++j)
+                                tma_load_2d_pair(sb + j * 64 * 128, map_b, fb, bn0 + 64 * j, k0);
+                        }
+                        continue;
+                    }
+                    mbar_expect_tx(&full_bar[s], (uint32_t)L::kStageBytes);
                     if (!AMN) {
                         tma_load_2d(sa, map_a, &full_bar[s], k0, tile_m);  // box [128 rows][64 k]
                     } else if (ps.a_blocked[w.p]) {
@@ -565,18 +693,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                             tma_load_2d(sb + j * 64 * 128, map_b, &full_bar[s], tile_n + 64 * j, k0);
                     }
                 }
-                if (ps.trace != nullptr && cta == 0 && tslot < 8) ps.trace[tslot * 32 + 1] = gtimer();
+                if (ps.trace != nullptr && cta == 0 && leader && tslot < 8) ps.trace[tslot * 32 + 1] = gtimer();
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
+        if (lane == 0 && leader) {
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((AMN ? 1u : 0u) << 15) |
-                                   ((BMN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                                   ((BMN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
+                                   ((uint32_t)((PAIR ? 2 * BM : BM) >> 4) << 24);
             uint32_t it = 0, tc = 0;
             bool ok = true;
             for (int unit = cta; unit < total_units && ok; unit += n_cta) {
-                const int num_kt = decode_unit<BN>(ps, unit, ag).num_kt;
+                const int num_kt = decode_unit<BN, PAIR>(ps, unit, ag, cr).num_kt;
                 if (num_kt == 0) continue;
                 const uint32_t buf = tc & 1u, tph = (tc >> 1) & 1u;
                 if (!mbar_wait(&tempty_bar[buf], tph ^ 1u, limit_ns)) {
@@ -586,7 +715,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + buf * (uint32_t)BN;
                 const int tslot = (unit - cta) / n_cta;
-                const bool tr = ps.trace != nullptr && cta == 0 && tslot < 8;
+                const bool tr = ps.trace != nullptr && cta == 0 && leader && tslot < 8;
                 if (tr) ps.trace[tslot * 32 + 2] = gtimer();
                 for (int kt = 0; kt < num_kt; ++kt, ++it) {
                     const int s = it % L::kStages;
@@ -598,7 +727,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                         break;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    if (tr && kt == 0) ps.trace[tslot * 32 + 3] = gtimer();
+                    if (tr && kt == 0) {
+                        ps.trace[tslot * 32 + 3] = gtimer();
+                        ps.trace[tslot * 32 + 20] = (unsigned long long)clock64();
+                    }
                     const uint32_t sa = smem_u32(smem + s * L::kStageBytes);
                     const uint32_t sb = sa + L::kABytes;
 #pragma unroll
@@ -608,13 +740,46 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                         // 8-k-row groups 1024 B apart, a K step of 16 rows is 2048 B.
                         const uint64_t da = AMN ? make_desc(sa + k * 2048, 8192, 1024) : make_desc(sa + k * 32, 16, 1024);
                         const uint64_t db = BMN ? make_desc(sb + k * 2048, 8192, 1024) : make_desc(sb + k * 32, 16, 1024);
-                        umma_bf16(tmem_d, da, db, idesc, (kt | k) ? 1u : 0u);
+                        if constexpr (PAIR) umma_bf16_pair(tmem_d, da, db, idesc, (kt | k) ? 1u : 0u);
+                        else umma_bf16(tmem_d, da, db, idesc, (kt | k) ? 1u : 0u);
                     }
-                    umma_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
+                    // frees the stage (in both CTAs of a pair) when these MMAs have read it
+                    if constexpr (PAIR) umma_commit_pair(&empty_bar[s]);
+                    else umma_commit(&empty_bar[s]);
                 }
-                umma_commit(&tfull_bar[buf]);  // accumulator complete (also on error, so the epilogue moves on)
-                if (tr) ps.trace[tslot * 32 + 4] = gtimer();
+                // accumulator complete (also on error, so the epilogue moves on)
+                if constexpr (PAIR) umma_commit_pair(&tfull_bar[buf]);
+                else umma_commit(&tfull_bar[buf]);
+                if (tr) {
+                    ps.trace[tslot * 32 + 4] = gtimer();
+                    ps.trace[tslot * 32 + 21] = (unsigned long long)clock64();
+                }
                 ++tc;
+            }
+        }
+    } else if (warp == kPublisherWarp) {
+        // ------------------------------ publisher (chain mode) --------------------
+        if (ps.chain && lane < kEpilogueWarps) {
+            uint32_t* box = pub_req + lane;
+            const unsigned long long t0 = gtimer();
+            unsigned spins = 0;
+            for (;;) {
+                const uint32_t r = ld_acquire_cta_smem(box);
+                if (r == kPubExit) break;
+                if (r != 0u) {
+                    // the epilogue warp saw its stores complete before it posted: fence, then tell the next layer
+                    __threadfence();
+                    atomicAdd(ps.done + (r - 1u), 1u);
+                    st_release_cta_smem(box, 0u);
+                    continue;
+                }
+                __nanosleep(40);
+                // every epilogue warp posts kPubExit on its way out, also after an error: this bound only guards
+                // against a warp that never gets there
+                if ((++spins & 255u) == 0 && gtimer() - t0 > limit_ns * 64) {
+                    atomicCAS(err_flag, 0u, 9u);
+                    break;
+                }
             }
         }
     } else {
@@ -625,23 +790,24 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
         const int etid = ew * 32 + lane;     // 0 .. 255
         constexpr int kChunks = BN / 64;     // 32-column chunks per warp
         uint32_t tc = 0;
-        bool pending_publish = false;        // chain mode: a finished tile whose completion counter is not bumped yet
-        unsigned* pending_counter = nullptr;
         bool store_in_flight = false;        // lane 0: a TMA store may still be reading this warp's staging piece
+        int bias_unit = -1;                  // the unit whose bias the previous tile already staged
         for (int unit = cta; unit < total_units; unit += n_cta) {
-            const WorkUnit w = decode_unit<BN>(ps, unit, ag);
+            const WorkUnit w = decode_unit<BN, PAIR>(ps, unit, ag, cr);
             const int tile_n = w.tile_n, tile_m = w.tile_m, num_kt = w.num_kt;
             const GemmEpilogue& ep = ps.ep[w.p];
             const int M = ps.M[w.p], N = ps.N[w.p];
             if (num_kt == 0) continue;
             const uint32_t buf = tc & 1u, tph = (tc >> 1) & 1u;
-            // the bias of the tile's columns does not depend on the MMAs: stage it while they run
+            // The bias of the tile's columns, staged in shared memory (double-buffered with the accumulator). It was
+            // fetched during the tile before this one; only the first tile of a CTA waits for the load here.
             float* bs = bias_smem + buf * 256;
             const bool has_bias = ep.bias != nullptr || ep.bias_bf16 != nullptr;
-            float bias_v = 0.f;
-            if (has_bias && etid < BN) {
+            if (has_bias && etid < BN && bias_unit != unit) {
                 const int col = tile_n + etid;
-                if (col < N) bias_v = ep.bias != nullptr ? ep.bias[col] : __bfloat162float(ep.bias_bf16[col]);
+                float v = 0.f;
+                if (col < N) v = ep.bias != nullptr ? ep.bias[col] : __bfloat162float(ep.bias_bf16[col]);
+                bs[etid] = v;
             }
             // Mask (ReLU backward) of this lane's row: the first piece is requested here, before the wait for the
             // accumulator, and each following piece while the one before it is converted and stored, so that no
@@ -657,22 +823,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                 for (int j = 0; j < 4; ++j) mreg[j] = ld_nc_v4(mrow + j * 8);
                 mhave = true;
             }
-            if (pending_publish) {
-                // The tile before this one (chain mode): its stores must be complete before the next layer reads them.
-                // Lane 0 issued the TMA stores; rows stored by the other lanes (the non-TMA path) are ordered before
-                // its fence by the warp barrier.
-                __syncwarp();
-                if (lane == 0) {
-                    bulk_wait0();
-                    __threadfence();
-                    atomicAdd(pending_counter, 1u);
-                }
-                pending_publish = false;
-            }
-            if (has_bias && etid < BN) bs[etid] = bias_v;
             const bool waited = mbar_wait(&tfull_bar[buf], tph, limit_ns * 4);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (ps.trace != nullptr && cta == 0 && (unit - cta) / n_cta < 8 && ew == 0 && lane == 0)
+            if (ps.trace != nullptr && cta == 0 && leader && (unit - cta) / n_cta < 8 && ew == 0 && lane == 0)
                 ps.trace[(unit - cta) / n_cta * 32 + 8] = gtimer();
             // One barrier of the epilogue warps per tile: it publishes the staged bias and makes the decision to give
             // up uniform (a warp that timed out must not leave the others waiting at the next tile's barrier).
@@ -690,7 +843,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                 break;
             }
             const int tslot = (unit - cta) / n_cta;
-            const bool tr = ps.trace != nullptr && cta == 0 && tslot < 8 && ew == 0 && lane == 0;
+            const bool tr = ps.trace != nullptr && cta == 0 && leader && tslot < 8 && ew == 0 && lane == 0;
             if (tr) ps.trace[tslot * 32 + 5] = gtimer();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)BN + (uint32_t)cbase;
             uint32_t v[32];
@@ -728,8 +881,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                 }
                 if (tr && c == 0) ps.trace[tslot * 32 + 15] = gtimer();
                 if (d_mode == 1) {
-                    // bf16: the warp's [32 rows][32 cols] piece, one row (64 bytes) per lane. Once the values are
-                    // packed their registers are free: the next piece leaves TMEM while this one is stored.
+                    // bf16: the warp's [32 rows][32 cols] piece goes through shared memory so that every store
+                    // instruction writes whole 64-byte row segments (8 rows per instruction) instead of 16 bytes
+                    // in each of 32 rows. Lane l writes row l; the 16-byte column blocks of a row are XOR-swizzled
+                    // by (row / 2) % 4, which makes both the row-wise writes and the 8-row reads conflict-free.
+                    // Once the values are packed their registers are free: the next piece leaves TMEM meanwhile.
                     uint4 raw[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -740,23 +896,35 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                         h[3] = __floats2bfloat162_rn(f[8 * j + 6], f[8 * j + 7]);
                     }
                     if (more) tmem_ld32_issue(taddr + (uint32_t)(c + 1) * 32u, v);
-                    // the staging piece is free once the store before this one has read it
-                    if (store_in_flight) {
-                        if (lane == 0) bulk_wait_read0();
-                        __syncwarp();
-                    }
+                    __syncwarp();   // the reads of the previous piece are done
+                    {
+                        const int sw = (lane >> 1) & 3;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) *(uint4*)(my_stage + j * 16) = raw[j];
-                    if (tr && c == 0) ps.trace[tslot * 32 + 16] = gtimer();
-                    fence_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (tr && c == 0) ps.trace[tslot * 32 + 10] = gtimer();
-                        tma_store_2d(map_d, stage_out + ew * 2048, col0, row0);
-                        bulk_commit();
-                        if (tr && c == 0) ps.trace[tslot * 32 + 11] = gtimer();
+                        for (int j = 0; j < 4; ++j) *(uint4*)(my_stage + ((j ^ sw) << 4)) = raw[j];
                     }
-                    store_in_flight = true;
+                    if (tr && c == 0) ps.trace[tslot * 32 + 16] = gtimer();
+                    __syncwarp();
+                    {
+                        const int cb = lane & 3;            // 16-byte column block of this lane
+                        const int gcol = col0 + cb * 8;
+                        __nv_bfloat16* orow = ep.out_bf16 + (size_t)row0 * ep.ldd + gcol;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int r = i * 8 + (lane >> 2);
+                            const uint4 d = *(const uint4*)(stage_out + ew * 2048 + r * 64 + ((cb ^ ((r >> 1) & 3)) << 4));
+                            if (row0 + r < M) {
+                                __nv_bfloat16* op = orow + (size_t)r * ep.ldd;
+                                if (gcol + 8 <= N) {
+                                    *(uint4*)op = d;
+                                } else {
+                                    const __nv_bfloat16* h = (const __nv_bfloat16*)&d;
+                                    for (int t = 0; t < 8; ++t)
+                                        if (gcol + t < N) op[t] = h[t];
+                                }
+                            }
+                        }
+                    }
+                    if (tr && c == 0) ps.trace[tslot * 32 + 10] = gtimer();
                 } else {
                     // fp32: two [32 rows][16 cols] pieces per chunk
                     if (store_in_flight) {
@@ -787,34 +955,50 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
             // this warp is done reading the buffer: hand it back to the MMA warp
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&tempty_bar[buf]);
-            if (ps.chain) {
-                // This warp's part of the tile is published to the next layer (stores complete -> fence -> counter)
-                // right before the warp next waits for an accumulator, or after the loop: the latency of the
-                // completion overlaps the set-up of the next tile, and nothing this CTA waits for can depend on a
-                // tile it has not published.
-                pending_publish = true;
-                pending_counter = ps.done + (size_t)w.p * kMaxChainMTiles + tile_m / BM;
+            if (lane == 0) {
+                if constexpr (PAIR) mbar_arrive_cluster(mapa_cluster(smem_u32(&tempty_bar[buf]), 0));
+                else mbar_arrive(&tempty_bar[buf]);
+                // Chain mode: this warp's part of the tile is handed to the publisher at once. The output of a chained
+                // layer is bf16 and written with ordinary stores (by all lanes, ordered before this hand-off by the
+                // warp barrier above), so there is nothing to wait for here: the publisher's fence covers them.
+                if (ps.chain && tile_m < M)
+                    post_publish(pub_req + ew, (uint32_t)(w.p * kMaxChainMTiles + tile_m / BM) + 1u, limit_ns, err_flag);
+            }
+            // fetch the bias of the next tile now: its latency hides behind the rest of this iteration
+            {
+                const int nu = unit + n_cta;
+                if (nu < total_units) {
+                    const WorkUnit nw = decode_unit<BN, PAIR>(ps, nu, ag, cr);
+                    const GemmEpilogue& nep = ps.ep[nw.p];
+                    if (nw.num_kt != 0 && (nep.bias != nullptr || nep.bias_bf16 != nullptr) && etid < BN) {
+                        const int col = nw.tile_n + etid;
+                        float v = 0.f;
+                        if (col < ps.N[nw.p]) v = nep.bias != nullptr ? nep.bias[col] : __bfloat162float(nep.bias_bf16[col]);
+                        bias_smem[(buf ^ 1u) * 256 + etid] = v;
+                    }
+                    bias_unit = nu;
+                }
             }
             ++tc;
         }
         __syncwarp();
         if (lane == 0) {
-            if (pending_publish) {
-                bulk_wait0();
-                __threadfence();
-                atomicAdd(pending_counter, 1u);
-            } else if (store_in_flight) {
-                bulk_wait_read0();   // the staging piece must outlive the store that reads it
-            }
+            if (store_in_flight) bulk_wait_read0();   // the staging piece must outlive the store that reads it
+            if (ps.chain) post_publish(pub_req + ew, kPubExit, limit_ns, err_flag);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
+    // a pair leaves together: until here the peer may still signal this CTA's barriers or read its shared memory
+    if constexpr (PAIR) cluster_sync_all();
+    else __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN))
-                     : "memory");
+        if constexpr (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN))
+                         : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN))
+                         : "memory");
     }
 }
 
@@ -890,14 +1074,34 @@ bool pdl_enabled() {
     return on;
 }
 
-template <int BN, bool AMN, bool BMN>
+template <int BN, bool AMN, bool BMN, bool PAIR>
 cudaError_t launch_variant(const GemmProblemSet& ps, unsigned* err, unsigned long long limit_ns, cudaStream_t s,
                            const GemmGather& ag) {
-    auto kern = gemm_bf16_tcgen05_kernel<BN, AMN, BMN>;
+    auto kern = gemm_bf16_tcgen05_kernel<BN, AMN, BMN, PAIR>;
     static bool configured = false;
+    static int max_pairs = 0;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::kTotal);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN, PAIR>::kTotal);
         if (e != cudaSuccess) return e;
+        if (PAIR) {
+            // how many 2-CTA clusters the device can hold at once (one CTA per SM): the size of the persistent grid
+            cudaLaunchConfig_t q = {};
+            q.gridDim = dim3(2);
+            q.blockDim = dim3(kThreads);
+            q.dynamicSmemBytes = SmemLayout<BN, PAIR>::kTotal;
+            cudaLaunchAttribute qa[1];
+            qa[0].id = cudaLaunchAttributeClusterDimension;
+            qa[0].val.clusterDim.x = 2;
+            qa[0].val.clusterDim.y = 1;
+            qa[0].val.clusterDim.z = 1;
+            q.attrs = qa;
+            q.numAttrs = 1;
+            int n = 0;
+            e = cudaOccupancyMaxActiveClusters(&n, kern, &q);
+            if (e != cudaSuccess) return e;
+            if (n <= 0) return cudaErrorLaunchOutOfResources;
+            max_pairs = n;
+        }
         configured = true;
     }
     static int num_sms = 0;
@@ -909,61 +1113,92 @@ cudaError_t launch_variant(const GemmProblemSet& ps, unsigned* err, unsigned lon
     const int units = ps.unit_end[ps.count - 1];
     int ctas = units < num_sms ? units : num_sms;
     if (ag.enabled) ctas = std::max(ag.gather_ctas + 1, std::min(num_sms, units + ag.gather_ctas));
+    if (PAIR) ctas = 2 * std::min(units, std::min(max_pairs, num_sms / 2));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas);
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = SmemLayout<BN>::kTotal;
+    cfg.dynamicSmemBytes = SmemLayout<BN, PAIR>::kTotal;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (PAIR) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 2;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (pdl_enabled() && !ag.enabled) {  // the prologue of this launch may overlap the previous kernel's tail
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() && !ag.enabled ? 1 : 0;  // the prologue of this launch may overlap the previous kernel's tail
+    cfg.numAttrs = na;
     return cudaLaunchKernelEx(&cfg, kern, ps, err, limit_ns, ag);
 }
 
-cudaError_t dispatch(int BN, bool a_mn, bool b_mn, const GemmProblemSet& ps, unsigned* err, unsigned long long lim,
-                     cudaStream_t s, const GemmGather& ag) {
+template <bool PAIR>
+cudaError_t dispatch_mode(int BN, bool a_mn, bool b_mn, const GemmProblemSet& ps, unsigned* err, unsigned long long lim,
+                          cudaStream_t s, const GemmGather& ag) {
     const int v = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
     if (BN == 256) {
         switch (v) {
-            case 0: return launch_variant<256, false, false>(ps, err, lim, s, ag);
-            case 1: return launch_variant<256, false, true>(ps, err, lim, s, ag);
-            case 2: return launch_variant<256, true, false>(ps, err, lim, s, ag);
-            default: return launch_variant<256, true, true>(ps, err, lim, s, ag);
+            case 0: return launch_variant<256, false, false, PAIR>(ps, err, lim, s, ag);
+            case 1: return launch_variant<256, false, true, PAIR>(ps, err, lim, s, ag);
+            case 2: return launch_variant<256, true, false, PAIR>(ps, err, lim, s, ag);
+            default: return launch_variant<256, true, true, PAIR>(ps, err, lim, s, ag);
         }
     }
     switch (v) {
-        case 0: return launch_variant<128, false, false>(ps, err, lim, s, ag);
-        case 1: return launch_variant<128, false, true>(ps, err, lim, s, ag);
-        case 2: return launch_variant<128, true, false>(ps, err, lim, s, ag);
-        default: return launch_variant<128, true, true>(ps, err, lim, s, ag);
+        case 0: return launch_variant<128, false, false, PAIR>(ps, err, lim, s, ag);
+        case 1: return launch_variant<128, false, true, PAIR>(ps, err, lim, s, ag);
+        case 2: return launch_variant<128, true, false, PAIR>(ps, err, lim, s, ag);
+        default: return launch_variant<128, true, true, PAIR>(ps, err, lim, s, ag);
     }
+}
+
+cudaError_t dispatch(int BN, bool pair, bool a_mn, bool b_mn, const GemmProblemSet& ps, unsigned* err, unsigned long long lim,
+                     cudaStream_t s, const GemmGather& ag) {
+    return pair ? dispatch_mode<true>(BN, a_mn, b_mn, ps, err, lim, s, ag) : dispatch_mode<false>(BN, a_mn, b_mn, ps, err, lim, s, ag);
+}
+
+// CTA pairs are used whenever a problem has more than one 128-row block (and never with the gather role, whose
+// copy CTAs are not part of a pair). PSB_GEMM_PAIR=0 forces the 1-CTA kernel.
+bool pair_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("PSB_GEMM_PAIR");
+        return !(e != nullptr && e[0] == '0');
+    }();
+    return on;
 }
 
 // Fills slot i of a problem set; returns 0, -2 (alignment) or -3 (tensor map).
 unsigned long long* g_gemm_trace = nullptr;
 
-int add_problem(GemmProblemSet* ps, int i, int BN, const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep, int M,
-                int N, int K) {
+int add_problem(GemmProblemSet* ps, int i, int BN, bool pair, const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep,
+                int M, int N, int K) {
+    const int BNL = pair ? BN / 2 : BN;   // rows of B that one CTA loads per stage
     if ((A.ld % 8) || (B.ld % 8) || ((uintptr_t)A.ptr % 16) || ((uintptr_t)B.ptr % 16)) return -2;  // TMA: 16-byte rule
     // K-major: tensor [MN rows][K cols], box [tile rows][64]; MN-major: tensor [K rows][MN cols], box [64][64], or the
     // blocked 3-D form (one load per stage) when the MN extent is a whole number of 64-wide blocks covering the tile
     ps->a_blocked[i] = (A.mn_major && M % 64 == 0 && M >= BM) ? 1 : 0;
     ps->b_blocked[i] = (B.mn_major && N % 64 == 0 && N >= BN) ? 1 : 0;
+    if (pair && BNL < 64) ps->b_blocked[i] = 0;
     // (if the driver refuses the blocked form, the per-block form does the same job with more loads)
     if (ps->a_blocked[i] && !make_map_blocked(&ps->map_a[i], A.ptr, (uint64_t)K, (uint64_t)M, (uint64_t)A.ld, BM / 64)) ps->a_blocked[i] = 0;
-    if (ps->b_blocked[i] && !make_map_blocked(&ps->map_b[i], B.ptr, (uint64_t)K, (uint64_t)N, (uint64_t)B.ld, BN / 64)) ps->b_blocked[i] = 0;
+    if (ps->b_blocked[i] && !make_map_blocked(&ps->map_b[i], B.ptr, (uint64_t)K, (uint64_t)N, (uint64_t)B.ld, BNL / 64)) ps->b_blocked[i] = 0;
     bool ok = A.mn_major ? (ps->a_blocked[i] ? make_map_blocked(&ps->map_a[i], A.ptr, (uint64_t)K, (uint64_t)M, (uint64_t)A.ld, BM / 64)
                                              : make_map(&ps->map_a[i], A.ptr, (uint64_t)K, (uint64_t)M, (uint64_t)A.ld, 64))
                          : make_map(&ps->map_a[i], A.ptr, (uint64_t)M, (uint64_t)K, (uint64_t)A.ld, BM);
-    ok = ok && (B.mn_major ? (ps->b_blocked[i] ? make_map_blocked(&ps->map_b[i], B.ptr, (uint64_t)K, (uint64_t)N, (uint64_t)B.ld, BN / 64)
+    ok = ok && (B.mn_major ? (ps->b_blocked[i] ? make_map_blocked(&ps->map_b[i], B.ptr, (uint64_t)K, (uint64_t)N, (uint64_t)B.ld, BNL / 64)
                                                : make_map(&ps->map_b[i], B.ptr, (uint64_t)K, (uint64_t)N, (uint64_t)B.ld, 64))
-                           : make_map(&ps->map_b[i], B.ptr, (uint64_t)N, (uint64_t)K, (uint64_t)B.ld, BN));
+                           : make_map(&ps->map_b[i], B.ptr, (uint64_t)N, (uint64_t)K, (uint64_t)B.ld, BNL));
     if (!ok) return -3;
     ps->d_mode[i] = 0;
     if (ep.out_bf16 != nullptr && ep.out_f32 == nullptr) {
-        if (make_map_out(&ps->map_d[i], ep.out_bf16, false, (uint64_t)M, (uint64_t)N, (uint64_t)ep.ldd)) ps->d_mode[i] = 1;
+        // coalesced 16-byte stores through a staging piece: rows must start on 16-byte boundaries
+        if (((uintptr_t)ep.out_bf16 % 16) == 0 && (ep.ldd % 8) == 0) ps->d_mode[i] = 1;
     } else if (ep.out_f32 != nullptr && ep.out_bf16 == nullptr) {
         if (make_map_out(&ps->map_d[i], ep.out_f32, true, (uint64_t)M, (uint64_t)N, (uint64_t)ep.ldd))
             ps->d_mode[i] = (ep.split_k > 1 || ep.accumulate) ? 2 : 3;
@@ -972,7 +1207,8 @@ int add_problem(GemmProblemSet* ps, int i, int BN, const GemmOperand& A, const G
     ps->M[i] = M;
     ps->N[i] = N;
     ps->K[i] = K;
-    const int units = ((N + BN - 1) / BN) * ((M + BM - 1) / BM) * (ep.split_k > 1 ? ep.split_k : 1);
+    const int bmu = pair ? 2 * BM : BM;
+    const int units = ((N + BN - 1) / BN) * ((M + bmu - 1) / bmu) * (ep.split_k > 1 ? ep.split_k : 1);
     ps->unit_end[i] = (i > 0 ? ps->unit_end[i - 1] : 0) + units;
     return 0;
 }
@@ -998,10 +1234,11 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep
     ps.chain = 0;
     ps.done = nullptr;
     ps.trace = g_gemm_trace;
-    int rc = add_problem(&ps, 0, BN, A, B, ep, M, N, K);
+    const bool pair = pair_enabled() && !ag.enabled && M > BM;
+    int rc = add_problem(&ps, 0, BN, pair, A, B, ep, M, N, K);
     if (rc != 0) return rc;
     const unsigned long long lim = (unsigned long long)(wait_limit_s * 1e9);
-    return (int)dispatch(BN, A.mn_major, B.mn_major, ps, err_flag, lim, (cudaStream_t)stream, ag);
+    return (int)dispatch(BN, pair, A.mn_major, B.mn_major, ps, err_flag, lim, (cudaStream_t)stream, ag);
 }
 
 void gemm_set_trace(void* device_buffer_of_256_u64) { g_gemm_trace = (unsigned long long*)device_buffer_of_256_u64; }
@@ -1033,13 +1270,16 @@ int gemm_bf16_grouped(const GemmOperand* A, const GemmOperand* B, const GemmEpil
         cudaError_t e = cudaMemsetAsync(chain_done, 0, (size_t)count * kMaxChainMTiles * sizeof(unsigned), (cudaStream_t)stream);
         if (e != cudaSuccess) return (int)e;
     }
+    bool pair = false;
+    for (int i = 0; i < count; ++i) pair = pair || M[i] > BM;
+    pair = pair && pair_enabled();
     for (int i = 0; i < count; ++i) {
-        int rc = add_problem(&ps, i, BN, A[i], B[i], ep[i], M[i], N[i], K[i]);
+        int rc = add_problem(&ps, i, BN, pair, A[i], B[i], ep[i], M[i], N[i], K[i]);
         if (rc != 0) return rc;
     }
     const unsigned long long lim = (unsigned long long)(wait_limit_s * 1e9);
     GemmGather none;
-    return (int)dispatch(BN, A[0].mn_major, B[0].mn_major, ps, err_flag, lim, (cudaStream_t)stream, none);
+    return (int)dispatch(BN, pair, A[0].mn_major, B[0].mn_major, ps, err_flag, lim, (cudaStream_t)stream, none);
 }
 
 }  // namespace psb

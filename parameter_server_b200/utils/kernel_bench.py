@@ -320,7 +320,8 @@ def cmd_chain(a):
         print(" unit " + " ".join(f"{n:>8s}" for n in names) + "   (ns after CTA 0's first load)")
         for r in v:
             if r[0]:
-                print(f"{r[7]:5d} " + " ".join(f"{(r[k] - t0) if r[k] else -1:8d}" for k in order))
+                mhz = (r[21] - r[20]) / max(1, r[4] - r[3]) * 1e3
+                print(f"{r[7]:5d} " + " ".join(f"{(r[k] - t0) if r[k] else -1:8d}" for k in order) + f"   SM clock {mhz:6.0f} MHz")
 
 
 def main():
