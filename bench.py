@@ -60,8 +60,10 @@ def parse_args():
     ap.add_argument("--breakdown", action="store_true", help="after the timed regions, add per-section device times of an eager step")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-overlap", action="store_true", help="run the sparse pull / push in line with the dense work (one stream)")
+    ap.add_argument("--overlap", action="store_true", help="force the side-stream overlap (default: on for up to two GPUs)")
     ap.add_argument("--no-chain", action="store_true", help="one GEMM launch per MLP layer instead of one chained launch per MLP pass")
-    ap.add_argument("--sparse-ctas", type=int, default=2, help="CTAs per SM of the fused sparse kernels while they share the SMs with the GEMMs")
+    ap.add_argument("--pull-sms", type=int, default=112, help="SMs of the fused sparse pull while it runs beside the bottom MLP (the GEMMs get the rest)")
+    ap.add_argument("--push-sms", type=int, default=90, help="SMs of the fused sparse push while it runs beside the dense backward pass")
     ap.add_argument("--micro-keys", type=int, default=1 << 20, help="keys per GPU per step of the microbenchmark")
     ap.add_argument("--micro-rows", type=int, default=62_500_000, help="resident rows per GPU of the microbenchmark table (config 2: 500 M keys / 8)")
     ap.add_argument("--sizes", default="65536,262144,1048576,4194304", help="--config sparse: keys per GPU per step")
@@ -281,8 +283,8 @@ def main():
                          chain_gemms=not args.no_chain)
             graph = False      # variable all-to-all split sizes need the host: not capturable
         else:
-            model = DLRM(cfg, B, table_capacity=capacity, seed=0, overlap=not args.no_overlap,
-                         sparse_ctas_per_sm=args.sparse_ctas, chain_gemms=not args.no_chain)
+            model = DLRM(cfg, B, table_capacity=capacity, seed=0, overlap=(False if args.no_overlap else (True if args.overlap else None)),
+                         pull_sms=args.pull_sms, push_sms=args.push_sms, chain_gemms=not args.no_chain)
         data = SyntheticCTR(cfg, B, pool=16, seed=1000 + rank)
         sampler = ClockSampler(uuid)
         sampler.start()          # returns once the first sample is in
@@ -363,7 +365,7 @@ def main():
             "vocab": "26 fields log-spaced 1e3..4e7 (~300M rows), rows created on first pull",
             "launch": "whole step replayed from one CUDA graph" if own["graph"] else "eager",
             "streams": ("sparse pull beside the bottom MLP forward and sparse push beside bottom dgrad + weight / bias "
-                        "gradients (side stream, %d CTAs per SM)" % args.sparse_ctas) if own["overlap"] else "one stream",
+                        "gradients (side stream; the GPU is split by SMs: pull %d / push %d SMs, GEMMs on the rest)" % (args.pull_sms, args.push_sms)) if own["overlap"] else "one stream",
             "l2": "inputs larger than L2: ~55 MB of bf16 embedding rows gathered + ~109 MB of fp32 row gradients per step "
                   "per GPU, new batch (pool of 16) every step",
         },

@@ -233,7 +233,7 @@ PYBIND11_MODULE(_C, m) {
         .def("scratch_bytes", &SparseEngine::scratch_bytes)
         .def("kernel_launches", &SparseEngine::kernel_launches)
         .def("set_wait_limit", &SparseEngine::set_wait_limit)
-        .def("set_cta_budget", &SparseEngine::set_cta_budget)
+        .def("set_sm_budget", &SparseEngine::set_sm_budget)
         .def("set_deterministic", &SparseEngine::set_deterministic)
         .def("set_mirror", &SparseEngine::set_mirror, py::keep_alive<1, 2>())
         .def("deterministic", &SparseEngine::deterministic)

@@ -153,6 +153,8 @@ void bind_dense(py::module_& m) {
           py::arg("stream") = 0);
     m.def("gemm_chain_scratch_words", &gemm_chain_scratch_words);
     m.def("gemm_set_trace", [](uintptr_t p) { gemm_set_trace((void*)p); });
+    m.def("gemm_set_cta_limit", &gemm_set_cta_limit);
+    m.def("gemm_set_pair", &gemm_set_pair);
 
     bind_model_kernels(m);
 }

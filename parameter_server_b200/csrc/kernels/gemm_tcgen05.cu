@@ -1066,6 +1066,8 @@ bool make_map_out(CUtensorMap* map, void* base, bool f32, uint64_t rows, uint64_
     return r == CUDA_SUCCESS;
 }
 
+extern int g_gemm_cta_limit;
+
 bool pdl_enabled() {
     static const bool on = [] {
         const char* e = std::getenv("PSB_GEMM_PDL");
@@ -1113,7 +1115,10 @@ cudaError_t launch_variant(const GemmProblemSet& ps, unsigned* err, unsigned lon
     const int units = ps.unit_end[ps.count - 1];
     int ctas = units < num_sms ? units : num_sms;
     if (ag.enabled) ctas = std::max(ag.gather_ctas + 1, std::min(num_sms, units + ag.gather_ctas));
-    if (PAIR) ctas = 2 * std::min(units, std::min(max_pairs, num_sms / 2));
+    int sms = num_sms;
+    if (g_gemm_cta_limit > 0 && !ag.enabled) sms = std::max(2, std::min(num_sms, g_gemm_cta_limit));
+    if (!ag.enabled) ctas = std::min(ctas, sms);
+    if (PAIR) ctas = 2 * std::min(units, std::min(max_pairs, sms / 2));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas);
     cfg.blockDim = dim3(kThreads);
@@ -1165,16 +1170,18 @@ cudaError_t dispatch(int BN, bool pair, bool a_mn, bool b_mn, const GemmProblemS
 
 // CTA pairs are used whenever a problem has more than one 128-row block (and never with the gather role, whose
 // copy CTAs are not part of a pair). PSB_GEMM_PAIR=0 forces the 1-CTA kernel.
+int g_gemm_pair = 1;
 bool pair_enabled() {
     static const bool on = [] {
         const char* e = std::getenv("PSB_GEMM_PAIR");
         return !(e != nullptr && e[0] == '0');
     }();
-    return on;
+    return on && g_gemm_pair != 0;
 }
 
 // Fills slot i of a problem set; returns 0, -2 (alignment) or -3 (tensor map).
 unsigned long long* g_gemm_trace = nullptr;
+int g_gemm_cta_limit = 0;   // 0 = one CTA per SM
 
 int add_problem(GemmProblemSet* ps, int i, int BN, bool pair, const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep,
                 int M, int N, int K) {
@@ -1240,6 +1247,9 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep
     const unsigned long long lim = (unsigned long long)(wait_limit_s * 1e9);
     return (int)dispatch(BN, pair, A.mn_major, B.mn_major, ps, err_flag, lim, (cudaStream_t)stream, ag);
 }
+
+void gemm_set_cta_limit(int ctas) { g_gemm_cta_limit = ctas > 0 ? ctas : 0; }
+void gemm_set_pair(int on) { g_gemm_pair = on ? 1 : 0; }
 
 void gemm_set_trace(void* device_buffer_of_256_u64) { g_gemm_trace = (unsigned long long*)device_buffer_of_256_u64; }
 

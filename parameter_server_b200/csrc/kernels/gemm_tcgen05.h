@@ -63,6 +63,12 @@ int gemm_bf16_grouped(const GemmOperand* A, const GemmOperand* B, const GemmEpil
                       const int* K, int count, unsigned* err_flag, double wait_limit_s, void* stream,
                       unsigned* chain_done = nullptr);
 int gemm_chain_scratch_words();
+// Upper bound on the CTAs (= SMs) of the following launches; 0 = all SMs. A GEMM CTA fills its SM, so a smaller grid
+// leaves whole SMs to kernels of another stream that run at the same time (the sparse push beside the dense backward).
+void gemm_set_cta_limit(int ctas);
+// CTA pairs (two CTAs of a cluster per 256-row tile) on or off for the following launches. A pair needs two free SMs
+// of one TPC at the same moment; launches that share the GPU with another kernel run better without.
+void gemm_set_pair(int on);
 // Tracing of the following launches (nullptr = off): CTA 0 writes %globaltimer stamps for the first 8 work units it runs
 // into this device buffer of 256 x u64, 32 slots per unit (producer, MMA and epilogue milestones; unit index in slot 7). The tool behind the per-tile timelines in profiles/.
 void gemm_set_trace(void* device_buffer_of_256_u64);

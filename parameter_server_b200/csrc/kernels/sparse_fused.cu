@@ -39,10 +39,10 @@ namespace psb {
 
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 1024;
 // block-local accumulation of hot gradient rows in the push (Q1)
-constexpr int kHotSlots = 512;   // shared-memory counting table per CTA
-constexpr int kHotRows = 24;     // most rows cached per CTA (FusedArgs::hot_rows chooses; dynamic shared memory)
+constexpr int kHotSlots = 2048;  // shared-memory counting table per CTA
+constexpr int kHotRows = 64;     // most rows cached per CTA (FusedArgs::hot_rows chooses; dynamic shared memory)
 constexpr unsigned kHotMaxDim = 128;
 constexpr size_t kPushSmemBytes = (size_t)kHotRows * kHotMaxDim * sizeof(float);
 
@@ -105,7 +105,7 @@ struct RowSrc {
         if (a.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 0) a.prof[slot] = global_timer_ns(); \
     } while (0)
 
-__global__ void __launch_bounds__(kThreads, 4) fused_pull_kernel(const FusedArgs a) {
+__global__ void __launch_bounds__(kThreads, 1) fused_pull_kernel(const FusedArgs a) {
     const unsigned nblocks = gridDim.x;
     const unsigned tid = blockIdx.x * kThreads + threadIdx.x;
     const unsigned nthreads = nblocks * kThreads;
@@ -520,7 +520,7 @@ __global__ void __launch_bounds__(kThreads, 4) fused_pull_kernel(const FusedArgs
     if (blockIdx.x == 0 && threadIdx.x == 0) a.ctl->epoch = epoch;
 }
 
-__global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs a) {
+__global__ void __launch_bounds__(kThreads, 1) fused_push_kernel(const FusedArgs a) {
     const unsigned nblocks = gridDim.x;
     const unsigned tid = blockIdx.x * kThreads + threadIdx.x;
     const unsigned nthreads = nblocks * kThreads;
@@ -600,7 +600,9 @@ __global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs
             __syncthreads();
             // 1. count the keys of this range
             for (unsigned i = lo + threadIdx.x; i < hi; i += kThreads) {
-                const unsigned u = (unsigned)a.inverse[i] & ~kDupBit;
+                const unsigned iv = (unsigned)a.inverse[i];
+                if (!(iv & kDupBit)) continue;   // a key that occurs once in the batch needs no summing
+                const unsigned u = iv & ~kDupBit;
                 unsigned h = (u * 2654435761u) & (kHotSlots - 1);
                 for (int probe = 0; probe < 8; ++probe) {
                     const unsigned prev = atomicCAS(&s_hkey[h], 0xFFFFFFFFu, u);
@@ -640,7 +642,7 @@ __global__ void __launch_bounds__(kThreads, 4) fused_push_kernel(const FusedArgs
             if (use_cache) {
 #pragma unroll
                 for (int k = 0; k < kPos; ++k) {
-                    if (active[k] && lane == 0) {
+                    if (active[k] && dup[k] && lane == 0) {
                         unsigned h = (u[k] * 2654435761u) & (kHotSlots - 1);
                         for (int probe = 0; probe < 8; ++probe) {
                             const unsigned key = s_hkey[h];
@@ -1018,6 +1020,9 @@ int fused_max_blocks(int device, int* pull_blocks, int* push_blocks) {
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_pull_kernel, kThreads, 0);
     if (e != cudaSuccess) return (int)e;
     *pull_blocks = per_sm * prop.multiProcessorCount;
+    // static counting tables + the dynamic row cache exceed the 48 KB a kernel gets without asking
+    e = cudaFuncSetAttribute(fused_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPushSmemBytes);
+    if (e != cudaSuccess) return (int)e;
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_push_kernel, kThreads, kPushSmemBytes);
     if (e != cudaSuccess) return (int)e;
     *push_blocks = per_sm * prop.multiProcessorCount;

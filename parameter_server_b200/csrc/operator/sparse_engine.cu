@@ -127,7 +127,7 @@ SparseEngine::SparseEngine(GpuTable* table, const SparseEngineConfig& cfg) : tab
     int rc = fused_max_blocks(table_->device(), &max_pull_blocks_, &max_push_blocks_);
     if (rc != 0) throw std::runtime_error("SparseEngine: occupancy query failed");
     cudaDeviceGetAttribute(&num_sms_, cudaDevAttrMultiProcessorCount, table_->device());
-    set_cta_budget(0);
+    set_sm_budget(0, 0);
     cudaDeviceSynchronize();
     std::vector<void*> self(1, symm_->local());
     if (W == 1) symm_->connect_local(self, 0);
@@ -171,16 +171,10 @@ Status SparseEngine::connect(const std::vector<std::string>& handles) {
     return symm_->connect(handles, cfg_.rank);
 }
 
-void SparseEngine::set_cta_budget(int ctas_per_sm) {
-    pull_blocks_ = max_pull_blocks_;
-    push_blocks_ = max_push_blocks_;
-    // a budgeted push also keeps its shared memory small (8 hot rows = 4 KB), so that two of its CTAs fit beside
-    // the ~194 KB of a GEMM CTA
-    hot_rows_ = ctas_per_sm > 0 ? 8u : 24u;
-    if (ctas_per_sm > 0 && num_sms_ > 0) {
-        pull_blocks_ = std::min(max_pull_blocks_, ctas_per_sm * num_sms_);
-        push_blocks_ = std::min(max_push_blocks_, ctas_per_sm * num_sms_);
-    }
+void SparseEngine::set_sm_budget(int pull_sms, int push_sms) {
+    // one CTA of the fused kernels fills an SM (1024 threads): the grid size is the number of SMs the call occupies
+    pull_blocks_ = pull_sms > 0 ? std::min(max_pull_blocks_, pull_sms) : max_pull_blocks_;
+    push_blocks_ = push_sms > 0 ? std::min(max_push_blocks_, push_sms) : max_push_blocks_;
 }
 
 void SparseEngine::connect_local(const std::vector<SparseEngine*>& engines) {

@@ -50,10 +50,11 @@ public:
     Status check(void* stream);
     // Re-arm after an error (clears scratch, barriers and flags on THIS rank; every rank must do it).
     Status reset(void* stream);
-    // CTA budget of the two kernels: 0 = as many CTAs as can be resident on the idle GPU; n > 0 = at most n CTAs
-    // per SM, which leaves registers and thread slots for kernels of another stream (the dense GEMMs of the same
-    // step) to run beside them.
-    void set_cta_budget(int ctas_per_sm);
+    // SM budget of the two kernels: a CTA of the fused kernels fills its SM (1024 threads, the whole register file),
+    // so n > 0 = the call occupies n SMs and leaves the others, whole, to kernels of another stream (the dense GEMMs
+    // of the same step, whose CTAs also fill an SM each: whichever starts first, the two share the GPU by SMs).
+    // 0 = every SM.
+    void set_sm_budget(int pull_sms, int push_sms);
     // Reproducible pushes: duplicate keys of a batch are summed in position order (a stable sort + an ordered
     // segment sum before the fused kernel) instead of with fp32 atomics. Together with the rank-ordered fold of the
     // owners this makes the table after a push a function of the requests alone. Allocates its scratch on first use.
@@ -112,7 +113,7 @@ private:
     int pull_blocks_ = 0, push_blocks_ = 0;          // grid of the next launches
     int max_pull_blocks_ = 0, max_push_blocks_ = 0;  // full residency on the idle GPU
     int num_sms_ = 0;
-    unsigned hot_rows_ = 24;
+    unsigned hot_rows_ = 64;
     bool failed_ = false;                            // a fatal device status was seen: reset() first
     bool deterministic_ = false;
     unsigned *sorted_ids_ = nullptr, *sorted_pos_ = nullptr;   // scratch of the ordered pre-aggregation

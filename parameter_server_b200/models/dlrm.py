@@ -95,8 +95,8 @@ class DLRM:
 
     def __init__(self, cfg: DLRMConfig, batch: int, *, table_capacity: int = 1 << 22, device=None, group=None,
                  seed: int = 0, wgrad_split_k: int = 0, sparse_kwargs: Optional[dict] = None,
-                 sparse_cls=SparseTable, dense_cls=DenseTable, overlap: bool = True, sparse_ctas_per_sm: int = 2,
-                 chain_gemms: bool = True):
+                 sparse_cls=SparseTable, dense_cls=DenseTable, overlap: Optional[bool] = None, pull_sms: int = 112,
+                 push_sms: int = 90, chain_gemms: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("DLRM runs on the sm_100a kernels and needs a CUDA device")
         self.cfg = cfg
@@ -177,12 +177,21 @@ class DLRM:
         # the layers of each MLP pass (bottom forward, top forward, top dgrad, bottom dgrad) run as one chained launch
         self.chain_gemms = bool(chain_gemms)
         # Overlap: the sparse pull runs on a side stream beside the bottom MLP forward, the sparse push beside the
-        # bottom dgrad + weight / bias gradients. The fused sparse kernels then get a bounded CTA budget, which
-        # leaves registers, thread slots and shared memory on every SM for one GEMM CTA.
-        self.overlap = bool(overlap) and hasattr(self.sparse, "set_cta_budget")
+        # bottom dgrad + weight / bias gradients. The GPU is shared by SMs: a CTA of the fused sparse kernels and a
+        # CTA of the GEMM each fill an SM, so the pull (push) is launched on ``pull_sms`` (``push_sms``) SMs and the
+        # GEMMs of the concurrent branch on the others, whichever kernel happens to start first.
+        # Measured on B200: the split pays on one GPU (about 5 % of the step) and on two (2 %); from four ranks on the
+        # pull and push spend much of their time waiting for peers, and SMs held by a waiting kernel are lost to the
+        # GEMMs, so the default (None) turns the overlap on for up to two ranks only.
+        if overlap is None:
+            overlap = self.sparse.world <= 2
+        self.overlap = bool(overlap) and hasattr(self.sparse, "set_sm_budget")
+        self.n_sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        self.pull_sms = max(8, min(int(pull_sms), self.n_sms - 8))
+        self.push_sms = max(8, min(int(push_sms), self.n_sms - 8))
         if self.overlap:
             self.side = torch.cuda.Stream(device=dev)
-            self.sparse.set_cta_budget(sparse_ctas_per_sm)
+            self.sparse.set_sm_budget(self.pull_sms, self.push_sms)
         self.graph = None
         self.graphs = [None, None]   # one captured step per input-buffer set
         self.trace = None   # list of (section, CUDA event) while a step is being traced
@@ -312,6 +321,9 @@ class DLRM:
                 self.sparse.pull(self.d_keys, out=self.emb); n_launch += 1
                 if self.stamps is not None:
                     self._mark("pull_done")
+            # the GEMMs beside the pull: single CTAs (a pair needs two free SMs of one TPC) on the other SMs
+            C.gemm_set_cta_limit(self.n_sms - self.pull_sms)
+            C.gemm_set_pair(0)
         self.dense.zero_grads()  # torch fill kernels (not counted as own launches)
         self.loss.zero_()
         chk(C.cast_pad(self.d_dense.data_ptr(), B, cfg.num_dense, self.x16.data_ptr(), self.k_in, s)); n_launch += 1
@@ -319,6 +331,8 @@ class DLRM:
         n_launch += self._mlp_forward(self.x16, self.bot_act, "bot")
         self._mark("bottom_fwd")
         if self.overlap:
+            C.gemm_set_cta_limit(0)
+            C.gemm_set_pair(1)
             main.wait_stream(self.side)   # join: the interaction needs the embedding rows
         else:
             self.sparse.pull(self.d_keys, out=self.emb); n_launch += 1
@@ -363,6 +377,8 @@ class DLRM:
                 self.sparse.push(self.d_emb); n_launch += 1
                 if self.stamps is not None:
                     self._mark("push_done")
+            C.gemm_set_cta_limit(self.n_sms - self.push_sms)
+            C.gemm_set_pair(0)
         else:
             self.sparse.push(self.d_emb); n_launch += 1
         self._mark("sparse_push")
@@ -383,6 +399,8 @@ class DLRM:
         G.bias_grads(bg); n_launch += (len(bg) + 7) // 8
         self._mark("bias_grad")
         if self.overlap:
+            C.gemm_set_cta_limit(0)
+            C.gemm_set_pair(1)
             # join before the dense push: it waits for the other ranks like the sparse push does, and two kernels
             # that wait for peers must not compete for the same SMs
             main.wait_stream(self.side)

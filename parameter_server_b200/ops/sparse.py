@@ -330,11 +330,11 @@ class SparseTable:
         if self.is_cuda:
             raise_if_error(self.engine.set_deterministic(bool(on)))
 
-    def set_cta_budget(self, ctas_per_sm: int) -> None:
-        """Bound the grid of the fused kernels to ``ctas_per_sm`` CTAs per SM (0 = fill the idle GPU), so that
-        kernels of another stream can run beside them."""
+    def set_sm_budget(self, pull_sms: int = 0, push_sms: int = 0) -> None:
+        """Bound the fused pull / push kernels to that many SMs (0 = all). One of their CTAs fills an SM, so the
+        remaining SMs stay free, whole, for kernels of another stream that run at the same time."""
         if self.is_cuda:
-            self.engine.set_cta_budget(int(ctas_per_sm))
+            self.engine.set_sm_budget(int(pull_sms), int(push_sms))
 
     # ------------------------------------------------------------------------------------------
     def size(self) -> int:

@@ -276,7 +276,7 @@ def test_pull_in_bf16_is_the_fp32_pull_rounded_once(dim, bag):
 
 def test_bounded_cta_budget_gives_the_same_results():
     g, c = pair(32, "adagrad", lr=0.05, init_accumulator=0.1)
-    g.set_cta_budget(1)
+    g.set_sm_budget(37, 50)
     assert g.engine.pull_blocks() <= 148 and g.engine.push_blocks() <= 148
     keys = torch.from_numpy(np.random.default_rng(3).permutation(1 << 20)[:20000].astype(np.int64))
     for step in range(3):
