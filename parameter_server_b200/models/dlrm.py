@@ -184,7 +184,7 @@ class DLRM:
         # pull and push spend much of their time waiting for peers, and SMs held by a waiting kernel are lost to the
         # GEMMs, so the default (None) turns the overlap on for up to two ranks only.
         if overlap is None:
-            overlap = self.sparse.world <= 2
+            overlap = getattr(self.sparse, "world", 1) <= 2
         self.overlap = bool(overlap) and hasattr(self.sparse, "set_sm_budget")
         self.n_sms = torch.cuda.get_device_properties(dev).multi_processor_count
         self.pull_sms = max(8, min(int(pull_sms), self.n_sms - 8))
