@@ -39,12 +39,18 @@ namespace psb {
 
 namespace {
 
-constexpr int kThreads = 1024;
+// Two CTA shapes, same code: 256 threads (four CTAs per SM; fastest on an idle GPU, whose large batches like many small
+// row caches) and 1024 threads (one CTA fills an SM: the shape for sharing the GPU by SMs with another kernel).
+constexpr int kThreadsSmall = 256;
+constexpr int kThreadsWide = 1024;
 // block-local accumulation of hot gradient rows in the push (Q1)
-constexpr int kHotSlots = 2048;  // shared-memory counting table per CTA
-constexpr int kHotRows = 64;     // most rows cached per CTA (FusedArgs::hot_rows chooses; dynamic shared memory)
+// push, per CTA: counting table of kHotSlots keys, at most kHotRows rows cached (FusedArgs::hot_rows may ask for fewer)
+template <int kThreads> struct HotCfg {
+    static constexpr int kHotSlots = kThreads >= 1024 ? 2048 : 512;
+    static constexpr int kHotRows = kThreads >= 1024 ? 64 : 24;
+};
 constexpr unsigned kHotMaxDim = 128;
-constexpr size_t kPushSmemBytes = (size_t)kHotRows * kHotMaxDim * sizeof(float);
+template <int kThreads> constexpr size_t push_smem_bytes() { return (size_t)HotCfg<kThreads>::kHotRows * kHotMaxDim * sizeof(float); }
 
 enum Where : unsigned {
     W_P1 = 1, W_P2, W_KEYFLAG, W_P3A, W_P3B, W_P3C, W_ROWFLAG, W_MAILBOX_OVERFLOW, W_INDEX_FULL, W_POOL_FULL,
@@ -105,7 +111,8 @@ struct RowSrc {
         if (a.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 0) a.prof[slot] = global_timer_ns(); \
     } while (0)
 
-__global__ void __launch_bounds__(kThreads, 1) fused_pull_kernel(const FusedArgs a) {
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_pull_kernel(const FusedArgs a) {
     const unsigned nblocks = gridDim.x;
     const unsigned tid = blockIdx.x * kThreads + threadIdx.x;
     const unsigned nthreads = nblocks * kThreads;
@@ -520,7 +527,10 @@ __global__ void __launch_bounds__(kThreads, 1) fused_pull_kernel(const FusedArgs
     if (blockIdx.x == 0 && threadIdx.x == 0) a.ctl->epoch = epoch;
 }
 
-__global__ void __launch_bounds__(kThreads, 1) fused_push_kernel(const FusedArgs a) {
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_push_kernel(const FusedArgs a) {
+    constexpr int kHotSlots = HotCfg<kThreads>::kHotSlots;
+    constexpr int kHotRows = HotCfg<kThreads>::kHotRows;
     const unsigned nblocks = gridDim.x;
     const unsigned tid = blockIdx.x * kThreads + threadIdx.x;
     const unsigned nthreads = nblocks * kThreads;
@@ -622,6 +632,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_push_kernel(const FusedArgs
             for (unsigned t = threadIdx.x; t < nc * a.dim; t += kThreads) s_cache[t] = 0.f;
             __syncthreads();
         }
+        PROF(13);
         const unsigned gl0 = (threadIdx.x & 31u) / lanes * lanes;  // first lane of this group inside its warp
         // Four positions per lane group and iteration: their index lookups and gradient-row loads are all issued
         // before the first accumulation (the loop is bound by load latency, not by bytes).
@@ -675,6 +686,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_push_kernel(const FusedArgs
                 }
             }
         }
+        PROF(14);
         if (use_cache) {
             __syncthreads();
             const unsigned nc = min(s_ncache, hot_rows);
@@ -685,6 +697,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_push_kernel(const FusedArgs
             }
         }
     }
+    PROF(15);
     PROF_CTA(3);
     if (!grid_sync(a.ctl, nblocks, a.limit_ns, W_Q1)) return;
 
@@ -1010,36 +1023,51 @@ __global__ void __launch_bounds__(kThreads, 1) fused_push_kernel(const FusedArgs
     if (blockIdx.x == 0 && threadIdx.x == 0) a.ctl->epoch = epoch;
 }
 
-int fused_threads_per_block() { return kThreads; }
-
-int fused_max_blocks(int device, int* pull_blocks, int* push_blocks) {
-    cudaDeviceProp prop;
-    cudaError_t e = cudaGetDeviceProperties(&prop, device);
-    if (e != cudaSuccess) return (int)e;
+namespace {
+template <int kThreads>
+int max_blocks_of(const cudaDeviceProp& prop, int* pull_blocks, int* push_blocks) {
     int per_sm = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_pull_kernel, kThreads, 0);
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_pull_kernel<kThreads>, kThreads, 0);
     if (e != cudaSuccess) return (int)e;
     *pull_blocks = per_sm * prop.multiProcessorCount;
-    // static counting tables + the dynamic row cache exceed the 48 KB a kernel gets without asking
-    e = cudaFuncSetAttribute(fused_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPushSmemBytes);
+    // static counting tables + the dynamic row cache may exceed the 48 KB a kernel gets without asking
+    e = cudaFuncSetAttribute(fused_push_kernel<kThreads>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)push_smem_bytes<kThreads>());
     if (e != cudaSuccess) return (int)e;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_push_kernel, kThreads, kPushSmemBytes);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_push_kernel<kThreads>, kThreads, push_smem_bytes<kThreads>());
     if (e != cudaSuccess) return (int)e;
     *push_blocks = per_sm * prop.multiProcessorCount;
     return 0;
 }
-
-int launch_fused_pull(const FusedArgs& a, int nblocks, void* stream) {
+template <int kThreads>
+int launch_push_of(const FusedArgs& a, int nblocks, void* stream) {
     void* params[] = {(void*)&a};
-    return (int)cudaLaunchCooperativeKernel((const void*)fused_pull_kernel, dim3(nblocks), dim3(kThreads), params, 0,
+    const unsigned cap = (unsigned)HotCfg<kThreads>::kHotRows;
+    const size_t smem = (size_t)(a.hot_rows < cap ? a.hot_rows : cap) * kHotMaxDim * sizeof(float);
+    return (int)cudaLaunchCooperativeKernel((const void*)fused_push_kernel<kThreads>, dim3(nblocks), dim3(kThreads), params, smem,
                                             (cudaStream_t)stream);
 }
+}  // namespace
 
-int launch_fused_push(const FusedArgs& a, int nblocks, void* stream) {
+int fused_max_blocks(int device, bool wide, int* pull_blocks, int* push_blocks) {
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) return (int)e;
+    return wide ? max_blocks_of<kThreadsWide>(prop, pull_blocks, push_blocks)
+                : max_blocks_of<kThreadsSmall>(prop, pull_blocks, push_blocks);
+}
+
+int launch_fused_pull(const FusedArgs& a, int nblocks, bool wide, void* stream) {
     void* params[] = {(void*)&a};
-    const size_t smem = (size_t)(a.hot_rows < (unsigned)kHotRows ? a.hot_rows : (unsigned)kHotRows) * kHotMaxDim * sizeof(float);
-    return (int)cudaLaunchCooperativeKernel((const void*)fused_push_kernel, dim3(nblocks), dim3(kThreads), params, smem,
-                                            (cudaStream_t)stream);
+    if (wide)
+        return (int)cudaLaunchCooperativeKernel((const void*)fused_pull_kernel<kThreadsWide>, dim3(nblocks), dim3(kThreadsWide),
+                                                params, 0, (cudaStream_t)stream);
+    return (int)cudaLaunchCooperativeKernel((const void*)fused_pull_kernel<kThreadsSmall>, dim3(nblocks), dim3(kThreadsSmall),
+                                            params, 0, (cudaStream_t)stream);
+}
+
+int launch_fused_push(const FusedArgs& a, int nblocks, bool wide, void* stream) {
+    return wide ? launch_push_of<kThreadsWide>(a, nblocks, stream) : launch_push_of<kThreadsSmall>(a, nblocks, stream);
 }
 
 }  // namespace psb

@@ -89,9 +89,9 @@ constexpr unsigned kProfMaxCtas = 2048;   // per-CTA profile stamps: prof[16 + k
 constexpr unsigned kDupBit = 0x80000000u;   // in FusedArgs::inverse: the position's key occurs more than once in the batch
 
 // Host launchers (defined in sparse_fused.cu). `stream` is a cudaStream_t. Return cudaError_t as int.
-int launch_fused_pull(const FusedArgs& a, int nblocks, void* stream);
-int launch_fused_push(const FusedArgs& a, int nblocks, void* stream);
-int fused_max_blocks(int device, int* pull_blocks, int* push_blocks);
-int fused_threads_per_block();
+// wide = the 1024-thread CTA shape (one CTA per SM); otherwise 256 threads, four CTAs per SM
+int launch_fused_pull(const FusedArgs& a, int nblocks, bool wide, void* stream);
+int launch_fused_push(const FusedArgs& a, int nblocks, bool wide, void* stream);
+int fused_max_blocks(int device, bool wide, int* pull_blocks, int* push_blocks);
 
 }  // namespace psb

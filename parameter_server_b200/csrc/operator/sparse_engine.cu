@@ -124,7 +124,8 @@ SparseEngine::SparseEngine(GpuTable* table, const SparseEngineConfig& cfg) : tab
     std::vector<int> owner(std::max(cfg_.n_shards, 1));
     for (size_t i = 0; i < owner.size(); ++i) owner[i] = (int)(i % (size_t)W);
     set_shard_owner(owner);
-    int rc = fused_max_blocks(table_->device(), &max_pull_blocks_, &max_push_blocks_);
+    int rc = fused_max_blocks(table_->device(), false, &max_pull_blocks_, &max_push_blocks_);
+    if (rc == 0) rc = fused_max_blocks(table_->device(), true, &max_pull_wide_, &max_push_wide_);
     if (rc != 0) throw std::runtime_error("SparseEngine: occupancy query failed");
     cudaDeviceGetAttribute(&num_sms_, cudaDevAttrMultiProcessorCount, table_->device());
     set_sm_budget(0, 0);
@@ -172,9 +173,13 @@ Status SparseEngine::connect(const std::vector<std::string>& handles) {
 }
 
 void SparseEngine::set_sm_budget(int pull_sms, int push_sms) {
-    // one CTA of the fused kernels fills an SM (1024 threads): the grid size is the number of SMs the call occupies
-    pull_blocks_ = pull_sms > 0 ? std::min(max_pull_blocks_, pull_sms) : max_pull_blocks_;
-    push_blocks_ = push_sms > 0 ? std::min(max_push_blocks_, push_sms) : max_push_blocks_;
+    // No budget: 256-thread CTAs, four per SM, on every SM. With a budget the call runs as 1024-thread CTAs, each of
+    // which fills an SM, so the grid size is the number of SMs the call occupies.
+    pull_wide_ = pull_sms > 0;
+    push_wide_ = push_sms > 0;
+    pull_blocks_ = pull_wide_ ? std::min(max_pull_wide_, pull_sms) : max_pull_blocks_;
+    push_blocks_ = push_wide_ ? std::min(max_push_wide_, push_sms) : max_push_blocks_;
+    hot_rows_ = push_wide_ ? 64u : 24u;
 }
 
 void SparseEngine::connect_local(const std::vector<SparseEngine*>& engines) {
@@ -272,7 +277,7 @@ Status SparseEngine::pull(const long long* keys, uint32_t n, uint32_t bag_size, 
     a.out = out;
     a.grads = nullptr;
     a.hot_rows = 0;
-    int rc = launch_fused_pull(a, pull_blocks_, stream);
+    int rc = launch_fused_pull(a, pull_blocks_, pull_wide_, stream);
     ++launches_;
     if (flags & FUSED_INSERT) table_->refresh_usage_async(stream);
     if (rc != 0) return Status::Error(std::string("fused_pull launch: ") + cudaGetErrorString((cudaError_t)rc));
@@ -325,7 +330,7 @@ Status SparseEngine::push(const float* grads, uint32_t n_rows, const OptConfig& 
     a.grads = grads;
     a.opt = opt;
     a.hot_rows = hot_rows_;
-    int rc = launch_fused_push(a, push_blocks_, stream);
+    int rc = launch_fused_push(a, push_blocks_, push_wide_, stream);
     ++launches_;
     if (mirror_ != nullptr) mirror_->refresh_usage_async(stream);
     if (rc != 0) return Status::Error(std::string("fused_push launch: ") + cudaGetErrorString((cudaError_t)rc));

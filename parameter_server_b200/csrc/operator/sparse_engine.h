@@ -50,10 +50,10 @@ public:
     Status check(void* stream);
     // Re-arm after an error (clears scratch, barriers and flags on THIS rank; every rank must do it).
     Status reset(void* stream);
-    // SM budget of the two kernels: a CTA of the fused kernels fills its SM (1024 threads, the whole register file),
-    // so n > 0 = the call occupies n SMs and leaves the others, whole, to kernels of another stream (the dense GEMMs
-    // of the same step, whose CTAs also fill an SM each: whichever starts first, the two share the GPU by SMs).
-    // 0 = every SM.
+    // SM budget of the two kernels. 0 = the whole GPU (256-thread CTAs, four per SM). n > 0 = the call runs as
+    // 1024-thread CTAs, each of which fills its SM (the whole register file), on n SMs, and leaves the others, whole,
+    // to kernels of another stream (the dense GEMMs of the same step, whose CTAs also fill an SM each: whichever
+    // starts first, the two share the GPU by SMs).
     void set_sm_budget(int pull_sms, int push_sms);
     // Reproducible pushes: duplicate keys of a batch are summed in position order (a stable sort + an ordered
     // segment sum before the fused kernel) instead of with fp32 atomics. Together with the rank-ordered fold of the
@@ -111,9 +111,11 @@ private:
     std::vector<int> shard_owner_host_;
     unsigned pull_epoch_ = 0, push_epoch_ = 0;
     int pull_blocks_ = 0, push_blocks_ = 0;          // grid of the next launches
-    int max_pull_blocks_ = 0, max_push_blocks_ = 0;  // full residency on the idle GPU
+    int max_pull_blocks_ = 0, max_push_blocks_ = 0;  // full residency on the idle GPU (256-thread CTAs)
+    int max_pull_wide_ = 0, max_push_wide_ = 0;      // the same for the 1024-thread shape (one CTA per SM)
+    bool pull_wide_ = false, push_wide_ = false;
     int num_sms_ = 0;
-    unsigned hot_rows_ = 64;
+    unsigned hot_rows_ = 24;
     bool failed_ = false;                            // a fatal device status was seen: reset() first
     bool deterministic_ = false;
     unsigned *sorted_ids_ = nullptr, *sorted_pos_ = nullptr;   // scratch of the ordered pre-aggregation

@@ -99,6 +99,10 @@ def cmd_sparse(a):
         pool.append(torch.from_numpy(k.astype(np.int64)).cuda())
     grads = torch.randn(n, dim, device="cuda") * 1e-3
     out = torch.empty(n, dim, device="cuda")
+    if a.deterministic:
+        t.set_deterministic(True)
+    if a.sms:
+        t.set_sm_budget(a.sms, a.sms)
     t.reserve(8 * n, exact=True)
     for i in range(8):
         t.pull(pool[i % 4], out=out)
@@ -135,7 +139,11 @@ def cmd_sparse(a):
         names = ["P1 dedup", "P2 ship", "P3a resolve", "P3b init", "P3c rows", "P5 gather"]
         for i, nm in enumerate(names):
             print(f"   {nm:12s} {(st[i+1]-st[i])/1e3:8.1f} us")
-        print(f"   {'Q1 segsum':12s} {(st[10]-st[8])/1e3:8.1f} us")
+        print(f"   {'Q1 segsum':12s} {(st[10]-st[8])/1e3:8.1f} us  (CTA 0: chain + cache set-up {(st[13]-st[8])/1e3:.1f}, sums {(st[14]-st[13])/1e3:.1f}, "
+              f"cache flush {(st[15]-st[14])/1e3:.1f}, barrier {(st[10]-st[15])/1e3:.1f})")
+        v = sorted((x - st[8]) / 1e3 for x in t.engine.cta_stamps(3, 0) if x)
+        if v:
+            print(f"   Q1 CTA arrival at the barrier: min {v[0]:.1f}  median {v[len(v)//2]:.1f}  max {v[-1]:.1f} us")
         print(f"   {'Q3c update':12s} {(st[12]-st[11])/1e3:8.1f} us")
 
 
@@ -324,6 +332,66 @@ def cmd_chain(a):
                 print(f"{r[7]:5d} " + " ".join(f"{(r[k] - t0) if r[k] else -1:8d}" for k in order) + f"   SM clock {mhz:6.0f} MHz")
 
 
+def cmd_scaling(a):
+    """How the GEMM launches of the DLRM step and the fused sparse kernels scale with the SMs they get: the input to
+    the choice of the SM split when the two run side by side (``DLRM(overlap=True, pull_sms=, push_sms=)``)."""
+    import contextlib
+    import io
+    from .._lib import C
+    from ..ops.sparse import SparseTable
+    n_sms = torch.cuda.get_device_properties(0).multi_processor_count
+    for lim in (0, 112, 74, 36):
+        C.gemm_set_cta_limit(lim)
+        C.gemm_set_pair(0 if lim else 1)
+        buf = io.StringIO()
+        with contextlib.redirect_stdout(buf):
+            cmd_mlp(a)
+        print(f"== GEMM launches on {lim or n_sms} SMs" + ("" if lim else " (CTA pairs)"))
+        for ln in buf.getvalue().splitlines():
+            if "chained" in ln or "grouped" in ln:
+                print(ln)
+    C.gemm_set_cta_limit(0)
+    C.gemm_set_pair(1)
+    # a DLRM-like batch: 26 fields, Zipf(1.1) per field, vocabularies log-spaced 1e3 .. 4e7, dim 128
+    B, F, dim = a.batch, 26, 128
+    rng = np.random.default_rng(0)
+    vocab = np.logspace(3, np.log10(4e7), F).astype(np.int64)
+
+    def batch():
+        ks = [(rng.zipf(1.1, size=B).astype(np.int64) % vocab[f]) + (np.int64(f) << np.int64(40)) for f in range(F)]
+        return torch.from_numpy(np.stack(ks, 1).reshape(-1)).cuda()
+
+    n = B * F
+    t = SparseTable(dim, "adagrad", dict(lr=0.05, init_accumulator=0.1), capacity=8 * n, max_keys=n)
+    pool = [batch() for _ in range(8)]
+    grads = torch.randn(n, dim, device="cuda") * 1e-3
+    out = torch.empty(n, dim, device="cuda", dtype=torch.bfloat16)
+    t.reserve(8 * n, exact=True)
+    for i in range(16):
+        t.pull(pool[i % 8], out=out)
+        t.push(grads)
+    t.check()
+    it = [0]
+
+    def pull():
+        t.pull(pool[it[0] % 8], out=out)
+        it[0] += 1
+
+    def both():
+        pull()
+        t.push(grads)
+
+    for sms in (0, 148, 112, 90, 74, 37):
+        if sms > n_sms:
+            continue
+        t.set_sm_budget(sms, sms)
+        tp = timed(pull, a.iters)
+        tb = timed(both, a.iters)
+        t.check()
+        shape = f"{sms} SMs, 1024-thread CTAs" if sms else f"{n_sms} SMs, 256-thread CTAs x 4"
+        print(f"sparse pull / push of {n} keys, dim {dim}, on {shape}: pull {tp*1e6:7.1f} us   push {(tb-tp)*1e6:7.1f} us")
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -334,6 +402,8 @@ def main():
     s.add_argument("--keys", type=int, default=1 << 20); s.add_argument("--dim", type=int, default=64)
     s.add_argument("--zipf", type=float, default=1.05); s.add_argument("--vocab", type=int, default=62_500_000)
     s.add_argument("--phases", action="store_true")
+    s.add_argument("--deterministic", action="store_true", help="reproducible pushes (sorted segment sum)")
+    s.add_argument("--sms", type=int, default=0, help="SM budget of pull and push (0 = whole GPU, 256-thread CTAs)")
     i = sub.add_parser("interaction")
     i.add_argument("--batch", type=int, default=8192)
     d = sub.add_parser("dense")
@@ -344,11 +414,14 @@ def main():
     c.add_argument("--which", default="top_fwd", choices=["top_fwd", "top_dgrad", "wgrad"])
     c.add_argument("--batch", type=int, default=8192)
     c.add_argument("--trace", action="store_true", help="print the per-tile timeline of CTA 0")
-    for p in (g, s, i, d, m, c):
+    sc = sub.add_parser("scaling")
+    sc.add_argument("--batch", type=int, default=8192)
+    for p in (g, s, i, d, m, c, sc):
         p.add_argument("--iters", type=int, default=10)
         p.add_argument("--no-flush", action="store_true")
     a = ap.parse_args()
-    {"gemm": cmd_gemm, "sparse": cmd_sparse, "interaction": cmd_interaction, "dense": cmd_dense, "mlp": cmd_mlp, "chain": cmd_chain}[a.cmd](a)
+    {"gemm": cmd_gemm, "sparse": cmd_sparse, "interaction": cmd_interaction, "dense": cmd_dense, "mlp": cmd_mlp, "chain": cmd_chain,
+     "scaling": cmd_scaling}[a.cmd](a)
 
 
 if __name__ == "__main__":
