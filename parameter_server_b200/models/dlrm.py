@@ -156,6 +156,7 @@ class DLRM:
                          torch.empty((B, F), dtype=torch.int64, device=dev),
                          torch.empty((B,), dtype=torch.float32, device=dev)) for _ in range(2)]
         self._slot = 0
+        self._staged = None   # input-buffer set holding a batch that no step has consumed yet
         self.d_dense, self.d_keys, self.d_labels = self._inputs[0]
         self.copy_stream = torch.cuda.Stream(device=dev)
         self._in_ready = [torch.cuda.Event() for _ in range(2)]
@@ -460,19 +461,35 @@ class DLRM:
         self._use_slot(keep)
         self.graph = self.graphs[keep]
 
-    def train_step(self, dense: torch.Tensor, keys: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
-        """Public API: copy one pinned host batch in, run the step, return the device loss. The copy goes into the
-        input-buffer set that the previous step is NOT using, on a copy stream: when the caller queues steps without
-        waiting for each (the usual training loop), the transfer of batch t + 1 overlaps the compute of step t."""
-        main = torch.cuda.current_stream()
+    def stage(self, dense: torch.Tensor, keys: torch.Tensor, labels: torch.Tensor) -> None:
+        """Start the host -> device copy of the NEXT step's batch (pinned host tensors) on the copy stream, into the
+        input-buffer set that the running step is not using. Called right after ``train_step`` it lets the transfer
+        overlap the compute of the step just queued, also in a loop that reads the loss back after every step."""
         slot = self._slot ^ 1
-        self._use_slot(slot)
+        d_dense, d_keys, d_labels = self._inputs[slot]
         with torch.cuda.stream(self.copy_stream):
             self.copy_stream.wait_event(self._in_consumed[slot])   # the step that last read this set has finished
-            self.d_dense.copy_(dense, non_blocking=True)
-            self.d_keys.copy_(keys, non_blocking=True)
-            self.d_labels.copy_(labels, non_blocking=True)
+            d_dense.copy_(dense, non_blocking=True)
+            d_keys.copy_(keys, non_blocking=True)
+            d_labels.copy_(labels, non_blocking=True)
             self._in_ready[slot].record(self.copy_stream)
+        self._staged = slot
+
+    def train_step(self, dense: Optional[torch.Tensor] = None, keys: Optional[torch.Tensor] = None,
+                   labels: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Public API: run one step and return the device loss. With a batch (pinned host tensors) the batch is
+        staged first; without arguments the step runs on the batch handed to ``stage`` before. Either way the copy
+        goes into the input-buffer set that the previous step is NOT using, on a copy stream: when the caller
+        queues steps without waiting for each, or stages batch t + 1 before it reads the loss of step t, the
+        transfer of batch t + 1 overlaps the compute of step t."""
+        if dense is not None:
+            self.stage(dense, keys, labels)
+        if self._staged is None:
+            raise RuntimeError("train_step() without a batch needs a stage(...) call before it")
+        main = torch.cuda.current_stream()
+        slot = self._staged
+        self._staged = None
+        self._use_slot(slot)
         main.wait_event(self._in_ready[slot])
         if self.graphs[slot] is None:
             out = self.forward_backward()
