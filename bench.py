@@ -366,7 +366,7 @@ def main():
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": None,
-        "dtype": "bf16 MLP, fp32 embeddings + optimizer state",
+        "dtype": "bf16 MLP; fp32 embedding rows + optimizer state, fp32 sums; rows and row gradients cross NVLink as bf16",
         "data": "synthetic (Zipf(1.1) keys per field, log-normal dense, Bernoulli(0.03) labels), random-init weights",
         "impl": args.impl,
         "config": {

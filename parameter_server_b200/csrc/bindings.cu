@@ -235,6 +235,7 @@ PYBIND11_MODULE(_C, m) {
         .def("set_wait_limit", &SparseEngine::set_wait_limit)
         .def("set_sm_budget", &SparseEngine::set_sm_budget)
         .def("set_deterministic", &SparseEngine::set_deterministic)
+        .def("set_grad_wire_bf16", &SparseEngine::set_grad_wire_bf16)
         .def("set_mirror", &SparseEngine::set_mirror, py::keep_alive<1, 2>())
         .def("deterministic", &SparseEngine::deterministic)
         .def("pull_blocks", &SparseEngine::pull_blocks)

@@ -67,6 +67,11 @@ __device__ __forceinline__ float4 init4(const TableView& t, long long key, unsig
     return v;
 }
 
+__device__ __forceinline__ float4 unpack_bf16x4(const uint2& p) {
+    const __nv_bfloat162 lo = *(const __nv_bfloat162*)&p.x, hi = *(const __nv_bfloat162*)&p.y;
+    const float2 a = __bfloat1622float2(lo), b = __bfloat1622float2(hi);
+    return make_float4(a.x, a.y, b.x, b.y);
+}
 __device__ __forceinline__ uint2 pack_bf16x4(const float4& v) {
     __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
     uint2 p;
@@ -547,6 +552,7 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_push_kernel(c
     const TableView T = *a.table;
     const PeerBufs& mine = a.peer[me];
     const unsigned lanes = lanes_for_dim(a.dim);
+    const bool grads16 = (a.flags & FUSED_GRAD_BF16) != 0;
     const unsigned group = tid / lanes, ngroups = nthreads / lanes, lane = tid % lanes;
     const unsigned L = a.bag_size;
 
@@ -735,7 +741,9 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_push_kernel(c
                 while (e >= s_pre[o + 1]) ++o;
                 const unsigned p = e - s_pre[o];
                 src[k] = a.agg + (size_t)a.send_ret[(size_t)o * C + p] * a.dim;
-                dst[k] = a.peer[o].mail_grad + ((size_t)me * C + p) * a.dim;
+                // bf16 on the wire: the same mailbox, rows packed at half the pitch
+                dst[k] = grads16 ? (float*)((__nv_bfloat16*)a.peer[o].mail_grad + ((size_t)me * C + p) * a.dim)
+                                 : a.peer[o].mail_grad + ((size_t)me * C + p) * a.dim;
             }
             for (unsigned d = lane * 4; d < a.dim; d += lanes * 4) {
                 float4 v[kIn];
@@ -743,8 +751,11 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_push_kernel(c
                 for (int k = 0; k < kIn; ++k)
                     if (act[k]) v[k] = *(const float4*)(src[k] + d);
 #pragma unroll
-                for (int k = 0; k < kIn; ++k)
-                    if (act[k]) *(float4*)(dst[k] + d) = v[k];
+                for (int k = 0; k < kIn; ++k) {
+                    if (!act[k]) continue;
+                    if (grads16) *(uint2*)((__nv_bfloat16*)dst[k] + d) = pack_bf16x4(v[k]);
+                    else *(float4*)(dst[k] + d) = v[k];
+                }
             }
         }
         if (cta_arrive_last(&a.ctl->arrive[0], nblocks)) {
@@ -870,12 +881,18 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_push_kernel(c
             j = __shfl_sync(gmask, j, gl0);
             if (j < (unsigned)W * C) rep_dst = a.peer[partner].rep_grad + (size_t)j * dim;
         }
+        // gradient row of chain entry k: this rank's own sum (fp32) or a row of the mailbox (fp32 or bf16)
+        auto grad4 = [&](int k, unsigned d) -> float4 {
+            if ((int)(ids[k] / C) == me) return *(const float4*)(own + d);
+            if (grads16) return unpack_bf16x4(*(const uint2*)((const __nv_bfloat16*)mine.mail_grad + (size_t)ids[k] * dim + d));
+            return *(const float4*)(mine.mail_grad + (size_t)ids[k] * dim + d);
+        };
         for (unsigned d = lane * 4; d < dim; d += lanes * 4) {
-            float4 gv = *(const float4*)(((int)(ids[0] / C) == me ? own : mine.mail_grad + (size_t)ids[0] * dim) + d);
+            float4 gv = grad4(0, d);
 #pragma unroll
             for (int k = 1; k < kMaxWorld; ++k) {
                 if (ids[k] == kNoRow) continue;
-                const float4 o = *(const float4*)(((int)(ids[k] / C) == me ? own : mine.mail_grad + (size_t)ids[k] * dim) + d);
+                const float4 o = grad4(k, d);
                 gv.x = __fadd_rn(gv.x, o.x); gv.y = __fadd_rn(gv.y, o.y);
                 gv.z = __fadd_rn(gv.z, o.z); gv.w = __fadd_rn(gv.w, o.w);
             }

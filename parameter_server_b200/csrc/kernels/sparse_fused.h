@@ -37,6 +37,7 @@ enum FusedFlags : unsigned {
                               // also cross NVLink as bf16, which halves the bytes of the row-return phase
     FUSED_AGG_READY = 64u,    // push: the per-unique gradient sums are already in `agg` (deterministic pre-pass)
     FUSED_REPLICATE = 128u,   // push: every row update is also applied to the row's replica on the partner GPU
+    FUSED_GRAD_BF16 = 256u,   // push: merged gradient rows cross NVLink as bf16 (summed in fp32 on both sides)
 };
 
 struct FusedArgs {

@@ -314,6 +314,7 @@ Status SparseEngine::push(const float* grads, uint32_t n_rows, const OptConfig& 
     FusedArgs a;
     fill_common(a);
     a.flags = (plan_flags_ & FUSED_MEAN) | (flags & (FUSED_SYNC_PUSH | FUSED_AGG_READY));
+    if (grad_wire_bf16_) a.flags |= FUSED_GRAD_BF16;
     if (mirror_ != nullptr) {
         a.flags |= FUSED_REPLICATE;
         // the mirror may get a row for every entry of the mirrored rank's log

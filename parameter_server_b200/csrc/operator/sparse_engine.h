@@ -59,6 +59,10 @@ public:
     // segment sum before the fused kernel) instead of with fp32 atomics. Together with the rank-ordered fold of the
     // owners this makes the table after a push a function of the requests alone. Allocates its scratch on first use.
     Status set_deterministic(bool on);
+    // Gradient rows that go to another rank cross NVLink as bf16 (half the bytes of the push's link-bound phase); each
+    // rank's partial sum is rounded once, the owner adds the rows in fp32. Off by default: results then differ from
+    // the fp32 oracle in the last bits of a bf16 value.
+    void set_grad_wire_bf16(bool on) { grad_wire_bf16_ = on; }
     // Replication inside the push (needs SparseEngineConfig::replicate on every rank): `mirror` is the table on THIS
     // GPU that mirrors the shards of rank (rank - 1) % world (with world 1: of this rank). From then on every push
     // forwards, per updated row, the key and the folded gradient to rank (rank + 1) % world, whose kernel applies
@@ -114,6 +118,7 @@ private:
     int max_pull_blocks_ = 0, max_push_blocks_ = 0;  // full residency on the idle GPU (256-thread CTAs)
     int max_pull_wide_ = 0, max_push_wide_ = 0;      // the same for the 1024-thread shape (one CTA per SM)
     bool pull_wide_ = false, push_wide_ = false;
+    bool grad_wire_bf16_ = false;
     int num_sms_ = 0;
     unsigned hot_rows_ = 24;
     bool failed_ = false;                            // a fatal device status was seen: reset() first

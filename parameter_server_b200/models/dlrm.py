@@ -96,7 +96,7 @@ class DLRM:
     def __init__(self, cfg: DLRMConfig, batch: int, *, table_capacity: int = 1 << 22, device=None, group=None,
                  seed: int = 0, wgrad_split_k: int = 0, sparse_kwargs: Optional[dict] = None,
                  sparse_cls=SparseTable, dense_cls=DenseTable, overlap: Optional[bool] = None, pull_sms: int = 112,
-                 push_sms: int = 90, chain_gemms: bool = True):
+                 push_sms: int = 90, chain_gemms: bool = True, grad_wire_bf16: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("DLRM runs on the sm_100a kernels and needs a CUDA device")
         self.cfg = cfg
@@ -193,6 +193,9 @@ class DLRM:
         if self.overlap:
             self.side = torch.cuda.Stream(device=dev)
             self.sparse.set_sm_budget(self.pull_sms, self.push_sms)
+        # the row gradients come out of bf16 tensor-core arithmetic; between ranks they travel as bf16 like the rows
+        if grad_wire_bf16 and hasattr(self.sparse, "set_grad_wire_bf16"):
+            self.sparse.set_grad_wire_bf16(True)
         self.graph = None
         self.graphs = [None, None]   # one captured step per input-buffer set
         self.trace = None   # list of (section, CUDA event) while a step is being traced

@@ -330,6 +330,12 @@ class SparseTable:
         if self.is_cuda:
             raise_if_error(self.engine.set_deterministic(bool(on)))
 
+    def set_grad_wire_bf16(self, on: bool = True) -> None:
+        """Ship the merged gradient rows of a push to their owners as bf16 (the sums on both sides stay fp32). Halves
+        the bytes of the push's NVLink phase; for models whose gradients come out of bf16 arithmetic anyway."""
+        if self.is_cuda:
+            self.engine.set_grad_wire_bf16(bool(on))
+
     def set_sm_budget(self, pull_sms: int = 0, push_sms: int = 0) -> None:
         """Bound the fused pull / push kernels to that many SMs (0 = all). One of their CTAs fills an SM, so the
         remaining SMs stay free, whole, for kernels of another stream that run at the same time."""

@@ -41,12 +41,19 @@ def main():
         # Twice: with the default (atomic) duplicate sums, compared within a tolerance, and in reproducible mode, where
         # every rank sums its duplicates in position order and the owners fold the ranks in rank order: then the tables
         # must equal, bit for bit, an oracle that adds in that same order.
-        for deterministic in (False, True):
+        # A third time with the gradient rows crossing NVLink as bf16: every rank's partial sum is rounded once (relative
+        # error 2^-9), so the comparison is looser.
+        for mode in ("atomic", "ordered", "bf16wire"):
+            deterministic = mode == "ordered"
+            wire16 = mode == "bf16wire"
             for dim, opt, kw in [(64, "adagrad", dict(lr=0.05, init_accumulator=0.1)), (16, "sgd", dict(lr=0.5)),
                                  (128, "adam", dict(lr=0.01))]:
+                if wire16 and opt == "adam":
+                    continue   # Adam divides by sqrt(v): a rounded gradient near zero moves the update visibly
                 n_shards = world * 3 + 1
                 g = SparseTable(dim, opt, kw, n_shards=n_shards, capacity=1 << 16, max_keys=1 << 15, wait_limit_s=5.0)
                 g.set_deterministic(deterministic)
+                g.set_grad_wire_bf16(wire16)
                 c = SparseTable(dim, opt, kw, n_shards=n_shards, device="cpu", group="none") if rank == 0 else None
                 if c is not None:
                     c.world, c.rank = 1, 0
@@ -75,6 +82,10 @@ def main():
                                 np.add.at(agg, inv, g_r.numpy())
                                 us.append(torch.from_numpy(u)); aggs.append(torch.from_numpy(agg))
                             c.push(torch.cat(aggs), keys=torch.cat(us))
+                        elif wire16:
+                            assert mostly_close(got, ref, 1e-2, 1e-3, 5e-3), \
+                                f"pull mismatch (bf16 wire) dim={dim} step={step}: {(got-ref).abs().max()}"
+                            c.push(torch.cat(all_grads))
                         else:
                             assert mostly_close(got, ref, 1e-3, 2e-5, 2e-3 if opt == "adam" else 2e-5), \
                                 f"pull mismatch dim={dim} step={step}: {(got-ref).abs().max()}"
@@ -96,6 +107,8 @@ def main():
                     assert found.all()
                     if deterministic:
                         assert torch.equal(R, ref), f"table differs from the oracle, {opt}: {(R-ref).abs().max()}"
+                    elif wire16:
+                        assert mostly_close(R, ref, 1e-2, 1e-3, 1e-2), f"table mismatch (bf16 wire) {opt}: {(R-ref).abs().max()}"
                     else:
                         assert mostly_close(R, ref, 2e-3, 1e-4, 4e-3 if opt == "adam" else 1e-4), f"table mismatch {opt}: {(R-ref).abs().max()}"
                 dist.barrier()
