@@ -558,6 +558,7 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_push_kernel(c
 
     __shared__ unsigned s_pre[kMaxWorld + 1];   // shipment prefix (Q2)
     __shared__ unsigned s_in[kMaxWorld + 1];    // received-entry prefix (Q0 / Q3)
+    __shared__ unsigned s_nheads;               // chain heads this CTA found in its stripe (world > 1)
     if (threadIdx.x == 0) {
         unsigned acc = 0;
         for (int r = 0; r < W; ++r) {
@@ -762,6 +763,57 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_push_kernel(c
             if (threadIdx.x < (unsigned)W && (int)threadIdx.x != me)
                 st_release_sys(&a.peer[threadIdx.x].grad_flag[me], epoch);
         }
+        // While the peers' gradient rows are on their way: find the chain heads of this CTA's stripe of the received
+        // entries and write out every head's chain in rank order, one THREAD per entry. The walk is a string of
+        // dependent loads (slot, head test, up to world - 1 links); done here it runs thousands at a time, done by
+        // the lane groups of the update loop below it was the longer part of that loop from two ranks on.
+        {
+            if (threadIdx.x == 0) s_nheads = 0;
+            __syncthreads();
+            const unsigned per_e = (total_in + nblocks - 1) / nblocks;
+            const unsigned e_lo = min(total_in, blockIdx.x * per_e), e_hi = min(total_in, e_lo + per_e);
+            for (unsigned e = e_lo + threadIdx.x; e < e_hi; e += kThreads) {
+                int r = 0;
+                while (e >= s_in[r + 1]) ++r;
+                const unsigned id = (unsigned)r * C + (e - s_in[r]);
+                const unsigned slot = a.res_slot[id];
+                if (slot == kNoSlot) {
+                    set_soft_status(a.ctl, kStOom, W_NOROW);
+                    continue;
+                }
+                if (*((volatile unsigned*)&T.slots[slot].aux) != id) continue;  // not the head of its chain
+                unsigned ids[kMaxWorld];
+                ids[0] = id;
+                unsigned cur = id;
+#pragma unroll
+                for (int k = 1; k < kMaxWorld; ++k) {
+                    if (cur != kNoRow) cur = a.ent_next[cur];
+                    ids[k] = cur;
+                }
+                // ascending entry id = ascending source rank (sorting network for 8 keys; kNoRow sorts last)
+#define PSB_CSWAP(i, j)                                          \
+    do {                                                         \
+        const unsigned lo_ = min(ids[i], ids[j]), hi_ = max(ids[i], ids[j]); \
+        ids[i] = lo_;                                            \
+        ids[j] = hi_;                                            \
+    } while (0)
+                PSB_CSWAP(0, 1); PSB_CSWAP(2, 3); PSB_CSWAP(4, 5); PSB_CSWAP(6, 7);
+                PSB_CSWAP(0, 2); PSB_CSWAP(1, 3); PSB_CSWAP(4, 6); PSB_CSWAP(5, 7);
+                PSB_CSWAP(1, 2); PSB_CSWAP(5, 6); PSB_CSWAP(0, 4); PSB_CSWAP(3, 7);
+                PSB_CSWAP(1, 5); PSB_CSWAP(2, 6);
+                PSB_CSWAP(1, 4); PSB_CSWAP(3, 6);
+                PSB_CSWAP(2, 4); PSB_CSWAP(3, 5);
+                PSB_CSWAP(3, 4);
+#undef PSB_CSWAP
+                const unsigned pos = atomicAdd(&s_nheads, 1u);
+                a.head_ids[e_lo + pos] = id;
+#pragma unroll
+                for (int k = 0; k < kMaxWorld; ++k)
+                    if (k < W) a.chain_buf[(size_t)id * W + k] = ids[k];
+                T.slots[slot].aux = kNoRow;   // the chain is consumed: the slot is clean for the next call
+            }
+            __syncthreads();
+        }
         if (!wait_all_flags(mine.grad_flag, epoch, a, W_GRADFLAG)) return;
     }
 
@@ -800,61 +852,48 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_push_kernel(c
         *r_out = r;
         return (unsigned)r * C + (e - s_in[r]);
     };
-    if (group < total_in) {
-        int r0;
-        const unsigned id0 = entry_id(group, &r0);
-        row_nx = ent_row[id0];
-        if (W == 1) u_nx = a.send_ret[id0];
-    }
-    for (unsigned e = group; e < total_in; e += ngroups) {
-        int r;
-        const unsigned id = entry_id(e, &r);
-        const unsigned row = row_nx, u_own = u_nx;
-        if (e + ngroups < total_in) {
-            int rn;
-            const unsigned idn = entry_id(e + ngroups, &rn);
-            row_nx = ent_row[idn];
-            if (W == 1) u_nx = a.send_ret[idn];
+    // Work list: every received entry (one rank), or the chain heads this CTA found in its stripe (several ranks).
+    const unsigned lgroup3 = threadIdx.x / lanes, lgroups3 = kThreads / lanes;
+    const unsigned per_e3 = (total_in + nblocks - 1) / nblocks;
+    const unsigned h_lo = min(total_in, blockIdx.x * per_e3);
+    const unsigned n_work = (W == 1) ? total_in : s_nheads;
+    const unsigned w_first = (W == 1) ? group : lgroup3, w_step = (W == 1) ? ngroups : lgroups3;
+    unsigned id_nx = kNoRow;
+    if (w_first < n_work) {
+        if (W == 1) {
+            int r0;
+            id_nx = entry_id(w_first, &r0);
+            u_nx = a.send_ret[id_nx];
+        } else {
+            id_nx = a.head_ids[h_lo + w_first];
         }
-        unsigned slot = kNoSlot;
+        row_nx = ent_row[id_nx];
+    }
+    for (unsigned e = w_first; e < n_work; e += w_step) {
+        const unsigned id = id_nx;
+        const int r = (int)(id / C);
+        const unsigned row = row_nx, u_own = u_nx;
+        if (e + w_step < n_work) {
+            if (W == 1) {
+                int rn;
+                id_nx = entry_id(e + w_step, &rn);
+                u_nx = a.send_ret[id_nx];
+            } else {
+                id_nx = a.head_ids[h_lo + e + w_step];
+            }
+            row_nx = ent_row[id_nx];
+        }
         unsigned ids[kMaxWorld];
         ids[0] = id;
 #pragma unroll
         for (int k = 1; k < kMaxWorld; ++k) ids[k] = kNoRow;
         if (W > 1) {
-            slot = a.res_slot[id];
-            if (slot == kNoSlot) {
-                if (lane == 0) set_soft_status(a.ctl, kStOom, W_NOROW);
-                continue;
-            }
-            if (*((volatile unsigned*)&T.slots[slot].aux) != id) continue;  // not the head of its chain
-            unsigned cur = id;
 #pragma unroll
-            for (int k = 1; k < kMaxWorld; ++k) {
-                if (cur != kNoRow) cur = a.ent_next[cur];
-                ids[k] = cur;
-            }
-            // ascending entry id = ascending source rank (sorting network for 8 keys; kNoRow sorts last)
-#define PSB_CSWAP(i, j)                                          \
-    do {                                                         \
-        const unsigned lo_ = min(ids[i], ids[j]), hi_ = max(ids[i], ids[j]); \
-        ids[i] = lo_;                                            \
-        ids[j] = hi_;                                            \
-    } while (0)
-            PSB_CSWAP(0, 1); PSB_CSWAP(2, 3); PSB_CSWAP(4, 5); PSB_CSWAP(6, 7);
-            PSB_CSWAP(0, 2); PSB_CSWAP(1, 3); PSB_CSWAP(4, 6); PSB_CSWAP(5, 7);
-            PSB_CSWAP(1, 2); PSB_CSWAP(5, 6); PSB_CSWAP(0, 4); PSB_CSWAP(3, 7);
-            PSB_CSWAP(1, 5); PSB_CSWAP(2, 6);
-            PSB_CSWAP(1, 4); PSB_CSWAP(3, 6);
-            PSB_CSWAP(2, 4); PSB_CSWAP(3, 5);
-            PSB_CSWAP(3, 4);
-#undef PSB_CSWAP
+            for (int k = 0; k < kMaxWorld; ++k)
+                if (k < W) ids[k] = a.chain_buf[(size_t)id * W + k];
         }
         if (row == kNoRow) {
-            if (lane == 0) {
-                set_soft_status(a.ctl, kStOom, W_NOROW);
-                if (W > 1) T.slots[slot].aux = kNoRow;
-            }
+            if (lane == 0) set_soft_status(a.ctl, kStOom, W_NOROW);
             continue;
         }
         // at most one entry of a chain is this rank's own (its gradient sits in `agg`, the others in the mailbox)
@@ -925,7 +964,6 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_push_kernel(c
             }
         }
         if (T.dirty_bits != nullptr && lane == 0) atomicOr(&T.dirty_bits[row >> 5], 1u << (row & 31u));
-        if (W > 1 && lane == 0) T.slots[slot].aux = kNoRow;
     }
 
     if (W > 1) {

@@ -62,6 +62,8 @@ struct FusedArgs {
     unsigned* res_slot;    // [world][C] owner side: table slot of each received key
     unsigned* new_list;    // [world*C] owner side: slots whose rows were attached by this call
     unsigned* ent_next;    // [world*C] owner side, push: next entry (other source rank) that holds the same table row
+    unsigned* head_ids;    // [world*C] push, world > 1: chain heads found by each CTA in its stripe of the entries
+    unsigned* chain_buf;   // [world*C][world] push, world > 1: entry ids of a head's chain in ascending (= rank) order
     unsigned* counters;    // [2][16] per epoch parity: 0 n_uniq, 1 n_new, 4.. send_cnt[world]
     unsigned* in_cnt;      // [2][kMaxWorld] per epoch parity: keys received from each source rank
     KernelCtl* ctl;       // control block of this kernel family (holds the call epoch)

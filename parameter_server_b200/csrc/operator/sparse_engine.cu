@@ -91,6 +91,8 @@ SparseEngine::SparseEngine(GpuTable* table, const SparseEngineConfig& cfg) : tab
     const size_t o_skeys = carve((size_t)W * C_ * 8), o_sret = carve((size_t)W * C_ * 4);
     const size_t o_agg = carve(N * dim * 4);
     const size_t o_res = carve((size_t)W * C_ * 4), o_new = carve((size_t)W * C_ * 4), o_next = carve((size_t)W * C_ * 4);
+    // push, several ranks: per-CTA lists of chain heads and the sorted chain of every head
+    const size_t o_heads = carve(W > 1 ? (size_t)W * C_ * 4 : 0), o_chain = carve(W > 1 ? (size_t)W * C_ * (size_t)W * 4 : 0);
     const size_t o_rslot = carve(cfg_.replicate ? (size_t)W * C_ * 4 : 0), o_rnew = carve(cfg_.replicate ? (size_t)W * C_ * 4 : 0);
     const size_t o_cnt = carve(2 * 16 * 4), o_in = carve(2 * kMaxWorld * 4);
     const size_t o_ctl1 = carve(sizeof(KernelCtl)), o_ctl2 = carve(sizeof(KernelCtl));
@@ -111,6 +113,8 @@ SparseEngine::SparseEngine(GpuTable* table, const SparseEngineConfig& cfg) : tab
     res_slot_ = (unsigned*)(scratch_ + o_res);
     new_list_ = (unsigned*)(scratch_ + o_new);
     ent_next_ = (unsigned*)(scratch_ + o_next);
+    head_ids_ = (unsigned*)(scratch_ + o_heads);
+    chain_buf_ = (unsigned*)(scratch_ + o_chain);
     rep_slot_ = (unsigned*)(scratch_ + o_rslot);
     rep_new_ = (unsigned*)(scratch_ + o_rnew);
     counters_ = (unsigned*)(scratch_ + o_cnt);
@@ -238,6 +242,8 @@ void SparseEngine::fill_common(FusedArgs& a) const {
     a.res_slot = res_slot_;
     a.new_list = new_list_;
     a.ent_next = ent_next_;
+    a.head_ids = head_ids_;
+    a.chain_buf = chain_buf_;
     a.counters = counters_;
     a.in_cnt = in_cnt_;
     a.prof = profile_ ? prof_ : nullptr;

@@ -117,6 +117,8 @@ private:
     int pull_blocks_ = 0, push_blocks_ = 0;          // grid of the next launches
     int max_pull_blocks_ = 0, max_push_blocks_ = 0;  // full residency on the idle GPU (256-thread CTAs)
     int max_pull_wide_ = 0, max_push_wide_ = 0;      // the same for the 1024-thread shape (one CTA per SM)
+    unsigned* head_ids_ = nullptr;
+    unsigned* chain_buf_ = nullptr;
     bool pull_wide_ = false, push_wide_ = false;
     bool grad_wire_bf16_ = false;
     int num_sms_ = 0;
