@@ -366,13 +366,16 @@ __device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
     return v;
 }
 
-// Gather role of the all-gather + GEMM kernel (one CTA): copies the remote n-tile row blocks assigned to
-// this CTA from the owners' memory into the local copy of B with bulk async copies staged through shared
-// memory (4 x 32 KB in flight), then publishes the n-tile's flag. Only thread 0 works.
+// All-gather role of a CTA: copy the row blocks of B that other ranks own and that are assigned to this CTA from the
+// owners' memory into the local copy of B with bulk async copies staged through shared memory, and publish each
+// n-tile's flag. One thread drives a ring of kDepth staging buffers: the load of piece j + kDepth - 1 is issued
+// before the store of piece j, a buffer is reloaded as soon as the store that used it has READ it
+// (`wait_group.read`), and nothing waits for a store to complete except the flag of an n-tile. So kDepth - 1 loads
+// are always in flight over NVLink while the stores drain into local memory (one round trip per piece otherwise).
 template <int BN>
 __device__ void gather_rows(const GemmGather& ag, int K, uint8_t* smem, uint64_t* bars, unsigned* err_flag,
                             unsigned long long limit_ns, int N) {
-    constexpr int kDepth = 4;
+    constexpr int kDepth = 6;
     constexpr uint32_t kPiece = 32768;
     if (threadIdx.x != 0) return;
     for (int d = 0; d < kDepth; ++d) mbar_init(&bars[d], 1);
@@ -380,49 +383,64 @@ __device__ void gather_rows(const GemmGather& ag, int K, uint8_t* smem, uint64_t
     const int n_tiles = (N + BN - 1) / BN;
     const int tpr = ag.rows_per_rank / BN;
     const size_t tile_bytes = (size_t)BN * K * 2;
-    uint32_t phase[kDepth] = {0, 0, 0, 0};  // parity of the next completion of each staging barrier
-    int order = 0;
-    // remote n-tiles in the order the GEMM CTAs will ask for them
-    for (int j = tpr; j < n_tiles; ++j, ++order) {
-        if (order % ag.gather_ctas != (int)blockIdx.x) continue;
-        const int nt = (j + ag.rank * tpr) % n_tiles;
-        const int owner = nt / tpr;
-        const uint8_t* src = (const uint8_t*)ag.peer_b[owner] + (size_t)nt * tile_bytes;
-        uint8_t* dst = (uint8_t*)ag.local_b + (size_t)nt * tile_bytes;
-        for (size_t off = 0; off < tile_bytes; off += (size_t)kDepth * kPiece) {
-            int issued = 0;
-            for (int d = 0; d < kDepth; ++d) {
-                const size_t o = off + (size_t)d * kPiece;
-                if (o >= tile_bytes) break;
-                const uint32_t bytes = (uint32_t)min((size_t)kPiece, tile_bytes - o);
-                mbar_expect_tx(&bars[d], bytes);
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                 smem_u32(smem + (size_t)d * kPiece)),
-                             "l"(src + o), "r"(bytes), "r"(smem_u32(&bars[d]))
-                             : "memory");
-                ++issued;
-            }
-            for (int d = 0; d < issued; ++d) {
-                const size_t o = off + (size_t)d * kPiece;
-                const uint32_t bytes = (uint32_t)min((size_t)kPiece, tile_bytes - o);
-                if (!mbar_wait(&bars[d], phase[d], limit_ns)) {
-                    atomicCAS(err_flag, 0u, 6u);
-                    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-                    return;
-                }
-                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst + o),
-                             "r"(smem_u32(smem + (size_t)d * kPiece)), "r"(bytes)
-                             : "memory");
-                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                phase[d] ^= 1u;
-            }
-            // the staging buffers are reused by the next round: their stores must have read them
-            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    const uint32_t pieces_per_tile = (uint32_t)((tile_bytes + kPiece - 1) / kPiece);
+    // this CTA's n-tiles, in the order the GEMM CTAs will ask for them
+    int my_tiles = 0;
+    for (int j = tpr, order = 0; j < n_tiles; ++j, ++order)
+        if (order % ag.gather_ctas == (int)blockIdx.x) ++my_tiles;
+    const uint32_t total = (uint32_t)my_tiles * pieces_per_tile;
+    auto tile_of = [&](uint32_t t) -> int {   // t-th tile of this CTA -> n-tile index
+        const int j = tpr + (int)blockIdx.x + (int)t * ag.gather_ctas;
+        return (j + ag.rank * tpr) % n_tiles;
+    };
+    auto issue_load = [&](uint32_t q) {
+        const uint32_t t = q / pieces_per_tile, i = q % pieces_per_tile;
+        const int nt = tile_of(t);
+        const size_t o = (size_t)i * kPiece;
+        const uint32_t bytes = (uint32_t)min((size_t)kPiece, tile_bytes - o);
+        const uint8_t* src = (const uint8_t*)ag.peer_b[nt / tpr] + (size_t)nt * tile_bytes + o;
+        const int d = (int)(q % kDepth);
+        mbar_expect_tx(&bars[d], bytes);
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                         smem_u32(smem + (size_t)d * kPiece)),
+                     "l"(src), "r"(bytes), "r"(smem_u32(&bars[d]))
+                     : "memory");
+    };
+    // prologue: kDepth - 1 loads in flight
+    for (uint32_t q = 0; q < total && q < (uint32_t)(kDepth - 1); ++q) issue_load(q);
+    for (uint32_t q = 0; q < total; ++q) {
+        const int d = (int)(q % kDepth);
+        // next load: its buffer was last used by the store of piece q - 1, committed one group ago
+        const uint32_t qn = q + (uint32_t)(kDepth - 1);
+        if (qn < total) {
+            if (q > 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            issue_load(qn);
         }
-        asm volatile("fence.proxy.async.global;" ::: "memory");
-        __threadfence();
-        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ag.ready + nt), "r"(ag.epoch) : "memory");
+        if (!mbar_wait(&bars[d], (q / kDepth) & 1u, limit_ns)) {
+            atomicCAS(err_flag, 0u, 6u);
+            // the loads still in flight land in this CTA's shared memory: let them finish (bounded) before leaving
+            for (uint32_t w = q + 1; w < total && w <= qn; ++w) mbar_wait(&bars[w % kDepth], (w / kDepth) & 1u, limit_ns);
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            return;
+        }
+        const uint32_t t = q / pieces_per_tile, i = q % pieces_per_tile;
+        const int nt = tile_of(t);
+        const size_t o = (size_t)i * kPiece;
+        const uint32_t bytes = (uint32_t)min((size_t)kPiece, tile_bytes - o);
+        uint8_t* dst = (uint8_t*)ag.local_b + (size_t)nt * tile_bytes + o;
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+                     "r"(smem_u32(smem + (size_t)d * kPiece)), "r"(bytes)
+                     : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        if (i + 1 == pieces_per_tile) {
+            // the n-tile is complete once its stores are: publish its flag (loads of the next tile stay in flight)
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            __threadfence();
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ag.ready + nt), "r"(ag.epoch) : "memory");
+        }
     }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
 // One launch can carry several independent GEMMs (a "group": e.g. the weight gradients of every layer of an
