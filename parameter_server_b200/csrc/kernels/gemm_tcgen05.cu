@@ -43,8 +43,13 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kEpilogueWarps = 8;
-constexpr int kPublisherWarp = 2 + kEpilogueWarps;   // chain mode: bumps the completion counters for the epilogue warps
-constexpr int kThreads = 64 + 32 * kEpilogueWarps + 32;
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-9 epilogue, warp 10 publisher (chain mode:
+// bumps the completion counters for the epilogue warps). Moving registers from the single-thread roles to the
+// epilogue warps (setmaxnreg) was tried and dropped: the producer and MMA code paths need about as many registers
+// as the epilogue, and with 168 for everybody nothing spills.
+constexpr int kFirstEpilogueWarp = 2;
+constexpr int kPublisherWarp = kFirstEpilogueWarp + kEpilogueWarps;
+constexpr int kThreads = 32 * (kPublisherWarp + 1);
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -263,6 +268,28 @@ __device__ __forceinline__ void post_publish(uint32_t* box, uint32_t req, unsign
 }
 
 
+// ReLU-backward mask of one piece read straight from global memory (rows whose mask was not prefetched).
+__device__ __noinline__ void apply_mask_slow(const GemmEpilogue& ep, float* f, int row, int col0, int N) {
+    const bool full = (col0 + 32 <= N);
+    {
+        const __nv_bfloat16* mp = ep.mask + (size_t)row * ep.ldmask + col0;
+        if (full && (ep.ldmask % 8 == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+                uint4 raw = *(const uint4*)(mp + j);
+                const __nv_bfloat16* h = (const __nv_bfloat16*)&raw;
+#pragma unroll
+                for (int t = 0; t < 8; ++t)
+                    if (!(__bfloat162float(h[t]) > 0.f)) f[j + t] = 0.f;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < N && !(__bfloat162float(mp[j]) > 0.f)) f[j] = 0.f;
+        }
+    }
+}
+
 // Epilogue of one 32-column chunk held by one thread (one output row). `bias_s`: the chunk's 32 bias values in
 // shared memory (every lane reads the same words: a broadcast), or nullptr.
 // mpre != nullptr: the chunk's 32 mask values were loaded ahead of time (4 x uint4, this lane's row).
@@ -291,26 +318,43 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpilogue& ep, float* f,
         return;
     }
     if (ep.mask != nullptr && row_valid) {
-        const __nv_bfloat16* mp = ep.mask + (size_t)row * ep.ldmask + col0;
-        if (full && (ep.ldmask % 8 == 0)) {
+        // not prefetched (partial piece or unaligned mask): the slow path, kept out of the loop's code
+        float tmp[32];
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-                uint4 raw = *(const uint4*)(mp + j);
-                const __nv_bfloat16* h = (const __nv_bfloat16*)&raw;
+        for (int j = 0; j < 32; ++j) tmp[j] = f[j];
+        apply_mask_slow(ep, tmp, row, col0, N);
 #pragma unroll
-                for (int t = 0; t < 8; ++t)
-                    if (!(__bfloat162float(h[t]) > 0.f)) f[j + t] = 0.f;
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-                if (col0 + j < N && !(__bfloat162float(mp[j]) > 0.f)) f[j] = 0.f;
-        }
+        for (int j = 0; j < 32; ++j) f[j] = tmp[j];
     }
 }
 
-// The thread-per-row output path (d_mode 0).
-__device__ __forceinline__ void store_chunk_rows(const GemmEpilogue& ep, const float* f, int row, int col0, int N) {
+// fp32 output of one 32-column piece: two [32 rows][16 cols] halves through the warp's staging piece and the TMA unit
+// (store, or reduce-add for split-K partial sums and `accumulate`). Called by the whole warp.
+__device__ __noinline__ void store_piece_f32(const CUtensorMap* map_d, int d_mode, uint8_t* stage, int lane, const float* f,
+                                             int col0, int row0, int N) {
+    uint8_t* my_stage = stage + lane * 64;
+#pragma unroll 1
+    for (int hcol = 0; hcol < 32; hcol += 16) {
+        if (col0 + hcol >= N) break;   // warp-uniform
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+            *(float4*)(my_stage + j * 4) = make_float4(f[hcol + j], f[hcol + j + 1], f[hcol + j + 2], f[hcol + j + 3]);
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            if (d_mode == 2) tma_reduce_add_2d(map_d, stage, col0 + hcol, row0);
+            else tma_store_2d(map_d, stage, col0 + hcol, row0);
+            bulk_commit();
+            if (hcol == 0) bulk_wait_read0();   // the second half follows at once
+        }
+        if (hcol == 0) __syncwarp();
+    }
+}
+
+// The thread-per-row output path (d_mode 0). Out of line, like every rarely taken path of the epilogue: the loop
+// over a tile's pieces must stay small enough for the instruction cache close to the schedulers; with all paths
+// inlined a piece cost about 8 cycles per instruction.
+__device__ __noinline__ void store_chunk_rows(const GemmEpilogue& ep, const float* f, int row, int col0, int N) {
     const bool full = (col0 + 32 <= N);
     if (ep.out_f32 != nullptr) {
         float* op = ep.out_f32 + (size_t)row * ep.ldd + col0;
@@ -471,6 +515,7 @@ struct GemmProblemSet {
     // the TMA store, 6 last piece handed to the TMA store, 7 unit index, 20 / 21 the SM's cycle counter at 3 and 4 (their ratio to the timer gives the SM clock); inside the first piece:
     // 15 bias / activation / mask applied, 16 piece written to shared memory.
     unsigned long long* trace;
+    int epi_skip;   // diagnosis only (PSB_GEMM_EPI_SKIP): 1 = no bias / activation / mask, 2 = no staging and no stores, 4 = no global stores
     int count;
     // Chain: problem i + 1 reads the output of problem i as its A operand (the layers of an MLP, forward or dgrad).
     // done[i * kMaxChainMTiles + m] counts the epilogue warps that have stored their part of an n-tile of row block m
@@ -802,7 +847,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
         }
     } else {
         // ------------------------------ epilogue ----------------------------------
-        const int ew = warp - 2;             // 0 .. kEpilogueWarps-1
+        const int ew = warp - kFirstEpilogueWarp;   // 0 .. kEpilogueWarps-1
         const int q = warp & 3;              // TMEM lane quarter this warp may read
         const int half = ew >> 2;            // which half of the tile's columns this warp drains
         const int etid = ew * 32 + lane;     // 0 .. 255
@@ -864,18 +909,20 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
             const bool tr = ps.trace != nullptr && cta == 0 && leader && tslot < 8 && ew == 0 && lane == 0;
             if (tr) ps.trace[tslot * 32 + 5] = gtimer();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)BN + (uint32_t)cbase;
-            uint32_t v[32];
-            if (tile_n + cbase < N) tmem_ld32_issue(taddr, v);
+            // One register buffer for the accumulator pieces and ONE copy of the loop body: the load of piece c + 1 is
+            // issued once the values of piece c are packed. (Two buffers with the load issued right after the wait
+            // hide the TMEM latency, but need two copies of the body, and the loop is bound by instruction fetch:
+            // 74.7 instead of 69.6 us for the top forward chain.)
+            uint32_t va[32];
+            if (tile_n + cbase < N) tmem_ld32_issue(taddr, va);
             const int d_mode = ps.d_mode[w.p];
             const CUtensorMap* map_d = &ps.map_d[w.p];
             uint8_t* my_stage = stage_out + ew * 2048 + lane * 64;   // this lane's row of the warp's staging piece
             const int row0 = tile_m + q * 32;
-            // not unrolled: the body is long, and four copies of it per output mode cost more in instruction fetch
-            // than the loop saves
-#pragma unroll 1
-            for (int c = 0; c < kChunks; ++c) {
+            // one piece: returns false when the tile has no more columns
+            auto piece = [&](uint32_t* v, const int c) -> bool {
                 const int col0 = tile_n + cbase + c * 32;
-                if (col0 >= N) break;  // warp-uniform
+                if (col0 >= N) return false;  // warp-uniform
                 const bool more = c + 1 < kChunks && col0 + 32 < N;
                 tmem_wait_ld(v);
                 if (tr && c == 0) ps.trace[tslot * 32 + 9] = gtimer();
@@ -885,12 +932,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                 if (d_mode == 0) {
                     if (row < M) {
                         epilogue_chunk(ep, f, row, col0, N, has_bias ? bs + cbase + c * 32 : nullptr, true);
-                        store_chunk_rows(ep, f, row, col0, N);
+                        float tmp[32];   // a copy: the values of the common path must not live in local memory
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) tmp[j] = f[j];
+                        store_chunk_rows(ep, tmp, row, col0, N);
                     }
                     if (more) tmem_ld32_issue(taddr + (uint32_t)(c + 1) * 32u, v);
-                    continue;
+                    return true;
                 }
-                epilogue_chunk(ep, f, row, col0, N, has_bias ? bs + cbase + c * 32 : nullptr, row < M, mhave ? mreg : nullptr);
+                if (!(ps.epi_skip & 1))
+                    epilogue_chunk(ep, f, row, col0, N, has_bias ? bs + cbase + c * 32 : nullptr, row < M, mhave ? mreg : nullptr);
                 mhave = false;
                 if (mask_fast && c + 1 < kChunks && col0 + 64 <= N) {
 #pragma unroll
@@ -903,7 +954,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                     // instruction writes whole 64-byte row segments (8 rows per instruction) instead of 16 bytes
                     // in each of 32 rows. Lane l writes row l; the 16-byte column blocks of a row are XOR-swizzled
                     // by (row / 2) % 4, which makes both the row-wise writes and the 8-row reads conflict-free.
-                    // Once the values are packed their registers are free: the next piece leaves TMEM meanwhile.
                     uint4 raw[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -913,7 +963,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                         h[2] = __floats2bfloat162_rn(f[8 * j + 4], f[8 * j + 5]);
                         h[3] = __floats2bfloat162_rn(f[8 * j + 6], f[8 * j + 7]);
                     }
-                    if (more) tmem_ld32_issue(taddr + (uint32_t)(c + 1) * 32u, v);
+                    if (more) tmem_ld32_issue(taddr + (uint32_t)(c + 1) * 32u, v);   // the values are packed: v is free
+                    if (ps.epi_skip & 2) {
+                        if (raw[0].x == 0x7fc07fc1u && raw[3].w == 0x12345678u) atomicAdd(err_flag, 0u);   // keeps the values alive
+                        return true;
+                    }
                     __syncwarp();   // the reads of the previous piece are done
                     {
                         const int sw = (lane >> 1) & 3;
@@ -930,7 +984,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                         for (int i = 0; i < 4; ++i) {
                             const int r = i * 8 + (lane >> 2);
                             const uint4 d = *(const uint4*)(stage_out + ew * 2048 + r * 64 + ((cb ^ ((r >> 1) & 3)) << 4));
-                            if (row0 + r < M) {
+                            if (row0 + r < M && !(ps.epi_skip & 4)) {
                                 __nv_bfloat16* op = orow + (size_t)r * ep.ldd;
                                 if (gcol + 8 <= N) {
                                     *(uint4*)op = d;
@@ -944,31 +998,43 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                     }
                     if (tr && c == 0) ps.trace[tslot * 32 + 10] = gtimer();
                 } else {
-                    // fp32: two [32 rows][16 cols] pieces per chunk
+                    // fp32 (weight gradients, split-K partial sums): out of line, once per long K loop
                     if (store_in_flight) {
                         if (lane == 0) bulk_wait_read0();
                         __syncwarp();
                     }
+                    if constexpr (AMN && BMN) {
+                        // the weight-gradient variant of the kernel: this IS its output path, kept in line
 #pragma unroll
-                    for (int hcol = 0; hcol < 32; hcol += 16) {
-                        if (col0 + hcol >= N) break;   // warp-uniform
+                        for (int hcol = 0; hcol < 32; hcol += 16) {
+                            if (col0 + hcol >= N) break;   // warp-uniform
 #pragma unroll
-                        for (int j = 0; j < 16; j += 4)
-                            *(float4*)(my_stage + j * 4) = make_float4(f[hcol + j], f[hcol + j + 1], f[hcol + j + 2], f[hcol + j + 3]);
-                        fence_async_smem();
-                        __syncwarp();
-                        if (lane == 0) {
-                            if (d_mode == 2) tma_reduce_add_2d(map_d, stage_out + ew * 2048, col0 + hcol, row0);
-                            else tma_store_2d(map_d, stage_out + ew * 2048, col0 + hcol, row0);
-                            bulk_commit();
-                            if (hcol == 0) bulk_wait_read0();   // the second half follows at once
+                            for (int j = 0; j < 16; j += 4)
+                                *(float4*)(my_stage + j * 4) = make_float4(f[hcol + j], f[hcol + j + 1], f[hcol + j + 2], f[hcol + j + 3]);
+                            fence_async_smem();
+                            __syncwarp();
+                            if (lane == 0) {
+                                if (d_mode == 2) tma_reduce_add_2d(map_d, stage_out + ew * 2048, col0 + hcol, row0);
+                                else tma_store_2d(map_d, stage_out + ew * 2048, col0 + hcol, row0);
+                                bulk_commit();
+                                if (hcol == 0) bulk_wait_read0();   // the second half follows at once
+                            }
+                            if (hcol == 0) __syncwarp();
                         }
-                        if (hcol == 0) __syncwarp();
+                    } else {
+                        float tmp[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) tmp[j] = f[j];
+                        store_piece_f32(map_d, d_mode, stage_out + ew * 2048, lane, tmp, col0, row0, N);
                     }
                     store_in_flight = true;
                     if (more) tmem_ld32_issue(taddr + (uint32_t)(c + 1) * 32u, v);
                 }
-            }
+                return true;
+            };
+#pragma unroll 1
+            for (int c = 0; c < kChunks; ++c)
+                if (!piece(va, c)) break;
             if (tr) ps.trace[tslot * 32 + 6] = gtimer();
             // this warp is done reading the buffer: hand it back to the MMA warp
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -1188,6 +1254,13 @@ cudaError_t dispatch(int BN, bool pair, bool a_mn, bool b_mn, const GemmProblemS
 
 // CTA pairs are used whenever a problem has more than one 128-row block (and never with the gather role, whose
 // copy CTAs are not part of a pair). PSB_GEMM_PAIR=0 forces the 1-CTA kernel.
+int epi_skip_env() {
+    static const int v = [] {
+        const char* e = std::getenv("PSB_GEMM_EPI_SKIP");
+        return e != nullptr ? std::atoi(e) : 0;
+    }();
+    return v;
+}
 int g_gemm_pair = 1;
 bool pair_enabled() {
     static const bool on = [] {
@@ -1259,6 +1332,7 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& ep
     ps.chain = 0;
     ps.done = nullptr;
     ps.trace = g_gemm_trace;
+    ps.epi_skip = epi_skip_env();
     const bool pair = pair_enabled() && !ag.enabled && M > BM;
     int rc = add_problem(&ps, 0, BN, pair, A, B, ep, M, N, K);
     if (rc != 0) return rc;
@@ -1288,6 +1362,7 @@ int gemm_bf16_grouped(const GemmOperand* A, const GemmOperand* B, const GemmEpil
     ps.chain = chain_done != nullptr ? 1 : 0;
     ps.done = chain_done;
     ps.trace = g_gemm_trace;
+    ps.epi_skip = epi_skip_env();
     if (ps.chain) {
         // layer i + 1 consumes the bf16 output of layer i: same rows, K of the consumer = N of the producer
         for (int i = 0; i < count; ++i) {
