@@ -293,8 +293,13 @@ __device__ __noinline__ void apply_mask_slow(const GemmEpilogue& ep, float* f, i
 // Epilogue of one 32-column chunk held by one thread (one output row). `bias_s`: the chunk's 32 bias values in
 // shared memory (every lane reads the same words: a broadcast), or nullptr.
 // mpre != nullptr: the chunk's 32 mask values were loaded ahead of time (4 x uint4, this lane's row).
+// LEAN_FWD / LEAN_BWD: the lean launches of a forward layer (bias and activation, never a mask) and of a dgrad layer
+// (a prefetched mask, never bias or activation) carry only their own code.
+template <bool LEAN_FWD = false, bool LEAN_BWD = false>
 __device__ __forceinline__ void epilogue_chunk(const GemmEpilogue& ep, float* f, int row, int col0, int N,
                                                const float* bias_s, bool row_valid, const uint4* mpre = nullptr) {
+    constexpr bool LEAN = LEAN_FWD || LEAN_BWD;
+    if constexpr (!LEAN_BWD) {
     if (bias_s != nullptr) {
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
@@ -306,7 +311,8 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpilogue& ep, float* f,
 #pragma unroll
         for (int j = 0; j < 32; ++j) f[j] = fmaxf(f[j], 0.f);
     }
-    const bool full = (col0 + 32 <= N);
+    }
+    if constexpr (LEAN_FWD) return;
     if (mpre != nullptr) {
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
@@ -317,6 +323,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpilogue& ep, float* f,
         }
         return;
     }
+    if constexpr (LEAN) return;   // a mask of a lean launch is always prefetched
     if (ep.mask != nullptr && row_valid) {
         // not prefetched (partial piece or unaligned mask): the slow path, kept out of the loop's code
         float tmp[32];
@@ -572,7 +579,10 @@ __device__ __forceinline__ WorkUnit decode_unit(const GemmProblemSet& ps, int u,
 // AMN / BMN: operand is MN-major. The box of an MN-major operand is [64 k-rows][64 mn-elements].
 // PAIR: launched as clusters of two CTAs that share every work unit (see the CTA-pair helpers above); the gather
 // role exists only without it.
-template <int BN, bool AMN, bool BMN, bool PAIR>
+// LEAN: every problem of the launch writes bf16 through the staged path, N is a multiple of 32 and a mask (if any) has
+// 16-byte aligned rows: the epilogue loop is compiled without the other output paths, the partial-piece code, the
+// tracing stamps and the diagnostic switch. The loop is bound by instruction fetch, so less code is less time.
+template <int BN, bool AMN, bool BMN, bool PAIR, bool LEAN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* err_flag, unsigned long long limit_ns,
                          const GemmGather ag) {
@@ -865,7 +875,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
             // The bias of the tile's columns, staged in shared memory (double-buffered with the accumulator). It was
             // fetched during the tile before this one; only the first tile of a CTA waits for the load here.
             float* bs = bias_smem + buf * 256;
-            const bool has_bias = ep.bias != nullptr || ep.bias_bf16 != nullptr;
+            const bool has_bias = !(LEAN && BMN) && (ep.bias != nullptr || ep.bias_bf16 != nullptr);
             if (has_bias && etid < BN && bias_unit != unit) {
                 const int col = tile_n + etid;
                 float v = 0.f;
@@ -877,7 +887,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
             // piece waits for memory.
             const int row = tile_m + q * 32 + lane;
             const int cbase = half * (BN / 2);
-            const bool mask_fast = ep.mask != nullptr && (ep.ldmask % 8 == 0) && row < M;
+            const bool mask_fast = !(LEAN && !BMN) && ep.mask != nullptr && (ep.ldmask % 8 == 0) && row < M;
             const __nv_bfloat16* mrow = mask_fast ? ep.mask + (size_t)row * ep.ldmask + tile_n + cbase : nullptr;
             uint4 mreg[4];
             bool mhave = false;
@@ -888,7 +898,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
             }
             const bool waited = mbar_wait(&tfull_bar[buf], tph, limit_ns * 4);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (ps.trace != nullptr && cta == 0 && leader && (unit - cta) / n_cta < 8 && ew == 0 && lane == 0)
+            if (!LEAN && ps.trace != nullptr && cta == 0 && leader && (unit - cta) / n_cta < 8 && ew == 0 && lane == 0)
                 ps.trace[(unit - cta) / n_cta * 32 + 8] = gtimer();
             // One barrier of the epilogue warps per tile: it publishes the staged bias and makes the decision to give
             // up uniform (a warp that timed out must not leave the others waiting at the next tile's barrier).
@@ -906,7 +916,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                 break;
             }
             const int tslot = (unit - cta) / n_cta;
-            const bool tr = ps.trace != nullptr && cta == 0 && leader && tslot < 8 && ew == 0 && lane == 0;
+            const bool tr = !LEAN && ps.trace != nullptr && cta == 0 && leader && tslot < 8 && ew == 0 && lane == 0;
             if (tr) ps.trace[tslot * 32 + 5] = gtimer();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)BN + (uint32_t)cbase;
             // One register buffer for the accumulator pieces and ONE copy of the loop body: the load of piece c + 1 is
@@ -915,7 +925,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
             // 74.7 instead of 69.6 us for the top forward chain.)
             uint32_t va[32];
             if (tile_n + cbase < N) tmem_ld32_issue(taddr, va);
-            const int d_mode = ps.d_mode[w.p];
+            const int d_mode = LEAN ? 1 : ps.d_mode[w.p];
             const CUtensorMap* map_d = &ps.map_d[w.p];
             uint8_t* my_stage = stage_out + ew * 2048 + lane * 64;   // this lane's row of the warp's staging piece
             const int row0 = tile_m + q * 32;
@@ -929,7 +939,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                 float f[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                if (d_mode == 0) {
+                if (!LEAN && d_mode == 0) {
                     if (row < M) {
                         epilogue_chunk(ep, f, row, col0, N, has_bias ? bs + cbase + c * 32 : nullptr, true);
                         float tmp[32];   // a copy: the values of the common path must not live in local memory
@@ -940,8 +950,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                     if (more) tmem_ld32_issue(taddr + (uint32_t)(c + 1) * 32u, v);
                     return true;
                 }
-                if (!(ps.epi_skip & 1))
-                    epilogue_chunk(ep, f, row, col0, N, has_bias ? bs + cbase + c * 32 : nullptr, row < M, mhave ? mreg : nullptr);
+                if (LEAN || !(ps.epi_skip & 1))
+                    epilogue_chunk<LEAN && !BMN, LEAN && BMN>(ep, f, row, col0, N, has_bias ? bs + cbase + c * 32 : nullptr, row < M,
+                                                              mhave ? mreg : nullptr);
                 mhave = false;
                 if (mask_fast && c + 1 < kChunks && col0 + 64 <= N) {
 #pragma unroll
@@ -949,7 +960,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                     mhave = true;
                 }
                 if (tr && c == 0) ps.trace[tslot * 32 + 15] = gtimer();
-                if (d_mode == 1) {
+                if (LEAN || d_mode == 1) {
                     // bf16: the warp's [32 rows][32 cols] piece goes through shared memory so that every store
                     // instruction writes whole 64-byte row segments (8 rows per instruction) instead of 16 bytes
                     // in each of 32 rows. Lane l writes row l; the 16-byte column blocks of a row are XOR-swizzled
@@ -964,7 +975,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                         h[3] = __floats2bfloat162_rn(f[8 * j + 6], f[8 * j + 7]);
                     }
                     if (more) tmem_ld32_issue(taddr + (uint32_t)(c + 1) * 32u, v);   // the values are packed: v is free
-                    if (ps.epi_skip & 2) {
+                    if (!LEAN && (ps.epi_skip & 2)) {
                         if (raw[0].x == 0x7fc07fc1u && raw[3].w == 0x12345678u) atomicAdd(err_flag, 0u);   // keeps the values alive
                         return true;
                     }
@@ -984,9 +995,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                         for (int i = 0; i < 4; ++i) {
                             const int r = i * 8 + (lane >> 2);
                             const uint4 d = *(const uint4*)(stage_out + ew * 2048 + r * 64 + ((cb ^ ((r >> 1) & 3)) << 4));
-                            if (row0 + r < M && !(ps.epi_skip & 4)) {
+                            if (row0 + r < M && (LEAN || !(ps.epi_skip & 4))) {
                                 __nv_bfloat16* op = orow + (size_t)r * ep.ldd;
-                                if (gcol + 8 <= N) {
+                                if (LEAN || gcol + 8 <= N) {
                                     *(uint4*)op = d;
                                 } else {
                                     const __nv_bfloat16* h = (const __nv_bfloat16*)&d;
@@ -997,7 +1008,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                         }
                     }
                     if (tr && c == 0) ps.trace[tslot * 32 + 10] = gtimer();
-                } else {
+                } else if constexpr (!LEAN) {
                     // fp32 (weight gradients, split-K partial sums): out of line, once per long K loop
                     if (store_in_flight) {
                         if (lane == 0) bulk_wait_read0();
@@ -1054,7 +1065,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                 if (nu < total_units) {
                     const WorkUnit nw = decode_unit<BN, PAIR>(ps, nu, ag, cr);
                     const GemmEpilogue& nep = ps.ep[nw.p];
-                    if (nw.num_kt != 0 && (nep.bias != nullptr || nep.bias_bf16 != nullptr) && etid < BN) {
+                    if (!(LEAN && BMN) && nw.num_kt != 0 && (nep.bias != nullptr || nep.bias_bf16 != nullptr) && etid < BN) {
                         const int col = nw.tile_n + etid;
                         float v = 0.f;
                         if (col < ps.N[nw.p]) v = nep.bias != nullptr ? nep.bias[col] : __bfloat162float(nep.bias_bf16[col]);
@@ -1160,10 +1171,10 @@ bool pdl_enabled() {
     return on;
 }
 
-template <int BN, bool AMN, bool BMN, bool PAIR>
+template <int BN, bool AMN, bool BMN, bool PAIR, bool LEAN>
 cudaError_t launch_variant(const GemmProblemSet& ps, unsigned* err, unsigned long long limit_ns, cudaStream_t s,
                            const GemmGather& ag) {
-    auto kern = gemm_bf16_tcgen05_kernel<BN, AMN, BMN, PAIR>;
+    auto kern = gemm_bf16_tcgen05_kernel<BN, AMN, BMN, PAIR, LEAN>;
     static bool configured = false;
     static int max_pairs = 0;
     if (!configured) {
@@ -1227,29 +1238,57 @@ cudaError_t launch_variant(const GemmProblemSet& ps, unsigned* err, unsigned lon
     return cudaLaunchKernelEx(&cfg, kern, ps, err, limit_ns, ag);
 }
 
-template <bool PAIR>
+template <bool PAIR, bool LEAN>
 cudaError_t dispatch_mode(int BN, bool a_mn, bool b_mn, const GemmProblemSet& ps, unsigned* err, unsigned long long lim,
                           cudaStream_t s, const GemmGather& ag) {
     const int v = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
-    if (BN == 256) {
+    if constexpr (LEAN) {
+        // lean launches are forward / dgrad layers: A is K-major
+        if (BN == 256) return v == 0 ? launch_variant<256, false, false, PAIR, true>(ps, err, lim, s, ag)
+                                     : launch_variant<256, false, true, PAIR, true>(ps, err, lim, s, ag);
+        return v == 0 ? launch_variant<128, false, false, PAIR, true>(ps, err, lim, s, ag)
+                      : launch_variant<128, false, true, PAIR, true>(ps, err, lim, s, ag);
+    } else {
+        if (BN == 256) {
+            switch (v) {
+                case 0: return launch_variant<256, false, false, PAIR, false>(ps, err, lim, s, ag);
+                case 1: return launch_variant<256, false, true, PAIR, false>(ps, err, lim, s, ag);
+                case 2: return launch_variant<256, true, false, PAIR, false>(ps, err, lim, s, ag);
+                default: return launch_variant<256, true, true, PAIR, false>(ps, err, lim, s, ag);
+            }
+        }
         switch (v) {
-            case 0: return launch_variant<256, false, false, PAIR>(ps, err, lim, s, ag);
-            case 1: return launch_variant<256, false, true, PAIR>(ps, err, lim, s, ag);
-            case 2: return launch_variant<256, true, false, PAIR>(ps, err, lim, s, ag);
-            default: return launch_variant<256, true, true, PAIR>(ps, err, lim, s, ag);
+            case 0: return launch_variant<128, false, false, PAIR, false>(ps, err, lim, s, ag);
+            case 1: return launch_variant<128, false, true, PAIR, false>(ps, err, lim, s, ag);
+            case 2: return launch_variant<128, true, false, PAIR, false>(ps, err, lim, s, ag);
+            default: return launch_variant<128, true, true, PAIR, false>(ps, err, lim, s, ag);
         }
     }
-    switch (v) {
-        case 0: return launch_variant<128, false, false, PAIR>(ps, err, lim, s, ag);
-        case 1: return launch_variant<128, false, true, PAIR>(ps, err, lim, s, ag);
-        case 2: return launch_variant<128, true, false, PAIR>(ps, err, lim, s, ag);
-        default: return launch_variant<128, true, true, PAIR>(ps, err, lim, s, ag);
+}
+
+// Whether every problem of the set qualifies for the lean epilogue.
+bool lean_ok(const GemmProblemSet& ps, bool a_mn, bool b_mn, const GemmGather& ag) {
+    if (a_mn || ag.enabled || ps.trace != nullptr || ps.epi_skip != 0) return false;
+    for (int i = 0; i < ps.count; ++i) {
+        const GemmEpilogue& e = ps.ep[i];
+        if (ps.d_mode[i] != 1 || (ps.N[i] % 32) != 0) return false;
+        if (b_mn) {   // the lean dgrad kernel: a mask (aligned rows) or nothing
+            if (e.bias != nullptr || e.bias_bf16 != nullptr || e.relu) return false;
+            if (e.mask != nullptr && ((e.ldmask % 8) != 0 || ((uintptr_t)e.mask % 16) != 0)) return false;
+        } else if (e.mask != nullptr) {   // the lean forward kernel: bias and activation, no mask
+            return false;
+        }
     }
+    return true;
 }
 
 cudaError_t dispatch(int BN, bool pair, bool a_mn, bool b_mn, const GemmProblemSet& ps, unsigned* err, unsigned long long lim,
                      cudaStream_t s, const GemmGather& ag) {
-    return pair ? dispatch_mode<true>(BN, a_mn, b_mn, ps, err, lim, s, ag) : dispatch_mode<false>(BN, a_mn, b_mn, ps, err, lim, s, ag);
+    if (lean_ok(ps, a_mn, b_mn, ag))
+        return pair ? dispatch_mode<true, true>(BN, a_mn, b_mn, ps, err, lim, s, ag)
+                    : dispatch_mode<false, true>(BN, a_mn, b_mn, ps, err, lim, s, ag);
+    return pair ? dispatch_mode<true, false>(BN, a_mn, b_mn, ps, err, lim, s, ag)
+                : dispatch_mode<false, false>(BN, a_mn, b_mn, ps, err, lim, s, ag);
 }
 
 // CTA pairs are used whenever a problem has more than one 128-row block (and never with the gather role, whose
