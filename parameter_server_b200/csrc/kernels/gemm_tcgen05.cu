@@ -307,12 +307,14 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpilogue& ep, float* f,
             f[j] += b.x; f[j + 1] += b.y; f[j + 2] += b.z; f[j + 3] += b.w;
         }
     }
+    if constexpr (!LEAN_FWD) {   // the lean forward kernel applies the activation to the packed pairs
     if (ep.relu) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) f[j] = fmaxf(f[j], 0.f);
     }
     }
-    if constexpr (LEAN_FWD) return;
+    }
+    if constexpr (LEAN) return;
     if (mpre != nullptr) {
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
@@ -950,9 +952,35 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                     if (more) tmem_ld32_issue(taddr + (uint32_t)(c + 1) * 32u, v);
                     return true;
                 }
-                if (LEAN || !(ps.epi_skip & 1))
-                    epilogue_chunk<LEAN && !BMN, LEAN && BMN>(ep, f, row, col0, N, has_bias ? bs + cbase + c * 32 : nullptr, row < M,
-                                                              mhave ? mreg : nullptr);
+                if constexpr (!(LEAN && BMN)) {   // (the lean dgrad kernel has neither bias nor activation)
+                    if (LEAN || !(ps.epi_skip & 1))
+                        epilogue_chunk<LEAN && !BMN, LEAN && BMN>(ep, f, row, col0, N, has_bias ? bs + cbase + c * 32 : nullptr,
+                                                                  row < M, mhave ? mreg : nullptr);
+                }
+                uint4 raw[4];
+                if constexpr (LEAN) {
+                    // Lean kernels finish on the packed pairs: ReLU as a packed max, the ReLU-backward mask as a packed
+                    // compare + AND (the same values as on fp32: rounding keeps sign and zero), a third of the
+                    // instructions.
+                    const __nv_bfloat162 zero2 = __floats2bfloat162_rn(0.f, 0.f);
+                    const bool relu = !BMN && ep.relu != 0;
+                    const bool masked = BMN && mhave;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        __nv_bfloat162* h = (__nv_bfloat162*)&raw[j];
+                        const __nv_bfloat162* m2 = (const __nv_bfloat162*)&mreg[j];
+                        uint32_t* hb = (uint32_t*)&raw[j];
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            h[t] = __floats2bfloat162_rn(f[8 * j + 2 * t], f[8 * j + 2 * t + 1]);
+                            if constexpr (!BMN) {
+                                if (relu) h[t] = __hmax2(h[t], zero2);
+                            } else {
+                                if (masked) hb[t] &= __hgt2_mask(m2[t], zero2);
+                            }
+                        }
+                    }
+                }
                 mhave = false;
                 if (mask_fast && c + 1 < kChunks && col0 + 64 <= N) {
 #pragma unroll
@@ -965,14 +993,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmProblemSet ps, unsigned* er
                     // instruction writes whole 64-byte row segments (8 rows per instruction) instead of 16 bytes
                     // in each of 32 rows. Lane l writes row l; the 16-byte column blocks of a row are XOR-swizzled
                     // by (row / 2) % 4, which makes both the row-wise writes and the 8-row reads conflict-free.
-                    uint4 raw[4];
+                    if constexpr (!LEAN) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        __nv_bfloat162* h = (__nv_bfloat162*)&raw[j];
-                        h[0] = __floats2bfloat162_rn(f[8 * j], f[8 * j + 1]);
-                        h[1] = __floats2bfloat162_rn(f[8 * j + 2], f[8 * j + 3]);
-                        h[2] = __floats2bfloat162_rn(f[8 * j + 4], f[8 * j + 5]);
-                        h[3] = __floats2bfloat162_rn(f[8 * j + 6], f[8 * j + 7]);
+                        for (int j = 0; j < 4; ++j) {
+                            __nv_bfloat162* h = (__nv_bfloat162*)&raw[j];
+                            h[0] = __floats2bfloat162_rn(f[8 * j], f[8 * j + 1]);
+                            h[1] = __floats2bfloat162_rn(f[8 * j + 2], f[8 * j + 3]);
+                            h[2] = __floats2bfloat162_rn(f[8 * j + 4], f[8 * j + 5]);
+                            h[3] = __floats2bfloat162_rn(f[8 * j + 6], f[8 * j + 7]);
+                        }
                     }
                     if (more) tmem_ld32_issue(taddr + (uint32_t)(c + 1) * 32u, v);   // the values are packed: v is free
                     if (!LEAN && (ps.epi_skip & 2)) {
