@@ -65,8 +65,8 @@ def parse_args():
     ap.add_argument("--no-overlap", action="store_true", help="run the sparse pull / push in line with the dense work (one stream)")
     ap.add_argument("--overlap", action="store_true", help="force the side-stream overlap (default: on for up to two GPUs)")
     ap.add_argument("--no-chain", action="store_true", help="one GEMM launch per MLP layer instead of one chained launch per MLP pass")
-    ap.add_argument("--pull-sms", type=int, default=112, help="SMs of the fused sparse pull while it runs beside the bottom MLP (the GEMMs get the rest)")
-    ap.add_argument("--push-sms", type=int, default=90, help="SMs of the fused sparse push while it runs beside the dense backward pass")
+    ap.add_argument("--pull-sms", type=int, default=124, help="SMs of the fused sparse pull while it runs beside the bottom MLP (the GEMMs get the rest)")
+    ap.add_argument("--push-sms", type=int, default=96, help="SMs of the fused sparse push while it runs beside the dense backward pass")
     ap.add_argument("--micro-keys", type=int, default=1 << 20, help="keys per GPU per step of the microbenchmark")
     ap.add_argument("--micro-rows", type=int, default=62_500_000, help="resident rows per GPU of the microbenchmark table (config 2: 500 M keys / 8)")
     ap.add_argument("--sizes", default="65536,262144,1048576,4194304", help="--config sparse: keys per GPU per step")

@@ -95,8 +95,8 @@ class DLRM:
 
     def __init__(self, cfg: DLRMConfig, batch: int, *, table_capacity: int = 1 << 22, device=None, group=None,
                  seed: int = 0, wgrad_split_k: int = 0, sparse_kwargs: Optional[dict] = None,
-                 sparse_cls=SparseTable, dense_cls=DenseTable, overlap: Optional[bool] = None, pull_sms: int = 112,
-                 push_sms: int = 90, chain_gemms: bool = True, grad_wire_bf16: bool = True):
+                 sparse_cls=SparseTable, dense_cls=DenseTable, overlap: Optional[bool] = None, pull_sms: int = 124,
+                 push_sms: int = 96, chain_gemms: bool = True, grad_wire_bf16: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("DLRM runs on the sm_100a kernels and needs a CUDA device")
         self.cfg = cfg
