@@ -160,7 +160,7 @@ Status SparseEngine::set_mirror(GpuTable* mirror) {
 Status SparseEngine::set_deterministic(bool on) {
     if (on && sort_temp_ == nullptr) {
         cudaSetDevice(table_->device());
-        sort_temp_bytes_ = ordered_segment_sum_temp_bytes(cfg_.max_keys);
+        sort_temp_bytes_ = ordered_segment_sum_temp_bytes(cfg_.max_keys, table_->dim());
         if (cudaMalloc(&sorted_ids_, (size_t)cfg_.max_keys * 4) != cudaSuccess || cudaMalloc(&sorted_pos_, (size_t)cfg_.max_keys * 4) != cudaSuccess ||
             cudaMalloc(&sort_temp_, sort_temp_bytes_) != cudaSuccess) {
             cudaGetLastError();
@@ -312,7 +312,7 @@ Status SparseEngine::push(const float* grads, uint32_t n_rows, const OptConfig& 
     if (deterministic_ && !(flags & FUSED_AGG_READY)) {
         // position-ordered sums of the duplicates, then the fused kernel without its own (atomic) segment sum
         const float scale = (plan_flags_ & FUSED_MEAN) && plan_bag_ > 1 ? 1.0f / (float)plan_bag_ : 1.0f;
-        int rc0 = ordered_segment_sum(inverse_, plan_n_, counters_, &ctl_pull_->epoch, grads, plan_bag_, table_->dim(), scale,
+        int rc0 = ordered_segment_sum(inverse_, plan_n_, cfg_.max_keys, counters_, &ctl_pull_->epoch, grads, plan_bag_, table_->dim(), scale,
                                       agg_, sorted_ids_, sorted_pos_, sort_temp_, sort_temp_bytes_, stream);
         if (rc0 != 0) return Status::Error(std::string("ordered_segment_sum: ") + cudaGetErrorString((cudaError_t)rc0));
         flags |= FUSED_AGG_READY;

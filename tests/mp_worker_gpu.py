@@ -13,6 +13,7 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from parameter_server_b200 import SparseTable  # noqa: E402
+from blocked_sum import blocked_segment_sum  # noqa: E402
 from parameter_server_b200.ops.dense import DenseTable  # noqa: E402
 
 
@@ -74,12 +75,10 @@ def main():
                         got = torch.cat(all_out)
                         if deterministic:
                             assert torch.equal(got, ref), f"pull differs dim={dim} step={step}: {(got-ref).abs().max()}"
-                            # the oracle adds like the kernels: per rank in position order, then the ranks in rank order
+                            # the oracle adds like the kernels: per rank in the blocked position order, then the ranks in rank order
                             us, aggs = [], []
                             for k_r, g_r in zip(all_keys, all_grads):
-                                u, inv = np.unique(k_r.numpy(), return_inverse=True)
-                                agg = np.zeros((len(u), dim), dtype=np.float32)
-                                np.add.at(agg, inv, g_r.numpy())
+                                u, agg = blocked_segment_sum(k_r.numpy(), g_r.numpy())
                                 us.append(torch.from_numpy(u)); aggs.append(torch.from_numpy(agg))
                             c.push(torch.cat(aggs), keys=torch.cat(us))
                         elif wire16:

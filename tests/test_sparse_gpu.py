@@ -75,9 +75,12 @@ def test_push_with_duplicates_close_to_oracle():
 
 @pytest.mark.parametrize("opt,kw", [("adagrad", dict(lr=0.05, init_accumulator=0.1)), ("ftrl", dict(alpha=0.05, beta=1.0, l1=0.001, l2=0.01))])
 def test_deterministic_push_with_duplicates_is_bitwise_the_oracle(opt, kw):
-    """In reproducible mode the duplicates of a batch are summed in position order, which is what the host table
-    (and the reference's client-side merge, pico-ps/operator/SparsePushOperator.h:130-146) computes: the tables agree
-    bit for bit, also for a batch whose head key repeats thousands of times."""
+    """In reproducible mode the duplicates of a batch are summed in a fixed order that depends on the batch alone
+    (position order, in blocks of 64: tests/blocked_sum.py restates it on the host), as the reference's client-side
+    merge makes the result a function of the request (pico-ps/operator/SparsePushOperator.h:130-146): the tables
+    agree bit for bit with a host table that is given those sums, also for a batch whose head key repeats thousands
+    of times."""
+    from blocked_sum import blocked_segment_sum
     g, c = pair(64, opt, **kw)
     g.set_deterministic(True)
     for step in range(4):
@@ -86,7 +89,8 @@ def test_deterministic_push_with_duplicates_is_bitwise_the_oracle(opt, kw):
         g.pull(keys.cuda())
         g.push(grads.cuda())
         c.pull(keys)
-        c.push(grads)
+        uk_, agg_ = blocked_segment_sum(keys.numpy(), grads.numpy())
+        c.push(torch.from_numpy(agg_), keys=torch.from_numpy(uk_))
     g.check()
     uk = torch.unique(torch.cat([zipf_keys(30000, 4000, 1.05, s_) for s_ in range(4)]))
     a, fa = g.get_rows(uk.cuda(), emb_only=False)
