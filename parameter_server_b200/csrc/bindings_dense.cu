@@ -54,7 +54,8 @@ void bind_dense(py::module_& m) {
         .def("check", [](DenseEngine& e, uintptr_t s) { return e.check((void*)s); })
         .def("reset", [](DenseEngine& e, uintptr_t s) { return e.reset((void*)s); })
         .def("kernel_launches", &DenseEngine::kernel_launches)
-        .def("set_scatter_peers", &DenseEngine::set_scatter_peers);
+        .def("set_scatter_peers", &DenseEngine::set_scatter_peers)
+        .def("set_sm_budget", &DenseEngine::set_sm_budget);
 
     m.def("gemm_bf16",
           [](uintptr_t a, int64_t lda, bool a_mn, uintptr_t b, int64_t ldb, bool b_mn, int M, int N, int K,

@@ -22,7 +22,8 @@ namespace psb {
 
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kThreadsSmall = 256;   // four CTAs per SM
+constexpr int kThreadsWide = 1024;   // one CTA fills an SM: the shape for sharing the GPU by SMs with another kernel
 
 template <typename GT>
 struct Vec4;  // four gradient elements; a warp's loads cover one contiguous 512-byte (fp32) / 256-byte (bf16) span
@@ -43,8 +44,8 @@ struct Vec4<__nv_bfloat16> {
     }
 };
 
-template <typename GT>
-__global__ void __launch_bounds__(kThreads, 4) dense_rs_opt_ag_kernel(const DenseArgs a) {
+template <typename GT, int kThreads>
+__global__ void __launch_bounds__(kThreads, 1024 / kThreads) dense_rs_opt_ag_kernel(const DenseArgs a) {
     const int me = a.rank;
     const unsigned epoch = *((volatile unsigned*)&a.ctl->epoch) + 1u;
     const int W = a.world;
@@ -143,11 +144,15 @@ __global__ void __launch_bounds__(kThreads, 4) dense_rs_opt_ag_kernel(const Dens
 
 }  // namespace
 
-int launch_dense_rs_opt_ag(const DenseArgs& a, int grad_is_bf16, int nblocks, void* stream) {
-    if (grad_is_bf16)
-        dense_rs_opt_ag_kernel<__nv_bfloat16><<<nblocks, kThreads, 0, (cudaStream_t)stream>>>(a);
-    else
-        dense_rs_opt_ag_kernel<float><<<nblocks, kThreads, 0, (cudaStream_t)stream>>>(a);
+int launch_dense_rs_opt_ag(const DenseArgs& a, int grad_is_bf16, int nblocks, bool wide, void* stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (wide) {
+        if (grad_is_bf16) dense_rs_opt_ag_kernel<__nv_bfloat16, kThreadsWide><<<nblocks, kThreadsWide, 0, s>>>(a);
+        else dense_rs_opt_ag_kernel<float, kThreadsWide><<<nblocks, kThreadsWide, 0, s>>>(a);
+    } else {
+        if (grad_is_bf16) dense_rs_opt_ag_kernel<__nv_bfloat16, kThreadsSmall><<<nblocks, kThreadsSmall, 0, s>>>(a);
+        else dense_rs_opt_ag_kernel<float, kThreadsSmall><<<nblocks, kThreadsSmall, 0, s>>>(a);
+    }
     return (int)cudaGetLastError();
 }
 

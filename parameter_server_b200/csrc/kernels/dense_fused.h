@@ -27,6 +27,7 @@ struct DenseArgs {
     KernelCtl* ctl;
 };
 
-int launch_dense_rs_opt_ag(const DenseArgs& a, int grad_is_bf16, int nblocks, void* stream);
+// wide: 1024-thread CTAs (one per SM, nblocks = SMs used) instead of 256-thread ones
+int launch_dense_rs_opt_ag(const DenseArgs& a, int grad_is_bf16, int nblocks, bool wide, void* stream);
 
 }  // namespace psb

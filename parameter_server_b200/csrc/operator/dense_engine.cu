@@ -108,7 +108,9 @@ Status DenseEngine::step(const OptConfig& opt, float grad_scale, void* stream) {
     a.ctl = ctl_;
     const size_t chunks = shard_len_ / 4;
     int nblocks = (int)std::min<size_t>(148 * 4, std::max<size_t>(1, (chunks + 255) / 256));  // 4 resident CTAs per SM, one wave
-    int rc = launch_dense_rs_opt_ag(a, grad_bf16_ ? 1 : 0, nblocks, stream);
+    const bool wide = sm_budget_ > 0;
+    if (wide) nblocks = (int)std::min<size_t>((size_t)sm_budget_, std::max<size_t>(1, (chunks + 1023) / 1024));
+    int rc = launch_dense_rs_opt_ag(a, grad_bf16_ ? 1 : 0, nblocks, wide, stream);
     ++launches_;
     if (rc != 0) return Status::Error(std::string("dense_rs_opt_ag launch: ") + cudaGetErrorString((cudaError_t)rc));
     return Status::Ok();

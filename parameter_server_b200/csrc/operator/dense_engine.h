@@ -43,6 +43,9 @@ public:
     // false: dense push leaves the other ranks' copies of this table stale; they are gathered by the
     // consuming kernel (all-gather fused with the first GEMM).
     void set_scatter_peers(bool on) { scatter_peers_ = on; }
+    // n > 0: the push runs as 1024-thread CTAs (each fills an SM) on at most n SMs and leaves the others, whole, to a
+    // kernel of another stream (the sparse push of the same step); 0 = the whole GPU.
+    void set_sm_budget(int sms) { sm_budget_ = sms > 0 ? sms : 0; }
     int world() const { return world_; }
     int rank() const { return rank_; }
 
@@ -59,6 +62,7 @@ private:
     unsigned epoch_ = 0;
     uint64_t launches_ = 0;
     bool scatter_peers_ = true;
+    int sm_budget_ = 0;
 };
 
 }  // namespace psb

@@ -96,7 +96,8 @@ class DLRM:
     def __init__(self, cfg: DLRMConfig, batch: int, *, table_capacity: int = 1 << 22, device=None, group=None,
                  seed: int = 0, wgrad_split_k: int = 0, sparse_kwargs: Optional[dict] = None,
                  sparse_cls=SparseTable, dense_cls=DenseTable, overlap: Optional[bool] = None, pull_sms: int = 124,
-                 push_sms: int = 96, chain_gemms: bool = True, grad_wire_bf16: bool = True):
+                 push_sms: int = 96, chain_gemms: bool = True, grad_wire_bf16: bool = True,
+                 tail_overlap: Optional[bool] = None):
         if not torch.cuda.is_available():
             raise RuntimeError("DLRM runs on the sm_100a kernels and needs a CUDA device")
         self.cfg = cfg
@@ -190,9 +191,20 @@ class DLRM:
         self.n_sms = torch.cuda.get_device_properties(dev).multi_processor_count
         self.pull_sms = max(8, min(int(pull_sms), self.n_sms - 8))
         self.push_sms = max(8, min(int(push_sms), self.n_sms - 8))
+        # From three ranks on another pairing pays instead: the two kernels that wait for peers, the sparse push and the
+        # dense push, run side by side at the end of the step (the sparse push on all SMs but `dense_sms`, the dense
+        # push, which is small, on those), so the waits of the dense push hide under the sparse push.
+        self.dense_sms = 16
+        want_tail = (getattr(self.sparse, "world", 1) > 2) if tail_overlap is None else bool(tail_overlap)
+        self.tail_overlap = (not self.overlap) and want_tail and hasattr(self.sparse, "set_sm_budget") and \
+            hasattr(self.dense, "set_sm_budget")
         if self.overlap:
             self.side = torch.cuda.Stream(device=dev)
             self.sparse.set_sm_budget(self.pull_sms, self.push_sms)
+        elif self.tail_overlap:
+            self.side = torch.cuda.Stream(device=dev)
+            self.sparse.set_sm_budget(0, self.n_sms - self.dense_sms)
+            self.dense.set_sm_budget(self.dense_sms)
         # the row gradients come out of bf16 tensor-core arithmetic; between ranks they travel as bf16 like the rows
         if grad_wire_bf16 and hasattr(self.sparse, "set_grad_wire_bf16"):
             self.sparse.set_grad_wire_bf16(True)
@@ -383,7 +395,7 @@ class DLRM:
                     self._mark("push_done")
             C.gemm_set_cta_limit(self.n_sms - self.push_sms)
             C.gemm_set_pair(0)
-        else:
+        elif not self.tail_overlap:
             self.sparse.push(self.d_emb); n_launch += 1
         self._mark("sparse_push")
         # ---------------- backward: bottom MLP ----------------
@@ -409,7 +421,16 @@ class DLRM:
             # that wait for peers must not compete for the same SMs
             main.wait_stream(self.side)
             self._mark("join_push")
+        if self.tail_overlap:
+            # fork: the sparse push beside the dense push; both wait for their peers, on disjoint SMs
+            self.side.wait_stream(main)
+            with torch.cuda.stream(self.side):
+                self.sparse.push(self.d_emb); n_launch += 1
+                if self.stamps is not None:
+                    self._mark("push_done")
         self.dense.push(); n_launch += 1
+        if self.tail_overlap:
+            main.wait_stream(self.side)
         self._mark("dense_push")
         self.launches_per_step = n_launch
         return self.loss

@@ -125,6 +125,12 @@ class DenseTable:
     def zero_grads(self) -> None:
         self.flat_grads.zero_()
 
+    def set_sm_budget(self, sms: int = 0) -> None:
+        """Bound the fused dense push to ``sms`` SMs (0 = all): it then runs as CTAs that fill an SM each, so that a
+        kernel of another stream (the sparse push of the same step) keeps the other SMs, whichever starts first."""
+        if self.is_cuda:
+            self.engine.set_sm_budget(int(sms))
+
     def push(self, grad_scale: Optional[float] = None) -> None:
         """Collective dense push: gradients of all ranks are summed (times ``grad_scale``, default
         ``1/world``), the owner of each slice applies the update rule, new values reach every rank."""
