@@ -74,9 +74,12 @@ PSB_HD int opt_num_slots(int type) {
 #define PSB_SQRT(a) sqrtf((a))
 #endif
 
-// One coordinate: weight w, slots s0/s1, incoming (merged) push value g.
+// One coordinate: weight w, slots s0/s1, incoming (merged) push value g. kOpt >= 0 fixes the update rule at compile
+// time (the caller vouches that c.type == kOpt): a kernel that inlines this four times per row then carries one
+// rule's code instead of all of them.
+template <int kOpt = -1>
 PSB_HD void opt_update(const OptConfig& c, float& w, float& s0, float& s1, float g) {
-    switch (c.type) {
+    switch (kOpt >= 0 ? kOpt : c.type) {
         case OPT_SGD: {
             if (c.weight_decay != 0.f) w = PSB_SUB(w, PSB_MUL(PSB_MUL(c.lr, c.weight_decay), w));
             w = PSB_SUB(w, PSB_MUL(c.lr, g));

@@ -80,6 +80,14 @@ __device__ __forceinline__ uint2 pack_bf16x4(const float4& v) {
     return p;
 }
 
+// The update rule on four coordinates, any rule, out of line (for paths that are not worth four inlined copies).
+__device__ __noinline__ void opt_update4_any(const OptConfig& opt, float4& w, float4& s0, float4& s1, const float4& g) {
+    opt_update(opt, w.x, s0.x, s1.x, g.x);
+    opt_update(opt, w.y, s0.y, s1.y, g.y);
+    opt_update(opt, w.z, s0.z, s1.z, g.z);
+    opt_update(opt, w.w, s0.w, s1.w, g.w);
+}
+
 // Each CTA waits until every peer's flag in `flags` (local memory, written remotely) reached `target`.
 __device__ __forceinline__ bool wait_all_flags(const unsigned* flags, unsigned target, const FusedArgs& a,
                                                unsigned where) {
@@ -116,7 +124,9 @@ struct RowSrc {
         if (a.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 0) a.prof[slot] = global_timer_ns(); \
     } while (0)
 
-template <int kThreads>
+// MULTI = false: the single-rank variant; `W` is then the constant 1 and all code for peers drops out of the kernel
+// (less code in the phase loops, which the instruction fetch of these long kernels feels).
+template <int kThreads, bool MULTI>
 __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_pull_kernel(const FusedArgs a) {
     const unsigned nblocks = gridDim.x;
     const unsigned tid = blockIdx.x * kThreads + threadIdx.x;
@@ -129,7 +139,7 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_pull_kernel(c
     unsigned* send_cnt = cnt + 4;
     unsigned* in_cnt = a.in_cnt + par * kMaxWorld;
     const int me = a.rank;
-    const int W = a.world;
+    const int W = MULTI ? a.world : 1;
     const unsigned C = a.C;
     const TableView T = *a.table;
     const PeerBufs& mine = a.peer[me];
@@ -532,7 +542,7 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_pull_kernel(c
     if (blockIdx.x == 0 && threadIdx.x == 0) a.ctl->epoch = epoch;
 }
 
-template <int kThreads>
+template <int kThreads, bool MULTI>
 __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_push_kernel(const FusedArgs a) {
     constexpr int kHotSlots = HotCfg<kThreads>::kHotSlots;
     constexpr int kHotRows = HotCfg<kThreads>::kHotRows;
@@ -547,7 +557,7 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_push_kernel(c
     const unsigned* send_cnt = cnt + 4;
     const unsigned* in_cnt = a.in_cnt + plan_par * kMaxWorld;
     const int me = a.rank;
-    const int W = a.world;
+    const int W = MULTI ? a.world : 1;
     const unsigned C = a.C;
     const TableView T = *a.table;
     const PeerBufs& mine = a.peer[me];
@@ -1056,10 +1066,7 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_push_kernel(c
                 float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
                 if (R.n_opt_slots > 0) s0 = *(float4*)(w + dim + d);
                 if (R.n_opt_slots > 1) s1 = *(float4*)(w + 2 * dim + d);
-                opt_update(opt, wv.x, s0.x, s1.x, gv.x);
-                opt_update(opt, wv.y, s0.y, s1.y, gv.y);
-                opt_update(opt, wv.z, s0.z, s1.z, gv.z);
-                opt_update(opt, wv.w, s0.w, s1.w, gv.w);
+                opt_update4_any(opt, wv, s0, s1, gv);   // out of line: the replica path is the rare one
                 *(float4*)(w + d) = wv;
                 if (R.n_opt_slots > 0) *(float4*)(w + dim + d) = s0;
                 if (R.n_opt_slots > 1) *(float4*)(w + 2 * dim + d) = s1;
@@ -1080,16 +1087,23 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_push_kernel(c
 
 namespace {
 template <int kThreads>
+const void* push_kernel_of(bool multi) {
+    return multi ? (const void*)fused_push_kernel<kThreads, true> : (const void*)fused_push_kernel<kThreads, false>;
+}
+
+template <int kThreads>
 int max_blocks_of(const cudaDeviceProp& prop, int* pull_blocks, int* push_blocks) {
     int per_sm = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_pull_kernel<kThreads>, kThreads, 0);
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_pull_kernel<kThreads, true>, kThreads, 0);
     if (e != cudaSuccess) return (int)e;
     *pull_blocks = per_sm * prop.multiProcessorCount;
     // static counting tables + the dynamic row cache may exceed the 48 KB a kernel gets without asking
-    e = cudaFuncSetAttribute(fused_push_kernel<kThreads>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)push_smem_bytes<kThreads>());
-    if (e != cudaSuccess) return (int)e;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_push_kernel<kThreads>, kThreads, push_smem_bytes<kThreads>());
+    for (int multi = 0; multi < 2; ++multi) {
+        e = cudaFuncSetAttribute(push_kernel_of<kThreads>(multi != 0), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)push_smem_bytes<kThreads>());
+        if (e != cudaSuccess) return (int)e;
+    }
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_push_kernel<kThreads, true>, kThreads, push_smem_bytes<kThreads>());
     if (e != cudaSuccess) return (int)e;
     *push_blocks = per_sm * prop.multiProcessorCount;
     return 0;
@@ -1099,8 +1113,8 @@ int launch_push_of(const FusedArgs& a, int nblocks, void* stream) {
     void* params[] = {(void*)&a};
     const unsigned cap = (unsigned)HotCfg<kThreads>::kHotRows;
     const size_t smem = (size_t)(a.hot_rows < cap ? a.hot_rows : cap) * kHotMaxDim * sizeof(float);
-    return (int)cudaLaunchCooperativeKernel((const void*)fused_push_kernel<kThreads>, dim3(nblocks), dim3(kThreads), params, smem,
-                                            (cudaStream_t)stream);
+    const void* kern = push_kernel_of<kThreads>(a.world > 1);
+    return (int)cudaLaunchCooperativeKernel(kern, dim3(nblocks), dim3(kThreads), params, smem, (cudaStream_t)stream);
 }
 }  // namespace
 
@@ -1114,11 +1128,10 @@ int fused_max_blocks(int device, bool wide, int* pull_blocks, int* push_blocks) 
 
 int launch_fused_pull(const FusedArgs& a, int nblocks, bool wide, void* stream) {
     void* params[] = {(void*)&a};
-    if (wide)
-        return (int)cudaLaunchCooperativeKernel((const void*)fused_pull_kernel<kThreadsWide>, dim3(nblocks), dim3(kThreadsWide),
-                                                params, 0, (cudaStream_t)stream);
-    return (int)cudaLaunchCooperativeKernel((const void*)fused_pull_kernel<kThreadsSmall>, dim3(nblocks), dim3(kThreadsSmall),
-                                            params, 0, (cudaStream_t)stream);
+    const bool multi = a.world > 1;
+    const void* kern = wide ? (multi ? (const void*)fused_pull_kernel<kThreadsWide, true> : (const void*)fused_pull_kernel<kThreadsWide, false>)
+                            : (multi ? (const void*)fused_pull_kernel<kThreadsSmall, true> : (const void*)fused_pull_kernel<kThreadsSmall, false>);
+    return (int)cudaLaunchCooperativeKernel(kern, dim3(nblocks), dim3(wide ? kThreadsWide : kThreadsSmall), params, 0, (cudaStream_t)stream);
 }
 
 int launch_fused_push(const FusedArgs& a, int nblocks, bool wide, void* stream) {
