@@ -542,7 +542,8 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_pull_kernel(c
     if (blockIdx.x == 0 && threadIdx.x == 0) a.ctl->epoch = epoch;
 }
 
-template <int kThreads, bool MULTI>
+// PLAIN: the common push (no replication, no sync delta): those two features drop out of the update loop.
+template <int kThreads, bool MULTI, bool PLAIN>
 __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_push_kernel(const FusedArgs a) {
     constexpr int kHotSlots = HotCfg<kThreads>::kHotSlots;
     constexpr int kHotRows = HotCfg<kThreads>::kHotRows;
@@ -834,12 +835,12 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_push_kernel(c
     PROF(11);
     OptConfig opt = a.opt;
     if (opt.step_from_epoch) opt_set_step(opt, epoch);
-    const bool sync_mode = (a.flags & FUSED_SYNC_PUSH) != 0;
+    const bool sync_mode = !PLAIN && (a.flags & FUSED_SYNC_PUSH) != 0;
     const unsigned dim = a.dim;
     // Replication: this rank's updates go to the GPU to its right, and it applies the updates of the GPU to its left.
     // (a sync push only buffers deltas: it appends nothing, but it keeps the hand-shake of the log going so that
     // the epochs of later pushes line up)
-    const bool replicate = (a.flags & FUSED_REPLICATE) != 0;
+    const bool replicate = !PLAIN && (a.flags & FUSED_REPLICATE) != 0;
     const bool rep_log = replicate && !sync_mode;
     const int partner = (me + 1) % W, mirrored = (me + W - 1) % W;
     unsigned* rep_fill = a.ctl->pad;   // entries appended to the partner's log by this call (reset by the last CTA)
@@ -1087,8 +1088,9 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_push_kernel(c
 
 namespace {
 template <int kThreads>
-const void* push_kernel_of(bool multi) {
-    return multi ? (const void*)fused_push_kernel<kThreads, true> : (const void*)fused_push_kernel<kThreads, false>;
+const void* push_kernel_of(bool multi, bool plain) {
+    if (plain) return multi ? (const void*)fused_push_kernel<kThreads, true, true> : (const void*)fused_push_kernel<kThreads, false, true>;
+    return multi ? (const void*)fused_push_kernel<kThreads, true, false> : (const void*)fused_push_kernel<kThreads, false, false>;
 }
 
 template <int kThreads>
@@ -1098,12 +1100,12 @@ int max_blocks_of(const cudaDeviceProp& prop, int* pull_blocks, int* push_blocks
     if (e != cudaSuccess) return (int)e;
     *pull_blocks = per_sm * prop.multiProcessorCount;
     // static counting tables + the dynamic row cache may exceed the 48 KB a kernel gets without asking
-    for (int multi = 0; multi < 2; ++multi) {
-        e = cudaFuncSetAttribute(push_kernel_of<kThreads>(multi != 0), cudaFuncAttributeMaxDynamicSharedMemorySize,
+    for (int v = 0; v < 4; ++v) {
+        e = cudaFuncSetAttribute(push_kernel_of<kThreads>((v & 1) != 0, (v & 2) != 0), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)push_smem_bytes<kThreads>());
         if (e != cudaSuccess) return (int)e;
     }
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_push_kernel<kThreads, true>, kThreads, push_smem_bytes<kThreads>());
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_push_kernel<kThreads, true, false>, kThreads, push_smem_bytes<kThreads>());
     if (e != cudaSuccess) return (int)e;
     *push_blocks = per_sm * prop.multiProcessorCount;
     return 0;
@@ -1113,7 +1115,7 @@ int launch_push_of(const FusedArgs& a, int nblocks, void* stream) {
     void* params[] = {(void*)&a};
     const unsigned cap = (unsigned)HotCfg<kThreads>::kHotRows;
     const size_t smem = (size_t)(a.hot_rows < cap ? a.hot_rows : cap) * kHotMaxDim * sizeof(float);
-    const void* kern = push_kernel_of<kThreads>(a.world > 1);
+    const void* kern = push_kernel_of<kThreads>(a.world > 1, (a.flags & (FUSED_SYNC_PUSH | FUSED_REPLICATE)) == 0);
     return (int)cudaLaunchCooperativeKernel(kern, dim3(nblocks), dim3(kThreads), params, smem, (cudaStream_t)stream);
 }
 }  // namespace
