@@ -58,6 +58,16 @@ enum Where : unsigned {
     W_Q1 = 32, W_ACK, W_Q2, W_GRADFLAG, W_Q3A, W_Q3B, W_NOROW, W_REPACK, W_REPFLAG, W_REP_A, W_REP_FULL,
 };
 
+// Initial value of four columns of a key that has no row (read-only pulls of unknown keys): rare, so out of line in
+// the gather loops, whose bodies should stay small.
+__device__ __noinline__ float4 init4_rare(long long key, unsigned d, unsigned long long seed, float range) {
+    float4 v;
+    v.x = init_uniform(key, d + 0, seed, range);
+    v.y = init_uniform(key, d + 1, seed, range);
+    v.z = init_uniform(key, d + 2, seed, range);
+    v.w = init_uniform(key, d + 3, seed, range);
+    return v;
+}
 __device__ __forceinline__ float4 init4(const TableView& t, long long key, unsigned d) {
     float4 v;
     v.x = init_uniform(key, d + 0, t.init_seed, t.init_range);
@@ -406,7 +416,7 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_pull_kernel(c
                     float4 v[kIn];
 #pragma unroll
                     for (int k = 0; k < kIn; ++k)
-                        if (act[k]) v[k] = src[k] != nullptr ? *(const float4*)(src[k] + d) : init4(T, key[k], d);
+                        if (act[k]) v[k] = src[k] != nullptr ? *(const float4*)(src[k] + d) : init4_rare(key[k], d, T.init_seed, T.init_range);
 #pragma unroll
                     for (int k = 0; k < kIn; ++k) {
                         if (!act[k]) continue;
@@ -442,7 +452,7 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_pull_kernel(c
             a.inverse[i] = (int)(u | (ds.aux == dup_tag ? kDupBit : 0u));
             const unsigned s = a.uniq_row[u];
             unsigned row = s;  // kRemoteRow stays
-            if (s != kRemoteRow) row = (s == kNoSlot) ? kNoRow : T.slots[s].row;
+            if (!MULTI || s != kRemoteRow) row = (s == kNoSlot) ? kNoRow : T.slots[s].row;
             a.pos_slot[i] = row;  // from here on: the row of position i
         }
         if (W > 1) {
@@ -472,7 +482,7 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_pull_kernel(c
                         src[k].b16 = nullptr;
                         if (act[k]) {
                             const unsigned row = a.pos_slot[bb[k]];
-                            if (row == kRemoteRow) {
+                            if (MULTI && row == kRemoteRow) {
                                 const size_t uq = (unsigned)a.inverse[bb[k]] & ~kDupBit;
                                 if (rows16) src[k].b16 = rin16 + uq * a.dim;
                                 else src[k].f32 = mine.rows_in + uq * a.dim;
@@ -487,14 +497,14 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_pull_kernel(c
 #pragma unroll
                         for (int k = 0; k < kBags; ++k) {
                             if (!act[k]) continue;
-                            if (src[k].b16 != nullptr) hv[k] = *(const uint2*)(src[k].b16 + d);
-                            else v[k] = src[k].f32 != nullptr ? *(const float4*)(src[k].f32 + d) : init4(T, a.keys[bb[k]], d);
+                            if (MULTI && src[k].b16 != nullptr) hv[k] = *(const uint2*)(src[k].b16 + d);
+                            else v[k] = src[k].f32 != nullptr ? *(const float4*)(src[k].f32 + d) : init4_rare(a.keys[bb[k]], d, T.init_seed, T.init_range);
                         }
 #pragma unroll
                         for (int k = 0; k < kBags; ++k) {
                             if (!act[k]) continue;
                             if (out16) {
-                                if (src[k].b16 == nullptr) hv[k] = pack_bf16x4(v[k]);
+                                if (!MULTI || src[k].b16 == nullptr) hv[k] = pack_bf16x4(v[k]);
                                 *(uint2*)(outh + (size_t)bb[k] * a.dim + d) = hv[k];
                             } else {
                                 *(float4*)(outf + (size_t)bb[k] * a.dim + d) = v[k];
@@ -510,9 +520,9 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) fused_pull_kernel(c
                         const unsigned i = b * L + j;
                         const unsigned row = a.pos_slot[i];
                         float4 v;
-                        if (row == kRemoteRow) v = *(const float4*)(mine.rows_in + (size_t)((unsigned)a.inverse[i] & ~kDupBit) * a.dim + d);
+                        if (MULTI && row == kRemoteRow) v = *(const float4*)(mine.rows_in + (size_t)((unsigned)a.inverse[i] & ~kDupBit) * a.dim + d);
                         else if (row < kRowPending) v = *(const float4*)(T.row_ptr(row) + d);
-                        else v = init4(T, a.keys[i], d);
+                        else v = init4_rare(a.keys[i], d, T.init_seed, T.init_range);
                         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
                     }
                     if (L > 1) { acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale; }
