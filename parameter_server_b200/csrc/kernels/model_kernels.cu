@@ -308,6 +308,60 @@ __global__ void __launch_bounds__(256) bce_head_kernel(const __nv_bfloat16* __re
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const float b0 = bias ? __bfloat162float(bias[0]) : 0.f;
+    if (K <= 256 && (K % 8) == 0 && (ldh % 8) == 0 && (dz_prev == nullptr || (lddz % 8) == 0)) {
+        // Fast path (hidden widths up to 256): a lane owns 8 consecutive columns: one 16-byte load of h per row, the
+        // weight slice and the dw partial sums stay in registers across all rows of the warp, one 16-byte store of dz.
+        const bool on = lane * 8 < K;
+        float wv[8], dwv[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) { wv[t] = on ? __bfloat162float(w[lane * 8 + t]) : 0.f; dwv[t] = 0.f; }
+        float loss_acc = 0.f, db_acc = 0.f;
+        for (int b = blockIdx.x * nwarps + warp; b < B; b += gridDim.x * nwarps) {
+            float hv[8];
+            if (on) {
+                const uint4 raw = *(const uint4*)(h + (size_t)b * ldh + lane * 8);
+                const __nv_bfloat162* p2 = (const __nv_bfloat162*)&raw;
+#pragma unroll
+                for (int t = 0; t < 4; ++t) { const float2 f = __bfloat1622float2(p2[t]); hv[2 * t] = f.x; hv[2 * t + 1] = f.y; }
+            } else {
+#pragma unroll
+                for (int t = 0; t < 8; ++t) hv[t] = 0.f;
+            }
+            float acc = 0.f;
+#pragma unroll
+            for (int t = 0; t < 8; ++t) acc = fmaf(hv[t], wv[t], acc);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            const float z = acc + b0;
+            const float yy = y[b];
+            const float p = 1.f / (1.f + __expf(-z));
+            const float loss = fmaxf(z, 0.f) - z * yy + log1pf(__expf(-fabsf(z)));
+            const float dl = (p - yy) * inv_batch;
+            if (lane == 0) {
+                loss_acc += loss * inv_batch;
+                db_acc += dl;
+                if (logits) logits[b] = z;
+            }
+            if (dz_prev != nullptr && on) {
+                uint4 outv;
+                __nv_bfloat162* o2 = (__nv_bfloat162*)&outv;
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+                    o2[t] = __floats2bfloat162_rn(hv[2 * t] > 0.f ? dl * wv[2 * t] : 0.f, hv[2 * t + 1] > 0.f ? dl * wv[2 * t + 1] : 0.f);
+                *(uint4*)(dz_prev + (size_t)b * lddz + lane * 8) = outv;
+#pragma unroll
+                for (int t = 0; t < 8; ++t) dwv[t] = fmaf(dl, hv[t], dwv[t]);
+            }
+        }
+        if (on) {
+#pragma unroll
+            for (int t = 0; t < 8; ++t) atomicAdd(&s_dw[lane * 8 + t], dwv[t]);
+        }
+        if (lane == 0) {
+            atomicAdd(&s_loss, loss_acc);
+            atomicAdd(&s_db, db_acc);
+        }
+    } else
     for (int b = blockIdx.x * nwarps + warp; b < B; b += gridDim.x * nwarps) {
         const __nv_bfloat16* hr = h + (size_t)b * ldh;
         float acc = 0.f;
