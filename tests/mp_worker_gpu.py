@@ -270,6 +270,19 @@ def main():
         sig = float(model.dense.flat_params.float().sum().item())
         sigs = gather(sig)
         assert max(sigs) - min(sigs) == 0.0, sigs
+        # the arrangement used from three ranks on: one stream, but the sparse push beside the dense push
+        model2 = DLRM(cfg, 1024, table_capacity=1 << 18, overlap=False, tail_overlap=True)
+        assert model2.tail_overlap
+        data2 = SyntheticCTR(cfg, 1024, pool=4, seed=rank)
+        for i in range(12):
+            if i == 4:
+                model2.enable_graph()
+            model2.train_step(*data2.next())
+            l2 = model2.read_loss()
+            assert np.isfinite(l2), l2
+        model2.check()
+        sigs = gather(float(model2.dense.flat_params.float().sum().item()))
+        assert max(sigs) - min(sigs) == 0.0, sigs
         if rank == 0:
             print("dlrm ok", [round(x, 3) for x in losses[:3]], "...", round(losses[-1], 3), flush=True)
 

@@ -158,3 +158,43 @@ def test_overlapped_step_matches_the_serial_step():
         assert no == ns
         assert max(abs(a - b) for a, b in zip(ls, lo)) < 5e-3, (ls, lo)
         assert torch.allclose(ps_, po, rtol=0, atol=2e-2)
+
+
+def test_staged_batches_and_tail_overlap_match_the_plain_step():
+    """``stage`` + ``train_step()`` (the next batch crosses PCIe while the queued step runs) and the arrangement used
+    from three ranks on (sparse push beside the dense push, both as whole-SM CTAs on disjoint SMs) compute the same
+    step as ``train_step(batch)`` on one stream."""
+    cfg = DLRMConfig(vocab_max=2e4)
+    B = 512
+
+    def run(staged, tail, graph):
+        model = DLRM(cfg, B, table_capacity=1 << 17, seed=3, overlap=False, tail_overlap=tail)
+        assert model.tail_overlap == tail
+        data = SyntheticCTR(cfg, B, pool=3, seed=9)
+        for _ in range(3):
+            model.train_step(*data.next())
+        if graph:
+            model.enable_graph()
+        losses = []
+        if staged:
+            model.stage(*data.next())
+            for i in range(6):
+                model.train_step()
+                if i + 1 < 6:
+                    model.stage(*data.next())
+                losses.append(model.read_loss())
+        else:
+            for _ in range(6):
+                model.train_step(*data.next())
+                losses.append(model.read_loss())
+        model.check()
+        return losses, model.dense.flat_params.float().clone(), model.sparse.size()
+
+    ls, ps_, ns = run(False, False, False)
+    for staged, tail, graph in ((True, False, True), (False, True, False), (True, True, True)):
+        lo, po, no = run(staged, tail, graph)
+        assert no == ns
+        assert max(abs(a - b) for a, b in zip(ls, lo)) < 5e-3, (ls, lo)
+        assert torch.allclose(ps_, po, rtol=0, atol=2e-2)
+    with pytest.raises(RuntimeError):
+        DLRM(cfg, B, table_capacity=1 << 17, seed=3, overlap=False).train_step()
