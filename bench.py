@@ -64,6 +64,7 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-overlap", action="store_true", help="run the sparse pull / push in line with the dense work (one stream)")
     ap.add_argument("--overlap", action="store_true", help="force the side-stream overlap (default: on for up to two GPUs)")
+    ap.add_argument("--overlap-fwd", action="store_true", help="only the pull beside the bottom MLP (the backward pass on one stream)")
     ap.add_argument("--no-tail-overlap", action="store_true", help="from 3 GPUs on: do not run the sparse push beside the dense push")
     ap.add_argument("--tail-overlap", action="store_true", help="run the sparse push beside the dense push at any number of GPUs (with --no-overlap)")
     ap.add_argument("--no-chain", action="store_true", help="one GEMM launch per MLP layer instead of one chained launch per MLP pass")
@@ -288,7 +289,7 @@ def main():
                          chain_gemms=not args.no_chain)
             graph = False      # variable all-to-all split sizes need the host: not capturable
         else:
-            model = DLRM(cfg, B, table_capacity=capacity, seed=0, overlap=(False if args.no_overlap else (True if args.overlap else None)),
+            model = DLRM(cfg, B, table_capacity=capacity, seed=0, overlap=(False if args.no_overlap else ("fwd" if args.overlap_fwd else (True if args.overlap else None))),
                          pull_sms=args.pull_sms, push_sms=args.push_sms, chain_gemms=not args.no_chain,
                          tail_overlap=(False if args.no_tail_overlap else (True if args.tail_overlap else None)))
         data = SyntheticCTR(cfg, B, pool=16, seed=1000 + rank)
@@ -341,7 +342,7 @@ def main():
         model.check()
         out = {"ms": ms, "e2e_ms": e2e_ms, "clocks": clocks, "launches": launches, "last_loss": last_loss,
                "h2d": data.bytes_per_batch(), "rows": model.sparse.size(), "graph": graph,
-               "overlap": bool(getattr(model, "overlap", False)), "tail_overlap": bool(getattr(model, "tail_overlap", False))}
+               "overlap": bool(getattr(model, "overlap", False)), "overlap_fwd": bool(getattr(model, "overlap_fwd", False)), "tail_overlap": bool(getattr(model, "tail_overlap", False))}
         if want_breakdown and hasattr(model, "step_breakdown"):
             barrier()
             out["breakdown"] = model.step_breakdown()
@@ -383,8 +384,8 @@ def main():
             "launch": "whole step replayed from one CUDA graph" if own["graph"] else "eager",
             "streams": ("sparse pull beside the bottom MLP forward and sparse push beside bottom dgrad + weight / bias "
                         "gradients (side stream; the GPU is split by SMs: pull %d / push %d SMs, GEMMs on the rest)" % (args.pull_sms, args.push_sms)) if own["overlap"] else (
-                            "one stream, except that the sparse push (all SMs but 16) and the dense push (16 SMs) run side by side"
-                            if own.get("tail_overlap") else "one stream"),
+                            ("pull beside the bottom MLP (%d SMs / rest); " % args.pull_sms if own.get("overlap_fwd") else "one stream; ") +
+                            ("the sparse push (all SMs but 16) and the dense push (16 SMs) run side by side" if own.get("tail_overlap") else "")),
             "l2": "inputs larger than L2: ~55 MB of bf16 embedding rows gathered + ~109 MB of fp32 row gradients per step "
                   "per GPU, new batch (pool of 16) every step",
         },

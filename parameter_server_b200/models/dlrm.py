@@ -185,9 +185,13 @@ class DLRM:
         # Measured on B200: the split pays on one GPU (about 5 % of the step) and on two (2 %); from four ranks on the
         # pull and push spend much of their time waiting for peers, and SMs held by a waiting kernel are lost to the
         # GEMMs, so the default (None) turns the overlap on for up to two ranks only.
+        # ``overlap="fwd"``: only the pull runs beside the bottom MLP; the backward pass keeps one stream (plus the tail
+        # arrangement below).
         if overlap is None:
             overlap = getattr(self.sparse, "world", 1) <= 2
-        self.overlap = bool(overlap) and hasattr(self.sparse, "set_sm_budget")
+        can_split = hasattr(self.sparse, "set_sm_budget")
+        self.overlap_fwd = (overlap == "fwd" or overlap is True) and can_split
+        self.overlap = (overlap is True) and can_split
         self.n_sms = torch.cuda.get_device_properties(dev).multi_processor_count
         self.pull_sms = max(8, min(int(pull_sms), self.n_sms - 8))
         self.push_sms = max(8, min(int(push_sms), self.n_sms - 8))
@@ -198,12 +202,11 @@ class DLRM:
         want_tail = (getattr(self.sparse, "world", 1) > 2) if tail_overlap is None else bool(tail_overlap)
         self.tail_overlap = (not self.overlap) and want_tail and hasattr(self.sparse, "set_sm_budget") and \
             hasattr(self.dense, "set_sm_budget")
-        if self.overlap:
+        if self.overlap or self.overlap_fwd or self.tail_overlap:
             self.side = torch.cuda.Stream(device=dev)
-            self.sparse.set_sm_budget(self.pull_sms, self.push_sms)
-        elif self.tail_overlap:
-            self.side = torch.cuda.Stream(device=dev)
-            self.sparse.set_sm_budget(0, self.n_sms - self.dense_sms)
+            self.sparse.set_sm_budget(self.pull_sms if self.overlap_fwd else 0,
+                                      self.push_sms if self.overlap else (self.n_sms - self.dense_sms if self.tail_overlap else 0))
+        if self.tail_overlap:
             self.dense.set_sm_budget(self.dense_sms)
         # the row gradients come out of bf16 tensor-core arithmetic; between ranks they travel as bf16 like the rows
         if grad_wire_bf16 and hasattr(self.sparse, "set_grad_wire_bf16"):
@@ -330,7 +333,7 @@ class DLRM:
 
         # ---------------- forward ----------------
         main = torch.cuda.current_stream()
-        if self.overlap:
+        if self.overlap_fwd:
             # fork: the pull needs only the keys; it runs beside the dense-feature cast and the bottom MLP
             self.side.wait_stream(main)
             with torch.cuda.stream(self.side):
@@ -346,7 +349,7 @@ class DLRM:
         self._mark("zero_cast")
         n_launch += self._mlp_forward(self.x16, self.bot_act, "bot")
         self._mark("bottom_fwd")
-        if self.overlap:
+        if self.overlap_fwd:
             C.gemm_set_cta_limit(0)
             C.gemm_set_pair(1)
             main.wait_stream(self.side)   # join: the interaction needs the embedding rows
