@@ -43,7 +43,8 @@ def main():
         # every rank sums its duplicates in position order and the owners fold the ranks in rank order: then the tables
         # must equal, bit for bit, an oracle that adds in that same order.
         # A third time with the gradient rows crossing NVLink as bf16: every rank's partial sum is rounded once (relative
-        # error 2^-9), so the comparison is looser.
+        # error 2^-9 of a sum that reaches 0.5 for the head keys), so the comparison is looser, in proportion to the
+        # number of ranks that contribute.
         for mode in ("atomic", "ordered", "bf16wire"):
             deterministic = mode == "ordered"
             wire16 = mode == "bf16wire"
@@ -82,7 +83,7 @@ def main():
                                 us.append(torch.from_numpy(u)); aggs.append(torch.from_numpy(agg))
                             c.push(torch.cat(aggs), keys=torch.cat(us))
                         elif wire16:
-                            assert mostly_close(got, ref, 1e-2, 1e-3, 5e-3), \
+                            assert mostly_close(got, ref, 2e-2, 1e-3 * world, 5e-3 * world), \
                                 f"pull mismatch (bf16 wire) dim={dim} step={step}: {(got-ref).abs().max()}"
                             c.push(torch.cat(all_grads))
                         else:
@@ -107,7 +108,7 @@ def main():
                     if deterministic:
                         assert torch.equal(R, ref), f"table differs from the oracle, {opt}: {(R-ref).abs().max()}"
                     elif wire16:
-                        assert mostly_close(R, ref, 1e-2, 1e-3, 1e-2), f"table mismatch (bf16 wire) {opt}: {(R-ref).abs().max()}"
+                        assert mostly_close(R, ref, 2e-2, 1e-3 * world, 1e-2 * world), f"table mismatch (bf16 wire) {opt}: {(R-ref).abs().max()}"
                     else:
                         assert mostly_close(R, ref, 2e-3, 1e-4, 4e-3 if opt == "adam" else 1e-4), f"table mismatch {opt}: {(R-ref).abs().max()}"
                 dist.barrier()
