@@ -252,6 +252,13 @@ void bind_service(py::module_& m) {
         return std::make_tuple(st, py::bytes((const char*)out.data(), out.size()));
     });
     m.def("byte2str", [](py::bytes b) { std::string s = b; return byte2str((const uint8_t*)s.data(), s.size()); });
+    // a config text as the native layer reads it (JSON, or the YAML subset of Json::parse_config), as JSON
+    m.def("config_to_json", [](const std::string& text) {
+        Json j;
+        std::string err;
+        if (!Json::parse_config(text, &j, &err)) throw std::runtime_error("config does not parse: " + err);
+        return j.dump();
+    });
     // logging of the host runtime: level by name ("debug", "info", "warning", "error", "off"); lines go to stderr or,
     // with a sink, to a Python callable (level: int, message: str) - e.g. a forwarder into the `logging` module
     m.def("set_log_level", [](const std::string& name) { set_log_level(log_detail::parse(name.c_str(), LogLevel::WARNING)); });

@@ -8,6 +8,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <cerrno>
 #include <map>
 #include <memory>
 #include <sstream>
@@ -105,6 +106,34 @@ public:
             return false;
         }
     }
+    // Operator and storage configs may be written as JSON or as YAML (the reference reads its configs with a YAML
+    // reader, pico-ps/service/Context.cpp:14-25). The YAML accepted here is the subset such configs use: block
+    // mappings and block sequences by indentation (spaces), flow sequences `[a, b]`, scalars (numbers, true / false /
+    // yes / no, null / ~, plain and quoted strings) and `#` comments; no anchors, tags or multi-line scalars. A text
+    // that starts with `{` or `[` is JSON.
+    static bool parse_config(const std::string& text, Json* out, std::string* err = nullptr) {
+        size_t p = 0;
+        skip_ws(text, p);
+        if (p >= text.size()) {
+            *out = object();
+            return true;
+        }
+        if (text[p] == '{' || text[p] == '[') return parse(text, out, err);
+        try {
+            std::vector<YamlLine> lines = yaml_lines(text);
+            if (lines.empty()) {
+                *out = object();
+                return true;
+            }
+            size_t i = 0;
+            *out = yaml_node(lines, i, lines[0].indent, 0);
+            if (i != lines.size()) throw std::runtime_error("bad indentation in line " + std::to_string(lines[i].number));
+            return true;
+        } catch (const std::exception& e) {
+            if (err) *err = std::string("YAML: ") + e.what();
+            return false;
+        }
+    }
     static Json parse_or_throw(const std::string& text) {
         Json j;
         std::string err;
@@ -113,6 +142,177 @@ public:
     }
 
 private:
+    // ---- YAML subset ------------------------------------------------------------------------------
+    struct YamlLine {
+        int indent;
+        std::string text;
+        int number;
+    };
+    static std::string trim(const std::string& s) {
+        size_t a = 0, b = s.size();
+        while (a < b && (s[a] == ' ' || s[a] == '\t' || s[a] == '\r')) ++a;
+        while (b > a && (s[b - 1] == ' ' || s[b - 1] == '\t' || s[b - 1] == '\r')) --b;
+        return s.substr(a, b - a);
+    }
+    static std::vector<YamlLine> yaml_lines(const std::string& text) {
+        std::vector<YamlLine> out;
+        size_t pos = 0;
+        int number = 0;
+        while (pos <= text.size()) {
+            size_t nl = text.find('\n', pos);
+            if (nl == std::string::npos) nl = text.size();
+            std::string line = text.substr(pos, nl - pos);
+            pos = nl + 1;
+            ++number;
+            // strip a comment: '#' at the start or after a space, outside quotes
+            char quote = 0;
+            for (size_t k = 0; k < line.size(); ++k) {
+                const char c = line[k];
+                if (quote) {
+                    if (c == quote) quote = 0;
+                } else if (c == '"' || c == '\'') {
+                    quote = c;
+                } else if (c == '#' && (k == 0 || line[k - 1] == ' ' || line[k - 1] == '\t')) {
+                    line.resize(k);
+                    break;
+                }
+            }
+            int indent = 0;
+            while ((size_t)indent < line.size() && line[indent] == ' ') ++indent;
+            if ((size_t)indent < line.size() && line[indent] == '\t') throw std::runtime_error("tab in the indentation of line " + std::to_string(number));
+            const std::string t = trim(line);
+            if (t.empty() || t == "---") continue;
+            out.push_back({indent, t, number});
+        }
+        return out;
+    }
+    static bool yaml_is_dash(const std::string& t) { return t == "-" || (t.size() > 1 && t[0] == '-' && t[1] == ' '); }
+    // position of the ':' that ends a mapping key (followed by a space or the end of the line, outside quotes), or npos
+    static size_t yaml_key_end(const std::string& t) {
+        char quote = 0;
+        for (size_t k = 0; k < t.size(); ++k) {
+            const char c = t[k];
+            if (quote) {
+                if (c == quote) quote = 0;
+            } else if (c == '"' || c == '\'') {
+                quote = c;
+            } else if (c == '[' || c == '{') {
+                return std::string::npos;
+            } else if (c == ':' && (k + 1 == t.size() || t[k + 1] == ' ')) {
+                return k;
+            }
+        }
+        return std::string::npos;
+    }
+    static Json yaml_scalar(const std::string& raw) {
+        const std::string t = trim(raw);
+        if (t.empty() || t == "~" || t == "null" || t == "Null" || t == "NULL") return Json();
+        if (t.size() >= 2 && ((t.front() == '"' && t.back() == '"') || (t.front() == '\'' && t.back() == '\''))) {
+            if (t.front() == '"') {   // the JSON string rules are the double-quoted YAML rules for what configs contain
+                Json j;
+                if (parse(t, &j)) return j;
+            }
+            return Json(t.substr(1, t.size() - 2));
+        }
+        if (t.front() == '[' || t.front() == '{') {
+            // flow collection: items separated by commas at depth 1, each a scalar or a nested flow collection
+            const bool map = t.front() == '{';
+            if (t.back() != (map ? '}' : ']')) throw std::runtime_error("unterminated flow collection: " + t);
+            Json out = map ? object() : array();
+            std::vector<std::string> items;
+            int depth = 0;
+            char quote = 0;
+            std::string cur;
+            for (size_t k = 1; k + 1 < t.size(); ++k) {
+                const char c = t[k];
+                if (quote) {
+                    if (c == quote) quote = 0;
+                } else if (c == '"' || c == '\'') {
+                    quote = c;
+                } else if (c == '[' || c == '{') {
+                    ++depth;
+                } else if (c == ']' || c == '}') {
+                    --depth;
+                } else if (c == ',' && depth == 0) {
+                    items.push_back(cur);
+                    cur.clear();
+                    continue;
+                }
+                cur.push_back(c);
+            }
+            if (!trim(cur).empty()) items.push_back(cur);
+            for (const std::string& it : items) {
+                if (!map) {
+                    out.push_back(yaml_scalar(it));
+                    continue;
+                }
+                const std::string e = trim(it);
+                const size_t ke = yaml_key_end(e + " ");
+                if (ke == std::string::npos) throw std::runtime_error("flow mapping entry without a key: " + e);
+                out[yaml_scalar(e.substr(0, ke)).scalar_text()] = yaml_scalar(e.substr(ke + 1));
+            }
+            return out;
+        }
+        if (t == "true" || t == "True" || t == "yes" || t == "Yes" || t == "on") return Json(true);
+        if (t == "false" || t == "False" || t == "no" || t == "No" || t == "off") return Json(false);
+        char* end = nullptr;
+        errno = 0;
+        const long long iv = std::strtoll(t.c_str(), &end, 10);
+        if (errno == 0 && end != t.c_str() && *end == 0) return Json((int64_t)iv);
+        const double dv = std::strtod(t.c_str(), &end);
+        if (end != t.c_str() && *end == 0) return Json(dv);
+        return Json(t);
+    }
+    // text of a scalar used as a mapping key
+    std::string scalar_text() const {
+        if (type_ == STR) return str_;
+        if (type_ == NUL) return "null";
+        if (type_ == BOOL) return num_ != 0 ? "true" : "false";
+        return dump();
+    }
+    static Json yaml_node(std::vector<YamlLine>& lines, size_t& i, int indent, int depth) {
+        if (depth > kMaxDepth) throw std::runtime_error("nested too deeply");
+        if (yaml_is_dash(lines[i].text)) {
+            Json arr = array();
+            while (i < lines.size() && lines[i].indent == indent && yaml_is_dash(lines[i].text)) {
+                const std::string rest = trim(lines[i].text.substr(1));
+                if (rest.empty()) {
+                    ++i;
+                    if (i < lines.size() && lines[i].indent > indent) arr.push_back(yaml_node(lines, i, lines[i].indent, depth + 1));
+                    else arr.push_back(Json());
+                } else if (yaml_key_end(rest) != std::string::npos) {
+                    // "- key: value": a mapping whose first entry sits on the dash line, two columns further in
+                    lines[i].indent = indent + 2;
+                    lines[i].text = rest;
+                    arr.push_back(yaml_node(lines, i, indent + 2, depth + 1));
+                } else {
+                    arr.push_back(yaml_scalar(rest));
+                    ++i;
+                }
+            }
+            return arr;
+        }
+        Json obj = object();
+        while (i < lines.size() && lines[i].indent == indent && !yaml_is_dash(lines[i].text)) {
+            const std::string& t = lines[i].text;
+            const size_t ke = yaml_key_end(t);
+            if (ke == std::string::npos) throw std::runtime_error("expected 'key: value' in line " + std::to_string(lines[i].number));
+            const std::string key = yaml_scalar(t.substr(0, ke)).scalar_text();
+            const std::string val = trim(t.substr(ke + 1));
+            ++i;
+            if (!val.empty()) {
+                obj[key] = yaml_scalar(val);
+            } else if (i < lines.size() && lines[i].indent > indent) {
+                obj[key] = yaml_node(lines, i, lines[i].indent, depth + 1);
+            } else if (i < lines.size() && lines[i].indent == indent && yaml_is_dash(lines[i].text)) {
+                obj[key] = yaml_node(lines, i, indent, depth + 1);   // a sequence may sit at its key's indentation
+            } else {
+                obj[key] = Json();
+            }
+        }
+        return obj;
+    }
+
     static void skip_ws(const std::string& s, size_t& p) {
         while (p < s.size() && (s[p] == ' ' || s[p] == '\n' || s[p] == '\t' || s[p] == '\r')) ++p;
     }

@@ -74,7 +74,7 @@ public:
         Json placement;
         PSB_RETURN_IF_ERROR(place(shard_num, replica_num, nodes, current_load(), &placement));
         Json op_cfg;
-        if (!Json::parse(op_config_json.empty() ? "{}" : op_config_json, &op_cfg)) return Status::InvalidConfig("op_config JSON does not parse");
+        if (!Json::parse_config(op_config_json.empty() ? "{}" : op_config_json, &op_cfg)) return Status::InvalidConfig("op_config parses neither as JSON nor as YAML");
         Json cfg = Json::object();
         cfg["nodes"] = placement;
         cfg["op_config"] = op_cfg;

@@ -19,7 +19,7 @@ public:
     Status create_storage(const std::string& lib, const std::string& op, const std::string& op_config_json, int shard_num,
                           int32_t* sid) {
         Json cfg = Json::object(), opc;
-        if (!Json::parse(op_config_json.empty() ? "{}" : op_config_json, &opc)) return Status::InvalidConfig("op_config JSON does not parse");
+        if (!Json::parse_config(op_config_json.empty() ? "{}" : op_config_json, &opc)) return Status::InvalidConfig("op_config parses neither as JSON nor as YAML");
         Json node = Json::object();
         node["g_rank"] = 0;
         Json sl = Json::array();

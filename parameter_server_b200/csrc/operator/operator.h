@@ -59,8 +59,8 @@ public:
     Status create(const std::string& lib, const std::string& op, const std::string& config_str,
                   std::shared_ptr<Operator>* out) {
         Json cfg = Json::object();
-        if (!config_str.empty() && !Json::parse(config_str, &cfg))
-            return Status::InvalidConfig("operator config of " + lib + "/" + op + " is not valid JSON");
+        if (!config_str.empty() && !Json::parse_config(config_str, &cfg))
+            return Status::InvalidConfig("operator config of " + lib + "/" + op + " is neither valid JSON nor YAML");
         Producer p;
         {
             std::lock_guard<std::mutex> g(mu_);

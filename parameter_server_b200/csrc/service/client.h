@@ -146,7 +146,7 @@ public:
     Status create_storage(const std::string& lib, const std::string& op, const std::string& cfg_json, int32_t* sid,
                           int timeout_ms = 30000) {
         Json cfg;
-        if (!Json::parse(cfg_json, &cfg)) return Status::InvalidConfig("storage config is not valid JSON");
+        if (!Json::parse_config(cfg_json, &cfg)) return Status::InvalidConfig("storage config is neither valid JSON nor YAML");
         PSB_RETURN_IF_ERROR(master_.generate_id(STORAGE_ID_KEY, sid));
         std::shared_ptr<TableEntry> e;
         PSB_RETURN_IF_ERROR(ctx_.create_storage(*sid, lib, op, cfg, -1, &e));

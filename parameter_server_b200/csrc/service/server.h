@@ -828,7 +828,7 @@ private:
         std::string lib, op, cfg_str;
         in >> lib >> op >> cfg_str;
         Json cfg;
-        if (!Json::parse(cfg_str, &cfg)) return Status::InvalidConfig("storage config is not valid JSON");
+        if (!Json::parse_config(cfg_str, &cfg)) return Status::InvalidConfig("storage config is neither valid JSON nor YAML");
         std::shared_ptr<TableEntry> e;
         PSB_RETURN_IF_ERROR(ctx_.create_storage(meta.sid, lib, op, cfg, node_id_, &e));
         if (std::string(e->storage_op->kind()) != "storage") return Status::InvalidConfig(op + " is not a storage operator");

@@ -69,6 +69,12 @@ def nodes_json(nodes: Dict[int, Sequence[int]]) -> str:
     return json.dumps([{"g_rank": int(n), "shard_list": [int(s) for s in shards]} for n, shards in nodes.items()])
 
 
+def config_to_json(text: str) -> str:
+    """A config text as the native layer reads it, as JSON: operator and storage configs may be written as JSON or as
+    YAML (block mappings / sequences, flow sequences, scalars, comments)."""
+    return C.config_to_json(text)
+
+
 def standard_ops(compress: str = "", block_size: int = 1000) -> List["C.OpSpec"]:
     """The usual operator set of a sparse table (what the reference's tests register one by one)."""
     c = json.dumps({"compress_algorithm": compress, "block_size": block_size})
