@@ -280,8 +280,9 @@ private:
                     ++i;
                     if (i < lines.size() && lines[i].indent > indent) arr.push_back(yaml_node(lines, i, lines[i].indent, depth + 1));
                     else arr.push_back(Json());
-                } else if (yaml_key_end(rest) != std::string::npos) {
-                    // "- key: value": a mapping whose first entry sits on the dash line, two columns further in
+                } else if (yaml_is_dash(rest) || yaml_key_end(rest) != std::string::npos) {
+                    // "- key: value" (or "- - item"): a mapping (sequence) whose first entry sits on the dash line, two
+                    // columns further in
                     lines[i].indent = indent + 2;
                     lines[i].text = rest;
                     arr.push_back(yaml_node(lines, i, indent + 2, depth + 1));

@@ -72,3 +72,29 @@ op_config:
         for s in servers:
             s.stop()
         master.stop()
+
+
+def _scalars():
+    from hypothesis import strategies as st
+    plain = st.text(alphabet="abcdefghijklmnopqrstuvwxyzABCXYZ_0123456789./-", min_size=1, max_size=12).filter(
+        lambda s: s[0].isalpha() and s.lower() not in ("true", "false", "yes", "no", "on", "off", "null", "y", "n"))
+    return st.one_of(st.integers(-10**9, 10**9), st.booleans(), st.none(), plain,
+                     st.floats(allow_nan=False, allow_infinity=False, width=32).map(lambda x: round(x, 3)))
+
+
+def test_generated_documents_round_trip_like_pyyaml():
+    """Nested mappings / sequences of scalars, written by PyYAML in block style, read back by the native parser."""
+    from hypothesis import given, settings, strategies as st
+    keys = st.text(alphabet="abcdefghijklmnopqrstuvwxyz_", min_size=1, max_size=8).filter(
+        lambda s: s not in ("true", "false", "yes", "no", "on", "off", "null", "y", "n"))
+    tree = st.recursive(_scalars(), lambda ch: st.one_of(st.lists(ch, max_size=4), st.dictionaries(keys, ch, max_size=4)), max_leaves=12)
+    docs = st.dictionaries(keys, tree, min_size=1, max_size=5)
+
+    @settings(max_examples=200, deadline=None)
+    @given(docs)
+    def check(doc):
+        text = yaml.safe_dump(doc, default_flow_style=False)
+        got = json.loads(S.config_to_json(text))
+        assert got == yaml.safe_load(text), text
+
+    check()
