@@ -28,6 +28,8 @@ void bind_host(py::module_& m) {
         .def_readwrite("slot_init0", &HostTableConfig::slot_init0)
         .def_readwrite("slot_init1", &HostTableConfig::slot_init1)
         .def_readwrite("expected_max_items", &HostTableConfig::expected_max_items)
+        .def_readwrite("index_grow_ratio", &HostTableConfig::index_grow_ratio)
+        .def_readwrite("index_shrink_ratio", &HostTableConfig::index_shrink_ratio)
         .def_readwrite("soft_limit_bytes", &HostTableConfig::soft_limit_bytes)
         .def_readwrite("hard_limit_bytes", &HostTableConfig::hard_limit_bytes);
 

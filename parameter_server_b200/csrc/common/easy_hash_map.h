@@ -2,7 +2,8 @@
 // and inside the host storage shards.
 //
 // Parity: same contract as pico-ps/common/EasyHashMap.h:18-247 - power-of-two bucket count, load
-// factor kept at or below 1/2, triangular probing (step grows by one each probe), one reserved
+// factor kept at or below 1/2 (the default; set_max_load changes it, the `grow_ratio` of the reference's storage
+// configs, pico-ps/storage/KVShardStorage.h:444-452,881-897), triangular probing (step grows by one each probe), one reserved
 // "empty" key, try_emplace / force_emplace / find / at / clear / reserve. Erase (not in the
 // reference's map) is added with backward-shift-free tombstones because the host storage needs it.
 #pragma once
@@ -35,6 +36,26 @@ public:
         if (b > table_.size()) rehash(b);
     }
 
+    // Highest load (live entries + tombstones over buckets) before the table doubles. Kept inside [0.25, 0.85]:
+    // triangular probing over a power-of-two table reaches every bucket, so any load below 1 ends, but probes get
+    // long near it.
+    void set_max_load(double f) {
+        max_load_ = f < 0.25 ? 0.25 : (f > 0.85 ? 0.85 : f);
+        if ((double)used_ > max_load_ * (double)table_.size()) rehash(buckets_for(size_));
+    }
+    double max_load() const { return max_load_; }
+
+    // Rebuild into the smallest table that holds the live entries when they fill less than `min_load` of the buckets
+    // (also drops the tombstones). Invalidates bucket cursors, like growth does. Returns whether it rebuilt.
+    bool shrink_if_below(double min_load) {
+        if (min_load <= 0.0 || table_.size() <= 8) return false;
+        if ((double)size_ >= min_load * (double)table_.size()) return false;
+        const size_t want = buckets_for(size_);
+        if (want >= table_.size()) return false;
+        rehash(want);
+        return true;
+    }
+
     void clear() {
         // shrink when the table is much larger than what it held (keeps clear() cheap for small batches)
         size_t want = buckets_for(size_);
@@ -49,7 +70,7 @@ public:
 
     // Returns (entry*, inserted)
     std::pair<Entry*, bool> try_emplace(const K& key, const V& value = V()) {
-        if ((used_ + 1) * 2 > table_.size()) rehash(table_.size() * 2);
+        if ((double)(used_ + 1) > max_load_ * (double)table_.size()) rehash(used_ > size_ * 2 + 8 ? table_.size() : table_.size() * 2);
         size_t mask = table_.size() - 1;
         size_t p = (size_t)slot_hash((int64_t)key) & mask;
         Entry* first_tomb = nullptr;
@@ -106,9 +127,9 @@ public:
     bool live(const Entry& e) const { return e.first != empty_ && e.first != tomb_; }
 
 private:
-    static size_t buckets_for(size_t n) {
+    size_t buckets_for(size_t n) const {
         size_t b = 8;
-        while (b < 2 * n) b <<= 1;
+        while ((double)n > max_load_ * (double)b) b <<= 1;
         return b;
     }
     void rehash(size_t nb) {
@@ -122,6 +143,7 @@ private:
     }
 
     K empty_, tomb_;
+    double max_load_ = 0.5;
     std::vector<Entry> table_;
     size_t size_ = 0;  // live entries
     size_t used_ = 0;  // live + tombstones (drives growth)

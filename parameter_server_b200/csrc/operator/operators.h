@@ -95,10 +95,24 @@ public:
         h.slot_init0 = opt_.slot_init0;
         h.slot_init1 = opt_.slot_init1;
         h.soft_limit_bytes = h.hard_limit_bytes = (uint64_t)config_.at("memory_limit").as_int(0);
-        // "expected_max_items": N, or the reference's spelling "pool_hash_map": {"expected_max_items": N}
+        // Index sizing, under the plain names or under the reference's sections `pool_hash_map` (its default
+        // storage) and `google_dense_hash_map` (pico-ps/storage/KVShardStorage.h:439-456,880-897); the pool section
+        // wins where both are given, as it does there.
+        const Json& pool = config_.at("pool_hash_map");
+        const Json& gdh = config_.at("google_dense_hash_map");
         h.expected_max_items = (uint64_t)std::max<int64_t>(0, config_.at("expected_max_items").as_int(
-            config_.at("pool_hash_map").at("expected_max_items").as_int(0)));
+            pool.at("expected_max_items").as_int(gdh.at("expected_max_items").as_int(0))));
+        h.index_grow_ratio = config_.at("grow_ratio").as_double(pool.at("grow_ratio").as_double(gdh.at("grow_ratio").as_double(0.0)));
+        h.index_shrink_ratio = config_.at("shrink_ratio").as_double(gdh.at("shrink_ratio").as_double(0.0));
         return h;
+    }
+    // Whether this node's saved image of the table outlives the table's deletion. The reference's persistent-memory
+    // storage keeps or removes its pool when it is destroyed by `pmem_create_storage.retain_dcpmm_data_after_deconstruction`
+    // (pico-ps/storage/DCPmemory.h:355-365,378-385); the `storage_id` of that section is filled in by the server there
+    // and here alike, so a value given by the user is ignored.
+    bool retain_local_image() const {
+        return config_.at("retain_local_image").as_bool(
+            config_.at("pmem_create_storage").at("retain_dcpmm_data_after_deconstruction").as_int(0) != 0);
     }
     // Server side: build the storage and create the local shards.
     Status create_storage(int32_t n_shards, const std::set<int32_t>& local_shards, std::unique_ptr<KVStorage>* out) const {

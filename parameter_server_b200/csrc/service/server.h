@@ -706,6 +706,9 @@ private:
             case RequestType::STORAGE_DELETE: {
                 auto gone = ctx_.get(meta.sid);
                 const bool followed = gone && gone->sync_enabled;
+                // the table's saved image goes with it, unless its storage config asks to keep it
+                if (gone && gone->storage_op && !cfg_.local_image_dir.empty() && !storage_op_of(*gone)->retain_local_image())
+                    ::unlink(image_path(cfg_.local_image_dir, node_id_, meta.sid).c_str());
                 ctx_.erase(meta.sid);
                 PSB_LOG(INFO) << "storage " << meta.sid << " deleted on node " << node_id_;
                 if (followed) notify_sync(meta.sid, true);

@@ -10,11 +10,13 @@
 // iteration (pico-ps/storage/KVShardStorage.h:52-92) and a byte budget that turns into
 // OUT_OF_MEMORY (pico-ps/storage/Storage.cpp:114-136).
 #pragma once
+#include <algorithm>
 #include <atomic>
 #include <cstdint>
 #include <map>
 #include <memory>
 #include <mutex>
+#include <set>
 #include <shared_mutex>
 #include <vector>
 
@@ -42,6 +44,11 @@ struct HostTableConfig {
     // the index is not rebuilt again and again while the table fills (`pool_hash_map.expected_max_items` of the
     // reference's default storage, pico-ps/storage/KVShardStorage.h:881-897).
     uint64_t expected_max_items = 0;
+    // Load of a shard's index before it doubles (0 = the default 1/2), and the load under which the index is rebuilt
+    // smaller after keys were erased (0 = never): `grow_ratio` / `shrink_ratio` of the reference's storage configs
+    // (pico-ps/storage/KVShardStorage.h:425-429,444-449,863-866).
+    double index_grow_ratio = 0.0;
+    double index_shrink_ratio = 0.0;
 };
 
 constexpr int64_t kHostEmptyKey = (int64_t)0x8000000000000000ull;
@@ -86,6 +93,7 @@ public:
         std::unique_lock<std::shared_mutex> g(mu_);
         if (!shards_.count(s)) {
             shards_[s].reset(new Shard());
+            if (cfg_.index_grow_ratio > 0.0) shards_[s]->map.set_max_load(cfg_.index_grow_ratio);
             if (cfg_.expected_max_items) {
                 const uint64_t share = cfg_.expected_max_items / (uint64_t)std::max<int32_t>(1, cfg_.n_shards);
                 shards_[s]->map.reserve((size_t)(share + share / 8 + 16));   // shards are not perfectly even
@@ -255,12 +263,14 @@ public:
 
     uint64_t erase_keys(const int64_t* keys, size_t n) {
         uint64_t erased = 0;
+        std::set<Shard*> thinned;
         for (size_t i = 0; i < n; ++i) {
             Shard* sh = get(shard_of(keys[i]));
             if (!sh) continue;
             std::unique_lock<std::shared_mutex> g(sh->mu);
             auto* e = sh->map.find(keys[i]);
             if (!e) continue;
+            if (cfg_.index_shrink_ratio > 0.0) thinned.insert(sh);
             uint32_t row = e->second;
             sh->map.erase(keys[i]);
             sh->free_rows.push_back(row);
@@ -272,6 +282,10 @@ public:
             ++erased;
         }
         n_items_ -= erased;
+        for (Shard* sh : thinned) {   // safe_shrink of the reference (pico-ps/storage/KVShardStorage.h:786-834)
+            std::unique_lock<std::shared_mutex> g(sh->mu);
+            sh->map.shrink_if_below(std::min(cfg_.index_shrink_ratio, 0.5 * sh->map.max_load()));
+        }
         return erased;
     }
 

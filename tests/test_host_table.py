@@ -206,3 +206,43 @@ def test_expected_max_items_sizes_the_index_up_front():
     big.create_shard(1)
     big.set_rows(keys, np.zeros((20_000, 4), np.float32), False)
     assert buckets(big) == before                                     # filling it did not rebuild the index
+
+
+def test_grow_and_shrink_ratio_of_the_index():
+    """`grow_ratio` is the load at which a shard's index doubles, `shrink_ratio` the load under which it is rebuilt
+    smaller after keys were erased (the resizing parameters of the reference's storage configs)."""
+    buckets = lambda t: t.export_shard(0, 0, 1 << 30, False)[2]
+    n = 3000
+    keys = np.arange(n, dtype=np.int64)
+    sizes = {}
+    for grow in (0.0, 0.25, 0.8, 2.0):
+        hc = C.HostTableConfig()
+        hc.dim, hc.n_shards = 4, 1
+        hc.index_grow_ratio = grow
+        t = C.HostTable(hc)
+        t.create_shard(0)
+        t.set_rows(keys, np.ones((n, 4), np.float32), True)
+        sizes[grow] = buckets(t)
+        load = n / buckets(t)
+        assert load <= (min(max(grow, 0.25), 0.85) if grow else 0.5) + 1e-9
+        rows, found = t.get_rows(keys, True)
+        assert found.all() and np.all(rows[:, :4] == 1.0)
+    assert sizes[0.25] > sizes[0.0] >= sizes[0.8] == sizes[2.0]       # 2.0 is clamped: open addressing needs room
+    for shrink in (0.0, 0.2):
+        hc = C.HostTableConfig()
+        hc.dim, hc.n_shards = 4, 1
+        hc.index_shrink_ratio = shrink
+        t = C.HostTable(hc)
+        t.create_shard(0)
+        t.set_rows(keys, np.ones((n, 4), np.float32), True)
+        full = buckets(t)
+        assert t.erase_keys(keys[100:]) == n - 100
+        if shrink:
+            assert buckets(t) < full and 100 / buckets(t) <= 0.5
+        else:
+            assert buckets(t) == full
+        rows, found = t.get_rows(keys, True)
+        assert found[:100].all() and not found[100:].any()
+        t.set_rows(keys, 2 * np.ones((n, 4), np.float32), True)      # grows back
+        rows, found = t.get_rows(keys, True)
+        assert found.all() and np.all(rows[:, :4] == 2.0) and t.size() == n

@@ -924,6 +924,38 @@ def test_sync_pred_backs_off_and_resumes_after_the_predictor_comes_back():
         cl.close()
 
 
+def test_deleting_a_table_removes_its_image_unless_retained(tmp_path):
+    """A table's saved image goes with the table; `pmem_create_storage.retain_dcpmm_data_after_deconstruction` (the
+    reference's spelling) or `retain_local_image` keeps it. The index ratios of the reference's storage sections are
+    accepted on the same config."""
+    cfg = S.ServerConfig()
+    cfg.local_image_dir = str(tmp_path / "images")
+    master = S.Master()
+    server = S.Server(master.address(), cfg)
+    client = S.Client(master.address())
+    try:
+        nid = server.node_id()
+        plain = op_cfg()
+        plain["google_dense_hash_map"] = {"shrink_ratio": 0.2, "grow_ratio": 0.7, "expected_max_items": 1000}
+        kept = op_cfg()
+        kept["pmem_create_storage"] = {"storage_id": 7, "retain_dcpmm_data_after_deconstruction": 1}
+        sids = []
+        for c in (plain, kept):
+            st, sid = client.create_storage(S.LIB, "SparseTableStorageOperator", S.storage_config({nid: [0, 1]}, c))
+            assert st.ok(), st
+            sids.append(sid)
+        st, n = server.save_local_images()
+        assert st.ok() and n == 2
+        imgs = [tmp_path / "images" / f"node_{nid}" / f"storage_{sid}.img" for sid in sids]
+        assert all(p.exists() for p in imgs)
+        for sid in sids:
+            assert client.delete_storage(sid).ok()
+        assert not imgs[0].exists() and imgs[1].exists()
+    finally:
+        server.stop()
+        master.stop()
+
+
 def test_restore_from_the_hosts_own_image_when_no_replica(tmp_path):
     """No replica, no dump: the replacement server opens the persistent image that the dead node left on this host
     (the role of the reference's persistent-memory pool). An image of another data layout is refused."""
