@@ -122,6 +122,7 @@ void bind_host(py::module_& m) {
                  return py::make_tuple(out, found);
              })
         .def("erase_keys", [](HostTable& t, KeyArray keys) { return t.erase_keys(keys.data(), (size_t)keys.size()); })
+        .def("layout_epoch", &HostTable::layout_epoch)
         .def("export_shard",
              [](HostTable& t, int s, size_t cursor, size_t window, bool dirty_only) {
                  std::vector<int64_t> keys;

@@ -44,6 +44,8 @@ public:
         if ((double)used_ > max_load_ * (double)table_.size()) rehash(buckets_for(size_));
     }
     double max_load() const { return max_load_; }
+    // Counts the rebuilds of the bucket array: a bucket cursor taken under one value is meaningless under another.
+    uint64_t generation() const { return generation_; }
 
     // Rebuild into the smallest table that holds the live entries when they fill less than `min_load` of the buckets
     // (also drops the tombstones). Invalidates bucket cursors, like growth does. Returns whether it rebuilt.
@@ -61,6 +63,7 @@ public:
         size_t want = buckets_for(size_);
         if (table_.size() > 4 * want) {
             table_.assign(want, Entry{empty_, V()});
+            ++generation_;
         } else {
             for (auto& e : table_) e.first = empty_;
         }
@@ -135,6 +138,7 @@ private:
     void rehash(size_t nb) {
         std::vector<Entry> old;
         old.swap(table_);
+        ++generation_;
         table_.assign(nb, Entry{empty_, V()});
         size_ = 0;
         used_ = 0;
@@ -147,6 +151,7 @@ private:
     std::vector<Entry> table_;
     size_t size_ = 0;  // live entries
     size_t used_ = 0;  // live + tombstones (drives growth)
+    uint64_t generation_ = 0;
 };
 
 }  // namespace psb

@@ -652,17 +652,13 @@ public:
         KVStorage* st = e.storage.get();
         const uint32_t dim = st->dim(), stride = st->stride();
         *result = init_result(carried);
-        uint64_t cursor = 0;
-        bool finished = false;
-        std::vector<int64_t> keys;
-        std::vector<float> rows;
-        while (!finished) {
-            keys.clear();
-            rows.clear();
-            PSB_RETURN_IF_ERROR(st->export_shard(shard, cursor, 1 << 16, false, &keys, &rows, &cursor, &finished));
-            for (size_t i = 0; i < keys.size(); ++i) for_each(keys[i], rows.data() + i * stride, dim, stride, carried, result);
-        }
-        return Status::Ok();
+        return st->scan_shard(
+            shard, 1 << 16, false,
+            [&](const std::vector<int64_t>& keys, const std::vector<float>& rows) {
+                for (size_t i = 0; i < keys.size(); ++i) for_each(keys[i], rows.data() + i * stride, dim, stride, carried, result);
+                return Status::Ok();
+            },
+            [&] { *result = init_result(carried); });
     }
 };
 
@@ -740,17 +736,16 @@ public:
         KVStorage* st = e.storage.get();
         PSB_RETURN_IF_ERROR(check_carried(*st, carried));
         const uint32_t dim = st->dim(), stride = st->stride();
-        uint64_t cursor = 0;
-        bool finished = false;
-        std::vector<int64_t> keys, doomed;
-        std::vector<float> rows;
-        while (!finished) {
-            keys.clear();
-            rows.clear();
-            PSB_RETURN_IF_ERROR(st->export_shard(shard, cursor, 1 << 16, false, &keys, &rows, &cursor, &finished));
-            for (size_t i = 0; i < keys.size(); ++i)
-                if (erase_if(keys[i], rows.data() + i * stride, dim, stride, carried)) doomed.push_back(keys[i]);
-        }
+        // the doomed keys are collected during the scan and erased after it: the scan holds the shard for reading
+        std::vector<int64_t> doomed;
+        PSB_RETURN_IF_ERROR(st->scan_shard(
+            shard, 1 << 16, false,
+            [&](const std::vector<int64_t>& keys, const std::vector<float>& rows) {
+                for (size_t i = 0; i < keys.size(); ++i)
+                    if (erase_if(keys[i], rows.data() + i * stride, dim, stride, carried)) doomed.push_back(keys[i]);
+                return Status::Ok();
+            },
+            [&] { doomed.clear(); }));
         *erased = 0;
         if (!doomed.empty()) PSB_RETURN_IF_ERROR(st->erase_keys(doomed.data(), doomed.size(), erased));
         return Status::Ok();
@@ -977,18 +972,14 @@ public:
         KVStorage* st = e.storage.get();
         DsWriter w(dir + "/model_" + std::to_string(node_id) + "_" + std::to_string(file_id), format, st->stride(), &comp_);
         *n_records = 0;
-        std::vector<int64_t> keys;
-        std::vector<float> rows;
+        // every shard is written as one snapshot: its writers wait while it is read, as under the write lock that
+        // the reference holds per shard (pico-ps/operator/DumpOperator.h:170-190)
         for (int32_t s : shards) {
-            uint64_t cursor = 0;
-            bool finished = false;
-            while (!finished) {
-                keys.clear();
-                rows.clear();
-                PSB_RETURN_IF_ERROR(st->export_shard(s, cursor, 1 << 16, false, &keys, &rows, &cursor, &finished));
+            PSB_RETURN_IF_ERROR(st->scan_shard(s, 1 << 16, false, [&](const std::vector<int64_t>& keys, const std::vector<float>& rows) {
                 for (size_t i = 0; i < keys.size(); ++i) w.write(keys[i], rows.data() + i * st->stride());
                 *n_records += keys.size();
-            }
+                return Status::Ok();
+            }));
         }
         return w.close();
     }

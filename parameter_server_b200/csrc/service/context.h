@@ -31,6 +31,7 @@ struct IncrementStorage {
 struct RestoreIterator {
     int shard = -1;
     uint64_t cursor = 0;
+    uint64_t epoch = 0;   // KVStorage::layout_epoch of the shard when the cursor was taken
 };
 
 struct TableEntry {

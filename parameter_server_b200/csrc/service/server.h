@@ -373,21 +373,15 @@ public:
                 f.write((const char*)&stride, 4);
                 const auto n_pos = f.tellp();
                 f.write((const char*)&n, 8);
-                std::vector<int64_t> keys;
-                std::vector<float> rows;
                 for (int s : e->storage->shard_list()) {
-                    uint64_t cursor = 0;
-                    bool finished = false;
-                    while (!finished) {
-                        keys.clear();
-                        rows.clear();
-                        PSB_RETURN_IF_ERROR(e->storage->export_shard(s, cursor, 1 << 14, false, &keys, &rows, &cursor, &finished));
+                    PSB_RETURN_IF_ERROR(e->storage->scan_shard(s, 1 << 14, false, [&](const std::vector<int64_t>& keys, const std::vector<float>& rows) {
                         for (size_t i = 0; i < keys.size(); ++i) {
                             f.write((const char*)&keys[i], 8);
                             f.write((const char*)(rows.data() + i * stride), (std::streamsize)stride * 4);
                         }
                         n += keys.size();
-                    }
+                        return Status::Ok();
+                    }));
                 }
                 f.seekp(n_pos);
                 f.write((const char*)&n, 8);
@@ -1023,22 +1017,43 @@ private:
         uint64_t offset = 0, batch = 0;
         in >> iterator_id >> offset >> batch >> shard;
         if (!e.storage || !e.storage->has_shard(shard)) return Status::InvalidID("restore: shard is not on this node");
+        // The iterator remembers under which layout of the index its cursor was taken. Pushes go on between two
+        // batches and may make the index rebuild itself; the cursor then means nothing, and the iteration starts over
+        // from the first bucket (the restoring side overwrites, so rows that it gets twice do no harm). A cursor that
+        // comes without a known iterator (this server was restarted in between) starts over as well.
+        uint64_t epoch = 0;
+        bool known = false;
         {
             std::lock_guard<std::mutex> ig(e.iter_mu);
-            if (iterator_id < 0 || !e.restore_iters.count(iterator_id)) {
+            auto it = iterator_id < 0 ? e.restore_iters.end() : e.restore_iters.find(iterator_id);
+            if (it != e.restore_iters.end() && it->second.shard == shard) {
+                epoch = it->second.epoch;
+                known = true;
+            } else {
                 iterator_id = e.next_iter_id++;
-                e.restore_iters[iterator_id] = RestoreIterator{shard, offset};
+                e.restore_iters[iterator_id] = RestoreIterator{shard, 0, 0};
             }
         }
         std::vector<int64_t> keys;
         std::vector<float> rows;
         uint64_t next = offset;
         bool finished = false;
-        PSB_RETURN_IF_ERROR(e.storage->export_shard(shard, offset, std::max<uint64_t>(batch, 1), false, &keys, &rows, &next, &finished));
+        for (int attempt = 0;; ++attempt) {
+            const uint64_t now = e.storage->layout_epoch(shard);
+            if (!known || now != epoch) offset = 0;
+            keys.clear();
+            rows.clear();
+            PSB_RETURN_IF_ERROR(e.storage->export_shard(shard, offset, std::max<uint64_t>(batch, 1), false, &keys, &rows, &next, &finished));
+            epoch = now;
+            known = true;
+            if (e.storage->layout_epoch(shard) == now) break;   // nothing moved under the export
+            known = false;
+            if (attempt == 8) return Status::Error("restore: the index of shard " + std::to_string(shard) + " keeps being rebuilt");
+        }
         {
             std::lock_guard<std::mutex> ig(e.iter_mu);
             if (finished) e.restore_iters.erase(iterator_id);
-            else e.restore_iters[iterator_id].cursor = next;
+            else e.restore_iters[iterator_id] = RestoreIterator{shard, next, epoch};
         }
         *out << e.sid << shard << (int32_t)(finished ? 1 : 0) << iterator_id << next << (uint64_t)keys.size() << (int32_t)e.storage->stride();
         out->write_raw(keys.data(), keys.size() * 8);

@@ -223,6 +223,12 @@ public:
         return Status::Ok();
     }
 
+    // slot cursors hold until the index is rebuilt larger
+    uint64_t layout_epoch(int) override {
+        std::lock_guard<std::mutex> g(mu_);
+        return table_->grow_count();
+    }
+
     Status erase_keys(const int64_t* keys, size_t n, uint64_t* erased) override {
         std::lock_guard<std::mutex> g(mu_);
         PSB_RETURN_IF_ERROR(screen_keys(keys, n));

@@ -57,6 +57,7 @@ class HostTable {
 public:
     struct Shard {
         explicit Shard() : map(kHostEmptyKey) {}
+        uint64_t born = 0;                   // which creation of a shard of this table this is (see layout_epoch)
         EasyHashMap<int64_t, uint32_t> map;
         std::vector<float> rows;
         std::vector<uint32_t> free_rows;
@@ -93,6 +94,7 @@ public:
         std::unique_lock<std::shared_mutex> g(mu_);
         if (!shards_.count(s)) {
             shards_[s].reset(new Shard());
+            shards_[s]->born = ++shards_born_;
             if (cfg_.index_grow_ratio > 0.0) shards_[s]->map.set_max_load(cfg_.index_grow_ratio);
             if (cfg_.expected_max_items) {
                 const uint64_t share = cfg_.expected_max_items / (uint64_t)std::max<int32_t>(1, cfg_.n_shards);
@@ -310,6 +312,44 @@ public:
         return end;
     }
 
+    // Scan of a whole shard as one snapshot: the shard's read lock is held from the first window to the last, so
+    // pushes and inserting pulls of that shard wait until the scan is over, while reads go on - what the reference
+    // gets by iterating a shard under its lock (pico-ps/operator/DumpOperator.h:170-190,
+    // pico-ps/operator/ForEachOperator.h:182-191). `fn(keys, rows)` sees at most `window` buckets' entries per call
+    // and must not touch this table.
+    template <class F>
+    Status scan_shard(int s, size_t window, bool dirty_only, F&& fn) const {
+        Shard* sh = get(s);
+        if (!sh) return Status::Ok();
+        std::shared_lock<std::shared_mutex> g(sh->mu);
+        const auto& b = sh->map.buckets();
+        std::vector<int64_t> keys;
+        std::vector<float> rows;
+        window = std::max<size_t>(window, 1);
+        for (size_t cursor = 0; cursor < b.size(); cursor += window) {
+            keys.clear();
+            rows.clear();
+            const size_t end = std::min(b.size(), cursor + window);
+            for (size_t i = cursor; i < end; ++i) {
+                if (!sh->map.live(b[i])) continue;
+                if (dirty_only && !sh->dirty[b[i].second]) continue;
+                keys.push_back(b[i].first);
+                const float* w = sh->rows.data() + (size_t)b[i].second * stride_;
+                rows.insert(rows.end(), w, w + stride_);
+            }
+            if (!keys.empty()) PSB_RETURN_IF_ERROR(fn(keys, rows));
+        }
+        return Status::Ok();
+    }
+    // Changes whenever the bucket cursors of export_shard lose their meaning for shard `s`: the index was rebuilt
+    // (growth, shrink, clear) or the shard was dropped and created again.
+    uint64_t layout_epoch(int s) const {
+        Shard* sh = get(s);
+        if (!sh) return 0;
+        std::shared_lock<std::shared_mutex> g(sh->mu);
+        return (sh->born << 32) + sh->map.generation();
+    }
+
     uint64_t shard_size(int s) const {
         Shard* sh = get(s);
         if (!sh) return 0;
@@ -504,6 +544,7 @@ private:
     std::atomic<bool> healthy_{true};
     std::atomic<uint64_t> n_parked_{0};
     std::atomic<uint32_t> fail_period_{0}, fail_counter_{0};
+    uint64_t shards_born_ = 0;   // under mu_
     std::atomic<uint64_t> failed_extra_{0}, failed_at_bytes_{0};   // the growth that made the table unhealthy
     std::atomic<bool> track_dirty_{false};   // may be switched on while pushes run (a follower table appears)
 };

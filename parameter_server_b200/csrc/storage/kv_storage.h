@@ -7,6 +7,7 @@
 // fp32 rows [embedding | optimizer slots | optional sync delta] so that one interface serves both
 // back-ends.
 #pragma once
+#include <functional>
 #include <memory>
 #include <vector>
 
@@ -61,6 +62,34 @@ public:
     virtual Status export_shard(int s, uint64_t cursor, uint64_t window, bool dirty_only, std::vector<int64_t>* keys,
                                 std::vector<float>* rows, uint64_t* next_cursor, bool* finished) = 0;
     virtual Status erase_keys(const int64_t* keys, size_t n, uint64_t* erased) = 0;
+    // A number that changes whenever cursors of export_shard lose their meaning for shard s (the index was rebuilt).
+    // A resumable scan that spans several requests compares it between windows and starts over when it moved.
+    virtual uint64_t layout_epoch(int /*s*/) { return 0; }
+    // Scan of a whole shard, entries handed to `fn` in windows (rows: stride floats per key). `fn` must not call into
+    // this storage. A host shard is read as one snapshot under its lock. This default walks export_shard windows: when
+    // the index is rebuilt between two of them, the scan starts over after `restart()` (the consumer forgets what it
+    // got) - or fails with an error when the consumer cannot forget (`restart` empty), so the caller runs it again.
+    using ScanFn = std::function<Status(const std::vector<int64_t>& keys, const std::vector<float>& rows)>;
+    virtual Status scan_shard(int s, uint64_t window, bool dirty_only, const ScanFn& fn, const std::function<void()>& restart = nullptr) {
+        std::vector<int64_t> keys;
+        std::vector<float> rows;
+        for (int attempt = 0; attempt < 8; ++attempt) {
+            const uint64_t epoch = layout_epoch(s);
+            uint64_t cursor = 0;
+            bool finished = false, moved = false;
+            while (!finished && !moved) {
+                keys.clear();
+                rows.clear();
+                PSB_RETURN_IF_ERROR(export_shard(s, cursor, window, dirty_only, &keys, &rows, &cursor, &finished));
+                moved = layout_epoch(s) != epoch;
+                if (!moved && !keys.empty()) PSB_RETURN_IF_ERROR(fn(keys, rows));
+            }
+            if (!moved) return Status::Ok();
+            if (!restart) break;
+            restart();
+        }
+        return Status::Error("the index of shard " + std::to_string(s) + " was rebuilt during the scan: run it again");
+    }
 
     virtual uint64_t shard_size(int s) = 0;
     virtual uint64_t size() = 0;
@@ -110,6 +139,10 @@ public:
     Status erase_keys(const int64_t* keys, size_t n, uint64_t* erased) override {
         *erased = t_.erase_keys(keys, n);
         return Status::Ok();
+    }
+    uint64_t layout_epoch(int s) override { return t_.layout_epoch(s); }
+    Status scan_shard(int s, uint64_t window, bool dirty_only, const ScanFn& fn, const std::function<void()>& = nullptr) override {
+        return t_.scan_shard(s, (size_t)window, dirty_only, fn);
     }
     uint64_t shard_size(int s) override { return t_.shard_size(s); }
     uint64_t size() override { return t_.size(); }

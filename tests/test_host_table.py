@@ -246,3 +246,31 @@ def test_grow_and_shrink_ratio_of_the_index():
         t.set_rows(keys, 2 * np.ones((n, 4), np.float32), True)      # grows back
         rows, found = t.get_rows(keys, True)
         assert found.all() and np.all(rows[:, :4] == 2.0) and t.size() == n
+
+
+def test_layout_epoch_moves_exactly_when_bucket_cursors_lose_their_meaning():
+    hc = C.HostTableConfig()
+    hc.dim, hc.n_shards = 4, 1
+    hc.expected_max_items = 1000
+    hc.index_shrink_ratio = 0.2
+    t = C.HostTable(hc)
+    assert t.layout_epoch(0) == 0                                     # no such shard
+    t.create_shard(0)
+    e0 = t.layout_epoch(0)
+    keys = np.arange(1000, dtype=np.int64)
+    t.set_rows(keys, np.ones((1000, 4), np.float32), True)
+    assert t.layout_epoch(0) == e0                                    # inserts into a table with room move nothing
+    # a scan by cursor in two halves sees every key once while the epoch stands
+    half = t.export_shard(0, 0, 1 << 30, False)[2] // 2
+    k1, _, c, fin = t.export_shard(0, 0, half, False)
+    k2, _, c, fin2 = t.export_shard(0, c, 1 << 30, False)
+    assert not fin and fin2 and sorted(np.concatenate([k1, k2]).tolist()) == keys.tolist()
+    t.set_rows(np.arange(1000, 5000, dtype=np.int64), np.ones((4000, 4), np.float32), True)
+    e1 = t.layout_epoch(0)
+    assert e1 != e0                                                   # growth rebuilt the index
+    t.erase_keys(np.arange(100, 5000, dtype=np.int64))
+    e2 = t.layout_epoch(0)
+    assert e2 != e1                                                   # so did the shrink after the erase
+    t.erase_shard(0)
+    t.create_shard(0)
+    assert t.layout_epoch(0) not in (e0, e1, e2)                      # a shard created anew is another shard

@@ -321,6 +321,79 @@ def test_ha_dead_node_detection_and_restore(tmp_path):
         cl.close()
 
 
+def test_scans_of_a_live_table_see_every_old_key_exactly_once(tmp_path):
+    """Dumps and a replica restore run while another client keeps inserting new keys, which makes the shard's index
+    rebuild itself several times. A dump reads each shard as one snapshot (writers of the shard wait), the resumable
+    restore iteration starts over when the index moved under its cursor: no key that was there before is lost or
+    written twice."""
+    cl = Cluster(2)
+    try:
+        ids = cl.ids()
+        sid, h = make_table(cl, {ids[0]: [0], ids[1]: [0]})                   # one shard, two replicas
+        push = S.PushHandler(cl.client, sid, h["push"])
+        old = np.arange(60_000, dtype=np.int64)
+        assert push.async_push(old, np.ones((len(old), DIM), np.float32)).ok()
+        stop, pushed, bad = threading.Event(), [len(old)], []
+
+        def feeder():
+            c = S.Client(cl.master.address())
+            assert c.initialize_storage(sid).ok()
+            q = S.PushHandler(c, sid, h["push"])
+            while not stop.is_set() and pushed[0] < 1_500_000:
+                k = np.arange(pushed[0], pushed[0] + 10_000, dtype=np.int64)
+                st = q.async_push(k, 2 * np.ones((len(k), DIM), np.float32), 20000)
+                if not st.ok():
+                    bad.append(str(st))
+                    return
+                pushed[0] += len(k)
+
+        t = threading.Thread(target=feeder)
+        t.start()
+        try:
+            for i in range(4):
+                before = pushed[0]
+                uri = str(tmp_path / f"dump{i}") + "?format=binary"
+                st, n = S.DumpHandler(cl.client, sid, h["dump"]).dump(uri, 1)
+                assert st.ok(), st
+                assert n >= before                                            # one replica dumps the shard
+                sid2, h2 = make_table(cl, {ids[0]: [0, 1]})
+                st, loaded = S.LoadHandler(cl.client, sid2, h2["load"]).load(uri)
+                assert st.ok(), st
+                st, rows = S.PullHandler(cl.client, sid2, h2["pull_ro"]).pull(old)
+                assert st.ok() and np.all(rows == 1.0)                        # nothing old is missing
+                st, info = cl.client.query_storage_info(sid2)
+                uniq = sum(x.item_number for x in info)
+                assert uniq == n == loaded                                    # and the snapshot holds no key twice
+                assert cl.client.delete_storage(sid2).ok()
+            # replica restore in small batches while the inserts go on
+            cl.servers[1].stop()
+            pull = S.PullHandler(cl.client, sid, h["pull_ro"])
+            td = S.TableDescriptor()
+            for _ in range(64):
+                assert pull.pull(old[:100], 20000, True)[0].ok()
+                td.from_json_str(S.MasterClient(cl.master.address()).get_context(f"storage/{sid}")[1])
+                if td.node_status()[ids[1]] == 1:
+                    break
+            assert td.node_status()[ids[1]] == 1
+            cfg = S.ServerConfig()
+            cfg.restore_batch_size = 4096
+            fresh = S.Server(cl.master.address(), cfg)
+            cl.servers.append(fresh)
+            grown = pushed[0]
+            st, n = fresh.restore_storages()
+            assert st.ok() and n == 1, st
+        finally:
+            stop.set()
+            t.join(60)
+        assert not bad and not t.is_alive(), bad
+        assert pushed[0] > grown or pushed[0] >= 1_500_000                    # the inserts did go on during the restore
+        cl.servers[0].stop()                                                  # only the restored replica is left
+        st, rows = pull.pull(old, 20000, True)
+        assert st.ok() and np.all(rows == 1.0)
+    finally:
+        cl.close()
+
+
 def test_restore_from_dump_when_no_replica(tmp_path):
     cl = Cluster(2)
     try:
