@@ -438,15 +438,26 @@ public:
         return with_retry([&](int left) -> Status {
             *result = fop->init_result(carried);
             auto e = entry();
+            // a reading scan asks one replica of every shard; a writing scan goes to every holder, so that replicas
+            // stay alike, and the answer of the first holder of a shard is the one that counts
             std::vector<std::pair<int, int32_t>> targets;
+            std::map<int32_t, int> primary;
             int32_t built_under = -1;
             {
                 std::shared_lock<std::shared_mutex> g(e->mu);
                 built_under = e->td.version;
                 for (auto& kv : e->rt.shards()) {
+                    if (fop->writes()) {
+                        for (int node : kv.second) {
+                            targets.push_back({node, kv.first});
+                            if (!primary.count(kv.first)) primary[kv.first] = node;
+                        }
+                        continue;
+                    }
                     int node = e->rt.pick_one_replica(kv.first);
                     if (node < 0) return Status::NoReplica("for_each: no live replica of shard " + std::to_string(kv.first));
                     targets.push_back({node, kv.first});
+                    primary[kv.first] = node;
                 }
             }
             for (auto& t : targets) {
@@ -456,7 +467,7 @@ public:
                 PSB_RETURN_IF_ERROR(client_->send_and_wait(sid_, hid_, RequestType::OP_FOREACH, body, left, &rs, built_under));
                 std::string part;
                 rs[0].body >> part;
-                fop->merge_result(part, result);
+                if (primary[t.second] == t.first) fop->merge_result(part, result);
             }
             return Status::Ok();
         }, timeout_ms);

@@ -22,6 +22,7 @@ void register_builtin_operators() {
         PSB_REG(DenseTablePullOperator);
         PSB_REG(DenseTablePushOperator);
         PSB_REG(ForEachOperator);
+        PSB_REG(ForEachWriteOperator);
         PSB_REG(EraseIfOperator);
         PSB_REG(DumpOperator);
         PSB_REG(LoadOperator);

@@ -644,8 +644,9 @@ public:
                           std::string* result) const = 0;
     // *out = merge(*out, in); must be associative and commutative (shards answer in any order).
     virtual void merge_result(const std::string& in, std::string* out) const = 0;
-    // A mutating scan (the reference's SparseTableForEachWriteOperator) would return rows to write back; this build
-    // keeps scans read-only and offers UDF operators for writes.
+    // Whether the scan changes rows (ForEachWriteOperatorBase): the client then sends it to every holder of a shard,
+    // so that replicas stay alike, and counts the answer of one of them.
+    virtual bool writes() const { return false; }
 
     // Server half: the scan of one shard. The default walks the shard in windows and calls for_each per entry.
     virtual Status apply_request(TableEntry& e, int32_t shard, const Json& carried, std::string* result) const {
@@ -719,6 +720,86 @@ public:
             return Status::Ok();
         }
         return ForEachOperatorBase::apply_request(e, shard, carried, result);
+    }
+};
+
+// The writing scan (SparseTableForEachWriteOperator, pico-ps/operator/ForEachOperator.h:277-359): for_each_write may
+// change the row it is shown and folds something into the result as the reading scan does. A host shard is updated in
+// place under its write lock; rows marked for the incremental sync are marked by it as well.
+class ForEachWriteOperatorBase : public ForEachOperatorBase {
+public:
+    explicit ForEachWriteOperatorBase(const Json& c) : ForEachOperatorBase(c) {}
+    bool writes() const final { return true; }
+    // Returns whether it changed `row` (stride floats: embedding, optimizer slots, pending delta).
+    virtual bool for_each_write(int64_t key, float* row, uint32_t dim, uint32_t stride, const Json& carried,
+                                std::string* result) const = 0;
+    void for_each(int64_t, const float*, uint32_t, uint32_t, const Json&, std::string*) const final {}
+    // Checked once per request before the scan.
+    virtual Status check_carried(const KVStorage&, const Json&) const { return Status::Ok(); }
+    Status apply_request(TableEntry& e, int32_t shard, const Json& carried, std::string* result) const override {
+        KVStorage* st = e.storage.get();
+        PSB_RETURN_IF_ERROR(check_carried(*st, carried));
+        const uint32_t dim = st->dim(), stride = st->stride();
+        *result = init_result(carried);
+        std::shared_lock<std::shared_mutex> ig(e.incr.mu);   // like a push: not while the increment is collected
+        uint64_t changed = 0;
+        Status status = st->update_shard(
+            shard, 1 << 16, [&](int64_t key, float* row) { return for_each_write(key, row, dim, stride, carried, result); }, &changed);
+        if (changed) e.incr.updated = true;
+        return status;
+    }
+};
+
+// The built-in writing scans, chosen by the carried item; `section` 0 = embedding, 1 / 2 = optimizer slots:
+//   {"type":"scale","factor":f} | {"type":"clip","limit":c} (to [-c, c]) | {"type":"fill","value":v}
+// The result is the statistics record of the reading scan over the section AFTER the write, counted over the rows
+// that changed.
+class ForEachWriteOperator : public ForEachWriteOperatorBase {
+public:
+    explicit ForEachWriteOperator(const Json& c) : ForEachWriteOperatorBase(c) {}
+    std::string init_result(const Json&) const override { return ForEachResult().pack(); }
+    Status check_carried(const KVStorage& st, const Json& carried) const override {
+        const std::string type = carried.at("type").as_string();
+        if (type != "scale" && type != "clip" && type != "fill") return Status::InvalidConfig("for_each (write): unknown type '" + type + "'");
+        const int64_t section = carried.at("section").as_int(0);
+        if (section < 0 || (uint64_t)(section + 1) * st.dim() > st.stride()) return Status::InvalidConfig("for_each (write): no such row section");
+        if (type == "clip" && carried.at("limit").as_double(-1) < 0) return Status::InvalidConfig("for_each (write): clip needs a limit >= 0");
+        return Status::Ok();
+    }
+    bool for_each_write(int64_t, float* row, uint32_t dim, uint32_t, const Json& carried, std::string* result) const override {
+        const std::string type = carried.at("type").as_string();
+        float* v = row + (size_t)carried.at("section").as_int(0) * dim;
+        bool changed = false;
+        auto put = [&](uint32_t k, float x) {
+            if (std::memcmp(&v[k], &x, sizeof(float)) != 0) changed = true;
+            v[k] = x;
+        };
+        if (type == "scale") {
+            const float f = (float)carried.at("factor").as_double(1.0);
+            for (uint32_t k = 0; k < dim; ++k) put(k, v[k] * f);
+        } else if (type == "clip") {
+            const float c = (float)carried.at("limit").as_double(0.0);
+            for (uint32_t k = 0; k < dim; ++k) put(k, std::min(c, std::max(-c, v[k])));
+        } else {
+            const float x = (float)carried.at("value").as_double(0.0);
+            for (uint32_t k = 0; k < dim; ++k) put(k, x);
+        }
+        if (changed) {
+            ForEachResult* r = (ForEachResult*)&(*result)[0];
+            ++r->count;
+            for (uint32_t k = 0; k < dim; ++k) {
+                r->sum += v[k];
+                r->sum_sq += (double)v[k] * v[k];
+                r->max_abs = std::max(r->max_abs, (double)std::fabs(v[k]));
+            }
+        }
+        return changed;
+    }
+    void merge_result(const std::string& in, std::string* out) const override {
+        ForEachResult a, b;
+        if (!ForEachResult::unpack(in, &a) || !ForEachResult::unpack(*out, &b)) return;
+        b.merge(a);
+        *out = b.pack();
     }
 };
 

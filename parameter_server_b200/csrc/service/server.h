@@ -920,6 +920,7 @@ private:
         std::string result;
         PSB_RETURN_IF_ERROR(op->apply_request(e, shard, carried, &result));
         *out << result;   // bytes whose layout the operator defines
+        if (op->writes() && e.sync_enabled.load(std::memory_order_acquire)) notify_sync(meta.sid, false);   // followers get the changed rows
         return Status::Ok();
     }
 

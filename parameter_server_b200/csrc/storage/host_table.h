@@ -341,6 +341,23 @@ public:
         }
         return Status::Ok();
     }
+    // Writing scan of a whole shard: `fn(key, row)` may change the row (stride floats) in place and says whether it
+    // did. The shard's write lock is held for the scan, as in the reference's writing for_each
+    // (pico-ps/operator/ForEachOperator.h:303-313 write_shard): no push lands between reading a row and writing it.
+    template <class F>
+    Status update_shard(int s, F&& fn, uint64_t* changed) {
+        if (changed) *changed = 0;
+        Shard* sh = get(s);
+        if (!sh) return Status::Ok();
+        std::unique_lock<std::shared_mutex> g(sh->mu);
+        for (const auto& b : sh->map.buckets()) {
+            if (!sh->map.live(b)) continue;
+            if (!fn(b.first, sh->rows.data() + (size_t)b.second * stride_)) continue;
+            if (track_dirty_) sh->dirty[b.second] = 1;
+            if (changed) ++*changed;
+        }
+        return Status::Ok();
+    }
     // Changes whenever the bucket cursors of export_shard lose their meaning for shard `s`: the index was rebuilt
     // (growth, shrink, clear) or the shard was dropped and created again.
     uint64_t layout_epoch(int s) const {

@@ -91,6 +91,38 @@ public:
         return Status::Error("the index of shard " + std::to_string(s) + " was rebuilt during the scan: run it again");
     }
 
+    // Writing scan of a whole shard: `fn(key, row)` may change the row (stride floats) and says whether it did. A host
+    // shard is updated in place under its write lock. This default reads windows through export_shard and writes the
+    // changed rows back with set_rows after each window: pushes of other clients that land in between are overwritten,
+    // and a rebuild of the index in mid-scan ends it with an error (rows of the windows before it stay updated).
+    using UpdateFn = std::function<bool(int64_t key, float* row)>;
+    virtual Status update_shard(int s, uint64_t window, const UpdateFn& fn, uint64_t* changed) {
+        if (changed) *changed = 0;
+        const uint32_t w = stride();
+        const uint64_t epoch = layout_epoch(s);
+        std::vector<int64_t> keys, ckeys;
+        std::vector<float> rows, crows;
+        uint64_t cursor = 0;
+        bool finished = false;
+        while (!finished) {
+            keys.clear();
+            rows.clear();
+            ckeys.clear();
+            crows.clear();
+            PSB_RETURN_IF_ERROR(export_shard(s, cursor, window, false, &keys, &rows, &cursor, &finished));
+            if (layout_epoch(s) != epoch)
+                return Status::Error("the index of shard " + std::to_string(s) + " was rebuilt during the writing scan");
+            for (size_t i = 0; i < keys.size(); ++i) {
+                if (!fn(keys[i], rows.data() + i * w)) continue;
+                ckeys.push_back(keys[i]);
+                crows.insert(crows.end(), rows.begin() + i * w, rows.begin() + (i + 1) * w);
+            }
+            if (!ckeys.empty()) PSB_RETURN_IF_ERROR(set_rows(ckeys.data(), crows.data(), ckeys.size(), false));
+            if (changed) *changed += ckeys.size();
+        }
+        return Status::Ok();
+    }
+
     virtual uint64_t shard_size(int s) = 0;
     virtual uint64_t size() = 0;
     virtual uint64_t memory_usage() = 0;
@@ -144,6 +176,7 @@ public:
     Status scan_shard(int s, uint64_t window, bool dirty_only, const ScanFn& fn, const std::function<void()>& = nullptr) override {
         return t_.scan_shard(s, (size_t)window, dirty_only, fn);
     }
+    Status update_shard(int s, uint64_t, const UpdateFn& fn, uint64_t* changed) override { return t_.update_shard(s, fn, changed); }
     uint64_t shard_size(int s) override { return t_.shard_size(s); }
     uint64_t size() override { return t_.size(); }
     uint64_t memory_usage() override { return t_.memory_usage(); }

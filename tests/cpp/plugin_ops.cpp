@@ -44,6 +44,20 @@ public:
     }
 };
 
+// A writing scan: rows of odd keys get their first value replaced by the key; the result counts them (one int64).
+class StampOddKeys : public ForEachWriteOperatorBase {
+public:
+    explicit StampOddKeys(const Json& c) : ForEachWriteOperatorBase(c) {}
+    std::string init_result(const Json&) const override { return std::string(8, '\0'); }
+    bool for_each_write(int64_t key, float* row, uint32_t, uint32_t, const Json&, std::string* result) const override {
+        if (key % 2 == 0) return false;
+        row[0] = (float)key;
+        ++*(int64_t*)&(*result)[0];
+        return true;
+    }
+    void merge_result(const std::string& in, std::string* out) const override { *(int64_t*)&(*out)[0] += *(const int64_t*)in.data(); }
+};
+
 // A dense value cut back to front: slice j holds the j-th block counted from the END of the tensor.
 static void reversed_partition(int64_t id, size_t numel, uint32_t slice_len, std::vector<DenseSlice>* out) {
     dense_default_partition(id, numel, slice_len, out);
@@ -87,6 +101,7 @@ private:
 
 PSB_REGISTER_OPERATOR(testplugin, EraseEvenAbove);
 PSB_REGISTER_OPERATOR(testplugin, KeyHistogram);
+PSB_REGISTER_OPERATOR(testplugin, StampOddKeys);
 PSB_REGISTER_OPERATOR(testplugin, ReversedDensePull);
 PSB_REGISTER_OPERATOR(testplugin, ReversedDensePush);
 PSB_REGISTER_OPERATOR(testplugin, TracingUpdateContext);

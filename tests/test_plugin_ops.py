@@ -98,6 +98,15 @@ def test_plugin_erase_predicate_and_reducer_run_on_the_servers(plugin):
         st, rows = S.PullHandler(cl.client, sid, h["pull"]).pull(keys)
         assert st.ok()
         assert np.array_equal(rows[:, 0] != 0, ~doomed & (keys % 10 != 0))
+        # the plug-in's writing scan: odd keys get their key stamped into the first value, in place on the servers
+        st, hw = cl.client.register_handler("stamp", "testplugin", "StampOddKeys", "{}", sid)
+        assert st.ok(), st
+        st, raw = S.ForEachHandler(cl.client, sid, hw).for_each_raw("{}")
+        assert st.ok() and struct.unpack("<q", raw)[0] == int((keys % 2 == 1).sum())
+        st, after = S.PullHandler(cl.client, sid, h["pull"]).pull(keys)
+        odd = keys % 2 == 1
+        assert st.ok() and np.array_equal(after[odd, 0], keys[odd].astype(np.float32))
+        assert np.array_equal(after[~odd], rows[~odd]) and np.array_equal(after[odd, 1:], rows[odd, 1:])
     finally:
         cl.close()
 

@@ -394,6 +394,42 @@ def test_scans_of_a_live_table_see_every_old_key_exactly_once(tmp_path):
         cl.close()
 
 
+def test_writing_for_each_updates_every_replica_in_place(cluster3):
+    """The writing scan (the reference's SparseTableForEachWriteOperator): every holder of a shard applies it, so
+    replicas stay alike; the result counts each shard once; bad carried items are refused before anything changes."""
+    cl = cluster3
+    ids = cl.ids()
+    cfg = op_cfg(optimizer="adagrad", lr=0.1, init_accumulator=0.5)
+    sid, h = make_table(cl, {ids[0]: [0, 1], ids[1]: [1, 2], ids[2]: [2, 0]}, cfg=cfg)
+    st, hw = cl.client.register_handler("for_each_write", S.LIB, "ForEachWriteOperator", "{}", sid)
+    assert st.ok(), st
+    push, pull = S.PushHandler(cl.client, sid, h["push"]), S.PullHandler(cl.client, sid, h["pull_ro"])
+    keys = np.arange(1, 2001, dtype=np.int64)
+    assert push.async_push(keys, np.ones((2000, DIM), np.float32) * (keys[:, None] % 5 + 1)).ok()
+    st, before = pull.pull(keys)
+    assert st.ok()
+    scan = S.ForEachHandler(cl.client, sid, hw)
+    for bad in ({"type": "rotate"}, {"type": "scale", "section": 7}, {"type": "clip"}):
+        assert scan.for_each(json.dumps(bad))[0].code() == StatusCode.INVALID_CONFIG
+    st, r = scan.for_each(json.dumps({"type": "scale", "factor": 0.5}))
+    assert st.ok() and r["count"] == 2000                                   # every key once, not once per replica
+    assert abs(r["sum"] - 0.5 * float(before.sum())) < 1e-3 * abs(before.sum())
+    for _ in range(6):                                                      # reads pick a replica at random
+        st, rows = pull.pull(keys)
+        assert st.ok() and np.array_equal(rows, np.float32(0.5) * before)
+    lim = float(np.abs(before).max()) * 0.25
+    st, r = scan.for_each(json.dumps({"type": "clip", "limit": lim}))
+    changed = np.abs(np.float32(0.5) * before).max(axis=1) > np.float32(lim)
+    assert st.ok() and r["count"] == int(changed.sum()) and r["max_abs"] <= lim * (1 + 1e-6)
+    # the accumulator slot is a section of its own: reset it and see the reading scan agree
+    st, r = scan.for_each(json.dumps({"type": "fill", "section": 1, "value": 0.25}))
+    assert st.ok() and r["count"] == 2000
+    st, d = S.ForEachHandler(cl.client, sid, h["for_each"]).for_each(json.dumps({"section": 1}))
+    assert st.ok() and d["count"] == 2000 and abs(d["sum"] - 0.25 * 2000 * DIM) < 1e-3 and abs(d["max_abs"] - 0.25) < 1e-7
+    st, r = scan.for_each(json.dumps({"type": "fill", "section": 1, "value": 0.25}))
+    assert st.ok() and r["count"] == 0                                      # nothing left to change
+
+
 def test_restore_from_dump_when_no_replica(tmp_path):
     cl = Cluster(2)
     try:
@@ -591,6 +627,16 @@ def test_predictor_sync_udf_and_native_ps(tmp_path, cluster3):
     assert sum(s.push_sync_table(trainer, sync)[1] for s in cl.servers[:2]) == 7
     assert np.all(ppull.pull(keys[:7])[1] == 2.0)
     assert sum(s.push_sync_table(trainer, sync)[1] for s in cl.servers[:2]) == 0
+    # rows that a writing scan changed are part of the next increment, rows that it left alone are not
+    st, hw = cl.client.register_handler("for_each_write", S.LIB, "ForEachWriteOperator", "{}", trainer)
+    assert st.ok(), st
+    st, r = S.ForEachHandler(cl.client, trainer, hw).for_each(json.dumps({"type": "clip", "limit": 1.5}))
+    assert st.ok() and r["count"] == 7
+    assert sum(s.push_sync_table(trainer, sync)[1] for s in cl.servers[:2]) == 7
+    assert np.all(ppull.pull(keys[:7])[1] == 1.5) and np.all(ppull.pull(keys[7:])[1] == 1.0)
+    st, r = S.ForEachHandler(cl.client, trainer, hw).for_each(json.dumps({"type": "fill", "value": 2.0}))
+    assert st.ok() and r["count"] == 500 and push.async_push(keys[:7], np.zeros((7, DIM), np.float32)).ok()
+    assert sum(s.push_sync_table(trainer, sync)[1] for s in cl.servers[:2]) == 500
     # UDF: a Python function registered on the servers
     S.register_udf("count_items", lambda sid, items, param: f"{items}:{param.decode()}".encode())
     st, hid = cl.client.register_handler("udf", S.LIB, "UDFOperator", json.dumps({"function": "count_items"}), trainer)
@@ -618,7 +664,7 @@ def test_predictor_sync_udf_and_native_ps(tmp_path, cluster3):
     st, n = S.NativeLoadHandler(nps, nsid, lh).load(uri, 4)
     assert st.ok() and n == 500 and nps.size(nsid) == 500
     st, rows = S.NativePullHandler(nps, nsid, ph).pull(keys, DIM)
-    assert st.ok() and np.all(rows[:7] == 2.0) and np.all(rows[7:] == 1.0)
+    assert st.ok() and np.all(rows == 2.0)
 
 
 def test_common_pieces():
