@@ -37,6 +37,7 @@
 #include "../service/master.h"
 #include "../service/metrics_http.h"
 #include "../service/server.h"
+#include "../service/local_images.h"
 #include "../service/table_syncer.h"
 
 using namespace psb;
@@ -106,10 +107,51 @@ int ctl_main(int argc, char** argv) {
     return 0;
 }
 
+// psb_node images DIR [--master HOST:PORT] [--remove-unused [--dead-nodes-too]]: what lies under an image directory
+// (JSON on stdout) and removal of what no node can use any more.
+int images_main(int argc, char** argv) {
+    std::string dir, master;
+    bool remove = false, dead_too = false;
+    for (int i = 2; i < argc; ++i) {
+        const std::string a = argv[i];
+        if (a == "--master" && i + 1 < argc) master = argv[++i];
+        else if (a == "--remove-unused") remove = true;
+        else if (a == "--dead-nodes-too") dead_too = true;
+        else if (dir.empty() && a.compare(0, 2, "--") != 0) dir = a;
+        else return 2;
+    }
+    if (dir.empty() || (remove && master.empty())) {
+        std::fprintf(stderr, "usage: psb_node images DIR [--master HOST:PORT] [--remove-unused [--dead-nodes-too]]\n");
+        return 2;
+    }
+    try {
+        std::unique_ptr<MasterClient> mc;
+        if (!master.empty()) mc.reset(new MasterClient(master));
+        Status st;
+        if (remove) {
+            int removed = 0;
+            st = remove_unused_local_images(dir, mc.get(), dead_too, &removed);
+            if (st.ok()) std::fprintf(stderr, "removed=%d\n", removed);
+        }
+        std::vector<LocalImage> images;
+        if (st.ok()) st = list_local_images(dir, mc.get(), &images);
+        if (!st.ok()) {
+            std::fprintf(stderr, "psb_node images: %s\n", st.to_string().c_str());
+            return 1;
+        }
+        std::printf("%s\n", local_images_json(images).dump().c_str());
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "psb_node images: %s\n", e.what());
+        return 1;
+    }
+    return 0;
+}
+
 int usage() {
     std::fprintf(stderr,
                  "usage: psb_node master [--threads N] [--port P] [--state-file FILE] [--host ADDR]\n"
                  "       psb_node ctl --master HOST:PORT VERB ...   (the controller; `psb_node ctl` lists the verbs)\n"
+                 "       psb_node images DIR [--master HOST:PORT] [--remove-unused [--dead-nodes-too]]\n"
                  "       psb_node pserver --master HOST:PORT [--restore] [--restore-wait S] [--image-dir DIR] [--image-interval-ms N] [--report-interval S]\n"
                  "                        [--load-threads N] [--c2s-threads N] [--s2s-threads N] [--sync-master HOST:PORT] [--hadoop-bin PATH]\n"
                  "                        [--metrics-port P] [--log-level debug|info|warning|error|off] [--host ADDR]\n");
@@ -123,6 +165,7 @@ int main(int argc, char** argv) {
     std::signal(SIGTERM, on_signal);
     const std::string role = argv[1];
     if (role == "ctl") return ctl_main(argc, argv);
+    if (role == "images") return images_main(argc, argv);
     std::string master_addr, sync_master, state_file;
     int master_port = 0;
     bool restore = false;

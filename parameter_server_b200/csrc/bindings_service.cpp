@@ -11,6 +11,7 @@
 #include "controller/controller.h"
 #include "handler/handlers.h"
 #include "native_ps/native_ps.h"
+#include "service/local_images.h"
 #include "service/table_syncer.h"
 
 namespace py = pybind11;
@@ -281,6 +282,21 @@ void bind_service(py::module_& m) {
         });
     });
     // dump / load paths with a remote scheme (hdfs://...) go through this command (`<bin> fs -cat / -put / -ls ...`)
+    // housekeeping of an image directory from outside a server (psb_node images): JSON list, removal of unused ones
+    m.def("list_local_images", [](const std::string& dir, const std::string& master) {
+        std::unique_ptr<MasterClient> mc;
+        if (!master.empty()) mc.reset(new MasterClient(master));
+        std::vector<LocalImage> images;
+        Status st = list_local_images(dir, mc.get(), &images);
+        return py::make_tuple(st, local_images_json(images).dump());
+    }, py::arg("dir"), py::arg("master") = "");
+    m.def("remove_unused_local_images", [](const std::string& dir, const std::string& master, bool dead_nodes_too) {
+        std::unique_ptr<MasterClient> mc;
+        if (!master.empty()) mc.reset(new MasterClient(master));
+        int removed = 0;
+        Status st = remove_unused_local_images(dir, mc.get(), dead_nodes_too, &removed);
+        return py::make_tuple(st, removed);
+    }, py::arg("dir"), py::arg("master"), py::arg("dead_nodes_too") = false);
     m.def("set_hadoop_bin", &fs::set_hadoop_bin);
     m.def("hadoop_bin", &fs::hadoop_bin);
     m.def("register_udf", [](const std::string& name, py::function fn) {

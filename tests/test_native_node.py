@@ -102,6 +102,12 @@ def test_planned_shutdown_leaves_an_image_that_a_replacement_opens(tmp_path):
         first.send_signal(signal.SIGTERM)                       # planned shutdown: the image is written
         out, _ = first.communicate(timeout=20)
         assert "images: OK (1 tables)" in out and first.returncode == 0
+        # the housekeeping verb: the image of a node that is gone is listed, and kept unless asked otherwise
+        ls = subprocess.run([NODE, "images", img, "--master", addr, "--remove-unused"], capture_output=True, text=True, timeout=60)
+        assert ls.returncode == 0 and "removed=0" in ls.stderr, ls.stderr
+        (im,) = json.loads(ls.stdout)
+        assert (im["node"], im["storage_id"], im["records"], im["state"]) == (node, sid, 800, "dead_node")
+        assert subprocess.run([NODE, "images"], capture_output=True).returncode == 2
         second = _spawn("pserver", "--master", addr, "--image-dir", img, "--restore")
         procs.append(second)
         assert "node_id=" in _first_line(second)

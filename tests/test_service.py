@@ -1126,8 +1126,26 @@ def test_restore_from_the_hosts_own_image_when_no_replica(tmp_path):
         servers.append(last)
         st, n = last.restore_storages()
         assert not st.ok()                                          # no replica, foreign image refused, no dump either
+        # the same housekeeping from outside a server: what lies in the directory and whose it is
+        st, listing = C.list_local_images(str(tmp_path / "images"), master.address())
+        assert st.ok()
+        states = {(im["node"], im["storage_id"]): im["state"] for im in json.loads(listing)}
+        assert states[(fresh.node_id(), sid2)] == "stale"          # copied from another table
+        assert states[(ids[1], sid)] == "current" and all(im["records"] > 0 for im in json.loads(listing))
+        assert [im["state"] for im in json.loads(C.list_local_images(str(tmp_path / "images"))[1])] == ["unknown"] * len(states)
+        (tmp_path / "images" / f"node_{ids[1]}" / "storage_77.img").write_bytes(b"PSBIMG1\0garbage")
+        st, n = C.remove_unused_local_images(str(tmp_path / "images"), master.address())
+        assert st.ok() and n == 2 and not dst.exists()              # the foreign image and the damaged one go
+        assert (tmp_path / "images" / f"node_{ids[1]}" / f"storage_{sid}.img").exists()
+        servers[1].stop()                                           # its image is now that of a node that is gone
+        for _ in range(100):
+            if json.loads(C.list_local_images(str(tmp_path / "images"), master.address())[1])[0]["state"] == "dead_node":
+                break
+            time.sleep(0.05)
+        assert C.remove_unused_local_images(str(tmp_path / "images"), master.address())[1] == 0   # kept for a restore
+        assert C.remove_unused_local_images(str(tmp_path / "images"), master.address(), True)[1] == 1
         st, n = last.clean_local_images()
-        assert st.ok() and n == 1 and not dst.exists()              # the foreign image goes when somebody cleans up
+        assert st.ok() and n == 0
     finally:
         for s in servers:
             s.stop()
