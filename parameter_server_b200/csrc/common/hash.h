@@ -55,6 +55,12 @@ PSB_HD int32_t dense_shard_of(int64_t id, int32_t slice_id, int32_t num_shards) 
     return (int32_t)(h % (uint64_t)num_shards);
 }
 
+// Key -> shard id by plain modulo (non-negative for negative keys too): for tables whose producer lays the keys out.
+PSB_HD int32_t modulo_shard_of(int64_t key, int32_t num_shards) {
+    const int64_t r = key % (int64_t)num_shards;
+    return (int32_t)(r < 0 ? r + num_shards : r);
+}
+
 // Slot hash for the open-addressing tables (decorrelated from the shard hash by a second mix).
 PSB_HD uint64_t slot_hash(int64_t key) { return fmix64((uint64_t)key ^ kMurmurSeed); }
 

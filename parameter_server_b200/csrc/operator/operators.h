@@ -71,7 +71,12 @@ public:
         Status st = parse_opt_config(c, &opt_);
         if (!st.ok()) throw std::runtime_error(st.msg());
         dim_ = (uint32_t)c.at("dim").as_int(16);
-        partition_ = c.at("partition").as_string() == "dense" ? 1 : 0;
+        // key -> shard: "hash" (the default: jump-consistent hash of the mixed key), "dense" (slices of dense values,
+        // hash % N) or "modulo" (key mod N, for tables whose keys are laid out by their producer - the custom
+        // partitioner of the reference's predictor test family, pico-ps/test/TestPredictorOps.h:52-64)
+        const std::string part = c.at("partition").as_string();
+        if (!part.empty() && part != "hash" && part != "dense" && part != "modulo") throw std::runtime_error("unknown partition '" + part + "'");
+        partition_ = part == "dense" ? 1 : (part == "modulo" ? 2 : 0);
         if (partition_ == 1 && !c.has("init_range")) init_range_ = 0.f;
         else init_range_ = c.has("init_range") ? (float)c.at("init_range").as_double() : 0.01f;
     }
@@ -81,6 +86,7 @@ public:
     int partition() const { return partition_; }
     int shard_of(int64_t key, int32_t n_shards) const {
         if (partition_ == 1) return dense_shard_of(key >> 24, (int32_t)(key & 0xFFFFFF), n_shards);
+        if (partition_ == 2) return modulo_shard_of(key, n_shards);
         return sparse_shard_of(key, n_shards);
     }
     HostTableConfig table_config(int32_t n_shards) const {

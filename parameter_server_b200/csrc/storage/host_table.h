@@ -33,7 +33,8 @@ struct HostTableConfig {
     bool sync_delta = false;
     int32_t n_shards = 1;  // global shard count
     int32_t partition = 0; // 0: sparse keys, jump_consistent_hash(murmur(key)); 1: dense slices, key = (id << 24) | slice,
-                           //    shard = hash(id, slice) % n_shards (pico-ps/common/dense_common.h:58-65)
+                           //    shard = hash(id, slice) % n_shards (pico-ps/common/dense_common.h:58-65);
+                           // 2: key mod n_shards
     uint64_t init_seed = 0;
     float init_range = 0.01f;
     float slot_init0 = 0.f;
@@ -125,6 +126,7 @@ public:
 
     int shard_of(int64_t key) const {
         if (cfg_.partition == 1) return dense_shard_of(key >> 24, (int32_t)(key & 0xFFFFFF), cfg_.n_shards);
+        if (cfg_.partition == 2) return modulo_shard_of(key, cfg_.n_shards);
         return sparse_shard_of(key, cfg_.n_shards);
     }
     // Change the global shard count (reshard): existing shards keep their ids, the caller migrates keys.

@@ -430,6 +430,32 @@ def test_writing_for_each_updates_every_replica_in_place(cluster3):
     assert st.ok() and r["count"] == 0                                      # nothing left to change
 
 
+def test_modulo_partition_places_keys_by_their_value_and_survives_a_reshard(cluster3):
+    """`partition: modulo` (the custom partitioner of the reference's predictor test family): key k lives in shard
+    k mod N, on client and servers alike, before and after a change of the shard count."""
+    cl = cluster3
+    ids = cl.ids()
+    sid, h = make_table(cl, {ids[0]: [0], ids[1]: [1, 2], ids[2]: [3]}, cfg=op_cfg(partition="modulo"))
+    keys = np.concatenate([np.arange(-50, 0), np.arange(1000)]).astype(np.int64)
+    vals = np.ones((len(keys), DIM), np.float32) * (np.abs(keys)[:, None] % 13 + 1)
+    assert S.PushHandler(cl.client, sid, h["push"]).async_push(keys, vals).ok()
+    st, info = cl.client.query_storage_info(sid)
+    assert st.ok()
+    per_shard = {i.shard_id: i.item_number for i in info}
+    assert per_shard == {s: int((np.mod(keys, 4) == s).sum()) for s in range(4)}       # numpy's mod is non-negative too
+    pull = S.PullHandler(cl.client, sid, h["pull_ro"])
+    st, rows = pull.pull(keys)
+    assert st.ok() and np.array_equal(rows, vals)
+    assert S.UpdateContextHandler(cl.client, sid, h["update_ctx"]).update_context(
+        S.nodes_json({ids[0]: [0, 1], ids[1]: [2, 3], ids[2]: [4, 5]})).ok()
+    st, info = cl.client.query_storage_info(sid)
+    assert st.ok() and {i.shard_id: i.item_number for i in info} == {s: int((np.mod(keys, 6) == s).sum()) for s in range(6)}
+    st, rows = pull.pull(keys, 20000, True)
+    assert st.ok() and np.array_equal(rows, vals)
+    st, _ = cl.client.create_storage(S.LIB, "SparseTableStorageOperator", S.storage_config({ids[0]: [0]}, op_cfg(partition="zigzag")))
+    assert not st.ok() and "partition" in str(st)
+
+
 def test_restore_from_dump_when_no_replica(tmp_path):
     cl = Cluster(2)
     try:
