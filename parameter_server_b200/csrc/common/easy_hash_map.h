@@ -44,6 +44,12 @@ public:
         if ((double)used_ > max_load_ * (double)table_.size()) rehash(buckets_for(size_));
     }
     double max_load() const { return max_load_; }
+    // Memory of the bucket array, and how much it grows by when the next new key is inserted (0 when there is room).
+    size_t bytes() const { return table_.size() * sizeof(Entry); }
+    size_t next_insert_growth_bytes() const {
+        if ((double)(used_ + 1) <= max_load_ * (double)table_.size()) return 0;
+        return used_ > size_ * 2 + 8 ? 0 : table_.size() * sizeof(Entry);   // tombstone-heavy: rebuilt at the same size
+    }
     // Counts the rebuilds of the bucket array: a bucket cursor taken under one value is meaningless under another.
     uint64_t generation() const { return generation_; }
 

@@ -59,6 +59,7 @@ public:
     struct Shard {
         explicit Shard() : map(kHostEmptyKey) {}
         uint64_t born = 0;                   // which creation of a shard of this table this is (see layout_epoch)
+        uint64_t index_bytes = 0;            // what of map.bytes() is counted in the table's memory usage
         EasyHashMap<int64_t, uint32_t> map;
         std::vector<float> rows;
         std::vector<uint32_t> free_rows;
@@ -101,13 +102,14 @@ public:
                 const uint64_t share = cfg_.expected_max_items / (uint64_t)std::max<int32_t>(1, cfg_.n_shards);
                 shards_[s]->map.reserve((size_t)(share + share / 8 + 16));   // shards are not perfectly even
             }
+            account_index(*shards_[s]);
         }
     }
     void erase_shard(int s) {
         std::unique_lock<std::shared_mutex> g(mu_);
         auto it = shards_.find(s);
         if (it != shards_.end()) {
-            bytes_ -= it->second->rows.capacity() * sizeof(float);
+            bytes_ -= it->second->rows.capacity() * sizeof(float) + it->second->index_bytes;
             n_items_ -= it->second->map.size();
             n_parked_ -= it->second->overflow.size();
             shards_.erase(it);
@@ -288,7 +290,7 @@ public:
         n_items_ -= erased;
         for (Shard* sh : thinned) {   // safe_shrink of the reference (pico-ps/storage/KVShardStorage.h:786-834)
             std::unique_lock<std::shared_mutex> g(sh->mu);
-            sh->map.shrink_if_below(std::min(cfg_.index_shrink_ratio, 0.5 * sh->map.max_load()));
+            if (sh->map.shrink_if_below(std::min(cfg_.index_shrink_ratio, 0.5 * sh->map.max_load()))) account_index(*sh);
         }
         return erased;
     }
@@ -484,6 +486,7 @@ public:
             std::unique_lock<std::shared_mutex> g(sh->mu);
             bytes_ -= sh->rows.capacity() * sizeof(float);
             sh->map.clear();
+            account_index(*sh);
             std::vector<float>().swap(sh->rows);
             sh->free_rows.clear(); sh->touched.clear(); sh->touched_flag.clear(); sh->dirty.clear();
             sh->overflow.clear();
@@ -510,24 +513,32 @@ private:
             healthy_ = false;
             return Status::OOM("injected allocation failure");
         }
+        // What this insert makes the table grow by: the row pool when it is full (it doubles) and the index when it
+        // is at its load limit (it doubles too; the old bucket array beside the new one during the rebuild is not
+        // counted). Both are refused together when they would cross a limit (the governor of the reference counts
+        // its maps the same way, pico-ps/storage/KVShardStorage.h:875-877, pico-ps/storage/Storage.cpp:154-204).
+        const bool reuse = !sh.free_rows.empty();
+        const size_t old_cap = sh.rows.capacity();
+        const size_t need = sh.rows.size() + stride_;
+        size_t new_cap = old_cap;
+        if (!reuse && need > old_cap) new_cap = std::max<size_t>(old_cap * 2, (size_t)stride_ * 64);
+        const uint64_t extra = (new_cap - old_cap) * sizeof(float) + sh.map.next_insert_growth_bytes();
+        if (extra) {
+            const uint64_t b = bytes_;
+            if ((cfg_.hard_limit_bytes && b + extra > cfg_.hard_limit_bytes) ||
+                (cfg_.soft_limit_bytes && b + extra > cfg_.soft_limit_bytes)) {
+                failed_extra_ = extra;
+                failed_at_bytes_ = b;
+                healthy_ = false;
+                return Status::OOM("host table would exceed the memory limit");
+            }
+        }
         uint32_t r;
-        if (!sh.free_rows.empty()) {
+        if (reuse) {
             r = sh.free_rows.back();
             sh.free_rows.pop_back();
         } else {
-            size_t old_cap = sh.rows.capacity();
-            size_t need = sh.rows.size() + stride_;
-            if (need > old_cap) {
-                size_t new_cap = std::max<size_t>(old_cap * 2, (size_t)stride_ * 64);
-                uint64_t extra = (new_cap - old_cap) * sizeof(float);
-                uint64_t b = bytes_;
-                if ((cfg_.hard_limit_bytes && b + extra > cfg_.hard_limit_bytes) ||
-                    (cfg_.soft_limit_bytes && b + extra > cfg_.soft_limit_bytes)) {
-                    failed_extra_ = extra;
-                    failed_at_bytes_ = b;
-                    healthy_ = false;
-                    return Status::OOM("host row pool would exceed the memory limit");
-                }
+            if (new_cap != old_cap) {
                 sh.rows.reserve(new_cap);
                 bytes_ += (sh.rows.capacity() - old_cap) * sizeof(float);
             }
@@ -538,10 +549,19 @@ private:
         }
         init_row(sh.rows.data() + (size_t)r * stride_, key);
         sh.map.force_emplace(key, r);
+        if (sh.map.bytes() != sh.index_bytes) account_index(sh);
         if (track_dirty_) sh.dirty[r] = 1;
         ++n_items_;
         *row = r;
         return Status::Ok();
+    }
+
+    // Keep the table's byte count in step with the shard's bucket array (called with the shard locked for writing).
+    void account_index(Shard& sh) {
+        const uint64_t now = sh.map.bytes();
+        if (now >= sh.index_bytes) bytes_ += now - sh.index_bytes;
+        else bytes_ -= sh.index_bytes - now;
+        sh.index_bytes = now;
     }
 
     void apply(const OptConfig& opt, float* w, const float* g) const {
