@@ -33,3 +33,23 @@ def test_control_plane_under_sanitizer(tmp_path, sanitizer, marker):
     assert "STRESS OK" in run.stdout, run.stdout[-2000:] + run.stderr[-2000:]
     assert marker not in run.stderr and "runtime error:" not in run.stderr, run.stderr[:6000]
     assert run.returncode == 0
+
+
+@pytest.mark.timeout(600)
+def test_window_walking_scans_of_a_storage_without_snapshots(tmp_path):
+    """KVStorage's default scan_shard / update_shard (what the GPU back-end runs) on the CPU, under
+    AddressSanitizer: every key once on a quiet table, a restart or an error when the index is rebuilt under the
+    scan, changed rows written back exactly once (tests/cpp/kv_window_scan.cpp)."""
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("no g++")
+    exe = str(tmp_path / "kv_window_scan")
+    flags = ["-fsanitize=address,undefined", "-fno-omit-frame-pointer"]
+    cmd = [gxx, "-std=c++17", "-O1", "-g", *flags, "-I", CSRC, os.path.join(HERE, "cpp", "kv_window_scan.cpp"), "-o", exe, "-lpthread"]
+    build = subprocess.run(cmd, capture_output=True, text=True, timeout=400)
+    if build.returncode != 0 and "asan" in build.stderr.lower():
+        build = subprocess.run([c for c in cmd if c not in flags], capture_output=True, text=True, timeout=400)
+    assert build.returncode == 0, build.stderr[-3000:]
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=200)
+    assert run.returncode == 0 and "WINDOW SCAN OK" in run.stdout, run.stdout[-2000:] + run.stderr[-2000:]
+    assert "ERROR: AddressSanitizer" not in run.stderr and "runtime error:" not in run.stderr, run.stderr[:4000]
