@@ -64,7 +64,7 @@ void bind_host(py::module_& m) {
         .def("check_healthy", &HostTable::check_healthy)
         .def("inject_insert_failures", &HostTable::inject_insert_failures)
         .def("overflow_size", &HostTable::overflow_size)
-        .def("drain_overflow", &HostTable::drain_overflow)
+        .def("drain_overflow", [](HostTable& t) { return t.drain_overflow(); })
         .def("set_limits", &HostTable::set_limits)
         .def("enable_dirty_tracking", &HostTable::enable_dirty_tracking)
         .def("clear_dirty", &HostTable::clear_dirty)

@@ -395,8 +395,13 @@ public:
             return false;
         }
         if (!healthy_) {
+            // parked items first: they take the rows that an erase freed in their shard, or memory that came back.
+            // While some of them still find no room the table stays as it is - it does not turn healthy for a
+            // moment only to refuse the next insert.
+            if (n_parked_) drain_overflow(true);
+            const uint64_t now = bytes_;
             const uint64_t extra = failed_extra_;
-            const bool fits = (!hard || b + extra <= hard) && (!soft || b + extra <= soft);
+            const bool fits = (!hard || now + extra <= hard) && (!soft || now + extra <= soft);
             bool free_rows = false;
             for (int s : shard_list()) {
                 Shard* sh = get(s);
@@ -404,7 +409,7 @@ public:
                 std::shared_lock<std::shared_mutex> g(sh->mu);
                 free_rows = free_rows || !sh->free_rows.empty();
             }
-            if (fits || free_rows || b < failed_at_bytes_) healthy_ = true;
+            if (n_parked_ == 0 && (fits || free_rows || now < failed_at_bytes_)) healthy_ = true;
         }
         if (healthy_ && n_parked_) drain_overflow();
         return healthy_;
@@ -445,7 +450,7 @@ public:
     }
     // Apply the parked items now (after memory came back: the monitor, a purge, raised limits). Items that still find
     // no room stay parked. Returns how many are left.
-    uint64_t drain_overflow() {
+    uint64_t drain_overflow(bool while_unhealthy = false) {
         for (int s : shard_list()) {
             Shard* sh = get(s);
             if (!sh) continue;
@@ -453,7 +458,7 @@ public:
             std::vector<typename Shard::Parked> still;
             for (auto& it : sh->overflow) {
                 uint32_t row;
-                if (!still.empty() || !find_or_insert(*sh, it.key, &row).ok()) {   // keep the order of what is left
+                if (!still.empty() || !find_or_insert(*sh, it.key, &row, while_unhealthy).ok()) {   // keep the order of what is left
                     still.push_back(std::move(it));
                     continue;
                 }
@@ -503,10 +508,11 @@ private:
         return it == shards_.end() ? nullptr : it->second.get();
     }
 
-    Status find_or_insert(Shard& sh, int64_t key, uint32_t* row) {
+    // `draining`: the caller re-applies parked items of an unhealthy table (check_healthy); the limits still hold.
+    Status find_or_insert(Shard& sh, int64_t key, uint32_t* row, bool draining = false) {
         auto* e = sh.map.find(key);
         if (e) { *row = e->second; return Status::Ok(); }
-        if (!healthy_) return Status::OOM("storage is unhealthy");
+        if (!healthy_ && !draining) return Status::OOM("storage is unhealthy");
         if (fail_period_ && ++fail_counter_ % fail_period_ == 0) {   // fault injection, see inject_insert_failures
             failed_extra_ = 0;
             failed_at_bytes_ = bytes_.load();

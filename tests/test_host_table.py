@@ -274,3 +274,37 @@ def test_layout_epoch_moves_exactly_when_bucket_cursors_lose_their_meaning():
     t.erase_shard(0)
     t.create_shard(0)
     assert t.layout_epoch(0) not in (e0, e1, e2)                      # a shard created anew is another shard
+
+
+def test_health_does_not_flap_while_parked_items_find_no_room():
+    """Rows freed in one shard do not help the parked items of another: the table drains what it can at every
+    re-evaluation and stays unhealthy until the last parked item has a row."""
+    hc = C.HostTableConfig()
+    hc.dim, hc.n_shards = 64, 2
+    hc.soft_limit_bytes = hc.hard_limit_bytes = 64 * 1024
+    t = C.HostTable(hc)
+    t.create_shard(0)
+    t.create_shard(1)
+    opt = C.OptConfig()
+    keys = np.arange(300, dtype=np.int64)
+    shard = C.sparse_shards_of(keys, 2, [])
+    for i in range(3):
+        st = t.push(keys[i * 100:(i + 1) * 100], np.ones((100, 64), np.float32), opt)
+        if not t.healthy():
+            break
+    assert st.ok() and not t.healthy() and t.overflow_size() > 0          # the push that hit the limit was taken whole
+    parked_before = t.overflow_size()
+    # the shard whose row pool could not double holds the parked items; free rows in the OTHER shard only
+    full = 0 if t.shard_size(0) < t.shard_size(1) else 1
+    have = keys[:(i + 1) * 100]
+    rows, found = t.get_rows(have, True)
+    lone = have[(found == 1) & (shard[:len(have)] == 1 - full)]
+    assert t.erase_keys(lone[:40]) == 40
+    for _ in range(3):
+        assert not t.check_healthy()                                       # no healthy moment in between
+        assert t.overflow_size() == parked_before                          # those rows are of no use to the full shard
+    # now the full shard makes room as well
+    mine = have[(found == 1) & (shard[:len(have)] == full)]
+    assert t.erase_keys(mine[: parked_before + 5]) == parked_before + 5
+    assert t.check_healthy() and t.overflow_size() == 0
+    assert t.push(keys[:10], np.ones((10, 64), np.float32), opt).ok()
