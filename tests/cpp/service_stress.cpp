@@ -7,7 +7,7 @@
 // checks that every gradient was applied exactly once. A second phase reads a table with two replicas per
 // shard from four threads while one server is stopped, a fresh one restores the lost shards from the live
 // replicas, and a second original server is stopped. A third phase mixes immediate and buffered (sync + store)
-// pushes from four threads with statistics scans and dumps. In a fourth the controller changes the shard count
+// pushes from four threads with statistics scans, writing scans and dumps. In a fourth the controller changes the shard count
 // and the replica count of a table and rebalances it while four threads read it. In a fifth the rows that change
 // on a trainer table are shipped to a predictor table again and again while four threads keep pushing, and the
 // predictor must end up equal to the trainer. A sixth loads the trainer's dump into an in-process table with four
@@ -215,6 +215,8 @@ int main() {
         MUST(client.register_handler("push", "psb", "SparseTablePushOperator", "{}", sid3, &hq));
         MUST(client.register_handler("for_each", "psb", "ForEachOperator", "{}", sid3, &hf));
         MUST(client.register_handler("dump", "psb", "DumpOperator", "{}", sid3, &hd));
+        int32_t hw = -1;
+        MUST(client.register_handler("for_each_write", "psb", "ForEachWriteOperator", "{}", sid3, &hw));
         std::vector<std::atomic<uint64_t>> sent(kKeys);
         for (auto& x : sent) x = 0;
         std::atomic<int> bad{0};
@@ -246,6 +248,13 @@ int main() {
                 ForEachResult r;
                 Status st = fe.for_each("{}", &r, 20000);
                 if (!st.ok()) { std::fprintf(stderr, "for_each: %s\n", st.msg().c_str()); ++bad; }
+                // the writing scan walks the rows in place under each shard's write lock, against the pushes; these two
+                // leave every value as it is, so the sums checked below still count every gradient once
+                ForEachHandler fw(&client, sid3, hw);
+                for (const char* carried : {"{\"type\":\"scale\",\"factor\":1.0}", "{\"type\":\"clip\",\"limit\":1e30}"}) {
+                    st = fw.for_each(carried, &r, 20000);
+                    if (!st.ok()) { std::fprintf(stderr, "for_each (write): %s\n", st.msg().c_str()); ++bad; }
+                }
                 DumpArgs da;
                 da.uri = std::string(dir) + "/d" + std::to_string(round);
                 da.file_number = 2;
