@@ -416,6 +416,96 @@ class SparseTable:
                     if len(k):
                         yield torch.from_numpy(k), torch.from_numpy(r)
 
+    # ---- scans over the local entries: the for_each / erase_if verbs of the operator API ------------
+    # A scan is written with torch over batches of (keys, rows) that lie where the table lies (device tensors for
+    # a CUDA table: nothing crosses PCIe). Every rank scans its own entries; ``collective=True`` combines the
+    # answers of all ranks. Parity: pico-ps/operator/ForEachOperator.h:150-233 (reading scan, init / for_each /
+    # merge), :277-359 (writing scan), pico-ps/operator/EraseIfOperator.h:17-58.
+    def _predicate(self, spec):
+        """A built-in predicate ``{"type": "key_mod", "mod": m, "rem": r} | {"type": "l2_below", "threshold": t} |
+        {"type": "slot0_below", "threshold": t} | {"type": "all"}`` (the menu of the RPC path's EraseIfOperator) as
+        a function of a batch."""
+        if callable(spec):
+            return spec
+        kind, dim = spec.get("type"), self.dim
+        if kind == "key_mod":
+            mod, rem = int(spec.get("mod", 2)), int(spec.get("rem", 1))
+            return lambda k, r: torch.remainder(k, mod) == rem
+        if kind == "l2_below":
+            t = float(spec.get("threshold", 0.0))
+            return lambda k, r: r[:, :dim].double().pow(2).sum(1).sqrt() < t
+        if kind == "slot0_below":
+            if self.table.stride() < 2 * dim:
+                raise ValueError("slot0_below needs an optimizer with a slot")
+            t = float(spec.get("threshold", 0.0))
+            return lambda k, r: r[:, dim:2 * dim].double().mean(1) < t
+        if kind == "all":
+            return lambda k, r: torch.ones(k.numel(), dtype=torch.bool, device=k.device)
+        raise ValueError("unknown predicate %r" % (kind,))
+
+    def _all_reduce(self, value: torch.Tensor, op: str) -> torch.Tensor:
+        if self.world > 1:
+            import torch.distributed as dist
+            value = value.to(self.device if self.is_cuda else "cpu")
+            dist.all_reduce(value, op=dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.SUM, group=self.group)
+        return value
+
+    def erase_if(self, predicate, *, collective: bool = False, batch: int = 1 << 18) -> int:
+        """Erase the local entries for which ``predicate(keys, rows) -> bool mask`` holds (or a built-in predicate
+        given as a dict, see ``_predicate``). Returns the number erased here, or on all ranks with ``collective``."""
+        pred = self._predicate(predicate)
+        doomed = []
+        for k, r in self.export(batch=batch):
+            m = pred(k, r)
+            if bool(m.any()):
+                doomed.append(k[m])
+        # erased after the walk: an erase may make a host index rebuild itself, which would move the entries under it
+        n = self.erase_keys(torch.cat(doomed)) if doomed else 0
+        if collective:
+            n = int(self._all_reduce(torch.tensor([n], dtype=torch.int64), "sum").item())
+        return n
+
+    def for_each(self, fn=None, *, section: int = 0, collective: bool = False, batch: int = 1 << 18):
+        """Reading scan. With ``fn(keys, rows)``: called per batch, the list of its results is returned (the caller
+        merges). Without: the built-in statistics of row section ``section`` (0 = embedding, 1 / 2 = optimizer
+        slots) as ``{"count", "sum", "sum_sq", "max_abs"}``, over all ranks with ``collective``."""
+        if fn is not None:
+            return [fn(k, r) for k, r in self.export(batch=batch)]
+        dim = self.dim
+        if (section + 1) * dim > self.table.stride():
+            raise ValueError("no such row section")
+        acc = torch.zeros(3, dtype=torch.float64)
+        mx = torch.zeros(1, dtype=torch.float64)
+        for k, r in self.export(batch=batch):
+            v = r[:, section * dim:(section + 1) * dim].double()
+            acc += torch.stack([torch.tensor(float(k.numel()), dtype=torch.float64, device=v.device), v.sum(), v.pow(2).sum()]).cpu()
+            mx = torch.maximum(mx, v.abs().max().reshape(1).cpu())
+        if collective:
+            acc, mx = self._all_reduce(acc, "sum").cpu(), self._all_reduce(mx, "max").cpu()
+        return {"count": int(acc[0].item()), "sum": acc[1].item(), "sum_sq": acc[2].item(), "max_abs": mx.item()}
+
+    def for_each_write(self, fn, *, collective: bool = False, batch: int = 1 << 18) -> int:
+        """Writing scan: ``fn(keys, rows)`` returns the new rows of the batch (same shape: embedding, optimizer
+        slots and, if present, the sync delta) or ``None``; rows that differ are written back. Returns how many
+        rows changed here, or on all ranks with ``collective``. Call it between steps: a push that lands between
+        the read of a batch and its write-back would be overwritten."""
+        n = 0
+        for k, r in self.export(batch=batch):
+            new = fn(k, r)
+            if new is None:
+                continue
+            if new.shape != r.shape:
+                raise ValueError("for_each_write: fn must return rows of the shape it was given")
+            new = new.to(dtype=torch.float32)
+            changed = (new != r).any(1)
+            c = int(changed.sum().item())
+            if c:
+                self.set_rows(k[changed], new[changed], emb_only=False)   # existing keys: the index does not move
+                n += c
+        if collective:
+            n = int(self._all_reduce(torch.tensor([n], dtype=torch.int64), "sum").item())
+        return n
+
     # ---- cold tier (pinned host DRAM under the HBM table) ---------------------------------------
     def enable_cold_tier(self, capacity_rows: int, window: int = 1 << 16) -> None:
         """Attach a pinned-host tier of ``capacity_rows`` rows (the role of the reference's PMEM tier)."""

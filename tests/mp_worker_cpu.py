@@ -86,6 +86,50 @@ def elastic(rank, world):
         shutil.rmtree(uri[0], ignore_errors=True)
 
 
+def scans(rank, world):
+    """for_each / for_each_write / erase_if of the collective table: every rank scans its own entries, the answers
+    are combined over the ranks."""
+    dim = 4
+    t = SparseTable(dim, "adagrad", dict(lr=0.1, init_accumulator=0.5), n_shards=5, device="cpu", init_range=0.0)
+    keys = torch.arange(1, 1201, dtype=torch.int64)
+    mine = keys[rank::world]
+    t.pull(mine)
+    t.push(-(mine % 7 + 1).float()[:, None] * torch.ones(1, dim))            # row = +lr * g / sqrt(acc): depends on key % 7
+    want = t.pull(keys, insert=False)
+    st = t.for_each(collective=True)
+    assert st["count"] == 1200 and abs(st["sum"] - float(want.double().sum())) < 1e-6 * abs(st["sum"])
+    assert abs(st["max_abs"] - float(want.abs().max())) < 1e-12
+    acc = t.for_each(section=1, collective=True)
+    assert acc["count"] == 1200 and acc["sum"] > 0.5 * 1200 * dim
+    # a user reducer: the largest key that this rank holds; merged by the caller
+    parts = t.for_each(lambda k, r: int(k.max()))
+    assert max(max(p) if p else 0 for p in gather(parts)) == 1200
+    # writing scan: halve the embeddings of even keys, everywhere
+    def halve(k, r):
+        new = r.clone()
+        new[k % 2 == 0, :dim] *= 0.5
+        return new
+    assert t.for_each_write(halve, collective=True) == 600
+    got = t.pull(keys, insert=False)
+    even = keys % 2 == 0
+    assert torch.equal(got[even], 0.5 * want[even]) and torch.equal(got[~even], want[~even])
+    assert t.for_each(section=1, collective=True)["sum"] == acc["sum"]        # the slots were left alone
+    assert t.for_each_write(lambda k, r: None) == 0
+    # erase_if: a built-in predicate, then a torch predicate over keys and rows
+    assert t.erase_if({"type": "key_mod", "mod": 3, "rem": 0}, collective=True) == 400
+    small = float(got.norm(dim=1).median())
+    n = t.erase_if(lambda k, r: r[:, :dim].norm(dim=1) < small, collective=True)
+    left = keys[keys % 3 != 0]
+    assert n == int((got[keys % 3 != 0].norm(dim=1) < small).sum()) and sum(gather(t.size())) == len(left) - n
+    assert t.erase_if({"type": "all"}, collective=True) == len(left) - n and sum(gather(t.size())) == 0
+    try:
+        t.erase_if({"type": "nonsense"})
+        raise AssertionError("an unknown predicate must be refused")
+    except ValueError:
+        pass
+    dist.barrier()
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dist.init_process_group("gloo")
@@ -114,6 +158,7 @@ def main():
             owners = {t.shard_owner[__import__("parameter_server_b200").C.sparse_shard_of(int(x), n_shards)] for x in k.tolist()}
             assert owners <= {rank}, owners
     elastic(rank, world)
+    scans(rank, world)
     # dense table: all-reduce + optimizer on every rank, identical parameters everywhere
     d = DenseTable({"w": (64, 8), "b": (64,)}, "adamw", dict(lr=1e-2, weight_decay=0.01), device="cpu")
     d.load({"w": torch.ones(64, 8), "b": torch.zeros(64)})
