@@ -152,3 +152,77 @@ def test_two_followers_and_one_of_them_appears_late():
             syncer.stop()
         server.stop()
         m.stop()
+
+
+def test_collective_training_table_feeds_a_predictor_table_of_the_service_layer():
+    """`parallel.PredictorSync`: the rows that a collective (training) table changed travel to a predictor table of
+    the RPC path in blocks; a round that the predictor refused is sent again in full, marks are cleared only after a
+    whole round."""
+    import torch
+    from parameter_server_b200 import SparseTable
+    from parameter_server_b200.parallel import PredictorSync
+    from parameter_server_b200.utils.status import StatusError
+
+    master = S.Master()
+    servers = [S.Server(master.address()) for _ in range(2)]
+    client = S.Client(master.address())
+    try:
+        ids = [s.node_id() for s in servers]
+        # full rows travel: the predictor keeps the same row layout (adagrad: embedding + accumulator)
+        cfg = dict(dim=DIM, optimizer="adagrad", lr=0.1, init_accumulator=0.5, init_range=0.0)
+        st, sid = client.create_storage(S.LIB, "SparseTableStorageOperator", S.storage_config({ids[0]: [0, 1], ids[1]: [1, 0]}, cfg))
+        assert st.ok(), st
+        _, h_pull = client.register_handler("pull_ro", S.LIB, "SparseTablePullOperator", json.dumps({"read_only": True}), sid)
+        _, h_sync = client.register_handler("sync", S.LIB, "KVSyncOperator", json.dumps({"block_size": 64}), sid)
+        pull = S.PullHandler(client, sid, h_pull)
+        train = SparseTable(DIM, "adagrad", dict(lr=0.1, init_accumulator=0.5), init_range=0.0, device="cpu", group="none")
+        sync = PredictorSync(train, S.SyncHandler(client, sid, h_sync))
+        assert sync.block == 64
+        keys = torch.arange(1, 1001, dtype=torch.int64)
+        train.pull(keys)
+        train.push(-torch.ones(1000, DIM) * (keys % 5 + 1).float()[:, None])
+        assert sync.sync() == 1000
+        want = train.pull(keys, insert=False).numpy()
+        for _ in range(4):                                                     # either replica
+            st, rows = pull.pull(keys.numpy())
+            assert st.ok() and np.array_equal(rows, want)
+        assert sync.sync() == 0
+        # only what changed travels
+        some = keys[::10]
+        train.pull(some)
+        train.push(torch.ones(100, DIM))
+        for s in servers:
+            s.stop()                                                           # the predictor cluster is away
+        try:
+            sync.timeout_ms = 500
+            sync.sync()
+            raise AssertionError("a round that nobody took must raise")
+        except StatusError:
+            pass
+        assert sync.failed_rounds == 1
+        # a new predictor cluster (its table starts empty): the handler is replaced, the kept marks send the increment
+        servers = [S.Server(master.address()) for _ in range(2)]
+        ids = [s.node_id() for s in servers]
+        st, sid2 = client.create_storage(S.LIB, "SparseTableStorageOperator", S.storage_config({ids[0]: [0], ids[1]: [1]}, cfg))
+        assert st.ok(), st
+        _, h_pull2 = client.register_handler("pull_ro", S.LIB, "SparseTablePullOperator", json.dumps({"read_only": True}), sid2)
+        _, h_sync2 = client.register_handler("sync", S.LIB, "KVSyncOperator", "{}", sid2)
+        sync.handler = S.SyncHandler(client, sid2, h_sync2)
+        sync.timeout_ms = 30000
+        assert sync.sync() == 100
+        st, rows = S.PullHandler(client, sid2, h_pull2).pull(some.numpy())
+        assert st.ok() and np.array_equal(rows, train.pull(some, insert=False).numpy())
+        # embeddings only, into a predictor table without optimizer state
+        st, sid3 = client.create_storage(S.LIB, "SparseTableStorageOperator",
+                                         S.storage_config({ids[0]: [0, 1, 2]}, dict(dim=DIM, optimizer="set", init_range=0.0)))
+        assert st.ok(), st
+        _, h_pull3 = client.register_handler("pull_ro", S.LIB, "SparseTablePullOperator", json.dumps({"read_only": True}), sid3)
+        _, h_sync3 = client.register_handler("sync", S.LIB, "KVSyncOperator", "{}", sid3)
+        emb = PredictorSync(train, S.SyncHandler(client, sid3, h_sync3), embedding_only=True)
+        assert emb.sync() == 1000
+        st, rows = S.PullHandler(client, sid3, h_pull3).pull(keys.numpy())
+        assert st.ok() and np.array_equal(rows, train.pull(keys, insert=False).numpy())
+    finally:
+        for s in servers:
+            s.stop()
+        master.stop()
