@@ -78,7 +78,13 @@ public:
     }
 
     // Returns (entry*, inserted)
+    // The two reserved keys (the empty marker and the one after it, the tombstone) cannot be stored: find never
+    // matches them and try_emplace refuses them, so a caller that lets one through reads "absent" instead of the
+    // contents of an empty bucket.
+    bool reserved(const K& key) const { return key == empty_ || key == tomb_; }
+
     std::pair<Entry*, bool> try_emplace(const K& key, const V& value = V()) {
+        if (reserved(key)) throw std::invalid_argument("EasyHashMap: reserved key");
         if ((double)(used_ + 1) > max_load_ * (double)table_.size()) rehash(used_ > size_ * 2 + 8 ? table_.size() : table_.size() * 2);
         size_t mask = table_.size() - 1;
         size_t p = (size_t)slot_hash((int64_t)key) & mask;
@@ -102,6 +108,7 @@ public:
     Entry* force_emplace(const K& key, const V& value = V()) { return try_emplace(key, value).first; }
 
     Entry* find(const K& key) {
+        if (reserved(key)) return nullptr;
         size_t mask = table_.size() - 1;
         size_t p = (size_t)slot_hash((int64_t)key) & mask;
         for (size_t np = 1;; ++np) {

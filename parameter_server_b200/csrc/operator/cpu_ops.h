@@ -22,6 +22,7 @@ inline Status cpu_pull(HostTable& t, const int64_t* keys, size_t n, size_t bag_s
     uint32_t n_uniq = 0;
     std::vector<uint32_t> inverse(n);
     for (size_t i = 0; i < n; ++i) {
+        if (whole.reserved(keys[i])) return Status::InvalidConfig("key " + std::to_string(keys[i]) + " is reserved");
         auto r = whole.try_emplace(keys[i], n_uniq);
         if (r.second) {
             int s = t.shard_of(keys[i]);
@@ -67,6 +68,7 @@ inline Status cpu_push(HostTable& t, const int64_t* keys, const float* grads, si
     std::vector<float> agg;
     const float scale = mean ? 1.0f / (float)bag_size : 1.0f;
     for (size_t i = 0; i < n; ++i) {
+        if (whole.reserved(keys[i])) return Status::InvalidConfig("key " + std::to_string(keys[i]) + " is reserved");
         auto r = whole.try_emplace(keys[i], (uint32_t)uniq_keys.size());
         if (r.second) {
             uniq_keys.push_back(keys[i]);

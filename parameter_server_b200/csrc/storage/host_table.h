@@ -512,6 +512,7 @@ private:
     Status find_or_insert(Shard& sh, int64_t key, uint32_t* row, bool draining = false) {
         auto* e = sh.map.find(key);
         if (e) { *row = e->second; return Status::Ok(); }
+        if (sh.map.reserved(key)) return Status::InvalidConfig("key " + std::to_string(key) + " is reserved (the two smallest int64 values mark empty and erased slots)");
         if (!healthy_ && !draining) return Status::OOM("storage is unhealthy");
         if (fail_period_ && ++fail_counter_ % fail_period_ == 0) {   // fault injection, see inject_insert_failures
             failed_extra_ = 0;

@@ -308,3 +308,21 @@ def test_health_does_not_flap_while_parked_items_find_no_room():
     assert t.erase_keys(mine[: parked_before + 5]) == parked_before + 5
     assert t.check_healthy() and t.overflow_size() == 0
     assert t.push(keys[:10], np.ones((10, 64), np.float32), opt).ok()
+
+
+def test_reserved_keys_are_refused_by_the_host_table_and_the_collective_cpu_path():
+    """INT64_MIN and INT64_MIN + 1 mark empty and erased buckets: pull / push / set_rows refuse them with a status,
+    reads report them absent; nothing is inserted."""
+    from parameter_server_b200 import SparseTable
+    from parameter_server_b200.utils.status import StatusError
+    t = SparseTable(8, "adagrad", dict(lr=0.1), device="cpu", group="none")
+    t.pull(torch.arange(10))
+    for k in (-2 ** 63, -2 ** 63 + 1):
+        for call in (lambda: t.pull(torch.tensor([5, k])), lambda: t.pull(torch.tensor([k]), insert=False),
+                     lambda: t.push(torch.ones(2, 8), torch.tensor([5, k])),
+                     lambda: t.set_rows(torch.tensor([k]), torch.ones(1, 16))):
+            with pytest.raises(StatusError) as e:
+                call()
+            assert "reserved" in str(e.value)
+        assert t.get_rows(torch.tensor([k]))[1].tolist() == [0] and t.erase_keys(torch.tensor([k])) == 0
+    assert t.size() == 10
