@@ -304,7 +304,8 @@ public:
         if (!sh) return 0;
         std::shared_lock<std::shared_mutex> g(sh->mu);
         const auto& b = sh->map.buckets();
-        size_t end = std::min(b.size(), cursor + window);
+        cursor = std::min(cursor, b.size());
+        size_t end = std::min(b.size(), cursor + std::max<size_t>(window, 1));   // a window of 0 still moves on
         for (size_t i = cursor; i < end; ++i) {
             if (!sh->map.live(b[i])) continue;
             if (dirty_only && !sh->dirty[b[i].second]) continue;

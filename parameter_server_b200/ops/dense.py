@@ -107,10 +107,18 @@ class DenseTable:
 
     # ------------------------------------------------------------------------------------------
     def load(self, values: Dict[str, torch.Tensor]) -> None:
-        """Set the parameters from full fp32 tensors (identical on every rank)."""
+        """Set the parameters from full fp32 tensors (identical on every rank). Tensors that are not named become
+        zero: a load replaces the whole table."""
         full = torch.zeros(self.numel, dtype=torch.float32, device=self.device)
         for name, v in values.items():
+            if name not in self.offsets:
+                raise KeyError("no dense tensor %r in this table" % (name,))
             off, shape = self.offsets[name]
+            want = 1
+            for d in shape:
+                want *= int(d)
+            if v.numel() != want:
+                raise ValueError("dense tensor %r has %d elements, the table holds %s" % (name, v.numel(), tuple(shape)))
             full[off:off + v.numel()] = v.reshape(-1).to(self.device, torch.float32)
         if self.is_cuda:
             raise_if_error(self.engine.load_full(full.data_ptr(), _stream()))

@@ -68,6 +68,8 @@ class SparseTable:
         self.group = group
         self.world, self.rank = _dist_info(group)
         self.n_shards = int(n_shards or self.world)
+        if self.n_shards < 1:
+            raise ValueError("n_shards must be at least 1")
         self.read_only = read_only
         self.sync = bool(sync)
         self.opt = make_opt_config(optimizer, **(opt_kwargs or {}))

@@ -1,6 +1,7 @@
 """The switches of the GPU kernels exist on the host back-end too (as no-ops), so that a script written for a GPU
 job runs unchanged on CPU, and the host restatement of the reproducible push's summation order is what it says."""
 import numpy as np
+import pytest
 import torch
 
 from blocked_sum import BLOCK, blocked_segment_sum
@@ -47,3 +48,25 @@ def test_blocked_sum_is_a_plain_left_to_right_sum_up_to_one_block():
     for p_ in parts:
         tot = tot + p_
     assert np.array_equal(tot, agg[0])
+
+
+def test_misuse_is_answered_with_an_exception_not_with_silent_damage():
+    import numpy as np
+    from parameter_server_b200 import SparseTable
+    from parameter_server_b200.ops.dense import DenseTable
+    d = DenseTable({"w": (4, 4), "b": (4,)}, "adamw", dict(lr=1e-2), device="cpu")
+    with pytest.raises(ValueError):
+        d.load({"w": torch.ones(5, 5)})                      # would have run over the neighbour's parameters
+    with pytest.raises(KeyError):
+        d.load({"zzz": torch.ones(4)})
+    d.load({"w": torch.ones(4, 4)})
+    assert float(d.pull("w").sum()) == 16.0 and float(d.pull("b").abs().sum()) == 0.0
+    with pytest.raises(ValueError):
+        SparseTable(8, "sgd", dict(lr=0.1), device="cpu", group="none", n_shards=-1)
+    t = SparseTable(8, "sgd", dict(lr=0.1), device="cpu", group="none")
+    t.pull(torch.arange(50))
+    # a scan cursor always moves on, whatever window the caller asks for
+    k, r, cursor, finished = t.table.export_shard(0, 0, 0, False)
+    assert cursor == 1 and not finished
+    k, r, cursor, finished = t.table.export_shard(0, 1 << 60, 10, False)
+    assert finished and len(k) == 0
