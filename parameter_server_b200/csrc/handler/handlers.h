@@ -522,6 +522,9 @@ public:
     Status dump(const DumpArgs& args, uint64_t* n_records, int timeout_ms = -1) {
         std::string dir, format;
         DumpArgs::split_uri(args.uri, &dir, &format);
+        *n_records = 0;
+        if (dir.empty()) return Status::InvalidConfig("dump: the uri names no directory");
+        if (args.file_number < 1) return Status::InvalidConfig("dump: file_number must be at least 1");
         PSB_RETURN_IF_ERROR(mkdir_p(dir));
         return with_retry([&](int left) -> Status {
             *n_records = 0;
@@ -578,6 +581,8 @@ private:
     Status run(const std::string& uri, bool rehash, uint64_t* n_records, int conc, int timeout_ms) {
         std::string dir, format;
         DumpArgs::split_uri(uri, &dir, &format);
+        *n_records = 0;
+        if (dir.empty()) return Status::InvalidConfig("load: the uri names no directory");
         std::vector<std::string> files = list_model_files(dir);
         if (files.empty()) return Status::Error("load: no model_* files under " + dir);
         return with_retry([&](int left) -> Status {

@@ -70,7 +70,9 @@ public:
     explicit SparseTableStorageOperator(const Json& c) : Operator(c) {
         Status st = parse_opt_config(c, &opt_);
         if (!st.ok()) throw std::runtime_error(st.msg());
-        dim_ = (uint32_t)c.at("dim").as_int(16);
+        const int64_t dim = c.at("dim").as_int(16);
+        if (dim < 1 || dim > 65536) throw std::runtime_error("dim must be between 1 and 65536, not " + std::to_string(dim));
+        dim_ = (uint32_t)dim;
         // key -> shard: "hash" (the default: jump-consistent hash of the mixed key), "dense" (slices of dense values,
         // hash % N) or "modulo" (key mod N, for tables whose keys are laid out by their producer - the custom
         // partitioner of the reference's predictor test family, pico-ps/test/TestPredictorOps.h:52-64)
@@ -1055,6 +1057,7 @@ public:
                          uint64_t* n_records) const {
         std::string dir, format;
         DumpArgs::split_uri(args.uri, &dir, &format);
+        if (dir.empty()) return Status::InvalidConfig("dump: the uri names no directory");   // never "/model_..." by accident
         PSB_RETURN_IF_ERROR(mkdir_p(dir));
         KVStorage* st = e.storage.get();
         DsWriter w(dir + "/model_" + std::to_string(node_id) + "_" + std::to_string(file_id), format, st->stride(), &comp_);

@@ -12,6 +12,7 @@
 // choice is uniformly random among RUNNING holders (:425-439).
 #pragma once
 #include <algorithm>
+#include <climits>
 #include <cstdint>
 #include <map>
 #include <random>
@@ -159,8 +160,24 @@ struct TableDescriptor {
             d.node_id = (int)n.at("g_rank").as_int(-1);
             if (d.node_id < 0) return Status::InvalidConfig("node without g_rank");
             if (!seen.insert(d.node_id).second) return Status::InvalidConfig("duplicate g_rank in nodes");
-            for (auto& s : n.at("shard_list").elements()) d.shard_list.push_back((int32_t)s.as_int());
+            std::set<int32_t> mine;
+            for (auto& s : n.at("shard_list").elements()) {
+                const int64_t id = s.as_int(-1);
+                if (id < 0 || id > INT32_MAX) return Status::InvalidConfig("shard ids are non-negative integers");
+                if (!mine.insert((int32_t)id).second) return Status::InvalidConfig("shard " + std::to_string(id) + " is listed twice for node " + std::to_string(d.node_id));
+                d.shard_list.push_back((int32_t)id);
+            }
             out->push_back(d);
+        }
+        // Keys map to shards 0 .. G-1, so a placement must name exactly those: a gap would be a shard that nobody
+        // holds (every key of it unreachable), an empty placement a table without data.
+        std::set<int32_t> all;
+        for (auto& d : *out) all.insert(d.shard_list.begin(), d.shard_list.end());
+        if (all.empty()) return Status::InvalidConfig("the placement holds no shard");
+        if ((size_t)*all.rbegin() + 1 != all.size()) {
+            int32_t missing = 0;
+            while (all.count(missing)) ++missing;
+            return Status::InvalidConfig("shard ids must be 0 .. G-1 without gaps: nobody holds shard " + std::to_string(missing));
         }
         return Status::Ok();
     }

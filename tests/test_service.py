@@ -456,6 +456,36 @@ def test_modulo_partition_places_keys_by_their_value_and_survives_a_reshard(clus
     assert not st.ok() and "partition" in str(st)
 
 
+def test_bad_placements_and_arguments_are_refused_before_they_cost_data(cluster3, tmp_path):
+    """A placement with a gap, without shards or with a shard listed twice, a dim out of range, a dump into no
+    directory or into zero files: each is answered with INVALID_CONFIG and the table is as it was."""
+    cl = cluster3
+    ids = cl.ids()
+    create = lambda nodes, **kw: cl.client.create_storage(S.LIB, "SparseTableStorageOperator", S.storage_config(nodes, op_cfg(**kw)))[0]
+    for nodes in ({}, {ids[0]: []}, {ids[0]: [0, 7]}, {ids[0]: [-1, 0]}, {ids[0]: [0, 1, 1]}):
+        assert create(nodes).code() == StatusCode.INVALID_CONFIG, nodes
+    for dim in (0, -4, 1 << 40):
+        assert create({ids[0]: [0]}, dim=dim).code() == StatusCode.INVALID_CONFIG
+    sid, h = make_table(cl, {ids[0]: [0], ids[1]: [1], ids[2]: [2]})
+    keys = np.arange(300, dtype=np.int64)
+    assert S.PushHandler(cl.client, sid, h["push"]).async_push(keys, np.ones((300, DIM), np.float32)).ok()
+    upd = S.UpdateContextHandler(cl.client, sid, h["update_ctx"])
+    for nodes in ("[]", S.nodes_json({ids[0]: [0, 2]}), S.nodes_json({ids[0]: [0], ids[1]: [0, 3]})):
+        assert upd.update_context(nodes).code() == StatusCode.INVALID_CONFIG, nodes
+    dump = S.DumpHandler(cl.client, sid, h["dump"])
+    assert dump.dump("", 1)[0].code() == StatusCode.INVALID_CONFIG              # would have been files in "/"
+    assert dump.dump("?format=binary", 1)[0].code() == StatusCode.INVALID_CONFIG
+    for n_files in (0, -3):
+        assert dump.dump(str(tmp_path / "d"), n_files)[0].code() == StatusCode.INVALID_CONFIG
+    assert S.LoadHandler(cl.client, sid, h["load"]).load("")[0].code() == StatusCode.INVALID_CONFIG
+    # nothing of all that touched the table
+    st, rows = S.PullHandler(cl.client, sid, h["pull_ro"]).pull(keys)
+    assert st.ok() and np.all(rows == 1.0)
+    assert S.PushHandler(cl.client, sid, h["push"]).async_push(keys, np.ones((300, DIM), np.float32)).ok()
+    st, n = dump.dump(str(tmp_path / "d"), 2)
+    assert st.ok() and n == 300
+
+
 def test_restore_from_dump_when_no_replica(tmp_path):
     cl = Cluster(2)
     try:
