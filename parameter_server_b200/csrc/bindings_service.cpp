@@ -616,11 +616,18 @@ void bind_service(py::module_& m) {
         });
     py::class_<NativePullHandler>(m, "NativePullHandler")
         .def(py::init<NativePS*, int32_t, int32_t>(), py::keep_alive<1, 2>())
+        .def("dim", &NativePullHandler::dim)
         .def("pull", [](NativePullHandler& h, KeyArray keys, int dim) {
-            F32Array out({(py::ssize_t)keys.size(), (py::ssize_t)dim});
-            Status st = h.pull(keys.data(), (size_t)keys.size(), out.mutable_data());
+            // the handler writes rows of the table's width: a caller that names another one would get a buffer of
+            // the wrong size written to (dim <= 0: use the table's)
+            const uint32_t have = h.dim();
+            if (dim <= 0) dim = (int)have;
+            F32Array out({(py::ssize_t)keys.size(), (py::ssize_t)std::max(dim, 0)});
+            Status st = have != 0 && (uint32_t)dim != have
+                            ? Status::InvalidConfig("the table's rows are " + std::to_string(have) + " wide, not " + std::to_string(dim))
+                            : h.pull(keys.data(), (size_t)keys.size(), out.mutable_data());
             return py::make_tuple(st, out);
-        });
+        }, py::arg("keys"), py::arg("dim") = 0);
     py::class_<NativeLoadHandler>(m, "NativeLoadHandler")
         .def(py::init<NativePS*, int32_t, int32_t>(), py::keep_alive<1, 2>())
         .def("load", [](NativeLoadHandler& h, const std::string& uri, int threads) {

@@ -54,6 +54,11 @@ private:
 class NativePullHandler {
 public:
     NativePullHandler(NativePS* ps, int32_t sid, int32_t hid) : ps_(ps), sid_(sid), hid_(hid) {}
+    // Width of a pulled row (0 when the storage is unknown): `out` of pull() holds n * dim() floats.
+    uint32_t dim() const {
+        auto e = ps_->entry(sid_);
+        return e && e->storage_op ? storage_op_of(*e)->dim() : 0;
+    }
     Status pull(const int64_t* keys, size_t n, float* out) {
         auto e = ps_->entry(sid_);
         if (!e) return Status::InvalidID("unknown storage");

@@ -723,6 +723,9 @@ def test_predictor_sync_udf_and_native_ps(tmp_path, cluster3):
     assert st.ok() and n == 500 and nps.size(nsid) == 500
     st, rows = S.NativePullHandler(nps, nsid, ph).pull(keys, DIM)
     assert st.ok() and np.all(rows == 2.0)
+    native = S.NativePullHandler(nps, nsid, ph)
+    assert native.dim() == DIM and native.pull(keys)[1].shape == (500, DIM)                 # the table's width by default
+    assert native.pull(keys, DIM - 1)[0].code() == StatusCode.INVALID_CONFIG                # not a short buffer written over
 
 
 def test_common_pieces():
