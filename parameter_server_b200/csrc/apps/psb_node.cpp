@@ -66,7 +66,14 @@ int ctl_main(int argc, char** argv) {
     try {
         Controller ctl(master);
         const std::string& verb = a[0];
-        auto num = [&](size_t i) { return std::atoi(a.at(i).c_str()); };
+        auto num = [&](size_t i) {   // a number, all of it: "abc" or "12x" is a mistake, not a 0 or a 12
+            const std::string& t = a.at(i);
+            size_t used = 0;
+            int v = 0;
+            try { v = std::stoi(t, &used); } catch (const std::exception&) { used = 0; }
+            if (used == 0 || used != t.size()) throw std::invalid_argument("'" + t + "' is not a number");
+            return v;
+        };
         Status st;
         Json out;
         bool has_out = false;
