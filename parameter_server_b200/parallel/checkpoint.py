@@ -50,6 +50,10 @@ def _record_dtype(stride: int) -> np.dtype:
 def dump(table: SparseTable, uri: str, file_number: int = 1, batch: int = 1 << 18) -> int:
     """Collective. Returns the number of records this rank wrote."""
     target = uri.split("?", 1)[0]
+    if not target:
+        raise ValueError("dump: the uri names no directory")
+    if int(file_number) < 1:
+        raise ValueError("dump: file_number must be at least 1")
     remote = _is_remote(target)
     path = tempfile.mkdtemp(prefix="psb_dump_") if remote else target
     os.makedirs(path, exist_ok=True)
