@@ -199,6 +199,8 @@ class SparseTable:
         """Prepare a push for ``keys`` without returning rows (push without a preceding pull)."""
         keys = keys.reshape(-1)
         if self.is_cuda:
+            if keys.dtype != torch.int64 or not keys.is_cuda:
+                raise TypeError("keys must be a CUDA int64 tensor")   # a host pointer must never reach the kernel
             keys = keys.contiguous()
             flags = C.FUSED_INSERT | C.FUSED_PREPARE_PUSH | (C.FUSED_MEAN if mean else 0)
             raise_if_error(self.engine.pull(keys.data_ptr(), keys.numel(), bag_size, 0, flags, _stream()))
@@ -355,6 +357,8 @@ class SparseTable:
         """Read rows of LOCAL keys without inserting. Returns (rows, found)."""
         keys = keys.reshape(-1)
         if self.is_cuda:
+            if keys.dtype != torch.int64 or not keys.is_cuda:
+                raise TypeError("keys must be a CUDA int64 tensor")
             keys = keys.contiguous()
             w = self.dim if emb_only else self.table.stride()
             out = torch.empty((keys.numel(), w), dtype=torch.float32, device=self.device)
@@ -381,6 +385,8 @@ class SparseTable:
     def erase_keys(self, keys: torch.Tensor) -> int:
         keys = keys.reshape(-1)
         if self.is_cuda:
+            if keys.dtype != torch.int64 or not keys.is_cuda:
+                raise TypeError("keys must be a CUDA int64 tensor")
             keys = keys.contiguous()
             st, n = self.table.erase_keys(keys.data_ptr(), keys.numel(), _stream())
             raise_if_error(st)
@@ -523,7 +529,7 @@ class SparseTable:
         return int(n)
 
     def spill_keys(self, keys: torch.Tensor) -> int:
-        k = keys.reshape(-1).cpu().contiguous()
+        k = keys.reshape(-1).cpu().to(torch.int64).contiguous()
         torch.cuda.current_stream().synchronize()
         st, n = self.cold.spill_keys(k.data_ptr(), k.numel())
         raise_if_error(st)
@@ -532,7 +538,7 @@ class SparseTable:
     def prefetch_cold(self, keys: torch.Tensor) -> int:
         """Bring the rows of ``keys`` (a host tensor, e.g. the next batch while it is still in pinned
         memory) back from the cold tier before they are pulled. Returns how many came back."""
-        k = keys.reshape(-1).cpu().contiguous()
+        k = keys.reshape(-1).cpu().to(torch.int64).contiguous()
         st, n = self.cold.fetch(k.data_ptr(), k.numel())
         raise_if_error(st)
         return int(n)
@@ -541,7 +547,7 @@ class SparseTable:
         """Start bringing back the cold rows among ``keys`` (at most one staging window of them) without
         blocking: lookup, packing and the host-to-device copy run on a worker thread and a side stream while
         the current step computes. ``commit_prefetch()`` inserts them."""
-        k = keys.reshape(-1).cpu().contiguous()
+        k = keys.reshape(-1).cpu().to(torch.int64).contiguous()
         self.cold.stage_fetch_async(k.data_ptr(), k.numel())
 
     def commit_prefetch(self) -> int:
