@@ -49,8 +49,21 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         K = a.shape[0] if a_mn else a.shape[1]
     if N is None:
         N = b.shape[1] if b_mn else b.shape[0]
+    # the kernel reads and writes what M, N, K say: they must lie inside the tensors that were handed in
+    if a.dim() != 2 or b.dim() != 2:
+        raise ValueError("gemm operands are 2-D")
+    am, ak = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    bn, bk = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if M > am or K > ak or N > bn or K > bk:
+        raise ValueError(f"gemm: M, N, K = {M}, {N}, {K} exceed the operands ({am} x {ak} and {bn} x {bk})")
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    elif not out.is_cuda or out.dim() != 2 or out.shape[0] < M or out.shape[1] < N:
+        raise ValueError(f"gemm: out must be a CUDA tensor of at least {M} x {N}")
+    if bias is not None and (not bias.is_cuda or bias.numel() < N):
+        raise ValueError(f"gemm: bias must be a CUDA tensor of at least {N} elements")
+    if mask is not None and (not mask.is_cuda or mask.dim() != 2 or mask.shape[0] < M or mask.shape[1] < N):
+        raise ValueError(f"gemm: mask must be a CUDA tensor of at least {M} x {N}")
     assert out.stride(-1) == 1
     o16 = out if out.dtype == torch.bfloat16 else None
     o32 = out if out.dtype == torch.float32 else None
