@@ -242,3 +242,47 @@ def test_base64_decoder_refuses_what_is_not_base64(text):
     else:
         assert got == want
     assert not C.get_base64_config('{"k": 5}', "k")[0].ok() and not C.get_base64_config('{}', "k")[0].ok()
+
+
+@settings(max_examples=60, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@given(steps=st.lists(st.tuples(st.sampled_from(["insert", "erase", "clear"]), st.integers(0, 400), st.integers(1, 120)), min_size=1, max_size=30),
+       grow=st.sampled_from([0.0, 0.25, 0.5, 0.8, 3.0]), shrink=st.sampled_from([0.0, 0.1, 0.3]), expected=st.sampled_from([0, 500]))
+def test_index_ratios_never_lose_a_key_and_the_byte_count_follows_the_buckets(steps, grow, shrink, expected):
+    """Whatever grow / shrink ratios and whatever sequence of inserts, erases and clears: a scan by cursor sees exactly
+    the live keys, the load stays under the configured limit, the layout epoch moves exactly when the bucket count
+    does, and the table's byte count moves by 16 bytes per bucket with it."""
+    hc = C.HostTableConfig()
+    hc.dim, hc.n_shards = DIM, 1
+    hc.index_grow_ratio, hc.index_shrink_ratio, hc.expected_max_items = grow, shrink, expected
+    t = C.HostTable(hc)
+    t.create_shard(0)
+    buckets = lambda: t.export_shard(0, 0, 1 << 30, False)[2]
+    live = set()
+    limit = min(max(grow, 0.25), 0.85) if grow else 0.5
+    for what, start, count in steps:
+        b0, e0, m0 = buckets(), t.layout_epoch(0), t.memory_usage()
+        keys = np.arange(start, start + count, dtype=np.int64) * 3 - 200
+        rows_before = t.size()
+        if what == "insert":
+            assert t.set_rows(keys, np.ones((count, DIM), F), True).ok()
+            live |= set(keys.tolist())
+        elif what == "erase":
+            assert t.erase_keys(keys) == len(live & set(keys.tolist()))
+            live -= set(keys.tolist())
+        else:
+            t.clear()
+            t.create_shard(0)
+            live.clear()
+        b1 = buckets()
+        assert t.size() == len(live) and len(live) <= limit * b1 + 1e-9
+        assert (t.layout_epoch(0) != e0) == (b1 != b0) or what == "clear" or (what == "insert" and b1 == b0 and t.layout_epoch(0) != e0)
+        if what != "clear":
+            rows_grew = t.memory_usage() - m0 - 16 * (b1 - b0)
+            assert rows_grew >= 0 and rows_grew % (DIM * 4) == 0          # what is not index is row pool, which only grows
+            if what == "erase":
+                assert rows_grew == 0
+        seen, cursor, finished = [], 0, False
+        while not finished:
+            k, _, cursor, finished = t.export_shard(0, cursor, 37, False)
+            seen += k.tolist()
+        assert sorted(seen) == sorted(live)
