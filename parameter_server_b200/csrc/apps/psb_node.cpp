@@ -159,7 +159,7 @@ int usage() {
                  "usage: psb_node master [--threads N] [--port P] [--state-file FILE] [--host ADDR]\n"
                  "       psb_node ctl --master HOST:PORT VERB ...   (the controller; `psb_node ctl` lists the verbs)\n"
                  "       psb_node images DIR [--master HOST:PORT] [--remove-unused [--dead-nodes-too]]\n"
-                 "       psb_node pserver --master HOST:PORT [--restore] [--restore-wait S] [--image-dir DIR] [--image-interval-ms N] [--report-interval S]\n"
+                 "       psb_node pserver --master HOST:PORT [--restore] [--restore-wait S] [--restore-pauses-writes] [--image-dir DIR] [--image-interval-ms N] [--report-interval S]\n"
                  "                        [--load-threads N] [--c2s-threads N] [--s2s-threads N] [--sync-master HOST:PORT] [--hadoop-bin PATH]\n"
                  "                        [--metrics-port P] [--log-level debug|info|warning|error|off] [--host ADDR]\n");
     return 2;
@@ -191,6 +191,7 @@ int main(int argc, char** argv) {
         else if (a == "--host" && i + 1 < argc) ::setenv("PSB_HOST", argv[++i], 1);   // before any server is created
         else if (a == "--port") { if (!next(&master_port)) return usage(); }
         else if (a == "--restore") restore = true;
+        else if (a == "--restore-pauses-writes") cfg.restore_pauses_writes = true;
         else if (a == "--image-dir" && i + 1 < argc) cfg.local_image_dir = argv[++i];
         else if (a == "--hadoop-bin" && i + 1 < argc) cfg.hadoop_bin = argv[++i];
         else if (a == "--log-level" && i + 1 < argc) set_log_level(log_detail::parse(argv[++i], LogLevel::WARNING));

@@ -168,6 +168,7 @@ void bind_service(py::module_& m) {
         .def_readwrite("load_thread_num", &ServerConfig::load_thread_num)
         .def_readwrite("load_block_size", &ServerConfig::load_block_size)
         .def_readwrite("restore_batch_size", &ServerConfig::restore_batch_size)
+        .def_readwrite("restore_pauses_writes", &ServerConfig::restore_pauses_writes)
         .def_readwrite("restore_thread_num", &ServerConfig::restore_thread_num)
         .def_readwrite("s2s_timeout_ms", &ServerConfig::s2s_timeout_ms)
         .def_readwrite("local_image_dir", &ServerConfig::local_image_dir)

@@ -35,6 +35,12 @@ struct ServerConfig {
     int report_interval_s = -1;
     int restore_wait_timeout_s = -1;
     int restore_batch_size = 1000;
+    // A server in restore mode pauses the writes of a table while it copies the table's shards from the live
+    // replicas (the table's status is LOADING for that time: pushes and inserting pulls answer OUT_OF_MEMORY, their
+    // clients wait and send them again afterwards; reads go on). The restored replica is then exactly equal to its
+    // source. Off: writes go on, and a push that meets a row between its export and its arrival can be missing on
+    // the restored replica (the reference sends no writes at all to a node that is LOADING).
+    bool restore_pauses_writes = false;
     int restore_thread_num = 4;
     int s2s_timeout_ms = 60000;
     // Directory of this host's persistent table images (empty: none). A server in restore mode that finds the image
@@ -264,6 +270,8 @@ public:
                 std::unique_lock<std::shared_mutex> g(e->mu);
                 PSB_RETURN_IF_ERROR(ensure_storage(*e));
             }
+            bool paused = false;
+            if (cfg_.restore_pauses_writes) PSB_RETURN_IF_ERROR(pause_writes_for_restore(*e, true, &paused));
             // a live replica has the current data; without one, this host's own image of the dead node (if its
             // layout identity matches); then the table's dump
             Status rs = restore_storage_coordinated(*e);
@@ -278,7 +286,10 @@ public:
                     rs = fs.ok() ? fs : Status(fs.code(), fs.msg() + " (replica: " + rs.msg() + "; local image: " + li.msg() + ")");
                 }
             }
-            if (!rs.ok()) PSB_LOG(ERROR) << "storage " << sid << ": restore failed: " << rs.to_string();
+            if (!rs.ok()) {
+                PSB_LOG(ERROR) << "storage " << sid << ": restore failed: " << rs.to_string();
+                if (paused) pause_writes_for_restore(*e, false, nullptr);   // the table must not stay closed to writes
+            }
             PSB_RETURN_IF_ERROR(rs);
             PSB_LOG(INFO) << "storage " << sid << ": restored from " << source << ", " << e->storage->size() << " items on node " << node_id_;
             {
@@ -293,6 +304,7 @@ public:
                 std::unique_lock<std::shared_mutex> g(e->mu);
                 e->td.from_json_str(json);
                 e->td.set_node_status_to_running(node_id_);
+                if (paused && e->td.status == StorageStatus::LOADING) e->td.status = StorageStatus::NORMAL;   // writes resume
                 e->rt.build(e->td, node_id_);
                 st = master_.set_context(ctx_key(sid), e->td.to_json_str());
             }
@@ -558,6 +570,7 @@ private:
     Status check_write_ctx_version(TableEntry& e, const PSMessageMeta& meta) {
         PSB_RETURN_IF_ERROR(check_ctx_version(e, meta));
         if (e.td.status == StorageStatus::RESHARD) return Status::OOM("write when update context");
+        if (e.td.status == StorageStatus::LOADING) return Status::OOM("write while a replica of the table is being restored");
         return Status::Ok();
     }
     Status check_table_version(TableEntry& e, const PSMessageMeta& meta) {
@@ -1059,6 +1072,41 @@ private:
         *out << e.sid << shard << (int32_t)(finished ? 1 : 0) << iterator_id << next << (uint64_t)keys.size() << (int32_t)e.storage->stride();
         out->write_raw(keys.data(), keys.size() * 8);
         out->write_raw(rows.data(), rows.size() * 4);
+        return Status::Ok();
+    }
+
+    // Close (or open again) a table to writes around a restore: the status LOADING is published under the global lock
+    // and handed to every reachable server before the first row is copied, so no push is applied anywhere between a
+    // row's export and the end of the restore. A table in the middle of a reshard is left alone (*paused stays false).
+    Status pause_writes_for_restore(TableEntry& e, bool on, bool* paused) {
+        if (paused) *paused = false;
+        PSB_RETURN_IF_ERROR(master_.acquire_lock(PSERVER_LOCK_NAME));
+        std::string json;
+        Status st = master_.get_context(ctx_key(e.sid), &json);
+        bool changed = false;
+        if (st.ok()) {
+            std::unique_lock<std::shared_mutex> g(e.mu);
+            e.td.from_json_str(json);
+            if (on && e.td.status == StorageStatus::NORMAL) {
+                e.td.status = StorageStatus::LOADING;
+                changed = true;
+            } else if (!on && e.td.status == StorageStatus::LOADING) {
+                e.td.status = StorageStatus::NORMAL;
+                changed = true;
+            }
+            if (changed) {
+                ++e.td.version;
+                e.rt.build(e.td, node_id_);
+                st = master_.set_context(ctx_key(e.sid), e.td.to_json_str());
+            }
+        }
+        master_.release_lock(PSERVER_LOCK_NAME);
+        PSB_RETURN_IF_ERROR(st);
+        if (changed) {
+            broadcast_ctx_update(e);   // waits for the peers' answers: they hold the new status when it returns
+            if (paused) *paused = on;
+            PSB_LOG(INFO) << "storage " << e.sid << ": writes " << (on ? "paused for the restore" : "resumed");
+        }
         return Status::Ok();
     }
 

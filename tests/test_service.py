@@ -486,6 +486,68 @@ def test_bad_placements_and_arguments_are_refused_before_they_cost_data(cluster3
     assert st.ok() and n == 300
 
 
+def test_a_restore_that_pauses_writes_leaves_the_new_replica_exact():
+    """`ServerConfig.restore_pauses_writes`: while a replacement copies a table from the live replica the table is
+    closed to writes (pushes wait in their handlers and go on afterwards), so every push is on the restored replica
+    exactly once - also pushes to rows that were on their way."""
+    cl = Cluster(2)
+    try:
+        ids = cl.ids()
+        sid, h = make_table(cl, {ids[0]: [0, 1], ids[1]: [0, 1]})             # two replicas of everything
+        keys = np.arange(20_000, dtype=np.int64)
+        ones = np.ones((len(keys), DIM), np.float32)
+        assert S.PushHandler(cl.client, sid, h["push"]).async_push(keys, ones).ok()
+        stop, applied, bad = threading.Event(), [1], []
+
+        def trainer():
+            c = S.Client(cl.master.address())
+            assert c.initialize_storage(sid).ok()
+            push = S.PushHandler(c, sid, h["push"])
+            while not stop.is_set():
+                st = push.async_push(keys, ones, 60000)
+                if not st.ok():
+                    bad.append(str(st))
+                    return
+                applied[0] += 1
+
+        t = threading.Thread(target=trainer)
+        t.start()
+        try:
+            time.sleep(0.2)
+            cl.servers[1].stop()                                               # the trainer's handler finds out and goes on
+            deadline = time.time() + 30
+            td = S.TableDescriptor()
+            while time.time() < deadline:
+                td.from_json_str(S.MasterClient(cl.master.address()).get_context(f"storage/{sid}")[1])
+                if td.node_status()[ids[1]] == 1:
+                    break
+                time.sleep(0.05)
+            assert td.node_status()[ids[1]] == 1
+            cfg = S.ServerConfig()
+            cfg.restore_pauses_writes = True
+            cfg.restore_batch_size = 512                                       # many batches: the copy takes a while
+            fresh = S.Server(cl.master.address(), cfg)
+            cl.servers.append(fresh)
+            before = applied[0]
+            st, n = fresh.restore_storages()
+            assert st.ok() and n == 1, st
+            td.from_json_str(S.MasterClient(cl.master.address()).get_context(f"storage/{sid}")[1])
+            assert td.status() == 0 and td.node_status()[fresh.node_id()] == 0     # NORMAL again, the new node RUNNING
+            deadline = time.time() + 30
+            while time.time() < deadline and applied[0] < before + 3:          # the trainer goes on after the pause
+                time.sleep(0.05)
+            assert applied[0] >= before + 3, (applied, bad)
+        finally:
+            stop.set()
+            t.join(90)
+        assert not bad and not t.is_alive(), bad
+        cl.servers[0].stop()                                                   # only the restored replica answers now
+        st, rows = S.PullHandler(cl.client, sid, h["pull_ro"]).pull(keys, 20000, True)
+        assert st.ok() and np.all(rows == float(applied[0])), (float(rows.min()), float(rows.max()), applied[0])
+    finally:
+        cl.close()
+
+
 def test_restore_from_dump_when_no_replica(tmp_path):
     cl = Cluster(2)
     try:
