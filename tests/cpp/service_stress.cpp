@@ -181,10 +181,30 @@ int main() {
                     ++reads;
                 }
             });
+        // one writer as well: it adds zeros (the values that the readers check stay), so that the restore below, which
+        // closes the table to writes while it copies, has pushes to hold back and to let through again
+        std::atomic<int> writes{0};
+        readers.emplace_back([&] {
+            PushHandler h(&client, sid2, hq);
+            std::vector<int64_t> keys(kBatch);
+            std::vector<float> zeros((size_t)kBatch * kDim, 0.0f);
+            uint64_t x = 424243;
+            while (!stop_readers.load()) {
+                for (auto& k : keys) {
+                    x ^= x << 13; x ^= x >> 7; x ^= x << 17;
+                    k = (int64_t)(x % kKeys);
+                }
+                Status st = h.async_push(keys.data(), zeros.data(), keys.size(), 30000);
+                if (!st.ok()) { std::fprintf(stderr, "phase 2 write: %s\n", st.msg().c_str()); ++bad_reads; continue; }
+                ++writes;
+            }
+        });
         std::this_thread::sleep_for(std::chrono::milliseconds(30));
         servers[1]->stop();                                        // host-side fault: this node is gone
         std::this_thread::sleep_for(std::chrono::milliseconds(200));
-        servers.emplace_back(new Server(master.address()));        // a fresh server replaces it from the live replicas
+        ServerConfig restoring;
+        restoring.restore_pauses_writes = true;
+        servers.emplace_back(new Server(master.address(), restoring));   // a fresh server replaces it from the live replicas
         int restored = 0;
         Status st = servers.back()->restore_storages(&restored);
         if (!st.ok() || restored < 1) { std::fprintf(stderr, "restore: %s (%d tables)\n", st.msg().c_str(), restored); ++wrong2; }
@@ -193,7 +213,7 @@ int main() {
         stop_readers = true;
         for (auto& r : readers) r.join();
         wrong2 += bad_reads.load();
-        std::printf("phase 2: %d reads, %d bad, %d tables restored\n", reads.load(), bad_reads.load(), restored);
+        std::printf("phase 2: %d reads, %d writes, %d bad, %d tables restored\n", reads.load(), writes.load(), bad_reads.load(), restored);
     }
     wrong += wrong2;
 
