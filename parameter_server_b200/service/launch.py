@@ -28,6 +28,8 @@ def main(argv=None) -> int:
     p = sub.add_parser("pserver")
     p.add_argument("--master", required=True)
     p.add_argument("--restore", action="store_true")
+    p.add_argument("--restore-pauses-writes", action="store_true",
+                   help="close a table to writes while it is copied from the live replicas (the new replica is exact)")
     p.add_argument("--image-dir", default="", help="persistent table images: written on a planned shutdown, opened in restore mode")
     p.add_argument("--c2s-threads", type=int, default=4)
     p.add_argument("--s2s-threads", type=int, default=4)
@@ -53,6 +55,7 @@ def main(argv=None) -> int:
     cfg.c2s_thread_num, cfg.s2s_thread_num = a.c2s_threads, a.s2s_threads
     cfg.local_image_dir = a.image_dir
     cfg.restore_wait_timeout_s, cfg.report_interval_s, cfg.hadoop_bin = a.restore_wait, a.report_interval, a.hadoop_bin
+    cfg.restore_pauses_writes = a.restore_pauses_writes
     server = Server(a.master, cfg)
     print(f"pserver node_id={server.node_id()} c2s={server.c2s_address()} s2s={server.s2s_address()}", flush=True)
     httpd = None
