@@ -48,7 +48,7 @@ class Farm:
     def start(self, restore=False, sources=("replica", "image", "dump")):
         args = ["pserver", "--master", self.addr, "--image-dir", self.image_dir]
         if restore:
-            args += ["--restore", "--restore-wait", "10"]
+            args += ["--restore", "--restore-wait", "10", "--restore-pauses-writes"]   # the table is closed to writes while it is copied
         p = _spawn(*args)
         self.all.append(p)
         node = int(_line(p).split("node_id=")[1].split()[0])
