@@ -304,7 +304,8 @@ public:
                 std::unique_lock<std::shared_mutex> g(e->mu);
                 e->td.from_json_str(json);
                 e->td.set_node_status_to_running(node_id_);
-                if (paused && e->td.status == StorageStatus::LOADING) e->td.status = StorageStatus::NORMAL;   // writes resume
+                // writes resume - unless another server is still copying this table: the last one to finish opens it
+                if (paused && e->td.status == StorageStatus::LOADING && !others_loading(e->td)) e->td.status = StorageStatus::NORMAL;
                 e->rt.build(e->td, node_id_);
                 st = master_.set_context(ctx_key(sid), e->td.to_json_str());
             }
@@ -1078,6 +1079,15 @@ private:
     // Close (or open again) a table to writes around a restore: the status LOADING is published under the global lock
     // and handed to every reachable server before the first row is copied, so no push is applied anywhere between a
     // row's export and the end of the restore. A table in the middle of a reshard is left alone (*paused stays false).
+    // Whether another server is still copying this table. A LOADING entry whose server is no longer registered (its
+    // restore failed and the process went away) does not count: it must not keep the table closed.
+    bool others_loading(const TableDescriptor& td) {
+        std::map<int32_t, std::string> live;
+        if (!master_.get_nodes(PSERVER_S2S_RPC_NAME, &live).ok()) return false;
+        for (auto& n : td.nodes)
+            if (n.status == NodeStatus::LOADING && n.node_id != node_id_ && live.count(n.node_id)) return true;
+        return false;
+    }
     Status pause_writes_for_restore(TableEntry& e, bool on, bool* paused) {
         if (paused) *paused = false;
         PSB_RETURN_IF_ERROR(master_.acquire_lock(PSERVER_LOCK_NAME));
@@ -1090,7 +1100,9 @@ private:
             if (on && e.td.status == StorageStatus::NORMAL) {
                 e.td.status = StorageStatus::LOADING;
                 changed = true;
-            } else if (!on && e.td.status == StorageStatus::LOADING) {
+            } else if (on && e.td.status == StorageStatus::LOADING) {
+                if (paused) *paused = true;   // another restoring server closed the table already: the last one opens it
+            } else if (!on && e.td.status == StorageStatus::LOADING && !others_loading(e.td)) {
                 e.td.status = StorageStatus::NORMAL;
                 changed = true;
             }

@@ -486,14 +486,16 @@ def test_bad_placements_and_arguments_are_refused_before_they_cost_data(cluster3
     assert st.ok() and n == 300
 
 
-def test_a_restore_that_pauses_writes_leaves_the_new_replica_exact():
-    """`ServerConfig.restore_pauses_writes`: while a replacement copies a table from the live replica the table is
-    closed to writes (pushes wait in their handlers and go on afterwards), so every push is on the restored replica
-    exactly once - also pushes to rows that were on their way."""
-    cl = Cluster(2)
+@pytest.mark.parametrize("n_lost", [1, 2])
+def test_a_restore_that_pauses_writes_leaves_the_new_replica_exact(n_lost):
+    """`ServerConfig.restore_pauses_writes`: while replacements copy a table from the live replica the table is closed
+    to writes (pushes wait in their handlers and go on afterwards), so every push is on the restored replicas exactly
+    once - also pushes to rows that were on their way. With two replacements at once the last one to finish opens
+    the table again."""
+    cl = Cluster(1 + n_lost)
     try:
         ids = cl.ids()
-        sid, h = make_table(cl, {ids[0]: [0, 1], ids[1]: [0, 1]})             # two replicas of everything
+        sid, h = make_table(cl, {n: [0, 1] for n in ids})                     # every node holds everything
         keys = np.arange(20_000, dtype=np.int64)
         ones = np.ones((len(keys), DIM), np.float32)
         assert S.PushHandler(cl.client, sid, h["push"]).async_push(keys, ones).ok()
@@ -514,25 +516,29 @@ def test_a_restore_that_pauses_writes_leaves_the_new_replica_exact():
         t.start()
         try:
             time.sleep(0.2)
-            cl.servers[1].stop()                                               # the trainer's handler finds out and goes on
+            for s in cl.servers[1:]:
+                s.stop()                                                       # the trainer's handler finds out and goes on
             deadline = time.time() + 30
             td = S.TableDescriptor()
             while time.time() < deadline:
                 td.from_json_str(S.MasterClient(cl.master.address()).get_context(f"storage/{sid}")[1])
-                if td.node_status()[ids[1]] == 1:
+                if all(td.node_status()[n] == 1 for n in ids[1:]):
                     break
                 time.sleep(0.05)
-            assert td.node_status()[ids[1]] == 1
+            assert all(td.node_status()[n] == 1 for n in ids[1:])
             cfg = S.ServerConfig()
             cfg.restore_pauses_writes = True
             cfg.restore_batch_size = 512                                       # many batches: the copy takes a while
-            fresh = S.Server(cl.master.address(), cfg)
-            cl.servers.append(fresh)
+            fresh = [S.Server(cl.master.address(), cfg) for _ in range(n_lost)]
+            cl.servers += fresh
             before = applied[0]
-            st, n = fresh.restore_storages()
-            assert st.ok() and n == 1, st
+            results = [None] * n_lost
+            workers = [threading.Thread(target=lambda i=i: results.__setitem__(i, fresh[i].restore_storages())) for i in range(n_lost)]
+            [w.start() for w in workers]
+            [w.join(120) for w in workers]
+            assert all(r is not None and r[0].ok() and r[1] == 1 for r in results), results
             td.from_json_str(S.MasterClient(cl.master.address()).get_context(f"storage/{sid}")[1])
-            assert td.status() == 0 and td.node_status()[fresh.node_id()] == 0     # NORMAL again, the new node RUNNING
+            assert td.status() == 0 and all(td.node_status()[f.node_id()] == 0 for f in fresh)   # NORMAL again, the new nodes RUNNING
             deadline = time.time() + 30
             while time.time() < deadline and applied[0] < before + 3:          # the trainer goes on after the pause
                 time.sleep(0.05)
@@ -541,9 +547,11 @@ def test_a_restore_that_pauses_writes_leaves_the_new_replica_exact():
             stop.set()
             t.join(90)
         assert not bad and not t.is_alive(), bad
-        cl.servers[0].stop()                                                   # only the restored replica answers now
-        st, rows = S.PullHandler(cl.client, sid, h["pull_ro"]).pull(keys, 20000, True)
-        assert st.ok() and np.all(rows == float(applied[0])), (float(rows.min()), float(rows.max()), applied[0])
+        cl.servers[0].stop()                                                   # only the restored replicas answer now
+        pull = S.PullHandler(cl.client, sid, h["pull_ro"])
+        for _ in range(1 if n_lost == 1 else 8):                               # reads pick a replica at random
+            st, rows = pull.pull(keys, 20000, True)
+            assert st.ok() and np.all(rows == float(applied[0])), (float(rows.min()), float(rows.max()), applied[0])
     finally:
         cl.close()
 
