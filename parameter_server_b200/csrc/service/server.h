@@ -1093,7 +1093,7 @@ private:
         PSB_RETURN_IF_ERROR(master_.acquire_lock(PSERVER_LOCK_NAME));
         std::string json;
         Status st = master_.get_context(ctx_key(e.sid), &json);
-        bool changed = false;
+        bool changed = false, notify = false;
         if (st.ok()) {
             std::unique_lock<std::shared_mutex> g(e.mu);
             e.td.from_json_str(json);
@@ -1101,7 +1101,10 @@ private:
                 e.td.status = StorageStatus::LOADING;
                 changed = true;
             } else if (on && e.td.status == StorageStatus::LOADING) {
-                if (paused) *paused = true;   // another restoring server closed the table already: the last one opens it
+                // another restoring server closed the table already (the last one to finish opens it). Its notice to
+                // the other servers may still be on its way: this server sends its own before it copies anything.
+                if (paused) *paused = true;
+                notify = true;
             } else if (!on && e.td.status == StorageStatus::LOADING && !others_loading(e.td)) {
                 e.td.status = StorageStatus::NORMAL;
                 changed = true;
@@ -1114,8 +1117,8 @@ private:
         }
         master_.release_lock(PSERVER_LOCK_NAME);
         PSB_RETURN_IF_ERROR(st);
+        if (changed || notify) broadcast_ctx_update(e);   // waits for the peers' answers: they hold the status when it returns
         if (changed) {
-            broadcast_ctx_update(e);   // waits for the peers' answers: they hold the new status when it returns
             if (paused) *paused = on;
             PSB_LOG(INFO) << "storage " << e.sid << ": writes " << (on ? "paused for the restore" : "resumed");
         }
