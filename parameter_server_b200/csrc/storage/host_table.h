@@ -243,6 +243,14 @@ public:
             float* w = sh->rows.data() + (size_t)row * stride_;
             if (emb_only) std::copy_n(rows + i * cfg_.dim, cfg_.dim, w);
             else std::copy_n(rows + i * stride_, stride_, w);
+            if (!emb_only && cfg_.sync_delta && !sh->touched_flag[row]) {
+                // a full row may carry a pending sync delta (a restore from a replica that buffered sync pushes): it
+                // must be folded by the next store here as it will be there
+                const float* delta = w + (size_t)(n_slots_ + 1) * cfg_.dim;
+                bool pending = false;
+                for (uint32_t d = 0; d < cfg_.dim && !pending; ++d) pending = delta[d] != 0.f;
+                if (pending) { sh->touched_flag[row] = 1; sh->touched.push_back(row); }
+            }
             if (track_dirty_) sh->dirty[row] = 1;
         }
         return Status::Ok();

@@ -556,6 +556,41 @@ def test_a_restore_that_pauses_writes_leaves_the_new_replica_exact(n_lost):
         cl.close()
 
 
+def test_buffered_sync_pushes_survive_a_reshard_and_a_replica_restore():
+    """Sync pushes wait in the rows' delta section until `store`. Rows that move in between - to the new owners of a
+    reshard, to a replacement replica - take their pending delta along, and the store folds it there as well."""
+    cl = Cluster(2)
+    try:
+        ids = cl.ids()
+        sid, h = make_table(cl, {ids[0]: [0, 1], ids[1]: [0, 1]}, cfg=op_cfg(sync=True))
+        keys = np.arange(600, dtype=np.int64)
+        push, pull = S.PushHandler(cl.client, sid, h["push"]), S.PullHandler(cl.client, sid, h["pull_ro"])
+        assert push.async_push(keys, np.ones((600, DIM), np.float32)).ok()
+        assert push.sync_push(keys, 2 * np.ones((600, DIM), np.float32)).ok()          # buffered on both replicas
+        # a reshard to three shards moves most rows
+        assert S.UpdateContextHandler(cl.client, sid, h["update_ctx"]).update_context(
+            S.nodes_json({ids[0]: [0, 1, 2], ids[1]: [0, 1, 2]})).ok()
+        assert np.all(pull.pull(keys)[1] == 1.0)                                       # still buffered
+        # one replica is lost and replaced
+        cl.servers[1].stop()
+        td = S.TableDescriptor()
+        for _ in range(100):
+            assert pull.pull(keys, 20000, True)[0].ok()
+            td.from_json_str(S.MasterClient(cl.master.address()).get_context(f"storage/{sid}")[1])
+            if td.node_status()[ids[1]] == 1:
+                break
+        fresh = S.Server(cl.master.address())
+        cl.servers.append(fresh)
+        st, n = fresh.restore_storages()
+        assert st.ok() and n == 1, st
+        assert push.store(20000).ok()
+        for _ in range(10):                                                            # either replica
+            st, rows = pull.pull(keys, 20000, True)
+            assert st.ok() and np.all(rows == 3.0), np.unique(rows)
+    finally:
+        cl.close()
+
+
 def test_restore_from_dump_when_no_replica(tmp_path):
     cl = Cluster(2)
     try:
