@@ -51,6 +51,7 @@ int ctl_usage() {
     std::fprintf(stderr,
                  "usage: psb_node ctl --master HOST:PORT VERB ...\n"
                  "  nodes | node ID | table SID | clean | shutdown NODE | delete SID | balance SID\n"
+                 "  purge SID   (abort a reshard that its client left unfinished: writes resume)\n"
                  "  shards SID N | replicas SID N | expand SID SHARDS_PER_NODE NODE [NODE ...]\n"
                  "  create NAME SHARDS REPLICAS OP_CONFIG_JSON [TABLE_URI]   (prints storage_id=N)\n");
     return 2;
@@ -88,6 +89,7 @@ int ctl_main(int argc, char** argv) {
         else if (verb == "shutdown" && a.size() == 2) st = ctl.shutdown_node(num(1));
         else if (verb == "delete" && a.size() == 2) st = ctl.delete_table(num(1));
         else if (verb == "balance" && a.size() == 2) st = ctl.balance_table(num(1));
+        else if (verb == "purge" && a.size() == 2) st = ctl.purge_table(num(1));
         else if (verb == "shards" && a.size() == 3) st = ctl.update_table_shard(num(1), num(2));
         else if (verb == "replicas" && a.size() == 3) st = ctl.update_table_replica(num(1), num(2));
         else if (verb == "expand" && a.size() >= 4) {

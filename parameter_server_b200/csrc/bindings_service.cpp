@@ -562,6 +562,7 @@ void bind_service(py::module_& m) {
            py::arg("replica_num"), py::arg("ops"), py::arg("table_uri") = "", nogil())
         .def("delete_table", &Controller::delete_table, nogil())
         .def("balance_table", &Controller::balance_table, nogil())
+        .def("purge_table", &Controller::purge_table, nogil())
         .def("update_table_shard", &Controller::update_table_shard, nogil())
         .def("update_table_replica", &Controller::update_table_replica, nogil())
         .def("update_table", &Controller::update_table, nogil())

@@ -121,6 +121,17 @@ public:
         UpdateContextHandler h(&client_, sid, hid);
         return h.update_context(nodes_json);
     }
+    // The abort path of update_table for an operator: a table that a dead client left in the middle of a reshard (status
+    // RESHARD: writes are refused) - or closed by a restore that never finished - goes back to its last published
+    // placement, the half-built shards are dropped, writes resume (UpdateContextHandler::purge,
+    // pico-ps/handler/UpdateContextHandler.cpp:279-298).
+    Status purge_table(int32_t sid) {
+        PSB_RETURN_IF_ERROR(client_.initialize_storage(sid));
+        int32_t hid = -1;
+        PSB_RETURN_IF_ERROR(client_.handler_by_key(sid, "update_ctx", &hid));
+        UpdateContextHandler h(&client_, sid, hid);
+        return h.purge();
+    }
     // Scale out: every new node gets `local_shard_num` NEW shards appended (single-replica tables only).
     Status expand_storage_nodes(int32_t sid, const std::vector<int>& new_nodes, int local_shard_num) {
         PSB_RETURN_IF_ERROR(client_.initialize_storage(sid));

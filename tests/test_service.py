@@ -591,6 +591,36 @@ def test_buffered_sync_pushes_survive_a_reshard_and_a_replica_restore():
         cl.close()
 
 
+def test_an_operator_can_abort_a_reshard_that_its_client_left_unfinished(cluster3):
+    """A client that dies after publishing the target placement leaves the table in RESHARD: reads go on, writes
+    wait. `Controller.purge_table` (`psb_node ctl purge SID`) drops the unfinished update; writes resume."""
+    cl = cluster3
+    ids = cl.ids()
+    sid, h = make_table(cl, {ids[0]: [0], ids[1]: [1]})
+    keys = np.arange(400, dtype=np.int64)
+    ones = np.ones((400, DIM), np.float32)
+    push, pull = S.PushHandler(cl.client, sid, h["push"]), S.PullHandler(cl.client, sid, h["pull_ro"])
+    assert push.async_push(keys, ones).ok()
+    # what the first step of update_context publishes, and then nothing more (the client is gone)
+    m = S.MasterClient(cl.master.address())
+    td = S.TableDescriptor()
+    assert td.from_json_str(m.get_context(f"storage/{sid}")[1])
+    assert td.create_update_info(S.nodes_json({ids[0]: [0], ids[1]: [1], ids[2]: [2]})).ok()
+    assert m.set_context(f"storage/{sid}", td.to_json_str()).ok() and td.status() == 1
+    assert cl.client.pull_context(sid).ok() and cl.client.notify_ctx_update(sid).ok()   # ... and hands to the servers
+    st = push.async_push(keys, ones, 1500)
+    assert st.code() in (StatusCode.OUT_OF_MEMORY, StatusCode.TIMEOUT), st           # writes wait for the reshard to end
+    st, rows = pull.pull(keys, 20000, True)
+    assert st.ok() and np.all(rows == 1.0)                                          # reads go on
+    ctl = S.Controller(cl.master.address())
+    assert ctl.purge_table(sid).ok()
+    assert td.from_json_str(m.get_context(f"storage/{sid}")[1]) and td.status() == 0
+    assert push.async_push(keys, ones, 20000).ok()
+    st, rows = pull.pull(keys, 20000, True)
+    assert st.ok() and np.all(rows == 2.0)
+    assert ctl.purge_table(4242).code() == StatusCode.INVALID_ID
+
+
 def test_restore_from_dump_when_no_replica(tmp_path):
     cl = Cluster(2)
     try:
