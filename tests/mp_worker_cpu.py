@@ -130,6 +130,58 @@ def scans(rank, world):
     dist.barrier()
 
 
+def predictor_sync(rank, world):
+    """Every rank ships the rows of its own shards to one predictor table of the service layer."""
+    import json
+    from parameter_server_b200 import service as S
+    from parameter_server_b200.parallel import PredictorSync
+
+    dim = 4
+    cluster = None
+    info = [None]
+    if rank == 0:                                     # the serving side lives in rank 0's process, reachable over TCP
+        master = S.Master()
+        servers = [S.Server(master.address()) for _ in range(2)]
+        admin = S.Client(master.address())
+        ids = [s.node_id() for s in servers]
+        cfg = dict(dim=dim, optimizer="set", init_range=0.0)
+        st, sid = admin.create_storage(S.LIB, "SparseTableStorageOperator", S.storage_config({ids[0]: [0, 1], ids[1]: [2]}, cfg))
+        assert st.ok(), st
+        _, h_pull = admin.register_handler("pull_ro", S.LIB, "SparseTablePullOperator", json.dumps({"read_only": True}), sid)
+        _, h_sync = admin.register_handler("sync", S.LIB, "KVSyncOperator", json.dumps({"block_size": 50}), sid)
+        cluster = (master, servers, admin)
+        info = [(master.address(), sid, h_pull, h_sync)]
+    dist.broadcast_object_list(info, src=0)
+    addr, sid, h_pull, h_sync = info[0]
+    client = S.Client(addr)
+    assert client.initialize_storage(sid).ok()
+    t = SparseTable(dim, "sgd", dict(lr=1.0), n_shards=2 * world + 1, device="cpu", init_range=0.0)
+    keys = torch.arange(1, 901, dtype=torch.int64)
+    mine = keys[rank::world]
+    t.pull(mine)
+    t.push(-(mine % 9 + 1).float()[:, None] * torch.ones(1, dim))
+    sync = PredictorSync(t, S.SyncHandler(client, sid, h_sync), embedding_only=True)
+    sent = gather(sync.sync())
+    assert sum(sent) == 900 and all(n > 0 for n in sent), sent              # every rank sent its own rows only
+    want = t.pull(keys, insert=False)
+    dist.barrier()
+    st, rows = S.PullHandler(client, sid, h_pull).pull(keys.numpy())
+    assert st.ok() and np.array_equal(rows, want.numpy())
+    some = keys[:30]
+    t.pull(some[rank::world])
+    t.push(torch.ones(some[rank::world].numel(), dim))
+    assert sum(gather(sync.sync())) == 30
+    want = t.pull(keys, insert=False)
+    dist.barrier()
+    st, rows = S.PullHandler(client, sid, h_pull).pull(keys.numpy())
+    assert st.ok() and np.array_equal(rows, want.numpy())
+    dist.barrier()
+    if cluster is not None:
+        for s_ in cluster[1]:
+            s_.stop()
+        cluster[0].stop()
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dist.init_process_group("gloo")
@@ -159,6 +211,7 @@ def main():
             assert owners <= {rank}, owners
     elastic(rank, world)
     scans(rank, world)
+    predictor_sync(rank, world)
     # dense table: all-reduce + optimizer on every rank, identical parameters everywhere
     d = DenseTable({"w": (64, 8), "b": (64,)}, "adamw", dict(lr=1e-2, weight_decay=0.01), device="cpu")
     d.load({"w": torch.ones(64, 8), "b": torch.zeros(64)})
