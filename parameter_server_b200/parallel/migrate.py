@@ -229,7 +229,11 @@ def reshard(table: SparseTable, new_owner: Sequence[int], batch: int = 1 << 18, 
     (optional, collective) runs after every round of the exchange: reads stay served during a migration by
     issuing read-only pulls (``insert=False``) there, since rows are purged from their old owners and the owner
     map is swapped only at the very end, every key is still found where the current map says (the reference keeps
-    serving reads during a reshard the same way, pico-ps/handler/UpdateContextHandler.cpp:62-153)."""
+    serving reads during a reshard the same way, pico-ps/handler/UpdateContextHandler.cpp:62-153).
+
+    A table created with ``sync=True``: call ``store()`` before moving rows of a CUDA table. A row travels with its
+    pending delta, but the GPU table does not put it on the list that the next ``store`` walks at its new place (the
+    host table does)."""
     import time
     if not table.is_cuda:
         return _host.reshard(table, new_owner, stats, between_rounds)
