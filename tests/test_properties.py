@@ -286,3 +286,49 @@ def test_index_ratios_never_lose_a_key_and_the_byte_count_follows_the_buckets(st
             k, _, cursor, finished = t.export_shard(0, cursor, 37, False)
             seen += k.tolist()
         assert sorted(seen) == sorted(live)
+
+
+_cfg_values = st.one_of(st.none(), st.booleans(), st.integers(-(2 ** 40), 2 ** 40), st.floats(allow_nan=False, allow_infinity=False, width=32),
+                        st.text(max_size=12), st.lists(st.integers(-5, 5), max_size=3),
+                        st.dictionaries(st.sampled_from(["expected_max_items", "grow_ratio", "shrink_ratio", "storage_id", "x"]),
+                                        st.one_of(st.integers(-10, 10 ** 7), st.floats(-5, 5), st.text(max_size=4)), max_size=3))
+_cfg_keys = ["dim", "optimizer", "lr", "eps", "init_range", "init_accumulator", "sync", "seed", "partition", "backend", "memory_limit",
+             "expected_max_items", "grow_ratio", "shrink_ratio", "pool_hash_map", "google_dense_hash_map", "pmem_create_storage",
+             "retain_local_image", "alpha", "beta", "l1", "l2", "beta1", "beta2", "weight_decay", "capacity", "max_rows"]
+
+
+@pytest.fixture(scope="module")
+def one_server():
+    from parameter_server_b200 import service as S
+    master = S.Master()
+    server = S.Server(master.address())
+    client = S.Client(master.address())
+    yield S, server, client
+    server.stop()
+    master.stop()
+
+
+@settings(max_examples=120, deadline=None, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@given(cfg=st.dictionaries(st.sampled_from(_cfg_keys), _cfg_values, max_size=8))
+def test_no_storage_config_takes_a_server_down(one_server, cfg):
+    """Whatever a client writes into a storage config - wrong types, absurd numbers, nested junk under the
+    reference's section names - the answer is a status: the table works, or it is refused; the server lives."""
+    import json
+    S, server, client = one_server
+    cfg = dict(cfg)
+    if cfg.get("backend") == "gpu":
+        cfg.pop("backend")                                   # no device here: that refusal is tested elsewhere
+    st_, sid = client.create_storage(S.LIB, "SparseTableStorageOperator", S.storage_config({server.node_id(): [0, 1]}, cfg))
+    if st_.ok():
+        _, hq = client.register_handler("push", S.LIB, "SparseTablePushOperator", "{}", sid)
+        _, hp = client.register_handler("pull", S.LIB, "SparseTablePullOperator", "{}", sid)
+        push, pull = S.PushHandler(client, sid, hq), S.PullHandler(client, sid, hp)
+        dim = pull.dim()
+        assert 1 <= dim <= 65536
+        if dim <= 256:
+            keys = np.array([1, 2, 3, 2], dtype=np.int64)
+            s1 = push.async_push(keys, np.ones((4, dim), F), 5000)
+            s2, rows = pull.pull(keys, 5000, False)
+            assert rows.shape == (4, dim) and (not s1.ok() or s2.ok())          # a table that took the push serves the pull
+        assert client.delete_storage(sid).ok()
+    assert not server.exited()
