@@ -244,7 +244,7 @@ def test_base64_decoder_refuses_what_is_not_base64(text):
     assert not C.get_base64_config('{"k": 5}', "k")[0].ok() and not C.get_base64_config('{}', "k")[0].ok()
 
 
-@settings(max_examples=60, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@settings(max_examples=60, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow])
 @given(steps=st.lists(st.tuples(st.sampled_from(["insert", "erase", "clear"]), st.integers(0, 400), st.integers(1, 120)), min_size=1, max_size=30),
        grow=st.sampled_from([0.0, 0.25, 0.5, 0.8, 3.0]), shrink=st.sampled_from([0.0, 0.1, 0.3]), expected=st.sampled_from([0, 500]))
 def test_index_ratios_never_lose_a_key_and_the_byte_count_follows_the_buckets(steps, grow, shrink, expected):
@@ -308,7 +308,7 @@ def one_server():
     master.stop()
 
 
-@settings(max_examples=120, deadline=None, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@settings(max_examples=120, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
 @given(cfg=st.dictionaries(st.sampled_from(_cfg_keys), _cfg_values, max_size=8))
 def test_no_storage_config_takes_a_server_down(one_server, cfg):
     """Whatever a client writes into a storage config - wrong types, absurd numbers, nested junk under the
