@@ -332,3 +332,49 @@ def test_no_storage_config_takes_a_server_down(one_server, cfg):
             assert rows.shape == (4, dim)                    # a status either way (a memory_limit of 1 byte parks the push and refuses the pull)
         assert client.delete_storage(sid).ok()
     assert not server.exited()
+
+
+_op_classes = ["SparseTablePullOperator", "SparseTablePushOperator", "ForEachOperator", "ForEachWriteOperator", "EraseIfOperator",
+               "DumpOperator", "LoadOperator", "KVSyncOperator", "ShardUpdateContextOperator", "UDFOperator", "RestoreOperator"]
+_op_cfg = st.dictionaries(st.sampled_from(["read_only", "max_request_merge_num", "node_selection", "compress_algorithm", "block_size",
+                                           "block_serialized_size", "sync_table", "function", "optimizer", "lr", "section"]),
+                          st.one_of(st.none(), st.booleans(), st.integers(-(2 ** 33), 2 ** 33), st.text(max_size=8),
+                                    st.lists(st.dictionaries(st.sampled_from(["model_name", "table_name", "op_key", "x"]), st.text(max_size=6), max_size=3), max_size=2)),
+                          max_size=5)
+_carried = st.dictionaries(st.sampled_from(["type", "mod", "rem", "threshold", "section", "factor", "limit", "value", "junk"]),
+                           st.one_of(st.none(), st.booleans(), st.integers(-(2 ** 40), 2 ** 40), st.floats(allow_nan=False, allow_infinity=False),
+                                     st.sampled_from(["key_mod", "l2_below", "slot0_below", "all", "scale", "clip", "fill", "nonsense"]),
+                                     st.lists(st.integers(0, 3), max_size=2)), max_size=6)
+
+
+@settings(max_examples=100, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@given(op=st.sampled_from(_op_classes), cfg=_op_cfg, carried=_carried)
+def test_no_operator_config_or_carried_item_takes_a_server_down(one_server, op, cfg, carried):
+    """Handlers registered with junk configs are refused or work; scans with junk carried items answer with a status;
+    the table keeps its rows unless a well-formed scan changed them, and the server lives."""
+    import json
+    S, server, client = one_server
+    st_, sid = client.create_storage(S.LIB, "SparseTableStorageOperator",
+                                     S.storage_config({server.node_id(): [0, 1, 2]}, dict(dim=4, optimizer="adagrad", lr=0.1, init_range=0.0)))
+    assert st_.ok()
+    try:
+        _, hq = client.register_handler("push", S.LIB, "SparseTablePushOperator", "{}", sid)
+        keys = np.arange(50, dtype=np.int64)
+        assert S.PushHandler(client, sid, hq).async_push(keys, np.ones((50, 4), F), 5000).ok()
+        st_, hid = client.register_handler("probe", S.LIB, op, json.dumps(cfg), sid)
+        if st_.ok():
+            text = json.dumps(carried)
+            if op in ("ForEachOperator", "ForEachWriteOperator"):
+                S.ForEachHandler(client, sid, hid).for_each_raw(text)
+            elif op == "EraseIfOperator":
+                S.EraseIfHandler(client, sid, hid).erase_if(text)
+            elif op == "SparseTablePullOperator":
+                st2, rows = S.PullHandler(client, sid, hid).pull(keys, 5000, False)
+                assert rows.shape == (50, 4)
+            elif op == "SparseTablePushOperator":
+                S.PushHandler(client, sid, hid).async_push(keys, np.ones((50, 4), F), 5000)
+        info = client.query_storage_info(sid)
+        assert info[0].ok() and sum(i.item_number for i in info[1]) <= 50
+    finally:
+        assert client.delete_storage(sid).ok()
+    assert not server.exited()
