@@ -52,6 +52,7 @@ int ctl_usage() {
                  "usage: psb_node ctl --master HOST:PORT VERB ...\n"
                  "  nodes | node ID | table SID | clean | shutdown NODE | delete SID | balance SID\n"
                  "  purge SID   (abort a reshard that its client left unfinished: writes resume)\n"
+                 "  dump SID URI [FILES_PER_NODE] | load SID URI | stats SID [SECTION] | erase SID PREDICATE_JSON\n"
                  "  shards SID N | replicas SID N | expand SID SHARDS_PER_NODE NODE [NODE ...]\n"
                  "  create NAME SHARDS REPLICAS OP_CONFIG_JSON [TABLE_URI]   (prints storage_id=N)\n");
     return 2;
@@ -90,6 +91,22 @@ int ctl_main(int argc, char** argv) {
         else if (verb == "delete" && a.size() == 2) st = ctl.delete_table(num(1));
         else if (verb == "balance" && a.size() == 2) st = ctl.balance_table(num(1));
         else if (verb == "purge" && a.size() == 2) st = ctl.purge_table(num(1));
+        else if (verb == "dump" && (a.size() == 3 || a.size() == 4)) {
+            uint64_t n = 0;
+            st = ctl.dump_table(num(1), a[2], a.size() == 4 ? num(3) : 1, &n);
+            if (st.ok()) std::printf("records=%llu\n", (unsigned long long)n);
+        }
+        else if (verb == "load" && a.size() == 3) {
+            uint64_t n = 0;
+            st = ctl.load_table(num(1), a[2], &n);
+            if (st.ok()) std::printf("records=%llu\n", (unsigned long long)n);
+        }
+        else if (verb == "stats" && (a.size() == 2 || a.size() == 3)) { st = ctl.table_stats(num(1), a.size() == 3 ? num(2) : 0, &out); has_out = true; }
+        else if (verb == "erase" && a.size() == 3) {
+            uint64_t n = 0;
+            st = ctl.erase_from_table(num(1), a[2], &n);
+            if (st.ok()) std::printf("erased=%llu\n", (unsigned long long)n);
+        }
         else if (verb == "shards" && a.size() == 3) st = ctl.update_table_shard(num(1), num(2));
         else if (verb == "replicas" && a.size() == 3) st = ctl.update_table_replica(num(1), num(2));
         else if (verb == "expand" && a.size() >= 4) {

@@ -132,6 +132,44 @@ public:
         UpdateContextHandler h(&client_, sid, hid);
         return h.purge();
     }
+    // Data operations of a table created with the standard operator set, for the command line: the handlers are found
+    // by their keys ("dump", "load", "for_each", "erase_if").
+    Status dump_table(int32_t sid, const std::string& uri, int file_number, uint64_t* n_records) {
+        PSB_RETURN_IF_ERROR(client_.initialize_storage(sid));
+        int32_t hid = -1;
+        PSB_RETURN_IF_ERROR(client_.handler_by_key(sid, "dump", &hid));
+        DumpArgs args;
+        args.uri = uri;
+        args.file_number = file_number;
+        return DumpHandler(&client_, sid, hid).dump(args, n_records);
+    }
+    Status load_table(int32_t sid, const std::string& uri, uint64_t* n_records) {
+        PSB_RETURN_IF_ERROR(client_.initialize_storage(sid));
+        int32_t hid = -1;
+        PSB_RETURN_IF_ERROR(client_.handler_by_key(sid, "load", &hid));
+        return LoadHandler(&client_, sid, hid).load(uri, n_records);
+    }
+    // count / sum / sum of squares / max |x| over a row section (0 = embedding, 1 / 2 = optimizer slots)
+    Status table_stats(int32_t sid, int section, Json* out) {
+        PSB_RETURN_IF_ERROR(client_.initialize_storage(sid));
+        int32_t hid = -1;
+        PSB_RETURN_IF_ERROR(client_.handler_by_key(sid, "for_each", &hid));
+        ForEachResult r;
+        PSB_RETURN_IF_ERROR(ForEachHandler(&client_, sid, hid).for_each("{\"section\":" + std::to_string(section) + "}", &r));
+        *out = Json::object();
+        (*out)["count"] = (int64_t)r.count;
+        (*out)["sum"] = r.sum;
+        (*out)["sum_sq"] = r.sum_sq;
+        (*out)["max_abs"] = r.max_abs;
+        return Status::Ok();
+    }
+    // `carried_json`: a built-in predicate, e.g. {"type":"slot0_below","threshold":0.2}
+    Status erase_from_table(int32_t sid, const std::string& carried_json, uint64_t* erased) {
+        PSB_RETURN_IF_ERROR(client_.initialize_storage(sid));
+        int32_t hid = -1;
+        PSB_RETURN_IF_ERROR(client_.handler_by_key(sid, "erase_if", &hid));
+        return EraseIfHandler(&client_, sid, hid).erase_if(carried_json, erased);
+    }
     // Scale out: every new node gets `local_shard_num` NEW shards appended (single-replica tables only).
     Status expand_storage_nodes(int32_t sid, const std::vector<int>& new_nodes, int local_shard_num) {
         PSB_RETURN_IF_ERROR(client_.initialize_storage(sid));

@@ -3,8 +3,10 @@ table on two native server processes, pushes, pulls, loses one server (SIGKILL),
 restore mode and shuts everything down through the admin API. No Python in the serving processes."""
 import json
 import os
+import shutil
 import signal
 import subprocess
+import tempfile
 import time
 
 import numpy as np
@@ -168,6 +170,23 @@ def test_controller_from_the_command_line():
         assert st.ok() and np.array_equal(rows, vals)
         rc, out, err = _ctl(addr, "node", str(new_id))
         assert rc == 0 and json.loads(out)["alive"], (out, err)
+        # data verbs: statistics, dump, a second table loaded from the dump, erase by a built-in predicate
+        rc, out, err = _ctl(addr, "stats", str(sid))
+        stats = json.loads(out)
+        assert rc == 0 and stats["count"] == 900 and abs(stats["sum"] - float(vals.sum())) < 1e-3, (out, err)
+        dump_dir = tempfile.mkdtemp(prefix="psb_ctl_dump_")
+        rc, out, err = _ctl(addr, "dump", str(sid), dump_dir, "2")
+        assert rc == 0 and out == "records=900", (out, err)
+        rc, out, err = _ctl(addr, "create", "copy", "3", "1", json.dumps(dict(dim=4, optimizer="sum", init_range=0.0)))
+        sid2 = int(out.split("=")[1])
+        rc, out, err = _ctl(addr, "load", str(sid2), dump_dir)
+        assert rc == 0 and out == "records=900", (out, err)
+        rc, out, err = _ctl(addr, "erase", str(sid2), json.dumps({"type": "key_mod", "mod": 3, "rem": 0}))
+        assert rc == 0 and out == "erased=300", (out, err)
+        assert json.loads(_ctl(addr, "stats", str(sid2))[1])["count"] == 600
+        assert _ctl(addr, "erase", str(sid2), "{not json")[0] == 1 and _ctl(addr, "dump", str(sid2), dump_dir, "0")[0] == 1
+        assert _ctl(addr, "delete", str(sid2))[0] == 0
+        shutil.rmtree(dump_dir, ignore_errors=True)
         assert _ctl(addr, "table", "4242")[0] == 1                      # an unknown table is an error, with a message
         assert _ctl(addr, "bogus")[0] == 2
         assert _ctl(addr, "delete", str(sid))[0] == 0
