@@ -563,6 +563,26 @@ void bind_service(py::module_& m) {
         .def("delete_table", &Controller::delete_table, nogil())
         .def("balance_table", &Controller::balance_table, nogil())
         .def("purge_table", &Controller::purge_table, nogil())
+        .def("dump_table", [](Controller& c, int32_t sid, const std::string& uri, int files) {
+            uint64_t n = 0;
+            Status st = c.dump_table(sid, uri, files, &n);
+            return std::make_tuple(st, n);
+        }, py::arg("sid"), py::arg("uri"), py::arg("file_number") = 1, nogil())
+        .def("load_table", [](Controller& c, int32_t sid, const std::string& uri) {
+            uint64_t n = 0;
+            Status st = c.load_table(sid, uri, &n);
+            return std::make_tuple(st, n);
+        }, nogil())
+        .def("table_stats", [](Controller& c, int32_t sid, int section) {
+            Json out;
+            Status st = c.table_stats(sid, section, &out);
+            return std::make_tuple(st, out.dump());
+        }, py::arg("sid"), py::arg("section") = 0, nogil())
+        .def("erase_from_table", [](Controller& c, int32_t sid, const std::string& carried) {
+            uint64_t n = 0;
+            Status st = c.erase_from_table(sid, carried, &n);
+            return std::make_tuple(st, n);
+        }, nogil())
         .def("update_table_shard", &Controller::update_table_shard, nogil())
         .def("update_table_replica", &Controller::update_table_replica, nogil())
         .def("update_table", &Controller::update_table, nogil())

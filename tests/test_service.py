@@ -780,6 +780,18 @@ def test_controller_placement_resize_and_introspection(tmp_path):
         assert np.array_equal(pull.pull(keys)[1], vals)
         nodes_view = json.loads(ctl.show_nodes()[1])
         assert len(nodes_view) == 5 and all(n["alive"] for n in nodes_view)
+        # the data verbs of the command line, from Python
+        st, stats = ctl.table_stats(sid)
+        assert st.ok() and json.loads(stats)["count"] == 4000
+        st, n = ctl.dump_table(sid, str(tmp_path / "ctl_dump"), 2)
+        assert st.ok() and n == 4000
+        st, sid_copy = ctl.create_table("copy", S.LIB, "SparseTableStorageOperator", json.dumps(op_cfg()), 3, 1, S.standard_ops())
+        assert st.ok(), st
+        st, n = ctl.load_table(sid_copy, str(tmp_path / "ctl_dump"))
+        assert st.ok() and n == 4000
+        assert json.loads(ctl.table_stats(sid_copy)[1])["count"] == 4000
+        st, n = ctl.erase_from_table(sid_copy, json.dumps({"type": "key_mod", "mod": 4, "rem": 1}))
+        assert st.ok() and n == 1000 and ctl.delete_table(sid_copy).ok()
         # a storage without a table object is cleaned up
         st, orphan = client.create_storage(S.LIB, "SparseTableStorageOperator", S.storage_config({cl.ids()[0]: [0]}, op_cfg()))
         st, removed = ctl.clean_unused_storage()
