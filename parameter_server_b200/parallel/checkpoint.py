@@ -158,3 +158,106 @@ def load(table: SparseTable, uri: str, batch: int = 1 << 18, inbox: Optional[Pee
     if table.world > 1:
         dist.barrier(group=table.group)
     return got
+
+
+# ---- dense tables -----------------------------------------------------------------------------------
+# A dense table is cut into one contiguous slice per rank; the owner of a slice holds its fp32 master values and its
+# optimizer slots. A checkpoint is that, rank by rank: <uri>/dense_<rank>.npz = {lo, numel, world, step_count,
+# optimizer, master[len], slot0[len], slot1[len], layout (names, offsets, shapes as JSON)}. A load puts the slices
+# back together and cuts them again for the world that reads them, so a job may resume on another number of GPUs.
+# The reference dumps dense tables through the same operators as sparse ones (slices are records of a table with the
+# dense partitioner, pico-ps/operator/DumpOperator.h:116-202); the RPC path here does the same. This is the
+# collective path's form, where the slices never were records.
+def _dense_local_state(table):
+    import json
+    from .._lib import C
+    n_slots = int(C.opt_num_slots(table.opt.type))
+    if table.is_cuda:
+        lo, length = int(table.engine.shard_lo()), int(table.engine.shard_len())
+        torch.cuda.current_stream().synchronize()
+        master = table.master.detach().cpu().numpy().copy()
+        slots = []
+        for s in range(n_slots):
+            from ..ops.dense import _view
+            slots.append(_view(table.engine.slot_ptr(s), length, torch.float32, table.device, table.engine).cpu().numpy().copy())
+    else:
+        length = table.numel // table.world
+        lo = length * table.rank
+        if table.rank == table.world - 1:
+            length = table.numel - lo
+        master = table.flat_master[lo:lo + length].numpy().copy()
+        slots = [t[lo:lo + length].numpy().copy() for t in (table._m, table._v)[:n_slots]]
+    layout = json.dumps({n: [int(off), [int(d) for d in shape]] for n, (off, shape) in table.offsets.items()})
+    return lo, length, master, slots, layout
+
+
+def dump_dense(table, uri: str) -> int:
+    """Collective. Every rank writes the slice it owns (fp32 master values, optimizer slots, step count) to
+    ``<uri>/dense_<rank>.npz``. Returns the number of elements this rank wrote."""
+    path = uri.split("?", 1)[0]
+    if not path:
+        raise ValueError("dump_dense: the uri names no directory")
+    if _is_remote(path):
+        raise ValueError("dump_dense writes to a local directory")
+    os.makedirs(path, exist_ok=True)
+    lo, length, master, slots, layout = _dense_local_state(table)
+    tmp = os.path.join(path, f".dense_{table.rank}.tmp.npz")
+    np.savez(tmp, lo=np.int64(lo), numel=np.int64(table.numel), world=np.int64(table.world),
+             step_count=np.int64(table.step_count), opt_type=np.int64(table.opt.type), layout=np.array(layout),
+             master=master, **{f"slot{i}": s for i, s in enumerate(slots)})
+    os.replace(tmp, os.path.join(path, f"dense_{table.rank}.npz"))      # never a torn file under the final name
+    if table.world > 1:
+        dist.barrier(group=table.group)
+    return int(length)
+
+
+def load_dense(table, uri: str) -> int:
+    """Collective. Reads the slices that ``dump_dense`` wrote - by any number of ranks - and installs values,
+    optimizer slots and the step count in ``table``; the tensor names and shapes must be the table's. Returns the
+    number of elements of the checkpoint."""
+    import json
+    from .._lib import C
+    path = uri.split("?", 1)[0]
+    names = sorted(n for n in os.listdir(path) if n.startswith("dense_") and n.endswith(".npz"))
+    if not names:
+        raise FileNotFoundError(f"no dense_<rank>.npz under {path}")
+    parts = [np.load(os.path.join(path, n), allow_pickle=False) for n in names]
+    world0 = int(parts[0]["world"])
+    if len(parts) != world0 or sorted(int(p["lo"]) for p in parts) != sorted({int(p["lo"]) for p in parts}):
+        raise RuntimeError(f"{path}: the checkpoint was written by {world0} ranks, {len(parts)} slices are here")
+    mine = {n: [int(off), [int(d) for d in shape]] for n, (off, shape) in table.offsets.items()}
+    if json.loads(str(parts[0]["layout"])) != mine:
+        raise RuntimeError(f"{path}: the checkpoint holds other tensors than this table")
+    if int(parts[0]["opt_type"]) != int(table.opt.type):
+        raise RuntimeError(f"{path}: the checkpoint was written with another optimizer")
+    n_slots = int(C.opt_num_slots(table.opt.type))
+    total = max(int(p["lo"]) + len(p["master"]) for p in parts)
+    full = [np.zeros(max(total, table.numel), dtype=np.float32) for _ in range(1 + n_slots)]
+    covered = 0
+    for p in parts:
+        lo, m = int(p["lo"]), p["master"]
+        full[0][lo:lo + len(m)] = m
+        for i in range(n_slots):
+            full[1 + i][lo:lo + len(m)] = p[f"slot{i}"]
+        covered += len(m)
+    if covered != total:
+        raise RuntimeError(f"{path}: the slices do not cover the table ({covered} of {total} elements)")
+    table.step_count = int(parts[0]["step_count"])
+    if table.is_cuda:
+        from ..ops.dense import _view
+        from ..utils.status import raise_if_error
+        dev = torch.from_numpy(full[0][:table.numel]).to(table.device)
+        stream = torch.cuda.current_stream()
+        raise_if_error(table.engine.load_full(dev.data_ptr(), stream.cuda_stream))
+        lo, length = int(table.engine.shard_lo()), int(table.engine.shard_len())
+        for i in range(n_slots):
+            _view(table.engine.slot_ptr(i), length, torch.float32, table.device, table.engine).copy_(
+                torch.from_numpy(full[1 + i][lo:lo + length]).to(table.device))
+        stream.synchronize()
+    else:
+        table.flat_master.copy_(torch.from_numpy(full[0][:table.numel]))
+        for i, t in enumerate((table._m, table._v)[:n_slots]):
+            t.copy_(torch.from_numpy(full[1 + i][:table.numel]))
+    if table.world > 1:
+        dist.barrier(group=table.group)
+    return int(total)

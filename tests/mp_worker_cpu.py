@@ -222,6 +222,31 @@ def main():
         d.push()
     sigs = gather((float(d.pull("w").sum()), float(d.pull("b").sum())))
     assert all(s == sigs[0] for s in sigs), sigs
+    # checkpoint of the dense table: every rank writes its slice; a table of the same job and a single-process
+    # table (another world size) resume from it and take the next step exactly like the original
+    import tempfile
+    from parameter_server_b200.parallel import checkpoint
+    ck = [tempfile.mkdtemp(prefix="psb_dense_") if rank == 0 else None]
+    dist.broadcast_object_list(ck, src=0)
+    wrote = gather(checkpoint.dump_dense(d, ck[0]))
+    assert sum(wrote) == d.numel, wrote
+    d2 = DenseTable({"w": (64, 8), "b": (64,)}, "adamw", dict(lr=1e-2, weight_decay=0.01), device="cpu")
+    assert checkpoint.load_dense(d2, ck[0]) == d.numel and d2.step_count == d.step_count
+    solo = DenseTable({"w": (64, 8), "b": (64,)}, "adamw", dict(lr=1e-2, weight_decay=0.01), device="cpu", group="none")
+    checkpoint.load_dense(solo, ck[0])
+    for t_ in (d, d2):
+        t_.zero_grads()
+        t_.grads["w"].add_(torch.full((64, 8), 0.25))
+        t_.push()
+    solo.zero_grads()
+    solo.grads["w"].add_(torch.full((64, 8), 0.25 * world))               # what the three ranks sum to
+    solo.push(grad_scale=1.0 / world)
+    assert torch.equal(d.pull("w"), d2.pull("w")) and torch.equal(d.pull("b"), d2.pull("b"))
+    assert torch.allclose(d.pull("w"), solo.pull("w"), rtol=0, atol=1e-7)
+    dist.barrier()
+    if rank == 0:
+        import shutil
+        shutil.rmtree(ck[0], ignore_errors=True)
     assert d.pull("w").mean().item() < 1.0           # the weights moved against the (positive) gradient
     dist.barrier()
     if rank == 0:

@@ -70,3 +70,37 @@ def test_misuse_is_answered_with_an_exception_not_with_silent_damage():
     assert cursor == 1 and not finished
     k, r, cursor, finished = t.table.export_shard(0, 1 << 60, 10, False)
     assert finished and len(k) == 0
+
+
+@pytest.mark.parametrize("opt,kw", [("adamw", dict(lr=1e-2, weight_decay=0.01)), ("sgd", dict(lr=0.1)), ("adagrad", dict(lr=0.1))])
+def test_a_dense_table_resumes_from_its_checkpoint_exactly(tmp_path, opt, kw):
+    """`checkpoint.dump_dense / load_dense`: master values, optimizer slots and the step count come back, so the next
+    step of the resumed table is the next step of the original; a checkpoint of other tensors or of another optimizer
+    is refused."""
+    from parameter_server_b200.parallel import checkpoint
+    shapes = {"w": (33, 7), "b": (33,), "g": (5,)}
+    a = DenseTable(shapes, opt, kw, device="cpu", group="none")
+    gen = torch.Generator().manual_seed(3)
+    a.load({"w": torch.randn(33, 7, generator=gen), "b": torch.randn(33, generator=gen), "g": torch.ones(5)})
+    for _ in range(3):
+        a.zero_grads()
+        a.grads["w"].add_(torch.randn(33, 7, generator=gen))
+        a.grads["b"].add_(0.1)
+        a.push()
+    n = checkpoint.dump_dense(a, str(tmp_path))
+    assert n == a.numel and sorted(p.name for p in tmp_path.iterdir()) == ["dense_0.npz"]
+    b = DenseTable(shapes, opt, kw, device="cpu", group="none")
+    assert checkpoint.load_dense(b, str(tmp_path)) == n and b.step_count == a.step_count == 3
+    g = torch.randn(33, 7, generator=gen)
+    for t in (a, b):
+        t.zero_grads()
+        t.grads["w"].add_(g)
+        t.push()
+    assert all(torch.equal(a.pull(k), b.pull(k)) for k in shapes)
+    with pytest.raises(RuntimeError):
+        checkpoint.load_dense(DenseTable({"w": (33, 7)}, opt, kw, device="cpu", group="none"), str(tmp_path))
+    other = "sgd" if opt != "sgd" else "adagrad"
+    with pytest.raises(RuntimeError):
+        checkpoint.load_dense(DenseTable(shapes, other, dict(lr=0.1), device="cpu", group="none"), str(tmp_path))
+    with pytest.raises(FileNotFoundError):
+        checkpoint.load_dense(b, str(tmp_path / "nothing_here"))
