@@ -536,6 +536,22 @@ class DLRM:
     def check(self) -> None:
         self.sparse.check()
         self.dense.check()
+
+    # ---- checkpoint / resume: the embedding table in the dump layout of the operator API, the MLPs with their
+    # optimizer state as one slice per rank; both load on another number of ranks -------------------------------
+    def save_checkpoint(self, uri: str, file_number: int = 1) -> None:
+        """Collective, between steps. ``<uri>/sparse`` and ``<uri>/dense``."""
+        from ..parallel import checkpoint
+        torch.cuda.synchronize(self.device)
+        checkpoint.dump(self.sparse, uri.rstrip("/") + "/sparse", file_number=file_number)
+        checkpoint.dump_dense(self.dense, uri.rstrip("/") + "/dense")
+
+    def load_checkpoint(self, uri: str) -> None:
+        """Collective, between steps: the tables keep their buffers, so a captured step graph stays valid."""
+        from ..parallel import checkpoint
+        torch.cuda.synchronize(self.device)
+        checkpoint.load(self.sparse, uri.rstrip("/") + "/sparse")
+        checkpoint.load_dense(self.dense, uri.rstrip("/") + "/dense")
         G.check_gemm_errors()
 
     # ------------------------------------------------------------------------------------------

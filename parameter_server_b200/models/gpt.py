@@ -175,6 +175,20 @@ class GPT:
             t.check()
         G.check_gemm_errors()
 
+    def save_checkpoint(self, uri: str) -> None:
+        """Collective, between steps: every dense table (values, optimizer slots, step count) under ``<uri>/table_<i>``."""
+        from ..parallel import checkpoint
+        torch.cuda.synchronize(self.device)
+        for i, t in enumerate(self.tables):
+            checkpoint.dump_dense(t, f"{uri.rstrip('/')}/table_{i}")
+
+    def load_checkpoint(self, uri: str) -> None:
+        """Collective, between steps; the checkpoint may come from a job with another number of ranks."""
+        from ..parallel import checkpoint
+        torch.cuda.synchronize(self.device)
+        for i, t in enumerate(self.tables):
+            checkpoint.load_dense(t, f"{uri.rstrip('/')}/table_{i}")
+
 
 def _bench(args) -> None:
     import torch.distributed as dist
