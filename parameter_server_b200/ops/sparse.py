@@ -353,6 +353,26 @@ class SparseTable:
     def memory_usage(self) -> int:
         return int(self.table.memory_usage())
 
+    def storage_info(self, collective: bool = False):
+        """What ``Client.query_storage_info`` answers on the service path: one record per local shard,
+        ``{"node_id": rank, "shard_id", "item_number", "memory_usage"}`` (the table's bytes spread evenly over its
+        shards, as there); with ``collective`` the records of all ranks."""
+        mine = [s for s in range(self.n_shards) if self.world == 1 or self.shard_owner[s] == self.rank]
+        if self.is_cuda:
+            st, counts = self.table.shard_counts(self.n_shards, _stream())
+            raise_if_error(st)
+            items = {s: int(counts[s]) for s in mine}
+        else:
+            items = {s: int(self.table.shard_size(s)) for s in mine}
+        per = self.memory_usage() // max(1, len(mine))
+        info = [{"node_id": self.rank, "shard_id": s, "item_number": items[s], "memory_usage": per} for s in mine]
+        if collective and self.world > 1:
+            import torch.distributed as dist
+            parts = [None] * self.world
+            dist.all_gather_object(parts, info, group=self.group)
+            info = [r for p in parts for r in p]
+        return info
+
     def get_rows(self, keys: torch.Tensor, emb_only: bool = True):
         """Read rows of LOCAL keys without inserting. Returns (rows, found)."""
         keys = keys.reshape(-1)

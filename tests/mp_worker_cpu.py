@@ -101,6 +101,9 @@ def scans(rank, world):
     assert abs(st["max_abs"] - float(want.abs().max())) < 1e-12
     acc = t.for_each(section=1, collective=True)
     assert acc["count"] == 1200 and acc["sum"] > 0.5 * 1200 * dim
+    info = t.storage_info(collective=True)
+    assert sorted(r["shard_id"] for r in info) == list(range(5)) and sum(r["item_number"] for r in info) == 1200
+    assert all(r["node_id"] == t.shard_owner[r["shard_id"]] for r in info) and len(t.storage_info()) == len([s for s in range(5) if t.shard_owner[s] == rank])
     # a user reducer: the largest key that this rank holds; merged by the caller
     parts = t.for_each(lambda k, r: int(k.max()))
     assert max(max(p) if p else 0 for p in gather(parts)) == 1200
