@@ -34,6 +34,12 @@ class KeyDeduper:
         """Returns ``(unique_keys, unique_owner, inverse, counts)``; ``counts[0]`` is the number of distinct
         keys, ``counts[1 + r]`` how many of them rank ``r`` owns. ``shard_owner`` is an int32 tensor
         ``[n_shards]`` (absent: everything belongs to rank 0)."""
+        if keys.dtype != torch.int64 or not keys.is_cuda:
+            raise TypeError("keys must be a CUDA int64 tensor")           # a host pointer must never reach the kernel
+        if shard_owner is not None and (shard_owner.dtype != torch.int32 or not shard_owner.is_cuda or not shard_owner.is_contiguous()):
+            raise TypeError("shard_owner must be a contiguous CUDA int32 tensor")
+        if world < 1:
+            raise ValueError("world must be at least 1")
         keys = keys.reshape(-1).contiguous()
         n = keys.numel()
         if n > self.max_keys:
