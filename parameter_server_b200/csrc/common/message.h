@@ -6,6 +6,8 @@
 // (keys, rows, gradients) moves through NVLink peer memory from inside the fused kernels; this
 // envelope carries the control plane and the non-collective (RPC) data path.
 #pragma once
+#include <cctype>
+#include <string>
 #include <cstdint>
 
 #include "archive.h"
@@ -51,6 +53,24 @@ inline const char* request_type_name(RequestType t) {
         "OP_COORDINATED_RESTORE_ITERATE", "HEALTH_CHECK", "OP_UDF"};
     int i = (int)t;
     return (i >= 0 && i < 26) ? names[i] : "UNKNOWN";
+}
+
+// The request type as the metric series name it: the reference's labels where it has them (c2s_pull, c2s_async_push,
+// c2s_store, c2s_udf_op, s2s_async_push: pico-ps/service/Service.cpp:703-764,820-862,872-894,937-974), the enum name in
+// lower case without its OP_ prefix for the rest.
+inline std::string request_type_label(RequestType t) {
+    switch (t) {
+        case RequestType::OP_PULL: return "pull";
+        case RequestType::OP_PUSH_ASYNC: return "async_push";
+        case RequestType::OP_PUSH_SYNC: return "sync_push";
+        case RequestType::OP_STORE: return "store";
+        case RequestType::OP_UDF: return "udf_op";
+        default: break;
+    }
+    std::string n = request_type_name(t);
+    if (n.compare(0, 3, "OP_") == 0) n = n.substr(3);
+    for (auto& c : n) c = (char)std::tolower((unsigned char)c);
+    return n;
 }
 
 struct PSMessageMeta {

@@ -512,7 +512,7 @@ private:
         const PSMessageMeta meta = msg.meta;
         Archive out;
         Status st;
-        const std::string label = std::string(s2s ? "s2s_" : "c2s_") + request_type_name(meta.req_type);
+        const std::string label = std::string(s2s ? "s2s_" : "c2s_") + request_type_label(meta.req_type);
         count(label);
         const size_t req_bytes = msg.ar.size();
         const auto t0 = std::chrono::steady_clock::now();

@@ -224,7 +224,7 @@ def test_native_server_exports_prometheus_metrics():
         for _ in range(3):
             assert S.PushHandler(client, sid, h_push).async_push(keys, np.ones((100, 4), np.float32)).ok()
         text = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5).read().decode()
-        assert f'ps_requests_total{{node_id="{node}",request_type="c2s_OP_PUSH_ASYNC",storage_id="{sid}"}} 3' in text
+        assert f'ps_requests_total{{node_id="{node}",request_type="c2s_async_push",storage_id="{sid}"}} 3' in text
         assert "ps_request_duration_ms_bucket" in text
         with pytest.raises(urllib.error.HTTPError) as ei:
             urllib.request.urlopen(f"http://127.0.0.1:{port}/other", timeout=5)

@@ -1175,9 +1175,9 @@ def test_one_way_context_refresh_and_predictor_create(cluster3):
     before = [s.metrics_text().count("CTX_UPDATE") for s in cl.servers]
     cl.client.require_update_ctx_async(sid)            # returns at once
     deadline = time.time() + 5
-    while time.time() < deadline and not all('request_type="c2s_CTX_UPDATE"' in s.metrics_text() for s in cl.servers):
+    while time.time() < deadline and not all('request_type="c2s_ctx_update"' in s.metrics_text() for s in cl.servers):
         time.sleep(0.02)
-    assert all('request_type="c2s_CTX_UPDATE"' in s.metrics_text() for s in cl.servers), before
+    assert all('request_type="c2s_ctx_update"' in s.metrics_text() for s in cl.servers), before
     # the channel is still good for ordinary calls afterwards (the late answers were dropped by the reader)
     st, hid = cl.client.register_handler("pull_ro", S.LIB, "SparseTablePullOperator", json.dumps({"read_only": True}), sid)
     assert st.ok() and S.PullHandler(cl.client, sid, hid).pull(np.arange(10, dtype=np.int64))[0].ok()
@@ -1199,8 +1199,8 @@ def test_prometheus_metrics_endpoint(cluster3):
     finally:
         httpd.shutdown()
     node = cl.servers[0].node_id()
-    assert f'ps_requests_total{{node_id="{node}",request_type="c2s_OP_PULL",storage_id="{sid}"}} 1' in text
-    assert f'ps_requests_total{{node_id="{node}",request_type="c2s_OP_PUSH_ASYNC",storage_id="{sid}"}} 1' in text
+    assert f'ps_requests_total{{node_id="{node}",request_type="c2s_pull",storage_id="{sid}"}} 1' in text
+    assert f'ps_requests_total{{node_id="{node}",request_type="c2s_async_push",storage_id="{sid}"}} 1' in text
     assert 'ps_request_duration_ms_bucket' in text and 'le="+Inf"' in text and "ps_response_size_bytes" in text
     assert f'ps_storage_items{{node_id="{node}",storage_id="{sid}"}}' in text
     assert "ps_wait_request_count" in handler_metrics_text(pull, "pull")
