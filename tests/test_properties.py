@@ -378,3 +378,58 @@ def test_no_operator_config_or_carried_item_takes_a_server_down(one_server, op, 
     finally:
         assert client.delete_storage(sid).ok()
     assert not server.exited()
+
+
+@pytest.fixture(scope="module")
+def dumps_to_damage(one_server, tmp_path_factory):
+    """One small table dumped in every format / compression: the raw material of the next test."""
+    import json
+    S, server, client = one_server
+    st_, sid = client.create_storage(S.LIB, "SparseTableStorageOperator",
+                                     S.storage_config({server.node_id(): [0, 1]}, dict(dim=4, optimizer="adagrad", lr=0.1, init_range=0.01)))
+    assert st_.ok()
+    _, hq = client.register_handler("push", S.LIB, "SparseTablePushOperator", "{}", sid)
+    keys = np.arange(1, 400, dtype=np.int64) * 1_000_003
+    assert S.PushHandler(client, sid, hq).async_push(keys, np.ones((len(keys), 4), F), 5000).ok()
+    out = {}
+    for fmt in ("binary", "archiveline"):
+        for algo in ("", "zstd", "lz4"):
+            _, hd = client.register_handler(f"dump_{fmt}_{algo}", S.LIB, "DumpOperator", json.dumps({"compress_algorithm": algo}), sid)
+            d = tmp_path_factory.mktemp(f"dump_{fmt}_{algo or 'plain'}")
+            st_, n = S.DumpHandler(client, sid, hd).dump(str(d) + "?format=" + fmt, 1)
+            assert st_.ok() and n == len(keys)
+            out[(fmt, algo)] = (d, {p.name: p.read_bytes() for p in d.iterdir()})
+    return out
+
+
+@settings(max_examples=120, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@given(fmt=st.sampled_from(["binary", "archiveline"]), algo=st.sampled_from(["", "zstd", "lz4"]),
+       flips=st.lists(st.tuples(st.integers(0, 1 << 20), st.integers(0, 255)), max_size=6), cut=st.integers(0, 1 << 20),
+       junk=st.binary(max_size=64))
+def test_damaged_dump_files_are_refused_or_loaded_never_followed_off_a_cliff(one_server, dumps_to_damage, fmt, algo, flips, cut, junk):
+    """Bytes of a dump are flipped, its tail is cut or replaced by junk: the load answers with a status (a flipped
+    value may well load) and the server goes on serving."""
+    import json
+    S, server, client = one_server
+    d, files = dumps_to_damage[(fmt, algo)]
+    for name, data in files.items():
+        b = bytearray(data)
+        for pos, val in flips:
+            if b:
+                b[pos % len(b)] = val
+        b = b[:cut % (len(b) + 1)] + junk
+        (d / name).write_bytes(bytes(b))
+    st_, sid = client.create_storage(S.LIB, "SparseTableStorageOperator",
+                                     S.storage_config({server.node_id(): [0, 1, 2]}, dict(dim=4, optimizer="adagrad", lr=0.1, init_range=0.01)))
+    assert st_.ok()
+    try:
+        _, hl = client.register_handler("load", S.LIB, "LoadOperator", json.dumps({"compress_algorithm": algo, "block_size": 64}), sid)
+        st_, n = S.LoadHandler(client, sid, hl).load(str(d) + "?format=" + fmt, 2, 20000)
+        assert st_.ok() or st_.code() != 0
+        info = client.query_storage_info(sid)
+        assert info[0].ok() and sum(i.item_number for i in info[1]) <= 10 * 400
+    finally:
+        assert client.delete_storage(sid).ok()
+        for name, data in files.items():
+            (d / name).write_bytes(data)
+    assert not server.exited()
