@@ -152,7 +152,11 @@ void bind_service(py::module_& m) {
         .def("get_context", [](MasterClient& c, const std::string& k) { std::string v; Status st = c.get_context(k, &v); return std::make_tuple(st, v); }, nogil())
         .def("delete_context", &MasterClient::delete_context, nogil())
         .def("list_contexts", [](MasterClient& c) { std::vector<std::string> k; Status st = c.list_contexts(&k); return std::make_tuple(st, k); }, nogil())
-        .def("register_node", [](MasterClient& c, const std::string& s, const std::string& a) { int32_t id = -1; Status st = c.register_node(s, a, &id); return std::make_tuple(st, id); }, nogil())
+        .def("register_node", [](MasterClient& c, const std::string& s, const std::string& a, int32_t want_id) {
+            int32_t id = -1;
+            Status st = c.register_node(s, a, &id, want_id);
+            return std::make_tuple(st, id);
+        }, py::arg("service"), py::arg("address"), py::arg("want_id") = -1, nogil())
         .def("get_nodes", [](MasterClient& c, const std::string& s) { std::map<int32_t, std::string> n; Status st = c.get_nodes(s, &n); return std::make_tuple(st, n); }, nogil())
         .def("barrier", &MasterClient::barrier, nogil())
         .def("tree_node_set", &MasterClient::tree_node_set, nogil())

@@ -143,6 +143,14 @@ private:
                 if (want_id >= next_node_id_) next_node_id_ = want_id + 1;
                 if (want_id < 0) save_state_locked();   // ids are never handed out twice, also across a restart
                 registry_[service][id] = addr;
+                // the entry now belongs to THIS connection: a node that lost its session and registers again over a
+                // new one must not be wiped when the close of the old connection is noticed afterwards
+                auto& owner = owner_[{service, id}];
+                if (owner != 0 && owner != resp.conn_id()) {
+                    auto old = sessions_.find(owner);
+                    if (old != sessions_.end()) old->second.erase({service, id});
+                }
+                owner = resp.conn_id();
                 sessions_[resp.conn_id()].insert({service, id});
                 Archive out;
                 out << id;
@@ -154,6 +162,7 @@ private:
                 int32_t id = -1;
                 ar >> service >> id;
                 registry_[service].erase(id);
+                owner_.erase({service, id});
                 resp.send(ok_reply());
                 break;
             }
@@ -293,7 +302,12 @@ private:
         std::lock_guard<std::mutex> g(mu_);
         auto it = sessions_.find(conn);
         if (it != sessions_.end()) {
-            for (auto& sn : it->second) registry_[sn.first].erase(sn.second);
+            for (auto& sn : it->second) {
+                auto o = owner_.find(sn);
+                if (o == owner_.end() || o->second != conn) continue;   // registered again over another connection
+                registry_[sn.first].erase(sn.second);
+                owner_.erase(o);
+            }
             sessions_.erase(it);
         }
         // a client that died while holding a lock must not wedge everyone else
@@ -312,6 +326,7 @@ private:
     std::map<std::string, std::string> ctx_;
     std::map<std::string, std::map<int32_t, std::string>> registry_;
     std::map<uint64_t, std::set<std::pair<std::string, int32_t>>> sessions_;
+    std::map<std::pair<std::string, int32_t>, uint64_t> owner_;   // which connection a registry entry belongs to
     std::map<std::string, std::vector<RpcServer::Responder>> barriers_;
     std::map<std::string, std::string> tree_;
     int32_t next_node_id_ = 0;

@@ -68,6 +68,29 @@ def uneven(ids):
     return out
 
 
+def test_a_node_that_registers_again_is_not_wiped_by_the_close_of_its_old_session():
+    """A server whose connection to the master broke registers again over a new one. The master may notice the close
+    of the old connection only afterwards: the entry belongs to the new session by then and stays."""
+    m = S.Master()
+    try:
+        old, new, reader = (S.MasterClient(m.address()) for _ in range(3))
+        st, nid = old.register_node("svc", "127.0.0.1:1")
+        assert st.ok() and reader.get_nodes("svc")[1] == {nid: "127.0.0.1:1"}
+        st, same = new.register_node("svc", "127.0.0.1:2", nid)          # the same node, over another connection
+        assert st.ok() and same == nid
+        old.close()                                                        # noticed after the new registration
+        for _ in range(20):
+            time.sleep(0.02)
+            assert reader.get_nodes("svc")[1] == {nid: "127.0.0.1:2"}
+        new.close()                                                        # the session that owns the entry: now it goes
+        deadline = time.time() + 5
+        while time.time() < deadline and reader.get_nodes("svc")[1]:
+            time.sleep(0.02)
+        assert reader.get_nodes("svc")[1] == {}
+    finally:
+        m.stop()
+
+
 def test_master_basics():
     m = S.Master()
     a, b = S.MasterClient(m.address()), S.MasterClient(m.address())
