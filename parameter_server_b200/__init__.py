@@ -10,5 +10,6 @@ from ._lib import C  # noqa: F401
 from .utils.status import Status, StatusCode, StatusError  # noqa: F401
 from .ops.optim import make_opt_config, OPTIMIZERS  # noqa: F401
 from .ops.sparse import SparseTable, sparse_lookup  # noqa: F401
+from .ops.dense import DenseTable  # noqa: F401
 
 __version__ = "0.1.0"
