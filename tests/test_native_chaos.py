@@ -337,3 +337,76 @@ def test_the_master_is_killed_and_restarted_from_its_state_file(tmp_path):
         for p in procs:
             if p.poll() is None:
                 p.kill()
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.skipif(not os.path.exists(NODE), reason="psb_node is not built")
+def test_a_replica_replaced_under_a_stream_of_pushes_is_exact_when_the_restore_pauses_writes():
+    """Real processes: one of two replicas is SIGKILLed while a client pushes without a break, a replacement started
+    with --restore --restore-pauses-writes copies the table from the survivor, the survivor is killed as well, and the
+    replacement alone must hold every push exactly once."""
+    import threading
+    master = _spawn("master")
+    addr = _line(master)
+    procs = [master]
+    try:
+        servers = [_spawn("pserver", "--master", addr) for _ in range(2)]
+        procs += servers
+        nodes = [int(_line(p).split("node_id=")[1].split()[0]) for p in servers]
+        client = S.Client(addr)
+        st, sid = client.create_storage(S.LIB, "SparseTableStorageOperator",
+                                        S.storage_config({n: [0, 1, 2] for n in nodes}, dict(dim=DIM, optimizer="sum", init_range=0.0)))
+        assert st.ok(), st
+        _, h_push = client.register_handler("push", S.LIB, "SparseTablePushOperator", "{}", sid)
+        _, h_pull = client.register_handler("pull_ro", S.LIB, "SparseTablePullOperator", json.dumps({"read_only": True}), sid)
+        keys = np.arange(30_000, dtype=np.int64)
+        ones = np.ones((len(keys), DIM), np.float32)
+        stop, applied, bad = threading.Event(), [0], []
+
+        def trainer():
+            c = S.Client(addr)
+            assert c.initialize_storage(sid).ok()
+            push = S.PushHandler(c, sid, h_push)
+            while not stop.is_set():
+                st_ = push.async_push(keys, ones, 60000)
+                if not st_.ok():
+                    bad.append(str(st_))
+                    return
+                applied[0] += 1
+
+        t = threading.Thread(target=trainer)
+        t.start()
+        try:
+            time.sleep(0.3)
+            servers[1].send_signal(signal.SIGKILL)
+            servers[1].wait(timeout=10)
+            before = applied[0]
+            fresh = _spawn("pserver", "--master", addr, "--restore", "--restore-wait", "30", "--restore-pauses-writes")
+            procs.append(fresh)
+            assert "node_id=" in _line(fresh)
+            assert _line(fresh, 90.0) == "restore: OK (1 tables) from replica"
+            deadline = time.time() + 30
+            while time.time() < deadline and applied[0] < before + 3:
+                time.sleep(0.05)
+            assert applied[0] >= before + 3, (applied, bad)                    # the pushes went on after the pause
+        finally:
+            stop.set()
+            t.join(90)
+        assert not bad and not t.is_alive(), bad
+        servers[0].send_signal(signal.SIGKILL)                                 # only the replacement is left
+        servers[0].wait(timeout=10)
+        pull = S.PullHandler(client, sid, h_pull)
+        deadline = time.time() + 40
+        rows = None
+        while time.time() < deadline:
+            st, rows = pull.pull(keys, 3000, True)
+            if st.ok():
+                break
+            time.sleep(0.05)
+        assert st.ok() and np.all(rows == float(applied[0])), (str(st), float(rows.min()), float(rows.max()), applied[0])
+        master.send_signal(signal.SIGTERM)
+        master.wait(timeout=15)
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
