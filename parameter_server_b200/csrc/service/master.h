@@ -88,7 +88,10 @@ private:
             case MasterOp::UNLOCK: {
                 std::string name;
                 ar >> name;
-                release_lock_locked(name);
+                // only the holder releases: a client whose connection broke lost the lock with it (on_disconnect), and
+                // its late release over a new connection must not take the lock away from whoever holds it now
+                auto& l = locks_[name];
+                if (l.held && l.owner_conn == resp.conn_id()) release_lock_locked(name);
                 resp.send(ok_reply());
                 break;
             }
@@ -96,7 +99,9 @@ private:
                 std::string key, value;
                 int32_t only_if_absent = 0;
                 ar >> key >> value >> only_if_absent;
-                if (only_if_absent && ctx_.count(key)) {
+                if (fenced_off(key, resp.conn_id())) {
+                    resp.send(err_reply(Status::Error("context " + key + " is written under the global lock, which another session holds")));
+                } else if (only_if_absent && ctx_.count(key)) {
                     resp.send(err_reply(Status::Error("context " + key + " already exists")));
                 } else {
                     ctx_[key] = value;
@@ -121,6 +126,10 @@ private:
             case MasterOp::CTX_DEL: {
                 std::string key;
                 ar >> key;
+                if (fenced_off(key, resp.conn_id())) {
+                    resp.send(err_reply(Status::Error("context " + key + " is written under the global lock, which another session holds")));
+                    break;
+                }
                 ctx_.erase(key);
                 save_state_locked();
                 resp.send(ok_reply());
@@ -286,6 +295,14 @@ private:
         return 0;
     }
 
+    // Table contexts ("storage/<sid>") change only under the global lock. A writer that does not hold it while somebody
+    // else does is a client that lost the lock with its connection and has not noticed: it is turned away instead of
+    // writing over the holder's work. (Writes while nobody holds the lock pass: tools and tests edit contexts that way.)
+    bool fenced_off(const std::string& key, uint64_t conn) {
+        if (key.compare(0, 8, "storage/") != 0) return false;
+        auto it = locks_.find(PSERVER_LOCK_NAME);
+        return it != locks_.end() && it->second.held && it->second.owner_conn != conn;
+    }
     void release_lock_locked(const std::string& name) {
         auto& l = locks_[name];
         while (!l.waiters.empty()) {

@@ -91,6 +91,37 @@ def test_a_node_that_registers_again_is_not_wiped_by_the_close_of_its_old_sessio
         m.stop()
 
 
+def test_a_client_that_lost_the_lock_with_its_connection_cannot_undo_the_holders_work():
+    """The global lock belongs to a connection. A client whose connection broke in the middle of its critical section
+    comes back over a new one without the lock: its late release leaves the new holder's lock alone, and its write
+    to a table context is refused while somebody else holds the lock."""
+    m = S.Master()
+    try:
+        a, b, c = (S.MasterClient(m.address()) for _ in range(3))
+        assert a.set_context("storage/7", "v0").ok()                      # nobody holds the lock: tools may edit
+        assert a.acquire_lock("PSERVER_LOCK").ok()
+        a.close()                                                          # the fault: the lock goes with the connection
+        assert b.acquire_lock("PSERVER_LOCK").ok()                        # somebody else is in the critical section now
+        assert b.set_context("storage/7", "by the holder").ok()
+        st = a.set_context("storage/7", "by the one who lost it")         # over a new connection, unaware
+        assert not st.ok() and "lock" in str(st)
+        assert not a.delete_context("storage/7").ok()
+        assert a.set_context("model/x", "not a table context").ok()        # other keys are not under the lock
+        assert a.release_lock("PSERVER_LOCK").ok()                        # a no-op: it is not a's lock
+        got = []
+        t = threading.Thread(target=lambda: got.append(c.acquire_lock("PSERVER_LOCK").ok()))
+        t.start()
+        time.sleep(0.3)
+        assert t.is_alive() and not got                                    # b still holds it: c waits
+        assert b.get_context("storage/7")[1] == "by the holder"
+        assert b.release_lock("PSERVER_LOCK").ok()
+        t.join(10)
+        assert got == [True]
+        assert c.release_lock("PSERVER_LOCK").ok()
+    finally:
+        m.stop()
+
+
 def test_master_basics():
     m = S.Master()
     a, b = S.MasterClient(m.address()), S.MasterClient(m.address())
