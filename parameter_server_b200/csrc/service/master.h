@@ -9,6 +9,7 @@
 // barrier, tree_node_add / get, get_model / set_model. The in-process TCP master of the reference's
 // tests (pico-ps/test/TestUtils.h:16-92) corresponds to constructing Master directly.
 #pragma once
+#include <algorithm>
 #include <chrono>
 #include <cstdio>
 #include <fstream>
@@ -326,6 +327,13 @@ private:
                 owner_.erase(o);
             }
             sessions_.erase(it);
+        }
+        // a participant that went away no longer stands at its barriers: the next arrival must not complete one with it
+        for (auto it = barriers_.begin(); it != barriers_.end();) {
+            auto& v = it->second;
+            v.erase(std::remove_if(v.begin(), v.end(), [&](const RpcServer::Responder& r) { return r.conn_id() == conn; }), v.end());
+            if (v.empty()) it = barriers_.erase(it);
+            else ++it;
         }
         // a client that died while holding a lock must not wedge everyone else
         for (auto& kv : locks_)

@@ -122,6 +122,28 @@ def test_a_client_that_lost_the_lock_with_its_connection_cannot_undo_the_holders
         m.stop()
 
 
+def test_a_participant_that_went_away_no_longer_stands_at_its_barrier():
+    m = S.Master()
+    try:
+        a, b, c = (S.MasterClient(m.address()) for _ in range(3))
+        res = {}
+        ta = threading.Thread(target=lambda: res.__setitem__("a", a.barrier("sync", 2)))
+        ta.start()
+        time.sleep(0.2)
+        a.close()                                                          # a waits at the barrier and is lost
+        ta.join(10)
+        assert not ta.is_alive() and not res["a"].ok()
+        tb = threading.Thread(target=lambda: res.__setitem__("b", b.barrier("sync", 2)))
+        tb.start()
+        time.sleep(0.4)
+        assert tb.is_alive()                                               # b alone does not complete it with a's ghost
+        assert c.barrier("sync", 2).ok()
+        tb.join(10)
+        assert res["b"].ok()
+    finally:
+        m.stop()
+
+
 def test_master_basics():
     m = S.Master()
     a, b = S.MasterClient(m.address()), S.MasterClient(m.address())
