@@ -695,6 +695,16 @@ def test_an_operator_can_abort_a_reshard_that_its_client_left_unfinished(cluster
     st, rows = pull.pull(keys, 20000, True)
     assert st.ok() and np.all(rows == 2.0)
     assert ctl.purge_table(4242).code() == StatusCode.INVALID_ID
+    # the same way out for a table that a restore with the write pause left closed (status LOADING) when it died
+    ctx = json.loads(m.get_context(f"storage/{sid}")[1])
+    ctx["status"], ctx["version"] = 2, ctx["version"] + 1
+    assert m.set_context(f"storage/{sid}", json.dumps(ctx)).ok()
+    assert cl.client.pull_context(sid).ok() and cl.client.notify_ctx_update(sid).ok()
+    st = push.async_push(keys, ones, 1500)
+    assert st.code() in (StatusCode.OUT_OF_MEMORY, StatusCode.TIMEOUT), st
+    assert ctl.purge_table(sid).ok()
+    assert td.from_json_str(m.get_context(f"storage/{sid}")[1]) and td.status() == 0
+    assert push.async_push(keys, ones, 20000).ok()
 
 
 def test_restore_from_dump_when_no_replica(tmp_path):
