@@ -173,6 +173,7 @@ public:
         auto e = entry();
         if (!e) return Status::InvalidID("storage is not initialised on this client");
         const uint32_t slice = storage_op_of(*e)->dim();
+        PSB_RETURN_IF_ERROR(dense_check_id(id, numel, slice));
         std::shared_ptr<SparseTablePullOperator> p;
         PSB_RETURN_IF_ERROR(op(&p));
         const auto* dp = dynamic_cast<const DenseTablePullOperator*>(p.get());
@@ -304,6 +305,7 @@ public:
         auto e = entry();
         if (!e) return Status::InvalidID("storage is not initialised on this client");
         const uint32_t slice = storage_op_of(*e)->dim();
+        PSB_RETURN_IF_ERROR(dense_check_id(id, numel, slice));
         std::shared_ptr<SparseTablePushOperator> p;
         PSB_RETURN_IF_ERROR(op(&p));
         const auto* dp = dynamic_cast<const DenseTablePushOperator*>(p.get());

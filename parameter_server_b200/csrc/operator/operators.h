@@ -596,6 +596,15 @@ struct DenseSlice {
     uint32_t len;    // elements of the value in this slice (<= the table's slice width)
 };
 // The default cut: consecutive slices of `slice_len` elements.
+// A dense key is (id << 24) | slice: 2^24 slices per value and ids of 39 bits and a sign. What does not fit would land
+// on another value's keys (or on a reserved key), so it is refused before anything is sent.
+inline Status dense_check_id(int64_t id, size_t numel, uint32_t slice_len) {
+    constexpr int64_t kIdLimit = 1LL << 39;
+    if (id <= -kIdLimit || id >= kIdLimit) return Status::InvalidConfig("dense id " + std::to_string(id) + " does not fit 40 bits");
+    if (slice_len == 0 || (numel + slice_len - 1) / slice_len > (size_t)(1 << 24))
+        return Status::InvalidConfig("a dense value of " + std::to_string(numel) + " elements needs more than 2^24 slices of " + std::to_string(slice_len));
+    return Status::Ok();
+}
 inline void dense_default_partition(int64_t id, size_t numel, uint32_t slice_len, std::vector<DenseSlice>* out) {
     const size_t ns = (numel + slice_len - 1) / slice_len;
     out->resize(ns);

@@ -707,6 +707,28 @@ def test_an_operator_can_abort_a_reshard_that_its_client_left_unfinished(cluster
     assert push.async_push(keys, ones, 20000).ok()
 
 
+def test_dense_ids_and_sizes_that_would_land_on_another_values_keys_are_refused(cluster3):
+    """A dense key is (id << 24) | slice. An id of more than 40 bits or a value of more than 2^24 slices would alias
+    another value's slices (it used to, silently): both are INVALID_CONFIG now; ids below zero are fine."""
+    cl = cluster3
+    st, dsid = cl.client.create_storage(S.LIB, "DenseTableStorageOperator", S.storage_config(uneven(cl.ids()), op_cfg(dim=5)))
+    assert st.ok()
+    _, hp = cl.client.register_handler("pull", S.LIB, "DenseTablePullOperator", "{}", dsid)
+    _, hq = cl.client.register_handler("push", S.LIB, "DenseTablePushOperator", "{}", dsid)
+    pull, push = S.PullHandler(cl.client, dsid, hp), S.PushHandler(cl.client, dsid, hq)
+    v = np.arange(1, 14, dtype=np.float32)
+    for tid in (0, 7, -5, (1 << 39) - 1, -(1 << 39) + 1):
+        assert push.push_dense(tid, v + tid % 3).ok()
+    for tid in (0, 7, -5, (1 << 39) - 1, -(1 << 39) + 1):
+        st, back = pull.pull_dense(tid, v.size)
+        assert st.ok() and np.array_equal(back, v + tid % 3), tid           # five values, none on another's keys
+    for tid in (1 << 39, 1 << 40, -(1 << 39), -(1 << 62)):
+        assert push.push_dense(tid, v).code() == StatusCode.INVALID_CONFIG
+        assert pull.pull_dense(tid, v.size)[0].code() == StatusCode.INVALID_CONFIG
+    assert pull.pull_dense(3, 5 * (1 << 24) + 1)[0].code() == StatusCode.INVALID_CONFIG
+    assert pull.pull_dense(0, v.size)[0].ok()
+
+
 def test_restore_from_dump_when_no_replica(tmp_path):
     cl = Cluster(2)
     try:
