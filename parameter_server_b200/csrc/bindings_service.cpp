@@ -396,6 +396,7 @@ void bind_service(py::module_& m) {
             {
                 py::gil_scoped_release g;
                 st = h.pull(keys.data(), (size_t)keys.size(), out.mutable_data(), timeout_ms, auto_retry);
+                if (!st.ok()) std::fill_n(out.mutable_data(), (size_t)out.size(), 0.f);   // never hand out memory that nobody wrote
             }
             return py::make_tuple(st, out);
         }, py::arg("keys"), py::arg("timeout_ms") = -1, py::arg("auto_retry") = true)
@@ -405,6 +406,7 @@ void bind_service(py::module_& m) {
             {
                 py::gil_scoped_release g;
                 st = h.pull_dense(id, numel, out.mutable_data(), timeout_ms);
+                if (!st.ok()) std::fill_n(out.mutable_data(), numel, 0.f);   // never hand out memory that nobody wrote
             }
             return py::make_tuple(st, out);
         }, py::arg("id"), py::arg("numel"), py::arg("timeout_ms") = -1);
